@@ -1,0 +1,735 @@
+// Causal flash attention, forward and backward, on tcgen05 tensor cores with
+// the score / probability tiles in TMEM and shared memory only: the [T, T]
+// score matrix never reaches HBM.
+//
+// Replaces the reference training path that materialises scores with baddbmm,
+// runs the scaled upper-triangular masked softmax kernel and a second bmm
+// (metaseq/modules/multihead_attention.py:356-426,
+//  metaseq/modules/megatron/fused_kernels/scaled_upper_triang_masked_softmax.h:113-330),
+// and lifts that kernel's 2048-token limit.  The reference scales q and k by
+// d^-1/4 each before the product; here the product is scaled once by d^-1/2,
+// which is the same function in exact arithmetic.
+//
+// Layout: q, k, v are [B, T, H, HD] views with arbitrary row / batch strides
+// (they are column slices of the fused qkv projection output); the output is
+// [B, T, H*HD].  One TMA box is 128 rows x 64 columns with 128-byte swizzle; a
+// tile of HD columns is HD/64 such boxes.  The same physical tile serves as a
+// K-major operand (rows = M or N, 64 columns = K) and as an MN-major operand
+// (rows = K, 64 columns = M or N), which is what lets the backward pass reuse
+// Q, dO, P and dS for the transposed products without any transposed copy.
+#include "sm100_common.cuh"
+
+namespace msq {
+
+constexpr int ATT_THREADS = 192;
+constexpr int TILE = 128;
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float LN2 = 0.6931471805599453f;
+
+// Byte offset of the 16-byte unit `unit` (0..7) of row `r` inside a
+// [rows x 128 B] 128-byte-swizzled chunk.
+__device__ __forceinline__ uint32_t sw128_offset(int r, int unit) {
+  return static_cast<uint32_t>(r) * 128u + (static_cast<uint32_t>(unit ^ (r & 7)) << 4);
+}
+
+struct AttnFwdParams {
+  void* out;  // [B, T, H*HD]
+  long long o_row_stride, o_batch_stride;
+  float* lse;  // [B, H, T]
+  int T, H;
+  float scale_log2;  // softmax scale * log2(e)
+  int causal;
+  int bf16;
+  int* status;
+};
+
+template <int HD>
+struct FwdCfg {
+  static constexpr int CHUNKS = HD / 64;
+  static constexpr uint32_t TILE_BYTES = TILE * HD * 2;  // one Q/K/V tile
+  static constexpr uint32_t CHUNK_BYTES = TILE * 128;    // 16 KB
+  static constexpr int SLOTS = 3;                        // K/V ring
+  static constexpr uint32_t P_BYTES = TILE * TILE * 2;
+  static constexpr uint32_t SMEM = TILE_BYTES * (1 + SLOTS) + P_BYTES + 1024 + 128;
+  static constexpr uint32_t TMEM_COLS = 256;
+  static constexpr uint32_t O_COL = 128;
+};
+
+template <int HD, bool BF16>
+__global__ void __launch_bounds__(ATT_THREADS, (HD == 64) ? 2 : 1)
+flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const AttnFwdParams p) {
+  using Cfg = FwdCfg<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sKV = sQ + Cfg::TILE_BYTES;
+  uint8_t* sP = sKV + Cfg::SLOTS * Cfg::TILE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + Cfg::P_BYTES);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;
+  uint64_t* kv_empty = kv_full + Cfg::SLOTS;
+  uint64_t* s_full = kv_empty + Cfg::SLOTS;
+  uint64_t* p_full = s_full + 1;
+  uint64_t* o_full = p_full + 1;
+  uint64_t* o_empty = o_full + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_empty + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_qblocks = gridDim.x;
+  const int qb = n_qblocks - 1 - blockIdx.x;  // heaviest (longest causal prefix) blocks first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int n_kv = p.causal ? (qb + 1) : (p.T + TILE - 1) / TILE;
+
+  if (p.status && *reinterpret_cast<volatile int*>(p.status) != 0) return;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < Cfg::SLOTS; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 128);
+    mbar_init(o_full, 1);
+    mbar_init(o_empty, 128);
+    *abort_flag = 0;
+    mbar_fence_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base, tO = tmem_base + Cfg::O_COL;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, Cfg::TILE_BYTES);
+#pragma unroll
+      for (int c = 0; c < Cfg::CHUNKS; ++c)
+        tma_load_3d(sQ + c * Cfg::CHUNK_BYTES, &tmQ, q_full, h * HD + c * 64, qb * TILE, b);
+      int slot = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int j = 0; j < n_kv && ok; ++j) {
+#pragma unroll 1
+        for (int which = 0; which < 2; ++which) {
+          ok = mbar_wait(&kv_empty[slot], phase ^ 1, abort_flag, p.status, ST_TIMEOUT_SMEM_EMPTY);
+          if (!ok) break;
+          mbar_expect_tx(&kv_full[slot], Cfg::TILE_BYTES);
+          uint8_t* dst = sKV + slot * Cfg::TILE_BYTES;
+          const CUtensorMap* tm = which ? &tmV : &tmK;
+#pragma unroll
+          for (int c = 0; c < Cfg::CHUNKS; ++c)
+            tma_load_3d(dst + c * Cfg::CHUNK_BYTES, tm, &kv_full[slot], h * HD + c * 64, j * TILE, b);
+          if (++slot == Cfg::SLOTS) { slot = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        const unsigned long long t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 2000000ull) { }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc_f16(BF16 ? 1 : 0, 0, 0, TILE, TILE);
+      const uint32_t idesc_o = make_idesc_f16(BF16 ? 1 : 0, 0, 1, TILE, HD);
+      int slot = 0;
+      uint32_t phase = 0;
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
+      const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
+      auto issue_s = [&]() -> bool {
+        if (!mbar_wait(&kv_full[slot], phase, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL)) return false;
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(sKV + slot * Cfg::TILE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * Cfg::CHUNK_BYTES + (kk & 3) * 32;
+          tc_mma_f16(tS, make_smem_desc_sw128(q_addr + off, 16, 1024), make_smem_desc_sw128(k_addr + off, 16, 1024),
+                     idesc_s, kk > 0 ? 1u : 0u);
+        }
+        tc_commit(&kv_empty[slot]);
+        tc_commit(s_full);
+        if (++slot == Cfg::SLOTS) { slot = 0; phase ^= 1; }
+        return true;
+      };
+      if (ok) ok = issue_s();
+      for (int j = 0; j < n_kv && ok; ++j) {
+        ok = mbar_wait(p_full, j & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
+        if (!ok) break;
+        if (j > 0) {
+          ok = mbar_wait(o_empty, (j - 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
+          if (!ok) break;
+        }
+        ok = mbar_wait(&kv_full[slot], phase, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t v_addr = smem_u32(sKV + slot * Cfg::TILE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < TILE / 16; ++kk) {
+          const uint32_t a_off = (kk >> 2) * Cfg::CHUNK_BYTES + (kk & 3) * 32;
+          tc_mma_f16(tO, make_smem_desc_sw128(p_addr + a_off, 16, 1024),
+                     make_smem_desc_sw128(v_addr + kk * 2048, Cfg::CHUNK_BYTES, 1024), idesc_o, kk > 0 ? 1u : 0u);
+        }
+        tc_commit(&kv_empty[slot]);
+        tc_commit(o_full);
+        if (++slot == Cfg::SLOTS) { slot = 0; phase ^= 1; }
+        if (j + 1 < n_kv) ok = issue_s();
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;       // row inside the q tile == TMEM lane
+    const int q_idx = qb * TILE + row;         // position in the sequence
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    float m_run = -INFINITY, l_run = 0.f;
+    float acc[HD];
+#pragma unroll
+    for (int i = 0; i < HD; ++i) acc[i] = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_kv && ok; ++j) {
+      ok = mbar_wait_warp(s_full, j & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
+      if (!ok) break;
+      tc_fence_after();
+      // Columns of this block that row q_idx may attend to: [0, limit).
+      int limit = p.T - j * TILE;
+      if (p.causal) limit = min(limit, q_idx - j * TILE + 1);
+      limit = max(0, min(limit, TILE));
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tS + lane_off + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (c * 32 + i < limit) mx = fmaxf(mx, __uint_as_float(r[i]));
+      }
+      const float m_new = fmaxf(m_run, mx * p.scale_log2);
+      // A row with nothing to attend to yet (only rows past T) keeps m = -inf; guard the subtraction.
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      const float alpha = exp2f(m_run - m_use);
+      float psum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tS + lane_off + c * 32, r);
+        tmem_ld_wait();
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float a = (c * 32 + 2 * i < limit) ? exp2f(__uint_as_float(r[2 * i]) * p.scale_log2 - m_use) : 0.f;
+          float bb = (c * 32 + 2 * i + 1 < limit) ? exp2f(__uint_as_float(r[2 * i + 1]) * p.scale_log2 - m_use) : 0.f;
+          psum += a + bb;
+          packed[i] = pack2<BF16>(a, bb);
+        }
+        uint8_t* chunk = sP + (c >> 1) * Cfg::CHUNK_BYTES;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const uint4 v4 = make_uint4(packed[4 * u], packed[4 * u + 1], packed[4 * u + 2], packed[4 * u + 3]);
+          *reinterpret_cast<uint4*>(chunk + sw128_offset(row, (c & 1) * 4 + u)) = v4;
+        }
+      }
+      l_run = l_run * alpha + psum;
+      m_run = m_new;
+      tc_fence_before();
+      fence_proxy_async_smem();
+      mbar_arrive(p_full);
+#pragma unroll
+      for (int i = 0; i < HD; ++i) acc[i] *= alpha;
+      ok = mbar_wait_warp(o_full, j & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tO + lane_off + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc[c * 32 + i] += __uint_as_float(r[i]);
+      }
+      tc_fence_before();
+      mbar_arrive(o_empty);
+    }
+    if (ok && q_idx < p.T) {
+      const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
+      uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + static_cast<long long>(b) * p.o_batch_stride +
+                    static_cast<long long>(q_idx) * p.o_row_stride + h * HD;
+#pragma unroll
+      for (int v = 0; v < HD / 8; ++v) {
+        uint4 ov;
+        ov.x = pack2<BF16>(acc[v * 8 + 0] * inv_l, acc[v * 8 + 1] * inv_l);
+        ov.y = pack2<BF16>(acc[v * 8 + 2] * inv_l, acc[v * 8 + 3] * inv_l);
+        ov.z = pack2<BF16>(acc[v * 8 + 4] * inv_l, acc[v * 8 + 5] * inv_l);
+        ov.w = pack2<BF16>(acc[v * 8 + 6] * inv_l, acc[v * 8 + 7] * inv_l);
+        *reinterpret_cast<uint4*>(o + v * 8) = ov;
+      }
+      if (p.lse) p.lse[(static_cast<long long>(b) * p.H + h) * p.T + q_idx] = (m_run + log2f(l_run)) * LN2;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------ backward
+struct AttnBwdParams {
+  const float* lse;    // [B, H, T]
+  const float* delta;  // [B, H, T] rowsum(dO * O)
+  float* dq_accum;     // [B, T, H*HD] fp32, zero-initialised; receives sum over kv blocks
+  void* dk;            // [B, T, H, HD] view
+  void* dv;
+  long long dk_row_stride, dk_batch_stride, dv_row_stride, dv_batch_stride;
+  int T, H;
+  float scale;  // softmax scale
+  int causal;
+  int bf16;
+  int* status;
+};
+
+template <int HD>
+struct BwdCfg {
+  static constexpr int CHUNKS = HD / 64;
+  static constexpr uint32_t TILE_BYTES = TILE * HD * 2;
+  static constexpr uint32_t CHUNK_BYTES = TILE * 128;
+  static constexpr int QSTAGES = (HD == 64) ? 2 : 1;
+  static constexpr uint32_t P_BYTES = TILE * TILE * 2;
+  static constexpr uint32_t SMEM = TILE_BYTES * (2 + 2 * QSTAGES) + 2 * P_BYTES + 1024 + 256;
+  static constexpr uint32_t TMEM_COLS = 512;
+  static constexpr uint32_t S_COL = 0, DP_COL = 128, DV_COL = 256, DK_COL = 256 + HD;
+  static constexpr uint32_t DQ_COL = (HD == 64) ? 384 : 0;  // HD = 128 reuses the S columns
+  static constexpr bool DQ_ALIASES_S = (HD != 64);
+};
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+
+template <int HD, bool BF16>
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                 const AttnBwdParams p) {
+  using Cfg = BwdCfg<HD>;
+  constexpr int QS = Cfg::QSTAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + Cfg::TILE_BYTES;
+  uint8_t* sQ = sV + Cfg::TILE_BYTES;
+  uint8_t* sDO = sQ + QS * Cfg::TILE_BYTES;
+  uint8_t* sP = sDO + QS * Cfg::TILE_BYTES;
+  uint8_t* sDS = sP + Cfg::P_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + Cfg::P_BYTES);
+  uint64_t* kv_full = bars;
+  uint64_t* qdo_full = bars + 1;
+  uint64_t* qdo_empty = qdo_full + QS;
+  uint64_t* sdp_full = qdo_empty + QS;
+  uint64_t* pds_full = sdp_full + 1;
+  uint64_t* dq_full = pds_full + 1;
+  uint64_t* dq_empty = dq_full + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_empty + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nb = blockIdx.x;  // kv block; low indices have the longest causal q range and launch first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int n_q = (p.T + TILE - 1) / TILE;
+  const int m_start = p.causal ? nb : 0;
+  const int n_it = n_q - m_start;
+
+  if (p.status && *reinterpret_cast<volatile int*>(p.status) != 0) return;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < QS; ++s) {
+      mbar_init(&qdo_full[s], 1);
+      mbar_init(&qdo_empty[s], 1);
+    }
+    mbar_init(sdp_full, 1);
+    mbar_init(pds_full, 128);
+    mbar_init(dq_full, 1);
+    mbar_init(dq_empty, 128);
+    *abort_flag = 0;
+    mbar_fence_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(kv_full, 2 * Cfg::TILE_BYTES);
+#pragma unroll
+      for (int c = 0; c < Cfg::CHUNKS; ++c) {
+        tma_load_3d(sK + c * Cfg::CHUNK_BYTES, &tmK, kv_full, h * HD + c * 64, nb * TILE, b);
+        tma_load_3d(sV + c * Cfg::CHUNK_BYTES, &tmV, kv_full, h * HD + c * 64, nb * TILE, b);
+      }
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int m = m_start + it;
+        ok = mbar_wait(&qdo_empty[stage], phase ^ 1, abort_flag, p.status, ST_TIMEOUT_SMEM_EMPTY);
+        if (!ok) break;
+        mbar_expect_tx(&qdo_full[stage], 2 * Cfg::TILE_BYTES);
+#pragma unroll
+        for (int c = 0; c < Cfg::CHUNKS; ++c) {
+          tma_load_3d(sQ + stage * Cfg::TILE_BYTES + c * Cfg::CHUNK_BYTES, &tmQ, &qdo_full[stage], h * HD + c * 64,
+                      m * TILE, b);
+          tma_load_3d(sDO + stage * Cfg::TILE_BYTES + c * Cfg::CHUNK_BYTES, &tmDO, &qdo_full[stage],
+                      h * HD + c * 64, m * TILE, b);
+        }
+        if (++stage == QS) { stage = 0; phase ^= 1; }
+      }
+      if (!ok) {
+        const unsigned long long t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 2000000ull) { }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const int dt = BF16 ? 1 : 0;
+      const uint32_t idesc_s = make_idesc_f16(dt, 0, 0, TILE, TILE);   // Q K^T and dO V^T
+      const uint32_t idesc_t = make_idesc_f16(dt, 1, 1, TILE, HD);     // P^T dO and dS^T Q
+      const uint32_t idesc_q = make_idesc_f16(dt, 0, 1, TILE, HD);     // dS K
+      const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), p_addr = smem_u32(sP), ds_addr = smem_u32(sDS);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
+      for (int it = 0; it < n_it && ok; ++it) {
+        ok = mbar_wait(&qdo_full[stage], phase, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
+        if (!ok) break;
+        if (Cfg::DQ_ALIASES_S && it > 0) {
+          ok = mbar_wait(dq_empty, (it - 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
+          if (!ok) break;
+        }
+        tc_fence_after();
+        const uint32_t q_addr = smem_u32(sQ + stage * Cfg::TILE_BYTES);
+        const uint32_t do_addr = smem_u32(sDO + stage * Cfg::TILE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * Cfg::CHUNK_BYTES + (kk & 3) * 32;
+          tc_mma_f16(tmem_base + Cfg::S_COL, make_smem_desc_sw128(q_addr + off, 16, 1024),
+                     make_smem_desc_sw128(k_addr + off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * Cfg::CHUNK_BYTES + (kk & 3) * 32;
+          tc_mma_f16(tmem_base + Cfg::DP_COL, make_smem_desc_sw128(do_addr + off, 16, 1024),
+                     make_smem_desc_sw128(v_addr + off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+        }
+        tc_commit(sdp_full);
+        ok = mbar_wait(pds_full, it & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
+        if (!ok) break;
+        if (!Cfg::DQ_ALIASES_S && it > 0) {
+          ok = mbar_wait(dq_empty, (it - 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
+          if (!ok) break;
+        }
+        tc_fence_after();
+        const uint32_t acc = it > 0 ? 1u : 0u;
+#pragma unroll
+        for (int kk = 0; kk < TILE / 16; ++kk) {  // dV += P^T dO   (K = q rows)
+          tc_mma_f16(tmem_base + Cfg::DV_COL, make_smem_desc_sw128(p_addr + kk * 2048, Cfg::CHUNK_BYTES, 1024),
+                     make_smem_desc_sw128(do_addr + kk * 2048, Cfg::CHUNK_BYTES, 1024), idesc_t,
+                     (kk > 0) ? 1u : acc);
+        }
+#pragma unroll
+        for (int kk = 0; kk < TILE / 16; ++kk) {  // dK += dS^T Q
+          tc_mma_f16(tmem_base + Cfg::DK_COL, make_smem_desc_sw128(ds_addr + kk * 2048, Cfg::CHUNK_BYTES, 1024),
+                     make_smem_desc_sw128(q_addr + kk * 2048, Cfg::CHUNK_BYTES, 1024), idesc_t,
+                     (kk > 0) ? 1u : acc);
+        }
+#pragma unroll
+        for (int kk = 0; kk < TILE / 16; ++kk) {  // dQ = dS K      (K = kv rows)
+          const uint32_t a_off = (kk >> 2) * Cfg::CHUNK_BYTES + (kk & 3) * 32;
+          tc_mma_f16(tmem_base + Cfg::DQ_COL, make_smem_desc_sw128(ds_addr + a_off, 16, 1024),
+                     make_smem_desc_sw128(k_addr + kk * 2048, Cfg::CHUNK_BYTES, 1024), idesc_q, kk > 0 ? 1u : 0u);
+        }
+        tc_commit(&qdo_empty[stage]);
+        tc_commit(dq_full);
+        if (++stage == QS) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    const float scale_log2 = p.scale * LOG2E;
+    const long long bh = static_cast<long long>(b) * p.H + h;
+    bool ok = true;
+    for (int it = 0; it < n_it && ok; ++it) {
+      const int m = m_start + it;
+      const int q_idx = m * TILE + row;
+      const bool q_ok = q_idx < p.T;
+      const float lse2 = q_ok ? p.lse[bh * p.T + q_idx] * LOG2E : 0.f;
+      const float delta = q_ok ? p.delta[bh * p.T + q_idx] : 0.f;
+      int limit = p.T - nb * TILE;
+      if (p.causal) limit = min(limit, q_idx - nb * TILE + 1);
+      limit = q_ok ? max(0, min(limit, TILE)) : 0;
+      ok = mbar_wait_warp(sdp_full, it & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t s[32], dp[32];
+        tmem_ld_32x32(tmem_base + Cfg::S_COL + lane_off + c * 32, s);
+        tmem_ld_32x32(tmem_base + Cfg::DP_COL + lane_off + c * 32, dp);
+        tmem_ld_wait();
+        uint32_t pp[16], dd[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float p0 = 0.f, p1 = 0.f, d0 = 0.f, d1 = 0.f;
+          if (c * 32 + 2 * i < limit) {
+            p0 = exp2f(__uint_as_float(s[2 * i]) * scale_log2 - lse2);
+            d0 = p0 * (__uint_as_float(dp[2 * i]) - delta) * p.scale;
+          }
+          if (c * 32 + 2 * i + 1 < limit) {
+            p1 = exp2f(__uint_as_float(s[2 * i + 1]) * scale_log2 - lse2);
+            d1 = p1 * (__uint_as_float(dp[2 * i + 1]) - delta) * p.scale;
+          }
+          pp[i] = pack2<BF16>(p0, p1);
+          dd[i] = pack2<BF16>(d0, d1);
+        }
+        const uint32_t chunk_off = (c >> 1) * Cfg::CHUNK_BYTES;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const uint32_t off = chunk_off + sw128_offset(row, (c & 1) * 4 + u);
+          *reinterpret_cast<uint4*>(sP + off) = make_uint4(pp[4 * u], pp[4 * u + 1], pp[4 * u + 2], pp[4 * u + 3]);
+          *reinterpret_cast<uint4*>(sDS + off) = make_uint4(dd[4 * u], dd[4 * u + 1], dd[4 * u + 2], dd[4 * u + 3]);
+        }
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      mbar_arrive(pds_full);
+      ok = mbar_wait_warp(dq_full, it & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
+      if (!ok) break;
+      tc_fence_after();
+      float* dq_row = p.dq_accum + (static_cast<long long>(b) * p.T + (q_ok ? q_idx : 0)) * (p.H * HD) + h * HD;
+#pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + Cfg::DQ_COL + lane_off + c * 32, r);
+        tmem_ld_wait();
+        if (q_ok) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            red_add_v4(dq_row + c * 32 + i * 4, __uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
+                       __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(dq_empty);
+    }
+    // dK / dV of this kv block are complete once the last dq_full phase has been observed.
+    const int kv_idx = nb * TILE + row;
+    if (ok && n_it > 0) {
+      // The TMEM loads are warp-wide (.sync.aligned): every lane runs them; only the
+      // global stores are predicated on the row being inside the sequence.
+      const bool kv_ok = kv_idx < p.T;
+      const long long kv_row = kv_ok ? kv_idx : 0;
+      uint16_t* dk = reinterpret_cast<uint16_t*>(p.dk) + static_cast<long long>(b) * p.dk_batch_stride +
+                     kv_row * p.dk_row_stride + h * HD;
+      uint16_t* dv = reinterpret_cast<uint16_t*>(p.dv) + static_cast<long long>(b) * p.dv_batch_stride +
+                     kv_row * p.dv_row_stride + h * HD;
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        uint16_t* dst = which ? dv : dk;
+        const uint32_t col = which ? Cfg::DV_COL : Cfg::DK_COL;
+#pragma unroll 1
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_base + col + lane_off + c * 32, r);
+          tmem_ld_wait();
+          if (kv_ok) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 ov;
+              ov.x = pack2<BF16>(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+              ov.y = pack2<BF16>(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+              ov.z = pack2<BF16>(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+              ov.w = pack2<BF16>(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+              *reinterpret_cast<uint4*>(dst + c * 32 + v * 8) = ov;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// delta[b, h, t] = sum_d dO[b, t, h, d] * O[b, t, h, d]; one warp per (b, t, h).
+template <bool BF16>
+__global__ void attn_delta_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o, long long row_stride,
+                                  long long batch_stride, float* __restrict__ delta, int B, int T, int H, int HD) {
+  const long long gw = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long total = static_cast<long long>(B) * T * H;
+  if (gw >= total) return;
+  const int hh = static_cast<int>(gw % H);
+  const long long bt = gw / H;
+  const int t = static_cast<int>(bt % T);
+  const int bb = static_cast<int>(bt / T);
+  const long long off = static_cast<long long>(bb) * batch_stride + static_cast<long long>(t) * row_stride + hh * HD;
+  const uint32_t* po = reinterpret_cast<const uint32_t*>(o + off);
+  const uint32_t* pd = reinterpret_cast<const uint32_t*>(d_o + off);
+  float s = 0.f;
+  for (int i = lane; i < HD / 2; i += 32) {
+    const float2 a = unpack2<BF16>(po[i]);
+    const float2 g = unpack2<BF16>(pd[i]);
+    s += a.x * g.x + a.y * g.y;
+  }
+  s = warp_sum(s);
+  if (lane == 0) delta[(static_cast<long long>(bb) * H + hh) * T + t] = s;
+}
+
+// ---------------------------------------------------------------------- host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn attn_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// [B, T, cols] view with the given strides (elements); box = 1 x 128 rows x 64 columns.
+static int make_tmap_btc(CUtensorMap* out, const void* base, int B, int T, long long cols, long long row_stride,
+                         long long batch_stride, int bf16) {
+  EncodeTiledFn enc = attn_encode_fn();
+  if (!enc) return -1;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || ((row_stride * 2) & 15) || ((batch_stride * 2) & 15)) return -2;
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(T), static_cast<cuuint64_t>(B)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(row_stride) * 2, static_cast<cuuint64_t>(batch_stride) * 2};
+  cuuint32_t box[3] = {64u, static_cast<cuuint32_t>(TILE), 1u};
+  cuuint32_t estr[3] = {1u, 1u, 1u};
+  CUresult r = enc(out, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -3;
+}
+
+template <int HD, bool BF16>
+static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnFwdParams& p,
+                      int B, cudaStream_t stream) {
+  auto kern = flash_fwd_kernel<HD, BF16>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdCfg<HD>::SMEM) != cudaSuccess)
+      return -10;
+    configured = true;
+  }
+  dim3 grid((p.T + TILE - 1) / TILE, p.H, B);
+  kern<<<grid, ATT_THREADS, FwdCfg<HD>::SMEM, stream>>>(tq, tk, tv, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+template <int HD, bool BF16>
+static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
+                      const AttnBwdParams& p, int B, cudaStream_t stream) {
+  auto kern = flash_bwd_kernel<HD, BF16>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg<HD>::SMEM) != cudaSuccess)
+      return -10;
+    configured = true;
+  }
+  dim3 grid((p.T + TILE - 1) / TILE, p.H, B);
+  kern<<<grid, ATT_THREADS, BwdCfg<HD>::SMEM, stream>>>(tq, tk, tv, tdo, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+}  // namespace msq
+
+// q, k, v: 16-bit [B, T, H, HD] views; *_rs / *_bs are row (token) and batch strides in
+// elements.  out: [B, T, H*HD] with its own strides.  lse: fp32 [B, H, T].
+extern "C" int msq_flash_fwd(const void* q, const void* k, const void* v, long long q_rs, long long q_bs,
+                             long long k_rs, long long k_bs, long long v_rs, long long v_bs, void* out,
+                             long long o_rs, long long o_bs, float* lse, int B, int T, int H, int HD, float scale,
+                             int causal, int bf16, int* status, cudaStream_t stream) {
+  using namespace msq;
+  if (B <= 0 || T <= 0) return 0;
+  if (HD != 64 && HD != 128) return -4;
+  if ((reinterpret_cast<uintptr_t>(out) & 15) || (o_rs & 7) || (o_bs & 7)) return -2;
+  CUtensorMap tq, tk, tv;
+  int rc;
+  if ((rc = make_tmap_btc(&tq, q, B, T, static_cast<long long>(H) * HD, q_rs, q_bs, bf16))) return rc;
+  if ((rc = make_tmap_btc(&tk, k, B, T, static_cast<long long>(H) * HD, k_rs, k_bs, bf16))) return rc;
+  if ((rc = make_tmap_btc(&tv, v, B, T, static_cast<long long>(H) * HD, v_rs, v_bs, bf16))) return rc;
+  AttnFwdParams p;
+  p.out = out; p.o_row_stride = o_rs; p.o_batch_stride = o_bs; p.lse = lse;
+  p.T = T; p.H = H; p.scale_log2 = scale * LOG2E; p.causal = causal; p.bf16 = bf16; p.status = status;
+  if (HD == 64) return bf16 ? launch_fwd<64, true>(tq, tk, tv, p, B, stream) : launch_fwd<64, false>(tq, tk, tv, p, B, stream);
+  return bf16 ? launch_fwd<128, true>(tq, tk, tv, p, B, stream) : launch_fwd<128, false>(tq, tk, tv, p, B, stream);
+}
+
+// delta: fp32 [B, H, T] scratch (written here); dq_accum: fp32 [B, T, H*HD], zeroed by the caller.
+extern "C" int msq_flash_bwd(const void* q, const void* k, const void* v, const void* out, const void* d_out,
+                             long long q_rs, long long q_bs, long long k_rs, long long k_bs, long long v_rs,
+                             long long v_bs, long long o_rs, long long o_bs, long long do_rs, long long do_bs,
+                             const float* lse, float* delta, float* dq_accum, void* dk, void* dv, long long dk_rs,
+                             long long dk_bs, long long dv_rs, long long dv_bs, int B, int T, int H, int HD,
+                             float scale, int causal, int bf16, int* status, cudaStream_t stream) {
+  using namespace msq;
+  if (B <= 0 || T <= 0) return 0;
+  if (HD != 64 && HD != 128) return -4;
+  if (o_rs != do_rs || o_bs != do_bs) return -5;
+  if ((dk_rs & 7) || (dk_bs & 7) || (dv_rs & 7) || (dv_bs & 7)) return -2;
+  CUtensorMap tq, tk, tv, tdo;
+  int rc;
+  if ((rc = make_tmap_btc(&tq, q, B, T, static_cast<long long>(H) * HD, q_rs, q_bs, bf16))) return rc;
+  if ((rc = make_tmap_btc(&tk, k, B, T, static_cast<long long>(H) * HD, k_rs, k_bs, bf16))) return rc;
+  if ((rc = make_tmap_btc(&tv, v, B, T, static_cast<long long>(H) * HD, v_rs, v_bs, bf16))) return rc;
+  if ((rc = make_tmap_btc(&tdo, d_out, B, T, static_cast<long long>(H) * HD, do_rs, do_bs, bf16))) return rc;
+  {
+    const long long warps = static_cast<long long>(B) * T * H;
+    const int threads = 256;
+    const long long blocks = (warps * 32 + threads - 1) / threads;
+    if (bf16)
+      attn_delta_kernel<true><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(
+          static_cast<const uint16_t*>(out), static_cast<const uint16_t*>(d_out), o_rs, o_bs, delta, B, T, H, HD);
+    else
+      attn_delta_kernel<false><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(
+          static_cast<const uint16_t*>(out), static_cast<const uint16_t*>(d_out), o_rs, o_bs, delta, B, T, H, HD);
+  }
+  AttnBwdParams p;
+  p.lse = lse; p.delta = delta; p.dq_accum = dq_accum; p.dk = dk; p.dv = dv;
+  p.dk_row_stride = dk_rs; p.dk_batch_stride = dk_bs; p.dv_row_stride = dv_rs; p.dv_batch_stride = dv_bs;
+  p.T = T; p.H = H; p.scale = scale; p.causal = causal; p.bf16 = bf16; p.status = status;
+  if (HD == 64)
+    return bf16 ? launch_bwd<64, true>(tq, tk, tv, tdo, p, B, stream) : launch_bwd<64, false>(tq, tk, tv, tdo, p, B, stream);
+  return bf16 ? launch_bwd<128, true>(tq, tk, tv, tdo, p, B, stream) : launch_bwd<128, false>(tq, tk, tv, tdo, p, B, stream);
+}

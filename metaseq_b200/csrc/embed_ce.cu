@@ -1,0 +1,324 @@
+// Token + learned-position embedding (forward gather, backward scatter-add),
+// softmax cross-entropy over a [rows, V] logits matrix with the gradient
+// written in place, and a column-sum reduction used for bias gradients.
+//
+// Reference behaviour:
+//   * embedding: token row * embed_scale + position row, positions counted from
+//     padding_idx + 1 over non-pad tokens (metaseq/models/transformer_decoder.py:263-346,
+//     metaseq/utils.py:83-93, metaseq/modules/learned_positional_embedding.py:23-54)
+//   * cross entropy: fp32 log-softmax, summed NLL, ignore pad targets
+//     (metaseq/criterions/cross_entropy.py:40-136,
+//      metaseq/modules/megatron/mpu/cross_entropy.py:19-109 for the in-place
+//      "overwrite logits with softmax" trick the backward relies on)
+#include "sm100_common.cuh"
+
+namespace msq {
+
+// ------------------------------------------------------------ embedding fwd
+// out[r, :] = tok_w[tokens[r] - vocab_start, :] * scale + pos_w[positions[r], :]
+// Rows whose token is outside [vocab_start, vocab_end) contribute only the
+// position term on partition 0 and nothing elsewhere (vocab-parallel masking).
+template <bool BF16>
+__global__ void embed_fwd_kernel(const long long* __restrict__ tokens, const long long* __restrict__ positions,
+                                 const uint16_t* __restrict__ tok_w, const uint16_t* __restrict__ pos_w,
+                                 uint16_t* __restrict__ out, int rows, int D, float scale, long long vocab_start,
+                                 long long vocab_end, int add_positions) {
+  const int nvec = D >> 3;
+  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    const long long tok = tokens[r];
+    const bool in_range = tok >= vocab_start && tok < vocab_end;
+    const uint16_t* tw = tok_w + (tok - vocab_start) * D;
+    const uint16_t* pw = (pos_w && add_positions) ? pos_w + positions[r] * D : nullptr;
+    uint16_t* o = out + static_cast<long long>(r) * D;
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+      float f[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = 0.f;
+      if (in_range) {
+        const uint4 a = *reinterpret_cast<const uint4*>(tw + v * 8);
+        const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 t = unpack2<BF16>(w[j]);
+          f[2 * j] = t.x * scale;
+          f[2 * j + 1] = t.y * scale;
+        }
+      }
+      if (pw) {
+        const uint4 a = *reinterpret_cast<const uint4*>(pw + v * 8);
+        const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 t = unpack2<BF16>(w[j]);
+          f[2 * j] += t.x;
+          f[2 * j + 1] += t.y;
+        }
+      }
+      uint4 ov;
+      ov.x = pack2<BF16>(f[0], f[1]);
+      ov.y = pack2<BF16>(f[2], f[3]);
+      ov.z = pack2<BF16>(f[4], f[5]);
+      ov.w = pack2<BF16>(f[6], f[7]);
+      *reinterpret_cast<uint4*>(o + v * 8) = ov;
+    }
+  }
+}
+
+// ------------------------------------------------------------ embedding bwd
+// Scatter-add of dy rows into fp32 gradient tables (atomics); the caller folds
+// the fp32 tables into the 16-bit flat gradient afterwards.
+template <bool BF16>
+__global__ void embed_bwd_kernel(const long long* __restrict__ tokens, const long long* __restrict__ positions,
+                                 const uint16_t* __restrict__ dy, float* __restrict__ dtok, float* __restrict__ dpos,
+                                 int rows, int D, float scale, long long vocab_start, long long vocab_end,
+                                 long long pad_idx) {
+  const int nh = D >> 1;
+  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    const long long tok = tokens[r];
+    const bool in_range = tok >= vocab_start && tok < vocab_end && tok != pad_idx;
+    const long long pos = positions ? positions[r] : -1;
+    const uint32_t* d = reinterpret_cast<const uint32_t*>(dy + static_cast<long long>(r) * D);
+    float* tw = dtok + (tok - vocab_start) * D;
+    float* pw = (dpos && pos >= 0 && pos != pad_idx) ? dpos + pos * D : nullptr;
+    for (int h = threadIdx.x; h < nh; h += blockDim.x) {
+      const float2 t = unpack2<BF16>(d[h]);
+      if (in_range && dtok) {
+        atomicAdd(tw + 2 * h, t.x * scale);
+        atomicAdd(tw + 2 * h + 1, t.y * scale);
+      }
+      if (pw) {
+        atomicAdd(pw + 2 * h, t.x);
+        atomicAdd(pw + 2 * h + 1, t.y);
+      }
+    }
+  }
+}
+
+// dst16[i] = (accumulate ? dst16[i] : 0) + src32[i]
+template <bool BF16>
+__global__ void fold_fp32_kernel(const float* __restrict__ src, uint16_t* __restrict__ dst, long long n,
+                                 int accumulate) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const long long n2 = n >> 1;
+  uint32_t* d2 = reinterpret_cast<uint32_t*>(dst);
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n2; i += stride) {
+    float a = src[2 * i], b = src[2 * i + 1];
+    if (accumulate) {
+      const float2 o = unpack2<BF16>(d2[i]);
+      a += o.x;
+      b += o.y;
+    }
+    d2[i] = pack2<BF16>(a, b);
+  }
+}
+
+// ------------------------------------------------------------ cross entropy
+// One CTA per row.  The row (V 16-bit logits) is staged in shared memory, so
+// HBM sees one read and, when the gradient is requested, one write.
+//   loss[r]  = logsumexp(logits[r, :]) - logits[r, target[r]]      (0 for ignored rows)
+//   lse[r]   = logsumexp
+//   grad     : logits[r, :] <- (softmax - onehot) * grad_scale      (0 for ignored rows)
+// vocab_valid <= V lets the caller exclude padded columns at the end of a row.
+template <bool BF16>
+__global__ void __launch_bounds__(512)
+cross_entropy_kernel(uint16_t* __restrict__ logits, long long ld, const long long* __restrict__ target,
+                     float* __restrict__ loss, float* __restrict__ lse_out, int rows, int V, long long ignore_index,
+                     float grad_scale, int write_grad) {
+  extern __shared__ uint4 row_smem[];
+  __shared__ float red[32];
+  uint16_t* srow = reinterpret_cast<uint16_t*>(row_smem);
+  const int nvec = V >> 3;
+  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    uint16_t* grow = logits + static_cast<long long>(r) * ld;
+    const long long tgt = target[r];
+    const bool ignored = tgt == ignore_index;
+    float mx = -INFINITY;
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+      const uint4 a = *reinterpret_cast<const uint4*>(grow + v * 8);
+      row_smem[v] = a;
+      const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 t = unpack2<BF16>(w[j]);
+        mx = fmaxf(mx, fmaxf(t.x, t.y));
+      }
+    }
+    mx = block_max(mx, red);
+    float se = 0.f;
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+      const uint4 a = row_smem[v];
+      const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 t = unpack2<BF16>(w[j]);
+        se += __expf(t.x - mx) + __expf(t.y - mx);
+      }
+    }
+    se = block_sum(se, red);
+    const float lse = mx + __logf(se);
+    if (threadIdx.x == 0) {
+      float tl = 0.f;
+      if (!ignored) {
+        const uint16_t raw = srow[tgt];
+        tl = BF16 ? __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(&raw))
+                  : __half2float(*reinterpret_cast<const __half*>(&raw));
+      }
+      if (loss) loss[r] = ignored ? 0.f : (lse - tl);
+      if (lse_out) lse_out[r] = lse;
+    }
+    if (write_grad) {
+      const float gs = ignored ? 0.f : grad_scale;
+      for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+        const uint4 a = row_smem[v];
+        const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+        float f[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 t = unpack2<BF16>(w[j]);
+          f[2 * j] = __expf(t.x - lse) * gs;
+          f[2 * j + 1] = __expf(t.y - lse) * gs;
+        }
+        const long long c0 = static_cast<long long>(v) * 8;
+        if (!ignored && tgt >= c0 && tgt < c0 + 8) f[tgt - c0] -= gs;
+        uint4 o;
+        o.x = pack2<BF16>(f[0], f[1]);
+        o.y = pack2<BF16>(f[2], f[3]);
+        o.z = pack2<BF16>(f[4], f[5]);
+        o.w = pack2<BF16>(f[6], f[7]);
+        *reinterpret_cast<uint4*>(grow + v * 8) = o;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// ------------------------------------------------------------------ colsum
+// acc[n] += sum over a slice of rows of x[m, n]; fp32 atomics, one per column
+// per CTA.  Block = 32 x 8 threads, each thread owns 8 adjacent columns.
+template <bool BF16>
+__global__ void __launch_bounds__(256)
+colsum_kernel(const uint16_t* __restrict__ x, long long ld, int rows, int N, float* __restrict__ acc,
+              int rows_per_cta) {
+  __shared__ float sm[8][256 + 8];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int col = blockIdx.x * 256 + tx * 8;
+  const int r0 = blockIdx.y * rows_per_cta;
+  const int r1 = min(rows, r0 + rows_per_cta);
+  float s[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) s[j] = 0.f;
+  if (col < N) {
+    for (int r = r0 + ty; r < r1; r += 8) {
+      const uint4 a = *reinterpret_cast<const uint4*>(x + static_cast<long long>(r) * ld + col);
+      const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 t = unpack2<BF16>(w[j]);
+        s[2 * j] += t.x;
+        s[2 * j + 1] += t.y;
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) sm[ty][tx * 8 + j] = s[j];
+  __syncthreads();
+  const int c = threadIdx.x;
+  if (blockIdx.x * 256 + c < N) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += sm[k][c];
+    atomicAdd(acc + blockIdx.x * 256 + c, t);
+  }
+}
+
+}  // namespace msq
+
+extern "C" int msq_embed_fwd(const long long* tokens, const long long* positions, const void* tok_w,
+                             const void* pos_w, void* out, int rows, int D, float scale, long long vocab_start,
+                             long long vocab_end, int add_positions, int bf16, cudaStream_t stream) {
+  using namespace msq;
+  if (rows <= 0) return 0;
+  if (D & 7) return -2;
+  const int threads = (D >> 3) < 256 ? (((D >> 3) + 31) / 32 * 32) : 256;
+  const int grid = rows < 148 * 16 ? rows : 148 * 16;
+  if (bf16)
+    embed_fwd_kernel<true><<<grid, threads, 0, stream>>>(tokens, positions, static_cast<const uint16_t*>(tok_w),
+                                                         static_cast<const uint16_t*>(pos_w),
+                                                         static_cast<uint16_t*>(out), rows, D, scale, vocab_start,
+                                                         vocab_end, add_positions);
+  else
+    embed_fwd_kernel<false><<<grid, threads, 0, stream>>>(tokens, positions, static_cast<const uint16_t*>(tok_w),
+                                                          static_cast<const uint16_t*>(pos_w),
+                                                          static_cast<uint16_t*>(out), rows, D, scale, vocab_start,
+                                                          vocab_end, add_positions);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+extern "C" int msq_embed_bwd(const long long* tokens, const long long* positions, const void* dy, float* dtok,
+                             float* dpos, int rows, int D, float scale, long long vocab_start, long long vocab_end,
+                             long long pad_idx, int bf16, cudaStream_t stream) {
+  using namespace msq;
+  if (rows <= 0) return 0;
+  if (D & 1) return -2;
+  const int grid = rows < 148 * 16 ? rows : 148 * 16;
+  if (bf16)
+    embed_bwd_kernel<true><<<grid, 256, 0, stream>>>(tokens, positions, static_cast<const uint16_t*>(dy), dtok, dpos,
+                                                     rows, D, scale, vocab_start, vocab_end, pad_idx);
+  else
+    embed_bwd_kernel<false><<<grid, 256, 0, stream>>>(tokens, positions, static_cast<const uint16_t*>(dy), dtok, dpos,
+                                                      rows, D, scale, vocab_start, vocab_end, pad_idx);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+extern "C" int msq_fold_fp32(const float* src, void* dst, long long n, int accumulate, int bf16,
+                             cudaStream_t stream) {
+  using namespace msq;
+  if (n <= 0) return 0;
+  if (n & 1) return -2;
+  long long blocks = (n / 2 + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  if (bf16) fold_fp32_kernel<true><<<static_cast<int>(blocks), 256, 0, stream>>>(src, static_cast<uint16_t*>(dst), n, accumulate);
+  else fold_fp32_kernel<false><<<static_cast<int>(blocks), 256, 0, stream>>>(src, static_cast<uint16_t*>(dst), n, accumulate);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+extern "C" int msq_cross_entropy(void* logits, long long ld, const long long* target, float* loss, float* lse,
+                                 int rows, int V, long long ignore_index, float grad_scale, int write_grad, int bf16,
+                                 cudaStream_t stream) {
+  using namespace msq;
+  if (rows <= 0) return 0;
+  if ((V & 7) || (ld & 7)) return -2;
+  const size_t smem = static_cast<size_t>(V) * 2;
+  if (smem > 200 * 1024) return -3;
+  static bool configured[2] = {false, false};
+  if (!configured[bf16 ? 1 : 0]) {
+    cudaError_t e = bf16 ? cudaFuncSetAttribute(cross_entropy_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)
+                         : cudaFuncSetAttribute(cross_entropy_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return -10;
+    configured[bf16 ? 1 : 0] = true;
+  }
+  const int grid = rows < 148 * 2 ? rows : 148 * 2;
+  if (bf16)
+    cross_entropy_kernel<true><<<grid, 512, smem, stream>>>(static_cast<uint16_t*>(logits), ld, target, loss, lse, rows,
+                                                            V, ignore_index, grad_scale, write_grad);
+  else
+    cross_entropy_kernel<false><<<grid, 512, smem, stream>>>(static_cast<uint16_t*>(logits), ld, target, loss, lse, rows,
+                                                             V, ignore_index, grad_scale, write_grad);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// acc (fp32, [N], zeroed or holding a running sum) += column sums of x[rows, N].
+extern "C" int msq_colsum(const void* x, long long ld, int rows, int N, float* acc, int bf16, cudaStream_t stream) {
+  using namespace msq;
+  if (rows <= 0 || N <= 0) return 0;
+  if ((N & 7) || (ld & 7)) return -2;
+  const int gx = (N + 255) / 256;
+  int gy = (148 * 8 + gx - 1) / gx;
+  int rows_per = (rows + gy - 1) / gy;
+  rows_per = (rows_per + 7) / 8 * 8;
+  gy = (rows + rows_per - 1) / rows_per;
+  dim3 grid(gx, gy);
+  if (bf16) colsum_kernel<true><<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(x), ld, rows, N, acc, rows_per);
+  else colsum_kernel<false><<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(x), ld, rows, N, acc, rows_per);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}

@@ -1,0 +1,193 @@
+// Optimizer-side kernels: squared-L2-norm of a flat gradient shard, the
+// device-side clip / overflow decision, and the fused AdamW update for the
+// memory-efficient fp16 optimizer (16-bit params and grads, fp32 moments, no
+// fp32 master copy).
+//
+// Reference behaviour being reproduced:
+//   * grad norm: metaseq/utils.py:104-127 (multi_tensor_l2norm) + :199-229 (clip)
+//   * lazy _multiply_factor folding 1/loss_scale, dp/sample_size and the clip
+//     coefficient: metaseq/optim/fp16_optimizer.py:397-455
+//   * Adam math: metaseq/optim/adam.py:170-213 (decoupled weight decay, bias
+//     correction folded into the step size, eps added outside the sqrt)
+// Unlike the reference, the overflow / clip decision stays on the device: the
+// update kernel reads a two-float control block, so no host sync sits between
+// the norm and the step.
+#include "sm100_common.cuh"
+
+namespace msq {
+
+constexpr int SUMSQ_THREADS = 512;
+
+template <int DT>  // 0 fp16, 1 bf16, 2 fp32
+__device__ __forceinline__ float load_as_float(const void* base, long long i) {
+  if constexpr (DT == 0) return __half2float(static_cast<const __half*>(base)[i]);
+  else if constexpr (DT == 1) return __bfloat162float(static_cast<const __nv_bfloat16*>(base)[i]);
+  else return static_cast<const float*>(base)[i];
+}
+
+// Each CTA writes one partial sum of squares to scratch[blockIdx.x].
+template <int DT>
+__global__ void __launch_bounds__(SUMSQ_THREADS)
+sumsq_partial_kernel(const void* __restrict__ g, long long n, float* __restrict__ scratch) {
+  __shared__ float red[32];
+  float acc = 0.f;
+  const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  if constexpr (DT == 2) {
+    const long long n4 = n >> 2;
+    const float4* g4 = static_cast<const float4*>(g);
+    for (long long i = tid; i < n4; i += stride) {
+      const float4 v = g4[i];
+      acc += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    for (long long i = (n4 << 2) + tid; i < n; i += stride) {
+      const float v = static_cast<const float*>(g)[i];
+      acc += v * v;
+    }
+  } else {
+    const long long n8 = n >> 3;
+    const uint4* g8 = static_cast<const uint4*>(g);
+    for (long long i = tid; i < n8; i += stride) {
+      const uint4 v = g8[i];
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 t = unpack2<DT == 1>(w[j]);
+        acc += t.x * t.x + t.y * t.y;
+      }
+    }
+    for (long long i = (n8 << 3) + tid; i < n; i += stride) {
+      const float v = load_as_float<DT>(g, i);
+      acc += v * v;
+    }
+  }
+  const float total = block_sum(acc, red);
+  if (threadIdx.x == 0) scratch[blockIdx.x] = total;
+}
+
+// Single CTA: out[0] = (accumulate ? out[0] : 0) + sum(scratch[0..parts)).
+__global__ void __launch_bounds__(SUMSQ_THREADS)
+sumsq_finalize_kernel(const float* __restrict__ scratch, int parts, float* __restrict__ out, int accumulate) {
+  __shared__ float red[32];
+  float acc = 0.f;
+  for (int i = threadIdx.x; i < parts; i += blockDim.x) acc += scratch[i];
+  const float total = block_sum(acc, red);
+  if (threadIdx.x == 0) out[0] = total + (accumulate ? out[0] : 0.f);
+}
+
+// ctrl_out[0] = multiplier the update applies to raw grads (pre_factor * clip_coef)
+// ctrl_out[1] = 1 when the step must be skipped (non-finite norm), else 0
+// ctrl_out[2] = unclipped gradient norm (pre_factor * sqrt(sum of squares))
+// ctrl_out[3] = clip coefficient
+__global__ void clip_decision_kernel(const float* __restrict__ sumsq, int n_terms, float pre_factor, float max_norm,
+                                     float* __restrict__ ctrl_out) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  float s = 0.f;
+  for (int i = 0; i < n_terms; ++i) s += sumsq[i];
+  const float norm = pre_factor * sqrtf(s);
+  const bool bad = !isfinite(norm);
+  float coef = 1.f;
+  if (!bad && max_norm > 0.f) coef = fminf(1.f, max_norm / (norm + 1e-6f));
+  ctrl_out[0] = pre_factor * coef;
+  ctrl_out[1] = bad ? 1.f : 0.f;
+  ctrl_out[2] = norm;
+  ctrl_out[3] = coef;
+}
+
+// AdamW on a flat shard.  P and G are 16-bit (PDT / GDT codes as above; PDT may be
+// fp32 for a master-weight flavour, in which case p16_out, if given, receives the
+// 16-bit copy).  m, v fp32.
+template <int PDT, int GDT>
+__global__ void __launch_bounds__(512)
+adamw_kernel(void* __restrict__ p, const void* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
+             void* __restrict__ p16_out, int p16_bf16, long long n, float lr, float beta1, float beta2, float eps,
+             float weight_decay, float step_size, float inv_sqrt_bc2_unused, const float* __restrict__ ctrl) {
+  const float gmul = ctrl ? ctrl[0] : 1.f;
+  if (ctrl && ctrl[1] != 0.f) return;  // overflow: leave params and moments untouched
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const float gi = load_as_float<GDT>(g, i) * gmul;
+    float pi = load_as_float<PDT>(p, i);
+    const float mi = beta1 * m[i] + (1.f - beta1) * gi;
+    const float vi = beta2 * v[i] + (1.f - beta2) * gi * gi;
+    m[i] = mi;
+    v[i] = vi;
+    const float denom = sqrtf(vi) + eps;
+    pi = pi - lr * weight_decay * pi;
+    pi = pi - step_size * (mi / denom);
+    if constexpr (PDT == 0) static_cast<__half*>(p)[i] = __float2half(pi);
+    else if constexpr (PDT == 1) static_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16(pi);
+    else {
+      static_cast<float*>(p)[i] = pi;
+      if (p16_out) {
+        if (p16_bf16) static_cast<__nv_bfloat16*>(p16_out)[i] = __float2bfloat16(pi);
+        else static_cast<__half*>(p16_out)[i] = __float2half(pi);
+      }
+    }
+  }
+}
+
+static int device_sms() {
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return sms;
+}
+
+}  // namespace msq
+
+// Number of scratch floats msq_sumsq needs for an n-element tensor.
+extern "C" int msq_sumsq_parts(long long n) {
+  const long long per = 8LL * msq::SUMSQ_THREADS;
+  long long b = (n + per - 1) / per;
+  const long long cap = 4LL * msq::device_sms();
+  if (b > cap) b = cap;
+  if (b < 1) b = 1;
+  return static_cast<int>(b);
+}
+
+// out[0] (+)= sum(g^2).  `scratch` holds msq_sumsq_parts(n) floats of global memory.
+extern "C" int msq_sumsq(const void* g, long long n, int dtype, float* scratch, float* out, int accumulate,
+                         cudaStream_t stream) {
+  using namespace msq;
+  const int parts = msq_sumsq_parts(n);
+  if (dtype == 0) sumsq_partial_kernel<0><<<parts, SUMSQ_THREADS, 0, stream>>>(g, n, scratch);
+  else if (dtype == 1) sumsq_partial_kernel<1><<<parts, SUMSQ_THREADS, 0, stream>>>(g, n, scratch);
+  else if (dtype == 2) sumsq_partial_kernel<2><<<parts, SUMSQ_THREADS, 0, stream>>>(g, n, scratch);
+  else return -2;
+  sumsq_finalize_kernel<<<1, SUMSQ_THREADS, 0, stream>>>(scratch, parts, out, accumulate);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+extern "C" int msq_clip_decision(const float* sumsq, int n_terms, float pre_factor, float max_norm, float* ctrl_out,
+                                 cudaStream_t stream) {
+  msq::clip_decision_kernel<<<1, 32, 0, stream>>>(sumsq, n_terms, pre_factor, max_norm, ctrl_out);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+extern "C" int msq_adamw(void* p, const void* g, float* m, float* v, void* p16_out, int p16_bf16, long long n,
+                         int p_dtype, int g_dtype, float lr, float beta1, float beta2, float eps, float weight_decay,
+                         float step_size, const float* ctrl, cudaStream_t stream) {
+  using namespace msq;
+  if (n <= 0) return 0;
+  long long blocks = (n + 511) / 512;
+  const long long cap = 16LL * device_sms();
+  if (blocks > cap) blocks = cap;
+  const int b = static_cast<int>(blocks);
+#define MSQ_ADAM(PD, GD)                                                                                       \
+  adamw_kernel<PD, GD><<<b, 512, 0, stream>>>(p, g, m, v, p16_out, p16_bf16, n, lr, beta1, beta2, eps,        \
+                                              weight_decay, step_size, 0.f, ctrl)
+  if (p_dtype == 0 && g_dtype == 0) MSQ_ADAM(0, 0);
+  else if (p_dtype == 1 && g_dtype == 1) MSQ_ADAM(1, 1);
+  else if (p_dtype == 2 && g_dtype == 0) MSQ_ADAM(2, 0);
+  else if (p_dtype == 2 && g_dtype == 1) MSQ_ADAM(2, 1);
+  else if (p_dtype == 2 && g_dtype == 2) MSQ_ADAM(2, 2);
+  else if (p_dtype == 0 && g_dtype == 2) MSQ_ADAM(0, 2);
+  else if (p_dtype == 1 && g_dtype == 2) MSQ_ADAM(1, 2);
+  else return -2;
+#undef MSQ_ADAM
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}

@@ -1,0 +1,181 @@
+"""Symbol <-> index mapping.
+
+Special symbols occupy indices 0..3 in the order ``<s>, <pad>, </s>, <unk>`` and the
+table can be padded with ``madeupwordNNNN`` entries to a multiple (OPT pads the
+50265-entry GPT-2 BPE table to 50272 = 8 * 6284).  Reference:
+metaseq/data/dictionary.py (specials :22-41, ``pad_to_multiple_`` :189-196).
+"""
+from __future__ import annotations
+
+import os
+from collections import Counter
+from typing import Iterable, List, Optional
+
+import torch
+
+
+class Dictionary:
+    def __init__(self, *, bos="<s>", pad="<pad>", eos="</s>", unk="<unk>", extra_special_symbols=None):
+        self.bos_word, self.unk_word, self.pad_word, self.eos_word = bos, unk, pad, eos
+        self.symbols: List[str] = []
+        self.count: List[int] = []
+        self.indices = {}
+        self.bos_index = self.add_symbol(bos)
+        self.pad_index = self.add_symbol(pad)
+        self.eos_index = self.add_symbol(eos)
+        self.unk_index = self.add_symbol(unk)
+        for s in extra_special_symbols or []:
+            self.add_symbol(s)
+        self.nspecial = len(self.symbols)
+
+    def __eq__(self, other):
+        return isinstance(other, Dictionary) and self.indices == other.indices
+
+    def __getitem__(self, idx: int) -> str:
+        return self.symbols[idx] if idx < len(self.symbols) else self.unk_word
+
+    def __len__(self) -> int:
+        return len(self.symbols)
+
+    def __contains__(self, sym) -> bool:
+        return sym in self.indices
+
+    def index(self, sym: str) -> int:
+        return self.indices.get(sym, self.unk_index)
+
+    def string(self, tensor, bpe_symbol=None, escape_unk=False, extra_symbols_to_ignore=None, unk_string=None) -> str:
+        if torch.is_tensor(tensor) and tensor.dim() == 2:
+            return "\n".join(self.string(t, bpe_symbol, escape_unk, extra_symbols_to_ignore) for t in tensor)
+        ignore = set(extra_symbols_to_ignore or [])
+        ignore.add(self.eos())
+
+        def tok(i):
+            if i == self.unk():
+                return unk_string if unk_string is not None else self.unk_string(escape_unk)
+            return self[i]
+
+        if hasattr(self, "bos_index"):
+            ignore.add(self.bos())
+        sent = " ".join(tok(int(i)) for i in tensor if int(i) not in ignore)
+        if bpe_symbol:
+            sent = (sent + " ").replace(bpe_symbol, "").rstrip()
+        return sent
+
+    def unk_string(self, escape=False) -> str:
+        return "<{}>".format(self.unk_word) if escape else self.unk_word
+
+    def add_symbol(self, word: str, n: int = 1, overwrite: bool = False) -> int:
+        if word in self.indices and not overwrite:
+            idx = self.indices[word]
+            self.count[idx] += n
+            return idx
+        idx = len(self.symbols)
+        self.indices[word] = idx
+        self.symbols.append(word)
+        self.count.append(n)
+        return idx
+
+    def update(self, other: "Dictionary"):
+        for word, c in zip(other.symbols, other.count):
+            self.add_symbol(word, c)
+
+    def finalize(self, threshold: int = -1, nwords: int = -1, padding_factor: int = 8):
+        """Sort by decreasing frequency (specials stay first), drop rare words, pad."""
+        if nwords <= 0:
+            nwords = len(self)
+        new_symbols = self.symbols[: self.nspecial]
+        new_count = self.count[: self.nspecial]
+        c = Counter(dict(sorted(zip(self.symbols[self.nspecial:], self.count[self.nspecial:]))))
+        for sym, cnt in c.most_common(nwords - self.nspecial):
+            if cnt >= threshold:
+                new_symbols.append(sym)
+                new_count.append(cnt)
+            else:
+                break
+        self.symbols, self.count = list(new_symbols), list(new_count)
+        self.indices = {s: i for i, s in enumerate(self.symbols)}
+        self.pad_to_multiple_(padding_factor)
+
+    def pad_to_multiple_(self, padding_factor: int):
+        if padding_factor > 1:
+            i = 0
+            while len(self) % padding_factor != 0:
+                self.add_symbol("madeupword{:04d}".format(i), n=0)
+                i += 1
+
+    def bos(self) -> int:
+        return self.bos_index
+
+    def pad(self) -> int:
+        return self.pad_index
+
+    def eos(self) -> int:
+        return self.eos_index
+
+    def unk(self) -> int:
+        return self.unk_index
+
+    @classmethod
+    def load(cls, f) -> "Dictionary":
+        """``<symbol> <count> [#fairseq:overwrite]`` per line."""
+        d = cls()
+        d.add_from_file(f)
+        return d
+
+    def add_from_file(self, f):
+        if isinstance(f, str):
+            with open(f, "r", encoding="utf-8") as fd:
+                return self.add_from_file(fd)
+        for line in f.readlines():
+            try:
+                line, field = line.rstrip().rsplit(" ", 1)
+                overwrite = False
+                if field == "#fairseq:overwrite":
+                    overwrite = True
+                    line, field = line.rsplit(" ", 1)
+                count = int(field)
+                if line in self and not overwrite:
+                    raise RuntimeError(f"Duplicate word found when loading Dictionary: '{line}'")
+                self.add_symbol(line, n=count, overwrite=overwrite)
+            except ValueError:
+                raise ValueError("Incorrect dictionary format, expected '<token> <cnt> [flags]'")
+
+    def save(self, f):
+        if isinstance(f, str):
+            os.makedirs(os.path.dirname(f) or ".", exist_ok=True)
+            with open(f, "w", encoding="utf-8") as fd:
+                return self.save(fd)
+        for sym, cnt in zip(self.symbols[self.nspecial:], self.count[self.nspecial:]):
+            print(f"{sym} {cnt}", file=f)
+
+    def dummy_sentence(self, length: int) -> torch.Tensor:
+        t = torch.Tensor(length).uniform_(self.nspecial + 1, len(self)).long()
+        t[-1] = self.eos()
+        return t
+
+    def encode_line(self, line: str, line_tokenizer=None, add_if_not_exist=True, consumer=None, append_eos=True,
+                    reverse_order=False) -> torch.IntTensor:
+        from metaseq_b200.utils import tokenize_line
+
+        words = (line_tokenizer or tokenize_line)(line)
+        if reverse_order:
+            words = list(reversed(words))
+        n = len(words)
+        ids = torch.IntTensor(n + 1 if append_eos else n)
+        for i, w in enumerate(words):
+            idx = self.add_symbol(w) if add_if_not_exist else self.index(w)
+            if consumer is not None:
+                consumer(w, idx)
+            ids[i] = idx
+        if append_eos:
+            ids[n] = self.eos_index
+        return ids
+
+    @classmethod
+    def synthetic(cls, vocab_size: int) -> "Dictionary":
+        """Dictionary with ``vocab_size`` entries (4 specials + numbered words), for tasks that
+        train on synthetic token ids."""
+        d = cls()
+        for i in range(vocab_size - d.nspecial):
+            d.add_symbol(f"w{i}")
+        return d

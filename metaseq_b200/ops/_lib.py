@@ -1,0 +1,149 @@
+"""ctypes loader for the in-tree native libraries.
+
+The CUDA kernels live in ``metaseq_b200/_C/libmsq_kernels.so`` (built by
+``metaseq_b200.build_ext``) and export a C ABI that takes raw device pointers
+and a ``cudaStream_t``.  On a machine with a GPU the library must be present:
+falling back silently to PyTorch ops there would hide a broken build, so
+``kernels()`` raises instead.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from pathlib import Path
+
+import torch
+
+_ROOT = Path(__file__).resolve().parent.parent / "_C"
+_KLIB = None
+_HLIB = None
+
+P = c_void_p
+I = c_int
+L = c_longlong
+F = c_float
+
+
+def _sig(lib, name, argtypes, restype=c_int):
+    fn = getattr(lib, name)
+    fn.argtypes = argtypes
+    fn.restype = restype
+    return fn
+
+
+def _declare_kernels(lib):
+    _sig(lib, "msq_gemm", [P, P, P, I, I, I, L, L, L, I, I, I, P, P, L, P, L, I, I, I, I, P, P])
+    _sig(lib, "msq_layernorm_bwd_parts", [I])
+    _sig(lib, "msq_layernorm_fwd", [P, P, P, P, P, P, I, I, F, I, P])
+    _sig(lib, "msq_layernorm_bwd", [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, P])
+    _sig(lib, "msq_sumsq_parts", [L])
+    _sig(lib, "msq_sumsq", [P, L, I, P, P, I, P])
+    _sig(lib, "msq_clip_decision", [P, I, F, F, P, P])
+    _sig(lib, "msq_adamw", [P, P, P, P, P, I, L, I, I, F, F, F, F, F, F, P, P])
+    _sig(lib, "msq_embed_fwd", [P, P, P, P, P, I, I, F, L, L, I, I, P])
+    _sig(lib, "msq_embed_bwd", [P, P, P, P, P, I, I, F, L, L, L, I, P])
+    _sig(lib, "msq_fold_fp32", [P, P, L, I, I, P])
+    _sig(lib, "msq_cross_entropy", [P, L, P, P, P, I, I, L, F, I, I, P])
+    _sig(lib, "msq_colsum", [P, L, I, I, P, I, P])
+    _sig(lib, "msq_flash_fwd", [P, P, P, L, L, L, L, L, L, P, L, L, P, I, I, I, I, F, I, I, P, P])
+    _sig(
+        lib,
+        "msq_flash_bwd",
+        [P, P, P, P, P] + [L] * 10 + [P, P, P, P, P] + [L] * 4 + [I, I, I, I, F, I, I, P, P],
+    )
+    for name, sig in _OPTIONAL.items():
+        if hasattr(lib, name):
+            _sig(lib, name, sig)
+
+
+# Entry points added by later source files; declared when present.
+_OPTIONAL = {
+    "msq_decode_attn": [P, P, P, P, P, L, L, L, L, L, L, I, I, I, I, I, F, I, P],
+    "msq_kv_append": [P, P, P, P, P, L, L, L, L, I, I, I, I, I, P],
+    "msq_allreduce_oneshot": [P, P, P, L, I, I, I, P, I, P, P],
+    "msq_gemm_ag": None,
+}
+_OPTIONAL = {k: v for k, v in _OPTIONAL.items() if v is not None}
+
+
+def kernels_path() -> Path:
+    return _ROOT / "libmsq_kernels.so"
+
+
+def host_path() -> Path:
+    return _ROOT / "libmsq_host.so"
+
+
+def have_kernels() -> bool:
+    """True when the CUDA library is built and a GPU is present to run it."""
+    return torch.cuda.is_available() and kernels_path().exists() and not os.environ.get("MSQ_DISABLE_KERNELS")
+
+
+def kernels():
+    """The CUDA kernel library (loaded on first use)."""
+    global _KLIB
+    if _KLIB is None:
+        path = kernels_path()
+        if not path.exists():
+            raise RuntimeError(
+                f"{path} is missing: run `python -m metaseq_b200.build_ext` (or __graft_entry__.build()) first"
+            )
+        lib = ctypes.CDLL(str(path))
+        _declare_kernels(lib)
+        _KLIB = lib
+    return _KLIB
+
+
+def host():
+    """The host-side C++ helper library, or None when it has not been built."""
+    global _HLIB
+    if _HLIB is None:
+        path = host_path()
+        if not path.exists():
+            return None
+        _HLIB = ctypes.CDLL(str(path))
+    return _HLIB
+
+
+def stream_ptr() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def ptr(t) -> c_void_p:
+    return c_void_p(t.data_ptr()) if t is not None else c_void_p(0)
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float16:
+        return 0
+    if dt == torch.bfloat16:
+        return 1
+    if dt == torch.float32:
+        return 2
+    raise TypeError(f"unsupported dtype {dt}")
+
+
+_STATUS = {}
+
+
+def status_word(device) -> torch.Tensor:
+    """Per-device int32 word that kernels set when one of their bounded waits runs out."""
+    key = torch.device(device).index or 0
+    if key not in _STATUS:
+        _STATUS[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _STATUS[key]
+
+
+def check_status(device="cuda") -> int:
+    """Reads (and clears) the kernel status word; non-zero means a wait timed out."""
+    w = status_word(device)
+    v = int(w.item())
+    if v:
+        w.zero_()
+    return v
+
+
+def check_rc(rc: int, what: str):
+    if rc != 0:
+        raise RuntimeError(f"{what} failed to launch (code {rc})")

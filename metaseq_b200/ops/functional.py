@@ -1,0 +1,480 @@
+"""Raw (non-autograd) operator entry points.
+
+Every function has two implementations with the same contract:
+
+* the sm_100a kernel from ``libmsq_kernels.so`` when the tensors are CUDA
+  fp16/bf16 and the library is present;
+* a plain PyTorch fp32-accumulating restatement used on CPU, as the numerical
+  oracle in the tests, and as the ``torch`` baseline backend.
+
+``set_backend("torch")`` forces the PyTorch path on a GPU too (that is the
+cuBLAS + unfused-ops baseline the kernels are compared against).
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+
+_BACKEND = "auto"  # "auto" | "torch"
+
+
+def set_backend(name: str):
+    global _BACKEND
+    if name not in ("auto", "kernels", "torch"):
+        raise ValueError(name)
+    _BACKEND = "auto" if name == "kernels" else name
+
+
+def get_backend() -> str:
+    return _BACKEND
+
+
+def use_kernels(*tensors) -> bool:
+    if _BACKEND == "torch":
+        return False
+    t = tensors[0]
+    if not t.is_cuda or t.dtype not in (torch.float16, torch.bfloat16):
+        return False
+    if not _lib.kernels_path().exists():
+        raise RuntimeError(
+            "CUDA tensors were passed to metaseq_b200.ops but libmsq_kernels.so is not built; "
+            "run `python -m metaseq_b200.build_ext`"
+        )
+    return True
+
+
+def _bf(t) -> int:
+    return 1 if t.dtype == torch.bfloat16 else 0
+
+
+# ----------------------------------------------------------------------- GEMM
+def gemm(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    *,
+    a_mn: bool = False,
+    b_mn: bool = False,
+    bias: Optional[torch.Tensor] = None,
+    residual: Optional[torch.Tensor] = None,
+    mask: Optional[torch.Tensor] = None,
+    relu: bool = False,
+    out: Optional[torch.Tensor] = None,
+    accumulate: bool = False,
+    bn: int = 0,
+    max_ctas: int = 0,
+) -> torch.Tensor:
+    """``out[M,N] = epilogue(op(a) @ op(b))`` for 2-D operands.
+
+    ``a`` is stored ``[M,K]`` (``a_mn=False``) or ``[K,M]`` (``a_mn=True``);
+    ``b`` is stored ``[N,K]`` (``b_mn=False``, an ``nn.Linear`` weight) or
+    ``[K,N]`` (``b_mn=True``).  Epilogue order: ``+bias`` -> ReLU ->
+    zero where ``mask<=0`` -> ``+residual`` -> ``+out`` (when ``accumulate``).
+    Operands may be row-strided views (last dim contiguous).
+    """
+    assert a.dim() == 2 and b.dim() == 2
+    M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
+    N, Kb = (b.shape[1], b.shape[0]) if b_mn else (b.shape[0], b.shape[1])
+    assert K == Kb, f"inner dims differ: {K} vs {Kb}"
+    if out is None:
+        assert not accumulate
+        out = torch.empty((M, N), dtype=a.dtype, device=a.device)
+    if M == 0 or N == 0:
+        return out
+    if use_kernels(a) and K % 8 == 0 and N % 8 == 0 and _gemm_operands_ok(a, b, out, residual, mask) \
+            and (bias is None or bias.data_ptr() % 16 == 0):
+        lib = _lib.kernels()
+        rc = lib.msq_gemm(
+            _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), M, N, K,
+            a.stride(0), b.stride(0), out.stride(0),
+            int(a_mn), int(b_mn), _bf(a),
+            _lib.ptr(bias), _lib.ptr(residual), residual.stride(0) if residual is not None else 0,
+            _lib.ptr(mask), mask.stride(0) if mask is not None else 0,
+            int(relu), int(accumulate), bn, max_ctas,
+            _lib.ptr(_lib.status_word(a.device)), _lib.stream_ptr(),
+        )
+        _lib.check_rc(rc, "msq_gemm")
+        return out
+    return _gemm_torch(a, b, a_mn, b_mn, bias, residual, mask, relu, out, accumulate)
+
+
+def _gemm_operands_ok(a, b, out, residual, mask) -> bool:
+    for t in (a, b, out, residual, mask):  # 2-D operands
+        if t is None:
+            continue
+        if t.stride(-1) != 1 or t.data_ptr() % 16 or (t.dim() == 2 and t.stride(0) % 8):
+            return False
+    return True
+
+
+def _gemm_torch(a, b, a_mn, b_mn, bias, residual, mask, relu, out, accumulate):
+    am = a.t() if a_mn else a
+    bm = b if b_mn else b.t()
+    if a.is_cuda:
+        acc = torch.matmul(am, bm).float()  # cuBLAS, fp32 accumulate inside
+    else:
+        acc = torch.matmul(am.float(), bm.float())
+    if bias is not None:
+        acc = acc + bias.float()
+    if relu:
+        acc = torch.relu(acc)
+    if mask is not None:
+        acc = acc * (mask > 0)
+    if residual is not None:
+        acc = acc + residual.float()
+    if accumulate:
+        acc = acc + out.float()
+    out.copy_(acc)
+    return out
+
+
+# ------------------------------------------------------------------ LayerNorm
+def layer_norm_fwd(x2d, gamma, beta, eps: float):
+    """Returns ``(y, mean, rstd)`` for ``x2d`` of shape ``[rows, D]``; statistics are fp32."""
+    rows, D = x2d.shape
+    if use_kernels(x2d) and D % 8 == 0 and D <= 16384 and x2d.is_contiguous():
+        y = torch.empty_like(x2d)
+        mean = torch.empty(rows, dtype=torch.float32, device=x2d.device)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x2d.device)
+        rc = _lib.kernels().msq_layernorm_fwd(
+            _lib.ptr(x2d), _lib.ptr(gamma), _lib.ptr(beta), _lib.ptr(y), _lib.ptr(mean), _lib.ptr(rstd),
+            rows, D, float(eps), _bf(x2d), _lib.stream_ptr(),
+        )
+        _lib.check_rc(rc, "msq_layernorm_fwd")
+        return y, mean, rstd
+    xf = x2d.float()
+    mean = xf.mean(dim=1)
+    var = xf.var(dim=1, unbiased=False)
+    rstd = torch.rsqrt(var + eps)
+    y = (xf - mean[:, None]) * rstd[:, None]
+    if gamma is not None:
+        y = y * gamma.float()
+    if beta is not None:
+        y = y + beta.float()
+    return y.to(x2d.dtype), mean, rstd
+
+
+def layer_norm_bwd(dy, x2d, mean, rstd, gamma, add=None, dgamma_out=None, dbeta_out=None, accumulate=False,
+                   need_param_grads=True):
+    """Returns ``(dx, dgamma, dbeta)``.  ``add`` (same shape as ``x2d``) is summed into ``dx``:
+    it carries the residual-branch gradient so no separate add kernel is needed."""
+    rows, D = x2d.shape
+    affine = gamma is not None and need_param_grads
+    if use_kernels(x2d) and D % 8 == 0 and D <= 16384 and x2d.is_contiguous() and dy.is_contiguous():
+        lib = _lib.kernels()
+        dx = torch.empty_like(x2d)
+        part_g = part_b = None
+        if affine:
+            parts = lib.msq_layernorm_bwd_parts(rows)
+            part = torch.empty((2, parts, D), dtype=torch.float32, device=x2d.device)
+            part_g, part_b = part[0], part[1]
+            if dgamma_out is None:
+                dgamma_out = torch.empty(D, dtype=x2d.dtype, device=x2d.device)
+                dbeta_out = torch.empty(D, dtype=x2d.dtype, device=x2d.device)
+                accumulate = False
+        rc = lib.msq_layernorm_bwd(
+            _lib.ptr(dy), _lib.ptr(x2d), _lib.ptr(mean), _lib.ptr(rstd), _lib.ptr(gamma), _lib.ptr(add),
+            _lib.ptr(dx), _lib.ptr(part_g), _lib.ptr(part_b),
+            _lib.ptr(dgamma_out if affine else None), _lib.ptr(dbeta_out if affine else None),
+            int(accumulate), rows, D, _bf(x2d), _lib.stream_ptr(),
+        )
+        _lib.check_rc(rc, "msq_layernorm_bwd")
+        return dx, (dgamma_out if affine else None), (dbeta_out if affine else None)
+    xf, dyf = x2d.float(), dy.float()
+    xhat = (xf - mean[:, None]) * rstd[:, None]
+    gdy = dyf * gamma.float() if gamma is not None else dyf
+    m1 = gdy.mean(dim=1, keepdim=True)
+    m2 = (gdy * xhat).mean(dim=1, keepdim=True)
+    dx = rstd[:, None] * (gdy - m1 - xhat * m2)
+    if add is not None:
+        dx = dx + add.float()
+    dg = db = None
+    if affine:
+        dg = (dyf * xhat).sum(dim=0)
+        db = dyf.sum(dim=0)
+        if dgamma_out is not None:
+            if accumulate:
+                dgamma_out.add_(dg.to(dgamma_out.dtype))
+                dbeta_out.add_(db.to(dbeta_out.dtype))
+            else:
+                dgamma_out.copy_(dg)
+                dbeta_out.copy_(db)
+            dg, db = dgamma_out, dbeta_out
+        else:
+            dg, db = dg.to(x2d.dtype), db.to(x2d.dtype)
+    return dx.to(x2d.dtype), dg, db
+
+
+# ------------------------------------------------------------------ attention
+def flash_attn_fwd(q, k, v, scale: float, causal: bool = True):
+    """``q, k, v``: ``[B, T, H, d]`` views (last dim contiguous, head stride ``d``).
+    Returns ``(out [B, T, H*d], lse [B, H, T] fp32)``."""
+    B, T, H, d = q.shape
+    if use_kernels(q) and d in (64, 128) and _attn_views_ok(q, k, v):
+        out = torch.empty((B, T, H * d), dtype=q.dtype, device=q.device)
+        lse = torch.empty((B, H, T), dtype=torch.float32, device=q.device)
+        rc = _lib.kernels().msq_flash_fwd(
+            _lib.ptr(q), _lib.ptr(k), _lib.ptr(v),
+            q.stride(1), q.stride(0), k.stride(1), k.stride(0), v.stride(1), v.stride(0),
+            _lib.ptr(out), out.stride(1), out.stride(0), _lib.ptr(lse),
+            B, T, H, d, float(scale), int(causal), _bf(q),
+            _lib.ptr(_lib.status_word(q.device)), _lib.stream_ptr(),
+        )
+        _lib.check_rc(rc, "msq_flash_fwd")
+        return out, lse
+    return _attn_fwd_torch(q, k, v, scale, causal)
+
+
+def _attn_views_ok(*ts) -> bool:
+    for t in ts:
+        d = t.shape[-1]
+        if t.stride(3) != 1 or t.stride(2) != d or t.data_ptr() % 16 or t.stride(1) % 8 or t.stride(0) % 8:
+            return False
+    return True
+
+
+def _attn_fwd_torch(q, k, v, scale, causal):
+    B, T, H, d = q.shape
+    qf, kf, vf = (t.float().permute(0, 2, 1, 3) for t in (q, k, v))  # [B,H,T,d]
+    s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    if causal:
+        mask = torch.ones(T, T, dtype=torch.bool, device=q.device).triu(1)
+        s = s.masked_fill(mask, float("-inf"))
+    lse = torch.logsumexp(s, dim=-1)
+    p = torch.exp(s - lse[..., None])
+    o = torch.matmul(p, vf).permute(0, 2, 1, 3).reshape(B, T, H * d)
+    return o.to(q.dtype), lse
+
+
+def flash_attn_bwd(q, k, v, out, d_out, lse, scale: float, causal: bool, dq, dk, dv):
+    """Writes gradients into the ``[B, T, H, d]`` views ``dq, dk, dv`` (typically column slices
+    of the qkv-gradient buffer)."""
+    B, T, H, d = q.shape
+    if (
+        use_kernels(q) and d in (64, 128) and _attn_views_ok(q, k, v, dk, dv)
+        and out.stride() == d_out.stride() and out.stride(2) == 1
+    ):
+        delta = torch.empty((B, H, T), dtype=torch.float32, device=q.device)
+        dq_acc = torch.zeros((B, T, H * d), dtype=torch.float32, device=q.device)
+        rc = _lib.kernels().msq_flash_bwd(
+            _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(out), _lib.ptr(d_out),
+            q.stride(1), q.stride(0), k.stride(1), k.stride(0), v.stride(1), v.stride(0),
+            out.stride(1), out.stride(0), d_out.stride(1), d_out.stride(0),
+            _lib.ptr(lse), _lib.ptr(delta), _lib.ptr(dq_acc), _lib.ptr(dk), _lib.ptr(dv),
+            dk.stride(1), dk.stride(0), dv.stride(1), dv.stride(0),
+            B, T, H, d, float(scale), int(causal), _bf(q),
+            _lib.ptr(_lib.status_word(q.device)), _lib.stream_ptr(),
+        )
+        _lib.check_rc(rc, "msq_flash_bwd")
+        dq.copy_(dq_acc.view(B, T, H, d))
+        return
+    qf, kf, vf = (t.float().permute(0, 2, 1, 3) for t in (q, k, v))
+    of = out.float().view(B, T, H, d).permute(0, 2, 1, 3)
+    dof = d_out.float().reshape(B, T, H, d).permute(0, 2, 1, 3)
+    s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    if causal:
+        mask = torch.ones(T, T, dtype=torch.bool, device=q.device).triu(1)
+        s = s.masked_fill(mask, float("-inf"))
+    p = torch.exp(s - lse[..., None])
+    dvf = torch.matmul(p.transpose(-1, -2), dof)
+    dp = torch.matmul(dof, vf.transpose(-1, -2))
+    delta = (dof * of).sum(dim=-1, keepdim=True)
+    ds = p * (dp - delta) * scale
+    dqf = torch.matmul(ds, kf)
+    dkf = torch.matmul(ds.transpose(-1, -2), qf)
+    dq.copy_(dqf.permute(0, 2, 1, 3))
+    dk.copy_(dkf.permute(0, 2, 1, 3))
+    dv.copy_(dvf.permute(0, 2, 1, 3))
+
+
+# ------------------------------------------------------------------ embedding
+def embed_fwd(tokens, positions, tok_w, pos_w, scale: float, vocab_start: int = 0, vocab_end: Optional[int] = None,
+              add_positions: bool = True):
+    """``out[r] = tok_w[tokens[r]-vocab_start]*scale (0 outside the partition) + pos_w[positions[r]]``."""
+    D = tok_w.shape[1]
+    if vocab_end is None:
+        vocab_end = vocab_start + tok_w.shape[0]
+    flat_tok = tokens.reshape(-1)
+    flat_pos = positions.reshape(-1) if positions is not None else None
+    rows = flat_tok.numel()
+    use_pos = bool(add_positions and pos_w is not None and positions is not None)
+    if use_kernels(tok_w) and D % 8 == 0:
+        out = torch.empty((rows, D), dtype=tok_w.dtype, device=tok_w.device)
+        rc = _lib.kernels().msq_embed_fwd(
+            _lib.ptr(flat_tok.contiguous()), _lib.ptr(flat_pos.contiguous() if use_pos else None),
+            _lib.ptr(tok_w), _lib.ptr(pos_w if use_pos else None), _lib.ptr(out),
+            rows, D, float(scale), int(vocab_start), int(vocab_end), int(use_pos), _bf(tok_w), _lib.stream_ptr(),
+        )
+        _lib.check_rc(rc, "msq_embed_fwd")
+        return out.view(*tokens.shape, D)
+    in_range = (flat_tok >= vocab_start) & (flat_tok < vocab_end)
+    idx = (flat_tok - vocab_start).clamp(0, tok_w.shape[0] - 1)
+    out = tok_w[idx].float() * scale * in_range[:, None]
+    if use_pos:
+        out = out + pos_w[flat_pos].float()
+    return out.to(tok_w.dtype).view(*tokens.shape, D)
+
+
+def embed_bwd(tokens, positions, dy, tok_rows: int, pos_rows: int, scale: float, pad_idx: int,
+              vocab_start: int = 0, need_pos: bool = True):
+    """Returns fp32 gradient tables ``(dtok [tok_rows, D], dpos [pos_rows, D] or None)``."""
+    D = dy.shape[-1]
+    flat_tok = tokens.reshape(-1).contiguous()
+    flat_pos = positions.reshape(-1).contiguous() if (positions is not None and need_pos) else None
+    dy2 = dy.reshape(-1, D)
+    vocab_end = vocab_start + tok_rows
+    dtok = torch.zeros((tok_rows, D), dtype=torch.float32, device=dy.device)
+    dpos = torch.zeros((pos_rows, D), dtype=torch.float32, device=dy.device) if flat_pos is not None else None
+    if use_kernels(dy2) and D % 2 == 0 and dy2.is_contiguous():
+        rc = _lib.kernels().msq_embed_bwd(
+            _lib.ptr(flat_tok), _lib.ptr(flat_pos), _lib.ptr(dy2), _lib.ptr(dtok), _lib.ptr(dpos),
+            dy2.shape[0], D, float(scale), int(vocab_start), int(vocab_end), int(pad_idx), _bf(dy2),
+            _lib.stream_ptr(),
+        )
+        _lib.check_rc(rc, "msq_embed_bwd")
+        return dtok, dpos
+    dyf = dy2.float()
+    ok = (flat_tok >= vocab_start) & (flat_tok < vocab_end) & (flat_tok != pad_idx)
+    idx = (flat_tok - vocab_start).clamp(0, tok_rows - 1)
+    dtok.index_add_(0, idx, dyf * scale * ok[:, None])
+    if dpos is not None:
+        okp = flat_pos != pad_idx
+        dpos.index_add_(0, flat_pos, dyf * okp[:, None])
+    return dtok, dpos
+
+
+def fold_fp32_into(src32: torch.Tensor, dst16: torch.Tensor, accumulate: bool):
+    """``dst16 (+)= src32`` elementwise, with the sum formed in fp32."""
+    n = src32.numel()
+    if use_kernels(dst16) and n % 2 == 0 and dst16.is_contiguous() and src32.is_contiguous():
+        rc = _lib.kernels().msq_fold_fp32(_lib.ptr(src32), _lib.ptr(dst16), n, int(accumulate), _bf(dst16),
+                                          _lib.stream_ptr())
+        _lib.check_rc(rc, "msq_fold_fp32")
+        return dst16
+    if accumulate:
+        dst16.copy_(dst16.float() + src32.view_as(dst16))
+    else:
+        dst16.copy_(src32.view_as(dst16))
+    return dst16
+
+
+# -------------------------------------------------------------- cross entropy
+def cross_entropy_fwd_bwd(logits2d, target, ignore_index: int, grad_scale: float, write_grad: bool):
+    """Per-row NLL (fp32, 0 where ``target == ignore_index``) and log-sum-exp.  With
+    ``write_grad`` the logits buffer is overwritten by ``(softmax - onehot) * grad_scale``."""
+    rows, V = logits2d.shape
+    if use_kernels(logits2d) and V % 8 == 0 and V * 2 <= 200 * 1024 and logits2d.stride(1) == 1 \
+            and logits2d.stride(0) % 8 == 0:
+        loss = torch.empty(rows, dtype=torch.float32, device=logits2d.device)
+        lse = torch.empty(rows, dtype=torch.float32, device=logits2d.device)
+        rc = _lib.kernels().msq_cross_entropy(
+            _lib.ptr(logits2d), logits2d.stride(0), _lib.ptr(target.contiguous()), _lib.ptr(loss), _lib.ptr(lse),
+            rows, V, int(ignore_index), float(grad_scale), int(write_grad), _bf(logits2d), _lib.stream_ptr(),
+        )
+        _lib.check_rc(rc, "msq_cross_entropy")
+        return loss, lse
+    lf = logits2d.float()
+    lse = torch.logsumexp(lf, dim=1)
+    valid = target != ignore_index
+    tgt = target.clamp(0, V - 1)
+    loss = (lse - lf.gather(1, tgt[:, None]).squeeze(1)) * valid
+    if write_grad:
+        g = torch.exp(lf - lse[:, None])
+        g.scatter_add_(1, tgt[:, None], -torch.ones_like(lse)[:, None])
+        g = g * (valid[:, None] * grad_scale)
+        logits2d.copy_(g)
+    return loss, lse
+
+
+# --------------------------------------------------------------------- colsum
+def colsum(x2d, out16=None, accumulate=False):
+    """Column sums of ``[rows, N]`` (bias gradient), fp32 accumulation."""
+    rows, N = x2d.shape
+    if use_kernels(x2d) and N % 8 == 0 and x2d.stride(1) == 1 and x2d.stride(0) % 8 == 0:
+        acc = torch.zeros(N, dtype=torch.float32, device=x2d.device)
+        rc = _lib.kernels().msq_colsum(_lib.ptr(x2d), x2d.stride(0), rows, N, _lib.ptr(acc), _bf(x2d),
+                                       _lib.stream_ptr())
+        _lib.check_rc(rc, "msq_colsum")
+    else:
+        acc = x2d.float().sum(dim=0)
+    if out16 is None:
+        return acc.to(x2d.dtype)
+    return fold_fp32_into(acc, out16, accumulate)
+
+
+# ------------------------------------------------------------------ optimizer
+def sumsq(g: torch.Tensor, out: torch.Tensor, accumulate: bool):
+    """``out[0] (+)= sum(g**2)`` in fp32; ``out`` is a 1-element fp32 tensor on ``g``'s device."""
+    n = g.numel()
+    if g.is_cuda and _BACKEND != "torch" and g.is_contiguous() and _lib.kernels_path().exists():
+        lib = _lib.kernels()
+        parts = lib.msq_sumsq_parts(n)
+        scratch = torch.empty(parts, dtype=torch.float32, device=g.device)
+        rc = lib.msq_sumsq(_lib.ptr(g), n, _lib.dtype_code(g.dtype), _lib.ptr(scratch), _lib.ptr(out),
+                           int(accumulate), _lib.stream_ptr())
+        _lib.check_rc(rc, "msq_sumsq")
+        return out
+    s = g.float().pow(2).sum()
+    if accumulate:
+        out.add_(s)
+    else:
+        out.fill_(0).add_(s)
+    return out
+
+
+def clip_decision(sumsq_terms: torch.Tensor, pre_factor: float, max_norm: float, ctrl: torch.Tensor):
+    """Fills ``ctrl`` (4 fp32): [grad multiplier, skip flag, grad norm, clip coefficient]."""
+    if sumsq_terms.is_cuda and _BACKEND != "torch" and _lib.kernels_path().exists():
+        rc = _lib.kernels().msq_clip_decision(_lib.ptr(sumsq_terms), sumsq_terms.numel(), float(pre_factor),
+                                              float(max_norm), _lib.ptr(ctrl), _lib.stream_ptr())
+        _lib.check_rc(rc, "msq_clip_decision")
+        return ctrl
+    norm = pre_factor * torch.sqrt(sumsq_terms.float().sum())
+    bad = not bool(torch.isfinite(norm))
+    coef = 1.0
+    if not bad and max_norm > 0:
+        coef = min(1.0, max_norm / (float(norm) + 1e-6))
+    ctrl[0] = pre_factor * coef
+    ctrl[1] = 1.0 if bad else 0.0
+    ctrl[2] = norm
+    ctrl[3] = coef
+    return ctrl
+
+
+def adamw_step(p, g, m, v, *, lr, beta1, beta2, eps, weight_decay, step, ctrl=None, p16_out=None):
+    """One AdamW update of a flat tensor (decoupled decay, bias correction folded into the
+    step size, eps outside the sqrt).  ``ctrl`` is the device control block from
+    ``clip_decision``: grads are multiplied by ``ctrl[0]`` and the whole update is a no-op
+    when ``ctrl[1] != 0``."""
+    bc1 = 1.0 - beta1 ** step
+    bc2 = 1.0 - beta2 ** step
+    step_size = lr * math.sqrt(bc2) / bc1
+    n = p.numel()
+    if p.is_cuda and _BACKEND != "torch" and _lib.kernels_path().exists() and p.is_contiguous() and g.is_contiguous():
+        rc = _lib.kernels().msq_adamw(
+            _lib.ptr(p), _lib.ptr(g), _lib.ptr(m), _lib.ptr(v), _lib.ptr(p16_out),
+            1 if (p16_out is not None and p16_out.dtype == torch.bfloat16) else 0,
+            n, _lib.dtype_code(p.dtype), _lib.dtype_code(g.dtype),
+            float(lr), float(beta1), float(beta2), float(eps), float(weight_decay), float(step_size),
+            _lib.ptr(ctrl), _lib.stream_ptr(),
+        )
+        _lib.check_rc(rc, "msq_adamw")
+        return
+    gmul = 1.0
+    if ctrl is not None:
+        if float(ctrl[1]) != 0.0:
+            return
+        gmul = float(ctrl[0])
+    gf = g.float() * gmul
+    m.mul_(beta1).add_(gf, alpha=1 - beta1)
+    v.mul_(beta2).addcmul_(gf, gf, value=1 - beta2)
+    pf = p.float()
+    pf = pf - lr * weight_decay * pf
+    pf = pf - step_size * (m / (v.sqrt() + eps))
+    p.copy_(pf)
+    if p16_out is not None:
+        p16_out.copy_(pf)

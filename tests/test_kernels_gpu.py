@@ -1,0 +1,261 @@
+"""Numerics of every sm_100a kernel against a plain PyTorch fp32 restatement of the same op.
+
+The reference repository has no kernel-level tests for its vendored CUDA; these
+fill that gap.  Inputs are 16-bit, the oracle accumulates in fp32 from the same
+16-bit values, and outputs are compared after rounding to the output dtype.
+"""
+import math
+
+import pytest
+import torch
+
+from metaseq_b200.ops import functional as F
+from metaseq_b200.ops import _lib
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float16, torch.bfloat16]
+
+
+def _tol(dtype):
+    return (2e-2, 2e-2) if dtype == torch.bfloat16 else (4e-3, 4e-3)
+
+
+def _close(got, want, dtype, scale=1.0):
+    rtol, atol = _tol(dtype)
+    torch.testing.assert_close(got.float(), want.float(), rtol=rtol, atol=atol * scale)
+
+
+def _ref(fn, *args, **kw):
+    prev = F.get_backend()
+    F.set_backend("torch")
+    try:
+        return fn(*args, **kw)
+    finally:
+        F.set_backend(prev)
+
+
+def _status_ok():
+    assert _lib.check_status("cuda") == 0, "a kernel reported a timed-out wait"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (200, 264, 136), (1024, 2048, 512), (384, 96, 1024)])
+def test_gemm_layouts(dtype, a_mn, b_mn, M, N, K):
+    torch.manual_seed(0)
+    if a_mn and M % 8:
+        pytest.skip("MN-major A needs M % 8 == 0")
+    a = torch.randn((K, M) if a_mn else (M, K), device="cuda", dtype=dtype)
+    b = torch.randn((K, N) if b_mn else (N, K), device="cuda", dtype=dtype)
+    got = F.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    am = a.t() if a_mn else a
+    bm = b if b_mn else b.t()
+    want = am.float() @ bm.float()
+    _status_ok()
+    _close(got, want.to(dtype), dtype, scale=math.sqrt(K))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("bn", [128, 256])
+def test_gemm_epilogue(dtype, bn):
+    torch.manual_seed(1)
+    M, N, K = 520, 776, 320
+    a = torch.randn(M, K, device="cuda", dtype=dtype)
+    w = torch.randn(N, K, device="cuda", dtype=dtype) * 0.05
+    bias = torch.randn(N, device="cuda", dtype=dtype)
+    res = torch.randn(M, N, device="cuda", dtype=dtype)
+    mask = torch.randn(M, N, device="cuda", dtype=dtype)
+    base = a.float() @ w.float().t()
+    # bias + relu
+    got = F.gemm(a, w, bias=bias, relu=True, bn=bn)
+    _close(got, torch.relu(base + bias.float()).to(dtype), dtype)
+    # bias + residual
+    got = F.gemm(a, w, bias=bias, residual=res, bn=bn)
+    _close(got, (base + bias.float() + res.float()).to(dtype), dtype)
+    # mask (ReLU backward) and accumulate into an existing output
+    prev = torch.randn(M, N, device="cuda", dtype=dtype)
+    out = prev.clone()
+    F.gemm(a, w, mask=mask, out=out, accumulate=True, bn=bn)
+    _close(out, (base * (mask > 0) + prev.float()).to(dtype), dtype)
+    _status_ok()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_gemm_strided_views(dtype):
+    torch.manual_seed(2)
+    M, K, N = 256, 128, 192
+    big = torch.randn(M, 3 * K, device="cuda", dtype=dtype)
+    a = big[:, K:2 * K]
+    w = torch.randn(N, K, device="cuda", dtype=dtype)
+    outbig = torch.zeros(M, 2 * N, device="cuda", dtype=dtype)
+    F.gemm(a, w, out=outbig[:, N:])
+    _close(outbig[:, N:], (a.float() @ w.float().t()).to(dtype), dtype, scale=math.sqrt(K))
+    assert float(outbig[:, :N].abs().max()) == 0.0
+    _status_ok()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("D", [64, 2048, 4096, 7168])
+@pytest.mark.parametrize("affine", [True, False])
+def test_layernorm(dtype, D, affine):
+    torch.manual_seed(3)
+    rows = 777
+    x = (torch.randn(rows, D, device="cuda") * 2 + 0.5).to(dtype)
+    g = (torch.randn(D, device="cuda") * 0.2 + 1).to(dtype) if affine else None
+    b = (torch.randn(D, device="cuda") * 0.2).to(dtype) if affine else None
+    y, mean, rstd = F.layer_norm_fwd(x, g, b, 1e-5)
+    yr, meanr, rstdr = _ref(F.layer_norm_fwd, x, g, b, 1e-5)
+    _close(y, yr, dtype)
+    torch.testing.assert_close(mean, meanr, rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(rstd, rstdr, rtol=1e-4, atol=1e-4)
+    dy = torch.randn(rows, D, device="cuda").to(dtype)
+    add = torch.randn(rows, D, device="cuda").to(dtype)
+    dx, dg, db = F.layer_norm_bwd(dy, x, mean, rstd, g, add=add)
+    dxr, dgr, dbr = _ref(F.layer_norm_bwd, dy, x, mean, rstd, g, add=add)
+    _close(dx, dxr, dtype)
+    if affine:
+        _close(dg, dgr, dtype, scale=math.sqrt(rows))
+        _close(db, dbr, dtype, scale=math.sqrt(rows))
+
+
+def _attn_inputs(B, T, H, d, dtype):
+    qkv = (torch.randn(B, T, 3 * H * d, device="cuda") * 0.7).to(dtype)
+    D = H * d
+    k = qkv[..., 0:D].view(B, T, H, d)
+    v = qkv[..., D:2 * D].view(B, T, H, d)
+    q = qkv[..., 2 * D:].view(B, T, H, d)
+    return qkv, q, k, v
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("T", [128, 256, 200, 640])
+def test_flash_attention_forward(dtype, d, T):
+    torch.manual_seed(4)
+    B, H = 2, 3
+    _, q, k, v = _attn_inputs(B, T, H, d, dtype)
+    scale = d ** -0.5
+    out, lse = F.flash_attn_fwd(q, k, v, scale, True)
+    outr, lser = _ref(F.flash_attn_fwd, q, k, v, scale, True)
+    _status_ok()
+    _close(out, outr, dtype)
+    torch.testing.assert_close(lse, lser, rtol=2e-3, atol=2e-3)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("T", [128, 384, 200])
+def test_flash_attention_backward(dtype, d, T):
+    torch.manual_seed(5)
+    B, H = 2, 2
+    qkv, q, k, v = _attn_inputs(B, T, H, d, dtype)
+    D = H * d
+    scale = d ** -0.5
+    out, lse = _ref(F.flash_attn_fwd, q, k, v, scale, True)
+    d_out = (torch.randn(B, T, D, device="cuda") * 0.5).to(dtype)
+
+    def run(use_ref):
+        dqkv = torch.zeros_like(qkv)
+        dk = dqkv[..., 0:D].view(B, T, H, d)
+        dv = dqkv[..., D:2 * D].view(B, T, H, d)
+        dq = dqkv[..., 2 * D:].view(B, T, H, d)
+        if use_ref:
+            _ref(F.flash_attn_bwd, q, k, v, out, d_out, lse, scale, True, dq, dk, dv)
+        else:
+            F.flash_attn_bwd(q, k, v, out, d_out, lse, scale, True, dq, dk, dv)
+        return dqkv
+
+    got, want = run(False), run(True)
+    _status_ok()
+    _close(got, want, dtype, scale=4.0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_cross_entropy(dtype):
+    torch.manual_seed(6)
+    rows, V = 300, 50272
+    logits = (torch.randn(rows, V, device="cuda") * 3).to(dtype)
+    target = torch.randint(0, V, (rows,), device="cuda")
+    target[::7] = 1  # ignored (pad)
+    l1 = logits.clone()
+    loss, lse = F.cross_entropy_fwd_bwd(l1, target, 1, 128.0, True)
+    l2 = logits.clone()
+    lossr, lser = _ref(F.cross_entropy_fwd_bwd, l2, target, 1, 128.0, True)
+    torch.testing.assert_close(loss, lossr, rtol=1e-3, atol=1e-3)
+    torch.testing.assert_close(lse, lser, rtol=1e-3, atol=1e-3)
+    _close(l1, l2, dtype, scale=2.0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding(dtype):
+    torch.manual_seed(7)
+    V, P, D, B, T = 1000, 70, 256, 3, 50
+    tok_w = torch.randn(V, D, device="cuda").to(dtype)
+    pos_w = torch.randn(P, D, device="cuda").to(dtype)
+    tokens = torch.randint(0, V, (B, T), device="cuda")
+    tokens[0, -5:] = 1
+    positions = torch.randint(2, P, (B, T), device="cuda")
+    positions[0, -5:] = 1
+    out = F.embed_fwd(tokens, positions, tok_w, pos_w, 1.0)
+    outr = _ref(F.embed_fwd, tokens, positions, tok_w, pos_w, 1.0)
+    _close(out, outr, dtype)
+    # vocab-parallel partition
+    out = F.embed_fwd(tokens, positions, tok_w[500:], pos_w, 1.0, vocab_start=500, add_positions=False)
+    outr = _ref(F.embed_fwd, tokens, positions, tok_w[500:], pos_w, 1.0, vocab_start=500, add_positions=False)
+    _close(out, outr, dtype)
+    dy = torch.randn(B, T, D, device="cuda").to(dtype)
+    dt, dp = F.embed_bwd(tokens, positions, dy, V, P, 1.0, 1)
+    dtr, dpr = _ref(F.embed_bwd, tokens, positions, dy, V, P, 1.0, 1)
+    torch.testing.assert_close(dt, dtr, rtol=1e-3, atol=1e-3)
+    torch.testing.assert_close(dp, dpr, rtol=1e-3, atol=1e-3)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_colsum_and_fold(dtype):
+    torch.manual_seed(8)
+    x = torch.randn(3001, 776, device="cuda").to(dtype)
+    got = F.colsum(x)
+    _close(got, x.float().sum(0).to(dtype), dtype, scale=60.0)
+    dst = torch.randn(776, device="cuda").to(dtype)
+    want = (dst.float() + x.float().sum(0)).to(dtype)
+    F.colsum(x, out16=dst, accumulate=True)
+    _close(dst, want, dtype, scale=60.0)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+def test_sumsq_clip_adamw(dtype):
+    torch.manual_seed(9)
+    n = 1_000_003
+    g = (torch.randn(n, device="cuda") * 3).to(dtype)
+    acc = torch.zeros(2, dtype=torch.float32, device="cuda")
+    F.sumsq(g, acc[0:1], False)
+    F.sumsq(g[: n // 2], acc[1:2], False)
+    want0 = g.float().pow(2).sum()
+    torch.testing.assert_close(acc[0], want0, rtol=1e-4, atol=1e-2)
+    ctrl = torch.zeros(4, dtype=torch.float32, device="cuda")
+    F.clip_decision(acc, 1.0 / 128, 1.0, ctrl)
+    norm = (acc.sum().sqrt() / 128).item()
+    assert abs(ctrl[2].item() - norm) / norm < 1e-4
+    assert ctrl[1].item() == 0.0
+    assert abs(ctrl[0].item() - (1 / 128) * min(1.0, 1.0 / (norm + 1e-6))) < 1e-6
+    # AdamW against the PyTorch restatement
+    pdt = dtype
+    p = torch.randn(n, device="cuda").to(pdt)
+    m = torch.zeros(n, device="cuda")
+    v = torch.zeros(n, device="cuda")
+    p2, m2, v2 = p.clone(), m.clone(), v.clone()
+    kw = dict(lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1)
+    for step in (1, 2):
+        F.adamw_step(p, g, m, v, step=step, ctrl=ctrl, **kw)
+        _ref(F.adamw_step, p2, g, m2, v2, step=step, ctrl=ctrl, **kw)
+    torch.testing.assert_close(m, m2, rtol=1e-4, atol=1e-6)
+    torch.testing.assert_close(v, v2, rtol=1e-4, atol=1e-8)
+    torch.testing.assert_close(p.float(), p2.float(), rtol=1e-2 if pdt != torch.float32 else 1e-4, atol=1e-2 if pdt != torch.float32 else 1e-5)
+    # overflow: non-finite norm sets the skip flag and the step leaves everything untouched
+    acc[0] = float("inf")
+    F.clip_decision(acc, 1.0, 1.0, ctrl)
+    assert ctrl[1].item() == 1.0
+    before = p.clone()
+    F.adamw_step(p, g, m, v, step=3, ctrl=ctrl, **kw)
+    assert torch.equal(before, p)
