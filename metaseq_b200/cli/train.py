@@ -1,0 +1,365 @@
+"""``metaseq-train``: train a model on one or more GPUs.
+
+Flow (reference: metaseq/cli/train.py:54-224 main, :238-411 train, :427-505
+validate_and_save, :535-645 post-checkpoint callback, :743-830 validate): parse flags ->
+nested config -> one process per GPU -> build task, model (FSDP-wrapped when
+``--ddp-backend fully_sharded``), criterion, Trainer -> restore the latest checkpoint ->
+loop over epochs / updates with periodic validation and checkpointing.
+"""
+from __future__ import annotations
+
+import functools
+import logging
+import math
+import os
+import re
+import shutil
+import socket
+import subprocess
+import sys
+import time
+from typing import Any, Dict, List, Optional, Tuple
+
+import numpy as np
+import torch
+
+from metaseq_b200 import checkpoint_utils, options, tasks, utils
+from metaseq_b200.data import iterators
+from metaseq_b200.dataclass.utils import Cfg, convert_namespace_to_config
+from metaseq_b200.file_io import PathManager
+from metaseq_b200.logging import meters, metrics, progress_bar
+from metaseq_b200.ops import functional as ops_f
+from metaseq_b200.parallel import utils as dist_utils
+from metaseq_b200.parallel.fsdp import FullyShardedDataParallel, fsdp_enable_wrap, fsdp_wrap
+from metaseq_b200.trainer import Trainer
+
+logging.basicConfig(format="%(asctime)s | %(levelname)s | %(name)s | %(message)s", datefmt="%Y-%m-%d %H:%M:%S",
+                    level=os.environ.get("LOGLEVEL", "INFO").upper(), stream=sys.stdout)
+logging.Formatter.converter = time.gmtime  # UTC timestamps
+logger = logging.getLogger("metaseq_b200.cli.train")
+
+
+def main(cfg: Cfg) -> None:
+    utils_import_user_module(cfg.common)
+    ops_f.set_backend(getattr(cfg.common, "kernel_backend", "auto") or "auto")
+    if dist_utils.is_master(cfg.distributed_training) and "job_logging_cfg" in cfg:
+        pass
+    assert cfg.dataset.max_tokens is not None or cfg.dataset.batch_size is not None, \
+        "Must specify batch size either with --max-tokens or --batch-size"
+    metrics.reset()
+    if cfg.common.log_file is not None:
+        handler = logging.FileHandler(filename=cfg.common.log_file)
+        logger.addHandler(handler)
+    np.random.seed(cfg.common.seed)
+    utils.set_torch_seed(cfg.common.seed)
+    checkpoint_utils.verify_checkpoint_directory(cfg.checkpoint.save_dir)
+    if dist_utils.is_master(cfg.distributed_training):
+        logger.info(cfg.to_container() if isinstance(cfg, Cfg) else cfg)
+    task = tasks.setup_task(cfg.task)
+    model, criterion = build_model_and_criterion(cfg, task)
+    n_params = sum(p.numel() for p in model.parameters())
+    logger.info(f"task: {task.__class__.__name__}; model: {model.__class__.__name__}; "
+                f"criterion: {criterion.__class__.__name__}; local params: {n_params:,}")
+    for valid_sub_split in cfg.dataset.valid_subset.split(","):
+        if valid_sub_split and not cfg.dataset.disable_validation:
+            task.load_dataset(valid_sub_split, combine=False, epoch=1)
+    trainer = Trainer(cfg, task, model, criterion)
+    logger.info(f"training on {cfg.distributed_training.distributed_world_size} devices (GPUs/TPUs); "
+                f"max tokens per GPU = {cfg.dataset.max_tokens} and batch size per GPU = {cfg.dataset.batch_size}")
+    extra_state, epoch_itr = checkpoint_utils.load_checkpoint(cfg, trainer, disable_iterator_cache=True)
+    max_epoch = cfg.optimization.max_epoch or math.inf
+    train_meter = meters.StopwatchMeter()
+    train_meter.start()
+    while epoch_itr.next_epoch_idx <= max_epoch:
+        valid_losses, should_stop = train(cfg, trainer, task, epoch_itr)
+        if should_stop:
+            break
+        trainer.lr_step(epoch_itr.epoch, valid_losses[0] if valid_losses else None)
+        epoch_itr = trainer.get_train_iterator(epoch_itr.next_epoch_idx, load_dataset=True,
+                                               disable_iterator_cache=True)
+    train_meter.stop()
+    checkpoint_utils.wait_for_pending_writes()
+    logger.info("done training in {:.1f} seconds".format(train_meter.sum))
+
+
+def build_model_and_criterion(cfg, task):
+    """Model wrapped per the data-parallel backend, and the criterion."""
+    if cfg.distributed_training.ddp_backend == "fully_sharded":
+        extra = {"use_sharded_state": cfg.distributed_training.use_sharded_state}
+        with fsdp_enable_wrap(cfg.distributed_training, **extra):
+            model = fsdp_wrap(task.build_model(cfg.model), process_group=dist_utils.get_data_parallel_group())
+    else:
+        model = task.build_model(cfg.model)
+    criterion = task.build_criterion(cfg.criterion)
+    return model, criterion
+
+
+def utils_import_user_module(common):
+    if getattr(common, "user_dir", None):
+        options._import_user_module(common)
+
+
+def get_skip_batches(to_skip: str) -> Optional[Dict[int, int]]:
+    """``"100-200,150-250"`` -> {start update: number of batches to skip}."""
+    if not to_skip:
+        return None
+    out = {}
+    for rng in to_skip.split(","):
+        lo, hi = (int(x) for x in rng.split("-"))
+        out[lo] = hi - lo + 1
+    return out
+
+
+@metrics.aggregate("train")
+def train(cfg, trainer: Trainer, task, epoch_itr) -> Tuple[List[Optional[float]], bool]:
+    """One epoch (or until ``max_update``)."""
+    itr = epoch_itr.next_epoch_itr(fix_batches_to_gpus=cfg.distributed_training.fix_batches_to_gpus, shuffle=True)
+    update_freq = cfg.optimization.update_freq[epoch_itr.epoch - 1] \
+        if epoch_itr.epoch <= len(cfg.optimization.update_freq) else cfg.optimization.update_freq[-1]
+    if isinstance(epoch_itr, iterators.StreamingEpochBatchIterator):
+        assert update_freq == 1, "the streaming iterator yields one batch per update (--update-freq 1)"
+        grouped = False
+    else:
+        itr = iterators.GroupedIterator(itr, update_freq, skip_remainder_batch=True)
+        grouped = True
+    progress = progress_bar.get_progress_bar(
+        itr, log_format=cfg.common.log_format, log_file=None, log_interval=cfg.common.log_interval,
+        epoch=epoch_itr.epoch,
+        tensorboard_logdir=cfg.common.tensorboard_logdir if dist_utils.is_master(cfg.distributed_training) else None,
+        wandb_project=cfg.common.wandb_project if dist_utils.is_master(cfg.distributed_training) else None,
+        wandb_run_name=os.environ.get("WANDB_NAME", os.path.basename(cfg.checkpoint.save_dir)),
+        aim_repo=cfg.common.aim_repo if dist_utils.is_master(cfg.distributed_training) else None,
+        aim_run_hash=cfg.common.aim_run_hash if dist_utils.is_master(cfg.distributed_training) else None)
+    progress.update_config(_flatten_config(cfg))
+    trainer.begin_epoch(epoch_itr.epoch)
+    valid_subsets = cfg.dataset.valid_subset.split(",")
+    should_stop = False
+    valid_losses = [None]
+    skip_batches = get_skip_batches(cfg.dataset.skip_batches)
+    to_skip = 0
+
+    def train_one(i, samples):
+        with metrics.aggregate("train_inner"):
+            if getattr(cfg.common, "profile", False) and trainer.get_num_updates() == 5 and \
+                    dist_utils.get_global_rank() == 0:
+                return _profiled_step(cfg, trainer, samples)
+            return trainer.train_step(samples)
+
+    progress_iter = iter(progress)
+    i = 0
+    while True:
+        metrics.log_start_time("time_sample_fetch", priority=900, round=4)
+        try:
+            samples = next(progress_iter)
+        except StopIteration:
+            break
+        metrics.log_stop_time("time_sample_fetch")
+        if not grouped:
+            samples = [samples]
+        if skip_batches is not None and trainer.get_num_updates() in skip_batches and to_skip == 0:
+            to_skip = skip_batches.pop(trainer.get_num_updates())
+        if to_skip > 0:
+            to_skip -= 1
+            logger.info(f"Skipping batch at update {trainer.get_num_updates()} ({to_skip} more to skip)")
+            continue
+        log_output = train_one(i, samples)
+        if log_output is not None:
+            num_updates = trainer.get_num_updates()
+            if num_updates % cfg.common.log_interval == 0:
+                stats = get_training_stats(metrics.get_smoothed_values("train_inner"))
+                progress.log(stats, tag="train_inner", step=num_updates)
+                metrics.reset_meters("train_inner")
+        end_of_epoch = not itr.has_next() if hasattr(itr, "has_next") else False
+        valid_losses, should_stop = validate_and_save(cfg, trainer, task, epoch_itr, valid_subsets, end_of_epoch,
+                                                      log_output is not None)
+        i += 1
+        if should_stop:
+            break
+    logger.info("end of epoch {} (average epoch stats below)".format(epoch_itr.epoch))
+    stats = get_training_stats(metrics.get_smoothed_values("train"))
+    progress.print(stats, tag="train", step=trainer.get_num_updates())
+    metrics.reset_meters("train")
+    return valid_losses, should_stop
+
+
+def _profiled_step(cfg, trainer, samples):
+    """Wraps one update in the torch profiler and writes a memory table and a chrome trace."""
+    from torch.profiler import ProfilerActivity, profile
+
+    acts = [ProfilerActivity.CPU] + ([ProfilerActivity.CUDA] if torch.cuda.is_available() else [])
+    with profile(activities=acts, profile_memory=True, with_stack=True, record_shapes=True) as prof:
+        out = trainer.train_step(samples)
+    sort_key = "self_cuda_memory_usage" if torch.cuda.is_available() else "self_cpu_memory_usage"
+    with open(os.path.join(cfg.checkpoint.save_dir, "memory_usage.txt"), "w") as f:
+        f.write(prof.key_averages(group_by_stack_n=5).table(sort_by=sort_key, row_limit=10))
+    prof.export_chrome_trace(os.path.join(cfg.checkpoint.save_dir, "profiler_trace.json"))
+    return out
+
+
+def _flatten_config(cfg):
+    out = {}
+    for k, v in (cfg.items() if hasattr(cfg, "items") else []):
+        if hasattr(v, "items"):
+            for kk, vv in v.items():
+                out[f"{k}.{kk}"] = vv
+        else:
+            out[k] = str(v)
+    return out
+
+
+def validate_and_save(cfg, trainer: Trainer, task, epoch_itr, valid_subsets: List[str], end_of_epoch: bool,
+                      was_successful_step: bool) -> Tuple[List[Optional[float]], bool]:
+    num_updates = trainer.get_num_updates()
+    max_update = cfg.optimization.max_update or math.inf
+    should_stop = False
+    if num_updates >= max_update:
+        should_stop = True
+        logger.info(f"Stopping training due to num_updates: {num_updates} >= max_update: {max_update}")
+    save_locally = cfg.checkpoint.local_save_interval_updates > 0 and num_updates > 0 and \
+        num_updates % cfg.checkpoint.local_save_interval_updates == 0
+    save_to_nfs = cfg.checkpoint.save_interval_updates > 0 and num_updates > 0 and \
+        num_updates % cfg.checkpoint.save_interval_updates == 0
+    do_save = (end_of_epoch and cfg.checkpoint.save_interval_epochs > 0
+               and epoch_itr.epoch % cfg.checkpoint.save_interval_epochs == 0) or \
+              ((save_locally or save_to_nfs) and num_updates >= cfg.dataset.validate_after_updates
+               and was_successful_step) or should_stop
+    do_validate = (should_stop or (cfg.dataset.validate_interval_updates > 0 and num_updates > 0
+                                   and num_updates % cfg.dataset.validate_interval_updates == 0
+                                   and was_successful_step)) and not cfg.dataset.disable_validation \
+        and num_updates >= cfg.dataset.validate_after_updates
+    # save first: a crash during validation must not lose the checkpoint
+    if do_save:
+        checkpoint_utils.save_checkpoint(
+            cfg, trainer, epoch_itr, training_finished=should_stop,
+            async_callback_fn=functools.partial(post_checkpoint_callback, cfg, num_updates, should_stop)
+            if cfg.checkpoint.cloud_upload_path else None)
+    valid_losses = [None]
+    if do_validate:
+        valid_losses = validate(cfg, trainer, task, epoch_itr, valid_subsets)
+    trainer.reset_dummy_batch(epoch_itr.first_batch)
+    return valid_losses, should_stop
+
+
+def post_checkpoint_callback(cfg, num_updates, training_finished, filename, files_to_symlink_to):
+    """Runs on the writer thread after a checkpoint file is complete: upload to blob storage
+    with azcopy, copy to an ``nfs:`` directory through a temporary name (atomic rename, so a
+    reader never sees a partial checkpoint), or generic copy; then recreate the symlinks."""
+    upload = cfg.checkpoint.cloud_upload_path
+    if upload is not None:
+        if "blob.core.windows.net" in upload:
+            azcopy_logs = filename + "_azcopy_logs"
+            os.environ["AZCOPY_CONCURRENCY_VALUE"] = "10"
+            os.environ["AZCOPY_LOG_LOCATION"] = azcopy_logs
+            os.makedirs(azcopy_logs, exist_ok=True)
+            logger.info(f"preparing to azcopy {filename} to {upload}; logs in {azcopy_logs}")
+            cmd = ["azcopy", "copy", "--cap-mbps", "96.0", filename, upload]
+            res = _run_azcopy(cmd, stdout=subprocess.PIPE)
+            if res.returncode != 0:
+                print("Error: {}, azcopy failed".format(res.returncode))
+                print("Azcopy stdout = {}".format(res.stdout))
+                sys.exit(1)
+            logger.info(f"Successfully copied {filename} to {upload}")
+            if os.path.exists(filename):
+                os.remove(filename)
+        elif upload.startswith("nfs:"):
+            path, basename = os.path.split(filename)
+            checkpoint_dir = os.path.join(upload[4:], f"checkpoint_{num_updates}")
+            os.makedirs(checkpoint_dir, exist_ok=True)
+            tmp_name = os.path.join(checkpoint_dir, "_" + basename + ".tmp")
+            shutil.copyfile(filename, tmp_name)
+            os.replace(tmp_name, os.path.join(checkpoint_dir, basename))
+            logger.info(f"Successfully copied {filename} to {checkpoint_dir}")
+            if cfg.checkpoint.nfs_eval_script_path and dist_utils.get_global_rank() == 0 and \
+                    num_updates % max(1, cfg.checkpoint.nfs_eval_frequency) == 0:
+                _run_nfs_eval(cfg, checkpoint_dir)
+            if os.path.exists(filename):
+                os.remove(filename)
+        else:
+            try:
+                PathManager.copy_from_local(filename, os.path.join(upload, os.path.basename(filename)), overwrite=True)
+                if os.path.exists(filename):
+                    os.remove(filename)
+            except (FileNotFoundError, AssertionError) as e:
+                logger.info(f"could not upload {filename}: {e}")
+    elif files_to_symlink_to:
+        for other in files_to_symlink_to:
+            if os.path.lexists(other):
+                os.remove(other)
+            os.symlink(os.path.basename(filename), other)
+
+
+def _run_nfs_eval(cfg, checkpoint_dir):
+    for attempt in range(max(1, cfg.checkpoint.nfs_eval_num_attempts)):
+        n_files = len([f for f in os.listdir(checkpoint_dir) if f.endswith(".pt")])
+        if n_files >= cfg.distributed_training.distributed_world_size:
+            subprocess.Popen(["bash", cfg.checkpoint.nfs_eval_script_path, checkpoint_dir])
+            return
+        time.sleep(60 * cfg.checkpoint.nfs_eval_attempt_wait_minutes)
+
+
+def _run_azcopy(cmd, stdout):
+    return subprocess.run(cmd, stdout=stdout)
+
+
+def get_training_stats(stats: Dict[str, Any]) -> Dict[str, Any]:
+    stats["wall"] = round(metrics.get_meter("default", "wall").elapsed_time, 0)
+    return stats
+
+
+def validate(cfg, trainer: Trainer, task, epoch_itr, subsets: List[str]) -> List[Optional[float]]:
+    if cfg.dataset.fixed_validation_seed is not None:
+        utils.set_torch_seed(cfg.dataset.fixed_validation_seed)
+    trainer.begin_valid_epoch(epoch_itr.epoch)
+    valid_losses = []
+    with metrics.aggregate(new_root=True) as combined_agg:
+        for subset in subsets:
+            logger.info(f'begin validation on "{subset}" subset on rank {dist_utils.get_global_rank()}')
+            itr = trainer.get_valid_iterator(subset).next_epoch_itr(shuffle=False, set_dataset_epoch=False)
+            progress = progress_bar.get_progress_bar(
+                itr, log_format=cfg.common.log_format, log_interval=cfg.common.log_interval, epoch=epoch_itr.epoch,
+                prefix=f"valid on '{subset}' subset",
+                tensorboard_logdir=cfg.common.tensorboard_logdir if dist_utils.is_master(cfg.distributed_training) else None,
+                wandb_project=cfg.common.wandb_project if dist_utils.is_master(cfg.distributed_training) else None)
+            with metrics.aggregate(new_root=True) as agg:
+                for i, sample in enumerate(progress):
+                    if cfg.dataset.max_valid_steps is not None and i > cfg.dataset.max_valid_steps:
+                        break
+                    trainer.valid_step(sample, num_step=i)
+            stats = get_valid_stats(cfg, trainer, subset, agg.get_smoothed_values())
+            progress.print(stats, tag=subset, step=trainer.get_num_updates())
+            valid_losses.append(stats.get("loss"))
+    stats = get_valid_stats(cfg, trainer, "combined", combined_agg.get_smoothed_values())
+    return valid_losses
+
+
+def get_valid_stats(cfg, trainer: Trainer, subset: str, stats: Dict[str, Any]) -> Dict[str, Any]:
+    stats["num_updates"] = trainer.get_num_updates()
+    return stats
+
+
+def set_local_per_worker_env_variables(cfg=None):
+    """Per-rank NCCL debug file and an environment dump next to the checkpoints (only when
+    ``METASEQ_SAVE_DIR`` is set, as the launcher does)."""
+    save_dir = os.environ.get("METASEQ_SAVE_DIR")
+    if not save_dir:
+        return
+    os.makedirs(os.path.join(save_dir, "envs"), exist_ok=True)
+    host = socket.gethostname()
+    restart = os.environ.get("SLURM_RESTART_COUNT", "0")
+    rank = os.environ.get("SLURM_PROCID", os.environ.get("RANK", "0"))
+    os.environ.setdefault("NCCL_DEBUG_FILE", os.path.join(save_dir, f"nccl.{restart}.{host}.{rank}.%p.log"))
+    with open(os.path.join(save_dir, "envs", f"env.{restart}.{host}.{rank}.txt"), "w") as f:
+        for k, v in sorted(os.environ.items()):
+            f.write(f"{k}={v}\n")
+
+
+def cli_main(modify_parser=None, input_args=None) -> None:
+    set_local_per_worker_env_variables()
+    parser = options.get_training_parser()
+    args = options.parse_args_and_arch(parser, input_args=input_args, modify_parser=modify_parser)
+    cfg = convert_namespace_to_config(args)
+    dist_utils.call_main(cfg, main)
+
+
+if __name__ == "__main__":
+    cli_main()

@@ -1,0 +1,64 @@
+"""Cross entropy on vocabulary-sharded logits: the model keeps ``[B, T, V/p]`` on each
+tensor-parallel rank and the loss is assembled with reductions over the group (reference:
+metaseq/criterions/vocab_parallel_cross_entropy.py:15-110).  Sample size is the number of
+non-pad target tokens."""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+from metaseq_b200.dataclass.configs import MetaseqDataclass
+from metaseq_b200.logging import metrics
+from metaseq_b200.parallel import mpu
+from metaseq_b200.parallel.cross_entropy import vocab_parallel_cross_entropy
+
+from . import register_criterion
+from .base_criterion import BaseCriterion
+from .cross_entropy import _ppl, nll_loss_sum
+
+
+@dataclass
+class VocabParallelCrossEntropyConfig(MetaseqDataclass):
+    pass
+
+
+@register_criterion("vocab_parallel_cross_entropy", dataclass=VocabParallelCrossEntropyConfig)
+class VocabParallelCrossEntropyCriterion(BaseCriterion):
+    def __init__(self, task):
+        super().__init__(task)
+
+    def forward(self, model, sample, reduce=True):
+        target = sample["target"]
+        # Non-pad target count comes from the collater (computed on the host before the batch is
+        # copied to the device), so no device-to-host sync is needed here.
+        has_pad = True
+        net_output = model(**sample["net_input"])
+        logits = net_output[0]
+        if mpu.get_tensor_model_parallel_world_size() == 1:
+            loss = nll_loss_sum(logits.reshape(-1, logits.size(-1)), target.reshape(-1), self.padding_idx)
+        else:
+            per_tok = vocab_parallel_cross_entropy(logits.float(), target)
+            if has_pad:
+                per_tok = per_tok * (target != self.padding_idx)
+            loss = per_tok.sum()
+        ntok_target = sample.get("ntokens_target", sample["ntokens"])
+        logging_output = {
+            "loss": loss.data,
+            "ntokens": sample["ntokens"],
+            "nsentences": target.size(0),
+            "sample_size": ntok_target,
+        }
+        return loss, ntok_target, logging_output
+
+    @staticmethod
+    def reduce_metrics(logging_outputs) -> None:
+        loss_sum = sum(float(log.get("loss", 0)) for log in logging_outputs)
+        sample_size = sum(float(log.get("sample_size", 0)) for log in logging_outputs)
+        metrics.log_scalar("loss", loss_sum / max(sample_size, 1) / math.log(2), sample_size, round=3)
+        metrics.log_derived("ppl", lambda meters: _ppl(meters["loss"].avg))
+
+    @staticmethod
+    def logging_outputs_can_be_summed() -> bool:
+        return True

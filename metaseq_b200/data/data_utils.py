@@ -1,0 +1,151 @@
+"""Batching helpers.  The inner loops of ``batch_by_size`` run in the host C++ library when
+it is built (``csrc/host/batching.cpp``) and in numpy/python otherwise; both produce the same
+batches (reference: metaseq/data/data_utils.py:203-257 and data_utils_fast.pyx:20-178)."""
+from __future__ import annotations
+
+import contextlib
+import ctypes
+import itertools
+import logging
+import os
+from typing import List, Optional
+
+import numpy as np
+import torch
+
+logger = logging.getLogger(__name__)
+
+
+def collate_tokens(values, pad_idx, eos_idx=None, left_pad=False, move_eos_to_beginning=False, pad_to_length=None,
+                   pad_to_multiple=1, pad_to_bsz=None):
+    """1-D tensors -> padded 2-D tensor."""
+    size = max(v.size(0) for v in values)
+    size = size if pad_to_length is None else max(size, pad_to_length)
+    if pad_to_multiple != 1 and size % pad_to_multiple != 0:
+        size = int(((size - 0.1) // pad_to_multiple + 1) * pad_to_multiple)
+    batch = len(values) if pad_to_bsz is None else max(len(values), pad_to_bsz)
+    res = values[0].new(batch, size).fill_(pad_idx)
+    for i, v in enumerate(values):
+        dst = res[i][size - len(v):] if left_pad else res[i][: len(v)]
+        if move_eos_to_beginning:
+            if eos_idx is None:
+                dst[0] = v[-1]
+            else:
+                dst[0] = eos_idx
+            dst[1:] = v[:-1]
+        else:
+            dst.copy_(v)
+    return res
+
+
+def _filter_by_size_dynamic(indices, size_fn, max_positions, raise_exception=False):
+    def ok(idx):
+        s = size_fn(idx)
+        if isinstance(max_positions, (float, int)):
+            return s <= max_positions
+        if isinstance(s, (tuple, list)) and isinstance(max_positions, (tuple, list)):
+            return all(a is None or b is None or a <= b for a, b in zip(s, max_positions))
+        return all(a <= max_positions[0] for a in (s if isinstance(s, (tuple, list)) else [s]))
+
+    ignored = []
+    kept = []
+    for i in indices:
+        (kept if ok(i) else ignored).append(i)
+    return np.asarray(kept, dtype=np.int64), ignored
+
+
+def batch_fixed(indices, bsz):
+    for i in range(0, len(indices), bsz):
+        yield list(indices[i:i + bsz])
+
+
+def _host_lib():
+    from metaseq_b200.ops import _lib
+
+    return _lib.host()
+
+
+def batch_by_size_py(indices, num_tokens_vec, max_tokens, max_sentences, bsz_mult):
+    """Greedy batching in index order.  A batch is closed when adding the next sample would
+    exceed ``max_sentences`` rows or ``rows * longest > max_tokens``; the closed batch is cut to
+    the largest multiple of ``bsz_mult`` (or kept whole when shorter than one multiple) and
+    the remainder starts the next batch."""
+    batches = []
+    batch: List[int] = []
+    lens: List[int] = []
+    longest = 0
+    for k, idx in enumerate(indices):
+        n = int(num_tokens_vec[k])
+        lens.append(n)
+        longest = max(longest, n)
+        rows = len(batch)
+        full = rows > 0 and ((max_sentences > 0 and rows == max_sentences) or
+                             (max_tokens > 0 and (rows + 1) * longest > max_tokens))
+        if full:
+            cut = max(bsz_mult * (rows // bsz_mult), rows % bsz_mult)
+            batches.append(batch[:cut])
+            batch = batch[cut:]
+            lens = lens[cut:]
+            longest = max(lens) if lens else 0
+        batch.append(int(idx))
+    if batch:
+        batches.append(batch)
+    return batches
+
+
+def batch_by_size(indices, num_tokens_fn=None, num_tokens_vec=None, max_tokens=None, max_sentences=None,
+                  required_batch_size_multiple=1, fixed_shapes=None):
+    max_tokens = int(max_tokens) if max_tokens is not None else -1
+    max_sentences = int(max_sentences) if max_sentences is not None else -1
+    bsz_mult = int(required_batch_size_multiple)
+    if not isinstance(indices, np.ndarray):
+        indices = np.fromiter(indices, dtype=np.int64, count=-1)
+    indices = indices.astype(np.int64, copy=False)
+    if num_tokens_vec is None:
+        num_tokens_vec = np.fromiter((num_tokens_fn(int(i)) for i in indices), dtype=np.int64, count=len(indices))
+    else:
+        num_tokens_vec = np.asarray(num_tokens_vec, dtype=np.int64)
+    if fixed_shapes is not None:
+        return batch_fixed_shapes(indices, num_tokens_vec, np.asarray(fixed_shapes, dtype=np.int64))
+    lib = _host_lib()
+    if lib is not None and hasattr(lib, "msq_batch_by_size"):
+        n = len(indices)
+        ends = np.zeros(n + 1, dtype=np.int64)
+        fn = lib.msq_batch_by_size
+        fn.restype = ctypes.c_longlong
+        nb = fn(num_tokens_vec.ctypes.data_as(ctypes.c_void_p), ctypes.c_longlong(n), ctypes.c_longlong(max_tokens),
+                ctypes.c_longlong(max_sentences), ctypes.c_longlong(bsz_mult), ends.ctypes.data_as(ctypes.c_void_p))
+        out, start = [], 0
+        for b in range(int(nb)):
+            out.append(indices[start:ends[b]].tolist())
+            start = int(ends[b])
+        return out
+    return batch_by_size_py(indices, num_tokens_vec, max_tokens, max_sentences, bsz_mult)
+
+
+def batch_fixed_shapes(indices, num_tokens_vec, fixed_shapes):
+    """``fixed_shapes``: rows of (batch_size, max_len) sorted by max_len; each sample goes to the
+    smallest shape that fits, batches are emitted when a shape's bucket is full."""
+    order = np.argsort(fixed_shapes[:, 1], kind="stable")
+    shapes = fixed_shapes[order]
+    buckets = [[] for _ in shapes]
+    out = []
+    for k, idx in enumerate(indices):
+        n = num_tokens_vec[k]
+        j = int(np.searchsorted(shapes[:, 1], n, side="left"))
+        if j >= len(shapes):
+            continue
+        buckets[j].append(int(idx))
+        if len(buckets[j]) == shapes[j, 0]:
+            out.append(buckets[j])
+            buckets[j] = []
+    out.extend(b for b in buckets if b)
+    return out
+
+
+@contextlib.contextmanager
+def numpy_seed(seed, *addl_seeds):
+    from metaseq_b200.utils import numpy_seed as _ns
+
+    with _ns(seed, *addl_seeds):
+        yield

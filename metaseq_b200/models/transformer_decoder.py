@@ -1,0 +1,222 @@
+"""Decoder stack: vocab-parallel token embedding + learned positions, N pre-LN layers,
+final LayerNorm, tied output projection.
+
+Behavioural contract from the reference (metaseq/models/transformer_decoder.py):
+embedding = ``embed_scale * tok + pos`` with optional dropout (:263-346); under
+sequence parallelism the activations are scattered across the tensor-parallel group
+right after the embedding (:343-345); incremental decoding feeds only the new tokens
+through the layers while positions are computed from the full prefix (:324-327);
+logits stay vocabulary-sharded for the vocab-parallel criterion and are gathered
+otherwise (:398-428); ``--self-attn-doc-sep`` restarts positions after every
+separator token and blocks attention across documents (:270-313, :459-472).
+
+Activations are batch-first ``[B, T, D]`` (sequence-parallel shards are
+``[B*T/p, D]`` row blocks of the flattened tokens), so the final logits need no
+transpose.
+"""
+from __future__ import annotations
+
+import math
+from typing import Any, Dict, List, Optional
+
+import torch
+import torch.nn as nn
+
+from metaseq_b200 import utils
+from metaseq_b200.dataclass.constants import UNSPECIFIED_DOC_SEP
+from metaseq_b200.models.base_decoder import IncrementalDecoder
+from metaseq_b200.modules.dropout import Dropout
+from metaseq_b200.modules.layer_norm import LayerNorm
+from metaseq_b200.modules.learned_positional_embedding import PositionalEmbedding
+from metaseq_b200.modules.multihead_attention import KVCache
+from metaseq_b200.modules.transformer_decoder_layer import ModelParallelTransformerDecoderLayer
+from metaseq_b200.ops import autograd as ops_ag
+from metaseq_b200.ops import functional as ops_f
+from metaseq_b200.parallel import mappings, mpu
+
+
+def _get(args, name, default=None):
+    return getattr(args, name, default)
+
+
+class _TiedProjection(nn.Module):
+    """Holds the (shared) output-projection weight so that ``decoder.output_projection.weight``
+    appears in the state dict next to ``decoder.embed_tokens.weight``."""
+
+    def __init__(self, weight: nn.Parameter):
+        super().__init__()
+        self.weight = weight
+
+
+class ModelParallelTransformerDecoder(IncrementalDecoder):
+    def __init__(self, args, dictionary, embed_tokens):
+        super().__init__(dictionary)
+        self.args = args
+        self.register_buffer("version", torch.Tensor([3]))
+        self.padding_idx = embed_tokens.padding_idx
+        self.embed_dim = args.decoder_embed_dim
+        self.max_target_positions = _get(args, "max_target_positions", None) or _get(args, "tokens_per_sample", 2048)
+        self.embed_tokens = embed_tokens
+        self.embed_scale = 1.0 if _get(args, "no_scale_embedding", False) else math.sqrt(self.embed_dim)
+        self.sequence_parallel = bool(_get(args, "sequence_parallel", False))
+        self.self_attn_doc_sep = _get(args, "self_attn_doc_sep", UNSPECIFIED_DOC_SEP)
+        self.dropout_module = None
+        if not _get(args, "no_emb_dropout", False) and _get(args, "dropout", 0.0) > 0:
+            self.dropout_module = Dropout(args.dropout, module_name=self.__class__.__name__)
+        dtype = embed_tokens.weight.dtype
+        device = embed_tokens.weight.device if embed_tokens.weight.is_cuda else None
+        self.embed_positions = None
+        if _get(args, "decoder_learned_pos", False) and not _get(args, "alibi", False):
+            self.embed_positions = PositionalEmbedding(
+                self.max_target_positions, self.embed_dim, self.padding_idx, learned=True,
+                learned_sinusoidal=_get(args, "decoder_learned_sinusoidal", False),
+                full_megatron_init=_get(args, "full_megatron_init", False),
+                pos_init_scalar=_get(args, "pos_init_scalar", 1.0),
+                megatron_init_sigma=_get(args, "megatron_init_sigma", 0.006),
+                truncate_init=_get(args, "truncate_init", False), dtype=dtype, device=device)
+        self.layers = nn.ModuleList([self.build_decoder_layer(args) for _ in range(args.decoder_layers)])
+        self.num_layers = len(self.layers)
+        self.layer_norm = LayerNorm(self.embed_dim, elementwise_affine=not _get(args, "disable_affine_ln", False))
+        if dtype != torch.float32:
+            self.layer_norm.to(dtype)
+        if device is not None:
+            self.layer_norm.to(device)
+        if _get(args, "share_decoder_input_output_embed", False):
+            self.output_projection = _TiedProjection(self.embed_tokens.weight)
+        else:
+            w = nn.Parameter(torch.empty_like(self.embed_tokens.weight))
+            nn.init.normal_(w, mean=0, std=self.embed_dim ** -0.5)
+            self.output_projection = _TiedProjection(w)
+        self.inference = False
+        self._cache_key = "decoder_state_" + str(id(self))
+
+    def build_decoder_layer(self, args):
+        layer = ModelParallelTransformerDecoderLayer(args)
+        dt = utils.get_precise_dtype(args)
+        if _get(args, "fp16", False) or _get(args, "memory_efficient_fp16", False) or _get(args, "bf16", False):
+            layer = layer.to(dt)
+        from metaseq_b200.parallel.fsdp import fsdp_wrap
+
+        return fsdp_wrap(layer, min_num_params=_get(args, "min_params_to_wrap", None))
+
+    # ------------------------------------------------------------- embedding
+    def _doc_sep_positions(self, tokens):
+        """Positions that restart at ``padding_idx + 1`` after every separator token."""
+        sep = tokens.eq(self.self_attn_doc_sep)
+        starts = torch.zeros_like(tokens, dtype=torch.bool)
+        starts[:, 1:] = sep[:, :-1]
+        starts[:, 0] = True
+        idx = torch.arange(tokens.shape[1], device=tokens.device).expand_as(tokens)
+        last_start = torch.where(starts, idx, torch.zeros_like(idx)).cummax(dim=1)[0]
+        mask = tokens.ne(self.padding_idx)
+        return ((idx - last_start + 1) * mask).long() + self.padding_idx, last_start
+
+    def forward_embedding(self, tokens, incremental_state=None, past: int = 0):
+        doc_start = None
+        if self.self_attn_doc_sep != UNSPECIFIED_DOC_SEP:
+            positions, doc_start = self._doc_sep_positions(tokens)
+        elif self.embed_positions is not None:
+            positions = utils.make_positions(tokens, self.padding_idx)
+        else:
+            positions = None
+        if past > 0:
+            tokens = tokens[:, past:]
+            if positions is not None:
+                positions = positions[:, past:]
+        w = self.embed_tokens.weight
+        tp = mpu.get_tensor_model_parallel_world_size()
+        pos_w = self.embed_positions.weight if (self.embed_positions is not None and positions is not None
+                                                and hasattr(self.embed_positions, "weight")) else None
+        if ops_f.use_kernels(w) and w.shape[1] % 8 == 0 and (pos_w is None or pos_w.dtype == w.dtype):
+            if tp == 1:
+                x = ops_ag.embedding(tokens, positions, w, pos_w, self.embed_scale, self.padding_idx, 0)
+            else:
+                x = ops_ag.embedding(tokens, None, w, None, self.embed_scale, self.padding_idx,
+                                     self.embed_tokens.vocab_start_index)
+                x = mappings.reduce_from_tensor_model_parallel_region(x)
+                if pos_w is not None:
+                    x = x + torch.nn.functional.embedding(positions, pos_w)
+            embed = x
+        else:
+            embed = self.embed_scale * self.embed_tokens(tokens)
+            x = embed
+            if positions is not None and self.embed_positions is not None:
+                if pos_w is not None:
+                    x = x + torch.nn.functional.embedding(positions, pos_w, self.padding_idx)
+                else:
+                    x = x + self.embed_positions(tokens, positions=positions)
+        if self.dropout_module is not None:
+            x = self.dropout_module(x)
+        return x, embed, positions, doc_start
+
+    # ---------------------------------------------------------------- forward
+    def forward(self, prev_output_tokens, src_lengths=None, incremental_state=None, features_only: bool = False,
+                self_attn_padding_mask=None, **unused):
+        x, extra = self.extract_features(prev_output_tokens, incremental_state=incremental_state,
+                                         self_attn_padding_mask=self_attn_padding_mask)
+        if not features_only:
+            x = self.output_layer(x, bt=extra["bt"])
+        return x, extra
+
+    def _past_length(self, incremental_state) -> int:
+        if not incremental_state:
+            return 0
+        for v in incremental_state.values():
+            if isinstance(v, KVCache):
+                return v.length
+        return 0
+
+    def extract_features(self, prev_output_tokens, incremental_state=None, self_attn_padding_mask=None, **unused):
+        past = self._past_length(incremental_state)
+        B = prev_output_tokens.shape[0]
+        x, tok_emb, positions, doc_start = self.forward_embedding(prev_output_tokens, incremental_state, past)
+        T = x.shape[1]
+        attn_mask = None
+        if doc_start is not None and incremental_state is None:
+            # block-diagonal causal mask: a token attends only inside its own document
+            idx = torch.arange(T, device=x.device)
+            same_doc = doc_start[:, :, None] == doc_start[:, None, :]
+            causal = idx[None, :, None] >= idx[None, None, :]
+            attn_mask = torch.zeros(B, 1, T, T, device=x.device, dtype=torch.float32)
+            attn_mask.masked_fill_(~(same_doc & causal)[:, None], float("-inf"))
+        if self.sequence_parallel:
+            x = mappings.scatter_to_sequence_parallel_region(x.reshape(B * T, -1))
+        inner_states: List[Optional[torch.Tensor]] = []
+        for layer in self.layers:
+            x = layer(x, bt=(B, T), incremental_state=incremental_state,
+                      self_attn_padding_mask=self_attn_padding_mask, self_attn_mask=attn_mask)
+        x = self.layer_norm(x)
+        return x, {"inner_states": inner_states, "tok_emb": tok_emb, "positions": positions, "bt": (B, T)}
+
+    def output_layer(self, features, **kwargs):
+        """Project to the vocabulary with the (tied) embedding matrix."""
+        w = self.output_projection.weight
+        tp = mpu.get_tensor_model_parallel_world_size()
+        if self.sequence_parallel:
+            features = mappings.gather_from_sequence_parallel_region(features, True)
+        elif tp > 1:
+            features = mappings.copy_to_tensor_model_parallel_region(features)
+        if ops_f.use_kernels(features) and features.dtype == w.dtype and w.shape[0] % 8 == 0:
+            logits = ops_ag.linear(features, w)
+        else:
+            logits = torch.nn.functional.linear(features, w)
+        vocab_parallel = _get(self.args, "criterion", None) == "vocab_parallel_cross_entropy"
+        if tp > 1 and (self.inference or not vocab_parallel):
+            logits = mappings.gather_from_tensor_model_parallel_region(logits)
+        if logits.dim() == 2 and "bt" in kwargs:
+            logits = logits.view(*kwargs["bt"], -1)
+        return logits
+
+    def max_positions(self):
+        if self.embed_positions is None:
+            return self.max_target_positions
+        return min(self.max_target_positions, self.embed_positions.max_positions)
+
+    def make_generation_fast_(self, **kwargs):
+        self.inference = True
+
+    def upgrade_state_dict_named(self, state_dict, name):
+        key = f"{name}.version" if name else "version"
+        if key not in state_dict:
+            state_dict[key] = torch.Tensor([3])
+        return state_dict

@@ -1,0 +1,145 @@
+"""Pre-LN transformer decoder block (self-attention + feed-forward), tensor parallel.
+
+Parameter names and registration order are part of the checkpoint contract
+(flat-parameter order inside an FSDP unit):
+``self_attn.qkv_proj.{weight,bias}``, ``self_attn.out_proj.{weight,bias}``,
+``self_attn_layer_norm.{weight,bias}``, ``fc1.{weight,bias}``, ``fc2.{weight,bias}``,
+``final_layer_norm.{weight,bias}`` (reference:
+metaseq/modules/transformer_decoder_layer.py:52-101; init options :103-177).
+
+``forward`` picks between two implementations of the same math:
+* the fused path (one autograd function over the sm_100a kernels,
+  ``metaseq_b200.modules.fused_layer``) for 16-bit CUDA training / prefill without cache;
+* the modular path (LayerNorm / attention / parallel linear modules) everywhere else:
+  CPU, fp32, incremental decoding, dropout > 0, non-ReLU activations.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+import torch
+import torch.nn as nn
+
+from metaseq_b200 import utils
+from metaseq_b200.modules.activation_functions import ActivationFn
+from metaseq_b200.modules.dropout import Dropout
+from metaseq_b200.modules.fused_layer import LayerSpec, fused_decoder_layer
+from metaseq_b200.modules.layer_norm import LayerNorm
+from metaseq_b200.modules.multihead_attention import ModelParallelMultiheadAttention
+from metaseq_b200.ops import functional as ops_f
+from metaseq_b200.parallel import mpu
+from metaseq_b200.parallel.layers import ColumnParallelLinear, RowParallelLinear
+
+
+def _get(args, name, default=None):
+    return getattr(args, name, default)
+
+
+class ModelParallelTransformerDecoderLayer(nn.Module):
+    def __init__(self, args):
+        super().__init__()
+        self.args = args
+        self.embed_dim = args.decoder_embed_dim
+        self.sequence_parallel = bool(_get(args, "sequence_parallel", False))
+        self.dropout_module = Dropout(_get(args, "dropout", 0.0), module_name=self.__class__.__name__)
+        self.num_layers = args.decoder_layers
+        dtype = utils.get_precise_dtype(args) if _get(args, "tensor_parallel_init_model_on_gpu", False) or \
+            _get(args, "init_dtype_from_flags", False) else None
+        device = torch.cuda.current_device() if (_get(args, "tensor_parallel_init_model_on_gpu", False)
+                                                 and torch.cuda.is_available()) else None
+        cpu_init = not _get(args, "tensor_parallel_init_model_on_gpu", False)
+        full_init = bool(_get(args, "full_megatron_init", False))
+        sigma = _get(args, "megatron_init_sigma", 0.006)
+        scalar = _get(args, "full_megatron_init_scalar", 1.0)
+        disable_bias = bool(_get(args, "disable_bias", False))
+        affine = not bool(_get(args, "disable_affine_ln", False))
+        ffn_dim = args.decoder_ffn_embed_dim
+        self.activation_name = _get(args, "activation_fn", "relu") or "relu"
+
+        self.self_attn = ModelParallelMultiheadAttention(
+            self.embed_dim, args.decoder_attention_heads, dropout=_get(args, "attention_dropout", 0.0),
+            bias=not disable_bias, use_cpu_initialization=cpu_init, full_megatron_init=full_init,
+            full_megatron_init_scalar=scalar, megatron_init_sigma=sigma, num_layers=self.num_layers, dtype=dtype,
+            device=device, sequence_parallel=self.sequence_parallel,
+            max_positions=_get(args, "max_target_positions", None) or _get(args, "tokens_per_sample", 2048))
+        self.self_attn_layer_norm = LayerNorm(self.embed_dim, elementwise_affine=affine)
+        if full_init:
+            init_fc1 = utils.init_method_normal(sigma * scalar)
+            init_fc2 = utils.scaled_init_method_normal(sigma * scalar, self.num_layers)
+        else:
+            import math
+
+            def init_fc1(w):
+                return nn.init.kaiming_uniform_(w, a=math.sqrt(5))
+
+            init_fc2 = init_fc1
+        self.activation_fn = ActivationFn(self.activation_name, self._plain_fc1, self.embed_dim, ffn_dim,
+                                          bias=not disable_bias, init=init_fc1, cpu_init=cpu_init, dtype=dtype,
+                                          device=device, sp=self.sequence_parallel)
+        self.fc1 = self._plain_fc1(self.embed_dim, ffn_dim, bias=not disable_bias, init=init_fc1, cpu_init=cpu_init,
+                                   dtype=dtype, device=device, sp=self.sequence_parallel)
+        self.fc2 = RowParallelLinear(ffn_dim, self.embed_dim, bias=not disable_bias, input_is_parallel=True,
+                                     init_method=init_fc2, skip_bias_add=False, use_cpu_initialization=cpu_init,
+                                     dtype=dtype, device=device, sequence_parallel=self.sequence_parallel)
+        self.final_layer_norm = LayerNorm(self.embed_dim, elementwise_affine=affine)
+        self.checkpoint_activations = bool(_get(args, "checkpoint_activations", False))
+        self.use_fused_layer = not bool(_get(args, "no_fused_layer", False))
+        self.tp_comm = None  # set by the trainer when fused tensor-parallel communication is on
+
+    @staticmethod
+    def _plain_fc1(embed_dim, ffn_dim, bias, init, cpu_init, dtype, device, sp):
+        return ColumnParallelLinear(embed_dim, ffn_dim, bias=bias, gather_output=False, init_method=init,
+                                    use_cpu_initialization=cpu_init, dtype=dtype, device=device, sequence_parallel=sp)
+
+    # ------------------------------------------------------------------ paths
+    def _fused_ok(self, x, incremental_state, key_padding_mask, attn_mask) -> bool:
+        if not self.use_fused_layer or incremental_state is not None or key_padding_mask is not None \
+                or attn_mask is not None:
+            return False
+        if not ops_f.use_kernels(x) or self.activation_name != "relu":
+            return False
+        if self.training and (self.dropout_module.p > 0 or self.self_attn.dropout_module.p > 0):
+            return False
+        if self.self_attn.head_dim not in (64, 128) or self.embed_dim % 8 != 0:
+            return False
+        if self.self_attn.qkv_proj.weight.dtype != x.dtype:
+            return False
+        return True
+
+    def forward(self, x, bt: Optional[Tuple[int, int]] = None, incremental_state: Optional[Dict] = None,
+                self_attn_padding_mask=None, self_attn_mask=None, recompute: Optional[bool] = None):
+        """``x``: ``[B, T, D]`` (``[B*T/p, D]`` with sequence parallelism; then ``bt`` is required)."""
+        if bt is None:
+            bt = (x.shape[0], x.shape[1])
+        if self._fused_ok(x, incremental_state, self_attn_padding_mask, self_attn_mask):
+            a = self.self_attn
+            spec = LayerSpec(
+                B=bt[0], T=bt[1], heads_local=a.num_heads_partition, head_dim=a.head_dim, scale=a.scaling,
+                eps=self.self_attn_layer_norm.eps, tp_group=mpu.get_tensor_model_parallel_group(),
+                tp_world=mpu.get_tensor_model_parallel_world_size(), sequence_parallel=self.sequence_parallel,
+                recompute=self.checkpoint_activations if recompute is None else recompute, comm=self.tp_comm)
+            ln1, ln2 = self.self_attn_layer_norm, self.final_layer_norm
+            return fused_decoder_layer(
+                x, spec, ln1.weight, ln1.bias, a.qkv_proj.weight, a.qkv_proj.bias, a.out_proj.weight, a.out_proj.bias,
+                ln2.weight, ln2.bias, self.fc1.weight, self.fc1.bias, self.fc2.weight, self.fc2.bias)
+        return self._modular_forward(x, bt, incremental_state, self_attn_padding_mask, self_attn_mask)
+
+    def _modular_forward(self, x, bt, incremental_state, key_padding_mask, attn_mask):
+        residual = x
+        h = self.self_attn_layer_norm(x)
+        h, attn_bias = self.self_attn(h, bt, incremental_state=incremental_state, key_padding_mask=key_padding_mask,
+                                      attn_mask=attn_mask)
+        if attn_bias is not None:
+            h = h + attn_bias
+        h = self.dropout_module(h)
+        x = residual + h.view_as(residual)
+        residual = x
+        h = self.final_layer_norm(x)
+        fc1_out, _ = self.fc1(h)
+        h = self.activation_fn(h, fc1_out, model_parallel=True)
+        h, _ = self.fc2(h)
+        h = self.dropout_module(h)
+        return residual + h.view_as(residual)
+
+    def make_generation_fast_(self, **kwargs):
+        pass

@@ -1,0 +1,172 @@
+"""Tensor-parallel building blocks: vocab-parallel embedding, column- and
+row-parallel linear layers.
+
+Weight layouts and semantics follow the reference
+(metaseq/modules/megatron/mpu/layers.py: VocabParallelEmbedding :144-250,
+ColumnParallelLinear :386-536, RowParallelLinear :539-676): column-parallel
+weights are ``[out/p, in]``, row-parallel weights ``[out, in/p]``; with
+``skip_bias_add`` the bias is returned instead of added so the caller can add it
+after the tensor-parallel reduction; under sequence parallelism the
+column-parallel input is all-gathered along the first dimension and the
+row-parallel output reduce-scattered.
+
+Initialisation: ``use_cpu_initialization`` builds the full master weight on
+every rank and keeps this rank's slice (:61-101), otherwise the slice is drawn
+directly inside the tensor-parallel RNG fork (:50-58).
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as TF
+
+from metaseq_b200.ops import autograd as ops_ag
+from metaseq_b200.ops import functional as ops_f
+
+from . import mappings, mpu
+
+
+def _init_partition(weight: torch.Tensor, full_shape, partition_dim: int, init_method: Callable, cpu_init: bool,
+                    stride: int = 1, dtype=None):
+    """Fills ``weight`` (this rank's partition) from ``init_method``."""
+    world = mpu.get_tensor_model_parallel_world_size()
+    with torch.no_grad():
+        if world == 1:
+            if cpu_init and weight.device.type != "cpu":
+                master = torch.empty(full_shape, dtype=torch.float32)
+                init_method(master)
+                weight.copy_(master)
+            else:
+                init_method(weight)
+            return
+        if cpu_init:
+            master = torch.empty(full_shape, dtype=torch.float32)
+            init_method(master)
+            per = full_shape[partition_dim] // world
+            per_stride = per // stride
+            pieces = torch.split(master, per_stride, dim=partition_dim)
+            rank = mpu.get_tensor_model_parallel_rank()
+            mine = pieces[rank::world]
+            weight.copy_(torch.cat(mine, dim=partition_dim))
+        else:
+            with mpu.get_cuda_rng_tracker().fork():
+                init_method(weight)
+
+
+class VocabParallelEmbedding(nn.Module):
+    """Embedding whose rows (vocabulary) are split across tensor-parallel ranks; tokens
+    outside this rank's range contribute zero and the partial results are all-reduced."""
+
+    def __init__(self, num_embeddings: int, embedding_dim: int, padding_idx: Optional[int] = None,
+                 init_method: Callable = nn.init.xavier_normal_, use_cpu_initialization: bool = False, dtype=None,
+                 device=None):
+        super().__init__()
+        self.num_embeddings = num_embeddings
+        self.embedding_dim = embedding_dim
+        self.padding_idx = padding_idx
+        world = mpu.get_tensor_model_parallel_world_size()
+        self.vocab_start_index, self.vocab_end_index = mpu.vocab_range(
+            num_embeddings, mpu.get_tensor_model_parallel_rank(), world)
+        self.num_embeddings_per_partition = self.vocab_end_index - self.vocab_start_index
+        self.weight = nn.Parameter(torch.empty(self.num_embeddings_per_partition, embedding_dim, dtype=dtype,
+                                               device=device))
+        _init_partition(self.weight, (num_embeddings, embedding_dim), 0, init_method, use_cpu_initialization)
+        if padding_idx is not None and self.vocab_start_index <= padding_idx < self.vocab_end_index:
+            with torch.no_grad():
+                self.weight[padding_idx - self.vocab_start_index].zero_()
+        self.weight.model_parallel = world > 1
+        self.weight.partition_dim = 0
+
+    def forward(self, tokens):
+        world = mpu.get_tensor_model_parallel_world_size()
+        if world > 1:
+            mask = (tokens < self.vocab_start_index) | (tokens >= self.vocab_end_index)
+            local = (tokens - self.vocab_start_index).masked_fill(mask, 0)
+        else:
+            mask, local = None, tokens
+        out = TF.embedding(local, self.weight, self.padding_idx if world == 1 else None)
+        if mask is not None:
+            out = out.masked_fill(mask.unsqueeze(-1), 0.0)
+            out = mappings.reduce_from_tensor_model_parallel_region(out)
+        return out
+
+
+def _linear(x, weight, bias=None):
+    if ops_f.use_kernels(x) and x.dtype == weight.dtype:
+        return ops_ag.linear(x, weight, bias)
+    return TF.linear(x, weight, bias)
+
+
+class ColumnParallelLinear(nn.Module):
+    """``Y = X A^T + b`` with A split along its output dimension: ``A = [A_1; ...; A_p]``."""
+
+    def __init__(self, input_size: int, output_size: int, bias: bool = True, gather_output: bool = True,
+                 init_method: Callable = nn.init.xavier_normal_, stride: int = 1, skip_bias_add: bool = False,
+                 use_cpu_initialization: bool = False, dtype=None, device=None, sequence_parallel: bool = False):
+        super().__init__()
+        self.input_size, self.output_size = input_size, output_size
+        self.gather_output = gather_output
+        self.skip_bias_add = skip_bias_add
+        self.sequence_parallel = sequence_parallel
+        world = mpu.get_tensor_model_parallel_world_size()
+        self.output_size_per_partition = mpu.divide(output_size, world)
+        self.weight = nn.Parameter(torch.empty(self.output_size_per_partition, input_size, dtype=dtype, device=device))
+        _init_partition(self.weight, (output_size, input_size), 0, init_method, use_cpu_initialization, stride)
+        self.weight.model_parallel = world > 1
+        self.weight.partition_dim = 0
+        if bias:
+            self.bias = nn.Parameter(torch.zeros(self.output_size_per_partition, dtype=dtype, device=device))
+            self.bias.model_parallel = world > 1
+            self.bias.partition_dim = 0
+        else:
+            self.register_parameter("bias", None)
+
+    def forward(self, x):
+        if self.sequence_parallel:
+            xin = mappings.gather_from_sequence_parallel_region(x, True)
+        else:
+            xin = mappings.copy_to_tensor_model_parallel_region(x)
+        bias = self.bias if not self.skip_bias_add else None
+        out = _linear(xin, self.weight, bias)
+        if self.gather_output:
+            assert not self.sequence_parallel
+            out = mappings.gather_from_tensor_model_parallel_region(out)
+        return out, (self.bias if self.skip_bias_add else None)
+
+
+class RowParallelLinear(nn.Module):
+    """``Y = X A^T + b`` with A split along its input dimension and X split to match."""
+
+    def __init__(self, input_size: int, output_size: int, bias: bool = True, input_is_parallel: bool = False,
+                 init_method: Callable = nn.init.xavier_normal_, stride: int = 1, skip_bias_add: bool = False,
+                 use_cpu_initialization: bool = False, dtype=None, device=None, sequence_parallel: bool = False):
+        super().__init__()
+        self.input_size, self.output_size = input_size, output_size
+        self.input_is_parallel = input_is_parallel
+        self.skip_bias_add = skip_bias_add
+        self.sequence_parallel = sequence_parallel
+        world = mpu.get_tensor_model_parallel_world_size()
+        self.input_size_per_partition = mpu.divide(input_size, world)
+        self.weight = nn.Parameter(torch.empty(output_size, self.input_size_per_partition, dtype=dtype, device=device))
+        _init_partition(self.weight, (output_size, input_size), 1, init_method, use_cpu_initialization, stride)
+        self.weight.model_parallel = world > 1
+        self.weight.partition_dim = 1
+        if bias:
+            self.bias = nn.Parameter(torch.zeros(output_size, dtype=dtype, device=device))
+        else:
+            self.register_parameter("bias", None)
+
+    def forward(self, x):
+        xin = x if self.input_is_parallel else mappings.scatter_to_tensor_model_parallel_region(x)
+        part = _linear(xin, self.weight, None)
+        if self.sequence_parallel:
+            out = mappings.reduce_scatter_to_sequence_parallel_region(part)
+        else:
+            out = mappings.reduce_from_tensor_model_parallel_region(part)
+        if self.skip_bias_add:
+            return out, self.bias
+        if self.bias is not None:
+            out = out + self.bias
+        return out, None
