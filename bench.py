@@ -1,0 +1,328 @@
+"""Headline benchmark: OPT training throughput on N B200 GPUs of one node.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--model opt-1.3b]
+
+Config (the reference's OPT-1.3B FSDP setting): 24 layers, d_model 2048, 32 heads, FFN 8192
+ReLU, learned positions, tied embeddings, vocab 50272, sequence length 2048, micro-batch 8
+sequences per GPU, fp16 parameters with the memory-efficient fp16 optimizer and dynamic loss
+scaling, AdamW (0.9, 0.95) eps 1e-8 weight decay 0.1, gradient clipping 1.0, polynomial decay
+with warm-up, FSDP full-shard over all N GPUs (tensor parallel 1).  Data are synthetic uniform
+token ids; weights are randomly initialised (N(0, 0.006), output projections scaled by
+1/sqrt(2L)).
+
+Two timed regions, each of exactly K optimizer steps after W warm-up steps, bracketed by a
+barrier and ``torch.cuda.synchronize()``:
+
+* ``value``: CUDA events on the launching stream around K full training steps (forward,
+  backward, gradient norm / clip, AdamW) with the batches already resident on the device;
+  max over ranks.
+* ``e2e``: wall clock around K calls of the public ``Trainer.train_step`` with each step's
+  batch copied from pinned host memory and the step's loss read back to the host.
+
+For N > 1 launch with ``python -m torch.distributed.run --nproc-per-node N bench.py --gpus N``;
+when started directly with ``--gpus N`` it re-launches itself that way.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+MODELS = {
+    "opt-125m": dict(arch="opt_125m", layers=12, dim=768, heads=12),
+    "opt-350m": dict(arch="opt_350m", layers=24, dim=1024, heads=16),
+    "opt-1.3b": dict(arch="opt_1_3b", layers=24, dim=2048, heads=32),
+    "opt-2.7b": dict(arch="opt_2_7b", layers=32, dim=2560, heads=32),
+    "opt-6.7b": dict(arch="opt_6_7b", layers=32, dim=4096, heads=32),
+}
+VOCAB = 50272
+
+
+def reference_arm(args):
+    """The unmodified reference cannot run here: it does not install offline in this image."""
+    why = ("reference metaseq not installable offline: its vendored CUDA extensions fail to compile against "
+           "torch 2.11 (AT_DISPATCH on DeprecatedTypeProperties) and fairscale / hydra-core / omegaconf are "
+           "not in the wheelhouse")
+    ref_dir = os.path.join(ROOT, "baseline", "_ref", "metaseq")
+    if os.path.isdir(ref_dir):
+        sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
+        try:
+            import metaseq  # noqa: F401
+
+            why = "reference package present but its training entry point needs fairscale (not installed)"
+        except Exception as e:  # missing hydra / omegaconf / fairscale
+            why = f"reference import failed: {type(e).__name__}: {str(e)[:120]}"
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
+    return 0
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU every 200 ms through NVML (read-only)."""
+
+    REASONS = {
+        0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown",
+        0x10: "sync_boost", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+        0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting",
+    }
+
+    def __init__(self, index: int):
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                try:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.h))
+                except Exception:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
+                for bit, name in self.REASONS.items():
+                    if mask & bit and name != "gpu_idle":
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def start(self):
+        if self.nv is not None:
+            self._stop.clear()
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join(timeout=2)
+            self._thread = None
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        return {"sm_mhz": int(statistics.median(self.samples)), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def flops_per_token(layers, dim, seq, vocab):
+    """Model FLOPs per trained token (forward + backward = 3x forward), causal attention counted
+    at half of the full T x T product."""
+    linear = layers * 12 * dim * dim + vocab * dim
+    attn = layers * 2 * seq * dim * 0.5  # QK^T and PV, 2 * T * D MACs per token each, causal half
+    return 6.0 * linear + 6.0 * attn
+
+
+def build_trainer(args, world, rank, local_rank):
+    import torch
+
+    from metaseq_b200 import options, tasks
+    from metaseq_b200.cli.train import build_model_and_criterion
+    from metaseq_b200.dataclass.utils import convert_namespace_to_config
+    from metaseq_b200.ops import functional as ops_f
+    from metaseq_b200.parallel import utils as dist_utils
+    from metaseq_b200.trainer import Trainer
+
+    m = MODELS[args.model]
+    argv = [
+        "--task", "dummy_lm", "--dict-size", str(VOCAB), "--tokens-per-sample", str(args.seq),
+        "--batch-size", str(args.batch), "--arch", m["arch"],
+        "--dropout", "0.0", "--attention-dropout", "0.0",
+        "--criterion", "vocab_parallel_cross_entropy",
+        "--optimizer", "adam", "--adam-betas", "(0.9, 0.95)", "--adam-eps", "1e-8", "--weight-decay", "0.1",
+        "--clip-norm", "1.0", "--lr", "2e-4", "--lr-scheduler", "polynomial_decay", "--warmup-updates", "2000",
+        "--total-num-update", "286102", "--end-learning-rate", "2e-5",
+        "--memory-efficient-fp16", "--fp16-init-scale", "4", "--fp16-scale-window", "256",
+        "--ddp-backend", "fully_sharded", "--use-sharded-state", "--no-reshard-after-forward",
+        "--min-params-to-wrap", "1000000", "--tensor-parallel-init-model-on-gpu",
+        "--distributed-world-size", str(world), "--model-parallel-size", "1",
+        "--save-dir", "/tmp/msq_bench_ckpt", "--disable-validation", "--log-format", "none",
+        "--kernel-backend", args.kernel_backend, "--comm-backend", args.comm_backend, "--seed", "1",
+    ]
+    if args.checkpoint_activations:
+        argv.append("--checkpoint-activations")
+    parser = options.get_training_parser()
+    ns = options.parse_args_and_arch(parser, input_args=argv)
+    cfg = convert_namespace_to_config(ns)
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        cfg.distributed_training.distributed_init_method = "env://"
+        cfg.distributed_training.distributed_rank = rank
+        cfg.distributed_training.device_id = local_rank
+        dist_utils.distributed_init(cfg)
+    ops_f.set_backend(args.kernel_backend)
+    torch.manual_seed(1)
+    task = tasks.setup_task(cfg.task)
+    model, criterion = build_model_and_criterion(cfg, task)
+    trainer = Trainer(cfg, task, model, criterion)
+    return cfg, trainer
+
+
+def make_batches(args, n, pinned: bool, device=None, seed=0):
+    import torch
+
+    g = torch.Generator().manual_seed(1234 + seed)
+    out = []
+    for _ in range(n):
+        blk = torch.randint(4, VOCAB, (args.batch, args.seq + 1), generator=g)
+        src, tgt = blk[:, :-1].contiguous(), blk[:, 1:].contiguous()
+        if pinned:
+            src, tgt = src.pin_memory(), tgt.pin_memory()
+        if device is not None:
+            src, tgt = src.to(device), tgt.to(device)
+        out.append({"id": 1, "net_input": {"src_tokens": src}, "target": tgt, "nsentences": args.batch,
+                    "ntokens": args.batch * args.seq, "ntokens_target": args.batch * args.seq})
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=8)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="opt-1.3b", choices=sorted(MODELS))
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--seq", type=int, default=2048)
+    ap.add_argument("--kernel-backend", default="auto", choices=["auto", "torch"])
+    ap.add_argument("--comm-backend", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--checkpoint-activations", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    if args.gpus > 1 and "RANK" not in os.environ:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", str(29500 + os.getpid() % 2000), __file__] + sys.argv[1:]
+        return subprocess.call(cmd)
+
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    from metaseq_b200.ops import _lib
+
+    cfg, trainer = build_trainer(args, world, rank, local_rank)
+    dev = torch.device("cuda", local_rank)
+    m = MODELS[args.model]
+    tokens_per_step = args.batch * args.seq * world
+    n_pool = 4
+    dev_batches = make_batches(args, n_pool, pinned=False, device=dev, seed=rank)
+    host_batches = make_batches(args, n_pool, pinned=True, seed=100 + rank)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def run_steps(batches, n, read_loss):
+        last = None
+        done = 0
+        i = 0
+        while done < n:
+            out = trainer.train_step([batches[i % len(batches)]])
+            i += 1
+            if out is None:  # loss-scale overflow: the update was skipped, it does not count
+                continue
+            done += 1
+            if read_loss:
+                last = float(out["loss"])
+        return last
+
+    # warm-up (also lets the dynamic loss scale settle so that timed steps are real updates)
+    run_steps(dev_batches, args.warmup, read_loss=False)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    _lib.reset_launch_count()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    start.record()
+    run_steps(dev_batches, args.steps, read_loss=False)
+    end.record()
+    barrier()
+    dev_ms = start.elapsed_time(end)
+    launches = _lib.launch_count()
+    # end-to-end region through the public API: pinned host batch -> device, loss -> host
+    run_steps(host_batches, 1, read_loss=True)
+    barrier()
+    t0 = time.perf_counter()
+    loss = run_steps(host_batches, args.steps, read_loss=True)
+    barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+    sampler.stop()
+    t = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dev_ms, e2e_ms = float(t[0]), float(t[1])
+    mem_gb = torch.cuda.max_memory_allocated() / 2 ** 30
+    if rank == 0:
+        ms_step = dev_ms / args.steps
+        value = tokens_per_step / (ms_step / 1e3)
+        fpt = flops_per_token(m["layers"], m["dim"], args.seq, VOCAB)
+        e2e_value = tokens_per_step / (e2e_ms / args.steps / 1e3)
+        h2d = 2 * args.batch * args.seq * 8  # src_tokens + target, int64
+        rec = {
+            "metric": f"{args.model.replace('-', '_')}_train_tokens_per_s",
+            "value": round(value, 1),
+            "unit": "tokens/s",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": args.warmup,
+            "ms_per_step": round(ms_step, 3),
+            "higher_is_better": True,
+            "scaling": "weak",
+            "vs_baseline": None,
+            "dtype": "fp16",
+            "data": "synthetic uniform token ids, random-init weights",
+            "impl": "ours",
+            "tokens_per_s_per_gpu": round(value / world, 1),
+            "tflops_per_gpu": round(value / world * fpt / 1e12, 1),
+            "config": {
+                "model": args.model, "global_batch": args.batch * world, "micro_batch_per_gpu": args.batch,
+                "seq_len": args.seq, "parallelism": f"fsdp{world}_tp1", "optimizer": "adamw_me_fp16_dynamic_loss_scale",
+                "dropout": 0.0, "activation_checkpointing": bool(args.checkpoint_activations),
+                "kernel_backend": args.kernel_backend, "comm_backend": args.comm_backend,
+                "l2": "no explicit flush: each step streams >2.6 GB of weights and >15 GB of activations, far "
+                      "larger than the 126 MB L2",
+            },
+            "clocks": sampler.summary(),
+            "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms / args.steps, 3),
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * 4, "final_loss": loss},
+            "gpu_launches": launches,
+            "peak_mem_gb": round(mem_gb, 2),
+            "kernel_status": _lib.check_status(dev),
+        }
+        print(json.dumps(rec), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -86,7 +86,12 @@ class ModelParallelTransformerLanguageModel(LanguageModel):
             args.max_target_positions = getattr(args, "tokens_per_sample", DEFAULT_MAX_TARGET_POSITIONS)
         embed_tokens = cls.build_embedding(args, task.source_dictionary, args.decoder_embed_dim)
         decoder = ModelParallelTransformerDecoder(args, task.target_dictionary, embed_tokens)
-        return cls(decoder)
+        model = cls(decoder)
+        dt = utils.get_precise_dtype(args)
+        if dt != torch.float32 and getattr(args, "ddp_backend", None) == "fully_sharded":
+            # sharded units are built from parameters that already have the training dtype
+            model = model.to(dt)
+        return model
 
     @classmethod
     def build_embedding(cls, args, dictionary, embed_dim, path=None):

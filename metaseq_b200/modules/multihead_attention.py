@@ -138,7 +138,7 @@ class ModelParallelMultiheadAttention(nn.Module):
                 cache.append(k, v)
                 k = cache.k[:, : cache.length]
                 v = cache.v[:, : cache.length]
-            ctx = self._attend(q, k, v, B, T, past, key_padding_mask, attn_mask)
+            ctx = self._attend(q, k, v, B, T, past, key_padding_mask, attn_mask)  # cached or masked path
         if self.sequence_parallel:
             ctx = ctx.reshape(B * T, -1)
         out, bias = self.out_proj(ctx)
@@ -152,6 +152,14 @@ class ModelParallelMultiheadAttention(nn.Module):
             out, _ = ops_f.flash_attn_fwd(q.reshape(B, T, H, d), k.reshape(B, S, H, d), v.reshape(B, S, H, d),
                                           self.scaling, True)
             return out
+        if q.is_cuda and past == 0 and T == S and key_padding_mask is None and attn_mask is None and \
+                q.dtype in (torch.float16, torch.bfloat16) and not (self.training and self.dropout_module.p > 0):
+            # library attention (PyTorch SDPA): only reached with the "torch" operator backend, where it
+            # stands in for the baseline without materialising [T, T] scores
+            o = TF.scaled_dot_product_attention(
+                q.reshape(B, T, H, d).transpose(1, 2), k.reshape(B, S, H, d).transpose(1, 2),
+                v.reshape(B, S, H, d).transpose(1, 2), is_causal=True, scale=self.scaling)
+            return o.transpose(1, 2).reshape(B, T, H * d)
         qh = q.reshape(B, T, H, d).transpose(1, 2).float() * self.scaling
         kh = k.reshape(B, S, H, d).transpose(1, 2).float()
         vh = v.reshape(B, S, H, d).transpose(1, 2)

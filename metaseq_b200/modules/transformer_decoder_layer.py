@@ -31,6 +31,11 @@ from metaseq_b200.parallel import mpu
 from metaseq_b200.parallel.layers import ColumnParallelLinear, RowParallelLinear
 
 
+# Tests set this to run the fused layer function on CPU / fp32 through the PyTorch
+# restatements of the operators, which checks the hand-written backward exactly.
+FORCE_FUSED_LAYER = False
+
+
 def _get(args, name, default=None):
     return getattr(args, name, default)
 
@@ -96,11 +101,11 @@ class ModelParallelTransformerDecoderLayer(nn.Module):
         if not self.use_fused_layer or incremental_state is not None or key_padding_mask is not None \
                 or attn_mask is not None:
             return False
-        if not ops_f.use_kernels(x) or self.activation_name != "relu":
+        if not (ops_f.use_kernels(x) or FORCE_FUSED_LAYER) or self.activation_name != "relu":
             return False
         if self.training and (self.dropout_module.p > 0 or self.self_attn.dropout_module.p > 0):
             return False
-        if self.self_attn.head_dim not in (64, 128) or self.embed_dim % 8 != 0:
+        if (self.self_attn.head_dim not in (64, 128) and not FORCE_FUSED_LAYER) or self.embed_dim % 8 != 0:
             return False
         if self.self_attn.qkv_proj.weight.dtype != x.dtype:
             return False

@@ -25,6 +25,47 @@ L = c_longlong
 F = c_float
 
 
+# kernels launched by one call of each entry point (used for the launch counter)
+_KERNELS_PER_CALL = {"msq_sumsq": 2, "msq_layernorm_bwd": 2, "msq_flash_bwd": 2, "msq_layernorm_bwd_parts": 0,
+                     "msq_sumsq_parts": 0}
+_LAUNCHES = [0]
+
+
+def reset_launch_count():
+    _LAUNCHES[0] = 0
+
+
+def launch_count() -> int:
+    """Number of kernels of this library launched since the last reset."""
+    return _LAUNCHES[0]
+
+
+class _Counted:
+    """ctypes function wrapper that adds the entry point's kernel count to the launch counter."""
+
+    __slots__ = ("fn", "n")
+
+    def __init__(self, fn, n):
+        self.fn, self.n = fn, n
+
+    def __call__(self, *args):
+        _LAUNCHES[0] += self.n
+        return self.fn(*args)
+
+
+class _CountingLib:
+    def __init__(self, lib):
+        self._lib = lib
+        self._cache = {}
+
+    def __getattr__(self, name):
+        c = self._cache.get(name)
+        if c is None:
+            c = _Counted(getattr(self._lib, name), _KERNELS_PER_CALL.get(name, 1))
+            self._cache[name] = c
+        return c
+
+
 def _sig(lib, name, argtypes, restype=c_int):
     fn = getattr(lib, name)
     fn.argtypes = argtypes
@@ -91,7 +132,7 @@ def kernels():
             )
         lib = ctypes.CDLL(str(path))
         _declare_kernels(lib)
-        _KLIB = lib
+        _KLIB = _CountingLib(lib)
     return _KLIB
 
 

@@ -248,7 +248,7 @@ class FullyShardedDataParallel(nn.Module):
         return getattr(root, "_side_stream", None)
 
     def _root(self) -> "FullyShardedDataParallel":
-        return getattr(self, "_root_ref", None) or self
+        return self.__dict__.get("_root_ref") or self
 
     def _aliases_shard(self) -> bool:
         return self.world_size == 1 and self._compute_dtype() == self.flat_param.dtype
@@ -326,7 +326,7 @@ class FullyShardedDataParallel(nn.Module):
         for u in self._units:
             if u is not self:
                 u._is_root = False
-                u._root_ref = self
+                object.__setattr__(u, "_root_ref", self)  # plain attribute: not a submodule
         self._step_gathered = False
 
     def prefetch_all(self):
