@@ -261,9 +261,11 @@ def main():
     _lib.reset_launch_count()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    torch.cuda.profiler.start()  # lets a profiler started with --profile-from-start off see only this region
     start.record()
     run_steps(dev_batches, args.steps, read_loss=False)
     end.record()
+    torch.cuda.profiler.stop()
     barrier()
     dev_ms = start.elapsed_time(end)
     launches = _lib.launch_count()

@@ -608,38 +608,14 @@ __global__ void attn_delta_kernel(const uint16_t* __restrict__ o, const uint16_t
 }
 
 // ---------------------------------------------------------------------- host
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn attn_encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
-        qres != cudaDriverEntryPointSuccess)
-      return nullptr;
-    fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  }
-  return fn;
-}
-
 // [B, T, cols] view with the given strides (elements); box = 1 x 128 rows x 64 columns.
 static int make_tmap_btc(CUtensorMap* out, const void* base, int B, int T, long long cols, long long row_stride,
                          long long batch_stride, int bf16) {
-  EncodeTiledFn enc = attn_encode_fn();
-  if (!enc) return -1;
   if ((reinterpret_cast<uintptr_t>(base) & 15) || ((row_stride * 2) & 15) || ((batch_stride * 2) & 15)) return -2;
   cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(T), static_cast<cuuint64_t>(B)};
   cuuint64_t strides[2] = {static_cast<cuuint64_t>(row_stride) * 2, static_cast<cuuint64_t>(batch_stride) * 2};
   cuuint32_t box[3] = {64u, static_cast<cuuint32_t>(TILE), 1u};
-  cuuint32_t estr[3] = {1u, 1u, 1u};
-  CUresult r = enc(out, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
-                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -3;
+  return encode_tiled_16bit(out, base, 3, dims, strides, box, bf16) == CUDA_SUCCESS ? 0 : -3;
 }
 
 template <int HD, bool BF16>

@@ -17,6 +17,8 @@
 // Roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner,
 // warps 2..5 = epilogue (one TMEM lane quarter each).  Two accumulator buffers in
 // TMEM let the epilogue of tile i overlap the main loop of tile i+1.
+#include <cstdio>
+
 #include "sm100_common.cuh"
 
 namespace msq {
@@ -300,39 +302,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 }
 
 // ------------------------------------------------------------------- host
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn get_encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
-        qres != cudaDriverEntryPointSuccess)
-      return nullptr;
-    fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  }
-  return fn;
-}
-
 // 2-D map over a row-major 16-bit matrix [rows, cols] with row stride `ld` elements;
 // box = [box_rows, 64 columns] (128 bytes), 128-byte swizzle, zero fill out of range.
 int make_tmap_2d(CUtensorMap* out, const void* base, long long rows, long long cols, long long ld, int box_rows,
                  int bf16) {
-  EncodeTiledFn enc = get_encode_fn();
-  if (!enc) return -1;
   if ((reinterpret_cast<uintptr_t>(base) & 15) || ((ld * 2) & 15)) return -2;
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
   cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
   cuuint32_t box[2] = {64u, static_cast<cuuint32_t>(box_rows)};
-  cuuint32_t estr[2] = {1u, 1u};
-  CUresult r = enc(out, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
-                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -3;
+  CUresult r = encode_tiled_16bit(out, base, 2, dims, strides, box, bf16);
+  if (r != CUDA_SUCCESS) {
+    std::fprintf(stderr,
+                 "msq_gemm: cuTensorMapEncodeTiled failed (CUresult %d): base=%p rows=%lld cols=%lld ld=%lld "
+                 "box_rows=%d bf16=%d\n",
+                 static_cast<int>(r), base, rows, cols, ld, box_rows, bf16);
+    return -3;
+  }
+  return 0;
 }
 
 static int g_num_sms = 0;

@@ -307,4 +307,44 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
   }
 }
 
+// ------------------------------------------------------------ host: tensor maps
+typedef CUresult (*TensorMapEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                           const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                           CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                           CUtensorMapFloatOOBfill);
+
+inline TensorMapEncodeTiledFn tensor_map_encode_fn() {
+  static TensorMapEncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<TensorMapEncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// 16-bit tiled map with 128-byte swizzle and zero fill.  The driver call needs a context bound
+// to the calling thread; a thread that has made no runtime call yet (an autograd worker running
+// its first backward) has none, so on that error the runtime is asked to bind one and the call
+// is repeated once.
+inline CUresult encode_tiled_16bit(CUtensorMap* out, const void* base, int rank, const cuuint64_t* dims,
+                                   const cuuint64_t* strides, const cuuint32_t* box, int bf16) {
+  TensorMapEncodeTiledFn enc = tensor_map_encode_fn();
+  if (!enc) return CUDA_ERROR_NOT_FOUND;
+  const cuuint32_t estr[5] = {1u, 1u, 1u, 1u, 1u};
+  const CUtensorMapDataType dt = bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = CUDA_SUCCESS;
+  for (int attempt = 0; attempt < 2; ++attempt) {
+    r = enc(out, dt, static_cast<cuuint32_t>(rank), const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_ERROR_INVALID_CONTEXT) break;
+    cudaFree(nullptr);  // binds the primary context of the current device to this thread
+  }
+  return r;
+}
+
 }  // namespace msq

@@ -304,8 +304,12 @@ def embed_fwd(tokens, positions, tok_w, pos_w, scale: float, vocab_start: int = 
     use_pos = bool(add_positions and pos_w is not None and positions is not None)
     if use_kernels(tok_w) and D % 8 == 0:
         out = torch.empty((rows, D), dtype=tok_w.dtype, device=tok_w.device)
+        # keep the contiguous copies alive until after the launch: two temporaries created inside the
+        # argument list would be freed one after the other and end up at the same address
+        tok_c = flat_tok.contiguous()
+        pos_c = flat_pos.contiguous() if use_pos else None
         rc = _lib.kernels().msq_embed_fwd(
-            _lib.ptr(flat_tok.contiguous()), _lib.ptr(flat_pos.contiguous() if use_pos else None),
+            _lib.ptr(tok_c), _lib.ptr(pos_c),
             _lib.ptr(tok_w), _lib.ptr(pos_w if use_pos else None), _lib.ptr(out),
             rows, D, float(scale), int(vocab_start), int(vocab_end), int(use_pos), _bf(tok_w), _lib.stream_ptr(),
         )
@@ -371,8 +375,9 @@ def cross_entropy_fwd_bwd(logits2d, target, ignore_index: int, grad_scale: float
             and logits2d.stride(0) % 8 == 0:
         loss = torch.empty(rows, dtype=torch.float32, device=logits2d.device)
         lse = torch.empty(rows, dtype=torch.float32, device=logits2d.device)
+        target_c = target.contiguous()
         rc = _lib.kernels().msq_cross_entropy(
-            _lib.ptr(logits2d), logits2d.stride(0), _lib.ptr(target.contiguous()), _lib.ptr(loss), _lib.ptr(lse),
+            _lib.ptr(logits2d), logits2d.stride(0), _lib.ptr(target_c), _lib.ptr(loss), _lib.ptr(lse),
             rows, V, int(ignore_index), float(grad_scale), int(write_grad), _bf(logits2d), _lib.stream_ptr(),
         )
         _lib.check_rc(rc, "msq_cross_entropy")

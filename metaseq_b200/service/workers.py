@@ -1,0 +1,32 @@
+"""A unit of queued work: one prompt plus its generation settings.  Ordering is by cost
+(prompt length + tokens to generate) so that cheap requests batch first (reference:
+metaseq/service/workers.py:26-62)."""
+from __future__ import annotations
+
+import queue
+from dataclasses import dataclass, field
+from typing import Any
+
+from .queue import PriorityQueueRingShard, PriorityQueueRingShardKeyable
+
+
+@dataclass
+class WorkItem(PriorityQueueRingShardKeyable):
+    cost: int
+    uid: int
+    return_queue: Any
+    data: Any
+    prompt_len: int = 0
+    gen_len: int = 0
+
+    def __lt__(self, other):
+        return (self.cost, self.uid) < (other.cost, other.uid)
+
+    def __eq__(self, other):
+        return isinstance(other, WorkItem) and self.uid == other.uid and self.cost == other.cost
+
+    def queue_key(self):
+        # requests can share a batch only when every sampling parameter matches
+        d = {k: v for k, v in self.data.items() if k not in ("input", "seed", "min_tokens", "max_tokens")}
+        d = {k: (tuple(v) if isinstance(v, list) else v) for k, v in d.items()}
+        return PriorityQueueRingShard.key_from_dict(d)
