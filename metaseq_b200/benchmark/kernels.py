@@ -90,8 +90,10 @@ def main(argv=None):
     ap.add_argument("--out", default=None)
     ap.add_argument("--only", default=None, help="comma-separated op-name prefixes")
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--gemm-variant", default="auto", choices=["auto", "1cta", "2cta"])
     args = ap.parse_args(argv)
     dt = torch.float16 if args.dtype == "fp16" else torch.bfloat16
+    F.set_gemm_variant(args.gemm_variant)
     cfg = SHAPES[args.model]
     D, H, FFN, V = cfg["D"], cfg["H"], cfg["FFN"], cfg["V"]
     B, T = args.batch, args.seq

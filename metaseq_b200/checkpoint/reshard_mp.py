@@ -1,0 +1,120 @@
+"""Change the tensor-parallel size of a consolidated (unflattened) checkpoint.
+
+    python -m metaseq_b200.checkpoint.reshard_mp --src-dir-pattern "reshard-model_part-*.pt" \
+        --dst-dir-pattern "out/reshard-model_part-{i}.pt" --num-output-parts 4
+
+Keys are classified by name (reference: metaseq/scripts/reshard_mp.py:17-119 and
+metaseq/distributed/stitch_fsdp_ckpt.py:246-351): split along dim 0 (embeddings, fc1, q/k/v
+projections), split along dim 1 (fc2 / out_proj weights), replicated (positions, layer norms,
+fc2 / out_proj biases, version).  The fused ``qkv_proj`` is viewed as ``[3, rows/3, ...]`` so
+that the k | v | q blocks of every input part are merged block-wise and re-chunked block-wise.
+"""
+from __future__ import annotations
+
+import argparse
+import glob
+import logging
+import os
+import re
+from typing import Any, Dict, List
+
+import torch
+
+from metaseq_b200.file_io import torch_load_cpu
+
+logger = logging.getLogger(__name__)
+
+DIM0 = re.compile(r"embed_tokens|output_projection|ffn_layernorm|fc1|(k|q|v)_proj")
+DIM1 = re.compile(r"(fc2|out_proj)\.weight")
+SHARED = re.compile(r"embed_positions|layer_norm|(fc2|out_proj)\.bias|version")
+
+
+def _sorted_parts(pattern: str) -> List[str]:
+    files = glob.glob(pattern)
+
+    def key(p):
+        m = re.search(r"model_part-(\d+)", os.path.basename(p))
+        return int(m.group(1)) if m else 0
+
+    return sorted(files, key=key)
+
+
+def merge_parts(tensors: List[torch.Tensor], key: str) -> torch.Tensor:
+    if "qkv_proj" in key:
+        viewed = [t.view(3, t.shape[0] // 3, *t.shape[1:]) for t in tensors]
+        merged = torch.cat(viewed, dim=1)
+        return merged.reshape(-1, *tensors[0].shape[1:])
+    if SHARED.search(key):
+        for t in tensors[1:]:
+            if t.shape != tensors[0].shape or not torch.allclose(t.float(), tensors[0].float(), atol=1e-3, rtol=1e-3):
+                logger.warning(f"replicated tensor {key} differs between parts; keeping part 0")
+                break
+        return tensors[0]
+    if DIM1.search(key):
+        return torch.cat(tensors, dim=1)
+    if DIM0.search(key):
+        return torch.cat(tensors, dim=0)
+    return tensors[0]
+
+
+def split_part(t: torch.Tensor, key: str, n: int) -> List[torch.Tensor]:
+    if "qkv_proj" in key:
+        v = t.view(3, t.shape[0] // 3, *t.shape[1:])
+        return [c.reshape(-1, *t.shape[1:]).clone() for c in v.chunk(n, dim=1)]
+    if SHARED.search(key):
+        return [t.clone() for _ in range(n)]
+    if DIM1.search(key):
+        return [c.clone() for c in t.chunk(n, dim=1)]
+    if DIM0.search(key):
+        return [c.clone() for c in t.chunk(n, dim=0)]
+    return [t.clone() for _ in range(n)]
+
+
+def reshard_mp(src_dir_pattern: str, dst_dir_pattern: str, num_output_parts: int = 1, drop_optimizer_state: bool = True):
+    paths = _sorted_parts(src_dir_pattern)
+    assert len(paths) > 0, f"no files match {src_dir_pattern}"
+    states = [torch_load_cpu(p) for p in paths]
+    keys = list(states[0]["model"].keys())
+    merged = {k: merge_parts([s["model"][k] for s in states], k) for k in keys}
+    outs = [dict() for _ in range(num_output_parts)]
+    for k, t in merged.items():
+        for i, piece in enumerate(split_part(t, k, num_output_parts)):
+            outs[i][k] = piece
+    written = []
+    for i, model in enumerate(outs):
+        st = {k: v for k, v in states[0].items() if k != "model"}
+        if drop_optimizer_state:
+            st.pop("last_optimizer_state", None)
+        st.pop("shard_metadata", None)
+        st["model"] = model
+        cfg = st.get("cfg")
+        if isinstance(cfg, dict):
+            if isinstance(cfg.get("common"), dict):
+                cfg["common"]["model_parallel_size"] = num_output_parts
+            m = cfg.get("model")
+            if m is not None:
+                if isinstance(m, dict):
+                    m["model_parallel_size"] = num_output_parts
+                else:
+                    setattr(m, "model_parallel_size", num_output_parts)
+        dst = dst_dir_pattern.format(i=i)
+        os.makedirs(os.path.dirname(os.path.abspath(dst)), exist_ok=True)
+        torch.save(st, dst)
+        written.append(dst)
+    return written
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--src-dir-pattern", required=True)
+    ap.add_argument("--dst-dir-pattern", required=True)
+    ap.add_argument("--num-output-parts", type=int, default=1)
+    ap.add_argument("--keep-optimizer-state", action="store_true")
+    a = ap.parse_args(argv)
+    logging.basicConfig(level=logging.INFO)
+    for p in reshard_mp(a.src_dir_pattern, a.dst_dir_pattern, a.num_output_parts, not a.keep_optimizer_state):
+        print(p)
+
+
+if __name__ == "__main__":
+    main()

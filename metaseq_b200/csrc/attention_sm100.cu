@@ -21,6 +21,12 @@
 
 namespace msq {
 
+#ifdef MSQ_EXPERIMENT_NO_EXP
+#define MSQ_EXP2(x) (x)
+#else
+#define MSQ_EXP2(x) exp2f(x)
+#endif
+
 constexpr int ATT_THREADS = 192;
 constexpr int TILE = 128;
 constexpr float LOG2E = 1.4426950408889634f;
@@ -41,6 +47,7 @@ struct AttnFwdParams {
   int causal;
   int bf16;
   int* status;
+  long long* prof;  // optional phase timestamps of CTA (0,0,0), see msq_attn_set_prof
 };
 
 template <int HD>
@@ -197,63 +204,105 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       ok = mbar_wait_warp(s_full, j & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
       if (!ok) break;
       tc_fence_after();
-      // Columns of this block that row q_idx may attend to: [0, limit).
+      // Columns of this block that row q_idx may attend to: [0, limit).  Only the diagonal block of a
+      // causal problem and the last block of a ragged sequence need per-element masks; every other
+      // block takes the unmasked path (uniform over the CTA).
+      const bool prof_on = p.prof != nullptr && row == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j < 32;
+      if (prof_on) p.prof[j * 8 + 0] = clock64();
+      const bool need_mask = (p.causal && j == qb) || ((j + 1) * TILE > p.T);
       int limit = p.T - j * TILE;
       if (p.causal) limit = min(limit, q_idx - j * TILE + 1);
       limit = max(0, min(limit, TILE));
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tS + lane_off + c * 32, r);
-        tmem_ld_wait();
+      float mx;
+      {
+        // four independent running maxima keep the dependency chains short
+        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        uint32_t r[2][32];
+        tmem_ld_32x32(tS + lane_off, r[0]);
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (c * 32 + i < limit) mx = fmaxf(mx, __uint_as_float(r[i]));
+        for (int c = 0; c < 4; ++c) {
+          tmem_ld_wait();
+          if (c + 1 < 4) tmem_ld_32x32(tS + lane_off + (c + 1) * 32, r[(c + 1) & 1]);
+          if (need_mask) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (c * 32 + i < limit) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(r[c & 1][i]));
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(r[c & 1][i]));
+          }
+        }
+        mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
       }
+      if (prof_on) p.prof[j * 8 + 1] = clock64();
       const float m_new = fmaxf(m_run, mx * p.scale_log2);
       // A row with nothing to attend to yet (only rows past T) keeps m = -inf; guard the subtraction.
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
       const float alpha = exp2f(m_run - m_use);
-      float psum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tS + lane_off + c * 32, r);
-        tmem_ld_wait();
-        uint32_t packed[16];
+      float psum;
+      float ps4[4] = {0.f, 0.f, 0.f, 0.f};
+      {
+        uint32_t r[2][32];
+        tmem_ld_32x32(tS + lane_off, r[0]);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float a = (c * 32 + 2 * i < limit) ? exp2f(__uint_as_float(r[2 * i]) * p.scale_log2 - m_use) : 0.f;
-          float bb = (c * 32 + 2 * i + 1 < limit) ? exp2f(__uint_as_float(r[2 * i + 1]) * p.scale_log2 - m_use) : 0.f;
-          psum += a + bb;
-          packed[i] = pack2<BF16>(a, bb);
-        }
-        uint8_t* chunk = sP + (c >> 1) * Cfg::CHUNK_BYTES;
+        for (int c = 0; c < 4; ++c) {
+          tmem_ld_wait();
+          if (c + 1 < 4) tmem_ld_32x32(tS + lane_off + (c + 1) * 32, r[(c + 1) & 1]);
+          uint32_t packed[16];
+          if (need_mask) {
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const uint4 v4 = make_uint4(packed[4 * u], packed[4 * u + 1], packed[4 * u + 2], packed[4 * u + 3]);
-          *reinterpret_cast<uint4*>(chunk + sw128_offset(row, (c & 1) * 4 + u)) = v4;
+            for (int i = 0; i < 16; ++i) {
+              const float a = (c * 32 + 2 * i < limit)
+                                  ? exp2f(fmaf(__uint_as_float(r[c & 1][2 * i]), p.scale_log2, -m_use)) : 0.f;
+              const float bb = (c * 32 + 2 * i + 1 < limit)
+                                   ? exp2f(fmaf(__uint_as_float(r[c & 1][2 * i + 1]), p.scale_log2, -m_use)) : 0.f;
+              ps4[i & 3] += a + bb;
+              packed[i] = pack2<BF16>(a, bb);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float a = MSQ_EXP2(fmaf(__uint_as_float(r[c & 1][2 * i]), p.scale_log2, -m_use));
+              const float bb = MSQ_EXP2(fmaf(__uint_as_float(r[c & 1][2 * i + 1]), p.scale_log2, -m_use));
+              ps4[i & 3] += a + bb;
+              packed[i] = pack2<BF16>(a, bb);
+            }
+          }
+          uint8_t* chunk = sP + (c >> 1) * Cfg::CHUNK_BYTES;
+#ifndef MSQ_EXPERIMENT_NO_STS
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const uint4 v4 = make_uint4(packed[4 * u], packed[4 * u + 1], packed[4 * u + 2], packed[4 * u + 3]);
+            *reinterpret_cast<uint4*>(chunk + sw128_offset(row, (c & 1) * 4 + u)) = v4;
+          }
+#else
+          if (packed[0] == 0x12345678u) *reinterpret_cast<uint32_t*>(chunk) = packed[1] ^ packed[15] ^ packed[7];
+#endif
         }
       }
+      psum = (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
       l_run = l_run * alpha + psum;
       m_run = m_new;
+      if (prof_on) p.prof[j * 8 + 2] = clock64();
       tc_fence_before();
       fence_proxy_async_smem();
       mbar_arrive(p_full);
-#pragma unroll
-      for (int i = 0; i < HD; ++i) acc[i] *= alpha;
       ok = mbar_wait_warp(o_full, j & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
       if (!ok) break;
       tc_fence_after();
+      if (prof_on) p.prof[j * 8 + 3] = clock64();
+      {
+        uint32_t r[2][32];
+        tmem_ld_32x32(tO + lane_off, r[0]);
 #pragma unroll
-      for (int c = 0; c < HD / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tO + lane_off + c * 32, r);
-        tmem_ld_wait();
+        for (int c = 0; c < HD / 32; ++c) {
+          tmem_ld_wait();
+          if (c + 1 < HD / 32) tmem_ld_32x32(tO + lane_off + (c + 1) * 32, r[(c + 1) & 1]);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) acc[c * 32 + i] += __uint_as_float(r[i]);
+          for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(acc[c * 32 + i], alpha, __uint_as_float(r[c & 1][i]));
+        }
       }
+      if (prof_on) p.prof[j * 8 + 4] = clock64();
       tc_fence_before();
       mbar_arrive(o_empty);
     }
@@ -295,6 +344,7 @@ struct AttnBwdParams {
   int causal;
   int bf16;
   int* status;
+  long long* prof;
 };
 
 template <int HD>
@@ -484,9 +534,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       int limit = p.T - nb * TILE;
       if (p.causal) limit = min(limit, q_idx - nb * TILE + 1);
       limit = q_ok ? max(0, min(limit, TILE)) : 0;
+      // uniform over the CTA: only diagonal blocks and ragged tails (rows or columns past T) need masks
+      const bool need_mask = (p.causal && m == nb) || ((m + 1) * TILE > p.T) || ((nb + 1) * TILE > p.T);
+      const bool prof_on = p.prof != nullptr && row == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && it < 32;
+      if (prof_on) p.prof[256 + it * 8 + 0] = clock64();
       ok = mbar_wait_warp(sdp_full, it & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
       if (!ok) break;
       tc_fence_after();
+      if (prof_on) p.prof[256 + it * 8 + 1] = clock64();
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t s[32], dp[32];
@@ -494,19 +549,32 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tmem_ld_32x32(tmem_base + Cfg::DP_COL + lane_off + c * 32, dp);
         tmem_ld_wait();
         uint32_t pp[16], dd[16];
+        if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float p0 = 0.f, p1 = 0.f, d0 = 0.f, d1 = 0.f;
-          if (c * 32 + 2 * i < limit) {
-            p0 = exp2f(__uint_as_float(s[2 * i]) * scale_log2 - lse2);
-            d0 = p0 * (__uint_as_float(dp[2 * i]) - delta) * p.scale;
+          for (int i = 0; i < 16; ++i) {
+            float p0 = 0.f, p1 = 0.f, d0 = 0.f, d1 = 0.f;
+            if (c * 32 + 2 * i < limit) {
+              p0 = exp2f(fmaf(__uint_as_float(s[2 * i]), scale_log2, -lse2));
+              d0 = p0 * (__uint_as_float(dp[2 * i]) - delta) * p.scale;
+            }
+            if (c * 32 + 2 * i + 1 < limit) {
+              p1 = exp2f(fmaf(__uint_as_float(s[2 * i + 1]), scale_log2, -lse2));
+              d1 = p1 * (__uint_as_float(dp[2 * i + 1]) - delta) * p.scale;
+            }
+            pp[i] = pack2<BF16>(p0, p1);
+            dd[i] = pack2<BF16>(d0, d1);
           }
-          if (c * 32 + 2 * i + 1 < limit) {
-            p1 = exp2f(__uint_as_float(s[2 * i + 1]) * scale_log2 - lse2);
-            d1 = p1 * (__uint_as_float(dp[2 * i + 1]) - delta) * p.scale;
+        } else {
+          const float nds = -delta * p.scale;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float p0 = exp2f(fmaf(__uint_as_float(s[2 * i]), scale_log2, -lse2));
+            const float p1 = exp2f(fmaf(__uint_as_float(s[2 * i + 1]), scale_log2, -lse2));
+            const float d0 = p0 * fmaf(__uint_as_float(dp[2 * i]), p.scale, nds);
+            const float d1 = p1 * fmaf(__uint_as_float(dp[2 * i + 1]), p.scale, nds);
+            pp[i] = pack2<BF16>(p0, p1);
+            dd[i] = pack2<BF16>(d0, d1);
           }
-          pp[i] = pack2<BF16>(p0, p1);
-          dd[i] = pack2<BF16>(d0, d1);
         }
         const uint32_t chunk_off = (c >> 1) * Cfg::CHUNK_BYTES;
 #pragma unroll
@@ -516,12 +584,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           *reinterpret_cast<uint4*>(sDS + off) = make_uint4(dd[4 * u], dd[4 * u + 1], dd[4 * u + 2], dd[4 * u + 3]);
         }
       }
+      if (prof_on) p.prof[256 + it * 8 + 2] = clock64();
       tc_fence_before();
       fence_proxy_async_smem();
       mbar_arrive(pds_full);
       ok = mbar_wait_warp(dq_full, it & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
       if (!ok) break;
       tc_fence_after();
+      if (prof_on) p.prof[256 + it * 8 + 3] = clock64();
       float* dq_row = p.dq_accum + (static_cast<long long>(b) * p.T + (q_ok ? q_idx : 0)) * (p.H * HD) + h * HD;
 #pragma unroll 1
       for (int c = 0; c < HD / 32; ++c) {
@@ -535,6 +605,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                        __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
         }
       }
+      if (prof_on) p.prof[256 + it * 8 + 4] = clock64();
       tc_fence_before();
       mbar_arrive(dq_empty);
     }
@@ -650,6 +721,12 @@ static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
 
 }  // namespace msq
 
+static long long* g_attn_prof = nullptr;
+
+// Debug aid: when set to a device buffer of at least 512 int64, CTA (0,0,0) of the next attention
+// launches records clock64() at its phase boundaries (forward in [0,256), backward in [256,512)).
+extern "C" void msq_attn_set_prof(long long* buf) { g_attn_prof = buf; }
+
 // q, k, v: 16-bit [B, T, H, HD] views; *_rs / *_bs are row (token) and batch strides in
 // elements.  out: [B, T, H*HD] with its own strides.  lse: fp32 [B, H, T].
 extern "C" int msq_flash_fwd(const void* q, const void* k, const void* v, long long q_rs, long long q_bs,
@@ -668,6 +745,7 @@ extern "C" int msq_flash_fwd(const void* q, const void* k, const void* v, long l
   AttnFwdParams p;
   p.out = out; p.o_row_stride = o_rs; p.o_batch_stride = o_bs; p.lse = lse;
   p.T = T; p.H = H; p.scale_log2 = scale * LOG2E; p.causal = causal; p.bf16 = bf16; p.status = status;
+  p.prof = g_attn_prof;
   if (HD == 64) return bf16 ? launch_fwd<64, true>(tq, tk, tv, p, B, stream) : launch_fwd<64, false>(tq, tk, tv, p, B, stream);
   return bf16 ? launch_fwd<128, true>(tq, tk, tv, p, B, stream) : launch_fwd<128, false>(tq, tk, tv, p, B, stream);
 }
@@ -705,6 +783,7 @@ extern "C" int msq_flash_bwd(const void* q, const void* k, const void* v, const 
   p.lse = lse; p.delta = delta; p.dq_accum = dq_accum; p.dk = dk; p.dv = dv;
   p.dk_row_stride = dk_rs; p.dk_batch_stride = dk_bs; p.dv_row_stride = dv_rs; p.dv_batch_stride = dv_bs;
   p.T = T; p.H = H; p.scale = scale; p.causal = causal; p.bf16 = bf16; p.status = status;
+  p.prof = g_attn_prof;
   if (HD == 64)
     return bf16 ? launch_bwd<64, true>(tq, tk, tv, tdo, p, B, stream) : launch_bwd<64, false>(tq, tk, tv, tdo, p, B, stream);
   return bf16 ? launch_bwd<128, true>(tq, tk, tv, tdo, p, B, stream) : launch_bwd<128, false>(tq, tk, tv, tdo, p, B, stream);

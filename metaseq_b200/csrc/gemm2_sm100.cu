@@ -1,0 +1,415 @@
+// Two-CTA (cta_group::2) variant of the persistent tcgen05 GEMM: a cluster of two CTAs on
+// neighbouring SMs computes one 256 x 256 output tile.  Each CTA loads its own 128 rows of A
+// and half (128 rows) of the B tile, the leader CTA issues one tcgen05.mma.cta_group::2 per
+// 16-wide k step that drives the tensor cores of both SMs, and each CTA keeps its 128 x 256
+// fp32 accumulator in its own TMEM.  Against the one-CTA kernel (gemm_sm100.cu) this halves
+// the B traffic from L2 into each SM (32 KB instead of 48 KB per 64-wide k block), which is
+// what limits that kernel, and leaves room for six pipeline stages.
+//
+// No load uses cluster multicast: every CTA issues plain tiled TMA loads into its own shared
+// memory and only the completion is signalled on the leader's mbarrier (cta_group::2 form).
+//
+// Same operand layouts and epilogue as msq_gemm; see gemm_sm100.cu.
+#include <cstdio>
+
+#include "sm100_common.cuh"
+
+namespace msq {
+
+struct Gemm2Params {
+  int M, N, K;
+  void* C;
+  long long ldc;
+  const void* bias;
+  const void* residual;
+  long long ldr;
+  const void* mask;
+  long long ldm;
+  int relu;
+  int accumulate;
+  int bf16;
+  int* status;
+};
+
+constexpr int G2_BM = 128;   // rows per CTA (256 per pair)
+constexpr int G2_BN = 256;   // columns per pair; each CTA stages half of the B tile
+constexpr int G2_BK = 64;
+constexpr int G2_STAGES = 6;
+constexpr int G2_THREADS = 192;
+constexpr uint32_t G2_A_BYTES = G2_BM * G2_BK * 2;        // 16 KB
+constexpr uint32_t G2_B_BYTES = (G2_BN / 2) * G2_BK * 2;  // 16 KB
+constexpr uint32_t G2_SMEM = G2_STAGES * (G2_A_BYTES + G2_B_BYTES) + 1024 + 256;
+constexpr uint32_t G2_TMEM_COLS = 2 * G2_BN;
+constexpr uint32_t PEER_BIT_MASK = 0xFEFFFFFFu;  // clears the CTA-parity bit of a shared address
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+// Tiled load into this CTA's shared memory; completion bytes are credited to the barrier at the
+// same offset in the even (leader) CTA of the pair.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* tmap, uint64_t* bar, int c0,
+                                                 int c1) {
+  const uint32_t leader_bar = smem_u32(bar) & PEER_BIT_MASK;
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(leader_bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                                uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on the barrier at this offset in both CTAs of the pair once all earlier MMAs are done.
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
+  const uint16_t mask = 0x3;
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+          smem_u32(bar)),
+      "h"(mask)
+      : "memory");
+}
+
+__device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  constexpr int GROUP = 8;  // 8 x 256 rows share the same sweep over column tiles
+  const int per_group = GROUP * tiles_n;
+  const int g = tile / per_group;
+  const int first_m = g * GROUP;
+  const int gsize = min(GROUP, tiles_m - first_m);
+  const int r = tile - g * per_group;
+  tm = first_m + (r % gsize);
+  tn = r / gsize;
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
+gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                         const Gemm2Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + G2_STAGES * G2_A_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(sB + G2_STAGES * G2_B_BYTES);
+  uint64_t* empty_bar = full_bar + G2_STAGES;
+  uint64_t* tfull_bar = empty_bar + G2_STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile uint32_t* skip_flag = reinterpret_cast<volatile uint32_t*>(tmem_slot + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  const int tiles_m = (p.M + 2 * G2_BM - 1) / (2 * G2_BM);
+  const int tiles_n = (p.N + G2_BN - 1) / G2_BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int k_blocks = (p.K + G2_BK - 1) / G2_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < G2_STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tfull_bar[b], 1);
+      mbar_init(&tempty_bar[b], 8);  // 4 epilogue warps in each CTA of the pair
+    }
+    *abort_flag = 0;
+    if (rank == 0) {
+      // One decision for the pair: skip all work when an earlier launch left a timeout code behind.
+      const uint32_t skip = (p.status && *reinterpret_cast<volatile int*>(p.status) != 0) ? 1u : 0u;
+      *skip_flag = skip;
+      st_shared_cluster_u32(map_to_cta(smem_u32(const_cast<uint32_t*>(skip_flag)), 1), skip);
+    }
+    mbar_fence_init();
+    fence_proxy_async_smem();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  __syncthreads();
+  cluster_sync_all();  // barriers of both CTAs are initialised, skip flag is in place
+  if (*skip_flag) return;
+
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, G2_TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        int tm, tn;
+        pair_tile_coords(tile, tiles_m, tiles_n, tm, tn);
+        const int m0 = tm * 2 * G2_BM + static_cast<int>(rank) * G2_BM;
+        const int n0 = tn * G2_BN + static_cast<int>(rank) * (G2_BN / 2);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, ST_TIMEOUT_SMEM_EMPTY);
+          if (!ok) break;
+          if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * (G2_A_BYTES + G2_B_BYTES));
+          uint8_t* a_dst = sA + stage * G2_A_BYTES;
+          uint8_t* b_dst = sB + stage * G2_B_BYTES;
+          const int k0 = kb * G2_BK;
+          if constexpr (!A_MN) {
+            tma_load_2d_pair(a_dst, &tmA, &full_bar[stage], k0, m0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < G2_BM / 64; ++c)
+              tma_load_2d_pair(a_dst + c * (G2_BK * 128), &tmA, &full_bar[stage], m0 + c * 64, k0);
+          }
+          if constexpr (!B_MN) {
+            tma_load_2d_pair(b_dst, &tmB, &full_bar[stage], k0, n0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < (G2_BN / 2) / 64; ++c)
+              tma_load_2d_pair(b_dst + c * (G2_BK * 128), &tmB, &full_bar[stage], n0 + c * 64, k0);
+          }
+          if (++stage == G2_STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        const unsigned long long t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 2000000ull) { }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader only)
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = make_idesc_f16(p.bf16, A_MN ? 1 : 0, B_MN ? 1 : 0, 2 * G2_BM, G2_BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int it = 0;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++it) {
+        const int buf = it & 1;
+        const uint32_t acc = tmem_base + buf * G2_BN;
+        ok = mbar_wait(&tempty_bar[buf], ((it >> 1) & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
+        if (!ok) break;
+        tc_fence_after();
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(sA + stage * G2_A_BYTES);
+          const uint32_t b_addr = smem_u32(sB + stage * G2_B_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < G2_BK / 16; ++kk) {
+            uint64_t da, db;
+            if constexpr (!A_MN) da = make_smem_desc_sw128(a_addr + kk * 32, 16, 1024);
+            else da = make_smem_desc_sw128(a_addr + kk * 2048, G2_BK * 128, 1024);
+            if constexpr (!B_MN) db = make_smem_desc_sw128(b_addr + kk * 32, 16, 1024);
+            else db = make_smem_desc_sw128(b_addr + kk * 2048, G2_BK * 128, 1024);
+            tc_mma_f16_pair(acc, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+          }
+          tc_commit_pair(&empty_bar[stage]);  // frees this stage in both CTAs
+          if (++stage == G2_STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        tc_commit_pair(&tfull_bar[buf]);  // accumulator ready in both CTAs
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue (both CTAs)
+    const int quarter = warp & 3;
+    const uint32_t leader_tempty0 = map_to_cta(smem_u32(&tempty_bar[0]), 0);
+    const uint32_t leader_tempty1 = map_to_cta(smem_u32(&tempty_bar[1]), 0);
+    bool ok = true;
+    int it = 0;
+    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++it) {
+      int tm, tn;
+      pair_tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      const int buf = it & 1;
+      ok = mbar_wait_warp(&tfull_bar[buf], (it >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
+      if (!ok) break;
+      tc_fence_after();
+      const int row = tm * 2 * G2_BM + static_cast<int>(rank) * G2_BM + quarter * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t taddr0 = tmem_base + buf * G2_BN + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < G2_BN / 32; ++c) {
+        const int col0 = tn * G2_BN + c * 32;
+        if (col0 >= p.N) break;
+        uint32_t r[32];
+        tmem_ld_32x32(taddr0 + c * 32, r);
+        tmem_ld_wait();
+        if (row_ok) {
+          uint16_t* crow = reinterpret_cast<uint16_t*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const int col = col0 + v * 8;
+            if (col < p.N) {
+              float f[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]);
+              if (p.bias) {
+                const uint4 bv = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.bias) + col);
+                const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  float2 b2 = p.bf16 ? unpack2<true>(bw[j]) : unpack2<false>(bw[j]);
+                  f[2 * j] += b2.x;
+                  f[2 * j + 1] += b2.y;
+                }
+              }
+              if (p.relu) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] = fmaxf(f[j], 0.f);
+              }
+              if (p.mask) {
+                const uint4 mv = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.mask) +
+                                                                 static_cast<long long>(row) * p.ldm + col);
+                const uint32_t mw[4] = {mv.x, mv.y, mv.z, mv.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  float2 m2 = p.bf16 ? unpack2<true>(mw[j]) : unpack2<false>(mw[j]);
+                  if (!(m2.x > 0.f)) f[2 * j] = 0.f;
+                  if (!(m2.y > 0.f)) f[2 * j + 1] = 0.f;
+                }
+              }
+              if (p.residual) {
+                const uint4 rv = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.residual) +
+                                                                 static_cast<long long>(row) * p.ldr + col);
+                const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  float2 r2 = p.bf16 ? unpack2<true>(rw[j]) : unpack2<false>(rw[j]);
+                  f[2 * j] += r2.x;
+                  f[2 * j + 1] += r2.y;
+                }
+              }
+              if (p.accumulate) {
+                const uint4 cv = *reinterpret_cast<const uint4*>(crow + v * 8);
+                const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  float2 c2 = p.bf16 ? unpack2<true>(cw[j]) : unpack2<false>(cw[j]);
+                  f[2 * j] += c2.x;
+                  f[2 * j + 1] += c2.y;
+                }
+              }
+              uint4 o;
+              if (p.bf16) {
+                o.x = pack2<true>(f[0], f[1]); o.y = pack2<true>(f[2], f[3]);
+                o.z = pack2<true>(f[4], f[5]); o.w = pack2<true>(f[6], f[7]);
+              } else {
+                o.x = pack2<false>(f[0], f[1]); o.y = pack2<false>(f[2], f[3]);
+                o.z = pack2<false>(f[4], f[5]); o.w = pack2<false>(f[6], f[7]);
+              }
+              *reinterpret_cast<uint4*>(crow + v * 8) = o;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(buf ? leader_tempty1 : leader_tempty0);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer may still signal or read this CTA until it, too, is done
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, G2_TMEM_COLS);
+  }
+}
+
+int make_tmap_2d(CUtensorMap* out, const void* base, long long rows, long long cols, long long ld, int box_rows,
+                 int bf16);  // gemm_sm100.cu
+
+static int g2_num_sms = 0;
+
+template <bool A_MN, bool B_MN>
+static int launch_gemm2(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gemm2Params& p, int max_ctas,
+                        cudaStream_t stream) {
+  auto kern = gemm_tcgen05_2cta_kernel<A_MN, B_MN>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM) != cudaSuccess) return -10;
+    configured = true;
+  }
+  const int tiles = ((p.M + 2 * G2_BM - 1) / (2 * G2_BM)) * ((p.N + G2_BN - 1) / G2_BN);
+  int pairs = g2_num_sms / 2;
+  if (max_ctas > 0 && pairs > max_ctas / 2) pairs = max_ctas / 2;
+  if (pairs > tiles) pairs = tiles;
+  if (pairs <= 0) return 0;
+  kern<<<2 * pairs, G2_THREADS, G2_SMEM, stream>>>(tmA, tmB, p);  // cluster shape comes from __cluster_dims__
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+}  // namespace msq
+
+// Same contract as msq_gemm.  Intended for M >= 256; smaller problems should use msq_gemm.
+extern "C" int msq_gemm2(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                         long long ldc, int a_mn, int b_mn, int bf16, const void* bias, const void* residual,
+                         long long ldr, const void* mask, long long ldm, int relu, int accumulate, int bn,
+                         int max_ctas, int* status, cudaStream_t stream) {
+  using namespace msq;
+  (void)bn;
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (N & 7) || (ldc & 7) || (reinterpret_cast<uintptr_t>(C) & 15)) return -4;
+  if (g2_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g2_num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  CUtensorMap tmA, tmB;
+  int rc;
+  rc = a_mn ? make_tmap_2d(&tmA, A, K, M, lda, G2_BK, bf16) : make_tmap_2d(&tmA, A, M, K, lda, G2_BM, bf16);
+  if (rc) return rc;
+  rc = b_mn ? make_tmap_2d(&tmB, B, K, N, ldb, G2_BK, bf16) : make_tmap_2d(&tmB, B, N, K, ldb, G2_BN / 2, bf16);
+  if (rc) return rc - 100;
+  Gemm2Params p;
+  p.M = M; p.N = N; p.K = K;
+  p.C = C; p.ldc = ldc;
+  p.bias = bias; p.residual = residual; p.ldr = ldr; p.mask = mask; p.ldm = ldm;
+  p.relu = relu; p.accumulate = accumulate; p.bf16 = bf16; p.status = status;
+  if (!a_mn && !b_mn) return launch_gemm2<false, false>(tmA, tmB, p, max_ctas, stream);
+  if (!a_mn && b_mn) return launch_gemm2<false, true>(tmA, tmB, p, max_ctas, stream);
+  if (a_mn && !b_mn) return launch_gemm2<true, false>(tmA, tmB, p, max_ctas, stream);
+  return launch_gemm2<true, true>(tmA, tmB, p, max_ctas, stream);
+}

@@ -75,6 +75,8 @@ def _sig(lib, name, argtypes, restype=c_int):
 
 def _declare_kernels(lib):
     _sig(lib, "msq_gemm", [P, P, P, I, I, I, L, L, L, I, I, I, P, P, L, P, L, I, I, I, I, P, P])
+    if hasattr(lib, "msq_gemm2"):
+        _sig(lib, "msq_gemm2", [P, P, P, I, I, I, L, L, L, I, I, I, P, P, L, P, L, I, I, I, I, P, P])
     _sig(lib, "msq_layernorm_bwd_parts", [I])
     _sig(lib, "msq_layernorm_fwd", [P, P, P, P, P, P, I, I, F, I, P])
     _sig(lib, "msq_layernorm_bwd", [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, P])
@@ -109,7 +111,8 @@ _OPTIONAL = {k: v for k, v in _OPTIONAL.items() if v is not None}
 
 
 def kernels_path() -> Path:
-    return _ROOT / "libmsq_kernels.so"
+    override = os.environ.get("MSQ_KERNELS_LIB")  # development aid: load an alternative build
+    return Path(override) if override else _ROOT / "libmsq_kernels.so"
 
 
 def host_path() -> Path:

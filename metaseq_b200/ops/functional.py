@@ -13,6 +13,7 @@ cuBLAS + unfused-ops baseline the kernels are compared against).
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional
 
 import torch
@@ -32,6 +33,18 @@ def set_backend(name: str):
 
 def get_backend() -> str:
     return _BACKEND
+
+
+_GEMM_VARIANT = os.environ.get("MSQ_GEMM_VARIANT", "auto")  # "auto" | "1cta" | "2cta"
+
+
+def set_gemm_variant(name: str):
+    """``1cta``: one CTA per 128x256 tile; ``2cta``: CTA pairs on 256x256 tiles (cta_group::2);
+    ``auto``: pairs for problems with at least 256 rows."""
+    global _GEMM_VARIANT
+    if name not in ("auto", "1cta", "2cta"):
+        raise ValueError(name)
+    _GEMM_VARIANT = name
 
 
 def use_kernels(*tensors) -> bool:
@@ -88,7 +101,9 @@ def gemm(
     if use_kernels(a) and K % 8 == 0 and N % 8 == 0 and _gemm_operands_ok(a, b, out, residual, mask) \
             and (bias is None or bias.data_ptr() % 16 == 0):
         lib = _lib.kernels()
-        rc = lib.msq_gemm(
+        pair = _GEMM_VARIANT == "2cta" or (_GEMM_VARIANT == "auto" and M >= 256 and N >= 128 and bn == 0)
+        fn = lib.msq_gemm2 if pair else lib.msq_gemm
+        rc = fn(
             _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), M, N, K,
             a.stride(0), b.stride(0), out.stride(0),
             int(a_mn), int(b_mn), _bf(a),

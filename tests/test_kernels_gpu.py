@@ -259,3 +259,48 @@ def test_sumsq_clip_adamw(dtype):
     before = p.clone()
     F.adamw_step(p, g, m, v, step=3, ctrl=ctrl, **kw)
     assert torch.equal(before, p)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 768, 320), (1000, 264, 136), (2048, 2048, 1024), (384, 96 * 2, 512)])
+def test_gemm_two_cta_layouts(dtype, a_mn, b_mn, M, N, K):
+    """The cta_group::2 kernel (CTA pairs on 256x256 tiles) against fp32 matmul, all four layouts."""
+    torch.manual_seed(10)
+    a = torch.randn((K, M) if a_mn else (M, K), device="cuda", dtype=dtype)
+    b = torch.randn((K, N) if b_mn else (N, K), device="cuda", dtype=dtype)
+    F.set_gemm_variant("2cta")
+    try:
+        got = F.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    finally:
+        F.set_gemm_variant("auto")
+    am = a.t() if a_mn else a
+    bm = b if b_mn else b.t()
+    want = am.float() @ bm.float()
+    _status_ok()
+    _close(got, want.to(dtype), dtype, scale=math.sqrt(K))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_gemm_two_cta_epilogue(dtype):
+    torch.manual_seed(12)
+    M, N, K = 776, 520, 320
+    a = torch.randn(M, K, device="cuda", dtype=dtype)
+    w = torch.randn(N, K, device="cuda", dtype=dtype) * 0.05
+    bias = torch.randn(N, device="cuda", dtype=dtype)
+    res = torch.randn(M, N, device="cuda", dtype=dtype)
+    mask = torch.randn(M, N, device="cuda", dtype=dtype)
+    base = a.float() @ w.float().t()
+    F.set_gemm_variant("2cta")
+    try:
+        got = F.gemm(a, w, bias=bias, relu=True)
+        _close(got, torch.relu(base + bias.float()).to(dtype), dtype)
+        got = F.gemm(a, w, bias=bias, residual=res)
+        _close(got, (base + bias.float() + res.float()).to(dtype), dtype)
+        prev = torch.randn(M, N, device="cuda", dtype=dtype)
+        out = prev.clone()
+        F.gemm(a, w, mask=mask, out=out, accumulate=True)
+        _close(out, (base * (mask > 0) + prev.float()).to(dtype), dtype)
+    finally:
+        F.set_gemm_variant("auto")
+    _status_ok()
