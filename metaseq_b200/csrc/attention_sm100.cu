@@ -21,13 +21,9 @@
 
 namespace msq {
 
-#ifdef MSQ_EXPERIMENT_NO_EXP
-#define MSQ_EXP2(x) (x)
-#else
-#define MSQ_EXP2(x) exp2f(x)
-#endif
 
-constexpr int ATT_THREADS = 192;
+constexpr int ATT_THREADS = 192;      // forward: TMA warp, MMA warp, 4 softmax warps
+constexpr int ATT_BWD_THREADS = 320;  // backward: TMA warp, MMA warp, 8 element-wise warps
 constexpr int TILE = 128;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
@@ -55,11 +51,14 @@ struct FwdCfg {
   static constexpr int CHUNKS = HD / 64;
   static constexpr uint32_t TILE_BYTES = TILE * HD * 2;  // one Q/K/V tile
   static constexpr uint32_t CHUNK_BYTES = TILE * 128;    // 16 KB
-  static constexpr int SLOTS = 3;                        // K/V ring
-  static constexpr uint32_t P_BYTES = TILE * TILE * 2;
-  static constexpr uint32_t SMEM = TILE_BYTES * (1 + SLOTS) + P_BYTES + 1024 + 128;
-  static constexpr uint32_t TMEM_COLS = 256;
+  // K/V ring.  Four slots at HD = 64 also keep the footprint above a third of an SM's shared memory, so
+  // at most two CTAs (2 x 256 TMEM columns) are ever co-resident and tcgen05.alloc never has to wait.
+  static constexpr int SLOTS = (HD == 64) ? 4 : 3;
+  static constexpr uint32_t SMEM = TILE_BYTES * (1 + SLOTS) + 1024 + 128;
+  // TMEM columns: S (128 fp32), O (HD fp32), P (128 16-bit values = 64 columns)
   static constexpr uint32_t O_COL = 128;
+  static constexpr uint32_t P_COL = 128 + HD;
+  static constexpr uint32_t TMEM_COLS = (HD == 64) ? 256 : 512;
 };
 
 template <int HD, bool BF16>
@@ -71,8 +70,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
   uint8_t* sKV = sQ + Cfg::TILE_BYTES;
-  uint8_t* sP = sKV + Cfg::SLOTS * Cfg::TILE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + Cfg::P_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + Cfg::SLOTS * Cfg::TILE_BYTES);
   uint64_t* q_full = bars;
   uint64_t* kv_full = bars + 1;
   uint64_t* kv_empty = kv_full + Cfg::SLOTS;
@@ -113,7 +111,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS = tmem_base, tO = tmem_base + Cfg::O_COL;
+  const uint32_t tS = tmem_base, tO = tmem_base + Cfg::O_COL, tP = tmem_base + Cfg::P_COL;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -144,61 +142,71 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc_s = make_idesc_f16(BF16 ? 1 : 0, 0, 0, TILE, TILE);
-      const uint32_t idesc_o = make_idesc_f16(BF16 ? 1 : 0, 0, 1, TILE, HD);
-      int slot = 0;
-      uint32_t phase = 0;
-      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
-      const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
-      auto issue_s = [&]() -> bool {
-        if (!mbar_wait(&kv_full[slot], phase, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL)) return false;
-        tc_fence_after();
-        const uint32_t k_addr = smem_u32(sKV + slot * Cfg::TILE_BYTES);
+    // The whole warp runs the control flow (so addresses and descriptors stay warp-uniform); one elected
+    // lane issues the tensor-core instructions.  Descriptors are built once and advanced by adding the
+    // byte offset >> 4 to their address field: the issue loop is the latency-critical path of the kernel.
+    const bool leader = elect_one();
+    const uint32_t idesc_s = make_idesc_f16(BF16 ? 1 : 0, 0, 0, TILE, TILE);
+    const uint32_t idesc_o = make_idesc_f16(BF16 ? 1 : 0, 0, 1, TILE, HD);
+    const uint64_t q_desc = make_smem_desc_sw128(smem_u32(sQ), 16, 1024);
+    const uint64_t k_desc0 = make_smem_desc_sw128(smem_u32(sKV), 16, 1024);                 // K-major (S = Q K^T)
+    const uint64_t v_desc0 = make_smem_desc_sw128(smem_u32(sKV), Cfg::CHUNK_BYTES, 1024);   // MN-major (O = P V)
+    // Ring order is K0 V0 K1 V1 ...: tile i (K of block i/2 when even, V when odd) sits in slot i % SLOTS
+    // and completes phase (i / SLOTS) & 1 of that slot's barriers.
+    bool ok = mbar_wait_warp(q_full, 0, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
+    auto issue_s = [&](int j) -> bool {
+      const int i = 2 * j, slot = i % Cfg::SLOTS;
+      if (!mbar_wait_warp(&kv_full[slot], (i / Cfg::SLOTS) & 1, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL)) return false;
+      tc_fence_after();
+      if (leader) {
+        const uint64_t k_desc = k_desc0 + ((slot * Cfg::TILE_BYTES) >> 4);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * Cfg::CHUNK_BYTES + (kk & 3) * 32;
-          tc_mma_f16(tS, make_smem_desc_sw128(q_addr + off, 16, 1024), make_smem_desc_sw128(k_addr + off, 16, 1024),
-                     idesc_s, kk > 0 ? 1u : 0u);
+          const uint32_t off = ((kk >> 2) * Cfg::CHUNK_BYTES + (kk & 3) * 32) >> 4;
+          tc_mma_f16(tS, q_desc + off, k_desc + off, idesc_s, kk > 0 ? 1u : 0u);
         }
         tc_commit(&kv_empty[slot]);
         tc_commit(s_full);
-        if (++slot == Cfg::SLOTS) { slot = 0; phase ^= 1; }
-        return true;
-      };
-      if (ok) ok = issue_s();
-      for (int j = 0; j < n_kv && ok; ++j) {
-        ok = mbar_wait(p_full, j & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
-        if (!ok) break;
-        if (j > 0) {
-          ok = mbar_wait(o_empty, (j - 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
-          if (!ok) break;
-        }
-        ok = mbar_wait(&kv_full[slot], phase, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t v_addr = smem_u32(sKV + slot * Cfg::TILE_BYTES);
+      }
+      __syncwarp();
+      return true;
+    };
+    if (ok) ok = issue_s(0);
+    for (int j = 0; j < n_kv && ok; ++j) {
+      // p_full(j): every softmax thread has read S(j), written P(j) and finished any rescale of O.
+      ok = mbar_wait_warp(p_full, j & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
+      if (!ok) break;
+      const bool mprof = p.prof != nullptr && lane == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j < 32;
+      if (mprof) p.prof[j * 8 + 3] = clock64();
+      // The softmax warps are idle until the next score tile exists, so it goes first; P V (j) then runs
+      // under their first pass over S(j+1).
+      if (j + 1 < n_kv) ok = issue_s(j + 1);
+      if (!ok) break;
+      if (mprof) p.prof[j * 8 + 5] = clock64();
+      const int i = 2 * j + 1, slot = i % Cfg::SLOTS;
+      ok = mbar_wait_warp(&kv_full[slot], (i / Cfg::SLOTS) & 1, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
+      if (!ok) break;
+      tc_fence_after();
+      if (leader) {
+        const uint64_t v_desc = v_desc0 + ((slot * Cfg::TILE_BYTES) >> 4);
 #pragma unroll
-        for (int kk = 0; kk < TILE / 16; ++kk) {
-          const uint32_t a_off = (kk >> 2) * Cfg::CHUNK_BYTES + (kk & 3) * 32;
-          tc_mma_f16(tO, make_smem_desc_sw128(p_addr + a_off, 16, 1024),
-                     make_smem_desc_sw128(v_addr + kk * 2048, Cfg::CHUNK_BYTES, 1024), idesc_o, kk > 0 ? 1u : 0u);
-        }
+        for (int kk = 0; kk < TILE / 16; ++kk)  // O += P V: P read from TMEM (8 columns per K = 16), O accumulated there
+          tc_mma_f16_ts(tO, tP + kk * 8, v_desc + ((kk * 2048) >> 4), idesc_o, (kk > 0 || j > 0) ? 1u : 0u);
         tc_commit(&kv_empty[slot]);
         tc_commit(o_full);
-        if (++slot == Cfg::SLOTS) { slot = 0; phase ^= 1; }
-        if (j + 1 < n_kv) ok = issue_s();
       }
+      __syncwarp();
+      if (mprof) p.prof[j * 8 + 7] = clock64();
     }
   } else {
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;       // row inside the q tile == TMEM lane
     const int q_idx = qb * TILE + row;         // position in the sequence
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    // m_run is the reference maximum used for P and l; it may lag the true running maximum by up to
+    // RESCALE_LOG2 (so P <= 2^RESCALE_LOG2), which keeps rescales of the TMEM accumulator rare.
+    constexpr float RESCALE_LOG2 = 8.f;
     float m_run = -INFINITY, l_run = 0.f;
-    float acc[HD];
-#pragma unroll
-    for (int i = 0; i < HD; ++i) acc[i] = 0.f;
     bool ok = true;
     for (int j = 0; j < n_kv && ok; ++j) {
       ok = mbar_wait_warp(s_full, j & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
@@ -229,18 +237,43 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
               if (c * 32 + i < limit) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(r[c & 1][i]));
           } else {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(r[c & 1][i]));
+            for (int i = 0; i < 16; ++i)
+              m4[i & 3] = fmax3(m4[i & 3], __uint_as_float(r[c & 1][2 * i]), __uint_as_float(r[c & 1][2 * i + 1]));
           }
         }
         mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
       }
       if (prof_on) p.prof[j * 8 + 1] = clock64();
       const float m_new = fmaxf(m_run, mx * p.scale_log2);
+      if (j == 0) {
+        m_run = m_new;  // the first P V product overwrites O: nothing to rescale
+      } else {
+        // P V (j-1) was issued after S(j); it must have completed before P(j) overwrites its operand or O
+        // is rescaled.  It ran under the pass above, so this wait is normally already satisfied.
+        ok = mbar_wait_warp(o_full, (j - 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
+        if (!ok) break;
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, m_new - m_run > RESCALE_LOG2)) {
+          const float alpha = (m_new == -INFINITY) ? 1.f : exp2f(m_run - m_new);
+#pragma unroll 1
+          for (int c = 0; c < HD / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(tO + lane_off + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st_32x32(tO + lane_off + c * 32, r);
+          }
+          l_run *= alpha;
+          m_run = m_new;
+        }
+      }
       // A row with nothing to attend to yet (only rows past T) keeps m = -inf; guard the subtraction.
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = exp2f(m_run - m_use);
+      const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
       float psum;
       float ps4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint64_t ps2[2] = {0ull, 0ull};  // packed pairs of partial sums (unmasked path)
+      const uint64_t scale2 = f2_pack(p.scale_log2, p.scale_log2), neg_m2 = f2_pack(-m_use, -m_use);
       {
         uint32_t r[2][32];
         tmem_ld_32x32(tS + lane_off, r[0]);
@@ -262,64 +295,53 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           } else {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-              const float a = MSQ_EXP2(fmaf(__uint_as_float(r[c & 1][2 * i]), p.scale_log2, -m_use));
-              const float bb = MSQ_EXP2(fmaf(__uint_as_float(r[c & 1][2 * i + 1]), p.scale_log2, -m_use));
-              ps4[i & 3] += a + bb;
+              float x0, x1;
+              f2_unpack(f2_fma(f2_pack_bits(r[c & 1][2 * i], r[c & 1][2 * i + 1]), scale2, neg_m2), x0, x1);
+              const float a = exp2f(x0), bb = exp2f(x1);
+              ps2[i & 1] = f2_add(ps2[i & 1], f2_pack(a, bb));
               packed[i] = pack2<BF16>(a, bb);
             }
           }
-          uint8_t* chunk = sP + (c >> 1) * Cfg::CHUNK_BYTES;
-#ifndef MSQ_EXPERIMENT_NO_STS
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const uint4 v4 = make_uint4(packed[4 * u], packed[4 * u + 1], packed[4 * u + 2], packed[4 * u + 3]);
-            *reinterpret_cast<uint4*>(chunk + sw128_offset(row, (c & 1) * 4 + u)) = v4;
-          }
-#else
-          if (packed[0] == 0x12345678u) *reinterpret_cast<uint32_t*>(chunk) = packed[1] ^ packed[15] ^ packed[7];
-#endif
+          tmem_st_32x16(tP + lane_off + c * 16, packed);  // row = lane, two 16-bit probabilities per column
         }
       }
-      psum = (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
-      l_run = l_run * alpha + psum;
-      m_run = m_new;
+      {
+        float s0, s1, s2, s3;
+        f2_unpack(ps2[0], s0, s1);
+        f2_unpack(ps2[1], s2, s3);
+        psum = ((ps4[0] + ps4[1]) + (ps4[2] + ps4[3])) + ((s0 + s1) + (s2 + s3));
+      }
+      l_run += psum;
+      tmem_st_wait();
       if (prof_on) p.prof[j * 8 + 2] = clock64();
       tc_fence_before();
-      fence_proxy_async_smem();
       mbar_arrive(p_full);
-      ok = mbar_wait_warp(o_full, j & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
-      if (!ok) break;
-      tc_fence_after();
-      if (prof_on) p.prof[j * 8 + 3] = clock64();
-      {
-        uint32_t r[2][32];
-        tmem_ld_32x32(tO + lane_off, r[0]);
-#pragma unroll
-        for (int c = 0; c < HD / 32; ++c) {
-          tmem_ld_wait();
-          if (c + 1 < HD / 32) tmem_ld_32x32(tO + lane_off + (c + 1) * 32, r[(c + 1) & 1]);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(acc[c * 32 + i], alpha, __uint_as_float(r[c & 1][i]));
-        }
-      }
-      if (prof_on) p.prof[j * 8 + 4] = clock64();
-      tc_fence_before();
-      mbar_arrive(o_empty);
     }
-    if (ok && q_idx < p.T) {
+    if (ok) ok = mbar_wait_warp(o_full, (n_kv - 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
+    tc_fence_after();
+    if (ok) {
       const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
       uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + static_cast<long long>(b) * p.o_batch_stride +
-                    static_cast<long long>(q_idx) * p.o_row_stride + h * HD;
+                    static_cast<long long>(q_idx < p.T ? q_idx : 0) * p.o_row_stride + h * HD;
+      uint32_t r[2][32];
+      tmem_ld_32x32(tO + lane_off, r[0]);
 #pragma unroll
-      for (int v = 0; v < HD / 8; ++v) {
-        uint4 ov;
-        ov.x = pack2<BF16>(acc[v * 8 + 0] * inv_l, acc[v * 8 + 1] * inv_l);
-        ov.y = pack2<BF16>(acc[v * 8 + 2] * inv_l, acc[v * 8 + 3] * inv_l);
-        ov.z = pack2<BF16>(acc[v * 8 + 4] * inv_l, acc[v * 8 + 5] * inv_l);
-        ov.w = pack2<BF16>(acc[v * 8 + 6] * inv_l, acc[v * 8 + 7] * inv_l);
-        *reinterpret_cast<uint4*>(o + v * 8) = ov;
+      for (int c = 0; c < HD / 32; ++c) {
+        tmem_ld_wait();
+        if (c + 1 < HD / 32) tmem_ld_32x32(tO + lane_off + (c + 1) * 32, r[(c + 1) & 1]);
+        if (q_idx < p.T) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 ov;
+            ov.x = pack2<BF16>(__uint_as_float(r[c & 1][v * 8 + 0]) * inv_l, __uint_as_float(r[c & 1][v * 8 + 1]) * inv_l);
+            ov.y = pack2<BF16>(__uint_as_float(r[c & 1][v * 8 + 2]) * inv_l, __uint_as_float(r[c & 1][v * 8 + 3]) * inv_l);
+            ov.z = pack2<BF16>(__uint_as_float(r[c & 1][v * 8 + 4]) * inv_l, __uint_as_float(r[c & 1][v * 8 + 5]) * inv_l);
+            ov.w = pack2<BF16>(__uint_as_float(r[c & 1][v * 8 + 6]) * inv_l, __uint_as_float(r[c & 1][v * 8 + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(o + c * 32 + v * 8) = ov;
+          }
+        }
       }
-      if (p.lse) p.lse[(static_cast<long long>(b) * p.H + h) * p.T + q_idx] = (m_run + log2f(l_run)) * LN2;
+      if (p.lse && q_idx < p.T) p.lse[(static_cast<long long>(b) * p.H + h) * p.T + q_idx] = (m_run + log2f(l_run)) * LN2;
     }
   }
 
@@ -354,23 +376,19 @@ struct BwdCfg {
   static constexpr uint32_t CHUNK_BYTES = TILE * 128;
   static constexpr int QSTAGES = (HD == 64) ? 2 : 1;
   static constexpr uint32_t P_BYTES = TILE * TILE * 2;
-  static constexpr uint32_t SMEM = TILE_BYTES * (2 + 2 * QSTAGES) + 2 * P_BYTES + 1024 + 256;
+  static constexpr uint32_t STAGE_BYTES = 8 * 4096;  // one 32 x 32 fp32 box per element-wise warp
+  static constexpr uint32_t SMEM = TILE_BYTES * (2 + 2 * QSTAGES) + 2 * P_BYTES + STAGE_BYTES + 1024 + 256;
   static constexpr uint32_t TMEM_COLS = 512;
   static constexpr uint32_t S_COL = 0, DP_COL = 128, DV_COL = 256, DK_COL = 256 + HD;
   static constexpr uint32_t DQ_COL = (HD == 64) ? 384 : 0;  // HD = 128 reuses the S columns
   static constexpr bool DQ_ALIASES_S = (HD != 64);
 };
 
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
-               : "memory");
-}
-
 template <int HD, bool BF16>
-__global__ void __launch_bounds__(ATT_THREADS, 1)
+__global__ void __launch_bounds__(ATT_BWD_THREADS, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
-                 const AttnBwdParams p) {
+                 const __grid_constant__ CUtensorMap tmDQ, const AttnBwdParams p) {
   using Cfg = BwdCfg<HD>;
   constexpr int QS = Cfg::QSTAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -381,7 +399,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint8_t* sDO = sQ + QS * Cfg::TILE_BYTES;
   uint8_t* sP = sDO + QS * Cfg::TILE_BYTES;
   uint8_t* sDS = sP + Cfg::P_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + Cfg::P_BYTES);
+  uint8_t* sStage = sDS + Cfg::P_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sStage + Cfg::STAGE_BYTES);
   uint64_t* kv_full = bars;
   uint64_t* qdo_full = bars + 1;
   uint64_t* qdo_empty = qdo_full + QS;
@@ -389,7 +408,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* pds_full = sdp_full + 1;
   uint64_t* dq_full = pds_full + 1;
   uint64_t* dq_empty = dq_full + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_empty + 1);
+  uint64_t* dkv_full = dq_empty + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dkv_full + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -408,9 +428,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_init(&qdo_empty[s], 1);
     }
     mbar_init(sdp_full, 1);
-    mbar_init(pds_full, 128);
+    mbar_init(pds_full, 256);
     mbar_init(dq_full, 1);
-    mbar_init(dq_empty, 128);
+    mbar_init(dq_empty, 256);
+    mbar_init(dkv_full, 1);
     *abort_flag = 0;
     mbar_fence_init();
     fence_proxy_async_smem();
@@ -455,75 +476,92 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      const int dt = BF16 ? 1 : 0;
-      const uint32_t idesc_s = make_idesc_f16(dt, 0, 0, TILE, TILE);   // Q K^T and dO V^T
-      const uint32_t idesc_t = make_idesc_f16(dt, 1, 1, TILE, HD);     // P^T dO and dS^T Q
-      const uint32_t idesc_q = make_idesc_f16(dt, 0, 1, TILE, HD);     // dS K
-      const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), p_addr = smem_u32(sP), ds_addr = smem_u32(sDS);
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
-      for (int it = 0; it < n_it && ok; ++it) {
-        ok = mbar_wait(&qdo_full[stage], phase, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
+    // Whole-warp control flow, one elected issuing lane, descriptors built once (see the forward kernel).
+    const bool leader = elect_one();
+    const int dt = BF16 ? 1 : 0;
+    const uint32_t idesc_s = make_idesc_f16(dt, 0, 0, TILE, TILE);   // Q K^T and dO V^T
+    const uint32_t idesc_t = make_idesc_f16(dt, 1, 1, TILE, HD);     // P^T dO and dS^T Q
+    const uint32_t idesc_q = make_idesc_f16(dt, 0, 1, TILE, HD);     // dS K
+    const uint64_t k_km = make_smem_desc_sw128(smem_u32(sK), 16, 1024);
+    const uint64_t v_km = make_smem_desc_sw128(smem_u32(sV), 16, 1024);
+    const uint64_t k_mn = make_smem_desc_sw128(smem_u32(sK), Cfg::CHUNK_BYTES, 1024);
+    const uint64_t p_mn = make_smem_desc_sw128(smem_u32(sP), Cfg::CHUNK_BYTES, 1024);
+    const uint64_t ds_mn = make_smem_desc_sw128(smem_u32(sDS), Cfg::CHUNK_BYTES, 1024);
+    const uint64_t ds_km = make_smem_desc_sw128(smem_u32(sDS), 16, 1024);
+    const uint64_t q_km0 = make_smem_desc_sw128(smem_u32(sQ), 16, 1024);
+    const uint64_t q_mn0 = make_smem_desc_sw128(smem_u32(sQ), Cfg::CHUNK_BYTES, 1024);
+    const uint64_t do_km0 = make_smem_desc_sw128(smem_u32(sDO), 16, 1024);
+    const uint64_t do_mn0 = make_smem_desc_sw128(smem_u32(sDO), Cfg::CHUNK_BYTES, 1024);
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = mbar_wait_warp(kv_full, 0, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
+    for (int it = 0; it < n_it && ok; ++it) {
+      ok = mbar_wait_warp(&qdo_full[stage], phase, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
+      if (!ok) break;
+      if (Cfg::DQ_ALIASES_S && it > 0) {
+        ok = mbar_wait_warp(dq_empty, (it - 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
         if (!ok) break;
-        if (Cfg::DQ_ALIASES_S && it > 0) {
-          ok = mbar_wait(dq_empty, (it - 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
-          if (!ok) break;
-        }
-        tc_fence_after();
-        const uint32_t q_addr = smem_u32(sQ + stage * Cfg::TILE_BYTES);
-        const uint32_t do_addr = smem_u32(sDO + stage * Cfg::TILE_BYTES);
+      }
+      tc_fence_after();
+      const uint32_t st_off = (stage * Cfg::TILE_BYTES) >> 4;
+      if (leader) {
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * Cfg::CHUNK_BYTES + (kk & 3) * 32;
-          tc_mma_f16(tmem_base + Cfg::S_COL, make_smem_desc_sw128(q_addr + off, 16, 1024),
-                     make_smem_desc_sw128(k_addr + off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+          const uint32_t off = ((kk >> 2) * Cfg::CHUNK_BYTES + (kk & 3) * 32) >> 4;
+          tc_mma_f16(tmem_base + Cfg::S_COL, q_km0 + st_off + off, k_km + off, idesc_s, kk > 0 ? 1u : 0u);
         }
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * Cfg::CHUNK_BYTES + (kk & 3) * 32;
-          tc_mma_f16(tmem_base + Cfg::DP_COL, make_smem_desc_sw128(do_addr + off, 16, 1024),
-                     make_smem_desc_sw128(v_addr + off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+          const uint32_t off = ((kk >> 2) * Cfg::CHUNK_BYTES + (kk & 3) * 32) >> 4;
+          tc_mma_f16(tmem_base + Cfg::DP_COL, do_km0 + st_off + off, v_km + off, idesc_s, kk > 0 ? 1u : 0u);
         }
         tc_commit(sdp_full);
-        ok = mbar_wait(pds_full, it & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
+      }
+      __syncwarp();
+      ok = mbar_wait_warp(pds_full, it & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
+      if (!ok) break;
+      if (!Cfg::DQ_ALIASES_S && it > 0) {
+        ok = mbar_wait_warp(dq_empty, (it - 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
         if (!ok) break;
-        if (!Cfg::DQ_ALIASES_S && it > 0) {
-          ok = mbar_wait(dq_empty, (it - 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
-          if (!ok) break;
-        }
-        tc_fence_after();
+      }
+      tc_fence_after();
+      if (leader) {
         const uint32_t acc = it > 0 ? 1u : 0u;
+        // dQ first: the element-wise warps are waiting for it, while dV / dK only accumulate
+#pragma unroll
+        for (int kk = 0; kk < TILE / 16; ++kk) {  // dQ = dS K      (K = kv rows)
+          const uint32_t a_off = ((kk >> 2) * Cfg::CHUNK_BYTES + (kk & 3) * 32) >> 4;
+          tc_mma_f16(tmem_base + Cfg::DQ_COL, ds_km + a_off, k_mn + ((kk * 2048) >> 4), idesc_q, kk > 0 ? 1u : 0u);
+        }
+        tc_commit(dq_full);
 #pragma unroll
         for (int kk = 0; kk < TILE / 16; ++kk) {  // dV += P^T dO   (K = q rows)
-          tc_mma_f16(tmem_base + Cfg::DV_COL, make_smem_desc_sw128(p_addr + kk * 2048, Cfg::CHUNK_BYTES, 1024),
-                     make_smem_desc_sw128(do_addr + kk * 2048, Cfg::CHUNK_BYTES, 1024), idesc_t,
-                     (kk > 0) ? 1u : acc);
+          const uint32_t off = (kk * 2048) >> 4;
+          tc_mma_f16(tmem_base + Cfg::DV_COL, p_mn + off, do_mn0 + st_off + off, idesc_t, (kk > 0) ? 1u : acc);
         }
 #pragma unroll
         for (int kk = 0; kk < TILE / 16; ++kk) {  // dK += dS^T Q
-          tc_mma_f16(tmem_base + Cfg::DK_COL, make_smem_desc_sw128(ds_addr + kk * 2048, Cfg::CHUNK_BYTES, 1024),
-                     make_smem_desc_sw128(q_addr + kk * 2048, Cfg::CHUNK_BYTES, 1024), idesc_t,
-                     (kk > 0) ? 1u : acc);
-        }
-#pragma unroll
-        for (int kk = 0; kk < TILE / 16; ++kk) {  // dQ = dS K      (K = kv rows)
-          const uint32_t a_off = (kk >> 2) * Cfg::CHUNK_BYTES + (kk & 3) * 32;
-          tc_mma_f16(tmem_base + Cfg::DQ_COL, make_smem_desc_sw128(ds_addr + a_off, 16, 1024),
-                     make_smem_desc_sw128(k_addr + kk * 2048, Cfg::CHUNK_BYTES, 1024), idesc_q, kk > 0 ? 1u : 0u);
+          const uint32_t off = (kk * 2048) >> 4;
+          tc_mma_f16(tmem_base + Cfg::DK_COL, ds_mn + off, q_mn0 + st_off + off, idesc_t, (kk > 0) ? 1u : acc);
         }
         tc_commit(&qdo_empty[stage]);
-        tc_commit(dq_full);
-        if (++stage == QS) { stage = 0; phase ^= 1; }
+        if (it == n_it - 1) tc_commit(dkv_full);
       }
+      __syncwarp();
+      if (++stage == QS) { stage = 0; phase ^= 1; }
     }
   } else {
-    const int quarter = warp & 3;
+    // Eight warps: warp w owns TMEM lanes / tile rows 32 * (w % 4) .. +31 (the hardware's lane window of
+    // that warp) and the column half (w - 2) / 4 of every tile it reads.
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
     const int row = quarter * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t col0 = half * 64;
     const float scale_log2 = p.scale * LOG2E;
     const long long bh = static_cast<long long>(b) * p.H + h;
+    // dQ staging for the bulk reduce: one swizzled 32-row x 32-column fp32 box per warp
+    constexpr int DQ_BOXES = HD / 64;  // boxes per warp and iteration
+    uint8_t* stage_buf = sStage + (warp - 2) * 4096;
     bool ok = true;
     for (int it = 0; it < n_it && ok; ++it) {
       const int m = m_start + it;
@@ -536,52 +574,63 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       limit = q_ok ? max(0, min(limit, TILE)) : 0;
       // uniform over the CTA: only diagonal blocks and ragged tails (rows or columns past T) need masks
       const bool need_mask = (p.causal && m == nb) || ((m + 1) * TILE > p.T) || ((nb + 1) * TILE > p.T);
-      const bool prof_on = p.prof != nullptr && row == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && it < 32;
+      const bool prof_on = p.prof != nullptr && row == 0 && half == 0 && blockIdx.x == 0 && blockIdx.y == 0 &&
+                           blockIdx.z == 0 && it < 32;
       if (prof_on) p.prof[256 + it * 8 + 0] = clock64();
       ok = mbar_wait_warp(sdp_full, it & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
       if (!ok) break;
       tc_fence_after();
       if (prof_on) p.prof[256 + it * 8 + 1] = clock64();
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      {
         uint32_t s[32], dp[32];
-        tmem_ld_32x32(tmem_base + Cfg::S_COL + lane_off + c * 32, s);
-        tmem_ld_32x32(tmem_base + Cfg::DP_COL + lane_off + c * 32, dp);
-        tmem_ld_wait();
-        uint32_t pp[16], dd[16];
-        if (need_mask) {
+        tmem_ld_32x32(tmem_base + Cfg::S_COL + lane_off + col0, s);
+        tmem_ld_32x32(tmem_base + Cfg::DP_COL + lane_off + col0, dp);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            float p0 = 0.f, p1 = 0.f, d0 = 0.f, d1 = 0.f;
-            if (c * 32 + 2 * i < limit) {
-              p0 = exp2f(fmaf(__uint_as_float(s[2 * i]), scale_log2, -lse2));
-              d0 = p0 * (__uint_as_float(dp[2 * i]) - delta) * p.scale;
+        for (int c = 0; c < 2; ++c) {
+          tmem_ld_wait();
+          uint32_t pp[16], dd[16];
+          const int cbase = col0 + c * 32;
+          if (need_mask) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              float p0 = 0.f, p1 = 0.f, d0 = 0.f, d1 = 0.f;
+              if (cbase + 2 * i < limit) {
+                p0 = exp2f(fmaf(__uint_as_float(s[2 * i]), scale_log2, -lse2));
+                d0 = p0 * (__uint_as_float(dp[2 * i]) - delta) * p.scale;
+              }
+              if (cbase + 2 * i + 1 < limit) {
+                p1 = exp2f(fmaf(__uint_as_float(s[2 * i + 1]), scale_log2, -lse2));
+                d1 = p1 * (__uint_as_float(dp[2 * i + 1]) - delta) * p.scale;
+              }
+              pp[i] = pack2<BF16>(p0, p1);
+              dd[i] = pack2<BF16>(d0, d1);
             }
-            if (c * 32 + 2 * i + 1 < limit) {
-              p1 = exp2f(fmaf(__uint_as_float(s[2 * i + 1]), scale_log2, -lse2));
-              d1 = p1 * (__uint_as_float(dp[2 * i + 1]) - delta) * p.scale;
+          } else {
+            const float nds = -delta * p.scale;
+            const uint64_t sl2 = f2_pack(scale_log2, scale_log2), nl2 = f2_pack(-lse2, -lse2);
+            const uint64_t sc2 = f2_pack(p.scale, p.scale), nds2 = f2_pack(nds, nds);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              float x0, x1, d0, d1;
+              f2_unpack(f2_fma(f2_pack_bits(s[2 * i], s[2 * i + 1]), sl2, nl2), x0, x1);
+              const float p0 = exp2f(x0), p1 = exp2f(x1);
+              const uint64_t g = f2_fma(f2_pack_bits(dp[2 * i], dp[2 * i + 1]), sc2, nds2);
+              f2_unpack(f2_mul(f2_pack(p0, p1), g), d0, d1);
+              pp[i] = pack2<BF16>(p0, p1);
+              dd[i] = pack2<BF16>(d0, d1);
             }
-            pp[i] = pack2<BF16>(p0, p1);
-            dd[i] = pack2<BF16>(d0, d1);
           }
-        } else {
-          const float nds = -delta * p.scale;
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float p0 = exp2f(fmaf(__uint_as_float(s[2 * i]), scale_log2, -lse2));
-            const float p1 = exp2f(fmaf(__uint_as_float(s[2 * i + 1]), scale_log2, -lse2));
-            const float d0 = p0 * fmaf(__uint_as_float(dp[2 * i]), p.scale, nds);
-            const float d1 = p1 * fmaf(__uint_as_float(dp[2 * i + 1]), p.scale, nds);
-            pp[i] = pack2<BF16>(p0, p1);
-            dd[i] = pack2<BF16>(d0, d1);
+          if (c == 0) {  // the second half's loads fly while the first half is stored
+            tmem_ld_32x32(tmem_base + Cfg::S_COL + lane_off + col0 + 32, s);
+            tmem_ld_32x32(tmem_base + Cfg::DP_COL + lane_off + col0 + 32, dp);
           }
-        }
-        const uint32_t chunk_off = (c >> 1) * Cfg::CHUNK_BYTES;
+          const uint32_t chunk_off = half * Cfg::CHUNK_BYTES;
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const uint32_t off = chunk_off + sw128_offset(row, (c & 1) * 4 + u);
-          *reinterpret_cast<uint4*>(sP + off) = make_uint4(pp[4 * u], pp[4 * u + 1], pp[4 * u + 2], pp[4 * u + 3]);
-          *reinterpret_cast<uint4*>(sDS + off) = make_uint4(dd[4 * u], dd[4 * u + 1], dd[4 * u + 2], dd[4 * u + 3]);
+          for (int u = 0; u < 4; ++u) {
+            const uint32_t off = chunk_off + sw128_offset(row, c * 4 + u);
+            *reinterpret_cast<uint4*>(sP + off) = make_uint4(pp[4 * u], pp[4 * u + 1], pp[4 * u + 2], pp[4 * u + 3]);
+            *reinterpret_cast<uint4*>(sDS + off) = make_uint4(dd[4 * u], dd[4 * u + 1], dd[4 * u + 2], dd[4 * u + 3]);
+          }
         }
       }
       if (prof_on) p.prof[256 + it * 8 + 2] = clock64();
@@ -592,40 +641,53 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (!ok) break;
       tc_fence_after();
       if (prof_on) p.prof[256 + it * 8 + 3] = clock64();
-      float* dq_row = p.dq_accum + (static_cast<long long>(b) * p.T + (q_ok ? q_idx : 0)) * (p.H * HD) + h * HD;
-#pragma unroll 1
-      for (int c = 0; c < HD / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_base + Cfg::DQ_COL + lane_off + c * 32, r);
-        tmem_ld_wait();
-        if (q_ok) {
+      // dQ tile of this pair: TMEM -> swizzled fp32 staging -> one bulk add per 32 x 32 box into dq_accum
+      const bool rows_in_range = m * TILE + quarter * 32 < p.T;  // rows past T inside a box are dropped by the copy engine
 #pragma unroll
-          for (int i = 0; i < 8; ++i)
-            red_add_v4(dq_row + c * 32 + i * 4, __uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
-                       __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+      for (int c = 0; c < DQ_BOXES; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + Cfg::DQ_COL + lane_off + half * (HD / 2) + c * 32, r);
+        if (it > 0 || c > 0) {  // the previous bulk add must have read the staging box
+          if (lane == 0) bulk_wait_read_all();
+          __syncwarp();
+        }
+        tmem_ld_wait();
+        uint8_t* dst = stage_buf + lane * 128;
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          *reinterpret_cast<uint4*>(dst + ((u ^ (lane & 7)) << 4)) = make_uint4(r[4 * u], r[4 * u + 1], r[4 * u + 2], r[4 * u + 3]);
+        if (c == DQ_BOXES - 1) {
+          tc_fence_before();
+          mbar_arrive(dq_empty);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (rows_in_range) tma_reduce_add_3d(&tmDQ, stage_buf, h * HD + half * (HD / 2) + c * 32, m * TILE + quarter * 32, b);
+          bulk_commit_group();
         }
       }
       if (prof_on) p.prof[256 + it * 8 + 4] = clock64();
-      tc_fence_before();
-      mbar_arrive(dq_empty);
     }
-    // dK / dV of this kv block are complete once the last dq_full phase has been observed.
+    // dK / dV of this kv block are complete when the products of the last iteration have been committed.
     const int kv_idx = nb * TILE + row;
+    if (ok && n_it > 0) ok = mbar_wait_warp(dkv_full, 0, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
+    tc_fence_after();
     if (ok && n_it > 0) {
       // The TMEM loads are warp-wide (.sync.aligned): every lane runs them; only the
       // global stores are predicated on the row being inside the sequence.
       const bool kv_ok = kv_idx < p.T;
       const long long kv_row = kv_ok ? kv_idx : 0;
       uint16_t* dk = reinterpret_cast<uint16_t*>(p.dk) + static_cast<long long>(b) * p.dk_batch_stride +
-                     kv_row * p.dk_row_stride + h * HD;
+                     kv_row * p.dk_row_stride + h * HD + half * (HD / 2);
       uint16_t* dv = reinterpret_cast<uint16_t*>(p.dv) + static_cast<long long>(b) * p.dv_batch_stride +
-                     kv_row * p.dv_row_stride + h * HD;
+                     kv_row * p.dv_row_stride + h * HD + half * (HD / 2);
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {
         uint16_t* dst = which ? dv : dk;
-        const uint32_t col = which ? Cfg::DV_COL : Cfg::DK_COL;
+        const uint32_t col = (which ? Cfg::DV_COL : Cfg::DK_COL) + half * (HD / 2);
 #pragma unroll 1
-        for (int c = 0; c < HD / 32; ++c) {
+        for (int c = 0; c < HD / 64; ++c) {
           uint32_t r[32];
           tmem_ld_32x32(tmem_base + col + lane_off + c * 32, r);
           tmem_ld_wait();
@@ -643,6 +705,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
       }
     }
+    // shared memory must outlive the bulk reduces that read it
+    if (lane == 0) bulk_wait_all();
   }
 
   tc_fence_before();
@@ -706,7 +770,7 @@ static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
 
 template <int HD, bool BF16>
 static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
-                      const AttnBwdParams& p, int B, cudaStream_t stream) {
+                      const CUtensorMap& tdq, const AttnBwdParams& p, int B, cudaStream_t stream) {
   auto kern = flash_bwd_kernel<HD, BF16>;
   static bool configured = false;
   if (!configured) {
@@ -715,7 +779,7 @@ static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
     configured = true;
   }
   dim3 grid((p.T + TILE - 1) / TILE, p.H, B);
-  kern<<<grid, ATT_THREADS, BwdCfg<HD>::SMEM, stream>>>(tq, tk, tv, tdo, p);
+  kern<<<grid, ATT_BWD_THREADS, BwdCfg<HD>::SMEM, stream>>>(tq, tk, tv, tdo, tdq, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -768,6 +832,16 @@ extern "C" int msq_flash_bwd(const void* q, const void* k, const void* v, const 
   if ((rc = make_tmap_btc(&tk, k, B, T, static_cast<long long>(H) * HD, k_rs, k_bs, bf16))) return rc;
   if ((rc = make_tmap_btc(&tv, v, B, T, static_cast<long long>(H) * HD, v_rs, v_bs, bf16))) return rc;
   if ((rc = make_tmap_btc(&tdo, d_out, B, T, static_cast<long long>(H) * HD, do_rs, do_bs, bf16))) return rc;
+  CUtensorMap tdq;
+  {
+    // fp32 [B, T, H*HD] accumulator, reduced into by 32-row x 32-column boxes
+    if (reinterpret_cast<uintptr_t>(dq_accum) & 15) return -2;
+    const cuuint64_t cols = static_cast<cuuint64_t>(H) * HD;
+    cuuint64_t dims[3] = {cols, static_cast<cuuint64_t>(T), static_cast<cuuint64_t>(B)};
+    cuuint64_t strides[2] = {cols * 4, cols * 4 * static_cast<cuuint64_t>(T)};
+    cuuint32_t box[3] = {32u, 32u, 1u};
+    if (encode_tiled(&tdq, dq_accum, 3, dims, strides, box, CU_TENSOR_MAP_DATA_TYPE_FLOAT32) != CUDA_SUCCESS) return -3;
+  }
   {
     const long long warps = static_cast<long long>(B) * T * H;
     const int threads = 256;
@@ -785,6 +859,6 @@ extern "C" int msq_flash_bwd(const void* q, const void* k, const void* v, const 
   p.T = T; p.H = H; p.scale = scale; p.causal = causal; p.bf16 = bf16; p.status = status;
   p.prof = g_attn_prof;
   if (HD == 64)
-    return bf16 ? launch_bwd<64, true>(tq, tk, tv, tdo, p, B, stream) : launch_bwd<64, false>(tq, tk, tv, tdo, p, B, stream);
-  return bf16 ? launch_bwd<128, true>(tq, tk, tv, tdo, p, B, stream) : launch_bwd<128, false>(tq, tk, tv, tdo, p, B, stream);
+    return bf16 ? launch_bwd<64, true>(tq, tk, tv, tdo, tdq, p, B, stream) : launch_bwd<64, false>(tq, tk, tv, tdo, tdq, p, B, stream);
+  return bf16 ? launch_bwd<128, true>(tq, tk, tv, tdo, tdq, p, B, stream) : launch_bwd<128, false>(tq, tk, tv, tdo, tdq, p, B, stream);
 }
