@@ -717,29 +717,38 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
 }
 
-// delta[b, h, t] = sum_d dO[b, t, h, d] * O[b, t, h, d]; one warp per (b, t, h).
-template <bool BF16>
-__global__ void attn_delta_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o, long long row_stride,
-                                  long long batch_stride, float* __restrict__ delta, int B, int T, int H, int HD) {
-  const long long gw = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
+// delta[b, h, t] = sum_d dO[b, t, h, d] * O[b, t, h, d].  HD / 8 adjacent lanes own one (b, t, h) row and
+// load 16 bytes each, so a warp reads 512 contiguous bytes of a token row from each tensor.
+template <bool BF16, int HD>
+__global__ void __launch_bounds__(256)
+attn_delta_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o, long long row_stride,
+                  long long batch_stride, float* __restrict__ delta, int B, int T, int H) {
+  constexpr int LPG = HD / 8;  // lanes per row
+  const long long gt = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long item = gt / LPG;
+  const int sub = static_cast<int>(gt % LPG);
   const long long total = static_cast<long long>(B) * T * H;
-  if (gw >= total) return;
-  const int hh = static_cast<int>(gw % H);
-  const long long bt = gw / H;
-  const int t = static_cast<int>(bt % T);
-  const int bb = static_cast<int>(bt / T);
-  const long long off = static_cast<long long>(bb) * batch_stride + static_cast<long long>(t) * row_stride + hh * HD;
-  const uint32_t* po = reinterpret_cast<const uint32_t*>(o + off);
-  const uint32_t* pd = reinterpret_cast<const uint32_t*>(d_o + off);
   float s = 0.f;
-  for (int i = lane; i < HD / 2; i += 32) {
-    const float2 a = unpack2<BF16>(po[i]);
-    const float2 g = unpack2<BF16>(pd[i]);
-    s += a.x * g.x + a.y * g.y;
+  int hh = 0, t = 0, bb = 0;
+  if (item < total) {
+    hh = static_cast<int>(item % H);
+    const long long bt = item / H;
+    t = static_cast<int>(bt % T);
+    bb = static_cast<int>(bt / T);
+    const long long off = static_cast<long long>(bb) * batch_stride + static_cast<long long>(t) * row_stride + hh * HD + sub * 8;
+    const uint4 a = *reinterpret_cast<const uint4*>(o + off);
+    const uint4 g = *reinterpret_cast<const uint4*>(d_o + off);
+    const uint32_t av[4] = {a.x, a.y, a.z, a.w}, gv[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 x = unpack2<BF16>(av[i]);
+      const float2 y = unpack2<BF16>(gv[i]);
+      s += x.x * y.x + x.y * y.y;
+    }
   }
-  s = warp_sum(s);
-  if (lane == 0) delta[(static_cast<long long>(bb) * H + hh) * T + t] = s;
+#pragma unroll
+  for (int m = LPG / 2; m > 0; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
+  if (item < total && sub == 0) delta[(static_cast<long long>(bb) * H + hh) * T + t] = s;
 }
 
 // ---------------------------------------------------------------------- host
@@ -843,15 +852,19 @@ extern "C" int msq_flash_bwd(const void* q, const void* k, const void* v, const 
     if (encode_tiled(&tdq, dq_accum, 3, dims, strides, box, CU_TENSOR_MAP_DATA_TYPE_FLOAT32) != CUDA_SUCCESS) return -3;
   }
   {
-    const long long warps = static_cast<long long>(B) * T * H;
+    const long long nthreads = static_cast<long long>(B) * T * H * (HD / 8);
     const int threads = 256;
-    const long long blocks = (warps * 32 + threads - 1) / threads;
-    if (bf16)
-      attn_delta_kernel<true><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(
-          static_cast<const uint16_t*>(out), static_cast<const uint16_t*>(d_out), o_rs, o_bs, delta, B, T, H, HD);
-    else
-      attn_delta_kernel<false><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(
-          static_cast<const uint16_t*>(out), static_cast<const uint16_t*>(d_out), o_rs, o_bs, delta, B, T, H, HD);
+    const unsigned blocks = static_cast<unsigned>((nthreads + threads - 1) / threads);
+    const uint16_t* po = static_cast<const uint16_t*>(out);
+    const uint16_t* pd = static_cast<const uint16_t*>(d_out);
+    if ((reinterpret_cast<uintptr_t>(out) & 15) || (reinterpret_cast<uintptr_t>(d_out) & 15) || (o_rs & 7) || (o_bs & 7)) return -2;
+    if (HD == 64) {
+      if (bf16) attn_delta_kernel<true, 64><<<blocks, threads, 0, stream>>>(po, pd, o_rs, o_bs, delta, B, T, H);
+      else attn_delta_kernel<false, 64><<<blocks, threads, 0, stream>>>(po, pd, o_rs, o_bs, delta, B, T, H);
+    } else {
+      if (bf16) attn_delta_kernel<true, 128><<<blocks, threads, 0, stream>>>(po, pd, o_rs, o_bs, delta, B, T, H);
+      else attn_delta_kernel<false, 128><<<blocks, threads, 0, stream>>>(po, pd, o_rs, o_bs, delta, B, T, H);
+    }
   }
   AttnBwdParams p;
   p.lse = lse; p.delta = delta; p.dq_accum = dq_accum; p.dk = dk; p.dv = dv;

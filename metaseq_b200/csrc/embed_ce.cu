@@ -112,6 +112,27 @@ __global__ void fold_fp32_kernel(const float* __restrict__ src, uint16_t* __rest
   }
 }
 
+// dst16[r, c] = src32[r, c]: contiguous fp32 rows to 16-bit rows of a strided view, 8 elements per thread.
+template <bool BF16>
+__global__ void convert_rows_kernel(const float* __restrict__ src, uint16_t* __restrict__ dst, long long rows,
+                                    int cols, long long dst_ld) {
+  const int vec_per_row = cols >> 3;
+  const long long total = rows * vec_per_row;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const long long r = i / vec_per_row;
+    const int v = static_cast<int>(i - r * vec_per_row);
+    const float4 a = *reinterpret_cast<const float4*>(src + r * cols + v * 8);
+    const float4 b = *reinterpret_cast<const float4*>(src + r * cols + v * 8 + 4);
+    uint4 o;
+    o.x = pack2<BF16>(a.x, a.y);
+    o.y = pack2<BF16>(a.z, a.w);
+    o.z = pack2<BF16>(b.x, b.y);
+    o.w = pack2<BF16>(b.z, b.w);
+    *reinterpret_cast<uint4*>(dst + r * dst_ld + v * 8) = o;
+  }
+}
+
 // ------------------------------------------------------------ cross entropy
 // One CTA per row.  The row (V 16-bit logits) is staged in shared memory, so
 // HBM sees one read and, when the gradient is requested, one write.
@@ -279,6 +300,19 @@ extern "C" int msq_fold_fp32(const float* src, void* dst, long long n, int accum
   if (blocks > 148 * 32) blocks = 148 * 32;
   if (bf16) fold_fp32_kernel<true><<<static_cast<int>(blocks), 256, 0, stream>>>(src, static_cast<uint16_t*>(dst), n, accumulate);
   else fold_fp32_kernel<false><<<static_cast<int>(blocks), 256, 0, stream>>>(src, static_cast<uint16_t*>(dst), n, accumulate);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// src: contiguous fp32 [rows, cols]; dst: 16-bit [rows, cols] with row stride dst_ld (elements).
+extern "C" int msq_convert_rows(const float* src, void* dst, long long rows, int cols, long long dst_ld, int bf16,
+                                cudaStream_t stream) {
+  using namespace msq;
+  if (rows <= 0 || cols <= 0) return 0;
+  if ((cols & 7) || (dst_ld & 7) || (reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 15)) return -2;
+  long long blocks = (rows * (cols >> 3) + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (bf16) convert_rows_kernel<true><<<static_cast<int>(blocks), 256, 0, stream>>>(src, static_cast<uint16_t*>(dst), rows, cols, dst_ld);
+  else convert_rows_kernel<false><<<static_cast<int>(blocks), 256, 0, stream>>>(src, static_cast<uint16_t*>(dst), rows, cols, dst_ld);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

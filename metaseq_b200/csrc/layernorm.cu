@@ -178,19 +178,32 @@ layernorm_bwd_kernel(const uint16_t* __restrict__ dy, const uint16_t* __restrict
   }
 }
 
-// One thread per column: sums `parts` partial rows, then writes (or adds to) the
-// 16-bit gradient.
+// Sums `parts` partial rows per column, then writes (or adds to) the 16-bit gradient.  A CTA owns 32
+// columns; its 8 warps each sum every 8th partial row (coalesced 128-byte reads) and the eight
+// partial results meet in shared memory.
 template <bool BF16>
-__global__ void layernorm_bwd_finalize(const float* __restrict__ part_g, const float* __restrict__ part_b, int parts,
-                                       int D, uint16_t* __restrict__ dgamma, uint16_t* __restrict__ dbeta,
-                                       int accumulate) {
-  const int col = blockIdx.x * blockDim.x + threadIdx.x;
-  if (col >= D) return;
-  float sg = 0.f, sb = 0.f;
-  for (int p = 0; p < parts; ++p) {
-    sg += part_g[static_cast<long long>(p) * D + col];
-    sb += part_b[static_cast<long long>(p) * D + col];
+__global__ void __launch_bounds__(256)
+layernorm_bwd_finalize(const float* __restrict__ part_g, const float* __restrict__ part_b, int parts,
+                       int D, uint16_t* __restrict__ dgamma, uint16_t* __restrict__ dbeta,
+                       int accumulate) {
+  __shared__ float red_g[8][33], red_b[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int col = blockIdx.x * 32 + tx;
+  float ag = 0.f, ab = 0.f;
+  if (col < D) {
+#pragma unroll 4
+    for (int p = ty; p < parts; p += 8) {
+      ag += part_g[static_cast<long long>(p) * D + col];
+      ab += part_b[static_cast<long long>(p) * D + col];
+    }
   }
+  red_g[ty][tx] = ag;
+  red_b[ty][tx] = ab;
+  __syncthreads();
+  if (ty != 0 || col >= D) return;
+  float sg = 0.f, sb = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { sg += red_g[i][tx]; sb += red_b[i][tx]; }
   auto rd = [](const uint16_t* p) -> float {
     if constexpr (BF16) return __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(p));
     else return __half2float(*reinterpret_cast<const __half*>(p));
@@ -267,7 +280,7 @@ extern "C" int msq_layernorm_bwd(const void* dy, const void* x, const float* mea
     MSQ_LN_DISPATCH(nvec, (layernorm_bwd_kernel<false, VPT><<<grid, LN_THREADS, 0, stream>>>(DY, X, mean, rstd, G, A, DX, part_g, part_b, rows, D)))
   }
   if (part_g && (dgamma || dbeta)) {
-    const int t = 128, b = (D + t - 1) / t;
+    const int t = 256, b = (D + 31) / 32;
     if (bf16)
       layernorm_bwd_finalize<true><<<b, t, 0, stream>>>(part_g, part_b, grid, D, static_cast<uint16_t*>(dgamma),
                                                         static_cast<uint16_t*>(dbeta), accumulate);

@@ -87,6 +87,7 @@ def _declare_kernels(lib):
     _sig(lib, "msq_embed_fwd", [P, P, P, P, P, I, I, F, L, L, I, I, P])
     _sig(lib, "msq_embed_bwd", [P, P, P, P, P, I, I, F, L, L, L, I, P])
     _sig(lib, "msq_fold_fp32", [P, P, L, I, I, P])
+    _sig(lib, "msq_convert_rows", [P, P, L, I, L, I, P])
     _sig(lib, "msq_cross_entropy", [P, L, P, P, P, I, I, L, F, I, I, P])
     _sig(lib, "msq_colsum", [P, L, I, I, P, I, P])
     _sig(lib, "msq_flash_fwd", [P, P, P, L, L, L, L, L, L, P, L, L, P, I, I, I, I, F, I, I, P, P])

@@ -285,7 +285,13 @@ def flash_attn_bwd(q, k, v, out, d_out, lse, scale: float, causal: bool, dq, dk,
             _lib.ptr(_lib.status_word(q.device)), _lib.stream_ptr(),
         )
         _lib.check_rc(rc, "msq_flash_bwd")
-        dq.copy_(dq_acc.view(B, T, H, d))
+        # dq is a column slice of the qkv gradient: rows of H*d elements, row stride dq.stride(1)
+        if dq.stride(2) == d and dq.stride(3) == 1 and dq.stride(0) == T * dq.stride(1) and dq.stride(1) % 8 == 0:
+            rc = _lib.kernels().msq_convert_rows(_lib.ptr(dq_acc), _lib.ptr(dq), B * T, H * d, dq.stride(1), _bf(dq),
+                                                 _lib.stream_ptr())
+            _lib.check_rc(rc, "msq_convert_rows")
+        else:
+            dq.copy_(dq_acc.view(B, T, H, d))
         return
     qf, kf, vf = (t.float().permute(0, 2, 1, 3) for t in (q, k, v))
     of = out.float().view(B, T, H, d).permute(0, 2, 1, 3)
