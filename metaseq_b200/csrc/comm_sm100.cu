@@ -1,0 +1,438 @@
+// Collectives over NVLink peer memory, written as plain kernels over peer pointers.
+//
+// Every rank owns one symmetric region (same layout on every GPU of the node) that its peers
+// have mapped; `PeerPtrs` carries the base address of that region on each rank as seen from the
+// calling process.  Data moves with 16-byte peer stores ("push"), so a consumer always reads its
+// own HBM; completion is published with a system-scope release store to a flag word in the
+// destination's signal pad and observed with acquire loads under a bounded wait.
+//
+// These kernels replace the NCCL calls of the reference's FSDP and tensor-parallel paths:
+//   parameter all-gather      (fairscale FSDP `_rebuild_full_params`, all_gather_base)
+//   gradient reduce-scatter   (fairscale FSDP `_post_backward_hook`, reduce_scatter_base)
+//   activations all-reduce    (metaseq/modules/megatron/mpu/mappings.py:27 `_reduce`)
+// and add what the reference leaves to separate kernels: the reduce-scatter epilogue also
+// unscales, accumulates the squared gradient norm and raises the overflow flag.
+//
+// No kernel here waits on another launch of the same GPU: a wait is always on a flag written by a
+// different rank's kernel, and every wait gives up after WAIT_NS_PEER, records a code in the
+// status word and lets the kernel finish.
+#include "sm100_common.cuh"
+
+#include <cstring>
+
+namespace msq {
+
+constexpr int MAX_PEERS = 16;
+
+struct PeerPtrs {
+  void* p[MAX_PEERS];
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* addr, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* addr) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+
+// Epochs only grow; the comparison is wrap-safe.
+__device__ __forceinline__ bool epoch_reached(uint32_t seen, uint32_t want) {
+  return static_cast<int32_t>(seen - want) >= 0;
+}
+
+__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, int* status) {
+  if (epoch_reached(ld_acquire_sys(flag), epoch)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if (epoch_reached(ld_acquire_sys(flag), epoch)) return true;
+    if ((++spins & 0x3f) == 0) {
+      if (status && *reinterpret_cast<volatile int*>(status) != 0) return false;
+      if (globaltimer_ns() - t0 > WAIT_NS_PEER) {
+        if (status) atomicCAS(status, 0, ST_TIMEOUT_PEER_FLAG);
+        return false;
+      }
+      __nanosleep(64);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ barrier
+// Flag words [flag_base, flag_base + world) of every rank's signal pad: word `src` is written by rank src.
+__global__ void comm_barrier_kernel(PeerPtrs sig, int rank, int world, long long flag_base, uint32_t epoch, int* status) {
+  const int t = threadIdx.x;
+  if (t < world) {
+    __threadfence_system();
+    st_release_sys(static_cast<uint32_t*>(sig.p[t]) + flag_base + rank, epoch);
+    wait_flag(static_cast<const uint32_t*>(sig.p[rank]) + flag_base + t, epoch, status);
+  }
+}
+
+// Waits until flags [lo, hi) of the local signal pad have reached `epoch`.
+__global__ void comm_wait_flags_kernel(const uint32_t* flags, long long lo, long long hi, uint32_t epoch, int* status) {
+  for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x)
+    if (!wait_flag(flags + i, epoch, status)) break;
+}
+
+// ------------------------------------------------------------- all-gather
+// Rank `rank` owns bytes [rank * shard_bytes, (rank + 1) * shard_bytes) of the gathered buffer, cut
+// into chunks of `chunk_bytes`.  A CTA reads one chunk of the local shard once and stores it into the
+// gathered buffer of every rank (its own included), then publishes flag `flag_base + global chunk
+// index` on each destination.  Consumers (the GEMM producer warp, or comm_wait_flags_kernel) poll
+// those flags, so a weight tile can be multiplied as soon as its chunks have landed.
+__global__ void __launch_bounds__(512)
+comm_allgather_push_kernel(PeerPtrs dst, long long dst_off_bytes, const uint4* __restrict__ src, long long shard_bytes,
+                           int chunk_bytes, int rank, int world, PeerPtrs sig, long long flag_base, uint32_t epoch,
+                           int* status) {
+  if (status && *reinterpret_cast<volatile int*>(status) != 0) return;
+  const long long chunks = (shard_bytes + chunk_bytes - 1) / chunk_bytes;
+  for (long long c = blockIdx.x; c < chunks; c += gridDim.x) {
+    const long long b0 = c * chunk_bytes;
+    const long long nb = (shard_bytes - b0 < chunk_bytes) ? (shard_bytes - b0) : chunk_bytes;
+    const int nvec = static_cast<int>(nb >> 4);
+    const uint4* s = src + (b0 >> 4);
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+      const uint4 v = s[i];
+      for (int pp = 0; pp < world; ++pp) {
+        const int peer = (rank + pp) % world;  // spread the first stores over different links
+        uint4* d = reinterpret_cast<uint4*>(static_cast<uint8_t*>(dst.p[peer]) + dst_off_bytes + rank * shard_bytes + b0);
+        d[i] = v;
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x < world) {
+      __threadfence_system();
+      st_release_sys(static_cast<uint32_t*>(sig.p[threadIdx.x]) + flag_base + rank * chunks + c, epoch);
+    }
+    __syncthreads();
+  }
+}
+
+// --------------------------------------------------------- reduce-scatter
+// Push phase: slice p of the local full-size buffer goes to slot `rank` of rank p's slot area
+// (slot area = world slots of shard_bytes each), then flag `flag_base + rank` is published on rank p.
+__global__ void __launch_bounds__(512)
+comm_reduce_scatter_push_kernel(PeerPtrs slots, long long slots_off_bytes, const uint4* __restrict__ full,
+                                long long shard_bytes, int rank, int world, PeerPtrs sig, long long flag_base,
+                                uint32_t epoch, unsigned int* done_counter, int* status) {
+  if (status && *reinterpret_cast<volatile int*>(status) != 0) return;
+  const long long vec_per_shard = shard_bytes >> 4;
+  const long long total = vec_per_shard * world;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int pp = static_cast<int>(i / vec_per_shard);
+    const long long off = i - pp * vec_per_shard;
+    const int peer = (rank + pp) % world;
+    uint4* d = reinterpret_cast<uint4*>(static_cast<uint8_t*>(slots.p[peer]) + slots_off_bytes + rank * shard_bytes);
+    d[off] = full[peer * vec_per_shard + off];
+  }
+  // the last CTA to finish publishes the flags (every CTA's stores are fenced before it counts itself)
+  __threadfence_system();
+  __syncthreads();
+  __shared__ bool last;
+  if (threadIdx.x == 0) last = (atomicAdd(done_counter, 1u) == gridDim.x - 1);
+  __syncthreads();
+  if (last) {
+    if (threadIdx.x < world) {
+      __threadfence_system();
+      st_release_sys(static_cast<uint32_t*>(sig.p[threadIdx.x]) + flag_base + rank, epoch);
+    }
+    if (threadIdx.x == 0) *done_counter = 0;
+  }
+}
+
+// Reduce phase (local reads only): waits for the `world` source flags, sums the slots in fp32, applies
+// `scale`, writes the 16-bit (or fp32) shard and accumulates sum(g^2) of the scaled result into
+// sumsq_acc; a non-finite value sets *overflow.
+template <bool BF16, bool OUT32>
+__global__ void __launch_bounds__(256)
+comm_reduce_slots_kernel(const uint4* __restrict__ slots, long long shard_numel, int world, float scale,
+                         void* __restrict__ out, float* sumsq_acc, int* overflow, const uint32_t* flags,
+                         long long flag_base, uint32_t epoch, int* status) {
+  __shared__ bool ok_s;
+  if (threadIdx.x == 0) ok_s = true;
+  __syncthreads();
+  if (threadIdx.x < world) {
+    if (!wait_flag(flags + flag_base + threadIdx.x, epoch, status)) ok_s = false;
+  }
+  __syncthreads();
+  if (!ok_s) return;
+  const long long nvec = shard_numel >> 3;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  float ss = 0.f;
+  bool bad = false;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < world; ++s) {
+      const uint4 v = slots[s * nvec + i];
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack2<BF16>(w[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      acc[j] *= scale;
+      ss += acc[j] * acc[j];
+      bad |= !isfinite(acc[j]);
+    }
+    if (OUT32) {
+      float4* o = reinterpret_cast<float4*>(out) + 2 * i;
+      o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    } else {
+      uint4 o;
+      o.x = pack2<BF16>(acc[0], acc[1]);
+      o.y = pack2<BF16>(acc[2], acc[3]);
+      o.z = pack2<BF16>(acc[4], acc[5]);
+      o.w = pack2<BF16>(acc[6], acc[7]);
+      reinterpret_cast<uint4*>(out)[i] = o;
+    }
+  }
+  __shared__ float red[32];
+  ss = block_sum(ss, red);
+  if (threadIdx.x == 0 && sumsq_acc) atomicAdd(sumsq_acc, ss);
+  if (bad && overflow) *overflow = 1;
+}
+
+// ------------------------------------------------------- one-shot all-reduce
+// For small tensors (decode activations, vocab-parallel loss statistics): every rank stores its
+// input into slot `rank` of every peer's slot area, publishes a flag, waits for the other ranks'
+// flags and sums the slots locally.  Slot areas alternate with the epoch's parity, so a fast rank
+// starting the next all-reduce never overwrites data a slow rank is still reading.
+template <int MODE>  // 0: 16-bit fp16, 1: bf16, 2: fp32
+__global__ void __launch_bounds__(512)
+comm_allreduce_oneshot_kernel(PeerPtrs slots, long long slots_off_bytes, long long slot_stride, const void* in, void* out,
+                              long long bytes, int rank, int world, PeerPtrs sig, long long flag_base, uint32_t epoch,
+                              int* status) {
+  if (status && *reinterpret_cast<volatile int*>(status) != 0) return;
+  const long long parity_off = (epoch & 1u) ? slot_stride * world : 0;
+  const long long nvec = bytes >> 4;
+  const uint4* src = static_cast<const uint4*>(in);
+  for (long long i = threadIdx.x; i < nvec; i += blockDim.x) {
+    const uint4 v = src[i];
+    for (int pp = 0; pp < world; ++pp) {
+      const int peer = (rank + pp) % world;
+      uint4* d = reinterpret_cast<uint4*>(static_cast<uint8_t*>(slots.p[peer]) + slots_off_bytes + parity_off + rank * slot_stride);
+      d[i] = v;
+    }
+  }
+  __syncthreads();
+  __shared__ bool ok_s;
+  if (threadIdx.x == 0) ok_s = true;
+  __syncthreads();
+  if (threadIdx.x < world) {
+    __threadfence_system();
+    st_release_sys(static_cast<uint32_t*>(sig.p[threadIdx.x]) + flag_base + rank, epoch);
+    if (!wait_flag(static_cast<const uint32_t*>(sig.p[rank]) + flag_base + threadIdx.x, epoch, status)) ok_s = false;
+  }
+  __syncthreads();
+  if (!ok_s) return;
+  const uint8_t* mine = static_cast<const uint8_t*>(slots.p[rank]) + slots_off_bytes + parity_off;
+  for (long long i = threadIdx.x; i < nvec; i += blockDim.x) {
+    if (MODE == 2) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int s = 0; s < world; ++s) {
+        const float4 v = reinterpret_cast<const float4*>(mine + s * slot_stride)[i];
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+      static_cast<float4*>(out)[i] = acc;
+    } else {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int s = 0; s < world; ++s) {
+        const uint4 v = reinterpret_cast<const uint4*>(mine + s * slot_stride)[i];
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack2<MODE == 1>(w[j]);
+          acc[2 * j] += f.x;
+          acc[2 * j + 1] += f.y;
+        }
+      }
+      uint4 o;
+      o.x = pack2<MODE == 1>(acc[0], acc[1]);
+      o.y = pack2<MODE == 1>(acc[2], acc[3]);
+      o.z = pack2<MODE == 1>(acc[4], acc[5]);
+      o.w = pack2<MODE == 1>(acc[6], acc[7]);
+      static_cast<uint4*>(out)[i] = o;
+    }
+  }
+}
+
+// In-switch variant: `mc` is the multicast address of the input buffers (same offset on every rank).
+// After a barrier each rank asks the switch for the sum of its share of the elements
+// (multimem.ld_reduce) and broadcasts the result to all ranks (multimem.st), i.e. a two-shot
+// all-reduce whose additions happen inside NVSwitch.  fp32 accumulation for 16-bit inputs.
+template <int MODE>
+__global__ void __launch_bounds__(512)
+comm_allreduce_multimem_kernel(void* mc, long long bytes, int rank, int world, PeerPtrs sig, long long flag_base,
+                               uint32_t epoch, int* status) {
+  if (status && *reinterpret_cast<volatile int*>(status) != 0) return;
+  __shared__ bool ok_s;
+  if (threadIdx.x == 0) ok_s = true;
+  __syncthreads();
+  if (blockIdx.x == 0 && threadIdx.x < world) {
+    __threadfence_system();
+    st_release_sys(static_cast<uint32_t*>(sig.p[threadIdx.x]) + flag_base + rank, epoch);
+  }
+  if (threadIdx.x < world) {
+    if (!wait_flag(static_cast<const uint32_t*>(sig.p[rank]) + flag_base + threadIdx.x, epoch, status)) ok_s = false;
+  }
+  __syncthreads();
+  if (!ok_s) return;
+  const long long nvec = bytes >> 4;
+  const long long per = (nvec + world - 1) / world;
+  const long long lo = rank * per, hi = (lo + per < nvec) ? lo + per : nvec;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = lo + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < hi; i += stride) {
+    uint8_t* a = static_cast<uint8_t*>(mc) + (i << 4);
+    uint32_t x, y, z, w;
+    if (MODE == 2)
+      asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                   : "=r"(x), "=r"(y), "=r"(z), "=r"(w) : "l"(a) : "memory");
+    else if (MODE == 1)
+      asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                   : "=r"(x), "=r"(y), "=r"(z), "=r"(w) : "l"(a) : "memory");
+    else
+      asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+                   : "=r"(x), "=r"(y), "=r"(z), "=r"(w) : "l"(a) : "memory");
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                 ::"l"(a), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+  }
+}
+
+}  // namespace msq
+
+using msq::PeerPtrs;
+
+static PeerPtrs make_ptrs(void* const* ptrs, int world) {
+  PeerPtrs r;
+  for (int i = 0; i < msq::MAX_PEERS; ++i) r.p[i] = i < world ? ptrs[i] : nullptr;
+  return r;
+}
+
+// ---------------------------------------------------------------- IPC heap
+// Symmetric regions for processes that cannot share a CUDA virtual-memory handle: plain cudaMalloc
+// plus cudaIpc handles exchanged by the caller.
+extern "C" int msq_symm_alloc(long long bytes, void** ptr, void* handle64) {
+  if (cudaMalloc(ptr, static_cast<size_t>(bytes)) != cudaSuccess) return -1;
+  if (cudaMemset(*ptr, 0, static_cast<size_t>(bytes)) != cudaSuccess) return -2;
+  cudaIpcMemHandle_t h;
+  if (cudaIpcGetMemHandle(&h, *ptr) != cudaSuccess) return -3;
+  static_assert(sizeof(h) == 64, "ipc handle size");
+  memcpy(handle64, &h, 64);
+  return 0;
+}
+extern "C" int msq_symm_open(const void* handle64, void** ptr) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  return cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess ? 0 : -1;
+}
+extern "C" int msq_symm_close(void* ptr) { return cudaIpcCloseMemHandle(ptr) == cudaSuccess ? 0 : -1; }
+extern "C" int msq_symm_free(void* ptr) { return cudaFree(ptr) == cudaSuccess ? 0 : -1; }
+
+// ------------------------------------------------------------ entry points
+extern "C" int msq_comm_barrier(void* const* sig_ptrs, int rank, int world, long long flag_base, unsigned epoch,
+                                int* status, cudaStream_t stream) {
+  if (world > msq::MAX_PEERS) return -2;
+  msq::comm_barrier_kernel<<<1, 32, 0, stream>>>(make_ptrs(sig_ptrs, world), rank, world, flag_base, epoch, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+extern "C" int msq_comm_wait_flags(const void* flags, long long lo, long long hi, unsigned epoch, int* status,
+                                   cudaStream_t stream) {
+  if (hi <= lo) return 0;
+  msq::comm_wait_flags_kernel<<<1, 128, 0, stream>>>(static_cast<const uint32_t*>(flags), lo, hi, epoch, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+extern "C" int msq_comm_allgather_push(void* const* dst_ptrs, long long dst_off_bytes, const void* src, long long shard_bytes,
+                                       int chunk_bytes, int rank, int world, void* const* sig_ptrs, long long flag_base,
+                                       unsigned epoch, int max_ctas, int* status, cudaStream_t stream) {
+  if (world > msq::MAX_PEERS) return -2;
+  if ((shard_bytes & 15) || (chunk_bytes & 15) || (dst_off_bytes & 15) || (reinterpret_cast<uintptr_t>(src) & 15)) return -2;
+  if (shard_bytes <= 0) return 0;
+  long long chunks = (shard_bytes + chunk_bytes - 1) / chunk_bytes;
+  int grid = static_cast<int>(chunks < max_ctas ? chunks : max_ctas);
+  if (grid < 1) grid = 1;
+  msq::comm_allgather_push_kernel<<<grid, 512, 0, stream>>>(make_ptrs(dst_ptrs, world), dst_off_bytes,
+                                                           static_cast<const uint4*>(src), shard_bytes, chunk_bytes, rank,
+                                                           world, make_ptrs(sig_ptrs, world), flag_base, epoch, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+extern "C" int msq_comm_reduce_scatter_push(void* const* slot_ptrs, long long slots_off_bytes, const void* full,
+                                            long long shard_bytes, int rank, int world, void* const* sig_ptrs,
+                                            long long flag_base, unsigned epoch, unsigned* done_counter, int max_ctas,
+                                            int* status, cudaStream_t stream) {
+  if (world > msq::MAX_PEERS) return -2;
+  if ((shard_bytes & 15) || (slots_off_bytes & 15) || (reinterpret_cast<uintptr_t>(full) & 15)) return -2;
+  if (shard_bytes <= 0) return 0;
+  long long want = ((shard_bytes >> 4) * world + 511) / 512;
+  int grid = static_cast<int>(want < max_ctas ? want : max_ctas);
+  if (grid < 1) grid = 1;
+  msq::comm_reduce_scatter_push_kernel<<<grid, 512, 0, stream>>>(make_ptrs(slot_ptrs, world), slots_off_bytes,
+                                                                static_cast<const uint4*>(full), shard_bytes, rank, world,
+                                                                make_ptrs(sig_ptrs, world), flag_base, epoch, done_counter,
+                                                                status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+extern "C" int msq_comm_reduce_slots(const void* slots, long long shard_numel, int world, float scale, void* out,
+                                     int out_fp32, int bf16, float* sumsq_acc, int* overflow, const void* flags,
+                                     long long flag_base, unsigned epoch, int max_ctas, int* status, cudaStream_t stream) {
+  if ((shard_numel & 7) || (reinterpret_cast<uintptr_t>(slots) & 15) || (reinterpret_cast<uintptr_t>(out) & 15)) return -2;
+  if (shard_numel <= 0) return 0;
+  long long want = ((shard_numel >> 3) + 255) / 256;
+  int grid = static_cast<int>(want < max_ctas ? want : max_ctas);
+  if (grid < 1) grid = 1;
+  const uint4* s = static_cast<const uint4*>(slots);
+  const uint32_t* f = static_cast<const uint32_t*>(flags);
+#define MSQ_RS(BF, O32) \
+  msq::comm_reduce_slots_kernel<BF, O32><<<grid, 256, 0, stream>>>(s, shard_numel, world, scale, out, sumsq_acc, overflow, f, flag_base, epoch, status)
+  if (bf16) { if (out_fp32) MSQ_RS(true, true); else MSQ_RS(true, false); }
+  else { if (out_fp32) MSQ_RS(false, true); else MSQ_RS(false, false); }
+#undef MSQ_RS
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// dtype: 0 fp16, 1 bf16, 2 fp32.  bytes must be a multiple of 16 and at most slot_stride; the slot area
+// holds 2 * world slots of slot_stride bytes at slots_off_bytes (one set per epoch parity).  in == out is allowed.
+extern "C" int msq_comm_allreduce_oneshot(void* const* slot_ptrs, long long slots_off_bytes, long long slot_stride,
+                                          const void* in, void* out,
+                                          long long bytes, int dtype, int rank, int world, void* const* sig_ptrs,
+                                          long long flag_base, unsigned epoch, int* status, cudaStream_t stream) {
+  if (world > msq::MAX_PEERS) return -2;
+  if ((bytes & 15) || (slot_stride & 15) || bytes > slot_stride || (reinterpret_cast<uintptr_t>(in) & 15) ||
+      (reinterpret_cast<uintptr_t>(out) & 15))
+    return -2;
+  if (bytes <= 0) return 0;
+  PeerPtrs sl = make_ptrs(slot_ptrs, world), sg = make_ptrs(sig_ptrs, world);
+  if (dtype == 0) msq::comm_allreduce_oneshot_kernel<0><<<1, 512, 0, stream>>>(sl, slots_off_bytes, slot_stride, in, out, bytes, rank, world, sg, flag_base, epoch, status);
+  else if (dtype == 1) msq::comm_allreduce_oneshot_kernel<1><<<1, 512, 0, stream>>>(sl, slots_off_bytes, slot_stride, in, out, bytes, rank, world, sg, flag_base, epoch, status);
+  else msq::comm_allreduce_oneshot_kernel<2><<<1, 512, 0, stream>>>(sl, slots_off_bytes, slot_stride, in, out, bytes, rank, world, sg, flag_base, epoch, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// In-place all-reduce of the symmetric buffer whose multicast address is `mc`.  The caller follows it
+// with msq_comm_barrier before reading the result.
+extern "C" int msq_comm_allreduce_multimem(void* mc, long long bytes, int dtype, int rank, int world, void* const* sig_ptrs,
+                                           long long flag_base, unsigned epoch, int max_ctas, int* status,
+                                           cudaStream_t stream) {
+  if (world > msq::MAX_PEERS) return -2;
+  if ((bytes & 15) || (reinterpret_cast<uintptr_t>(mc) & 15)) return -2;
+  if (bytes <= 0) return 0;
+  long long want = (((bytes >> 4) + world - 1) / world + 511) / 512;
+  int grid = static_cast<int>(want < max_ctas ? want : max_ctas);
+  if (grid < 1) grid = 1;
+  PeerPtrs sg = make_ptrs(sig_ptrs, world);
+  if (dtype == 0) msq::comm_allreduce_multimem_kernel<0><<<grid, 512, 0, stream>>>(mc, bytes, rank, world, sg, flag_base, epoch, status);
+  else if (dtype == 1) msq::comm_allreduce_multimem_kernel<1><<<grid, 512, 0, stream>>>(mc, bytes, rank, world, sg, flag_base, epoch, status);
+  else msq::comm_allreduce_multimem_kernel<2><<<grid, 512, 0, stream>>>(mc, bytes, rank, world, sg, flag_base, epoch, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}

@@ -88,6 +88,18 @@ def _declare_kernels(lib):
     _sig(lib, "msq_embed_bwd", [P, P, P, P, P, I, I, F, L, L, L, I, P])
     _sig(lib, "msq_fold_fp32", [P, P, L, I, I, P])
     _sig(lib, "msq_convert_rows", [P, P, L, I, L, I, P])
+    U = ctypes.c_uint
+    _sig(lib, "msq_symm_alloc", [L, P, P])
+    _sig(lib, "msq_symm_open", [P, P])
+    _sig(lib, "msq_symm_close", [P])
+    _sig(lib, "msq_symm_free", [P])
+    _sig(lib, "msq_comm_barrier", [P, I, I, L, U, P, P])
+    _sig(lib, "msq_comm_wait_flags", [P, L, L, U, P, P])
+    _sig(lib, "msq_comm_allgather_push", [P, L, P, L, I, I, I, P, L, U, I, P, P])
+    _sig(lib, "msq_comm_reduce_scatter_push", [P, L, P, L, I, I, P, L, U, P, I, P, P])
+    _sig(lib, "msq_comm_reduce_slots", [P, L, I, F, P, I, I, P, P, P, L, U, I, P, P])
+    _sig(lib, "msq_comm_allreduce_oneshot", [P, L, L, P, P, L, I, I, I, P, L, U, P, P])
+    _sig(lib, "msq_comm_allreduce_multimem", [P, L, I, I, I, P, L, U, I, P, P])
     _sig(lib, "msq_cross_entropy", [P, L, P, P, P, I, I, L, F, I, I, P])
     _sig(lib, "msq_colsum", [P, L, I, I, P, I, P])
     _sig(lib, "msq_flash_fwd", [P, P, P, L, L, L, L, L, L, P, L, L, P, I, I, I, I, F, I, I, P, P])

@@ -1,0 +1,337 @@
+"""Symmetric peer-mapped memory and the collectives built on it.
+
+Each rank of a node-local process group owns one region of device memory with the same layout on
+every GPU; all peers map it, so a kernel on any rank can store into (or load from) every other
+rank's copy over NVLink.  The first ``SIGNAL_BYTES`` of a region are 32-bit flag words ("signal
+pad"); the rest is handed out by a bump allocator that every rank drives identically, which keeps
+offsets equal across ranks without any exchange.
+
+``PeerComm`` implements the FSDP and tensor-parallel collectives with the kernels of
+``csrc/comm_sm100.cu`` (push all-gather with per-chunk arrival flags, push reduce-scatter with a fused
+fp32 reduce / unscale / squared-norm / overflow epilogue, one-shot and in-switch all-reduce for small
+tensors, flag barrier).  The reference reaches the same collectives through NCCL
+(fairscale FullyShardedDataParallel; metaseq/modules/megatron/mpu/mappings.py:27-177;
+metaseq/distributed/utils.py:335-352); NCCL remains the control plane and the ``--comm-backend nccl``
+baseline here.
+
+Two ways to obtain the mapping:
+  * ``torch``: ``torch.distributed._symmetric_memory`` (CUDA VMM handles; also yields the NVSwitch
+    multicast address used by the in-switch all-reduce);
+  * ``ipc``: ``cudaMalloc`` + ``cudaIpc`` handles exchanged through the process group.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from dataclasses import dataclass, field
+from typing import Dict, Optional
+
+import torch
+import torch.distributed as dist
+
+from metaseq_b200.ops import _lib
+
+SIGNAL_BYTES = 1 << 20  # 256 Ki flag words
+_DTYPE_CODE = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}
+
+
+class _RawCudaBuffer:
+    """Exposes a raw device allocation through the CUDA array interface (zero-copy ``torch.as_tensor``)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+class SymmetricHeap:
+    def __init__(self, group, nbytes: int, device: torch.device, provider: str = "auto"):
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.device = torch.device(device)
+        self.nbytes = int(SIGNAL_BYTES + (nbytes + 4095) // 4096 * 4096)
+        self.multicast_ptr = 0
+        self._ipc_peers = []
+        self._ipc_base = None
+        provider = os.environ.get("MSQ_SYMM_PROVIDER", provider)
+        err = None
+        if provider in ("auto", "torch"):
+            try:
+                self._init_torch()
+                self.provider = "torch"
+            except Exception as e:  # noqa: BLE001 - any failure falls back to the IPC mapping
+                err = e
+                if provider == "torch":
+                    raise
+        if not hasattr(self, "provider"):
+            self._init_ipc()
+            self.provider = "ipc"
+        self.fallback_reason = repr(err) if err is not None else None
+        self._ptr_array = (ctypes.c_void_p * self.world)(*self.ptrs)
+        self._bump = SIGNAL_BYTES
+        self._flag_bump = 0
+        self.local.zero_()
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group)
+
+    # ------------------------------------------------------------------ set-up
+    def _init_torch(self):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        t = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=self.device)
+        name = self.group.group_name if self.group is not None else dist.group.WORLD.group_name
+        hdl = symm_mem.rendezvous(t, group=name)
+        self.local = t
+        self._hdl = hdl
+        self.ptrs = [int(p) for p in hdl.buffer_ptrs]
+        try:
+            self.multicast_ptr = int(hdl.multicast_ptr or 0)
+        except Exception:  # noqa: BLE001
+            self.multicast_ptr = 0
+        if os.environ.get("MSQ_SYMM_MULTICAST", "1") == "0":
+            self.multicast_ptr = 0
+
+    def _init_ipc(self):
+        lib = _lib.kernels()
+        ptr = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(64)
+        with torch.cuda.device(self.device):
+            rc = lib.msq_symm_alloc(self.nbytes, ctypes.byref(ptr), handle)
+        if rc != 0:
+            raise RuntimeError(f"msq_symm_alloc failed ({rc})")
+        self._ipc_base = ptr.value
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle.raw), group=self.group)
+        self.ptrs = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                self.ptrs.append(ptr.value)
+                continue
+            peer = ctypes.c_void_p()
+            with torch.cuda.device(self.device):
+                rc = lib.msq_symm_open(ctypes.create_string_buffer(h, 64), ctypes.byref(peer))
+            if rc != 0:
+                raise RuntimeError(f"msq_symm_open failed for rank {r} ({rc})")
+            self.ptrs.append(peer.value)
+            self._ipc_peers.append(peer.value)
+        self._raw = _RawCudaBuffer(ptr.value, self.nbytes)
+        self.local = torch.as_tensor(self._raw, device=self.device)
+
+    def close(self):
+        if self._ipc_base is not None:
+            lib = _lib.kernels()
+            torch.cuda.synchronize(self.device)
+            dist.barrier(self.group)
+            for p in self._ipc_peers:
+                lib.msq_symm_close(ctypes.c_void_p(p))
+            lib.msq_symm_free(ctypes.c_void_p(self._ipc_base))
+            self._ipc_base = None
+            self._ipc_peers = []
+
+    # -------------------------------------------------------------- allocation
+    def alloc(self, nbytes: int, align: int = 1024) -> int:
+        off = (self._bump + align - 1) // align * align
+        if off + nbytes > self.nbytes:
+            raise MemoryError(f"symmetric heap exhausted: need {nbytes} bytes at {off}, size {self.nbytes}")
+        self._bump = off + nbytes
+        return off
+
+    def alloc_flags(self, n: int) -> int:
+        base = self._flag_bump
+        if (base + n) * 4 > SIGNAL_BYTES:
+            raise MemoryError("signal pad exhausted")
+        self._flag_bump = base + n
+        return base
+
+    def view(self, offset: int, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        nbytes = numel * torch.empty((), dtype=dtype).element_size()
+        return self.local[offset:offset + nbytes].view(dtype)
+
+    @property
+    def ptr_array(self):
+        return self._ptr_array
+
+    @property
+    def flags_ptr(self) -> int:
+        return self.ptrs[self.rank]
+
+
+@dataclass
+class _Gathered:
+    offset: int          # byte offset of the gathered buffer in the region
+    numel: int
+    dtype: torch.dtype
+    shard_bytes: int
+    chunk_bytes: int
+    chunks_per_shard: int
+    flag_base: int       # world * chunks_per_shard arrival flags
+    slots_offset: int    # world slots of shard_bytes (reduce-scatter landing area)
+    rs_flag_base: int    # world flags
+    ag_epoch: int = 0
+    rs_epoch: int = 0
+    tensor: torch.Tensor = field(default=None, repr=False)
+
+
+class PeerComm:
+    """Collectives over a ``SymmetricHeap`` for one process group (ranks of one NVSwitch node)."""
+
+    def __init__(self, group, device, heap_bytes: int, chunk_bytes: int = 1 << 21, max_ctas: int = 24,
+                 provider: str = "auto", small_bytes: int = 1 << 20):
+        self.group = group
+        self.device = torch.device(device)
+        self.heap = SymmetricHeap(group, heap_bytes + 2 * small_bytes * dist.get_world_size(group) + (1 << 20),
+                                  device, provider)
+        self.rank, self.world = self.heap.rank, self.heap.world
+        self.chunk_bytes = int(chunk_bytes)
+        self.max_ctas = int(max_ctas)
+        self._bufs: Dict[int, _Gathered] = {}
+        self._barrier_base = self.heap.alloc_flags(self.world)
+        self._barrier_epoch = 0
+        self._ar_base = self.heap.alloc_flags(self.world)
+        self._ar_epoch = 0
+        self._small_bytes = int(small_bytes)
+        self._ar_slots = self.heap.alloc(2 * self.world * self._small_bytes)
+        self._mc_base = self.heap.alloc_flags(2 * self.world)
+        self._mc_epoch = 0
+        self._mc_off = self.heap.alloc(self._small_bytes)
+        self._done = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self.grad_sumsq = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self.overflow = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    # ------------------------------------------------------------------ helpers
+    def _status(self):
+        return _lib.ptr(_lib.status_word(self.device))
+
+    def _check(self, rc, what):
+        _lib.check_rc(rc, what)
+
+    def barrier(self):
+        """Device-side barrier over the group on the current stream."""
+        self._barrier_epoch += 1
+        rc = _lib.kernels().msq_comm_barrier(self.heap.ptr_array, self.rank, self.world, self._barrier_base,
+                                             self._barrier_epoch, self._status(), _lib.stream_ptr())
+        self._check(rc, "msq_comm_barrier")
+
+    # -------------------------------------------------------------- FSDP buffers
+    def alloc_full(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        """A gathered-parameter buffer of ``numel`` elements (a multiple of 8 * world) in symmetric memory,
+        with its arrival flags and the reduce-scatter landing slots of the same unit."""
+        esz = torch.empty((), dtype=dtype).element_size()
+        assert numel % self.world == 0
+        shard_bytes = numel // self.world * esz
+        assert shard_bytes % 16 == 0, "shards must be a multiple of 16 bytes"
+        chunk = min(self.chunk_bytes, shard_bytes)
+        chunks = (shard_bytes + chunk - 1) // chunk
+        off = self.heap.alloc(numel * esz)
+        meta = _Gathered(offset=off, numel=numel, dtype=dtype, shard_bytes=shard_bytes, chunk_bytes=chunk,
+                         chunks_per_shard=chunks, flag_base=self.heap.alloc_flags(self.world * chunks),
+                         slots_offset=self.heap.alloc(numel * esz), rs_flag_base=self.heap.alloc_flags(self.world))
+        meta.tensor = self.heap.view(off, numel, dtype)
+        self._bufs[meta.tensor.data_ptr()] = meta
+        return meta.tensor
+
+    def meta_of(self, full: torch.Tensor) -> _Gathered:
+        return self._bufs[full.data_ptr()]
+
+    def all_gather(self, full: torch.Tensor, local: torch.Tensor, stream: Optional[torch.cuda.Stream] = None,
+                   wait: bool = True):
+        """Pushes ``local`` (this rank's shard) into ``full`` on every rank.  With ``wait`` the current stream
+        then blocks until every rank's chunks have arrived here; without it the caller hands the arrival
+        flags to a consumer that waits per tile (``gemm_flags``)."""
+        meta = self.meta_of(full)
+        meta.ag_epoch += 1
+        local = local.contiguous()
+        assert local.numel() * local.element_size() == meta.shard_bytes
+        cur = torch.cuda.current_stream(self.device)
+        if stream is not None:
+            stream.wait_stream(cur)
+        with torch.cuda.stream(stream if stream is not None else cur):
+            rc = _lib.kernels().msq_comm_allgather_push(
+                self.heap.ptr_array, meta.offset, _lib.ptr(local), meta.shard_bytes, meta.chunk_bytes, self.rank,
+                self.world, self.heap.ptr_array, meta.flag_base, meta.ag_epoch, self.max_ctas, self._status(),
+                _lib.stream_ptr())
+            self._check(rc, "msq_comm_allgather_push")
+            if stream is not None:
+                local.record_stream(stream)
+        if wait:
+            self.wait_gathered(full)
+
+    def wait_gathered(self, full: torch.Tensor):
+        """Blocks the current stream until all chunks of the latest all-gather of ``full`` are here."""
+        meta = self.meta_of(full)
+        rc = _lib.kernels().msq_comm_wait_flags(self.heap.flags_ptr, meta.flag_base,
+                                                meta.flag_base + self.world * meta.chunks_per_shard, meta.ag_epoch,
+                                                self._status(), _lib.stream_ptr())
+        self._check(rc, "msq_comm_wait_flags")
+
+    def gemm_flags(self, full: torch.Tensor):
+        """(flags pointer, first flag index, chunk bytes, chunks per shard, shard bytes, epoch) for consumers
+        that poll arrival per tile."""
+        meta = self.meta_of(full)
+        return (self.heap.flags_ptr, meta.flag_base, meta.chunk_bytes, meta.chunks_per_shard, meta.shard_bytes,
+                meta.ag_epoch)
+
+    def reduce_scatter(self, shard: torch.Tensor, full_grad: torch.Tensor, key: torch.Tensor,
+                       stream: Optional[torch.cuda.Stream] = None, scale: float = 1.0, accumulate_norm: bool = False):
+        """``shard = scale * sum_over_ranks(full_grad[rank's slice])``, summed in fp32.  ``key`` is the gathered
+        parameter buffer of the same unit (it names the landing slots).  With ``accumulate_norm`` the squared
+        norm of the result is added to ``self.grad_sumsq`` and non-finite values set ``self.overflow``."""
+        meta = self.meta_of(key)
+        meta.rs_epoch += 1
+        assert full_grad.is_contiguous() and full_grad.numel() == meta.numel and full_grad.dtype == meta.dtype
+        cur = torch.cuda.current_stream(self.device)
+        if stream is not None:
+            stream.wait_stream(cur)
+        lib = _lib.kernels()
+        with torch.cuda.stream(stream if stream is not None else cur):
+            rc = lib.msq_comm_reduce_scatter_push(
+                self.heap.ptr_array, meta.slots_offset, _lib.ptr(full_grad), meta.shard_bytes, self.rank, self.world,
+                self.heap.ptr_array, meta.rs_flag_base, meta.rs_epoch, _lib.ptr(self._done), self.max_ctas,
+                self._status(), _lib.stream_ptr())
+            self._check(rc, "msq_comm_reduce_scatter_push")
+            slots_ptr = self.heap.ptrs[self.rank] + meta.slots_offset
+            rc = lib.msq_comm_reduce_slots(
+                ctypes.c_void_p(slots_ptr), shard.numel(), self.world, float(scale), _lib.ptr(shard),
+                int(shard.dtype == torch.float32), int(meta.dtype == torch.bfloat16),
+                _lib.ptr(self.grad_sumsq) if accumulate_norm else None,
+                _lib.ptr(self.overflow) if accumulate_norm else None,
+                self.heap.flags_ptr, meta.rs_flag_base, meta.rs_epoch, 4 * self.max_ctas, self._status(),
+                _lib.stream_ptr())
+            self._check(rc, "msq_comm_reduce_slots")
+            if stream is not None:
+                full_grad.record_stream(stream)
+                shard.record_stream(stream)
+
+    # ------------------------------------------------------------ small tensors
+    def all_reduce(self, t: torch.Tensor, use_multicast: Optional[bool] = None) -> torch.Tensor:
+        """In-place sum over the group for small contiguous tensors (decode activations, loss statistics).
+        Falls back to NCCL above the staging size."""
+        nbytes = t.numel() * t.element_size()
+        if (not t.is_contiguous()) or t.dtype not in _DTYPE_CODE or nbytes % 16 or nbytes > self._small_bytes:
+            dist.all_reduce(t, group=self.group)
+            return t
+        lib = _lib.kernels()
+        code = _DTYPE_CODE[t.dtype]
+        if use_multicast is None:
+            use_multicast = self.heap.multicast_ptr != 0
+        if use_multicast and self.heap.multicast_ptr:
+            stage = self.heap.view(self._mc_off, t.numel(), t.dtype)
+            stage.copy_(t.view(-1))
+            self._mc_epoch += 1
+            rc = lib.msq_comm_allreduce_multimem(
+                ctypes.c_void_p(self.heap.multicast_ptr + self._mc_off), nbytes, code, self.rank, self.world,
+                self.heap.ptr_array, self._mc_base + (self._mc_epoch & 1) * self.world, self._mc_epoch, 8,
+                self._status(), _lib.stream_ptr())
+            self._check(rc, "msq_comm_allreduce_multimem")
+            self.barrier()  # every rank's share has been broadcast
+            t.view(-1).copy_(stage)
+            self.barrier()  # nobody restages before everyone has copied out
+            return t
+        self._ar_epoch += 1
+        rc = lib.msq_comm_allreduce_oneshot(
+            self.heap.ptr_array, self._ar_slots, self._small_bytes, _lib.ptr(t), _lib.ptr(t), nbytes, code, self.rank, self.world,
+            self.heap.ptr_array, self._ar_base, self._ar_epoch, self._status(), _lib.stream_ptr())
+        self._check(rc, "msq_comm_allreduce_oneshot")
+        return t
+
+    def close(self):
+        self.heap.close()

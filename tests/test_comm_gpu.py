@@ -1,0 +1,103 @@
+"""Peer-memory collectives against NCCL / plain PyTorch references, run as one process per GPU.
+
+Needs at least two GPUs; on a single-GPU machine the tests are skipped."""
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, provider, results):
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from metaseq_b200.ops import _lib
+        from metaseq_b200.parallel.symm import PeerComm
+
+        dev = torch.device("cuda", rank)
+        comm = PeerComm(dist.group.WORLD, dev, heap_bytes=256 << 20, chunk_bytes=1 << 18, provider=provider)
+        for _ in range(3):
+            comm.barrier()
+        torch.cuda.synchronize()
+        # ---- all-gather (several epochs, ragged last chunk)
+        numel = world * (3 * (1 << 17) + 8 * 13)
+        full = comm.alloc_full(numel, torch.float16)
+        for step in range(3):
+            g = torch.Generator(device=dev).manual_seed(100 * step + rank)
+            local = torch.randn(numel // world, device=dev, dtype=torch.float16, generator=g)
+            ref = torch.empty(numel, device=dev, dtype=torch.float16)
+            dist.all_gather_into_tensor(ref, local)
+            comm.all_gather(full, local, stream=torch.cuda.Stream() if step == 1 else None)
+            torch.cuda.synchronize()
+            assert torch.equal(full, ref), f"all_gather mismatch at step {step}"
+            dist.barrier()
+        # ---- reduce-scatter with fp32 sum, scale, norm and overflow flag
+        for step in range(3):
+            g = torch.Generator(device=dev).manual_seed(7 + 10 * step + rank)
+            grad = torch.randn(numel, device=dev, dtype=torch.float16, generator=g)
+            allg = [torch.empty_like(grad) for _ in range(world)]
+            dist.all_gather(allg, grad)
+            S = numel // world
+            ref = sum(t[rank * S:(rank + 1) * S].float() for t in allg) * 0.5
+            shard = torch.empty(S, device=dev, dtype=torch.float16)
+            comm.grad_sumsq.zero_()
+            comm.overflow.zero_()
+            comm.reduce_scatter(shard, grad, key=full, scale=0.5, accumulate_norm=True,
+                                stream=torch.cuda.Stream() if step == 2 else None)
+            torch.cuda.synchronize()
+            assert torch.allclose(shard.float(), ref, rtol=2e-3, atol=2e-3), "reduce_scatter mismatch"
+            assert abs(comm.grad_sumsq.item() - ref.pow(2).sum().item()) <= 2e-3 * ref.pow(2).sum().item()
+            assert comm.overflow.item() == 0
+            dist.barrier()
+        grad = torch.full((numel,), float("inf") if rank == 0 else 1.0, device=dev, dtype=torch.float16)
+        shard = torch.empty(numel // world, device=dev, dtype=torch.float16)
+        comm.reduce_scatter(shard, grad, key=full, scale=1.0, accumulate_norm=True)
+        torch.cuda.synchronize()
+        assert comm.overflow.item() == 1
+        dist.barrier()
+        # ---- small all-reduce: peer-slot kernel, and the in-switch kernel when a multicast mapping exists
+        for dtype in (torch.float16, torch.bfloat16, torch.float32):
+            for n in (8, 4096, 65536):
+                for use_mc in ([False, True] if comm.heap.multicast_ptr else [False]):
+                    for rep in range(3):
+                        x = (torch.arange(n, device=dev, dtype=torch.float32) % 7 + rank + rep).to(dtype)
+                        ref = x.clone()
+                        dist.all_reduce(ref)
+                        y = x.clone()
+                        comm.all_reduce(y, use_multicast=use_mc)
+                        torch.cuda.synchronize()
+                        assert torch.allclose(y.float(), ref.float(), rtol=1e-2, atol=1e-2), (dtype, n, use_mc)
+        assert _lib.check_status(dev) == 0
+        results[rank] = dict(provider=comm.heap.provider, multicast=bool(comm.heap.multicast_ptr),
+                             fallback=comm.heap.fallback_reason)
+        dist.barrier()
+        comm.close()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("provider", ["ipc", "auto"])
+def test_peer_collectives(provider):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least two GPUs")
+    import torch.multiprocessing as mp
+
+    world = min(torch.cuda.device_count(), 4)
+    with mp.Manager() as mgr:
+        results = mgr.dict()
+        mp.spawn(_worker, args=(world, _free_port(), provider, results), nprocs=world, join=True)
+        assert len(results) == world
+        print("symmetric memory:", dict(results[0]))
