@@ -85,7 +85,8 @@ def main(cfg: Cfg) -> None:
 def build_model_and_criterion(cfg, task):
     """Model wrapped per the data-parallel backend, and the criterion."""
     if cfg.distributed_training.ddp_backend == "fully_sharded":
-        extra = {"use_sharded_state": cfg.distributed_training.use_sharded_state}
+        extra = {"use_sharded_state": cfg.distributed_training.use_sharded_state,
+                 "comm": getattr(cfg.common, "comm_backend", "nccl")}
         with fsdp_enable_wrap(cfg.distributed_training, **extra):
             model = fsdp_wrap(task.build_model(cfg.model), process_group=dist_utils.get_data_parallel_group())
     else:

@@ -70,10 +70,15 @@ __global__ void comm_barrier_kernel(PeerPtrs sig, int rank, int world, long long
   }
 }
 
-// Waits until flags [lo, hi) of the local signal pad have reached `epoch`.
-__global__ void comm_wait_flags_kernel(const uint32_t* flags, long long lo, long long hi, uint32_t epoch, int* status) {
-  for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x)
+// Waits until flags [lo, hi) of the local signal pad, except [skip_lo, skip_hi), have reached `epoch`.
+// The skipped range is for flags that a kernel of this same GPU publishes: those are ordered with
+// stream events instead, so that no launch ever waits on another launch of its own device.
+__global__ void comm_wait_flags_kernel(const uint32_t* flags, long long lo, long long hi, long long skip_lo,
+                                       long long skip_hi, uint32_t epoch, int* status) {
+  for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    if (i >= skip_lo && i < skip_hi) continue;
     if (!wait_flag(flags + i, epoch, status)) break;
+  }
 }
 
 // ------------------------------------------------------------- all-gather
@@ -93,12 +98,22 @@ comm_allgather_push_kernel(PeerPtrs dst, long long dst_off_bytes, const uint4* _
     const long long nb = (shard_bytes - b0 < chunk_bytes) ? (shard_bytes - b0) : chunk_bytes;
     const int nvec = static_cast<int>(nb >> 4);
     const uint4* s = src + (b0 >> 4);
-    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
-      const uint4 v = s[i];
+    // four independent 16-byte loads per thread keep enough bytes in flight to fill the links
+    for (int i0 = threadIdx.x; i0 < nvec; i0 += 4 * blockDim.x) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * blockDim.x;
+        if (i < nvec) v[u] = s[i];
+      }
       for (int pp = 0; pp < world; ++pp) {
         const int peer = (rank + pp) % world;  // spread the first stores over different links
         uint4* d = reinterpret_cast<uint4*>(static_cast<uint8_t*>(dst.p[peer]) + dst_off_bytes + rank * shard_bytes + b0);
-        d[i] = v;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int i = i0 + u * blockDim.x;
+          if (i < nvec) d[i] = v[u];
+        }
       }
     }
     __syncthreads();
@@ -107,6 +122,17 @@ comm_allgather_push_kernel(PeerPtrs dst, long long dst_off_bytes, const uint4* _
       st_release_sys(static_cast<uint32_t*>(sig.p[threadIdx.x]) + flag_base + rank * chunks + c, epoch);
     }
     __syncthreads();
+  }
+}
+
+// Publishes `count` consecutive flags starting at flag_base + first on every rank.  Used after copy-engine
+// transfers (stream order guarantees they have completed) so that the data path needs no SM at all.
+__global__ void comm_signal_kernel(PeerPtrs sig, int world, long long flag_base, long long first, long long count,
+                                   uint32_t epoch) {
+  __threadfence_system();
+  for (long long i = threadIdx.x; i < count * world; i += blockDim.x) {
+    const int peer = static_cast<int>(i / count);
+    st_release_sys(static_cast<uint32_t*>(sig.p[peer]) + flag_base + first + (i - peer * count), epoch);
   }
 }
 
@@ -121,12 +147,23 @@ comm_reduce_scatter_push_kernel(PeerPtrs slots, long long slots_off_bytes, const
   const long long vec_per_shard = shard_bytes >> 4;
   const long long total = vec_per_shard * world;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
-    const int pp = static_cast<int>(i / vec_per_shard);
-    const long long off = i - pp * vec_per_shard;
-    const int peer = (rank + pp) % world;
-    uint4* d = reinterpret_cast<uint4*>(static_cast<uint8_t*>(slots.p[peer]) + slots_off_bytes + rank * shard_bytes);
-    d[off] = full[peer * vec_per_shard + off];
+  for (long long i0 = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < total; i0 += 4 * stride) {
+    uint4 v[4];
+    uint4* d[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < total) {
+        const int pp = static_cast<int>(i / vec_per_shard);
+        const long long off = i - pp * vec_per_shard;
+        const int peer = (rank + pp) % world;
+        d[u] = reinterpret_cast<uint4*>(static_cast<uint8_t*>(slots.p[peer]) + slots_off_bytes + rank * shard_bytes) + off;
+        v[u] = full[peer * vec_per_shard + off];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (i0 + u * stride < total) *d[u] = v[u];
   }
   // the last CTA to finish publishes the flags (every CTA's stores are fenced before it counts itself)
   __threadfence_system();
@@ -344,10 +381,11 @@ extern "C" int msq_comm_barrier(void* const* sig_ptrs, int rank, int world, long
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
-extern "C" int msq_comm_wait_flags(const void* flags, long long lo, long long hi, unsigned epoch, int* status,
-                                   cudaStream_t stream) {
+extern "C" int msq_comm_wait_flags(const void* flags, long long lo, long long hi, long long skip_lo, long long skip_hi,
+                                   unsigned epoch, int* status, cudaStream_t stream) {
   if (hi <= lo) return 0;
-  msq::comm_wait_flags_kernel<<<1, 128, 0, stream>>>(static_cast<const uint32_t*>(flags), lo, hi, epoch, status);
+  msq::comm_wait_flags_kernel<<<1, 128, 0, stream>>>(static_cast<const uint32_t*>(flags), lo, hi, skip_lo, skip_hi, epoch,
+                                                     status);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -363,6 +401,43 @@ extern "C" int msq_comm_allgather_push(void* const* dst_ptrs, long long dst_off_
   msq::comm_allgather_push_kernel<<<grid, 512, 0, stream>>>(make_ptrs(dst_ptrs, world), dst_off_bytes,
                                                            static_cast<const uint4*>(src), shard_bytes, chunk_bytes, rank,
                                                            world, make_ptrs(sig_ptrs, world), flag_base, epoch, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// Copy-engine variants: the shard (or gradient slice) travels by peer-to-peer DMA, one asynchronous copy
+// per destination, and a one-CTA kernel publishes the arrival flags afterwards.  No SM is taken from the
+// GEMMs that run concurrently on the compute stream.
+extern "C" int msq_comm_allgather_ce(void* const* dst_ptrs, long long dst_off_bytes, const void* src, long long shard_bytes,
+                                     int chunk_bytes, int rank, int world, void* const* sig_ptrs, long long flag_base,
+                                     unsigned epoch, cudaStream_t stream, cudaStream_t local_stream) {
+  // The copy into this rank's own gathered buffer goes to `local_stream` (normally the consumer's stream), so
+  // its completion is ordered by the stream itself and consumers only poll the flags of other ranks.
+  if (world > msq::MAX_PEERS) return -2;
+  if (shard_bytes <= 0) return 0;
+  for (int pp = 0; pp < world; ++pp) {
+    const int peer = (rank + pp) % world;
+    void* d = static_cast<uint8_t*>(dst_ptrs[peer]) + dst_off_bytes + static_cast<long long>(rank) * shard_bytes;
+    if (cudaMemcpyAsync(d, src, static_cast<size_t>(shard_bytes), cudaMemcpyDeviceToDevice,
+                        peer == rank ? local_stream : stream) != cudaSuccess)
+      return -12;
+  }
+  const long long chunks = (shard_bytes + chunk_bytes - 1) / chunk_bytes;
+  msq::comm_signal_kernel<<<1, 128, 0, stream>>>(make_ptrs(sig_ptrs, world), world, flag_base, rank * chunks, chunks, epoch);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+extern "C" int msq_comm_reduce_scatter_ce(void* const* slot_ptrs, long long slots_off_bytes, const void* full,
+                                          long long shard_bytes, int rank, int world, void* const* sig_ptrs,
+                                          long long flag_base, unsigned epoch, cudaStream_t stream) {
+  if (world > msq::MAX_PEERS) return -2;
+  if (shard_bytes <= 0) return 0;
+  for (int pp = 0; pp < world; ++pp) {
+    const int peer = (rank + pp) % world;
+    void* d = static_cast<uint8_t*>(slot_ptrs[peer]) + slots_off_bytes + static_cast<long long>(rank) * shard_bytes;
+    const void* sl = static_cast<const uint8_t*>(full) + static_cast<long long>(peer) * shard_bytes;
+    if (cudaMemcpyAsync(d, sl, static_cast<size_t>(shard_bytes), cudaMemcpyDeviceToDevice, stream) != cudaSuccess) return -12;
+  }
+  msq::comm_signal_kernel<<<1, 128, 0, stream>>>(make_ptrs(sig_ptrs, world), world, flag_base, rank, 1, epoch);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

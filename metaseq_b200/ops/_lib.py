@@ -26,7 +26,7 @@ F = c_float
 
 
 # kernels launched by one call of each entry point (used for the launch counter)
-_KERNELS_PER_CALL = {"msq_sumsq": 2, "msq_layernorm_bwd": 2, "msq_flash_bwd": 2, "msq_layernorm_bwd_parts": 0,
+_KERNELS_PER_CALL = {"msq_symm_alloc": 0, "msq_symm_open": 0, "msq_symm_close": 0, "msq_symm_free": 0, "msq_sumsq": 2, "msq_layernorm_bwd": 2, "msq_flash_bwd": 2, "msq_layernorm_bwd_parts": 0,
                      "msq_sumsq_parts": 0}
 _LAUNCHES = [0]
 
@@ -94,9 +94,11 @@ def _declare_kernels(lib):
     _sig(lib, "msq_symm_close", [P])
     _sig(lib, "msq_symm_free", [P])
     _sig(lib, "msq_comm_barrier", [P, I, I, L, U, P, P])
-    _sig(lib, "msq_comm_wait_flags", [P, L, L, U, P, P])
+    _sig(lib, "msq_comm_wait_flags", [P, L, L, L, L, U, P, P])
     _sig(lib, "msq_comm_allgather_push", [P, L, P, L, I, I, I, P, L, U, I, P, P])
     _sig(lib, "msq_comm_reduce_scatter_push", [P, L, P, L, I, I, P, L, U, P, I, P, P])
+    _sig(lib, "msq_comm_allgather_ce", [P, L, P, L, I, I, I, P, L, U, P, P])
+    _sig(lib, "msq_comm_reduce_scatter_ce", [P, L, P, L, I, I, P, L, U, P])
     _sig(lib, "msq_comm_reduce_slots", [P, L, I, F, P, I, I, P, P, P, L, U, I, P, P])
     _sig(lib, "msq_comm_allreduce_oneshot", [P, L, L, P, P, L, I, I, I, P, L, U, P, P])
     _sig(lib, "msq_comm_allreduce_multimem", [P, L, I, I, I, P, L, U, I, P, P])

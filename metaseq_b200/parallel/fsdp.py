@@ -112,7 +112,10 @@ class FullyShardedDataParallel(nn.Module):
         self.compute_dtype = compute_dtype
         self.use_sharded_state = use_sharded_state
         self.state_dict_device = state_dict_device
-        self.comm = comm
+        # ``comm``: a ``PeerComm``, or "fused" (one is built for the process group at first use, CUDA and
+        # world size > 1 only), or None / "nccl" for torch.distributed collectives
+        self.comm = comm if not isinstance(comm, str) else None
+        self._comm_request = comm if isinstance(comm, str) else None
         if gradient_predivide_factor is None:
             gradient_predivide_factor = self._default_predivide(self.world_size)
         self.gradient_predivide_factor = float(gradient_predivide_factor)
@@ -267,7 +270,12 @@ class FullyShardedDataParallel(nn.Module):
         else:
             nbytes = self.padded_numel * torch.empty((), dtype=cdt).element_size()
             if self._full_param is None:
-                self._full_param = torch.empty(self.padded_numel, dtype=cdt, device=src.device)
+                if self.comm is not None:
+                    # symmetric memory: peers store their shards straight into this buffer; it stays
+                    # allocated (the gathered copy is re-filled in place after every optimizer step)
+                    self._full_param = self.comm.alloc_full(self.padded_numel, cdt)
+                else:
+                    self._full_param = torch.empty(self.padded_numel, dtype=cdt, device=src.device)
                 self._set_views(self._full_param)
                 self._needs_gather = True
             elif self._full_param.untyped_storage().size() == 0:
@@ -281,7 +289,8 @@ class FullyShardedDataParallel(nn.Module):
                 else:
                     stream = self._comm_stream() if (asynchronous and src.is_cuda) else None
                     if self.comm is not None:
-                        self.comm.all_gather(full, local, stream=stream)
+                        self.comm.all_gather(full, local, stream=stream, wait=False)
+                        self._gather_flags_pending = True
                     elif stream is not None:
                         stream.wait_stream(torch.cuda.current_stream())
                         with torch.cuda.stream(stream):
@@ -297,20 +306,44 @@ class FullyShardedDataParallel(nn.Module):
             self._alloc_full_grad()
 
     def _alloc_full_grad(self):
+        """The unit's flat gradient buffer: a slice of one arena shared by all units of the root, allocated
+        (zeroed) once.  It is never cleared again: the first gradient written to a view in a step overwrites,
+        and views that received nothing are zeroed individually before the reduction."""
         cdt = self._compute_dtype()
-        self._full_grad = torch.zeros(self.padded_numel, dtype=cdt, device=self.flat_param.device)
+        root = self._root()
+        arena = root.__dict__.get("_grad_arena")
+        if arena is None or arena.dtype != cdt or arena.device != self.flat_param.device:
+            units = [u for u in (root.__dict__.get("_units") or [self]) if u.has_params and u.flat_param.requires_grad]
+            if self not in units:
+                units.append(self)
+            total, offs = 0, {}
+            for u in units:
+                offs[id(u)] = total
+                total += (u.padded_numel + 127) // 128 * 128
+            arena = torch.zeros(total, dtype=cdt, device=self.flat_param.device)
+            root.__dict__["_grad_arena"] = arena
+            root.__dict__["_grad_arena_offsets"] = offs
+        off = root.__dict__["_grad_arena_offsets"].get(id(self))
+        if off is None:
+            self._full_grad = torch.zeros(self.padded_numel, dtype=cdt, device=self.flat_param.device)
+        else:
+            self._full_grad = arena[off:off + self.padded_numel]
         for v in self._views:
             v._grad_filled = False
         self._refresh_grad_views()
 
     def _wait_gather(self):
+        if getattr(self, "_gather_flags_pending", False):
+            # arrival flags of every rank's chunks, polled by a kernel on the compute stream
+            self.comm.wait_gathered(self._full_param)
+            self._gather_flags_pending = False
         if self._gather_event is not None:
             torch.cuda.current_stream().wait_event(self._gather_event)
             self._gather_event = None
 
     def _free_full(self):
         """Releases the storage of the gathered copy (the tensor object and its views survive)."""
-        if self._full_param is None or self._aliases_shard():
+        if self._full_param is None or self._aliases_shard() or self.comm is not None:
             return
         self._wait_gather()
         self._full_param.untyped_storage().resize_(0)
@@ -328,10 +361,51 @@ class FullyShardedDataParallel(nn.Module):
                 u._is_root = False
                 object.__setattr__(u, "_root_ref", self)  # plain attribute: not a submodule
         self._step_gathered = False
+        self._build_comm()
+
+    def _build_comm(self):
+        """One ``PeerComm`` for all units when the fused communication backend was requested."""
+        units = [u for u in self._units if u.has_params and u._comm_request == "fused" and u.comm is None
+                 and u.world_size > 1 and u.flat_param.is_cuda]
+        if not units:
+            return
+        from .symm import PeerComm
+
+        need = 0
+        for u in units:
+            esz = torch.empty((), dtype=u._compute_dtype()).element_size()
+            need += 2 * (u.padded_numel * esz + 2048)  # gathered copy + reduce-scatter landing slots
+        comm = PeerComm(units[0].process_group, units[0].flat_param.device, heap_bytes=need)
+        for u in units:
+            u.comm = comm
+        self._peer_comm = comm
 
     def prefetch_all(self):
         """Queues the all-gathers of every unit, in module order, on the communication stream."""
         self._lazy_init()
+        comm = self.__dict__.get("_peer_comm")
+        if comm is not None:
+            # one stream hand-over for all units, then one native call per unit
+            items = []
+            for u in self._units:
+                if not u.has_params:
+                    continue
+                first = u._full_param is None
+                if first:
+                    u._full_param = comm.alloc_full(u.padded_numel, u._compute_dtype())
+                    u._set_views(u._full_param)
+                    u._needs_gather = True
+                if u._needs_gather:
+                    src = u.flat_param.data
+                    cdt = u._compute_dtype()
+                    items.append((u._full_param, src if src.dtype == cdt else src.to(cdt)))
+                    u._needs_gather = False
+                    u._gather_flags_pending = True
+                if u._full_grad is None and u.flat_param.requires_grad and torch.is_grad_enabled():
+                    u._alloc_full_grad()
+            if items:
+                comm.all_gather_many(items, self._comm_stream())
+            return
         for u in self._units:
             u._gather_full(asynchronous=True)
 
@@ -372,10 +446,22 @@ class FullyShardedDataParallel(nn.Module):
         self._collect_view_grads()
         if self._full_grad is None:
             return
+        for v in self._views:
+            if not getattr(v, "_grad_filled", True) and hasattr(v, "_grad_view"):
+                v._grad_view.zero_()  # parameter without a gradient this step: the buffer still holds the last one
+                v._grad_filled = True
         full_grad = self._full_grad
         if self.world_size == 1:
             shard = full_grad if full_grad.dtype == self.flat_param.dtype else full_grad.to(self.flat_param.dtype)
             self._accumulate_shard_grad(shard, owns_buffer=True)
+        elif self.comm is not None:
+            # peer-memory reduce-scatter: slices are pushed to their owners and summed there in fp32 with the
+            # 1 / world_size factor applied once, so neither pre-division nor an fp32 copy is needed
+            shard = torch.empty(self.shard_numel, dtype=self.flat_param.dtype, device=full_grad.device)
+            self.comm.reduce_scatter(shard, full_grad, key=self._full_param, stream=self._comm_stream(),
+                                     scale=1.0 / self.world_size)
+            self._root()._reduce_pending = True
+            self._accumulate_shard_grad(shard, owns_buffer=False)
         else:
             if self.fp32_reduce_scatter and full_grad.dtype != torch.float32:
                 full_grad = full_grad.float()
@@ -383,9 +469,7 @@ class FullyShardedDataParallel(nn.Module):
                 full_grad.div_(self.gradient_predivide_factor)
             shard = torch.empty(self.shard_numel, dtype=full_grad.dtype, device=full_grad.device)
             stream = self._comm_stream() if full_grad.is_cuda else None
-            if self.comm is not None:
-                self.comm.reduce_scatter(shard, full_grad, stream=stream)
-            elif stream is not None:
+            if stream is not None:
                 stream.wait_stream(torch.cuda.current_stream())
                 with torch.cuda.stream(stream):
                     dist.reduce_scatter_tensor(shard, full_grad, group=self.process_group)
@@ -398,17 +482,13 @@ class FullyShardedDataParallel(nn.Module):
                 dist.reduce_scatter_tensor(shard, full_grad, group=self.process_group)
                 if self.gradient_postdivide_factor > 1:
                     shard.div_(self.gradient_postdivide_factor)
-            if stream is None or self.comm is not None:
-                pass
             if shard.dtype != self.flat_param.dtype:
-                if stream is not None and self.comm is None:
+                if stream is not None:
                     with torch.cuda.stream(stream):
                         shard = shard.to(self.flat_param.dtype)
                 else:
                     shard = shard.to(self.flat_param.dtype)
             self._accumulate_shard_grad(shard, owns_buffer=False)
-            self._full_grad = None  # a new buffer is allocated for the next backward
-            self._refresh_grad_views()
         if self.reshard_after_forward:
             self._free_full()
 
@@ -437,6 +517,9 @@ class FullyShardedDataParallel(nn.Module):
                 for v in self._views:
                     v._grad_filled = True
         elif self.flat_param.grad.data_ptr() != shard.data_ptr():
+            side = getattr(self._root(), "_side_stream", None)
+            if side is not None and shard.is_cuda:
+                torch.cuda.current_stream().wait_stream(side)  # the shard is produced on the communication stream
             self.flat_param.grad.add_(shard)
 
     def _finish_backward(self):
@@ -454,16 +537,10 @@ class FullyShardedDataParallel(nn.Module):
         for u in (self._units if self._is_root else [self]):
             if u.flat_param is not None:
                 u.flat_param.grad = None
-            if u._full_grad is not None:
-                if u.world_size == 1:
-                    u._full_grad.zero_()
-                    for v in u._views:
-                        v._grad_filled = False
-                else:
-                    u._full_grad = None
-                    u._refresh_grad_views()
             for v in u._views:
                 v.grad = None
+                if hasattr(v, "_grad_filled"):
+                    v._grad_filled = False  # the next gradient written to the view overwrites
 
     def after_optimizer_step(self):
         """Local shards changed: every gathered copy is stale."""
@@ -472,6 +549,10 @@ class FullyShardedDataParallel(nn.Module):
             if u.has_params and not u._aliases_shard():
                 u._needs_gather = True
         self._step_gathered = False
+        if self.__dict__.get("_peer_comm") is not None and not self.reshard_after_forward:
+            # the shards are final: push them now, behind the optimizer kernels, instead of at the next forward
+            self.prefetch_all()
+            self._step_gathered = True
 
     # ------------------------------------------------------------ state dicts
     def _unit_paths(self) -> List[Tuple[str, "FullyShardedDataParallel"]]:
@@ -677,6 +758,7 @@ def fsdp_enable_wrap(cfg_dist, use_sharded_state: bool = False, **kwargs):
         "state_dict_device": torch.device("cpu"),
         "gradient_predivide_factor": getattr(cfg_dist, "gradient_predivide_factor", None),
         "use_sharded_state": use_sharded_state,
+        "comm": getattr(cfg_dist, "comm_backend", None),
         **kwargs,
     }
     try:

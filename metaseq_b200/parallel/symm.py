@@ -169,13 +169,17 @@ class _Gathered:
     ag_epoch: int = 0
     rs_epoch: int = 0
     tensor: torch.Tensor = field(default=None, repr=False)
+    push_event: object = field(default=None, repr=False)
 
 
 class PeerComm:
     """Collectives over a ``SymmetricHeap`` for one process group (ranks of one NVSwitch node)."""
 
-    def __init__(self, group, device, heap_bytes: int, chunk_bytes: int = 1 << 21, max_ctas: int = 24,
-                 provider: str = "auto", small_bytes: int = 1 << 20):
+    def __init__(self, group, device, heap_bytes: int, chunk_bytes: int = 1 << 21, max_ctas: int = 16,
+                 provider: str = "auto", small_bytes: int = 1 << 20, transport: Optional[str] = None):
+        # transport of the bulk collectives: "ce" = peer-to-peer DMA copies (no SM taken from concurrent GEMMs) or
+        # "sm" = store kernels with per-chunk arrival flags published as the chunks land
+        self.transport = transport or os.environ.get("MSQ_COMM_TRANSPORT", "ce")
         self.group = group
         self.device = torch.device(device)
         self.heap = SymmetricHeap(group, heap_bytes + 2 * small_bytes * dist.get_world_size(group) + (1 << 20),
@@ -245,21 +249,64 @@ class PeerComm:
         if stream is not None:
             stream.wait_stream(cur)
         with torch.cuda.stream(stream if stream is not None else cur):
-            rc = _lib.kernels().msq_comm_allgather_push(
-                self.heap.ptr_array, meta.offset, _lib.ptr(local), meta.shard_bytes, meta.chunk_bytes, self.rank,
-                self.world, self.heap.ptr_array, meta.flag_base, meta.ag_epoch, self.max_ctas, self._status(),
-                _lib.stream_ptr())
-            self._check(rc, "msq_comm_allgather_push")
+            if self.transport == "ce":
+                rc = _lib.kernels().msq_comm_allgather_ce(
+                    self.heap.ptr_array, meta.offset, _lib.ptr(local), meta.shard_bytes, meta.chunk_bytes, self.rank,
+                    self.world, self.heap.ptr_array, meta.flag_base, meta.ag_epoch, _lib.stream_ptr(),
+                    _lib.stream_ptr())
+            else:
+                rc = _lib.kernels().msq_comm_allgather_push(
+                    self.heap.ptr_array, meta.offset, _lib.ptr(local), meta.shard_bytes, meta.chunk_bytes, self.rank,
+                    self.world, self.heap.ptr_array, meta.flag_base, meta.ag_epoch, self.max_ctas, self._status(),
+                    _lib.stream_ptr())
+            self._check(rc, "msq_comm_allgather")
             if stream is not None:
                 local.record_stream(stream)
+            meta.push_event = torch.cuda.Event()
+            meta.push_event.record()
         if wait:
             self.wait_gathered(full)
+
+    def all_gather_many(self, items, stream: torch.cuda.Stream):
+        """All-gathers a list of ``(full, local shard)`` pairs with one stream hand-over: peer copies and flag
+        publication go to ``stream``, each rank's copy of its own shard to the current stream (so consumers on
+        the current stream need no event, only the peers' flags)."""
+        cur = torch.cuda.current_stream(self.device)
+        stream.wait_stream(cur)
+        lib = _lib.kernels()
+        sp, cp = ctypes.c_void_p(stream.cuda_stream), ctypes.c_void_p(cur.cuda_stream)
+        status = self._status()
+        for full, local in items:
+            meta = self.meta_of(full)
+            meta.ag_epoch += 1
+            meta.push_event = None
+            if self.transport == "ce":
+                rc = lib.msq_comm_allgather_ce(self.heap.ptr_array, meta.offset, _lib.ptr(local), meta.shard_bytes,
+                                               meta.chunk_bytes, self.rank, self.world, self.heap.ptr_array,
+                                               meta.flag_base, meta.ag_epoch, sp, cp)
+            else:
+                rc = lib.msq_comm_allgather_push(self.heap.ptr_array, meta.offset, _lib.ptr(local), meta.shard_bytes,
+                                                 meta.chunk_bytes, self.rank, self.world, self.heap.ptr_array,
+                                                 meta.flag_base, meta.ag_epoch, self.max_ctas, status, sp)
+                meta.push_event = True
+            self._check(rc, "msq_comm_allgather")
+            local.record_stream(stream)
+        if self.transport != "ce":
+            ev = torch.cuda.Event()
+            ev.record(stream)
+            for full, _ in items:
+                self.meta_of(full).push_event = ev
 
     def wait_gathered(self, full: torch.Tensor):
         """Blocks the current stream until all chunks of the latest all-gather of ``full`` are here."""
         meta = self.meta_of(full)
+        if meta.push_event is not None:
+            # this rank's own chunks: ordered by the event of the local push, never by polling its flags
+            torch.cuda.current_stream(self.device).wait_event(meta.push_event)
+        own = meta.flag_base + self.rank * meta.chunks_per_shard
         rc = _lib.kernels().msq_comm_wait_flags(self.heap.flags_ptr, meta.flag_base,
-                                                meta.flag_base + self.world * meta.chunks_per_shard, meta.ag_epoch,
+                                                meta.flag_base + self.world * meta.chunks_per_shard,
+                                                own, own + meta.chunks_per_shard, meta.ag_epoch,
                                                 self._status(), _lib.stream_ptr())
         self._check(rc, "msq_comm_wait_flags")
 
@@ -282,24 +329,28 @@ class PeerComm:
         if stream is not None:
             stream.wait_stream(cur)
         lib = _lib.kernels()
-        with torch.cuda.stream(stream if stream is not None else cur):
+        sp = ctypes.c_void_p((stream if stream is not None else cur).cuda_stream)
+        if self.transport == "ce":
+            rc = lib.msq_comm_reduce_scatter_ce(
+                self.heap.ptr_array, meta.slots_offset, _lib.ptr(full_grad), meta.shard_bytes, self.rank,
+                self.world, self.heap.ptr_array, meta.rs_flag_base, meta.rs_epoch, sp)
+        else:
             rc = lib.msq_comm_reduce_scatter_push(
-                self.heap.ptr_array, meta.slots_offset, _lib.ptr(full_grad), meta.shard_bytes, self.rank, self.world,
-                self.heap.ptr_array, meta.rs_flag_base, meta.rs_epoch, _lib.ptr(self._done), self.max_ctas,
-                self._status(), _lib.stream_ptr())
-            self._check(rc, "msq_comm_reduce_scatter_push")
-            slots_ptr = self.heap.ptrs[self.rank] + meta.slots_offset
-            rc = lib.msq_comm_reduce_slots(
-                ctypes.c_void_p(slots_ptr), shard.numel(), self.world, float(scale), _lib.ptr(shard),
-                int(shard.dtype == torch.float32), int(meta.dtype == torch.bfloat16),
-                _lib.ptr(self.grad_sumsq) if accumulate_norm else None,
-                _lib.ptr(self.overflow) if accumulate_norm else None,
-                self.heap.flags_ptr, meta.rs_flag_base, meta.rs_epoch, 4 * self.max_ctas, self._status(),
-                _lib.stream_ptr())
-            self._check(rc, "msq_comm_reduce_slots")
-            if stream is not None:
-                full_grad.record_stream(stream)
-                shard.record_stream(stream)
+                self.heap.ptr_array, meta.slots_offset, _lib.ptr(full_grad), meta.shard_bytes, self.rank,
+                self.world, self.heap.ptr_array, meta.rs_flag_base, meta.rs_epoch, _lib.ptr(self._done),
+                self.max_ctas, self._status(), sp)
+        self._check(rc, "msq_comm_reduce_scatter")
+        slots_ptr = self.heap.ptrs[self.rank] + meta.slots_offset
+        rc = lib.msq_comm_reduce_slots(
+            ctypes.c_void_p(slots_ptr), shard.numel(), self.world, float(scale), _lib.ptr(shard),
+            int(shard.dtype == torch.float32), int(meta.dtype == torch.bfloat16),
+            _lib.ptr(self.grad_sumsq) if accumulate_norm else None,
+            _lib.ptr(self.overflow) if accumulate_norm else None,
+            self.heap.flags_ptr, meta.rs_flag_base, meta.rs_epoch, 4 * self.max_ctas, self._status(), sp)
+        self._check(rc, "msq_comm_reduce_slots")
+        if stream is not None:
+            full_grad.record_stream(stream)
+            shard.record_stream(stream)
 
     # ------------------------------------------------------------ small tensors
     def all_reduce(self, t: torch.Tensor, use_multicast: Optional[bool] = None) -> torch.Tensor:

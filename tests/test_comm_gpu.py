@@ -16,7 +16,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, provider, results):
+def _worker(rank, world, port, provider, transport, results):
     import torch.distributed as dist
 
     os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -28,7 +28,8 @@ def _worker(rank, world, port, provider, results):
         from metaseq_b200.parallel.symm import PeerComm
 
         dev = torch.device("cuda", rank)
-        comm = PeerComm(dist.group.WORLD, dev, heap_bytes=256 << 20, chunk_bytes=1 << 18, provider=provider)
+        comm = PeerComm(dist.group.WORLD, dev, heap_bytes=256 << 20, chunk_bytes=1 << 18, provider=provider,
+                        transport=transport)
         for _ in range(3):
             comm.barrier()
         torch.cuda.synchronize()
@@ -89,8 +90,8 @@ def _worker(rank, world, port, provider, results):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("provider", ["ipc", "auto"])
-def test_peer_collectives(provider):
+@pytest.mark.parametrize("provider,transport", [("ipc", "sm"), ("auto", "sm"), ("auto", "ce"), ("ipc", "ce")])
+def test_peer_collectives(provider, transport):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs at least two GPUs")
     import torch.multiprocessing as mp
@@ -98,6 +99,6 @@ def test_peer_collectives(provider):
     world = min(torch.cuda.device_count(), 4)
     with mp.Manager() as mgr:
         results = mgr.dict()
-        mp.spawn(_worker, args=(world, _free_port(), provider, results), nprocs=world, join=True)
+        mp.spawn(_worker, args=(world, _free_port(), provider, transport, results), nprocs=world, join=True)
         assert len(results) == world
         print("symmetric memory:", dict(results[0]))
