@@ -81,6 +81,16 @@ __global__ void comm_wait_flags_kernel(const uint32_t* flags, long long lo, long
   }
 }
 
+struct FlagList {
+  int idx[32];
+  int n;
+};
+// Waits for an explicit list of flag words (the chunks that hold a unit's small parameters, while the
+// GEMMs poll the chunks of their own weight tiles).
+__global__ void comm_wait_flag_list_kernel(const uint32_t* flags, FlagList list, uint32_t epoch, int* status) {
+  if (threadIdx.x < list.n) wait_flag(flags + list.idx[threadIdx.x], epoch, status);
+}
+
 // ------------------------------------------------------------- all-gather
 // Rank `rank` owns bytes [rank * shard_bytes, (rank + 1) * shard_bytes) of the gathered buffer, cut
 // into chunks of `chunk_bytes`.  A CTA reads one chunk of the local shard once and stores it into the
@@ -386,6 +396,17 @@ extern "C" int msq_comm_wait_flags(const void* flags, long long lo, long long hi
   if (hi <= lo) return 0;
   msq::comm_wait_flags_kernel<<<1, 128, 0, stream>>>(static_cast<const uint32_t*>(flags), lo, hi, skip_lo, skip_hi, epoch,
                                                      status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+extern "C" int msq_comm_wait_flag_list(const void* flags, const int* idx, int n, unsigned epoch, int* status,
+                                       cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (n > 32) return -2;
+  msq::FlagList l;
+  for (int i = 0; i < 32; ++i) l.idx[i] = i < n ? idx[i] : 0;
+  l.n = n;
+  msq::comm_wait_flag_list_kernel<<<1, 32, 0, stream>>>(static_cast<const uint32_t*>(flags), l, epoch, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

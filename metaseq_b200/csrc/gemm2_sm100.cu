@@ -29,7 +29,56 @@ struct Gemm2Params {
   int accumulate;
   int bf16;
   int* status;
+  // Arrival flags of the B operand when it is (part of) a gathered buffer that peer GPUs fill over NVLink:
+  // the buffer is cut into `ready_world` shards of ready_shard_bytes, each into chunks of ready_chunk_bytes with
+  // one flag word per chunk; a chunk is usable once its flag has reached ready_epoch.  B starts
+  // ready_b_offset bytes into the buffer.  The producer warp polls (bounded) the flags covering the rows it is
+  // about to load, so the product starts while later chunks are still in flight.  Chunks of shard
+  // ready_skip_shard (the local rank's own, ordered by the stream) are not polled.  Null = no waiting.
+  const uint32_t* ready_flags;
+  long long ready_b_offset;
+  long long ready_ldb_bytes;
+  long long ready_shard_bytes;
+  long long ready_chunk_bytes;
+  int ready_chunks_per_shard;
+  int ready_skip_shard;
+  uint32_t ready_epoch;
 };
+
+// Bounded wait until every chunk overlapping bytes [lo, hi) of the gathered buffer has arrived.
+__device__ __forceinline__ bool wait_operand_ready(const Gemm2Params& p, long long lo, long long hi, volatile int* abort_flag) {
+  if (hi <= lo) return true;
+  const long long last = hi - 1;
+  long long shard = lo / p.ready_shard_bytes;
+  long long chunk = (lo - shard * p.ready_shard_bytes) / p.ready_chunk_bytes;
+  const long long shard_end = last / p.ready_shard_bytes;
+  const long long chunk_end = (last - shard_end * p.ready_shard_bytes) / p.ready_chunk_bytes;
+  while (shard < shard_end || (shard == shard_end && chunk <= chunk_end)) {
+    if (shard != p.ready_skip_shard) {
+      const uint32_t* f = p.ready_flags + shard * p.ready_chunks_per_shard + chunk;
+      const unsigned long long t0 = globaltimer_ns();
+      uint32_t spins = 0;
+      while (true) {
+        uint32_t v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+        if (static_cast<int32_t>(v - p.ready_epoch) >= 0) break;
+        if ((++spins & 0x3f) == 0) {
+          if (*abort_flag) return false;
+          if (globaltimer_ns() - t0 > WAIT_NS_PEER) {
+            *abort_flag = 1;
+            if (p.status) atomicCAS(p.status, 0, ST_TIMEOUT_PEER_FLAG);
+            return false;
+          }
+          __nanosleep(100);
+        }
+      }
+    }
+    if (++chunk == p.ready_chunks_per_shard) { chunk = 0; ++shard; }
+  }
+  // the chunks were written through the generic proxy (peer stores or DMA); the loads below use the async proxy
+  asm volatile("fence.proxy.async.global;" ::: "memory");
+  return true;
+}
 
 constexpr int G2_BM = 128;   // rows per CTA (256 per pair)
 constexpr int G2_BN = 256;   // columns per pair; each CTA stages half of the B tile
@@ -181,11 +230,23 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      const long long ldb_bytes = p.ready_ldb_bytes;
+      if (p.ready_flags && B_MN)  // every tile reads all k-rows of an MN-major B: the whole operand must be here
+        ok = wait_operand_ready(p, p.ready_b_offset, p.ready_b_offset + static_cast<long long>(p.K) * ldb_bytes, abort_flag);
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
         int tm, tn;
         pair_tile_coords(tile, tiles_m, tiles_n, tm, tn);
         const int m0 = tm * 2 * G2_BM + static_cast<int>(rank) * G2_BM;
         const int n0 = tn * G2_BN + static_cast<int>(rank) * (G2_BN / 2);
+        // Rows n0 .. n0+127 of a K-major B are one contiguous byte range.  The first tile is checked here; every
+        // later tile was checked one tile ahead (below), while the pipeline was full, so the system-scope
+        // acquire loads cost no issue time.
+        if (p.ready_flags && !B_MN && tile == pair) {
+          const long long r1 = min(n0 + G2_BN / 2, p.N);
+          ok = wait_operand_ready(p, p.ready_b_offset + n0 * ldb_bytes, p.ready_b_offset + r1 * ldb_bytes, abort_flag);
+          if (!ok) break;
+        }
+        const int check_kb = k_blocks > G2_STAGES ? G2_STAGES - 1 : k_blocks - 1;
         for (int kb = 0; kb < k_blocks; ++kb) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, ST_TIMEOUT_SMEM_EMPTY);
           if (!ok) break;
@@ -208,6 +269,14 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
               tma_load_2d_pair(b_dst + c * (G2_BK * 128), &tmB, &full_bar[stage], n0 + c * 64, k0);
           }
           if (++stage == G2_STAGES) { stage = 0; phase ^= 1; }
+          if (p.ready_flags && !B_MN && kb == check_kb && tile + num_pairs < num_tiles) {
+            int ntm, ntn;
+            pair_tile_coords(tile + num_pairs, tiles_m, tiles_n, ntm, ntn);
+            const int nn0 = ntn * G2_BN + static_cast<int>(rank) * (G2_BN / 2);
+            const long long r1 = min(nn0 + G2_BN / 2, p.N);
+            ok = wait_operand_ready(p, p.ready_b_offset + nn0 * ldb_bytes, p.ready_b_offset + r1 * ldb_bytes, abort_flag);
+            if (!ok) break;
+          }
         }
       }
       if (!ok) {
@@ -383,11 +452,33 @@ static int launch_gemm2(const CUtensorMap& tmA, const CUtensorMap& tmB, const Ge
 
 }  // namespace msq
 
+struct MsqGemmReady {
+  const void* flags;
+  long long b_offset, shard_bytes, chunk_bytes;
+  int chunks_per_shard, skip_shard;
+  unsigned epoch;
+};
+
+extern "C" int msq_gemm2_ready(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                               long long ldc, int a_mn, int b_mn, int bf16, const void* bias, const void* residual,
+                               long long ldr, const void* mask, long long ldm, int relu, int accumulate, int bn,
+                               int max_ctas, int* status, cudaStream_t stream, const MsqGemmReady* ready);
+
 // Same contract as msq_gemm.  Intended for M >= 256; smaller problems should use msq_gemm.
 extern "C" int msq_gemm2(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                          long long ldc, int a_mn, int b_mn, int bf16, const void* bias, const void* residual,
                          long long ldr, const void* mask, long long ldm, int relu, int accumulate, int bn,
                          int max_ctas, int* status, cudaStream_t stream) {
+  return msq_gemm2_ready(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, bf16, bias, residual, ldr, mask, ldm, relu,
+                         accumulate, bn, max_ctas, status, stream, nullptr);
+}
+
+// msq_gemm2 whose B operand lives in a gathered buffer that peers are still filling: `ready` describes the
+// arrival flags (see Gemm2Params).  This is the consumer half of the fused all-gather -> GEMM path.
+extern "C" int msq_gemm2_ready(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                               long long ldc, int a_mn, int b_mn, int bf16, const void* bias, const void* residual,
+                               long long ldr, const void* mask, long long ldm, int relu, int accumulate, int bn,
+                               int max_ctas, int* status, cudaStream_t stream, const MsqGemmReady* ready) {
   using namespace msq;
   (void)bn;
   if (M <= 0 || N <= 0) return 0;
@@ -408,6 +499,20 @@ extern "C" int msq_gemm2(const void* A, const void* B, void* C, int M, int N, in
   p.C = C; p.ldc = ldc;
   p.bias = bias; p.residual = residual; p.ldr = ldr; p.mask = mask; p.ldm = ldm;
   p.relu = relu; p.accumulate = accumulate; p.bf16 = bf16; p.status = status;
+  p.ready_flags = nullptr;
+  p.ready_b_offset = p.ready_ldb_bytes = p.ready_shard_bytes = p.ready_chunk_bytes = 0;
+  p.ready_chunks_per_shard = 0; p.ready_skip_shard = -1; p.ready_epoch = 0;
+  if (ready && ready->flags) {
+    if (ready->shard_bytes <= 0 || ready->chunk_bytes <= 0 || ready->chunks_per_shard <= 0) return -6;
+    p.ready_flags = static_cast<const uint32_t*>(ready->flags);
+    p.ready_b_offset = ready->b_offset;
+    p.ready_ldb_bytes = ldb * 2;
+    p.ready_shard_bytes = ready->shard_bytes;
+    p.ready_chunk_bytes = ready->chunk_bytes;
+    p.ready_chunks_per_shard = ready->chunks_per_shard;
+    p.ready_skip_shard = ready->skip_shard;
+    p.ready_epoch = ready->epoch;
+  }
   if (!a_mn && !b_mn) return launch_gemm2<false, false>(tmA, tmB, p, max_ctas, stream);
   if (!a_mn && b_mn) return launch_gemm2<false, true>(tmA, tmB, p, max_ctas, stream);
   if (a_mn && !b_mn) return launch_gemm2<true, false>(tmA, tmB, p, max_ctas, stream);

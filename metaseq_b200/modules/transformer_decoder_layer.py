@@ -96,6 +96,12 @@ class ModelParallelTransformerDecoderLayer(nn.Module):
         return ColumnParallelLinear(embed_dim, ffn_dim, bias=bias, gather_output=False, init_method=init,
                                     use_cpu_initialization=cpu_init, dtype=dtype, device=device, sequence_parallel=sp)
 
+    # Under FSDP with peer-memory collectives the four weight matrices may still be arriving from other
+    # ranks when forward starts: the fused path reads them only through ``ops.functional.gemm``, which polls
+    # the arrival flags per tile; every other path calls ``ensure_operand_ready`` first.
+    supports_operand_flags = True
+    operand_flag_parameters = ("self_attn.qkv_proj.weight", "self_attn.out_proj.weight", "fc1.weight", "fc2.weight")
+
     # ------------------------------------------------------------------ paths
     def _fused_ok(self, x, incremental_state, key_padding_mask, attn_mask) -> bool:
         if not self.use_fused_layer or incremental_state is not None or key_padding_mask is not None \
@@ -127,6 +133,9 @@ class ModelParallelTransformerDecoderLayer(nn.Module):
             return fused_decoder_layer(
                 x, spec, ln1.weight, ln1.bias, a.qkv_proj.weight, a.qkv_proj.bias, a.out_proj.weight, a.out_proj.bias,
                 ln2.weight, ln2.bias, self.fc1.weight, self.fc1.bias, self.fc2.weight, self.fc2.bias)
+        # the library ops of the modular path do not poll arrival flags: wait for the matrices here
+        for w in (self.self_attn.qkv_proj.weight, self.self_attn.out_proj.weight, self.fc1.weight, self.fc2.weight):
+            ops_f.ensure_operand_ready(w)
         return self._modular_forward(x, bt, incremental_state, self_attn_padding_mask, self_attn_mask)
 
     def _modular_forward(self, x, bt, incremental_state, key_padding_mask, attn_mask):

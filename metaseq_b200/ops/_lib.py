@@ -73,10 +73,20 @@ def _sig(lib, name, argtypes, restype=c_int):
     return fn
 
 
+class GemmReady(ctypes.Structure):
+    """Arrival-flag description of a GEMM operand that lives in a gathered buffer (``MsqGemmReady`` in
+    csrc/gemm2_sm100.cu)."""
+
+    _fields_ = [("flags", c_void_p), ("b_offset", c_longlong), ("shard_bytes", c_longlong),
+                ("chunk_bytes", c_longlong), ("chunks_per_shard", c_int), ("skip_shard", c_int),
+                ("epoch", ctypes.c_uint)]
+
+
 def _declare_kernels(lib):
     _sig(lib, "msq_gemm", [P, P, P, I, I, I, L, L, L, I, I, I, P, P, L, P, L, I, I, I, I, P, P])
     if hasattr(lib, "msq_gemm2"):
         _sig(lib, "msq_gemm2", [P, P, P, I, I, I, L, L, L, I, I, I, P, P, L, P, L, I, I, I, I, P, P])
+        _sig(lib, "msq_gemm2_ready", [P, P, P, I, I, I, L, L, L, I, I, I, P, P, L, P, L, I, I, I, I, P, P, P])
     _sig(lib, "msq_layernorm_bwd_parts", [I])
     _sig(lib, "msq_layernorm_fwd", [P, P, P, P, P, P, I, I, F, I, P])
     _sig(lib, "msq_layernorm_bwd", [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, P])
@@ -95,6 +105,7 @@ def _declare_kernels(lib):
     _sig(lib, "msq_symm_free", [P])
     _sig(lib, "msq_comm_barrier", [P, I, I, L, U, P, P])
     _sig(lib, "msq_comm_wait_flags", [P, L, L, L, L, U, P, P])
+    _sig(lib, "msq_comm_wait_flag_list", [P, P, I, U, P, P])
     _sig(lib, "msq_comm_allgather_push", [P, L, P, L, I, I, I, P, L, U, I, P, P])
     _sig(lib, "msq_comm_reduce_scatter_push", [P, L, P, L, I, I, P, L, U, P, I, P, P])
     _sig(lib, "msq_comm_allgather_ce", [P, L, P, L, I, I, I, P, L, U, P, P])

@@ -80,8 +80,13 @@ def gemm(
     accumulate: bool = False,
     bn: int = 0,
     max_ctas: int = 0,
+    b_ready=None,
 ) -> torch.Tensor:
     """``out[M,N] = epilogue(op(a) @ op(b))`` for 2-D operands.
+
+    ``b_ready`` (or an attribute ``_msq_ready`` on ``b``) names the arrival flags of a ``b`` that peer GPUs
+    are still writing (a view of a gathered FSDP buffer): an object with ``ready_struct(b)`` returning the
+    ``GemmReady`` descriptor and ``wait(b)`` blocking the stream; the 2-CTA kernel polls the flags per tile.
 
     ``a`` is stored ``[M,K]`` (``a_mn=False``) or ``[K,M]`` (``a_mn=True``);
     ``b`` is stored ``[N,K]`` (``b_mn=False``, an ``nn.Linear`` weight) or
@@ -102,6 +107,27 @@ def gemm(
             and (bias is None or bias.data_ptr() % 16 == 0):
         lib = _lib.kernels()
         pair = _GEMM_VARIANT == "2cta" or (_GEMM_VARIANT == "auto" and M >= 256 and N >= 128 and bn == 0)
+        if b_ready is None:
+            b_ready = getattr(b, "_msq_ready", None)
+        if b_ready is not None:
+            desc = b_ready.ready_struct(b) if pair else None
+            if desc is None:
+                b_ready.wait(b)  # kernel variant without flag polling: block the stream instead
+                b_ready = None
+        if b_ready is not None:
+            import ctypes as _ct
+
+            rc = lib.msq_gemm2_ready(
+                _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), M, N, K,
+                a.stride(0), b.stride(0), out.stride(0),
+                int(a_mn), int(b_mn), _bf(a),
+                _lib.ptr(bias), _lib.ptr(residual), residual.stride(0) if residual is not None else 0,
+                _lib.ptr(mask), mask.stride(0) if mask is not None else 0,
+                int(relu), int(accumulate), bn, max_ctas,
+                _lib.ptr(_lib.status_word(a.device)), _lib.stream_ptr(), _ct.byref(desc),
+            )
+            _lib.check_rc(rc, "msq_gemm2_ready")
+            return out
         fn = lib.msq_gemm2 if pair else lib.msq_gemm
         rc = fn(
             _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), M, N, K,
@@ -115,6 +141,14 @@ def gemm(
         _lib.check_rc(rc, "msq_gemm")
         return out
     return _gemm_torch(a, b, a_mn, b_mn, bias, residual, mask, relu, out, accumulate)
+
+
+def ensure_operand_ready(t: torch.Tensor):
+    """Blocks the current stream until ``t`` (a view of a gathered buffer that peers may still be filling)
+    is complete.  No-op for ordinary tensors."""
+    h = getattr(t, "_msq_ready", None)
+    if h is not None:
+        h.wait(t)
 
 
 def _gemm_operands_ok(a, b, out, residual, mask) -> bool:

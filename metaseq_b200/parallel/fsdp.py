@@ -225,6 +225,28 @@ class FullyShardedDataParallel(nn.Module):
             off += n
         for mod, pname, idx in self._shared_infos:
             mod.__dict__[pname] = self._views[idx]
+        self._ready_handle = None
+        if full is not None and self.comm is not None and self.world_size > 1:
+            # matrices carry the arrival flags of their chunks: the GEMMs that read them wait per tile inside
+            # the kernel, and only the chunks holding the small (non-matrix) parameters are awaited up front
+            inner = self.module
+            while not getattr(inner, "supports_operand_flags", False) and hasattr(inner, "module"):
+                inner = inner.module  # activation-checkpoint and similar wrappers
+            flagged = set(getattr(inner, "operand_flag_parameters", ())) \
+                if getattr(inner, "supports_operand_flags", False) else set()
+            if flagged:
+                handle = self.comm.ready_handle(full)
+                handle.active = False
+                esz = full.element_size()
+                off, small = 0, []
+                for v, n, name in zip(self._views, self.param_numels, self.param_names):
+                    if any(name == f or name.endswith("." + f) for f in flagged) and v.dim() == 2:
+                        v._msq_ready = handle
+                    else:
+                        small.append((off * esz, (off + n) * esz))
+                    off += n
+                self._ready_handle = handle
+                self._small_param_ranges = tuple(small)
         self._refresh_grad_views()
 
     def _refresh_grad_views(self):
@@ -334,8 +356,12 @@ class FullyShardedDataParallel(nn.Module):
 
     def _wait_gather(self):
         if getattr(self, "_gather_flags_pending", False):
-            # arrival flags of every rank's chunks, polled by a kernel on the compute stream
-            self.comm.wait_gathered(self._full_param)
+            handle = self.__dict__.get("_ready_handle")
+            if handle is not None and os.environ.get("MSQ_FSDP_GEMM_WAIT", "1") == "1":
+                # small parameters now; each weight matrix when (and where) its GEMM loads it
+                handle.active = self.comm.wait_byte_ranges(self._full_param, self._small_param_ranges)
+            else:
+                self.comm.wait_gathered(self._full_param)  # one kernel polling every chunk's flag
             self._gather_flags_pending = False
         if self._gather_event is not None:
             torch.cuda.current_stream().wait_event(self._gather_event)
@@ -426,6 +452,10 @@ class FullyShardedDataParallel(nn.Module):
             out = _map_first_tensor(out, lambda t: _UnitOutput.apply(self, t))
         if self.reshard_after_forward:
             self._free_full()
+        handle = self.__dict__.get("_ready_handle")
+        if handle is not None and handle.active:
+            # every matrix of the unit has been consumed at least once: later readers (backward) need no polling
+            handle.active = False
         return out
 
     # --------------------------------------------------------------- backward

@@ -172,6 +172,28 @@ class _Gathered:
     push_event: object = field(default=None, repr=False)
 
 
+class OperandReady:
+    """Arrival flags of one gathered buffer, as seen by kernels that consume views of it."""
+
+    def __init__(self, comm: "PeerComm", meta: _Gathered):
+        self.comm, self.meta = comm, meta
+        self.base_ptr = meta.tensor.data_ptr()
+        self.active = True  # cleared while no all-gather is in flight (nothing to wait for)
+
+    def ready_struct(self, view: torch.Tensor):
+        if not self.active:
+            return None
+        m = self.meta
+        off = view.data_ptr() - self.base_ptr
+        assert 0 <= off < m.numel * view.element_size()
+        return _lib.GemmReady(self.comm.heap.flags_ptr + 4 * m.flag_base, off, m.shard_bytes, m.chunk_bytes,
+                              m.chunks_per_shard, self.comm.rank, m.ag_epoch)
+
+    def wait(self, view: torch.Tensor):
+        if self.active:
+            self.comm.wait_gathered(self.meta.tensor)
+
+
 class PeerComm:
     """Collectives over a ``SymmetricHeap`` for one process group (ranks of one NVSwitch node)."""
 
@@ -188,6 +210,7 @@ class PeerComm:
         self.chunk_bytes = int(chunk_bytes)
         self.max_ctas = int(max_ctas)
         self._bufs: Dict[int, _Gathered] = {}
+        self._range_cache = {}
         self._barrier_base = self.heap.alloc_flags(self.world)
         self._barrier_epoch = 0
         self._ar_base = self.heap.alloc_flags(self.world)
@@ -309,6 +332,50 @@ class PeerComm:
                                                 own, own + meta.chunks_per_shard, meta.ag_epoch,
                                                 self._status(), _lib.stream_ptr())
         self._check(rc, "msq_comm_wait_flags")
+
+    def ready_handle(self, full: torch.Tensor) -> "OperandReady":
+        """Handle to hang on views of ``full`` (attribute ``_msq_ready``) so that GEMMs reading them poll the
+        arrival flags of exactly the chunks they load."""
+        return OperandReady(self, self.meta_of(full))
+
+    def wait_byte_ranges(self, full: torch.Tensor, ranges) -> bool:
+        """Blocks the current stream until the chunks overlapping the given ``(lo, hi)`` byte ranges of ``full``
+        have arrived from the other ranks.  Returns False (and waits for everything) when the ranges touch
+        more than 32 chunks."""
+        meta = self.meta_of(full)
+        key = (meta.offset, tuple(ranges))
+        cached = self._range_cache.get(key)
+        if cached is not None:
+            if cached is False:
+                self.wait_gathered(full)
+                return False
+            if len(cached):
+                rc = _lib.kernels().msq_comm_wait_flag_list(self.heap.flags_ptr, cached, len(cached), meta.ag_epoch,
+                                                            self._status(), _lib.stream_ptr())
+                self._check(rc, "msq_comm_wait_flag_list")
+            return True
+        idx = set()
+        for lo, hi in ranges:
+            if hi <= lo:
+                continue
+            b = lo
+            while b < hi:
+                shard = b // meta.shard_bytes
+                chunk = (b - shard * meta.shard_bytes) // meta.chunk_bytes
+                if shard != self.rank:
+                    idx.add(meta.flag_base + shard * meta.chunks_per_shard + chunk)
+                b = shard * meta.shard_bytes + (chunk + 1) * meta.chunk_bytes
+        if len(idx) > 32:
+            self._range_cache[key] = False
+            self.wait_gathered(full)
+            return False
+        arr = (ctypes.c_int * len(idx))(*sorted(idx))
+        self._range_cache[key] = arr
+        if idx:
+            rc = _lib.kernels().msq_comm_wait_flag_list(self.heap.flags_ptr, arr, len(idx), meta.ag_epoch, self._status(),
+                                                        _lib.stream_ptr())
+            self._check(rc, "msq_comm_wait_flag_list")
+        return True
 
     def gemm_flags(self, full: torch.Tensor):
         """(flags pointer, first flag index, chunk bytes, chunks per shard, shard bytes, epoch) for consumers

@@ -28,7 +28,7 @@ def _worker(rank, world, port, provider, transport, results):
         from metaseq_b200.parallel.symm import PeerComm
 
         dev = torch.device("cuda", rank)
-        comm = PeerComm(dist.group.WORLD, dev, heap_bytes=256 << 20, chunk_bytes=1 << 18, provider=provider,
+        comm = PeerComm(dist.group.WORLD, dev, heap_bytes=512 << 20, chunk_bytes=1 << 18, provider=provider,
                         transport=transport)
         for _ in range(3):
             comm.barrier()
@@ -44,6 +44,36 @@ def _worker(rank, world, port, provider, transport, results):
             comm.all_gather(full, local, stream=torch.cuda.Stream() if step == 1 else None)
             torch.cuda.synchronize()
             assert torch.equal(full, ref), f"all_gather mismatch at step {step}"
+            dist.barrier()
+        # ---- all-gather consumed by a GEMM that polls the arrival flags per tile (fused all-gather -> GEMM)
+        from metaseq_b200.ops import functional as F
+
+        Nw, Kw, Mx = 1024 * world, 512, 1024
+        fullw = comm.alloc_full(Nw * Kw, torch.float16)
+        handle = comm.ready_handle(fullw)
+        wview = fullw.view(Nw, Kw)
+        x = torch.randn(Mx, Kw, device=dev, dtype=torch.float16, generator=torch.Generator(device=dev).manual_seed(5))
+        dyv = torch.randn(Mx, Nw, device=dev, dtype=torch.float16, generator=torch.Generator(device=dev).manual_seed(6))
+        side = torch.cuda.Stream()
+        for step in range(4):
+            g = torch.Generator(device=dev).manual_seed(1000 + 10 * step + rank)
+            local = torch.randn(Nw * Kw // world, device=dev, dtype=torch.float16, generator=g) * 0.05
+            ref_w = torch.empty(Nw * Kw, device=dev, dtype=torch.float16)
+            dist.all_gather_into_tensor(ref_w, local)
+            ref_w = ref_w.view(Nw, Kw)
+            torch.cuda.synchronize()
+            dist.barrier()
+            comm.all_gather_many([(fullw, local)], side)   # peer copies in flight on the side stream
+            handle.active = True
+            if step % 2 == 0:
+                y = F.gemm(x, wview, b_ready=handle)                      # x @ W^T, K-major B: waits per tile
+                ref = x.float() @ ref_w.float().t()
+            else:
+                y = F.gemm(dyv, wview, b_mn=True, b_ready=handle)         # dy @ W, MN-major B: waits once
+                ref = dyv.float() @ ref_w.float()
+            torch.cuda.synchronize()
+            err = (y.float() - ref).abs().max().item()
+            assert err <= 2e-2 * ref.abs().max().item() + 1e-3, f"flag-polling GEMM mismatch at step {step}: {err}"
             dist.barrier()
         # ---- reduce-scatter with fp32 sum, scale, norm and overflow flag
         for step in range(3):
