@@ -43,6 +43,7 @@ struct Gemm2Params {
   int ready_chunks_per_shard;
   int ready_skip_shard;
   uint32_t ready_epoch;
+  long long* prof;  // debug: cycle counters of the first pair's MMA thread (see msq_gemm2_set_prof)
 };
 
 // Bounded wait until every chunk overlapping bytes [lo, hi) of the gathered buffer has arrived.
@@ -87,7 +88,8 @@ constexpr int G2_STAGES = 6;
 constexpr int G2_THREADS = 192;
 constexpr uint32_t G2_A_BYTES = G2_BM * G2_BK * 2;        // 16 KB
 constexpr uint32_t G2_B_BYTES = (G2_BN / 2) * G2_BK * 2;  // 16 KB
-constexpr uint32_t G2_SMEM = G2_STAGES * (G2_A_BYTES + G2_B_BYTES) + 1024 + 256;
+constexpr uint32_t G2_EPI_BYTES = 4 * 2048;  // per epilogue warp: 32 rows x 64 bytes of output being transposed
+constexpr uint32_t G2_SMEM = G2_STAGES * (G2_A_BYTES + G2_B_BYTES) + G2_EPI_BYTES + 1024 + 256;
 constexpr uint32_t G2_TMEM_COLS = 2 * G2_BN;
 constexpr uint32_t PEER_BIT_MASK = 0xFEFFFFFFu;  // clears the CTA-parity bit of a shared address
 
@@ -171,7 +173,8 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
   uint8_t* sB = smem + G2_STAGES * G2_A_BYTES;
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(sB + G2_STAGES * G2_B_BYTES);
+  uint8_t* sEpi = sB + G2_STAGES * G2_B_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(sEpi + G2_EPI_BYTES);
   uint64_t* empty_bar = full_bar + G2_STAGES;
   uint64_t* tfull_bar = empty_bar + G2_STAGES;
   uint64_t* tempty_bar = tfull_bar + 2;
@@ -292,15 +295,21 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       uint32_t phase = 0;
       bool ok = true;
       int it = 0;
+      long long prof_tempty = 0, prof_full = 0;
+      const long long prof_t0 = clock64();
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++it) {
         const int buf = it & 1;
         const uint32_t acc = tmem_base + buf * G2_BN;
+        const long long c0 = clock64();
         ok = mbar_wait(&tempty_bar[buf], ((it >> 1) & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
         if (!ok) break;
+        prof_tempty += clock64() - c0;
         tc_fence_after();
         for (int kb = 0; kb < k_blocks; ++kb) {
+          const long long c1 = clock64();
           ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
           if (!ok) break;
+          prof_full += clock64() - c1;
           tc_fence_after();
           const uint32_t a_addr = smem_u32(sA + stage * G2_A_BYTES);
           const uint32_t b_addr = smem_u32(sB + stage * G2_B_BYTES);
@@ -319,6 +328,12 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         if (!ok) break;
         tc_commit_pair(&tfull_bar[buf]);  // accumulator ready in both CTAs
       }
+      if (p.prof && pair == 0) {
+        p.prof[0] = clock64() - prof_t0;
+        p.prof[1] = prof_tempty;
+        p.prof[2] = prof_full;
+        p.prof[3] = it;
+      }
     }
   } else {
     // ---------------------------------------------------------------- epilogue (both CTAs)
@@ -334,8 +349,14 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       ok = mbar_wait_warp(&tfull_bar[buf], (it >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
       if (!ok) break;
       tc_fence_after();
-      const int row = tm * 2 * G2_BM + static_cast<int>(rank) * G2_BM + quarter * 32 + lane;
+      const int row_base = tm * 2 * G2_BM + static_cast<int>(rank) * G2_BM + quarter * 32;
+      const int row = row_base + lane;
       const bool row_ok = row < p.M;
+      // Output path: each lane owns one row of the accumulator, so direct stores would touch 32 different
+      // lines with 16 bytes each.  The packed values go through a swizzled shared-memory tile instead and
+      // leave as 8 rows x 64 contiguous bytes per store instruction (full 32-byte sectors).
+      uint8_t* stage = sEpi + (warp - 2) * 2048;
+      const int st_row = lane >> 2, st_vec = lane & 3;
       const uint32_t taddr0 = tmem_base + buf * G2_BN + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll 1
       for (int c = 0; c < G2_BN / 32; ++c) {
@@ -407,10 +428,21 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                 o.x = pack2<false>(f[0], f[1]); o.y = pack2<false>(f[2], f[3]);
                 o.z = pack2<false>(f[4], f[5]); o.w = pack2<false>(f[6], f[7]);
               }
-              *reinterpret_cast<uint4*>(crow + v * 8) = o;
+              *reinterpret_cast<uint4*>(stage + lane * 64 + ((v ^ ((lane >> 1) & 3)) << 4)) = o;
             }
           }
         }
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int r = j * 8 + st_row;
+          const int col = col0 + st_vec * 8;
+          if (row_base + r < p.M && col < p.N) {
+            const uint4 o = *reinterpret_cast<const uint4*>(stage + r * 64 + ((st_vec ^ ((r >> 1) & 3)) << 4));
+            *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.C) + static_cast<long long>(row_base + r) * p.ldc + col) = o;
+          }
+        }
+        __syncwarp();
       }
       tc_fence_before();
       __syncwarp();
@@ -451,6 +483,11 @@ static int launch_gemm2(const CUtensorMap& tmA, const CUtensorMap& tmB, const Ge
 }
 
 }  // namespace msq
+
+static long long* g_gemm2_prof = nullptr;
+// Debug aid: device buffer of 4 int64 that receives, from the MMA thread of pair 0 of the next launches,
+// {total cycles, cycles waiting for a free accumulator, cycles waiting for operand stages, tiles}.
+extern "C" void msq_gemm2_set_prof(long long* buf) { g_gemm2_prof = buf; }
 
 struct MsqGemmReady {
   const void* flags;
@@ -499,6 +536,7 @@ extern "C" int msq_gemm2_ready(const void* A, const void* B, void* C, int M, int
   p.C = C; p.ldc = ldc;
   p.bias = bias; p.residual = residual; p.ldr = ldr; p.mask = mask; p.ldm = ldm;
   p.relu = relu; p.accumulate = accumulate; p.bf16 = bf16; p.status = status;
+  p.prof = g_gemm2_prof;
   p.ready_flags = nullptr;
   p.ready_b_offset = p.ready_ldb_bytes = p.ready_shard_bytes = p.ready_chunk_bytes = 0;
   p.ready_chunks_per_shard = 0; p.ready_skip_shard = -1; p.ready_epoch = 0;
