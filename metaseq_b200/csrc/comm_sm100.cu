@@ -247,6 +247,74 @@ comm_reduce_slots_kernel(const uint4* __restrict__ slots, long long shard_numel,
   if (bad && overflow) *overflow = 1;
 }
 
+// Row-block reduction behind a scattering GEMM: this rank owns `rows` rows of an [*, N] matrix; slot s holds
+// the partial product computed by rank s.  out_row = sum_s slot_s + bias + residual, written to `out_local`
+// (reduce-scatter) and, when bcast.p[0] is set, also stored into every rank's copy of the full matrix at
+// row row0 + r (all-reduce = reduce-scatter + all-gather), after which flag `bcast_flag_base + rank` is
+// published on every rank by the last CTA.
+template <bool BF16>
+__global__ void __launch_bounds__(256)
+comm_reduce_rows_kernel(const uint4* __restrict__ slots, long long slot_stride_vec, int world, int rows, int N,
+                        const uint16_t* __restrict__ bias, const uint16_t* __restrict__ residual, long long ldr,
+                        uint16_t* __restrict__ out_local, long long ldo, PeerPtrs bcast, long long bcast_off_bytes,
+                        long long ld_bcast, int row0, int rank, const uint32_t* flags, long long flag_base, uint32_t epoch,
+                        PeerPtrs sig, long long bcast_flag_base, unsigned int* done_counter, int* status) {
+  __shared__ bool ok_s, last_s;
+  if (threadIdx.x == 0) ok_s = true;
+  __syncthreads();
+  if (threadIdx.x < world) {
+    if (!wait_flag(flags + flag_base + threadIdx.x, epoch, status)) ok_s = false;
+  }
+  __syncthreads();
+  if (!ok_s) return;
+  const int vec_per_row = N >> 3;
+  const long long total = static_cast<long long>(rows) * vec_per_row;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const bool do_bcast = bcast.p[0] != nullptr;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int r = static_cast<int>(i / vec_per_row);
+    const int c = static_cast<int>(i - static_cast<long long>(r) * vec_per_row) * 8;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    auto add16 = [&](const uint4& v) {
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack2<BF16>(w[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    };
+    for (int s = 0; s < world; ++s) add16(slots[s * slot_stride_vec + i]);
+    if (bias) add16(*reinterpret_cast<const uint4*>(bias + c));
+    if (residual) add16(*reinterpret_cast<const uint4*>(residual + static_cast<long long>(r) * ldr + c));
+    uint4 o;
+    o.x = pack2<BF16>(acc[0], acc[1]);
+    o.y = pack2<BF16>(acc[2], acc[3]);
+    o.z = pack2<BF16>(acc[4], acc[5]);
+    o.w = pack2<BF16>(acc[6], acc[7]);
+    if (out_local) *reinterpret_cast<uint4*>(out_local + static_cast<long long>(r) * ldo + c) = o;
+    if (do_bcast) {
+      for (int pp = 0; pp < world; ++pp) {
+        const int peer = (rank + pp) % world;
+        uint16_t* d = reinterpret_cast<uint16_t*>(static_cast<uint8_t*>(bcast.p[peer]) + bcast_off_bytes);
+        *reinterpret_cast<uint4*>(d + static_cast<long long>(row0 + r) * ld_bcast + c) = o;
+      }
+    }
+  }
+  if (!do_bcast) return;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) last_s = (atomicAdd(done_counter, 1u) == gridDim.x - 1);
+  __syncthreads();
+  if (last_s) {
+    if (threadIdx.x < world) {
+      __threadfence_system();
+      st_release_sys(static_cast<uint32_t*>(sig.p[threadIdx.x]) + bcast_flag_base + rank, epoch);
+    }
+    if (threadIdx.x == 0) *done_counter = 0;
+  }
+}
+
 // ------------------------------------------------------- one-shot all-reduce
 // For small tensors (decode activations, vocab-parallel loss statistics): every rank stores its
 // input into slot `rank` of every peer's slot area, publishes a flag, waits for the other ranks'
@@ -407,6 +475,43 @@ extern "C" int msq_comm_wait_flag_list(const void* flags, const int* idx, int n,
   for (int i = 0; i < 32; ++i) l.idx[i] = i < n ? idx[i] : 0;
   l.n = n;
   msq::comm_wait_flag_list_kernel<<<1, 32, 0, stream>>>(static_cast<const uint32_t*>(flags), l, epoch, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// Publishes one flag (flag_base + rank) on every rank; stream order makes everything launched before it on
+// this stream (for instance the peer stores of a scattering GEMM) visible first.
+extern "C" int msq_comm_signal(void* const* sig_ptrs, int rank, int world, long long flag_base, unsigned epoch,
+                               cudaStream_t stream) {
+  if (world > msq::MAX_PEERS) return -2;
+  msq::comm_signal_kernel<<<1, 128, 0, stream>>>(make_ptrs(sig_ptrs, world), world, flag_base, rank, 1, epoch);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+extern "C" int msq_comm_reduce_rows(const void* slots, long long slot_stride_bytes, int world, int rows, int N,
+                                    const void* bias, const void* residual, long long ldr, void* out_local, long long ldo,
+                                    void* const* bcast_ptrs, long long bcast_off_bytes, long long ld_bcast, int row0,
+                                    int rank, int bf16, const void* flags, long long flag_base, unsigned epoch,
+                                    void* const* sig_ptrs, long long bcast_flag_base, unsigned* done_counter, int max_ctas,
+                                    int* status, cudaStream_t stream) {
+  if (world > msq::MAX_PEERS) return -2;
+  if ((N & 7) || (slot_stride_bytes & 15) || (ldr & 7) || (ldo & 7) || (ld_bcast & 7)) return -2;
+  if (rows <= 0) return 0;
+  long long want = (static_cast<long long>(rows) * (N >> 3) + 255) / 256;
+  int grid = static_cast<int>(want < max_ctas ? want : max_ctas);
+  if (grid < 1) grid = 1;
+  PeerPtrs bc;
+  for (int i = 0; i < msq::MAX_PEERS; ++i) bc.p[i] = (bcast_ptrs && i < world) ? bcast_ptrs[i] : nullptr;
+  PeerPtrs sg = make_ptrs(sig_ptrs, world);
+  if (bf16)
+    msq::comm_reduce_rows_kernel<true><<<grid, 256, 0, stream>>>(
+        static_cast<const uint4*>(slots), slot_stride_bytes >> 4, world, rows, N, static_cast<const uint16_t*>(bias),
+        static_cast<const uint16_t*>(residual), ldr, static_cast<uint16_t*>(out_local), ldo, bc, bcast_off_bytes, ld_bcast,
+        row0, rank, static_cast<const uint32_t*>(flags), flag_base, epoch, sg, bcast_flag_base, done_counter, status);
+  else
+    msq::comm_reduce_rows_kernel<false><<<grid, 256, 0, stream>>>(
+        static_cast<const uint4*>(slots), slot_stride_bytes >> 4, world, rows, N, static_cast<const uint16_t*>(bias),
+        static_cast<const uint16_t*>(residual), ldr, static_cast<uint16_t*>(out_local), ldo, bc, bcast_off_bytes, ld_bcast,
+        row0, rank, static_cast<const uint32_t*>(flags), flag_base, epoch, sg, bcast_flag_base, done_counter, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

@@ -44,6 +44,13 @@ struct Gemm2Params {
   int ready_skip_shard;
   uint32_t ready_epoch;
   long long* prof;  // debug: cycle counters of the first pair's MMA thread (see msq_gemm2_set_prof)
+  // Row-scatter output (GEMM -> reduce-scatter over NVLink): when scatter_world > 0 the tile rows are not
+  // written to C but stored into peer memory: row r belongs to rank r / scatter_rows and lands at
+  // scatter_base[that rank] + (r % scatter_rows) * ldc.  Each base already points at the slot reserved for
+  // this source rank, so the owner later sums one slot per source.  Epilogue options are not applied.
+  void* scatter_base[16];
+  int scatter_world;
+  int scatter_rows;
 };
 
 // Bounded wait until every chunk overlapping bytes [lo, hi) of the gathered buffer has arrived.
@@ -366,7 +373,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         tmem_ld_32x32(taddr0 + c * 32, r);
         tmem_ld_wait();
         if (row_ok) {
-          uint16_t* crow = reinterpret_cast<uint16_t*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+          const uint16_t* crow = reinterpret_cast<const uint16_t*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             const int col = col0 + v * 8;
@@ -439,7 +446,14 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           const int col = col0 + st_vec * 8;
           if (row_base + r < p.M && col < p.N) {
             const uint4 o = *reinterpret_cast<const uint4*>(stage + r * 64 + ((st_vec ^ ((r >> 1) & 3)) << 4));
-            *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.C) + static_cast<long long>(row_base + r) * p.ldc + col) = o;
+            const int grow = row_base + r;
+            if (p.scatter_world > 0) {
+              const int owner = grow / p.scatter_rows;
+              *reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.scatter_base[owner]) +
+                                        static_cast<long long>(grow - owner * p.scatter_rows) * p.ldc + col) = o;
+            } else {
+              *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.C) + static_cast<long long>(grow) * p.ldc + col) = o;
+            }
           }
         }
         __syncwarp();
@@ -512,12 +526,39 @@ extern "C" int msq_gemm2(const void* A, const void* B, void* C, int M, int N, in
 
 // msq_gemm2 whose B operand lives in a gathered buffer that peers are still filling: `ready` describes the
 // arrival flags (see Gemm2Params).  This is the consumer half of the fused all-gather -> GEMM path.
+static int gemm2_common(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                        long long ldc, int a_mn, int b_mn, int bf16, const void* bias, const void* residual,
+                        long long ldr, const void* mask, long long ldm, int relu, int accumulate,
+                        int max_ctas, int* status, cudaStream_t stream, const MsqGemmReady* ready,
+                        void* const* scatter_ptrs, int scatter_world, int scatter_rows);
+
 extern "C" int msq_gemm2_ready(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                                long long ldc, int a_mn, int b_mn, int bf16, const void* bias, const void* residual,
                                long long ldr, const void* mask, long long ldm, int relu, int accumulate, int bn,
                                int max_ctas, int* status, cudaStream_t stream, const MsqGemmReady* ready) {
-  using namespace msq;
   (void)bn;
+  return gemm2_common(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, bf16, bias, residual, ldr, mask, ldm, relu, accumulate,
+                      max_ctas, status, stream, ready, nullptr, 0, 0);
+}
+
+// Producer half of the fused GEMM -> reduce-scatter path: rows [r * rows_per_rank, (r+1) * rows_per_rank) of
+// op(A) @ op(B) are stored into dst_ptrs[r] (peer memory, row stride ldc) instead of a local C.
+extern "C" int msq_gemm2_scatter(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb,
+                                 long long ldc, int a_mn, int b_mn, int bf16, void* const* dst_ptrs, int world,
+                                 int rows_per_rank, int max_ctas, int* status, cudaStream_t stream) {
+  if (world <= 0 || world > 16 || rows_per_rank <= 0 || static_cast<long long>(rows_per_rank) * world < M) return -7;
+  for (int i = 0; i < world; ++i)
+    if (reinterpret_cast<uintptr_t>(dst_ptrs[i]) & 15) return -4;
+  return gemm2_common(A, B, nullptr, M, N, K, lda, ldb, ldc, a_mn, b_mn, bf16, nullptr, nullptr, 0, nullptr, 0, 0, 0,
+                      max_ctas, status, stream, nullptr, dst_ptrs, world, rows_per_rank);
+}
+
+static int gemm2_common(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                        long long ldc, int a_mn, int b_mn, int bf16, const void* bias, const void* residual,
+                        long long ldr, const void* mask, long long ldm, int relu, int accumulate,
+                        int max_ctas, int* status, cudaStream_t stream, const MsqGemmReady* ready,
+                        void* const* scatter_ptrs, int scatter_world, int scatter_rows) {
+  using namespace msq;
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || (N & 7) || (ldc & 7) || (reinterpret_cast<uintptr_t>(C) & 15)) return -4;
   if (g2_num_sms == 0) {
@@ -537,6 +578,9 @@ extern "C" int msq_gemm2_ready(const void* A, const void* B, void* C, int M, int
   p.bias = bias; p.residual = residual; p.ldr = ldr; p.mask = mask; p.ldm = ldm;
   p.relu = relu; p.accumulate = accumulate; p.bf16 = bf16; p.status = status;
   p.prof = g_gemm2_prof;
+  p.scatter_world = scatter_world;
+  p.scatter_rows = scatter_rows;
+  for (int i = 0; i < 16; ++i) p.scatter_base[i] = (scatter_ptrs && i < scatter_world) ? scatter_ptrs[i] : nullptr;
   p.ready_flags = nullptr;
   p.ready_b_offset = p.ready_ldb_bytes = p.ready_shard_bytes = p.ready_chunk_bytes = 0;
   p.ready_chunks_per_shard = 0; p.ready_skip_shard = -1; p.ready_epoch = 0;

@@ -108,6 +108,9 @@ def _declare_kernels(lib):
     _sig(lib, "msq_comm_wait_flag_list", [P, P, I, U, P, P])
     _sig(lib, "msq_comm_allgather_push", [P, L, P, L, I, I, I, P, L, U, I, P, P])
     _sig(lib, "msq_comm_reduce_scatter_push", [P, L, P, L, I, I, P, L, U, P, I, P, P])
+    _sig(lib, "msq_comm_signal", [P, I, I, L, U, P])
+    _sig(lib, "msq_comm_reduce_rows", [P, L, I, I, I, P, P, L, P, L, P, L, L, I, I, I, P, L, U, P, L, P, I, P, P])
+    _sig(lib, "msq_gemm2_scatter", [P, P, I, I, I, L, L, L, I, I, I, P, I, I, I, P, P])
     _sig(lib, "msq_comm_allgather_ce", [P, L, P, L, I, I, I, P, L, U, P, P])
     _sig(lib, "msq_comm_reduce_scatter_ce", [P, L, P, L, I, I, P, L, U, P])
     _sig(lib, "msq_comm_reduce_slots", [P, L, I, F, P, I, I, P, P, P, L, U, I, P, P])

@@ -453,3 +453,127 @@ class PeerComm:
 
     def close(self):
         self.heap.close()
+
+
+class TPComm:
+    """Tensor-parallel collectives fused with the GEMMs that produce their input.
+
+    ``gemm_all_reduce`` / ``gemm_reduce_scatter`` run the row-parallel product (out_proj, fc2 and the
+    data-gradient products of the column-parallel layers) with the scattering epilogue of the 2-CTA GEMM:
+    every output tile is stored straight into the memory of the rank that owns its rows, tile by tile while
+    the main loop continues, and the owner sums one slot per source rank, adds bias and residual once and
+    (for the all-reduce) stores the finished rows into every rank's copy.  This replaces
+    ``F.linear`` + ``dist.all_reduce`` / ``_reduce_scatter_base`` of the reference
+    (metaseq/modules/megatron/mpu/layers.py:539-676, mappings.py:27-177).
+    """
+
+    def __init__(self, group, device, max_rows: int, max_cols: int, dtype=torch.float16, provider: str = "auto"):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.dtype = dtype
+        esz = torch.empty((), dtype=dtype).element_size()
+        self.max_bytes = int(max_rows) * int(max_cols) * esz
+        self.comm = PeerComm(group, device, heap_bytes=4 * (self.max_bytes + 4096) + (8 << 20), provider=provider)
+        heap = self.comm.heap
+        self.slots_off = [heap.alloc(self.max_bytes), heap.alloc(self.max_bytes)]
+        self.bcast_off = [heap.alloc(self.max_bytes), heap.alloc(self.max_bytes)]
+        self.rs_base = heap.alloc_flags(self.world)
+        self.bc_base = heap.alloc_flags(self.world)
+        self.epoch = 0
+        self._done = torch.zeros(1, dtype=torch.int32, device=device)
+        self.fused_calls = 0
+        self.fallback_calls = 0
+
+    # ----------------------------------------------------------------- helpers
+    def _eligible(self, a, w, M, N, b_mn) -> bool:
+        return (a.is_cuda and a.dtype == self.dtype and w.dtype == self.dtype and M % self.world == 0 and M >= 256
+                and N >= 128 and N % 8 == 0 and M * N * a.element_size() <= self.max_bytes
+                and a.stride(-1) == 1 and w.stride(-1) == 1 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+                and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and (M // self.world) * N * a.element_size() % 16 == 0)
+
+    def _scatter_reduce(self, a, w, bias, residual, b_mn, broadcast: bool):
+        M = a.shape[0]
+        N = w.shape[1] if b_mn else w.shape[0]
+        K = a.shape[1]
+        heap, lib = self.comm.heap, _lib.kernels()
+        self.epoch += 1
+        par = self.epoch & 1
+        rows = M // self.world
+        esz = a.element_size()
+        slot_bytes = rows * N * esz
+        dst = (ctypes.c_void_p * self.world)(*[heap.ptrs[r] + self.slots_off[par] + self.rank * slot_bytes
+                                               for r in range(self.world)])
+        status, stream = self.comm._status(), _lib.stream_ptr()
+        rc = lib.msq_gemm2_scatter(_lib.ptr(a), _lib.ptr(w), M, N, K, a.stride(0), w.stride(0), N, 0, int(b_mn),
+                                   int(self.dtype == torch.bfloat16), dst, self.world, rows, 0, status, stream)
+        _lib.check_rc(rc, "msq_gemm2_scatter")
+        rc = lib.msq_comm_signal(heap.ptr_array, self.rank, self.world, self.rs_base, self.epoch, stream)
+        _lib.check_rc(rc, "msq_comm_signal")
+        out_local = None
+        if not broadcast:
+            out_local = torch.empty((rows, N), dtype=a.dtype, device=a.device)
+        res_ptr, ldr = None, 0
+        if residual is not None:
+            res = residual if not broadcast else residual[self.rank * rows:(self.rank + 1) * rows]
+            assert res.stride(-1) == 1
+            res_ptr, ldr = _lib.ptr(res), res.stride(0)
+        rc = lib.msq_comm_reduce_rows(
+            ctypes.c_void_p(heap.ptrs[self.rank] + self.slots_off[par]), slot_bytes, self.world, rows, N,
+            _lib.ptr(bias) if bias is not None else None, res_ptr, ldr,
+            _lib.ptr(out_local) if out_local is not None else None, N,
+            heap.ptr_array if broadcast else None, self.bcast_off[par], N, self.rank * rows, self.rank,
+            int(self.dtype == torch.bfloat16), heap.flags_ptr, self.rs_base, self.epoch, heap.ptr_array, self.bc_base,
+            _lib.ptr(self._done), 64, status, stream)
+        _lib.check_rc(rc, "msq_comm_reduce_rows")
+        self.fused_calls += 1
+        if not broadcast:
+            return out_local
+        rc = lib.msq_comm_wait_flags(heap.flags_ptr, self.bc_base, self.bc_base + self.world, 0, 0, self.epoch, status, stream)
+        _lib.check_rc(rc, "msq_comm_wait_flags")
+        out = torch.empty((M, N), dtype=a.dtype, device=a.device)
+        out.copy_(heap.view(self.bcast_off[par], M * N, a.dtype).view(M, N))
+        return out
+
+    # ------------------------------------------------------------------- public
+    def gemm_all_reduce(self, a, w, bias=None, residual=None, b_mn: bool = False):
+        """``residual + bias + sum_over_ranks(a @ op(w))`` on every rank (``op(w) = w^T`` unless ``b_mn``)."""
+        M = a.shape[0]
+        N = w.shape[1] if b_mn else w.shape[0]
+        if self._eligible(a, w, M, N, b_mn):
+            return self._scatter_reduce(a, w, bias, residual, b_mn, broadcast=True)
+        from metaseq_b200.ops import functional as F
+
+        self.fallback_calls += 1
+        part = F.gemm(a, w, b_mn=b_mn)
+        self.all_reduce_(part)
+        if bias is not None:
+            part = part + bias
+        if residual is not None:
+            part = part.add_(residual)
+        return part
+
+    def gemm_reduce_scatter(self, a, w, bias=None, residual_shard=None, b_mn: bool = False):
+        """Rows ``[rank * M/p, (rank+1) * M/p)`` of ``bias + sum_over_ranks(a @ op(w))`` plus the local residual
+        shard (sequence parallelism)."""
+        M = a.shape[0]
+        N = w.shape[1] if b_mn else w.shape[0]
+        if self._eligible(a, w, M, N, b_mn):
+            return self._scatter_reduce(a, w, bias, residual_shard, b_mn, broadcast=False)
+        from metaseq_b200.ops import functional as F
+
+        self.fallback_calls += 1
+        part = F.gemm(a, w, b_mn=b_mn)
+        out = torch.empty((M // self.world, N), dtype=part.dtype, device=part.device)
+        dist.reduce_scatter_tensor(out, part, group=self.group)
+        if bias is not None:
+            out = out + bias
+        if residual_shard is not None:
+            out = out.add_(residual_shard)
+        return out
+
+    def all_reduce_(self, t: torch.Tensor) -> torch.Tensor:
+        return self.comm.all_reduce(t)
+
+    def close(self):
+        self.comm.close()

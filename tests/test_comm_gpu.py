@@ -132,3 +132,62 @@ def test_peer_collectives(provider, transport):
         mp.spawn(_worker, args=(world, _free_port(), provider, transport, results), nprocs=world, join=True)
         assert len(results) == world
         print("symmetric memory:", dict(results[0]))
+
+
+def _tp_worker(rank, world, port, results):
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from metaseq_b200.ops import _lib
+        from metaseq_b200.parallel.symm import TPComm
+
+        M, N, K = 2048, 1024, 512  # K is this rank's slice of the contraction dimension
+        tp = TPComm(dist.group.WORLD, dev, max_rows=M, max_cols=N)
+        bias = torch.randn(N, device=dev, dtype=torch.float16, generator=torch.Generator(device=dev).manual_seed(3))
+        resid = torch.randn(M, N, device=dev, dtype=torch.float16, generator=torch.Generator(device=dev).manual_seed(4))
+        for step in range(4):
+            g = torch.Generator(device=dev).manual_seed(50 + 10 * step + rank)
+            a = torch.randn(M, K, device=dev, dtype=torch.float16, generator=g)
+            w = torch.randn(N, K, device=dev, dtype=torch.float16, generator=g) * 0.05
+            ref = a.float() @ w.float().t()
+            dist.all_reduce(ref)
+            ref = ref + bias.float() + resid.float()
+            out = tp.gemm_all_reduce(a, w, bias, resid)
+            torch.cuda.synchronize()
+            tol = 2e-2 * ref.abs().max().item()
+            assert (out.float() - ref).abs().max().item() <= tol, f"gemm_all_reduce mismatch at step {step}"
+            rows = M // world
+            shard = tp.gemm_reduce_scatter(a, w, bias, resid[rank * rows:(rank + 1) * rows])
+            torch.cuda.synchronize()
+            assert (shard.float() - ref[rank * rows:(rank + 1) * rows]).abs().max().item() <= tol, "gemm_reduce_scatter mismatch"
+            # data-gradient form: dy @ W with W stored [K, N]
+            wt = w.t().contiguous()
+            out2 = tp.gemm_all_reduce(a, wt, None, None, b_mn=True)
+            ref2 = a.float() @ wt.float()
+            dist.all_reduce(ref2)
+            torch.cuda.synchronize()
+            assert (out2.float() - ref2).abs().max().item() <= 2e-2 * ref2.abs().max().item()
+        assert tp.fused_calls == 12 and tp.fallback_calls == 0
+        assert _lib.check_status(dev) == 0
+        results[rank] = True
+        dist.barrier()
+        tp.close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_gemm_fused_with_tensor_parallel_reduction():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least two GPUs")
+    import torch.multiprocessing as mp
+
+    world = 2
+    with mp.Manager() as mgr:
+        results = mgr.dict()
+        mp.spawn(_tp_worker, args=(world, _free_port(), results), nprocs=world, join=True)
+        assert len(results) == world
