@@ -84,6 +84,9 @@ def main(cfg: Cfg) -> None:
 
 def build_model_and_criterion(cfg, task):
     """Model wrapped per the data-parallel backend, and the criterion."""
+    from metaseq_b200.parallel import symm
+
+    symm.set_comm_backend(getattr(cfg.common, "comm_backend", "nccl"))
     if cfg.distributed_training.ddp_backend == "fully_sharded":
         extra = {"use_sharded_state": cfg.distributed_training.use_sharded_state,
                  "comm": getattr(cfg.common, "comm_backend", "nccl")}

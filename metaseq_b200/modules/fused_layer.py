@@ -73,7 +73,9 @@ def _row_parallel_out(a, w, bias, residual, spec):
     """``residual + bias + reduce(a @ w^T)`` over the tensor-parallel group."""
     if spec.tp_world == 1:
         return F.gemm(a, w, bias=bias, residual=residual)
-    if spec.comm is not None and not spec.sequence_parallel:
+    if spec.comm is not None:
+        if spec.sequence_parallel:
+            return spec.comm.gemm_reduce_scatter(a, w, bias, residual)
         return spec.comm.gemm_all_reduce(a, w, bias, residual)
     part = F.gemm(a, w)
     if spec.sequence_parallel:
@@ -83,6 +85,17 @@ def _row_parallel_out(a, w, bias, residual, spec):
     if bias is not None:
         part = part + bias
     return part.add_(residual)
+
+
+def _dgrad_reduced(dy, w, spec: LayerSpec):
+    """``reduce(dy @ w)`` over the tensor-parallel group: the input gradient of a column-parallel layer
+    (all-reduce, or reduce-scatter along the sequence with sequence parallelism)."""
+    if spec.tp_world > 1 and spec.comm is not None:
+        if spec.sequence_parallel:
+            return spec.comm.gemm_reduce_scatter(dy, w, None, None, b_mn=True)
+        return spec.comm.gemm_all_reduce(dy, w, None, None, b_mn=True)
+    d = F.gemm(dy, w, b_mn=True)
+    return _reduce_scatter_rows(d, spec) if spec.sequence_parallel else _all_reduce(d, spec)
 
 
 def _forward(x2, p, spec: LayerSpec):
@@ -169,12 +182,11 @@ class FusedDecoderLayerFn(torch.autograd.Function):
         g_fc2_w = wgrad(fc2_w, dy_full, act)
         g_fc2_b = bgrad(fc2_b, dy2)
         # ---- FC1 (column parallel)
-        dh2 = F.gemm(d_act, fc1_w, b_mn=True)
+        dh2 = _dgrad_reduced(d_act, fc1_w, spec)
         h2_full = _all_gather_rows(h2, spec) if sp else h2
         g_fc1_w = wgrad(fc1_w, d_act, h2_full)
         g_fc1_b = bgrad(fc1_b, d_act)
         del d_act, h2_full
-        dh2 = _reduce_scatter_rows(dh2, spec) if sp else _all_reduce(dh2, spec)
         # ---- LN2 (+ residual branch gradient dy)
         dx_mid, g_ln2_w, g_ln2_b = ln_bwd(dh2, x_mid, mean2, rstd2, ln2_w, ln2_b, dy2)
         del dh2
@@ -193,12 +205,11 @@ class FusedDecoderLayerFn(torch.autograd.Function):
                          sl(dq3, 2), sl(dq3, 0), sl(dq3, 1))
         del d_attn
         # ---- QKV (column parallel)
-        dh1 = F.gemm(dqkv, qkv_w, b_mn=True)
+        dh1 = _dgrad_reduced(dqkv, qkv_w, spec)
         h1_full = _all_gather_rows(h1, spec) if sp else h1
         g_qkv_w = wgrad(qkv_w, dqkv, h1_full)
         g_qkv_b = bgrad(qkv_b, dqkv)
         del dqkv, h1_full
-        dh1 = _reduce_scatter_rows(dh1, spec) if sp else _all_reduce(dh1, spec)
         # ---- LN1 (+ residual branch gradient dx_mid)
         dx, g_ln1_w, g_ln1_b = ln_bwd(dh1, x2, mean1, rstd1, ln1_w, ln1_b, dx_mid)
         hook = getattr(spec, "post_backward", None)

@@ -124,6 +124,12 @@ class ModelParallelTransformerDecoderLayer(nn.Module):
             bt = (x.shape[0], x.shape[1])
         if self._fused_ok(x, incremental_state, self_attn_padding_mask, self_attn_mask):
             a = self.self_attn
+            if self.tp_comm is None and mpu.get_tensor_model_parallel_world_size() > 1 and x.is_cuda:
+                from metaseq_b200.parallel import symm
+
+                # every fused row-parallel product of the layer has a [B*T, D] result
+                self.tp_comm = symm.get_tp_comm(mpu.get_tensor_model_parallel_group(), x.device, bt[0] * bt[1],
+                                                self.embed_dim, x.dtype)
             spec = LayerSpec(
                 B=bt[0], T=bt[1], heads_local=a.num_heads_partition, head_dim=a.head_dim, scale=a.scaling,
                 eps=self.self_attn_layer_norm.eps, tp_group=mpu.get_tensor_model_parallel_group(),

@@ -22,6 +22,7 @@ Two ways to obtain the mapping:
 from __future__ import annotations
 
 import ctypes
+import logging
 import os
 from dataclasses import dataclass, field
 from typing import Dict, Optional
@@ -30,6 +31,8 @@ import torch
 import torch.distributed as dist
 
 from metaseq_b200.ops import _lib
+
+logger = logging.getLogger(__name__)
 
 SIGNAL_BYTES = 1 << 20  # 256 Ki flag words
 _DTYPE_CODE = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}
@@ -526,6 +529,9 @@ class TPComm:
             int(self.dtype == torch.bfloat16), heap.flags_ptr, self.rs_base, self.epoch, heap.ptr_array, self.bc_base,
             _lib.ptr(self._done), 64, status, stream)
         _lib.check_rc(rc, "msq_comm_reduce_rows")
+        if self.fused_calls == 0 and self.rank == 0:
+            logger.info("TPComm: fused GEMM -> %s active (M=%d N=%d K=%d, %d ranks, %s mapping)",
+                        "all-reduce" if broadcast else "reduce-scatter", M, N, K, self.world, heap.provider)
         self.fused_calls += 1
         if not broadcast:
             return out_local
@@ -577,3 +583,37 @@ class TPComm:
 
     def close(self):
         self.comm.close()
+
+
+# ------------------------------------------------------------------ process-wide selection
+_COMM_BACKEND = "nccl"
+_TP_COMMS: Dict[tuple, TPComm] = {}
+
+
+def set_comm_backend(name: str):
+    """``fused`` routes tensor-parallel row-parallel products through ``TPComm``; ``nccl`` keeps library
+    collectives.  Set once from the command line (``--comm-backend``)."""
+    global _COMM_BACKEND
+    assert name in ("fused", "nccl")
+    _COMM_BACKEND = name
+
+
+def comm_backend() -> str:
+    return _COMM_BACKEND
+
+
+def get_tp_comm(group, device, rows: int, cols: int, dtype) -> Optional[TPComm]:
+    """The shared ``TPComm`` of a tensor-parallel group, created at first use and sized for ``rows x cols``
+    activations (``None`` when the fused backend is off, on CPU, or for a group of one)."""
+    if _COMM_BACKEND != "fused" or group is None or torch.device(device).type != "cuda":
+        return None
+    if dist.get_world_size(group) < 2:
+        return None
+    key = (id(group), str(device), dtype)
+    tp = _TP_COMMS.get(key)
+    if tp is None or tp.max_bytes < rows * cols * torch.empty((), dtype=dtype).element_size():
+        if tp is not None:
+            tp.close()
+        tp = TPComm(group, device, max_rows=rows, max_cols=cols, dtype=dtype)
+        _TP_COMMS[key] = tp
+    return tp
