@@ -1,0 +1,201 @@
+// Single-query attention over a preallocated key/value cache (incremental decoding).
+//
+// The reference concatenates the new key/value onto the cached ones with torch.cat and runs
+// bmm + fp32 softmax + bmm per generated token (metaseq/modules/multihead_attention.py:428-476).  Here the
+// cache is a preallocated [B, Tmax, H*HD] buffer that the caller appends to in place, and one kernel
+// reads every cached key and value exactly once: the operation is bound by that read, so the kernel is
+// organised around 16-byte loads with HD/8 lanes per key, an online softmax per lane group, and a merge
+// of the groups' (max, sum, accumulator) triples at the end.  Long sequences with few (batch, head)
+// pairs are split along the sequence; a second kernel merges the splits.
+#include "sm100_common.cuh"
+
+namespace msq {
+
+constexpr int DEC_THREADS = 128;
+constexpr float DEC_LOG2E = 1.4426950408889634f;
+
+struct Partial {
+  float m, l;
+};
+
+template <int HD, bool BF16>
+__global__ void __launch_bounds__(DEC_THREADS)
+decode_attn_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ kc, const uint16_t* __restrict__ vc,
+                   uint16_t* __restrict__ out, const uint8_t* __restrict__ mask, int S, long long q_bs, long long kv_rs,
+                   long long kv_bs, long long o_bs, long long mask_bs, float scale_log2, int splits,
+                   float* __restrict__ ws) {
+  constexpr int G = HD / 8;    // lanes per key
+  constexpr int KPW = 32 / G;  // keys per warp and iteration
+  const int h = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane / G, part = lane % G;
+  const int chunk = (S + splits - 1) / splits;
+  const int s0 = split * chunk, s1 = min(S, s0 + chunk);
+
+  float qv[8];
+  {
+    const uint4 v = *reinterpret_cast<const uint4*>(q + b * q_bs + h * HD + part * 8);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = unpack2<BF16>(w[j]);
+      qv[2 * j] = f.x * scale_log2;
+      qv[2 * j + 1] = f.y * scale_log2;
+    }
+  }
+  float m = -INFINITY, l = 0.f, acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  const uint16_t* kb = kc + b * kv_bs + h * HD + part * 8;
+  const uint16_t* vb = vc + b * kv_bs + h * HD + part * 8;
+  const uint8_t* mb = mask ? mask + b * mask_bs : nullptr;
+  // warp-uniform trip count: the shuffles below are executed by all 32 lanes in every iteration
+  for (int base = s0 + warp * KPW; base < s1; base += (DEC_THREADS / 32) * KPW) {
+    const int s = base + sub;
+    const bool valid = s < s1;
+    uint4 kv4 = make_uint4(0u, 0u, 0u, 0u), vv4 = make_uint4(0u, 0u, 0u, 0u);
+    if (valid) {
+      kv4 = *reinterpret_cast<const uint4*>(kb + s * kv_rs);
+      vv4 = *reinterpret_cast<const uint4*>(vb + s * kv_rs);
+    }
+    const uint32_t kw[4] = {kv4.x, kv4.y, kv4.z, kv4.w};
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = unpack2<BF16>(kw[j]);
+      dot = fmaf(qv[2 * j], f.x, dot);
+      dot = fmaf(qv[2 * j + 1], f.y, dot);
+    }
+#pragma unroll
+    for (int o = G / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    if (valid && !(mb && mb[s])) {
+      const float m_new = fmaxf(m, dot);
+      const float alpha = exp2f(m - m_new);
+      const float p = exp2f(dot - m_new);
+      l = l * alpha + p;
+      const uint32_t vw[4] = {vv4.x, vv4.y, vv4.z, vv4.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack2<BF16>(vw[j]);
+        acc[2 * j] = fmaf(acc[2 * j], alpha, p * f.x);
+        acc[2 * j + 1] = fmaf(acc[2 * j + 1], alpha, p * f.y);
+      }
+      m = m_new;
+    }
+  }
+  // merge the lane groups of the warp (they hold different keys, same dimensions)
+#pragma unroll
+  for (int o = G; o < 32; o <<= 1) {
+    const float m_o = __shfl_xor_sync(0xffffffffu, m, o);
+    const float l_o = __shfl_xor_sync(0xffffffffu, l, o);
+    const float m_new = fmaxf(m, m_o);
+    const float a = (m == -INFINITY) ? 0.f : exp2f(m - m_new);
+    const float bsc = (m_o == -INFINITY) ? 0.f : exp2f(m_o - m_new);
+    l = l * a + l_o * bsc;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = acc[j] * a + __shfl_xor_sync(0xffffffffu, acc[j], o) * bsc;
+    m = m_new;
+  }
+  // merge the warps through shared memory
+  __shared__ float s_acc[DEC_THREADS / 32][HD];
+  __shared__ float s_m[DEC_THREADS / 32], s_l[DEC_THREADS / 32];
+  if (sub == 0) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s_acc[warp][part * 8 + j] = acc[j];
+    if (part == 0) { s_m[warp] = m; s_l[warp] = l; }
+  }
+  __syncthreads();
+  if (threadIdx.x < HD) {
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DEC_THREADS / 32; ++w) mm = fmaxf(mm, s_m[w]);
+    float ll = 0.f, a = 0.f;
+#pragma unroll
+    for (int w = 0; w < DEC_THREADS / 32; ++w) {
+      const float sc = (s_m[w] == -INFINITY) ? 0.f : exp2f(s_m[w] - mm);
+      ll += s_l[w] * sc;
+      a += s_acc[w][threadIdx.x] * sc;
+    }
+    if (splits == 1) {
+      const float r = ll > 0.f ? a / ll : 0.f;
+      uint16_t* o = out + b * o_bs + h * HD + threadIdx.x;
+      if (BF16) *reinterpret_cast<__nv_bfloat16*>(o) = __float2bfloat16(r);
+      else *reinterpret_cast<__half*>(o) = __float2half(r);
+    } else {
+      float* w = ws + ((static_cast<long long>(b) * gridDim.x + h) * splits + split) * (HD + 2);
+      w[threadIdx.x] = a;
+      if (threadIdx.x == 0) { w[HD] = mm; w[HD + 1] = ll; }
+    }
+  }
+}
+
+template <int HD, bool BF16>
+__global__ void decode_attn_merge_kernel(const float* __restrict__ ws, uint16_t* __restrict__ out, long long o_bs, int splits) {
+  const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+  const float* w = ws + (static_cast<long long>(b) * gridDim.x + h) * splits * (HD + 2);
+  float mm = -INFINITY;
+  for (int s = 0; s < splits; ++s) mm = fmaxf(mm, w[s * (HD + 2) + HD]);
+  float ll = 0.f, a = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float ms = w[s * (HD + 2) + HD];
+    const float sc = (ms == -INFINITY) ? 0.f : exp2f(ms - mm);
+    ll += w[s * (HD + 2) + HD + 1] * sc;
+    a += w[s * (HD + 2) + d] * sc;
+  }
+  const float r = ll > 0.f ? a / ll : 0.f;
+  uint16_t* o = out + b * o_bs + h * HD + d;
+  if (BF16) *reinterpret_cast<__nv_bfloat16*>(o) = __float2bfloat16(r);
+  else *reinterpret_cast<__half*>(o) = __float2half(r);
+}
+
+template <int HD, bool BF16>
+static int launch_decode(const void* q, const void* kc, const void* vc, void* out, const void* mask, int B, int H, int S,
+                         long long q_bs, long long kv_rs, long long kv_bs, long long o_bs, long long mask_bs, float scale,
+                         int splits, float* ws, cudaStream_t stream) {
+  dim3 grid(H, B, splits);
+  decode_attn_kernel<HD, BF16><<<grid, DEC_THREADS, 0, stream>>>(
+      static_cast<const uint16_t*>(q), static_cast<const uint16_t*>(kc), static_cast<const uint16_t*>(vc),
+      static_cast<uint16_t*>(out), static_cast<const uint8_t*>(mask), S, q_bs, kv_rs, kv_bs, o_bs, mask_bs,
+      scale * DEC_LOG2E, splits, ws);
+  if (splits > 1) {
+    dim3 g2(H, B);
+    decode_attn_merge_kernel<HD, BF16><<<g2, HD, 0, stream>>>(ws, static_cast<uint16_t*>(out), o_bs, splits);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+}  // namespace msq
+
+// Number of sequence splits the launch will use for this problem (the caller sizes the workspace:
+// B * H * splits * (HD + 2) floats; none needed when the answer is 1).
+extern "C" int msq_decode_attn_splits(int B, int H, int S) {
+  const long long pairs = static_cast<long long>(B) * H;
+  if (pairs >= 256 || S < 256) return 1;
+  long long want = (296 + pairs - 1) / pairs;
+  const long long cap = S / 128;
+  if (want > cap) want = cap;
+  if (want > 32) want = 32;
+  return want < 1 ? 1 : static_cast<int>(want);
+}
+
+// q: [B, H*HD] rows (batch stride q_bs); k/v cache: [B, >=S, H*HD] with row stride kv_rs and batch stride
+// kv_bs; out: [B, H*HD] (batch stride o_bs); mask: optional uint8 [B, >=S], non-zero = key excluded.
+// Strides in elements.  All 16-bit pointers 16-byte aligned, strides multiples of 8.
+extern "C" int msq_decode_attn(const void* q, const void* kc, const void* vc, void* out, const void* mask, int B, int H,
+                               int HD, int S, long long q_bs, long long kv_rs, long long kv_bs, long long o_bs,
+                               long long mask_bs, float scale, int bf16, float* workspace, int splits,
+                               cudaStream_t stream) {
+  using namespace msq;
+  if (B <= 0 || H <= 0 || S <= 0) return 0;
+  if (HD != 64 && HD != 128) return -4;
+  if ((q_bs & 7) || (kv_rs & 7) || (kv_bs & 7) || (reinterpret_cast<uintptr_t>(q) & 15) ||
+      (reinterpret_cast<uintptr_t>(kc) & 15) || (reinterpret_cast<uintptr_t>(vc) & 15))
+    return -2;
+  if (splits < 1) splits = 1;
+  if (splits > 1 && !workspace) return -3;
+#define MSQ_DEC(HDV, BF) \
+  return launch_decode<HDV, BF>(q, kc, vc, out, mask, B, H, S, q_bs, kv_rs, kv_bs, o_bs, mask_bs, scale, splits, workspace, stream)
+  if (HD == 64) { if (bf16) MSQ_DEC(64, true); else MSQ_DEC(64, false); }
+  if (bf16) MSQ_DEC(128, true); else MSQ_DEC(128, false);
+#undef MSQ_DEC
+}

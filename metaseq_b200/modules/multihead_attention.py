@@ -136,6 +136,13 @@ class ModelParallelMultiheadAttention(nn.Module):
                     incremental_state[self._cache_key] = cache
                 past = cache.length
                 cache.append(k, v)
+                if T == 1 and attn_mask is None and not self.training and ops_f.use_kernels(q) \
+                        and self.head_dim in (64, 128):
+                    # one generated token: a single kernel streams the preallocated cache once
+                    ctx = ops_f.decode_attn(q, cache.k, cache.v, cache.length, self.num_heads_partition, self.scaling,
+                                            key_padding_mask)
+                    out, bias = self.out_proj(ctx)
+                    return out, bias
                 k = cache.k[:, : cache.length]
                 v = cache.v[:, : cache.length]
             ctx = self._attend(q, k, v, B, T, past, key_padding_mask, attn_mask)  # cached or masked path

@@ -131,10 +131,8 @@ def _declare_kernels(lib):
 
 # Entry points added by later source files; declared when present.
 _OPTIONAL = {
-    "msq_decode_attn": [P, P, P, P, P, L, L, L, L, L, L, I, I, I, I, I, F, I, P],
-    "msq_kv_append": [P, P, P, P, P, L, L, L, L, I, I, I, I, I, P],
-    "msq_allreduce_oneshot": [P, P, P, L, I, I, I, P, I, P, P],
-    "msq_gemm_ag": None,
+    "msq_decode_attn": [P, P, P, P, P, I, I, I, I, L, L, L, L, L, F, I, P, I, P],
+    "msq_decode_attn_splits": [I, I, I],
 }
 _OPTIONAL = {k: v for k, v in _OPTIONAL.items() if v is not None}
 

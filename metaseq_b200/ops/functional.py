@@ -421,6 +421,44 @@ def fold_fp32_into(src32: torch.Tensor, dst16: torch.Tensor, accumulate: bool):
     return dst16
 
 
+def decode_attn(q, k_cache, v_cache, length: int, num_heads: int, scale: float, key_padding_mask=None):
+    """Single-query attention for incremental decoding.
+
+    ``q``: ``[B, 1, H*d]`` (or ``[B, H*d]``); ``k_cache`` / ``v_cache``: ``[B, Tmax, H*d]`` of which the first
+    ``length`` positions are valid (the new token's key/value already appended); ``key_padding_mask``:
+    optional ``[B, >=length]`` bool / uint8, non-zero = excluded.  Returns ``[B, 1, H*d]``."""
+    B = q.shape[0]
+    D = q.shape[-1]
+    d = D // num_heads
+    q2 = q.reshape(B, D)
+    if use_kernels(q) and d in (64, 128) and q2.stride(-1) == 1 and k_cache.stride(-1) == 1 and v_cache.stride(-1) == 1 \
+            and k_cache.stride() == v_cache.stride() and q2.data_ptr() % 16 == 0 and k_cache.data_ptr() % 16 == 0 \
+            and v_cache.data_ptr() % 16 == 0 and q2.stride(0) % 8 == 0 and k_cache.stride(1) % 8 == 0:
+        lib = _lib.kernels()
+        out = torch.empty((B, D), dtype=q.dtype, device=q.device)
+        splits = lib.msq_decode_attn_splits(B, num_heads, length)
+        ws = torch.empty((B * num_heads * splits * (d + 2),), dtype=torch.float32, device=q.device) if splits > 1 else None
+        mask_c = None
+        if key_padding_mask is not None:
+            mask_c = key_padding_mask.to(torch.uint8)
+            if mask_c.stride(-1) != 1:
+                mask_c = mask_c.contiguous()
+        rc = lib.msq_decode_attn(_lib.ptr(q2), _lib.ptr(k_cache), _lib.ptr(v_cache), _lib.ptr(out), _lib.ptr(mask_c),
+                                 B, num_heads, d, length, q2.stride(0), k_cache.stride(1), k_cache.stride(0), out.stride(0),
+                                 mask_c.stride(0) if mask_c is not None else 0, float(scale), _bf(q), _lib.ptr(ws), splits,
+                                 _lib.stream_ptr())
+        _lib.check_rc(rc, "msq_decode_attn")
+        return out.view(B, 1, D)
+    k = k_cache[:, :length].reshape(B, length, num_heads, d).transpose(1, 2).float()
+    v = v_cache[:, :length].reshape(B, length, num_heads, d).transpose(1, 2).float()
+    qh = q2.reshape(B, num_heads, 1, d).float() * scale
+    scores = torch.matmul(qh, k.transpose(-1, -2))
+    if key_padding_mask is not None:
+        scores = scores.masked_fill(key_padding_mask[:, None, None, :length].bool(), float("-inf"))
+    probs = torch.softmax(scores, dim=-1)
+    return torch.matmul(probs, v).transpose(1, 2).reshape(B, 1, D).to(q.dtype)
+
+
 # -------------------------------------------------------------- cross entropy
 def cross_entropy_fwd_bwd(logits2d, target, ignore_index: int, grad_scale: float, write_grad: bool):
     """Per-row NLL (fp32, 0 where ``target == ignore_index``) and log-sum-exp.  With

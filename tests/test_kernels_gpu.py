@@ -304,3 +304,27 @@ def test_gemm_two_cta_epilogue(dtype):
     finally:
         F.set_gemm_variant("auto")
     _status_ok()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("B,H,d,S,Tmax", [(2, 4, 64, 37, 64), (16, 32, 64, 1000, 2050), (1, 8, 128, 2048, 2050), (3, 2, 128, 5, 8)])
+@pytest.mark.parametrize("masked", [False, True])
+def test_decode_attention_kv_cache(dtype, B, H, d, S, Tmax, masked):
+    g = torch.Generator(device="cuda").manual_seed(B * 131 + S)
+    D = H * d
+    q = torch.randn(B, 1, D, device="cuda", dtype=dtype, generator=g)
+    kc = torch.randn(B, Tmax, D, device="cuda", dtype=dtype, generator=g)
+    vc = torch.randn(B, Tmax, D, device="cuda", dtype=dtype, generator=g)
+    mask = None
+    if masked:
+        mask = torch.zeros(B, Tmax, dtype=torch.bool, device="cuda")
+        for b in range(B):
+            mask[b, : (b * 3) % max(1, S - 1)] = True  # left padding of different lengths
+    out = F.decode_attn(q, kc, vc, S, H, d ** -0.5, mask)
+    F.set_backend("torch")
+    try:
+        ref = F.decode_attn(q.float(), kc.float(), vc.float(), S, H, d ** -0.5, mask)
+    finally:
+        F.set_backend("auto")
+    tol = 2e-2 if dtype == torch.bfloat16 else 4e-3
+    assert torch.allclose(out.float(), ref.float(), rtol=tol, atol=tol), (out.float() - ref.float()).abs().max()

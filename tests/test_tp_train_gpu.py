@@ -25,7 +25,7 @@ def _run(backend, tmp_path, extra=()):
         "--master-port", str(_free_port()), "-m", "metaseq_b200.cli.train",
         "--task", "dummy_lm", "--dict-size", "1020", "--tokens-per-sample", "256", "--batch-size", "4",
         "--arch", "transformer_lm_megatron", "--decoder-layers", "2", "--decoder-embed-dim", "256",
-        "--decoder-ffn-embed-dim", "1024", "--decoder-attention-heads", "4", "--decoder-learned-pos",
+        "--decoder-ffn-embed-dim", "1024", "--decoder-attention-heads", "4", "--decoder-learned-pos", "--activation-fn", "relu",
         "--share-decoder-input-output-embed", "--no-scale-embedding", "--dropout", "0.0", "--attention-dropout", "0.0",
         "--criterion", "vocab_parallel_cross_entropy", "--optimizer", "adam", "--adam-betas", "(0.9, 0.95)",
         "--lr", "1e-3", "--lr-scheduler", "polynomial_decay", "--warmup-updates", "2", "--total-num-update", "100",
