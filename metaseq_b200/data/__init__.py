@@ -9,3 +9,17 @@ from .streaming_shuffle_dataset import StreamingShuffleDataset  # noqa: F401
 from .concat_dataset import ConcatDataset  # noqa: F401
 from .resampling_dataset import ResamplingDataset  # noqa: F401
 from .synthetic import SyntheticDocumentDataset  # noqa: F401
+from .base_wrapper_dataset import BaseWrapperDataset  # noqa: F401,E402
+from .token_transforms import (  # noqa: F401,E402
+    AppendTokenDataset, IdDataset, LeftPadDataset, ListDataset, NumelDataset, PadDataset, PrependTokenDataset,
+    RandomCropDataset, RightPadDataset, SortDataset, StripTokenDataset, TruncateDataset,
+)
+from .nested_dictionary_dataset import NestedDictionaryDataset  # noqa: F401,E402
+from .token_block_dataset import TokenBlockDataset  # noqa: F401,E402
+from .monolingual_dataset import MonolingualDataset  # noqa: F401,E402
+from .lm_context_window_dataset import LMContextWindowDataset  # noqa: F401,E402
+from .indexed_dataset import (  # noqa: F401,E402
+    IndexedCachedDataset, IndexedDataset, IndexedRawTextDataset, MMapIndexedDataset,
+)
+from .streaming_blocks import StreamingSrcTgtDataset, StreamingTokenBlockDataset  # noqa: F401,E402
+from .cm3_dataset import CausalMaskedDocumentToSequenceDataset  # noqa: F401,E402
