@@ -1,0 +1,292 @@
+"""Small host-side components: utils, metrics / meters, module proxy, service queue and responses, sequence
+generator on a scripted model, launcher, options -> config, NaN detector, file chunker."""
+import json
+import logging
+import os
+
+import pytest
+import torch
+
+from metaseq_b200 import utils
+from metaseq_b200.logging import meters, metrics
+
+
+# ------------------------------------------------------------------------------ utils
+def test_make_positions_skips_padding_and_offsets_by_pad_index():
+    pad = 1
+    toks = torch.tensor([[9, 9, 9, 1, 1], [1, 1, 9, 9, 9], [9, 1, 9, 1, 9]])
+    pos = utils.make_positions(toks, pad)
+    assert pos.tolist() == [[2, 3, 4, 1, 1], [1, 1, 2, 3, 4], [2, 1, 3, 1, 4]]
+
+
+def test_clip_grad_norm_scales_in_place_and_reports_total():
+    params = [torch.nn.Parameter(torch.zeros(5)) for _ in range(3)]
+    assert float(utils.clip_grad_norm_(params, 1.0)) == 0.0  # no gradients
+    for p in params:
+        p.grad = torch.full((5,), 2.0)
+    total = utils.clip_grad_norm_(params, 1.0)
+    assert float(total) == pytest.approx((15 * 4.0) ** 0.5)
+    assert float(utils.clip_grad_norm_(params, 1.0)) == pytest.approx(1.0, rel=1e-5)
+    for p in params:
+        p.grad = torch.full((5,), 2.0)
+    assert float(utils.clip_grad_norm_(params, 0.0)) == pytest.approx((15 * 4.0) ** 0.5)  # 0 = measure only
+    assert params[0].grad[0].item() == 2.0
+    params[1].grad[0] = 7.0
+    assert float(utils.clip_grad_norm_(params, 0.0, norm_type="inf")) == 7.0
+
+
+# --------------------------------------------------------------------- metrics / meters
+def test_metrics_aggregators_nest_and_average():
+    metrics.reset()
+    with metrics.aggregate("train") as outer:
+        metrics.log_scalar("loss", 2.0, weight=1)
+        with metrics.aggregate("inner") as inner:
+            metrics.log_scalar("loss", 4.0, weight=3)
+        metrics.log_scalar_sum("n", 5)
+        metrics.log_derived("double", lambda m: 2 * m["loss"].avg)
+    assert inner.get_smoothed_value("loss") == 4.0
+    assert outer.get_smoothed_value("loss") == pytest.approx((2.0 + 12.0) / 4)
+    assert outer.get_smoothed_value("n") == 5
+    assert outer.get_smoothed_value("double") == pytest.approx(7.0)
+    state = metrics.state_dict()
+    metrics.reset()
+    metrics.load_state_dict(state)
+    assert metrics.get_smoothed_value("train", "loss") == pytest.approx(3.5)
+
+
+def test_meters_roundtrip_and_priority_order():
+    d = meters.MetersDict()
+    d.add_meter("late", meters.AverageMeter(round=2), priority=50)
+    d.add_meter("early", meters.SumMeter(), priority=10)
+    d.add_meter("derived", meters.MetersDict._DerivedMeter(lambda m: m["early"].sum + 1), priority=20)
+    assert list(d.keys()) == ["early", "derived", "late"]
+    d["late"].update(1.23456, n=2)
+    d["early"].update(3)
+    assert d.get_smoothed_values() == {"early": 3, "derived": 4, "late": 1.23}
+    d2 = meters.MetersDict()
+    d2.load_state_dict(d.state_dict())
+    assert d2["late"].avg == pytest.approx(1.23456) and "derived" not in d2
+    sw = meters.StopwatchMeter()
+    sw.start()
+    sw.stop(n=2)
+    assert sw.n == 2 and sw.sum >= 0
+    tm = meters.TimeMeter()
+    tm.update(10)
+    restored = meters.TimeMeter()
+    restored.load_state_dict(tm.state_dict())
+    assert restored.n == 10
+
+
+def test_module_proxy_wrapper_forwards_attributes_and_state():
+    from metaseq_b200.parallel.module_proxy_wrapper import ModuleProxyWrapper
+
+    class Inner(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.linear = torch.nn.Linear(2, 2)
+            self.custom = "x"
+
+        def forward(self, x):
+            return self.linear(x)
+
+        def get_custom(self):
+            return self.custom
+
+    class FakeDDP(torch.nn.Module):
+        def __init__(self, module):
+            super().__init__()
+            self.module = module
+            self.ddp_only = 3
+
+        def forward(self, x):
+            return self.module(x)
+
+    inner = Inner()
+    wrapped = ModuleProxyWrapper(FakeDDP(inner))
+    assert wrapped.get_custom() == "x" and wrapped.ddp_only == 3 and wrapped.linear is inner.linear
+    assert set(wrapped.state_dict().keys()) == {"linear.weight", "linear.bias"}
+    with pytest.raises(AttributeError):
+        wrapped.nope
+    with pytest.raises(AssertionError):
+        ModuleProxyWrapper(inner)
+    x = torch.randn(3, 2)
+    assert torch.equal(wrapped(x), inner(x))
+
+
+# ------------------------------------------------------------------------------ service
+def test_service_queue_batches_compatible_requests_cheapest_first():
+    from metaseq_b200.service.queue import PriorityQueueRing
+    from metaseq_b200.service.workers import WorkItem
+
+    ring = PriorityQueueRing(num_shards=2)
+    for uid, (cost, temp) in enumerate([(30, 1.0), (10, 1.0), (20, 0.7), (5, 1.0)]):
+        ring.put(WorkItem(cost=cost, uid=uid, return_queue=None, data={"input": [1], "temperature": temp, "n": 1}))
+    assert not ring.empty()
+    seen = []
+    while not ring.empty():
+        shard = ring.largest_shard()
+        q = shard.get_deepest_queue() if hasattr(shard, "get_deepest_queue") else shard
+        item = shard.get()
+        seen.append((item.cost, item.data["temperature"]))
+    assert sorted(seen) == [(5, 1.0), (10, 1.0), (20, 0.7), (30, 1.0)]
+    same_key = [c for c, t in seen if t == 1.0]
+    assert same_key == sorted(same_key)  # within one sampling configuration the cheapest request comes first
+
+
+def test_oai_response_envelope():
+    from metaseq_b200.service.responses import OAIResponse
+
+    r = OAIResponse([{"text": "hi", "tokens": ["h", "i"], "token_scores": [-0.1, -0.2], "text_offset": [0, 1],
+                      "top_logprobs": None}]).__dict__()
+    assert r["object"] == "text_completion" and r["choices"][0]["text"] == "hi"
+    assert r["choices"][0]["logprobs"]["token_logprobs"] == [-0.1, -0.2]
+    json.dumps(r)
+
+
+def test_service_newline_normalisation():
+    from metaseq_b200.service.utils import normalize_newlines
+
+    assert normalize_newlines("a\r\nb\rc\n") == "a\nb\nc\n"
+
+
+# ------------------------------------------------------------------- sequence generator
+class ScriptedDecoder(torch.nn.Module):
+    """Next-token distribution depends only on the last token: t -> t + 1 (mod V), EOS after token 7."""
+
+    def __init__(self, vocab, eos):
+        super().__init__()
+        self.vocab, self.eos = vocab, eos
+        self.calls = []
+
+    def forward(self, tokens, incremental_state=None, **kw):
+        self.calls.append(tokens.shape[1])
+        nxt = torch.where(tokens == 7, torch.full_like(tokens, self.eos), (tokens + 1) % self.vocab)
+        logits = torch.full((*tokens.shape, self.vocab), -10.0)
+        logits.scatter_(-1, nxt.unsqueeze(-1), 10.0)
+        return logits, None
+
+
+class ScriptedModel(torch.nn.Module):
+    def __init__(self, vocab, eos):
+        super().__init__()
+        self.decoder = ScriptedDecoder(vocab, eos)
+
+    def forward(self, tokens, **kw):
+        return self.decoder(tokens, **kw)
+
+    def max_decoder_positions(self):
+        return 32
+
+
+def test_sequence_generator_greedy_follows_the_model_and_stops_at_eos():
+    from metaseq_b200.data import Dictionary
+    from metaseq_b200.sequence_generator import SequenceGenerator
+
+    d = Dictionary()
+    for i in range(12):
+        d.add_symbol(str(i))
+    gen = SequenceGenerator(ScriptedModel(len(d), d.eos()), d, beam_size=1, max_len_b=20, temperature=1.0, topp=-1.0,
+                            sampling=False) if "sampling" in SequenceGenerator.__init__.__code__.co_varnames else \
+        SequenceGenerator(ScriptedModel(len(d), d.eos()), d, beam_size=1, max_len_b=20, topp=-1.0)
+    src = torch.tensor([[d.eos(), 4, 5], [d.eos(), 6, d.pad()]])
+    out = gen._generate({"net_input": {"src_tokens": src}})
+    toks = out["tokens"][:, 0]
+    assert toks[0, :6].tolist() == [d.eos(), 4, 5, 6, 7, d.eos()]
+    # the second prompt is one token shorter: generation continues from its own last real token
+    assert toks[1, :2].tolist() == [d.eos(), 6] and 7 in toks[1].tolist()
+    assert out["scores"].shape == out["tokens"].shape
+
+
+# ------------------------------------------------------------------------------ launcher
+def test_launcher_grid_expands_to_one_command_per_combination(tmp_path, capsys):
+    from metaseq_b200.launcher import slurm, sweep
+
+    def get_grid(args):
+        return [sweep.hyperparam("--lr", [0.1, 0.2], save_dir_key=lambda v: f"lr{v}"),
+                sweep.hyperparam("--fp16", binary_flag=True, values=True),
+                sweep.hyperparam("--seed", 3)]
+
+    args = sweep.get_args(input_args=["-p", "exp", "-g", "2", "-n", "1", "--dry-run", "--local", "--checkpoints-dir",
+                                      str(tmp_path)])
+    dirs = slurm.main(get_grid, lambda a, c: None, args)
+    out = capsys.readouterr().out
+    assert len(dirs) == 2 and any(d.endswith("exp.lr0.1.ngpu2") for d in dirs)
+    assert out.count("train command:") == 2 and "--lr 0.2 --fp16 --seed 3" in out
+    with pytest.raises(ValueError):
+        sweep.hyperparam("--x", [1, 2])  # several values need a save_dir_key
+
+
+def test_launcher_skips_finished_runs_and_builds_sbatch(tmp_path):
+    from metaseq_b200.launcher import slurm, sweep
+
+    args = sweep.get_args(input_args=["-p", "exp", "-g", "8", "-n", "2", "--checkpoints-dir", str(tmp_path),
+                                      "--partition", "learn", "--time", "60"])
+    done = tmp_path / "run"
+    done.mkdir()
+    (done / "train.log").write_text("step 1\ndone training in 3 seconds\n")
+    assert slurm.is_finished(str(done)) and not slurm.is_job_valid(args, str(done), lambda m: False)
+    cmd, text = slurm.gen_sbatch_command_and_str(args, "job", "log", "err", "", "srun python x")
+    assert "--signal" in cmd and "B:USR1@180" in cmd and "--partition" in cmd
+    assert "scontrol requeue $SLURM_JOB_ID" in cmd[-1]
+    env = {}
+    slurm.set_env(args, env, lambda m: False)
+    assert env["NCCL_ASYNC_ERROR_HANDLING"] == "1"
+
+
+def test_tombstone_triggers_action_and_is_removed(tmp_path):
+    from metaseq_b200.launcher.tombyard import tombstones, tombstones_procedure
+
+    fired = []
+    actions = {k: (lambda k=k: fired.append(k)) for k in ("scancel", "requeuehold", "release")}
+    assert tombstones_procedure("42", str(tmp_path), period=0.0, actions=actions, max_polls=2) is None and not fired
+    open(tombstones("42", str(tmp_path))["scancel"], "w").close()
+    assert tombstones_procedure("42", str(tmp_path), period=0.0, actions=actions, max_polls=2) == "scancel"
+    assert fired == ["scancel"] and not os.path.exists(tombstones("42", str(tmp_path))["scancel"])
+
+
+def test_opt_baselines_grid_matches_model_table():
+    from metaseq_b200.launcher import opt_baselines, sweep
+    from metaseq_b200.launcher.opt_job_constants import MODEL_SIZES
+
+    args = sweep.get_args(opt_baselines.add_extra_options_func,
+                          ["-p", "t", "-g", "8", "--model-size", "1.3b", "--benchmark", "--local", "--dry-run"])
+    grid = {h.name: h for h in opt_baselines.get_grid(args)}
+    size = MODEL_SIZES["1.3b"]
+    assert grid["--decoder-layers"].values == [size.n_layers] and grid["--decoder-embed-dim"].values == [size.emb_size]
+    assert grid["--task"].values == ["dummy_lm"] and grid["--max-update"].values == [50]
+    assert grid["--model-parallel-size"].values == [size.model_parallel]
+    assert grid["--lr"].values == [size.lr] and "--no-reshard-after-forward" in grid
+
+
+# ------------------------------------------------------------------------ options / config
+def test_training_parser_builds_nested_config_with_arch_defaults():
+    from metaseq_b200 import options
+    from metaseq_b200.dataclass.utils import convert_namespace_to_config
+
+    parser = options.get_training_parser()
+    ns = options.parse_args_and_arch(parser, input_args=[
+        "--task", "dummy_lm", "--arch", "opt_125m", "--optimizer", "adam", "--lr", "3e-4", "--lr-scheduler",
+        "polynomial_decay", "--total-num-update", "10", "--criterion", "cross_entropy", "--batch-size", "2",
+        "--tokens-per-sample", "64", "--adam-betas", "(0.9, 0.95)", "--memory-efficient-fp16", "--model-parallel-size", "1"])
+    cfg = convert_namespace_to_config(ns)
+    assert cfg.common.memory_efficient_fp16 and cfg.common.fp16
+    assert cfg.optimizer._name == "adam" and cfg.optimizer.adam_betas == "(0.9, 0.95)"
+    assert cfg.lr_scheduler._name == "polynomial_decay" and cfg.task._name == "dummy_lm"
+    assert cfg.model.decoder_layers == 12 and cfg.model.decoder_embed_dim == 768  # from the architecture function
+    assert cfg.dataset.batch_size == 2 and cfg.optimization.lr == [3e-4]
+
+
+# ---------------------------------------------------------------------------- nan detector
+def test_nan_detector_names_the_first_bad_module(caplog):
+    from metaseq_b200.nan_detector import NanDetector
+
+    class Bad(torch.nn.Module):
+        def forward(self, x):
+            return x / 0.0 * 0.0
+
+    model = torch.nn.Sequential(torch.nn.Linear(4, 4), Bad(), torch.nn.Linear(4, 4))
+    with caplog.at_level(logging.WARNING, logger="metaseq_b200.nan_detector"):
+        with NanDetector(model, backward=False) as det:
+            model(torch.ones(2, 4))
+    assert det.has_printed_f
+    assert any("NaN detected in output of 1" in r.getMessage() for r in caplog.records)
