@@ -23,7 +23,10 @@ class _VocabParallelCrossEntropy(torch.autograd.Function):
         group = mpu.get_tensor_model_parallel_group()
         world = mpu.get_tensor_model_parallel_world_size()
         rank = mpu.get_tensor_model_parallel_rank()
-        logits = vocab_parallel_logits
+        # The buffer is overwritten in place (it becomes the softmax).  Working on the ``.data`` alias keeps
+        # autograd's version counter of the incoming tensor untouched, which matters when that tensor is
+        # itself the (view) output of another custom function.
+        logits = vocab_parallel_logits.data
         part = logits.shape[-1]
         start, end = rank * part, (rank + 1) * part
 

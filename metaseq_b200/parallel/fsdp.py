@@ -304,7 +304,9 @@ class FullyShardedDataParallel(nn.Module):
                 self._full_param.untyped_storage().resize_(nbytes)
                 self._needs_gather = True
             if self._needs_gather:
-                full = self._full_param
+                # ``.data`` aliases the storage under a separate version counter: re-filling the buffer between
+                # forward and backward must not invalidate the views autograd saved
+                full = self._full_param.data
                 local = src if src.dtype == cdt else src.to(cdt)
                 if self.world_size == 1:
                     full[: local.numel()].copy_(local)
