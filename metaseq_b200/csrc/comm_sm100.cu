@@ -379,6 +379,130 @@ comm_allreduce_oneshot_kernel(PeerPtrs slots, long long slots_off_bytes, long lo
   }
 }
 
+// Multi-CTA form of the one-shot all-reduce: CTA c owns slice c of the tensor and shakes hands only with the
+// CTAs of the same index on the other ranks (flag words flag_base + c * world + src), so no grid-wide or
+// cross-CTA synchronisation is needed and large tensors use many SMs.
+template <int MODE>
+__global__ void __launch_bounds__(512)
+comm_allreduce_sliced_kernel(PeerPtrs slots, long long slots_off_bytes, long long slot_stride, const void* in, void* out,
+                             long long bytes, long long slice_bytes, int rank, int world, PeerPtrs sig, long long flag_base,
+                             uint32_t epoch, int* status) {
+  if (status && *reinterpret_cast<volatile int*>(status) != 0) return;
+  const long long parity_off = (epoch & 1u) ? slot_stride * world : 0;
+  const long long b0 = static_cast<long long>(blockIdx.x) * slice_bytes;
+  const long long nb = (bytes - b0 < slice_bytes) ? (bytes - b0) : slice_bytes;
+  if (nb <= 0) return;
+  const long long v0 = b0 >> 4, nvec = nb >> 4;
+  const uint4* src = static_cast<const uint4*>(in) + v0;
+  for (long long i = threadIdx.x; i < nvec; i += blockDim.x) {
+    const uint4 v = src[i];
+    for (int pp = 0; pp < world; ++pp) {
+      const int peer = (rank + pp) % world;
+      uint4* d = reinterpret_cast<uint4*>(static_cast<uint8_t*>(slots.p[peer]) + slots_off_bytes + parity_off + rank * slot_stride) + v0;
+      d[i] = v;
+    }
+  }
+  __syncthreads();
+  __shared__ bool ok_s;
+  if (threadIdx.x == 0) ok_s = true;
+  __syncthreads();
+  const long long my_flags = flag_base + static_cast<long long>(blockIdx.x) * world;
+  if (threadIdx.x < world) {
+    __threadfence_system();
+    st_release_sys(static_cast<uint32_t*>(sig.p[threadIdx.x]) + my_flags + rank, epoch);
+    if (!wait_flag(static_cast<const uint32_t*>(sig.p[rank]) + my_flags + threadIdx.x, epoch, status)) ok_s = false;
+  }
+  __syncthreads();
+  if (!ok_s) return;
+  const uint8_t* mine = static_cast<const uint8_t*>(slots.p[rank]) + slots_off_bytes + parity_off;
+  for (long long i = threadIdx.x; i < nvec; i += blockDim.x) {
+    if (MODE == 2) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int s = 0; s < world; ++s) {
+        const float4 v = reinterpret_cast<const float4*>(mine + s * slot_stride)[v0 + i];
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+      static_cast<float4*>(out)[v0 + i] = acc;
+    } else {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int s = 0; s < world; ++s) {
+        const uint4 v = reinterpret_cast<const uint4*>(mine + s * slot_stride)[v0 + i];
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack2<MODE == 1>(w[j]);
+          acc[2 * j] += f.x;
+          acc[2 * j + 1] += f.y;
+        }
+      }
+      uint4 o;
+      o.x = pack2<MODE == 1>(acc[0], acc[1]);
+      o.y = pack2<MODE == 1>(acc[2], acc[3]);
+      o.z = pack2<MODE == 1>(acc[4], acc[5]);
+      o.w = pack2<MODE == 1>(acc[6], acc[7]);
+      static_cast<uint4*>(out)[v0 + i] = o;
+    }
+  }
+}
+
+// One-launch in-switch all-reduce.  CTA c stages slice c of the input in this rank's symmetric buffer, shakes
+// hands with the same-index CTAs of the other ranks, reduces its 1/world share of the slice inside NVSwitch
+// (multimem.ld_reduce on the multicast address) and broadcasts it (multimem.st), shakes hands again and copies
+// the finished slice to the output.
+template <int MODE>
+__global__ void __launch_bounds__(512)
+comm_allreduce_multimem_fused_kernel(void* mc, void* stage_local, const void* in, void* out, long long bytes,
+                                     long long slice_bytes, int rank, int world, PeerPtrs sig, long long flag_base,
+                                     uint32_t epoch, int* status) {
+  if (status && *reinterpret_cast<volatile int*>(status) != 0) return;
+  const long long b0 = static_cast<long long>(blockIdx.x) * slice_bytes;
+  const long long nb = (bytes - b0 < slice_bytes) ? (bytes - b0) : slice_bytes;
+  if (nb <= 0) return;
+  const long long v0 = b0 >> 4, nvec = nb >> 4;
+  const uint4* src = static_cast<const uint4*>(in) + v0;
+  uint4* stg = static_cast<uint4*>(stage_local) + v0;
+  for (long long i = threadIdx.x; i < nvec; i += blockDim.x) stg[i] = src[i];
+  __shared__ bool ok_s;
+  if (threadIdx.x == 0) ok_s = true;
+  __syncthreads();
+  const long long f1 = flag_base + static_cast<long long>(blockIdx.x) * 2 * world;
+  const long long f2 = f1 + world;
+  if (threadIdx.x < world) {
+    __threadfence_system();
+    st_release_sys(static_cast<uint32_t*>(sig.p[threadIdx.x]) + f1 + rank, epoch);
+    if (!wait_flag(static_cast<const uint32_t*>(sig.p[rank]) + f1 + threadIdx.x, epoch, status)) ok_s = false;
+  }
+  __syncthreads();
+  if (!ok_s) return;
+  const long long per = (nvec + world - 1) / world;
+  const long long lo = rank * per, hi = (lo + per < nvec) ? lo + per : nvec;
+  for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    uint8_t* a = static_cast<uint8_t*>(mc) + ((v0 + i) << 4);
+    uint32_t x, y, z, w;
+    if (MODE == 2)
+      asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                   : "=r"(x), "=r"(y), "=r"(z), "=r"(w) : "l"(a) : "memory");
+    else if (MODE == 1)
+      asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                   : "=r"(x), "=r"(y), "=r"(z), "=r"(w) : "l"(a) : "memory");
+    else
+      asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+                   : "=r"(x), "=r"(y), "=r"(z), "=r"(w) : "l"(a) : "memory");
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                 ::"l"(a), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x < world) {
+    __threadfence_system();
+    st_release_sys(static_cast<uint32_t*>(sig.p[threadIdx.x]) + f2 + rank, epoch);
+    if (!wait_flag(static_cast<const uint32_t*>(sig.p[rank]) + f2 + threadIdx.x, epoch, status)) ok_s = false;
+  }
+  __syncthreads();
+  if (!ok_s) return;
+  uint4* dst = static_cast<uint4*>(out) + v0;
+  for (long long i = threadIdx.x; i < nvec; i += blockDim.x) dst[i] = stg[i];
+}
+
 // In-switch variant: `mc` is the multicast address of the input buffers (same offset on every rank).
 // After a barrier each rank asks the switch for the sum of its share of the elements
 // (multimem.ld_reduce) and broadcasts the result to all ranks (multimem.st), i.e. a two-shot
@@ -617,6 +741,44 @@ extern "C" int msq_comm_allreduce_oneshot(void* const* slot_ptrs, long long slot
   if (dtype == 0) msq::comm_allreduce_oneshot_kernel<0><<<1, 512, 0, stream>>>(sl, slots_off_bytes, slot_stride, in, out, bytes, rank, world, sg, flag_base, epoch, status);
   else if (dtype == 1) msq::comm_allreduce_oneshot_kernel<1><<<1, 512, 0, stream>>>(sl, slots_off_bytes, slot_stride, in, out, bytes, rank, world, sg, flag_base, epoch, status);
   else msq::comm_allreduce_oneshot_kernel<2><<<1, 512, 0, stream>>>(sl, slots_off_bytes, slot_stride, in, out, bytes, rank, world, sg, flag_base, epoch, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// Multi-CTA one-shot all-reduce (see comm_allreduce_sliced_kernel).  Needs ceil(bytes / slice_bytes) * world flag
+// words at flag_base; slots as for msq_comm_allreduce_oneshot.
+extern "C" int msq_comm_allreduce_sliced(void* const* slot_ptrs, long long slots_off_bytes, long long slot_stride,
+                                         const void* in, void* out, long long bytes, long long slice_bytes, int dtype,
+                                         int rank, int world, void* const* sig_ptrs, long long flag_base, unsigned epoch,
+                                         int* status, cudaStream_t stream) {
+  if (world > msq::MAX_PEERS) return -2;
+  if ((bytes & 15) || (slice_bytes & 15) || slice_bytes <= 0 || bytes > slot_stride || (reinterpret_cast<uintptr_t>(in) & 15) ||
+      (reinterpret_cast<uintptr_t>(out) & 15))
+    return -2;
+  if (bytes <= 0) return 0;
+  const int grid = static_cast<int>((bytes + slice_bytes - 1) / slice_bytes);
+  PeerPtrs sl = make_ptrs(slot_ptrs, world), sg = make_ptrs(sig_ptrs, world);
+  if (dtype == 0) msq::comm_allreduce_sliced_kernel<0><<<grid, 512, 0, stream>>>(sl, slots_off_bytes, slot_stride, in, out, bytes, slice_bytes, rank, world, sg, flag_base, epoch, status);
+  else if (dtype == 1) msq::comm_allreduce_sliced_kernel<1><<<grid, 512, 0, stream>>>(sl, slots_off_bytes, slot_stride, in, out, bytes, slice_bytes, rank, world, sg, flag_base, epoch, status);
+  else msq::comm_allreduce_sliced_kernel<2><<<grid, 512, 0, stream>>>(sl, slots_off_bytes, slot_stride, in, out, bytes, slice_bytes, rank, world, sg, flag_base, epoch, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// One-launch in-switch all-reduce: `mc` is the multicast address and `stage_local` this rank's address of the
+// same symmetric staging buffer.  Needs 2 * world flag words per slice at flag_base.
+extern "C" int msq_comm_allreduce_multimem_fused(void* mc, void* stage_local, const void* in, void* out, long long bytes,
+                                                 long long slice_bytes, int dtype, int rank, int world,
+                                                 void* const* sig_ptrs, long long flag_base, unsigned epoch, int* status,
+                                                 cudaStream_t stream) {
+  if (world > msq::MAX_PEERS) return -2;
+  if ((bytes & 15) || (slice_bytes & 15) || slice_bytes <= 0 || (reinterpret_cast<uintptr_t>(mc) & 15) ||
+      (reinterpret_cast<uintptr_t>(in) & 15) || (reinterpret_cast<uintptr_t>(out) & 15))
+    return -2;
+  if (bytes <= 0) return 0;
+  const int grid = static_cast<int>((bytes + slice_bytes - 1) / slice_bytes);
+  PeerPtrs sg = make_ptrs(sig_ptrs, world);
+  if (dtype == 0) msq::comm_allreduce_multimem_fused_kernel<0><<<grid, 512, 0, stream>>>(mc, stage_local, in, out, bytes, slice_bytes, rank, world, sg, flag_base, epoch, status);
+  else if (dtype == 1) msq::comm_allreduce_multimem_fused_kernel<1><<<grid, 512, 0, stream>>>(mc, stage_local, in, out, bytes, slice_bytes, rank, world, sg, flag_base, epoch, status);
+  else msq::comm_allreduce_multimem_fused_kernel<2><<<grid, 512, 0, stream>>>(mc, stage_local, in, out, bytes, slice_bytes, rank, world, sg, flag_base, epoch, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

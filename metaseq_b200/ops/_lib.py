@@ -115,6 +115,8 @@ def _declare_kernels(lib):
     _sig(lib, "msq_comm_reduce_scatter_ce", [P, L, P, L, I, I, P, L, U, P])
     _sig(lib, "msq_comm_reduce_slots", [P, L, I, F, P, I, I, P, P, P, L, U, I, P, P])
     _sig(lib, "msq_comm_allreduce_oneshot", [P, L, L, P, P, L, I, I, I, P, L, U, P, P])
+    _sig(lib, "msq_comm_allreduce_sliced", [P, L, L, P, P, L, L, I, I, I, P, L, U, P, P])
+    _sig(lib, "msq_comm_allreduce_multimem_fused", [P, P, P, P, L, L, I, I, I, P, L, U, P, P])
     _sig(lib, "msq_comm_allreduce_multimem", [P, L, I, I, I, P, L, U, I, P, P])
     _sig(lib, "msq_cross_entropy", [P, L, P, P, P, I, I, L, F, I, I, P])
     _sig(lib, "msq_colsum", [P, L, I, I, P, I, P])

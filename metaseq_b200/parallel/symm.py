@@ -216,11 +216,13 @@ class PeerComm:
         self._range_cache = {}
         self._barrier_base = self.heap.alloc_flags(self.world)
         self._barrier_epoch = 0
-        self._ar_base = self.heap.alloc_flags(self.world)
-        self._ar_epoch = 0
         self._small_bytes = int(small_bytes)
+        self._slice_bytes = 32 << 10  # one CTA per 32 KiB of an all-reduced tensor
+        n_slices = (self._small_bytes + self._slice_bytes - 1) // self._slice_bytes
+        self._ar_base = self.heap.alloc_flags(self.world * n_slices)
+        self._ar_epoch = 0
         self._ar_slots = self.heap.alloc(2 * self.world * self._small_bytes)
-        self._mc_base = self.heap.alloc_flags(2 * self.world)
+        self._mc_base = self.heap.alloc_flags(2 * self.world * n_slices)
         self._mc_epoch = 0
         self._mc_off = self.heap.alloc(self._small_bytes)
         self._done = torch.zeros(4, dtype=torch.int32, device=self.device)
@@ -434,24 +436,21 @@ class PeerComm:
         code = _DTYPE_CODE[t.dtype]
         if use_multicast is None:
             use_multicast = self.heap.multicast_ptr != 0
+        slice_bytes = self._slice_bytes
         if use_multicast and self.heap.multicast_ptr:
-            stage = self.heap.view(self._mc_off, t.numel(), t.dtype)
-            stage.copy_(t.view(-1))
+            # one launch: stage, handshake, in-switch reduce + broadcast of this rank's share, handshake, copy out
             self._mc_epoch += 1
-            rc = lib.msq_comm_allreduce_multimem(
-                ctypes.c_void_p(self.heap.multicast_ptr + self._mc_off), nbytes, code, self.rank, self.world,
-                self.heap.ptr_array, self._mc_base + (self._mc_epoch & 1) * self.world, self._mc_epoch, 8,
-                self._status(), _lib.stream_ptr())
-            self._check(rc, "msq_comm_allreduce_multimem")
-            self.barrier()  # every rank's share has been broadcast
-            t.view(-1).copy_(stage)
-            self.barrier()  # nobody restages before everyone has copied out
+            rc = lib.msq_comm_allreduce_multimem_fused(
+                ctypes.c_void_p(self.heap.multicast_ptr + self._mc_off), ctypes.c_void_p(self.heap.ptrs[self.rank] + self._mc_off),
+                _lib.ptr(t), _lib.ptr(t), nbytes, slice_bytes, code, self.rank, self.world, self.heap.ptr_array,
+                self._mc_base, self._mc_epoch, self._status(), _lib.stream_ptr())
+            self._check(rc, "msq_comm_allreduce_multimem_fused")
             return t
         self._ar_epoch += 1
-        rc = lib.msq_comm_allreduce_oneshot(
-            self.heap.ptr_array, self._ar_slots, self._small_bytes, _lib.ptr(t), _lib.ptr(t), nbytes, code, self.rank, self.world,
-            self.heap.ptr_array, self._ar_base, self._ar_epoch, self._status(), _lib.stream_ptr())
-        self._check(rc, "msq_comm_allreduce_oneshot")
+        rc = lib.msq_comm_allreduce_sliced(
+            self.heap.ptr_array, self._ar_slots, self._small_bytes, _lib.ptr(t), _lib.ptr(t), nbytes, slice_bytes, code,
+            self.rank, self.world, self.heap.ptr_array, self._ar_base, self._ar_epoch, self._status(), _lib.stream_ptr())
+        self._check(rc, "msq_comm_allreduce_sliced")
         return t
 
     def close(self):
