@@ -53,7 +53,7 @@ def main(argv=None):
     chunk = min(2 << 20, shard_bytes)
     chunks = (shard_bytes + chunk - 1) // chunk
     flags = torch.full((W * chunks,), 7, dtype=torch.int32, device=dev)
-    desc = _lib.GemmReady(flags.data_ptr(), 0, shard_bytes, chunk, chunks, -1, 7)
+    desc = _lib.GemmReady(flags.data_ptr(), 0, shard_bytes, chunk, chunks, -1, 7, 0)
 
     def ready():
         rc = lib.msq_gemm2_ready(_lib.ptr(a), _lib.ptr(w), _lib.ptr(out), M, N, K, K, K, N, 0, 0, 0, None, None, 0, None, 0,

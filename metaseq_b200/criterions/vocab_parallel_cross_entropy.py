@@ -39,7 +39,12 @@ class VocabParallelCrossEntropyCriterion(BaseCriterion):
         if mpu.get_tensor_model_parallel_world_size() == 1:
             loss = nll_loss_sum(logits.reshape(-1, logits.size(-1)), target.reshape(-1), self.padding_idx)
         else:
-            per_tok = vocab_parallel_cross_entropy(logits.float(), target)
+            from metaseq_b200.parallel.cross_entropy import fused_vocab_parallel_cross_entropy_ok
+
+            if fused_vocab_parallel_cross_entropy_ok(logits):
+                per_tok = vocab_parallel_cross_entropy(logits, target, self.padding_idx)  # 16-bit logits, in place
+            else:
+                per_tok = vocab_parallel_cross_entropy(logits.float(), target)
             if has_pad:
                 per_tok = per_tok * (target != self.padding_idx)
             loss = per_tok.sum()

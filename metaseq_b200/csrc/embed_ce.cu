@@ -213,6 +213,104 @@ cross_entropy_kernel(uint16_t* __restrict__ logits, long long ld, const long lon
   }
 }
 
+// ------------------------------------------------- vocabulary-parallel cross entropy
+// Each tensor-parallel rank holds logits[rows, V_local] for vocabulary ids [vocab_start, vocab_start + V_local).
+// Phase 1 writes, per row, (local max, sum of exp(x - local max), target logit or 0) into this rank's block of a
+// [world, rows, 3] fp32 table whose other blocks stay zero, so one SUM all-reduce of the table is an all-gather.
+// Phase 2 combines the `world` triples of a row into the global log-sum-exp, writes the loss and overwrites the
+// local logits with (softmax - onehot) * grad_scale.  Reference: three separate all-reduces around unfused ops
+// (metaseq/modules/megatron/mpu/cross_entropy.py:19-109).
+template <bool BF16>
+__global__ void __launch_bounds__(256)
+vp_ce_partial_kernel(const uint16_t* __restrict__ logits, long long ld, const long long* __restrict__ target,
+                     float* __restrict__ stats_block, int rows, int V, long long vocab_start) {
+  __shared__ float red[32];
+  const int nvec = V >> 3;
+  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    const uint16_t* grow = logits + static_cast<long long>(r) * ld;
+    float mx = -INFINITY;
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+      const uint4 a = *reinterpret_cast<const uint4*>(grow + v * 8);
+      const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 t = unpack2<BF16>(w[j]);
+        mx = fmaxf(mx, fmaxf(t.x, t.y));
+      }
+    }
+    mx = block_max(mx, red);
+    float se = 0.f;
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {  // second read comes from L2 / L1
+      const uint4 a = *reinterpret_cast<const uint4*>(grow + v * 8);
+      const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 t = unpack2<BF16>(w[j]);
+        se += __expf(t.x - mx) + __expf(t.y - mx);
+      }
+    }
+    se = block_sum(se, red);
+    if (threadIdx.x == 0) {
+      const long long lt = target[r] - vocab_start;
+      float tl = 0.f;
+      if (lt >= 0 && lt < V) {
+        const uint16_t raw = grow[lt];
+        tl = BF16 ? __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(&raw))
+                  : __half2float(*reinterpret_cast<const __half*>(&raw));
+      }
+      float* o = stats_block + static_cast<long long>(r) * 3;
+      o[0] = mx;
+      o[1] = se;
+      o[2] = tl;
+    }
+    __syncthreads();
+  }
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(256)
+vp_ce_finish_kernel(uint16_t* __restrict__ logits, long long ld, const long long* __restrict__ target,
+                    const float* __restrict__ stats, int world, float* __restrict__ loss, int rows, int V,
+                    long long vocab_start, long long ignore_index, float grad_scale) {
+  const int nvec = V >> 3;
+  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    float gmax = -INFINITY;
+    for (int w = 0; w < world; ++w) gmax = fmaxf(gmax, stats[(static_cast<long long>(w) * rows + r) * 3]);
+    float gsum = 0.f, tl = 0.f;
+    for (int w = 0; w < world; ++w) {
+      const float* st = stats + (static_cast<long long>(w) * rows + r) * 3;
+      gsum += st[1] * __expf(st[0] - gmax);
+      tl += st[2];
+    }
+    const float lse = gmax + __logf(gsum);
+    const long long tgt = target[r];
+    const bool ignored = tgt == ignore_index;
+    if (threadIdx.x == 0 && loss) loss[r] = ignored ? 0.f : (lse - tl);
+    const float gs = ignored ? 0.f : grad_scale;
+    const long long lt = tgt - vocab_start;
+    uint16_t* grow = logits + static_cast<long long>(r) * ld;
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+      const uint4 a = *reinterpret_cast<const uint4*>(grow + v * 8);
+      const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+      float f[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 t = unpack2<BF16>(w[j]);
+        f[2 * j] = __expf(t.x - lse) * gs;
+        f[2 * j + 1] = __expf(t.y - lse) * gs;
+      }
+      const long long c0 = static_cast<long long>(v) * 8;
+      if (!ignored && lt >= c0 && lt < c0 + 8) f[lt - c0] -= gs;
+      uint4 o;
+      o.x = pack2<BF16>(f[0], f[1]);
+      o.y = pack2<BF16>(f[2], f[3]);
+      o.z = pack2<BF16>(f[4], f[5]);
+      o.w = pack2<BF16>(f[6], f[7]);
+      *reinterpret_cast<uint4*>(grow + v * 8) = o;
+    }
+  }
+}
+
 // ------------------------------------------------------------------ colsum
 // acc[n] += sum over a slice of rows of x[m, n]; fp32 atomics, one per column
 // per CTA.  Block = 32 x 8 threads, each thread owns 8 adjacent columns.
@@ -338,6 +436,31 @@ extern "C" int msq_cross_entropy(void* logits, long long ld, const long long* ta
   else
     cross_entropy_kernel<false><<<grid, 512, smem, stream>>>(static_cast<uint16_t*>(logits), ld, target, loss, lse, rows,
                                                              V, ignore_index, grad_scale, write_grad);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// stats_block: this rank's [rows, 3] block of the zero-initialised [world, rows, 3] table.
+extern "C" int msq_vp_ce_partial(const void* logits, long long ld, const long long* target, float* stats_block, int rows,
+                                 int V, long long vocab_start, int bf16, cudaStream_t stream) {
+  using namespace msq;
+  if (rows <= 0) return 0;
+  if ((V & 7) || (ld & 7) || (reinterpret_cast<uintptr_t>(logits) & 15)) return -2;
+  const int grid = rows < 148 * 8 ? rows : 148 * 8;
+  if (bf16) vp_ce_partial_kernel<true><<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(logits), ld, target, stats_block, rows, V, vocab_start);
+  else vp_ce_partial_kernel<false><<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(logits), ld, target, stats_block, rows, V, vocab_start);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// stats: the all-reduced [world, rows, 3] table.  The logits are overwritten with the gradient.
+extern "C" int msq_vp_ce_finish(void* logits, long long ld, const long long* target, const float* stats, int world,
+                                float* loss, int rows, int V, long long vocab_start, long long ignore_index,
+                                float grad_scale, int bf16, cudaStream_t stream) {
+  using namespace msq;
+  if (rows <= 0) return 0;
+  if ((V & 7) || (ld & 7) || (reinterpret_cast<uintptr_t>(logits) & 15)) return -2;
+  const int grid = rows < 148 * 8 ? rows : 148 * 8;
+  if (bf16) vp_ce_finish_kernel<true><<<grid, 256, 0, stream>>>(static_cast<uint16_t*>(logits), ld, target, stats, world, loss, rows, V, vocab_start, ignore_index, grad_scale);
+  else vp_ce_finish_kernel<false><<<grid, 256, 0, stream>>>(static_cast<uint16_t*>(logits), ld, target, stats, world, loss, rows, V, vocab_start, ignore_index, grad_scale);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

@@ -43,6 +43,7 @@ struct Gemm2Params {
   int ready_chunks_per_shard;
   int ready_skip_shard;
   uint32_t ready_epoch;
+  int ready_operand;  // 0: the flags describe B (weights arriving, FSDP); 1: they describe A (rows arriving, sequence parallel)
   long long* prof;  // debug: cycle counters of the first pair's MMA thread (see msq_gemm2_set_prof)
   // Row-scatter output (GEMM -> reduce-scatter over NVLink): when scatter_world > 0 the tile rows are not
   // written to C but stored into peer memory: row r belongs to rank r / scatter_rows and lands at
@@ -241,7 +242,11 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       uint32_t phase = 0;
       bool ok = true;
       const long long ldb_bytes = p.ready_ldb_bytes;
-      if (p.ready_flags && B_MN)  // every tile reads all k-rows of an MN-major B: the whole operand must be here
+      const bool poll_b = p.ready_flags && p.ready_operand == 0;
+      const bool poll_a = p.ready_flags && p.ready_operand == 1 && !A_MN;
+      if (poll_b && B_MN)  // every tile reads all k-rows of an MN-major B: the whole operand must be here
+        ok = wait_operand_ready(p, p.ready_b_offset, p.ready_b_offset + static_cast<long long>(p.K) * ldb_bytes, abort_flag);
+      if (p.ready_flags && p.ready_operand == 1 && A_MN)  // MN-major A: all k-rows of the operand
         ok = wait_operand_ready(p, p.ready_b_offset, p.ready_b_offset + static_cast<long long>(p.K) * ldb_bytes, abort_flag);
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
         int tm, tn;
@@ -251,9 +256,14 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         // Rows n0 .. n0+127 of a K-major B are one contiguous byte range.  The first tile is checked here; every
         // later tile was checked one tile ahead (below), while the pipeline was full, so the system-scope
         // acquire loads cost no issue time.
-        if (p.ready_flags && !B_MN && tile == pair) {
+        if (poll_b && !B_MN && tile == pair) {
           const long long r1 = min(n0 + G2_BN / 2, p.N);
           ok = wait_operand_ready(p, p.ready_b_offset + n0 * ldb_bytes, p.ready_b_offset + r1 * ldb_bytes, abort_flag);
+          if (!ok) break;
+        }
+        if (poll_a && tile == pair) {  // rows m0 .. m0+127 of a K-major A (ready_ldb_bytes is its row pitch here)
+          const long long r1 = min(m0 + G2_BM, p.M);
+          ok = wait_operand_ready(p, p.ready_b_offset + m0 * ldb_bytes, p.ready_b_offset + r1 * ldb_bytes, abort_flag);
           if (!ok) break;
         }
         const int check_kb = k_blocks > G2_STAGES ? G2_STAGES - 1 : k_blocks - 1;
@@ -279,12 +289,18 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
               tma_load_2d_pair(b_dst + c * (G2_BK * 128), &tmB, &full_bar[stage], n0 + c * 64, k0);
           }
           if (++stage == G2_STAGES) { stage = 0; phase ^= 1; }
-          if (p.ready_flags && !B_MN && kb == check_kb && tile + num_pairs < num_tiles) {
+          if ((poll_a || (poll_b && !B_MN)) && kb == check_kb && tile + num_pairs < num_tiles) {
             int ntm, ntn;
             pair_tile_coords(tile + num_pairs, tiles_m, tiles_n, ntm, ntn);
-            const int nn0 = ntn * G2_BN + static_cast<int>(rank) * (G2_BN / 2);
-            const long long r1 = min(nn0 + G2_BN / 2, p.N);
-            ok = wait_operand_ready(p, p.ready_b_offset + nn0 * ldb_bytes, p.ready_b_offset + r1 * ldb_bytes, abort_flag);
+            long long lo, hi;
+            if (poll_a) {
+              lo = ntm * 2 * G2_BM + static_cast<int>(rank) * G2_BM;
+              hi = min(lo + G2_BM, static_cast<long long>(p.M));
+            } else {
+              lo = ntn * G2_BN + static_cast<int>(rank) * (G2_BN / 2);
+              hi = min(lo + G2_BN / 2, static_cast<long long>(p.N));
+            }
+            ok = wait_operand_ready(p, p.ready_b_offset + lo * ldb_bytes, p.ready_b_offset + hi * ldb_bytes, abort_flag);
             if (!ok) break;
           }
         }
@@ -508,6 +524,7 @@ struct MsqGemmReady {
   long long b_offset, shard_bytes, chunk_bytes;
   int chunks_per_shard, skip_shard;
   unsigned epoch;
+  int operand;  // 0 = B, 1 = A
 };
 
 extern "C" int msq_gemm2_ready(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
@@ -583,12 +600,13 @@ static int gemm2_common(const void* A, const void* B, void* C, int M, int N, int
   for (int i = 0; i < 16; ++i) p.scatter_base[i] = (scatter_ptrs && i < scatter_world) ? scatter_ptrs[i] : nullptr;
   p.ready_flags = nullptr;
   p.ready_b_offset = p.ready_ldb_bytes = p.ready_shard_bytes = p.ready_chunk_bytes = 0;
-  p.ready_chunks_per_shard = 0; p.ready_skip_shard = -1; p.ready_epoch = 0;
+  p.ready_chunks_per_shard = 0; p.ready_skip_shard = -1; p.ready_epoch = 0; p.ready_operand = 0;
   if (ready && ready->flags) {
     if (ready->shard_bytes <= 0 || ready->chunk_bytes <= 0 || ready->chunks_per_shard <= 0) return -6;
     p.ready_flags = static_cast<const uint32_t*>(ready->flags);
     p.ready_b_offset = ready->b_offset;
-    p.ready_ldb_bytes = ldb * 2;
+    p.ready_operand = ready->operand ? 1 : 0;
+    p.ready_ldb_bytes = (ready->operand ? lda : ldb) * 2;
     p.ready_shard_bytes = ready->shard_bytes;
     p.ready_chunk_bytes = ready->chunk_bytes;
     p.ready_chunks_per_shard = ready->chunks_per_shard;

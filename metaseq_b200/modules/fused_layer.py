@@ -56,6 +56,9 @@ def _all_reduce(t, spec):
 def _all_gather_rows(t, spec):
     if spec.tp_world == 1:
         return t
+    if spec.comm is not None and hasattr(spec.comm, "all_gather_rows"):
+        # peer push with arrival flags: the GEMM that reads the result as its A operand polls them per tile
+        return spec.comm.all_gather_rows(t)
     out = torch.empty((t.shape[0] * spec.tp_world, t.shape[1]), dtype=t.dtype, device=t.device)
     dist.all_gather_into_tensor(out, t.contiguous(), group=spec.tp_group)
     return out

@@ -79,7 +79,7 @@ class GemmReady(ctypes.Structure):
 
     _fields_ = [("flags", c_void_p), ("b_offset", c_longlong), ("shard_bytes", c_longlong),
                 ("chunk_bytes", c_longlong), ("chunks_per_shard", c_int), ("skip_shard", c_int),
-                ("epoch", ctypes.c_uint)]
+                ("epoch", ctypes.c_uint), ("operand", c_int)]
 
 
 def _declare_kernels(lib):
@@ -135,6 +135,8 @@ def _declare_kernels(lib):
 _OPTIONAL = {
     "msq_decode_attn": [P, P, P, P, P, I, I, I, I, L, L, L, L, L, F, I, P, I, P],
     "msq_decode_attn_splits": [I, I, I],
+    "msq_vp_ce_partial": [P, L, P, P, I, I, L, I, P],
+    "msq_vp_ce_finish": [P, L, P, P, I, P, I, I, L, L, F, I, P],
 }
 _OPTIONAL = {k: v for k, v in _OPTIONAL.items() if v is not None}
 

@@ -107,12 +107,26 @@ def gemm(
             and (bias is None or bias.data_ptr() % 16 == 0):
         lib = _lib.kernels()
         pair = _GEMM_VARIANT == "2cta" or (_GEMM_VARIANT == "auto" and M >= 256 and N >= 128 and bn == 0)
-        if b_ready is None:
-            b_ready = getattr(b, "_msq_ready", None)
+        # Operands that peers are still writing carry a handle.  The kernel can poll one operand: a weight used as B
+        # (handle.operand == 0) or a row-gathered activation used as A (handle.operand == 1); anything else is
+        # awaited on the stream before the launch.
+        hb = b_ready if b_ready is not None else getattr(b, "_msq_ready", None)
+        ha = getattr(a, "_msq_ready", None)
+        b_ready, target = None, None
+        if hb is not None:
+            if getattr(hb, "operand", 0) == 0:
+                b_ready, target = hb, b
+            else:
+                hb.wait(b)
+        if ha is not None:
+            if b_ready is None and getattr(ha, "operand", 0) == 1:
+                b_ready, target = ha, a
+            else:
+                ha.wait(a)
         if b_ready is not None:
-            desc = b_ready.ready_struct(b) if pair else None
+            desc = b_ready.ready_struct(target) if pair else None
             if desc is None:
-                b_ready.wait(b)  # kernel variant without flag polling: block the stream instead
+                b_ready.wait(target)  # kernel variant without flag polling: block the stream instead
                 b_ready = None
         if b_ready is not None:
             import ctypes as _ct
@@ -140,6 +154,8 @@ def gemm(
         )
         _lib.check_rc(rc, "msq_gemm")
         return out
+    ensure_operand_ready(a)
+    ensure_operand_ready(b)
     return _gemm_torch(a, b, a_mn, b_mn, bias, residual, mask, relu, out, accumulate)
 
 

@@ -64,6 +64,60 @@ class _VocabParallelCrossEntropy(torch.autograd.Function):
         return grad, None
 
 
-def vocab_parallel_cross_entropy(vocab_parallel_logits, target):
-    """Per-token NLL for ``[..., V/p]`` logits and global-vocabulary targets."""
+class _FusedVocabParallelCrossEntropy(torch.autograd.Function):
+    """Kernel path for 16-bit logits on a GPU: per-row (max, sum-exp, target logit) triples computed by one
+    kernel, exchanged in a single small all-reduce (peer-memory kernel when available), then one kernel that
+    writes the loss and overwrites the logits with the gradient.  fp32 logits are never materialised."""
+
+    @staticmethod
+    def forward(ctx, logits, target, ignore_index):
+        from metaseq_b200.ops import _lib
+        from metaseq_b200.parallel import symm
+
+        group = mpu.get_tensor_model_parallel_group()
+        world = mpu.get_tensor_model_parallel_world_size()
+        rank = mpu.get_tensor_model_parallel_rank()
+        V = logits.shape[-1]
+        l2 = logits.data.reshape(-1, V)
+        rows = l2.shape[0]
+        tgt = target.reshape(-1).contiguous()
+        lib = _lib.kernels()
+        bf = int(logits.dtype == torch.bfloat16)
+        stats = torch.zeros((world, rows, 3), dtype=torch.float32, device=logits.device)
+        rc = lib.msq_vp_ce_partial(_lib.ptr(l2), l2.stride(0), _lib.ptr(tgt), _lib.ptr(stats[rank]), rows, V, rank * V, bf,
+                                   _lib.stream_ptr())
+        _lib.check_rc(rc, "msq_vp_ce_partial")
+        tp = symm.get_tp_comm(group, logits.device, 1, 8, logits.dtype) if symm.comm_backend() == "fused" else None
+        if tp is not None:
+            tp.comm.all_reduce(stats.view(-1))
+        else:
+            dist.all_reduce(stats, group=group)
+        loss = torch.empty(rows, dtype=torch.float32, device=logits.device)
+        rc = lib.msq_vp_ce_finish(_lib.ptr(l2), l2.stride(0), _lib.ptr(tgt), _lib.ptr(stats), world, _lib.ptr(loss), rows, V,
+                                  rank * V, int(ignore_index), 1.0, bf, _lib.stream_ptr())
+        _lib.check_rc(rc, "msq_vp_ce_finish")
+        ctx.save_for_backward(l2)
+        ctx.shape = logits.shape
+        return loss.view(target.shape)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        (grad,) = ctx.saved_tensors  # (softmax - onehot), zero rows where the target is ignored
+        g = grad_output.reshape(-1, 1).to(grad.dtype)
+        return (grad * g).view(ctx.shape), None, None
+
+
+def fused_vocab_parallel_cross_entropy_ok(logits) -> bool:
+    from metaseq_b200.ops import functional as F
+
+    return (logits.is_cuda and logits.dtype in (torch.float16, torch.bfloat16) and F.use_kernels(logits)
+            and logits.shape[-1] % 8 == 0 and logits.is_contiguous())
+
+
+def vocab_parallel_cross_entropy(vocab_parallel_logits, target, ignore_index: int = -100):
+    """Per-token NLL for ``[..., V/p]`` logits and global-vocabulary targets.  16-bit logits on a GPU take the
+    kernel path (rows whose target equals ``ignore_index`` get zero loss and gradient there); otherwise the
+    PyTorch implementation, which needs fp32 logits and leaves the masking of ignored targets to the caller."""
+    if fused_vocab_parallel_cross_entropy_ok(vocab_parallel_logits):
+        return _FusedVocabParallelCrossEntropy.apply(vocab_parallel_logits, target, ignore_index)
     return _VocabParallelCrossEntropy.apply(vocab_parallel_logits, target)

@@ -190,7 +190,7 @@ class OperandReady:
         off = view.data_ptr() - self.base_ptr
         assert 0 <= off < m.numel * view.element_size()
         return _lib.GemmReady(self.comm.heap.flags_ptr + 4 * m.flag_base, off, m.shard_bytes, m.chunk_bytes,
-                              m.chunks_per_shard, self.comm.rank, m.ag_epoch)
+                              m.chunks_per_shard, self.comm.rank, m.ag_epoch, 0)
 
     def wait(self, view: torch.Tensor):
         if self.active:
@@ -457,6 +457,34 @@ class PeerComm:
         self.heap.close()
 
 
+class _RowsReady:
+    """Arrival flags of a row-gathered activation (the A operand of the GEMM that consumes it)."""
+
+    operand = 1
+
+    def __init__(self, tp: "TPComm", full: torch.Tensor, shard_bytes: int, chunk: int, chunks: int, epoch: int):
+        self.tp, self.base_ptr = tp, full.data_ptr()
+        self.shard_bytes, self.chunk, self.chunks, self.epoch = shard_bytes, chunk, chunks, epoch
+        self.active = True
+
+    def ready_struct(self, view: torch.Tensor):
+        if not self.active:
+            return None
+        heap = self.tp.comm.heap
+        return _lib.GemmReady(heap.flags_ptr + 4 * self.tp.ag_base, view.data_ptr() - self.base_ptr, self.shard_bytes,
+                              self.chunk, self.chunks, self.tp.rank, self.epoch, 1)
+
+    def wait(self, view: torch.Tensor):
+        if not self.active:
+            return
+        heap = self.tp.comm.heap
+        own = self.tp.ag_base + self.tp.rank * self.chunks
+        rc = _lib.kernels().msq_comm_wait_flags(heap.flags_ptr, self.tp.ag_base, self.tp.ag_base + self.tp.world * self.chunks,
+                                                own, own + self.chunks, self.epoch, self.tp.comm._status(), _lib.stream_ptr())
+        _lib.check_rc(rc, "msq_comm_wait_flags")
+        self.active = False
+
+
 class TPComm:
     """Tensor-parallel collectives fused with the GEMMs that produce their input.
 
@@ -476,16 +504,23 @@ class TPComm:
         self.dtype = dtype
         esz = torch.empty((), dtype=dtype).element_size()
         self.max_bytes = int(max_rows) * int(max_cols) * esz
-        self.comm = PeerComm(group, device, heap_bytes=4 * (self.max_bytes + 4096) + (8 << 20), provider=provider)
+        self.comm = PeerComm(group, device, heap_bytes=6 * (self.max_bytes + 4096) + (8 << 20), provider=provider)
         heap = self.comm.heap
         self.slots_off = [heap.alloc(self.max_bytes), heap.alloc(self.max_bytes)]
         self.bcast_off = [heap.alloc(self.max_bytes), heap.alloc(self.max_bytes)]
         self.rs_base = heap.alloc_flags(self.world)
         self.bc_base = heap.alloc_flags(self.world)
+        self.ag_off = [heap.alloc(self.max_bytes), heap.alloc(self.max_bytes)]
+        self._ag_flag_words = self.world * (self.max_bytes // self.world // self.comm.chunk_bytes + 2)
+        self.ag_base = heap.alloc_flags(self._ag_flag_words)
+        self.ag_epoch = 0
+        self._side = None
         self.epoch = 0
         self._done = torch.zeros(1, dtype=torch.int32, device=device)
         self.fused_calls = 0
         self.fallback_calls = 0
+        self._logged_reduce = False
+        self._logged_gather = False
 
     # ----------------------------------------------------------------- helpers
     def _eligible(self, a, w, M, N, b_mn) -> bool:
@@ -528,7 +563,8 @@ class TPComm:
             int(self.dtype == torch.bfloat16), heap.flags_ptr, self.rs_base, self.epoch, heap.ptr_array, self.bc_base,
             _lib.ptr(self._done), 64, status, stream)
         _lib.check_rc(rc, "msq_comm_reduce_rows")
-        if self.fused_calls == 0 and self.rank == 0:
+        if not self._logged_reduce and self.rank == 0:
+            self._logged_reduce = True
             logger.info("TPComm: fused GEMM -> %s active (M=%d N=%d K=%d, %d ranks, %s mapping)",
                         "all-reduce" if broadcast else "reduce-scatter", M, N, K, self.world, heap.provider)
         self.fused_calls += 1
@@ -579,6 +615,46 @@ class TPComm:
 
     def all_reduce_(self, t: torch.Tensor) -> torch.Tensor:
         return self.comm.all_reduce(t)
+
+    # ------------------------------------------------- sequence-parallel all-gather -> GEMM
+    def all_gather_rows(self, x: torch.Tensor) -> torch.Tensor:
+        """Starts the all-gather of ``x`` ([M/p, K] rows of this rank) along dim 0 and returns the gathered
+        ``[M, K]`` tensor (a view of symmetric memory, valid until the second next call) immediately.  The tensor
+        carries ``_msq_ready``: a GEMM that takes it as its A operand polls the arrival flags of the rows each
+        tile loads, so the product starts on the local rows while the peers' rows are still in flight; any
+        other consumer must call ``ops.functional.ensure_operand_ready`` first."""
+        rows, K = x.shape
+        esz = x.element_size()
+        shard_bytes = rows * K * esz
+        if (not x.is_cuda) or x.dtype != self.dtype or shard_bytes * self.world > self.max_bytes or shard_bytes % 16 \
+                or not x.is_contiguous():
+            out = torch.empty((rows * self.world, K), dtype=x.dtype, device=x.device)
+            dist.all_gather_into_tensor(out, x.contiguous(), group=self.group)
+            self.fallback_calls += 1
+            return out
+        heap, lib = self.comm.heap, _lib.kernels()
+        self.ag_epoch += 1
+        par = self.ag_epoch & 1
+        chunk = min(self.comm.chunk_bytes, shard_bytes)
+        chunks = (shard_bytes + chunk - 1) // chunk
+        assert self.world * chunks <= self._ag_flag_words
+        cur = torch.cuda.current_stream(x.device)
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=x.device)
+        self._side.wait_stream(cur)
+        rc = lib.msq_comm_allgather_ce(heap.ptr_array, self.ag_off[par], _lib.ptr(x), shard_bytes, chunk, self.rank,
+                                       self.world, heap.ptr_array, self.ag_base, self.ag_epoch,
+                                       ctypes.c_void_p(self._side.cuda_stream), ctypes.c_void_p(cur.cuda_stream))
+        _lib.check_rc(rc, "msq_comm_allgather_ce")
+        x.record_stream(self._side)
+        full = heap.view(self.ag_off[par], rows * self.world * K, x.dtype).view(rows * self.world, K)
+        full._msq_ready = _RowsReady(self, full, shard_bytes, chunk, chunks, self.ag_epoch)
+        if not self._logged_gather and self.rank == 0:
+            self._logged_gather = True
+            logger.info("TPComm: fused all-gather -> GEMM active (%d x %d rows of %d, %d ranks)", self.world, rows, K,
+                        self.world)
+        self.fused_calls += 1
+        return full
 
     def close(self):
         self.comm.close()

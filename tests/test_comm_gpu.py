@@ -172,7 +172,52 @@ def _tp_worker(rank, world, port, results):
             dist.all_reduce(ref2)
             torch.cuda.synchronize()
             assert (out2.float() - ref2).abs().max().item() <= 2e-2 * ref2.abs().max().item()
-        assert tp.fused_calls == 12 and tp.fallback_calls == 0
+        # sequence-parallel all-gather consumed by a GEMM that polls the rows' arrival flags
+        from metaseq_b200.ops import functional as F
+
+        calls_before = tp.fused_calls
+        for step in range(4):
+            g = torch.Generator(device=dev).manual_seed(900 + 10 * step + rank)
+            xs = torch.randn(M // world, K, device=dev, dtype=torch.float16, generator=g)
+            w = torch.randn(N, K, device=dev, dtype=torch.float16, generator=torch.Generator(device=dev).manual_seed(step)) * 0.05
+            ref_x = torch.empty(M, K, device=dev, dtype=torch.float16)
+            dist.all_gather_into_tensor(ref_x, xs)
+            torch.cuda.synchronize()
+            dist.barrier()
+            full = tp.all_gather_rows(xs)
+            if step % 2 == 0:
+                y = F.gemm(full, w, bias=bias)                     # [M, K] x [N, K]^T, A polled per tile
+                ref = ref_x.float() @ w.float().t() + bias.float()
+            else:
+                dyv = torch.randn(M, N, device=dev, dtype=torch.float16, generator=torch.Generator(device=dev).manual_seed(77))
+                y = F.gemm(dyv, full, a_mn=True, b_mn=True)          # weight-gradient form: gathered rows as B
+                ref = dyv.float().t() @ ref_x.float()
+            torch.cuda.synchronize()
+            assert torch.equal(full, ref_x), "gathered rows differ"
+            assert (y.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-3, f"SP gemm mismatch {step}"
+            dist.barrier()
+        assert tp.fused_calls == calls_before + 4
+        assert tp.fused_calls == 16 and tp.fallback_calls == 0
+        # vocabulary-parallel cross entropy: kernels + one small all-reduce against full-vocabulary PyTorch
+        from metaseq_b200.parallel import mpu, symm
+        from metaseq_b200.parallel.cross_entropy import vocab_parallel_cross_entropy
+
+        mpu.initialize_model_parallel(world)
+        symm.set_comm_backend("fused")
+        Vl, R = 1024, 600
+        gen = torch.Generator(device=dev).manual_seed(4242)
+        full_logits = torch.randn(R, Vl * world, device=dev, dtype=torch.float16, generator=gen) * 3
+        tgt = torch.randint(0, Vl * world, (R,), device=dev, generator=gen)
+        tgt[::7] = 1  # padding rows
+        local = full_logits[:, rank * Vl:(rank + 1) * Vl].contiguous().requires_grad_(True)
+        per_tok = vocab_parallel_cross_entropy(local, tgt, ignore_index=1)
+        (per_tok.sum() * 2.0).backward()
+        ref_in = full_logits.float().requires_grad_(True)
+        ref = torch.nn.functional.cross_entropy(ref_in, tgt, ignore_index=1, reduction="none")
+        (ref.sum() * 2.0).backward()
+        torch.cuda.synchronize()
+        assert torch.allclose(per_tok, ref, rtol=2e-3, atol=2e-3)
+        assert torch.allclose(local.grad.float(), ref_in.grad[:, rank * Vl:(rank + 1) * Vl], rtol=2e-2, atol=2e-3)
         assert _lib.check_status(dev) == 0
         results[rank] = True
         dist.barrier()

@@ -57,6 +57,8 @@ def test_tensor_parallel_fused_matches_nccl(tmp_path, sp):
     nccl, _ = _run("nccl", tmp_path, extra)
     assert len(fused) >= 5 and len(fused) == len(nccl), log[-2000:]
     assert "TPComm: fused GEMM -> " + ("reduce-scatter" if sp else "all-reduce") + " active" in log, log[-3000:]
+    if sp:
+        assert "TPComm: fused all-gather -> GEMM active" in log
     for a, b in zip(fused, nccl):
         assert abs(a - b) <= 2e-2 * max(1.0, abs(b)), (fused, nccl)
     assert fused[-1] < fused[0]
