@@ -409,7 +409,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* dq_full = pds_full + 1;
   uint64_t* dq_empty = dq_full + 1;
   uint64_t* dkv_full = dq_empty + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dkv_full + 1);
+  uint64_t* pds_free = dkv_full + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pds_free + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -432,6 +433,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     mbar_init(dq_full, 1);
     mbar_init(dq_empty, 256);
     mbar_init(dkv_full, 1);
+    mbar_init(pds_free, 1);
     *abort_flag = 0;
     mbar_fence_init();
     fence_proxy_async_smem();
@@ -492,16 +494,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const uint64_t q_mn0 = make_smem_desc_sw128(smem_u32(sQ), Cfg::CHUNK_BYTES, 1024);
     const uint64_t do_km0 = make_smem_desc_sw128(smem_u32(sDO), 16, 1024);
     const uint64_t do_mn0 = make_smem_desc_sw128(smem_u32(sDO), Cfg::CHUNK_BYTES, 1024);
-    int stage = 0;
-    uint32_t phase = 0;
     bool ok = mbar_wait_warp(kv_full, 0, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
-    for (int it = 0; it < n_it && ok; ++it) {
-      ok = mbar_wait_warp(&qdo_full[stage], phase, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
-      if (!ok) break;
-      if (Cfg::DQ_ALIASES_S && it > 0) {
-        ok = mbar_wait_warp(dq_empty, (it - 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
-        if (!ok) break;
-      }
+    // Q / dO tiles of iteration `it` sit in stage it % QS and complete phase (it / QS) & 1 of that stage's barriers.
+    auto issue_sdp = [&](int it) -> bool {  // S = Q K^T and dP = dO V^T of iteration `it`
+      const int stage = it % QS;
+      if (!mbar_wait_warp(&qdo_full[stage], (it / QS) & 1, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL)) return false;
       tc_fence_after();
       const uint32_t st_off = (stage * Cfg::TILE_BYTES) >> 4;
       if (leader) {
@@ -518,16 +515,30 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tc_commit(sdp_full);
       }
       __syncwarp();
+      return true;
+    };
+    // Without aliasing (HD = 64) the scores of the next iteration are issued before the three gradient products
+    // of this one: the element-wise warps then work on S / dP (it+1) while dQ, dV, dK (it) run on the tensor
+    // pipe.  With dQ aliased onto the S columns (HD = 128) the order stays strictly sequential.
+    constexpr bool PIPELINED = !Cfg::DQ_ALIASES_S;
+    if (ok && n_it > 0) ok = issue_sdp(0);
+    for (int it = 0; it < n_it && ok; ++it) {
+      const int stage = it % QS;
+      const uint32_t st_off = (stage * Cfg::TILE_BYTES) >> 4;
+      // P and dS of this iteration are in shared memory (and S / dP have been read out of TMEM)
       ok = mbar_wait_warp(pds_full, it & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
       if (!ok) break;
-      if (!Cfg::DQ_ALIASES_S && it > 0) {
+      if (PIPELINED && it + 1 < n_it) {
+        ok = issue_sdp(it + 1);
+        if (!ok) break;
+      }
+      if (it > 0) {  // dQ of the previous iteration has been drained from TMEM
         ok = mbar_wait_warp(dq_empty, (it - 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
         if (!ok) break;
       }
       tc_fence_after();
       if (leader) {
         const uint32_t acc = it > 0 ? 1u : 0u;
-        // dQ first: the element-wise warps are waiting for it, while dV / dK only accumulate
 #pragma unroll
         for (int kk = 0; kk < TILE / 16; ++kk) {  // dQ = dS K      (K = kv rows)
           const uint32_t a_off = ((kk >> 2) * Cfg::CHUNK_BYTES + (kk & 3) * 32) >> 4;
@@ -545,10 +556,16 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           tc_mma_f16(tmem_base + Cfg::DK_COL, ds_mn + off, q_mn0 + st_off + off, idesc_t, (kk > 0) ? 1u : acc);
         }
         tc_commit(&qdo_empty[stage]);
+        tc_commit(pds_free);  // P / dS in shared memory may be overwritten
         if (it == n_it - 1) tc_commit(dkv_full);
       }
       __syncwarp();
-      if (++stage == QS) { stage = 0; phase ^= 1; }
+      if (!PIPELINED && it + 1 < n_it) {
+        // dQ (it) lives in the S columns: it must be drained before the next scores are written there
+        ok = mbar_wait_warp(dq_empty, it & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
+        if (!ok) break;
+        ok = issue_sdp(it + 1);
+      }
     }
   } else {
     // Eight warps: warp w owns TMEM lanes / tile rows 32 * (w % 4) .. +31 (the hardware's lane window of
@@ -563,6 +580,40 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     constexpr int DQ_BOXES = HD / 64;  // boxes per warp and iteration
     uint8_t* stage_buf = sStage + (warp - 2) * 4096;
     bool ok = true;
+    int staged = 0;  // bulk reduces issued so far from this warp's staging box
+    // dQ tile of iteration `dit`: TMEM -> swizzled fp32 staging -> one bulk add per 32 x 32 box into dq_accum
+    auto drain_dq = [&](int dit) -> bool {
+      if (!mbar_wait_warp(dq_full, dit & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) return false;
+      tc_fence_after();
+      const int dm = m_start + dit;
+      const bool rows_in_range = dm * TILE + quarter * 32 < p.T;  // rows past T inside a box are dropped by the copy engine
+#pragma unroll
+      for (int c = 0; c < DQ_BOXES; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + Cfg::DQ_COL + lane_off + half * (HD / 2) + c * 32, r);
+        if (staged > 0) {  // the previous bulk add must have read the staging box
+          if (lane == 0) bulk_wait_read_all();
+          __syncwarp();
+        }
+        tmem_ld_wait();
+        uint8_t* dst = stage_buf + lane * 128;
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          *reinterpret_cast<uint4*>(dst + ((u ^ (lane & 7)) << 4)) = make_uint4(r[4 * u], r[4 * u + 1], r[4 * u + 2], r[4 * u + 3]);
+        if (c == DQ_BOXES - 1) {
+          tc_fence_before();
+          mbar_arrive(dq_empty);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (rows_in_range) tma_reduce_add_3d(&tmDQ, stage_buf, h * HD + half * (HD / 2) + c * 32, dm * TILE + quarter * 32, b);
+          bulk_commit_group();
+        }
+        ++staged;
+      }
+      return true;
+    };
     for (int it = 0; it < n_it && ok; ++it) {
       const int m = m_start + it;
       const int q_idx = m * TILE + row;
@@ -581,6 +632,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (!ok) break;
       tc_fence_after();
       if (prof_on) p.prof[256 + it * 8 + 1] = clock64();
+      // P and dS of this thread's 64 columns, kept in registers until shared memory is free to take them
+      uint32_t pp[2][16], dd[2][16];
       {
         uint32_t s[32], dp[32];
         tmem_ld_32x32(tmem_base + Cfg::S_COL + lane_off + col0, s);
@@ -588,7 +641,6 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           tmem_ld_wait();
-          uint32_t pp[16], dd[16];
           const int cbase = col0 + c * 32;
           if (need_mask) {
 #pragma unroll
@@ -602,8 +654,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 p1 = exp2f(fmaf(__uint_as_float(s[2 * i + 1]), scale_log2, -lse2));
                 d1 = p1 * (__uint_as_float(dp[2 * i + 1]) - delta) * p.scale;
               }
-              pp[i] = pack2<BF16>(p0, p1);
-              dd[i] = pack2<BF16>(d0, d1);
+              pp[c][i] = pack2<BF16>(p0, p1);
+              dd[c][i] = pack2<BF16>(d0, d1);
             }
           } else {
             const float nds = -delta * p.scale;
@@ -616,20 +668,30 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
               const float p0 = exp2f(x0), p1 = exp2f(x1);
               const uint64_t g = f2_fma(f2_pack_bits(dp[2 * i], dp[2 * i + 1]), sc2, nds2);
               f2_unpack(f2_mul(f2_pack(p0, p1), g), d0, d1);
-              pp[i] = pack2<BF16>(p0, p1);
-              dd[i] = pack2<BF16>(d0, d1);
+              pp[c][i] = pack2<BF16>(p0, p1);
+              dd[c][i] = pack2<BF16>(d0, d1);
             }
           }
-          if (c == 0) {  // the second half's loads fly while the first half is stored
+          if (c == 0) {
             tmem_ld_32x32(tmem_base + Cfg::S_COL + lane_off + col0 + 32, s);
             tmem_ld_32x32(tmem_base + Cfg::DP_COL + lane_off + col0 + 32, dp);
           }
-          const uint32_t chunk_off = half * Cfg::CHUNK_BYTES;
+        }
+      }
+      if (it > 0) {
+        // the products of the previous iteration that read P / dS from shared memory have completed
+        ok = mbar_wait_warp(pds_free, (it - 1) & 1, abort_flag, p.status, ST_TIMEOUT_SMEM_EMPTY);
+        if (!ok) break;
+      }
+      {
+        const uint32_t chunk_off = half * Cfg::CHUNK_BYTES;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             const uint32_t off = chunk_off + sw128_offset(row, c * 4 + u);
-            *reinterpret_cast<uint4*>(sP + off) = make_uint4(pp[4 * u], pp[4 * u + 1], pp[4 * u + 2], pp[4 * u + 3]);
-            *reinterpret_cast<uint4*>(sDS + off) = make_uint4(dd[4 * u], dd[4 * u + 1], dd[4 * u + 2], dd[4 * u + 3]);
+            *reinterpret_cast<uint4*>(sP + off) = make_uint4(pp[c][4 * u], pp[c][4 * u + 1], pp[c][4 * u + 2], pp[c][4 * u + 3]);
+            *reinterpret_cast<uint4*>(sDS + off) = make_uint4(dd[c][4 * u], dd[c][4 * u + 1], dd[c][4 * u + 2], dd[c][4 * u + 3]);
           }
         }
       }
@@ -637,38 +699,17 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tc_fence_before();
       fence_proxy_async_smem();
       mbar_arrive(pds_full);
-      ok = mbar_wait_warp(dq_full, it & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
-      if (!ok) break;
-      tc_fence_after();
-      if (prof_on) p.prof[256 + it * 8 + 3] = clock64();
-      // dQ tile of this pair: TMEM -> swizzled fp32 staging -> one bulk add per 32 x 32 box into dq_accum
-      const bool rows_in_range = m * TILE + quarter * 32 < p.T;  // rows past T inside a box are dropped by the copy engine
-#pragma unroll
-      for (int c = 0; c < DQ_BOXES; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_base + Cfg::DQ_COL + lane_off + half * (HD / 2) + c * 32, r);
-        if (it > 0 || c > 0) {  // the previous bulk add must have read the staging box
-          if (lane == 0) bulk_wait_read_all();
-          __syncwarp();
-        }
-        tmem_ld_wait();
-        uint8_t* dst = stage_buf + lane * 128;
-#pragma unroll
-        for (int u = 0; u < 8; ++u)
-          *reinterpret_cast<uint4*>(dst + ((u ^ (lane & 7)) << 4)) = make_uint4(r[4 * u], r[4 * u + 1], r[4 * u + 2], r[4 * u + 3]);
-        if (c == DQ_BOXES - 1) {
-          tc_fence_before();
-          mbar_arrive(dq_empty);
-        }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          if (rows_in_range) tma_reduce_add_3d(&tmDQ, stage_buf, h * HD + half * (HD / 2) + c * 32, m * TILE + quarter * 32, b);
-          bulk_commit_group();
-        }
+      // Drain dQ.  When the next scores are issued ahead of the gradient products (HD = 64) the drain of iteration
+      // it-1 happens here, after P / dS (it) have been handed over, so the tensor pipe never waits for it; the
+      // last iteration is drained after the loop.  With aliasing (HD = 128) dQ (it) is drained right away.
+      const int drain_it = Cfg::DQ_ALIASES_S ? it : it - 1;
+      if (drain_it >= 0) {
+        ok = drain_dq(drain_it);
+        if (!ok) break;
       }
       if (prof_on) p.prof[256 + it * 8 + 4] = clock64();
     }
+    if (ok && !Cfg::DQ_ALIASES_S && n_it > 0) ok = drain_dq(n_it - 1);
     // dK / dV of this kv block are complete when the products of the last iteration have been committed.
     const int kv_idx = nb * TILE + row;
     if (ok && n_it > 0) ok = mbar_wait_warp(dkv_full, 0, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);

