@@ -23,7 +23,7 @@ namespace msq {
 
 
 constexpr int ATT_THREADS = 192;      // forward: TMA warp, MMA warp, 4 softmax warps
-constexpr int ATT_BWD_THREADS = 320;  // backward: TMA warp, MMA warp, 8 element-wise warps
+constexpr int ATT_BWD_THREADS = 448;  // backward: TMA warp, MMA warp, 8 element-wise warps, 4 dQ-drain warps
 constexpr int TILE = 128;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
@@ -431,7 +431,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     mbar_init(sdp_full, 1);
     mbar_init(pds_full, 256);
     mbar_init(dq_full, 1);
-    mbar_init(dq_empty, 256);
+    mbar_init(dq_empty, Cfg::DQ_ALIASES_S ? 256 : 128);  // drained by the element-wise warps when aliased, else by the drain warps
     mbar_init(dkv_full, 1);
     mbar_init(pds_free, 1);
     *abort_flag = 0;
@@ -567,6 +567,48 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         ok = issue_sdp(it + 1);
       }
     }
+  } else if (warp >= 10) {
+    // dQ drain warps (one per TMEM lane quarter): TMEM -> swizzled fp32 staging -> bulk add into dq_accum, off
+    // the element-wise warps' critical path.  Idle when dQ aliases the score columns (HD = 128).
+    if (!Cfg::DQ_ALIASES_S) {
+      const int quarter = warp & 3;
+      const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+      uint8_t* boxes = sStage + (warp - 10) * 8192;  // two 32 x 32 fp32 boxes (dQ columns 0-31 and 32-63)
+      bool ok = true;
+      for (int dit = 0; dit < n_it && ok; ++dit) {
+        ok = mbar_wait_warp(dq_full, dit & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t r0[32], r1[32];
+        tmem_ld_32x32(tmem_base + Cfg::DQ_COL + lane_off, r0);
+        tmem_ld_32x32(tmem_base + Cfg::DQ_COL + lane_off + 32, r1);
+        if (dit > 0) {  // the bulk adds of the previous iteration must have read the boxes
+          if (lane == 0) bulk_wait_read_all();
+          __syncwarp();
+        }
+        tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(dq_empty);  // dQ is in registers: the tensor pipe may overwrite the accumulator
+        uint8_t* d0 = boxes + lane * 128;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int sw = (u ^ (lane & 7)) << 4;
+          *reinterpret_cast<uint4*>(d0 + sw) = make_uint4(r0[4 * u], r0[4 * u + 1], r0[4 * u + 2], r0[4 * u + 3]);
+          *reinterpret_cast<uint4*>(d0 + 4096 + sw) = make_uint4(r1[4 * u], r1[4 * u + 1], r1[4 * u + 2], r1[4 * u + 3]);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          const int row0 = (m_start + dit) * TILE + quarter * 32;
+          if (row0 < p.T) {  // rows past T inside a box are dropped by the copy engine
+            tma_reduce_add_3d(&tmDQ, boxes, h * HD, row0, b);
+            tma_reduce_add_3d(&tmDQ, boxes + 4096, h * HD + 32, row0, b);
+          }
+          bulk_commit_group();
+        }
+      }
+      if (lane == 0) bulk_wait_all();  // shared memory must outlive the bulk adds that read it
+    }
   } else {
     // Eight warps: warp w owns TMEM lanes / tile rows 32 * (w % 4) .. +31 (the hardware's lane window of
     // that warp) and the column half (w - 2) / 4 of every tile it reads.
@@ -583,8 +625,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     int staged = 0;  // bulk reduces issued so far from this warp's staging box
     // dQ tile of iteration `dit`: TMEM -> swizzled fp32 staging -> one bulk add per 32 x 32 box into dq_accum
     auto drain_dq = [&](int dit) -> bool {
+      const bool dprof = p.prof != nullptr && row == 0 && half == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && dit < 31;
+      if (dprof) p.prof[256 + (dit + 1) * 8 + 5] = clock64();
       if (!mbar_wait_warp(dq_full, dit & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) return false;
       tc_fence_after();
+      if (dprof) p.prof[256 + (dit + 1) * 8 + 6] = clock64();
       const int dm = m_start + dit;
       const bool rows_in_range = dm * TILE + quarter * 32 < p.T;  // rows past T inside a box are dropped by the copy engine
 #pragma unroll
@@ -596,6 +641,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           __syncwarp();
         }
         tmem_ld_wait();
+        if (dprof) p.prof[256 + (dit + 1) * 8 + 7] = clock64();
         uint8_t* dst = stage_buf + lane * 128;
 #pragma unroll
         for (int u = 0; u < 8; ++u)
@@ -699,17 +745,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tc_fence_before();
       fence_proxy_async_smem();
       mbar_arrive(pds_full);
-      // Drain dQ.  When the next scores are issued ahead of the gradient products (HD = 64) the drain of iteration
-      // it-1 happens here, after P / dS (it) have been handed over, so the tensor pipe never waits for it; the
-      // last iteration is drained after the loop.  With aliasing (HD = 128) dQ (it) is drained right away.
-      const int drain_it = Cfg::DQ_ALIASES_S ? it : it - 1;
-      if (drain_it >= 0) {
-        ok = drain_dq(drain_it);
+      // With aliasing (HD = 128) dQ (it) is drained here, before the next scores overwrite its columns; otherwise
+      // the drain warps take care of it concurrently.
+      if (Cfg::DQ_ALIASES_S) {
+        ok = drain_dq(it);
         if (!ok) break;
       }
       if (prof_on) p.prof[256 + it * 8 + 4] = clock64();
     }
-    if (ok && !Cfg::DQ_ALIASES_S && n_it > 0) ok = drain_dq(n_it - 1);
     // dK / dV of this kv block are complete when the products of the last iteration have been committed.
     const int kv_idx = nb * TILE + row;
     if (ok && n_it > 0) ok = mbar_wait_warp(dkv_full, 0, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
