@@ -1,0 +1,86 @@
+"""Prefill and per-token decode latency of a random-init OPT model through the generation stack
+(``GeneratorInterface`` -> ``SequenceGenerator`` -> model with KV cache), on one GPU.
+
+    python -m metaseq_b200.benchmark.decode --arch opt_1_3b --batch 32 --prompt 512 --gen 128
+
+Timing: CUDA events on the launching stream around whole ``generate`` calls, after warm-up calls.  The prefill
+time is a call that generates one token; the decode time per token is the difference between a call generating
+``--gen`` tokens and that call, divided by ``gen - 1``.  ``--kernel-backend torch`` runs the same model on
+PyTorch ops (library attention, cuBLAS) for comparison."""
+from __future__ import annotations
+
+import argparse
+import json
+
+import numpy as np
+import torch
+
+from metaseq_b200 import options, tasks
+from metaseq_b200.dataclass.utils import convert_namespace_to_config
+from metaseq_b200.hub_utils import GeneratorInterface
+from metaseq_b200.ops import _lib
+from metaseq_b200.ops import functional as F
+
+
+def build(arch: str, max_positions: int):
+    parser = options.get_training_parser()
+    ns = options.parse_args_and_arch(parser, input_args=[
+        "--task", "dummy_lm", "--dict-size", "50268", "--tokens-per-sample", str(max_positions), "--batch-size", "1",
+        "--arch", arch, "--criterion", "vocab_parallel_cross_entropy", "--optimizer", "adam", "--lr", "1e-3",
+        "--memory-efficient-fp16", "--tensor-parallel-init-model-on-gpu", "--distributed-world-size", "1",
+        "--dropout", "0.0", "--attention-dropout", "0.0"])
+    cfg = convert_namespace_to_config(ns)
+    task = tasks.setup_task(cfg.task)
+    torch.manual_seed(1)
+    model = task.build_model(cfg.model).half().cuda().eval()
+    return cfg, task, model
+
+
+def timed(fn, warmup, repeats):
+    for _ in range(warmup):
+        fn()
+    samples = []
+    for _ in range(repeats):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        samples.append(s.elapsed_time(e))
+    return float(np.median(samples))
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--arch", default="opt_1_3b")
+    ap.add_argument("--batch", type=int, default=32)
+    ap.add_argument("--prompt", type=int, default=512)
+    ap.add_argument("--gen", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--repeats", type=int, default=3)
+    ap.add_argument("--kernel-backend", default="auto", choices=["auto", "torch"])
+    args = ap.parse_args(argv)
+    F.set_backend(args.kernel_backend)
+    cfg, task, model = build(args.arch, args.prompt + args.gen + 8)
+    gen = GeneratorInterface.from_model(cfg, model, task)
+    rng = np.random.RandomState(0)
+    prompts = rng.randint(100, 50000, size=(args.batch, args.prompt)).tolist()
+
+    def call(n_new):
+        return gen.generate(prompts, min_tokens=[n_new] * args.batch, max_tokens=[n_new] * args.batch, temperature=1.0,
+                            top_p=-1.0, n=1, echo=False)
+
+    _lib.reset_launch_count()
+    t1 = timed(lambda: call(1), args.warmup, args.repeats)
+    tn = timed(lambda: call(args.gen), 1, args.repeats)
+    per_tok = (tn - t1) / max(1, args.gen - 1)
+    out = dict(metric="decode_ms_per_token", arch=args.arch, batch=args.batch, prompt_len=args.prompt, gen_len=args.gen,
+               prefill_ms=round(t1, 2), total_ms=round(tn, 2), decode_ms_per_token=round(per_tok, 3),
+               decode_tokens_per_s=round(args.batch / per_tok * 1e3, 1), kernel_backend=args.kernel_backend,
+               kernel_launches=_lib.launch_count(), kernel_status=_lib.check_status(torch.device("cuda")),
+               dtype="fp16", data="synthetic uniform token ids, random-init weights")
+    print(json.dumps(out), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -44,6 +44,11 @@ struct AttnFwdParams {
   int bf16;
   int* status;
   long long* prof;  // optional phase timestamps of CTA (0,0,0), see msq_attn_set_prof
+  // attention dropout: weights are dropped with probability threshold16 / 65536 and the kept ones scaled by
+  // inv_keep; the mask of element (b, h, q, k) is a hash of the seed and its index (see dropout_bits)
+  uint32_t drop_threshold16;
+  float inv_keep;
+  unsigned long long seed;
 };
 
 template <int HD>
@@ -61,7 +66,7 @@ struct FwdCfg {
   static constexpr uint32_t TMEM_COLS = (HD == 64) ? 256 : 512;
 };
 
-template <int HD, bool BF16>
+template <int HD, bool BF16, bool DROP>
 __global__ void __launch_bounds__(ATT_THREADS, (HD == 64) ? 2 : 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const AttnFwdParams p) {
@@ -207,6 +212,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     // RESCALE_LOG2 (so P <= 2^RESCALE_LOG2), which keeps rescales of the TMEM accumulator rare.
     constexpr float RESCALE_LOG2 = 8.f;
     float m_run = -INFINITY, l_run = 0.f;
+    // first pair index of this thread's row in the dropout mask: ((b*H + h)*T + q) * ceil(T/2)
+    const unsigned long long drop_row =
+        ((static_cast<unsigned long long>(b) * p.H + h) * p.T + q_idx) * static_cast<unsigned long long>((p.T + 1) >> 1);
     bool ok = true;
     for (int j = 0; j < n_kv && ok; ++j) {
       ok = mbar_wait_warp(s_full, j & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
@@ -290,7 +298,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
               const float bb = (c * 32 + 2 * i + 1 < limit)
                                    ? exp2f(fmaf(__uint_as_float(r[c & 1][2 * i + 1]), p.scale_log2, -m_use)) : 0.f;
               ps4[i & 3] += a + bb;
-              packed[i] = pack2<BF16>(a, bb);
+              float da = a, db = bb;
+              if (DROP) {
+                bool k0, k1;
+                dropout_keep2(dropout_bits(p.seed, drop_row + ((j * TILE + c * 32) >> 1) + i), p.drop_threshold16, k0, k1);
+                da = k0 ? a * p.inv_keep : 0.f;
+                db = k1 ? bb * p.inv_keep : 0.f;
+              }
+              packed[i] = pack2<BF16>(da, db);
             }
           } else {
 #pragma unroll
@@ -298,8 +313,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
               float x0, x1;
               f2_unpack(f2_fma(f2_pack_bits(r[c & 1][2 * i], r[c & 1][2 * i + 1]), scale2, neg_m2), x0, x1);
               const float a = exp2f(x0), bb = exp2f(x1);
-              ps2[i & 1] = f2_add(ps2[i & 1], f2_pack(a, bb));
-              packed[i] = pack2<BF16>(a, bb);
+              ps2[i & 1] = f2_add(ps2[i & 1], f2_pack(a, bb));  // the normaliser uses the undropped weights
+              float da = a, db = bb;
+              if (DROP) {
+                bool k0, k1;
+                dropout_keep2(dropout_bits(p.seed, drop_row + ((j * TILE + c * 32) >> 1) + i), p.drop_threshold16, k0, k1);
+                da = k0 ? a * p.inv_keep : 0.f;
+                db = k1 ? bb * p.inv_keep : 0.f;
+              }
+              packed[i] = pack2<BF16>(da, db);
             }
           }
           tmem_st_32x16(tP + lane_off + c * 16, packed);  // row = lane, two 16-bit probabilities per column
@@ -367,6 +389,9 @@ struct AttnBwdParams {
   int bf16;
   int* status;
   long long* prof;
+  uint32_t drop_threshold16;
+  float inv_keep;
+  unsigned long long seed;
 };
 
 template <int HD>
@@ -384,7 +409,7 @@ struct BwdCfg {
   static constexpr bool DQ_ALIASES_S = (HD != 64);
 };
 
-template <int HD, bool BF16>
+template <int HD, bool BF16, bool DROP>
 __global__ void __launch_bounds__(ATT_BWD_THREADS, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
@@ -688,17 +713,30 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int c = 0; c < 2; ++c) {
           tmem_ld_wait();
           const int cbase = col0 + c * 32;
-          if (need_mask) {
+          if (need_mask || DROP) {
+            // general path: per-element bounds and, with dropout, the keep factor of each weight.  dV uses the
+            // dropped and rescaled weights; dS = P * (keep / (1-p) * dP - delta) * scale.
+            const unsigned long long drop_row =
+                ((static_cast<unsigned long long>(b) * p.H + h) * p.T + (q_ok ? q_idx : 0)) *
+                    static_cast<unsigned long long>((p.T + 1) >> 1) + ((nb * TILE + cbase) >> 1);
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-              float p0 = 0.f, p1 = 0.f, d0 = 0.f, d1 = 0.f;
+              float p0 = 0.f, p1 = 0.f, d0 = 0.f, d1 = 0.f, ks0 = 1.f, ks1 = 1.f;
+              if (DROP) {
+                bool k0, k1;
+                dropout_keep2(dropout_bits(p.seed, drop_row + i), p.drop_threshold16, k0, k1);
+                ks0 = k0 ? p.inv_keep : 0.f;
+                ks1 = k1 ? p.inv_keep : 0.f;
+              }
               if (cbase + 2 * i < limit) {
                 p0 = exp2f(fmaf(__uint_as_float(s[2 * i]), scale_log2, -lse2));
-                d0 = p0 * (__uint_as_float(dp[2 * i]) - delta) * p.scale;
+                d0 = p0 * (ks0 * __uint_as_float(dp[2 * i]) - delta) * p.scale;
+                p0 *= ks0;
               }
               if (cbase + 2 * i + 1 < limit) {
                 p1 = exp2f(fmaf(__uint_as_float(s[2 * i + 1]), scale_log2, -lse2));
-                d1 = p1 * (__uint_as_float(dp[2 * i + 1]) - delta) * p.scale;
+                d1 = p1 * (ks1 * __uint_as_float(dp[2 * i + 1]) - delta) * p.scale;
+                p1 *= ks1;
               }
               pp[c][i] = pack2<BF16>(p0, p1);
               dd[c][i] = pack2<BF16>(d0, d1);
@@ -846,10 +884,10 @@ static int make_tmap_btc(CUtensorMap* out, const void* base, int B, int T, long 
   return encode_tiled_16bit(out, base, 3, dims, strides, box, bf16) == CUDA_SUCCESS ? 0 : -3;
 }
 
-template <int HD, bool BF16>
+template <int HD, bool BF16, bool DROP>
 static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnFwdParams& p,
                       int B, cudaStream_t stream) {
-  auto kern = flash_fwd_kernel<HD, BF16>;
+  auto kern = flash_fwd_kernel<HD, BF16, DROP>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdCfg<HD>::SMEM) != cudaSuccess)
@@ -861,10 +899,10 @@ static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
-template <int HD, bool BF16>
+template <int HD, bool BF16, bool DROP>
 static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
                       const CUtensorMap& tdq, const AttnBwdParams& p, int B, cudaStream_t stream) {
-  auto kern = flash_bwd_kernel<HD, BF16>;
+  auto kern = flash_bwd_kernel<HD, BF16, DROP>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg<HD>::SMEM) != cudaSuccess)
@@ -879,6 +917,23 @@ static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
 }  // namespace msq
 
 static long long* g_attn_prof = nullptr;
+
+// Attention dropout of the next msq_flash_fwd / msq_flash_bwd calls made by this thread (0 = off).  Kept out of
+// the two entry points' argument lists so that callers which never use dropout are unaffected; a forward and its
+// backward must be given the same probability and seed.
+struct AttnDropState {
+  uint32_t threshold16;
+  float inv_keep;
+  unsigned long long seed;
+};
+static thread_local AttnDropState g_attn_drop = {0u, 1.f, 0ull};
+extern "C" int msq_attn_set_dropout(float p, unsigned long long seed) {
+  if (p < 0.f || p >= 1.f) return -2;
+  g_attn_drop.threshold16 = static_cast<uint32_t>(p * 65536.f + 0.5f);
+  g_attn_drop.inv_keep = 1.f / (1.f - static_cast<float>(g_attn_drop.threshold16) / 65536.f);
+  g_attn_drop.seed = seed;
+  return 0;
+}
 
 // Debug aid: when set to a device buffer of at least 512 int64, CTA (0,0,0) of the next attention
 // launches records clock64() at its phase boundaries (forward in [0,256), backward in [256,512)).
@@ -903,8 +958,14 @@ extern "C" int msq_flash_fwd(const void* q, const void* k, const void* v, long l
   p.out = out; p.o_row_stride = o_rs; p.o_batch_stride = o_bs; p.lse = lse;
   p.T = T; p.H = H; p.scale_log2 = scale * LOG2E; p.causal = causal; p.bf16 = bf16; p.status = status;
   p.prof = g_attn_prof;
-  if (HD == 64) return bf16 ? launch_fwd<64, true>(tq, tk, tv, p, B, stream) : launch_fwd<64, false>(tq, tk, tv, p, B, stream);
-  return bf16 ? launch_fwd<128, true>(tq, tk, tv, p, B, stream) : launch_fwd<128, false>(tq, tk, tv, p, B, stream);
+  p.drop_threshold16 = g_attn_drop.threshold16;
+  p.inv_keep = g_attn_drop.inv_keep;
+  p.seed = g_attn_drop.seed;
+#define MSQ_FWD(HDV, BF) \
+  (p.drop_threshold16 ? launch_fwd<HDV, BF, true>(tq, tk, tv, p, B, stream) : launch_fwd<HDV, BF, false>(tq, tk, tv, p, B, stream))
+  if (HD == 64) return bf16 ? MSQ_FWD(64, true) : MSQ_FWD(64, false);
+  return bf16 ? MSQ_FWD(128, true) : MSQ_FWD(128, false);
+#undef MSQ_FWD
 }
 
 // delta: fp32 [B, H, T] scratch (written here); dq_accum: fp32 [B, T, H*HD], zeroed by the caller.
@@ -955,7 +1016,13 @@ extern "C" int msq_flash_bwd(const void* q, const void* k, const void* v, const 
   p.dk_row_stride = dk_rs; p.dk_batch_stride = dk_bs; p.dv_row_stride = dv_rs; p.dv_batch_stride = dv_bs;
   p.T = T; p.H = H; p.scale = scale; p.causal = causal; p.bf16 = bf16; p.status = status;
   p.prof = g_attn_prof;
-  if (HD == 64)
-    return bf16 ? launch_bwd<64, true>(tq, tk, tv, tdo, tdq, p, B, stream) : launch_bwd<64, false>(tq, tk, tv, tdo, tdq, p, B, stream);
-  return bf16 ? launch_bwd<128, true>(tq, tk, tv, tdo, tdq, p, B, stream) : launch_bwd<128, false>(tq, tk, tv, tdo, tdq, p, B, stream);
+  p.drop_threshold16 = g_attn_drop.threshold16;
+  p.inv_keep = g_attn_drop.inv_keep;
+  p.seed = g_attn_drop.seed;
+#define MSQ_BWD(HDV, BF) \
+  (p.drop_threshold16 ? launch_bwd<HDV, BF, true>(tq, tk, tv, tdo, tdq, p, B, stream) \
+                      : launch_bwd<HDV, BF, false>(tq, tk, tv, tdo, tdq, p, B, stream))
+  if (HD == 64) return bf16 ? MSQ_BWD(64, true) : MSQ_BWD(64, false);
+  return bf16 ? MSQ_BWD(128, true) : MSQ_BWD(128, false);
+#undef MSQ_BWD
 }

@@ -213,6 +213,57 @@ cross_entropy_kernel(uint16_t* __restrict__ logits, long long ld, const long lon
   }
 }
 
+// ------------------------------------------------------------------ dropout
+// out[r, c] = residual[r, c] + keep(r, c) ? (y[r, c] + bias[c]) / (1 - p) : 0      (residual, bias optional)
+// With y == dy, no bias and no residual this is also the backward of the dropped branch.  The mask is the hash of
+// (seed, r * cols + c); rows of y / residual / out may be strided.
+template <bool BF16>
+__global__ void dropout_add_kernel(const uint16_t* __restrict__ y, long long ldy, const uint16_t* __restrict__ bias,
+                                   const uint16_t* __restrict__ residual, long long ldr, uint16_t* __restrict__ out,
+                                   long long ldo, long long rows, int cols, uint32_t threshold16, float inv_keep,
+                                   unsigned long long seed) {
+  const int vec_per_row = cols >> 3;
+  const long long total = rows * vec_per_row;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const long long r = i / vec_per_row;
+    const int c = static_cast<int>(i - r * vec_per_row) * 8;
+    const uint4 a = *reinterpret_cast<const uint4*>(y + r * ldy + c);
+    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+    uint32_t bw[4] = {0u, 0u, 0u, 0u}, rw[4] = {0u, 0u, 0u, 0u};
+    if (bias) {
+      const uint4 b4 = *reinterpret_cast<const uint4*>(bias + c);
+      bw[0] = b4.x; bw[1] = b4.y; bw[2] = b4.z; bw[3] = b4.w;
+    }
+    if (residual) {
+      const uint4 r4 = *reinterpret_cast<const uint4*>(residual + r * ldr + c);
+      rw[0] = r4.x; rw[1] = r4.y; rw[2] = r4.z; rw[3] = r4.w;
+    }
+    const unsigned long long pair0 = (static_cast<unsigned long long>(r) * cols + c) >> 1;
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 v = unpack2<BF16>(w[j]);
+      if (bias) {
+        const float2 b2 = unpack2<BF16>(bw[j]);
+        v.x += b2.x;
+        v.y += b2.y;
+      }
+      bool k0, k1;
+      dropout_keep2(dropout_bits(seed, pair0 + j), threshold16, k0, k1);
+      v.x = k0 ? v.x * inv_keep : 0.f;
+      v.y = k1 ? v.y * inv_keep : 0.f;
+      if (residual) {
+        const float2 r2 = unpack2<BF16>(rw[j]);
+        v.x += r2.x;
+        v.y += r2.y;
+      }
+      o[j] = pack2<BF16>(v.x, v.y);
+    }
+    *reinterpret_cast<uint4*>(out + r * ldo + c) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
 // ------------------------------------------------- vocabulary-parallel cross entropy
 // Each tensor-parallel rank holds logits[rows, V_local] for vocabulary ids [vocab_start, vocab_start + V_local).
 // Phase 1 writes, per row, (local max, sum of exp(x - local max), target logit or 0) into this rank's block of a
@@ -436,6 +487,28 @@ extern "C" int msq_cross_entropy(void* logits, long long ld, const long long* ta
   else
     cross_entropy_kernel<false><<<grid, 512, smem, stream>>>(static_cast<uint16_t*>(logits), ld, target, loss, lse, rows,
                                                              V, ignore_index, grad_scale, write_grad);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// p in [0, 1); cols a multiple of 8; all pointers 16-byte aligned, strides multiples of 8 elements.
+extern "C" int msq_dropout_add(const void* y, long long ldy, const void* bias, const void* residual, long long ldr,
+                               void* out, long long ldo, long long rows, int cols, float p, unsigned long long seed,
+                               int bf16, cudaStream_t stream) {
+  using namespace msq;
+  if (rows <= 0 || cols <= 0) return 0;
+  if ((cols & 7) || (ldy & 7) || (ldr & 7) || (ldo & 7) || p < 0.f || p >= 1.f) return -2;
+  const uint32_t thr = static_cast<uint32_t>(p * 65536.f + 0.5f);
+  const float inv_keep = 1.f / (1.f - static_cast<float>(thr) / 65536.f);
+  long long blocks = (rows * (cols >> 3) + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (bf16)
+    dropout_add_kernel<true><<<static_cast<int>(blocks), 256, 0, stream>>>(
+        static_cast<const uint16_t*>(y), ldy, static_cast<const uint16_t*>(bias), static_cast<const uint16_t*>(residual), ldr,
+        static_cast<uint16_t*>(out), ldo, rows, cols, thr, inv_keep, seed);
+  else
+    dropout_add_kernel<false><<<static_cast<int>(blocks), 256, 0, stream>>>(
+        static_cast<const uint16_t*>(y), ldy, static_cast<const uint16_t*>(bias), static_cast<const uint16_t*>(residual), ldr,
+        static_cast<uint16_t*>(out), ldo, rows, cols, thr, inv_keep, seed);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

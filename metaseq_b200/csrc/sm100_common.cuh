@@ -91,6 +91,28 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
   return r;
 }
 
+// ------------------------------------------------------------ dropout masks
+// Stateless keep / drop decisions: element pair `pair_index` of a tensor gets one 32-bit hash of (seed, index),
+// whose two 16-bit halves are compared with threshold = round(p * 65536).  The same function is evaluated
+// in forward and backward kernels, so no mask is ever stored.
+__device__ __forceinline__ uint32_t hash32(uint32_t x) {
+  x ^= x >> 16;
+  x *= 0x7feb352dU;
+  x ^= x >> 15;
+  x *= 0x846ca68bU;
+  x ^= x >> 16;
+  return x;
+}
+__device__ __forceinline__ uint32_t dropout_bits(unsigned long long seed, unsigned long long pair_index) {
+  const uint32_t hi = hash32(static_cast<uint32_t>(pair_index >> 32) ^ static_cast<uint32_t>(seed >> 32));
+  return hash32(static_cast<uint32_t>(pair_index) ^ static_cast<uint32_t>(seed) ^ hi);
+}
+// keep flags of the two elements of a pair
+__device__ __forceinline__ void dropout_keep2(uint32_t bits, uint32_t threshold16, bool& k0, bool& k1) {
+  k0 = (bits & 0xFFFFu) >= threshold16;
+  k1 = (bits >> 16) >= threshold16;
+}
+
 // ----------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");

@@ -43,6 +43,11 @@ class LayerSpec:
     sequence_parallel: bool = False
     recompute: bool = False
     comm: Any = None  # optional fused-communication provider (metaseq_b200.parallel.symm.TPComm)
+    # dropout (training only): probability after out_proj / fc2, probability on the attention weights, and the
+    # seeds of the three masks (drawn once per forward call, reused by recomputation and backward)
+    dropout_p: float = 0.0
+    attn_dropout_p: float = 0.0
+    seeds: Any = None
 
 
 def _all_reduce(t, spec):
@@ -72,8 +77,17 @@ def _reduce_scatter_rows(t, spec):
     return out
 
 
-def _row_parallel_out(a, w, bias, residual, spec):
-    """``residual + bias + reduce(a @ w^T)`` over the tensor-parallel group."""
+def _row_parallel_out(a, w, bias, residual, spec, seed=None):
+    """``residual + dropout(bias + reduce(a @ w^T))`` over the tensor-parallel group (dropout when ``seed``)."""
+    if seed is not None and spec.dropout_p > 0:
+        if spec.tp_world == 1:
+            part = F.gemm(a, w)
+        elif spec.comm is not None:
+            part = spec.comm.gemm_reduce_scatter(a, w) if spec.sequence_parallel else spec.comm.gemm_all_reduce(a, w)
+        else:
+            part = F.gemm(a, w)
+            part = _reduce_scatter_rows(part, spec) if spec.sequence_parallel else _all_reduce(part, spec)
+        return F.dropout_add(part, bias, residual, spec.dropout_p, seed)
     if spec.tp_world == 1:
         return F.gemm(a, w, bias=bias, residual=residual)
     if spec.comm is not None:
@@ -113,13 +127,15 @@ def _forward(x2, p, spec: LayerSpec):
     k = q3[..., 0:Dp].view(B, T, H, d)
     v = q3[..., Dp:2 * Dp].view(B, T, H, d)
     q = q3[..., 2 * Dp:].view(B, T, H, d)
-    ctx, lse = F.flash_attn_fwd(q, k, v, spec.scale, True)
+    s_attn, s_res1, s_res2 = spec.seeds if spec.seeds is not None else (None, None, None)
+    ctx, lse = F.flash_attn_fwd(q, k, v, spec.scale, True, dropout_p=spec.attn_dropout_p if s_attn is not None else 0.0,
+                                seed=s_attn or 0)
     ctx2 = ctx.view(B * T, Dp)
-    x_mid = _row_parallel_out(ctx2, out_w, out_b, x2, spec)
+    x_mid = _row_parallel_out(ctx2, out_w, out_b, x2, spec, s_res1)
     h2, mean2, rstd2 = F.layer_norm_fwd(x_mid, ln2_w, ln2_b, spec.eps)
     h2_full = _all_gather_rows(h2, spec) if spec.sequence_parallel else h2
     act = F.gemm(h2_full, fc1_w, bias=fc1_b, relu=True)
-    y = _row_parallel_out(act, fc2_w, fc2_b, x_mid, spec)
+    y = _row_parallel_out(act, fc2_w, fc2_b, x_mid, spec, s_res2)
     saved = (h1 if not spec.sequence_parallel else h1, mean1, rstd1, qkv, ctx, lse, x_mid, h2, mean2, rstd2, act)
     return y, saved
 
@@ -179,11 +195,15 @@ class FusedDecoderLayerFn(torch.autograd.Function):
                 return dx, None, None
             return F.layer_norm_bwd(dyh, xin, mean, rstd, gw, add=add, need_param_grads=gw is not None)
 
-        # ---- FC2 (row parallel): y = x_mid + b2 + reduce(act @ W2^T)
-        dy_full = _all_gather_rows(dy2, spec) if sp else dy2
+        s_attn, s_res1, s_res2 = spec.seeds if spec.seeds is not None else (None, None, None)
+        drop = spec.dropout_p > 0 and s_res2 is not None
+        # ---- FC2 (row parallel): y = x_mid + dropout(b2 + reduce(act @ W2^T))
+        dyb = F.dropout_add(dy2, None, None, spec.dropout_p, s_res2) if drop else dy2  # gradient of the dropped branch
+        dy_full = _all_gather_rows(dyb, spec) if sp else dyb
         d_act = F.gemm(dy_full, fc2_w, b_mn=True, mask=act)  # ReLU backward fused
         g_fc2_w = wgrad(fc2_w, dy_full, act)
-        g_fc2_b = bgrad(fc2_b, dy2)
+        g_fc2_b = bgrad(fc2_b, dyb)
+        del dyb
         # ---- FC1 (column parallel)
         dh2 = _dgrad_reduced(d_act, fc1_w, spec)
         h2_full = _all_gather_rows(h2, spec) if sp else h2
@@ -194,18 +214,22 @@ class FusedDecoderLayerFn(torch.autograd.Function):
         dx_mid, g_ln2_w, g_ln2_b = ln_bwd(dh2, x_mid, mean2, rstd2, ln2_w, ln2_b, dy2)
         del dh2
         # ---- out_proj (row parallel)
-        dxm_full = _all_gather_rows(dx_mid, spec) if sp else dx_mid
+        dxb = F.dropout_add(dx_mid, None, None, spec.dropout_p, s_res1) if (spec.dropout_p > 0 and s_res1 is not None) \
+            else dx_mid
+        dxm_full = _all_gather_rows(dxb, spec) if sp else dxb
         attn2 = attn.view(B * T, -1)
         d_attn = F.gemm(dxm_full, out_w, b_mn=True)
         g_out_w = wgrad(out_w, dxm_full, attn2)
-        g_out_b = bgrad(out_b, dx_mid)
+        g_out_b = bgrad(out_b, dxb)
+        del dxb
         # ---- attention
         Dp = qkv.shape[1] // 3
         dqkv = torch.empty_like(qkv)
         q3, dq3 = qkv.view(B, T, 3 * Dp), dqkv.view(B, T, 3 * Dp)
         sl = lambda t, i: t[..., i * Dp:(i + 1) * Dp].view(B, T, H, d)
         F.flash_attn_bwd(sl(q3, 2), sl(q3, 0), sl(q3, 1), attn, d_attn.view(B, T, Dp), lse, spec.scale, True,
-                         sl(dq3, 2), sl(dq3, 0), sl(dq3, 1))
+                         sl(dq3, 2), sl(dq3, 0), sl(dq3, 1),
+                         dropout_p=spec.attn_dropout_p if s_attn is not None else 0.0, seed=s_attn or 0)
         del d_attn
         # ---- QKV (column parallel)
         dh1 = _dgrad_reduced(dqkv, qkv_w, spec)

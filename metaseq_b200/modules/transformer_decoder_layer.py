@@ -109,8 +109,6 @@ class ModelParallelTransformerDecoderLayer(nn.Module):
             return False
         if not (ops_f.use_kernels(x) or FORCE_FUSED_LAYER) or self.activation_name != "relu":
             return False
-        if self.training and (self.dropout_module.p > 0 or self.self_attn.dropout_module.p > 0):
-            return False
         if (self.self_attn.head_dim not in (64, 128) and not FORCE_FUSED_LAYER) or self.embed_dim % 8 != 0:
             return False
         if self.self_attn.qkv_proj.weight.dtype != x.dtype:
@@ -130,11 +128,23 @@ class ModelParallelTransformerDecoderLayer(nn.Module):
                 # every fused row-parallel product of the layer has a [B*T, D] result
                 self.tp_comm = symm.get_tp_comm(mpu.get_tensor_model_parallel_group(), x.device, bt[0] * bt[1],
                                                 self.embed_dim, x.dtype)
+            seeds, p_res, p_attn = None, 0.0, 0.0
+            if self.training and (self.dropout_module.p > 0 or self.self_attn.dropout_module.p > 0):
+                # Three mask seeds per call from the host generator (reseeded per update by the trainer, so runs are
+                # reproducible and no device sync is needed).  Residual masks are shared by the tensor-parallel
+                # ranks (they hold the same activations) unless the sequence is sharded; attention heads differ
+                # per rank, so that seed is offset by the rank.
+                base = torch.randint(0, 2 ** 62, (3,), dtype=torch.int64).tolist()
+                tp_rank = mpu.get_tensor_model_parallel_rank()
+                res_off = tp_rank if self.sequence_parallel else 0
+                seeds = (base[0] + 7919 * tp_rank, base[1] + res_off, base[2] + res_off)
+                p_res, p_attn = float(self.dropout_module.p), float(self.self_attn.dropout_module.p)
             spec = LayerSpec(
                 B=bt[0], T=bt[1], heads_local=a.num_heads_partition, head_dim=a.head_dim, scale=a.scaling,
                 eps=self.self_attn_layer_norm.eps, tp_group=mpu.get_tensor_model_parallel_group(),
                 tp_world=mpu.get_tensor_model_parallel_world_size(), sequence_parallel=self.sequence_parallel,
-                recompute=self.checkpoint_activations if recompute is None else recompute, comm=self.tp_comm)
+                recompute=self.checkpoint_activations if recompute is None else recompute, comm=self.tp_comm,
+                dropout_p=p_res, attn_dropout_p=p_attn, seeds=seeds)
             ln1, ln2 = self.self_attn_layer_norm, self.final_layer_norm
             return fused_decoder_layer(
                 x, spec, ln1.weight, ln1.bias, a.qkv_proj.weight, a.qkv_proj.bias, a.out_proj.weight, a.out_proj.bias,

@@ -26,7 +26,7 @@ F = c_float
 
 
 # kernels launched by one call of each entry point (used for the launch counter)
-_KERNELS_PER_CALL = {"msq_symm_alloc": 0, "msq_symm_open": 0, "msq_symm_close": 0, "msq_symm_free": 0, "msq_sumsq": 2, "msq_layernorm_bwd": 2, "msq_flash_bwd": 2, "msq_layernorm_bwd_parts": 0,
+_KERNELS_PER_CALL = {"msq_attn_set_dropout": 0, "msq_symm_alloc": 0, "msq_symm_open": 0, "msq_symm_close": 0, "msq_symm_free": 0, "msq_sumsq": 2, "msq_layernorm_bwd": 2, "msq_flash_bwd": 2, "msq_layernorm_bwd_parts": 0,
                      "msq_sumsq_parts": 0}
 _LAUNCHES = [0]
 
@@ -135,6 +135,8 @@ def _declare_kernels(lib):
 _OPTIONAL = {
     "msq_decode_attn": [P, P, P, P, P, I, I, I, I, L, L, L, L, L, F, I, P, I, P],
     "msq_decode_attn_splits": [I, I, I],
+    "msq_attn_set_dropout": [F, ctypes.c_ulonglong],
+    "msq_dropout_add": [P, L, P, P, L, P, L, L, I, F, ctypes.c_ulonglong, I, P],
     "msq_vp_ce_partial": [P, L, P, P, I, I, L, I, P],
     "msq_vp_ce_finish": [P, L, P, P, I, P, I, I, L, L, F, I, P],
 }

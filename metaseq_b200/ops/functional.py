@@ -275,23 +275,56 @@ def layer_norm_bwd(dy, x2d, mean, rstd, gamma, add=None, dgamma_out=None, dbeta_
 
 
 # ------------------------------------------------------------------ attention
-def flash_attn_fwd(q, k, v, scale: float, causal: bool = True):
+def attn_keep_mask_reference(B: int, H: int, T: int, p: float, seed: int, device) -> torch.Tensor:
+    """``[B, H, T, T]`` keep mask of the attention-dropout kernels, recomputed with integer tensor ops."""
+    thr = int(p * 65536.0 + 0.5)
+    rows = torch.arange(B * H * T, device=device, dtype=torch.int64).view(B, H, T, 1)
+    kcol = torch.arange(T, device=device, dtype=torch.int64).view(1, 1, 1, T)
+    pair = rows * ((T + 1) >> 1) + (kcol >> 1)
+
+    def h32(x):
+        x = x & 0xFFFFFFFF
+        x = x ^ (x >> 16)
+        x = (x * 0x7FEB352D) & 0xFFFFFFFF
+        x = x ^ (x >> 15)
+        x = (x * 0x846CA68B) & 0xFFFFFFFF
+        return x ^ (x >> 16)
+
+    hi = h32((pair >> 32) ^ ((seed >> 32) & 0xFFFFFFFF))
+    bits = h32((pair & 0xFFFFFFFF) ^ (seed & 0xFFFFFFFF) ^ hi)
+    half = torch.where((kcol & 1) == 0, bits & 0xFFFF, bits >> 16)
+    return half >= thr
+
+
+def flash_attn_fwd(q, k, v, scale: float, causal: bool = True, dropout_p: float = 0.0, seed: int = 0):
     """``q, k, v``: ``[B, T, H, d]`` views (last dim contiguous, head stride ``d``).
-    Returns ``(out [B, T, H*d], lse [B, H, T] fp32)``."""
+    Returns ``(out [B, T, H*d], lse [B, H, T] fp32)``.  With ``dropout_p > 0`` the attention weights are dropped
+    with the mask derived from ``seed`` (the normaliser is unaffected); pass the same values to the backward."""
     B, T, H, d = q.shape
     if use_kernels(q) and d in (64, 128) and _attn_views_ok(q, k, v):
         out = torch.empty((B, T, H * d), dtype=q.dtype, device=q.device)
         lse = torch.empty((B, H, T), dtype=torch.float32, device=q.device)
-        rc = _lib.kernels().msq_flash_fwd(
-            _lib.ptr(q), _lib.ptr(k), _lib.ptr(v),
-            q.stride(1), q.stride(0), k.stride(1), k.stride(0), v.stride(1), v.stride(0),
-            _lib.ptr(out), out.stride(1), out.stride(0), _lib.ptr(lse),
-            B, T, H, d, float(scale), int(causal), _bf(q),
-            _lib.ptr(_lib.status_word(q.device)), _lib.stream_ptr(),
-        )
+        lib = _lib.kernels()
+        if dropout_p > 0:
+            _lib.check_rc(lib.msq_attn_set_dropout(float(dropout_p), int(seed)), "msq_attn_set_dropout")
+        try:
+            rc = _flash_fwd_call(lib, q, k, v, out, lse, B, T, H, d, scale, causal)
+        finally:
+            if dropout_p > 0:
+                lib.msq_attn_set_dropout(0.0, 0)
         _lib.check_rc(rc, "msq_flash_fwd")
         return out, lse
-    return _attn_fwd_torch(q, k, v, scale, causal)
+    return _attn_fwd_torch(q, k, v, scale, causal, dropout_p, seed)
+
+
+def _flash_fwd_call(lib, q, k, v, out, lse, B, T, H, d, scale, causal):
+    return lib.msq_flash_fwd(
+        _lib.ptr(q), _lib.ptr(k), _lib.ptr(v),
+        q.stride(1), q.stride(0), k.stride(1), k.stride(0), v.stride(1), v.stride(0),
+        _lib.ptr(out), out.stride(1), out.stride(0), _lib.ptr(lse),
+        B, T, H, d, float(scale), int(causal), _bf(q),
+        _lib.ptr(_lib.status_word(q.device)), _lib.stream_ptr(),
+    )
 
 
 def _attn_views_ok(*ts) -> bool:
@@ -302,7 +335,7 @@ def _attn_views_ok(*ts) -> bool:
     return True
 
 
-def _attn_fwd_torch(q, k, v, scale, causal):
+def _attn_fwd_torch(q, k, v, scale, causal, dropout_p: float = 0.0, seed: int = 0):
     B, T, H, d = q.shape
     qf, kf, vf = (t.float().permute(0, 2, 1, 3) for t in (q, k, v))  # [B,H,T,d]
     s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
@@ -311,11 +344,15 @@ def _attn_fwd_torch(q, k, v, scale, causal):
         s = s.masked_fill(mask, float("-inf"))
     lse = torch.logsumexp(s, dim=-1)
     p = torch.exp(s - lse[..., None])
+    if dropout_p > 0:
+        keep = attn_keep_mask_reference(B, H, T, dropout_p, seed, q.device)
+        p = torch.where(keep, p / (1.0 - int(dropout_p * 65536.0 + 0.5) / 65536.0), torch.zeros_like(p))
     o = torch.matmul(p, vf).permute(0, 2, 1, 3).reshape(B, T, H * d)
     return o.to(q.dtype), lse
 
 
-def flash_attn_bwd(q, k, v, out, d_out, lse, scale: float, causal: bool, dq, dk, dv):
+def flash_attn_bwd(q, k, v, out, d_out, lse, scale: float, causal: bool, dq, dk, dv, dropout_p: float = 0.0,
+                   seed: int = 0):
     """Writes gradients into the ``[B, T, H, d]`` views ``dq, dk, dv`` (typically column slices
     of the qkv-gradient buffer)."""
     B, T, H, d = q.shape
@@ -325,6 +362,8 @@ def flash_attn_bwd(q, k, v, out, d_out, lse, scale: float, causal: bool, dq, dk,
     ):
         delta = torch.empty((B, H, T), dtype=torch.float32, device=q.device)
         dq_acc = torch.zeros((B, T, H * d), dtype=torch.float32, device=q.device)
+        if dropout_p > 0:
+            _lib.check_rc(_lib.kernels().msq_attn_set_dropout(float(dropout_p), int(seed)), "msq_attn_set_dropout")
         rc = _lib.kernels().msq_flash_bwd(
             _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(out), _lib.ptr(d_out),
             q.stride(1), q.stride(0), k.stride(1), k.stride(0), v.stride(1), v.stride(0),
@@ -334,6 +373,8 @@ def flash_attn_bwd(q, k, v, out, d_out, lse, scale: float, causal: bool, dq, dk,
             B, T, H, d, float(scale), int(causal), _bf(q),
             _lib.ptr(_lib.status_word(q.device)), _lib.stream_ptr(),
         )
+        if dropout_p > 0:
+            _lib.kernels().msq_attn_set_dropout(0.0, 0)
         _lib.check_rc(rc, "msq_flash_bwd")
         # dq is a column slice of the qkv gradient: rows of H*d elements, row stride dq.stride(1)
         if dq.stride(2) == d and dq.stride(3) == 1 and dq.stride(0) == T * dq.stride(1) and dq.stride(1) % 8 == 0:
@@ -351,8 +392,14 @@ def flash_attn_bwd(q, k, v, out, d_out, lse, scale: float, causal: bool, dq, dk,
         mask = torch.ones(T, T, dtype=torch.bool, device=q.device).triu(1)
         s = s.masked_fill(mask, float("-inf"))
     p = torch.exp(s - lse[..., None])
-    dvf = torch.matmul(p.transpose(-1, -2), dof)
     dp = torch.matmul(dof, vf.transpose(-1, -2))
+    if dropout_p > 0:
+        keep = attn_keep_mask_reference(B, H, T, dropout_p, seed, q.device)
+        ks = keep.float() / (1.0 - int(dropout_p * 65536.0 + 0.5) / 65536.0)
+        dvf = torch.matmul((p * ks).transpose(-1, -2), dof)
+        dp = dp * ks
+    else:
+        dvf = torch.matmul(p.transpose(-1, -2), dof)
     delta = (dof * of).sum(dim=-1, keepdim=True)
     ds = p * (dp - delta) * scale
     dqf = torch.matmul(ds, kf)
@@ -435,6 +482,49 @@ def fold_fp32_into(src32: torch.Tensor, dst16: torch.Tensor, accumulate: bool):
     else:
         dst16.copy_(src32.view_as(dst16))
     return dst16
+
+
+def _keep_mask_reference(rows: int, cols: int, p: float, seed: int, device) -> torch.Tensor:
+    """The kernels' keep mask recomputed with integer tensor ops (oracle for tests and the PyTorch backend)."""
+    thr = int(p * 65536.0 + 0.5)
+    idx = torch.arange(rows * cols, device=device, dtype=torch.int64)
+    pair = idx >> 1
+
+    def h32(x):
+        x = x & 0xFFFFFFFF
+        x = x ^ (x >> 16)
+        x = (x * 0x7FEB352D) & 0xFFFFFFFF
+        x = x ^ (x >> 15)
+        x = (x * 0x846CA68B) & 0xFFFFFFFF
+        return x ^ (x >> 16)
+
+    hi = h32((pair >> 32) ^ ((seed >> 32) & 0xFFFFFFFF))
+    bits = h32((pair & 0xFFFFFFFF) ^ (seed & 0xFFFFFFFF) ^ hi)
+    half = torch.where((idx & 1) == 0, bits & 0xFFFF, bits >> 16)
+    return (half >= thr).view(rows, cols)
+
+
+def dropout_add(y: torch.Tensor, bias, residual, p: float, seed: int, out: Optional[torch.Tensor] = None):
+    """``residual + dropout(y + bias, p)`` for 2-D ``y`` with the mask derived from ``seed`` (same mask for the
+    same seed, so the backward pass calls this again on the gradient with ``bias = residual = None``)."""
+    rows, cols = y.shape
+    if out is None:
+        out = torch.empty_like(y)
+    thr = int(p * 65536.0 + 0.5)
+    if use_kernels(y) and cols % 8 == 0 and y.stride(1) == 1 and out.stride(1) == 1 and y.stride(0) % 8 == 0 \
+            and out.stride(0) % 8 == 0 and (residual is None or (residual.stride(1) == 1 and residual.stride(0) % 8 == 0)):
+        rc = _lib.kernels().msq_dropout_add(_lib.ptr(y), y.stride(0), _lib.ptr(bias), _lib.ptr(residual),
+                                            residual.stride(0) if residual is not None else 0, _lib.ptr(out), out.stride(0),
+                                            rows, cols, float(p), int(seed), _bf(y), _lib.stream_ptr())
+        _lib.check_rc(rc, "msq_dropout_add")
+        return out
+    keep = _keep_mask_reference(rows, cols, p, seed, y.device)
+    v = y.float() + (bias.float() if bias is not None else 0.0)
+    v = torch.where(keep, v / (1.0 - thr / 65536.0), torch.zeros_like(v))
+    if residual is not None:
+        v = v + residual.float()
+    out.copy_(v.to(out.dtype))
+    return out
 
 
 def decode_attn(q, k_cache, v_cache, length: int, num_heads: int, scale: float, key_padding_mask=None):

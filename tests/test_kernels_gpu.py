@@ -328,3 +328,53 @@ def test_decode_attention_kv_cache(dtype, B, H, d, S, Tmax, masked):
         F.set_backend("auto")
     tol = 2e-2 if dtype == torch.bfloat16 else 4e-3
     assert torch.allclose(out.float(), ref.float(), rtol=tol, atol=tol), (out.float() - ref.float()).abs().max()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_dropout_add_matches_hash_reference(dtype):
+    g = torch.Generator(device="cuda").manual_seed(1)
+    rows, cols = 777, 1024
+    y = torch.randn(rows, cols, device="cuda", dtype=dtype, generator=g)
+    bias = torch.randn(cols, device="cuda", dtype=dtype, generator=g)
+    res = torch.randn(rows, cols + 64, device="cuda", dtype=dtype, generator=g)[:, :cols]  # strided rows
+    out = F.dropout_add(y, bias, res, 0.1, 123456789012345)
+    keep = F._keep_mask_reference(rows, cols, 0.1, 123456789012345, y.device)
+    assert abs(keep.float().mean().item() - 0.9) < 5e-3
+    ref = torch.where(keep, (y.float() + bias.float()) / (1 - 6554 / 65536), torch.zeros_like(y, dtype=torch.float32)) + res.float()
+    tol = 3e-2 if dtype == torch.bfloat16 else 4e-3
+    assert torch.allclose(out.float(), ref, rtol=tol, atol=tol)
+    gout = F.dropout_add(y, None, None, 0.1, 123456789012345)  # backward form: same mask, no bias / residual
+    assert torch.equal(gout == 0, ~keep | (y == 0))
+
+
+@pytest.mark.parametrize("B,T,H,d", [(2, 256, 4, 64), (1, 384, 2, 128), (2, 200, 2, 64)])
+def test_flash_attention_dropout_matches_reference(B, T, H, d):
+    g = torch.Generator(device="cuda").manual_seed(7)
+    qkv = (torch.randn(B, T, 3 * H * d, device="cuda", generator=g) * 0.5).half()
+    D = H * d
+    k, v, q = (qkv[..., i * D:(i + 1) * D].view(B, T, H, d) for i in range(3))
+    p_drop, seed = 0.2, 9876543210123
+    out, lse = F.flash_attn_fwd(q, k, v, d ** -0.5, True, dropout_p=p_drop, seed=seed)
+    F.set_backend("torch")
+    try:
+        ref, lse_ref = F.flash_attn_fwd(q, k, v, d ** -0.5, True, dropout_p=p_drop, seed=seed)
+    finally:
+        F.set_backend("auto")
+    assert torch.allclose(lse, lse_ref, rtol=1e-3, atol=1e-3)
+    assert torch.allclose(out.float(), ref.float(), rtol=2e-2, atol=2e-2), (out.float() - ref.float()).abs().max()
+    d_out = torch.randn(B, T, D, device="cuda", generator=g).half()
+    grads = {}
+    for backend in ("auto", "torch"):
+        F.set_backend(backend)
+        try:
+            dqkv = torch.zeros_like(qkv)
+            dk, dv, dq = (dqkv[..., i * D:(i + 1) * D].view(B, T, H, d) for i in range(3))
+            F.flash_attn_bwd(q, k, v, out, d_out, lse, d ** -0.5, True, dq, dk, dv, dropout_p=p_drop, seed=seed)
+            grads[backend] = dqkv.float()
+        finally:
+            F.set_backend("auto")
+    err = (grads["auto"] - grads["torch"]).abs().max().item()
+    assert err <= 3e-2 * grads["torch"].abs().max().item() + 2e-3, err
+    # without dropout the same call gives a different (undropped) result
+    out0, _ = F.flash_attn_fwd(q, k, v, d ** -0.5, True)
+    assert (out0.float() - out.float()).abs().max().item() > 1e-2
