@@ -1,5 +1,5 @@
 """Prefill and per-token decode latency of a random-init OPT model through the generation stack
-(``GeneratorInterface`` -> ``SequenceGenerator`` -> model with KV cache), on one GPU.
+(``SequenceGenerator`` -> model with KV cache), on one GPU.
 
     python -m metaseq_b200.benchmark.decode --arch opt_1_3b --batch 32 --prompt 512 --gen 128
 
@@ -17,7 +17,7 @@ import torch
 
 from metaseq_b200 import options, tasks
 from metaseq_b200.dataclass.utils import convert_namespace_to_config
-from metaseq_b200.hub_utils import GeneratorInterface
+from metaseq_b200.sequence_generator import SequenceGenerator
 from metaseq_b200.ops import _lib
 from metaseq_b200.ops import functional as F
 
@@ -62,13 +62,16 @@ def main(argv=None):
     args = ap.parse_args(argv)
     F.set_backend(args.kernel_backend)
     cfg, task, model = build(args.arch, args.prompt + args.gen + 8)
-    gen = GeneratorInterface.from_model(cfg, model, task)
     rng = np.random.RandomState(0)
-    prompts = rng.randint(100, 50000, size=(args.batch, args.prompt)).tolist()
+    prompts = torch.from_numpy(rng.randint(100, 50000, size=(args.batch, args.prompt))).cuda()
+    sample = {"net_input": {"src_tokens": prompts}}
 
     def call(n_new):
-        return gen.generate(prompts, min_tokens=[n_new] * args.batch, max_tokens=[n_new] * args.batch, temperature=1.0,
-                            top_p=-1.0, n=1, echo=False)
+        total = args.prompt + n_new
+        sg = SequenceGenerator([model], task.target_dictionary, beam_size=1, max_len_b=total, min_len=total,
+                               temperature=1.0, topp=-1)
+        with torch.no_grad():
+            return sg.generate([model], sample)
 
     _lib.reset_launch_count()
     t1 = timed(lambda: call(1), args.warmup, args.repeats)

@@ -7,6 +7,11 @@
 // organised around 16-byte loads with HD/8 lanes per key, an online softmax per lane group, and a merge
 // of the groups' (max, sum, accumulator) triples at the end.  Long sequences with few (batch, head)
 // pairs are split along the sequence; a second kernel merges the splits.
+//
+// The "step" form serves a decode step captured in a CUDA graph: the number of cached positions is read
+// from device memory (the graph is replayed with a growing cache), and the new token's key/value are taken
+// from the projection output and written into the cache by the block that owns the last position, so that
+// the append needs no launch of its own.
 #include "sm100_common.cuh"
 
 namespace msq {
@@ -23,12 +28,18 @@ __global__ void __launch_bounds__(DEC_THREADS)
 decode_attn_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ kc, const uint16_t* __restrict__ vc,
                    uint16_t* __restrict__ out, const uint8_t* __restrict__ mask, int S, long long q_bs, long long kv_rs,
                    long long kv_bs, long long o_bs, long long mask_bs, float scale_log2, int splits,
-                   float* __restrict__ ws) {
+                   float* __restrict__ ws, const int* __restrict__ len_ptr, const uint16_t* __restrict__ k_new,
+                   const uint16_t* __restrict__ v_new, long long new_bs, int capacity) {
   constexpr int G = HD / 8;    // lanes per key
   constexpr int KPW = 32 / G;  // keys per warp and iteration
   const int h = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int sub = lane / G, part = lane % G;
+  int fresh = -1;  // index of the position whose key/value still sit in the projection output
+  if (len_ptr) {
+    S = min(*len_ptr + 1, capacity);
+    fresh = S - 1;
+  }
   const int chunk = (S + splits - 1) / splits;
   const int s0 = split * chunk, s1 = min(S, s0 + chunk);
 
@@ -51,12 +62,19 @@ decode_attn_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ 
   const uint8_t* mb = mask ? mask + b * mask_bs : nullptr;
   // warp-uniform trip count: the shuffles below are executed by all 32 lanes in every iteration
   for (int base = s0 + warp * KPW; base < s1; base += (DEC_THREADS / 32) * KPW) {
-    const int s = base + sub;
+    const long long s = base + sub;
     const bool valid = s < s1;
     uint4 kv4 = make_uint4(0u, 0u, 0u, 0u), vv4 = make_uint4(0u, 0u, 0u, 0u);
     if (valid) {
-      kv4 = *reinterpret_cast<const uint4*>(kb + s * kv_rs);
-      vv4 = *reinterpret_cast<const uint4*>(vb + s * kv_rs);
+      if (s == fresh) {
+        kv4 = *reinterpret_cast<const uint4*>(k_new + b * new_bs + h * HD + part * 8);
+        vv4 = *reinterpret_cast<const uint4*>(v_new + b * new_bs + h * HD + part * 8);
+        *reinterpret_cast<uint4*>(const_cast<uint16_t*>(kb) + s * kv_rs) = kv4;
+        *reinterpret_cast<uint4*>(const_cast<uint16_t*>(vb) + s * kv_rs) = vv4;
+      } else {
+        kv4 = *reinterpret_cast<const uint4*>(kb + s * kv_rs);
+        vv4 = *reinterpret_cast<const uint4*>(vb + s * kv_rs);
+      }
     }
     const uint32_t kw[4] = {kv4.x, kv4.y, kv4.z, kv4.w};
     float dot = 0.f;
@@ -151,12 +169,14 @@ __global__ void decode_attn_merge_kernel(const float* __restrict__ ws, uint16_t*
 template <int HD, bool BF16>
 static int launch_decode(const void* q, const void* kc, const void* vc, void* out, const void* mask, int B, int H, int S,
                          long long q_bs, long long kv_rs, long long kv_bs, long long o_bs, long long mask_bs, float scale,
-                         int splits, float* ws, cudaStream_t stream) {
+                         int splits, float* ws, cudaStream_t stream, const int* len_ptr = nullptr,
+                         const void* k_new = nullptr, const void* v_new = nullptr, long long new_bs = 0, int capacity = 0) {
   dim3 grid(H, B, splits);
   decode_attn_kernel<HD, BF16><<<grid, DEC_THREADS, 0, stream>>>(
       static_cast<const uint16_t*>(q), static_cast<const uint16_t*>(kc), static_cast<const uint16_t*>(vc),
       static_cast<uint16_t*>(out), static_cast<const uint8_t*>(mask), S, q_bs, kv_rs, kv_bs, o_bs, mask_bs,
-      scale * DEC_LOG2E, splits, ws);
+      scale * DEC_LOG2E, splits, ws, len_ptr, static_cast<const uint16_t*>(k_new), static_cast<const uint16_t*>(v_new),
+      new_bs, capacity);
   if (splits > 1) {
     dim3 g2(H, B);
     decode_attn_merge_kernel<HD, BF16><<<g2, HD, 0, stream>>>(ws, static_cast<uint16_t*>(out), o_bs, splits);
@@ -195,6 +215,32 @@ extern "C" int msq_decode_attn(const void* q, const void* kc, const void* vc, vo
   if (splits > 1 && !workspace) return -3;
 #define MSQ_DEC(HDV, BF) \
   return launch_decode<HDV, BF>(q, kc, vc, out, mask, B, H, S, q_bs, kv_rs, kv_bs, o_bs, mask_bs, scale, splits, workspace, stream)
+  if (HD == 64) { if (bf16) MSQ_DEC(64, true); else MSQ_DEC(64, false); }
+  if (bf16) MSQ_DEC(128, true); else MSQ_DEC(128, false);
+#undef MSQ_DEC
+}
+
+// Decode step with the cache length on the device: ``*len_ptr`` positions are cached; the new token's key and
+// value (rows of ``k_new`` / ``v_new``, batch stride ``new_bs``) become position ``*len_ptr``, are written into
+// the cache (row capacity ``capacity``) and take part in the attention.  The caller increments ``*len_ptr``
+// afterwards.  ``s_hint`` (a host estimate of the length) only sizes the sequence split.
+extern "C" int msq_decode_attn_step(const void* q, const void* k_new, const void* v_new, long long new_bs, void* kc, void* vc,
+                                    void* out, const void* mask, int B, int H, int HD, const int* len_ptr, int capacity,
+                                    long long q_bs, long long kv_rs, long long kv_bs, long long o_bs, long long mask_bs,
+                                    float scale, int bf16, float* workspace, int splits, cudaStream_t stream) {
+  using namespace msq;
+  if (B <= 0 || H <= 0 || capacity <= 0) return 0;
+  if (HD != 64 && HD != 128) return -4;
+  if (!len_ptr || !k_new || !v_new) return -5;
+  if ((q_bs & 7) || (kv_rs & 7) || (kv_bs & 7) || (new_bs & 7) || (reinterpret_cast<uintptr_t>(q) & 15) ||
+      (reinterpret_cast<uintptr_t>(kc) & 15) || (reinterpret_cast<uintptr_t>(vc) & 15) ||
+      (reinterpret_cast<uintptr_t>(k_new) & 15) || (reinterpret_cast<uintptr_t>(v_new) & 15))
+    return -2;
+  if (splits < 1) splits = 1;
+  if (splits > 1 && !workspace) return -3;
+#define MSQ_DEC(HDV, BF) \
+  return launch_decode<HDV, BF>(q, kc, vc, out, mask, B, H, 0, q_bs, kv_rs, kv_bs, o_bs, mask_bs, scale, splits, workspace, \
+                                stream, len_ptr, k_new, v_new, new_bs, capacity)
   if (HD == 64) { if (bf16) MSQ_DEC(64, true); else MSQ_DEC(64, false); }
   if (bf16) MSQ_DEC(128, true); else MSQ_DEC(128, false);
 #undef MSQ_DEC

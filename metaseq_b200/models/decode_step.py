@@ -1,0 +1,186 @@
+"""One-token decode step of a ``TransformerDecoder`` replayed from a CUDA graph.
+
+The reference decodes through the module tree, one Python call per op and per layer, with the key/value
+cache grown by ``torch.cat`` every step (metaseq/sequence_generator.py:246-330,
+metaseq/modules/multihead_attention.py:428-476).  At one token per sequence the device work of a step is a
+few hundred short kernels, so a step costs what the host needs to launch them.  Here the whole step —
+embedding, every layer, the final norm and the vocabulary projection — is captured once per batch size and
+replayed with one launch:
+
+* the key/value caches are preallocated and owned by the step object, so their addresses are constants of
+  the graph; they are handed to the prefill through the usual ``incremental_state`` dictionary;
+* everything that changes from step to step lives in device memory: the token ids, the running count of
+  non-padding tokens (learned positions), and the number of cached positions, which the attention kernel reads
+  and which the graph itself increments;
+* the append of the new key/value rows happens inside the attention kernel.
+
+Restrictions (the caller falls back to the module path otherwise): one tensor-parallel rank, 16-bit weights on
+a GPU, pre-norm layers with ReLU or GELU, head size 64 or 128, no document-separator attention.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from metaseq_b200.modules.multihead_attention import KVCache
+from metaseq_b200.modules.transformer_decoder_layer import ModelParallelTransformerDecoderLayer as TransformerDecoderLayer
+from metaseq_b200.ops import functional as F
+from metaseq_b200.parallel import mpu
+
+_MAX_CACHED_STEPS = 2
+
+
+def _tp_world() -> int:
+    try:
+        return mpu.get_tensor_model_parallel_world_size()
+    except Exception:
+        return 1
+
+
+class GraphedDecodeStep:
+    """Static buffers, caches and the captured graph for ``rows`` sequences decoded together."""
+
+    @staticmethod
+    def supported(decoder) -> bool:
+        from metaseq_b200.models.transformer_decoder import UNSPECIFIED_DOC_SEP
+
+        w = decoder.embed_tokens.weight
+        if not (w.is_cuda and w.dtype in (torch.float16, torch.bfloat16) and F.use_kernels(w)):
+            return False
+        if _tp_world() != 1 or decoder.training or decoder.sequence_parallel:
+            return False
+        if decoder.self_attn_doc_sep != UNSPECIFIED_DOC_SEP or w.shape[1] % 8 != 0:
+            return False
+        if decoder.embed_positions is not None and not hasattr(decoder.embed_positions, "weight"):
+            return False
+        if decoder.layer_norm is None or decoder.layer_norm.weight is None \
+                or decoder.output_projection.weight.dtype != w.dtype:
+            return False
+        for layer in decoder.layers:
+            if not isinstance(layer, TransformerDecoderLayer):
+                return False
+            a = layer.self_attn
+            if layer.activation_name not in ("relu", "gelu") or a.head_dim not in (64, 128):
+                return False
+            for lin in (a.qkv_proj, a.out_proj, layer.fc1, layer.fc2):
+                if lin.weight.dtype != w.dtype or lin.weight.shape[0] % 8 or lin.weight.shape[1] % 8:
+                    return False
+            if layer.self_attn_layer_norm.weight is None or layer.self_attn_layer_norm.weight.dtype != w.dtype:
+                return False
+        return True
+
+    @classmethod
+    def for_decoder(cls, decoder, rows: int, min_capacity: int) -> "GraphedDecodeStep":
+        """The step object for this batch size with room for ``min_capacity`` positions, kept on the decoder
+        (the newest few sizes only: each holds a full set of caches)."""
+        table: Dict[int, GraphedDecodeStep] = decoder.__dict__.setdefault("_graphed_decode_steps", {})
+        step = table.pop(rows, None)
+        if step is not None and step.capacity < min_capacity:
+            step = None
+        if step is None:
+            while len(table) >= _MAX_CACHED_STEPS:
+                table.pop(next(iter(table)))
+            limit = int(decoder.max_positions()) + 2
+            step = cls(decoder, rows, min(limit, max(min_capacity, -(-min_capacity // 256) * 256)))
+        table[rows] = step  # most recently used last
+        return step
+
+    def __init__(self, decoder, rows: int, capacity: int):
+        self.decoder = decoder
+        self.rows = rows
+        w = decoder.embed_tokens.weight
+        self.device, self.dtype = w.device, w.dtype
+        self.capacity = int(capacity)
+        self.pad = int(decoder.padding_idx)
+        self.caches: List[KVCache] = []
+        for layer in decoder.layers:
+            width = layer.self_attn.num_heads_partition * layer.self_attn.head_dim
+            self.caches.append(KVCache(rows, self.capacity, width, self.dtype, self.device))
+        self.tok = torch.zeros(rows, dtype=torch.long, device=self.device)
+        self.count = torch.zeros(rows, dtype=torch.long, device=self.device)  # non-padding tokens so far
+        self.length = torch.zeros(1, dtype=torch.int32, device=self.device)  # cached positions
+        self.logits: Optional[torch.Tensor] = None
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self._length_hint = 1
+
+    # ------------------------------------------------------------------ state
+    def new_state(self) -> Dict:
+        """An ``incremental_state`` whose caches are the ones the graph addresses, emptied."""
+        state: Dict = {}
+        for layer, cache in zip(self.decoder.layers, self.caches):
+            cache.length = 0
+            state[layer.self_attn._cache_key] = cache
+        return state
+
+    def begin(self, prefix_tokens: torch.Tensor) -> None:
+        """Call after the prefill over ``prefix_tokens`` ``[rows, T]`` went through the caches."""
+        assert prefix_tokens.shape[0] == self.rows
+        self.count.copy_(prefix_tokens.ne(self.pad).sum(dim=1))
+        filled = self.caches[0].length
+        assert filled == prefix_tokens.shape[1] and all(c.length == filled for c in self.caches)
+        self.length.fill_(filled)
+        self._length_hint = max(1, filled)
+
+    # ------------------------------------------------------------------- step
+    def _run(self) -> torch.Tensor:
+        dec = self.decoder
+        tok = self.tok
+        nonpad = tok.ne(self.pad)
+        self.count.add_(nonpad)
+        pos_w = dec.embed_positions.weight if dec.embed_positions is not None else None
+        positions = torch.where(nonpad, self.count + self.pad, torch.full_like(self.count, self.pad)) \
+            if pos_w is not None else None
+        x = F.embed_fwd(tok, positions, dec.embed_tokens.weight, pos_w, dec.embed_scale)
+        for layer, cache in zip(dec.layers, self.caches):
+            a = layer.self_attn
+            ln1, ln2 = layer.self_attn_layer_norm, layer.final_layer_norm
+            h, _, _ = F.layer_norm_fwd(x, ln1.weight, ln1.bias, ln1.eps)
+            qkv = F.gemm(h, a.qkv_proj.weight, bias=a.qkv_proj.bias)  # (k | v | q) per row
+            dp = qkv.shape[1] // 3
+            ctx = F.decode_attn_step(qkv[:, 2 * dp:], qkv[:, 0:dp], qkv[:, dp:2 * dp], cache.k, cache.v, self.length,
+                                     a.num_heads_partition, a.scaling, self._length_hint)
+            x = F.gemm(ctx, a.out_proj.weight, bias=a.out_proj.bias, residual=x)
+            h, _, _ = F.layer_norm_fwd(x, ln2.weight, ln2.bias, ln2.eps)
+            if layer.activation_name == "relu":
+                f = F.gemm(h, layer.fc1.weight, bias=layer.fc1.bias, relu=True)
+            else:
+                f = torch.nn.functional.gelu(F.gemm(h, layer.fc1.weight, bias=layer.fc1.bias).float()).to(h.dtype)
+            x = F.gemm(f, layer.fc2.weight, bias=layer.fc2.bias, residual=x)
+        fl = dec.layer_norm
+        x, _, _ = F.layer_norm_fwd(x, fl.weight, fl.bias, fl.eps)
+        logits = F.gemm(x, dec.output_projection.weight)
+        self.length.add_(1)
+        return logits
+
+    def _capture(self) -> None:
+        # Warm up on a side stream (lazy initialisation of libraries must not happen under capture), then
+        # restore the device-side state that the warm-up advanced.
+        saved = (self.count.clone(), self.length.clone())
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            self._run()
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        self.count.copy_(saved[0])
+        self.length.copy_(saved[1])
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self.logits = self._run()
+        # the capture itself executes nothing, so the state is still the restored one
+        self.graph = graph
+
+    @torch.no_grad()
+    def step(self, new_tokens: torch.Tensor) -> torch.Tensor:
+        """Feeds one token per row; returns the ``[rows, V]`` logits (a buffer reused by the next step)."""
+        filled = self.caches[0].length
+        if filled + 1 > self.capacity:
+            raise RuntimeError(f"decode step beyond the cache capacity of {self.capacity} positions")
+        self.tok.copy_(new_tokens)
+        if self.graph is None:
+            self._capture()
+        self.graph.replay()
+        for cache in self.caches:
+            cache.length = filled + 1
+        return self.logits

@@ -135,6 +135,7 @@ def _declare_kernels(lib):
 _OPTIONAL = {
     "msq_decode_attn": [P, P, P, P, P, I, I, I, I, L, L, L, L, L, F, I, P, I, P],
     "msq_decode_attn_splits": [I, I, I],
+    "msq_decode_attn_step": [P, P, P, L, P, P, P, P, I, I, I, P, I, L, L, L, L, L, F, I, P, I, P],
     "msq_attn_set_dropout": [F, ctypes.c_ulonglong],
     "msq_dropout_add": [P, L, P, P, L, P, L, L, I, F, ctypes.c_ulonglong, I, P],
     "msq_vp_ce_partial": [P, L, P, P, I, I, L, I, P],

@@ -565,6 +565,29 @@ def decode_attn(q, k_cache, v_cache, length: int, num_heads: int, scale: float, 
     return torch.matmul(probs, v).transpose(1, 2).reshape(B, 1, D).to(q.dtype)
 
 
+def decode_attn_step(q, k_new, v_new, k_cache, v_cache, length_dev, num_heads: int, scale: float, length_hint: int):
+    """One decode step with the cache length held on the device (usable inside a CUDA graph).
+
+    ``q`` / ``k_new`` / ``v_new``: ``[B, H*d]`` row views (last dim contiguous, equal batch strides for the two
+    new rows); ``k_cache`` / ``v_cache``: ``[B, Tmax, H*d]``; ``length_dev``: int32 tensor with the number of
+    cached positions.  The new key/value become position ``length_dev`` of the cache and take part in the
+    attention; the caller adds one to ``length_dev`` afterwards.  ``length_hint`` (host) sizes the sequence
+    split only.  Kernel-only: there is no PyTorch restatement because the point is the absence of host state."""
+    B, D = q.shape
+    d = D // num_heads
+    assert k_new.stride(0) == v_new.stride(0) and k_cache.stride() == v_cache.stride()
+    lib = _lib.kernels()
+    out = torch.empty((B, D), dtype=q.dtype, device=q.device)
+    splits = lib.msq_decode_attn_splits(B, num_heads, max(1, length_hint))
+    ws = torch.empty((B * num_heads * splits * (d + 2),), dtype=torch.float32, device=q.device) if splits > 1 else None
+    rc = lib.msq_decode_attn_step(_lib.ptr(q), _lib.ptr(k_new), _lib.ptr(v_new), k_new.stride(0), _lib.ptr(k_cache),
+                                  _lib.ptr(v_cache), _lib.ptr(out), None, B, num_heads, d, _lib.ptr(length_dev),
+                                  k_cache.shape[1], q.stride(0), k_cache.stride(1), k_cache.stride(0), out.stride(0), 0,
+                                  float(scale), _bf(q), _lib.ptr(ws), splits, _lib.stream_ptr())
+    _lib.check_rc(rc, "msq_decode_attn_step")
+    return out
+
+
 # -------------------------------------------------------------- cross entropy
 def cross_entropy_fwd_bwd(logits2d, target, ignore_index: int, grad_scale: float, write_grad: bool):
     """Per-row NLL (fp32, 0 where ``target == ignore_index``) and log-sum-exp.  With

@@ -21,6 +21,8 @@ import torch
 import torch.nn as nn
 from torch import Tensor
 
+from metaseq_b200.models.decode_step import GraphedDecodeStep
+
 logger = logging.getLogger(__name__)
 
 
@@ -30,8 +32,9 @@ class SequenceGenerator(nn.Module):
                  stop: Optional[List[int]] = None, topp: float = -1, profile: bool = False,
                  omega_bound: float = 0.3, lambda_decay: float = -1, alpha_presence: float = 0.0,
                  alpha_frequency: float = 0.0, alpha_presence_src: float = 0.0, alpha_frequency_src: float = 0.0,
-                 alpha_src_penalty_end_idx: int = -1, eos_check_interval: int = 1):
+                 alpha_src_penalty_end_idx: int = -1, eos_check_interval: int = 1, decode_graph: bool = True):
         super().__init__()
+        self.decode_graph = decode_graph  # replay the one-token step from a CUDA graph where the model allows it
         self.model = models[0] if isinstance(models, (list, tuple)) else models
         self.tgt_dict = tgt_dict
         self.pad = tgt_dict.pad()
@@ -99,8 +102,15 @@ class SequenceGenerator(nn.Module):
 
         start = src_len
         tokens[:, :start] = src_tokens.repeat_interleave(K, 0)
+        graphed = None
+        decoder = getattr(self.model, "decoder", None)
+        if self.decode_graph and decoder is not None and max_len > start and GraphedDecodeStep.supported(decoder):
+            graphed = GraphedDecodeStep.for_decoder(decoder, n, max_len)
+            state = graphed.new_state()
         # ---------------------------------------------------------- prefill
         logits, _ = self.model(tokens[:, :start], incremental_state=state)
+        if graphed is not None:
+            graphed.begin(tokens[:, :start])
         lp_all = self._logprobs(logits)  # [n, start, V]
         if all_lprobs is not None:
             all_lprobs[:, 1:start] = lp_all[:, :-1]
@@ -149,8 +159,11 @@ class SequenceGenerator(nn.Module):
                 break
             if step + 1 >= max_len:
                 break
-            logits, _ = self.model.decoder(tokens[:, : step + 1], incremental_state=state)
-            lprobs = self._logprobs(logits[:, -1, :])
+            if graphed is not None:
+                lprobs = self._logprobs(graphed.step(tokens[:, step]))
+            else:
+                logits, _ = self.model.decoder(tokens[:, : step + 1], incremental_state=state)
+                lprobs = self._logprobs(logits[:, -1, :])
         # ------------------------------------------------- order the samples
         total = scores.view(bsz, K, -1).sum(dim=-1)
         order = total.sort(dim=-1, descending=True).indices

@@ -331,6 +331,31 @@ def test_decode_attention_kv_cache(dtype, B, H, d, S, Tmax, masked):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("B,H,d,S,Tmax", [(2, 4, 64, 37, 64), (16, 32, 64, 999, 1024), (1, 8, 128, 2047, 2050), (3, 2, 128, 0, 8)])
+def test_decode_attention_step_appends_and_attends(dtype, B, H, d, S, Tmax):
+    """Device-side length: the new key/value rows land at position ``S`` of the cache and the result equals
+    attention over ``S + 1`` positions."""
+    g = torch.Generator(device="cuda").manual_seed(B * 17 + S)
+    D = H * d
+    qkv = torch.randn(B, 3 * D, device="cuda", dtype=dtype, generator=g)
+    kc = torch.randn(B, Tmax, D, device="cuda", dtype=dtype, generator=g)
+    vc = torch.randn(B, Tmax, D, device="cuda", dtype=dtype, generator=g)
+    k_ref, v_ref = kc.clone(), vc.clone()
+    k_ref[:, S] = qkv[:, 0:D]
+    v_ref[:, S] = qkv[:, D:2 * D]
+    length = torch.tensor([S], dtype=torch.int32, device="cuda")
+    out = F.decode_attn_step(qkv[:, 2 * D:], qkv[:, 0:D], qkv[:, D:2 * D], kc, vc, length, H, d ** -0.5, max(1, S))
+    assert torch.equal(kc, k_ref) and torch.equal(vc, v_ref)
+    F.set_backend("torch")
+    try:
+        ref = F.decode_attn(qkv[:, None, 2 * D:].float(), k_ref.float(), v_ref.float(), S + 1, H, d ** -0.5, None)
+    finally:
+        F.set_backend("auto")
+    tol = 2e-2 if dtype == torch.bfloat16 else 4e-3
+    assert torch.allclose(out.float(), ref[:, 0].float(), rtol=tol, atol=tol), (out.float() - ref[:, 0].float()).abs().max()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 def test_dropout_add_matches_hash_reference(dtype):
     g = torch.Generator(device="cuda").manual_seed(1)
     rows, cols = 777, 1024

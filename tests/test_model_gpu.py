@@ -169,3 +169,53 @@ def test_fused_layer_with_dropout_kernels_match_reference_masks():
     for a, b in zip(*losses):
         assert abs(a - b) <= 2e-2 * abs(b), losses
     assert losses[0][2] < losses[0][0]
+
+
+def test_graphed_decode_step_matches_module_path():
+    """The CUDA-graph replay of the one-token step gives the logits of the module path (which gives those of a
+    full forward), over several steps, with padding inside the prompt batch, and again after the step object
+    is reused for a second prompt batch."""
+    from metaseq_b200.models.decode_step import GraphedDecodeStep
+
+    cfg = _cfg(fsdp=False, extra=["--activation-fn", "relu"])
+    tr, batch = _trainer(cfg)
+    model = tr.get_model().eval()
+    dec = model.decoder
+    assert GraphedDecodeStep.supported(dec)
+    pad = dec.padding_idx
+    for trial in range(2):
+        tokens = torch.randint(4, 50272, (3, 48), device="cuda")
+        tokens[1, 20:24] = pad  # a hole: positions stop counting there
+        with torch.no_grad():
+            full, _ = model(tokens)
+            runner = GraphedDecodeStep.for_decoder(dec, 3, 64)
+            state = runner.new_state()
+            model(tokens[:, :32], incremental_state=state)
+            runner.begin(tokens[:, :32])
+            for t in range(32, 47):
+                logits = runner.step(tokens[:, t])
+                torch.testing.assert_close(logits.float(), full[:, t].float(), rtol=5e-2, atol=5e-2)
+        assert runner.caches[0].length == 47 and int(runner.length.item()) == 47
+        assert GraphedDecodeStep.for_decoder(dec, 3, 64) is runner
+    assert _lib.check_status(torch.device("cuda")) == 0
+
+
+def test_sequence_generator_with_decode_graph_matches_module_loop():
+    from metaseq_b200.sequence_generator import SequenceGenerator
+
+    cfg = _cfg(fsdp=False, extra=["--activation-fn", "relu"])
+    tr, batch = _trainer(cfg)
+    model = tr.get_model().eval()
+    d = tr.task.target_dictionary
+    src = torch.randint(10, 50000, (4, 24), device="cuda")
+    outs = []
+    for graph in (True, False):
+        sg = SequenceGenerator([model], d, beam_size=1, max_len_b=56, min_len=56, temperature=1.0, topp=-1,
+                               decode_graph=graph)
+        outs.append(sg.generate([model], {"net_input": {"src_tokens": src}}))
+    a, b = outs
+    # greedy on random weights: near-ties may flip a token, after which the continuations differ; compare up to
+    # the first difference and require most of the sequence to agree
+    same = (a["tokens"] == b["tokens"]).long().cumprod(-1).sum(-1).float().mean().item()
+    assert same >= 0.8 * a["tokens"].shape[-1], same
+    torch.testing.assert_close(a["scores"][..., :25], b["scores"][..., :25], rtol=5e-2, atol=5e-2)
