@@ -1,0 +1,330 @@
+// Linear layer for a handful of rows (one decode step):  C[M,N] = epilogue(X[M,K] * W[N,K]^T),  M <= 64.
+//
+// With so few rows the product is a single pass over the weight matrix, so the kernel is built to stream W at
+// memory speed rather than to fill the tensor cores:
+//
+//   * operands are swapped: a tile is 128 rows of W (the tcgen05 "M" side) against all rows of X padded to
+//     16 / 32 / 64 (the "N" side), so no tensor-core lanes or shared memory are spent on padding of X to 128;
+//   * the K range of a tile is split over the CTAs of a thread-block cluster (1, 2, 4 or 8), which gives
+//     every SM a slice of W to fetch even when N / 128 is far below the SM count (out-projection, fc2);
+//   * the cluster adds the partial products through distributed shared memory: each CTA parks its fp32
+//     partial tile in its own shared memory, and after a cluster barrier CTA c sums rows [c*128/S, (c+1)*128/S)
+//     over all peers and applies the epilogue (+bias -> ReLU -> +residual).  No workspace, no atomics, and the
+//     result does not depend on the order in which CTAs finish;
+//   * shared memory stays near 100 KB so that two CTAs share an SM and about 200 KB of loads are in flight
+//     per SM.
+//
+// The reference runs these products as torch.matmul plus separate bias / activation / residual kernels
+// (metaseq/modules/megatron/mpu/layers.py:290,373; metaseq/modules/feedforward.py:21-22).
+//
+// Roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner, warps 2..5 move the
+// accumulator to shared memory; all threads take part in the cluster reduction.
+#include <cstdio>
+
+#include "sm100_common.cuh"
+
+namespace msq {
+
+int make_tmap_2d(CUtensorMap* out, const void* base, long long rows, long long cols, long long ld, int box_rows,
+                 int bf16);  // gemm_sm100.cu
+
+struct SkinnyParams {
+  int M, N, K;
+  int k_blocks_per_cta;
+  int split;  // cluster size along K
+  void* C;
+  long long ldc;
+  const void* bias;      // [N] or null
+  const void* residual;  // [M, ldr] or null
+  long long ldr;
+  int relu;
+  int bf16;
+  int* status;
+};
+
+constexpr int SK_BM = 128;  // rows of W per tile
+constexpr int SK_BK = 64;
+constexpr int SK_THREADS = 192;
+
+template <int MP>
+struct SkinnyCfg {
+  static constexpr uint32_t W_BYTES = SK_BM * SK_BK * 2;
+  static constexpr uint32_t X_BYTES = MP * SK_BK * 2;
+  static constexpr int STAGES = (MP == 64) ? 4 : 5;
+  static constexpr uint32_t PARTIAL_BYTES = SK_BM * MP * 4;  // reuses the stage memory
+  static constexpr uint32_t SMEM = STAGES * (W_BYTES + X_BYTES) + 1024 /*align slack*/ + 256 /*barriers*/;
+  static constexpr uint32_t TMEM_COLS = MP < 32 ? 32 : MP;
+  static_assert(PARTIAL_BYTES <= STAGES * W_BYTES, "partial tile must fit in the stage memory");
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float2 ld_peer_f2(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  float2 v;
+  asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(remote) : "memory");
+  return v;
+}
+
+template <int MP>
+__global__ void __launch_bounds__(SK_THREADS, 2)
+gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
+                   const SkinnyParams p) {
+  using Cfg = SkinnyCfg<MP>;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sW = smem;
+  uint8_t* sX = smem + STAGES * Cfg::W_BYTES;
+  float* partial = reinterpret_cast<float*>(smem);  // [MP][128] after the main loop
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(sX + STAGES * Cfg::X_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tfull_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t crank = cluster_ctarank();
+  const int tile = blockIdx.x / p.split;
+  const int n0 = tile * SK_BM;
+  const int total_kb = (p.K + SK_BK - 1) / SK_BK;
+  const int kb0 = static_cast<int>(crank) * p.k_blocks_per_cta;
+  const int kb1 = min(total_kb, kb0 + p.k_blocks_per_cta);
+  const int my_kb = max(0, kb1 - kb0);
+
+  // A wait that ran out earlier on this stream left its code in the status word: do no work until the host has
+  // read and cleared it.  The CTA still walks through the cluster barriers below, because its peers may have
+  // read the word before it was set and will address this CTA's shared memory.
+  const bool skip = p.status && *reinterpret_cast<volatile int*>(p.status) != 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(tfull_bar, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    fence_proxy_async_smem();
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmX);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (!skip && my_kb > 0) {
+    if (warp == 0) {
+      // ---------------------------------------------------------- producer
+      if (lane == 0) {
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, ST_TIMEOUT_SMEM_EMPTY);
+          if (!ok) break;
+          mbar_expect_tx(&full_bar[stage], Cfg::W_BYTES + Cfg::X_BYTES);
+          tma_load_2d(sW + stage * Cfg::W_BYTES, &tmW, &full_bar[stage], kb * SK_BK, n0);
+          tma_load_2d(sX + stage * Cfg::X_BYTES, &tmX, &full_bar[stage], kb * SK_BK, 0);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) {
+          // Leaving early: give the copies already issued a bounded time to land before the stage memory is
+          // reused for the partial tile.
+          const unsigned long long t0 = globaltimer_ns();
+          while (globaltimer_ns() - t0 < 2000000ull) { }
+        }
+      }
+    } else if (warp == 1) {
+      // -------------------------------------------------------- MMA issuer
+      if (lane == 0) {
+        const uint32_t idesc = make_idesc_f16(p.bf16, 0, 0, SK_BM, MP);
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int i = 0; i < my_kb; ++i) {
+          ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t w_addr = smem_u32(sW + stage * Cfg::W_BYTES);
+          const uint32_t x_addr = smem_u32(sX + stage * Cfg::X_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < SK_BK / 16; ++kk) {
+            const uint64_t dw = make_smem_desc_sw128(w_addr + kk * 32, 16, 1024);
+            const uint64_t dx = make_smem_desc_sw128(x_addr + kk * 32, 16, 1024);
+            tc_mma_f16(tmem_base, dw, dx, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+          }
+          tc_commit(&empty_bar[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) tc_commit(tfull_bar);
+      }
+    } else {
+      // ------------------------------------- accumulator -> shared memory
+      const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) = rows of the W tile
+      if (mbar_wait_warp(tfull_bar, 0, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) {
+        tc_fence_after();
+        const int r = quarter * 32 + lane;
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll
+        for (int c = 0; c < MP / 16; ++c) {
+          uint32_t v[16];
+          tmem_ld_32x16(taddr + c * 16, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) partial[(c * 16 + j) * SK_BM + r] = __uint_as_float(v[j]);
+        }
+      }
+    }
+  } else if (warp >= 2) {
+    // no K range (or skipping): contribute zeros
+    const int r = (warp & 3) * 32 + lane;
+    for (int m = 0; m < MP; ++m) partial[m * SK_BM + r] = 0.f;
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+  cluster_sync_all();  // every CTA's partial tile is complete and visible
+
+  if (!skip) {
+    // CTA `crank` finishes rows [crank*R, crank*R + R) of the tile, two adjacent rows (= output columns) per item.
+    const int R = SK_BM / p.split;
+    const int half = R >> 1;
+    const int items = half * p.M;
+    const uint32_t partial_addr = smem_u32(partial);
+    for (int e = threadIdx.x; e < items; e += SK_THREADS) {
+      const int m = e / half;
+      const int rl = (e - m * half) * 2;
+      const int r = static_cast<int>(crank) * R + rl;
+      const int n = n0 + r;
+      if (n >= p.N) continue;  // N is even, so a pair is inside or outside as a whole
+      const uint32_t addr = partial_addr + static_cast<uint32_t>(m * SK_BM + r) * 4u;
+      float2 acc = make_float2(0.f, 0.f);
+      for (int j = 0; j < p.split; ++j) {
+        const float2 v = ld_peer_f2(addr, static_cast<uint32_t>(j));
+        acc.x += v.x;
+        acc.y += v.y;
+      }
+      if (p.bias) {
+        const uint32_t bw = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(p.bias) + n);
+        const float2 b2 = p.bf16 ? unpack2<true>(bw) : unpack2<false>(bw);
+        acc.x += b2.x;
+        acc.y += b2.y;
+      }
+      if (p.relu) {
+        acc.x = fmaxf(acc.x, 0.f);
+        acc.y = fmaxf(acc.y, 0.f);
+      }
+      if (p.residual) {
+        const uint32_t rw = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(p.residual) +
+                                                               static_cast<long long>(m) * p.ldr + n);
+        const float2 r2 = p.bf16 ? unpack2<true>(rw) : unpack2<false>(rw);
+        acc.x += r2.x;
+        acc.y += r2.y;
+      }
+      uint32_t* dst = reinterpret_cast<uint32_t*>(reinterpret_cast<uint16_t*>(p.C) + static_cast<long long>(m) * p.ldc + n);
+      *dst = p.bf16 ? pack2<true>(acc.x, acc.y) : pack2<false>(acc.x, acc.y);
+    }
+  }
+  __syncthreads();     // reconverge every warp before the aligned cluster barrier
+  cluster_sync_all();  // no CTA leaves while a peer may still read its shared memory
+}
+
+static int g_skinny_sms = 0;
+
+template <int MP>
+static int launch_skinny(const CUtensorMap& tmW, const CUtensorMap& tmX, const SkinnyParams& p, cudaStream_t stream) {
+  using Cfg = SkinnyCfg<MP>;
+  auto kern = gemm_skinny_kernel<MP>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) != cudaSuccess) return -10;
+    configured = true;
+  }
+  const int tiles = (p.N + SK_BM - 1) / SK_BM;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(tiles * p.split), 1, 1);
+  cfg.blockDim = dim3(SK_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(p.split);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kern, tmW, tmX, p) != cudaSuccess) {
+    cudaGetLastError();
+    return -11;
+  }
+  return 0;
+}
+
+}  // namespace msq
+
+// Cluster size along K that the launch will use (exposed for tests and benchmarks).
+extern "C" int msq_gemm_skinny_split(int N, int K) {
+  using namespace msq;
+  if (g_skinny_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&g_skinny_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || g_skinny_sms <= 0)
+      g_skinny_sms = 148;
+  }
+  const int tiles = (N + SK_BM - 1) / SK_BM;
+  const int k_blocks = (K + SK_BK - 1) / SK_BK;
+  const int slots = 2 * g_skinny_sms;  // two CTAs per SM
+  int split = 1;
+  for (int s = 8; s > 1; s >>= 1) {
+    if (tiles * s <= slots && k_blocks >= 2 * s) { split = s; break; }
+  }
+  return split;
+}
+
+// X: [M, K] (row stride ldx), W: [N, K] (row stride ldw), C: [M, N] (row stride ldc), all 16-bit of one type,
+// strides in elements.  M <= 64; K and N multiples of 8; base pointers 16-byte aligned, C / residual / bias 4-byte
+// aligned with even strides.  Returns 0 on a successful launch, a negative code for unsupported arguments.
+extern "C" int msq_gemm_skinny(const void* X, const void* W, void* C, int M, int N, int K, long long ldx, long long ldw,
+                               long long ldc, int bf16, const void* bias, const void* residual, long long ldr, int relu,
+                               int* status, cudaStream_t stream) {
+  using namespace msq;
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 64 || K <= 0 || (N & 7) || (K & 7) || (ldc & 1) || (ldr & 1) || (reinterpret_cast<uintptr_t>(C) & 3) ||
+      (reinterpret_cast<uintptr_t>(residual) & 3) || (reinterpret_cast<uintptr_t>(bias) & 3))
+    return -4;
+  const int mp = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+  CUtensorMap tmW, tmX;
+  int rc = make_tmap_2d(&tmW, W, N, K, ldw, SK_BM, bf16);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tmX, X, M, K, ldx, mp, bf16);
+  if (rc) return rc - 100;
+  SkinnyParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.split = msq_gemm_skinny_split(N, K);
+  const int k_blocks = (K + SK_BK - 1) / SK_BK;
+  p.k_blocks_per_cta = (k_blocks + p.split - 1) / p.split;
+  p.C = C; p.ldc = ldc;
+  p.bias = bias; p.residual = residual; p.ldr = ldr;
+  p.relu = relu; p.bf16 = bf16; p.status = status;
+  if (mp == 16) return launch_skinny<16>(tmW, tmX, p, stream);
+  if (mp == 32) return launch_skinny<32>(tmW, tmX, p, stream);
+  return launch_skinny<64>(tmW, tmX, p, stream);
+}

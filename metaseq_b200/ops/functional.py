@@ -106,6 +106,16 @@ def gemm(
     if use_kernels(a) and K % 8 == 0 and N % 8 == 0 and _gemm_operands_ok(a, b, out, residual, mask) \
             and (bias is None or bias.data_ptr() % 16 == 0):
         lib = _lib.kernels()
+        if M <= 64 and not a_mn and not b_mn and mask is None and not accumulate and bn == 0 and max_ctas == 0 \
+                and _GEMM_VARIANT == "auto" and b_ready is None and getattr(b, "_msq_ready", None) is None \
+                and getattr(a, "_msq_ready", None) is None and out.data_ptr() != (residual.data_ptr() if residual is not None else 0):
+            # a few rows (a decode step): one pass over the weights, K split over a thread-block cluster
+            rc = lib.msq_gemm_skinny(
+                _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), M, N, K, a.stride(0), b.stride(0), out.stride(0), _bf(a),
+                _lib.ptr(bias), _lib.ptr(residual), residual.stride(0) if residual is not None else 0, int(relu),
+                _lib.ptr(_lib.status_word(a.device)), _lib.stream_ptr())
+            _lib.check_rc(rc, "msq_gemm_skinny")
+            return out
         pair = _GEMM_VARIANT == "2cta" or (_GEMM_VARIANT == "auto" and M >= 256 and N >= 128 and bn == 0)
         # Operands that peers are still writing carry a handle.  The kernel can poll one operand: a weight used as B
         # (handle.operand == 0) or a row-gathered activation used as A (handle.operand == 1); anything else is
