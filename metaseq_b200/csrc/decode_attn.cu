@@ -18,6 +18,15 @@ namespace msq {
 
 constexpr int DEC_THREADS = 128;
 constexpr float DEC_LOG2E = 1.4426950408889634f;
+constexpr int DEC_UNROLL = 4;
+
+// 16-byte load of data that is read once per launch: do not keep it in L1.
+__device__ __forceinline__ uint4 ld_stream_16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
 
 struct Partial {
   float m, l;
@@ -35,6 +44,8 @@ decode_attn_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ 
   const int h = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int sub = lane / G, part = lane % G;
+  dependents_launch();
+  dependents_wait();
   int fresh = -1;  // index of the position whose key/value still sit in the projection output
   if (len_ptr) {
     S = min(*len_ptr + 1, capacity);
@@ -60,45 +71,57 @@ decode_attn_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ 
   const uint16_t* kb = kc + b * kv_bs + h * HD + part * 8;
   const uint16_t* vb = vc + b * kv_bs + h * HD + part * 8;
   const uint8_t* mb = mask ? mask + b * mask_bs : nullptr;
-  // warp-uniform trip count: the shuffles below are executed by all 32 lanes in every iteration
-  for (int base = s0 + warp * KPW; base < s1; base += (DEC_THREADS / 32) * KPW) {
-    const long long s = base + sub;
-    const bool valid = s < s1;
-    uint4 kv4 = make_uint4(0u, 0u, 0u, 0u), vv4 = make_uint4(0u, 0u, 0u, 0u);
-    if (valid) {
-      if (s == fresh) {
-        kv4 = *reinterpret_cast<const uint4*>(k_new + b * new_bs + h * HD + part * 8);
-        vv4 = *reinterpret_cast<const uint4*>(v_new + b * new_bs + h * HD + part * 8);
-        *reinterpret_cast<uint4*>(const_cast<uint16_t*>(kb) + s * kv_rs) = kv4;
-        *reinterpret_cast<uint4*>(const_cast<uint16_t*>(vb) + s * kv_rs) = vv4;
-      } else {
-        kv4 = *reinterpret_cast<const uint4*>(kb + s * kv_rs);
-        vv4 = *reinterpret_cast<const uint4*>(vb + s * kv_rs);
+  // warp-uniform trip count: the shuffles below are executed by all 32 lanes in every iteration.  The loads of
+  // DEC_UNROLL iterations are issued before the first of them is used: the kernel is bound by the cache read,
+  // and one key and one value row per thread do not keep enough bytes in flight to fill the memory pipeline.
+  constexpr int STRIDE = (DEC_THREADS / 32) * KPW;
+  for (int base = s0 + warp * KPW; base < s1; base += STRIDE * DEC_UNROLL) {
+    uint4 kq[DEC_UNROLL], vq[DEC_UNROLL];
+#pragma unroll
+    for (int u = 0; u < DEC_UNROLL; ++u) {
+      const long long s = base + u * STRIDE + sub;
+      kq[u] = make_uint4(0u, 0u, 0u, 0u);
+      vq[u] = make_uint4(0u, 0u, 0u, 0u);
+      if (s < s1) {
+        if (s == fresh) {
+          kq[u] = *reinterpret_cast<const uint4*>(k_new + b * new_bs + h * HD + part * 8);
+          vq[u] = *reinterpret_cast<const uint4*>(v_new + b * new_bs + h * HD + part * 8);
+          *reinterpret_cast<uint4*>(const_cast<uint16_t*>(kb) + s * kv_rs) = kq[u];
+          *reinterpret_cast<uint4*>(const_cast<uint16_t*>(vb) + s * kv_rs) = vq[u];
+        } else {
+          kq[u] = ld_stream_16(kb + s * kv_rs);
+          vq[u] = ld_stream_16(vb + s * kv_rs);
+        }
       }
     }
-    const uint32_t kw[4] = {kv4.x, kv4.y, kv4.z, kv4.w};
-    float dot = 0.f;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 f = unpack2<BF16>(kw[j]);
-      dot = fmaf(qv[2 * j], f.x, dot);
-      dot = fmaf(qv[2 * j + 1], f.y, dot);
-    }
-#pragma unroll
-    for (int o = G / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-    if (valid && !(mb && mb[s])) {
-      const float m_new = fmaxf(m, dot);
-      const float alpha = exp2f(m - m_new);
-      const float p = exp2f(dot - m_new);
-      l = l * alpha + p;
-      const uint32_t vw[4] = {vv4.x, vv4.y, vv4.z, vv4.w};
+    for (int u = 0; u < DEC_UNROLL; ++u) {
+      const long long s = base + u * STRIDE + sub;
+      const bool valid = s < s1;
+      const uint32_t kw[4] = {kq[u].x, kq[u].y, kq[u].z, kq[u].w};
+      float dot = 0.f;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const float2 f = unpack2<BF16>(vw[j]);
-        acc[2 * j] = fmaf(acc[2 * j], alpha, p * f.x);
-        acc[2 * j + 1] = fmaf(acc[2 * j + 1], alpha, p * f.y);
+        const float2 f = unpack2<BF16>(kw[j]);
+        dot = fmaf(qv[2 * j], f.x, dot);
+        dot = fmaf(qv[2 * j + 1], f.y, dot);
       }
-      m = m_new;
+#pragma unroll
+      for (int o = G / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      if (valid && !(mb && mb[s])) {
+        const float m_new = fmaxf(m, dot);
+        const float alpha = exp2f(m - m_new);
+        const float p = exp2f(dot - m_new);
+        l = l * alpha + p;
+        const uint32_t vw[4] = {vq[u].x, vq[u].y, vq[u].z, vq[u].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack2<BF16>(vw[j]);
+          acc[2 * j] = fmaf(acc[2 * j], alpha, p * f.x);
+          acc[2 * j + 1] = fmaf(acc[2 * j + 1], alpha, p * f.y);
+        }
+        m = m_new;
+      }
     }
   }
   // merge the lane groups of the warp (they hold different keys, same dimensions)
@@ -150,6 +173,8 @@ decode_attn_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ 
 template <int HD, bool BF16>
 __global__ void decode_attn_merge_kernel(const float* __restrict__ ws, uint16_t* __restrict__ out, long long o_bs, int splits) {
   const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+  dependents_launch();
+  dependents_wait();
   const float* w = ws + (static_cast<long long>(b) * gridDim.x + h) * splits * (HD + 2);
   float mm = -INFINITY;
   for (int s = 0; s < splits; ++s) mm = fmaxf(mm, w[s * (HD + 2) + HD]);
@@ -172,14 +197,15 @@ static int launch_decode(const void* q, const void* kc, const void* vc, void* ou
                          int splits, float* ws, cudaStream_t stream, const int* len_ptr = nullptr,
                          const void* k_new = nullptr, const void* v_new = nullptr, long long new_bs = 0, int capacity = 0) {
   dim3 grid(H, B, splits);
-  decode_attn_kernel<HD, BF16><<<grid, DEC_THREADS, 0, stream>>>(
-      static_cast<const uint16_t*>(q), static_cast<const uint16_t*>(kc), static_cast<const uint16_t*>(vc),
-      static_cast<uint16_t*>(out), static_cast<const uint8_t*>(mask), S, q_bs, kv_rs, kv_bs, o_bs, mask_bs,
-      scale * DEC_LOG2E, splits, ws, len_ptr, static_cast<const uint16_t*>(k_new), static_cast<const uint16_t*>(v_new),
-      new_bs, capacity);
+  launch_chained(decode_attn_kernel<HD, BF16>, grid, dim3(DEC_THREADS), 0, stream, 1u,
+                 static_cast<const uint16_t*>(q), static_cast<const uint16_t*>(kc), static_cast<const uint16_t*>(vc),
+                 static_cast<uint16_t*>(out), static_cast<const uint8_t*>(mask), S, q_bs, kv_rs, kv_bs, o_bs, mask_bs,
+                 scale * DEC_LOG2E, splits, ws, len_ptr, static_cast<const uint16_t*>(k_new),
+                 static_cast<const uint16_t*>(v_new), new_bs, capacity);
   if (splits > 1) {
     dim3 g2(H, B);
-    decode_attn_merge_kernel<HD, BF16><<<g2, HD, 0, stream>>>(ws, static_cast<uint16_t*>(out), o_bs, splits);
+    launch_chained(decode_attn_merge_kernel<HD, BF16>, g2, dim3(HD), 0, stream, 1u, static_cast<const float*>(ws),
+                   static_cast<uint16_t*>(out), o_bs, splits);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

@@ -104,6 +104,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   // read and cleared it.  The CTA still walks through the cluster barriers below, because its peers may have
   // read the word before it was set and will address this CTA's shared memory.
   const bool skip = p.status && *reinterpret_cast<volatile int*>(p.status) != 0;
+  dependents_launch();
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -130,10 +131,20 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     if (warp == 0) {
       // ---------------------------------------------------------- producer
       if (lane == 0) {
-        int stage = 0;
-        uint32_t phase = 0;
+        // The weights are not written by any kernel of the stream, so the first ring of W tiles is requested
+        // before the wait for the preceding kernels; X (their output) follows after it.
+        const int head = min(STAGES, my_kb);
+        for (int i = 0; i < head; ++i) {
+          mbar_expect_tx(&full_bar[i], Cfg::W_BYTES + Cfg::X_BYTES);
+          tma_load_2d(sW + i * Cfg::W_BYTES, &tmW, &full_bar[i], (kb0 + i) * SK_BK, n0);
+        }
+        dependents_wait();
+        for (int i = 0; i < head; ++i)
+          tma_load_2d(sX + i * Cfg::X_BYTES, &tmX, &full_bar[i], (kb0 + i) * SK_BK, 0);
+        int stage = 0;  // head == STAGES whenever the loop below runs
+        uint32_t phase = 1;
         bool ok = true;
-        for (int kb = kb0; kb < kb1; ++kb) {
+        for (int kb = kb0 + head; kb < kb1; ++kb) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, ST_TIMEOUT_SMEM_EMPTY);
           if (!ok) break;
           mbar_expect_tx(&full_bar[stage], Cfg::W_BYTES + Cfg::X_BYTES);
@@ -201,6 +212,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
+  dependents_wait();   // the residual is an output of the preceding kernels, and C may be memory they still read
   cluster_sync_all();  // every CTA's partial tile is complete and visible
 
   if (!skip) {
@@ -216,11 +228,14 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       const int n = n0 + r;
       if (n >= p.N) continue;  // N is even, so a pair is inside or outside as a whole
       const uint32_t addr = partial_addr + static_cast<uint32_t>(m * SK_BM + r) * 4u;
+      float2 part[8];  // all peer loads are issued before the first is used
+#pragma unroll
+      for (int j = 0; j < 8; ++j) part[j] = j < p.split ? ld_peer_f2(addr, static_cast<uint32_t>(j)) : make_float2(0.f, 0.f);
       float2 acc = make_float2(0.f, 0.f);
-      for (int j = 0; j < p.split; ++j) {
-        const float2 v = ld_peer_f2(addr, static_cast<uint32_t>(j));
-        acc.x += v.x;
-        acc.y += v.y;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        acc.x += part[j].x;
+        acc.y += part[j].y;
       }
       if (p.bias) {
         const uint32_t bw = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(p.bias) + n);
@@ -259,24 +274,15 @@ static int launch_skinny(const CUtensorMap& tmW, const CUtensorMap& tmX, const S
     configured = true;
   }
   const int tiles = (p.N + SK_BM - 1) / SK_BM;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>(tiles * p.split), 1, 1);
-  cfg.blockDim = dim3(SK_THREADS, 1, 1);
-  cfg.dynamicSmemBytes = Cfg::SMEM;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = static_cast<unsigned>(p.split);
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, kern, tmW, tmX, p) != cudaSuccess) {
+  if (launch_chained(kern, dim3(static_cast<unsigned>(tiles * p.split), 1, 1), dim3(SK_THREADS, 1, 1), Cfg::SMEM, stream,
+                     static_cast<unsigned>(p.split), tmW, tmX, p) != cudaSuccess) {
     cudaGetLastError();
     return -11;
   }
   return 0;
 }
+
+thread_local int g_dependent_launch = 0;
 
 }  // namespace msq
 
@@ -327,4 +333,13 @@ extern "C" int msq_gemm_skinny(const void* X, const void* W, void* C, int M, int
   if (mp == 16) return launch_skinny<16>(tmW, tmX, p, stream);
   if (mp == 32) return launch_skinny<32>(tmW, tmX, p, stream);
   return launch_skinny<64>(tmW, tmX, p, stream);
+}
+
+// Non-zero: the calling thread's launches of the few-row GEMM, the LayerNorm forward and the decode attention
+// carry the programmatic-dependent-launch attribute, so that each may start (and the GEMM may request its
+// first weight tiles) while its predecessor drains.  Only for call sequences in which the GEMM's W operand is
+// not written by any kernel in flight (a decode step: W are model weights).
+extern "C" int msq_set_dependent_launch(int on) {
+  msq::g_dependent_launch = on ? 1 : 0;
+  return 0;
 }

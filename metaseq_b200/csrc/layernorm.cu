@@ -50,6 +50,8 @@ layernorm_fwd_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict_
     }
   }
   const float inv_d = 1.f / static_cast<float>(D);
+  dependents_launch();
+  dependents_wait();  // gamma / beta above are parameters; x comes from the preceding kernel
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const uint16_t* xr = x + static_cast<long long>(row) * D;
     float f[VPT][8];
@@ -253,9 +255,9 @@ extern "C" int msq_layernorm_fwd(const void* x, const void* gamma, const void* b
   auto B = static_cast<const uint16_t*>(beta);
   auto Y = static_cast<uint16_t*>(y);
   if (bf16) {
-    MSQ_LN_DISPATCH(nvec, (layernorm_fwd_kernel<true, VPT><<<grid, LN_THREADS, 0, stream>>>(X, G, B, Y, mean, rstd, rows, D, eps)))
+    MSQ_LN_DISPATCH(nvec, (launch_chained(layernorm_fwd_kernel<true, VPT>, dim3(grid), dim3(LN_THREADS), 0, stream, 1u, X, G, B, Y, mean, rstd, rows, D, eps)))
   } else {
-    MSQ_LN_DISPATCH(nvec, (layernorm_fwd_kernel<false, VPT><<<grid, LN_THREADS, 0, stream>>>(X, G, B, Y, mean, rstd, rows, D, eps)))
+    MSQ_LN_DISPATCH(nvec, (launch_chained(layernorm_fwd_kernel<false, VPT>, dim3(grid), dim3(LN_THREADS), 0, stream, 1u, X, G, B, Y, mean, rstd, rows, D, eps)))
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

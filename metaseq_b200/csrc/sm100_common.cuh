@@ -42,6 +42,14 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
 
 __device__ __forceinline__ uint32_t lane_id() { return threadIdx.x & 31; }
 
+// Programmatic dependent launch.  A kernel launched with the attribute may start while its predecessor in the
+// stream is still running; `dependents_wait` blocks until every earlier grid has completed and its writes are
+// visible, so everything before it may touch only memory that no earlier kernel of the stream writes (and must
+// write nothing).  `dependents_launch` lets the next such kernel start once every CTA of this grid has issued
+// it.  Both are no-ops in a kernel launched the ordinary way.
+__device__ __forceinline__ void dependents_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void dependents_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred = 0;
   asm volatile(
@@ -404,6 +412,37 @@ typedef CUresult (*TensorMapEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cu
                                            const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
                                            CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
                                            CUtensorMapFloatOOBfill);
+
+// Set per host thread by msq_set_dependent_launch: kernels that support it are launched with the
+// programmatic-stream-serialization attribute (see dependents_wait above).
+extern thread_local int g_dependent_launch;
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                  unsigned cluster_x, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  unsigned n = 0;
+  if (cluster_x > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = cluster_x;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  if (g_dependent_launch) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 inline TensorMapEncodeTiledFn tensor_map_encode_fn() {
   static TensorMapEncodeTiledFn fn = nullptr;

@@ -124,6 +124,10 @@ class GraphedDecodeStep:
 
     # ------------------------------------------------------------------- step
     def _run(self) -> torch.Tensor:
+        with F.dependent_launch():  # every GEMM operand ``b`` below is a model weight
+            return self._run_chain()
+
+    def _run_chain(self) -> torch.Tensor:
         dec = self.decoder
         tok = self.tok
         nonpad = tok.ne(self.pad)

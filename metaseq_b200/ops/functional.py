@@ -575,6 +575,24 @@ def decode_attn(q, k_cache, v_cache, length: int, num_heads: int, scale: float, 
     return torch.matmul(probs, v).transpose(1, 2).reshape(B, 1, D).to(q.dtype)
 
 
+class dependent_launch:
+    """Context in which the few-row GEMM, the LayerNorm forward and the decode attention are launched with
+    programmatic dependent launch: each kernel may start while its predecessor drains, and the GEMM requests its
+    first weight tiles before waiting for it.  Valid only where the ``b`` operands of those GEMMs are not
+    written by kernels in flight (a decode step, where they are the model weights)."""
+
+    def __enter__(self):
+        self._lib = _lib.kernels() if torch.cuda.is_available() and get_backend() != "torch" else None
+        if self._lib is not None:
+            self._lib.msq_set_dependent_launch(1)
+        return self
+
+    def __exit__(self, *exc):
+        if self._lib is not None:
+            self._lib.msq_set_dependent_launch(0)
+        return False
+
+
 def decode_attn_step(q, k_new, v_new, k_cache, v_cache, length_dev, num_heads: int, scale: float, length_hint: int):
     """One decode step with the cache length held on the device (usable inside a CUDA graph).
 

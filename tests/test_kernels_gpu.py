@@ -344,6 +344,40 @@ def test_gemm_few_rows_cluster_split_k(dtype, M, N, K, epilogue):
     _status_ok()
 
 
+def test_dependent_launch_chain_matches_ordinary_launches():
+    """LayerNorm -> GEMM -> GEMM(+residual) chains launched with programmatic dependent launch (eagerly and from a
+    CUDA graph) give the results of ordinary launches: each kernel waits for its predecessor before touching
+    anything but the weights."""
+    torch.manual_seed(3)
+    dt = torch.float16
+    x = torch.randn(32, 2048, device="cuda", dtype=dt)
+    g, b = torch.randn(2048, device="cuda", dtype=dt), torch.randn(2048, device="cuda", dtype=dt)
+    w1 = torch.randn(8192, 2048, device="cuda", dtype=dt) * 0.02
+    w2 = torch.randn(2048, 8192, device="cuda", dtype=dt) * 0.02
+
+    def chain(x):
+        for _ in range(4):
+            h, _, _ = F.layer_norm_fwd(x, g, b, 1e-5)
+            f = F.gemm(h, w1, relu=True)
+            x = F.gemm(f, w2, residual=x)
+        return x
+
+    want = chain(x)
+    with F.dependent_launch():
+        got = chain(x)
+    assert torch.equal(got, want)
+    xs = x.clone()
+    with F.dependent_launch():
+        chain(xs)  # warm-up outside capture
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            out = chain(xs)
+    for _ in range(3):
+        graph.replay()
+    assert torch.equal(out, want)
+    _status_ok()
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("B,H,d,S,Tmax", [(2, 4, 64, 37, 64), (16, 32, 64, 1000, 2050), (1, 8, 128, 2048, 2050), (3, 2, 128, 5, 8)])
 @pytest.mark.parametrize("masked", [False, True])
