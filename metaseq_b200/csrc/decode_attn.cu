@@ -18,7 +18,7 @@ namespace msq {
 
 constexpr int DEC_THREADS = 128;
 constexpr float DEC_LOG2E = 1.4426950408889634f;
-constexpr int DEC_UNROLL = 4;
+constexpr int DEC_UNROLL = 2;
 
 // 16-byte load of data that is read once per launch: do not keep it in L1.
 __device__ __forceinline__ uint4 ld_stream_16(const void* p) {
@@ -33,7 +33,7 @@ struct Partial {
 };
 
 template <int HD, bool BF16>
-__global__ void __launch_bounds__(DEC_THREADS)
+__global__ void __launch_bounds__(DEC_THREADS, 7)
 decode_attn_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ kc, const uint16_t* __restrict__ vc,
                    uint16_t* __restrict__ out, const uint8_t* __restrict__ mask, int S, long long q_bs, long long kv_rs,
                    long long kv_bs, long long o_bs, long long mask_bs, float scale_log2, int splits,
@@ -71,15 +71,14 @@ decode_attn_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ 
   const uint16_t* kb = kc + b * kv_bs + h * HD + part * 8;
   const uint16_t* vb = vc + b * kv_bs + h * HD + part * 8;
   const uint8_t* mb = mask ? mask + b * mask_bs : nullptr;
-  // warp-uniform trip count: the shuffles below are executed by all 32 lanes in every iteration.  The loads of
-  // DEC_UNROLL iterations are issued before the first of them is used: the kernel is bound by the cache read,
-  // and one key and one value row per thread do not keep enough bytes in flight to fill the memory pipeline.
-  constexpr int STRIDE = (DEC_THREADS / 32) * KPW;
-  for (int base = s0 + warp * KPW; base < s1; base += STRIDE * DEC_UNROLL) {
-    uint4 kq[DEC_UNROLL], vq[DEC_UNROLL];
+  // Warp-uniform trip count: the shuffles are executed by all 32 lanes in every iteration.  The kernel is bound
+  // by the cache read, so the rows of the next iteration are requested before the current ones are used (two
+  // register buffers), and DEC_UNROLL keys share one update of the running maximum.
+  constexpr int STEP = (DEC_THREADS / 32) * KPW * DEC_UNROLL;
+  auto fetch = [&](uint4 (&kq)[DEC_UNROLL], uint4 (&vq)[DEC_UNROLL], int base) {
 #pragma unroll
     for (int u = 0; u < DEC_UNROLL; ++u) {
-      const long long s = base + u * STRIDE + sub;
+      const long long s = base + u * (STEP / DEC_UNROLL) + sub;
       kq[u] = make_uint4(0u, 0u, 0u, 0u);
       vq[u] = make_uint4(0u, 0u, 0u, 0u);
       if (s < s1) {
@@ -94,33 +93,68 @@ decode_attn_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ 
         }
       }
     }
+  };
+  auto consume = [&](const uint4 (&kq)[DEC_UNROLL], const uint4 (&vq)[DEC_UNROLL], int base) {
+    float dot[DEC_UNROLL];
+    float m_new = m;
 #pragma unroll
     for (int u = 0; u < DEC_UNROLL; ++u) {
-      const long long s = base + u * STRIDE + sub;
-      const bool valid = s < s1;
+      const long long s = base + u * (STEP / DEC_UNROLL) + sub;
       const uint32_t kw[4] = {kq[u].x, kq[u].y, kq[u].z, kq[u].w};
-      float dot = 0.f;
+      float d = 0.f;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const float2 f = unpack2<BF16>(kw[j]);
-        dot = fmaf(qv[2 * j], f.x, dot);
-        dot = fmaf(qv[2 * j + 1], f.y, dot);
+        d = fmaf(qv[2 * j], f.x, d);
+        d = fmaf(qv[2 * j + 1], f.y, d);
       }
 #pragma unroll
-      for (int o = G / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-      if (valid && !(mb && mb[s])) {
-        const float m_new = fmaxf(m, dot);
-        const float alpha = exp2f(m - m_new);
-        const float p = exp2f(dot - m_new);
-        l = l * alpha + p;
+      for (int o = G / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+      if (!(s < s1) || (mb && mb[s])) d = -INFINITY;
+      dot[u] = d;
+      m_new = fmaxf(m_new, d);
+    }
+    if (m_new > -INFINITY) {  // uniform within a lane group; no shuffles below
+      const float alpha = exp2f(m - m_new);  // 0 for the first keys (m = -inf)
+      float pr[DEC_UNROLL];
+      float psum = 0.f;
+#pragma unroll
+      for (int u = 0; u < DEC_UNROLL; ++u) {
+        pr[u] = exp2f(dot[u] - m_new);  // 0 for an excluded key
+        psum += pr[u];
+      }
+      l = fmaf(l, alpha, psum);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] *= alpha;
+#pragma unroll
+      for (int u = 0; u < DEC_UNROLL; ++u) {
         const uint32_t vw[4] = {vq[u].x, vq[u].y, vq[u].z, vq[u].w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const float2 f = unpack2<BF16>(vw[j]);
-          acc[2 * j] = fmaf(acc[2 * j], alpha, p * f.x);
-          acc[2 * j + 1] = fmaf(acc[2 * j + 1], alpha, p * f.y);
+          acc[2 * j] = fmaf(pr[u], f.x, acc[2 * j]);
+          acc[2 * j + 1] = fmaf(pr[u], f.y, acc[2 * j + 1]);
         }
-        m = m_new;
+      }
+      m = m_new;
+    }
+  };
+  {
+    uint4 ka[DEC_UNROLL], va[DEC_UNROLL], kb2[DEC_UNROLL], vb2[DEC_UNROLL];
+    int base = s0 + warp * KPW;
+    if (base < s1) {
+      fetch(ka, va, base);
+      while (true) {
+        int next = base + STEP;
+        if (next < s1) fetch(kb2, vb2, next);
+        consume(ka, va, base);
+        base = next;
+        if (base >= s1) break;
+        next = base + STEP;
+        if (next < s1) fetch(ka, va, next);
+        consume(kb2, vb2, base);
+        base = next;
+        if (base >= s1) break;
       }
     }
   }

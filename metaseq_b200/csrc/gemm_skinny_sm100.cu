@@ -7,10 +7,11 @@
 //     16 / 32 / 64 (the "N" side), so no tensor-core lanes or shared memory are spent on padding of X to 128;
 //   * the K range of a tile is split over the CTAs of a thread-block cluster (1, 2, 4 or 8), which gives
 //     every SM a slice of W to fetch even when N / 128 is far below the SM count (out-projection, fc2);
-//   * the cluster adds the partial products through distributed shared memory: each CTA parks its fp32
-//     partial tile in its own shared memory, and after a cluster barrier CTA c sums rows [c*128/S, (c+1)*128/S)
-//     over all peers and applies the epilogue (+bias -> ReLU -> +residual).  No workspace, no atomics, and the
-//     result does not depend on the order in which CTAs finish;
+//   * the cluster adds the partial products through distributed shared memory: CTA c owns rows
+//     [c*128/S, (c+1)*128/S) of the tile; every CTA stores its fp32 partial rows straight into the owner's shared
+//     memory (remote stores need no round trip), and after one cluster barrier the owner sums its S slots and
+//     applies the epilogue (+bias -> ReLU -> +residual).  No workspace, no atomics, and the result does not
+//     depend on the order in which CTAs finish;
 //   * shared memory stays near 100 KB so that two CTAs share an SM and about 200 KB of loads are in flight
 //     per SM.
 //
@@ -18,7 +19,7 @@
 // (metaseq/modules/megatron/mpu/layers.py:290,373; metaseq/modules/feedforward.py:21-22).
 //
 // Roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner, warps 2..5 move the
-// accumulator to shared memory; all threads take part in the cluster reduction.
+// accumulator to the owners' shared memory; all threads take part in the final sum.
 #include <cstdio>
 
 #include "sm100_common.cuh"
@@ -50,11 +51,11 @@ template <int MP>
 struct SkinnyCfg {
   static constexpr uint32_t W_BYTES = SK_BM * SK_BK * 2;
   static constexpr uint32_t X_BYTES = MP * SK_BK * 2;
-  static constexpr int STAGES = (MP == 64) ? 4 : 5;
-  static constexpr uint32_t PARTIAL_BYTES = SK_BM * MP * 4;  // reuses the stage memory
-  static constexpr uint32_t SMEM = STAGES * (W_BYTES + X_BYTES) + 1024 /*align slack*/ + 256 /*barriers*/;
+  static constexpr int STAGES = (MP == 64) ? 3 : (MP == 32 ? 4 : 5);
+  static constexpr uint32_t RECV_BYTES = SK_BM * MP * 4;  // S slots of [MP][128 / S] fp32, whatever S is
+  static constexpr uint32_t SMEM = STAGES * (W_BYTES + X_BYTES) + RECV_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
   static constexpr uint32_t TMEM_COLS = MP < 32 ? 32 : MP;
-  static_assert(PARTIAL_BYTES <= STAGES * W_BYTES, "partial tile must fit in the stage memory");
+  static_assert(2 * SMEM <= 227 * 1024, "two CTAs must fit in one SM");
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -62,15 +63,21 @@ __device__ __forceinline__ uint32_t cluster_ctarank() {
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
   return r;
 }
+// Barrier 1 only establishes that every CTA of the cluster has started (its shared memory exists) before a
+// peer stores into it: arrive early, wait just before the first remote store.  Not `.aligned`: the roles diverge.
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
+// Barrier 2 publishes the remote stores to their owners.
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-__device__ __forceinline__ float2 ld_peer_f2(uint32_t local_addr, uint32_t rank) {
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
   uint32_t remote;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-  float2 v;
-  asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(remote) : "memory");
-  return v;
+  return remote;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t remote_addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote_addr), "f"(v) : "memory");
 }
 
 template <int MP>
@@ -83,8 +90,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sW = smem;
   uint8_t* sX = smem + STAGES * Cfg::W_BYTES;
-  float* partial = reinterpret_cast<float*>(smem);  // [MP][128] after the main loop
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(sX + STAGES * Cfg::X_BYTES);
+  float* recv = reinterpret_cast<float*>(sX + STAGES * Cfg::X_BYTES);  // [S][MP][128 / S]
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(sX + STAGES * Cfg::X_BYTES + Cfg::RECV_BYTES);
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* tfull_bar = empty_bar + STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tfull_bar + 1);
@@ -106,6 +113,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   const bool skip = p.status && *reinterpret_cast<volatile int*>(p.status) != 0;
   dependents_launch();
 
+  const int head = (!skip) ? min(STAGES, my_kb) : 0;
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
@@ -115,8 +123,12 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     *abort_flag = 0;
     mbar_fence_init();
     fence_proxy_async_smem();
-    tma_prefetch_desc(&tmW);
-    tma_prefetch_desc(&tmX);
+    // The weights are not written by any kernel of the stream, so the first ring of W tiles is requested at
+    // once: before the rest of the set-up and before the wait for the preceding kernels.
+    for (int i = 0; i < head; ++i) {
+      mbar_expect_tx(&full_bar[i], Cfg::W_BYTES + Cfg::X_BYTES);
+      tma_load_2d(sW + i * Cfg::W_BYTES, &tmW, &full_bar[i], (kb0 + i) * SK_BK, n0);
+    }
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
@@ -125,19 +137,15 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  cluster_arrive_relaxed();  // barrier 1
+  bool waited = false;
   const uint32_t tmem_base = *tmem_slot;
+  const int R = SK_BM / p.split;  // rows of the tile that each CTA of the cluster owns
 
   if (!skip && my_kb > 0) {
     if (warp == 0) {
       // ---------------------------------------------------------- producer
       if (lane == 0) {
-        // The weights are not written by any kernel of the stream, so the first ring of W tiles is requested
-        // before the wait for the preceding kernels; X (their output) follows after it.
-        const int head = min(STAGES, my_kb);
-        for (int i = 0; i < head; ++i) {
-          mbar_expect_tx(&full_bar[i], Cfg::W_BYTES + Cfg::X_BYTES);
-          tma_load_2d(sW + i * Cfg::W_BYTES, &tmW, &full_bar[i], (kb0 + i) * SK_BK, n0);
-        }
         dependents_wait();
         for (int i = 0; i < head; ++i)
           tma_load_2d(sX + i * Cfg::X_BYTES, &tmX, &full_bar[i], (kb0 + i) * SK_BK, 0);
@@ -153,8 +161,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (!ok) {
-          // Leaving early: give the copies already issued a bounded time to land before the stage memory is
-          // reused for the partial tile.
+          // Leaving early: give the copies already issued a bounded time to land before this CTA's shared
+          // memory can be handed to another CTA.
           const unsigned long long t0 = globaltimer_ns();
           while (globaltimer_ns() - t0 < 2000000ull) { }
         }
@@ -184,11 +192,16 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         if (ok) tc_commit(tfull_bar);
       }
     } else {
-      // ------------------------------------- accumulator -> shared memory
+      // --------------------------- accumulator -> the owners' shared memory
       const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) = rows of the W tile
-      if (mbar_wait_warp(tfull_bar, 0, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) {
+      const bool ok = mbar_wait_warp(tfull_bar, 0, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
+      cluster_wait();  // barrier 1: the owners' shared memory exists
+      waited = true;
+      if (ok) {
         tc_fence_after();
         const int r = quarter * 32 + lane;
+        const uint32_t slot = smem_u32(recv) + static_cast<uint32_t>((static_cast<int>(crank) * MP) * R + (r % R)) * 4u;
+        const uint32_t dst = map_to_cta(slot, static_cast<uint32_t>(r / R));
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll
         for (int c = 0; c < MP / 16; ++c) {
@@ -196,15 +209,21 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           tmem_ld_32x16(taddr + c * 16, v);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 16; ++j) partial[(c * 16 + j) * SK_BM + r] = __uint_as_float(v[j]);
+          for (int j = 0; j < 16; ++j)
+            st_cluster_f32(dst + static_cast<uint32_t>((c * 16 + j) * R) * 4u, __uint_as_float(v[j]));
         }
       }
     }
   } else if (warp >= 2) {
     // no K range (or skipping): contribute zeros
+    cluster_wait();
+    waited = true;
     const int r = (warp & 3) * 32 + lane;
-    for (int m = 0; m < MP; ++m) partial[m * SK_BM + r] = 0.f;
+    const uint32_t slot = smem_u32(recv) + static_cast<uint32_t>((static_cast<int>(crank) * MP) * R + (r % R)) * 4u;
+    const uint32_t dst = map_to_cta(slot, static_cast<uint32_t>(r / R));
+    for (int m = 0; m < MP; ++m) st_cluster_f32(dst + static_cast<uint32_t>(m * R) * 4u, 0.f);
   }
+  if (!waited) cluster_wait();  // barrier 1 for the threads that store nothing
 
   tc_fence_before();
   __syncthreads();
@@ -213,32 +232,29 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
   dependents_wait();   // the residual is an output of the preceding kernels, and C may be memory they still read
-  cluster_sync_all();  // every CTA's partial tile is complete and visible
+  cluster_sync_all();  // barrier 2: every partial row has reached its owner
 
   if (!skip) {
-    // CTA `crank` finishes rows [crank*R, crank*R + R) of the tile, two adjacent rows (= output columns) per item.
-    const int R = SK_BM / p.split;
+    // This CTA finishes rows [crank*R, crank*R + R) of the tile, two adjacent rows (= output columns) per item.
     const int half = R >> 1;
     const int items = half * p.M;
-    const uint32_t partial_addr = smem_u32(partial);
     for (int e = threadIdx.x; e < items; e += SK_THREADS) {
       const int m = e / half;
       const int rl = (e - m * half) * 2;
-      const int r = static_cast<int>(crank) * R + rl;
-      const int n = n0 + r;
+      const int n = n0 + static_cast<int>(crank) * R + rl;
       if (n >= p.N) continue;  // N is even, so a pair is inside or outside as a whole
-      const uint32_t addr = partial_addr + static_cast<uint32_t>(m * SK_BM + r) * 4u;
-      float2 part[8];  // all peer loads are issued before the first is used
-#pragma unroll
-      for (int j = 0; j < 8; ++j) part[j] = j < p.split ? ld_peer_f2(addr, static_cast<uint32_t>(j)) : make_float2(0.f, 0.f);
+      uint32_t bw = 0u, rw = 0u;  // requested before the sum so that their latency overlaps it
+      if (p.bias) bw = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(p.bias) + n);
+      if (p.residual)
+        rw = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(p.residual) +
+                                                static_cast<long long>(m) * p.ldr + n);
       float2 acc = make_float2(0.f, 0.f);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        acc.x += part[j].x;
-        acc.y += part[j].y;
+      for (int j = 0; j < p.split; ++j) {
+        const float2 v = *reinterpret_cast<const float2*>(recv + (j * MP + m) * R + rl);
+        acc.x += v.x;
+        acc.y += v.y;
       }
       if (p.bias) {
-        const uint32_t bw = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(p.bias) + n);
         const float2 b2 = p.bf16 ? unpack2<true>(bw) : unpack2<false>(bw);
         acc.x += b2.x;
         acc.y += b2.y;
@@ -248,8 +264,6 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         acc.y = fmaxf(acc.y, 0.f);
       }
       if (p.residual) {
-        const uint32_t rw = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(p.residual) +
-                                                               static_cast<long long>(m) * p.ldr + n);
         const float2 r2 = p.bf16 ? unpack2<true>(rw) : unpack2<false>(rw);
         acc.x += r2.x;
         acc.y += r2.y;
@@ -258,8 +272,6 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       *dst = p.bf16 ? pack2<true>(acc.x, acc.y) : pack2<false>(acc.x, acc.y);
     }
   }
-  __syncthreads();     // reconverge every warp before the aligned cluster barrier
-  cluster_sync_all();  // no CTA leaves while a peer may still read its shared memory
 }
 
 static int g_skinny_sms = 0;
