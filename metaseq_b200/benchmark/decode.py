@@ -59,6 +59,9 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--repeats", type=int, default=3)
     ap.add_argument("--kernel-backend", default="auto", choices=["auto", "torch"])
+    ap.add_argument("--graph-replays", type=int, default=0,
+                    help="instead of whole generate calls: one prefill, then this many replays of the captured "
+                         "decode step, timed together (the workload for a per-kernel launch list)")
     args = ap.parse_args(argv)
     F.set_backend(args.kernel_backend)
     cfg, task, model = build(args.arch, args.prompt + args.gen + 8)
@@ -73,6 +76,27 @@ def main(argv=None):
         with torch.no_grad():
             return sg.generate([model], sample)
 
+    if args.graph_replays > 0:
+        from metaseq_b200.models.decode_step import GraphedDecodeStep
+
+        assert GraphedDecodeStep.supported(model.decoder), "the graphed step needs the kernel backend"
+        runner = GraphedDecodeStep.for_decoder(model.decoder, args.batch, args.prompt + args.graph_replays + 8)
+        with torch.no_grad():
+            model(prompts, incremental_state=runner.new_state())
+            runner.begin(prompts)
+            nxt = prompts[:, -1].clone()
+            runner.step(nxt)  # captures
+            torch.cuda.synchronize()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            for _ in range(args.graph_replays):
+                runner.step(nxt)
+            e.record()
+            torch.cuda.synchronize()
+        print(json.dumps(dict(metric="decode_graph_step_ms", arch=args.arch, batch=args.batch, cached=args.prompt,
+                              replays=args.graph_replays, ms_per_replay=round(s.elapsed_time(e) / args.graph_replays, 4),
+                              kernel_status=_lib.check_status(torch.device("cuda")))), flush=True)
+        return
     _lib.reset_launch_count()
     t1 = timed(lambda: call(1), args.warmup, args.repeats)
     tn = timed(lambda: call(args.gen), 1, args.repeats)

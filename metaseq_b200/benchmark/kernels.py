@@ -70,6 +70,35 @@ def time_op(fn, warmup=3, iters=10):
     return times[len(times) // 2], times[0]
 
 
+def time_graphed(fn, variants: int, launches: int = 24, dependent: bool = False):
+    """Mean time in ms of ``fn(i)`` launched ``launches`` times from one CUDA graph, ``i`` cycling over ``variants``
+    operand sets whose total size exceeds L2.  For kernels of a few microseconds an eager launch measures the
+    launch path, not the kernel; this is also how the decode step runs them.  ``dependent``: capture with
+    programmatic dependent launch, as the decode step does."""
+    import contextlib
+
+    for i in range(min(3, variants)):
+        fn(i)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with (F.dependent_launch() if dependent else contextlib.nullcontext()):
+        with torch.cuda.graph(graph):
+            for i in range(launches):
+                fn(i % variants)
+    graph.replay()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(5):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        graph.replay()
+        e.record()
+        torch.cuda.synchronize()
+        times.append(s.elapsed_time(e) / launches)
+    times.sort()
+    return times[len(times) // 2]
+
+
 def with_backend(name, fn):
     def run():
         prev = F.get_backend()
@@ -91,6 +120,8 @@ def main(argv=None):
     ap.add_argument("--only", default=None, help="comma-separated op-name prefixes")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--gemm-variant", default="auto", choices=["auto", "1cta", "2cta"])
+    ap.add_argument("--decode-batch", type=int, default=32, help="rows of the decode-step ops (--only decode)")
+    ap.add_argument("--decode-cache", type=int, default=567, help="cached positions for the decode attention")
     args = ap.parse_args(argv)
     dt = torch.float16 if args.dtype == "fp16" else torch.bfloat16
     F.set_gemm_variant(args.gemm_variant)
@@ -198,6 +229,42 @@ def main(argv=None):
     report("sumsq_layer_flat", 0, n * 2.0, lambda: F.sumsq(gr, acc, False), lambda: gr.float().pow(2).sum())
     kw = dict(lr=1e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=3)
     report("adamw_layer_flat", 0, n * (2 + 2 * 2 + 4 * 4.0), lambda: F.adamw_step(p, gr, m_, v_, **kw), None)
+    # ---- decode step: few-row products and single-query attention, launched from a graph
+    Bd, Sd = args.decode_batch, args.decode_cache
+    if want("decode"):
+        xd = torch.randn(Bd, max(D, FFN), device=dev, dtype=dt)
+        for name, N, K in [("qkv", 3 * D, D), ("out_proj", D, D), ("fc1", FFN, D), ("fc2", D, FFN), ("logits", V, D)]:
+            copies = max(2, int(300e6 / (N * K * 2)) + 1)
+            ws = [torch.randn(N, K, device=dev, dtype=dt) * 0.02 for _ in range(copies)]
+            outd = torch.empty(Bd, N, device=dev, dtype=dt)
+            xin = xd[:, :K]
+            rec = dict(op=f"decode_gemm_{name}", rows=Bd, N=N, K=K,
+                       split=_lib.kernels().msq_gemm_skinny_split(N, K))
+            for label, fn, dep in [("ms", lambda i: F.gemm(xin, ws[i], out=outd), False),
+                                   ("ms_dependent_launch", lambda i: F.gemm(xin, ws[i], out=outd), True),
+                                   ("cublas_ms", lambda i: torch.matmul(xin, ws[i].t(), out=outd), False)]:
+                rec[label] = round(time_graphed(fn, copies, dependent=dep), 5)
+            best = min(rec["ms"], rec["ms_dependent_launch"])
+            rec["gbs"] = round(N * K * 2 / best / 1e6, 1)
+            rec["frac_of_measured_hbm"] = round(rec["gbs"] / peaks["hbm_gbs"], 3)
+            rec["peaks"] = peaks["source"]
+            results.append(rec)
+            print(json.dumps(rec), flush=True)
+            del ws
+        cap = -(-(Sd + 1) // 256) * 256
+        copies = max(2, int(300e6 / (Bd * cap * D * 4)) + 1)
+        caches = [(torch.randn(Bd, cap, D, device=dev, dtype=dt), torch.randn(Bd, cap, D, device=dev, dtype=dt))
+                  for _ in range(copies)]
+        qkv_d = torch.randn(Bd, 3 * D, device=dev, dtype=dt)
+        length = torch.tensor([Sd], dtype=torch.int32, device=dev)
+        ms = time_graphed(lambda i: F.decode_attn_step(qkv_d[:, 2 * D:], qkv_d[:, :D], qkv_d[:, D:2 * D], caches[i][0],
+                                                       caches[i][1], length, H, scale, Sd), copies)
+        nbytes = 2.0 * Bd * (Sd + 1) * D * 2
+        rec = dict(op="decode_attn_step", batch=Bd, cached=Sd, ms=round(ms, 5), gbs=round(nbytes / ms / 1e6, 1),
+                   frac_of_measured_hbm=round(nbytes / ms / 1e6 / peaks["hbm_gbs"], 3), peaks=peaks["source"])
+        results.append(rec)
+        print(json.dumps(rec), flush=True)
+        del caches
     bad = _lib.check_status(dev)
     summary = dict(model=args.model, batch=B, seq=T, dtype=args.dtype, peaks=peaks, kernel_status=bad,
                    device=torch.cuda.get_device_name(0))
