@@ -112,6 +112,30 @@ __global__ void fold_fp32_kernel(const float* __restrict__ src, uint16_t* __rest
   }
 }
 
+// x[r, c] *= g[r] (or g[0] when `per_row` is 0), in place, 8 elements per thread: the chain-rule factor applied to
+// a stored gradient (the loss scale on d(loss)/d(logits)), read from device memory so that no host sync is needed.
+template <bool BF16, typename G>
+__global__ void scale_rows_kernel(uint16_t* __restrict__ x, long long ld, long long rows, int cols,
+                                  const G* __restrict__ g, int per_row) {
+  const int vec_per_row = cols >> 3;
+  const long long total = rows * vec_per_row;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const long long r = i / vec_per_row;
+    const int c = static_cast<int>(i - r * vec_per_row) * 8;
+    const float f = static_cast<float>(g[per_row ? r : 0]);
+    uint4* p = reinterpret_cast<uint4*>(x + r * ld + c);
+    uint4 v = *p;
+    uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 t = unpack2<BF16>(w[j]);
+      w[j] = pack2<BF16>(t.x * f, t.y * f);
+    }
+    *p = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
 // dst16[r, c] = src32[r, c]: contiguous fp32 rows to 16-bit rows of a strided view, 8 elements per thread.
 template <bool BF16>
 __global__ void convert_rows_kernel(const float* __restrict__ src, uint16_t* __restrict__ dst, long long rows,
@@ -462,6 +486,28 @@ extern "C" int msq_convert_rows(const float* src, void* dst, long long rows, int
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (bf16) convert_rows_kernel<true><<<static_cast<int>(blocks), 256, 0, stream>>>(src, static_cast<uint16_t*>(dst), rows, cols, dst_ld);
   else convert_rows_kernel<false><<<static_cast<int>(blocks), 256, 0, stream>>>(src, static_cast<uint16_t*>(dst), rows, cols, dst_ld);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// x: 16-bit [rows, cols] with row stride ld, scaled in place by g (fp32 when g_fp32, else the type of x): one
+// factor per row, or a single factor when per_row is 0.
+extern "C" int msq_scale_rows(void* x, long long ld, long long rows, int cols, const void* g, int g_fp32, int per_row,
+                              int bf16, cudaStream_t stream) {
+  using namespace msq;
+  if (rows <= 0 || cols <= 0) return 0;
+  if ((cols & 7) || (ld & 7) || (reinterpret_cast<uintptr_t>(x) & 15)) return -2;
+  long long blocks = (rows * (cols >> 3) + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  const int nb = static_cast<int>(blocks);
+  uint16_t* xp = static_cast<uint16_t*>(x);
+  if (g_fp32) {
+    if (bf16) scale_rows_kernel<true, float><<<nb, 256, 0, stream>>>(xp, ld, rows, cols, static_cast<const float*>(g), per_row);
+    else scale_rows_kernel<false, float><<<nb, 256, 0, stream>>>(xp, ld, rows, cols, static_cast<const float*>(g), per_row);
+  } else if (bf16) {
+    scale_rows_kernel<true, __nv_bfloat16><<<nb, 256, 0, stream>>>(xp, ld, rows, cols, static_cast<const __nv_bfloat16*>(g), per_row);
+  } else {
+    scale_rows_kernel<false, __half><<<nb, 256, 0, stream>>>(xp, ld, rows, cols, static_cast<const __half*>(g), per_row);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

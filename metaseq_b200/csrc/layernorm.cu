@@ -52,22 +52,35 @@ layernorm_fwd_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict_
   const float inv_d = 1.f / static_cast<float>(D);
   dependents_launch();
   dependents_wait();  // gamma / beta above are parameters; x comes from the preceding kernel
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+  // The row after this one is requested before this one is reduced: the two block-wide sums of a row are
+  // latency, and without the prefetch nothing of this CTA is in flight while they run.
+  float nxt[VPT][8];
+  auto fetch = [&](int row) {
     const uint16_t* xr = x + static_cast<long long>(row) * D;
-    float f[VPT][8];
-    float s = 0.f;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int v = threadIdx.x + i * LN_THREADS;
       if (v < nvec) {
-        load8<BF16>(xr + v * 8, f[i]);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) s += f[i][j];
+        load8<BF16>(xr + v * 8, nxt[i]);
       } else {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) f[i][j] = 0.f;
+        for (int j = 0; j < 8; ++j) nxt[i][j] = 0.f;
       }
     }
+  };
+  if (static_cast<int>(blockIdx.x) < rows) fetch(blockIdx.x);
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    float f[VPT][8];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        f[i][j] = nxt[i][j];
+        s += f[i][j];
+      }
+    }
+    if (row + static_cast<int>(gridDim.x) < rows) fetch(row + gridDim.x);
     const float mean = block_sum(s, red) * inv_d;
     float q = 0.f;
 #pragma unroll
@@ -229,6 +242,12 @@ static int ln_grid(int rows) {
   return rows < cap ? rows : cap;
 }
 
+// The forward kernel keeps fewer registers per thread, so five CTAs share an SM.
+static int ln_grid_fwd(int rows) {
+  const int cap = ln_grid(1 << 30) / 4 * 5;
+  return rows < cap ? rows : cap;
+}
+
 }  // namespace msq
 
 #define MSQ_LN_DISPATCH(NVEC, CALL)                          \
@@ -249,7 +268,7 @@ extern "C" int msq_layernorm_fwd(const void* x, const void* gamma, const void* b
   if (rows <= 0) return 0;
   if (D & 7) return -2;
   const int nvec = D >> 3;
-  const int grid = ln_grid(rows);
+  const int grid = ln_grid_fwd(rows);
   auto X = static_cast<const uint16_t*>(x);
   auto G = static_cast<const uint16_t*>(gamma);
   auto B = static_cast<const uint16_t*>(beta);

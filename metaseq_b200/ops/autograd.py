@@ -164,7 +164,8 @@ class CrossEntropyFn(torch.autograd.Function):
     def backward(ctx, g):
         (grad,) = ctx.saved_tensors
         # g is the scalar d(total)/d(loss); typically loss_scale.
-        grad = grad * g.to(grad.dtype) if g.numel() == 1 else grad
+        if g.numel() == 1:
+            F.scale_rows_(grad, g)  # in place: the saved tensor is the consumed logits buffer
         return grad.view(ctx.shape), None, None
 
 

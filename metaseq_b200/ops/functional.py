@@ -645,6 +645,22 @@ def cross_entropy_fwd_bwd(logits2d, target, ignore_index: int, grad_scale: float
     return loss, lse
 
 
+def scale_rows_(x2d, g):
+    """``x2d[r, :] *= g[r]`` in place (``g`` with one element scales everything); ``g`` stays on the device.
+    Used to apply the incoming gradient (the loss scale) to a gradient stored by the forward pass."""
+    rows, cols = x2d.shape
+    g = g.reshape(-1)
+    assert g.numel() in (1, rows)
+    if use_kernels(x2d) and cols % 8 == 0 and x2d.stride(1) == 1 and x2d.stride(0) % 8 == 0 \
+            and x2d.data_ptr() % 16 == 0 and g.dtype in (torch.float32, x2d.dtype) and g.is_cuda:
+        g = g.contiguous()
+        rc = _lib.kernels().msq_scale_rows(_lib.ptr(x2d), x2d.stride(0), rows, cols, _lib.ptr(g),
+                                           int(g.dtype == torch.float32), int(g.numel() > 1), _bf(x2d), _lib.stream_ptr())
+        _lib.check_rc(rc, "msq_scale_rows")
+        return x2d
+    return x2d.mul_(g.to(x2d.dtype).reshape(-1, 1) if g.numel() > 1 else g.to(x2d.dtype))
+
+
 # --------------------------------------------------------------------- colsum
 def colsum(x2d, out16=None, accumulate=False):
     """Column sums of ``[rows, N]`` (bias gradient), fp32 accumulation."""

@@ -103,8 +103,11 @@ class _FusedVocabParallelCrossEntropy(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_output):
         (grad,) = ctx.saved_tensors  # (softmax - onehot), zero rows where the target is ignored
-        g = grad_output.reshape(-1, 1).to(grad.dtype)
-        return (grad * g).view(ctx.shape), None, None
+        from metaseq_b200.ops import functional as ops_f
+
+        # in place: the saved tensor is the logits buffer, which nothing else reads after the loss
+        ops_f.scale_rows_(grad, grad_output)
+        return grad.view(ctx.shape), None, None
 
 
 def fused_vocab_parallel_cross_entropy_ok(logits) -> bool:

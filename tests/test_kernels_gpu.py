@@ -344,6 +344,23 @@ def test_gemm_few_rows_cluster_split_k(dtype, M, N, K, epilogue):
     _status_ok()
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("per_row,g_dtype", [(True, torch.float32), (False, torch.float32), (True, None), (False, None)])
+def test_scale_rows_in_place(dtype, per_row, g_dtype):
+    torch.manual_seed(5)
+    rows, cols = 300, 1000
+    buf = torch.randn(rows, cols + 24, device="cuda", dtype=dtype)
+    view = buf[:, 8:8 + cols]
+    g = torch.rand(rows if per_row else 1, device="cuda", dtype=g_dtype or dtype) * 4
+    want = view.float() * (g.float().reshape(-1, 1) if per_row else g.float())
+    untouched = buf.clone()
+    before = _lib.launch_count()
+    F.scale_rows_(view, g)
+    assert _lib.launch_count() == before + 1
+    _close(view, want, dtype)
+    assert torch.equal(buf[:, :8], untouched[:, :8]) and torch.equal(buf[:, 8 + cols:], untouched[:, 8 + cols:])
+
+
 def test_dependent_launch_chain_matches_ordinary_launches():
     """LayerNorm -> GEMM -> GEMM(+residual) chains launched with programmatic dependent launch (eagerly and from a
     CUDA graph) give the results of ordinary launches: each kernel waits for its predecessor before touching
