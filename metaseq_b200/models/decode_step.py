@@ -43,8 +43,10 @@ class GraphedDecodeStep:
 
     @staticmethod
     def supported(decoder) -> bool:
-        from metaseq_b200.models.transformer_decoder import UNSPECIFIED_DOC_SEP
+        from metaseq_b200.models.transformer_decoder import UNSPECIFIED_DOC_SEP, ModelParallelTransformerDecoder as TransformerDecoder
 
+        if not isinstance(decoder, TransformerDecoder):
+            return False
         w = decoder.embed_tokens.weight
         if not (w.is_cuda and w.dtype in (torch.float16, torch.bfloat16) and F.use_kernels(w)):
             return False
