@@ -15,8 +15,19 @@
 //   * shared memory stays near 100 KB so that two CTAs share an SM and about 200 KB of loads are in flight
 //     per SM.
 //
+// Tensor parallelism: a row-parallel product (K sharded over the ranks) ends in a sum over the ranks.  Here the
+// owner CTA stores its finished partial rows (16-bit, like the all-reduce payload of the reference) in this
+// rank's staging buffer, publishes an arrival flag to the same-index CTA of every peer, waits (bounded) for
+// theirs, then reads the same rows from every rank's staging buffer over NVLink, adds them in fp32 and applies
+// bias and residual: GEMM and all-reduce in one launch, tile by tile, without a grid-wide or rank-wide barrier.
+// Epochs live in device memory (one counter per CTA, advanced by the kernel), so the launch can be replayed from a
+// CUDA graph; consecutive products alternate between two staging halves (chosen by the caller), which together
+// with the per-CTA handshake keeps a fast rank from overwriting rows a slow rank is still reading, provided
+// every such product of the sequence uses the same grid.
+//
 // The reference runs these products as torch.matmul plus separate bias / activation / residual kernels
-// (metaseq/modules/megatron/mpu/layers.py:290,373; metaseq/modules/feedforward.py:21-22).
+// (metaseq/modules/megatron/mpu/layers.py:290,373; metaseq/modules/feedforward.py:21-22) and the sum over ranks
+// as an NCCL all-reduce after the product (metaseq/modules/megatron/mpu/mappings.py:27-40).
 //
 // Roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner, warps 2..5 move the
 // accumulator to the owners' shared memory; all threads take part in the final sum.
@@ -28,6 +39,8 @@ namespace msq {
 
 int make_tmap_2d(CUtensorMap* out, const void* base, long long rows, long long cols, long long ld, int box_rows,
                  int bf16);  // gemm_sm100.cu
+
+constexpr int SK_MAX_RANKS = 8;
 
 struct SkinnyParams {
   int M, N, K;
@@ -41,6 +54,12 @@ struct SkinnyParams {
   int relu;
   int bf16;
   int* status;
+  // sum over tensor-parallel ranks (world <= 1: none)
+  int world, rank;
+  void* stage[SK_MAX_RANKS];     // every rank's staging buffer for this product, 16-bit [M][N]
+  uint32_t* sig[SK_MAX_RANKS];   // every rank's flag words
+  long long flag_base;           // first flag word of this product: one per (CTA, source rank)
+  uint32_t* epoch_dev;           // this rank's per-CTA epoch counters
 };
 
 constexpr int SK_BM = 128;  // rows of W per tile
@@ -78,6 +97,13 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t ran
 }
 __device__ __forceinline__ void st_cluster_f32(uint32_t remote_addr, float v) {
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote_addr), "f"(v) : "memory");
+}
+
+// 4-byte load of a row pair from a staging buffer that may live on another GPU: system scope, never from L1.
+__device__ __forceinline__ uint32_t ld_relaxed_sys_u32(const void* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
 }
 
 template <int MP>
@@ -234,6 +260,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   dependents_wait();   // the residual is an output of the preceding kernels, and C may be memory they still read
   cluster_sync_all();  // barrier 2: every partial row has reached its owner
 
+  __shared__ int peers_ok;
+  const bool reduce_ranks = p.world > 1;
+  const uint32_t epoch = reduce_ranks ? p.epoch_dev[blockIdx.x] + 1u : 0u;
   if (!skip) {
     // This CTA finishes rows [crank*R, crank*R + R) of the tile, two adjacent rows (= output columns) per item.
     const int half = R >> 1;
@@ -244,15 +273,23 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       const int n = n0 + static_cast<int>(crank) * R + rl;
       if (n >= p.N) continue;  // N is even, so a pair is inside or outside as a whole
       uint32_t bw = 0u, rw = 0u;  // requested before the sum so that their latency overlaps it
-      if (p.bias) bw = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(p.bias) + n);
-      if (p.residual)
-        rw = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(p.residual) +
-                                                static_cast<long long>(m) * p.ldr + n);
+      if (!reduce_ranks) {
+        if (p.bias) bw = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(p.bias) + n);
+        if (p.residual)
+          rw = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(p.residual) +
+                                                  static_cast<long long>(m) * p.ldr + n);
+      }
       float2 acc = make_float2(0.f, 0.f);
       for (int j = 0; j < p.split; ++j) {
         const float2 v = *reinterpret_cast<const float2*>(recv + (j * MP + m) * R + rl);
         acc.x += v.x;
         acc.y += v.y;
+      }
+      if (reduce_ranks) {
+        // this rank's share of the sum goes to its staging buffer; the epilogue follows the exchange
+        uint32_t* dst = reinterpret_cast<uint32_t*>(static_cast<uint16_t*>(p.stage[p.rank]) + static_cast<long long>(m) * p.N + n);
+        *dst = p.bf16 ? pack2<true>(acc.x, acc.y) : pack2<false>(acc.x, acc.y);
+        continue;
       }
       if (p.bias) {
         const float2 b2 = p.bf16 ? unpack2<true>(bw) : unpack2<false>(bw);
@@ -272,6 +309,65 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       *dst = p.bf16 ? pack2<true>(acc.x, acc.y) : pack2<false>(acc.x, acc.y);
     }
   }
+  if (!reduce_ranks) return;
+
+  // ------------------------------------------------------- sum over ranks
+  if (threadIdx.x == 0) peers_ok = 1;
+  __syncthreads();  // every row of this CTA is in the staging buffer
+  if (!skip && threadIdx.x < p.world) {
+    const long long word = p.flag_base + static_cast<long long>(blockIdx.x) * p.world;
+    __threadfence_system();
+    st_release_sys(p.sig[threadIdx.x] + word + p.rank, epoch);
+    if (!wait_flag(p.sig[p.rank] + word + threadIdx.x, epoch, p.status)) peers_ok = 0;
+  }
+  __syncthreads();
+  if (skip || !peers_ok) return;  // the epoch is not advanced: the status word tells the host
+  {
+    const int half = R >> 1;
+    const int items = half * p.M;
+    for (int e = threadIdx.x; e < items; e += SK_THREADS) {
+      const int m = e / half;
+      const int rl = (e - m * half) * 2;
+      const int n = n0 + static_cast<int>(crank) * R + rl;
+      if (n >= p.N) continue;
+      const long long off = static_cast<long long>(m) * p.N + n;
+      uint32_t part[SK_MAX_RANKS];
+#pragma unroll
+      for (int r = 0; r < SK_MAX_RANKS; ++r)
+        part[r] = r < p.world ? ld_relaxed_sys_u32(static_cast<const uint16_t*>(p.stage[r]) + off) : 0u;
+      uint32_t bw = 0u, rw = 0u;
+      if (p.bias) bw = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(p.bias) + n);
+      if (p.residual)
+        rw = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(p.residual) +
+                                                static_cast<long long>(m) * p.ldr + n);
+      float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+      for (int r = 0; r < SK_MAX_RANKS; ++r) {
+        if (r < p.world) {
+          const float2 v = p.bf16 ? unpack2<true>(part[r]) : unpack2<false>(part[r]);
+          acc.x += v.x;
+          acc.y += v.y;
+        }
+      }
+      if (p.bias) {
+        const float2 b2 = p.bf16 ? unpack2<true>(bw) : unpack2<false>(bw);
+        acc.x += b2.x;
+        acc.y += b2.y;
+      }
+      if (p.relu) {
+        acc.x = fmaxf(acc.x, 0.f);
+        acc.y = fmaxf(acc.y, 0.f);
+      }
+      if (p.residual) {
+        const float2 r2 = p.bf16 ? unpack2<true>(rw) : unpack2<false>(rw);
+        acc.x += r2.x;
+        acc.y += r2.y;
+      }
+      uint32_t* dst = reinterpret_cast<uint32_t*>(reinterpret_cast<uint16_t*>(p.C) + static_cast<long long>(m) * p.ldc + n);
+      *dst = p.bf16 ? pack2<true>(acc.x, acc.y) : pack2<false>(acc.x, acc.y);
+    }
+  }
+  if (threadIdx.x == 0) p.epoch_dev[blockIdx.x] = epoch;
 }
 
 static int g_skinny_sms = 0;
@@ -317,13 +413,11 @@ extern "C" int msq_gemm_skinny_split(int N, int K) {
   return split;
 }
 
-// X: [M, K] (row stride ldx), W: [N, K] (row stride ldw), C: [M, N] (row stride ldc), all 16-bit of one type,
-// strides in elements.  M <= 64; K and N multiples of 8; base pointers 16-byte aligned, C / residual / bias 4-byte
-// aligned with even strides.  Returns 0 on a successful launch, a negative code for unsupported arguments.
-extern "C" int msq_gemm_skinny(const void* X, const void* W, void* C, int M, int N, int K, long long ldx, long long ldw,
-                               long long ldc, int bf16, const void* bias, const void* residual, long long ldr, int relu,
-                               int* status, cudaStream_t stream) {
-  using namespace msq;
+namespace msq {
+
+static int skinny_common(const void* X, const void* W, void* C, int M, int N, int K, long long ldx, long long ldw,
+                         long long ldc, int bf16, const void* bias, const void* residual, long long ldr, int relu,
+                         int* status, cudaStream_t stream, SkinnyParams& p, int split) {
   if (M <= 0 || N <= 0) return 0;
   if (M > 64 || K <= 0 || (N & 7) || (K & 7) || (ldc & 1) || (ldr & 1) || (reinterpret_cast<uintptr_t>(C) & 3) ||
       (reinterpret_cast<uintptr_t>(residual) & 3) || (reinterpret_cast<uintptr_t>(bias) & 3))
@@ -334,9 +428,8 @@ extern "C" int msq_gemm_skinny(const void* X, const void* W, void* C, int M, int
   if (rc) return rc;
   rc = make_tmap_2d(&tmX, X, M, K, ldx, mp, bf16);
   if (rc) return rc - 100;
-  SkinnyParams p;
   p.M = M; p.N = N; p.K = K;
-  p.split = msq_gemm_skinny_split(N, K);
+  p.split = split;
   const int k_blocks = (K + SK_BK - 1) / SK_BK;
   p.k_blocks_per_cta = (k_blocks + p.split - 1) / p.split;
   p.C = C; p.ldc = ldc;
@@ -345,6 +438,52 @@ extern "C" int msq_gemm_skinny(const void* X, const void* W, void* C, int M, int
   if (mp == 16) return launch_skinny<16>(tmW, tmX, p, stream);
   if (mp == 32) return launch_skinny<32>(tmW, tmX, p, stream);
   return launch_skinny<64>(tmW, tmX, p, stream);
+}
+
+}  // namespace msq
+
+// X: [M, K] (row stride ldx), W: [N, K] (row stride ldw), C: [M, N] (row stride ldc), all 16-bit of one type,
+// strides in elements.  M <= 64; K and N multiples of 8; base pointers 16-byte aligned, C / residual / bias 4-byte
+// aligned with even strides.  Returns 0 on a successful launch, a negative code for unsupported arguments.
+extern "C" int msq_gemm_skinny(const void* X, const void* W, void* C, int M, int N, int K, long long ldx, long long ldw,
+                               long long ldc, int bf16, const void* bias, const void* residual, long long ldr, int relu,
+                               int* status, cudaStream_t stream) {
+  msq::SkinnyParams p = {};
+  p.world = 1;
+  return msq::skinny_common(X, W, C, M, N, K, ldx, ldw, ldc, bf16, bias, residual, ldr, relu, status, stream, p,
+                            msq_gemm_skinny_split(N, K));
+}
+
+// Row-parallel product of a tensor-parallel layer: C = epilogue(sum over ranks of X_r W_r^T), every rank ending
+// with the full sum.  `stage_ptrs[r]` is rank r's staging buffer for this call (16-bit [M][N], the same offset
+// of a symmetric allocation on every rank; the caller alternates between two such buffers from call to call),
+// `sig_ptrs[r]` rank r's flag words, of which this call uses CTAs * world starting at `flag_base`; `epoch_dev`
+// holds one counter per CTA (this rank's, zero-initialised together with the flags).  `split` fixes the cluster
+// size (0 = choose as msq_gemm_skinny does): every product that shares flags and counters must use one grid.
+// Returns the number of CTAs launched, or a negative code.
+extern "C" int msq_gemm_skinny_allreduce(const void* X, const void* W, void* C, int M, int N, int K, long long ldx,
+                                         long long ldw, long long ldc, int bf16, const void* bias, const void* residual,
+                                         long long ldr, int relu, int rank, int world, void* const* stage_ptrs,
+                                         void* const* sig_ptrs, long long flag_base, unsigned* epoch_dev, int split,
+                                         int* status, cudaStream_t stream) {
+  using namespace msq;
+  if (world < 1 || world > SK_MAX_RANKS || rank < 0 || rank >= world) return -6;
+  if (world > 1 && (!stage_ptrs || !sig_ptrs || !epoch_dev)) return -6;
+  SkinnyParams p = {};
+  p.world = world;
+  p.rank = rank;
+  for (int r = 0; r < world && world > 1; ++r) {
+    p.stage[r] = stage_ptrs[r];
+    p.sig[r] = static_cast<uint32_t*>(sig_ptrs[r]);
+    if ((reinterpret_cast<uintptr_t>(p.stage[r]) & 3) || !p.sig[r]) return -6;
+  }
+  p.flag_base = flag_base;
+  p.epoch_dev = epoch_dev;
+  if (split != 1 && split != 2 && split != 4 && split != 8) split = msq_gemm_skinny_split(N, K);
+  const int k_blocks = (K + SK_BK - 1) / SK_BK;
+  while (split > 1 && k_blocks < split) split >>= 1;
+  const int rc = skinny_common(X, W, C, M, N, K, ldx, ldw, ldc, bf16, bias, residual, ldr, relu, status, stream, p, split);
+  return rc < 0 ? rc : ((N + SK_BM - 1) / SK_BM) * split;
 }
 
 // Non-zero: the calling thread's launches of the few-row GEMM, the LayerNorm forward and the decode attention

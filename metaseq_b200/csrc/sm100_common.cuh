@@ -42,6 +42,41 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
 
 __device__ __forceinline__ uint32_t lane_id() { return threadIdx.x & 31; }
 
+// ------------------------------------------------- flags between GPUs
+// Arrival flags in peer-visible memory carry monotonically growing epochs: the writer publishes with a
+// system-scope release store after its data, the reader polls with system-scope acquire loads, for a
+// bounded time.
+__device__ __forceinline__ void st_release_sys(uint32_t* addr, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* addr) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+
+// Epochs only grow; the comparison is wrap-safe.
+__device__ __forceinline__ bool epoch_reached(uint32_t seen, uint32_t want) {
+  return static_cast<int32_t>(seen - want) >= 0;
+}
+
+__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, int* status) {
+  if (epoch_reached(ld_acquire_sys(flag), epoch)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if (epoch_reached(ld_acquire_sys(flag), epoch)) return true;
+    if ((++spins & 0x3f) == 0) {
+      if (status && *reinterpret_cast<volatile int*>(status) != 0) return false;
+      if (globaltimer_ns() - t0 > WAIT_NS_PEER) {
+        if (status) atomicCAS(status, 0, ST_TIMEOUT_PEER_FLAG);
+        return false;
+      }
+      __nanosleep(64);
+    }
+  }
+}
+
 // Programmatic dependent launch.  A kernel launched with the attribute may start while its predecessor in the
 // stream is still running; `dependents_wait` blocks until every earlier grid has completed and its writes are
 // visible, so everything before it may touch only memory that no earlier kernel of the stream writes (and must

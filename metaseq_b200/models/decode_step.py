@@ -14,8 +14,14 @@ replayed with one launch:
   and which the graph itself increments;
 * the append of the new key/value rows happens inside the attention kernel.
 
-Restrictions (the caller falls back to the module path otherwise): one tensor-parallel rank, 16-bit weights on
-a GPU, pre-norm layers with ReLU or GELU, head size 64 or 128, no document-separator attention.
+With tensor parallelism the graph holds the layers: the row-parallel products (attention output, second
+feed-forward matrix) run as one kernel each that also sums over the ranks (``parallel/symm.py:DecodeReduce``),
+while the vocabulary-parallel embedding and projection, one collective each per step, stay outside the graph
+on the library's collectives.
+
+Restrictions (the caller falls back to the module path otherwise): 16-bit weights on a GPU, pre-norm layers with
+ReLU or GELU, head size 64 or 128, no document-separator attention; with tensor parallelism at most 8 ranks and
+64 sequences.
 """
 from __future__ import annotations
 
@@ -42,7 +48,7 @@ class GraphedDecodeStep:
     """Static buffers, caches and the captured graph for ``rows`` sequences decoded together."""
 
     @staticmethod
-    def supported(decoder) -> bool:
+    def supported(decoder, rows: int = 1) -> bool:
         from metaseq_b200.models.transformer_decoder import UNSPECIFIED_DOC_SEP, ModelParallelTransformerDecoder as TransformerDecoder
 
         if not isinstance(decoder, TransformerDecoder):
@@ -50,7 +56,9 @@ class GraphedDecodeStep:
         w = decoder.embed_tokens.weight
         if not (w.is_cuda and w.dtype in (torch.float16, torch.bfloat16) and F.use_kernels(w)):
             return False
-        if _tp_world() != 1 or decoder.training or decoder.sequence_parallel:
+        if decoder.training or decoder.sequence_parallel:
+            return False
+        if _tp_world() > 1 and (_tp_world() > 8 or rows > 64 or w.shape[1] % 128 != 0):
             return False
         if decoder.self_attn_doc_sep != UNSPECIFIED_DOC_SEP or w.shape[1] % 8 != 0:
             return False
@@ -105,6 +113,24 @@ class GraphedDecodeStep:
         self.logits: Optional[torch.Tensor] = None
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self._length_hint = 1
+        self.tp = _tp_world()
+        self.reduce = None
+        if self.tp > 1:
+            from metaseq_b200.ops import _lib
+            from metaseq_b200.parallel.symm import DecodeReduce
+
+            D = w.shape[1]
+            self.reduce = decoder.__dict__.get("_decode_reduce")
+            if self.reduce is None:  # created by all ranks together; shared by the step objects of this decoder
+                self.reduce = DecodeReduce(mpu.get_tensor_model_parallel_group(), self.device, 64, D, self.dtype)
+                decoder.__dict__["_decode_reduce"] = self.reduce
+            lib = _lib.kernels()
+            first = decoder.layers[0]
+            # one grid for every row-parallel product of the step (they share flags and epoch counters)
+            self._split = min(lib.msq_gemm_skinny_split(D, first.self_attn.out_proj.weight.shape[1]),
+                              lib.msq_gemm_skinny_split(D, first.fc2.weight.shape[1]))
+            self.x_in = torch.zeros(rows, D, dtype=self.dtype, device=self.device)
+            self.x_out: Optional[torch.Tensor] = None
 
     # ------------------------------------------------------------------ state
     def new_state(self) -> Dict:
@@ -125,11 +151,8 @@ class GraphedDecodeStep:
         self._length_hint = max(1, filled)
 
     # ------------------------------------------------------------------- step
-    def _run(self) -> torch.Tensor:
-        with F.dependent_launch():  # every GEMM operand ``b`` below is a model weight
-            return self._run_chain()
-
-    def _run_chain(self) -> torch.Tensor:
+    def _embed(self) -> torch.Tensor:
+        """Embedding of ``self.tok`` at the next position of every row; advances the position counters."""
         dec = self.decoder
         tok = self.tok
         nonpad = tok.ne(self.pad)
@@ -137,31 +160,64 @@ class GraphedDecodeStep:
         pos_w = dec.embed_positions.weight if dec.embed_positions is not None else None
         positions = torch.where(nonpad, self.count + self.pad, torch.full_like(self.count, self.pad)) \
             if pos_w is not None else None
-        x = F.embed_fwd(tok, positions, dec.embed_tokens.weight, pos_w, dec.embed_scale)
+        w = dec.embed_tokens.weight
+        if self.tp == 1:
+            return F.embed_fwd(tok, positions, w, pos_w, dec.embed_scale)
+        import torch.distributed as dist
+
+        start = dec.embed_tokens.vocab_start_index
+        x = F.embed_fwd(tok, None, w, None, dec.embed_scale, start, start + w.shape[0], add_positions=False)
+        dist.all_reduce(x, group=mpu.get_tensor_model_parallel_group())
+        if pos_w is not None:
+            x = x + torch.nn.functional.embedding(positions, pos_w)
+        return x
+
+    def _row_parallel(self, x, lin, residual):
+        if self.tp == 1:
+            return F.gemm(x, lin.weight, bias=lin.bias, residual=residual)
+        return self.reduce.gemm_all_reduce(x, lin.weight, bias=lin.bias, residual=residual, split=self._split)
+
+    def _layers(self, x: torch.Tensor) -> torch.Tensor:
+        dec = self.decoder
         for layer, cache in zip(dec.layers, self.caches):
             a = layer.self_attn
             ln1, ln2 = layer.self_attn_layer_norm, layer.final_layer_norm
             h, _, _ = F.layer_norm_fwd(x, ln1.weight, ln1.bias, ln1.eps)
-            qkv = F.gemm(h, a.qkv_proj.weight, bias=a.qkv_proj.bias)  # (k | v | q) per row
+            qkv = F.gemm(h, a.qkv_proj.weight, bias=a.qkv_proj.bias)  # (k | v | q) per row, this rank's heads
             dp = qkv.shape[1] // 3
             ctx = F.decode_attn_step(qkv[:, 2 * dp:], qkv[:, 0:dp], qkv[:, dp:2 * dp], cache.k, cache.v, self.length,
                                      a.num_heads_partition, a.scaling, self._length_hint)
-            x = F.gemm(ctx, a.out_proj.weight, bias=a.out_proj.bias, residual=x)
+            x = self._row_parallel(ctx, a.out_proj, x)
             h, _, _ = F.layer_norm_fwd(x, ln2.weight, ln2.bias, ln2.eps)
             if layer.activation_name == "relu":
                 f = F.gemm(h, layer.fc1.weight, bias=layer.fc1.bias, relu=True)
             else:
                 f = torch.nn.functional.gelu(F.gemm(h, layer.fc1.weight, bias=layer.fc1.bias).float()).to(h.dtype)
-            x = F.gemm(f, layer.fc2.weight, bias=layer.fc2.bias, residual=x)
+            x = self._row_parallel(f, layer.fc2, x)
         fl = dec.layer_norm
         x, _, _ = F.layer_norm_fwd(x, fl.weight, fl.bias, fl.eps)
-        logits = F.gemm(x, dec.output_projection.weight)
         self.length.add_(1)
-        return logits
+        return x
+
+    def _logits(self, x: torch.Tensor) -> torch.Tensor:
+        local = F.gemm(x, self.decoder.output_projection.weight)
+        if self.tp == 1:
+            return local
+        from metaseq_b200.parallel import mappings
+
+        return mappings.gather_from_tensor_model_parallel_region(local)
+
+    def _run(self) -> torch.Tensor:
+        """What the graph holds: the whole step on one rank, the layers under tensor parallelism."""
+        with F.dependent_launch():  # every GEMM operand ``b`` in the chain is a model weight
+            if self.tp == 1:
+                return self._logits(self._layers(self._embed()))
+            return self._layers(self.x_in)
 
     def _capture(self) -> None:
         # Warm up on a side stream (lazy initialisation of libraries must not happen under capture), then
         # restore the device-side state that the warm-up advanced.
+        assert self.reduce is None or self.reduce.calls % 2 == 0
         saved = (self.count.clone(), self.length.clone())
         side = torch.cuda.Stream(device=self.device)
         side.wait_stream(torch.cuda.current_stream(self.device))
@@ -173,7 +229,12 @@ class GraphedDecodeStep:
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            self.logits = self._run()
+            out = self._run()
+        if self.tp == 1:
+            self.logits = out
+        else:
+            self.x_out = out
+            assert self.reduce.calls % 2 == 0  # replays keep the alternation of the staging buffers
         # the capture itself executes nothing, so the state is still the restored one
         self.graph = graph
 
@@ -184,9 +245,11 @@ class GraphedDecodeStep:
         if filled + 1 > self.capacity:
             raise RuntimeError(f"decode step beyond the cache capacity of {self.capacity} positions")
         self.tok.copy_(new_tokens)
+        if self.tp > 1:
+            self.x_in.copy_(self._embed())
         if self.graph is None:
             self._capture()
         self.graph.replay()
         for cache in self.caches:
             cache.length = filled + 1
-        return self.logits
+        return self.logits if self.tp == 1 else self._logits(self.x_out)

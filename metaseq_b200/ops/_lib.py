@@ -137,6 +137,7 @@ _OPTIONAL = {
     "msq_decode_attn_splits": [I, I, I],
     "msq_gemm_skinny": [P, P, P, I, I, I, L, L, L, I, P, P, L, I, P, P],
     "msq_gemm_skinny_split": [I, I],
+    "msq_gemm_skinny_allreduce": [P, P, P, I, I, I, L, L, L, I, P, P, L, I, I, I, P, P, L, P, I, P, P],
     "msq_set_dependent_launch": [I],
     "msq_scale_rows": [P, L, L, I, P, I, I, I, P],
     "msq_decode_attn_step": [P, P, P, L, P, P, P, P, I, I, I, P, I, L, L, L, L, L, F, I, P, I, P],

@@ -660,6 +660,58 @@ class TPComm:
         self.comm.close()
 
 
+class DecodeReduce:
+    """Row-parallel products of a tensor-parallel decode step: GEMM and the sum over ranks in one launch
+    (``msq_gemm_skinny_allreduce``).  Each owner CTA stores its partial rows in this rank's staging buffer,
+    exchanges an arrival flag with the same-index CTA of every peer and adds the rows of all ranks read over
+    NVLink.  The epochs of that exchange are counters in device memory that the kernel advances itself, so a
+    captured launch can be replayed; consecutive calls alternate between two staging buffers.  Every call
+    must use the same grid (same ``N``, one cluster size), which the caller fixes with ``split``.
+
+    Stands in for ``RowParallelLinear`` + ``all_reduce`` of the reference's incremental decoding
+    (metaseq/modules/megatron/mpu/layers.py:660-676)."""
+
+    MAX_CTAS = 320
+
+    def __init__(self, group, device, max_rows: int, cols: int, dtype=torch.float16, provider: str = "auto"):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.dtype = dtype
+        self.cols = int(cols)
+        self.max_rows = int(max_rows)
+        nbytes = self.max_rows * self.cols * torch.empty((), dtype=dtype).element_size()
+        self.heap = SymmetricHeap(group, 2 * (nbytes + 4096) + (1 << 16), device, provider=provider)
+        offs = [self.heap.alloc(nbytes), self.heap.alloc(nbytes)]
+        self._stage = [(ctypes.c_void_p * self.world)(*[p + off for p in self.heap.ptrs]) for off in offs]
+        self.flag_base = self.heap.alloc_flags(self.MAX_CTAS * self.world)
+        self.epochs = torch.zeros(self.MAX_CTAS, dtype=torch.int32, device=device)
+        self.calls = 0
+
+    def gemm_all_reduce(self, x, w, bias=None, residual=None, relu: bool = False, split: int = 0):
+        """``epilogue(sum over ranks of x_r @ w_r^T)``: ``x`` ``[M <= max_rows, K_local]``, ``w`` ``[cols, K_local]``."""
+        M, K = x.shape
+        N = w.shape[0]
+        assert N == self.cols and M <= self.max_rows and x.dtype == self.dtype and w.dtype == self.dtype
+        out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+        lib = _lib.kernels()
+        rc = lib.msq_gemm_skinny_allreduce(
+            _lib.ptr(x), _lib.ptr(w), _lib.ptr(out), M, N, K, x.stride(0), w.stride(0), out.stride(0),
+            int(x.dtype == torch.bfloat16), _lib.ptr(bias), _lib.ptr(residual),
+            residual.stride(0) if residual is not None else 0, int(relu), self.rank, self.world,
+            self._stage[self.calls & 1], self.heap.ptr_array, self.flag_base, _lib.ptr(self.epochs), int(split),
+            _lib.ptr(_lib.status_word(x.device)), _lib.stream_ptr())
+        if rc < 0:
+            raise RuntimeError(f"msq_gemm_skinny_allreduce failed ({rc})")
+        if rc > self.MAX_CTAS:
+            raise RuntimeError(f"msq_gemm_skinny_allreduce launched {rc} CTAs, more than the {self.MAX_CTAS} flag rows")
+        self.calls += 1
+        return out
+
+    def close(self):
+        self.heap.close()
+
+
 # ------------------------------------------------------------------ process-wide selection
 _COMM_BACKEND = "nccl"
 _TP_COMMS: Dict[tuple, TPComm] = {}

@@ -104,7 +104,7 @@ class SequenceGenerator(nn.Module):
         tokens[:, :start] = src_tokens.repeat_interleave(K, 0)
         graphed = None
         decoder = getattr(self.model, "decoder", None)
-        if self.decode_graph and decoder is not None and max_len > start and GraphedDecodeStep.supported(decoder):
+        if self.decode_graph and decoder is not None and max_len > start and GraphedDecodeStep.supported(decoder, n):
             graphed = GraphedDecodeStep.for_decoder(decoder, n, max_len)
             state = graphed.new_state()
         # ---------------------------------------------------------- prefill

@@ -236,3 +236,119 @@ def test_gemm_fused_with_tensor_parallel_reduction():
         results = mgr.dict()
         mp.spawn(_tp_worker, args=(world, _free_port(), results), nprocs=world, join=True)
         assert len(results) == world
+
+
+def _decode_worker(rank, world, port, results):
+    """Few-row GEMM fused with the sum over ranks (eager and replayed from a CUDA graph), then the graphed decode
+    step of a tensor-parallel model against the module path."""
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from metaseq_b200 import options, tasks
+        from metaseq_b200.dataclass.utils import convert_namespace_to_config
+        from metaseq_b200.models.decode_step import GraphedDecodeStep
+        from metaseq_b200.ops import _lib
+        from metaseq_b200.ops import functional as F
+        from metaseq_b200.parallel import mpu
+        from metaseq_b200.parallel.symm import DecodeReduce
+
+        dev = torch.device("cuda", rank)
+        mpu.initialize_model_parallel(world)
+        mpu.model_parallel_cuda_manual_seed(7)
+        # ---- kernel level
+        N, M = 1024, 24
+        red = DecodeReduce(dist.group.WORLD, dev, 64, N, torch.float16)
+        lib = _lib.kernels()
+        split = min(lib.msq_gemm_skinny_split(N, 512), lib.msq_gemm_skinny_split(N, 2048))
+        bias = torch.randn(N, device=dev, dtype=torch.float16, generator=torch.Generator(device=dev).manual_seed(1))
+        res = torch.randn(M, N, device=dev, dtype=torch.float16, generator=torch.Generator(device=dev).manual_seed(2))
+
+        def reference(x, w, use_res):
+            part = x.float() @ w.float().t()
+            part = part.half().float()  # each rank contributes its rounded partial sum
+            dist.all_reduce(part)
+            return part + bias.float() + (res.float() if use_res else 0.0)
+
+        for step in range(6):
+            K = 512 if step % 2 == 0 else 2048
+            g = torch.Generator(device=dev).manual_seed(50 + 10 * step + rank)
+            x = torch.randn(M, K, device=dev, dtype=torch.float16, generator=g)
+            w = torch.randn(N, K, device=dev, dtype=torch.float16, generator=g) * (K ** -0.5)
+            y = red.gemm_all_reduce(x, w, bias=bias, residual=res if step % 3 else None, split=split)
+            ref = reference(x, w, bool(step % 3))
+            torch.cuda.synchronize()
+            assert (y.float() - ref).abs().max().item() <= 2e-2, f"fused GEMM + all-reduce mismatch at call {step}"
+        # replayed from a graph: four products per replay, inputs refreshed in place between replays
+        xs = [torch.zeros(M, K, device=dev, dtype=torch.float16) for K in (512, 2048, 512, 2048)]
+        ws = [torch.randn(N, K, device=dev, dtype=torch.float16, generator=torch.Generator(device=dev).manual_seed(9 + i + 4 * rank))
+              * (K ** -0.5) for i, K in enumerate((512, 2048, 512, 2048))]
+
+        def four():
+            return [red.gemm_all_reduce(x, w, bias=bias, residual=res, split=split) for x, w in zip(xs, ws)]
+
+        with F.dependent_launch():
+            four()
+            torch.cuda.synchronize()
+            dist.barrier()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                outs = four()
+        for it in range(4):
+            for i, x in enumerate(xs):
+                x.copy_(torch.randn(x.shape, device=dev, dtype=torch.float16,
+                                    generator=torch.Generator(device=dev).manual_seed(1000 + 100 * it + 10 * i + rank)))
+            graph.replay()
+            torch.cuda.synchronize()
+            for x, w, y in zip(xs, ws, outs):
+                ref = reference(x, w, True)
+                assert (y.float() - ref).abs().max().item() <= 2e-2, f"graph replay {it}: mismatch"
+        assert _lib.check_status(dev) == 0
+        # ---- model level
+        parser = options.get_training_parser()
+        ns = options.parse_args_and_arch(parser, input_args=[
+            "--task", "dummy_lm", "--dict-size", "2040", "--tokens-per-sample", "128", "--batch-size", "1",
+            "--arch", "transformer_lm_megatron", "--decoder-layers", "3", "--decoder-embed-dim", "256",
+            "--decoder-ffn-embed-dim", "1024", "--decoder-attention-heads", "4", "--decoder-learned-pos",
+            "--activation-fn", "relu", "--share-decoder-input-output-embed", "--no-scale-embedding", "--dropout", "0.0",
+            "--attention-dropout", "0.0", "--criterion", "vocab_parallel_cross_entropy", "--optimizer", "adam",
+            "--lr", "1e-3", "--memory-efficient-fp16", "--tensor-parallel-init-model-on-gpu",
+            "--distributed-world-size", str(world), "--model-parallel-size", str(world)])
+        cfg = convert_namespace_to_config(ns)
+        task = tasks.setup_task(cfg.task)
+        torch.manual_seed(3)
+        model = task.build_model(cfg.model).half().cuda().eval()
+        model.make_generation_fast_()
+        dec = model.decoder
+        assert GraphedDecodeStep.supported(dec, 3)
+        tokens = torch.randint(4, 2000, (3, 40), device=dev, generator=torch.Generator(device=dev).manual_seed(11))
+        with torch.no_grad():
+            full, _ = model(tokens)  # gathered logits [3, 40, V]
+            runner = GraphedDecodeStep.for_decoder(dec, 3, 64)
+            model(tokens[:, :24], incremental_state=runner.new_state())
+            runner.begin(tokens[:, :24])
+            for t in range(24, 39):
+                logits = runner.step(tokens[:, t])
+                assert logits.shape == full[:, t].shape
+                torch.testing.assert_close(logits.float(), full[:, t].float(), rtol=5e-2, atol=5e-2)
+        assert runner.reduce is not None and runner.reduce.calls > 0
+        assert _lib.check_status(dev) == 0
+        results[rank] = True
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_decode_gemm_fused_with_all_reduce_and_graphed_tensor_parallel_step():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least two GPUs")
+    import torch.multiprocessing as mp
+
+    world = 2
+    with mp.Manager() as mgr:
+        results = mgr.dict()
+        mp.spawn(_decode_worker, args=(world, _free_port(), results), nprocs=world, join=True)
+        assert all(results.get(r) for r in range(world))
