@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
 
 import numpy as np
 import torch
@@ -22,17 +23,34 @@ from metaseq_b200.ops import _lib
 from metaseq_b200.ops import functional as F
 
 
-def build(arch: str, max_positions: int):
+def init_tensor_parallel() -> int:
+    """Under ``torchrun`` every rank holds a 1 / WORLD_SIZE slice of the model (tensor parallelism)."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1:
+        import torch.distributed as dist
+
+        from metaseq_b200.parallel import mpu
+
+        local = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        mpu.initialize_model_parallel(world)
+        mpu.model_parallel_cuda_manual_seed(1)
+    return world
+
+
+def build(arch: str, max_positions: int, tp: int = 1):
     parser = options.get_training_parser()
     ns = options.parse_args_and_arch(parser, input_args=[
         "--task", "dummy_lm", "--dict-size", "50268", "--tokens-per-sample", str(max_positions), "--batch-size", "1",
         "--arch", arch, "--criterion", "vocab_parallel_cross_entropy", "--optimizer", "adam", "--lr", "1e-3",
-        "--memory-efficient-fp16", "--tensor-parallel-init-model-on-gpu", "--distributed-world-size", "1",
-        "--dropout", "0.0", "--attention-dropout", "0.0"])
+        "--memory-efficient-fp16", "--tensor-parallel-init-model-on-gpu", "--distributed-world-size", str(tp),
+        "--model-parallel-size", str(tp), "--dropout", "0.0", "--attention-dropout", "0.0"])
     cfg = convert_namespace_to_config(ns)
     task = tasks.setup_task(cfg.task)
     torch.manual_seed(1)
     model = task.build_model(cfg.model).half().cuda().eval()
+    model.make_generation_fast_()
     return cfg, task, model
 
 
@@ -59,12 +77,15 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--repeats", type=int, default=3)
     ap.add_argument("--kernel-backend", default="auto", choices=["auto", "torch"])
+    ap.add_argument("--no-decode-graph", action="store_true", help="decode through the module tree")
     ap.add_argument("--graph-replays", type=int, default=0,
                     help="instead of whole generate calls: one prefill, then this many replays of the captured "
                          "decode step, timed together (the workload for a per-kernel launch list)")
     args = ap.parse_args(argv)
     F.set_backend(args.kernel_backend)
-    cfg, task, model = build(args.arch, args.prompt + args.gen + 8)
+    tp = init_tensor_parallel()
+    rank0 = int(os.environ.get("RANK", "0")) == 0
+    cfg, task, model = build(args.arch, args.prompt + args.gen + 8, tp)
     rng = np.random.RandomState(0)
     prompts = torch.from_numpy(rng.randint(100, 50000, size=(args.batch, args.prompt))).cuda()
     sample = {"net_input": {"src_tokens": prompts}}
@@ -72,14 +93,14 @@ def main(argv=None):
     def call(n_new):
         total = args.prompt + n_new
         sg = SequenceGenerator([model], task.target_dictionary, beam_size=1, max_len_b=total, min_len=total,
-                               temperature=1.0, topp=-1)
+                               temperature=1.0, topp=-1, decode_graph=not args.no_decode_graph)
         with torch.no_grad():
             return sg.generate([model], sample)
 
     if args.graph_replays > 0:
         from metaseq_b200.models.decode_step import GraphedDecodeStep
 
-        assert GraphedDecodeStep.supported(model.decoder), "the graphed step needs the kernel backend"
+        assert GraphedDecodeStep.supported(model.decoder, args.batch), "the graphed step needs the kernel backend"
         runner = GraphedDecodeStep.for_decoder(model.decoder, args.batch, args.prompt + args.graph_replays + 8)
         with torch.no_grad():
             model(prompts, incremental_state=runner.new_state())
@@ -93,9 +114,11 @@ def main(argv=None):
                 runner.step(nxt)
             e.record()
             torch.cuda.synchronize()
-        print(json.dumps(dict(metric="decode_graph_step_ms", arch=args.arch, batch=args.batch, cached=args.prompt,
-                              replays=args.graph_replays, ms_per_replay=round(s.elapsed_time(e) / args.graph_replays, 4),
-                              kernel_status=_lib.check_status(torch.device("cuda")))), flush=True)
+        if rank0:
+            print(json.dumps(dict(metric="decode_graph_step_ms", arch=args.arch, batch=args.batch, cached=args.prompt,
+                                  replays=args.graph_replays, tensor_parallel=tp,
+                                  ms_per_replay=round(s.elapsed_time(e) / args.graph_replays, 4),
+                                  kernel_status=_lib.check_status(torch.device("cuda")))), flush=True)
         return
     _lib.reset_launch_count()
     t1 = timed(lambda: call(1), args.warmup, args.repeats)
@@ -105,8 +128,23 @@ def main(argv=None):
                prefill_ms=round(t1, 2), total_ms=round(tn, 2), decode_ms_per_token=round(per_tok, 3),
                decode_tokens_per_s=round(args.batch / per_tok * 1e3, 1), kernel_backend=args.kernel_backend,
                kernel_launches=_lib.launch_count(), kernel_status=_lib.check_status(torch.device("cuda")),
+               tensor_parallel=tp, decode_graph=not args.no_decode_graph,
                dtype="fp16", data="synthetic uniform token ids, random-init weights")
-    print(json.dumps(out), flush=True)
+    if tp > 1:
+        import torch.distributed as dist
+
+        worst = torch.tensor([t1, tn], device="cuda")
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)  # the slowest rank's device time
+        t1, tn = worst.tolist()
+        per_tok = (tn - t1) / max(1, args.gen - 1)
+        out.update(prefill_ms=round(t1, 2), total_ms=round(tn, 2), decode_ms_per_token=round(per_tok, 3),
+                   decode_tokens_per_s=round(args.batch / per_tok * 1e3, 1))
+    if rank0:
+        print(json.dumps(out), flush=True)
+    if tp > 1:
+        import torch.distributed as dist
+
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":
