@@ -44,6 +44,8 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--out", default=None)
     ap.add_argument("--transport", default="ce", choices=["ce", "sm"])
+    ap.add_argument("--decode-dim", type=int, default=4096, help="model width for the decode GEMM + all-reduce timing")
+    ap.add_argument("--decode-rows", type=int, default=32)
     args = ap.parse_args(argv)
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -85,6 +87,56 @@ def main(argv=None):
         if comm.heap.multicast_ptr:
             rec(f"all_reduce_in_switch_{nbytes >> 10}KiB", _time(lambda: comm.all_reduce(x, use_multicast=True), args.iters), nccl,
                 2 * nbytes * (world - 1) / world)
+    # ---- decode: few-row GEMM fused with the sum over ranks, launched from a graph, against the same product
+    # without the exchange and against the product followed by an NCCL all-reduce
+    from metaseq_b200.ops import functional as F
+    from metaseq_b200.parallel.symm import DecodeReduce
+
+    D, rows = args.decode_dim, args.decode_rows
+    red = DecodeReduce(dist.group.WORLD, dev, 64, D, torch.float16)
+    lib = _lib.kernels()
+    shapes = [("out_proj", D // world), ("fc2", 4 * D // world)]
+    split = min(lib.msq_gemm_skinny_split(D, k) for _, k in shapes)
+    res = torch.randn(rows, D, device=dev, dtype=torch.float16)
+    for name, K in shapes:
+        copies = max(2, int(300e6 / (D * K * 2)) + 1)
+        ws = [torch.randn(D, K, device=dev, dtype=torch.float16) * 0.02 for _ in range(copies)]
+        x = torch.randn(rows, K, device=dev, dtype=torch.float16)
+        launches = 24  # even: the staging halves keep alternating across replays
+
+        def graphed(fn, dependent):
+            import contextlib
+
+            for i in range(2):
+                fn(i)
+            torch.cuda.synchronize()
+            dist.barrier()
+            g = torch.cuda.CUDAGraph()
+            with (F.dependent_launch() if dependent else contextlib.nullcontext()):
+                with torch.cuda.graph(g):
+                    for i in range(launches):
+                        fn(i % copies)
+            return _time(g.replay, args.iters) / launches
+
+        plain = graphed(lambda i: F.gemm(x, ws[i], residual=res), True)
+        fused = graphed(lambda i: red.gemm_all_reduce(x, ws[i], residual=res, split=split), True)
+        fused_nodep = graphed(lambda i: red.gemm_all_reduce(x, ws[i], residual=res, split=split), False)
+
+        def gemm_then_nccl(i):
+            y = F.gemm(x, ws[i])
+            dist.all_reduce(y)
+            return y.add_(res)
+
+        for i in range(3):
+            gemm_then_nccl(i)
+        nccl = _time(lambda: [gemm_then_nccl(i % copies) for i in range(launches)], args.iters) / launches
+        r = dict(op=f"decode_gemm_allreduce_{name}", n_gpus=world, rows=rows, N=D, K_local=K, cluster=split,
+                 ms=round(fused, 5), ms_ordinary_launch=round(fused_nodep, 5), gemm_only_ms=round(plain, 5),
+                 gemm_then_nccl_eager_ms=round(nccl, 5), exchange_bytes=rows * D * 2 * (world - 1))
+        results.append(r)
+        if rank == 0:
+            print(json.dumps(r), flush=True)
+        del ws
     bad = _lib.check_status(dev)
     if rank == 0:
         summary = dict(provider=comm.heap.provider, transport=args.transport, multicast=bool(comm.heap.multicast_ptr), kernel_status=bad,

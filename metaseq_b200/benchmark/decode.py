@@ -101,7 +101,7 @@ def main(argv=None):
         from metaseq_b200.models.decode_step import GraphedDecodeStep
 
         assert GraphedDecodeStep.supported(model.decoder, args.batch), "the graphed step needs the kernel backend"
-        runner = GraphedDecodeStep.for_decoder(model.decoder, args.batch, args.prompt + args.graph_replays + 8)
+        runner = GraphedDecodeStep.for_decoder(model.decoder, args.batch, args.prompt + 2 * args.graph_replays + 8)
         with torch.no_grad():
             model(prompts, incremental_state=runner.new_state())
             runner.begin(prompts)
@@ -114,10 +114,18 @@ def main(argv=None):
                 runner.step(nxt)
             e.record()
             torch.cuda.synchronize()
+            # the captured part alone (under tensor parallelism the embedding and the projection are outside it)
+            s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s2.record()
+            for _ in range(args.graph_replays):
+                runner.graph.replay()
+            e2.record()
+            torch.cuda.synchronize()
         if rank0:
             print(json.dumps(dict(metric="decode_graph_step_ms", arch=args.arch, batch=args.batch, cached=args.prompt,
                                   replays=args.graph_replays, tensor_parallel=tp,
                                   ms_per_replay=round(s.elapsed_time(e) / args.graph_replays, 4),
+                                  ms_graph_only=round(s2.elapsed_time(e2) / args.graph_replays, 4),
                                   kernel_status=_lib.check_status(torch.device("cuda")))), flush=True)
         return
     _lib.reset_launch_count()

@@ -16,14 +16,17 @@
 //     per SM.
 //
 // Tensor parallelism: a row-parallel product (K sharded over the ranks) ends in a sum over the ranks.  Here the
-// owner CTA stores its finished partial rows (16-bit, like the all-reduce payload of the reference) in this
-// rank's staging buffer, publishes an arrival flag to the same-index CTA of every peer, waits (bounded) for
-// theirs, then reads the same rows from every rank's staging buffer over NVLink, adds them in fp32 and applies
-// bias and residual: GEMM and all-reduce in one launch, tile by tile, without a grid-wide or rank-wide barrier.
-// Epochs live in device memory (one counter per CTA, advanced by the kernel), so the launch can be replayed from a
-// CUDA graph; consecutive products alternate between two staging halves (chosen by the caller), which together
-// with the per-CTA handshake keeps a fast rank from overwriting rows a slow rank is still reading, provided
-// every such product of the sequence uses the same grid.
+// owner CTA stores its finished partial rows (16-bit, like the all-reduce payload of the reference) straight into
+// a receive buffer of every rank over NVLink, each 4 bytes of payload paired with a 4-byte epoch in one 8-byte
+// unit, and then polls its own receive buffer until the units of every source rank carry the epoch: the data
+// is its own arrival flag, so the exchange costs one one-way store latency, with no fence, no separate flag and
+// no remote load.  It then adds the ranks' rows in fp32 and applies bias and residual: GEMM and all-reduce in
+// one launch, tile by tile, without a grid-wide or rank-wide barrier.  Epochs live in device memory (one counter
+// per CTA, advanced by the kernel), so the launch can be replayed from a CUDA graph; consecutive products
+// alternate between two receive buffers (chosen by the caller), which keeps a fast rank from overwriting units
+// that a slow rank has not consumed yet, provided every such product of the sequence uses the same grid (CTA i
+// sends product n+2 only after it received product n+1 from CTA i of every peer, which they send after consuming
+// product n).
 //
 // The reference runs these products as torch.matmul plus separate bias / activation / residual kernels
 // (metaseq/modules/megatron/mpu/layers.py:290,373; metaseq/modules/feedforward.py:21-22) and the sum over ranks
@@ -56,10 +59,11 @@ struct SkinnyParams {
   int* status;
   // sum over tensor-parallel ranks (world <= 1: none)
   int world, rank;
-  void* stage[SK_MAX_RANKS];     // every rank's staging buffer for this product, 16-bit [M][N]
-  uint32_t* sig[SK_MAX_RANKS];   // every rank's flag words
-  long long flag_base;           // first flag word of this product: one per (CTA, source rank)
+  void* recv_buf[SK_MAX_RANKS];  // every rank's receive buffer for this product: [world][slot_rows][N] 4-byte cells,
+                                 // cell (src, m, n) = {two 16-bit values for columns n, n+1 | epoch} at even n
+  int slot_rows;                 // rows reserved per source rank
   uint32_t* epoch_dev;           // this rank's per-CTA epoch counters
+  long long* prof;               // debug: per-CTA cycle stamps (see msq_gemm_skinny_set_prof)
 };
 
 constexpr int SK_BM = 128;  // rows of W per tile
@@ -99,11 +103,18 @@ __device__ __forceinline__ void st_cluster_f32(uint32_t remote_addr, float v) {
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote_addr), "f"(v) : "memory");
 }
 
-// 4-byte load of a row pair from a staging buffer that may live on another GPU: system scope, never from L1.
-__device__ __forceinline__ uint32_t ld_relaxed_sys_u32(const void* p) {
-  uint32_t v;
-  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+// 16-byte load of two {payload, epoch} units that a peer GPU writes: never from L1.
+__device__ __forceinline__ uint4 ld_units(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
   return v;
+}
+// 16-byte store of two units into (possibly) another GPU's memory.  Each 8-byte half is self-validating, so no
+// ordering between stores is needed.
+__device__ __forceinline__ void st_units(void* p, uint32_t d0, uint32_t d1, uint32_t epoch) {
+  asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(d0), "r"(epoch), "r"(d1), "r"(epoch)
+               : "memory");
 }
 
 template <int MP>
@@ -137,6 +148,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   // read and cleared it.  The CTA still walks through the cluster barriers below, because its peers may have
   // read the word before it was set and will address this CTA's shared memory.
   const bool skip = p.status && *reinterpret_cast<volatile int*>(p.status) != 0;
+  const long long prof_t0 = p.prof ? clock64() : 0;
   dependents_launch();
 
   const int head = (!skip) ? min(STAGES, my_kb) : 0;
@@ -258,12 +270,14 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
   dependents_wait();   // the residual is an output of the preceding kernels, and C may be memory they still read
+  const long long prof_wait = p.prof ? clock64() : 0;
   cluster_sync_all();  // barrier 2: every partial row has reached its owner
+  const long long prof_sum = p.prof ? clock64() : 0;
 
-  __shared__ int peers_ok;
   const bool reduce_ranks = p.world > 1;
   const uint32_t epoch = reduce_ranks ? p.epoch_dev[blockIdx.x] + 1u : 0u;
-  if (!skip) {
+  long long prof_sent = 0;
+  if (!skip && !reduce_ranks) {
     // This CTA finishes rows [crank*R, crank*R + R) of the tile, two adjacent rows (= output columns) per item.
     const int half = R >> 1;
     const int items = half * p.M;
@@ -273,24 +287,16 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       const int n = n0 + static_cast<int>(crank) * R + rl;
       if (n >= p.N) continue;  // N is even, so a pair is inside or outside as a whole
       uint32_t bw = 0u, rw = 0u;  // requested before the sum so that their latency overlaps it
-      if (!reduce_ranks) {
-        if (p.bias) bw = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(p.bias) + n);
-        if (p.residual)
-          rw = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(p.residual) +
-                                                  static_cast<long long>(m) * p.ldr + n);
-      }
+      if (p.bias) bw = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(p.bias) + n);
+      if (p.residual)
+        rw = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(p.residual) +
+                                                static_cast<long long>(m) * p.ldr + n);
       float2 acc = make_float2(0.f, 0.f);
       for (int j = 0; j < p.split; ++j) {
         const float2 v = *reinterpret_cast<const float2*>(recv + (j * MP + m) * R + rl);
         acc.x += v.x;
         acc.y += v.y;
       }
-      if (reduce_ranks) {
-        // this rank's share of the sum goes to its staging buffer; the epilogue follows the exchange
-        uint32_t* dst = reinterpret_cast<uint32_t*>(static_cast<uint16_t*>(p.stage[p.rank]) + static_cast<long long>(m) * p.N + n);
-        *dst = p.bf16 ? pack2<true>(acc.x, acc.y) : pack2<false>(acc.x, acc.y);
-        continue;
-      }
       if (p.bias) {
         const float2 b2 = p.bf16 ? unpack2<true>(bw) : unpack2<false>(bw);
         acc.x += b2.x;
@@ -309,65 +315,116 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       *dst = p.bf16 ? pack2<true>(acc.x, acc.y) : pack2<false>(acc.x, acc.y);
     }
   }
-  if (!reduce_ranks) return;
+  if (!reduce_ranks || skip) return;
 
   // ------------------------------------------------------- sum over ranks
-  if (threadIdx.x == 0) peers_ok = 1;
-  __syncthreads();  // every row of this CTA is in the staging buffer
-  if (!skip && threadIdx.x < p.world) {
-    const long long word = p.flag_base + static_cast<long long>(blockIdx.x) * p.world;
-    __threadfence_system();
-    st_release_sys(p.sig[threadIdx.x] + word + p.rank, epoch);
-    if (!wait_flag(p.sig[p.rank] + word + threadIdx.x, epoch, p.status)) peers_ok = 0;
-  }
-  __syncthreads();
-  if (skip || !peers_ok) return;  // the epoch is not advanced: the status word tells the host
-  {
-    const int half = R >> 1;
-    const int items = half * p.M;
-    for (int e = threadIdx.x; e < items; e += SK_THREADS) {
-      const int m = e / half;
-      const int rl = (e - m * half) * 2;
-      const int n = n0 + static_cast<int>(crank) * R + rl;
-      if (n >= p.N) continue;
-      const long long off = static_cast<long long>(m) * p.N + n;
-      uint32_t part[SK_MAX_RANKS];
+  // 8 adjacent columns of one row per item: R is a multiple of 16 and N of 8, so a chunk is inside or outside N as
+  // a whole.  A chunk is four {payload, epoch} units = two 16-byte stores per destination rank.
+  const int chunks = R >> 3;
+  const int items = chunks * p.M;
+  for (int e = threadIdx.x; e < items; e += SK_THREADS) {
+    const int m = e / chunks;
+    const int rl = (e - m * chunks) * 8;
+    const int n = n0 + static_cast<int>(crank) * R + rl;
+    if (n >= p.N) continue;
+    uint32_t d[4];
 #pragma unroll
-      for (int r = 0; r < SK_MAX_RANKS; ++r)
-        part[r] = r < p.world ? ld_relaxed_sys_u32(static_cast<const uint16_t*>(p.stage[r]) + off) : 0u;
-      uint32_t bw = 0u, rw = 0u;
-      if (p.bias) bw = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(p.bias) + n);
-      if (p.residual)
-        rw = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(p.residual) +
-                                                static_cast<long long>(m) * p.ldr + n);
+    for (int q = 0; q < 4; ++q) {
       float2 acc = make_float2(0.f, 0.f);
+      for (int j = 0; j < p.split; ++j) {
+        const float2 v = *reinterpret_cast<const float2*>(recv + (j * MP + m) * R + rl + 2 * q);
+        acc.x += v.x;
+        acc.y += v.y;
+      }
+      d[q] = p.bf16 ? pack2<true>(acc.x, acc.y) : pack2<false>(acc.x, acc.y);
+    }
+    const long long cell = (static_cast<long long>(p.rank) * p.slot_rows + m) * p.N + n;  // 4-byte cells
 #pragma unroll
-      for (int r = 0; r < SK_MAX_RANKS; ++r) {
-        if (r < p.world) {
-          const float2 v = p.bf16 ? unpack2<true>(part[r]) : unpack2<false>(part[r]);
-          acc.x += v.x;
-          acc.y += v.y;
-        }
+    for (int r = 0; r < SK_MAX_RANKS; ++r) {
+      if (r < p.world) {
+        uint8_t* dst = static_cast<uint8_t*>(p.recv_buf[r]) + cell * 4;
+        st_units(dst, d[0], d[1], epoch);
+        st_units(dst + 16, d[2], d[3], epoch);
       }
-      if (p.bias) {
-        const float2 b2 = p.bf16 ? unpack2<true>(bw) : unpack2<false>(bw);
-        acc.x += b2.x;
-        acc.y += b2.y;
-      }
-      if (p.relu) {
-        acc.x = fmaxf(acc.x, 0.f);
-        acc.y = fmaxf(acc.y, 0.f);
-      }
-      if (p.residual) {
-        const float2 r2 = p.bf16 ? unpack2<true>(rw) : unpack2<false>(rw);
-        acc.x += r2.x;
-        acc.y += r2.y;
-      }
-      uint32_t* dst = reinterpret_cast<uint32_t*>(reinterpret_cast<uint16_t*>(p.C) + static_cast<long long>(m) * p.ldc + n);
-      *dst = p.bf16 ? pack2<true>(acc.x, acc.y) : pack2<false>(acc.x, acc.y);
     }
   }
-  if (threadIdx.x == 0) p.epoch_dev[blockIdx.x] = epoch;
+  if (p.prof) prof_sent = clock64();
+  bool all_ok = true;
+  for (int e = threadIdx.x; e < items && all_ok; e += SK_THREADS) {
+    const int m = e / chunks;
+    const int n = n0 + static_cast<int>(crank) * R + (e - m * chunks) * 8;
+    if (n >= p.N) continue;
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int r = 0; r < p.world && all_ok; ++r) {
+      const uint8_t* src = static_cast<const uint8_t*>(p.recv_buf[p.rank]) +
+                           ((static_cast<long long>(r) * p.slot_rows + m) * p.N + n) * 4;
+      uint4 u0 = ld_units(src), u1 = ld_units(src + 16);
+      if (u0.y != epoch || u0.w != epoch || u1.y != epoch || u1.w != epoch) {
+        const unsigned long long t0 = globaltimer_ns();
+        uint32_t spins = 0;
+        while (true) {
+          u0 = ld_units(src);
+          u1 = ld_units(src + 16);
+          if (u0.y == epoch && u0.w == epoch && u1.y == epoch && u1.w == epoch) break;
+          if ((++spins & 0x3f) == 0) {
+            if ((p.status && *reinterpret_cast<volatile int*>(p.status) != 0) || globaltimer_ns() - t0 > WAIT_NS_PEER) {
+              if (p.status) atomicCAS(p.status, 0, ST_TIMEOUT_PEER_FLAG);
+              all_ok = false;
+              break;
+            }
+          }
+        }
+      }
+      const uint32_t w4[4] = {u0.x, u0.z, u1.x, u1.z};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 v = p.bf16 ? unpack2<true>(w4[j]) : unpack2<false>(w4[j]);
+        acc[2 * j] += v.x;
+        acc[2 * j + 1] += v.y;
+      }
+    }
+    if (!all_ok) break;
+    const uint16_t* bias16 = reinterpret_cast<const uint16_t*>(p.bias);
+    const uint16_t* res16 = reinterpret_cast<const uint16_t*>(p.residual);
+    uint32_t out4[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float a0 = acc[2 * j], a1 = acc[2 * j + 1];
+      if (bias16) {
+        const uint32_t bw = *reinterpret_cast<const uint32_t*>(bias16 + n + 2 * j);
+        const float2 b2 = p.bf16 ? unpack2<true>(bw) : unpack2<false>(bw);
+        a0 += b2.x;
+        a1 += b2.y;
+      }
+      if (p.relu) {
+        a0 = fmaxf(a0, 0.f);
+        a1 = fmaxf(a1, 0.f);
+      }
+      if (res16) {
+        const uint32_t rw = *reinterpret_cast<const uint32_t*>(res16 + static_cast<long long>(m) * p.ldr + n + 2 * j);
+        const float2 r2 = p.bf16 ? unpack2<true>(rw) : unpack2<false>(rw);
+        a0 += r2.x;
+        a1 += r2.y;
+      }
+      out4[j] = p.bf16 ? pack2<true>(a0, a1) : pack2<false>(a0, a1);
+    }
+    uint32_t* dst = reinterpret_cast<uint32_t*>(reinterpret_cast<uint16_t*>(p.C) + static_cast<long long>(m) * p.ldc + n);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) dst[j] = out4[j];
+  }
+  // The counter advances only when every thread got its units: after a timeout the status word tells the host.
+  if (__syncthreads_and(all_ok ? 1 : 0) && threadIdx.x == 0) p.epoch_dev[blockIdx.x] = epoch;
+  if (p.prof && threadIdx.x == 0) {
+    long long* o = p.prof + static_cast<long long>(blockIdx.x) * 6;
+    o[0] = prof_wait - prof_t0;   // start -> previous kernels done, own K range multiplied (before the cluster barrier)
+    o[1] = prof_sum - prof_wait;  // cluster barrier
+    o[2] = prof_sent - prof_sum;  // cluster sum, units stored to every rank
+    o[3] = clock64() - prof_sent; // units of every rank received, epilogue
+    o[4] = 0;
+    o[5] = clock64() - prof_t0;
+  }
 }
 
 static int g_skinny_sms = 0;
@@ -391,6 +448,7 @@ static int launch_skinny(const CUtensorMap& tmW, const CUtensorMap& tmX, const S
 }
 
 thread_local int g_dependent_launch = 0;
+static long long* g_skinny_prof = nullptr;
 
 }  // namespace msq
 
@@ -455,36 +513,38 @@ extern "C" int msq_gemm_skinny(const void* X, const void* W, void* C, int M, int
 }
 
 // Row-parallel product of a tensor-parallel layer: C = epilogue(sum over ranks of X_r W_r^T), every rank ending
-// with the full sum.  `stage_ptrs[r]` is rank r's staging buffer for this call (16-bit [M][N], the same offset
-// of a symmetric allocation on every rank; the caller alternates between two such buffers from call to call),
-// `sig_ptrs[r]` rank r's flag words, of which this call uses CTAs * world starting at `flag_base`; `epoch_dev`
-// holds one counter per CTA (this rank's, zero-initialised together with the flags).  `split` fixes the cluster
-// size (0 = choose as msq_gemm_skinny does): every product that shares flags and counters must use one grid.
-// Returns the number of CTAs launched, or a negative code.
+// with the full sum.  `recv_ptrs[r]` is rank r's receive buffer for this call: world * slot_rows * N 4-byte cells
+// (zero-initialised once; the same offset of a symmetric allocation on every rank; the caller alternates between
+// two such buffers from call to call); `epoch_dev` holds one zero-initialised counter per CTA.  `split` fixes the
+// cluster size (0 = choose as msq_gemm_skinny does): every product that shares buffers and counters must use one
+// grid.  Returns the number of CTAs launched, or a negative code.
 extern "C" int msq_gemm_skinny_allreduce(const void* X, const void* W, void* C, int M, int N, int K, long long ldx,
                                          long long ldw, long long ldc, int bf16, const void* bias, const void* residual,
-                                         long long ldr, int relu, int rank, int world, void* const* stage_ptrs,
-                                         void* const* sig_ptrs, long long flag_base, unsigned* epoch_dev, int split,
-                                         int* status, cudaStream_t stream) {
+                                         long long ldr, int relu, int rank, int world, void* const* recv_ptrs,
+                                         int slot_rows, unsigned* epoch_dev, int split, int* status, cudaStream_t stream) {
   using namespace msq;
   if (world < 1 || world > SK_MAX_RANKS || rank < 0 || rank >= world) return -6;
-  if (world > 1 && (!stage_ptrs || !sig_ptrs || !epoch_dev)) return -6;
+  if (world > 1 && (!recv_ptrs || !epoch_dev || M > slot_rows)) return -6;
   SkinnyParams p = {};
   p.world = world;
   p.rank = rank;
   for (int r = 0; r < world && world > 1; ++r) {
-    p.stage[r] = stage_ptrs[r];
-    p.sig[r] = static_cast<uint32_t*>(sig_ptrs[r]);
-    if ((reinterpret_cast<uintptr_t>(p.stage[r]) & 3) || !p.sig[r]) return -6;
+    p.recv_buf[r] = recv_ptrs[r];
+    if (!p.recv_buf[r] || (reinterpret_cast<uintptr_t>(p.recv_buf[r]) & 15)) return -6;
   }
-  p.flag_base = flag_base;
+  p.slot_rows = slot_rows;
   p.epoch_dev = epoch_dev;
+  p.prof = g_skinny_prof;
   if (split != 1 && split != 2 && split != 4 && split != 8) split = msq_gemm_skinny_split(N, K);
   const int k_blocks = (K + SK_BK - 1) / SK_BK;
   while (split > 1 && k_blocks < split) split >>= 1;
   const int rc = skinny_common(X, W, C, M, N, K, ldx, ldw, ldc, bf16, bias, residual, ldr, relu, status, stream, p, split);
   return rc < 0 ? rc : ((N + SK_BM - 1) / SK_BM) * split;
 }
+
+// Debug aid: device buffer of 6 int64 per CTA that the next launches of msq_gemm_skinny_allreduce fill with the
+// cycle counts of their phases (null switches it off).
+extern "C" void msq_gemm_skinny_set_prof(long long* buf) { msq::g_skinny_prof = buf; }
 
 // Non-zero: the calling thread's launches of the few-row GEMM, the LayerNorm forward and the decode attention
 // carry the programmatic-dependent-launch attribute, so that each may start (and the GEMM may request its

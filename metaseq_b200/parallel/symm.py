@@ -662,11 +662,12 @@ class TPComm:
 
 class DecodeReduce:
     """Row-parallel products of a tensor-parallel decode step: GEMM and the sum over ranks in one launch
-    (``msq_gemm_skinny_allreduce``).  Each owner CTA stores its partial rows in this rank's staging buffer,
-    exchanges an arrival flag with the same-index CTA of every peer and adds the rows of all ranks read over
-    NVLink.  The epochs of that exchange are counters in device memory that the kernel advances itself, so a
-    captured launch can be replayed; consecutive calls alternate between two staging buffers.  Every call
-    must use the same grid (same ``N``, one cluster size), which the caller fixes with ``split``.
+    (``msq_gemm_skinny_allreduce``).  Each owner CTA stores its partial rows into a receive buffer of every
+    rank over NVLink, every 4 bytes of payload paired with an epoch word, and polls its own receive buffer until
+    the rows of all ranks carry the epoch; no fence, separate flag or remote load is involved.  The epochs are
+    counters in device memory that the kernel advances itself, so a captured launch can be replayed;
+    consecutive calls alternate between two receive buffers.  Every call must use the same grid (same ``N``,
+    one cluster size), which the caller fixes with ``split``.
 
     Stands in for ``RowParallelLinear`` + ``all_reduce`` of the reference's incremental decoding
     (metaseq/modules/megatron/mpu/layers.py:660-676)."""
@@ -680,11 +681,10 @@ class DecodeReduce:
         self.dtype = dtype
         self.cols = int(cols)
         self.max_rows = int(max_rows)
-        nbytes = self.max_rows * self.cols * torch.empty((), dtype=dtype).element_size()
-        self.heap = SymmetricHeap(group, 2 * (nbytes + 4096) + (1 << 16), device, provider=provider)
+        nbytes = self.world * self.max_rows * self.cols * 4  # one 4-byte cell per element: payload or epoch
+        self.heap = SymmetricHeap(group, 2 * (nbytes + 4096) + (1 << 16), device, provider=provider)  # zero-filled
         offs = [self.heap.alloc(nbytes), self.heap.alloc(nbytes)]
-        self._stage = [(ctypes.c_void_p * self.world)(*[p + off for p in self.heap.ptrs]) for off in offs]
-        self.flag_base = self.heap.alloc_flags(self.MAX_CTAS * self.world)
+        self._recv = [(ctypes.c_void_p * self.world)(*[p + off for p in self.heap.ptrs]) for off in offs]
         self.epochs = torch.zeros(self.MAX_CTAS, dtype=torch.int32, device=device)
         self.calls = 0
 
@@ -699,12 +699,12 @@ class DecodeReduce:
             _lib.ptr(x), _lib.ptr(w), _lib.ptr(out), M, N, K, x.stride(0), w.stride(0), out.stride(0),
             int(x.dtype == torch.bfloat16), _lib.ptr(bias), _lib.ptr(residual),
             residual.stride(0) if residual is not None else 0, int(relu), self.rank, self.world,
-            self._stage[self.calls & 1], self.heap.ptr_array, self.flag_base, _lib.ptr(self.epochs), int(split),
+            self._recv[self.calls & 1], self.max_rows, _lib.ptr(self.epochs), int(split),
             _lib.ptr(_lib.status_word(x.device)), _lib.stream_ptr())
         if rc < 0:
             raise RuntimeError(f"msq_gemm_skinny_allreduce failed ({rc})")
         if rc > self.MAX_CTAS:
-            raise RuntimeError(f"msq_gemm_skinny_allreduce launched {rc} CTAs, more than the {self.MAX_CTAS} flag rows")
+            raise RuntimeError(f"msq_gemm_skinny_allreduce launched {rc} CTAs, more than the {self.MAX_CTAS} counters")
         self.calls += 1
         return out
 
