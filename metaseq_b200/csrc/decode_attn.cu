@@ -249,9 +249,11 @@ static int launch_decode(const void* q, const void* kc, const void* vc, void* ou
 // Number of sequence splits the launch will use for this problem (the caller sizes the workspace:
 // B * H * splits * (HD + 2) floats; none needed when the answer is 1).
 extern "C" int msq_decode_attn_splits(int B, int H, int S) {
+  // The kernel keeps seven CTAs per SM busy (148 * 7 = 1036 CTAs in one wave); with fewer (batch, head) pairs
+  // than about five per SM the sequence is split so that the grid comes close to one full wave.
   const long long pairs = static_cast<long long>(B) * H;
-  if (pairs >= 256 || S < 256) return 1;
-  long long want = (296 + pairs - 1) / pairs;
+  if (pairs >= 740 || S < 256) return 1;
+  long long want = (1036 + pairs / 2) / pairs;
   const long long cap = S / 128;
   if (want > cap) want = cap;
   if (want > 32) want = 32;
