@@ -311,8 +311,8 @@ def _decode_worker(rank, world, port, results):
         parser = options.get_training_parser()
         ns = options.parse_args_and_arch(parser, input_args=[
             "--task", "dummy_lm", "--dict-size", "2040", "--tokens-per-sample", "128", "--batch-size", "1",
-            "--arch", "transformer_lm_megatron", "--decoder-layers", "3", "--decoder-embed-dim", "256",
-            "--decoder-ffn-embed-dim", "1024", "--decoder-attention-heads", "4", "--decoder-learned-pos",
+            "--arch", "transformer_lm_megatron", "--decoder-layers", "3", "--decoder-embed-dim", "512",
+            "--decoder-ffn-embed-dim", "2048", "--decoder-attention-heads", "8", "--decoder-learned-pos",
             "--activation-fn", "relu", "--share-decoder-input-output-embed", "--no-scale-embedding", "--dropout", "0.0",
             "--attention-dropout", "0.0", "--criterion", "vocab_parallel_cross_entropy", "--optimizer", "adam",
             "--lr", "1e-3", "--memory-efficient-fp16", "--tensor-parallel-init-model-on-gpu",
@@ -342,12 +342,12 @@ def _decode_worker(rank, world, port, results):
         dist.destroy_process_group()
 
 
-def test_decode_gemm_fused_with_all_reduce_and_graphed_tensor_parallel_step():
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs at least two GPUs")
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_decode_gemm_fused_with_all_reduce_and_graphed_tensor_parallel_step(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs at least {world} GPUs")
     import torch.multiprocessing as mp
 
-    world = 2
     with mp.Manager() as mgr:
         results = mgr.dict()
         mp.spawn(_decode_worker, args=(world, _free_port(), results), nprocs=world, join=True)
