@@ -492,3 +492,33 @@ def test_flash_attention_dropout_matches_reference(B, T, H, d):
     # without dropout the same call gives a different (undropped) result
     out0, _ = F.flash_attn_fwd(q, k, v, d ** -0.5, True)
     assert (out0.float() - out.float()).abs().max().item() > 1e-2
+
+
+def test_wait_on_a_flag_that_nothing_sets_times_out_and_the_context_stays_usable():
+    """The bounded wait for a peer's arrival flag: nothing ever publishes the awaited epoch, so after its limit
+    (4 s) the kernel gives up, leaves a code in the status word and returns.  While the word is set, kernels
+    that check it do no work; once the host has read (and thereby cleared) it, everything runs as before."""
+    import time
+
+    lib = _lib.kernels()
+    _status_ok()
+    flags = torch.zeros(8, dtype=torch.int32, device="cuda")
+    status = _lib.status_word(torch.device("cuda"))
+    t0 = time.time()
+    rc = lib.msq_comm_wait_flags(_lib.ptr(flags), 0, 4, 0, 0, 1, _lib.ptr(status), _lib.stream_ptr())
+    assert rc == 0
+    torch.cuda.synchronize()
+    waited = time.time() - t0
+    assert 2.0 < waited < 30.0, waited
+    # a GEMM launched while the word is set returns without touching its output
+    a = torch.randn(256, 128, device="cuda", dtype=torch.float16)
+    w = torch.randn(256, 128, device="cuda", dtype=torch.float16)
+    out = torch.full((256, 256), 7.0, device="cuda", dtype=torch.float16)
+    F.gemm(a, w, out=out)
+    torch.cuda.synchronize()
+    assert float(out.float().min()) == 7.0 and float(out.float().max()) == 7.0
+    code = _lib.check_status("cuda")
+    assert code == 5, code  # ST_TIMEOUT_PEER_FLAG; reading clears the word
+    F.gemm(a, w, out=out)
+    _close(out, a.float() @ w.float().t(), torch.float16)
+    _status_ok()
