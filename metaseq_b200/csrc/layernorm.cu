@@ -35,7 +35,7 @@ template <bool BF16, int VPT>
 __global__ void __launch_bounds__(LN_THREADS)
 layernorm_fwd_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ gamma,
                      const uint16_t* __restrict__ beta, uint16_t* __restrict__ y, float* __restrict__ mean_out,
-                     float* __restrict__ rstd_out, int rows, int D, float eps) {
+                     float* __restrict__ rstd_out, int rows, int D, float eps, int rms) {
   __shared__ float red[32];
   const int nvec = D >> 3;
   float g[VPT][8], b[VPT][8];
@@ -81,7 +81,7 @@ layernorm_fwd_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict_
       }
     }
     if (row + static_cast<int>(gridDim.x) < rows) fetch(row + gridDim.x);
-    const float mean = block_sum(s, red) * inv_d;
+    const float mean = rms ? 0.f : block_sum(s, red) * inv_d;  // RMS norm: no centring (uniform per launch)
     float q = 0.f;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
@@ -123,7 +123,7 @@ layernorm_bwd_kernel(const uint16_t* __restrict__ dy, const uint16_t* __restrict
                      const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
                      const uint16_t* __restrict__ gamma, const uint16_t* __restrict__ add,
                      uint16_t* __restrict__ dx, float* __restrict__ part_g, float* __restrict__ part_b, int rows,
-                     int D) {
+                     int D, int rms) {
   __shared__ float red[32];
   const int nvec = D >> 3;
   float g[VPT][8], ag[VPT][8], ab[VPT][8];
@@ -137,7 +137,7 @@ layernorm_bwd_kernel(const uint16_t* __restrict__ dy, const uint16_t* __restrict
   const float inv_d = 1.f / static_cast<float>(D);
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const long long off = static_cast<long long>(row) * D;
-    const float mean = mean_in[row], rstd = rstd_in[row];
+    const float mean = rms ? 0.f : mean_in[row], rstd = rstd_in[row];
     float xh[VPT][8], gd[VPT][8];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
@@ -158,7 +158,7 @@ layernorm_bwd_kernel(const uint16_t* __restrict__ dy, const uint16_t* __restrict
         }
       }
     }
-    const float m1 = block_sum(s1, red) * inv_d;
+    const float m1 = rms ? 0.f : block_sum(s1, red) * inv_d;
     const float m2 = block_sum(s2, red) * inv_d;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
@@ -262,9 +262,9 @@ static int ln_grid_fwd(int rows) {
 // partial buffers as [msq_layernorm_bwd_parts(rows), D] fp32 each.
 extern "C" int msq_layernorm_bwd_parts(int rows) { return msq::ln_grid(rows); }
 
-extern "C" int msq_layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean,
-                                 float* rstd, int rows, int D, float eps, int bf16, cudaStream_t stream) {
-  using namespace msq;
+namespace msq {
+static int norm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd, int rows, int D,
+                    float eps, int bf16, int rms, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (D & 7) return -2;
   const int nvec = D >> 3;
@@ -274,18 +274,16 @@ extern "C" int msq_layernorm_fwd(const void* x, const void* gamma, const void* b
   auto B = static_cast<const uint16_t*>(beta);
   auto Y = static_cast<uint16_t*>(y);
   if (bf16) {
-    MSQ_LN_DISPATCH(nvec, (launch_chained(layernorm_fwd_kernel<true, VPT>, dim3(grid), dim3(LN_THREADS), 0, stream, 1u, X, G, B, Y, mean, rstd, rows, D, eps)))
+    MSQ_LN_DISPATCH(nvec, (launch_chained(layernorm_fwd_kernel<true, VPT>, dim3(grid), dim3(LN_THREADS), 0, stream, 1u, X, G, B, Y, mean, rstd, rows, D, eps, rms)))
   } else {
-    MSQ_LN_DISPATCH(nvec, (launch_chained(layernorm_fwd_kernel<false, VPT>, dim3(grid), dim3(LN_THREADS), 0, stream, 1u, X, G, B, Y, mean, rstd, rows, D, eps)))
+    MSQ_LN_DISPATCH(nvec, (launch_chained(layernorm_fwd_kernel<false, VPT>, dim3(grid), dim3(LN_THREADS), 0, stream, 1u, X, G, B, Y, mean, rstd, rows, D, eps, rms)))
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
-extern "C" int msq_layernorm_bwd(const void* dy, const void* x, const float* mean, const float* rstd,
-                                 const void* gamma, const void* add, void* dx, float* part_g, float* part_b,
-                                 void* dgamma, void* dbeta, int accumulate, int rows, int D, int bf16,
-                                 cudaStream_t stream) {
-  using namespace msq;
+static int norm_bwd(const void* dy, const void* x, const float* mean, const float* rstd, const void* gamma,
+                    const void* add, void* dx, float* part_g, float* part_b, void* dgamma, void* dbeta, int accumulate,
+                    int rows, int D, int bf16, int rms, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (D & 7) return -2;
   const int nvec = D >> 3;
@@ -296,9 +294,9 @@ extern "C" int msq_layernorm_bwd(const void* dy, const void* x, const float* mea
   auto A = static_cast<const uint16_t*>(add);
   auto DX = static_cast<uint16_t*>(dx);
   if (bf16) {
-    MSQ_LN_DISPATCH(nvec, (layernorm_bwd_kernel<true, VPT><<<grid, LN_THREADS, 0, stream>>>(DY, X, mean, rstd, G, A, DX, part_g, part_b, rows, D)))
+    MSQ_LN_DISPATCH(nvec, (layernorm_bwd_kernel<true, VPT><<<grid, LN_THREADS, 0, stream>>>(DY, X, mean, rstd, G, A, DX, part_g, part_b, rows, D, rms)))
   } else {
-    MSQ_LN_DISPATCH(nvec, (layernorm_bwd_kernel<false, VPT><<<grid, LN_THREADS, 0, stream>>>(DY, X, mean, rstd, G, A, DX, part_g, part_b, rows, D)))
+    MSQ_LN_DISPATCH(nvec, (layernorm_bwd_kernel<false, VPT><<<grid, LN_THREADS, 0, stream>>>(DY, X, mean, rstd, G, A, DX, part_g, part_b, rows, D, rms)))
   }
   if (part_g && (dgamma || dbeta)) {
     const int t = 256, b = (D + 31) / 32;
@@ -310,4 +308,33 @@ extern "C" int msq_layernorm_bwd(const void* dy, const void* x, const float* mea
                                                          static_cast<uint16_t*>(dbeta), accumulate);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+}  // namespace msq
+
+extern "C" int msq_layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean,
+                                 float* rstd, int rows, int D, float eps, int bf16, cudaStream_t stream) {
+  return msq::norm_fwd(x, gamma, beta, y, mean, rstd, rows, D, eps, bf16, 0, stream);
+}
+
+extern "C" int msq_layernorm_bwd(const void* dy, const void* x, const float* mean, const float* rstd,
+                                 const void* gamma, const void* add, void* dx, float* part_g, float* part_b,
+                                 void* dgamma, void* dbeta, int accumulate, int rows, int D, int bf16,
+                                 cudaStream_t stream) {
+  return msq::norm_bwd(dy, x, mean, rstd, gamma, add, dx, part_g, part_b, dgamma, dbeta, accumulate, rows, D, bf16, 0,
+                       stream);
+}
+
+// RMS norm, y = x * rsqrt(mean(x^2) + eps) * gamma: the LayerNorm kernels without the centring terms (the
+// reference exposes it from the same extension: metaseq/modules/apex/layer_norm_cuda.cpp:459-471, rms_* entries).
+// `part_b` is still required as scratch by the backward kernel; its column sums are not used.
+extern "C" int msq_rmsnorm_fwd(const void* x, const void* gamma, void* y, float* rstd, int rows, int D, float eps, int bf16,
+                               cudaStream_t stream) {
+  return msq::norm_fwd(x, gamma, nullptr, y, nullptr, rstd, rows, D, eps, bf16, 1, stream);
+}
+
+extern "C" int msq_rmsnorm_bwd(const void* dy, const void* x, const float* rstd, const void* gamma, const void* add,
+                               void* dx, float* part_g, float* part_b, void* dgamma, int accumulate, int rows, int D,
+                               int bf16, cudaStream_t stream) {
+  return msq::norm_bwd(dy, x, nullptr, rstd, gamma, add, dx, part_g, part_b, dgamma, nullptr, accumulate, rows, D, bf16, 1,
+                       stream);
 }

@@ -22,6 +22,25 @@ def LayerNorm(normalized_shape, eps=1e-5, elementwise_affine=True, export=False)
     return FusedLayerNorm(normalized_shape, eps, elementwise_affine)
 
 
+class RMSNorm(nn.Module):
+    """``x * rsqrt(mean(x^2) + eps) * weight``: the LayerNorm kernels without centring and shift (the reference's
+    fused LayerNorm extension exports the same as ``rms_forward_affine`` / ``rms_backward_affine``:
+    metaseq/modules/apex/layer_norm_cuda.cpp:459-471; no Python module of the reference uses them)."""
+
+    def __init__(self, normalized_shape, eps: float = 1e-5, elementwise_affine: bool = True):
+        super().__init__()
+        dim = normalized_shape if isinstance(normalized_shape, int) else normalized_shape[-1]
+        self.normalized_shape = (dim,)
+        self.eps = eps
+        self.weight = nn.Parameter(torch.ones(dim)) if elementwise_affine else None
+
+    def forward(self, x):
+        w = self.weight
+        if w is not None and w.dtype != x.dtype:
+            w = w.to(x.dtype)
+        return ops_ag.rms_norm(x, w, self.eps)
+
+
 class LayerNormFp32(nn.LayerNorm):
     """LayerNorm computed in fp32 regardless of the input dtype."""
 

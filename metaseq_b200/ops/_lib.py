@@ -26,7 +26,7 @@ F = c_float
 
 
 # kernels launched by one call of each entry point (used for the launch counter)
-_KERNELS_PER_CALL = {"msq_attn_set_dropout": 0, "msq_symm_alloc": 0, "msq_symm_open": 0, "msq_symm_close": 0, "msq_symm_free": 0, "msq_sumsq": 2, "msq_layernorm_bwd": 2, "msq_flash_bwd": 2, "msq_layernorm_bwd_parts": 0,
+_KERNELS_PER_CALL = {"msq_attn_set_dropout": 0, "msq_symm_alloc": 0, "msq_symm_open": 0, "msq_symm_close": 0, "msq_symm_free": 0, "msq_sumsq": 2, "msq_layernorm_bwd": 2, "msq_rmsnorm_bwd": 2, "msq_flash_bwd": 2, "msq_layernorm_bwd_parts": 0,
                      "msq_sumsq_parts": 0, "msq_gemm_skinny_split": 0, "msq_set_dependent_launch": 0, "msq_gemm_skinny_set_prof": 0, "msq_decode_attn_splits": 0}
 _LAUNCHES = [0]
 
@@ -141,6 +141,8 @@ _OPTIONAL = {
     "msq_set_dependent_launch": [I],
     "msq_gemm_skinny_set_prof": [P],
     "msq_scale_rows": [P, L, L, I, P, I, I, I, P],
+    "msq_rmsnorm_fwd": [P, P, P, P, I, I, F, I, P],
+    "msq_rmsnorm_bwd": [P, P, P, P, P, P, P, P, P, I, I, I, I, P],
     "msq_decode_attn_step": [P, P, P, L, P, P, P, P, I, I, I, P, I, L, L, L, L, L, F, I, P, I, P],
     "msq_attn_set_dropout": [F, ctypes.c_ulonglong],
     "msq_dropout_add": [P, L, P, P, L, P, L, L, I, F, ctypes.c_ulonglong, I, P],

@@ -107,6 +107,27 @@ class LayerNormFn(torch.autograd.Function):
         return dx.view(ctx.in_shape), dg, db, None
 
 
+class RMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, gamma, eps: float):
+        shp = x.shape
+        x2 = x.reshape(-1, shp[-1]).contiguous()
+        y, rstd = F.rms_norm_fwd(x2, gamma, eps)
+        ctx.save_for_backward(x2, rstd, gamma)
+        ctx.in_shape = shp
+        return y.view(shp)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, rstd, gamma = ctx.saved_tensors
+        dx, dg = F.rms_norm_bwd(dy.reshape(x2.shape).contiguous(), x2, rstd, gamma)
+        return dx.view(ctx.in_shape), dg, None
+
+
+def rms_norm(x, gamma, eps: float = 1e-5):
+    return RMSNormFn.apply(x, gamma, eps)
+
+
 def layer_norm(x, gamma, beta, eps: float = 1e-5):
     return LayerNormFn.apply(x, gamma, beta, eps)
 

@@ -207,6 +207,50 @@ def _gemm_torch(a, b, a_mn, b_mn, bias, residual, mask, relu, out, accumulate):
     return out
 
 
+# -------------------------------------------------------------------- RMS norm
+def rms_norm_fwd(x2d, gamma, eps: float):
+    """``y = x * rsqrt(mean(x^2) + eps) * gamma``; returns ``(y, rstd)`` with fp32 ``rstd``."""
+    rows, D = x2d.shape
+    if use_kernels(x2d) and D % 8 == 0 and D <= 16384 and x2d.is_contiguous():
+        y = torch.empty_like(x2d)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x2d.device)
+        rc = _lib.kernels().msq_rmsnorm_fwd(_lib.ptr(x2d), _lib.ptr(gamma), _lib.ptr(y), _lib.ptr(rstd), rows, D,
+                                            float(eps), _bf(x2d), _lib.stream_ptr())
+        _lib.check_rc(rc, "msq_rmsnorm_fwd")
+        return y, rstd
+    xf = x2d.float()
+    rstd = torch.rsqrt(xf.pow(2).mean(dim=1) + eps)
+    y = xf * rstd[:, None]
+    if gamma is not None:
+        y = y * gamma.float()
+    return y.to(x2d.dtype), rstd
+
+
+def rms_norm_bwd(dy, x2d, rstd, gamma):
+    """Returns ``(dx, dgamma)`` (``dgamma`` is ``None`` without ``gamma``)."""
+    rows, D = x2d.shape
+    if use_kernels(x2d) and D % 8 == 0 and D <= 16384 and x2d.is_contiguous() and dy.is_contiguous():
+        lib = _lib.kernels()
+        dx = torch.empty_like(x2d)
+        part_g = part_b = dgamma = None
+        if gamma is not None:
+            parts = lib.msq_layernorm_bwd_parts(rows)
+            part = torch.empty((2, parts, D), dtype=torch.float32, device=x2d.device)
+            part_g, part_b = part[0], part[1]
+            dgamma = torch.empty(D, dtype=x2d.dtype, device=x2d.device)
+        rc = lib.msq_rmsnorm_bwd(_lib.ptr(dy), _lib.ptr(x2d), _lib.ptr(rstd), _lib.ptr(gamma), None, _lib.ptr(dx),
+                                 _lib.ptr(part_g), _lib.ptr(part_b), _lib.ptr(dgamma), 0, rows, D, _bf(x2d),
+                                 _lib.stream_ptr())
+        _lib.check_rc(rc, "msq_rmsnorm_bwd")
+        return dx, dgamma
+    xf, dyf = x2d.float(), dy.float()
+    xhat = xf * rstd[:, None]
+    gdy = dyf * gamma.float() if gamma is not None else dyf
+    dx = rstd[:, None] * (gdy - xhat * (gdy * xhat).mean(dim=1, keepdim=True))
+    dg = (dyf * xhat).sum(dim=0).to(x2d.dtype) if gamma is not None else None
+    return dx.to(x2d.dtype), dg
+
+
 # ------------------------------------------------------------------ LayerNorm
 def layer_norm_fwd(x2d, gamma, beta, eps: float):
     """Returns ``(y, mean, rstd)`` for ``x2d`` of shape ``[rows, D]``; statistics are fp32."""

@@ -522,3 +522,33 @@ def test_wait_on_a_flag_that_nothing_sets_times_out_and_the_context_stays_usable
     F.gemm(a, w, out=out)
     _close(out, a.float() @ w.float().t(), torch.float16)
     _status_ok()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,D,affine", [(64, 2048, True), (37, 768, True), (300, 4096, False), (5, 264, True)])
+def test_rms_norm_forward_backward(dtype, rows, D, affine):
+    from metaseq_b200.modules.layer_norm import RMSNorm
+
+    torch.manual_seed(rows + D)
+    mod = RMSNorm(D, eps=1e-5, elementwise_affine=affine).cuda().to(dtype)
+    if affine:
+        with torch.no_grad():
+            mod.weight.copy_(torch.randn(D, device="cuda").to(dtype))
+    x = torch.randn(rows, D, device="cuda", dtype=dtype, requires_grad=True)
+    dy = torch.randn(rows, D, device="cuda", dtype=dtype)
+    before = _lib.launch_count()
+    y = mod(x)
+    assert _lib.launch_count() == before + 1
+    y.backward(dy)
+    xr = x.detach().float().requires_grad_(True)
+    wr = mod.weight.detach().float().requires_grad_(True) if affine else None
+    yr = xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + 1e-5)
+    if affine:
+        yr = yr * wr
+    yr.backward(dy.float())
+    _close(y, yr, dtype)
+    _close(x.grad, xr.grad, dtype, scale=4.0)
+    if affine:
+        _close(mod.weight.grad, wr.grad, dtype, scale=float(rows) ** 0.5 * 2)
+    _status_ok()
+

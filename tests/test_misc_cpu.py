@@ -290,3 +290,23 @@ def test_nan_detector_names_the_first_bad_module(caplog):
             model(torch.ones(2, 4))
     assert det.has_printed_f
     assert any("NaN detected in output of 1" in r.getMessage() for r in caplog.records)
+
+
+def test_rms_norm_cpu_matches_definition():
+    from metaseq_b200.modules.layer_norm import RMSNorm
+
+    torch.manual_seed(0)
+    mod = RMSNorm(48)
+    with torch.no_grad():
+        mod.weight.copy_(torch.randn(48))
+    x = torch.randn(7, 48, requires_grad=True)
+    y = mod(x)
+    ref_in = x.detach().clone().requires_grad_(True)
+    ref = ref_in * torch.rsqrt(ref_in.pow(2).mean(-1, keepdim=True) + mod.eps) * mod.weight.detach()
+    dy = torch.randn(7, 48)
+    y.backward(dy)
+    ref.backward(dy)
+    assert torch.allclose(y, ref, atol=1e-5) and torch.allclose(x.grad, ref_in.grad, atol=1e-5)
+    want = (dy * ref_in.detach() * torch.rsqrt(ref_in.detach().pow(2).mean(-1, keepdim=True) + mod.eps)).sum(0)
+    assert torch.allclose(mod.weight.grad, want, atol=1e-4)
+
