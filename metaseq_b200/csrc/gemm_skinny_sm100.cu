@@ -54,7 +54,7 @@ struct SkinnyParams {
   const void* bias;      // [N] or null
   const void* residual;  // [M, ldr] or null
   long long ldr;
-  int relu;
+  int relu;  // activation after the bias: 0 none, 1 ReLU, 2 GELU (erf form)
   int bf16;
   int* status;
   // sum over tensor-parallel ranks (world <= 1: none)
@@ -101,6 +101,12 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t ran
 }
 __device__ __forceinline__ void st_cluster_f32(uint32_t remote_addr, float v) {
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote_addr), "f"(v) : "memory");
+}
+
+__device__ __forceinline__ float activate(float x, int kind) {
+  if (kind == 1) return fmaxf(x, 0.f);
+  if (kind == 2) return 0.5f * x * (1.f + erff(x * 0.70710678118654752f));
+  return x;
 }
 
 // 16-byte load of two {payload, epoch} units that a peer GPU writes: never from L1.
@@ -302,10 +308,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         acc.x += b2.x;
         acc.y += b2.y;
       }
-      if (p.relu) {
-        acc.x = fmaxf(acc.x, 0.f);
-        acc.y = fmaxf(acc.y, 0.f);
-      }
+      acc.x = activate(acc.x, p.relu);
+      acc.y = activate(acc.y, p.relu);
       if (p.residual) {
         const float2 r2 = p.bf16 ? unpack2<true>(rw) : unpack2<false>(rw);
         acc.x += r2.x;
@@ -398,10 +402,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         a0 += b2.x;
         a1 += b2.y;
       }
-      if (p.relu) {
-        a0 = fmaxf(a0, 0.f);
-        a1 = fmaxf(a1, 0.f);
-      }
+      a0 = activate(a0, p.relu);
+      a1 = activate(a1, p.relu);
       if (res16) {
         const uint32_t rw = *reinterpret_cast<const uint32_t*>(res16 + static_cast<long long>(m) * p.ldr + n + 2 * j);
         const float2 r2 = p.bf16 ? unpack2<true>(rw) : unpack2<false>(rw);
@@ -501,7 +503,7 @@ static int skinny_common(const void* X, const void* W, void* C, int M, int N, in
 }  // namespace msq
 
 // X: [M, K] (row stride ldx), W: [N, K] (row stride ldw), C: [M, N] (row stride ldc), all 16-bit of one type,
-// strides in elements.  M <= 64; K and N multiples of 8; base pointers 16-byte aligned, C / residual / bias 4-byte
+// strides in elements.  `relu`: 0 none, 1 ReLU, 2 GELU after the bias.  M <= 64; K and N multiples of 8; base pointers 16-byte aligned, C / residual / bias 4-byte
 // aligned with even strides.  Returns 0 on a successful launch, a negative code for unsupported arguments.
 extern "C" int msq_gemm_skinny(const void* X, const void* W, void* C, int M, int N, int K, long long ldx, long long ldw,
                                long long ldc, int bf16, const void* bias, const void* residual, long long ldr, int relu,

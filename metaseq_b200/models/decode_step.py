@@ -189,10 +189,8 @@ class GraphedDecodeStep:
                                      a.num_heads_partition, a.scaling, self._length_hint)
             x = self._row_parallel(ctx, a.out_proj, x)
             h, _, _ = F.layer_norm_fwd(x, ln2.weight, ln2.bias, ln2.eps)
-            if layer.activation_name == "relu":
-                f = F.gemm(h, layer.fc1.weight, bias=layer.fc1.bias, relu=True)
-            else:
-                f = torch.nn.functional.gelu(F.gemm(h, layer.fc1.weight, bias=layer.fc1.bias).float()).to(h.dtype)
+            relu = layer.activation_name == "relu"
+            f = F.gemm(h, layer.fc1.weight, bias=layer.fc1.bias, relu=relu, gelu=not relu)
             x = self._row_parallel(f, layer.fc2, x)
         fl = dec.layer_norm
         x, _, _ = F.layer_norm_fwd(x, fl.weight, fl.bias, fl.eps)

@@ -81,6 +81,7 @@ def gemm(
     bn: int = 0,
     max_ctas: int = 0,
     b_ready=None,
+    gelu: bool = False,
 ) -> torch.Tensor:
     """``out[M,N] = epilogue(op(a) @ op(b))`` for 2-D operands.
 
@@ -90,8 +91,9 @@ def gemm(
 
     ``a`` is stored ``[M,K]`` (``a_mn=False``) or ``[K,M]`` (``a_mn=True``);
     ``b`` is stored ``[N,K]`` (``b_mn=False``, an ``nn.Linear`` weight) or
-    ``[K,N]`` (``b_mn=True``).  Epilogue order: ``+bias`` -> ReLU ->
-    zero where ``mask<=0`` -> ``+residual`` -> ``+out`` (when ``accumulate``).
+    ``[K,N]`` (``b_mn=True``).  Epilogue order: ``+bias`` -> ReLU (or GELU with ``gelu``) ->
+    zero where ``mask<=0`` -> ``+residual`` -> ``+out`` (when ``accumulate``).  GELU is an epilogue of the
+    few-row kernel only; elsewhere it is applied by PyTorch after the product.
     Operands may be row-strided views (last dim contiguous).
     """
     assert a.dim() == 2 and b.dim() == 2
@@ -103,6 +105,17 @@ def gemm(
         out = torch.empty((M, N), dtype=a.dtype, device=a.device)
     if M == 0 or N == 0:
         return out
+    if gelu:
+        assert not relu and mask is None and not accumulate
+        few_rows = (use_kernels(a) and M <= 64 and not a_mn and not b_mn and bn == 0 and max_ctas == 0
+                    and _GEMM_VARIANT == "auto" and K % 8 == 0 and N % 8 == 0 and b_ready is None
+                    and _gemm_operands_ok(a, b, out, residual, None)
+                    and getattr(b, "_msq_ready", None) is None and getattr(a, "_msq_ready", None) is None)
+        if not few_rows:
+            gemm(a, b, a_mn=a_mn, b_mn=b_mn, bias=bias, out=out, bn=bn, max_ctas=max_ctas, b_ready=b_ready)
+            act = torch.nn.functional.gelu(out.float())
+            out.copy_(act + residual.float() if residual is not None else act)
+            return out
     if use_kernels(a) and K % 8 == 0 and N % 8 == 0 and _gemm_operands_ok(a, b, out, residual, mask) \
             and (bias is None or bias.data_ptr() % 16 == 0):
         lib = _lib.kernels()
@@ -112,8 +125,8 @@ def gemm(
             # a few rows (a decode step): one pass over the weights, K split over a thread-block cluster
             rc = lib.msq_gemm_skinny(
                 _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), M, N, K, a.stride(0), b.stride(0), out.stride(0), _bf(a),
-                _lib.ptr(bias), _lib.ptr(residual), residual.stride(0) if residual is not None else 0, int(relu),
-                _lib.ptr(_lib.status_word(a.device)), _lib.stream_ptr())
+                _lib.ptr(bias), _lib.ptr(residual), residual.stride(0) if residual is not None else 0,
+                2 if gelu else int(relu), _lib.ptr(_lib.status_word(a.device)), _lib.stream_ptr())
             _lib.check_rc(rc, "msq_gemm_skinny")
             return out
         pair = _GEMM_VARIANT == "2cta" or (_GEMM_VARIANT == "auto" and M >= 256 and N >= 128 and bn == 0)

@@ -309,7 +309,7 @@ def test_gemm_two_cta_epilogue(dtype):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("M,N,K", [(1, 128, 64), (4, 2048, 2048), (16, 6144, 2048), (17, 2048, 8192), (32, 8192, 2048),
                                    (33, 264, 136), (64, 50272, 768), (48, 96, 4096), (8, 1000, 200)])
-@pytest.mark.parametrize("epilogue", ["plain", "bias_relu", "bias_residual"])
+@pytest.mark.parametrize("epilogue", ["plain", "bias_relu", "bias_residual", "bias_gelu"])
 def test_gemm_few_rows_cluster_split_k(dtype, M, N, K, epilogue):
     """Products with at most 64 rows take the swapped-operand kernel whose K range is split over a cluster."""
     torch.manual_seed(M * 7 + N)
@@ -318,19 +318,22 @@ def test_gemm_few_rows_cluster_split_k(dtype, M, N, K, epilogue):
     bias = torch.randn(N, device="cuda", dtype=dtype) if epilogue != "plain" else None
     res = torch.randn(M, N, device="cuda", dtype=dtype) if epilogue == "bias_residual" else None
     relu = epilogue == "bias_relu"
+    gelu = epilogue == "bias_gelu"
     split = _lib.kernels().msq_gemm_skinny_split(N, K)
     assert split in (1, 2, 4, 8)
     torch.cuda.synchronize()
     if (N, K) == (2048, 8192):
         assert split == 8
     before = _lib.launch_count()
-    out = F.gemm(x, w, bias=bias, residual=res, relu=relu)
+    out = F.gemm(x, w, bias=bias, residual=res, relu=relu, gelu=gelu)
     assert _lib.launch_count() == before + 1
     ref = x.float() @ w.float().t()
     if bias is not None:
         ref = ref + bias.float()
     if relu:
         ref = torch.relu(ref)
+    if gelu:
+        ref = torch.nn.functional.gelu(ref)
     if res is not None:
         ref = ref + res.float()
     _close(out, ref, dtype)
@@ -338,7 +341,7 @@ def test_gemm_few_rows_cluster_split_k(dtype, M, N, K, epilogue):
     big = torch.zeros(M, N + 16, device="cuda", dtype=dtype)
     xs = torch.randn(M, K + 8, device="cuda", dtype=dtype)
     xs[:, :K] = x
-    F.gemm(xs[:, :K], w, bias=bias, residual=res, relu=relu, out=big[:, 8:8 + N])
+    F.gemm(xs[:, :K], w, bias=bias, residual=res, relu=relu, gelu=gelu, out=big[:, 8:8 + N])
     _close(big[:, 8:8 + N], ref, dtype)
     assert float(big[:, :8].abs().max()) == 0.0 and float(big[:, 8 + N:].abs().max()) == 0.0
     _status_ok()

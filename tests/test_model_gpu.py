@@ -171,13 +171,14 @@ def test_fused_layer_with_dropout_kernels_match_reference_masks():
     assert losses[0][2] < losses[0][0]
 
 
-def test_graphed_decode_step_matches_module_path():
+@pytest.mark.parametrize("activation", ["relu", "gelu"])
+def test_graphed_decode_step_matches_module_path(activation):
     """The CUDA-graph replay of the one-token step gives the logits of the module path (which gives those of a
     full forward), over several steps, with padding inside the prompt batch, and again after the step object
     is reused for a second prompt batch."""
     from metaseq_b200.models.decode_step import GraphedDecodeStep
 
-    cfg = _cfg(fsdp=False, extra=["--activation-fn", "relu"])
+    cfg = _cfg(fsdp=False, extra=["--activation-fn", activation])
     tr, batch = _trainer(cfg)
     model = tr.get_model().eval()
     dec = model.decoder
