@@ -78,6 +78,7 @@ def main(argv=None):
     ap.add_argument("--repeats", type=int, default=3)
     ap.add_argument("--kernel-backend", default="auto", choices=["auto", "torch"])
     ap.add_argument("--no-decode-graph", action="store_true", help="decode through the module tree")
+    ap.add_argument("--top-p", type=float, default=-1.0, help="nucleus sampling mass; <= 0 decodes greedily")
     ap.add_argument("--graph-replays", type=int, default=0,
                     help="instead of whole generate calls: one prefill, then this many replays of the captured "
                          "decode step, timed together (the workload for a per-kernel launch list)")
@@ -93,7 +94,7 @@ def main(argv=None):
     def call(n_new):
         total = args.prompt + n_new
         sg = SequenceGenerator([model], task.target_dictionary, beam_size=1, max_len_b=total, min_len=total,
-                               temperature=1.0, topp=-1, decode_graph=not args.no_decode_graph)
+                               temperature=1.0, topp=args.top_p, decode_graph=not args.no_decode_graph)
         with torch.no_grad():
             return sg.generate([model], sample)
 
@@ -136,7 +137,7 @@ def main(argv=None):
                prefill_ms=round(t1, 2), total_ms=round(tn, 2), decode_ms_per_token=round(per_tok, 3),
                decode_tokens_per_s=round(args.batch / per_tok * 1e3, 1), kernel_backend=args.kernel_backend,
                kernel_launches=_lib.launch_count(), kernel_status=_lib.check_status(torch.device("cuda")),
-               tensor_parallel=tp, decode_graph=not args.no_decode_graph,
+               tensor_parallel=tp, decode_graph=not args.no_decode_graph, top_p=args.top_p,
                dtype="fp16", data="synthetic uniform token ids, random-init weights")
     if tp > 1:
         import torch.distributed as dist

@@ -718,6 +718,41 @@ def scale_rows_(x2d, g):
     return x2d.mul_(g.to(x2d.dtype).reshape(-1, 1) if g.numel() > 1 else g.to(x2d.dtype))
 
 
+# ------------------------------------------------------------------- sampling
+def sample_top_p(lprobs, top_p, uniform=None):
+    """One token per row from the nucleus of mass ``top_p`` (a float, or a ``[rows]`` tensor) of fp32
+    log-probabilities ``[rows, V]`` (``-inf`` = banned).  Returns ``(log-prob of the token, token)``.
+    ``uniform``: optional ``[rows]`` numbers in [0, 1) (drawn from the torch generator otherwise)."""
+    rows, V = lprobs.shape
+    if uniform is None:
+        uniform = torch.rand(rows, device=lprobs.device, dtype=torch.float32)
+    per_row = torch.is_tensor(top_p) and top_p.numel() > 1
+    if lprobs.is_cuda and _BACKEND != "torch" and _lib.kernels_path().exists() and lprobs.dtype == torch.float32 \
+            and lprobs.stride(1) == 1 and V <= 56000:
+        p_t = top_p.to(device=lprobs.device, dtype=torch.float32).contiguous() if torch.is_tensor(top_p) else \
+            torch.full((1,), float(top_p), device=lprobs.device, dtype=torch.float32)
+        tok = torch.empty(rows, dtype=torch.long, device=lprobs.device)
+        lp = torch.empty(rows, dtype=torch.float32, device=lprobs.device)
+        rc = _lib.kernels().msq_sample_topp(_lib.ptr(lprobs), lprobs.stride(0), rows, V, _lib.ptr(p_t), int(per_row),
+                                            _lib.ptr(uniform.contiguous()), _lib.ptr(tok), _lib.ptr(lp), _lib.stream_ptr())
+        _lib.check_rc(rc, "msq_sample_topp")
+        return lp, tok
+    # the same draw in PyTorch: nucleus = {p >= threshold}, taken in index order
+    probs = torch.exp(lprobs.float())
+    probs = torch.where(torch.isfinite(probs), probs, torch.zeros_like(probs))
+    sprobs, _ = probs.sort(descending=True, dim=-1)
+    csum = sprobs.cumsum(dim=-1)
+    p = top_p.to(lprobs.device).float().reshape(-1, 1) if torch.is_tensor(top_p) else float(top_p)
+    keep_sorted = (csum - sprobs) < p  # always keeps the top token
+    last = keep_sorted.long().sum(dim=-1, keepdim=True).clamp(min=1) - 1
+    thr = sprobs.gather(-1, last)
+    kept = torch.where((probs >= thr) & (probs > 0), probs, torch.zeros_like(probs))
+    cdf = kept.cumsum(dim=-1)
+    draw = uniform.to(lprobs.device).float().clamp(0, 0.99999994).reshape(-1, 1) * cdf[:, -1:]
+    tok = (cdf <= draw).long().sum(dim=-1).clamp(max=V - 1)
+    return lprobs.gather(-1, tok[:, None]).squeeze(-1), tok
+
+
 # --------------------------------------------------------------------- colsum
 def colsum(x2d, out16=None, accumulate=False):
     """Column sums of ``[rows, N]`` (bias gradient), fp32 accumulation."""

@@ -22,6 +22,7 @@ import torch.nn as nn
 from torch import Tensor
 
 from metaseq_b200.models.decode_step import GraphedDecodeStep
+from metaseq_b200.ops import functional as ops_f
 
 logger = logging.getLogger(__name__)
 
@@ -179,6 +180,10 @@ class SequenceGenerator(nn.Module):
         if self.temperature == 0.0 or self.sampling_topp == 0.0:
             best = lprobs.max(dim=-1)
             return best.values, best.indices
+        if lprobs.is_cuda and lprobs.dtype == torch.float32 and lprobs.shape[-1] <= 56000 and ops_f.get_backend() != "torch":
+            # one kernel per step instead of sort + cumsum + mask + renormalise + multinomial over [rows, V]
+            p = sentence_p if sentence_p is not None else self.sampling_topp
+            return ops_f.sample_top_p(lprobs, p)
         probs = torch.exp(lprobs)
         sprobs, sidx = probs.sort(descending=True, dim=-1)
         csum = sprobs.cumsum(dim=-1)

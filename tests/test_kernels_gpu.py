@@ -555,3 +555,54 @@ def test_rms_norm_forward_backward(dtype, rows, D, affine):
         _close(mod.weight.grad, wr.grad, dtype, scale=float(rows) ** 0.5 * 2)
     _status_ok()
 
+
+def test_top_p_sampling_kernel_matches_the_sorted_definition():
+    torch.manual_seed(21)
+    rows, V = 64, 50272
+    logits = torch.randn(rows, V, device="cuda") * 3
+    logits[:, 1] = float("-inf")  # banned token
+    logits[::5, 100:40000] = float("-inf")
+    lprobs = torch.log_softmax(logits, -1)
+    u = torch.rand(rows, device="cuda")
+    # a vanishing nucleus is the arg-max
+    lp, tok = F.sample_top_p(lprobs, 1e-7, u)
+    assert torch.equal(tok, lprobs.argmax(-1)) and torch.equal(lp, lprobs.max(-1).values)
+    # against the same draw written with sort / cumsum (identical uniforms)
+    per_row_p = torch.linspace(0.3, 0.95, rows, device="cuda")
+    for p in (0.9, 0.5, 1.0, per_row_p):
+        before = _lib.launch_count()
+        lp, tok = F.sample_top_p(lprobs, p, u)
+        assert _lib.launch_count() == before + 1
+        F.set_backend("torch")
+        try:
+            lp_ref, tok_ref = F.sample_top_p(lprobs, p, u)
+        finally:
+            F.set_backend("auto")
+        assert torch.equal(lp, lprobs.gather(-1, tok[:, None]).squeeze(-1))
+        assert (tok != 1).all() and torch.isfinite(lp).all()
+        # every token lies in the nucleus of the sorted definition (ties with its last member included)
+        probs = lprobs.exp()
+        sp, _ = probs.sort(descending=True, dim=-1)
+        cs = sp.cumsum(-1)
+        pp = p.reshape(-1, 1) if torch.is_tensor(p) else p
+        last = ((cs - sp) < pp).long().sum(-1, keepdim=True).clamp(min=1) - 1
+        thr = sp.gather(-1, last).squeeze(-1)
+        chosen_p = probs.gather(-1, tok[:, None]).squeeze(-1)
+        assert (chosen_p >= thr * (1 - 1e-4)).all()
+        # cumulative sums in a different order move a draw across a token boundary only rarely
+        assert (tok == tok_ref).float().mean().item() >= 0.9
+    # frequencies over many rows with one distribution
+    V2, n = 96, 40000
+    base = torch.log_softmax(torch.randn(V2, device="cuda") * 1.5, -1)
+    many = base.expand(n, V2).contiguous()
+    _, tok = F.sample_top_p(many, 0.8, torch.rand(n, device="cuda"))
+    pr = base.exp()
+    sp, si = pr.sort(descending=True)
+    keep = (sp.cumsum(0) - sp) < 0.8
+    expect = torch.zeros(V2, device="cuda")
+    expect[si[keep]] = sp[keep] / sp[keep].sum()
+    freq = torch.bincount(tok, minlength=V2).float() / n
+    assert (freq[expect == 0] == 0).all()
+    assert (freq - expect).abs().max().item() < 0.01
+    _status_ok()
+
