@@ -310,3 +310,28 @@ def test_rms_norm_cpu_matches_definition():
     want = (dy * ref_in.detach() * torch.rsqrt(ref_in.detach().pow(2).mean(-1, keepdim=True) + mod.eps)).sum(0)
     assert torch.allclose(mod.weight.grad, want, atol=1e-4)
 
+
+
+def test_top_p_sampling_restatement_draws_from_the_nucleus():
+    from metaseq_b200.ops import functional as F
+
+    torch.manual_seed(0)
+    lp = torch.log_softmax(torch.randn(4, 50) * 2, -1)
+    lp[:, 3] = float("-inf")
+    chosen_lp, tok = F.sample_top_p(lp, 1e-6)
+    assert torch.equal(tok, lp.argmax(-1)) and torch.equal(chosen_lp, lp.max(-1).values)
+    counts = torch.zeros(50)
+    for _ in range(3000):
+        _, t = F.sample_top_p(lp[:1], 0.8)
+        counts[t[0]] += 1
+    p = lp[0].exp()
+    sp, si = p.sort(descending=True)
+    keep = (sp.cumsum(0) - sp) < 0.8
+    nucleus = si[keep]
+    expect = torch.zeros(50)
+    expect[nucleus] = p[nucleus] / p[nucleus].sum()
+    assert counts[expect == 0].sum() == 0
+    assert (counts / 3000 - expect).abs().max() < 0.03
+    # one nucleus size per row
+    _, t = F.sample_top_p(lp, torch.tensor([1e-6, 1e-6, 1e-6, 1e-6]))
+    assert torch.equal(t, lp.argmax(-1))
