@@ -70,13 +70,22 @@ def main(cfg: Cfg) -> None:
     max_epoch = cfg.optimization.max_epoch or math.inf
     train_meter = meters.StopwatchMeter()
     train_meter.start()
-    while epoch_itr.next_epoch_idx <= max_epoch:
-        valid_losses, should_stop = train(cfg, trainer, task, epoch_itr)
-        if should_stop:
-            break
-        trainer.lr_step(epoch_itr.epoch, valid_losses[0] if valid_losses else None)
-        epoch_itr = trainer.get_train_iterator(epoch_itr.next_epoch_idx, load_dataset=True,
-                                               disable_iterator_cache=True)
+    watchdog = trainer.start_watchdog()  # None unless --watchdog-timeout is set
+    try:
+        while epoch_itr.next_epoch_idx <= max_epoch:
+            valid_losses, should_stop = train(cfg, trainer, task, epoch_itr)
+            if should_stop:
+                break
+            trainer.lr_step(epoch_itr.epoch, valid_losses[0] if valid_losses else None)
+            epoch_itr = trainer.get_train_iterator(epoch_itr.next_epoch_idx, load_dataset=True,
+                                                   disable_iterator_cache=True)
+    except KeyboardInterrupt:
+        if watchdog is not None and watchdog.fired:
+            raise RuntimeError(f"training stopped by the watchdog: {watchdog.fired}") from None
+        raise
+    finally:
+        if watchdog is not None:
+            watchdog.stop()
     train_meter.stop()
     checkpoint_utils.wait_for_pending_writes()
     logger.info("done training in {:.1f} seconds".format(train_meter.sum))

@@ -97,6 +97,9 @@ class CommonConfig(MetaseqDataclass):
     all_gather_list_size: int = opt(16384, "number of bytes reserved for gathering stats from workers")
     model_parallel_size: int = opt(1, "total number of GPUs to parallelize model over")
     profile: bool = opt(False, "use pytorch profiler on the 6th step of rank 0")
+    watchdog_timeout: float = opt(0.0, "seconds without a finished training step (or with a kernel reporting a "
+                                       "timed-out wait) after which the host watchdog dumps all thread stacks and "
+                                       "interrupts the run; 0 disables it")
     use_plasma_view: bool = opt(False, "store indices and sizes in shared memory")
     plasma_path: Optional[str] = opt("/tmp/plasma", "path to run plasma_store")
     log_nvidia_smi: bool = opt(False, "log output from nvidia-smi during training")

@@ -222,6 +222,23 @@ def status_word(device) -> torch.Tensor:
     return _STATUS[key]
 
 
+_PEEK = {}
+
+
+def peek_status(device="cuda") -> int:
+    """Reads the status word without clearing it and without waiting for the work queued on the compute
+    streams: the copy runs on a stream of its own into pinned memory.  For the host watchdog thread."""
+    w = status_word(device)
+    key = w.device.index or 0
+    if key not in _PEEK:
+        _PEEK[key] = (torch.cuda.Stream(device=w.device), torch.zeros(1, dtype=torch.int32).pin_memory())
+    stream, host = _PEEK[key]
+    with torch.cuda.stream(stream):
+        host.copy_(w, non_blocking=True)
+    stream.synchronize()
+    return int(host[0])
+
+
 def check_status(device="cuda") -> int:
     """Reads (and clears) the kernel status word; non-zero means a wait timed out."""
     w = status_word(device)

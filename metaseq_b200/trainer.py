@@ -415,8 +415,24 @@ class Trainer:
 
     # ------------------------------------------------------------- train step
     @metrics.aggregate("train")
+    def start_watchdog(self):
+        """Host watchdog over the training loop (``--watchdog-timeout``); returns it, or ``None`` when disabled."""
+        timeout = float(getattr(self.cfg.common, "watchdog_timeout", 0.0) or 0.0)
+        if timeout <= 0 or getattr(self, "watchdog", None) is not None:
+            return getattr(self, "watchdog", None)
+        from metaseq_b200.ops import _lib
+        from metaseq_b200.utils.watchdog import StepWatchdog
+
+        status_fn = None
+        if self.device.type == "cuda" and _lib.kernels_path().exists():
+            status_fn = lambda: _lib.peek_status(self.device)  # noqa: E731
+        self.watchdog = StepWatchdog(timeout, status_fn=status_fn).start()
+        return self.watchdog
+
     def train_step(self, samples, raise_oom=False):
         """One optimizer update over ``samples`` (a list of micro-batches)."""
+        if getattr(self, "watchdog", None) is not None:
+            self.watchdog.beat()
         self._set_seed()
         self.model.train()
         self.criterion.train()
