@@ -129,7 +129,7 @@ class SequenceGenerator(nn.Module):
         sentence_p = torch.full((n,), self.sampling_topp, device=dev) if self.lambda_decay > 0 else None
         # ------------------------------------------------------- decode loop
         for step in range(start, max_len):
-            if step < min_len:
+            if step < min_len and step < max_len - 1:  # the forced EOS of the last position wins over min_len
                 lprobs[:, self.eos] = neg_inf
                 for s in self.stop:
                     lprobs[:, s] = neg_inf
@@ -190,7 +190,11 @@ class SequenceGenerator(nn.Module):
         p = sentence_p[:, None] if sentence_p is not None else self.sampling_topp
         # keep the smallest prefix whose mass reaches p (always at least the top token)
         cut = (csum - sprobs) >= p
-        sprobs = sprobs.masked_fill(cut, 0.0)
+        sprobs = torch.nan_to_num(sprobs.masked_fill(cut, 0.0), nan=0.0, posinf=0.0)
+        mass = sprobs.sum(dim=-1, keepdim=True)
+        # a row without any admissible token (everything banned) takes the first sorted entry instead of
+        # handing multinomial an all-zero row
+        sprobs[:, :1] = torch.where(mass > 0, sprobs[:, :1], torch.ones_like(mass))
         sprobs = sprobs / sprobs.sum(dim=-1, keepdim=True)
         choice = torch.multinomial(sprobs, 1)
         toks = sidx.gather(-1, choice).squeeze(-1)

@@ -335,3 +335,25 @@ def test_top_p_sampling_restatement_draws_from_the_nucleus():
     # one nucleus size per row
     _, t = F.sample_top_p(lp, torch.tensor([1e-6, 1e-6, 1e-6, 1e-6]))
     assert torch.equal(t, lp.argmax(-1))
+
+
+def test_sampling_with_min_len_equal_to_max_len_ends_in_eos():
+    """The last position forces EOS even when ``min_len`` still bans it, and a row whose tokens are all banned
+    never reaches multinomial as an all-zero distribution."""
+    from metaseq_b200.data import Dictionary
+    from metaseq_b200.sequence_generator import SequenceGenerator
+
+    d = Dictionary()
+    for i in range(12):
+        d.add_symbol(str(i))
+    torch.manual_seed(0)
+    gen = SequenceGenerator(ScriptedModel(len(d), d.eos()), d, beam_size=2, max_len_b=10, min_len=10, temperature=1.0,
+                            topp=0.9)
+    src = torch.tensor([[d.eos(), 4, 5]])
+    out = gen._generate({"net_input": {"src_tokens": src}})
+    toks = out["tokens"][0]
+    assert toks.shape == (2, 10)
+    assert (toks[:, -1] == d.eos()).all() and (toks[:, 3:-1] != d.eos()).all()
+    all_banned = torch.full((3, len(d)), float("-inf"))
+    lp, tok = gen._sample(all_banned)
+    assert tok.shape == (3,)
