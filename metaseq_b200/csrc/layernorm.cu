@@ -114,6 +114,82 @@ layernorm_fwd_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict_
   }
 }
 
+// Forward for rows of at most 2048 elements: one warp per row.  A lane holds VPW 16-byte vectors of the row (all
+// requested at once, kept packed), the two sums are warp shuffles, and nothing waits on a block-wide barrier, so
+// a CTA has eight independent rows in flight.  gamma / beta are re-read per row (they stay in L1).
+template <bool BF16, int VPW>
+__global__ void __launch_bounds__(LN_THREADS)
+layernorm_fwd_warp_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ gamma,
+                          const uint16_t* __restrict__ beta, uint16_t* __restrict__ y, float* __restrict__ mean_out,
+                          float* __restrict__ rstd_out, int rows, int D, float eps, int rms) {
+  const int nvec = D >> 3;
+  const int lane = threadIdx.x & 31;
+  const int warps = gridDim.x * (LN_THREADS / 32);
+  const float inv_d = 1.f / static_cast<float>(D);
+  dependents_launch();
+  dependents_wait();  // x comes from the preceding kernel
+  for (int row = blockIdx.x * (LN_THREADS / 32) + (threadIdx.x >> 5); row < rows; row += warps) {
+    const uint16_t* xr = x + static_cast<long long>(row) * D;
+    uint4 raw[VPW];
+#pragma unroll
+    for (int i = 0; i < VPW; ++i) {
+      const int v = lane + 32 * i;
+      raw[i] = v < nvec ? *reinterpret_cast<const uint4*>(xr + v * 8) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPW; ++i) {
+      const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 t = unpack2<BF16>(w[j]);
+        s += t.x + t.y;
+      }
+    }
+    const float mean = rms ? 0.f : warp_sum(s) * inv_d;
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPW; ++i) {
+      if (lane + 32 * i < nvec) {
+        const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 t = unpack2<BF16>(w[j]);
+          q += (t.x - mean) * (t.x - mean) + (t.y - mean) * (t.y - mean);
+        }
+      }
+    }
+    const float rstd = rsqrtf(warp_sum(q) * inv_d + eps);
+    if (lane == 0) {
+      if (mean_out) mean_out[row] = mean;
+      if (rstd_out) rstd_out[row] = rstd;
+    }
+    uint16_t* yr = y + static_cast<long long>(row) * D;
+#pragma unroll
+    for (int i = 0; i < VPW; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+        float f[8], g[8], b[8];
+        const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 t = unpack2<BF16>(w[j]);
+          f[2 * j] = t.x;
+          f[2 * j + 1] = t.y;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { g[j] = 1.f; b[j] = 0.f; }
+        if (gamma) load8<BF16>(gamma + v * 8, g);
+        if (beta) load8<BF16>(beta + v * 8, b);
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = (f[j] - mean) * rstd * g[j] + b[j];
+        store8<BF16>(yr + v * 8, o);
+      }
+    }
+  }
+}
+
 // dx = rstd * (gdy - mean(gdy) - xhat * mean(gdy * xhat)) [+ add], gdy = gamma * dy.
 // Per-CTA partial sums of dgamma (= dy * xhat) and dbeta (= dy) go to
 // part_g / part_b, each [gridDim.x, D] fp32, reduced by layernorm_bwd_finalize.
@@ -273,6 +349,24 @@ static int norm_fwd(const void* x, const void* gamma, const void* beta, void* y,
   auto G = static_cast<const uint16_t*>(gamma);
   auto B = static_cast<const uint16_t*>(beta);
   auto Y = static_cast<uint16_t*>(y);
+  if (nvec <= 256) {
+    // one warp per row; enough CTAs for eight per SM, each warp looping over rows
+    const int vpw = (nvec + 31) / 32;
+    const int want = (rows + LN_THREADS / 32 - 1) / (LN_THREADS / 32);
+    const int cap = ln_grid(1 << 30) * 2;
+    const dim3 g(want < cap ? want : cap), t(LN_THREADS);
+#define MSQ_LN_WARP(V)                                                                                                  \
+  case V:                                                                                                               \
+    if (bf16) launch_chained(layernorm_fwd_warp_kernel<true, V>, g, t, 0, stream, 1u, X, G, B, Y, mean, rstd, rows, D, eps, rms); \
+    else launch_chained(layernorm_fwd_warp_kernel<false, V>, g, t, 0, stream, 1u, X, G, B, Y, mean, rstd, rows, D, eps, rms);    \
+    break;
+    switch (vpw) {
+      MSQ_LN_WARP(1) MSQ_LN_WARP(2) MSQ_LN_WARP(3) MSQ_LN_WARP(4) MSQ_LN_WARP(5) MSQ_LN_WARP(6) MSQ_LN_WARP(7) MSQ_LN_WARP(8)
+      default: return -1;
+    }
+#undef MSQ_LN_WARP
+    return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  }
   if (bf16) {
     MSQ_LN_DISPATCH(nvec, (launch_chained(layernorm_fwd_kernel<true, VPT>, dim3(grid), dim3(LN_THREADS), 0, stream, 1u, X, G, B, Y, mean, rstd, rows, D, eps, rms)))
   } else {
