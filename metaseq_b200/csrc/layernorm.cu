@@ -349,8 +349,9 @@ static int norm_fwd(const void* x, const void* gamma, const void* beta, void* y,
   auto G = static_cast<const uint16_t*>(gamma);
   auto B = static_cast<const uint16_t*>(beta);
   auto Y = static_cast<uint16_t*>(y);
-  if (nvec <= 256) {
-    // one warp per row; enough CTAs for eight per SM, each warp looping over rows
+  if (nvec <= 256 && rows >= 2048) {
+    // Many rows: one warp per row, each warp looping over rows.  With few rows (a decode step) the block-per-row
+    // kernel below is quicker: a row is spread over 256 threads instead of walked by 32.
     const int vpw = (nvec + 31) / 32;
     const int want = (rows + LN_THREADS / 32 - 1) / (LN_THREADS / 32);
     const int cap = ln_grid(1 << 30) * 2;
