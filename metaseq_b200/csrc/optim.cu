@@ -127,6 +127,76 @@ adamw_kernel(void* __restrict__ p, const void* __restrict__ g, float* __restrict
   }
 }
 
+// List form: one launch updates every tensor of a table in device memory (blockIdx.y = tensor).  16-bit
+// parameters and gradients with 16-byte aligned storage are processed eight elements per thread and iteration
+// (one 16-byte load each for p and g, two each for m and v); other cases take the scalar loop.
+struct AdamTensor {
+  void* p;
+  const void* g;
+  float* m;
+  float* v;
+  long long n;
+};
+
+template <int PDT, int GDT>
+__global__ void __launch_bounds__(512)
+adamw_multi_kernel(const AdamTensor* __restrict__ table, float lr, float beta1, float beta2, float eps,
+                   float weight_decay, float step_size, const float* __restrict__ ctrl) {
+  const float gmul = ctrl ? ctrl[0] : 1.f;
+  if (ctrl && ctrl[1] != 0.f) return;  // overflow: leave params and moments untouched
+  const AdamTensor t = table[blockIdx.y];
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  auto update = [&](float pi, float gi, float& mi, float& vi) -> float {
+    gi *= gmul;
+    mi = beta1 * mi + (1.f - beta1) * gi;
+    vi = beta2 * vi + (1.f - beta2) * gi * gi;
+    pi = pi - lr * weight_decay * pi;
+    return pi - step_size * (mi / (sqrtf(vi) + eps));
+  };
+  long long done = 0;
+  if constexpr (PDT != 2 && GDT != 2) {
+    const bool aligned = ((reinterpret_cast<uintptr_t>(t.p) | reinterpret_cast<uintptr_t>(t.g) |
+                           reinterpret_cast<uintptr_t>(t.m) | reinterpret_cast<uintptr_t>(t.v)) & 15) == 0;
+    if (aligned) {
+      const long long n8 = t.n >> 3;
+      for (long long i = tid; i < n8; i += stride) {
+        const uint4 pv = static_cast<const uint4*>(t.p)[i];
+        const uint4 gv = static_cast<const uint4*>(t.g)[i];
+        float4 m0 = reinterpret_cast<float4*>(t.m)[2 * i], m1 = reinterpret_cast<float4*>(t.m)[2 * i + 1];
+        float4 v0 = reinterpret_cast<float4*>(t.v)[2 * i], v1 = reinterpret_cast<float4*>(t.v)[2 * i + 1];
+        const uint32_t pw[4] = {pv.x, pv.y, pv.z, pv.w}, gw[4] = {gv.x, gv.y, gv.z, gv.w};
+        float mm[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+        float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+        uint32_t out[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 pf = unpack2<PDT == 1>(pw[j]);
+          const float2 gf = unpack2<GDT == 1>(gw[j]);
+          const float a = update(pf.x, gf.x, mm[2 * j], vv[2 * j]);
+          const float b = update(pf.y, gf.y, mm[2 * j + 1], vv[2 * j + 1]);
+          out[j] = pack2<PDT == 1>(a, b);
+        }
+        static_cast<uint4*>(t.p)[i] = make_uint4(out[0], out[1], out[2], out[3]);
+        reinterpret_cast<float4*>(t.m)[2 * i] = make_float4(mm[0], mm[1], mm[2], mm[3]);
+        reinterpret_cast<float4*>(t.m)[2 * i + 1] = make_float4(mm[4], mm[5], mm[6], mm[7]);
+        reinterpret_cast<float4*>(t.v)[2 * i] = make_float4(vv[0], vv[1], vv[2], vv[3]);
+        reinterpret_cast<float4*>(t.v)[2 * i + 1] = make_float4(vv[4], vv[5], vv[6], vv[7]);
+      }
+      done = n8 << 3;
+    }
+  }
+  for (long long i = done + tid; i < t.n; i += stride) {
+    float mi = t.m[i], vi = t.v[i];
+    const float pi = update(load_as_float<PDT>(t.p, i), load_as_float<GDT>(t.g, i), mi, vi);
+    t.m[i] = mi;
+    t.v[i] = vi;
+    if constexpr (PDT == 0) static_cast<__half*>(t.p)[i] = __float2half(pi);
+    else if constexpr (PDT == 1) static_cast<__nv_bfloat16*>(t.p)[i] = __float2bfloat16(pi);
+    else static_cast<float*>(t.p)[i] = pi;
+  }
+}
+
 static int device_sms() {
   static int sms = 0;
   if (!sms) {
@@ -191,3 +261,33 @@ extern "C" int msq_adamw(void* p, const void* g, float* m, float* v, void* p16_o
 #undef MSQ_ADAM
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
+
+// List form of msq_adamw (the reference's apex multi_tensor_adam: metaseq/modules/apex/multi_tensor_adam.cu).
+// `table`: `count` records {p, g, m, v, n} (5 x 8 bytes each) in device memory; `max_n`: the largest n, which sizes
+// the grid.  All tensors share the data types and hyper-parameters.
+extern "C" int msq_adamw_multi(const void* table, int count, long long max_n, int p_dtype, int g_dtype, float lr,
+                               float beta1, float beta2, float eps, float weight_decay, float step_size,
+                               const float* ctrl, cudaStream_t stream) {
+  using namespace msq;
+  if (count <= 0 || max_n <= 0) return 0;
+  if (count > 65535) return -2;
+  long long blocks = (max_n / 8 + 511) / 512;
+  const long long cap = (16LL * device_sms() + count - 1) / count;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  const dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(count));
+  const AdamTensor* tb = static_cast<const AdamTensor*>(table);
+#define MSQ_ADAM_MULTI(PD, GD) \
+  adamw_multi_kernel<PD, GD><<<grid, 512, 0, stream>>>(tb, lr, beta1, beta2, eps, weight_decay, step_size, ctrl)
+  if (p_dtype == 0 && g_dtype == 0) MSQ_ADAM_MULTI(0, 0);
+  else if (p_dtype == 1 && g_dtype == 1) MSQ_ADAM_MULTI(1, 1);
+  else if (p_dtype == 2 && g_dtype == 0) MSQ_ADAM_MULTI(2, 0);
+  else if (p_dtype == 2 && g_dtype == 1) MSQ_ADAM_MULTI(2, 1);
+  else if (p_dtype == 2 && g_dtype == 2) MSQ_ADAM_MULTI(2, 2);
+  else if (p_dtype == 0 && g_dtype == 2) MSQ_ADAM_MULTI(0, 2);
+  else if (p_dtype == 1 && g_dtype == 2) MSQ_ADAM_MULTI(1, 2);
+  else return -2;
+#undef MSQ_ADAM_MULTI
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+

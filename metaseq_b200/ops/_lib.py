@@ -142,6 +142,7 @@ _OPTIONAL = {
     "msq_gemm_skinny_set_prof": [P],
     "msq_scale_rows": [P, L, L, I, P, I, I, I, P],
     "msq_sample_topp": [P, L, I, I, P, I, P, P, P, P],
+    "msq_adamw_multi": [P, I, L, I, I, F, F, F, F, F, F, P, P],
     "msq_rmsnorm_fwd": [P, P, P, P, I, I, F, I, P],
     "msq_rmsnorm_bwd": [P, P, P, P, P, P, P, P, P, I, I, I, I, P],
     "msq_decode_attn_step": [P, P, P, L, P, P, P, P, I, I, I, P, I, L, L, L, L, L, F, I, P, I, P],

@@ -808,6 +808,35 @@ def clip_decision(sumsq_terms: torch.Tensor, pre_factor: float, max_norm: float,
     return ctrl
 
 
+_ADAM_TABLES: dict = {}
+
+
+def adamw_step_multi(items, *, lr, beta1, beta2, eps, weight_decay, step, ctrl=None):
+    """One launch of the AdamW update over a list of ``(p, g, m, v)`` tensors that share data types,
+    hyper-parameters and step count (the reference's ``multi_tensor_adam``).  The table of pointers lives on the
+    device and is rebuilt only when a pointer or size changes.  Callers check eligibility (contiguous CUDA
+    tensors, kernel backend)."""
+    p0, g0 = items[0][0], items[0][1]
+    key = tuple((p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(), p.numel()) for p, g, m, v in items)
+    dev_key = (p0.device.index or 0, len(items), key[0][0])
+    cached = _ADAM_TABLES.get(dev_key)
+    if cached is None or cached[0] != key:
+        flat = [x for rec in key for x in rec]
+        table = torch.tensor(flat, dtype=torch.int64).to(p0.device, non_blocking=False)
+        if len(_ADAM_TABLES) > 32:
+            _ADAM_TABLES.clear()
+        cached = (key, table)
+        _ADAM_TABLES[dev_key] = cached
+    bc1 = 1.0 - beta1 ** step
+    bc2 = 1.0 - beta2 ** step
+    step_size = lr * math.sqrt(bc2) / bc1
+    rc = _lib.kernels().msq_adamw_multi(
+        _lib.ptr(cached[1]), len(items), max(rec[4] for rec in key), _lib.dtype_code(p0.dtype), _lib.dtype_code(g0.dtype),
+        float(lr), float(beta1), float(beta2), float(eps), float(weight_decay), float(step_size), _lib.ptr(ctrl),
+        _lib.stream_ptr())
+    _lib.check_rc(rc, "msq_adamw_multi")
+
+
 def adamw_step(p, g, m, v, *, lr, beta1, beta2, eps, weight_decay, step, ctrl=None, p16_out=None):
     """One AdamW update of a flat tensor (decoupled decay, bias correction folded into the
     step size, eps outside the sqrt).  ``ctrl`` is the device control block from

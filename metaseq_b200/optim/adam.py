@@ -80,6 +80,7 @@ class Adam(torch.optim.Optimizer):
                 loss = closure()
         for group in self.param_groups:
             beta1, beta2 = group["betas"]
+            batched = {}  # (step, param dtype, grad dtype, device) -> [(p, g, m, v)]: one launch each
             for p in group["params"]:
                 if p.grad is None:
                     continue
@@ -98,11 +99,7 @@ class Adam(torch.optim.Optimizer):
                 m, v = state["exp_avg"], state["exp_avg_sq"]
                 if p.is_cuda and self.use_kernels and p.is_contiguous() and grad.is_contiguous() \
                         and ops.get_backend() != "torch":
-                    local_ctrl = ctrl
-                    if local_ctrl is None and scale != 1.0:
-                        local_ctrl = self._scale_ctrl(p.device, scale)
-                    ops.adamw_step(p.data, grad, m, v, lr=group["lr"], beta1=beta1, beta2=beta2, eps=group["eps"],
-                                   weight_decay=group["weight_decay"], step=state["step"], ctrl=local_ctrl)
+                    batched.setdefault((state["step"], p.dtype, grad.dtype, p.device), []).append((p.data, grad, m, v))
                     continue
                 g32 = grad.float()
                 if ctrl is not None:
@@ -124,6 +121,16 @@ class Adam(torch.optim.Optimizer):
                 p32.addcdiv_(m, denom, value=-step_size)
                 if p.dtype != torch.float32:
                     p.data.copy_(p32)
+            for (step, _, _, device), items in batched.items():
+                local_ctrl = ctrl
+                if local_ctrl is None and scale != 1.0:
+                    local_ctrl = self._scale_ctrl(device, scale)
+                kw = dict(lr=group["lr"], beta1=beta1, beta2=beta2, eps=group["eps"],
+                          weight_decay=group["weight_decay"], step=step, ctrl=local_ctrl)
+                if len(items) == 1:
+                    ops.adamw_step(*items[0], **kw)
+                else:
+                    ops.adamw_step_multi(items, **kw)
         return loss
 
     _ctrl_cache = {}

@@ -606,3 +606,43 @@ def test_top_p_sampling_kernel_matches_the_sorted_definition():
     assert (freq - expect).abs().max().item() < 0.01
     _status_ok()
 
+
+
+@pytest.mark.parametrize("pdt,gdt", [(torch.float16, torch.float16), (torch.bfloat16, torch.bfloat16),
+                                     (torch.float32, torch.float16), (torch.float32, torch.float32)])
+def test_adamw_list_form_matches_one_launch_per_tensor(pdt, gdt):
+    torch.manual_seed(4)
+    sizes = [8 * 1000, 12345, 7, 262144 + 3, 64]
+    kw = dict(lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=3)
+
+    def make():
+        g = torch.Generator(device="cuda").manual_seed(9)
+        items = []
+        for i, n in enumerate(sizes):
+            base = torch.randn(n + 8, device="cuda", generator=g)
+            off = 1 if i == 3 else 0  # one parameter whose storage is not 16-byte aligned
+            p = base[off:off + n].to(pdt) if pdt != torch.float32 else base[off:off + n].clone()
+            gr = (torch.randn(n, device="cuda", generator=g) * 0.1).to(gdt)
+            m = torch.randn(n, device="cuda", generator=g) * 0.01
+            v = torch.rand(n, device="cuda", generator=g) * 0.01
+            items.append((p.contiguous(), gr, m, v))
+        return items
+
+    ctrl = torch.tensor([0.5, 0.0, 0.0, 1.0], device="cuda")
+    one, many = make(), make()
+    for it in one:
+        F.adamw_step(*it, ctrl=ctrl, **kw)
+    before = _lib.launch_count()
+    F.adamw_step_multi(many, ctrl=ctrl, **kw)
+    assert _lib.launch_count() == before + 1
+    for a, b in zip(one, many):
+        for x, y in zip(a, b):
+            torch.testing.assert_close(x.float(), y.float(), rtol=1e-6, atol=1e-7)
+    # the skip flag leaves everything untouched
+    skip = torch.tensor([1.0, 1.0, 0.0, 1.0], device="cuda")
+    snap = [[t.clone() for t in it] for it in many]
+    F.adamw_step_multi(many, ctrl=skip, **kw)
+    for a, b in zip(snap, many):
+        for x, y in zip(a, b):
+            assert torch.equal(x, y)
+    _status_ok()
