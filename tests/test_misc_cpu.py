@@ -357,3 +357,27 @@ def test_sampling_with_min_len_equal_to_max_len_ends_in_eos():
     all_banned = torch.full((3, len(d)), float("-inf"))
     lp, tok = gen._sample(all_banned)
     assert tok.shape == (3,)
+
+
+def test_graphed_decode_step_declines_models_it_cannot_serve():
+    """On a CPU (or any decoder that is not the framework's own) the generator keeps the module path."""
+    from metaseq_b200.models.decode_step import GraphedDecodeStep
+    from metaseq_b200.ops import functional as F
+
+    assert not GraphedDecodeStep.supported(ScriptedDecoder(16, 2))
+    with F.dependent_launch():  # no kernels library needed on a CPU: the context is a no-op
+        pass
+
+    from metaseq_b200 import options, tasks
+    from metaseq_b200.dataclass.utils import convert_namespace_to_config
+
+    parser = options.get_training_parser()
+    ns = options.parse_args_and_arch(parser, input_args=[
+        "--task", "dummy_lm", "--dict-size", "60", "--tokens-per-sample", "16", "--batch-size", "1",
+        "--arch", "transformer_lm_megatron", "--decoder-layers", "1", "--decoder-embed-dim", "32",
+        "--decoder-ffn-embed-dim", "64", "--decoder-attention-heads", "2", "--criterion", "cross_entropy",
+        "--optimizer", "adam", "--lr", "1e-3", "--distributed-world-size", "1", "--cpu"])
+    cfg = convert_namespace_to_config(ns)
+    task = tasks.setup_task(cfg.task)
+    model = task.build_model(cfg.model).eval()
+    assert not GraphedDecodeStep.supported(model.decoder)
