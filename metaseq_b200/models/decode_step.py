@@ -34,7 +34,17 @@ from metaseq_b200.modules.transformer_decoder_layer import ModelParallelTransfor
 from metaseq_b200.ops import functional as F
 from metaseq_b200.parallel import mpu
 
-_MAX_CACHED_STEPS = 2
+_MAX_CACHED_STEPS = 3
+
+
+def bucket_rows(rows: int) -> int:
+    """Batch sizes share graphs and caches in buckets (powers of two up to 64, then multiples of 64), so that a
+    service whose batches vary in size does not capture a graph and allocate caches for every size it meets.
+    The rows beyond the live ones carry padding tokens."""
+    b = 1
+    while b < rows and b < 64:
+        b *= 2
+    return b if rows <= 64 else -(-rows // 64) * 64
 
 
 def _tp_world() -> int:
@@ -58,7 +68,7 @@ class GraphedDecodeStep:
             return False
         if decoder.training or decoder.sequence_parallel:
             return False
-        if _tp_world() > 1 and (_tp_world() > 8 or rows > 64 or w.shape[1] % 128 != 0):
+        if _tp_world() > 1 and (_tp_world() > 8 or bucket_rows(rows) > 64 or w.shape[1] % 128 != 0):
             return False
         if decoder.self_attn_doc_sep != UNSPECIFIED_DOC_SEP or w.shape[1] % 8 != 0:
             return False
@@ -82,23 +92,28 @@ class GraphedDecodeStep:
 
     @classmethod
     def for_decoder(cls, decoder, rows: int, min_capacity: int) -> "GraphedDecodeStep":
-        """The step object for this batch size with room for ``min_capacity`` positions, kept on the decoder
-        (the newest few sizes only: each holds a full set of caches)."""
+        """The step object serving ``rows`` sequences (it is built for the bucket ``rows`` falls into) with room
+        for ``min_capacity`` positions, kept on the decoder (the newest few buckets only: each holds a full set of
+        caches)."""
         table: Dict[int, GraphedDecodeStep] = decoder.__dict__.setdefault("_graphed_decode_steps", {})
-        step = table.pop(rows, None)
+        width = bucket_rows(rows)
+        step = table.pop(width, None)
         if step is not None and step.capacity < min_capacity:
             step = None
         if step is None:
             while len(table) >= _MAX_CACHED_STEPS:
                 table.pop(next(iter(table)))
             limit = int(decoder.max_positions()) + 2
-            step = cls(decoder, rows, min(limit, max(min_capacity, -(-min_capacity // 256) * 256)))
-        table[rows] = step  # most recently used last
+            step = cls(decoder, width, min(limit, max(min_capacity, -(-min_capacity // 256) * 256)))
+        table[width] = step  # most recently used last
+        step.live = rows
         return step
 
     def __init__(self, decoder, rows: int, capacity: int):
         self.decoder = decoder
-        self.rows = rows
+        self.rows = rows  # rows of the graph and the caches
+        self.live = rows  # rows in use (set by for_decoder); the others carry padding
+        self.views: List[KVCache] = []
         w = decoder.embed_tokens.weight
         self.device, self.dtype = w.device, w.dtype
         self.capacity = int(capacity)
@@ -134,19 +149,31 @@ class GraphedDecodeStep:
 
     # ------------------------------------------------------------------ state
     def new_state(self) -> Dict:
-        """An ``incremental_state`` whose caches are the ones the graph addresses, emptied."""
+        """An ``incremental_state`` whose caches are the first ``live`` rows of the ones the graph addresses,
+        emptied."""
         state: Dict = {}
+        self.views = []
         for layer, cache in zip(self.decoder.layers, self.caches):
             cache.length = 0
-            state[layer.self_attn._cache_key] = cache
+            view = cache
+            if self.live != self.rows:
+                view = KVCache.__new__(KVCache)
+                view.k, view.v, view.length = cache.k[: self.live], cache.v[: self.live], 0
+            self.views.append(view)
+            state[layer.self_attn._cache_key] = view
         return state
 
     def begin(self, prefix_tokens: torch.Tensor) -> None:
-        """Call after the prefill over ``prefix_tokens`` ``[rows, T]`` went through the caches."""
-        assert prefix_tokens.shape[0] == self.rows
-        self.count.copy_(prefix_tokens.ne(self.pad).sum(dim=1))
-        filled = self.caches[0].length
-        assert filled == prefix_tokens.shape[1] and all(c.length == filled for c in self.caches)
+        """Call after the prefill over ``prefix_tokens`` ``[live, T]`` went through the caches."""
+        assert prefix_tokens.shape[0] == self.live and self.views
+        self.count.zero_()
+        self.count[: self.live] = prefix_tokens.ne(self.pad).sum(dim=1)
+        filled = self.views[0].length
+        assert filled == prefix_tokens.shape[1] and all(c.length == filled for c in self.views)
+        assert all(v.k.data_ptr() == c.k.data_ptr() for v, c in zip(self.views, self.caches)), \
+            "a cache was reallocated during the prefill"
+        for cache in self.caches:
+            cache.length = filled
         self.length.fill_(filled)
         self._length_hint = max(1, filled)
 
@@ -242,7 +269,11 @@ class GraphedDecodeStep:
         filled = self.caches[0].length
         if filled + 1 > self.capacity:
             raise RuntimeError(f"decode step beyond the cache capacity of {self.capacity} positions")
-        self.tok.copy_(new_tokens)
+        if self.live == self.rows:
+            self.tok.copy_(new_tokens)
+        else:
+            self.tok.fill_(self.pad)
+            self.tok[: self.live] = new_tokens
         if self.tp > 1:
             self.x_in.copy_(self._embed())
         if self.graph is None:
@@ -250,4 +281,7 @@ class GraphedDecodeStep:
         self.graph.replay()
         for cache in self.caches:
             cache.length = filled + 1
-        return self.logits if self.tp == 1 else self._logits(self.x_out)
+        for view in self.views:
+            view.length = filled + 1
+        logits = self.logits if self.tp == 1 else self._logits(self.x_out)
+        return logits if self.live == self.rows else logits[: self.live]

@@ -184,12 +184,15 @@ def test_graphed_decode_step_matches_module_path(activation):
     dec = model.decoder
     assert GraphedDecodeStep.supported(dec)
     pad = dec.padding_idx
-    for trial in range(2):
-        tokens = torch.randint(4, 50272, (3, 48), device="cuda")
+    runners = []
+    for trial, rows in enumerate((3, 4, 3)):  # 3 and 4 rows share one bucket: same graph and caches, padded rows
+        tokens = torch.randint(4, 50272, (rows, 48), device="cuda")
         tokens[1, 20:24] = pad  # a hole: positions stop counting there
         with torch.no_grad():
             full, _ = model(tokens)
-            runner = GraphedDecodeStep.for_decoder(dec, 3, 64)
+            runner = GraphedDecodeStep.for_decoder(dec, rows, 64)
+            runners.append(runner)
+            assert runner.rows == 4 and runner.live == rows
             state = runner.new_state()
             model(tokens[:, :32], incremental_state=state)
             runner.begin(tokens[:, :32])
@@ -197,7 +200,7 @@ def test_graphed_decode_step_matches_module_path(activation):
                 logits = runner.step(tokens[:, t])
                 torch.testing.assert_close(logits.float(), full[:, t].float(), rtol=5e-2, atol=5e-2)
         assert runner.caches[0].length == 47 and int(runner.length.item()) == 47
-        assert GraphedDecodeStep.for_decoder(dec, 3, 64) is runner
+    assert runners[0] is runners[1] and runners[1] is runners[2]
     assert _lib.check_status(torch.device("cuda")) == 0
 
 
@@ -208,7 +211,7 @@ def test_sequence_generator_with_decode_graph_matches_module_loop():
     tr, batch = _trainer(cfg)
     model = tr.get_model().eval()
     d = tr.task.target_dictionary
-    src = torch.randint(10, 50000, (4, 24), device="cuda")
+    src = torch.randint(10, 50000, (5, 24), device="cuda")  # five prompts run in the bucket of eight rows
     outs = []
     for graph in (True, False):
         sg = SequenceGenerator([model], d, beam_size=1, max_len_b=56, min_len=56, temperature=1.0, topp=-1,
