@@ -99,6 +99,15 @@ def time_graphed(fn, variants: int, launches: int = 24, dependent: bool = False)
     return times[len(times) // 2]
 
 
+def _torch_top_p(lprobs, uniform):
+    prev = F.get_backend()
+    F.set_backend("torch")
+    try:
+        return F.sample_top_p(lprobs, 0.9, uniform)
+    finally:
+        F.set_backend(prev)
+
+
 def with_backend(name, fn):
     def run():
         prev = F.get_backend()
@@ -265,6 +274,15 @@ def main(argv=None):
         results.append(rec)
         print(json.dumps(rec), flush=True)
         del caches
+        # nucleus sampling over the full vocabulary (fp32 log-probabilities), against the sort-based restatement
+        lps = [torch.log_softmax(torch.randn(Bd, V, device=dev) * 3, -1) for _ in range(4)]
+        uni = torch.rand(Bd, device=dev)
+        ms = time_graphed(lambda i: F.sample_top_p(lps[i], 0.9, uni), 4)
+        tms = time_graphed(lambda i: _torch_top_p(lps[i], uni), 4)
+        rec = dict(op="sample_top_p", rows=Bd, V=V, ms=round(ms, 5), torch_sort_ms=round(tms, 5),
+                   speedup_vs_torch=round(tms / ms, 2))
+        results.append(rec)
+        print(json.dumps(rec), flush=True)
     bad = _lib.check_status(dev)
     summary = dict(model=args.model, batch=B, seq=T, dtype=args.dtype, peaks=peaks, kernel_status=bad,
                    device=torch.cuda.get_device_name(0))
