@@ -11,7 +11,7 @@ from datetime import timedelta
 from urllib.parse import urlparse
 
 import torch.distributed as dist
-from torch.distributed import rendezvous as _rdzv
+from torch.distributed.rendezvous import register_rendezvous_handler
 
 logger = logging.getLogger(__name__)
 _MAX_RETRIES = 5
@@ -89,7 +89,7 @@ def _barrierless_handler(url, timeout=timedelta(minutes=30), **kwargs):
 def register():
     for scheme, handler in (("tcpr", _tcpr_handler), ("barrierlesstcpr", _barrierless_handler)):
         try:
-            _rdzv.register_rendezvous_handler(scheme, handler)
+            register_rendezvous_handler(scheme, handler)
         except RuntimeError:
             pass  # already registered
 

@@ -196,3 +196,63 @@ def test_flag_in_data_exchange_never_delivers_stale_rows():
     for t in threads:
         t.join(timeout=120)
     assert not errors, errors[:3]
+
+
+# --------------------------------------------------------------- rendezvous retries
+def test_tcp_store_connection_is_retried_with_backoff(monkeypatch):
+    """A start-up race (the store's host is not listening yet) is absorbed by retries; a persistent failure
+    surfaces after the last attempt."""
+    import torch.distributed as dist
+
+    from metaseq_b200.parallel import rendezvous
+
+    calls, sleeps = [], []
+
+    class FlakyStore:
+        def __init__(self, *a, **k):
+            calls.append(a)
+            if len(calls) < 3:
+                raise RuntimeError("connect() timed out")
+
+    monkeypatch.setattr(dist, "TCPStore", FlakyStore)
+    monkeypatch.setattr(rendezvous.time, "sleep", sleeps.append)
+    store = rendezvous._store_with_retries("127.0.0.1", 1234, 1, 2, datetime.timedelta(seconds=1))
+    assert isinstance(store, FlakyStore) and len(calls) == 3
+    assert len(sleeps) == 2 and sleeps[1] > sleeps[0] >= 1.0  # exponential backoff with jitter
+
+    class DeadStore:
+        def __init__(self, *a, **k):
+            calls.append(a)
+            raise RuntimeError("connection refused")
+
+    calls.clear()
+    monkeypatch.setattr(dist, "TCPStore", DeadStore)
+    with pytest.raises(RuntimeError):
+        rendezvous._store_with_retries("127.0.0.1", 1234, 1, 2, datetime.timedelta(seconds=1))
+    assert len(calls) == rendezvous._MAX_RETRIES
+    with pytest.raises(ValueError):
+        list(rendezvous._tcpr_handler("tcpr://127.0.0.1:1234?rank=0"))  # world_size missing
+
+
+def test_tcpr_rendezvous_initialises_a_process_group():
+    import torch.multiprocessing as mp
+
+    world = 2
+    with mp.Manager() as mgr:
+        out = mgr.dict()
+        mp.spawn(_tcpr_rank, args=(world, _free_port(), out), nprocs=world, join=True)
+        assert dict(out) == {0: 3.0, 1: 3.0}
+
+
+def _tcpr_rank(rank, world, port, out):
+    import torch.distributed as dist
+
+    from metaseq_b200.parallel import rendezvous  # noqa: F401 - registers the schemes
+
+    # torch appends rank and world_size to the URL itself
+    dist.init_process_group("gloo", init_method=f"tcpr://127.0.0.1:{port}", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=30))
+    t = torch.tensor([float(rank + 1)])
+    dist.all_reduce(t)
+    out[rank] = float(t)
+    dist.destroy_process_group()
