@@ -87,7 +87,8 @@ def main(cfg, do_profile: bool = False) -> None:
 
 def cli_main():
     parser = options.get_generation_parser()
-    parser.add_argument("--profile", action="store_true", help="record a profiler trace instead of timing")
+    if not any("--profile" in a.option_strings for a in parser._actions):  # the common options already carry it
+        parser.add_argument("--profile", action="store_true", help="record a profiler trace instead of timing")
     args = options.parse_args_and_arch(parser)
     cfg = convert_namespace_to_config(args)
     dist_utils.call_main(cfg, main, do_profile=getattr(args, "profile", False))

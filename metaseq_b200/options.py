@@ -151,12 +151,20 @@ def parse_args_and_arch(parser: argparse.ArgumentParser, input_args: Optional[Li
             raise RuntimeError(f"unknown --arch {args.arch}")
     if hasattr(args, "task"):
         TASK_REGISTRY[args.task].add_args(parser)
+        # the data directory may also be given positionally, as on the reference's command lines
+        # (metaseq/dataclass/utils.py:62-64: ``data`` is a positional argument there)
+        if any(a.dest == "data" for a in parser._actions) and not any(a.dest == "data_positional" for a in parser._actions):
+            parser.add_argument("data_positional", nargs="?", default=None, metavar="DATA",
+                                help="path to the data directory (same as --data)")
     for name, reg in _registry.REGISTRIES.items():
         choice = getattr(args, name, None)
         if choice is not None:
             cls = reg["registry"][choice]
             if hasattr(cls, "add_args"):
                 cls.add_args(parser)
+            elif choice in reg["dataclass_registry"]:
+                # a component registered with a config dataclass contributes that dataclass's flags
+                gen_parser_from_dataclass(parser, reg["dataclass_registry"][choice]())
     if modify_parser is not None:
         modify_parser(parser)
     if parse_known:
@@ -165,6 +173,10 @@ def parse_args_and_arch(parser: argparse.ArgumentParser, input_args: Optional[Li
         args = parser.parse_args(input_args)
         extra = None
 
+    if hasattr(args, "data_positional"):
+        if args.data_positional is not None and getattr(args, "data", None) is None:
+            args.data = args.data_positional
+        del args.data_positional
     if (hasattr(args, "batch_size_valid") and args.batch_size_valid is None) or not hasattr(args, "batch_size_valid"):
         args.batch_size_valid = getattr(args, "batch_size", None)
     if hasattr(args, "max_tokens_valid") and args.max_tokens_valid is None:

@@ -381,3 +381,23 @@ def test_graphed_decode_step_declines_models_it_cannot_serve():
     task = tasks.setup_task(cfg.task)
     model = task.build_model(cfg.model).eval()
     assert not GraphedDecodeStep.supported(model.decoder)
+
+
+def test_service_launch_args_parse_and_data_may_be_positional():
+    from metaseq_b200 import options
+    from metaseq_b200.service import constants as C
+
+    flat = []
+    for s in C.LAUNCH_ARGS:
+        flat += s.split()
+    args = options.parse_args_and_arch(options.get_generation_parser(), input_args=flat)
+    assert args.bpe == "hf_byte_bpe" and args.bpe_merges == C.BPE_MERGES and args.bpe_vocab == C.BPE_VOCAB
+    assert args.data == "/tmp" and not hasattr(args, "data_positional")
+    assert args.model_parallel_size == C.MODEL_PARALLEL
+
+    parser = options.get_training_parser()
+    base = ["--task", "streaming_language_modeling", "--arch", "transformer_lm_megatron", "--criterion", "cross_entropy",
+            "--optimizer", "adam", "--lr", "1e-3", "--batch-size", "1", "--tokens-per-sample", "16"]
+    a = options.parse_args_and_arch(parser, input_args=["/corpus"] + base)
+    b = options.parse_args_and_arch(options.get_training_parser(), input_args=base + ["--data", "/corpus"])
+    assert a.data == b.data == "/corpus"
