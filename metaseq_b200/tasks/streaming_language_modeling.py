@@ -240,6 +240,14 @@ class StreamingLanguageModelingTask(LegacyTask):
                            ignore_invalid_inputs=False, required_batch_size_multiple=1, seed=1, num_shards=1,
                            shard_id=0, num_workers=0, epoch=1, data_buffer_size=0, disable_iterator_cache=False,
                            batch_by_size=True, skip_remainder_batch=True):
+        if not isinstance(dataset, torch.utils.data.IterableDataset):
+            # a map-style dataset (the prompts of an inference request): the ordinary batch iterator
+            return super().get_batch_iterator(
+                dataset, max_tokens=max_tokens, max_sentences=max_sentences, max_positions=max_positions,
+                ignore_invalid_inputs=ignore_invalid_inputs, required_batch_size_multiple=required_batch_size_multiple,
+                seed=seed, num_shards=num_shards, shard_id=shard_id, num_workers=num_workers, epoch=epoch,
+                data_buffer_size=data_buffer_size, disable_iterator_cache=disable_iterator_cache,
+                batch_by_size=batch_by_size, skip_remainder_batch=skip_remainder_batch)
         assert max_tokens is None
         # larger buffer with more ranks, so that consecutive batches mix documents
         dataset.set_shuffle_buffer_size(10 * max_sentences * num_shards) if hasattr(dataset, "set_shuffle_buffer_size") \
