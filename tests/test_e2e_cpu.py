@@ -93,3 +93,69 @@ def test_generator_interface_loads_the_checkpoint_and_generates(trained):
     assert all(len(beams) == 2 for beams in sampled)
     r = sampled[0][0]
     assert r["top_logprobs"] is not None and r["text"].startswith("the quick brown")
+
+
+def test_completions_service_answers_over_http(trained):
+    """The hosted completions service in one process: model behind ``GeneratorInterface``, the batching thread, the
+    HTTP handler; two concurrent requests are batched and answered in OpenAI format."""
+    import json as _json
+    import socket
+    import threading
+    import urllib.error
+    import urllib.request
+    from http.server import ThreadingHTTPServer
+
+    from metaseq_b200 import options
+    from metaseq_b200.cli import interactive_hosted as svc
+    from metaseq_b200.dataclass.utils import convert_namespace_to_config
+    from metaseq_b200.hub_utils import GeneratorInterface
+
+    args = options.parse_args_and_arch(options.get_generation_parser(), input_args=[
+        str(trained["data"]), *trained["common"], "--path", _checkpoint(trained), "--bpe", "hf_byte_bpe",
+        "--bpe-vocab", trained["vocab"], "--bpe-merges", trained["merges"], "--beam", "1", "--batch-size", "2", "--cpu",
+        "--distributed-world-size", "1"])
+    gi = GeneratorInterface(convert_namespace_to_config(args))
+    gi.load_model()
+    svc.generator = gi
+    stop = threading.Event()
+    worker = threading.Thread(target=svc.batching_loop, kwargs=dict(timeout=50, stop_event=stop), daemon=True)
+    worker.start()
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    server = ThreadingHTTPServer(("127.0.0.1", port), svc.CompletionsHandler)
+    threading.Thread(target=server.serve_forever, daemon=True).start()
+
+    def post(body, path="/completions"):
+        req = urllib.request.Request(f"http://127.0.0.1:{port}{path}", data=_json.dumps(body).encode(),
+                                     headers={"Content-Type": "application/json"})
+        with urllib.request.urlopen(req, timeout=120) as r:
+            return _json.loads(r.read())
+
+    try:
+        answers = [None, None]
+
+        def ask(i, prompt):
+            answers[i] = post({"prompt": prompt, "max_tokens": 5, "temperature": 0.0})
+
+        threads = [threading.Thread(target=ask, args=(0, "the quick brown")),
+                   threading.Thread(target=ask, args=(1, ["shard 0 corpus a", "the lazy"]))]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join(timeout=180)
+        assert answers[0] is not None and answers[1] is not None
+        assert answers[0]["object"] == "text_completion" and len(answers[0]["choices"]) == 1
+        assert len(answers[1]["choices"]) == 2  # one choice per prompt of the list
+        for choice in answers[0]["choices"] + answers[1]["choices"]:
+            assert isinstance(choice["text"], str) and "logprobs" in choice
+        alt = post({"prompt": "the quick brown", "max_tokens": 4, "temperature": 0.7, "top_p": 0.9, "n": 2},
+                   path="/v1/engines/tiny/completions")
+        assert len(alt["choices"]) == 2
+        with pytest.raises(urllib.error.HTTPError) as err:
+            post({"max_tokens": 4})
+        assert err.value.code == 400
+    finally:
+        stop.set()
+        server.shutdown()
+        server.server_close()
