@@ -1,0 +1,135 @@
+"""Infrastructure pieces the reference tests with mocks: the post-checkpoint callback (fake NFS directory, fake
+azcopy), the object collectives over CPU ranks, and activation checkpointing against plain autograd."""
+import datetime
+import os
+import socket
+import types
+
+import pytest
+import torch
+
+from metaseq_b200.cli import train as train_cli
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+# ------------------------------------------------------- post-checkpoint callback
+def _ckpt_cfg(upload, world=1):
+    ck = types.SimpleNamespace(cloud_upload_path=upload, nfs_eval_script_path=None, nfs_eval_frequency=1,
+                               nfs_eval_num_attempts=1, nfs_eval_attempt_wait_minutes=0)
+    return types.SimpleNamespace(checkpoint=ck, distributed_training=types.SimpleNamespace(distributed_world_size=world))
+
+
+def test_checkpoint_callback_copies_to_nfs_atomically_and_removes_the_local_file(tmp_path):
+    local = tmp_path / "local"
+    nfs = tmp_path / "nfs"
+    local.mkdir()
+    nfs.mkdir()
+    f = local / "checkpoint_18-model_part-0-shard0.pt"
+    f.write_bytes(b"weights")
+    train_cli.post_checkpoint_callback(_ckpt_cfg(f"nfs:{nfs}"), 18, False, str(f), None)
+    target = nfs / "checkpoint_18" / f.name
+    assert target.read_bytes() == b"weights" and not f.exists()
+    assert [p.name for p in (nfs / "checkpoint_18").iterdir()] == [f.name]  # no temporary file left behind
+
+
+def test_checkpoint_callback_uploads_with_azcopy_and_fails_loudly(tmp_path, monkeypatch):
+    f = tmp_path / "checkpoint_6-model_part-0-shard0.pt"
+    f.write_bytes(b"w")
+    calls = []
+
+    def fake_azcopy(cmd, stdout):
+        calls.append(cmd)
+        return types.SimpleNamespace(returncode=0, stdout=b"")
+
+    monkeypatch.setattr(train_cli, "_run_azcopy", fake_azcopy)
+    url = "https://acct.blob.core.windows.net/container/run?sas"
+    train_cli.post_checkpoint_callback(_ckpt_cfg(url), 6, False, str(f), None)
+    assert calls and calls[0][:2] == ["azcopy", "copy"] and calls[0][-2:] == [str(f), url] and not f.exists()
+    f.write_bytes(b"w")
+    monkeypatch.setattr(train_cli, "_run_azcopy", lambda cmd, stdout: types.SimpleNamespace(returncode=3, stdout=b"boom"))
+    with pytest.raises(SystemExit):
+        train_cli.post_checkpoint_callback(_ckpt_cfg(url), 6, False, str(f), None)
+
+
+def test_checkpoint_callback_without_upload_recreates_symlinks(tmp_path):
+    f = tmp_path / "checkpoint_6.pt"
+    f.write_bytes(b"w")
+    last = tmp_path / "checkpoint_last.pt"
+    last.write_bytes(b"old")
+    train_cli.post_checkpoint_callback(_ckpt_cfg(None), 6, False, str(f), [str(last)])
+    assert os.path.islink(last) and os.readlink(last) == "checkpoint_6.pt" and last.read_bytes() == b"w"
+
+
+# --------------------------------------------------------------- object collectives
+def _collective_rank(rank, world, port, out):
+    import torch.distributed as dist
+
+    from metaseq_b200.parallel import utils as du
+
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    obj = {"rank": rank, "list": list(range(rank + 1)), "tensor": torch.arange(3) + rank, "text": "x" * (10 * rank)}
+    gathered = du.all_gather_list(obj, group=None, max_size=4096)
+    payload = {"a": torch.arange(6).view(2, 3).float(), "nested": [1, {"b": torch.ones(2)}], "s": "hello"} if rank == 0 else None
+    received = du.broadcast_object(payload, src_rank=0, group=None, dist_device=torch.device("cpu"))
+    stats = du.all_reduce_dict({"loss": float(rank + 1), "n": 2.0}, device=torch.device("cpu"), group=None)
+    out[rank] = dict(ranks=[g["rank"] for g in gathered], lens=[len(g["list"]) for g in gathered],
+                     tensors=[g["tensor"].tolist() for g in gathered], texts=[len(g["text"]) for g in gathered],
+                     bcast=(received["a"].tolist(), received["nested"][1]["b"].tolist(), received["s"]),
+                     stats={k: float(v) for k, v in stats.items()})
+    dist.destroy_process_group()
+
+
+def test_object_collectives_over_cpu_ranks():
+    import torch.multiprocessing as mp
+
+    world = 3
+    with mp.Manager() as mgr:
+        out = mgr.dict()
+        mp.spawn(_collective_rank, args=(world, _free_port(), out), nprocs=world, join=True)
+        res = dict(out)
+    for r in range(world):
+        assert res[r]["ranks"] == [0, 1, 2] and res[r]["lens"] == [1, 2, 3] and res[r]["texts"] == [0, 10, 20]
+        assert res[r]["tensors"] == [[0, 1, 2], [1, 2, 3], [2, 3, 4]]
+        assert res[r]["bcast"] == ([[0.0, 1.0, 2.0], [3.0, 4.0, 5.0]], [1.0, 1.0], "hello")
+        assert res[r]["stats"] == {"loss": 6.0, "n": 6.0}
+
+
+# ------------------------------------------------------------ activation checkpointing
+class _Block(torch.nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.a = torch.nn.Linear(16, 32)
+        self.drop = torch.nn.Dropout(0.3)  # the recomputation must replay the same mask
+        self.b = torch.nn.Linear(32, 16)
+
+    def forward(self, x):
+        return x + self.b(self.drop(torch.relu(self.a(x))))
+
+
+@pytest.mark.parametrize("offload", [False, True])
+def test_activation_checkpointing_matches_plain_autograd_with_dropout(offload):
+    from metaseq_b200.modules.checkpoint_activations import checkpoint_wrapper
+
+    def run(wrap):
+        torch.manual_seed(0)
+        net = torch.nn.Sequential(_Block(), _Block(), _Block())
+        if wrap:
+            for i in range(len(net)):
+                net[i] = checkpoint_wrapper(net[i], offload_to_cpu=offload)
+        net.train()
+        x = torch.randn(5, 16, generator=torch.Generator().manual_seed(1), requires_grad=True)
+        torch.manual_seed(7)  # dropout stream
+        loss = net(x).pow(2).sum()
+        loss.backward()
+        gnorm = torch.sqrt(sum(p.grad.pow(2).sum() for p in net.parameters()))
+        return float(loss.detach()), float(gnorm), x.grad.clone()
+
+    plain, ckpt = run(False), run(True)
+    assert plain[0] == pytest.approx(ckpt[0], rel=1e-6) and plain[1] == pytest.approx(ckpt[1], rel=1e-5)
+    assert torch.allclose(plain[2], ckpt[2], atol=1e-6)
