@@ -223,3 +223,36 @@ def test_sequence_generator_with_decode_graph_matches_module_loop():
     same = (a["tokens"] == b["tokens"]).long().cumprod(-1).sum(-1).float().mean().item()
     assert same >= 0.8 * a["tokens"].shape[-1], same
     torch.testing.assert_close(a["scores"][..., :25], b["scores"][..., :25], rtol=5e-2, atol=5e-2)
+
+
+def test_opt_baselines_launcher_trains_locally(tmp_path):
+    """The sweep launcher end to end, as the reference's integration test drives it (``opt-baselines --local
+    --benchmark`` on the 8M model): it builds the train command, runs it in a subprocess on this GPU for 50
+    updates of the synthetic task, and the loss of the fixed batch goes down."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    env = dict(os.environ, OMP_NUM_THREADS="1")
+    out = subprocess.run([sys.executable, "-m", "metaseq_b200.launcher.opt_baselines", "-p", "it", "-g", "1", "-n", "1",
+                          "--model-size", "8m_mp1", "--benchmark", "--local", "--checkpoints-dir", str(tmp_path)],
+                         capture_output=True, text=True, timeout=900, env=env)
+    log = out.stdout + out.stderr
+    assert out.returncode == 0, log[-3000:]
+    run_dirs = [d for d in os.listdir(tmp_path) if d.startswith("it.")]
+    assert len(run_dirs) == 1 and "ngpu1" in run_dirs[0]
+    text = log
+    for name in os.listdir(tmp_path / run_dirs[0]):  # the launcher may tee the training log into the run directory
+        if name.endswith((".log", ".out", ".err")):
+            text += open(tmp_path / run_dirs[0] / name).read()
+    losses = []
+    for line in text.splitlines():
+        i = line.find('{"epoch"')
+        if i >= 0 and '"num_updates"' in line and '"train_loss"' not in line:
+            rec = json.loads(line[i:])
+            losses.append((int(rec["num_updates"]), float(rec["loss"])))
+    assert losses and max(n for n, _ in losses) == 50, text[-2000:]
+    losses.sort()
+    # the recipe warms the learning rate up over thousands of updates, so 50 updates move the loss only slightly
+    assert all(math.isfinite(v) for _, v in losses) and losses[-1][1] < losses[0][1], losses
