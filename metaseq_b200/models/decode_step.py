@@ -98,8 +98,8 @@ class GraphedDecodeStep:
         table: Dict[int, GraphedDecodeStep] = decoder.__dict__.setdefault("_graphed_decode_steps", {})
         width = bucket_rows(rows)
         step = table.pop(width, None)
-        if step is not None and step.capacity < min_capacity:
-            step = None
+        if step is not None and (step.capacity < min_capacity or step.signature != cls._signature(decoder)):
+            step = None  # too short, or the model's parameters were replaced since the graph was captured
         if step is None:
             while len(table) >= _MAX_CACHED_STEPS:
                 table.pop(next(iter(table)))
@@ -109,8 +109,15 @@ class GraphedDecodeStep:
         step.live = rows
         return step
 
+    @staticmethod
+    def _signature(decoder):
+        """Addresses of the parameters the graph reads: a captured graph is valid only while they stay put
+        (``load_state_dict`` copies in place and keeps it valid; ``.half()`` or ``.to(device)`` do not)."""
+        return tuple(p.data_ptr() for p in decoder.parameters())
+
     def __init__(self, decoder, rows: int, capacity: int):
         self.decoder = decoder
+        self.signature = self._signature(decoder)
         self.rows = rows  # rows of the graph and the caches
         self.live = rows  # rows in use (set by for_decoder); the others carry padding
         self.views: List[KVCache] = []

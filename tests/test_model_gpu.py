@@ -201,6 +201,9 @@ def test_graphed_decode_step_matches_module_path(activation):
                 torch.testing.assert_close(logits.float(), full[:, t].float(), rtol=5e-2, atol=5e-2)
         assert runner.caches[0].length == 47 and int(runner.length.item()) == 47
     assert runners[0] is runners[1] and runners[1] is runners[2]
+    # replacing the parameters (here: a dtype round trip) invalidates the captured graph
+    model.float().half()
+    assert GraphedDecodeStep.for_decoder(dec, 3, 64) is not runners[0]
     assert _lib.check_status(torch.device("cuda")) == 0
 
 
