@@ -35,6 +35,7 @@ from metaseq_b200.ops import functional as F
 from metaseq_b200.parallel import mpu
 
 _MAX_CACHED_STEPS = 3
+_CACHE_MEMORY_FRACTION = 0.35  # of the device memory, for the key/value caches of all cached buckets together
 
 
 def bucket_rows(rows: int) -> int:
@@ -101,13 +102,37 @@ class GraphedDecodeStep:
         if step is not None and (step.capacity < min_capacity or step.signature != cls._signature(decoder)):
             step = None  # too short, or the model's parameters were replaced since the graph was captured
         if step is None:
-            while len(table) >= _MAX_CACHED_STEPS:
-                table.pop(next(iter(table)))
             limit = int(decoder.max_positions()) + 2
-            step = cls(decoder, width, min(limit, max(min_capacity, -(-min_capacity // 256) * 256)))
+            capacity = min(limit, max(min_capacity, -(-min_capacity // 256) * 256))
+            need = cls._cache_bytes(decoder, width, capacity)
+            budget = cls._cache_budget(decoder)
+            # least recently used buckets go first: by count, and so that all caches together stay within a
+            # fraction of the device memory (a 64-row bucket of a large model is tens of GB)
+            while table and (len(table) >= _MAX_CACHED_STEPS or
+                             need + sum(st.cache_bytes for st in table.values()) > budget):
+                table.pop(next(iter(table)))
+            try:
+                step = cls(decoder, width, capacity)
+            except torch.cuda.OutOfMemoryError:
+                table.clear()
+                torch.cuda.empty_cache()
+                step = cls(decoder, width, capacity)
         table[width] = step  # most recently used last
         step.live = rows
         return step
+
+    @staticmethod
+    def _cache_bytes(decoder, rows: int, capacity: int) -> int:
+        w = decoder.embed_tokens.weight
+        per_layer = sum(2 * rows * capacity * layer.self_attn.num_heads_partition * layer.self_attn.head_dim
+                        for layer in decoder.layers)
+        return per_layer * w.element_size()
+
+    @staticmethod
+    def _cache_budget(decoder) -> int:
+        w = decoder.embed_tokens.weight
+        total = torch.cuda.get_device_properties(w.device).total_memory if w.is_cuda else 1 << 40
+        return int(_CACHE_MEMORY_FRACTION * total)
 
     @staticmethod
     def _signature(decoder):
@@ -118,6 +143,7 @@ class GraphedDecodeStep:
     def __init__(self, decoder, rows: int, capacity: int):
         self.decoder = decoder
         self.signature = self._signature(decoder)
+        self.cache_bytes = self._cache_bytes(decoder, rows, capacity)
         self.rows = rows  # rows of the graph and the caches
         self.live = rows  # rows in use (set by for_decoder); the others carry padding
         self.views: List[KVCache] = []
