@@ -159,3 +159,49 @@ def test_completions_service_answers_over_http(trained):
         stop.set()
         server.shutdown()
         server.server_close()
+
+
+def test_resuming_mid_epoch_continues_the_same_data_order_and_losses(tmp_path):
+    """The streaming data iterator, the optimizer and the schedule are restored from the checkpoint: a run stopped
+    at update 6 and resumed reproduces the losses of an uninterrupted run (the reference's resume test:
+    tests/test_streaming_language_modeling_task.py:24-157)."""
+    import shutil
+
+    vocab, merges = _write_tokenizer(tmp_path)
+    data = tmp_path / "data"
+    _write_shards(data, n_shards=1, docs=60)
+
+    def run(save, max_update, extra=()):
+        log = _run([sys.executable, "-m", "metaseq_b200.cli.train", str(data), "--task", "streaming_language_modeling",
+                    "--vocab-filename", vocab, "--merges-filename", merges, "--tokens-per-sample", "16",
+                    "--sample-break-mode", "none", "--batch-size", "2", "--arch", "transformer_lm_megatron",
+                    "--decoder-layers", "1", "--decoder-embed-dim", "32", "--decoder-ffn-embed-dim", "64",
+                    "--decoder-attention-heads", "2", "--decoder-learned-pos", "--share-decoder-input-output-embed",
+                    "--dropout", "0.1", "--attention-dropout", "0.0", "--criterion", "cross_entropy", "--optimizer",
+                    "adam", "--lr", "3e-3", "--lr-scheduler", "polynomial_decay", "--warmup-updates", "2",
+                    "--total-num-update", "40", "--max-update", str(max_update), "--cpu", "--distributed-world-size",
+                    "1", "--log-format", "json", "--log-interval", "1", "--save-dir", str(save),
+                    "--save-interval-updates", "6", "--disable-validation", "--seed", "3", "--num-workers", "0", *extra])
+        out = {}
+        for line in log.splitlines():
+            i = line.find('{"epoch"')
+            if i >= 0 and '"num_updates"' in line and '"train_loss"' not in line:
+                rec = json.loads(line[i:])
+                out[int(rec["num_updates"])] = float(rec["loss"])
+        return out
+
+    straight = run(tmp_path / "a", 12)
+    assert sorted(straight) == list(range(1, 13))
+    resumed_dir = tmp_path / "b"
+    resumed_dir.mkdir()
+    for name in os.listdir(tmp_path / "a"):
+        if name.startswith("checkpoint_6"):
+            shutil.copy(tmp_path / "a" / name, resumed_dir / name)
+    assert os.listdir(resumed_dir), os.listdir(tmp_path / "a")
+    if not (resumed_dir / "checkpoint_last.pt").exists():
+        first = sorted(os.listdir(resumed_dir))[0]
+        os.symlink(first, resumed_dir / "checkpoint_last.pt")
+    resumed = run(resumed_dir, 12)
+    assert min(resumed) == 7 and max(resumed) == 12, resumed
+    for n in range(7, 13):
+        assert resumed[n] == pytest.approx(straight[n], abs=2e-3), (n, resumed[n], straight[n])
