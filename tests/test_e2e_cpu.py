@@ -205,3 +205,14 @@ def test_resuming_mid_epoch_continues_the_same_data_order_and_losses(tmp_path):
     assert min(resumed) == 7 and max(resumed) == 12, resumed
     for n in range(7, 13):
         assert resumed[n] == pytest.approx(straight[n], abs=2e-3), (n, resumed[n], straight[n])
+
+
+def test_interactive_cli_answers_a_prompt_from_stdin(trained):
+    cmd = [sys.executable, "-m", "metaseq_b200.cli.interactive_cli", *trained["common"], "--path", _checkpoint(trained),
+           "--bpe-vocab", trained["vocab"], "--bpe-merges", trained["merges"], "--model-parallel-size", "1",
+           "--distributed-world-size", "1", "--cpu", "--batch-size", "1"]
+    env = dict(os.environ, OMP_NUM_THREADS="2", CUDA_VISIBLE_DEVICES="")
+    out = subprocess.run(cmd, input="the quick brown\n\n", capture_output=True, text=True, timeout=300, env=env)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
+    answer = [line for line in out.stdout.splitlines() if line.strip() and "INFO" not in line and "|" not in line]
+    assert answer, out.stdout[-2000:] + out.stderr[-1000:]
