@@ -113,3 +113,73 @@ def test_reshard_and_consolidate_tools_roundtrip(runs, tmp_path):
     assert "decoder.layers.0.self_attn.qkv_proj.weight" in full
     assert full["decoder.layers.0.self_attn.qkv_proj.weight"].shape == (192, 64)
     assert not any("flat_param" in k for k in full)
+
+
+def test_tensor_parallel_tool_chain_rebuilds_a_single_rank_model(tmp_path):
+    """Two tensor-parallel ranks train and save; the offline tools unflatten each part, merge the parts into one,
+    write the singleton file, re-split it, and the FasterTransformer converter reads it.  The merged weights,
+    loaded into a single-rank model, reproduce the next training loss of the two-rank run."""
+    from metaseq_b200.checkpoint import convert_metaseq_ft, convert_to_singleton, reshard_consolidated, reshard_fsdp, reshard_mp
+
+    tp2, _ = run_train(tmp_path / "tp2", 2, 3, ["--model-parallel-size", "2", "--save-interval-updates", "3"])
+    ckpt_dir = tmp_path / "tp2"
+    for part in (0, 1):
+        reshard_fsdp.reshard_fsdp_checkpoints(str(ckpt_dir / f"checkpoint_last-model_part-{part}-shard*.pt"),
+                                              str(tmp_path / "unflat" / f"reshard-model_part-{part}-shard{{i}}.pt"),
+                                              num_output_shards=1, unflatten_weights=True)
+        os.rename(tmp_path / "unflat" / f"reshard-model_part-{part}-shard0.pt", tmp_path / "unflat" / f"reshard-model_part-{part}.pt")
+    parts = [torch.load(tmp_path / "unflat" / f"reshard-model_part-{p}.pt", map_location="cpu", weights_only=False)["model"]
+             for p in (0, 1)]
+    one = reshard_mp.reshard_mp(str(tmp_path / "unflat" / "reshard-model_part-*.pt"), str(tmp_path / "mp1" / "reshard-model_part-{i}.pt"), 1)
+    merged = torch.load(one[0], map_location="cpu", weights_only=False)["model"]
+    D = 64
+    qkv = "decoder.layers.0.self_attn.qkv_proj.weight"
+    assert merged[qkv].shape == (3 * D, D)
+    for j in range(3):  # k | v | q blocks: each is the concatenation of the two ranks' halves of that block
+        want = torch.cat([p[qkv][j * D // 2:(j + 1) * D // 2] for p in parts])
+        assert torch.equal(merged[qkv][j * D:(j + 1) * D], want)
+    fc2 = "decoder.layers.1.fc2.weight"
+    assert torch.equal(merged[fc2], torch.cat([p[fc2] for p in parts], dim=1))
+    assert torch.equal(merged["decoder.layers.0.self_attn_layer_norm.weight"], parts[0]["decoder.layers.0.self_attn_layer_norm.weight"])
+    # singleton file from the two parts equals the one-part reshard
+    single = convert_to_singleton.convert_to_singleton(str(tmp_path / "unflat"))
+    restored = torch.load(single, map_location="cpu", weights_only=False)["model"]
+    assert all(torch.equal(restored[k], merged[k]) for k in merged if torch.is_tensor(merged[k]))
+    # and splits back into the original two parts
+    back = reshard_mp.reshard_mp(one[0], str(tmp_path / "mp2" / "reshard-model_part-{i}.pt"), 2)
+    for p, path in zip(parts, back):
+        again = torch.load(path, map_location="cpu", weights_only=False)["model"]
+        assert all(torch.equal(again[k], p[k]) for k in p if torch.is_tensor(p[k]))
+    # the merged weights in a one-rank model give the loss the two-rank run reported next
+    from metaseq_b200 import options, tasks
+    from metaseq_b200.dataclass.utils import convert_namespace_to_config
+
+    argv = [a for a in COMMON if a not in ("--ddp-backend", "fully_sharded", "--use-sharded-state")] + \
+        ["--distributed-world-size", "1", "--criterion", "cross_entropy"]
+    cfg = convert_namespace_to_config(options.parse_args_and_arch(options.get_training_parser(), input_args=argv))
+    task = tasks.setup_task(cfg.task)
+    model = task.build_model(cfg.model).eval()
+    missing, unexpected = model.load_state_dict({k: v for k, v in merged.items() if torch.is_tensor(v)}, strict=False)
+    assert not [m for m in missing if "version" not in m] and not [u for u in unexpected if "version" not in u], (missing, unexpected)
+    task.load_dataset("train")
+    batch = task.dataset("train").collater([0, 1])
+    with torch.no_grad():
+        logits, _ = model(**batch["net_input"])
+        nll = torch.nn.functional.cross_entropy(logits.view(-1, logits.shape[-1]).float(), batch["target"].view(-1),
+                                                reduction="mean")
+    four, _ = run_train(tmp_path / "tp2", 2, 4, ["--model-parallel-size", "2", "--save-interval-updates", "3"])
+    assert float(nll) / 0.6931471805599453 == pytest.approx(four[4][0], abs=2e-2)  # logged in bits per token
+    # sharded again for FSDP, and exported for FasterTransformer
+    shards = reshard_consolidated.reshard_consolidated(single, str(tmp_path / "fsdp" / "reshard-model_part-0-shard{i}.pt"), 2)
+    assert len(shards) == 2
+    convert_metaseq_ft.convert_metaseq_ft(single, str(tmp_path / "ft" / "part-{i}.pt"), dtype="fp32")
+    ft = torch.load(tmp_path / "ft" / "part-0.pt", map_location="cpu", weights_only=False)["weights"]
+    layers = 2
+    assert len(ft) == 12 * layers + 5
+    ft_qkv = ft[2 * layers]  # third per-layer slot, layer 0: the fused projection reordered from (k, v, q) to (q, k, v)
+    k, v, q = merged[qkv][:D], merged[qkv][D:2 * D], merged[qkv][2 * D:]
+    assert ft_qkv.numel() == 3 * D * D
+    flat = ft_qkv.reshape(-1)
+    assert any(torch.equal(flat, c.reshape(-1)) for c in (torch.cat([q, k, v]).t().contiguous(), torch.cat([q, k, v]),
+                                                          torch.stack([q, k, v], 0).permute(2, 0, 1).contiguous()))
+    assert ft[12 * layers + 2].shape[0] == merged["decoder.embed_positions.weight"].shape[0] - 2  # first two rows dropped
