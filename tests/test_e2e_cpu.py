@@ -216,3 +216,18 @@ def test_interactive_cli_answers_a_prompt_from_stdin(trained):
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
     answer = [line for line in out.stdout.splitlines() if line.strip() and "INFO" not in line and "|" not in line]
     assert answer, out.stdout[-2000:] + out.stderr[-1000:]
+
+
+def test_profile_flag_writes_a_trace_and_a_memory_table(tmp_path):
+    save = tmp_path / "prof"
+    _run([sys.executable, "-m", "metaseq_b200.cli.train", "--task", "dummy_lm", "--dict-size", "60", "--tokens-per-sample",
+          "16", "--batch-size", "2", "--arch", "transformer_lm_megatron", "--decoder-layers", "1", "--decoder-embed-dim",
+          "32", "--decoder-ffn-embed-dim", "64", "--decoder-attention-heads", "2", "--criterion", "cross_entropy",
+          "--optimizer", "adam", "--lr", "1e-3", "--max-update", "8", "--cpu", "--distributed-world-size", "1",
+          "--log-format", "none", "--save-dir", str(save), "--disable-validation", "--save-interval-epochs", "0",
+          "--save-interval-updates", "0", "--profile"])
+    trace = save / "profiler_trace.json"
+    assert trace.exists() and trace.stat().st_size > 1000
+    events = json.loads(trace.read_text())
+    assert "traceEvents" in events and len(events["traceEvents"]) > 10
+    assert (save / "memory_usage.txt").exists()
