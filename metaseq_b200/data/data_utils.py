@@ -149,3 +149,27 @@ def numpy_seed(seed, *addl_seeds):
 
     with _ns(seed, *addl_seeds):
         yield
+
+
+def load_indexed_dataset(path, dictionary=None, dataset_impl=None, combine=False, default="cached"):
+    """Binary corpus at ``path`` (``.bin`` / ``.idx``).  With ``combine`` the numbered continuations
+    ``path1, path2, ...`` are concatenated behind it.  ``None`` when nothing exists at ``path``
+    (reference: metaseq/data/data_utils.py, ``load_indexed_dataset``)."""
+    from metaseq_b200.data import indexed_dataset
+    from metaseq_b200.data.concat_dataset import ConcatDataset
+
+    found = []
+    k = 0
+    while True:
+        prefix = path + (str(k) if k > 0 else "")
+        impl = dataset_impl or indexed_dataset.infer_dataset_impl(prefix)
+        if impl is None or not indexed_dataset.dataset_exists(prefix, impl):
+            break
+        found.append(indexed_dataset.make_dataset(prefix, impl or default, fix_lua_indexing=True, dictionary=dictionary))
+        if not combine:
+            break
+        k += 1
+    if not found:
+        return None
+    return found[0] if len(found) == 1 else ConcatDataset(found)
+

@@ -32,6 +32,14 @@ class LanguageModelingConfig(MetaseqDataclass):
     shorten_data_split_list: str = opt("", "comma-separated list of dataset splits to apply shortening to")
     vocab_filename: Optional[str] = opt("", "path to bpe-vocab.json (builds the dictionary when no dict.txt exists)")
     merges_filename: Optional[str] = opt("", "path to bpe-merges.txt")
+    hf_tokenizer: Optional[str] = opt("", "path to a HuggingFace tokenizers json file (alternative to vocab + merges)")
+    end_of_document_symbol: Optional[str] = opt("</s>", "symbol indicating an end-of-document")
+    final_vocab_size: Optional[int] = opt(None, "force the dictionary to this size by adding padding symbols")
+    pad_to_fixed_length: Optional[bool] = opt(False, "pad every batch to --tokens-per-sample")
+    pad_to_fixed_bsz: Optional[bool] = opt(False, "pad every batch to the batch size with empty rows")
+    shuffle_docs: bool = opt(False, "with --sample-break-mode none: shuffle whole documents before building blocks")
+    batch_size: Optional[int] = opt(None, link="dataset.batch_size")
+    batch_size_valid: Optional[int] = opt(None, link="dataset.batch_size_valid")
     seed: int = opt(1, link="common.seed")
     dataset_impl: Optional[str] = opt(None, link="dataset.dataset_impl")
 
@@ -110,14 +118,27 @@ class LanguageModelingTask(LegacyTask):
                 logger.info(f"dictionary: {len(d)} types")
                 return d, d
         vocab, merges = getattr(args, "vocab_filename", ""), getattr(args, "merges_filename", "")
-        if vocab and merges and os.path.exists(vocab) and os.path.exists(merges):
+        hf_file = getattr(args, "hf_tokenizer", "")
+        tok = None
+        if hf_file and os.path.exists(hf_file):
+            from tokenizers import Tokenizer
+
+            tok = Tokenizer.from_file(hf_file)
+        elif vocab and merges and os.path.exists(vocab) and os.path.exists(merges):
             from tokenizers import ByteLevelBPETokenizer
 
             tok = ByteLevelBPETokenizer.from_file(vocab, merges)
+        if tok is not None:
             d = Dictionary()
             for i in range(d.nspecial, tok.get_vocab_size()):
                 d.add_symbol(tok.id_to_token(i))
-            d.pad_to_multiple_(8)
+            final = getattr(args, "final_vocab_size", None)
+            if final is not None:
+                if final < tok.get_vocab_size():
+                    raise ValueError(f"incompatible: {final}, tok_vocab_size: {tok.get_vocab_size()}")
+                d.pad_to_multiple_(final)
+            else:
+                d.pad_to_multiple_(8)
             return d, d
         d = Dictionary.synthetic(int(getattr(args, "synthetic_vocab_size", 50272)))
         return d, d
@@ -128,24 +149,40 @@ class LanguageModelingTask(LegacyTask):
         return cls(args, dictionary, output_dictionary)
 
     def load_dataset(self, split, epoch=1, combine=False, **kwargs):
-        from metaseq_b200.data.indexed_dataset import load_indexed_dataset
+        from metaseq_b200.data.data_utils import load_indexed_dataset
         from metaseq_b200.data.monolingual_dataset import MonolingualDataset
         from metaseq_b200.data.token_block_dataset import TokenBlockDataset
 
         paths = self.args.data.split(os.pathsep)
         data_path = paths[(epoch - 1) % len(paths)]
         dataset = load_indexed_dataset(os.path.join(data_path, split), self.dictionary,
-                                       getattr(self.args, "dataset_impl", None))
+                                       getattr(self.args, "dataset_impl", None), combine=combine)
         if dataset is None:
             raise FileNotFoundError(f"Dataset not found: {split} ({os.path.join(data_path, split)})")
-        blocks = TokenBlockDataset(dataset, dataset.sizes, self.args.tokens_per_sample, pad=self.dictionary.pad(),
-                                   eos=self.dictionary.eos(), break_mode=self.args.sample_break_mode,
-                                   include_targets=True)
+        from metaseq_b200.data import data_utils as du
+        from metaseq_b200.data.token_transforms import SortDataset, maybe_shorten_dataset
+
+        dataset = maybe_shorten_dataset(dataset, split, self.args.shorten_data_split_list, self.args.shorten_method,
+                                        self.args.tokens_per_sample, self.args.seed)
+        common = dict(pad=self.dictionary.pad(), eos=self.dictionary.eos())
+        if getattr(self.args, "shuffle_docs", False):
+            assert self.args.sample_break_mode == "none", "shuffle docs is only for sample break mode none"
+            docs = TokenBlockDataset(dataset, dataset.sizes, self.args.tokens_per_sample, break_mode="complete_doc",
+                                     include_targets=False, **common)
+            with du.numpy_seed(self.args.seed + epoch):
+                order = np.random.permutation(len(docs))
+            dataset = SortDataset(docs, sort_order=[order, docs.sizes])
+        blocks = TokenBlockDataset(dataset, dataset.sizes, self.args.tokens_per_sample,
+                                   break_mode=self.args.sample_break_mode, include_targets=True, **common)
         add_eos = self.args.sample_break_mode is not None and self.args.sample_break_mode != "none"
+        fixed_len = self.args.tokens_per_sample if getattr(self.args, "pad_to_fixed_length", False) else None
+        pad_bsz = None
+        if getattr(self.args, "pad_to_fixed_bsz", False):
+            pad_bsz = getattr(self.args, "batch_size_valid", None) if "valid" in split else getattr(self.args, "batch_size", None)
         self.datasets[split] = MonolingualDataset(
             dataset=blocks, sizes=blocks.sizes, src_vocab=self.dictionary, tgt_vocab=self.output_dictionary,
-            add_eos_for_other_targets=add_eos, shuffle=True, targets=self.targets,
-            add_bos_token=self.args.add_bos_token)
+            add_eos_for_other_targets=add_eos, shuffle=True, add_bos_token=self.args.add_bos_token,
+            fixed_pad_length=fixed_len, pad_to_bsz=pad_bsz)
 
     def build_dataset_for_inference(self, src_tokens, src_lengths, **kwargs):
         return inference_dataset(src_tokens, src_lengths, self.source_dictionary)

@@ -140,3 +140,65 @@ def test_checkpoint_write_symlink_and_load_cpu(tmp_path):
     assert called == [(str(tmp_path / "checkpoint_4.pt"), [link])]
     checkpoint_utils.verify_checkpoint_directory(str(tmp_path))
     assert checkpoint_utils._is_checkpoint_sharded(str(tmp_path / "checkpoint_3-shard0.pt")) or True
+
+
+def _write_indexed_corpus(root, dictionary, docs, split="train"):
+    from metaseq_b200.data import indexed_dataset
+
+    prefix = str(root / split)
+    builder = indexed_dataset.make_builder(prefix + ".bin", "mmap", vocab_size=len(dictionary))
+    for d in docs:
+        builder.add_item(torch.tensor(d, dtype=torch.int64))
+    builder.finalize(prefix + ".idx")
+
+
+def test_legacy_language_modeling_task_loads_an_indexed_corpus(tmp_path):
+    """The map-style task (the one the completions service is launched with): mmap corpus -> token blocks ->
+    source / target pairs, plus its padding and document-shuffling options."""
+    from metaseq_b200.data import Dictionary
+
+    d = Dictionary()
+    for i in range(40):
+        d.add_symbol(f"w{i}")
+    d.save(str(tmp_path / "dict.txt"))
+    eos = d.eos()
+    docs = [[4 + (i + j) % 40 for j in range(3 + i % 7)] + [eos] for i in range(30)]
+    _write_indexed_corpus(tmp_path, d, docs)
+
+    def task_for(extra=()):
+        ns = options.parse_args_and_arch(options.get_training_parser(), input_args=[
+            "--task", "language_modeling", str(tmp_path), "--tokens-per-sample", "16", "--batch-size", "4", "--arch",
+            "transformer_lm_megatron", "--optimizer", "adam", "--lr", "1e-3", "--criterion", "cross_entropy", *extra])
+        cfg = convert_namespace_to_config(ns)
+        t = tasks.setup_task(cfg.task)
+        t.load_dataset("train")
+        return t
+
+    t = task_for()
+    ds = t.dataset("train")
+    total = sum(len(x) for x in docs)
+    assert len(ds) == -(-total // 16)
+    batch = ds.collater([ds[0], ds[1]])
+    src, tgt = batch["net_input"]["src_tokens"], batch["target"]
+    assert src.shape == (2, 16) and torch.equal(src[:, 1:], tgt[:, :-1])  # next-token targets
+    flat = [tok for doc in docs for tok in doc]
+    # the target is the block itself, the source the same tokens one position earlier (document separator first)
+    assert tgt[0].tolist() == flat[:16] and src[0].tolist() == [eos] + flat[:15]
+    # fixed batch shape
+    t2 = task_for(["--pad-to-fixed-length", "--pad-to-fixed-bsz"])
+    ds2 = t2.dataset("train")
+    last = ds2.collater([ds2[len(ds2) - 1]])
+    assert last["net_input"]["src_tokens"].shape == (4, 16)
+    assert (last["net_input"]["src_tokens"][1:] == d.pad()).all()
+    # document-level blocks under a shuffled sort order, then fixed-size blocks: every document arrives intact
+    t3 = task_for(["--shuffle-docs"])
+    ds3 = t3.dataset("train")
+    seen = [tok for i in range(len(ds3)) for tok in ds3[i]["target"].tolist()]
+    assert sorted(seen) == sorted(flat)
+    as_docs, cur = [], []
+    for tok in seen:
+        cur.append(tok)
+        if tok == eos:
+            as_docs.append(cur)
+            cur = []
+    assert sorted(map(tuple, as_docs)) == sorted(map(tuple, docs))
