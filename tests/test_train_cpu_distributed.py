@@ -183,3 +183,27 @@ def test_tensor_parallel_tool_chain_rebuilds_a_single_rank_model(tmp_path):
     assert any(torch.equal(flat, c.reshape(-1)) for c in (torch.cat([q, k, v]).t().contiguous(), torch.cat([q, k, v]),
                                                           torch.stack([q, k, v], 0).permute(2, 0, 1).contiguous()))
     assert ft[12 * layers + 2].shape[0] == merged["decoder.embed_positions.weight"].shape[0] - 2  # first two rows dropped
+
+
+def test_ddp_backend_matches_fully_sharded(tmp_path, runs):
+    """``--ddp-backend pytorch_ddp`` (replicated parameters, bucketed gradient all-reduce) follows the same
+    trajectory as the fully sharded run on two ranks and writes one consolidated file per model part."""
+    args = [a for a in COMMON if a not in ("--ddp-backend", "fully_sharded", "--use-sharded-state")]
+    cmd = [sys.executable, "-m", "metaseq_b200.cli.train", *args, "--ddp-backend", "pytorch_ddp",
+           "--distributed-world-size", "2", "--max-update", "4", "--save-dir", str(tmp_path / "ddp"),
+           "--save-interval-updates", "4"]
+    env = dict(os.environ, OMP_NUM_THREADS="2", MASTER_ADDR="127.0.0.1")
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    losses = {}
+    for line in out.stdout.splitlines():
+        i = line.find('{"epoch"')
+        if i >= 0:
+            rec = json.loads(line[i:])
+            if "num_updates" in rec and "loss" in rec and "train_loss" not in rec:
+                losses[int(rec["num_updates"])] = float(rec["loss"])
+    assert sorted(losses) == [1, 2, 3, 4]
+    for step in range(1, 5):
+        assert losses[step] == pytest.approx(runs["dp2"][step][0], abs=5e-3)
+    names = sorted(os.path.basename(p) for p in glob.glob(str(tmp_path / "ddp" / "checkpoint_last*")))
+    assert names == ["checkpoint_last-model_part-0.pt"]
