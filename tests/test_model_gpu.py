@@ -259,3 +259,49 @@ def test_opt_baselines_launcher_trains_locally(tmp_path):
     losses.sort()
     # the recipe warms the learning rate up over thousands of updates, so 50 updates move the loss only slightly
     assert all(math.isfinite(v) for _, v in losses) and losses[-1][1] < losses[0][1], losses
+
+
+GPU_VARIANTS = {
+    "fused_layer_relu": ["--activation-fn", "relu"],
+    "gelu_modular": ["--activation-fn", "gelu"],
+    "bf16": ["--activation-fn", "relu", "--bf16"],
+    "activation_checkpointing": ["--activation-fn", "relu", "--checkpoint-activations"],
+    "alibi": ["--activation-fn", "relu", "--alibi"],
+    "document_separator_attention": ["--activation-fn", "relu", "--self-attn-doc-sep", "2"],
+    "sinusoidal_positions": ["--activation-fn", "relu", "--decoder-learned-sinusoidal"],
+    "dropout": ["--activation-fn", "relu", "--dropout", "0.1", "--attention-dropout", "0.1"],
+    "no_fused_layer": ["--activation-fn", "relu", "--no-fused-layer"],
+    "cross_entropy_criterion": ["--activation-fn", "relu", "--criterion", "cross_entropy"],
+}
+
+
+@pytest.mark.parametrize("name", sorted(GPU_VARIANTS))
+def test_training_option_runs_and_learns_on_the_gpu(name):
+    """The options that change which kernels or PyTorch paths a step takes: a few updates each, finite and falling
+    loss on the fixed batch, no kernel reporting a timed-out wait."""
+    extra = list(GPU_VARIANTS[name])
+    if "--bf16" in extra:
+        cfg = _cfg(extra=[], fsdp=True)
+        # swap the precision flags of the helper's argv: bf16 has no loss scaler
+        argv_extra = [a for a in extra if a != "--bf16"]
+        parser = options.get_training_parser()
+        base = ["--task", "dummy_lm", "--dict-size", "50272", "--tokens-per-sample", "256", "--batch-size", "2",
+                "--arch", "opt_125m", "--decoder-layers", "2", "--decoder-embed-dim", "256", "--decoder-attention-heads", "4",
+                "--decoder-ffn-embed-dim", "1024", "--dropout", "0.0", "--attention-dropout", "0.0", "--criterion",
+                "vocab_parallel_cross_entropy", "--optimizer", "adam", "--adam-betas", "(0.9, 0.95)", "--clip-norm", "1.0",
+                "--lr", "1e-3", "--lr-scheduler", "polynomial_decay", "--warmup-updates", "2", "--total-num-update", "100",
+                "--bf16", "--distributed-world-size", "1", "--save-dir", "/tmp/msq_test_gpu", "--disable-validation",
+                "--log-format", "none", "--tensor-parallel-init-model-on-gpu", "--ddp-backend", "fully_sharded",
+                "--use-sharded-state", "--no-reshard-after-forward", "--min-params-to-wrap", "1000", *argv_extra]
+        cfg = convert_namespace_to_config(options.parse_args_and_arch(parser, input_args=base))
+    else:
+        cfg = _cfg(extra=extra)
+    tr, batch = _trainer(cfg, seed=5)
+    losses = []
+    for _ in range(6):
+        log = tr.train_step([batch])
+        if log is not None:
+            losses.append(float(log["loss"]))
+    assert len(losses) >= 4 and all(math.isfinite(v) for v in losses), losses
+    assert losses[-1] < losses[0], (name, losses)
+    assert _lib.check_status("cuda") == 0
