@@ -305,3 +305,44 @@ def test_training_option_runs_and_learns_on_the_gpu(name):
     assert len(losses) >= 4 and all(math.isfinite(v) for v in losses), losses
     assert losses[-1] < losses[0], (name, losses)
     assert _lib.check_status("cuda") == 0
+
+
+def test_generator_interface_options_on_the_gpu():
+    """``GeneratorInterface.generate`` over the graphed decode step and the sampling kernel: greedy, nucleus,
+    several samples per prompt with log-probabilities, stop tokens, repetition penalties and the factual-nucleus
+    decay, with prompts of different lengths in one batch."""
+    from metaseq_b200.hub_utils import GeneratorInterface
+
+    parser = options.get_training_parser()
+    ns = options.parse_args_and_arch(parser, input_args=[
+        "--task", "language_modeling", "--tokens-per-sample", "96", "--batch-size", "1", "--arch", "opt_125m",
+        "--decoder-layers", "2", "--decoder-embed-dim", "256", "--decoder-attention-heads", "4", "--decoder-ffn-embed-dim",
+        "1024", "--dropout", "0.0", "--attention-dropout", "0.0", "--criterion", "cross_entropy", "--optimizer", "adam",
+        "--lr", "1e-3", "--memory-efficient-fp16", "--tensor-parallel-init-model-on-gpu", "--distributed-world-size", "1"])
+    cfg = convert_namespace_to_config(ns)
+    task = tasks.setup_task(cfg.task)
+    torch.manual_seed(9)
+    model = task.build_model(cfg.model).half().cuda().eval()
+    gi = GeneratorInterface.from_model(cfg, model, task)
+    V = len(task.target_dictionary)
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(10, V - 10, (n,), generator=g).tolist() for n in (5, 9, 3)]
+    greedy = gi.generate(prompts, max_tokens=[8, 8, 8], temperature=0.0)
+    assert [len(b) for b in greedy] == [1, 1, 1]
+    for beams in greedy:
+        assert 1 <= len(beams[0]["tokens"]) <= 8 and all(s <= 0 for s in beams[0]["token_scores"])
+    again = gi.generate(prompts, max_tokens=[8, 8, 8], temperature=0.0)
+    assert [b[0]["tokens"] for b in greedy] == [b[0]["tokens"] for b in again]
+    sampled = gi.generate(prompts, max_tokens=[6, 6, 6], temperature=0.9, top_p=0.8, n=3, logprobs=4, echo=True, seed=3)
+    assert all(len(b) == 3 for b in sampled)
+    first = sampled[0][0]
+    assert first["top_logprobs"] is not None and len(first["top_logprobs"]) == len(first["tokens"])
+    same_seed = gi.generate(prompts, max_tokens=[6, 6, 6], temperature=0.9, top_p=0.8, n=3, logprobs=4, echo=True, seed=3)
+    assert [[x["tokens"] for x in b] for b in sampled] == [[x["tokens"] for x in b] for b in same_seed]
+    stop_id = int(greedy[0][0]["tokens"][1].strip("<>")) if len(greedy[0][0]["tokens"]) > 1 else 11
+    stopped = gi.generate(prompts[:1], max_tokens=[8], temperature=0.0, stop=[stop_id])
+    assert len(stopped[0][0]["tokens"]) <= 2
+    fancy = gi.generate(prompts, max_tokens=[6, 6, 6], temperature=1.0, top_p=0.9, lambda_decay=0.9, omega_bound=0.3,
+                        alpha_presence=0.2, alpha_frequency=0.2, alpha_presence_src=0.1, alpha_frequency_src=0.1, seed=5)
+    assert [len(b) for b in fancy] == [1, 1, 1]
+    assert _lib.check_status("cuda") == 0
