@@ -118,11 +118,19 @@ class MemoryEfficientFP16Optimizer(_ScaledMixin, BaseOptimizer):
             self.scaler.loss_scale = state_dict["loss_scale"]
         sd = {k: v for k, v in state_dict.items() if k != "loss_scale"}
         self.wrapped_optimizer.load_state_dict(sd, optimizer_overrides)
-        # moments stay fp32 even if the parameters they belong to are 16-bit
-        for st in self.optimizer.state.values():
-            for k, v in st.items():
-                if torch.is_tensor(v) and v.is_floating_point() and v.dtype != torch.float32:
-                    st[k] = v.float()
+        # torch.optim casts loaded state to the dtype of its parameter.  Here the parameters are 16-bit and the
+        # moments fp32: a second moment of 1e-9 does not survive fp16, and the first update after a resume would
+        # divide by eps alone.  Put the saved fp32 tensors back (they move to the device at the next step).
+        saved_groups = sd.get("param_groups", [])
+        saved_ids = [i for g in saved_groups for i in g["params"]]
+        params = [p for g in self.optimizer.param_groups for p in g["params"]]
+        by_id = dict(zip(saved_ids, params))
+        for key, st in sd.get("state", {}).items():
+            param = by_id.get(key)
+            if param is None:
+                continue
+            self.optimizer.state[param] = {
+                k: (v.detach().clone().float() if torch.is_tensor(v) and v.is_floating_point() else v) for k, v in st.items()}
 
     def backward(self, loss):
         if self.scaler is not None:

@@ -84,6 +84,27 @@ def test_memory_efficient_state_stays_fp32_after_reload():
                 assert v.dtype == torch.float32
 
 
+def test_memory_efficient_reload_keeps_values_that_fp16_cannot_hold():
+    """The second moments of a trained model are far below the smallest fp16 number; a reload that passes them
+    through the parameters' dtype turns them into zeros and the next update divides by eps alone."""
+    model, x, target = _problem(torch.float16)
+    opt = MemoryEfficientFP16Optimizer.build_optimizer(_cfg(), list(model.parameters()))
+    _run_iter(model, x, target, opt)
+    state = copy.deepcopy(opt.state_dict())
+    tiny = 3.0e-10
+    for st in state["state"].values():
+        st["exp_avg_sq"] = torch.full_like(st["exp_avg_sq"], tiny, dtype=torch.float32)
+        st["exp_avg"] = torch.full_like(st["exp_avg"], 1.2345678e-5, dtype=torch.float32)
+    model2, _, _ = _problem(torch.float16)
+    opt2 = MemoryEfficientFP16Optimizer.build_optimizer(_cfg(), list(model2.parameters()))
+    opt2.load_state_dict(state)
+    assert len(opt2.optimizer.state) == len(state["state"]) > 0
+    for st in opt2.optimizer.state.values():
+        assert st["exp_avg_sq"].dtype == torch.float32 and float(st["exp_avg_sq"].flatten()[0]) == pytest.approx(tiny, rel=1e-6)
+        assert float(st["exp_avg"].flatten()[0]) == pytest.approx(1.2345678e-5, rel=1e-6)
+        assert int(st["step"]) == 1
+
+
 def test_overflow_skips_update_and_halves_scale():
     model, x, target = _problem(torch.float16)
     cfg = _cfg()
