@@ -277,8 +277,14 @@ def load_checkpoint(cfg, trainer, **passthrough_args):
             logger.info(f"loading pretrained model from {checkpoint_path}: optimizer, lr scheduler, meters, "
                         "dataloader will be reset")
     elif suffix is not None and suffix != "":
-        checkpoint_path = ckpt.restore_file.replace(".pt", suffix + ".pt") \
-            if not ckpt.restore_file.endswith(suffix + ".pt") else ckpt.restore_file
+        # the name may be given bare ("checkpoint_3.pt") or with another rank's model-part / shard suffix
+        # the parts that this rank's suffix supplies are taken off the given name first
+        stem = re.sub(r"\.pt$", "", ckpt.restore_file)
+        if "-shard" in suffix:
+            stem = re.sub(r"-shard\d+$", "", stem)
+        if "-model_part-" in suffix:
+            stem = re.sub(r"-model_part-\d+$", "", stem)
+        checkpoint_path = stem + suffix + ".pt"
     else:
         checkpoint_path = ckpt.restore_file
     if ckpt.restore_file != default_restore_file and ckpt.finetune_from_model:

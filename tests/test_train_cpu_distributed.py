@@ -207,3 +207,17 @@ def test_ddp_backend_matches_fully_sharded(tmp_path, runs):
         assert losses[step] == pytest.approx(runs["dp2"][step][0], abs=5e-3)
     names = sorted(os.path.basename(p) for p in glob.glob(str(tmp_path / "ddp" / "checkpoint_last*")))
     assert names == ["checkpoint_last-model_part-0.pt"]
+
+
+def test_restore_on_more_ranks(runs, tmp_path):
+    """Two shard files restored by four ranks (the reference trains on 2 GPUs and restores on 4:
+    gpu_tests/test_checkpoint_loading_on_more_gpus.py): the run continues and writes four shard files."""
+    src = runs["root"] / "dp2" / "checkpoint_3-model_part-0-shard0.pt"
+    # four ranks see twice the data per update, so only the first restored update is comparable through its loss on the
+    # fixed synthetic batch (every rank gets the same batch): equal to the one-rank run
+    resized, log = run_train(tmp_path / "wide", 4, 5, ["--restore-file", str(src).replace("-shard0", ""),
+                                                      "--save-interval-updates", "5"])
+    assert min(resized) == 4
+    assert resized[4][0] == pytest.approx(runs["dp1"][4][0], abs=3e-3)
+    names = sorted(os.path.basename(p) for p in glob.glob(str(tmp_path / "wide" / "checkpoint_last*")))
+    assert names == [f"checkpoint_last-model_part-0-shard{i}.pt" for i in range(4)]
