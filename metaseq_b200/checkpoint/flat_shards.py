@@ -134,9 +134,17 @@ def reshard_optimizer_state(states: Sequence[Dict[str, Any]], new_rank: int, new
         for name, val in st.items():
             if torch.is_tensor(val) and val.dim() > 0 and key is not None and val.numel() == states[0]["model"][key].numel():
                 total = unpadded_numel(mds[0][key])
-                vec = logical_vector([s["last_optimizer_state"]["state"][idx][name] for s in states],
-                                     [m[key].get("padding", 0) for m in mds], total)
+                pieces = [s["last_optimizer_state"]["state"][idx] for s in states]
+                if name + "_scale" in st:
+                    # moments stored as scaled fp16: every shard has its own scale, so they are joined as fp32 and
+                    # the optimizer compresses them again after its next step
+                    tensors = [pc[name].float() * float(pc[name + "_scale"]) for pc in pieces]
+                else:
+                    tensors = [pc[name] for pc in pieces]
+                vec = logical_vector(tensors, [m[key].get("padding", 0) for m in mds], total)
                 entry[name], _ = slice_for_rank(vec, new_rank, new_world)
+            elif name.endswith("_scale") and name[: -len("_scale")] in st:
+                continue  # folded into the tensor above
             else:
                 entry[name] = val
         new_state[idx] = entry

@@ -27,7 +27,7 @@ class MetaseqAdamConfig(MetaseqDataclass):
     adam_eps: float = opt(1e-8, "epsilon for Adam optimizer")
     weight_decay: float = opt(0.0, "weight decay")
     use_old_adam: Optional[bool] = opt(False, "use the PyTorch-ops implementation even on a GPU")
-    fp16_adam_stats: bool = opt(False, "kept for command-line compatibility; moments are stored in fp32")
+    fp16_adam_stats: bool = opt(False, "store the moments in fp16 with a per-tensor scale (halves optimizer state)")
     block_wise: bool = opt(False, "kept for command-line compatibility")
 
 
@@ -49,14 +49,50 @@ class MetaseqAdam(BaseOptimizer):
             "eps": self.cfg.adam_eps,
             "weight_decay": self.cfg.weight_decay,
             "use_kernels": not getattr(self.cfg, "use_old_adam", False),
+            "use_fp16_stats": bool(getattr(self.cfg, "fp16_adam_stats", False)),
         }
 
 
 class Adam(torch.optim.Optimizer):
-    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, use_kernels=True):
+    """AdamW with fp32 arithmetic.  With ``use_fp16_stats`` the two moments are kept between steps as fp16 tensors
+    with one fp32 scale each (``exp_avg_scale``, ``exp_avg_sq_scale``: the tensor's largest magnitude mapped to the
+    top of the fp16 range), expanded to fp32 for the update and compressed again after it: the scheme of the
+    reference's fused optimizer (metaseq/optim/fused_adam.py:189-249)."""
+
+    FLOAT16_MAX = 65504.0
+
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, use_kernels=True,
+                 use_fp16_stats=False):
         defaults = dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
         super().__init__(params, defaults)
         self.use_kernels = use_kernels
+        self.use_fp16_stats = use_fp16_stats
+
+    def _expand_stats(self, state, p):
+        """fp32 working copies of the two moments of ``p``."""
+        if not self.use_fp16_stats:
+            state["exp_avg"] = state["exp_avg"].to(device=p.device, dtype=torch.float32)
+            state["exp_avg_sq"] = state["exp_avg_sq"].to(device=p.device, dtype=torch.float32)
+            return state["exp_avg"], state["exp_avg_sq"]
+        out = []
+        for name in ("exp_avg", "exp_avg_sq"):
+            t = state[name].to(device=p.device)
+            sc = state.get(name + "_scale")
+            if sc is not None:  # a loader may have cast the stored fp16 values to another dtype: the values stand
+                sc = sc.to(device=p.device, dtype=torch.float32) if torch.is_tensor(sc) else float(sc)
+                t = t.float() * sc
+            else:  # state written without compression (a checkpoint of an fp32-moment run, or a resharded one)
+                t = t.float()
+            out.append(t)
+        return out[0], out[1]
+
+    def _compress_stats(self, state, m, v):
+        for name, t in (("exp_avg", m), ("exp_avg_sq", v)):
+            # the reference adds 1e-8 here, which swamps the second moments of small gradients (1e-12 and below)
+            # into fp16 subnormals; the floor only has to keep an all-zero tensor from dividing by zero
+            sc = (t.abs().max().float() / self.FLOAT16_MAX).clamp_min(1e-30)
+            state[name + "_scale"] = sc
+            state[name] = (t / sc).half()
 
     @property
     def supports_memory_efficient_fp16(self):
@@ -81,6 +117,7 @@ class Adam(torch.optim.Optimizer):
         for group in self.param_groups:
             beta1, beta2 = group["betas"]
             batched = {}  # (step, param dtype, grad dtype, device) -> [(p, g, m, v)]: one launch each
+            compress = []  # (state, m, v) whose fp32 working copies go back to fp16 after the update
             for p in group["params"]:
                 if p.grad is None:
                     continue
@@ -92,11 +129,10 @@ class Adam(torch.optim.Optimizer):
                     state["step"] = 0
                     state["exp_avg"] = torch.zeros_like(p, dtype=torch.float32)
                     state["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32)
-                else:
-                    state["exp_avg"] = state["exp_avg"].to(device=p.device, dtype=torch.float32)
-                    state["exp_avg_sq"] = state["exp_avg_sq"].to(device=p.device, dtype=torch.float32)
                 state["step"] += 1
-                m, v = state["exp_avg"], state["exp_avg_sq"]
+                m, v = self._expand_stats(state, p)
+                if self.use_fp16_stats:
+                    compress.append((state, m, v))
                 if p.is_cuda and self.use_kernels and p.is_contiguous() and grad.is_contiguous() \
                         and ops.get_backend() != "torch":
                     batched.setdefault((state["step"], p.dtype, grad.dtype, p.device), []).append((p.data, grad, m, v))
@@ -131,6 +167,8 @@ class Adam(torch.optim.Optimizer):
                     ops.adamw_step(*items[0], **kw)
                 else:
                     ops.adamw_step_multi(items, **kw)
+            for state, m, v in compress:
+                self._compress_stats(state, m, v)
         return loss
 
     _ctrl_cache = {}

@@ -120,7 +120,8 @@ class MemoryEfficientFP16Optimizer(_ScaledMixin, BaseOptimizer):
         self.wrapped_optimizer.load_state_dict(sd, optimizer_overrides)
         # torch.optim casts loaded state to the dtype of its parameter.  Here the parameters are 16-bit and the
         # moments fp32: a second moment of 1e-9 does not survive fp16, and the first update after a resume would
-        # divide by eps alone.  Put the saved fp32 tensors back (they move to the device at the next step).
+        # divide by eps alone.  Put the saved tensors back in their saved dtype (they move to the device at the
+        # next step).
         saved_groups = sd.get("param_groups", [])
         saved_ids = [i for g in saved_groups for i in g["params"]]
         params = [p for g in self.optimizer.param_groups for p in g["params"]]
@@ -130,7 +131,7 @@ class MemoryEfficientFP16Optimizer(_ScaledMixin, BaseOptimizer):
             if param is None:
                 continue
             self.optimizer.state[param] = {
-                k: (v.detach().clone().float() if torch.is_tensor(v) and v.is_floating_point() else v) for k, v in st.items()}
+                k: (v.detach().clone() if torch.is_tensor(v) and v.is_floating_point() else v) for k, v in st.items()}
 
     def backward(self, loss):
         if self.scaler is not None:

@@ -1,7 +1,8 @@
 """``FusedAdam`` entry points.  The reference picks between two apex-backed classes
 (metaseq/optim/fused_adam.py:11-37: V1 = ``fused_adam_cuda.adam`` per parameter with a combined scale,
 V2 = ``multi_tensor_adam``); here both names resolve to the optimizer whose update is the ``msq_adamw`` kernel
-(``csrc/optim.cu``): decoupled weight decay, fp32 moments, 16-bit parameters updated in place from an fp32
+(``csrc/optim.cu``): decoupled weight decay, fp32 moments (stored as scaled fp16 between steps with
+``use_fp16_stats``), 16-bit parameters updated in place from an fp32
 computation, and the gradient scale (1 / loss-scale x clip coefficient) folded into the kernel's read of the
 gradient, so ``step(scale=...)`` needs no separate unscale pass."""
 from __future__ import annotations
@@ -21,9 +22,7 @@ class FusedAdamV1(Adam):
                  weight_decay=0.0, max_grad_norm=0.0, amsgrad=False, use_fp16_stats=False):
         if amsgrad:
             raise RuntimeError("FusedAdam does not support the AMSGrad variant.")
-        if use_fp16_stats:
-            raise NotImplementedError("16-bit optimizer statistics are not supported; moments are kept in fp32")
-        super().__init__(params, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
+        super().__init__(params, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, use_fp16_stats=use_fp16_stats)
         self.max_grad_norm = max_grad_norm
 
     def step(self, closure=None, grads=None, scale: float = 1.0, grad_norms=None, ctrl: Optional[torch.Tensor] = None):

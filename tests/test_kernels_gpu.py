@@ -646,3 +646,31 @@ def test_adamw_list_form_matches_one_launch_per_tensor(pdt, gdt):
         for x, y in zip(a, b):
             assert torch.equal(x, y)
     _status_ok()
+
+
+def test_adam_with_fp16_statistics_on_the_kernel_path():
+    """Moments kept as scaled fp16 between steps: the kernel updates fp32 working copies, and the result follows the
+    fp32-moment optimizer to within the quantisation of the moments."""
+    from metaseq_b200.optim.adam import Adam
+
+    torch.manual_seed(0)
+    shapes = [(1024, 64), (4096,), (333,)]
+    full = [torch.nn.Parameter(torch.randn(*s, device="cuda")) for s in shapes]
+    half = [torch.nn.Parameter(p.detach().clone()) for p in full]
+    a = Adam(full, lr=1e-2, betas=(0.9, 0.95), weight_decay=0.1)
+    b = Adam(half, lr=1e-2, betas=(0.9, 0.95), weight_decay=0.1, use_fp16_stats=True)
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    for _ in range(5):
+        for p, q in zip(full, half):
+            g = torch.randn(p.shape, device="cuda", generator=gen) * 1e-3
+            p.grad, q.grad = g.clone(), g.clone()
+        before = _lib.launch_count()
+        b.step()
+        assert _lib.launch_count() > before  # the update itself is the native kernel
+        a.step()
+    for p, q in zip(full, half):
+        st = b.state[q]
+        assert st["exp_avg"].dtype == torch.float16 and st["exp_avg_sq"].dtype == torch.float16
+        assert st["exp_avg_scale"].is_cuda  # no host synchronisation for the scale
+        assert (p - q).abs().max().item() < 5e-4
+    _status_ok()

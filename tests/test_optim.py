@@ -224,3 +224,104 @@ def test_optimizer_state_sharding_partitions_and_steps():
     opt.step()
     for b, p in zip(before, ps):
         assert torch.allclose(b - 0.1, p)
+
+
+def _adam_pair(fp16_stats_kw, n=513, steps=6, tiny_grads=False):
+    from metaseq_b200.optim.adam import Adam
+
+    torch.manual_seed(0)
+    p_a = torch.nn.Parameter(torch.randn(n))
+    p_b = torch.nn.Parameter(p_a.detach().clone())
+    a = Adam([p_a], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    b = Adam([p_b], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, **fp16_stats_kw)
+    for step in range(steps):
+        g = torch.randn(n, generator=torch.Generator().manual_seed(step))
+        if tiny_grads:
+            g = g * 1e-6  # second moments near 1e-13: far below what unscaled fp16 can hold
+        p_a.grad, p_b.grad = g.clone(), g.clone()
+        a.step()
+        b.step()
+    return p_a, p_b, a, b
+
+
+@pytest.mark.parametrize("tiny_grads", [False, True])
+def test_fp16_adam_stats_track_the_fp32_moments(tiny_grads):
+    p32, p16, _, opt = _adam_pair({"use_fp16_stats": True}, tiny_grads=tiny_grads)
+    st = opt.state[p16]
+    assert st["exp_avg"].dtype == torch.float16 and st["exp_avg_sq"].dtype == torch.float16
+    assert float(st["exp_avg"].float().abs().max()) == pytest.approx(65504.0, rel=2e-3)  # the scale uses the full range
+    # six steps of lr 1e-2: the scaled 11-bit moments move the parameters by well under a percent of a step
+    assert (p32 - p16).abs().max().item() < 2e-4
+    assert (p32 - p16).abs().max().item() > 0  # and they are really quantised
+
+
+def test_fp16_adam_stats_flag_reaches_the_optimizer_and_survives_reload():
+    cfg = _cfg()
+    cfg.optimizer.fp16_adam_stats = True
+    model, x, target = _problem(torch.float16)
+    opt = MemoryEfficientFP16Optimizer.build_optimizer(cfg, list(model.parameters()))
+    assert opt.optimizer.use_fp16_stats
+    _run_iter(model, x, target, opt)
+    saved = copy.deepcopy(opt.state_dict())
+    for st in saved["state"].values():
+        assert st["exp_avg"].dtype == torch.float16 and "exp_avg_scale" in st and "exp_avg_sq_scale" in st
+    model2, _, _ = _problem(torch.float16)
+    model2.load_state_dict(model.state_dict())
+    opt2 = MemoryEfficientFP16Optimizer.build_optimizer(cfg, list(model2.parameters()))
+    opt2.load_state_dict(saved)
+    for st, st2 in zip(opt.optimizer.state.values(), opt2.optimizer.state.values()):
+        assert st2["exp_avg"].dtype == torch.float16
+        assert torch.equal(st["exp_avg"], st2["exp_avg"]) and torch.equal(st["exp_avg_sq"], st2["exp_avg_sq"])
+        assert float(st2["exp_avg_sq_scale"]) == pytest.approx(float(st["exp_avg_sq_scale"]), rel=1e-6)
+    # the next update is the same on both
+    for m, o in ((model, opt), (model2, opt2)):
+        o.zero_grad()
+        loss = torch.nn.L1Loss()(m(x), target)
+        o.backward(loss)
+        o.clip_grad_norm(0)
+        o.step()
+    assert torch.equal(model.weight, model2.weight) and torch.equal(model.bias, model2.bias)
+
+
+def test_fp16_adam_stats_survive_a_loader_that_casts_state_to_fp32():
+    # torch.optim casts loaded state to the parameter's dtype: with fp32 parameters the stored fp16 values arrive as
+    # fp32 and the scale still applies
+    from metaseq_b200.optim.adam import Adam
+
+    _, p16, _, opt = _adam_pair({"use_fp16_stats": True}, n=64, steps=3)
+    saved = copy.deepcopy(opt.state_dict())
+    q = torch.nn.Parameter(p16.detach().clone())
+    opt2 = Adam([q], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, use_fp16_stats=True)
+    opt2.load_state_dict(saved)
+    assert opt2.state[q]["exp_avg"].dtype == torch.float32  # torch's cast
+    g = torch.randn(64, generator=torch.Generator().manual_seed(9))
+    p16.grad, q.grad = g.clone(), g.clone()
+    opt.step()
+    opt2.step()
+    assert torch.allclose(p16, q, rtol=0, atol=1e-7)
+    assert opt2.state[q]["exp_avg"].dtype == torch.float16
+
+
+def test_resharding_joins_scaled_fp16_moments_as_fp32():
+    from metaseq_b200.checkpoint import flat_shards
+
+    full_m = torch.linspace(-1.0, 1.0, 8)
+    full_v = torch.linspace(1e-12, 3e-9, 8)
+
+    def shard(i):
+        m, v = full_m[4 * i: 4 * i + 4], full_v[4 * i: 4 * i + 4]
+        ms, vs = m.abs().max() / 65504.0 + 1e-8, v.abs().max() / 65504.0 + 1e-8
+        md = {"param_metadata": [{"fsdp_path": "", "params": {"flat_param_0": {
+            "names": ["w"], "shapes": [[8]], "numels": [8], "padding": 0}},
+            "no_broadcast_optim_state": False, "shared_param_info": []}], "buffer_names": []}
+        return {"model": {"flat_param_0": torch.zeros(4)}, "shard_metadata": md,
+                "last_optimizer_state": {"state": {0: {"step": 3, "exp_avg": (m / ms).half(), "exp_avg_scale": ms,
+                                                       "exp_avg_sq": (v / vs).half(), "exp_avg_sq_scale": vs}},
+                                         "param_groups": [{"params": [0]}]}}
+
+    out = flat_shards.reshard_optimizer_state([shard(0), shard(1)], 0, 1)
+    st = out["state"][0]
+    assert "exp_avg_scale" not in st and "exp_avg_sq_scale" not in st and st["step"] == 3
+    assert st["exp_avg"].dtype == torch.float32 and st["exp_avg"].numel() == 8
+    assert torch.allclose(st["exp_avg"], full_m, rtol=2e-3, atol=1e-7)
+    assert torch.allclose(st["exp_avg_sq"], full_v, rtol=2e-3, atol=1e-15)
