@@ -28,6 +28,7 @@ VARIANTS = {
     "vocab_parallel_criterion": POLY + ["--criterion", "vocab_parallel_cross_entropy"],
     "dropout": POLY + ["--dropout", "0.1", "--attention-dropout", "0.1"],
     "fully_sharded": POLY + ["--ddp-backend", "fully_sharded", "--use-sharded-state"],
+    "fp16_adam_stats": POLY + ["--memory-efficient-fp16", "--fp16-init-scale", "4", "--fp16-adam-stats"],
     "loss_spike_guard": POLY + ["--ewm-ratio-to-skip-batch", "2.0"],
 }
 
