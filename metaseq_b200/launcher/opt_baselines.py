@@ -17,7 +17,7 @@ def add_extra_options_func(parser):
     parser.add_argument("--restore-file", help="load an existing checkpoint for continuing training")
     parser.add_argument("--reset-dataloader", action="store_true", help="reset the dataloader to epoch 1")
     parser.add_argument("--model-size", choices=MODEL_SIZES.keys(), required=True)
-    parser.add_argument("--data", default=None, help="path to the training data (directory with train/ and valid/)")
+    # --data (directory with train/ and valid/) is an option of the sweep parser itself
     parser.add_argument("--vocab-filename", default=None)
     parser.add_argument("--merges-filename", default=None)
     parser.add_argument("--valid-subset", default=None)

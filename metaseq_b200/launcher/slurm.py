@@ -144,8 +144,20 @@ def gen_train_command(args, env, hp_values, oss_destination, save_dir, save_dir_
     cmd += ["--distributed-world-size", str(args.num_nodes * args.num_gpus)]
     if args.num_nodes > 1 or (args.num_gpus > 1 and not args.local):
         cmd += ["--distributed-port", str(get_random_port())]
+    if getattr(args, "data", None) is not None and not any(hp.name == "--data" for hp in hp_values):
+        cmd.append(args.data)  # positional, unless the grid already passes it by name
+    run_name = save_dir_key  # <prefix>.<keys>.ngpu<N>, the basename of save_dir
     if not getattr(args, "no_save_dir", False):
-        cmd += ["--save-dir", save_dir]
+        local_root = getattr(args, "local_checkpoints_dir", None)
+        cmd += ["--save-dir", os.path.join(local_root, run_name) if local_root else save_dir]
+    upload = getattr(args, "full_azure_upload_path", None)
+    if upload is not None:
+        if getattr(args, "azure_folder_auto_name", False):
+            from urllib.parse import urlparse
+
+            url = urlparse(upload)
+            upload = url._replace(path=os.path.join(url.path, run_name) + "/").geturl()
+        cmd += ["--save-async", "--cloud-upload-path", upload]
     if args.update_freq:
         cmd += ["--update-freq", str(args.update_freq)]
     if getattr(args, "log_tensorboard", False) or args.tensorboard_logdir:

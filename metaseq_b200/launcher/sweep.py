@@ -71,6 +71,15 @@ def get_args(add_extra_options_func=None, input_args=None):
                                                                   str(datetime.date.today())),
                         help="save checkpoints and logs in <checkpoints-dir>/<prefix>.<save_dir_key>")
     parser.add_argument("--cluster-env", default="local", help="cluster environment: fair / aws / azure / rsc / local")
+    for env_name in ("azure", "aws", "fair", "rsc"):  # the reference's spelling of --cluster-env <name>
+        parser.add_argument(f"--{env_name}", action="store_true", help=f"running on {env_name}")
+    parser.add_argument("-d", "--data", help="path to data directory (appended to the training command)")
+    parser.add_argument("--local-checkpoints-dir", default=None,
+                        help="node-local directory for checkpoints (the job's save dir then holds logs only)")
+    parser.add_argument("--full-azure-upload-path", default=None,
+                        help="blob-store URL that checkpoints are uploaded to asynchronously")
+    parser.add_argument("--azure-folder-auto-name", action="store_true",
+                        help="append <prefix>.<save_dir_key>.ngpu<N>/ to the upload URL")
     parser.add_argument("--log-tensorboard", action="store_true")
     parser.add_argument("--tensorboard-logdir", default=None)
     parser.add_argument("--post-steps", nargs="+", help="additional steps to execute after the primary job is complete")
@@ -99,7 +108,13 @@ def get_args(add_extra_options_func=None, input_args=None):
     parser.add_argument("--jobarray-name", type=str, default=None)
     if add_extra_options_func is not None:
         add_extra_options_func(parser)
-    return parser.parse_args(input_args)
+    args = parser.parse_args(input_args)
+    chosen = [n for n in ("azure", "aws", "fair", "rsc") if getattr(args, n)]
+    if len(chosen) > 1:
+        parser.error("pass only one of --azure, --aws, --fair, --rsc")
+    if chosen:
+        args.cluster_env = chosen[0]
+    return args
 
 
 def grid_product(grid: List[hyperparam]):

@@ -233,6 +233,33 @@ def test_launcher_skips_finished_runs_and_builds_sbatch(tmp_path):
     assert env["NCCL_ASYNC_ERROR_HANDLING"] == "1"
 
 
+def test_launcher_cluster_flags_data_and_upload_paths(tmp_path, capsys):
+    from metaseq_b200.launcher import slurm, sweep
+
+    def get_grid(args):
+        return [sweep.hyperparam("--lr", [0.1], save_dir_key=lambda v: f"lr{v}")]
+
+    base = ["-p", "exp", "-g", "2", "-n", "1", "--dry-run", "--local", "--checkpoints-dir", str(tmp_path)]
+    args = sweep.get_args(input_args=base + ["--azure", "-d", "/data/corpus", "--local-checkpoints-dir", "/mnt/scratch",
+                                             "--full-azure-upload-path", "https://acct.blob.example/cont/run?sig=abc",
+                                             "--azure-folder-auto-name"])
+    assert args.cluster_env == "azure"
+    slurm.main(get_grid, lambda a, c: None, args)
+    out = capsys.readouterr().out
+    line = next(ln for ln in out.splitlines() if "train command:" in ln)
+    assert " /data/corpus " in line
+    assert "--save-dir /mnt/scratch/exp.lr0.1.ngpu2" in line
+    assert "--save-async --cloud-upload-path 'https://acct.blob.example/cont/run/exp.lr0.1.ngpu2/?sig=abc'" in line
+    # without the auto-name flag the URL is passed through; without a local dir the save dir is the job's own
+    args = sweep.get_args(input_args=base + ["--fair", "--full-azure-upload-path", "nfs:/shared/ckpt"])
+    assert args.cluster_env == "fair"
+    slurm.main(get_grid, lambda a, c: None, args)
+    line = next(ln for ln in capsys.readouterr().out.splitlines() if "train command:" in ln)
+    assert f"--save-dir {tmp_path}/exp.lr0.1.ngpu2" in line and "--cloud-upload-path nfs:/shared/ckpt" in line
+    with pytest.raises(SystemExit):
+        sweep.get_args(input_args=base + ["--aws", "--rsc"])
+
+
 def test_tombstone_triggers_action_and_is_removed(tmp_path):
     from metaseq_b200.launcher.tombyard import tombstones, tombstones_procedure
 
