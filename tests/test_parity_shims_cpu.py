@@ -4,6 +4,7 @@ import os
 import pickle
 
 import numpy as np
+import pytest
 import torch
 
 
@@ -120,3 +121,55 @@ def test_single_purpose_dataset_wrappers():
     assert padded.tolist() == [[0, 5, 6, 7, 2], [0, 8, 9, 2, 1]]
     order = sort_dataset.SortDataset(app, sort_order=[[1, 0]]).ordered_indices()
     assert list(order) == [1, 0]
+
+
+def test_faster_transformer_driver_passes_sampling_parameters_and_strips_special_tokens(tmp_path):
+    """The prompt loop for an external FasterTransformer build, run against a stand-in for the library's op."""
+    from metaseq_b200.cli import interactive_ft as ift
+
+    calls = {}
+
+    class FakeOp:
+        def __init__(self, *ctor):
+            calls["ctor"] = ctor
+
+        def forward(self, batch, lengths, output_length, beam_width, *rest):
+            calls["forward"] = (batch.clone(), lengths.clone(), output_length, beam_width, rest)
+            rows = []
+            for row, n in zip(batch, lengths):
+                # prompt, three new tokens, EOS, then garbage that must not be returned
+                rows.append(torch.cat([row[: int(n)], torch.tensor([40, 41, 42, ift.EOS, 77, 78], dtype=torch.int32)]))
+            width = max(len(r) for r in rows)
+            out = torch.full((len(rows), beam_width, width), ift.PAD, dtype=torch.int32)
+            for i, r in enumerate(rows):
+                out[i, 0, : len(r)] = r
+            return out, torch.tensor([[len(r)] * beam_width for r in rows], dtype=torch.int32)
+
+    class FakeLib:
+        ParallelGptOp = FakeOp
+
+    weights = tmp_path / "part-0.pt"
+    torch.save({"weights": [torch.ones(2, 2), torch.zeros(3)], "int8_weights": [torch.ones(2, dtype=torch.int8)],
+                "int8_scales": [torch.ones(1)]}, weights)
+    model = ift.build_model(FakeLib, str(weights), num_layers=2, num_heads=4, embed_size=32, vocab_size=100,
+                            tensor_para_size=1, dtype=torch.bfloat16, int8_mode=1, device="cpu")
+    ctor = calls["ctor"]
+    assert ctor[:4] == (4, 8, 128, 2) and ctor[5] == 100 and ctor[10] == 1
+    assert ctor[16][0].dtype == torch.bfloat16 and len(ctor[17]) == 1 and len(ctor[18]) == 1
+    # int8 mode without int8 tensors in the file falls back to 0
+    torch.save([torch.ones(2, 2)], weights)
+    ift.build_model(FakeLib, str(weights), 2, 4, 32, 100, 1, int8_mode=1, device="cpu")
+    assert calls["ctor"][10] == 0 and calls["ctor"][17] == []
+
+    args = ift.get_parser().parse_args(["--weight-path", "x", "--beam-width", "2", "--top-k", "7", "--len-penalty", "0.3",
+                                        "--diversity-rate", "0.1", "--repetition-penalty", "1.5", "--output-length", "4"])
+    out = ift.generate(model, [[10, 11, 12], [20]], device="cpu", **ift.sampling_kwargs(args))
+    assert out == [[10, 11, 12, 40, 41, 42], [20, 40, 41, 42]]  # prompt and continuation, nothing past the EOS
+    batch, lengths, output_length, beam_width, rest = calls["forward"]
+    assert batch[:, 0].tolist() == [ift.EOS, ift.EOS] and lengths.tolist() == [4, 2] and batch[1, 2:].tolist() == [ift.PAD] * 2
+    assert output_length == 4 and beam_width == 2
+    top_k, top_p, diversity, temperature, len_penalty, repetition, presence, min_length, seed, bad_words, cum = rest
+    assert int(top_k) == 7 and top_k.dtype == torch.int32 and float(top_p) == pytest.approx(0.95)
+    assert float(diversity) == pytest.approx(0.1) and float(len_penalty) == pytest.approx(0.3)
+    assert float(repetition) == pytest.approx(1.5) and float(temperature) == pytest.approx(0.7)
+    assert presence is None and min_length is None and int(seed) == 0 and bad_words is None and cum == 0
