@@ -139,6 +139,17 @@ def _prune(ckpt, suffix, end_of_epoch):
                 os.remove(old)
 
 
+def delete_old_checkpoint_files(cfg, end_of_epoch: bool, suffix: str) -> None:
+    """Keeps the newest ``keep_last_updates`` mid-epoch and ``keep_last_epochs`` end-of-epoch files of this rank's
+    suffix (metaseq/checkpoint_utils.py:112-129)."""
+    _prune(cfg, suffix, end_of_epoch)
+
+
+def is_singleton_tensor(x: Any) -> bool:
+    """A tensor without dimensions (optimizer step counts and scales are stored this way)."""
+    return torch.is_tensor(x) and x.dim() == 0
+
+
 def checkpoint_paths(path, pattern=r"checkpoint(\d+)\.pt"):
     """Checkpoints in ``path`` matching ``pattern``, sorted by the first group, newest first."""
     pt = re.compile(pattern)

@@ -24,7 +24,7 @@ import numpy as np
 import torch
 
 from metaseq_b200 import checkpoint_utils, options, tasks, utils
-from metaseq_b200.data import iterators
+from metaseq_b200.data import data_utils, iterators
 from metaseq_b200.dataclass.utils import Cfg, convert_namespace_to_config
 from metaseq_b200.file_io import PathManager
 from metaseq_b200.logging import meters, metrics, progress_bar
@@ -60,9 +60,13 @@ def main(cfg: Cfg) -> None:
     n_params = sum(p.numel() for p in model.parameters())
     logger.info(f"task: {task.__class__.__name__}; model: {model.__class__.__name__}; "
                 f"criterion: {criterion.__class__.__name__}; local params: {n_params:,}")
-    for valid_sub_split in cfg.dataset.valid_subset.split(","):
-        if valid_sub_split and not cfg.dataset.disable_validation:
-            task.load_dataset(valid_sub_split, combine=False, epoch=1)
+    data_utils.raise_if_valid_subsets_unintentionally_ignored(cfg)
+    if cfg.dataset.combine_valid_subsets and not cfg.dataset.disable_validation:
+        task.load_dataset("valid", combine=True, epoch=1)  # valid, valid1, valid2, ... as one set
+    else:
+        for valid_sub_split in cfg.dataset.valid_subset.split(","):
+            if valid_sub_split and not cfg.dataset.disable_validation:
+                task.load_dataset(valid_sub_split, combine=False, epoch=1)
     trainer = Trainer(cfg, task, model, criterion)
     logger.info(f"training on {cfg.distributed_training.distributed_world_size} devices (GPUs/TPUs); "
                 f"max tokens per GPU = {cfg.dataset.max_tokens} and batch size per GPU = {cfg.dataset.batch_size}")

@@ -173,3 +173,59 @@ def load_indexed_dataset(path, dictionary=None, dataset_impl=None, combine=False
         return None
     return found[0] if len(found) == 1 else ConcatDataset(found)
 
+
+
+def collect_filtered(function, iterable, filtered: list):
+    """Like ``filter``, but the rejected elements are appended to ``filtered``."""
+    for element in iterable:
+        if function(element):
+            yield element
+        else:
+            filtered.append(element)
+
+
+_JOINERS = {"sentencepiece": "▁", "wordpiece": "_", "letter": "|", "_EOW": "_EOW"}
+
+
+def post_process(sentence: str, symbol: Optional[str]) -> str:
+    """Undoes a sub-word segmentation written with spaces between pieces: the pieces are joined and the scheme's
+    word-boundary mark becomes a space (metaseq/data/data_utils.py:260-273)."""
+    if symbol is None or symbol == "none":
+        return sentence
+    if symbol not in _JOINERS:
+        raise NotImplementedError(f"Unknown post_process option: {symbol}")
+    return sentence.replace(" ", "").replace(_JOINERS[symbol], " ").strip()
+
+
+def _find_extra_valid_paths(dataset_path: str) -> set:
+    """Names (without extension) of the numbered validation sets (``valid1``, ``valid2.bin`` ...) in the local
+    directories of ``dataset_path``."""
+    import re
+
+    from metaseq_b200 import utils
+    from metaseq_b200.file_io import PathManager
+
+    found = set()
+    for sub_dir in utils.split_paths(dataset_path):
+        if "://" in sub_dir or not os.path.isdir(sub_dir):
+            continue
+        for entry in PathManager.ls(sub_dir):
+            name = os.path.basename(entry.rstrip("/"))
+            if re.match(r"valid*[0-9].*", name) is not None:
+                found.add(os.path.splitext(name)[0])
+    return found
+
+
+def raise_if_valid_subsets_unintentionally_ignored(train_cfg) -> None:
+    """Numbered validation sets on disk that ``--valid-subset`` does not name are an error unless they are combined
+    (``--combine-valid-subsets``), deliberately ignored (``--ignore-unused-valid-subsets``) or validation is off
+    (metaseq/data/data_utils.py:290-305)."""
+    ds = train_cfg.dataset
+    data = getattr(train_cfg.task, "data", None)
+    if ds.ignore_unused_valid_subsets or ds.combine_valid_subsets or ds.disable_validation or data is None:
+        return
+    named = ds.valid_subset.split(",")
+    ignored = sorted(p for p in _find_extra_valid_paths(data) if p not in named)
+    if ignored:
+        raise ValueError(f"Valid paths {ignored} will be ignored. Set --combine-val to combine them or "
+                         "--ignore-unused-valid-subsets to ignore them.")

@@ -486,7 +486,10 @@ class ShardedIterator(CountingIterator):
         super().__init__(itr, start=int(math.ceil(getattr(iterable, "n", 0) / float(num_shards))), total=sharded_len)
 
 
-class _BackgroundConsumer(threading.Thread):
+class BackgroundConsumer(threading.Thread):
+    """Feeds a queue from an iterable on a daemon thread; the end of the stream is a sentinel, an error of the
+    source is passed on as the exception object (metaseq/data/iterators.py:771-793)."""
+
     def __init__(self, q, source, max_len):
         super().__init__(daemon=True)
         self._queue, self._source, self._max_len = q, source, max_len
@@ -504,6 +507,9 @@ class _BackgroundConsumer(threading.Thread):
             self._queue.put(e)
 
 
+_BackgroundConsumer = BackgroundConsumer
+
+
 class BufferedIterator:
     """Prefetches up to ``size`` elements on a background thread."""
 
@@ -516,7 +522,7 @@ class BufferedIterator:
         self.total = len(iterable)
 
     def _start(self):
-        self._consumer = _BackgroundConsumer(self._queue, self._iterable, self.total)
+        self._consumer = BackgroundConsumer(self._queue, self._iterable, self.total)
         self._consumer.start()
 
     def __iter__(self):

@@ -47,6 +47,61 @@ class _IdTextCodec:
         return self._Enc(offs)
 
 
+def tensorize_input(tokenizer, prompt: str) -> torch.Tensor:
+    """``[1, T + 1]`` token ids of ``prompt`` with token 0 in front (metaseq/hub_utils.py:32)."""
+    ids = tokenizer.encode(prompt).ids
+    return torch.tensor([[0] + list(ids)], dtype=torch.long)
+
+
+def get_next_token(logits: torch.Tensor, tokenizer) -> str:
+    """Text of the most probable next token after the last position of the first sequence, without the
+    byte-level BPE's space marker (metaseq/hub_utils.py:39)."""
+    best = int(torch.argmax(logits[0, -1], dim=-1))
+    return tokenizer.decode([best]).replace("\u0120", "")
+
+
+def setup_vocab_and_merges(model_path: str):
+    """Paths of the GPT-2 vocabulary and merges files kept beside a model, and the tokenizer built from them
+    (metaseq/hub_utils.py:46)."""
+    from tokenizers import ByteLevelBPETokenizer
+
+    vocab_file = os.path.join(model_path, "gpt2-vocab.json")
+    merges_file = os.path.join(model_path, "gpt2-merges.txt")
+    return vocab_file, merges_file, ByteLevelBPETokenizer.from_file(vocab_file, merges_file)
+
+
+class _EncoderHubInterface:
+    """``encode`` / ``decode`` of one registered text encoder, built from keyword arguments."""
+
+    _kind = ""
+
+    def __init__(self, name, **kwargs):
+        from metaseq_b200.data import encoders
+
+        build = encoders.build_bpe if self._kind == "bpe" else encoders.build_tokenizer
+        self._impl = build(Namespace(**{self._kind: name}, **kwargs))
+        assert self._impl is not None, f"unknown {self._kind}: {name}"
+        setattr(self, self._kind, self._impl)
+
+    def encode(self, sentence: str) -> str:
+        return self._impl.encode(sentence)
+
+    def decode(self, sentence: str) -> str:
+        return self._impl.decode(sentence)
+
+
+class BPEHubInterface(_EncoderHubInterface):
+    """Byte-pair encoder by registry name (metaseq/hub_utils.py:53-66)."""
+
+    _kind = "bpe"
+
+
+class TokenizerHubInterface(_EncoderHubInterface):
+    """Word tokenizer by registry name (metaseq/hub_utils.py:69-82)."""
+
+    _kind = "tokenizer"
+
+
 class GeneratorInterface:
     def __init__(self, cfg):
         self.cfg = cfg

@@ -78,9 +78,15 @@ def get_reshard_parser(default_task=None):
     add_distributed_training_args(parser, default_world_size=1)
     group = parser.add_argument_group("Evaluation")
     gen_parser_from_dataclass(group, CommonEvalConfig())
+    add_reshard_args(parser)
+    return parser
+
+
+def add_reshard_args(parser):
+    """The options of checkpoint resharding at load time (metaseq/options.py:61)."""
     group = parser.add_argument_group("Reshard")
     gen_parser_from_dataclass(group, ReshardConfig())
-    return parser
+    return group
 
 
 def _import_user_module(args):

@@ -269,6 +269,12 @@ def get_world_size(group) -> int:
 
 
 # -------------------------------------------------------------- collectives
+def global_barrier():
+    """Waits for every process of the job, whatever groups it belongs to (metaseq/distributed/utils.py:223)."""
+    if torch.distributed.is_available() and torch.distributed.is_initialized():
+        torch.distributed.barrier(get_global_group())
+
+
 def all_reduce(tensor, group=None, op="sum"):
     if not is_initialized() or get_world_size(group) == 1:
         return tensor

@@ -791,6 +791,11 @@ class Trainer:
                 metrics.log_scalar(k, v, priority=1500, round=1, weight=0)
 
 
+class SpikeError(Exception):
+    """A loss far above its running mean.  ``Trainer.skip_spike`` handles spikes by skipping the batch; this type is
+    for callers that prefer to stop (the reference declares it without raising it: metaseq/trainer.py:1496)."""
+
+
 def utils_resolve_max_positions(*args):
     """Smallest of the given limits (None entries ignored)."""
     vals = []

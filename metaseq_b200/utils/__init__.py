@@ -4,7 +4,12 @@ metaseq/utils.py (make_positions :83-93, clip_grad_norm_ :133-229, seeds
 :372-410, CudaEnvironment :413-439, init functions :508-538)."""
 from __future__ import annotations
 
+import builtins
 import contextlib
+import copy
+import importlib
+import itertools
+import sys
 import logging
 import math
 import os
@@ -311,3 +316,185 @@ def print_r0(*a):
 
 def get_env(name, default=None):
     return os.environ.get(name, default)
+
+
+# ------------------------------------------------ further helpers of the reference's utils module
+def split_paths(paths: str) -> List[str]:
+    """``a:b`` (``os.pathsep``) for local paths, ``a|b`` when the entries are URLs (metaseq/utils.py:36)."""
+    return paths.split("|") if "://" in paths else paths.split(os.pathsep)
+
+
+def fill_with_neg_inf(t: torch.Tensor) -> torch.Tensor:
+    """``t`` filled with -inf in place, for any floating dtype (metaseq/utils.py:232)."""
+    return t.fill_(float("-inf"))
+
+
+def get_perplexity(loss, round: int = 2, base: float = 2):
+    """``base ** loss`` rounded; 0 for a missing loss, inf when the power overflows (metaseq/utils.py:340)."""
+    if loss is None:
+        return 0.0
+    try:
+        value = base ** float(loss)
+    except OverflowError:
+        return float("inf")
+    return builtins.round(value, round) if math.isfinite(value) else value
+
+
+def get_precise_epoch(epoch: Optional[int], count: int, iterator_size: int) -> Optional[float]:
+    """Fractional epoch after ``count + 1`` of ``iterator_size`` batches (metaseq/utils.py:494)."""
+    if epoch is None or iterator_size <= 0:
+        return None
+    return epoch - 1 + (count + 1) / float(iterator_size)
+
+
+def get_model_init_dtype(args) -> torch.dtype:
+    """Parameters are created in 16 bits when nothing keeps an fp32 copy of them (metaseq/utils.py:486)."""
+    if getattr(args, "memory_efficient_fp16", False) or getattr(args, "inference", False):
+        return torch.bfloat16 if getattr(args, "bf16", False) else torch.float16
+    return torch.float32
+
+
+def get_rng_state() -> Dict[str, torch.Tensor]:
+    state = {"torch_rng_state": torch.get_rng_state()}
+    if torch.cuda.is_available():
+        state["cuda_rng_state"] = torch.cuda.get_rng_state()
+    return state
+
+
+def set_rng_state(state: Dict[str, torch.Tensor]) -> None:
+    torch.set_rng_state(state["torch_rng_state"])
+    if torch.cuda.is_available() and "cuda_rng_state" in state:
+        torch.cuda.set_rng_state(state["cuda_rng_state"])
+
+
+@contextlib.contextmanager
+def set_rank_seed(seed: int, update: int):
+    """Seeds torch, numpy and ``random`` with ``seed + update * world + rank`` inside the block and restores all
+    three generators afterwards: every rank and every update draws its own stream (metaseq/utils.py:388-410)."""
+    if torch.distributed.is_available() and torch.distributed.is_initialized():
+        rank, world = torch.distributed.get_rank(), torch.distributed.get_world_size()
+    else:
+        rank, world = 0, 1
+    rank_seed = seed + update * world + rank
+    torch_state, np_state, py_state = get_rng_state(), np.random.get_state(), random.getstate()
+    torch.manual_seed(rank_seed)
+    if torch.cuda.is_available():
+        torch.cuda.manual_seed(rank_seed)
+    np.random.seed(rank_seed % (2 ** 32))
+    random.seed(rank_seed)
+    try:
+        yield rank_seed
+    finally:
+        random.setstate(py_state)
+        np.random.set_state(np_state)
+        set_rng_state(torch_state)
+
+
+def multi_tensor_l2_total_norm(grads, chunk_size: int = 2048 * 32) -> torch.Tensor:
+    """Norm over tensors that may live on several devices: one fused norm per device, combined on the first
+    (metaseq/utils.py:104-131).  ``chunk_size`` is accepted for call compatibility."""
+    by_device: Dict[torch.device, List[torch.Tensor]] = {}
+    for g in grads:
+        by_device.setdefault(g.device, []).append(g)
+    if not by_device:
+        return torch.tensor(0.0)
+    first = next(iter(by_device))
+    norms = [multi_tensor_l2_norm(ts).to(first) for ts in by_device.values()]
+    return torch.norm(torch.stack(norms))
+
+
+def resolve_max_positions(*limits):
+    """Element-wise smallest of several position limits.  A limit is a number, a tuple of numbers (one per stream)
+    or a dict of them; ``None`` (a whole limit or an entry) means "no constraint"; a number meets a tuple or a dict
+    by applying to every entry (metaseq/utils.py:259-293)."""
+
+    def smallest(a, b):
+        if a is None:
+            return b
+        if b is None:
+            return a
+        return min(a, b)
+
+    def broadcast(number, shape):
+        if isinstance(shape, tuple):
+            return tuple(number for _ in shape)
+        if isinstance(shape, dict):
+            return {k: broadcast(number, v) for k, v in shape.items()}
+        return number
+
+    def merge(a, b):
+        if isinstance(a, (int, float)) and not isinstance(b, (int, float)):
+            a = broadcast(a, b)
+        elif isinstance(b, (int, float)) and not isinstance(a, (int, float)):
+            b = broadcast(b, a)
+        if isinstance(a, dict):
+            out = copy.deepcopy(a)
+            for k, v in b.items():
+                out[k] = merge(out[k], v) if k in out and out[k] is not None and v is not None else smallest(out.get(k), v)
+            return out
+        if isinstance(a, (tuple, list)):
+            return tuple(smallest(x, y) for x, y in zip(a, b))
+        return smallest(a, b)
+
+    result = None
+    for limit in limits:
+        if limit is None:
+            continue
+        result = limit if result is None else merge(result, limit)
+    return result
+
+
+def import_user_module(args) -> None:
+    """Imports the package named by ``args.user_dir`` once, so that the components it registers exist before the
+    command line is parsed.  A relative path is also tried against this package and its parent; a module name that
+    is already imported from elsewhere is an error (metaseq/utils.py:296-329)."""
+    path = getattr(args, "user_dir", None)
+    if path is None:
+        return
+    candidates = [os.path.abspath(path)]
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    candidates += [os.path.join(here, path), os.path.join(os.path.dirname(here), path)]
+    found = next((c for c in candidates if os.path.exists(c)), None)
+    if found is None:
+        raise FileNotFoundError(candidates[0])
+    memo = import_user_module.__dict__.setdefault("memo", set())
+    if found in memo:
+        return
+    memo.add(found)
+    parent, name = os.path.split(found.rstrip(os.sep))
+    if name in sys.modules:
+        raise ImportError(f"Failed to import --user-dir={found}: a module called {name!r} is already imported; "
+                          "rename the directory to something unique")
+    sys.path.insert(0, parent)
+    importlib.import_module(name)
+
+
+def get_token_to_word_mapping(tokens, exclude_list) -> Dict[int, int]:
+    """Position -> running count of tokens that are not in ``exclude_list`` (metaseq/utils.py:541)."""
+    counts = itertools.accumulate(int(t not in exclude_list) for t in tokens)
+    return dict(enumerate(counts))
+
+
+def extract_hard_alignment(attn: torch.Tensor, src_sent, tgt_sent, pad: int, eos: int):
+    """For every real target token the source word with the largest attention weight, as (source word, target
+    word) pairs counted from 0.  ``attn``: [target, source] (metaseq/utils.py:549-570)."""
+    tgt_valid = ((tgt_sent != pad) & (tgt_sent != eos)).nonzero(as_tuple=False).squeeze(-1)
+    src_invalid = ((src_sent == pad) | (src_sent == eos)).nonzero(as_tuple=False).squeeze(-1)
+    if len(tgt_valid) == 0 or len(src_invalid) >= len(src_sent):
+        return []
+    src_word = get_token_to_word_mapping(src_sent, [eos, pad])
+    tgt_word = get_token_to_word_mapping(tgt_sent, [eos, pad])
+    weights = attn[tgt_valid].clone()
+    weights[:, src_invalid] = float("-inf")
+    best = weights.argmax(dim=1)
+    return [(src_word[int(s)] - 1, tgt_word[int(t)] - 1) for t, s in zip(tgt_valid.tolist(), best.tolist())]
+
+
+def extract_soft_alignment(attn: torch.Tensor, src_sent, tgt_sent, pad: int, eos: int):
+    """Attention rows of the non-pad target tokens over the non-pad source tokens, formatted with six decimals
+    (metaseq/utils.py:573-582)."""
+    tgt_valid = (tgt_sent != pad).nonzero(as_tuple=False)
+    src_valid = (src_sent != pad).nonzero(as_tuple=False).squeeze(-1)
+    if len(tgt_valid) == 0 or len(src_valid) == 0:
+        return []
+    return [[f"{p:.6f}" for p in row.tolist()] for row in attn[tgt_valid, src_valid]]

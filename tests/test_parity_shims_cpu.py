@@ -173,3 +173,94 @@ def test_faster_transformer_driver_passes_sampling_parameters_and_strips_special
     assert float(diversity) == pytest.approx(0.1) and float(len_penalty) == pytest.approx(0.3)
     assert float(repetition) == pytest.approx(1.5) and float(temperature) == pytest.approx(0.7)
     assert presence is None and min_length is None and int(seed) == 0 and bad_words is None and cum == 0
+
+
+def test_reference_utility_helpers():
+    from metaseq_b200 import checkpoint_utils, hub_utils, utils
+    from metaseq_b200.data import data_utils
+
+    assert utils.split_paths("/a:/b") == ["/a", "/b"] and utils.split_paths("s3://x|s3://y") == ["s3://x", "s3://y"]
+    assert utils.get_perplexity(3.0) == 8.0 and utils.get_perplexity(None) == 0.0 and utils.get_perplexity(1e9) == float("inf")
+    assert utils.get_precise_epoch(2, 4, 10) == pytest.approx(1.5) and utils.get_precise_epoch(None, 4, 10) is None
+    assert utils.get_model_init_dtype(type("A", (), {"memory_efficient_fp16": True, "bf16": True})) == torch.bfloat16
+    assert utils.get_model_init_dtype(type("A", (), {"inference": True})) == torch.float16
+    assert utils.get_model_init_dtype(type("A", (), {})) == torch.float32
+    t = utils.fill_with_neg_inf(torch.zeros(3, dtype=torch.float16))
+    assert t.dtype == torch.float16 and torch.isinf(t).all()
+    # limits: numbers, tuples, dicts, None
+    assert utils.resolve_max_positions(1024, (2048, 512), None) == (1024, 512)
+    assert utils.resolve_max_positions({"a": 5, "b": None}, {"a": 7, "b": 3, "c": 1}) == {"a": 5, "b": 3, "c": 1}
+    assert utils.resolve_max_positions(None, None) is None
+    # seeding by rank and update: reproducible inside, outer stream untouched
+    torch.manual_seed(0)
+    before = torch.get_rng_state()
+    with utils.set_rank_seed(3, 2) as seed:
+        a, n = torch.rand(2), np.random.rand()
+    with utils.set_rank_seed(3, 2):
+        b, m = torch.rand(2), np.random.rand()
+    assert seed == 5 and torch.equal(a, b) and n == m and torch.equal(before, torch.get_rng_state())
+    state = utils.get_rng_state()
+    x = torch.rand(1)
+    utils.set_rng_state(state)
+    assert torch.equal(x, torch.rand(1))
+    assert float(utils.multi_tensor_l2_total_norm([torch.ones(4), torch.ones(5)])) == pytest.approx(3.0)
+    # alignments
+    attn = torch.tensor([[0.1, 0.8, 0.1], [0.6, 0.3, 0.1], [0.3, 0.3, 0.4]])
+    src, tgt = torch.tensor([5, 6, 2]), torch.tensor([7, 8, 2])
+    assert utils.extract_hard_alignment(attn, src, tgt, pad=1, eos=2) == [(1, 0), (0, 1)]
+    soft = utils.extract_soft_alignment(attn, src, tgt, pad=1, eos=2)
+    assert len(soft) == 3 and soft[0] == ["0.100000", "0.800000", "0.100000"]
+    assert utils.get_token_to_word_mapping([5, 2, 6], [2]) == {0: 1, 1: 1, 2: 2}
+    # data helpers
+    rejected = []
+    assert list(data_utils.collect_filtered(lambda v: v % 2 == 0, range(5), rejected)) == [0, 2, 4] and rejected == [1, 3]
+    assert data_utils.post_process("\u2581he llo \u2581wor ld", "sentencepiece") == "hello world"
+    assert data_utils.post_process("a b", "none") == "a b" and data_utils.post_process("a b", None) == "a b"
+    with pytest.raises(NotImplementedError):
+        data_utils.post_process("a", "bogus")
+    assert checkpoint_utils.is_singleton_tensor(torch.tensor(1.0)) and not checkpoint_utils.is_singleton_tensor(torch.ones(1))
+
+    class Tok:
+        def encode(self, prompt):
+            return type("E", (), {"ids": [5, 6]})
+
+        def decode(self, ids):
+            return "\u0120there" if ids == [2] else "?"
+
+    assert hub_utils.tensorize_input(Tok(), "x").tolist() == [[0, 5, 6]]
+    assert hub_utils.get_next_token(torch.tensor([[[0.0, 0.0, 1.0]]]), Tok()) == "there"
+
+
+def test_unlisted_numbered_validation_sets_are_an_error_unless_combined_or_ignored(tmp_path):
+    from metaseq_b200.data import data_utils
+    from metaseq_b200.dataclass.utils import Cfg
+
+    for name in ("train.bin", "valid.bin", "valid.idx", "valid1.bin", "valid1.idx", "valid2.bin"):
+        (tmp_path / name).write_bytes(b"")
+
+    def cfg(**ds):
+        base = {"ignore_unused_valid_subsets": False, "combine_valid_subsets": None, "disable_validation": False,
+                "valid_subset": "valid"}
+        base.update(ds)
+        return Cfg({"dataset": Cfg(base), "task": Cfg({"data": str(tmp_path)})})
+
+    with pytest.raises(ValueError, match=r"valid1.*valid2"):
+        data_utils.raise_if_valid_subsets_unintentionally_ignored(cfg())
+    data_utils.raise_if_valid_subsets_unintentionally_ignored(cfg(valid_subset="valid,valid1,valid2"))
+    data_utils.raise_if_valid_subsets_unintentionally_ignored(cfg(ignore_unused_valid_subsets=True))
+    data_utils.raise_if_valid_subsets_unintentionally_ignored(cfg(combine_valid_subsets=True))
+    data_utils.raise_if_valid_subsets_unintentionally_ignored(cfg(disable_validation=True))
+
+
+def test_old_checkpoints_are_pruned_by_public_helper(tmp_path):
+    from metaseq_b200 import checkpoint_utils
+    from metaseq_b200.dataclass.utils import Cfg
+
+    for n in (10, 20, 30):
+        (tmp_path / f"checkpoint_{n}-model_part-0.pt").write_bytes(b"")
+        (tmp_path / f"checkpoint_{n}-model_part-1.pt").write_bytes(b"")
+    cfg = Cfg({"save_dir": str(tmp_path), "keep_last_updates": 2, "keep_last_epochs": -1})
+    checkpoint_utils.delete_old_checkpoint_files(cfg, end_of_epoch=False, suffix="-model_part-0")
+    assert sorted(os.listdir(tmp_path)) == ["checkpoint_10-model_part-1.pt", "checkpoint_20-model_part-0.pt",
+                                            "checkpoint_20-model_part-1.pt", "checkpoint_30-model_part-0.pt",
+                                            "checkpoint_30-model_part-1.pt"]
