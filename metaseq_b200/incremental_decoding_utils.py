@@ -6,9 +6,22 @@ The attention module here keeps its preallocated key/value cache under such a ke
 from __future__ import annotations
 
 import uuid
-from typing import Dict, Optional
+from typing import Dict, Optional, Protocol, runtime_checkable
 
 from torch import Tensor
+
+
+@runtime_checkable
+class HasIncrementalState(Protocol):
+    """What ``with_incremental_state`` gives a module: typed access to its own slot of the shared dictionary."""
+
+    def get_incremental_state(self, incremental_state: Optional[Dict[str, Dict[str, Optional[Tensor]]]],
+                              key: str) -> Optional[Dict[str, Optional[Tensor]]]:
+        ...
+
+    def set_incremental_state(self, incremental_state: Optional[Dict[str, Dict[str, Optional[Tensor]]]], key: str,
+                              value: Dict[str, Optional[Tensor]]) -> Optional[Dict[str, Dict[str, Optional[Tensor]]]]:
+        ...
 
 
 class IncrementalState:

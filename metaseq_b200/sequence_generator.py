@@ -15,6 +15,7 @@ from __future__ import annotations
 
 import logging
 import math
+import sys
 from typing import Dict, List, Optional
 
 import torch
@@ -245,3 +246,63 @@ class SequenceGenerator(nn.Module):
         if count_tokens is not None:
             count_tokens.scatter_add_(1, next_toks[:, None], torch.ones_like(next_toks[:, None]))
         return count_tokens
+
+
+class EnsembleModel(nn.Module):
+    """Several decoder-only language models scored as one: each model keeps its own incremental state and the
+    next-token distribution is the arithmetic mean of the models' probabilities (log-sum-exp of their log-probs
+    minus log n).  With one model it is that model's log-softmax.  Reference: metaseq/sequence_generator.py:537-685;
+    the encoder-side and alignment variants there (``forward_encoder``, ``SequenceGeneratorWithAlignment``) belong
+    to encoder-decoder models, which neither code base defines."""
+
+    def __init__(self, models):
+        super().__init__()
+        models = list(models)
+        assert len(models) > 0
+        self.models_size = len(models)
+        self.single_model = models[0]
+        self.models = nn.ModuleList(models)
+        self.has_incremental = all(hasattr(m, "decoder") for m in models)
+
+    def forward(self):  # scoring goes through forward_decoder
+        raise RuntimeError("call forward_decoder")
+
+    def has_encoder(self) -> bool:
+        return hasattr(self.single_model, "encoder")
+
+    def has_incremental_states(self) -> bool:
+        return self.has_incremental
+
+    def max_decoder_positions(self) -> int:
+        limits = [m.max_decoder_positions() for m in self.models if hasattr(m, "max_decoder_positions")]
+        return min([x for x in limits if x is not None] + [sys.maxsize])
+
+    def new_incremental_states(self):
+        return [{} for _ in range(self.models_size)]
+
+    @torch.no_grad()
+    def forward_decoder(self, tokens: Tensor, incremental_states=None, temperature: float = 1.0):
+        """``tokens``: [B, T] prefix.  Returns ([B, V] log-probabilities of the next token, None)."""
+        per_model = []
+        for i, model in enumerate(self.models):
+            if self.has_incremental and incremental_states is not None:
+                out = model.decoder(tokens, incremental_state=incremental_states[i])
+            elif hasattr(model, "decoder"):
+                out = model.decoder(tokens)
+            else:
+                out = model(tokens)
+            logits = out[0] if isinstance(out, (tuple, list)) else out
+            last = logits[:, -1, :].float()
+            if temperature != 1.0:
+                last = last / temperature
+            per_model.append(torch.log_softmax(last, dim=-1))
+        if self.models_size == 1:
+            return per_model[0], None
+        return torch.logsumexp(torch.stack(per_model, dim=0), dim=0) - math.log(self.models_size), None
+
+    def reorder_incremental_state(self, incremental_states, new_order):
+        if not self.has_incremental or incremental_states is None:
+            return
+        for model, state in zip(self.models, incremental_states):
+            if hasattr(model.decoder, "reorder_incremental_state"):
+                model.decoder.reorder_incremental_state(state, new_order)

@@ -140,3 +140,22 @@ def test_samples_of_one_prompt_come_back_best_first():
     for row in range(2):
         assert out["tokens"][row, :, :2].tolist() == [src[row].tolist()] * 4  # every sample keeps its prompt
     assert all(math.isfinite(v) for v in totals.flatten().tolist())
+
+
+def test_ensemble_averages_probabilities_and_keeps_one_state_per_model():
+    from metaseq_b200.sequence_generator import EnsembleModel
+
+    torch.manual_seed(0)
+    V = 9
+    tables = [torch.randn(V, V) for _ in range(3)]
+    tokens = torch.tensor([[2, 4, 5], [2, 7, 1]])
+    ens = EnsembleModel([TableModel(t) for t in tables])
+    assert ens.has_incremental_states() and not ens.has_encoder() and ens.max_decoder_positions() == 24
+    states = ens.new_incremental_states()
+    assert len(states) == 3 and all(s is not t for s, t in zip(states, states[1:]))
+    lprobs, attn = ens.forward_decoder(tokens, states, temperature=0.5)
+    probs = torch.stack([torch.softmax(t[tokens[:, -1]] / 0.5, dim=-1) for t in tables]).mean(0)
+    assert attn is None and torch.allclose(lprobs.exp(), probs, atol=1e-6)
+    assert torch.allclose(lprobs.exp().sum(-1), torch.ones(2), atol=1e-6)
+    single, _ = EnsembleModel([TableModel(tables[0])]).forward_decoder(tokens)
+    assert torch.allclose(single, torch.log_softmax(tables[0][tokens[:, -1]], dim=-1), atol=1e-6)
