@@ -1,5 +1,5 @@
 """Data pipeline: dictionary, datasets, iterators."""
-from .dictionary import Dictionary  # noqa: F401
+from .dictionary import Dictionary, TruncatedDictionary  # noqa: F401
 from .base_dataset import BaseDataset, EpochListening  # noqa: F401
 from . import data_utils  # noqa: F401
 from .document_to_sequence import DocumentToSequenceDataset, LockingArray  # noqa: F401

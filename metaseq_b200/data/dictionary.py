@@ -179,3 +179,22 @@ class Dictionary:
         for i in range(vocab_size - d.nspecial):
             d.add_symbol(f"w{i}")
         return d
+
+
+
+class TruncatedDictionary:
+    """The first ``length`` entries of a dictionary: everything else of the wrapped dictionary (symbols, special
+    indices, encoding) is shared, larger indices read as the unknown symbol (metaseq/data/dictionary.py:382-399)."""
+
+    def __init__(self, wrapped_dict, length: int):
+        # become a subclass of the wrapped dictionary's class so that isinstance checks and its methods keep working
+        self.__class__ = type(wrapped_dict.__class__.__name__, (self.__class__, wrapped_dict.__class__), {})
+        self.__dict__ = wrapped_dict.__dict__
+        self.wrapped_dict = wrapped_dict
+        self.length = min(len(self.wrapped_dict), length)
+
+    def __len__(self):
+        return self.length
+
+    def __getitem__(self, i):
+        return self.wrapped_dict[i] if i < self.length else self.wrapped_dict.unk()

@@ -142,6 +142,27 @@ class RightPadDataset(PadDataset):
         super().__init__(dataset, pad_idx, left_pad=False)
 
 
+class MultiplePadDataset(BaseWrapperDataset):
+    """Items and batches right-padded to the next multiple of ``multiple`` (metaseq/data/pad_dataset.py:37-76)."""
+
+    def __init__(self, dataset, pad_idx, multiple):
+        super().__init__(dataset)
+        self.pad_idx = pad_idx
+        self.multiple = int(multiple)
+
+    def _round_up(self, n: int) -> int:
+        return -(-n // self.multiple) * self.multiple
+
+    def __getitem__(self, index):
+        item = self.dataset[index]
+        extra = self._round_up(item.numel()) - item.numel()
+        return item if extra == 0 else torch.cat([item, item.new_full((extra,), self.pad_idx)])
+
+    def collater(self, samples):
+        longest = max(s.size(0) for s in samples)
+        return data_utils.collate_tokens(samples, self.pad_idx, left_pad=False, pad_to_length=self._round_up(longest))
+
+
 class SortDataset(BaseWrapperDataset):
     """Orders indices by one or more keys (last key is the primary one, as in ``np.lexsort``)."""
 

@@ -16,6 +16,7 @@ transpose.
 """
 from __future__ import annotations
 
+import logging
 import math
 from typing import Any, Dict, List, Optional
 
@@ -39,6 +40,17 @@ def _get(args, name, default=None):
     return getattr(args, name, default)
 
 
+
+logger = logging.getLogger(__name__)
+
+
+def log_weight_stats(tensor, name: str) -> None:
+    """Mean, spread and range of a parameter at debug level (metaseq/models/transformer_decoder.py:56)."""
+    if logger.isEnabledFor(logging.DEBUG):
+        t = tensor.detach().float()
+        logger.debug(f"{name}, mean: {t.mean():.5f}, std: {t.std():.5f}, min: {t.min():.5f}, max: {t.max():.5f}")
+
+
 class _TiedProjection(nn.Module):
     """Holds the (shared) output-projection weight so that ``decoder.output_projection.weight``
     appears in the state dict next to ``decoder.embed_tokens.weight``."""
@@ -57,6 +69,7 @@ class ModelParallelTransformerDecoder(IncrementalDecoder):
         self.embed_dim = args.decoder_embed_dim
         self.max_target_positions = _get(args, "max_target_positions", None) or _get(args, "tokens_per_sample", 2048)
         self.embed_tokens = embed_tokens
+        log_weight_stats(embed_tokens.weight, "embed tokens")
         self.embed_scale = 1.0 if _get(args, "no_scale_embedding", False) else math.sqrt(self.embed_dim)
         self.sequence_parallel = bool(_get(args, "sequence_parallel", False))
         self.self_attn_doc_sep = _get(args, "self_attn_doc_sep", UNSPECIFIED_DOC_SEP)
@@ -75,6 +88,9 @@ class ModelParallelTransformerDecoder(IncrementalDecoder):
                 megatron_init_sigma=_get(args, "megatron_init_sigma", 0.006),
                 truncate_init=_get(args, "truncate_init", False), dtype=dtype, device=device)
         self.layers = nn.ModuleList([self.build_decoder_layer(args) for _ in range(args.decoder_layers)])
+        if logger.isEnabledFor(logging.DEBUG):
+            for name, param in self.layers.named_parameters():
+                log_weight_stats(param, name)
         self.num_layers = len(self.layers)
         self.layer_norm = LayerNorm(self.embed_dim, elementwise_affine=not _get(args, "disable_affine_ln", False))
         if dtype != torch.float32:

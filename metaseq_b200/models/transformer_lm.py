@@ -107,6 +107,13 @@ class ModelParallelTransformerLanguageModel(LanguageModel):
             dtype=dtype, device=torch.cuda.current_device() if on_gpu else None)
 
 
+@register_model("transformer_lm", dataclass=TransformerLanguageModelConfig)
+class TransformerLanguageModel(ModelParallelTransformerLanguageModel):
+    """The model under the name the reference keeps for a decoder without tensor parallelism
+    (metaseq/models/transformer_lm.py:188-191, where it has no builder of its own).  With a tensor-parallel group
+    of one the parallel layers are ordinary layers, so the same class serves both names."""
+
+
 def base_lm_architecture(args):
     d = lambda k, v: setattr(args, k, getattr(args, k, v) if getattr(args, k, None) is not None else v)
     d("activation_fn", "relu")

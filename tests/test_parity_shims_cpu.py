@@ -264,3 +264,42 @@ def test_old_checkpoints_are_pruned_by_public_helper(tmp_path):
     assert sorted(os.listdir(tmp_path)) == ["checkpoint_10-model_part-1.pt", "checkpoint_20-model_part-0.pt",
                                             "checkpoint_20-model_part-1.pt", "checkpoint_30-model_part-0.pt",
                                             "checkpoint_30-model_part-1.pt"]
+
+
+def test_truncated_dictionary_multiple_pad_dataset_and_model_name():
+    import metaseq_b200.models as models
+    from metaseq_b200.data import Dictionary, TruncatedDictionary
+    from metaseq_b200.data.pad_dataset import MultiplePadDataset
+
+    d = Dictionary()
+    for w in "abcdef":
+        d.add_symbol(w)
+    t = TruncatedDictionary(d, 6)
+    assert len(t) == 6 and len(d) == 10 and isinstance(t, Dictionary)
+    assert t[5] == d[5] and t[7] == d.unk() and t.index("a") == d.index("a") and t.pad() == d.pad()
+
+    class Items(torch.utils.data.Dataset):
+        def __init__(self, items):
+            self.items, self.sizes = items, np.array([len(i) for i in items])
+
+        def __getitem__(self, i):
+            return self.items[i]
+
+        def __len__(self):
+            return len(self.items)
+
+    ds = MultiplePadDataset(Items([torch.arange(5), torch.arange(8), torch.arange(9)]), pad_idx=1, multiple=8)
+    assert ds[0].tolist() == [0, 1, 2, 3, 4, 1, 1, 1] and ds[1].numel() == 8 and ds[2].numel() == 16
+    batch = ds.collater([torch.arange(5), torch.arange(9)])
+    assert batch.shape == (2, 16) and batch[0, 5:].eq(1).all() and batch[1, 9:].eq(1).all()
+    assert "transformer_lm" in models.MODEL_REGISTRY and "model_parallel_transformer_lm" in models.MODEL_REGISTRY
+
+
+def test_weight_statistics_are_logged_at_debug_level(caplog):
+    import logging
+
+    from metaseq_b200.models.transformer_decoder import log_weight_stats
+
+    with caplog.at_level(logging.DEBUG, logger="metaseq_b200.models.transformer_decoder"):
+        log_weight_stats(torch.tensor([1.0, 3.0]), "probe")
+    assert "probe, mean: 2.00000" in caplog.text and "max: 3.00000" in caplog.text
