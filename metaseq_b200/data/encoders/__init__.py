@@ -48,12 +48,19 @@ class GPT2BPEConfig(MetaseqDataclass):
 @register_bpe("gpt2", dataclass=GPT2BPEConfig)
 class GPT2BPE:
     def __init__(self, cfg):
-        from tokenizers import ByteLevelBPETokenizer
+        try:
+            from tokenizers import ByteLevelBPETokenizer
 
-        self.bpe = ByteLevelBPETokenizer(cfg.gpt2_encoder_json, cfg.gpt2_vocab_bpe)
+            self.bpe = ByteLevelBPETokenizer(cfg.gpt2_encoder_json, cfg.gpt2_vocab_bpe)
+            self._ids = lambda text: self.bpe.encode(text).ids
+        except ImportError:  # the plain-Python implementation of the same scheme
+            from .gpt2_bpe_utils import get_encoder
+
+            self.bpe = get_encoder(cfg.gpt2_encoder_json, cfg.gpt2_vocab_bpe)
+            self._ids = self.bpe.encode
 
     def encode(self, x: str) -> str:
-        return " ".join(map(str, self.bpe.encode(x).ids))
+        return " ".join(map(str, self._ids(x)))
 
     def decode(self, x: str) -> str:
         return self.bpe.decode([int(tok) for tok in x.split() if tok.isdigit()])

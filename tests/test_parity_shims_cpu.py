@@ -303,3 +303,26 @@ def test_weight_statistics_are_logged_at_debug_level(caplog):
     with caplog.at_level(logging.DEBUG, logger="metaseq_b200.models.transformer_decoder"):
         log_weight_stats(torch.tensor([1.0, 3.0]), "probe")
     assert "probe, mean: 2.00000" in caplog.text and "max: 3.00000" in caplog.text
+
+
+def test_plain_python_byte_level_bpe_agrees_with_the_tokenizers_library(tmp_path):
+    tokenizers = pytest.importorskip("tokenizers")
+    from metaseq_b200.data.encoders.gpt2_bpe_utils import bytes_to_unicode, get_encoder, get_pairs
+
+    table = bytes_to_unicode()
+    assert len(table) == 256 and len(set(table.values())) == 256 and table[ord("A")] == "A" and table[32] == "Ġ"
+    assert get_pairs(("a", "b", "c", "b", "c")) == {("a", "b"), ("b", "c"), ("c", "b")}
+
+    corpus = tmp_path / "corpus.txt"
+    corpus.write_text("the quick brown fox jumps over the lazy dog\nthe dog's bark: 123 4567!  we'll see naïve café\n" * 20,
+                      encoding="utf-8")
+    tok = tokenizers.ByteLevelBPETokenizer()
+    tok.train([str(corpus)], vocab_size=400, min_frequency=1, show_progress=False)
+    tok.save_model(str(tmp_path))
+    enc = get_encoder(str(tmp_path / "vocab.json"), str(tmp_path / "merges.txt"))
+    for text in ["the quick brown fox", "we'll see 4567 dogs!", "  two  spaces\nand a newline", "naïve café — ünïcödé ✓",
+                 "unseen wordzzz"]:
+        ids = enc.encode(text)
+        assert ids == tok.encode(text).ids, text
+        assert enc.decode(ids) == text
+    assert len(enc.cache) > 0
