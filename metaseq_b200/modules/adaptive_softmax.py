@@ -22,6 +22,27 @@ class TiedLinear(nn.Module):
         return F.linear(input, self.weight.t() if self.transpose else self.weight)
 
 
+class TiedHeadModule(nn.Module):
+    """Head of an adaptive softmax whose frequent-word logits reuse the first band of an adaptive input embedding:
+    ``[word logits | cluster logits]``, the cluster logits from a projection of their own.  ``weights`` is the
+    band's (embedding weight, projection weight) pair (metaseq/modules/adaptive_softmax.py:26-55)."""
+
+    def __init__(self, weights, input_dim: int, num_classes: int, q_noise: float = 0, qn_block_size: int = 8):
+        super().__init__()
+        tied_emb, _ = weights
+        self.num_words, emb_dim = tied_emb.size()
+        words = quant_noise(TiedLinear(tied_emb, transpose=False), q_noise, qn_block_size)
+        if input_dim != emb_dim:
+            words = nn.Sequential(quant_noise(nn.Linear(input_dim, emb_dim, bias=False), q_noise, qn_block_size), words)
+        self.word_proj = words
+        self.class_proj = quant_noise(nn.Linear(input_dim, num_classes, bias=False), q_noise, qn_block_size)
+        self.out_dim = self.num_words + num_classes
+
+    def forward(self, input):
+        flat = input.reshape(-1, input.size(-1))
+        return torch.cat([self.word_proj(flat), self.class_proj(flat)], dim=1)
+
+
 class AdaptiveSoftmax(nn.Module):
     def __init__(self, vocab_size: int, input_dim: int, cutoff: List[int], dropout: float, factor: float = 4.0,
                  adaptive_inputs=None, tie_proj: bool = False, q_noise: float = 0, qn_block_size: int = 8):
@@ -34,14 +55,25 @@ class AdaptiveSoftmax(nn.Module):
         self.vocab_size, self.cutoff, self.input_dim, self.factor = vocab_size, cutoff, input_dim, factor
         self.dropout = nn.Dropout(dropout)
         n_clusters = len(cutoff) - 1
-        self.head = quant_noise(nn.Linear(input_dim, cutoff[0] + n_clusters, bias=False), q_noise, qn_block_size) \
-            if adaptive_inputs is None else TiedLinear(adaptive_inputs.weights_for_band(0)[0], transpose=False)
+        if adaptive_inputs is None:
+            self.head = quant_noise(nn.Linear(input_dim, cutoff[0] + n_clusters, bias=False), q_noise, qn_block_size)
+        else:
+            self.head = TiedHeadModule(adaptive_inputs.weights_for_band(0), input_dim, n_clusters, q_noise, qn_block_size)
         self.tail = nn.ModuleList()
         for i in range(n_clusters):
             dim = int(input_dim // factor ** (i + 1))
             size = cutoff[i + 1] - cutoff[i]
-            proj = quant_noise(nn.Linear(input_dim, dim, bias=False), q_noise, qn_block_size)
-            out = quant_noise(nn.Linear(dim, size, bias=False), q_noise, qn_block_size)
+            tied_emb, tied_proj = adaptive_inputs.weights_for_band(i + 1) if adaptive_inputs is not None else (None, None)
+            if tied_proj is not None and tie_proj:
+                proj = quant_noise(TiedLinear(tied_proj, transpose=True), q_noise, qn_block_size)
+            elif tied_proj is not None:
+                proj = quant_noise(nn.Linear(tied_proj.size(0), tied_proj.size(1), bias=False), q_noise, qn_block_size)
+            else:
+                proj = quant_noise(nn.Linear(input_dim, dim, bias=False), q_noise, qn_block_size)
+            if tied_emb is None:
+                out = quant_noise(nn.Linear(dim, size, bias=False), q_noise, qn_block_size)
+            else:
+                out = quant_noise(TiedLinear(tied_emb, transpose=False), q_noise, qn_block_size)
             self.tail.append(nn.Sequential(proj, nn.Dropout(dropout), out))
         self.lsm = nn.LogSoftmax(dim=1)
         self.apply(self._init)

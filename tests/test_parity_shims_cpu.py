@@ -326,3 +326,43 @@ def test_plain_python_byte_level_bpe_agrees_with_the_tokenizers_library(tmp_path
         assert ids == tok.encode(text).ids, text
         assert enc.decode(ids) == text
     assert len(enc.cache) > 0
+
+
+def test_adaptive_softmax_tied_to_adaptive_input_bands():
+    from metaseq_b200.modules.adaptive_softmax import AdaptiveSoftmax, TiedHeadModule
+
+    torch.manual_seed(0)
+    V, D, cutoff = 30, 16, [10, 20]
+
+    class Bands:
+        """Embedding and projection weights of three bands, as an adaptive input layer would expose them."""
+
+        def __init__(self):
+            dims = [16, 4, 1]
+            sizes = [10, 10, 10]
+            self.emb = [torch.nn.Parameter(torch.randn(n, d)) for n, d in zip(sizes, dims)]
+            self.proj = [torch.nn.Parameter(torch.randn(D, d)) for d in dims]
+
+        def weights_for_band(self, band):
+            return self.emb[band], self.proj[band]
+
+    bands = Bands()
+    asm = AdaptiveSoftmax(V, D, cutoff, dropout=0.0, adaptive_inputs=bands, tie_proj=True)
+    assert isinstance(asm.head, TiedHeadModule) and asm.head.out_dim == 10 + 2
+    before = [w.clone() for w in bands.emb + bands.proj]
+    x = torch.randn(2, 3, D)
+    lp = asm.get_log_prob(x, None)
+    assert lp.shape == (2, 3, V) and torch.allclose(lp.exp().sum(-1), torch.ones(2, 3), atol=1e-5)
+    # word logits of the head are the first band's embeddings applied to the input; the tied tensors were not re-initialised
+    head = asm.head(x)
+    assert torch.allclose(head[:, :10], x.reshape(-1, D) @ bands.emb[0].t(), atol=1e-5)
+    assert all(torch.equal(a, b) for a, b in zip(before, bands.emb + bands.proj))
+    # the first tail: input -> projection transposed (tied) -> band-1 embeddings
+    tail = asm.tail[0](x.reshape(-1, D))
+    assert torch.allclose(tail, (x.reshape(-1, D) @ bands.proj[1]) @ bands.emb[1].t(), atol=1e-4)
+    # the loss path sees the same parameters
+    target = torch.tensor([[1, 12, 25], [3, 29, 11]])
+    logits, targets = asm(x, target)
+    loss = sum(torch.nn.functional.cross_entropy(lg, tg) for lg, tg in zip(logits, targets) if lg is not None)
+    loss.backward()
+    assert bands.emb[0].grad is not None and bands.emb[2].grad is not None and bands.proj[1].grad is not None
