@@ -92,23 +92,50 @@ def get_azure_env():
 
 
 def is_job_valid(args, save_dir, dry_run):
+    """Whether a run should be (re)submitted: not when it finished (unless ``--resume-finished``), not when its last
+    job failed (unless ``--resume-failed``), not while it is in progress."""
     if is_finished(save_dir):
         if args.resume_finished:
             dry_run(f"restart previously finished run: {save_dir}")
         else:
             print(f"skip finished run (override with --resume-finished): {save_dir}")
             return False
-    elif os.path.exists(save_dir) and has_started(save_dir, args):
+    elif has_failed(save_dir):
+        if getattr(args, "resume_failed", False):
+            dry_run(f"resume failed run: {save_dir}")
+        else:
+            print(f"skip failed run (override with --resume-failed): {save_dir}")
+            return False
+    elif has_started(save_dir, args):
         print(f"skip in progress run: {save_dir}")
         return False
     return True
 
 
-def has_started(save_dir, args):
-    train_log = os.path.join(save_dir, "train.log")
-    if not os.path.exists(train_log):
+def has_failed(save_dir) -> bool:
+    """The stderr file of the newest job (``train.stderr.<jobid>``) has any non-blank line."""
+    if not os.path.isdir(save_dir):
         return False
-    return not getattr(args, "resume_failed", False)
+    job_ids = [int(fn.rsplit(".", 1)[1]) for fn in os.listdir(save_dir)
+               if fn.startswith("train.stderr.") and fn.rsplit(".", 1)[1].isdigit()]
+    if not job_ids:
+        return False
+    with open(os.path.join(save_dir, f"train.stderr.{max(job_ids)}"), "r", errors="replace") as h:
+        return any(line.strip() for line in h)
+
+
+def has_started(save_dir, args=None) -> bool:
+    return os.path.exists(os.path.join(save_dir, "train.log"))
+
+
+def write_git_commit(train_log: str) -> None:
+    """Appends the id of the checked-out commit to the training log (nothing outside a git checkout)."""
+    try:
+        commit = subprocess.check_output(["git", "rev-parse", "HEAD"], encoding="utf-8", stderr=subprocess.DEVNULL).strip()
+    except (OSError, subprocess.CalledProcessError):
+        return
+    with open(train_log, "a") as h:
+        print(f"commit {commit}", file=h)
 
 
 def is_finished(save_dir):
@@ -120,6 +147,9 @@ def is_finished(save_dir):
     if not lines:
         return False
     return "done training" in lines[-1]
+
+
+has_finished = is_finished
 
 
 def get_save_dir_name(args, hp_values) -> str:

@@ -428,3 +428,31 @@ def test_service_launch_args_parse_and_data_may_be_positional():
     a = options.parse_args_and_arch(parser, input_args=["/corpus"] + base)
     b = options.parse_args_and_arch(options.get_training_parser(), input_args=base + ["--data", "/corpus"])
     assert a.data == b.data == "/corpus"
+
+
+def test_launcher_tells_failed_runs_from_running_ones(tmp_path):
+    from metaseq_b200.launcher import slurm, sweep
+
+    base = ["-p", "exp", "-g", "1", "--checkpoints-dir", str(tmp_path)]
+    plain, resume = sweep.get_args(input_args=base), sweep.get_args(input_args=base + ["--resume-failed"])
+    said = []
+    run = tmp_path / "run"
+    run.mkdir()
+    assert slurm.is_job_valid(plain, str(run), said.append)  # nothing there yet
+    (run / "train.log").write_text("step 1\n")
+    assert slurm.has_started(str(run)) and not slurm.has_failed(str(run))
+    assert not slurm.is_job_valid(plain, str(run), said.append)   # in progress
+    assert not slurm.is_job_valid(resume, str(run), said.append)  # --resume-failed does not touch a healthy run
+    (run / "train.stderr.7").write_text("Traceback ...\n")
+    (run / "train.stderr.9").write_text("\n  \n")
+    assert not slurm.has_failed(str(run))                         # the newest job's stderr is blank
+    (run / "train.stderr.12").write_text("RuntimeError: boom\n")
+    assert slurm.has_failed(str(run))
+    assert not slurm.is_job_valid(plain, str(run), said.append)
+    assert slurm.is_job_valid(resume, str(run), said.append) and any("resume failed run" in m for m in said)
+    (run / "train.log").write_text("step 1\ndone training in 3 s\n")
+    assert slurm.has_finished(str(run)) and not slurm.is_job_valid(resume, str(run), said.append)
+    log = tmp_path / "git.log"
+    log.write_text("")
+    slurm.write_git_commit(str(log))
+    assert log.read_text() == "" or log.read_text().startswith("commit ")
