@@ -297,3 +297,29 @@ def get(cfg_or_ns, key: str, default=None):
     if isinstance(cfg_or_ns, dict):
         return cfg_or_ns.get(key, default)
     return getattr(cfg_or_ns, key, default)
+
+
+# ------------------------------------------------------------ names of the reference's config helpers
+convert_namespace_to_omegaconf = convert_namespace_to_config  # the config tree here is a plain ``Cfg``, not OmegaConf
+
+
+def overwrite_keys_not_present(cfg, overrides: Dict[str, Any]):
+    """For two-level ``{group: {key: value}}`` overrides: adds the keys that a checkpoint's group does not have yet
+    (options introduced after it was written) and leaves existing ones alone (metaseq/dataclass/utils.py:480-491)."""
+    for group, leaves in overrides.items():
+        if group in cfg and isinstance(leaves, dict) and isinstance(cfg[group], dict):
+            for key, value in leaves.items():
+                if key not in cfg[group]:
+                    cfg[group][key] = value
+    return cfg
+
+
+def merge_with_parent(dc: MetaseqDataclass, cfg):
+    """The defaults of the component's dataclass overlaid with the values of ``cfg``; keys of ``cfg`` that the
+    dataclass does not declare are kept, so configs written by other versions still load
+    (metaseq/dataclass/utils.py:462-475)."""
+    merged = Cfg({name: getattr(dc, name) for name in dc.field_names()})
+    items = cfg.items() if isinstance(cfg, dict) else vars(cfg).items()
+    for key, value in items:
+        merged[key] = value
+    return merged

@@ -366,3 +366,20 @@ def test_adaptive_softmax_tied_to_adaptive_input_bands():
     loss = sum(torch.nn.functional.cross_entropy(lg, tg) for lg, tg in zip(logits, targets) if lg is not None)
     loss.backward()
     assert bands.emb[0].grad is not None and bands.emb[2].grad is not None and bands.proj[1].grad is not None
+
+
+def test_config_helper_names_of_the_reference():
+    from metaseq_b200.dataclass.constants import AttentionVariants, ChoiceEnum
+    from metaseq_b200.dataclass.utils import (Cfg, convert_namespace_to_config, convert_namespace_to_omegaconf,
+                                              merge_with_parent, overwrite_keys_not_present)
+    from metaseq_b200.optim.adam import MetaseqAdamConfig
+
+    assert convert_namespace_to_omegaconf is convert_namespace_to_config
+    merged = merge_with_parent(MetaseqAdamConfig(), Cfg({"adam_eps": 1e-6, "legacy_key": 3}))
+    assert merged.adam_eps == 1e-6 and merged.weight_decay == 0.0 and merged.legacy_key == 3
+    cfg = Cfg({"model": Cfg({"a": 1})})
+    overwrite_keys_not_present(cfg, {"model": {"a": 9, "b": 2}, "absent": {"x": 1}})
+    assert dict(cfg.model) == {"a": 1, "b": 2} and "absent" not in cfg
+    Choice = ChoiceEnum(["json", "none"])
+    assert Choice.json == "json" and str(Choice.none) == "none" and {Choice.json: 1}[Choice.json] == 1
+    assert [v.value for v in AttentionVariants] == ["default", "xformers_default"]
