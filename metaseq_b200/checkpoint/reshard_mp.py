@@ -70,6 +70,40 @@ def split_part(t: torch.Tensor, key: str, n: int) -> List[torch.Tensor]:
     return [t.clone() for _ in range(n)]
 
 
+def reshard_megatron_parts(model_parts, new_model_part_count: int = 1) -> List[Dict[str, torch.Tensor]]:
+    """In-memory form: ``model_parts`` (a list, or a dict keyed by part index, of unflattened state dicts of one
+    model) re-cut into ``new_model_part_count`` parts; one part is the whole model
+    (metaseq/distributed/stitch_fsdp_ckpt.py:246-351)."""
+    if isinstance(model_parts, dict):
+        model_parts = [model_parts[k] for k in sorted(model_parts)]
+    out: List[Dict[str, torch.Tensor]] = [dict() for _ in range(new_model_part_count)]
+    for key in model_parts[0]:
+        tensors = [part[key] for part in model_parts]
+        if not torch.is_tensor(tensors[0]):
+            for o in out:
+                o[key] = tensors[0]
+            continue
+        whole = merge_parts(tensors, key) if len(tensors) > 1 else tensors[0]
+        for o, piece in zip(out, split_part(whole, key, new_model_part_count)):
+            o[key] = piece
+    return out
+
+
+def get_n_layers(glued_model: Dict[str, Any]) -> int:
+    """Number of decoder layers in a state dict, counted from its ``decoder.layers.<i>.fc1.weight`` keys."""
+    n = 0
+    while f"decoder.layers.{n}.fc1.weight" in glued_model:
+        n += 1
+    assert n > 0, "found 0 layers: no key decoder.layers.0.fc1.weight"
+    return n
+
+
+def find_num_parts(names) -> int:
+    """Number of tensor-parallel parts among file names (largest ``-model_part-<i>`` + 1; 0 when none has one)."""
+    found = [int(m.group(1)) for m in (re.search(r"-model_part-(\d+)", n) for n in names) if m is not None]
+    return max(found) + 1 if found else 0
+
+
 def reshard_mp(src_dir_pattern: str, dst_dir_pattern: str, num_output_parts: int = 1, drop_optimizer_state: bool = True):
     paths = _sorted_parts(src_dir_pattern)
     assert len(paths) > 0, f"no files match {src_dir_pattern}"

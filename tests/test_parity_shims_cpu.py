@@ -383,3 +383,30 @@ def test_config_helper_names_of_the_reference():
     Choice = ChoiceEnum(["json", "none"])
     assert Choice.json == "json" and str(Choice.none) == "none" and {Choice.json: 1}[Choice.json] == 1
     assert [v.value for v in AttentionVariants] == ["default", "xformers_default"]
+
+
+def test_tensor_parallel_parts_are_recut_in_memory():
+    from metaseq_b200.checkpoint.reshard_mp import find_num_parts, get_n_layers, reshard_megatron_parts
+
+    torch.manual_seed(0)
+    D, F, V = 8, 16, 12
+    whole = {"decoder.embed_tokens.weight": torch.randn(V, D), "decoder.embed_positions.weight": torch.randn(6, D),
+             "decoder.layers.0.self_attn.qkv_proj.weight": torch.randn(3 * D, D),
+             "decoder.layers.0.self_attn.qkv_proj.bias": torch.randn(3 * D),
+             "decoder.layers.0.self_attn.out_proj.weight": torch.randn(D, D),
+             "decoder.layers.0.self_attn.out_proj.bias": torch.randn(D),
+             "decoder.layers.0.fc1.weight": torch.randn(F, D), "decoder.layers.0.fc1.bias": torch.randn(F),
+             "decoder.layers.0.fc2.weight": torch.randn(D, F), "decoder.layers.0.fc2.bias": torch.randn(D),
+             "decoder.layers.0.final_layer_norm.weight": torch.randn(D), "decoder.version": torch.tensor([3.0])}
+    four = reshard_megatron_parts([whole], 4)
+    assert four[0]["decoder.layers.0.fc1.weight"].shape == (F // 4, D)
+    assert four[0]["decoder.layers.0.fc2.weight"].shape == (D, F // 4)
+    assert four[1]["decoder.layers.0.self_attn.qkv_proj.weight"].shape == (3 * D // 4, D)
+    # part 1 of the fused projection holds rows [2:4] of each of the three blocks
+    blocks = whole["decoder.layers.0.self_attn.qkv_proj.weight"].view(3, D, D)
+    assert torch.equal(four[1]["decoder.layers.0.self_attn.qkv_proj.weight"], blocks[:, 2:4].reshape(-1, D))
+    two = reshard_megatron_parts({i: p for i, p in enumerate(four)}, 2)
+    back = reshard_megatron_parts(two, 1)[0]
+    assert back.keys() == whole.keys() and all(torch.equal(back[k], whole[k]) for k in whole)
+    assert get_n_layers(back) == 1
+    assert find_num_parts(["a-model_part-0-shard1.pt", "a-model_part-3-shard0.pt"]) == 4 and find_num_parts(["a.pt"]) == 0
