@@ -55,3 +55,60 @@ def load_and_pop_last_optimizer_state(pth):
     st = torch_load_cpu(pth)
     st.pop("last_optimizer_state", None)
     return st
+
+
+def get_cache_dir(cache_dir: Optional[str] = None) -> str:
+    """Directory for local copies of remote files: the argument, else ``$FVCORE_CACHE``, else
+    ``~/.torch/iopath_cache``; a directory under the system's temporary folder when that one cannot be written
+    (metaseq/file_io/common/__init__.py:35-59)."""
+    import tempfile
+
+    if cache_dir is None:
+        cache_dir = os.path.expanduser(os.getenv("FVCORE_CACHE", "~/.torch/iopath_cache"))
+    try:
+        os.makedirs(cache_dir, exist_ok=True)
+        if not os.access(cache_dir, os.W_OK):
+            raise OSError(f"{cache_dir} is not writable")
+    except OSError:
+        fallback = os.path.join(tempfile.gettempdir(), "iopath_cache")
+        logger.warning(f"{cache_dir} is not accessible! Using {fallback} instead!")
+        os.makedirs(fallback, exist_ok=True)
+        cache_dir = fallback
+    return cache_dir
+
+
+class file_lock:
+    """``with file_lock(path):`` holds an exclusive advisory lock on ``path + ".lock"`` so that several workers do
+    not download or build the same file at once; waiting gives up with ``TimeoutError`` after ``timeout`` seconds
+    (metaseq/file_io/common/__init__.py:62-91, which uses ``portalocker`` for the same purpose)."""
+
+    def __init__(self, path: str, timeout: float = 1800.0, poll: float = 0.05):
+        self.lock_path, self.timeout, self.poll = path + ".lock", timeout, poll
+        self._fh = None
+
+    def __enter__(self):
+        import fcntl
+        import time
+
+        os.makedirs(os.path.dirname(os.path.abspath(self.lock_path)), exist_ok=True)
+        self._fh = open(self.lock_path, "a+")
+        deadline = time.monotonic() + self.timeout
+        while True:
+            try:
+                fcntl.flock(self._fh.fileno(), fcntl.LOCK_EX | fcntl.LOCK_NB)
+                return self
+            except OSError:
+                if time.monotonic() >= deadline:
+                    self._fh.close()
+                    self._fh = None
+                    raise TimeoutError(f"could not lock {self.lock_path} within {self.timeout} s")
+                time.sleep(self.poll)
+
+    def __exit__(self, *exc):
+        import fcntl
+
+        if self._fh is not None:
+            fcntl.flock(self._fh.fileno(), fcntl.LOCK_UN)
+            self._fh.close()
+            self._fh = None
+        return False

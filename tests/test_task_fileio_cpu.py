@@ -202,3 +202,22 @@ def test_legacy_language_modeling_task_loads_an_indexed_corpus(tmp_path):
             as_docs.append(cur)
             cur = []
     assert sorted(map(tuple, as_docs)) == sorted(map(tuple, docs))
+
+
+def test_cache_dir_and_file_lock(tmp_path, monkeypatch):
+    from metaseq_b200.file_io import file_lock, get_cache_dir
+
+    monkeypatch.setenv("FVCORE_CACHE", str(tmp_path / "cache"))
+    assert get_cache_dir() == str(tmp_path / "cache") and os.path.isdir(tmp_path / "cache")
+    assert get_cache_dir(str(tmp_path / "other")) == str(tmp_path / "other")
+    blocked = tmp_path / "file"  # a file where a directory is wanted: falls back to the temporary folder
+    blocked.write_text("")
+    assert get_cache_dir(str(blocked / "sub")).endswith("iopath_cache")
+    target = str(tmp_path / "sub" / "weights.bin")
+    with file_lock(target):
+        assert os.path.exists(target + ".lock")
+        with pytest.raises(TimeoutError):
+            with file_lock(target, timeout=0.2):
+                pass
+    with file_lock(target, timeout=0.2):  # free again
+        pass
