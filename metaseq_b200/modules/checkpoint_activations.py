@@ -9,13 +9,64 @@ The decoder layer's fused path has recomputation built in (``LayerSpec.recompute
 wrapper serves the modular path and user modules."""
 from __future__ import annotations
 
+import contextlib
 import functools
+import threading
 from typing import Any, Dict, List, Optional, Tuple
 
 import torch
 import torch.nn as nn
 
 from metaseq_b200.parallel import mpu
+
+
+class _State(threading.local):
+    def __init__(self):
+        self.disabled = False      # wrappers run their module directly
+        self.checkpointing = False  # inside the no-grad first pass of a wrapped module
+        self.recomputing = False    # inside the recomputation during backward
+
+
+_state = _State()
+
+
+@contextlib.contextmanager
+def _flag(name: str, value: bool = True):
+    before = getattr(_state, name)
+    setattr(_state, name, value)
+    try:
+        yield
+    finally:
+        setattr(_state, name, before)
+
+
+def disable_checkpointing():
+    """Context in which wrapped modules keep their activations (e.g. a forward pass for evaluation or for a
+    consumer that needs no backward); reference :41-48."""
+    return _flag("disabled")
+
+
+def enable_checkpointing():
+    return _flag("checkpointing")
+
+
+def enable_recomputing():
+    return _flag("recomputing")
+
+
+def is_checkpointing_disabled() -> bool:
+    return _state.disabled
+
+
+def is_checkpointing() -> bool:
+    """True during the first (activation-dropping) pass of a wrapped module."""
+    return _state.checkpointing
+
+
+def is_recomputing() -> bool:
+    """True while backward re-runs a wrapped module: modules with side effects in ``forward`` (counters, running
+    statistics) check it to apply them once."""
+    return _state.recomputing
 
 
 def checkpoint_wrapper(module: nn.Module, offload_to_cpu: bool = False,
@@ -33,7 +84,7 @@ def _checkpointed_forward(module, offload_to_cpu, distribute, *args, **kwargs):
     others = {i: a for i, a in enumerate(flat) if not torch.is_tensor(a)}
     meta = {"n_args": len(args), "kw_keys": flat_kwargs_keys, "others": others,
             "tensor_idx": [i for i, _ in tensors], "offload": offload_to_cpu, "distribute": distribute}
-    if not torch.is_grad_enabled() or not any(t.requires_grad for _, t in tensors) and \
+    if _state.disabled or not torch.is_grad_enabled() or not any(t.requires_grad for _, t in tensors) and \
             not any(p.requires_grad for p in module.parameters()):
         return module._checkpoint_orig_forward(*args, **kwargs)
     dummy = torch.zeros(1, requires_grad=True) if not any(t.requires_grad for _, t in tensors) else None
@@ -87,7 +138,7 @@ class _CheckpointFn(torch.autograd.Function):
                 s = s.to("cpu", non_blocking=True)
             saved.append(s)
         ctx.save_for_backward(*saved)
-        with torch.no_grad():
+        with torch.no_grad(), enable_checkpointing():
             args, kwargs = _rebuild(meta, tensors)
             out = run_fn(*args, **kwargs)
         ctx.out_is_tuple = isinstance(out, tuple)
@@ -106,7 +157,7 @@ class _CheckpointFn(torch.autograd.Function):
             inputs.append(s)
         now = _rng_state()
         _set_rng_state(ctx.rng)
-        with torch.enable_grad():
+        with torch.enable_grad(), enable_recomputing():
             args, kwargs = _rebuild(ctx.meta, inputs)
             out = ctx.run_fn(*args, **kwargs)
         _set_rng_state(now)

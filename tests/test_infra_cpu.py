@@ -133,3 +133,34 @@ def test_activation_checkpointing_matches_plain_autograd_with_dropout(offload):
     plain, ckpt = run(False), run(True)
     assert plain[0] == pytest.approx(ckpt[0], rel=1e-6) and plain[1] == pytest.approx(ckpt[1], rel=1e-5)
     assert torch.allclose(plain[2], ckpt[2], atol=1e-6)
+
+
+def test_checkpointing_state_queries_and_disable_context():
+    import torch
+
+    from metaseq_b200.modules import checkpoint_activations as ca
+
+    class Probe(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.lin = torch.nn.Linear(4, 4)
+            self.seen = []
+
+        def forward(self, x):
+            self.seen.append((ca.is_checkpointing(), ca.is_recomputing()))
+            return self.lin(x).relu()
+
+    torch.manual_seed(0)
+    m = ca.checkpoint_wrapper(Probe())
+    x = torch.randn(3, 4, requires_grad=True)
+    m(x).sum().backward()
+    assert m.seen == [(True, False), (False, True)]  # dropped pass, then the recomputation
+    grad = x.grad.clone()
+    assert not ca.is_checkpointing() and not ca.is_recomputing() and not ca.is_checkpointing_disabled()
+    m.seen.clear()
+    x.grad = None
+    with ca.disable_checkpointing():
+        assert ca.is_checkpointing_disabled()
+        m(x).sum().backward()
+    assert m.seen == [(False, False)]  # one ordinary pass
+    assert torch.allclose(x.grad, grad)
