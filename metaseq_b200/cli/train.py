@@ -305,6 +305,11 @@ def post_checkpoint_callback(cfg, num_updates, training_finished, filename, file
             os.symlink(os.path.basename(filename), other)
 
 
+def add_num_updates_to_stats(trainer: Trainer, stats: Dict[str, Any]) -> Dict[str, Any]:
+    stats["num_updates"] = trainer.get_num_updates()
+    return stats
+
+
 def _run_nfs_eval(cfg, checkpoint_dir):
     for attempt in range(max(1, cfg.checkpoint.nfs_eval_num_attempts)):
         n_files = len([f for f in os.listdir(checkpoint_dir) if f.endswith(".pt")])

@@ -32,6 +32,27 @@ def nll_loss_sum(logits, target, ignore_index):
     return TF.nll_loss(lprobs, target, ignore_index=ignore_index, reduction="sum")
 
 
+_GATHER_ABOVE = 2e9  # elements
+
+
+def nll_loss(lprobs, target, ignore_index=None, reduction: str = "mean"):
+    """NLL from log-probabilities.  ``torch.nn.functional.nll_loss`` below 2e9 elements; above that (where its
+    index arithmetic overflows) a gather, with ignored targets contributing zero
+    (metaseq/criterions/cross_entropy.py:15-37)."""
+    if reduction not in ("mean", "sum", "none"):
+        raise NotImplementedError(reduction)
+    if lprobs.numel() < _GATHER_ABOVE:
+        kw = {} if ignore_index is None else {"ignore_index": ignore_index}
+        return TF.nll_loss(lprobs, target, reduction=reduction, **kw)
+    index = target.unsqueeze(-1) if target.dim() == lprobs.dim() - 1 else target
+    picked = -lprobs.gather(dim=-1, index=index).squeeze(-1)
+    if ignore_index is not None:
+        picked = picked.masked_fill(index.squeeze(-1).eq(ignore_index), 0.0)
+    if reduction == "mean":
+        return picked.mean()
+    return picked.sum() if reduction == "sum" else picked
+
+
 @register_criterion("cross_entropy", dataclass=CrossEntropyCriterionConfig)
 class CrossEntropyCriterion(BaseCriterion):
     def __init__(self, task):

@@ -116,3 +116,13 @@ class BaseOptimizer:
         if hasattr(self.optimizer, "broadcast_global_state_dict"):
             return self.optimizer.broadcast_global_state_dict(state_dict)
         return state_dict
+
+
+
+class LegacyOptimizer(BaseOptimizer):
+    """Base for optimizers configured by an argparse namespace instead of a dataclass
+    (metaseq/optim/base_optimizer.py:179-181)."""
+
+    def __init__(self, args):
+        super().__init__(args)
+        self.args = args

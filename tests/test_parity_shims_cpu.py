@@ -410,3 +410,21 @@ def test_tensor_parallel_parts_are_recut_in_memory():
     assert back.keys() == whole.keys() and all(torch.equal(back[k], whole[k]) for k in whole)
     assert get_n_layers(back) == 1
     assert find_num_parts(["a-model_part-0-shard1.pt", "a-model_part-3-shard0.pt"]) == 4 and find_num_parts(["a.pt"]) == 0
+
+
+def test_nll_loss_gather_branch_matches_torch(monkeypatch):
+    from metaseq_b200.criterions import cross_entropy as ce
+
+    torch.manual_seed(0)
+    lp = torch.log_softmax(torch.randn(6, 7), -1)
+    tgt = torch.tensor([1, 2, 1, 0, 3, 6])
+    want = {r: torch.nn.functional.nll_loss(lp, tgt, ignore_index=1, reduction=r) for r in ("mean", "sum", "none")}
+    assert torch.allclose(ce.nll_loss(lp, tgt, ignore_index=1, reduction="sum"), want["sum"])
+    monkeypatch.setattr(ce, "_GATHER_ABOVE", 0)  # force the path meant for inputs beyond 2e9 elements
+    assert torch.allclose(ce.nll_loss(lp, tgt, ignore_index=1, reduction="sum"), want["sum"])
+    assert torch.allclose(ce.nll_loss(lp, tgt, ignore_index=1, reduction="none"), want["none"])
+    # "mean" on that path averages over all rows, as the reference's does
+    assert torch.allclose(ce.nll_loss(lp, tgt, ignore_index=1, reduction="mean"), want["sum"] / 6)
+    assert torch.allclose(ce.nll_loss(lp, tgt, reduction="mean"), torch.nn.functional.nll_loss(lp, tgt))
+    with pytest.raises(NotImplementedError):
+        ce.nll_loss(lp, tgt, reduction="bogus")
