@@ -119,3 +119,34 @@ class PlasmaView:
 
     def __len__(self):
         return len(self.array)
+
+
+class PlasmaStore:
+    """Owner of the shared segments of a job.  The reference starts a ``plasma_store`` server process here
+    (metaseq/data/plasma_utils.py:182-196); shared memory needs no server, so this object only remembers the
+    segments registered with it and unlinks them in ``close()`` (or when it is collected)."""
+
+    def __init__(self, path: str = "/tmp/plasma", nbytes: int = 0):
+        self.path, self.nbytes = path, nbytes
+        self._segments = []
+        self.server = None  # no process to manage
+
+    @staticmethod
+    def start(path: str = "/tmp/plasma", nbytes: int = 0) -> None:
+        return None
+
+    def register(self, segment: shared_memory.SharedMemory) -> shared_memory.SharedMemory:
+        self._segments.append(segment)
+        return segment
+
+    def close(self) -> None:
+        for seg in self._segments:
+            try:
+                seg.close()
+                seg.unlink()
+            except FileNotFoundError:
+                pass
+        self._segments = []
+
+    def __del__(self):
+        self.close()

@@ -428,3 +428,17 @@ def test_nll_loss_gather_branch_matches_torch(monkeypatch):
     assert torch.allclose(ce.nll_loss(lp, tgt, reduction="mean"), torch.nn.functional.nll_loss(lp, tgt))
     with pytest.raises(NotImplementedError):
         ce.nll_loss(lp, tgt, reduction="bogus")
+
+
+def test_plasma_store_owns_and_unlinks_shared_segments():
+    from multiprocessing import shared_memory
+
+    from metaseq_b200.data.plasma_utils import PlasmaStore
+
+    store = PlasmaStore()
+    seg = store.register(shared_memory.SharedMemory(create=True, size=64))
+    name = seg.name
+    store.close()
+    with pytest.raises(FileNotFoundError):
+        shared_memory.SharedMemory(name=name)
+    store.close()  # idempotent
