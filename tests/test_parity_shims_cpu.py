@@ -21,6 +21,16 @@ def test_file_chunker_splits_a_file_on_line_boundaries(tmp_path):
         with Chunker(str(path), a, b) as it:
             seen += [ln.rstrip("\n") for ln in it]
     assert seen == lines
+    # multi-byte text: a seek may land inside a character, the chunks still meet on line starts
+    wide = tmp_path / "wide.txt"
+    rows = ["naïve café ✓ " * (1 + i % 5) + str(i) for i in range(120)]
+    wide.write_text("\n".join(rows) + "\n", encoding="utf-8")
+    cuts = find_offsets(str(wide), 7)
+    got = []
+    for a, b in zip(cuts[:-1], cuts[1:]):
+        with Chunker(str(wide), a, b) as it:
+            got += [ln.rstrip("\n") for ln in it]
+    assert got == rows
 
 
 def test_file_utils_resolves_local_paths_and_names_cache_entries(tmp_path):
