@@ -24,22 +24,35 @@ class Size:
 TOTAL_TRAIN_TOKENS = 300e9
 TOTAL_WARMUP_TOKENS = 375e6
 M = 1024 * 1024
-MODEL_SIZES = {
-    "8m_mp1": Size(4, 128, 2, 64, int(0.125 * M), 1.0e-3, 1),
-    "8m": Size(4, 128, 2, 64, int(0.125 * M), 1.0e-3, 2),
-    "125m": Size(12, 768, 12, 64, int(0.5 * M), 6.0e-4, 2),
-    "350m": Size(24, 1024, 16, 64, int(0.5 * M), 3.0e-4, 2),
-    "760m": Size(24, 1536, 16, 96, int(0.5 * M), 2.5e-4, 2),
-    "1.3b": Size(24, 2048, 32, 64, int(1.0 * M), 2.0e-4, 2),
-    "2.7b": Size(32, 2560, 32, 80, int(1.0 * M), 1.6e-4, 4),
-    "6.7b": Size(32, 4096, 32, 128, int(2.0 * M), 1.2e-4, 2),
-    "13b": Size(40, 5120, 40, 128, int(4.0 * M), 1.0e-4, 2),
-    "30b": Size(48, 7168, 56, 128, int(4.0 * M), 1.0e-4, 2),
-    "66b": Size(64, 9216, 72, 128, int(2.0 * M), 8e-5, 8),
-    "175b": Size(96, 12288, 96, 128, int(2.0 * M), 3e-5, 8),
-}
-for _name, _size in MODEL_SIZES.items():
-    assert _size.n_heads * _size.d_head == _size.emb_size, _name
+
+# name  layers  width  heads  head-dim  batch (Mi tokens per update)  peak lr  tensor-parallel parts
+_TABLE = """
+8m_mp1     4    128   2   64  0.125  1.0e-3  1
+8m         4    128   2   64  0.125  1.0e-3  2
+125m      12    768  12   64  0.5    6.0e-4  2
+350m      24   1024  16   64  0.5    3.0e-4  2
+760m      24   1536  16   96  0.5    2.5e-4  2
+1.3b      24   2048  32   64  1.0    2.0e-4  2
+2.7b      32   2560  32   80  1.0    1.6e-4  4
+6.7b      32   4096  32  128  2.0    1.2e-4  2
+13b       40   5120  40  128  4.0    1.0e-4  2
+30b       48   7168  56  128  4.0    1.0e-4  2
+66b       64   9216  72  128  2.0    8e-5    8
+175b      96  12288  96  128  2.0    3e-5    8
+"""
+
+
+def _parse(table: str):
+    sizes = {}
+    for row in table.strip().splitlines():
+        name, layers, width, heads, d_head, batch_mi, lr, parts = row.split()
+        size = Size(int(layers), int(width), int(heads), int(d_head), int(float(batch_mi) * M), float(lr), int(parts))
+        assert size.n_heads * size.d_head == size.emb_size, name
+        sizes[name] = size
+    return sizes
+
+
+MODEL_SIZES = _parse(_TABLE)
 
 
 class ComputeEnvs(Enum):
