@@ -115,7 +115,11 @@ def save_checkpoint(cfg, trainer, epoch_itr, training_finished=False, async_call
     save_for_updates = not end_of_epoch and (save_to_nfs or save_locally)
     conds[f"checkpoint{epoch}{suffix}.pt"] = save_for_epoch
     conds[f"checkpoint_{updates}{suffix}.pt"] = save_for_updates
-    conds[f"checkpoint_last{suffix}.pt"] = (training_finished or save_for_epoch) and ckpt.save_last_checkpoint
+    # every save re-points ``checkpoint_last`` (a mid-epoch one too: a restart resumes from the newest state, not
+    # from the last epoch boundary); at the end of training it is written only when asked for
+    # (metaseq/checkpoint_utils.py:77-81)
+    conds[f"checkpoint_last{suffix}.pt"] = (training_finished and ckpt.save_last_checkpoint) or save_for_epoch \
+        or save_for_updates
     extra_state = {"train_iterator": epoch_itr.state_dict()}
     names = [os.path.join(ckpt.save_dir, fn) for fn, cond in conds.items() if cond]
     if len(names) > 0:

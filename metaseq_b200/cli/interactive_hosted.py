@@ -70,7 +70,6 @@ def batching_loop(timeout=100, max_tokens=None, stop_event=None):
     target_queue = None
     while stop_event is None or not stop_event.is_set():
         try:
-            assert len(BATCH_QUEUE.shards) == 1 or True
             shard = BATCH_QUEUE.largest_shard()
             timeout_s = timeout / 1000 if batch_dict else 0.2
             if target_queue is None:

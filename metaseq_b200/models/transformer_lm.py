@@ -78,7 +78,6 @@ class ModelParallelTransformerLanguageModel(LanguageModel):
         task.source_dictionary.pad_to_multiple_(8 * tp)
         task.target_dictionary.pad_to_multiple_(8 * tp)
         if getattr(args, "sequence_parallel", False):
-            assert tp > 1 or getattr(args, "model_parallel_size", 1) > 1 or True
             assert getattr(args, "dropout", 0.0) == 0.0 and getattr(args, "attention_dropout", 0.0) == 0.0, \
                 "sequence parallel requires dropout 0"
             assert args.activation_fn in ("relu", "gelu"), "sequence parallel supports relu / gelu"

@@ -39,6 +39,13 @@ def _build_scaler(cfg, bf16: bool):
                              threshold=c.threshold_loss_scale, min_loss_scale=c.min_loss_scale)
 
 
+def _reject_batch(grad_norm: float, max_norm: float):
+    """``--skip-gradient-update-on-clip-norm``: a gradient norm above the threshold rejects the whole batch.  The
+    trainer treats the exception like a loss-scale overflow: gradients are dropped and neither the update count,
+    the learning-rate schedule nor the optimizer state advances (metaseq/optim/fp16_optimizer.py:186-194)."""
+    raise OverflowError(f"Grad norm: {grad_norm:.2f} exceeds threshold: {max_norm:.2f}, rejecting batch.")
+
+
 class _ScaledMixin:
     """Loss scaling + lazy gradient multiplier shared by both wrappers."""
 
@@ -153,17 +160,14 @@ class MemoryEfficientFP16Optimizer(_ScaledMixin, BaseOptimizer):
             gn = None
         if max_norm is not None and max_norm > 0:
             gn = float(grad_norm) if gn is None else gn
-            clip_coef = min(1.0, max_norm / (gn + 1e-6))
-            if skip_gradient_update_on_clip_norm and gn > max_norm:
-                self._multiply_factor = 0.0
-            else:
-                self._multiply_factor *= clip_coef
+            if skip_gradient_update_on_clip_norm and self.scaler is not None and gn > max_norm:
+                _reject_batch(gn, max_norm)
+            self._multiply_factor *= min(1.0, max_norm / (gn + 1e-6))
         return grad_norm
 
     def step(self, closure=None, groups=None):
         if getattr(self, "supports_step_with_scale", False):
-            self.wrapped_optimizer.step(closure, scale=(1.0 / self._multiply_factor) if self._multiply_factor != 0
-                                        else float("inf"))
+            self.wrapped_optimizer.step(closure, scale=1.0 / self._multiply_factor)
         else:
             self._unscale_grads()
             self.wrapped_optimizer.step(closure)
@@ -341,10 +345,9 @@ class FP16Optimizer(_ScaledMixin, BaseOptimizer):
             self.scaler.check_overflow(float(grad_norm))
         if max_norm is not None and max_norm > 0:
             gn = float(grad_norm)
-            if skip_gradient_update_on_clip_norm and gn > max_norm:
-                self._multiply_factor = 0.0
-            else:
-                self._multiply_factor *= min(1.0, max_norm / (gn + 1e-6))
+            if skip_gradient_update_on_clip_norm and self.scaler is not None and gn > max_norm:
+                _reject_batch(gn, max_norm)
+            self._multiply_factor *= min(1.0, max_norm / (gn + 1e-6))
         return grad_norm
 
     def step(self, closure=None, groups=None):

@@ -521,6 +521,12 @@ class FullyShardedDataParallel(nn.Module):
                 else:
                     shard = shard.to(self.flat_param.dtype)
             self._accumulate_shard_grad(shard, owns_buffer=False)
+        if self.world_size > 1:
+            # the reduced slice now lives in ``flat_param.grad``; the next micro-batch of the same update
+            # (``--update-freq`` > 1) must overwrite the flat buffer, not add to what was already reduced
+            for v in self._views:
+                if hasattr(v, "_grad_filled"):
+                    v._grad_filled = False
         if self.reshard_after_forward:
             self._free_full()
 
@@ -766,8 +772,6 @@ def fsdp_enable_wrap(cfg_dist, use_sharded_state: bool = False, **kwargs):
     if getattr(cfg_dist, "ddp_backend", None) != "fully_sharded":
         yield
         return
-    if getattr(cfg_dist, "memory_efficient_fp16", False):
-        assert getattr(cfg_dist, "fp16", False) or getattr(cfg_dist, "bf16", False) or True
     group = kwargs.pop("process_group", None)
     if os.environ.get("RESHARD_OVERRIDE_PROCESS_GROUP", "False") == "True":
         group = DummyProcessGroup(rank=0, size=1)

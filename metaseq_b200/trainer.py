@@ -213,8 +213,6 @@ class Trainer:
                 self._optimizer = optim.FP16Optimizer.build_optimizer(self.cfg, params)
         else:
             self._optimizer = optim.build_optimizer(self.cfg.optimizer, params)
-        if self.is_fsdp:
-            assert self._optimizer.supports_flat_params or True
         self._lr_scheduler = lr_scheduler.build_lr_scheduler(self.cfg.lr_scheduler, self.optimizer)
         self._lr_scheduler.step_update(0)
 
@@ -414,7 +412,6 @@ class Trainer:
         self._dummy_batch = batch
 
     # ------------------------------------------------------------- train step
-    @metrics.aggregate("train")
     def start_watchdog(self):
         """Host watchdog over the training loop (``--watchdog-timeout``); returns it, or ``None`` when disabled."""
         timeout = float(getattr(self.cfg.common, "watchdog_timeout", 0.0) or 0.0)
@@ -429,6 +426,7 @@ class Trainer:
         self.watchdog = StepWatchdog(timeout, status_fn=status_fn).start()
         return self.watchdog
 
+    @metrics.aggregate("train")
     def train_step(self, samples, raise_oom=False):
         """One optimizer update over ``samples`` (a list of micro-batches)."""
         if getattr(self, "watchdog", None) is not None:
@@ -495,9 +493,12 @@ class Trainer:
             loss_now = sum(float(log.get("loss", 0)) for log in logging_outputs) / max(float(sample_size), 1.0) \
                 / math.log(2)
             ratio = self.skip_spike(loss_now, self.cfg.optimization.ewm_ratio_to_skip_batch)
-            if ratio is not None:
-                logger.info(f"skip spike: loss {loss_now:.3f} is {ratio:.2f}x its running mean; shrinking lr")
-                self.optimizer.set_lr(self.optimizer.get_lr() / (ratio ** 4))
+            if ratio > 1.0 and self._spike_guard_on(self.cfg.optimization.ewm_ratio_to_skip_batch):
+                # a loss above its running mean damps this update by ratio^-4 (the schedule restores the rate at
+                # the next update)
+                new_lr = self.optimizer.get_lr() / (ratio ** 4)
+                self.optimizer.set_lr(new_lr)
+                logger.info(f"Scaling LR by {1.0 / ratio ** 4:.2f} to {new_lr:.6f}")
             self.task.optimizer_step(self.optimizer, model=self.model, update_num=self.get_num_updates())
             if self.is_fsdp:
                 self.model.after_optimizer_step()
@@ -636,24 +637,28 @@ class Trainer:
             out = out ** 0.5
         return out
 
-    def skip_spike(self, loss_now: float, ewm_ratio_to_skip_batch: float) -> Optional[float]:
-        """Updates the exponentially weighted mean of the loss; returns the ratio when the current
-        loss exceeds ``ewm_ratio_to_skip_batch`` times the mean (and the feature is enabled)."""
-        span = 9
-        alpha = 2.0 / (1 + span)
+    @staticmethod
+    def _spike_guard_on(threshold) -> bool:
+        return threshold is not None and threshold > 0
+
+    def skip_spike(self, loss_now: float, ewm_ratio_to_skip_batch: float, span: int = 9) -> float:
+        """Ratio of the current loss (base 2) to its exponentially weighted mean, returned every step.  With the
+        guard on (a positive threshold) a loss above ``threshold x mean`` counts as a spike and leaves the mean
+        untouched, so one bad batch does not raise the baseline it is compared with
+        (metaseq/trainer.py:1115-1141); with the guard off the mean follows every step and is only logged."""
         if self._ewm_loss is None or not math.isfinite(self._ewm_loss):
             self._ewm_loss = loss_now
-            ratio = 1.0
-        else:
-            ratio = loss_now / self._ewm_loss if self._ewm_loss > 0 else 1.0
-            self._ewm_loss = (1 - alpha) * self._ewm_loss + alpha * loss_now
-        metrics.log_scalar("ewm_loss", self._ewm_loss, priority=700, round=2, weight=0)
-        metrics.log_scalar("ewm_loss_ratio", ratio, priority=710, round=4, weight=0)
-        if ewm_ratio_to_skip_batch is not None and ewm_ratio_to_skip_batch > 0 and ratio > ewm_ratio_to_skip_batch:
+        mean = self._ewm_loss
+        ratio = loss_now / mean if mean > 0 else 1.0
+        if self._spike_guard_on(ewm_ratio_to_skip_batch) and ratio > ewm_ratio_to_skip_batch:
             self._skipped_loss_spikes += 1
             metrics.log_scalar("skipped_loss_spikes", self._skipped_loss_spikes, priority=720, round=0, weight=0)
-            return ratio
-        return None
+        else:
+            alpha = 2.0 / (span + 1)
+            self._ewm_loss = (1 - alpha) * mean + alpha * loss_now
+        metrics.log_scalar("ewm_loss", self._ewm_loss, priority=700, round=2, weight=0)
+        metrics.log_scalar("ewm_loss_ratio", ratio, priority=710, round=4, weight=0)
+        return ratio
 
     def cumulative_training_time(self):
         if self._cumulative_training_time is None:

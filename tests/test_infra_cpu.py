@@ -65,6 +65,49 @@ def test_checkpoint_callback_without_upload_recreates_symlinks(tmp_path):
     assert os.path.islink(last) and os.readlink(last) == "checkpoint_6.pt" and last.read_bytes() == b"w"
 
 
+def test_checkpoint_last_follows_mid_epoch_saves_after_an_epoch_boundary(tmp_path):
+    """An end-of-epoch save, then a mid-epoch save: ``checkpoint_last`` must point at the newer state, so that a
+    restart does not fall back to the epoch boundary."""
+    from metaseq_b200 import checkpoint_utils
+
+    written = []
+
+    class FakeTrainer:
+        data_parallel_rank = 0
+        should_save_checkpoint_on_current_rank = True
+        checkpoint_suffix = ""
+        updates = 0
+
+        def consolidate_optimizer(self):
+            pass
+
+        def get_num_updates(self):
+            return self.updates
+
+        def save_checkpoint(self, filename, extra_state, training_finished=False, async_callback_fn=None,
+                            files_to_symlink_to=None):
+            written.append((os.path.basename(filename), [os.path.basename(f) for f in files_to_symlink_to or []]))
+
+    def itr(epoch, end):
+        return types.SimpleNamespace(epoch=epoch, end_of_epoch=lambda: end, state_dict=lambda: {"epoch": epoch})
+
+    ck = types.SimpleNamespace(save_dir=str(tmp_path), save_interval_epochs=1, save_interval_updates=5,
+                               local_save_interval_updates=0, save_last_checkpoint=True, keep_last_updates=-1,
+                               keep_last_epochs=-1)
+    tr = FakeTrainer()
+    tr.updates = 7
+    checkpoint_utils.save_checkpoint(ck, tr, itr(1, True))
+    tr.updates = 10
+    checkpoint_utils.save_checkpoint(ck, tr, itr(2, False))
+    tr.updates = 11
+    checkpoint_utils.save_checkpoint(ck, tr, itr(2, False))  # not a multiple of the interval: nothing is written
+    assert written == [("checkpoint1.pt", ["checkpoint_last.pt"]), ("checkpoint_10.pt", ["checkpoint_last.pt"])]
+    ck.save_last_checkpoint = False
+    tr.updates = 12
+    checkpoint_utils.save_checkpoint(ck, tr, itr(2, False), training_finished=True)
+    assert len(written) == 2
+
+
 # --------------------------------------------------------------- object collectives
 def _collective_rank(rank, world, port, out):
     import torch.distributed as dist
@@ -164,3 +207,20 @@ def test_checkpointing_state_queries_and_disable_context():
         m(x).sum().backward()
     assert m.seen == [(False, False)]  # one ordinary pass
     assert torch.allclose(x.grad, grad)
+
+
+def test_loss_spike_guard_keeps_spikes_out_of_the_running_mean():
+    """With a threshold, a spike returns its ratio and leaves the mean alone; ordinary steps move the mean by
+    alpha = 0.2; without a threshold the mean follows every step."""
+    from metaseq_b200.trainer import Trainer
+
+    t = types.SimpleNamespace(_ewm_loss=None, _skipped_loss_spikes=0, _spike_guard_on=Trainer._spike_guard_on)
+    assert Trainer.skip_spike(t, 10.0, 1.5) == 1.0 and t._ewm_loss == 10.0
+    assert Trainer.skip_spike(t, 11.0, 1.5) == pytest.approx(1.1)
+    assert t._ewm_loss == pytest.approx(10.2)
+    assert Trainer.skip_spike(t, 30.0, 1.5) == pytest.approx(30.0 / 10.2)
+    assert t._ewm_loss == pytest.approx(10.2) and t._skipped_loss_spikes == 1
+    off = types.SimpleNamespace(_ewm_loss=None, _skipped_loss_spikes=0, _spike_guard_on=Trainer._spike_guard_on)
+    Trainer.skip_spike(off, 10.0, -1)
+    Trainer.skip_spike(off, 30.0, -1)
+    assert off._ewm_loss == pytest.approx(14.0) and off._skipped_loss_spikes == 0

@@ -58,6 +58,26 @@ def test_fp16_optimizer_exact_update_and_scale_growth(cls):
         assert torch.allclose(flat, torch.tensor([3.1, 5.1]), atol=1e-6)
 
 
+@pytest.mark.parametrize("cls", [MemoryEfficientFP16Optimizer, FP16Optimizer])
+def test_skip_gradient_update_on_clip_norm_rejects_the_batch(cls):
+    """A norm above the threshold raises OverflowError (the trainer then skips the update); weights, moments and the
+    loss scale stay as they were; a norm below the threshold goes through."""
+    model, x, target = _problem(torch.float16)
+    opt = cls.build_optimizer(_cfg(), list(model.parameters()))
+    opt.zero_grad()
+    opt.backward(torch.nn.L1Loss()(model(x), target))
+    before = (model.weight.item(), model.bias.item(), opt.scaler.loss_scale)
+    with pytest.raises(OverflowError, match="rejecting batch"):
+        opt.clip_grad_norm(1.0, skip_gradient_update_on_clip_norm=True)  # the norm is 2.236
+    assert (model.weight.item(), model.bias.item(), opt.scaler.loss_scale) == before
+    opt.zero_grad()
+    opt.backward(torch.nn.L1Loss()(model(x), target))
+    gn = opt.clip_grad_norm(5.0, skip_gradient_update_on_clip_norm=True)
+    assert abs(float(gn) - 2.2361) < 1e-4
+    opt.step()
+    assert model.weight.item() == pytest.approx(3.0996, abs=1e-4)
+
+
 def test_bf16_has_no_loss_scaler():
     model, x, target = _problem(torch.bfloat16)
     opt = MemoryEfficientFP16Optimizer.build_optimizer(_cfg(bf16=True), list(model.parameters()))

@@ -56,6 +56,16 @@ def test_two_data_parallel_ranks_match_one_rank(runs):
     assert runs["dp1"][6][0] < runs["dp1"][1][0]
 
 
+def test_gradient_accumulation_over_two_ranks_matches_one_rank(tmp_path):
+    """``--update-freq 2``: each micro-batch's reduced gradient is added once.  Every rank draws the same synthetic
+    batches, so loss and gradient norm agree between one rank and two."""
+    one, _ = run_train(tmp_path / "one", 1, 3, ["--update-freq", "2"])
+    two, _ = run_train(tmp_path / "two", 2, 3, ["--update-freq", "2"])
+    for step in range(1, 4):
+        assert two[step][0] == pytest.approx(one[step][0], abs=2e-3)
+        assert two[step][1] == pytest.approx(one[step][1], rel=2e-2)
+
+
 def test_checkpoint_files_follow_the_sharded_naming_scheme(runs):
     names = sorted(os.path.basename(p) for p in glob.glob(str(runs["root"] / "dp2" / "*.pt")))
     assert names == ["checkpoint_3-model_part-0-shard0.pt", "checkpoint_3-model_part-0-shard1.pt",
