@@ -68,6 +68,43 @@ def timed(fn, warmup, repeats):
     return float(np.median(samples))
 
 
+def measure(arch: str, batch: int, prompt: int, gen: int, warmup: int = 2, repeats: int = 3, tp: int = 1,
+            top_p: float = -1.0, decode_graph: bool = True, kernel_backend: str = "auto") -> dict:
+    """Builds the random-init model (this rank's slice under tensor parallelism; the process group and the
+    model-parallel groups must exist already) and times whole ``generate`` calls.  Returns the record that
+    ``main`` prints; under tensor parallelism the times are the slowest rank's."""
+    cfg, task, model = build(arch, prompt + gen + 8, tp)
+    rng = np.random.RandomState(0)
+    prompts = torch.from_numpy(rng.randint(100, 50000, size=(batch, prompt))).cuda()
+    sample = {"net_input": {"src_tokens": prompts}}
+
+    def call(n_new):
+        total = prompt + n_new
+        sg = SequenceGenerator([model], task.target_dictionary, beam_size=1, max_len_b=total, min_len=total,
+                               temperature=1.0, topp=top_p, decode_graph=decode_graph)
+        with torch.no_grad():
+            return sg.generate([model], sample)
+
+    _lib.reset_launch_count()
+    t1 = timed(lambda: call(1), warmup, repeats)
+    tn = timed(lambda: call(gen), 1, repeats)
+    if tp > 1:
+        import torch.distributed as dist
+
+        worst = torch.tensor([t1, tn], device="cuda")
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)  # the slowest rank's device time
+        t1, tn = worst.tolist()
+    per_tok = (tn - t1) / max(1, gen - 1)
+    out = dict(metric="decode_ms_per_token", arch=arch, batch=batch, prompt_len=prompt, gen_len=gen,
+               prefill_ms=round(t1, 2), total_ms=round(tn, 2), decode_ms_per_token=round(per_tok, 3),
+               decode_tokens_per_s=round(batch / per_tok * 1e3, 1), kernel_backend=kernel_backend,
+               kernel_launches=_lib.launch_count(), kernel_status=_lib.check_status(torch.device("cuda")),
+               tensor_parallel=tp, decode_graph=decode_graph, top_p=top_p,
+               dtype="fp16", data="synthetic uniform token ids, random-init weights")
+    del model
+    return out
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--arch", default="opt_1_3b")
@@ -86,21 +123,12 @@ def main(argv=None):
     F.set_backend(args.kernel_backend)
     tp = init_tensor_parallel()
     rank0 = int(os.environ.get("RANK", "0")) == 0
-    cfg, task, model = build(args.arch, args.prompt + args.gen + 8, tp)
-    rng = np.random.RandomState(0)
-    prompts = torch.from_numpy(rng.randint(100, 50000, size=(args.batch, args.prompt))).cuda()
-    sample = {"net_input": {"src_tokens": prompts}}
-
-    def call(n_new):
-        total = args.prompt + n_new
-        sg = SequenceGenerator([model], task.target_dictionary, beam_size=1, max_len_b=total, min_len=total,
-                               temperature=1.0, topp=args.top_p, decode_graph=not args.no_decode_graph)
-        with torch.no_grad():
-            return sg.generate([model], sample)
-
     if args.graph_replays > 0:
         from metaseq_b200.models.decode_step import GraphedDecodeStep
 
+        cfg, task, model = build(args.arch, args.prompt + args.gen + 8, tp)
+        rng = np.random.RandomState(0)
+        prompts = torch.from_numpy(rng.randint(100, 50000, size=(args.batch, args.prompt))).cuda()
         assert GraphedDecodeStep.supported(model.decoder, args.batch), "the graphed step needs the kernel backend"
         runner = GraphedDecodeStep.for_decoder(model.decoder, args.batch, args.prompt + 2 * args.graph_replays + 8)
         with torch.no_grad():
@@ -129,25 +157,8 @@ def main(argv=None):
                                   ms_graph_only=round(s2.elapsed_time(e2) / args.graph_replays, 4),
                                   kernel_status=_lib.check_status(torch.device("cuda")))), flush=True)
         return
-    _lib.reset_launch_count()
-    t1 = timed(lambda: call(1), args.warmup, args.repeats)
-    tn = timed(lambda: call(args.gen), 1, args.repeats)
-    per_tok = (tn - t1) / max(1, args.gen - 1)
-    out = dict(metric="decode_ms_per_token", arch=args.arch, batch=args.batch, prompt_len=args.prompt, gen_len=args.gen,
-               prefill_ms=round(t1, 2), total_ms=round(tn, 2), decode_ms_per_token=round(per_tok, 3),
-               decode_tokens_per_s=round(args.batch / per_tok * 1e3, 1), kernel_backend=args.kernel_backend,
-               kernel_launches=_lib.launch_count(), kernel_status=_lib.check_status(torch.device("cuda")),
-               tensor_parallel=tp, decode_graph=not args.no_decode_graph, top_p=args.top_p,
-               dtype="fp16", data="synthetic uniform token ids, random-init weights")
-    if tp > 1:
-        import torch.distributed as dist
-
-        worst = torch.tensor([t1, tn], device="cuda")
-        dist.all_reduce(worst, op=dist.ReduceOp.MAX)  # the slowest rank's device time
-        t1, tn = worst.tolist()
-        per_tok = (tn - t1) / max(1, args.gen - 1)
-        out.update(prefill_ms=round(t1, 2), total_ms=round(tn, 2), decode_ms_per_token=round(per_tok, 3),
-                   decode_tokens_per_s=round(args.batch / per_tok * 1e3, 1))
+    out = measure(args.arch, args.batch, args.prompt, args.gen, args.warmup, args.repeats, tp, args.top_p,
+                  not args.no_decode_graph, args.kernel_backend)
     if rank0:
         print(json.dumps(out), flush=True)
     if tp > 1:

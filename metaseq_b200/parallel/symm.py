@@ -729,6 +729,12 @@ def comm_backend() -> str:
     return _COMM_BACKEND
 
 
+def drop_tp_comms():
+    """Forgets the cached tensor-parallel communicators (their symmetric memory is released with them).  For
+    programs that build several models with different process groups one after the other."""
+    _TP_COMMS.clear()
+
+
 def get_tp_comm(group, device, rows: int, cols: int, dtype) -> Optional[TPComm]:
     """The shared ``TPComm`` of a tensor-parallel group, created at first use and sized for ``rows x cols``
     activations (``None`` when the fused backend is off, on CPU, or for a group of one)."""

@@ -84,34 +84,29 @@ class DummyLMTask(BaseTask):
 
 
 class DummyDataset(BaseDataset):
-    def __init__(self, batch, num_items, item_size):
-        super().__init__()
-        self.batch = batch
-        self.num_items = num_items
-        self.item_size = item_size
+    """``num_items`` items of ``item_size`` tokens each; whatever indices a batch is made of, collating them yields
+    the one prepared ``batch``."""
 
-    def __getitem__(self, index):
-        return index
+    supports_prefetch = False
+
+    def __init__(self, batch, num_items: int, item_size: int):
+        super().__init__()
+        self.batch, self.num_items, self.item_size = batch, int(num_items), int(item_size)
+        self.sizes = np.full(self.num_items, self.item_size, dtype=np.int64)
 
     def __len__(self):
         return self.num_items
 
+    def __getitem__(self, index):
+        return index
+
     def collater(self, samples):
         return self.batch
-
-    @property
-    def sizes(self):
-        return np.array([self.item_size] * self.num_items)
 
     def num_tokens(self, index):
         return self.item_size
 
-    def size(self, index):
-        return self.item_size
+    size = num_tokens
 
     def ordered_indices(self):
         return np.arange(self.num_items)
-
-    @property
-    def supports_prefetch(self):
-        return False

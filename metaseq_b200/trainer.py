@@ -179,11 +179,28 @@ class Trainer:
         return self._ema
 
     def _build_ema(self):
-        if getattr(self.cfg.ema, "store_ema", False):
-            from metaseq_b200.models.ema import build_ema
+        if not getattr(self.cfg.ema, "store_ema", False):
+            return
+        from metaseq_b200.models.ema import build_ema
 
-            self._ema = build_ema(self._model, self.cfg.ema, self.device)
-            logger.info("Exponential Moving Average Shadow Model is initialized.")
+        self._ema = build_ema(self._sharded_twin() if self.is_fsdp else self._model, self.cfg.ema, self.device)
+        logger.info("Exponential Moving Average Shadow Model is initialized.")
+
+    def _sharded_twin(self):
+        """A second fully sharded instance of the model holding the same state as the trained one (a sharded
+        model cannot be deep-copied: its units share process groups and gathered buffers).  The shadow needs no
+        gathered copies, so it uses the library collectives (metaseq/trainer.py:239-262)."""
+        from metaseq_b200.parallel.fsdp import fsdp_enable_wrap, fsdp_wrap
+
+        with fsdp_enable_wrap(self.cfg.distributed_training, use_sharded_state=self.use_sharded_state, comm="nccl"):
+            twin = fsdp_wrap(self.task.build_model(self.cfg.model), process_group=self.data_parallel_process_group)
+        twin = twin.to(device=self.device)
+        state = self.model.state_dict()
+        if not self.use_sharded_state and self.data_parallel_world_size > 1:
+            state = dist_utils.broadcast_object(state, src_rank=0, group=self.data_parallel_process_group,
+                                                dist_device=self.device if self.cuda else None)
+        twin.load_state_dict(state)
+        return twin
 
     @property
     def optimizer(self):
@@ -487,6 +504,7 @@ class Trainer:
             grad_norm = self.clip_grad_norm(self.cfg.optimization.clip_norm, self.cfg.optimization.clip_norm_type,
                                             self.cfg.optimization.skip_gradient_update_on_clip_norm)
             self._check_grad_norms(grad_norm)
+            self.last_grad_norm = grad_norm
             if not torch.isfinite(torch.as_tensor(grad_norm)).all():
                 raise FloatingPointError("gradients are Nan/Inf")
             # skip the update when the loss spiked against its running mean
@@ -785,7 +803,8 @@ class Trainer:
     def _log_gpu_mem_stats(self):
         gb = 1024.0 ** 3
         alloc = torch.cuda.max_memory_allocated() / gb
-        torch.cuda.reset_peak_memory_stats()
+        torch.cuda.reset_peak_memory_stats()  # the logged value is the peak of this update alone
+        self.peak_gb_allocated = max(getattr(self, "peak_gb_allocated", 0.0), alloc)  # peak over all updates
         reserved = torch.cuda.max_memory_reserved() / gb
         total = self.cuda_env.total_memory_in_GB
         metrics.log_scalar("cuda_gb_allocated", alloc, priority=1500, round=1, weight=0)

@@ -272,3 +272,29 @@ def test_cm3_objective_moves_spans_behind_sentinels():
         # and the text between the sentinels continues after the removed span
         middle = toks[first + 1:second]
         assert middle == list(range(middle[0], middle[0] + len(middle))) if middle else True
+
+
+def test_monolingual_dataset_clips_targets_and_prepends_language_ids():
+    from metaseq_b200.data.dictionary import Dictionary
+    from metaseq_b200.data.monolingual_dataset import MonolingualDataset
+
+    src_vocab, tgt_vocab = Dictionary(), Dictionary()
+    for i in range(20):
+        src_vocab.add_symbol(f"w{i}")
+    for i in range(8):
+        tgt_vocab.add_symbol(f"w{i}")
+    n_tgt = len(tgt_vocab)
+    blocks = [(torch.tensor([5, 6, 7]), torch.tensor([6, 7, n_tgt + 3]), torch.tensor([4, 5, 6])),
+              (torch.tensor([9, 10]), torch.tensor([10, n_tgt]), torch.tensor([8, 9]))]
+    ds = MonolingualDataset(blocks, [3, 2], src_vocab, tgt_vocab, add_bos_token=True, src_lang_idx=17, tgt_lang_idx=6)
+    item = ds[0]
+    assert item["source"].tolist() == [17, 5, 6, 7]
+    assert item["target"].tolist() == [6, 6, 7, tgt_vocab.unk()]
+    assert blocks[0][1].tolist() == [6, 7, n_tgt + 3]  # the wrapped dataset's tensors are left alone
+    batch = ds.collater([ds[0], ds[1]])
+    assert batch["net_input"]["src_tokens"].tolist() == [[17, 5, 6, 7], [17, 9, 10, src_vocab.pad()]]
+    assert batch["target"][1].tolist() == [6, 10 if 10 < n_tgt else tgt_vocab.unk(), tgt_vocab.unk(), src_vocab.pad()]
+    assert batch["ntokens"] == 7 and batch["net_input"]["src_lengths"].tolist() == [4, 3]
+    plain = MonolingualDataset(blocks, [3, 2], src_vocab, add_bos_token=True)
+    assert plain[1]["source"].tolist() == [src_vocab.bos(), 9, 10] and plain[1]["target"].tolist()[0] == src_vocab.bos()
+    assert plain.ordered_indices().tolist() == [1, 0]

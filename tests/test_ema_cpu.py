@@ -54,3 +54,40 @@ def test_ema_follows_the_recurrence_and_round_trips_through_the_checkpoint_state
     tr2.ema.reverse(target)
     for k, want in shadow.items():
         assert torch.allclose(target.state_dict()[k].float(), want, atol=1e-5, rtol=1e-4)
+
+
+def test_ema_over_a_fully_sharded_model_averages_the_flat_shards(tmp_path):
+    decay = 0.5
+    tr, batch = _trainer(tmp_path, ["--store-ema", "--ema-decay", str(decay), "--ema-fp32", "--ddp-backend",
+                                    "fully_sharded", "--use-sharded-state"])
+    keys = [k for k in tr.get_model().state_dict() if k.endswith("flat_param_0")]
+    assert keys, list(tr.get_model().state_dict())
+    shadow = {k: tr.get_model().state_dict()[k].detach().clone().float() for k in keys}
+    for _ in range(3):
+        tr.train_step([batch])
+        live = tr.get_model().state_dict()
+        for k in keys:
+            shadow[k] = decay * shadow[k] + (1 - decay) * live[k].detach().float()
+    assert tr.ema.get_model() is not tr.get_model()
+    ema_state = tr.ema.get_model().state_dict()
+    for k in keys:
+        assert torch.allclose(ema_state[k].float(), shadow[k], atol=1e-5, rtol=1e-4), k
+        assert not torch.allclose(ema_state[k].float(), live[k].float(), atol=1e-7)
+
+
+def test_ema_seed_model_and_update_frequency(tmp_path):
+    tr, batch = _trainer(tmp_path, [])
+    seed_state = {k: torch.full_like(v, 0.25) if v.is_floating_point() else v.clone()
+                  for k, v in tr.get_model().state_dict().items()}
+    seed_path = tmp_path / "seed.pt"
+    torch.save({"model": {}, "extra_state": {"ema": seed_state}}, seed_path)
+    tr2, batch = _trainer(tmp_path, ["--store-ema", "--ema-decay", "0.5", "--ema-seed-model", str(seed_path),
+                                     "--ema-update-freq", "2"])
+    start = tr2.ema.get_model().state_dict()
+    name = next(k for k, v in start.items() if v.is_floating_point() and "version" not in k)
+    assert torch.all(start[name] == 0.25)
+    tr2.train_step([batch])  # first of two: no EMA update yet
+    assert torch.all(tr2.ema.get_model().state_dict()[name] == 0.25)
+    tr2.train_step([batch])
+    want = 0.5 * 0.25 + 0.5 * tr2.get_model().state_dict()[name].float()
+    assert torch.allclose(tr2.ema.get_model().state_dict()[name].float(), want, atol=1e-6)
