@@ -55,12 +55,26 @@ class VocabParallelCrossEntropyCriterion(BaseCriterion):
             "nsentences": target.size(0),
             "sample_size": ntok_target,
         }
+        if "src_tokens" in sample["net_input"] and hasattr(self.task, "eod"):
+            logging_output["ndocseps"] = (target == self.task.eod).sum()
+        extra = net_output[1] if len(net_output) > 1 and isinstance(net_output[1], dict) else {}
+        for kind, total in (extra.get("norm_sums") or {}).items():
+            logging_output[f"{kind}_norm"] = total  # sum over tokens of the L2 norm; averaged in reduce_metrics
         return loss, ntok_target, logging_output
 
     @staticmethod
     def reduce_metrics(logging_outputs) -> None:
         loss_sum = sum(float(log.get("loss", 0)) for log in logging_outputs)
         sample_size = sum(float(log.get("sample_size", 0)) for log in logging_outputs)
+        ntokens = sum(float(log.get("ntokens", 0)) for log in logging_outputs)
+        for kind in ("actv", "pos", "tok", "emb"):
+            key = f"{kind}_norm"
+            if any(key in log for log in logging_outputs):
+                metrics.log_scalar(key, sum(log.get(key, 0) for log in logging_outputs) / max(ntokens, 1), round=3)
+        if any("ndocseps" in log for log in logging_outputs):
+            nsentences = sum(float(log.get("nsentences", 0)) for log in logging_outputs)
+            ndocseps = sum(log.get("ndocseps", 0) for log in logging_outputs)
+            metrics.log_scalar("docsperex", (ndocseps + nsentences) / max(nsentences, 1))
         metrics.log_scalar("loss", loss_sum / max(sample_size, 1) / math.log(2), sample_size, round=3)
         metrics.log_derived("ppl", lambda meters: _ppl(meters["loss"].avg))
 

@@ -104,6 +104,8 @@ class CommonConfig(MetaseqDataclass):
     plasma_path: Optional[str] = opt("/tmp/plasma", "path to run plasma_store")
     log_nvidia_smi: bool = opt(False, "log output from nvidia-smi during training")
     quiet_logs: Optional[bool] = opt(False, "don't log per-parameter gnorm/pnorm stats")
+    log_param_stats: bool = opt(False, "log norm / max / zero share of every flat parameter and its gradient each "
+                                       "update (a few hundred small reductions per update; off by default)")
     # additions of this framework
     kernel_backend: str = opt("auto", "operator backend: sm_100a kernels when possible (auto) or PyTorch/cuBLAS "
                               "ops everywhere (torch), which is the unfused baseline", choices=("auto", "torch"))

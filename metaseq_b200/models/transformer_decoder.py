@@ -165,13 +165,36 @@ class ModelParallelTransformerDecoder(IncrementalDecoder):
             x = self.dropout_module(x)
         return x, embed, positions, doc_start
 
+    def _embedding_norm_sums(self, tokens, positions, x) -> dict:
+        """Sums over tokens of the L2 norms of the token embedding, the position embedding and their sum (what the
+        reference reads off ``inner_states[0]``, metaseq/criterions/vocab_parallel_cross_entropy.py:51-70).  The
+        token part comes from the row norms of the table, so the fused embedding kernel needs no second output."""
+        l2 = lambda t: torch.linalg.vector_norm(t.detach(), dim=-1, dtype=torch.float32)  # noqa: E731
+        out = {"emb": l2(x).sum()}
+        w = self.embed_tokens.weight
+        row_norm = l2(w) * self.embed_scale
+        tp = mpu.get_tensor_model_parallel_world_size()
+        if tp == 1:
+            out["tok"] = row_norm[tokens.reshape(-1)].sum()
+        else:  # rows of other ranks count zero here; the sum over the tensor-parallel group completes it
+            lo = self.embed_tokens.vocab_start_index
+            local = tokens.reshape(-1) - lo
+            mine = (local >= 0) & (local < w.shape[0])
+            part = (row_norm[local.clamp(0, w.shape[0] - 1)] * mine).sum()
+            torch.distributed.all_reduce(part, group=mpu.get_tensor_model_parallel_group())
+            out["tok"] = part
+        pos_w = getattr(self.embed_positions, "weight", None) if self.embed_positions is not None else None
+        if pos_w is not None and positions is not None:
+            out["pos"] = l2(pos_w)[positions.reshape(-1)].sum()
+        return out
+
     # ---------------------------------------------------------------- forward
     def forward(self, prev_output_tokens, src_lengths=None, incremental_state=None, features_only: bool = False,
                 self_attn_padding_mask=None, **unused):
         x, extra = self.extract_features(prev_output_tokens, incremental_state=incremental_state,
                                          self_attn_padding_mask=self_attn_padding_mask)
         if not features_only:
-            x = self.output_layer(x, bt=extra["bt"])
+            x = self.output_layer(x, bt=extra["bt"], norm_sums=extra.get("norm_sums"))
         return x, extra
 
     def _past_length(self, incremental_state) -> int:
@@ -187,6 +210,10 @@ class ModelParallelTransformerDecoder(IncrementalDecoder):
         B = prev_output_tokens.shape[0]
         x, tok_emb, positions, doc_start = self.forward_embedding(prev_output_tokens, incremental_state, past)
         T = x.shape[1]
+        norms = None
+        if self.training and incremental_state is None and _get(self.args, "log_activation_norms", True):
+            with torch.no_grad():
+                norms = self._embedding_norm_sums(prev_output_tokens, positions, x)
         attn_mask = None
         if doc_start is not None and incremental_state is None:
             # block-diagonal causal mask: a token attends only inside its own document
@@ -202,7 +229,8 @@ class ModelParallelTransformerDecoder(IncrementalDecoder):
             x = layer(x, bt=(B, T), incremental_state=incremental_state,
                       self_attn_padding_mask=self_attn_padding_mask, self_attn_mask=attn_mask)
         x = self.layer_norm(x)
-        return x, {"inner_states": inner_states, "tok_emb": tok_emb, "positions": positions, "bt": (B, T)}
+        return x, {"inner_states": inner_states, "tok_emb": tok_emb, "positions": positions, "bt": (B, T),
+                   "norm_sums": norms}
 
     def output_layer(self, features, **kwargs):
         """Project to the vocabulary with the (tied) embedding matrix."""
@@ -212,6 +240,9 @@ class ModelParallelTransformerDecoder(IncrementalDecoder):
             features = mappings.gather_from_sequence_parallel_region(features, True)
         elif tp > 1:
             features = mappings.copy_to_tensor_model_parallel_region(features)
+        if kwargs.get("norm_sums") is not None:  # final activations, all positions (after the sequence gather)
+            with torch.no_grad():
+                kwargs["norm_sums"]["actv"] = torch.linalg.vector_norm(features.detach(), dim=-1, dtype=torch.float32).sum()
         if ops_f.use_kernels(features) and features.dtype == w.dtype and w.shape[0] % 8 == 0:
             logits = ops_ag.linear(features, w)
         else:

@@ -47,58 +47,58 @@ class Trainer:
             from metaseq_b200.dataclass.utils import convert_namespace_to_config
 
             cfg = convert_namespace_to_config(cfg)
-        self.cfg = cfg
-        self.task = task
-        shared = _catalog_shared_params(model)
+        self.cfg, self.task = cfg, task
         self.cuda = torch.cuda.is_available() and not cfg.common.cpu
-        self.device = torch.device("cuda") if self.cuda else torch.device("cpu")
-        self._criterion = criterion
-        self._model = model
-        if not self.is_fsdp:
-            if cfg.common.fp16 or cfg.common.memory_efficient_fp16:
-                self._criterion = self._criterion.half()
-                self._model = self._model.half()
-            elif cfg.common.bf16:
-                self._criterion = self._criterion.to(dtype=torch.bfloat16)
-                self._model = self._model.to(dtype=torch.bfloat16)
-        if not getattr(cfg.distributed_training, "pipeline_model_parallel", False):
-            self._criterion = self._criterion.to(device=self.device)
-            self._model = self._model.to(device=self.device)
-        for shared_param in shared:
-            ref = _get_module_by_path(self._model, shared_param[0])
-            for path in shared_param[1:]:
-                logger.info(f"detected shared parameter: {shared_param[0]} <- {path}")
-                _set_module_by_path(self._model, path, ref)
+        self.device = torch.device("cuda" if self.cuda else "cpu")
+        # lazily built members
+        self._optimizer = self._lr_scheduler = self._optim_history = None
+        self._wrapped_model = self._wrapped_criterion = self._ema = None
         self._dummy_batch = None
-        self._lr_scheduler = None
+        # progress and loss-spike bookkeeping
         self._num_updates = 0
-        self._optim_history = None
-        self._optimizer = None
-        self._warn_once = set()
-        self._wrapped_criterion = None
-        self._wrapped_model = None
         self._ewm_loss = None
         self._skipped_loss_spikes = 0
-        self._ema = None
+        self._warn_once = set()
+        self._model, self._criterion = self._place(model, criterion)
+        self._grad_norm_buf = None
         if self.cuda and self.data_parallel_world_size > 1:
             self._grad_norm_buf = torch.zeros(self.data_parallel_world_size, dtype=torch.double, device=self.device)
-        else:
-            self._grad_norm_buf = None
-        if self.cuda:
-            self.cuda_env = utils.CudaEnvironment()
-            if self.data_parallel_world_size > 1:
-                self.cuda_env_arr = dist_utils.all_gather_list(self.cuda_env, group=dist_utils.get_global_group())
-            else:
-                self.cuda_env_arr = [self.cuda_env]
-            if self.data_parallel_rank == 0:
-                utils.CudaEnvironment.pretty_print_cuda_env_list(self.cuda_env_arr)
-        else:
-            self.cuda_env = None
-            self.cuda_env_arr = None
+        self.cuda_env, self.cuda_env_arr = self._survey_devices()
+        # wall-clock accounting (restored from checkpoints)
         metrics.log_start_time("wall", priority=790, round=2)
         self._start_time = time.time()
         self._previous_training_time = 0
         self._cumulative_training_time = None
+
+    def _place(self, model, criterion):
+        """Casts (unless the sharded wrapper owns the dtype) and moves model and criterion to the training device,
+        then re-ties parameters that were shared before the move."""
+        tied = _catalog_shared_params(model)
+        c = self.cfg.common
+        if not self.is_fsdp:
+            dtype = torch.float16 if (c.fp16 or c.memory_efficient_fp16) else (torch.bfloat16 if c.bf16 else None)
+            if dtype is not None:
+                model, criterion = model.to(dtype=dtype), criterion.to(dtype=dtype)
+        if not getattr(self.cfg.distributed_training, "pipeline_model_parallel", False):
+            model, criterion = model.to(device=self.device), criterion.to(device=self.device)
+        for first, *others in tied:
+            owner = _get_module_by_path(model, first)
+            for path in others:
+                logger.info(f"detected shared parameter: {first} <- {path}")
+                _set_module_by_path(model, path, owner)
+        return model, criterion
+
+    def _survey_devices(self):
+        """This rank's GPU description and every rank's (printed once by the first data-parallel rank)."""
+        if not self.cuda:
+            return None, None
+        mine = utils.CudaEnvironment()
+        everyone = [mine]
+        if self.data_parallel_world_size > 1:
+            everyone = dist_utils.all_gather_list(mine, group=dist_utils.get_global_group())
+        if self.data_parallel_rank == 0:
+            utils.CudaEnvironment.pretty_print_cuda_env_list(everyone)
+        return mine, everyone
 
     # ------------------------------------------------------------- properties
     def reinitialize(self):
@@ -790,15 +790,20 @@ class Trainer:
             return logging_output
 
     def _log_param_stats(self):
-        """Per flat-parameter gradient / parameter norms, maxima and zero counts."""
+        """Per flat parameter: L2 norm, maximum and the share of (near-)zero entries, of the gradient as the
+        optimizer will apply it and of the parameter itself (metaseq/trainer.py:1360-1390).  The values stay on
+        the device until the meters are printed."""
+        factor = getattr(self.optimizer, "_multiply_factor", None)
         for name, p in self.model.named_parameters():
-            short = name.replace(".flat_param", "").replace("module.", "")
+            if p.grad is None:
+                continue
+            short = name.replace(".flat_param", "").replace("module.", "").replace("decoder.layers.", "layer")
+            tiny = 2 * torch.finfo(p.grad.dtype).tiny
             with torch.no_grad():
-                metrics.log_scalar(f"pnorm_{short}", p.float().norm(), priority=900, round=4, weight=0)
-                metrics.log_scalar(f"pmax_{short}", p.float().abs().max(), priority=900, round=4, weight=0)
-                if p.grad is not None:
-                    metrics.log_scalar(f"gnorm_{short}", p.grad.float().norm(), priority=900, round=4, weight=0)
-                    metrics.log_scalar(f"gmax_{short}", p.grad.float().abs().max(), priority=900, round=4, weight=0)
+                for tag, t, prio in (("g", p.grad if factor is None else p.grad * factor, 10), ("p", p.detach(), 13)):
+                    metrics.log_scalar(f"{tag}norm_{short}", t.float().norm(), priority=prio, round=4)
+                    metrics.log_scalar(f"{tag}max_{short}", t.max().float(), priority=prio + 1, round=4)
+                    metrics.log_scalar(f"{tag}zero_{short}", (t.abs() < tiny).float().mean(), priority=prio + 2, round=4)
 
     def _log_gpu_mem_stats(self):
         gb = 1024.0 ** 3

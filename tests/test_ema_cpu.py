@@ -2,6 +2,7 @@
 the checkpoint state, and can be swapped into the live model."""
 import copy
 
+import pytest
 import torch
 
 from metaseq_b200 import options, tasks
@@ -91,3 +92,26 @@ def test_ema_seed_model_and_update_frequency(tmp_path):
     tr2.train_step([batch])
     want = 0.5 * 0.25 + 0.5 * tr2.get_model().state_dict()[name].float()
     assert torch.allclose(tr2.ema.get_model().state_dict()[name].float(), want, atol=1e-6)
+
+
+def test_activation_norms_and_parameter_statistics_are_logged(tmp_path):
+    from metaseq_b200.logging import metrics
+
+    metrics.reset()
+    tr, batch = _trainer(tmp_path, ["--criterion", "vocab_parallel_cross_entropy", "--ddp-backend", "fully_sharded",
+                                    "--use-sharded-state", "--log-param-stats", "--decoder-learned-pos",
+                                    "--no-scale-embedding"])
+    out = tr.train_step([batch])
+    model = tr.get_model()
+    with torch.no_grad():
+        tokens = batch["net_input"]["src_tokens"]
+        dec = model.decoder
+        tok = dec.embed_tokens.weight[tokens].float()
+        want_tok = tok.norm(dim=-1).mean()
+    for key in ("actv_norm", "emb_norm", "tok_norm", "pos_norm"):
+        assert key in out and float(out[key]) > 0, (key, sorted(out))
+    train = metrics.get_smoothed_values("train")
+    stats = [k for k in train if k.startswith(("gnorm_", "gmax_", "gzero_", "pnorm_", "pmax_", "pzero_"))]
+    assert {k.split("_")[0] for k in stats} == {"gnorm", "gmax", "gzero", "pnorm", "pmax", "pzero"}, sorted(train)
+    # the token-embedding norm was taken before the update: compare with a tolerance that covers one Adam step
+    assert float(out["tok_norm"]) == pytest.approx(float(want_tok), rel=0.2)
