@@ -42,6 +42,8 @@ logger = logging.getLogger("metaseq_b200.cli.train")
 def main(cfg: Cfg) -> None:
     utils_import_user_module(cfg.common)
     ops_f.set_backend(getattr(cfg.common, "kernel_backend", "auto") or "auto")
+    if getattr(cfg.common, "strict_kernels", False):
+        ops_f.set_strict_kernels(True)
     if dist_utils.is_master(cfg.distributed_training) and "job_logging_cfg" in cfg:
         pass
     assert cfg.dataset.max_tokens is not None or cfg.dataset.batch_size is not None, \

@@ -24,9 +24,13 @@ class CrossEntropyCriterionConfig(MetaseqDataclass):
     pass
 
 
-def nll_loss_sum(logits, target, ignore_index):
-    """Summed NLL of ``[N, V]`` logits."""
-    if ops_f.use_kernels(logits) and logits.shape[-1] % 8 == 0 and logits.shape[-1] * 2 <= 200 * 1024:
+def nll_loss_sum(logits, target, ignore_index, row_stats=None):
+    """Summed NLL of ``[N, V]`` logits.  ``row_stats``: the softmax pieces left by the logits product
+    (``ops.autograd.linear(..., row_stats=True)``), which lift the kernel's limit on the vocabulary size."""
+    if ops_f.use_kernels(logits) and logits.shape[-1] % 8 == 0 and \
+            (row_stats is not None or logits.shape[-1] * 2 <= 200 * 1024):
+        if row_stats is not None:
+            logits._msq_row_stats = row_stats
         return ops_ag.cross_entropy_sum(logits, target, ignore_index)
     lprobs = TF.log_softmax(logits, dim=-1, dtype=torch.float32)
     return TF.nll_loss(lprobs, target, ignore_index=ignore_index, reduction="sum")

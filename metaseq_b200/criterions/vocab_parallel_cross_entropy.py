@@ -36,13 +36,14 @@ class VocabParallelCrossEntropyCriterion(BaseCriterion):
         has_pad = True
         net_output = model(**sample["net_input"])
         logits = net_output[0]
+        row_stats = getattr(logits, "_msq_row_stats", None)  # left by the logits product's epilogue
         if mpu.get_tensor_model_parallel_world_size() == 1:
-            loss = nll_loss_sum(logits.reshape(-1, logits.size(-1)), target.reshape(-1), self.padding_idx)
+            loss = nll_loss_sum(logits.reshape(-1, logits.size(-1)), target.reshape(-1), self.padding_idx, row_stats)
         else:
             from metaseq_b200.parallel.cross_entropy import fused_vocab_parallel_cross_entropy_ok
 
             if fused_vocab_parallel_cross_entropy_ok(logits):
-                per_tok = vocab_parallel_cross_entropy(logits, target, self.padding_idx)  # 16-bit logits, in place
+                per_tok = vocab_parallel_cross_entropy(logits, target, self.padding_idx, row_stats)  # in place
             else:
                 per_tok = vocab_parallel_cross_entropy(logits.float(), target)
             if has_pad:

@@ -10,10 +10,20 @@
 // d^-1/4 each before the product; here the product is scaled once by d^-1/2,
 // which is the same function in exact arithmetic.
 //
-// Layout: q, k, v are [B, T, H, HD] views with arbitrary row / batch strides
+// Layout: q, k, v are [B, T, H, hd] views with arbitrary row / batch strides
 // (they are column slices of the fused qkv projection output); the output is
-// [B, T, H*HD].  One TMA box is 128 rows x 64 columns with 128-byte swizzle; a
-// tile of HD columns is HD/64 such boxes.  The same physical tile serves as a
+// [B, T, H*hd].  The tensor maps are 4-D (hd, H, T, B): one TMA box is 128 rows x 64 columns of
+// one head with 128-byte swizzle, and a tile of HD columns is HD/64 such boxes.  Head sizes
+// that are not 64 or 128 (80 and 96: OPT-2.7B, OPT-760M) run the HD = 128 kernels: columns
+// past hd lie outside the map's first dimension, so the loads fill them with zeros, which
+// contribute nothing to Q K^T and leave the padded columns of O, dQ, dK, dV unused.
+//
+// Masks beyond causality (both optional): `doc_start[b, t]` = first position of the document
+// that token t belongs to; a query attends to keys in [doc_start, t] only (the reference's
+// --self-attn-doc-sep block-diagonal mask, metaseq/modules/multihead_attention.py:400-409,
+// built there as a [B, T, T] tensor for the masked-softmax kernel).  Blocks that lie wholly
+// before the documents of a query tile are skipped.  `alibi_slopes[h]` adds slope * key
+// position to the scaled scores (metaseq/models/transformer_decoder.py:193-230).  The same physical tile serves as a
 // K-major operand (rows = M or N, 64 columns = K) and as an MN-major operand
 // (rows = K, 64 columns = M or N), which is what lets the backward pass reuse
 // Q, dO, P and dS for the transposed products without any transposed copy.
@@ -49,6 +59,9 @@ struct AttnFwdParams {
   uint32_t drop_threshold16;
   float inv_keep;
   unsigned long long seed;
+  int hd;                     // real head size (<= HD of the kernel)
+  const int* doc_start;       // [B, T] or null
+  const float* alibi_slopes;  // [H] or null
 };
 
 template <int HD>
@@ -90,7 +103,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int n_qblocks = gridDim.x;
   const int qb = n_qblocks - 1 - blockIdx.x;  // heaviest (longest causal prefix) blocks first
   const int h = blockIdx.y, b = blockIdx.z;
-  const int n_kv = p.causal ? (qb + 1) : (p.T + TILE - 1) / TILE;
+  // With document starts the first row of the tile has the earliest start: kv blocks before it are skipped.
+  const int* dstart = p.doc_start ? p.doc_start + static_cast<long long>(b) * p.T : nullptr;
+  const int j0 = dstart ? dstart[min(qb * TILE, p.T - 1)] / TILE : 0;
+  const int n_kv = (p.causal ? (qb + 1) : (p.T + TILE - 1) / TILE) - j0;  // blocks j0 .. j0 + n_kv - 1
 
   if (p.status && *reinterpret_cast<volatile int*>(p.status) != 0) return;
 
@@ -123,7 +139,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_expect_tx(q_full, Cfg::TILE_BYTES);
 #pragma unroll
       for (int c = 0; c < Cfg::CHUNKS; ++c)
-        tma_load_3d(sQ + c * Cfg::CHUNK_BYTES, &tmQ, q_full, h * HD + c * 64, qb * TILE, b);
+        tma_load_4d(sQ + c * Cfg::CHUNK_BYTES, &tmQ, q_full, c * 64, h, qb * TILE, b);
       int slot = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -137,7 +153,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           const CUtensorMap* tm = which ? &tmV : &tmK;
 #pragma unroll
           for (int c = 0; c < Cfg::CHUNKS; ++c)
-            tma_load_3d(dst + c * Cfg::CHUNK_BYTES, tm, &kv_full[slot], h * HD + c * 64, j * TILE, b);
+            tma_load_4d(dst + c * Cfg::CHUNK_BYTES, tm, &kv_full[slot], c * 64, h, (j0 + j) * TILE, b);
           if (++slot == Cfg::SLOTS) { slot = 0; phase ^= 1; }
         }
       }
@@ -216,20 +232,26 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const unsigned long long drop_row =
         ((static_cast<unsigned long long>(b) * p.H + h) * p.T + q_idx) * static_cast<unsigned long long>((p.T + 1) >> 1);
     bool ok = true;
+    const int row_start = (dstart && q_idx < p.T) ? dstart[q_idx] : 0;  // first key this row may attend to
+    const float slope2 = p.alibi_slopes ? p.alibi_slopes[h] * LOG2E : 0.f;
     for (int j = 0; j < n_kv && ok; ++j) {
       ok = mbar_wait_warp(s_full, j & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
       if (!ok) break;
       tc_fence_after();
-      // Columns of this block that row q_idx may attend to: [0, limit).  Only the diagonal block of a
-      // causal problem and the last block of a ragged sequence need per-element masks; every other
-      // block takes the unmasked path (uniform over the CTA).
+      const int ja = j0 + j;  // kv block index in the sequence
+      // Columns of this block that row q_idx may attend to: [lo, limit).  Only the diagonal block of a
+      // causal problem, the last block of a ragged sequence, blocks that a document start cuts and ALiBi need
+      // the per-element path; every other block takes the unmasked one (uniform over the warp).
       const bool prof_on = p.prof != nullptr && row == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j < 32;
       if (prof_on) p.prof[j * 8 + 0] = clock64();
-      const bool need_mask = (p.causal && j == qb) || ((j + 1) * TILE > p.T);
-      int limit = p.T - j * TILE;
-      if (p.causal) limit = min(limit, q_idx - j * TILE + 1);
+      const int lo = row_start - ja * TILE;
+      const bool need_mask = (p.causal && ja == qb) || ((ja + 1) * TILE > p.T) || p.alibi_slopes != nullptr ||
+                             __any_sync(0xffffffffu, lo > 0);
+      int limit = p.T - ja * TILE;
+      if (p.causal) limit = min(limit, q_idx - ja * TILE + 1);
       limit = max(0, min(limit, TILE));
-      float mx;
+      const float kpos0 = static_cast<float>(ja * TILE);  // ALiBi: bias of column i is slope2 * (kpos0 + i)
+      float mx;  // row maximum of this block in log2 units (scaled, biased)
       {
         // four independent running maxima keep the dependency chains short
         float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -241,8 +263,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           if (c + 1 < 4) tmem_ld_32x32(tS + lane_off + (c + 1) * 32, r[(c + 1) & 1]);
           if (need_mask) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (c * 32 + i < limit) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(r[c & 1][i]));
+            for (int i = 0; i < 32; ++i) {
+              const int col = c * 32 + i;
+              if (col < limit && col >= lo)
+                m4[i & 3] = fmaxf(m4[i & 3], fmaf(__uint_as_float(r[c & 1][i]), p.scale_log2, slope2 * (kpos0 + col)));
+            }
           } else {
 #pragma unroll
             for (int i = 0; i < 16; ++i)
@@ -250,9 +275,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
         }
         mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+        if (!need_mask) mx *= p.scale_log2;  // the per-element path already works in scaled units
       }
       if (prof_on) p.prof[j * 8 + 1] = clock64();
-      const float m_new = fmaxf(m_run, mx * p.scale_log2);
+      const float m_new = fmaxf(m_run, mx);
       if (j == 0) {
         m_run = m_new;  // the first P V product overwrites O: nothing to rescale
       } else {
@@ -293,15 +319,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           if (need_mask) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-              const float a = (c * 32 + 2 * i < limit)
-                                  ? exp2f(fmaf(__uint_as_float(r[c & 1][2 * i]), p.scale_log2, -m_use)) : 0.f;
-              const float bb = (c * 32 + 2 * i + 1 < limit)
-                                   ? exp2f(fmaf(__uint_as_float(r[c & 1][2 * i + 1]), p.scale_log2, -m_use)) : 0.f;
+              const int col = c * 32 + 2 * i;
+              const float a = (col < limit && col >= lo)
+                                  ? exp2f(fmaf(__uint_as_float(r[c & 1][2 * i]), p.scale_log2, slope2 * (kpos0 + col) - m_use)) : 0.f;
+              const float bb = (col + 1 < limit && col + 1 >= lo)
+                                   ? exp2f(fmaf(__uint_as_float(r[c & 1][2 * i + 1]), p.scale_log2, slope2 * (kpos0 + col + 1) - m_use)) : 0.f;
               ps4[i & 3] += a + bb;
               float da = a, db = bb;
               if (DROP) {
                 bool k0, k1;
-                dropout_keep2(dropout_bits(p.seed, drop_row + ((j * TILE + c * 32) >> 1) + i), p.drop_threshold16, k0, k1);
+                dropout_keep2(dropout_bits(p.seed, drop_row + ((ja * TILE + c * 32) >> 1) + i), p.drop_threshold16, k0, k1);
                 da = k0 ? a * p.inv_keep : 0.f;
                 db = k1 ? bb * p.inv_keep : 0.f;
               }
@@ -317,7 +344,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
               float da = a, db = bb;
               if (DROP) {
                 bool k0, k1;
-                dropout_keep2(dropout_bits(p.seed, drop_row + ((j * TILE + c * 32) >> 1) + i), p.drop_threshold16, k0, k1);
+                dropout_keep2(dropout_bits(p.seed, drop_row + ((ja * TILE + c * 32) >> 1) + i), p.drop_threshold16, k0, k1);
                 da = k0 ? a * p.inv_keep : 0.f;
                 db = k1 ? bb * p.inv_keep : 0.f;
               }
@@ -344,7 +371,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (ok) {
       const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
       uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + static_cast<long long>(b) * p.o_batch_stride +
-                    static_cast<long long>(q_idx < p.T ? q_idx : 0) * p.o_row_stride + h * HD;
+                    static_cast<long long>(q_idx < p.T ? q_idx : 0) * p.o_row_stride + h * p.hd;
       uint32_t r[2][32];
       tmem_ld_32x32(tO + lane_off, r[0]);
 #pragma unroll
@@ -354,6 +381,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (q_idx < p.T) {
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
+            if (c * 32 + v * 8 >= p.hd) break;  // padded columns of a head size below HD
             uint4 ov;
             ov.x = pack2<BF16>(__uint_as_float(r[c & 1][v * 8 + 0]) * inv_l, __uint_as_float(r[c & 1][v * 8 + 1]) * inv_l);
             ov.y = pack2<BF16>(__uint_as_float(r[c & 1][v * 8 + 2]) * inv_l, __uint_as_float(r[c & 1][v * 8 + 3]) * inv_l);
@@ -392,6 +420,9 @@ struct AttnBwdParams {
   uint32_t drop_threshold16;
   float inv_keep;
   unsigned long long seed;
+  int hd;                     // real head size (<= HD of the kernel)
+  const int* doc_start;       // [B, T] or null
+  const float* alibi_slopes;  // [H] or null
 };
 
 template <int HD>
@@ -443,7 +474,16 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int h = blockIdx.y, b = blockIdx.z;
   const int n_q = (p.T + TILE - 1) / TILE;
   const int m_start = p.causal ? nb : 0;
-  const int n_it = n_q - m_start;
+  // Document starts never decrease along the sequence: once the first row of a q tile starts after the last key of
+  // this block, that tile and every later one see none of its keys.
+  const int* dstart = p.doc_start ? p.doc_start + static_cast<long long>(b) * p.T : nullptr;
+  int m_end = n_q;
+  if (dstart) {
+    const int kv_last = nb * TILE + TILE - 1;
+    for (int m = m_start + 1; m < n_q; ++m)
+      if (dstart[min(m * TILE, p.T - 1)] > kv_last) { m_end = m; break; }
+  }
+  const int n_it = m_end - m_start;
 
   if (p.status && *reinterpret_cast<volatile int*>(p.status) != 0) return;
 
@@ -477,8 +517,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_expect_tx(kv_full, 2 * Cfg::TILE_BYTES);
 #pragma unroll
       for (int c = 0; c < Cfg::CHUNKS; ++c) {
-        tma_load_3d(sK + c * Cfg::CHUNK_BYTES, &tmK, kv_full, h * HD + c * 64, nb * TILE, b);
-        tma_load_3d(sV + c * Cfg::CHUNK_BYTES, &tmV, kv_full, h * HD + c * 64, nb * TILE, b);
+        tma_load_4d(sK + c * Cfg::CHUNK_BYTES, &tmK, kv_full, c * 64, h, nb * TILE, b);
+        tma_load_4d(sV + c * Cfg::CHUNK_BYTES, &tmV, kv_full, c * 64, h, nb * TILE, b);
       }
       int stage = 0;
       uint32_t phase = 0;
@@ -490,10 +530,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         mbar_expect_tx(&qdo_full[stage], 2 * Cfg::TILE_BYTES);
 #pragma unroll
         for (int c = 0; c < Cfg::CHUNKS; ++c) {
-          tma_load_3d(sQ + stage * Cfg::TILE_BYTES + c * Cfg::CHUNK_BYTES, &tmQ, &qdo_full[stage], h * HD + c * 64,
+          tma_load_4d(sQ + stage * Cfg::TILE_BYTES + c * Cfg::CHUNK_BYTES, &tmQ, &qdo_full[stage], c * 64, h,
                       m * TILE, b);
-          tma_load_3d(sDO + stage * Cfg::TILE_BYTES + c * Cfg::CHUNK_BYTES, &tmDO, &qdo_full[stage],
-                      h * HD + c * 64, m * TILE, b);
+          tma_load_4d(sDO + stage * Cfg::TILE_BYTES + c * Cfg::CHUNK_BYTES, &tmDO, &qdo_full[stage], c * 64, h,
+                      m * TILE, b);
         }
         if (++stage == QS) { stage = 0; phase ^= 1; }
       }
@@ -626,8 +666,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (lane == 0) {
           const int row0 = (m_start + dit) * TILE + quarter * 32;
           if (row0 < p.T) {  // rows past T inside a box are dropped by the copy engine
-            tma_reduce_add_3d(&tmDQ, boxes, h * HD, row0, b);
-            tma_reduce_add_3d(&tmDQ, boxes + 4096, h * HD + 32, row0, b);
+            tma_reduce_add_4d(&tmDQ, boxes, 0, h, row0, b);
+            if (p.hd > 32) tma_reduce_add_4d(&tmDQ, boxes + 4096, 32, h, row0, b);
           }
           bulk_commit_group();
         }
@@ -678,7 +718,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          if (rows_in_range) tma_reduce_add_3d(&tmDQ, stage_buf, h * HD + half * (HD / 2) + c * 32, dm * TILE + quarter * 32, b);
+          // a box that starts in the padded columns of a smaller head is dropped; one that straddles the end
+          // of the head is clipped by the copy engine
+          if (rows_in_range && half * (HD / 2) + c * 32 < p.hd)
+            tma_reduce_add_4d(&tmDQ, stage_buf, half * (HD / 2) + c * 32, h, dm * TILE + quarter * 32, b);
           bulk_commit_group();
         }
         ++staged;
@@ -694,8 +737,12 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       int limit = p.T - nb * TILE;
       if (p.causal) limit = min(limit, q_idx - nb * TILE + 1);
       limit = q_ok ? max(0, min(limit, TILE)) : 0;
-      // uniform over the CTA: only diagonal blocks and ragged tails (rows or columns past T) need masks
-      const bool need_mask = (p.causal && m == nb) || ((m + 1) * TILE > p.T) || ((nb + 1) * TILE > p.T);
+      const int lo = (dstart && q_ok) ? dstart[q_idx] - nb * TILE : 0;  // keys before the row's document are masked
+      const float slope2 = p.alibi_slopes ? p.alibi_slopes[h] * LOG2E : 0.f;
+      // uniform over the warp: only diagonal blocks, ragged tails (rows or columns past T), blocks cut by a
+      // document start and ALiBi need the per-element path
+      const bool need_mask = (p.causal && m == nb) || ((m + 1) * TILE > p.T) || ((nb + 1) * TILE > p.T) ||
+                             p.alibi_slopes != nullptr || __any_sync(0xffffffffu, lo > 0);
       const bool prof_on = p.prof != nullptr && row == 0 && half == 0 && blockIdx.x == 0 && blockIdx.y == 0 &&
                            blockIdx.z == 0 && it < 32;
       if (prof_on) p.prof[256 + it * 8 + 0] = clock64();
@@ -728,13 +775,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 ks0 = k0 ? p.inv_keep : 0.f;
                 ks1 = k1 ? p.inv_keep : 0.f;
               }
-              if (cbase + 2 * i < limit) {
-                p0 = exp2f(fmaf(__uint_as_float(s[2 * i]), scale_log2, -lse2));
+              const int col = cbase + 2 * i;
+              if (col < limit && col >= lo) {
+                p0 = exp2f(fmaf(__uint_as_float(s[2 * i]), scale_log2, slope2 * (nb * TILE + col) - lse2));
                 d0 = p0 * (ks0 * __uint_as_float(dp[2 * i]) - delta) * p.scale;
                 p0 *= ks0;
               }
-              if (cbase + 2 * i + 1 < limit) {
-                p1 = exp2f(fmaf(__uint_as_float(s[2 * i + 1]), scale_log2, -lse2));
+              if (col + 1 < limit && col + 1 >= lo) {
+                p1 = exp2f(fmaf(__uint_as_float(s[2 * i + 1]), scale_log2, slope2 * (nb * TILE + col + 1) - lse2));
                 d1 = p1 * (ks1 * __uint_as_float(dp[2 * i + 1]) - delta) * p.scale;
                 p1 *= ks1;
               }
@@ -801,9 +849,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const bool kv_ok = kv_idx < p.T;
       const long long kv_row = kv_ok ? kv_idx : 0;
       uint16_t* dk = reinterpret_cast<uint16_t*>(p.dk) + static_cast<long long>(b) * p.dk_batch_stride +
-                     kv_row * p.dk_row_stride + h * HD + half * (HD / 2);
+                     kv_row * p.dk_row_stride + h * p.hd + half * (HD / 2);
       uint16_t* dv = reinterpret_cast<uint16_t*>(p.dv) + static_cast<long long>(b) * p.dv_batch_stride +
-                     kv_row * p.dv_row_stride + h * HD + half * (HD / 2);
+                     kv_row * p.dv_row_stride + h * p.hd + half * (HD / 2);
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {
         uint16_t* dst = which ? dv : dk;
@@ -816,6 +864,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           if (kv_ok) {
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
+              if (half * (HD / 2) + c * 32 + v * 8 >= p.hd) break;  // padded columns of a head size below HD
               uint4 ov;
               ov.x = pack2<BF16>(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
               ov.y = pack2<BF16>(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
@@ -839,13 +888,13 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
 }
 
-// delta[b, h, t] = sum_d dO[b, t, h, d] * O[b, t, h, d].  HD / 8 adjacent lanes own one (b, t, h) row and
-// load 16 bytes each, so a warp reads 512 contiguous bytes of a token row from each tensor.
-template <bool BF16, int HD>
+// delta[b, h, t] = sum_d dO[b, t, h, d] * O[b, t, h, d].  LPG (a power of two >= hd / 8) adjacent lanes own one
+// (b, t, h) row and load 16 bytes each where they fall inside the head, so a warp reads contiguous runs of a token
+// row from each tensor.
+template <bool BF16, int LPG>
 __global__ void __launch_bounds__(256)
 attn_delta_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o, long long row_stride,
-                  long long batch_stride, float* __restrict__ delta, int B, int T, int H) {
-  constexpr int LPG = HD / 8;  // lanes per row
+                  long long batch_stride, float* __restrict__ delta, int B, int T, int H, int hd) {
   const long long gt = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const long long item = gt / LPG;
   const int sub = static_cast<int>(gt % LPG);
@@ -857,15 +906,17 @@ attn_delta_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d
     const long long bt = item / H;
     t = static_cast<int>(bt % T);
     bb = static_cast<int>(bt / T);
-    const long long off = static_cast<long long>(bb) * batch_stride + static_cast<long long>(t) * row_stride + hh * HD + sub * 8;
-    const uint4 a = *reinterpret_cast<const uint4*>(o + off);
-    const uint4 g = *reinterpret_cast<const uint4*>(d_o + off);
-    const uint32_t av[4] = {a.x, a.y, a.z, a.w}, gv[4] = {g.x, g.y, g.z, g.w};
+    if (sub * 8 < hd) {
+      const long long off = static_cast<long long>(bb) * batch_stride + static_cast<long long>(t) * row_stride + hh * hd + sub * 8;
+      const uint4 a = *reinterpret_cast<const uint4*>(o + off);
+      const uint4 g = *reinterpret_cast<const uint4*>(d_o + off);
+      const uint32_t av[4] = {a.x, a.y, a.z, a.w}, gv[4] = {g.x, g.y, g.z, g.w};
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float2 x = unpack2<BF16>(av[i]);
-      const float2 y = unpack2<BF16>(gv[i]);
-      s += x.x * y.x + x.y * y.y;
+      for (int i = 0; i < 4; ++i) {
+        const float2 x = unpack2<BF16>(av[i]);
+        const float2 y = unpack2<BF16>(gv[i]);
+        s += x.x * y.x + x.y * y.y;
+      }
     }
   }
 #pragma unroll
@@ -874,14 +925,17 @@ attn_delta_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d
 }
 
 // ---------------------------------------------------------------------- host
-// [B, T, cols] view with the given strides (elements); box = 1 x 128 rows x 64 columns.
-static int make_tmap_btc(CUtensorMap* out, const void* base, int B, int T, long long cols, long long row_stride,
-                         long long batch_stride, int bf16) {
-  if ((reinterpret_cast<uintptr_t>(base) & 15) || ((row_stride * 2) & 15) || ((batch_stride * 2) & 15)) return -2;
-  cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(T), static_cast<cuuint64_t>(B)};
-  cuuint64_t strides[2] = {static_cast<cuuint64_t>(row_stride) * 2, static_cast<cuuint64_t>(batch_stride) * 2};
-  cuuint32_t box[3] = {64u, static_cast<cuuint32_t>(TILE), 1u};
-  return encode_tiled_16bit(out, base, 3, dims, strides, box, bf16) == CUDA_SUCCESS ? 0 : -3;
+// [B, T, H, hd] view with the given token / batch strides (elements) as a 4-D map (hd, H, T, B); box = 64 columns of
+// one head x 128 rows.  Columns past hd are outside the first dimension: loads fill them with zeros.
+static int make_tmap_bthd(CUtensorMap* out, const void* base, int B, int T, int H, int hd, long long row_stride,
+                          long long batch_stride, int bf16) {
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || ((row_stride * 2) & 15) || ((batch_stride * 2) & 15) || (hd & 7)) return -2;
+  cuuint64_t dims[4] = {static_cast<cuuint64_t>(hd), static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(T),
+                        static_cast<cuuint64_t>(B)};
+  cuuint64_t strides[3] = {static_cast<cuuint64_t>(hd) * 2, static_cast<cuuint64_t>(row_stride) * 2,
+                           static_cast<cuuint64_t>(batch_stride) * 2};
+  cuuint32_t box[4] = {64u, 1u, static_cast<cuuint32_t>(TILE), 1u};
+  return encode_tiled_16bit(out, base, 4, dims, strides, box, bf16) == CUDA_SUCCESS ? 0 : -3;
 }
 
 template <int HD, bool BF16, bool DROP>
@@ -914,56 +968,57 @@ static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
+// Dropout threshold (16 bits) and keep scale for a probability; false when the probability is out of range.
+static bool drop_params(float p, uint32_t& threshold16, float& inv_keep) {
+  threshold16 = 0u;
+  inv_keep = 1.f;
+  if (p < 0.f || p >= 1.f) return false;
+  threshold16 = static_cast<uint32_t>(p * 65536.f + 0.5f);
+  inv_keep = 1.f / (1.f - static_cast<float>(threshold16) / 65536.f);
+  return true;
+}
+
 }  // namespace msq
 
 static long long* g_attn_prof = nullptr;
-
-// Attention dropout of the next msq_flash_fwd / msq_flash_bwd calls made by this thread (0 = off).  Kept out of
-// the two entry points' argument lists so that callers which never use dropout are unaffected; a forward and its
-// backward must be given the same probability and seed.
-struct AttnDropState {
-  uint32_t threshold16;
-  float inv_keep;
-  unsigned long long seed;
-};
-static thread_local AttnDropState g_attn_drop = {0u, 1.f, 0ull};
-extern "C" int msq_attn_set_dropout(float p, unsigned long long seed) {
-  if (p < 0.f || p >= 1.f) return -2;
-  g_attn_drop.threshold16 = static_cast<uint32_t>(p * 65536.f + 0.5f);
-  g_attn_drop.inv_keep = 1.f / (1.f - static_cast<float>(g_attn_drop.threshold16) / 65536.f);
-  g_attn_drop.seed = seed;
-  return 0;
-}
 
 // Debug aid: when set to a device buffer of at least 512 int64, CTA (0,0,0) of the next attention
 // launches records clock64() at its phase boundaries (forward in [0,256), backward in [256,512)).
 extern "C" void msq_attn_set_prof(long long* buf) { g_attn_prof = buf; }
 
+// Head sizes the kernels take: a multiple of 8 up to 128 (64 and 128 exactly; others zero-padded to the next of them).
+extern "C" int msq_flash_head_dim_ok(int HD) { return HD >= 8 && HD <= 128 && (HD & 7) == 0; }
+
 // q, k, v: 16-bit [B, T, H, HD] views; *_rs / *_bs are row (token) and batch strides in
 // elements.  out: [B, T, H*HD] with its own strides.  lse: fp32 [B, H, T].
+// doc_start: int32 [B, T] first position of each token's document, or null (needs `causal`).
+// alibi_slopes: fp32 [H] or null.  dropout_p / seed: attention dropout (0 = off); the backward call of the same
+// forward must get the same two values.
 extern "C" int msq_flash_fwd(const void* q, const void* k, const void* v, long long q_rs, long long q_bs,
                              long long k_rs, long long k_bs, long long v_rs, long long v_bs, void* out,
                              long long o_rs, long long o_bs, float* lse, int B, int T, int H, int HD, float scale,
-                             int causal, int bf16, int* status, cudaStream_t stream) {
+                             int causal, int bf16, const int* doc_start, const float* alibi_slopes, float dropout_p,
+                             unsigned long long seed, int* status, cudaStream_t stream) {
   using namespace msq;
   if (B <= 0 || T <= 0) return 0;
-  if (HD != 64 && HD != 128) return -4;
+  if (!msq_flash_head_dim_ok(HD)) return -4;
+  if (doc_start && !causal) return -6;
   if ((reinterpret_cast<uintptr_t>(out) & 15) || (o_rs & 7) || (o_bs & 7)) return -2;
   CUtensorMap tq, tk, tv;
   int rc;
-  if ((rc = make_tmap_btc(&tq, q, B, T, static_cast<long long>(H) * HD, q_rs, q_bs, bf16))) return rc;
-  if ((rc = make_tmap_btc(&tk, k, B, T, static_cast<long long>(H) * HD, k_rs, k_bs, bf16))) return rc;
-  if ((rc = make_tmap_btc(&tv, v, B, T, static_cast<long long>(H) * HD, v_rs, v_bs, bf16))) return rc;
+  if ((rc = make_tmap_bthd(&tq, q, B, T, H, HD, q_rs, q_bs, bf16))) return rc;
+  if ((rc = make_tmap_bthd(&tk, k, B, T, H, HD, k_rs, k_bs, bf16))) return rc;
+  if ((rc = make_tmap_bthd(&tv, v, B, T, H, HD, v_rs, v_bs, bf16))) return rc;
   AttnFwdParams p;
   p.out = out; p.o_row_stride = o_rs; p.o_batch_stride = o_bs; p.lse = lse;
   p.T = T; p.H = H; p.scale_log2 = scale * LOG2E; p.causal = causal; p.bf16 = bf16; p.status = status;
   p.prof = g_attn_prof;
-  p.drop_threshold16 = g_attn_drop.threshold16;
-  p.inv_keep = g_attn_drop.inv_keep;
-  p.seed = g_attn_drop.seed;
+  p.hd = HD; p.doc_start = doc_start; p.alibi_slopes = alibi_slopes;
+  if (!drop_params(dropout_p, p.drop_threshold16, p.inv_keep)) return -2;
+  p.seed = seed;
 #define MSQ_FWD(HDV, BF) \
   (p.drop_threshold16 ? launch_fwd<HDV, BF, true>(tq, tk, tv, p, B, stream) : launch_fwd<HDV, BF, false>(tq, tk, tv, p, B, stream))
-  if (HD == 64) return bf16 ? MSQ_FWD(64, true) : MSQ_FWD(64, false);
+  if (HD <= 64) return bf16 ? MSQ_FWD(64, true) : MSQ_FWD(64, false);
   return bf16 ? MSQ_FWD(128, true) : MSQ_FWD(128, false);
 #undef MSQ_FWD
 }
@@ -974,41 +1029,45 @@ extern "C" int msq_flash_bwd(const void* q, const void* k, const void* v, const 
                              long long v_bs, long long o_rs, long long o_bs, long long do_rs, long long do_bs,
                              const float* lse, float* delta, float* dq_accum, void* dk, void* dv, long long dk_rs,
                              long long dk_bs, long long dv_rs, long long dv_bs, int B, int T, int H, int HD,
-                             float scale, int causal, int bf16, int* status, cudaStream_t stream) {
+                             float scale, int causal, int bf16, const int* doc_start, const float* alibi_slopes,
+                             float dropout_p, unsigned long long seed, int* status, cudaStream_t stream) {
   using namespace msq;
   if (B <= 0 || T <= 0) return 0;
-  if (HD != 64 && HD != 128) return -4;
+  if (!msq_flash_head_dim_ok(HD)) return -4;
+  if (doc_start && !causal) return -6;
   if (o_rs != do_rs || o_bs != do_bs) return -5;
   if ((dk_rs & 7) || (dk_bs & 7) || (dv_rs & 7) || (dv_bs & 7)) return -2;
   CUtensorMap tq, tk, tv, tdo;
   int rc;
-  if ((rc = make_tmap_btc(&tq, q, B, T, static_cast<long long>(H) * HD, q_rs, q_bs, bf16))) return rc;
-  if ((rc = make_tmap_btc(&tk, k, B, T, static_cast<long long>(H) * HD, k_rs, k_bs, bf16))) return rc;
-  if ((rc = make_tmap_btc(&tv, v, B, T, static_cast<long long>(H) * HD, v_rs, v_bs, bf16))) return rc;
-  if ((rc = make_tmap_btc(&tdo, d_out, B, T, static_cast<long long>(H) * HD, do_rs, do_bs, bf16))) return rc;
+  if ((rc = make_tmap_bthd(&tq, q, B, T, H, HD, q_rs, q_bs, bf16))) return rc;
+  if ((rc = make_tmap_bthd(&tk, k, B, T, H, HD, k_rs, k_bs, bf16))) return rc;
+  if ((rc = make_tmap_bthd(&tv, v, B, T, H, HD, v_rs, v_bs, bf16))) return rc;
+  if ((rc = make_tmap_bthd(&tdo, d_out, B, T, H, HD, do_rs, do_bs, bf16))) return rc;
   CUtensorMap tdq;
   {
-    // fp32 [B, T, H*HD] accumulator, reduced into by 32-row x 32-column boxes
+    // fp32 [B, T, H, HD] accumulator as a 4-D map (HD, H, T, B), reduced into by 32-row x 32-column boxes of one head
     if (reinterpret_cast<uintptr_t>(dq_accum) & 15) return -2;
     const cuuint64_t cols = static_cast<cuuint64_t>(H) * HD;
-    cuuint64_t dims[3] = {cols, static_cast<cuuint64_t>(T), static_cast<cuuint64_t>(B)};
-    cuuint64_t strides[2] = {cols * 4, cols * 4 * static_cast<cuuint64_t>(T)};
-    cuuint32_t box[3] = {32u, 32u, 1u};
-    if (encode_tiled(&tdq, dq_accum, 3, dims, strides, box, CU_TENSOR_MAP_DATA_TYPE_FLOAT32) != CUDA_SUCCESS) return -3;
+    cuuint64_t dims[4] = {static_cast<cuuint64_t>(HD), static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(T),
+                          static_cast<cuuint64_t>(B)};
+    cuuint64_t strides[3] = {static_cast<cuuint64_t>(HD) * 4, cols * 4, cols * 4 * static_cast<cuuint64_t>(T)};
+    cuuint32_t box[4] = {32u, 1u, 32u, 1u};
+    if (encode_tiled(&tdq, dq_accum, 4, dims, strides, box, CU_TENSOR_MAP_DATA_TYPE_FLOAT32) != CUDA_SUCCESS) return -3;
   }
   {
-    const long long nthreads = static_cast<long long>(B) * T * H * (HD / 8);
+    const int lpg = HD <= 64 ? 8 : 16;  // lanes per (b, t, h) row
+    const long long nthreads = static_cast<long long>(B) * T * H * lpg;
     const int threads = 256;
     const unsigned blocks = static_cast<unsigned>((nthreads + threads - 1) / threads);
     const uint16_t* po = static_cast<const uint16_t*>(out);
     const uint16_t* pd = static_cast<const uint16_t*>(d_out);
     if ((reinterpret_cast<uintptr_t>(out) & 15) || (reinterpret_cast<uintptr_t>(d_out) & 15) || (o_rs & 7) || (o_bs & 7)) return -2;
-    if (HD == 64) {
-      if (bf16) attn_delta_kernel<true, 64><<<blocks, threads, 0, stream>>>(po, pd, o_rs, o_bs, delta, B, T, H);
-      else attn_delta_kernel<false, 64><<<blocks, threads, 0, stream>>>(po, pd, o_rs, o_bs, delta, B, T, H);
+    if (lpg == 8) {
+      if (bf16) attn_delta_kernel<true, 8><<<blocks, threads, 0, stream>>>(po, pd, o_rs, o_bs, delta, B, T, H, HD);
+      else attn_delta_kernel<false, 8><<<blocks, threads, 0, stream>>>(po, pd, o_rs, o_bs, delta, B, T, H, HD);
     } else {
-      if (bf16) attn_delta_kernel<true, 128><<<blocks, threads, 0, stream>>>(po, pd, o_rs, o_bs, delta, B, T, H);
-      else attn_delta_kernel<false, 128><<<blocks, threads, 0, stream>>>(po, pd, o_rs, o_bs, delta, B, T, H);
+      if (bf16) attn_delta_kernel<true, 16><<<blocks, threads, 0, stream>>>(po, pd, o_rs, o_bs, delta, B, T, H, HD);
+      else attn_delta_kernel<false, 16><<<blocks, threads, 0, stream>>>(po, pd, o_rs, o_bs, delta, B, T, H, HD);
     }
   }
   AttnBwdParams p;
@@ -1016,13 +1075,13 @@ extern "C" int msq_flash_bwd(const void* q, const void* k, const void* v, const 
   p.dk_row_stride = dk_rs; p.dk_batch_stride = dk_bs; p.dv_row_stride = dv_rs; p.dv_batch_stride = dv_bs;
   p.T = T; p.H = H; p.scale = scale; p.causal = causal; p.bf16 = bf16; p.status = status;
   p.prof = g_attn_prof;
-  p.drop_threshold16 = g_attn_drop.threshold16;
-  p.inv_keep = g_attn_drop.inv_keep;
-  p.seed = g_attn_drop.seed;
+  p.hd = HD; p.doc_start = doc_start; p.alibi_slopes = alibi_slopes;
+  if (!drop_params(dropout_p, p.drop_threshold16, p.inv_keep)) return -2;
+  p.seed = seed;
 #define MSQ_BWD(HDV, BF) \
   (p.drop_threshold16 ? launch_bwd<HDV, BF, true>(tq, tk, tv, tdo, tdq, p, B, stream) \
                       : launch_bwd<HDV, BF, false>(tq, tk, tv, tdo, tdq, p, B, stream))
-  if (HD == 64) return bf16 ? MSQ_BWD(64, true) : MSQ_BWD(64, false);
+  if (HD <= 64) return bf16 ? MSQ_BWD(64, true) : MSQ_BWD(64, false);
   return bf16 ? MSQ_BWD(128, true) : MSQ_BWD(128, false);
 #undef MSQ_BWD
 }

@@ -38,7 +38,9 @@ decode_attn_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ 
                    uint16_t* __restrict__ out, const uint8_t* __restrict__ mask, int S, long long q_bs, long long kv_rs,
                    long long kv_bs, long long o_bs, long long mask_bs, float scale_log2, int splits,
                    float* __restrict__ ws, const int* __restrict__ len_ptr, const uint16_t* __restrict__ k_new,
-                   const uint16_t* __restrict__ v_new, long long new_bs, int capacity) {
+                   const uint16_t* __restrict__ v_new, long long new_bs, int capacity, int hd) {
+  // hd: the real head size (a multiple of 8, <= HD).  Lanes whose eight columns lie past it hold zeros and touch no
+  // memory, so head sizes such as 80 and 96 run the HD = 128 instantiation.
   constexpr int G = HD / 8;    // lanes per key
   constexpr int KPW = 32 / G;  // keys per warp and iteration
   const int h = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
@@ -54,9 +56,10 @@ decode_attn_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ 
   const int chunk = (S + splits - 1) / splits;
   const int s0 = split * chunk, s1 = min(S, s0 + chunk);
 
+  const bool live = part * 8 < hd;
   float qv[8];
   {
-    const uint4 v = *reinterpret_cast<const uint4*>(q + b * q_bs + h * HD + part * 8);
+    const uint4 v = live ? *reinterpret_cast<const uint4*>(q + b * q_bs + h * hd + part * 8) : make_uint4(0u, 0u, 0u, 0u);
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -68,8 +71,8 @@ decode_attn_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ 
   float m = -INFINITY, l = 0.f, acc[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-  const uint16_t* kb = kc + b * kv_bs + h * HD + part * 8;
-  const uint16_t* vb = vc + b * kv_bs + h * HD + part * 8;
+  const uint16_t* kb = kc + b * kv_bs + h * hd + part * 8;
+  const uint16_t* vb = vc + b * kv_bs + h * hd + part * 8;
   const uint8_t* mb = mask ? mask + b * mask_bs : nullptr;
   // Warp-uniform trip count: the shuffles are executed by all 32 lanes in every iteration.  The kernel is bound
   // by the cache read, so the rows of the next iteration are requested before the current ones are used (two
@@ -81,10 +84,10 @@ decode_attn_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ 
       const long long s = base + u * (STEP / DEC_UNROLL) + sub;
       kq[u] = make_uint4(0u, 0u, 0u, 0u);
       vq[u] = make_uint4(0u, 0u, 0u, 0u);
-      if (s < s1) {
+      if (s < s1 && live) {
         if (s == fresh) {
-          kq[u] = *reinterpret_cast<const uint4*>(k_new + b * new_bs + h * HD + part * 8);
-          vq[u] = *reinterpret_cast<const uint4*>(v_new + b * new_bs + h * HD + part * 8);
+          kq[u] = *reinterpret_cast<const uint4*>(k_new + b * new_bs + h * hd + part * 8);
+          vq[u] = *reinterpret_cast<const uint4*>(v_new + b * new_bs + h * hd + part * 8);
           *reinterpret_cast<uint4*>(const_cast<uint16_t*>(kb) + s * kv_rs) = kq[u];
           *reinterpret_cast<uint4*>(const_cast<uint16_t*>(vb) + s * kv_rs) = vq[u];
         } else {
@@ -193,9 +196,11 @@ decode_attn_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ 
     }
     if (splits == 1) {
       const float r = ll > 0.f ? a / ll : 0.f;
-      uint16_t* o = out + b * o_bs + h * HD + threadIdx.x;
-      if (BF16) *reinterpret_cast<__nv_bfloat16*>(o) = __float2bfloat16(r);
-      else *reinterpret_cast<__half*>(o) = __float2half(r);
+      uint16_t* o = out + b * o_bs + h * hd + threadIdx.x;
+      if (static_cast<int>(threadIdx.x) < hd) {
+        if (BF16) *reinterpret_cast<__nv_bfloat16*>(o) = __float2bfloat16(r);
+        else *reinterpret_cast<__half*>(o) = __float2half(r);
+      }
     } else {
       float* w = ws + ((static_cast<long long>(b) * gridDim.x + h) * splits + split) * (HD + 2);
       w[threadIdx.x] = a;
@@ -205,7 +210,8 @@ decode_attn_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ 
 }
 
 template <int HD, bool BF16>
-__global__ void decode_attn_merge_kernel(const float* __restrict__ ws, uint16_t* __restrict__ out, long long o_bs, int splits) {
+__global__ void decode_attn_merge_kernel(const float* __restrict__ ws, uint16_t* __restrict__ out, long long o_bs, int splits,
+                                         int hd) {
   const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
   dependents_launch();
   dependents_wait();
@@ -220,7 +226,8 @@ __global__ void decode_attn_merge_kernel(const float* __restrict__ ws, uint16_t*
     a += w[s * (HD + 2) + d] * sc;
   }
   const float r = ll > 0.f ? a / ll : 0.f;
-  uint16_t* o = out + b * o_bs + h * HD + d;
+  if (d >= hd) return;
+  uint16_t* o = out + b * o_bs + h * hd + d;
   if (BF16) *reinterpret_cast<__nv_bfloat16*>(o) = __float2bfloat16(r);
   else *reinterpret_cast<__half*>(o) = __float2half(r);
 }
@@ -228,18 +235,18 @@ __global__ void decode_attn_merge_kernel(const float* __restrict__ ws, uint16_t*
 template <int HD, bool BF16>
 static int launch_decode(const void* q, const void* kc, const void* vc, void* out, const void* mask, int B, int H, int S,
                          long long q_bs, long long kv_rs, long long kv_bs, long long o_bs, long long mask_bs, float scale,
-                         int splits, float* ws, cudaStream_t stream, const int* len_ptr = nullptr,
+                         int splits, float* ws, cudaStream_t stream, int hd, const int* len_ptr = nullptr,
                          const void* k_new = nullptr, const void* v_new = nullptr, long long new_bs = 0, int capacity = 0) {
   dim3 grid(H, B, splits);
   launch_chained(decode_attn_kernel<HD, BF16>, grid, dim3(DEC_THREADS), 0, stream, 1u,
                  static_cast<const uint16_t*>(q), static_cast<const uint16_t*>(kc), static_cast<const uint16_t*>(vc),
                  static_cast<uint16_t*>(out), static_cast<const uint8_t*>(mask), S, q_bs, kv_rs, kv_bs, o_bs, mask_bs,
                  scale * DEC_LOG2E, splits, ws, len_ptr, static_cast<const uint16_t*>(k_new),
-                 static_cast<const uint16_t*>(v_new), new_bs, capacity);
+                 static_cast<const uint16_t*>(v_new), new_bs, capacity, hd);
   if (splits > 1) {
     dim3 g2(H, B);
     launch_chained(decode_attn_merge_kernel<HD, BF16>, g2, dim3(HD), 0, stream, 1u, static_cast<const float*>(ws),
-                   static_cast<uint16_t*>(out), o_bs, splits);
+                   static_cast<uint16_t*>(out), o_bs, splits, hd);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
@@ -247,7 +254,7 @@ static int launch_decode(const void* q, const void* kc, const void* vc, void* ou
 }  // namespace msq
 
 // Number of sequence splits the launch will use for this problem (the caller sizes the workspace:
-// B * H * splits * (HD + 2) floats; none needed when the answer is 1).
+// B * H * splits * (P + 2) floats with P = 64 for head sizes up to 64 and 128 above; none needed when the answer is 1).
 extern "C" int msq_decode_attn_splits(int B, int H, int S) {
   // The kernel keeps seven CTAs per SM busy (148 * 7 = 1036 CTAs in one wave); with fewer (batch, head) pairs
   // than about five per SM the sequence is split so that the grid comes close to one full wave.
@@ -269,15 +276,15 @@ extern "C" int msq_decode_attn(const void* q, const void* kc, const void* vc, vo
                                cudaStream_t stream) {
   using namespace msq;
   if (B <= 0 || H <= 0 || S <= 0) return 0;
-  if (HD != 64 && HD != 128) return -4;
+  if (HD < 8 || HD > 128 || (HD & 7)) return -4;
   if ((q_bs & 7) || (kv_rs & 7) || (kv_bs & 7) || (reinterpret_cast<uintptr_t>(q) & 15) ||
       (reinterpret_cast<uintptr_t>(kc) & 15) || (reinterpret_cast<uintptr_t>(vc) & 15))
     return -2;
   if (splits < 1) splits = 1;
   if (splits > 1 && !workspace) return -3;
 #define MSQ_DEC(HDV, BF) \
-  return launch_decode<HDV, BF>(q, kc, vc, out, mask, B, H, S, q_bs, kv_rs, kv_bs, o_bs, mask_bs, scale, splits, workspace, stream)
-  if (HD == 64) { if (bf16) MSQ_DEC(64, true); else MSQ_DEC(64, false); }
+  return launch_decode<HDV, BF>(q, kc, vc, out, mask, B, H, S, q_bs, kv_rs, kv_bs, o_bs, mask_bs, scale, splits, workspace, stream, HD)
+  if (HD <= 64) { if (bf16) MSQ_DEC(64, true); else MSQ_DEC(64, false); }
   if (bf16) MSQ_DEC(128, true); else MSQ_DEC(128, false);
 #undef MSQ_DEC
 }
@@ -292,7 +299,7 @@ extern "C" int msq_decode_attn_step(const void* q, const void* k_new, const void
                                     float scale, int bf16, float* workspace, int splits, cudaStream_t stream) {
   using namespace msq;
   if (B <= 0 || H <= 0 || capacity <= 0) return 0;
-  if (HD != 64 && HD != 128) return -4;
+  if (HD < 8 || HD > 128 || (HD & 7)) return -4;
   if (!len_ptr || !k_new || !v_new) return -5;
   if ((q_bs & 7) || (kv_rs & 7) || (kv_bs & 7) || (new_bs & 7) || (reinterpret_cast<uintptr_t>(q) & 15) ||
       (reinterpret_cast<uintptr_t>(kc) & 15) || (reinterpret_cast<uintptr_t>(vc) & 15) ||
@@ -302,8 +309,8 @@ extern "C" int msq_decode_attn_step(const void* q, const void* k_new, const void
   if (splits > 1 && !workspace) return -3;
 #define MSQ_DEC(HDV, BF) \
   return launch_decode<HDV, BF>(q, kc, vc, out, mask, B, H, 0, q_bs, kv_rs, kv_bs, o_bs, mask_bs, scale, splits, workspace, \
-                                stream, len_ptr, k_new, v_new, new_bs, capacity)
-  if (HD == 64) { if (bf16) MSQ_DEC(64, true); else MSQ_DEC(64, false); }
+                                stream, HD, len_ptr, k_new, v_new, new_bs, capacity)
+  if (HD <= 64) { if (bf16) MSQ_DEC(64, true); else MSQ_DEC(64, false); }
   if (bf16) MSQ_DEC(128, true); else MSQ_DEC(128, false);
 #undef MSQ_DEC
 }

@@ -386,6 +386,162 @@ vp_ce_finish_kernel(uint16_t* __restrict__ logits, long long ld, const long long
   }
 }
 
+// ---------------------------------------- cross entropy from the logits product's row statistics
+// The logits GEMM (msq_gemm2_rowstats) leaves, per column tile and row, the maximum of the stored logits and the sum
+// of exp(logit - max).  One warp per row folds the tiles into this rank's triple (max, sum-exp, target logit) and
+// delivers it: to a local [rows, 3] table (one rank), or into the exchange table of every tensor-parallel peer over
+// NVLink (plain peer stores, no library collective).  An exchanged value travels as an 8-byte unit {fp32 value,
+// epoch}; 8-byte stores are indivisible, so a reader that sees the epoch it waits for also sees the value, and no
+// separate flag, fence or remote load is needed.  Table layout on every rank: unit[(src_rank * rows_cap + row) * 3 + k].
+struct CePeers {
+  unsigned long long* table[16];
+};
+
+template <bool BF16>
+__global__ void __launch_bounds__(256)
+ce_merge_rowstats_kernel(const float* __restrict__ rs_max, const float* __restrict__ rs_sum, int tiles_n, int rows,
+                         const uint16_t* __restrict__ logits, long long ld, const long long* __restrict__ target,
+                         int V, long long vocab_start, float* __restrict__ local_stats, CePeers peers, int world,
+                         int rank, int rows_cap, uint32_t epoch) {
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
+    float m = -INFINITY;
+    for (int t = lane; t < tiles_n; t += 32) m = fmaxf(m, rs_max[static_cast<long long>(t) * rows + r]);
+    m = warp_max(m);
+    float s = 0.f;
+    for (int t = lane; t < tiles_n; t += 32) {
+      const long long i = static_cast<long long>(t) * rows + r;
+      s += rs_sum[i] * __expf(rs_max[i] - m);
+    }
+    s = warp_sum(s);
+    if (lane < 3) {
+      float val = lane == 0 ? m : s;
+      if (lane == 2) {
+        const long long lt = target[r] - vocab_start;
+        val = 0.f;
+        if (lt >= 0 && lt < V) {
+          const uint16_t raw = logits[static_cast<long long>(r) * ld + lt];
+          val = BF16 ? __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(&raw))
+                     : __half2float(*reinterpret_cast<const __half*>(&raw));
+        }
+      }
+      if (world <= 1) {
+        local_stats[static_cast<long long>(r) * 3 + lane] = val;
+      } else {
+        const unsigned long long unit =
+            (static_cast<unsigned long long>(epoch) << 32) | static_cast<unsigned long long>(__float_as_uint(val));
+        const long long slot = (static_cast<long long>(rank) * rows_cap + r) * 3 + lane;
+        for (int w = 0; w < world; ++w) {
+          unsigned long long* dst = peers.table[(rank + w) % world] + slot;  // own table first, then round the ring
+          asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst), "l"(unit) : "memory");
+        }
+      }
+    }
+  }
+}
+
+// Second half on every rank: waits (bounded) until the triples of all ranks for a row carry `epoch`, combines them
+// into the global log-sum-exp, writes the loss and overwrites the local logits with (softmax - onehot) * grad_scale.
+template <bool BF16>
+__global__ void __launch_bounds__(256)
+vp_ce_finish_exchanged_kernel(uint16_t* __restrict__ logits, long long ld, const long long* __restrict__ target,
+                              const unsigned long long* __restrict__ table, int world, int rows_cap, uint32_t epoch,
+                              float* __restrict__ loss, int rows, int V, long long vocab_start,
+                              long long ignore_index, float grad_scale, int* __restrict__ status) {
+  __shared__ float trip[16 * 3];
+  __shared__ int failed;
+  const int nvec = V >> 3;
+  if (threadIdx.x == 0) failed = (status && *reinterpret_cast<volatile int*>(status) != 0) ? 1 : 0;
+  __syncthreads();
+  if (failed) return;  // an earlier kernel timed out: do nothing until the host has cleared the status word
+  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    if (threadIdx.x < world * 3) {
+      const int w = threadIdx.x / 3, k = threadIdx.x - w * 3;
+      const unsigned long long* src = table + (static_cast<long long>(w) * rows_cap + r) * 3 + k;
+      const unsigned long long t0 = globaltimer_ns();
+      unsigned long long unit;
+      uint32_t spins = 0;
+      while (true) {
+        asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(unit) : "l"(src) : "memory");
+        if (static_cast<uint32_t>(unit >> 32) == epoch) break;
+        if ((++spins & 0x3f) == 0) {
+          if (globaltimer_ns() - t0 > WAIT_NS_PEER) {
+            if (status) atomicCAS(status, 0, ST_TIMEOUT_PEER_FLAG);
+            failed = 1;
+            break;
+          }
+          __nanosleep(200);
+        }
+      }
+      trip[threadIdx.x] = __uint_as_float(static_cast<uint32_t>(unit));
+    }
+    __syncthreads();
+    if (failed) return;
+    float gmax = -INFINITY;
+    for (int w = 0; w < world; ++w) gmax = fmaxf(gmax, trip[w * 3]);
+    float gsum = 0.f, tl = 0.f;
+    for (int w = 0; w < world; ++w) {
+      gsum += trip[w * 3 + 1] * __expf(trip[w * 3] - gmax);
+      tl += trip[w * 3 + 2];
+    }
+    __syncthreads();  // trip is rewritten for the next row
+    const float lse = gmax + __logf(gsum);
+    const long long tgt = target[r];
+    const bool ignored = tgt == ignore_index;
+    if (threadIdx.x == 0 && loss) loss[r] = ignored ? 0.f : (lse - tl);
+    const float gs = ignored ? 0.f : grad_scale;
+    const long long lt = tgt - vocab_start;
+    uint16_t* grow = logits + static_cast<long long>(r) * ld;
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+      const uint4 a = *reinterpret_cast<const uint4*>(grow + v * 8);
+      const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+      float f[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 t = unpack2<BF16>(w[j]);
+        f[2 * j] = __expf(t.x - lse) * gs;
+        f[2 * j + 1] = __expf(t.y - lse) * gs;
+      }
+      const long long c0 = static_cast<long long>(v) * 8;
+      if (!ignored && lt >= c0 && lt < c0 + 8) f[lt - c0] -= gs;
+      uint4 o;
+      o.x = pack2<BF16>(f[0], f[1]);
+      o.y = pack2<BF16>(f[2], f[3]);
+      o.z = pack2<BF16>(f[4], f[5]);
+      o.w = pack2<BF16>(f[6], f[7]);
+      *reinterpret_cast<uint4*>(grow + v * 8) = o;
+    }
+  }
+}
+
+// x[r, :] *= g[r or 0] * inv_ref, rows whose factor is exactly 1 left untouched (not even read).  The forward pass
+// stores a gradient already multiplied by the factor it expects from upstream (the loss scale, 1 / inv_ref); when
+// the backward pass brings exactly that factor this launch costs a few microseconds instead of a pass over memory.
+template <bool BF16, typename G>
+__global__ void __launch_bounds__(256)
+scale_rows_rel_kernel(uint16_t* __restrict__ x, long long ld, long long rows, int cols, const G* __restrict__ g,
+                      int per_row, float inv_ref) {
+  const int nvec = cols >> 3;
+  if (!per_row && static_cast<float>(g[0]) * inv_ref == 1.f) return;
+  for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
+    const float f = static_cast<float>(g[per_row ? r : 0]) * inv_ref;
+    if (f == 1.f) continue;
+    uint16_t* row = x + r * ld;
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+      uint4* p = reinterpret_cast<uint4*>(row + v * 8);
+      const uint4 a = *p;
+      uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 t = unpack2<BF16>(w[j]);
+        w[j] = pack2<BF16>(t.x * f, t.y * f);
+      }
+      *p = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+}
+
 // ------------------------------------------------------------------ colsum
 // acc[n] += sum over a slice of rows of x[m, n]; fp32 atomics, one per column
 // per CTA.  Block = 32 x 8 threads, each thread owns 8 adjacent columns.
@@ -580,6 +736,63 @@ extern "C" int msq_vp_ce_finish(void* logits, long long ld, const long long* tar
   const int grid = rows < 148 * 8 ? rows : 148 * 8;
   if (bf16) vp_ce_finish_kernel<true><<<grid, 256, 0, stream>>>(static_cast<uint16_t*>(logits), ld, target, stats, world, loss, rows, V, vocab_start, ignore_index, grad_scale);
   else vp_ce_finish_kernel<false><<<grid, 256, 0, stream>>>(static_cast<uint16_t*>(logits), ld, target, stats, world, loss, rows, V, vocab_start, ignore_index, grad_scale);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// Folds the row statistics of msq_gemm2_rowstats (rs_max / rs_sum: [tiles_n, rows]) into per-row triples (max,
+// sum-exp, target logit).  world <= 1: written to local_stats ([rows, 3] fp32).  world > 1: stored as {value, epoch}
+// units into peer_tables[w] (one table of world * rows_cap * 3 units per rank, this rank's included) at this rank's
+// block; `epoch` must differ from the one of the previous use of the same tables.
+extern "C" int msq_ce_merge_rowstats(const float* rs_max, const float* rs_sum, int tiles_n, int rows, const void* logits,
+                                     long long ld, const long long* target, int V, long long vocab_start,
+                                     float* local_stats, void* const* peer_tables, int world, int rank, int rows_cap,
+                                     unsigned epoch, int bf16, cudaStream_t stream) {
+  using namespace msq;
+  if (rows <= 0) return 0;
+  if (tiles_n <= 0 || world > 16 || (world > 1 && (!peer_tables || rows > rows_cap)) || (world <= 1 && !local_stats)) return -2;
+  CePeers peers;
+  for (int i = 0; i < 16; ++i)
+    peers.table[i] = (world > 1 && i < world) ? static_cast<unsigned long long*>(peer_tables[i]) : nullptr;
+  int grid = (rows + 7) / 8;
+  if (grid > 148 * 8) grid = 148 * 8;
+  const uint16_t* lg = static_cast<const uint16_t*>(logits);
+  if (bf16) ce_merge_rowstats_kernel<true><<<grid, 256, 0, stream>>>(rs_max, rs_sum, tiles_n, rows, lg, ld, target, V, vocab_start, local_stats, peers, world, rank, rows_cap, epoch);
+  else ce_merge_rowstats_kernel<false><<<grid, 256, 0, stream>>>(rs_max, rs_sum, tiles_n, rows, lg, ld, target, V, vocab_start, local_stats, peers, world, rank, rows_cap, epoch);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// msq_vp_ce_finish reading the triples from this rank's exchange table (filled by msq_ce_merge_rowstats on every
+// rank).  Waits are bounded; a timeout sets *status and leaves the remaining rows untouched.
+extern "C" int msq_vp_ce_finish_exchanged(void* logits, long long ld, const long long* target, const void* table,
+                                          int world, int rows_cap, unsigned epoch, float* loss, int rows, int V,
+                                          long long vocab_start, long long ignore_index, float grad_scale, int bf16,
+                                          int* status, cudaStream_t stream) {
+  using namespace msq;
+  if (rows <= 0) return 0;
+  if ((V & 7) || (ld & 7) || (reinterpret_cast<uintptr_t>(logits) & 15) || world < 1 || world > 16 || rows > rows_cap) return -2;
+  const int grid = rows < 148 * 8 ? rows : 148 * 8;
+  const unsigned long long* tb = static_cast<const unsigned long long*>(table);
+  if (bf16) vp_ce_finish_exchanged_kernel<true><<<grid, 256, 0, stream>>>(static_cast<uint16_t*>(logits), ld, target, tb, world, rows_cap, epoch, loss, rows, V, vocab_start, ignore_index, grad_scale, status);
+  else vp_ce_finish_exchanged_kernel<false><<<grid, 256, 0, stream>>>(static_cast<uint16_t*>(logits), ld, target, tb, world, rows_cap, epoch, loss, rows, V, vocab_start, ignore_index, grad_scale, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// msq_scale_rows relative to a reference: factors are g * inv_ref and rows whose factor is 1 are skipped.
+extern "C" int msq_scale_rows_rel(void* x, long long ld, long long rows, int cols, const void* g, int g_fp32, int per_row,
+                                  float inv_ref, int bf16, cudaStream_t stream) {
+  using namespace msq;
+  if (rows <= 0 || cols <= 0) return 0;
+  if ((cols & 7) || (ld & 7) || (reinterpret_cast<uintptr_t>(x) & 15)) return -2;
+  const int nb = rows < 148 * 16 ? static_cast<int>(rows) : 148 * 16;
+  uint16_t* xp = static_cast<uint16_t*>(x);
+  if (g_fp32) {
+    if (bf16) scale_rows_rel_kernel<true, float><<<nb, 256, 0, stream>>>(xp, ld, rows, cols, static_cast<const float*>(g), per_row, inv_ref);
+    else scale_rows_rel_kernel<false, float><<<nb, 256, 0, stream>>>(xp, ld, rows, cols, static_cast<const float*>(g), per_row, inv_ref);
+  } else if (bf16) {
+    scale_rows_rel_kernel<true, __nv_bfloat16><<<nb, 256, 0, stream>>>(xp, ld, rows, cols, static_cast<const __nv_bfloat16*>(g), per_row, inv_ref);
+  } else {
+    scale_rows_rel_kernel<false, __half><<<nb, 256, 0, stream>>>(xp, ld, rows, cols, static_cast<const __half*>(g), per_row, inv_ref);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

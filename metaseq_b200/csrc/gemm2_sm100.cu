@@ -52,6 +52,11 @@ struct Gemm2Params {
   void* scatter_base[16];
   int scatter_world;
   int scatter_rows;
+  // Row statistics of the stored output (softmax pieces for a cross entropy that follows a logits product):
+  // for column tile tn, rs_max[tn * M + r] = max over the tile's columns of row r and rs_sum[tn * M + r] =
+  // sum of exp(value - that max), both over the values as rounded for storage.  Null = not computed.
+  float* rs_max;
+  float* rs_sum;
 };
 
 // Bounded wait until every chunk overlapping bytes [lo, hi) of the gathered buffer has arrived.
@@ -318,21 +323,31 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       uint32_t phase = 0;
       bool ok = true;
       int it = 0;
+#ifdef MSQ_GEMM2_PROF
       long long prof_tempty = 0, prof_full = 0;
       const long long prof_t0 = clock64();
+#endif
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++it) {
         const int buf = it & 1;
         const uint32_t acc = tmem_base + buf * G2_BN;
+#ifdef MSQ_GEMM2_PROF
         const long long c0 = clock64();
+#endif
         ok = mbar_wait(&tempty_bar[buf], ((it >> 1) & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
         if (!ok) break;
+#ifdef MSQ_GEMM2_PROF
         prof_tempty += clock64() - c0;
+#endif
         tc_fence_after();
         for (int kb = 0; kb < k_blocks; ++kb) {
+#ifdef MSQ_GEMM2_PROF
           const long long c1 = clock64();
+#endif
           ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
           if (!ok) break;
+#ifdef MSQ_GEMM2_PROF
           prof_full += clock64() - c1;
+#endif
           tc_fence_after();
           const uint32_t a_addr = smem_u32(sA + stage * G2_A_BYTES);
           const uint32_t b_addr = smem_u32(sB + stage * G2_B_BYTES);
@@ -351,12 +366,14 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         if (!ok) break;
         tc_commit_pair(&tfull_bar[buf]);  // accumulator ready in both CTAs
       }
+#ifdef MSQ_GEMM2_PROF
       if (p.prof && pair == 0) {
         p.prof[0] = clock64() - prof_t0;
         p.prof[1] = prof_tempty;
         p.prof[2] = prof_full;
         p.prof[3] = it;
       }
+#endif
     }
   } else {
     // ---------------------------------------------------------------- epilogue (both CTAs)
@@ -381,6 +398,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       uint8_t* stage = sEpi + (warp - 2) * 2048;
       const int st_row = lane >> 2, st_vec = lane & 3;
       const uint32_t taddr0 = tmem_base + buf * G2_BN + (static_cast<uint32_t>(quarter * 32) << 16);
+      float rs_m = -INFINITY, rs_s = 0.f;  // this lane's row: running max and sum of exp(x - max) over the tile
 #pragma unroll 1
       for (int c = 0; c < G2_BN / 32; ++c) {
         const int col0 = tn * G2_BN + c * 32;
@@ -452,6 +470,25 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                 o.z = pack2<false>(f[4], f[5]); o.w = pack2<false>(f[6], f[7]);
               }
               *reinterpret_cast<uint4*>(stage + lane * 64 + ((v ^ ((lane >> 1) & 3)) << 4)) = o;
+              if (p.rs_max) {
+                const uint32_t ow[4] = {o.x, o.y, o.z, o.w};
+                float g[8];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float2 t = p.bf16 ? unpack2<true>(ow[j]) : unpack2<false>(ow[j]);
+                  g[2 * j] = t.x;
+                  g[2 * j + 1] = t.y;
+                }
+                float vm = g[0];
+#pragma unroll
+                for (int j = 1; j < 8; ++j) vm = fmaxf(vm, g[j]);
+                if (vm > rs_m) {
+                  rs_s *= __expf(rs_m - vm);  // exp(-inf) = 0 on the first vector
+                  rs_m = vm;
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) rs_s += __expf(g[j] - rs_m);
+              }
             }
           }
         }
@@ -473,6 +510,10 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           }
         }
         __syncwarp();
+      }
+      if (p.rs_max && row_ok) {
+        p.rs_max[static_cast<long long>(tn) * p.M + row] = rs_m;
+        p.rs_sum[static_cast<long long>(tn) * p.M + row] = rs_s;
       }
       tc_fence_before();
       __syncwarp();
@@ -515,7 +556,8 @@ static int launch_gemm2(const CUtensorMap& tmA, const CUtensorMap& tmB, const Ge
 }  // namespace msq
 
 static long long* g_gemm2_prof = nullptr;
-// Debug aid: device buffer of 4 int64 that receives, from the MMA thread of pair 0 of the next launches,
+// Debug aid (builds with -DMSQ_GEMM2_PROF only; otherwise the MMA thread carries no timing code and the buffer
+// stays untouched): device buffer of 4 int64 that receives, from the MMA thread of pair 0 of the next launches,
 // {total cycles, cycles waiting for a free accumulator, cycles waiting for operand stages, tiles}.
 extern "C" void msq_gemm2_set_prof(long long* buf) { g_gemm2_prof = buf; }
 
@@ -547,7 +589,22 @@ static int gemm2_common(const void* A, const void* B, void* C, int M, int N, int
                         long long ldc, int a_mn, int b_mn, int bf16, const void* bias, const void* residual,
                         long long ldr, const void* mask, long long ldm, int relu, int accumulate,
                         int max_ctas, int* status, cudaStream_t stream, const MsqGemmReady* ready,
-                        void* const* scatter_ptrs, int scatter_world, int scatter_rows);
+                        void* const* scatter_ptrs, int scatter_world, int scatter_rows, float* rs_max = nullptr,
+                        float* rs_sum = nullptr);
+
+// Column tiles of the pair kernel for N output columns: the first dimension of the row-statistics tables.
+extern "C" int msq_gemm2_tiles_n(int N) { return (N + msq::G2_BN - 1) / msq::G2_BN; }
+
+// msq_gemm2_ready that also fills the row-statistics tables rs_max / rs_sum ([msq_gemm2_tiles_n(N), M] fp32 each):
+// the producer half of cross entropy fused with the logits product.
+extern "C" int msq_gemm2_rowstats(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                                  long long ldb, long long ldc, int a_mn, int b_mn, int bf16, const void* bias,
+                                  float* rs_max, float* rs_sum, int max_ctas, int* status, cudaStream_t stream,
+                                  const MsqGemmReady* ready) {
+  if (!rs_max || !rs_sum) return -4;
+  return gemm2_common(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, bf16, bias, nullptr, 0, nullptr, 0, 0, 0, max_ctas,
+                      status, stream, ready, nullptr, 0, 0, rs_max, rs_sum);
+}
 
 extern "C" int msq_gemm2_ready(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                                long long ldc, int a_mn, int b_mn, int bf16, const void* bias, const void* residual,
@@ -574,7 +631,7 @@ static int gemm2_common(const void* A, const void* B, void* C, int M, int N, int
                         long long ldc, int a_mn, int b_mn, int bf16, const void* bias, const void* residual,
                         long long ldr, const void* mask, long long ldm, int relu, int accumulate,
                         int max_ctas, int* status, cudaStream_t stream, const MsqGemmReady* ready,
-                        void* const* scatter_ptrs, int scatter_world, int scatter_rows) {
+                        void* const* scatter_ptrs, int scatter_world, int scatter_rows, float* rs_max, float* rs_sum) {
   using namespace msq;
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || (N & 7) || (ldc & 7) || (reinterpret_cast<uintptr_t>(C) & 15)) return -4;
@@ -595,6 +652,8 @@ static int gemm2_common(const void* A, const void* B, void* C, int M, int N, int
   p.bias = bias; p.residual = residual; p.ldr = ldr; p.mask = mask; p.ldm = ldm;
   p.relu = relu; p.accumulate = accumulate; p.bf16 = bf16; p.status = status;
   p.prof = g_gemm2_prof;
+  p.rs_max = rs_max;
+  p.rs_sum = rs_sum;
   p.scatter_world = scatter_world;
   p.scatter_rows = scatter_rows;
   for (int i = 0; i < 16; ++i) p.scatter_base[i] = (scatter_ptrs && i < scatter_world) ? scatter_ptrs[i] : nullptr;

@@ -75,6 +75,87 @@ sumsq_finalize_kernel(const float* __restrict__ scratch, int parts, float* __res
   if (threadIdx.x == 0) out[0] = total + (accumulate ? out[0] : 0.f);
 }
 
+// List form (the reference's apex multi_tensor_l2norm: metaseq/modules/apex/multi_tensor_l2norm_kernel.cu:58-140):
+// one launch covers every tensor of a table in device memory.  CTA b works on the tensor whose block range
+// [first_block, next first_block) contains b, writes its partial to scratch[b], and the CTA that finishes last
+// (a ticket counter, reset for the next call) adds all partials in index order, so the result does not depend on
+// the order in which CTAs ran.
+struct SumsqTensor {
+  const void* g;
+  long long n;
+  long long first_block;  // of a table with count + 1 entries; the last entry holds the total block count
+};
+
+template <int DT>
+__global__ void __launch_bounds__(SUMSQ_THREADS)
+sumsq_multi_kernel(const SumsqTensor* __restrict__ table, int count, float* __restrict__ scratch,
+                   unsigned* __restrict__ ticket, float* __restrict__ out, int accumulate) {
+  __shared__ float red[32];
+  __shared__ int s_idx;
+  __shared__ bool s_last;
+  const int b = blockIdx.x;
+  if (threadIdx.x == 0) {
+    int lo = 0, hi = count - 1;  // last tensor whose first_block <= b
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (table[mid].first_block <= b) lo = mid; else hi = mid - 1;
+    }
+    s_idx = lo;
+  }
+  __syncthreads();
+  const SumsqTensor t = table[s_idx];
+  const long long nblk = table[s_idx + 1].first_block - t.first_block;
+  const long long tid = (static_cast<long long>(b) - t.first_block) * blockDim.x + threadIdx.x;
+  const long long stride = nblk * blockDim.x;
+  float acc = 0.f;
+  const bool aligned = (reinterpret_cast<uintptr_t>(t.g) & 15) == 0;
+  long long done = 0;
+  if (aligned) {
+    if constexpr (DT == 2) {
+      const long long n4 = t.n >> 2;
+      const float4* g4 = static_cast<const float4*>(t.g);
+      for (long long i = tid; i < n4; i += stride) {
+        const float4 v = g4[i];
+        acc += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+      }
+      done = n4 << 2;
+    } else {
+      const long long n8 = t.n >> 3;
+      const uint4* g8 = static_cast<const uint4*>(t.g);
+      for (long long i = tid; i < n8; i += stride) {
+        const uint4 v = g8[i];
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack2<DT == 1>(w[j]);
+          acc += f.x * f.x + f.y * f.y;
+        }
+      }
+      done = n8 << 3;
+    }
+  }
+  for (long long i = done + tid; i < t.n; i += stride) {
+    const float v = load_as_float<DT>(t.g, i);
+    acc += v * v;
+  }
+  const float total = block_sum(acc, red);
+  if (threadIdx.x == 0) {
+    scratch[b] = total;
+    __threadfence();
+    s_last = atomicAdd(ticket, 1u) == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  float sum = 0.f;
+  for (int i = threadIdx.x; i < static_cast<int>(gridDim.x); i += blockDim.x) sum += __ldcg(scratch + i);
+  sum = block_sum(sum, red);
+  if (threadIdx.x == 0) {
+    out[0] = sum + (accumulate ? out[0] : 0.f);
+    *ticket = 0;
+  }
+}
+
 // ctrl_out[0] = multiplier the update applies to raw grads (pre_factor * clip_coef)
 // ctrl_out[1] = 1 when the step must be skipped (non-finite norm), else 0
 // ctrl_out[2] = unclipped gradient norm (pre_factor * sqrt(sum of squares))
@@ -229,6 +310,22 @@ extern "C" int msq_sumsq(const void* g, long long n, int dtype, float* scratch, 
   else if (dtype == 2) sumsq_partial_kernel<2><<<parts, SUMSQ_THREADS, 0, stream>>>(g, n, scratch);
   else return -2;
   sumsq_finalize_kernel<<<1, SUMSQ_THREADS, 0, stream>>>(scratch, parts, out, accumulate);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// List form of msq_sumsq.  `table`: count + 1 records {pointer, elements, first block} (3 x 8 bytes) in device
+// memory, the block ranges consecutive and the last record's first block = total_blocks; `scratch`: total_blocks
+// floats; `ticket`: one zero-initialised unsigned that the kernel leaves at zero.  All tensors share `dtype`.
+// Note block_sum sums per-thread values in a fixed order, so equal inputs give equal bits from call to call.
+extern "C" int msq_sumsq_multi(const void* table, int count, int total_blocks, int dtype, float* scratch,
+                               unsigned* ticket, float* out, int accumulate, cudaStream_t stream) {
+  using namespace msq;
+  if (count <= 0 || total_blocks <= 0) return 0;
+  const SumsqTensor* tb = static_cast<const SumsqTensor*>(table);
+  if (dtype == 0) sumsq_multi_kernel<0><<<total_blocks, SUMSQ_THREADS, 0, stream>>>(tb, count, scratch, ticket, out, accumulate);
+  else if (dtype == 1) sumsq_multi_kernel<1><<<total_blocks, SUMSQ_THREADS, 0, stream>>>(tb, count, scratch, ticket, out, accumulate);
+  else if (dtype == 2) sumsq_multi_kernel<2><<<total_blocks, SUMSQ_THREADS, 0, stream>>>(tb, count, scratch, ticket, out, accumulate);
+  else return -2;
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

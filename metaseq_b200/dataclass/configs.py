@@ -109,6 +109,9 @@ class CommonConfig(MetaseqDataclass):
     # additions of this framework
     kernel_backend: str = opt("auto", "operator backend: sm_100a kernels when possible (auto) or PyTorch/cuBLAS "
                               "ops everywhere (torch), which is the unfused baseline", choices=("auto", "torch"))
+    strict_kernels: bool = opt(False, "raise when an operator on CUDA 16-bit tensors would leave the sm_100a "
+                                      "kernels for PyTorch ops (unsupported head size, stride or alignment) "
+                                      "instead of logging the fallback once")
     comm_backend: str = opt("fused", "collective path for FSDP / tensor parallel hot ops: in-kernel NVLink peer "
                             "access (fused) or NCCL calls (nccl)", choices=("fused", "nccl"))
 

@@ -73,6 +73,8 @@ class GraphedDecodeStep:
             return False
         if decoder.self_attn_doc_sep != UNSPECIFIED_DOC_SEP or w.shape[1] % 8 != 0:
             return False
+        if getattr(decoder, "alibi_slopes", None) is not None:
+            return False  # the decode-attention kernel carries no position bias
         if decoder.embed_positions is not None and not hasattr(decoder.embed_positions, "weight"):
             return False
         if decoder.layer_norm is None or decoder.layer_norm.weight is None \
@@ -82,7 +84,7 @@ class GraphedDecodeStep:
             if not isinstance(layer, TransformerDecoderLayer):
                 return False
             a = layer.self_attn
-            if layer.activation_name not in ("relu", "gelu") or a.head_dim not in (64, 128):
+            if layer.activation_name not in ("relu", "gelu") or not F.decode_head_dim_ok(a.head_dim):
                 return False
             for lin in (a.qkv_proj, a.out_proj, layer.fc1, layer.fc2):
                 if lin.weight.dtype != w.dtype or lin.weight.shape[0] % 8 or lin.weight.shape[1] % 8:

@@ -105,6 +105,16 @@ class ModelParallelTransformerDecoder(IncrementalDecoder):
             self.output_projection = _TiedProjection(w)
         self.inference = False
         self._cache_key = "decoder_state_" + str(id(self))
+        # ALiBi: learned positions are off (above) and every head adds slope * key position to its scores; this
+        # rank's heads are a contiguous slice of the slope list
+        self.alibi_slopes = None
+        if _get(args, "alibi", False):
+            from metaseq_b200.modules.attention_bias import alibi_slopes
+
+            tp, rank = mpu.get_tensor_model_parallel_world_size(), mpu.get_tensor_model_parallel_rank()
+            per = args.decoder_attention_heads // tp
+            self.alibi_slopes = torch.tensor(alibi_slopes(args.decoder_attention_heads)[rank * per:(rank + 1) * per],
+                                             dtype=torch.float32)
 
     def build_decoder_layer(self, args):
         layer = ModelParallelTransformerDecoderLayer(args)
@@ -214,14 +224,18 @@ class ModelParallelTransformerDecoder(IncrementalDecoder):
         if self.training and incremental_state is None and _get(self.args, "log_activation_norms", True):
             with torch.no_grad():
                 norms = self._embedding_norm_sums(prev_output_tokens, positions, x)
+        # What attention sees beyond causality travels in its compact form: one document start per token (a token
+        # attends only inside its own document; not applied while decoding incrementally) and one ALiBi slope per
+        # head.  The flash-attention kernels take both directly; other paths expand them to an additive mask.
         attn_mask = None
-        if doc_start is not None and incremental_state is None:
-            # block-diagonal causal mask: a token attends only inside its own document
-            idx = torch.arange(T, device=x.device)
-            same_doc = doc_start[:, :, None] == doc_start[:, None, :]
-            causal = idx[None, :, None] >= idx[None, None, :]
-            attn_mask = torch.zeros(B, 1, T, T, device=x.device, dtype=torch.float32)
-            attn_mask.masked_fill_(~(same_doc & causal)[:, None], float("-inf"))
+        use_doc = doc_start is not None and incremental_state is None
+        if use_doc or self.alibi_slopes is not None:
+            from metaseq_b200.modules.attention_bias import AttentionBias
+
+            if self.alibi_slopes is not None and self.alibi_slopes.device != x.device:
+                self.alibi_slopes = self.alibi_slopes.to(x.device)
+            attn_mask = AttentionBias(doc_start=doc_start.to(torch.int32) if use_doc else None,
+                                      slopes=self.alibi_slopes)
         if self.sequence_parallel:
             x = mappings.scatter_to_sequence_parallel_region(x.reshape(B * T, -1))
         inner_states: List[Optional[torch.Tensor]] = []
@@ -243,15 +257,21 @@ class ModelParallelTransformerDecoder(IncrementalDecoder):
         if kwargs.get("norm_sums") is not None:  # final activations, all positions (after the sequence gather)
             with torch.no_grad():
                 kwargs["norm_sums"]["actv"] = torch.linalg.vector_norm(features.detach(), dim=-1, dtype=torch.float32).sum()
+        vocab_parallel = _get(self.args, "criterion", None) == "vocab_parallel_cross_entropy"
+        gather = tp > 1 and (self.inference or not vocab_parallel)
+        # training straight into a cross entropy: the product also leaves the softmax pieces of every row
+        want_stats = self.training and not gather and torch.is_grad_enabled()
         if ops_f.use_kernels(features) and features.dtype == w.dtype and w.shape[0] % 8 == 0:
-            logits = ops_ag.linear(features, w)
+            logits = ops_ag.linear(features, w, row_stats=want_stats)
         else:
             logits = torch.nn.functional.linear(features, w)
-        vocab_parallel = _get(self.args, "criterion", None) == "vocab_parallel_cross_entropy"
-        if tp > 1 and (self.inference or not vocab_parallel):
+        row_stats = getattr(logits, "_msq_row_stats", None)
+        if gather:
             logits = mappings.gather_from_tensor_model_parallel_region(logits)
         if logits.dim() == 2 and "bt" in kwargs:
             logits = logits.view(*kwargs["bt"], -1)
+        if row_stats is not None:
+            logits._msq_row_stats = row_stats
         return logits
 
     def max_positions(self):

@@ -48,6 +48,9 @@ class LayerSpec:
     dropout_p: float = 0.0
     attn_dropout_p: float = 0.0
     seeds: Any = None
+    # attention beyond causality: per-token document starts ([B, T]) and per-head ALiBi slopes ([heads_local])
+    doc_start: Any = None
+    alibi_slopes: Any = None
 
 
 def _all_reduce(t, spec):
@@ -129,7 +132,7 @@ def _forward(x2, p, spec: LayerSpec):
     q = q3[..., 2 * Dp:].view(B, T, H, d)
     s_attn, s_res1, s_res2 = spec.seeds if spec.seeds is not None else (None, None, None)
     ctx, lse = F.flash_attn_fwd(q, k, v, spec.scale, True, dropout_p=spec.attn_dropout_p if s_attn is not None else 0.0,
-                                seed=s_attn or 0)
+                                seed=s_attn or 0, doc_start=spec.doc_start, alibi_slopes=spec.alibi_slopes)
     ctx2 = ctx.view(B * T, Dp)
     x_mid = _row_parallel_out(ctx2, out_w, out_b, x2, spec, s_res1)
     h2, mean2, rstd2 = F.layer_norm_fwd(x_mid, ln2_w, ln2_b, spec.eps)
@@ -229,7 +232,8 @@ class FusedDecoderLayerFn(torch.autograd.Function):
         sl = lambda t, i: t[..., i * Dp:(i + 1) * Dp].view(B, T, H, d)
         F.flash_attn_bwd(sl(q3, 2), sl(q3, 0), sl(q3, 1), attn, d_attn.view(B, T, Dp), lse, spec.scale, True,
                          sl(dq3, 2), sl(dq3, 0), sl(dq3, 1),
-                         dropout_p=spec.attn_dropout_p if s_attn is not None else 0.0, seed=s_attn or 0)
+                         dropout_p=spec.attn_dropout_p if s_attn is not None else 0.0, seed=s_attn or 0,
+                         doc_start=spec.doc_start, alibi_slopes=spec.alibi_slopes)
         del d_attn
         # ---- QKV (column parallel)
         dh1 = _dgrad_reduced(dqkv, qkv_w, spec)

@@ -22,6 +22,7 @@ import torch.nn as nn
 import torch.nn.functional as TF
 
 from metaseq_b200 import utils
+from metaseq_b200.modules.attention_bias import AttentionBias
 from metaseq_b200.modules.dropout import Dropout
 from metaseq_b200.ops import autograd as ops_ag
 from metaseq_b200.ops import functional as ops_f
@@ -122,9 +123,12 @@ class ModelParallelMultiheadAttention(nn.Module):
         cache = self._get_cache(incremental_state)
         use_cache = incremental_state is not None
 
-        if not use_cache and key_padding_mask is None and attn_mask is None and self.dropout_module.p == 0.0 \
-                and ops_f.use_kernels(qkv) and d in (64, 128):
-            ctx = ops_ag.flash_attention_packed(qkv.contiguous(), H, self.scaling, True)
+        structured = attn_mask if isinstance(attn_mask, AttentionBias) else None
+        if not use_cache and key_padding_mask is None and (attn_mask is None or structured is not None) \
+                and self.dropout_module.p == 0.0 and ops_f.use_kernels(qkv) and ops_f.attn_head_dim_ok(d):
+            ctx = ops_ag.flash_attention_packed(qkv.contiguous(), H, self.scaling, True,
+                                                structured.doc_start if structured is not None else None,
+                                                structured.slopes if structured is not None else None)
         else:
             k = qkv[..., 0:Dp]
             v = qkv[..., Dp:2 * Dp]
@@ -137,7 +141,7 @@ class ModelParallelMultiheadAttention(nn.Module):
                 past = cache.length
                 cache.append(k, v)
                 if T == 1 and attn_mask is None and not self.training and ops_f.use_kernels(q) \
-                        and self.head_dim in (64, 128):
+                        and ops_f.decode_head_dim_ok(self.head_dim):
                     # one generated token: a single kernel streams the preallocated cache once
                     ctx = ops_f.decode_attn(q, cache.k, cache.v, cache.length, self.num_heads_partition, self.scaling,
                                             key_padding_mask)
@@ -145,6 +149,8 @@ class ModelParallelMultiheadAttention(nn.Module):
                     return out, bias
                 k = cache.k[:, : cache.length]
                 v = cache.v[:, : cache.length]
+            if structured is not None:  # the PyTorch paths below take the additive mask (causality included)
+                attn_mask = structured.dense(T, k.shape[1], past, q.device)
             ctx = self._attend(q, k, v, B, T, past, key_padding_mask, attn_mask)  # cached or masked path
         if self.sequence_parallel:
             ctx = ctx.reshape(B * T, -1)
@@ -155,7 +161,7 @@ class ModelParallelMultiheadAttention(nn.Module):
         H, d = self.num_heads_partition, self.head_dim
         S = k.shape[1]
         if past == 0 and T == S and key_padding_mask is None and attn_mask is None and not self.training \
-                and ops_f.use_kernels(q) and d in (64, 128):
+                and ops_f.use_kernels(q) and ops_f.attn_head_dim_ok(d):
             out, _ = ops_f.flash_attn_fwd(q.reshape(B, T, H, d), k.reshape(B, S, H, d), v.reshape(B, S, H, d),
                                           self.scaling, True)
             return out

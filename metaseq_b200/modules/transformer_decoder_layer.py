@@ -22,6 +22,7 @@ import torch.nn as nn
 
 from metaseq_b200 import utils
 from metaseq_b200.modules.activation_functions import ActivationFn
+from metaseq_b200.modules.attention_bias import AttentionBias
 from metaseq_b200.modules.dropout import Dropout
 from metaseq_b200.modules.fused_layer import LayerSpec, fused_decoder_layer
 from metaseq_b200.modules.layer_norm import LayerNorm
@@ -105,11 +106,11 @@ class ModelParallelTransformerDecoderLayer(nn.Module):
     # ------------------------------------------------------------------ paths
     def _fused_ok(self, x, incremental_state, key_padding_mask, attn_mask) -> bool:
         if not self.use_fused_layer or incremental_state is not None or key_padding_mask is not None \
-                or attn_mask is not None:
-            return False
+                or not (attn_mask is None or isinstance(attn_mask, AttentionBias)):
+            return False  # dense masks take the modular path; document starts / ALiBi slopes go to the kernel
         if not (ops_f.use_kernels(x) or FORCE_FUSED_LAYER) or self.activation_name != "relu":
             return False
-        if (self.self_attn.head_dim not in (64, 128) and not FORCE_FUSED_LAYER) or self.embed_dim % 8 != 0:
+        if (not ops_f.attn_head_dim_ok(self.self_attn.head_dim) and not FORCE_FUSED_LAYER) or self.embed_dim % 8 != 0:
             return False
         if self.self_attn.qkv_proj.weight.dtype != x.dtype:
             return False
@@ -144,7 +145,9 @@ class ModelParallelTransformerDecoderLayer(nn.Module):
                 eps=self.self_attn_layer_norm.eps, tp_group=mpu.get_tensor_model_parallel_group(),
                 tp_world=mpu.get_tensor_model_parallel_world_size(), sequence_parallel=self.sequence_parallel,
                 recompute=self.checkpoint_activations if recompute is None else recompute, comm=self.tp_comm,
-                dropout_p=p_res, attn_dropout_p=p_attn, seeds=seeds)
+                dropout_p=p_res, attn_dropout_p=p_attn, seeds=seeds,
+                doc_start=self_attn_mask.doc_start if self_attn_mask is not None else None,
+                alibi_slopes=self_attn_mask.slopes if self_attn_mask is not None else None)
             ln1, ln2 = self.self_attn_layer_norm, self.final_layer_norm
             return fused_decoder_layer(
                 x, spec, ln1.weight, ln1.bias, a.qkv_proj.weight, a.qkv_proj.bias, a.out_proj.weight, a.out_proj.bias,

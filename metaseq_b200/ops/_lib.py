@@ -26,8 +26,8 @@ F = c_float
 
 
 # kernels launched by one call of each entry point (used for the launch counter)
-_KERNELS_PER_CALL = {"msq_attn_set_dropout": 0, "msq_symm_alloc": 0, "msq_symm_open": 0, "msq_symm_close": 0, "msq_symm_free": 0, "msq_sumsq": 2, "msq_layernorm_bwd": 2, "msq_rmsnorm_bwd": 2, "msq_flash_bwd": 2, "msq_layernorm_bwd_parts": 0,
-                     "msq_sumsq_parts": 0, "msq_gemm_skinny_split": 0, "msq_set_dependent_launch": 0, "msq_gemm_skinny_set_prof": 0, "msq_decode_attn_splits": 0}
+_KERNELS_PER_CALL = {"msq_flash_head_dim_ok": 0, "msq_symm_alloc": 0, "msq_symm_open": 0, "msq_symm_close": 0, "msq_symm_free": 0, "msq_sumsq": 2, "msq_layernorm_bwd": 2, "msq_rmsnorm_bwd": 2, "msq_flash_bwd": 2, "msq_layernorm_bwd_parts": 0,
+                     "msq_sumsq_parts": 0, "msq_gemm2_tiles_n": 0, "msq_gemm_skinny_split": 0, "msq_set_dependent_launch": 0, "msq_gemm_skinny_set_prof": 0, "msq_decode_attn_splits": 0}
 _LAUNCHES = [0]
 
 
@@ -120,12 +120,14 @@ def _declare_kernels(lib):
     _sig(lib, "msq_comm_allreduce_multimem", [P, L, I, I, I, P, L, U, I, P, P])
     _sig(lib, "msq_cross_entropy", [P, L, P, P, P, I, I, L, F, I, I, P])
     _sig(lib, "msq_colsum", [P, L, I, I, P, I, P])
-    _sig(lib, "msq_flash_fwd", [P, P, P, L, L, L, L, L, L, P, L, L, P, I, I, I, I, F, I, I, P, P])
+    ULL = ctypes.c_ulonglong
+    _sig(lib, "msq_flash_fwd", [P, P, P, L, L, L, L, L, L, P, L, L, P, I, I, I, I, F, I, I, P, P, F, ULL, P, P])
     _sig(
         lib,
         "msq_flash_bwd",
-        [P, P, P, P, P] + [L] * 10 + [P, P, P, P, P] + [L] * 4 + [I, I, I, I, F, I, I, P, P],
+        [P, P, P, P, P] + [L] * 10 + [P, P, P, P, P] + [L] * 4 + [I, I, I, I, F, I, I, P, P, F, ULL, P, P],
     )
+    _sig(lib, "msq_flash_head_dim_ok", [I])
     for name, sig in _OPTIONAL.items():
         if hasattr(lib, name):
             _sig(lib, name, sig)
@@ -146,10 +148,15 @@ _OPTIONAL = {
     "msq_rmsnorm_fwd": [P, P, P, P, I, I, F, I, P],
     "msq_rmsnorm_bwd": [P, P, P, P, P, P, P, P, P, I, I, I, I, P],
     "msq_decode_attn_step": [P, P, P, L, P, P, P, P, I, I, I, P, I, L, L, L, L, L, F, I, P, I, P],
-    "msq_attn_set_dropout": [F, ctypes.c_ulonglong],
     "msq_dropout_add": [P, L, P, P, L, P, L, L, I, F, ctypes.c_ulonglong, I, P],
     "msq_vp_ce_partial": [P, L, P, P, I, I, L, I, P],
     "msq_vp_ce_finish": [P, L, P, P, I, P, I, I, L, L, F, I, P],
+    "msq_gemm2_tiles_n": [I],
+    "msq_sumsq_multi": [P, I, I, I, P, P, P, I, P],
+    "msq_gemm2_rowstats": [P, P, P, I, I, I, L, L, L, I, I, I, P, P, P, I, P, P, P],
+    "msq_ce_merge_rowstats": [P, P, I, I, P, L, P, I, L, P, P, I, I, I, ctypes.c_uint, I, P],
+    "msq_vp_ce_finish_exchanged": [P, L, P, P, I, I, ctypes.c_uint, P, I, I, L, L, F, I, P, P],
+    "msq_scale_rows_rel": [P, L, L, I, P, I, I, F, I, P],
 }
 _OPTIONAL = {k: v for k, v in _OPTIONAL.items() if v is not None}
 

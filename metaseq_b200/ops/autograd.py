@@ -29,15 +29,34 @@ def _direct_grad(param: Optional[torch.Tensor], compute, shape_like: Optional[to
     return None
 
 
+_UPSTREAM_GRAD_HINT = [None]
+
+
+def set_upstream_grad_hint(value: Optional[float]):
+    """The factor that the backward pass is expected to bring to the loss (the fp16 optimizer's loss scale), told to
+    the loss kernels before the forward pass: they store their gradient already multiplied by it, and the backward
+    pass rescales only where the factor that really arrives differs.  ``None`` (or 1) switches the guess off."""
+    _UPSTREAM_GRAD_HINT[0] = float(value) if value else None
+
+
+def upstream_grad_hint() -> float:
+    v = _UPSTREAM_GRAD_HINT[0]
+    return v if (v is not None and v > 0 and v == v and v != float("inf")) else 1.0
+
+
 class LinearFn(torch.autograd.Function):
-    """``y = act(x @ W^T + b) + residual`` with the epilogue fused into the GEMM."""
+    """``y = act(x @ W^T + b) + residual`` with the epilogue fused into the GEMM.  ``stats_out`` (a dict) asks for
+    the per-tile softmax pieces of every output row (``functional.gemm_with_row_stats``) under ``"row_stats"``."""
 
     @staticmethod
-    def forward(ctx, x, weight, bias, residual, relu: bool):
+    def forward(ctx, x, weight, bias, residual, relu: bool, stats_out=None):
         shp = x.shape
         x2 = x.reshape(-1, shp[-1])
         res2 = residual.reshape(-1, weight.shape[0]) if residual is not None else None
-        y = F.gemm(x2, weight, bias=bias, residual=res2, relu=relu)
+        if stats_out is not None and res2 is None and not relu:
+            y, stats_out["row_stats"] = F.gemm_with_row_stats(x2, weight, bias)
+        else:
+            y = F.gemm(x2, weight, bias=bias, residual=res2, relu=relu)
         ctx.relu = relu
         ctx.has_bias = bias is not None
         ctx.has_res = residual is not None
@@ -67,11 +86,18 @@ class LinearFn(torch.autograd.Function):
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = _direct_grad(bparam, lambda out, acc: F.colsum(dz, out16=out, accumulate=acc))
         dres = dy if ctx.has_res else None
-        return (dx.view(ctx.in_shape) if dx is not None else None), dw, db, dres, None
+        return (dx.view(ctx.in_shape) if dx is not None else None), dw, db, dres, None, None
 
 
-def linear(x, weight, bias=None, residual=None, relu: bool = False):
+def linear(x, weight, bias=None, residual=None, relu: bool = False, row_stats: bool = False):
+    """With ``row_stats`` the result carries ``_msq_row_stats``: the ``(max, sum-exp)`` tables per column tile that
+    a cross entropy over the same rows can start from (``None`` where the kernel did not produce them)."""
     if torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad):
+        if row_stats:
+            holder = {}
+            y = LinearFn.apply(x, weight, bias, residual, relu, holder)
+            y._msq_row_stats = holder.get("row_stats")
+            return y
         return LinearFn.apply(x, weight, bias, residual, relu)
     shp = x.shape
     res2 = residual.reshape(-1, weight.shape[0]) if residual is not None else None
@@ -136,16 +162,17 @@ class FlashAttnFn(torch.autograd.Function):
     """Causal attention over a packed ``[B, T, 3*H*d]`` projection laid out as (k | v | q)."""
 
     @staticmethod
-    def forward(ctx, qkv, num_heads: int, scale: float, causal: bool):
+    def forward(ctx, qkv, num_heads: int, scale: float, causal: bool, doc_start=None, alibi_slopes=None):
         B, T, W = qkv.shape
         D = W // 3
         d = D // num_heads
         k = qkv[..., 0:D].view(B, T, num_heads, d)
         v = qkv[..., D:2 * D].view(B, T, num_heads, d)
         q = qkv[..., 2 * D:].view(B, T, num_heads, d)
-        out, lse = F.flash_attn_fwd(q, k, v, scale, causal)
+        out, lse = F.flash_attn_fwd(q, k, v, scale, causal, doc_start=doc_start, alibi_slopes=alibi_slopes)
         ctx.save_for_backward(qkv, out, lse)
         ctx.meta = (num_heads, scale, causal)
+        ctx.masks = (doc_start, alibi_slopes)  # integer / constant tensors: no gradient flows to them
         return out
 
     @staticmethod
@@ -159,12 +186,14 @@ class FlashAttnFn(torch.autograd.Function):
         views = lambda t: (t[..., 0:D].view(B, T, H, d), t[..., D:2 * D].view(B, T, H, d), t[..., 2 * D:].view(B, T, H, d))
         k, v, q = views(qkv)
         dk, dv, dq = views(dqkv)
-        F.flash_attn_bwd(q, k, v, out, d_out.contiguous(), lse, scale, causal, dq, dk, dv)
-        return dqkv, None, None, None
+        F.flash_attn_bwd(q, k, v, out, d_out.contiguous(), lse, scale, causal, dq, dk, dv, doc_start=ctx.masks[0],
+                         alibi_slopes=ctx.masks[1])
+        return dqkv, None, None, None, None, None
 
 
-def flash_attention_packed(qkv, num_heads: int, scale: float, causal: bool = True):
-    return FlashAttnFn.apply(qkv, num_heads, scale, causal)
+def flash_attention_packed(qkv, num_heads: int, scale: float, causal: bool = True, doc_start=None, alibi_slopes=None):
+    """``doc_start`` (``[B, T]``) / ``alibi_slopes`` (``[H]``): see ``functional.flash_attn_fwd``."""
+    return FlashAttnFn.apply(qkv, num_heads, scale, causal, doc_start, alibi_slopes)
 
 
 class CrossEntropyFn(torch.autograd.Function):
@@ -173,10 +202,14 @@ class CrossEntropyFn(torch.autograd.Function):
     gradient (1 in the usual ``loss.backward()``), so fp32 logits are never materialised."""
 
     @staticmethod
-    def forward(ctx, logits, target, ignore_index: int):
+    def forward(ctx, logits, target, ignore_index: int, row_stats=None):
         V = logits.shape[-1]
         l2 = logits.reshape(-1, V)
-        loss_rows, _ = F.cross_entropy_fwd_bwd(l2, target.reshape(-1), ignore_index, 1.0, True)
+        ctx.pre_scaled = upstream_grad_hint()
+        if row_stats is not None:
+            loss_rows = F.cross_entropy_from_row_stats(l2, target.reshape(-1), ignore_index, ctx.pre_scaled, row_stats)
+        else:
+            loss_rows, _ = F.cross_entropy_fwd_bwd(l2, target.reshape(-1), ignore_index, ctx.pre_scaled, True)
         ctx.save_for_backward(l2)
         ctx.shape = logits.shape
         return loss_rows.sum()
@@ -184,15 +217,17 @@ class CrossEntropyFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g):
         (grad,) = ctx.saved_tensors
-        # g is the scalar d(total)/d(loss); typically loss_scale.
+        # g is the scalar d(total)/d(loss), typically the loss scale, which the forward pass already applied when it
+        # was announced (set_upstream_grad_hint): then nothing is left to do
         if g.numel() == 1:
-            F.scale_rows_(grad, g)  # in place: the saved tensor is the consumed logits buffer
-        return grad.view(ctx.shape), None, None
+            F.scale_rows_(grad, g, ref=ctx.pre_scaled)  # in place: the saved tensor is the consumed logits buffer
+        return grad.view(ctx.shape), None, None, None
 
 
 def cross_entropy_sum(logits, target, ignore_index: int):
-    """``logits`` is consumed (overwritten in place)."""
-    return CrossEntropyFn.apply(logits, target, ignore_index)
+    """``logits`` is consumed (overwritten in place).  Logits that carry ``_msq_row_stats`` (``linear(...,
+    row_stats=True)``) skip the pass that finds the row maxima and sums."""
+    return CrossEntropyFn.apply(logits, target, ignore_index, getattr(logits, "_msq_row_stats", None))
 
 
 class EmbeddingFn(torch.autograd.Function):

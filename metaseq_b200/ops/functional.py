@@ -12,6 +12,7 @@ cuBLAS + unfused-ops baseline the kernels are compared against).
 """
 from __future__ import annotations
 
+import logging
 import math
 import os
 from typing import Optional
@@ -59,6 +60,30 @@ def use_kernels(*tensors) -> bool:
             "run `python -m metaseq_b200.build_ext`"
         )
     return True
+
+
+_STRICT = os.environ.get("MSQ_STRICT_KERNELS", "0") == "1"
+_FALLBACKS_SEEN: set = set()
+
+
+def set_strict_kernels(on: bool = True):
+    """With strict kernels an operator that would leave the sm_100a kernel path on CUDA 16-bit inputs (unsupported
+    head size, stride or alignment) raises instead of running the PyTorch restatement (``--strict-kernels``)."""
+    global _STRICT
+    _STRICT = bool(on)
+
+
+def _note_fallback(op: str, why: str):
+    """Called where CUDA 16-bit tensors miss a kernel's shape / layout conditions: logs the reason once per
+    (operator, reason), or raises under ``set_strict_kernels``."""
+    if _BACKEND == "torch":
+        return
+    if _STRICT:
+        raise RuntimeError(f"{op}: no sm_100a kernel for this call ({why}) and strict kernels are on")
+    key = (op, why)
+    if key not in _FALLBACKS_SEEN:
+        _FALLBACKS_SEEN.add(key)
+        logging.getLogger(__name__).warning("%s runs on PyTorch ops, not on the sm_100a kernel: %s", op, why)
 
 
 def _bf(t) -> int:
@@ -177,9 +202,51 @@ def gemm(
         )
         _lib.check_rc(rc, "msq_gemm")
         return out
+    if a.is_cuda and a.dtype in (torch.float16, torch.bfloat16):
+        _note_fallback("gemm", f"K={K} N={N} must be multiples of 8, operands 16-byte aligned with unit inner stride")
     ensure_operand_ready(a)
     ensure_operand_ready(b)
     return _gemm_torch(a, b, a_mn, b_mn, bias, residual, mask, relu, out, accumulate)
+
+
+def gemm_with_row_stats(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None):
+    """``a @ w^T (+ bias)`` for ``a`` ``[M, K]`` and an ``nn.Linear`` weight ``w`` ``[N, K]`` whose epilogue also leaves
+    the softmax pieces of every row per 256-column tile: returns ``(out, (rs_max, rs_sum))`` with the two fp32
+    ``[tiles_n, M]`` tables of the tile maxima and of ``sum(exp(x - max))`` over the values as stored, or
+    ``(out, None)`` where the pair kernel does not apply (the caller then reads the logits instead)."""
+    M, K = a.shape
+    N = w.shape[0]
+    out = torch.empty((M, N), dtype=a.dtype, device=a.device)
+    ok = (use_kernels(a) and a.dtype == w.dtype and M >= 256 and N >= 128 and K % 8 == 0 and N % 8 == 0
+          and _GEMM_VARIANT != "1cta" and _gemm_operands_ok(a, w, out, None, None)
+          and (bias is None or bias.data_ptr() % 16 == 0) and hasattr(_lib.kernels()._lib, "msq_gemm2_rowstats"))
+    if not ok:
+        return gemm(a, w, bias=bias, out=out), None
+    lib = _lib.kernels()
+    desc = None
+    hb, ha = getattr(w, "_msq_ready", None), getattr(a, "_msq_ready", None)
+    if hb is not None:
+        if getattr(hb, "operand", 0) == 0:
+            desc = hb.ready_struct(w)
+        if desc is None:
+            hb.wait(w)
+    if ha is not None:
+        if desc is None and getattr(ha, "operand", 0) == 1:
+            desc = ha.ready_struct(a)
+            if desc is None:
+                ha.wait(a)
+        else:
+            ha.wait(a)
+    tiles_n = int(lib.msq_gemm2_tiles_n(N))
+    stats = torch.empty((2, tiles_n, M), dtype=torch.float32, device=a.device)
+    import ctypes as _ct
+
+    rc = lib.msq_gemm2_rowstats(_lib.ptr(a), _lib.ptr(w), _lib.ptr(out), M, N, K, a.stride(0), w.stride(0), out.stride(0),
+                                0, 0, _bf(a), _lib.ptr(bias), _lib.ptr(stats[0]), _lib.ptr(stats[1]), 0,
+                                _lib.ptr(_lib.status_word(a.device)), _lib.stream_ptr(),
+                                _ct.byref(desc) if desc is not None else None)
+    _lib.check_rc(rc, "msq_gemm2_rowstats")
+    return out, (stats[0], stats[1])
 
 
 def ensure_operand_ready(t: torch.Tensor):
@@ -278,6 +345,8 @@ def layer_norm_fwd(x2d, gamma, beta, eps: float):
         )
         _lib.check_rc(rc, "msq_layernorm_fwd")
         return y, mean, rstd
+    if x2d.is_cuda and x2d.dtype in (torch.float16, torch.bfloat16):
+        _note_fallback("layer_norm", f"width {D} must be a multiple of 8 and at most 16384, rows contiguous")
     xf = x2d.float()
     mean = xf.mean(dim=1)
     var = xf.var(dim=1, unbiased=False)
@@ -363,35 +432,53 @@ def attn_keep_mask_reference(B: int, H: int, T: int, p: float, seed: int, device
     return half >= thr
 
 
-def flash_attn_fwd(q, k, v, scale: float, causal: bool = True, dropout_p: float = 0.0, seed: int = 0):
+_ATTN_HEAD_DIMS = "multiples of 8 up to 128"
+
+
+def attn_head_dim_ok(d: int) -> bool:
+    """Head sizes of the flash-attention kernels: 64 and 128 natively, other multiples of 8 up to 128 (80 and 96 of
+    OPT-2.7B / OPT-760M) zero-padded inside the kernel."""
+    return 8 <= d <= 128 and d % 8 == 0
+
+
+def _mask_args(doc_start, alibi_slopes, B, T, H, device):
+    """Device pointers for the optional per-token document starts (int32 ``[B, T]``) and per-head ALiBi slopes
+    (fp32 ``[H]``); the tensors are returned too so that they outlive the launch."""
+    ds = sl = None
+    if doc_start is not None:
+        ds = doc_start.to(device=device, dtype=torch.int32).contiguous()
+        assert ds.shape == (B, T), (ds.shape, B, T)
+    if alibi_slopes is not None:
+        sl = alibi_slopes.to(device=device, dtype=torch.float32).contiguous()
+        assert sl.numel() == H
+    return ds, sl
+
+
+def flash_attn_fwd(q, k, v, scale: float, causal: bool = True, dropout_p: float = 0.0, seed: int = 0,
+                   doc_start=None, alibi_slopes=None):
     """``q, k, v``: ``[B, T, H, d]`` views (last dim contiguous, head stride ``d``).
     Returns ``(out [B, T, H*d], lse [B, H, T] fp32)``.  With ``dropout_p > 0`` the attention weights are dropped
-    with the mask derived from ``seed`` (the normaliser is unaffected); pass the same values to the backward."""
+    with the mask derived from ``seed`` (the normaliser is unaffected); pass the same values to the backward.
+    ``doc_start`` (``[B, T]``, the first position of each token's document) restricts a query to the keys of its own
+    document; ``alibi_slopes`` (``[H]``) adds ``slope * key position`` to the scaled scores."""
     B, T, H, d = q.shape
-    if use_kernels(q) and d in (64, 128) and _attn_views_ok(q, k, v):
+    if use_kernels(q) and attn_head_dim_ok(d) and _attn_views_ok(q, k, v) and (doc_start is None or causal):
         out = torch.empty((B, T, H * d), dtype=q.dtype, device=q.device)
         lse = torch.empty((B, H, T), dtype=torch.float32, device=q.device)
-        lib = _lib.kernels()
-        if dropout_p > 0:
-            _lib.check_rc(lib.msq_attn_set_dropout(float(dropout_p), int(seed)), "msq_attn_set_dropout")
-        try:
-            rc = _flash_fwd_call(lib, q, k, v, out, lse, B, T, H, d, scale, causal)
-        finally:
-            if dropout_p > 0:
-                lib.msq_attn_set_dropout(0.0, 0)
+        ds, sl = _mask_args(doc_start, alibi_slopes, B, T, H, q.device)
+        rc = _lib.kernels().msq_flash_fwd(
+            _lib.ptr(q), _lib.ptr(k), _lib.ptr(v),
+            q.stride(1), q.stride(0), k.stride(1), k.stride(0), v.stride(1), v.stride(0),
+            _lib.ptr(out), out.stride(1), out.stride(0), _lib.ptr(lse),
+            B, T, H, d, float(scale), int(causal), _bf(q), _lib.ptr(ds), _lib.ptr(sl), float(dropout_p), int(seed),
+            _lib.ptr(_lib.status_word(q.device)), _lib.stream_ptr(),
+        )
         _lib.check_rc(rc, "msq_flash_fwd")
         return out, lse
-    return _attn_fwd_torch(q, k, v, scale, causal, dropout_p, seed)
-
-
-def _flash_fwd_call(lib, q, k, v, out, lse, B, T, H, d, scale, causal):
-    return lib.msq_flash_fwd(
-        _lib.ptr(q), _lib.ptr(k), _lib.ptr(v),
-        q.stride(1), q.stride(0), k.stride(1), k.stride(0), v.stride(1), v.stride(0),
-        _lib.ptr(out), out.stride(1), out.stride(0), _lib.ptr(lse),
-        B, T, H, d, float(scale), int(causal), _bf(q),
-        _lib.ptr(_lib.status_word(q.device)), _lib.stream_ptr(),
-    )
+    if q.is_cuda and q.dtype in (torch.float16, torch.bfloat16):
+        _note_fallback("flash_attn_fwd", f"head size {d} (kernels: {_ATTN_HEAD_DIMS}) or q/k/v views not 16-byte "
+                                         "aligned [B,T,H,d] slices; this path materialises [B,H,T,T] scores")
+    return _attn_fwd_torch(q, k, v, scale, causal, dropout_p, seed, doc_start, alibi_slopes)
 
 
 def _attn_views_ok(*ts) -> bool:
@@ -402,13 +489,25 @@ def _attn_views_ok(*ts) -> bool:
     return True
 
 
-def _attn_fwd_torch(q, k, v, scale, causal, dropout_p: float = 0.0, seed: int = 0):
+def _attn_scores_torch(qf, kf, scale, causal, doc_start, alibi_slopes):
+    """fp32 ``[B, H, T, T]`` scores with every mask applied (the oracle of the kernels' masking)."""
+    T = qf.shape[2]
+    s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    pos = torch.arange(T, device=qf.device)
+    if alibi_slopes is not None:
+        s = s + alibi_slopes.to(s.device).float().view(1, -1, 1, 1) * pos.view(1, 1, 1, T).float()
+    if causal:
+        s = s.masked_fill((pos[None, :] > pos[:, None])[None, None], float("-inf"))
+    if doc_start is not None:
+        before_doc = pos.view(1, 1, T) < doc_start.to(s.device).long().view(-1, T, 1)  # [B, Tq, Tk]
+        s = s.masked_fill(before_doc[:, None], float("-inf"))
+    return s
+
+
+def _attn_fwd_torch(q, k, v, scale, causal, dropout_p: float = 0.0, seed: int = 0, doc_start=None, alibi_slopes=None):
     B, T, H, d = q.shape
     qf, kf, vf = (t.float().permute(0, 2, 1, 3) for t in (q, k, v))  # [B,H,T,d]
-    s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
-    if causal:
-        mask = torch.ones(T, T, dtype=torch.bool, device=q.device).triu(1)
-        s = s.masked_fill(mask, float("-inf"))
+    s = _attn_scores_torch(qf, kf, scale, causal, doc_start, alibi_slopes)
     lse = torch.logsumexp(s, dim=-1)
     p = torch.exp(s - lse[..., None])
     if dropout_p > 0:
@@ -419,29 +518,26 @@ def _attn_fwd_torch(q, k, v, scale, causal, dropout_p: float = 0.0, seed: int = 
 
 
 def flash_attn_bwd(q, k, v, out, d_out, lse, scale: float, causal: bool, dq, dk, dv, dropout_p: float = 0.0,
-                   seed: int = 0):
+                   seed: int = 0, doc_start=None, alibi_slopes=None):
     """Writes gradients into the ``[B, T, H, d]`` views ``dq, dk, dv`` (typically column slices
-    of the qkv-gradient buffer)."""
+    of the qkv-gradient buffer).  Masks and dropout as given to the forward call."""
     B, T, H, d = q.shape
     if (
-        use_kernels(q) and d in (64, 128) and _attn_views_ok(q, k, v, dk, dv)
-        and out.stride() == d_out.stride() and out.stride(2) == 1
+        use_kernels(q) and attn_head_dim_ok(d) and _attn_views_ok(q, k, v, dk, dv)
+        and out.stride() == d_out.stride() and out.stride(2) == 1 and (doc_start is None or causal)
     ):
         delta = torch.empty((B, H, T), dtype=torch.float32, device=q.device)
         dq_acc = torch.zeros((B, T, H * d), dtype=torch.float32, device=q.device)
-        if dropout_p > 0:
-            _lib.check_rc(_lib.kernels().msq_attn_set_dropout(float(dropout_p), int(seed)), "msq_attn_set_dropout")
+        ds, sl = _mask_args(doc_start, alibi_slopes, B, T, H, q.device)
         rc = _lib.kernels().msq_flash_bwd(
             _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(out), _lib.ptr(d_out),
             q.stride(1), q.stride(0), k.stride(1), k.stride(0), v.stride(1), v.stride(0),
             out.stride(1), out.stride(0), d_out.stride(1), d_out.stride(0),
             _lib.ptr(lse), _lib.ptr(delta), _lib.ptr(dq_acc), _lib.ptr(dk), _lib.ptr(dv),
             dk.stride(1), dk.stride(0), dv.stride(1), dv.stride(0),
-            B, T, H, d, float(scale), int(causal), _bf(q),
+            B, T, H, d, float(scale), int(causal), _bf(q), _lib.ptr(ds), _lib.ptr(sl), float(dropout_p), int(seed),
             _lib.ptr(_lib.status_word(q.device)), _lib.stream_ptr(),
         )
-        if dropout_p > 0:
-            _lib.kernels().msq_attn_set_dropout(0.0, 0)
         _lib.check_rc(rc, "msq_flash_bwd")
         # dq is a column slice of the qkv gradient: rows of H*d elements, row stride dq.stride(1)
         if dq.stride(2) == d and dq.stride(3) == 1 and dq.stride(0) == T * dq.stride(1) and dq.stride(1) % 8 == 0:
@@ -451,13 +547,13 @@ def flash_attn_bwd(q, k, v, out, d_out, lse, scale: float, causal: bool, dq, dk,
         else:
             dq.copy_(dq_acc.view(B, T, H, d))
         return
+    if q.is_cuda and q.dtype in (torch.float16, torch.bfloat16):
+        _note_fallback("flash_attn_bwd", f"head size {d} (kernels: {_ATTN_HEAD_DIMS}) or views not 16-byte aligned "
+                                         "[B,T,H,d] slices; this path materialises [B,H,T,T] scores")
     qf, kf, vf = (t.float().permute(0, 2, 1, 3) for t in (q, k, v))
     of = out.float().view(B, T, H, d).permute(0, 2, 1, 3)
     dof = d_out.float().reshape(B, T, H, d).permute(0, 2, 1, 3)
-    s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
-    if causal:
-        mask = torch.ones(T, T, dtype=torch.bool, device=q.device).triu(1)
-        s = s.masked_fill(mask, float("-inf"))
+    s = _attn_scores_torch(qf, kf, scale, causal, doc_start, alibi_slopes)
     p = torch.exp(s - lse[..., None])
     dp = torch.matmul(dof, vf.transpose(-1, -2))
     if dropout_p > 0:
@@ -594,6 +690,15 @@ def dropout_add(y: torch.Tensor, bias, residual, p: float, seed: int, out: Optio
     return out
 
 
+def decode_head_dim_ok(d: int) -> bool:
+    """Head sizes of the decode-attention kernels (others than 64 and 128 run zero-padded lanes)."""
+    return 8 <= d <= 128 and d % 8 == 0
+
+
+def _decode_pad(d: int) -> int:
+    return 64 if d <= 64 else 128
+
+
 def decode_attn(q, k_cache, v_cache, length: int, num_heads: int, scale: float, key_padding_mask=None):
     """Single-query attention for incremental decoding.
 
@@ -604,13 +709,14 @@ def decode_attn(q, k_cache, v_cache, length: int, num_heads: int, scale: float, 
     D = q.shape[-1]
     d = D // num_heads
     q2 = q.reshape(B, D)
-    if use_kernels(q) and d in (64, 128) and q2.stride(-1) == 1 and k_cache.stride(-1) == 1 and v_cache.stride(-1) == 1 \
+    if use_kernels(q) and decode_head_dim_ok(d) and q2.stride(-1) == 1 and k_cache.stride(-1) == 1 and v_cache.stride(-1) == 1 \
             and k_cache.stride() == v_cache.stride() and q2.data_ptr() % 16 == 0 and k_cache.data_ptr() % 16 == 0 \
             and v_cache.data_ptr() % 16 == 0 and q2.stride(0) % 8 == 0 and k_cache.stride(1) % 8 == 0:
         lib = _lib.kernels()
         out = torch.empty((B, D), dtype=q.dtype, device=q.device)
         splits = lib.msq_decode_attn_splits(B, num_heads, length)
-        ws = torch.empty((B * num_heads * splits * (d + 2),), dtype=torch.float32, device=q.device) if splits > 1 else None
+        ws = torch.empty((B * num_heads * splits * (_decode_pad(d) + 2),), dtype=torch.float32, device=q.device) \
+            if splits > 1 else None
         mask_c = None
         if key_padding_mask is not None:
             mask_c = key_padding_mask.to(torch.uint8)
@@ -622,6 +728,8 @@ def decode_attn(q, k_cache, v_cache, length: int, num_heads: int, scale: float, 
                                  _lib.stream_ptr())
         _lib.check_rc(rc, "msq_decode_attn")
         return out.view(B, 1, D)
+    if q.is_cuda and q.dtype in (torch.float16, torch.bfloat16):
+        _note_fallback("decode_attn", f"head size {d} (kernels: {_ATTN_HEAD_DIMS}) or cache layout")
     k = k_cache[:, :length].reshape(B, length, num_heads, d).transpose(1, 2).float()
     v = v_cache[:, :length].reshape(B, length, num_heads, d).transpose(1, 2).float()
     qh = q2.reshape(B, num_heads, 1, d).float() * scale
@@ -664,7 +772,8 @@ def decode_attn_step(q, k_new, v_new, k_cache, v_cache, length_dev, num_heads: i
     lib = _lib.kernels()
     out = torch.empty((B, D), dtype=q.dtype, device=q.device)
     splits = lib.msq_decode_attn_splits(B, num_heads, max(1, length_hint))
-    ws = torch.empty((B * num_heads * splits * (d + 2),), dtype=torch.float32, device=q.device) if splits > 1 else None
+    ws = torch.empty((B * num_heads * splits * (_decode_pad(d) + 2),), dtype=torch.float32, device=q.device) \
+        if splits > 1 else None
     rc = lib.msq_decode_attn_step(_lib.ptr(q), _lib.ptr(k_new), _lib.ptr(v_new), k_new.stride(0), _lib.ptr(k_cache),
                                   _lib.ptr(v_cache), _lib.ptr(out), None, B, num_heads, d, _lib.ptr(length_dev),
                                   k_cache.shape[1], q.stride(0), k_cache.stride(1), k_cache.stride(0), out.stride(0), 0,
@@ -689,6 +798,8 @@ def cross_entropy_fwd_bwd(logits2d, target, ignore_index: int, grad_scale: float
         )
         _lib.check_rc(rc, "msq_cross_entropy")
         return loss, lse
+    if logits2d.is_cuda and logits2d.dtype in (torch.float16, torch.bfloat16):
+        _note_fallback("cross_entropy", f"vocabulary {V} must be a multiple of 8 and at most 102400 per rank")
     lf = logits2d.float()
     lse = torch.logsumexp(lf, dim=1)
     valid = target != ignore_index
@@ -702,14 +813,49 @@ def cross_entropy_fwd_bwd(logits2d, target, ignore_index: int, grad_scale: float
     return loss, lse
 
 
-def scale_rows_(x2d, g):
-    """``x2d[r, :] *= g[r]`` in place (``g`` with one element scales everything); ``g`` stays on the device.
-    Used to apply the incoming gradient (the loss scale) to a gradient stored by the forward pass."""
+def cross_entropy_from_row_stats(logits2d, target, ignore_index: int, grad_scale: float, row_stats):
+    """Per-row NLL for logits whose producing GEMM left ``row_stats = (rs_max, rs_sum)``; the logits are
+    overwritten with ``(softmax - onehot) * grad_scale``.  One small kernel folds the tiles of each row, one pass
+    over the logits writes the gradient."""
+    rows, V = logits2d.shape
+    rs_max, rs_sum = row_stats
+    tiles_n = rs_max.shape[0]
+    assert rs_max.shape[1] == rows and logits2d.stride(1) == 1
+    lib = _lib.kernels()
+    tgt = target.contiguous()
+    stats = torch.empty((1, rows, 3), dtype=torch.float32, device=logits2d.device)
+    rc = lib.msq_ce_merge_rowstats(_lib.ptr(rs_max), _lib.ptr(rs_sum), tiles_n, rows, _lib.ptr(logits2d),
+                                   logits2d.stride(0), _lib.ptr(tgt), V, 0, _lib.ptr(stats), None, 1, 0, rows, 0,
+                                   _bf(logits2d), _lib.stream_ptr())
+    _lib.check_rc(rc, "msq_ce_merge_rowstats")
+    loss = torch.empty(rows, dtype=torch.float32, device=logits2d.device)
+    rc = lib.msq_vp_ce_finish(_lib.ptr(logits2d), logits2d.stride(0), _lib.ptr(tgt), _lib.ptr(stats), 1, _lib.ptr(loss),
+                              rows, V, 0, int(ignore_index), float(grad_scale), _bf(logits2d), _lib.stream_ptr())
+    _lib.check_rc(rc, "msq_vp_ce_finish")
+    return loss
+
+
+def scale_rows_(x2d, g, ref: float = 1.0):
+    """``x2d[r, :] *= g[r] / ref`` in place (``g`` with one element scales everything); ``g`` stays on the device.
+    Used to apply the incoming gradient (the loss scale) to a gradient stored by the forward pass.  ``ref`` is the
+    factor the stored values were already multiplied by: rows whose ``g`` equals it are not touched, so a forward
+    pass that guessed the upstream factor makes this a launch of a few microseconds."""
     rows, cols = x2d.shape
     g = g.reshape(-1)
     assert g.numel() in (1, rows)
-    if use_kernels(x2d) and cols % 8 == 0 and x2d.stride(1) == 1 and x2d.stride(0) % 8 == 0 \
-            and x2d.data_ptr() % 16 == 0 and g.dtype in (torch.float32, x2d.dtype) and g.is_cuda:
+    kernel_ok = use_kernels(x2d) and cols % 8 == 0 and x2d.stride(1) == 1 and x2d.stride(0) % 8 == 0 \
+        and x2d.data_ptr() % 16 == 0 and g.dtype in (torch.float32, x2d.dtype) and g.is_cuda
+    if ref != 1.0:
+        if kernel_ok and hasattr(_lib.kernels()._lib, "msq_scale_rows_rel"):
+            g = g.contiguous()
+            rc = _lib.kernels().msq_scale_rows_rel(_lib.ptr(x2d), x2d.stride(0), rows, cols, _lib.ptr(g),
+                                                   int(g.dtype == torch.float32), int(g.numel() > 1), 1.0 / float(ref),
+                                                   _bf(x2d), _lib.stream_ptr())
+            _lib.check_rc(rc, "msq_scale_rows_rel")
+            return x2d
+        g = g.float() / float(ref)
+        return x2d.mul_(g.to(x2d.dtype).reshape(-1, 1) if g.numel() > 1 else g.to(x2d.dtype))
+    if kernel_ok:
         g = g.contiguous()
         rc = _lib.kernels().msq_scale_rows(_lib.ptr(x2d), x2d.stride(0), rows, cols, _lib.ptr(g),
                                            int(g.dtype == torch.float32), int(g.numel() > 1), _bf(x2d), _lib.stream_ptr())
@@ -786,6 +932,44 @@ def sumsq(g: torch.Tensor, out: torch.Tensor, accumulate: bool):
         out.add_(s)
     else:
         out.fill_(0).add_(s)
+    return out
+
+
+_SUMSQ_TABLES: dict = {}
+
+
+def sumsq_multi(tensors, out: torch.Tensor, accumulate: bool):
+    """``out[0] (+)= sum over all tensors of sum(t**2)`` in one launch (contiguous CUDA tensors of one dtype).  The
+    table of pointers and the scratch live on the device, keyed by device and stream, and are rebuilt only when a
+    pointer or size changes."""
+    t0 = tensors[0]
+    dev = t0.device
+    key = tuple((t.data_ptr(), t.numel()) for t in tensors)
+    slot = (dev.index or 0, torch.cuda.current_stream(dev).cuda_stream)
+    cached = _SUMSQ_TABLES.get(slot)
+    if cached is None or cached[0] != key:
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        total_n = sum(n for _, n in key)
+        budget = 8 * sms  # blocks over all tensors, shared in proportion to their sizes (at least one each)
+        per_block = 8 * 512
+        recs, first = [], 0
+        for ptr, n in key:
+            want = max(1, min((n + per_block - 1) // per_block, max(1, round(budget * n / max(total_n, 1)))))
+            recs.append((ptr, n, first))
+            first += want
+        recs.append((0, 0, first))
+        table = torch.tensor([x for r in recs for x in r], dtype=torch.int64).to(dev)
+        scratch = torch.empty(first, dtype=torch.float32, device=dev)
+        ticket = torch.zeros(1, dtype=torch.int32, device=dev)
+        if len(_SUMSQ_TABLES) > 16:
+            _SUMSQ_TABLES.clear()
+        cached = (key, table, scratch, ticket, first)
+        _SUMSQ_TABLES[slot] = cached
+    _, table, scratch, ticket, total_blocks = cached
+    rc = _lib.kernels().msq_sumsq_multi(_lib.ptr(table), len(tensors), total_blocks, _lib.dtype_code(t0.dtype),
+                                        _lib.ptr(scratch), _lib.ptr(ticket), _lib.ptr(out), int(accumulate),
+                                        _lib.stream_ptr())
+    _lib.check_rc(rc, "msq_sumsq_multi")
     return out
 
 

@@ -171,14 +171,24 @@ class Adam(torch.optim.Optimizer):
                 self._compress_stats(state, m, v)
         return loss
 
-    _ctrl_cache = {}
-
     def _scale_ctrl(self, device, scale):
-        key = (str(device), float(scale))
-        c = Adam._ctrl_cache.get(key)
-        if c is None:
-            if len(Adam._ctrl_cache) > 64:
-                Adam._ctrl_cache.clear()
-            c = torch.tensor([1.0 / scale, 0.0, 0.0, 1.0], dtype=torch.float32, device=device)
-            Adam._ctrl_cache[key] = c
-        return c
+        """Device control block [gradient multiplier, skip flag, norm, clip coefficient] for a host-side ``scale``:
+        one pinned staging buffer and one device buffer per optimizer and device, refilled with an asynchronous copy
+        (the scale changes with every clipped update, so nothing is cached by value)."""
+        bufs = self.__dict__.setdefault("_ctrl_bufs", {})
+        entry = bufs.get(str(device))
+        if entry is None:
+            host = torch.zeros(4, dtype=torch.float32)
+            if torch.cuda.is_available():
+                host = host.pin_memory()
+            entry = (host, torch.zeros(4, dtype=torch.float32, device=device), [None])
+            bufs[str(device)] = entry
+        host, dev, pending = entry
+        if pending[0] is not None:
+            pending[0].synchronize()  # the previous copy out of the staging buffer has to be done before a refill
+        host[0], host[1], host[2], host[3] = 1.0 / scale, 0.0, 0.0, 1.0
+        dev.copy_(host, non_blocking=True)
+        if dev.is_cuda:
+            pending[0] = torch.cuda.Event()
+            pending[0].record()
+        return dev

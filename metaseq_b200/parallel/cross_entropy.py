@@ -65,13 +65,17 @@ class _VocabParallelCrossEntropy(torch.autograd.Function):
 
 
 class _FusedVocabParallelCrossEntropy(torch.autograd.Function):
-    """Kernel path for 16-bit logits on a GPU: per-row (max, sum-exp, target logit) triples computed by one
-    kernel, exchanged in a single small all-reduce (peer-memory kernel when available), then one kernel that
-    writes the loss and overwrites the logits with the gradient.  fp32 logits are never materialised."""
+    """Kernel path for 16-bit logits on a GPU.  Every rank needs, per row, the (max, sum-exp, target logit) of each
+    rank's vocabulary slice.  Where the logits product left its row statistics (``row_stats``) one small kernel folds
+    them and, with the fused communication backend, stores the triple straight into every peer's exchange table over
+    NVLink; the kernel that writes the loss and overwrites the logits with the gradient polls its own table.  Without
+    row statistics one kernel reads the logits for the triples, and without the fused backend they travel in one
+    small NCCL all-reduce.  fp32 logits are never materialised."""
 
     @staticmethod
-    def forward(ctx, logits, target, ignore_index):
+    def forward(ctx, logits, target, ignore_index, row_stats=None):
         from metaseq_b200.ops import _lib
+        from metaseq_b200.ops import autograd as ops_ag
         from metaseq_b200.parallel import symm
 
         group = mpu.get_tensor_model_parallel_group()
@@ -83,31 +87,69 @@ class _FusedVocabParallelCrossEntropy(torch.autograd.Function):
         tgt = target.reshape(-1).contiguous()
         lib = _lib.kernels()
         bf = int(logits.dtype == torch.bfloat16)
-        stats = torch.zeros((world, rows, 3), dtype=torch.float32, device=logits.device)
-        rc = lib.msq_vp_ce_partial(_lib.ptr(l2), l2.stride(0), _lib.ptr(tgt), _lib.ptr(stats[rank]), rows, V, rank * V, bf,
-                                   _lib.stream_ptr())
-        _lib.check_rc(rc, "msq_vp_ce_partial")
-        tp = symm.get_tp_comm(group, logits.device, 1, 8, logits.dtype) if symm.comm_backend() == "fused" else None
-        if tp is not None:
-            tp.comm.all_reduce(stats.view(-1))
-        else:
-            dist.all_reduce(stats, group=group)
+        ctx.pre_scaled = ops_ag.upstream_grad_hint()
         loss = torch.empty(rows, dtype=torch.float32, device=logits.device)
-        rc = lib.msq_vp_ce_finish(_lib.ptr(l2), l2.stride(0), _lib.ptr(tgt), _lib.ptr(stats), world, _lib.ptr(loss), rows, V,
-                                  rank * V, int(ignore_index), 1.0, bf, _lib.stream_ptr())
-        _lib.check_rc(rc, "msq_vp_ce_finish")
+        exchange = symm.get_ce_exchange(group, logits.device, rows) if row_stats is not None else None
+        if exchange is not None:
+            tables, mine, epoch = exchange.next()
+            rc = lib.msq_ce_merge_rowstats(_lib.ptr(row_stats[0]), _lib.ptr(row_stats[1]), row_stats[0].shape[0], rows,
+                                           _lib.ptr(l2), l2.stride(0), _lib.ptr(tgt), V, rank * V, None, tables, world,
+                                           rank, exchange.rows_cap, epoch, bf, _lib.stream_ptr())
+            _lib.check_rc(rc, "msq_ce_merge_rowstats")
+            import ctypes
+
+            rc = lib.msq_vp_ce_finish_exchanged(_lib.ptr(l2), l2.stride(0), _lib.ptr(tgt), ctypes.c_void_p(mine), world,
+                                                exchange.rows_cap, epoch, _lib.ptr(loss), rows, V, rank * V,
+                                                int(ignore_index), ctx.pre_scaled, bf,
+                                                _lib.ptr(_lib.status_word(logits.device)), _lib.stream_ptr())
+            _lib.check_rc(rc, "msq_vp_ce_finish_exchanged")
+            _note_exchange_once(world, rows)
+        else:
+            stats = torch.zeros((world, rows, 3), dtype=torch.float32, device=logits.device)
+            if row_stats is not None:
+                rc = lib.msq_ce_merge_rowstats(_lib.ptr(row_stats[0]), _lib.ptr(row_stats[1]), row_stats[0].shape[0],
+                                               rows, _lib.ptr(l2), l2.stride(0), _lib.ptr(tgt), V, rank * V,
+                                               _lib.ptr(stats[rank]), None, 1, 0, rows, 0, bf, _lib.stream_ptr())
+                _lib.check_rc(rc, "msq_ce_merge_rowstats")
+            else:
+                rc = lib.msq_vp_ce_partial(_lib.ptr(l2), l2.stride(0), _lib.ptr(tgt), _lib.ptr(stats[rank]), rows, V,
+                                           rank * V, bf, _lib.stream_ptr())
+                _lib.check_rc(rc, "msq_vp_ce_partial")
+            if world > 1:
+                tp = symm.get_tp_comm(group, logits.device, 1, 8, logits.dtype) if symm.comm_backend() == "fused" else None
+                if tp is not None:
+                    tp.comm.all_reduce(stats.view(-1))
+                else:
+                    dist.all_reduce(stats, group=group)
+            rc = lib.msq_vp_ce_finish(_lib.ptr(l2), l2.stride(0), _lib.ptr(tgt), _lib.ptr(stats), world, _lib.ptr(loss),
+                                      rows, V, rank * V, int(ignore_index), ctx.pre_scaled, bf, _lib.stream_ptr())
+            _lib.check_rc(rc, "msq_vp_ce_finish")
         ctx.save_for_backward(l2)
         ctx.shape = logits.shape
         return loss.view(target.shape)
 
     @staticmethod
     def backward(ctx, grad_output):
-        (grad,) = ctx.saved_tensors  # (softmax - onehot), zero rows where the target is ignored
+        (grad,) = ctx.saved_tensors  # (softmax - onehot) * pre_scaled, zero rows where the target is ignored
         from metaseq_b200.ops import functional as ops_f
 
-        # in place: the saved tensor is the logits buffer, which nothing else reads after the loss
-        ops_f.scale_rows_(grad, grad_output)
-        return grad.view(ctx.shape), None, None
+        # in place: the saved tensor is the logits buffer, which nothing else reads after the loss.  Rows whose
+        # incoming factor equals the one already applied are left alone.
+        ops_f.scale_rows_(grad, grad_output, ref=ctx.pre_scaled)
+        return grad.view(ctx.shape), None, None, None
+
+
+_EXCHANGE_NOTED = [False]
+
+
+def _note_exchange_once(world, rows):
+    if not _EXCHANGE_NOTED[0]:
+        _EXCHANGE_NOTED[0] = True
+        import logging
+
+        logging.getLogger(__name__).info(
+            "vocab-parallel cross entropy: row statistics from the logits GEMM epilogue, exchanged over peer memory "
+            "(%d ranks, %d rows)", world, rows)
 
 
 def fused_vocab_parallel_cross_entropy_ok(logits) -> bool:
@@ -117,10 +159,14 @@ def fused_vocab_parallel_cross_entropy_ok(logits) -> bool:
             and logits.shape[-1] % 8 == 0 and logits.is_contiguous())
 
 
-def vocab_parallel_cross_entropy(vocab_parallel_logits, target, ignore_index: int = -100):
+def vocab_parallel_cross_entropy(vocab_parallel_logits, target, ignore_index: int = -100, row_stats=None):
     """Per-token NLL for ``[..., V/p]`` logits and global-vocabulary targets.  16-bit logits on a GPU take the
     kernel path (rows whose target equals ``ignore_index`` get zero loss and gradient there); otherwise the
-    PyTorch implementation, which needs fp32 logits and leaves the masking of ignored targets to the caller."""
+    PyTorch implementation, which needs fp32 logits and leaves the masking of ignored targets to the caller.
+    ``row_stats`` (default: the ``_msq_row_stats`` attribute of the logits): the softmax pieces that the logits
+    product computed in its epilogue."""
     if fused_vocab_parallel_cross_entropy_ok(vocab_parallel_logits):
-        return _FusedVocabParallelCrossEntropy.apply(vocab_parallel_logits, target, ignore_index)
+        if row_stats is None:
+            row_stats = getattr(vocab_parallel_logits, "_msq_row_stats", None)
+        return _FusedVocabParallelCrossEntropy.apply(vocab_parallel_logits, target, ignore_index, row_stats)
     return _VocabParallelCrossEntropy.apply(vocab_parallel_logits, target)

@@ -112,6 +112,9 @@ class FullyShardedDataParallel(nn.Module):
         self.compute_dtype = compute_dtype
         self.use_sharded_state = use_sharded_state
         self.state_dict_device = state_dict_device
+        # ``cpu_offload``: the trainable shard, its gradient and the optimizer state live in (pinned) host memory;
+        # the shard is copied to the compute device for every gather and the reduced gradient copied back
+        self.cpu_offload = bool(cpu_offload)
         # ``comm``: a ``PeerComm``, or "fused" (one is built for the process group at first use, CUDA and
         # world size > 1 only), or None / "nccl" for torch.distributed collectives
         self.comm = comm if not isinstance(comm, str) else None
@@ -193,6 +196,13 @@ class FullyShardedDataParallel(nn.Module):
             flat[off:off + p.numel()].copy_(p.data.reshape(-1))
             off += p.numel()
         local = flat[self.rank * shard:(self.rank + 1) * shard].clone()
+        if self.cpu_offload:
+            # compute where the module was built, or on the current GPU when it was built on the host
+            self._offload_compute_device = device if device.type != "cpu" or not torch.cuda.is_available() \
+                else torch.device("cuda", torch.cuda.current_device())
+            local = local.cpu()
+            if torch.cuda.is_available():
+                local = local.pin_memory()
         self.flat_param = nn.Parameter(local)
         self.flat_param._is_sharded = self.world_size > 1
         self.flat_param._fsdp_unit = self
@@ -216,7 +226,7 @@ class FullyShardedDataParallel(nn.Module):
         off = 0
         for (mod, pname), shape, n in zip(self._param_infos, self.param_shapes, self.param_numels):
             if full is None:
-                v = torch.empty(0, dtype=self.flat_param.dtype, device=self.flat_param.device)
+                v = torch.empty(0, dtype=self.flat_param.dtype, device=self._compute_device)
             else:
                 v = full[off:off + n].view(shape)
                 v.requires_grad_(self.flat_param.requires_grad)
@@ -268,15 +278,24 @@ class FullyShardedDataParallel(nn.Module):
     # ----------------------------------------------------------------- gather
     def _comm_stream(self):
         root = self._root()
-        if getattr(root, "_side_stream", None) is None and self.flat_param is not None and self.flat_param.is_cuda:
+        if getattr(root, "_side_stream", None) is None and self.flat_param is not None \
+                and self._compute_device.type == "cuda":
             root._side_stream = torch.cuda.Stream()
         return getattr(root, "_side_stream", None)
 
     def _root(self) -> "FullyShardedDataParallel":
         return self.__dict__.get("_root_ref") or self
 
+    @property
+    def _compute_device(self) -> torch.device:
+        """Where gathered parameters and gradients live: the shard's own device unless the shard is offloaded."""
+        if self.cpu_offload:
+            return self._offload_compute_device
+        return self.flat_param.device
+
     def _aliases_shard(self) -> bool:
-        return self.world_size == 1 and self._compute_dtype() == self.flat_param.dtype
+        return self.world_size == 1 and self._compute_dtype() == self.flat_param.dtype \
+            and self.flat_param.device == self._compute_device
 
     def _gather_full(self, asynchronous: bool = False):
         """Makes the full flat parameter current (idempotent until ``_needs_gather`` is set)."""
@@ -284,6 +303,8 @@ class FullyShardedDataParallel(nn.Module):
             return
         cdt = self._compute_dtype()
         src = self.flat_param.data
+        if src.device != self._compute_device:
+            src = src.to(self._compute_device, non_blocking=True)  # offloaded shard: host -> device per gather
         if self._aliases_shard():
             if self._full_param is None or self._full_param.data_ptr() != src.data_ptr():
                 self._full_param = src
@@ -336,7 +357,7 @@ class FullyShardedDataParallel(nn.Module):
         cdt = self._compute_dtype()
         root = self._root()
         arena = root.__dict__.get("_grad_arena")
-        if arena is None or arena.dtype != cdt or arena.device != self.flat_param.device:
+        if arena is None or arena.dtype != cdt or arena.device != self._compute_device:
             units = [u for u in (root.__dict__.get("_units") or [self]) if u.has_params and u.flat_param.requires_grad]
             if self not in units:
                 units.append(self)
@@ -344,12 +365,12 @@ class FullyShardedDataParallel(nn.Module):
             for u in units:
                 offs[id(u)] = total
                 total += (u.padded_numel + 127) // 128 * 128
-            arena = torch.zeros(total, dtype=cdt, device=self.flat_param.device)
+            arena = torch.zeros(total, dtype=cdt, device=self._compute_device)
             root.__dict__["_grad_arena"] = arena
             root.__dict__["_grad_arena_offsets"] = offs
         off = root.__dict__["_grad_arena_offsets"].get(id(self))
         if off is None:
-            self._full_grad = torch.zeros(self.padded_numel, dtype=cdt, device=self.flat_param.device)
+            self._full_grad = torch.zeros(self.padded_numel, dtype=cdt, device=self._compute_device)
         else:
             self._full_grad = arena[off:off + self.padded_numel]
         for v in self._views:
@@ -394,7 +415,13 @@ class FullyShardedDataParallel(nn.Module):
     def _build_comm(self):
         """One ``PeerComm`` for all units when the fused communication backend was requested."""
         units = [u for u in self._units if u.has_params and u._comm_request == "fused" and u.comm is None
-                 and u.world_size > 1 and u.flat_param.is_cuda]
+                 and u.world_size > 1 and u._compute_device.type == "cuda"]
+        if units and self.reshard_after_forward:
+            # the peer-memory collectives fill gathered copies that stay resident in symmetric memory; a model
+            # that asks for its gathered parameters to be dropped after forward gets the library collectives
+            logger.warning("--comm-backend fused keeps gathered parameters resident (use --no-reshard-after-forward); "
+                           "reshard-after-forward was requested, so FSDP uses NCCL collectives")
+            return
         if not units:
             return
         from .symm import PeerComm
@@ -403,7 +430,7 @@ class FullyShardedDataParallel(nn.Module):
         for u in units:
             esz = torch.empty((), dtype=u._compute_dtype()).element_size()
             need += 2 * (u.padded_numel * esz + 2048)  # gathered copy + reduce-scatter landing slots
-        comm = PeerComm(units[0].process_group, units[0].flat_param.device, heap_bytes=need)
+        comm = PeerComm(units[0].process_group, units[0]._compute_device, heap_bytes=need)
         for u in units:
             u.comm = comm
         self._peer_comm = comm
@@ -425,6 +452,8 @@ class FullyShardedDataParallel(nn.Module):
                     u._needs_gather = True
                 if u._needs_gather:
                     src = u.flat_param.data
+                    if src.device != u._compute_device:
+                        src = src.to(u._compute_device, non_blocking=True)
                     cdt = u._compute_dtype()
                     items.append((u._full_param, src if src.dtype == cdt else src.to(cdt)))
                     u._needs_gather = False
@@ -547,6 +576,12 @@ class FullyShardedDataParallel(nn.Module):
                 v.grad = None
 
     def _accumulate_shard_grad(self, shard: torch.Tensor, owns_buffer: bool):
+        if shard.device != self.flat_param.device:
+            side = getattr(self._root(), "_side_stream", None)
+            if side is not None and shard.is_cuda:
+                torch.cuda.current_stream().wait_stream(side)
+            shard = shard[: self.flat_param.numel()].to(self.flat_param.device)  # offloaded: device -> host
+            owns_buffer = False
         if self.flat_param.grad is None:
             self.flat_param.grad = shard if shard.numel() == self.flat_param.numel() else shard[: self.flat_param.numel()]
             if owns_buffer:

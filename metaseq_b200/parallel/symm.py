@@ -712,6 +712,55 @@ class DecodeReduce:
         self.heap.close()
 
 
+class CrossEntropyExchange:
+    """Tables through which the tensor-parallel ranks hand each other the per-row (max, sum-exp, target logit) of
+    their vocabulary slice (``msq_ce_merge_rowstats`` stores, ``msq_vp_ce_finish_exchanged`` polls).  Two tables
+    alternate between consecutive losses; every value travels with the epoch of its call.  Replaces the three
+    all-reduces of the reference's vocabulary-parallel cross entropy
+    (metaseq/modules/megatron/mpu/cross_entropy.py:24-66)."""
+
+    def __init__(self, group, device, rows_cap: int, provider: str = "auto"):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.rows_cap = int(rows_cap)
+        nbytes = self.world * self.rows_cap * 3 * 8
+        self.heap = SymmetricHeap(group, 2 * (nbytes + 4096) + (1 << 16), device, provider=provider)  # zero-filled
+        offs = [self.heap.alloc(nbytes), self.heap.alloc(nbytes)]
+        self._tables = [(ctypes.c_void_p * self.world)(*[p + off for p in self.heap.ptrs]) for off in offs]
+        self._local = [self.heap.ptrs[self.rank] + off for off in offs]
+        self.calls = 0
+
+    def next(self):
+        """(peer table pointers, this rank's table pointer, epoch) for the next loss."""
+        self.calls += 1
+        par = self.calls & 1
+        return self._tables[par], self._local[par], self.calls & 0xFFFFFFFF or 1
+
+    def close(self):
+        self.heap.close()
+
+
+_CE_EXCHANGES: Dict[tuple, CrossEntropyExchange] = {}
+
+
+def get_ce_exchange(group, device, rows: int) -> Optional[CrossEntropyExchange]:
+    """The exchange of a tensor-parallel group, created (collectively, at the first loss) for at least ``rows``
+    rows; ``None`` when the fused backend is off or the group has one rank."""
+    if _COMM_BACKEND != "fused" or group is None or torch.device(device).type != "cuda":
+        return None
+    if dist.get_world_size(group) < 2 or dist.get_world_size(group) > 16:
+        return None
+    key = (id(group), str(device))
+    ex = _CE_EXCHANGES.get(key)
+    if ex is None or ex.rows_cap < rows:
+        if ex is not None:
+            ex.close()
+        ex = CrossEntropyExchange(group, device, max(rows, 4096))
+        _CE_EXCHANGES[key] = ex
+    return ex
+
+
 # ------------------------------------------------------------------ process-wide selection
 _COMM_BACKEND = "nccl"
 _TP_COMMS: Dict[tuple, TPComm] = {}
@@ -733,6 +782,7 @@ def drop_tp_comms():
     """Forgets the cached tensor-parallel communicators (their symmetric memory is released with them).  For
     programs that build several models with different process groups one after the other."""
     _TP_COMMS.clear()
+    _CE_EXCHANGES.clear()
 
 
 def get_tp_comm(group, device, rows: int, cols: int, dtype) -> Optional[TPComm]:

@@ -33,6 +33,7 @@ from metaseq_b200 import checkpoint_utils, models, optim, utils
 from metaseq_b200.dataclass.utils import Cfg
 from metaseq_b200.logging import meters, metrics
 from metaseq_b200.nan_detector import NanDetector
+from metaseq_b200.ops import autograd as ops_autograd
 from metaseq_b200.optim import lr_scheduler
 from metaseq_b200.parallel import mpu
 from metaseq_b200.parallel import utils as dist_utils
@@ -79,8 +80,10 @@ class Trainer:
             dtype = torch.float16 if (c.fp16 or c.memory_efficient_fp16) else (torch.bfloat16 if c.bf16 else None)
             if dtype is not None:
                 model, criterion = model.to(dtype=dtype), criterion.to(dtype=dtype)
-        if not getattr(self.cfg.distributed_training, "pipeline_model_parallel", False):
-            model, criterion = model.to(device=self.device), criterion.to(device=self.device)
+        offloaded = self.is_fsdp and getattr(self.cfg.distributed_training, "cpu_offload", False)
+        if not offloaded:  # offloaded shards stay in host memory; their units compute on the device by themselves
+            model = model.to(device=self.device)
+        criterion = criterion.to(device=self.device)
         for first, *others in tied:
             owner = _get_module_by_path(model, first)
             for path in others:
@@ -452,6 +455,9 @@ class Trainer:
         self.model.train()
         self.criterion.train()
         self.zero_grad()
+        # the loss kernels store their gradient already multiplied by the loss scale that backward will bring
+        scaler = getattr(self.optimizer, "scaler", None)
+        ops_autograd.set_upstream_grad_hint(scaler.loss_scale if scaler is not None else None)
         metrics.log_start_time("train_wall", priority=800, round=2)
         logging_outputs, sample_size = [], 0
         for i, sample in enumerate(samples):

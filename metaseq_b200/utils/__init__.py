@@ -77,7 +77,7 @@ def make_positions(tokens: torch.Tensor, padding_idx: int) -> torch.Tensor:
 
 # ------------------------------------------------------------ grad norms
 def multi_tensor_l2_norm(tensors: List[torch.Tensor]) -> torch.Tensor:
-    """fp32 L2 norm over a list of tensors; one fused sum-of-squares kernel per tensor on a
+    """fp32 L2 norm over a list of tensors; one list-form sum-of-squares launch for all tensors on a
     GPU (the reference uses apex ``multi_tensor_l2norm``: metaseq/utils.py:104-127)."""
     from metaseq_b200.ops import functional as ops
 
@@ -85,9 +85,18 @@ def multi_tensor_l2_norm(tensors: List[torch.Tensor]) -> torch.Tensor:
         return torch.tensor(0.0)
     dev = tensors[0].device
     if dev.type == "cuda":
-        acc = torch.zeros(1, dtype=torch.float32, device=dev)
-        for t in tensors:
-            ops.sumsq(t.detach().reshape(-1) if t.is_contiguous() else t.detach().contiguous().view(-1), acc, True)
+        flat = [t.detach().reshape(-1) if t.is_contiguous() else t.detach().contiguous().view(-1) for t in tensors]
+        acc = torch.empty(1, dtype=torch.float32, device=dev)
+        from metaseq_b200.ops import _lib
+
+        if len(flat) > 1 and ops.get_backend() != "torch" and all(t.dtype == flat[0].dtype for t in flat) \
+                and flat[0].dtype in (torch.float16, torch.bfloat16, torch.float32) \
+                and _lib.kernels_path().exists() and hasattr(_lib.kernels()._lib, "msq_sumsq_multi"):
+            ops.sumsq_multi(flat, acc, False)  # the whole list in one launch
+        else:
+            acc.zero_()
+            for t in flat:
+                ops.sumsq(t, acc, True)
         return acc.sqrt()[0]
     return torch.norm(torch.stack([torch.norm(t.detach().float()) for t in tensors]))
 

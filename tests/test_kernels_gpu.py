@@ -674,3 +674,214 @@ def test_adam_with_fp16_statistics_on_the_kernel_path():
         assert st["exp_avg_scale"].is_cuda  # no host synchronisation for the scale
         assert (p - q).abs().max().item() < 5e-4
     _status_ok()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K", [(256, 512, 128), (600, 50272 // 8, 256), (1024, 1000, 512)])
+def test_gemm_row_statistics_fold_into_the_log_sum_exp(dtype, M, N, K):
+    """The logits product's epilogue leaves per-tile (max, sum-exp) of every row over the stored values; folded over
+    the tiles they give the row's log-sum-exp, and the cross entropy built on them equals the fp32 oracle."""
+    torch.manual_seed(21)
+    a = (torch.randn(M, K, device="cuda") * 0.5).to(dtype)
+    w = (torch.randn(N, K, device="cuda") * 0.5).to(dtype)
+    out, stats = F.gemm_with_row_stats(a, w)
+    assert stats is not None and stats[0].shape == (math.ceil(N / 256), M)
+    want = _ref(F.gemm, a, w)
+    _close(out, want, dtype, scale=4.0)
+    m = stats[0].max(dim=0)[0]
+    lse = m + torch.log((stats[1] * torch.exp(stats[0] - m)).sum(dim=0))
+    torch.testing.assert_close(lse, torch.logsumexp(out.float(), dim=1), rtol=1e-4, atol=1e-3)
+    target = torch.randint(0, N, (M,), device="cuda")
+    target[::5] = 1
+    l1, l2 = out.clone(), out.clone()
+    loss = F.cross_entropy_from_row_stats(l1, target, 1, 64.0, stats)
+    lossr, _ = _ref(F.cross_entropy_fwd_bwd, l2, target, 1, 64.0, True)
+    torch.testing.assert_close(loss, lossr, rtol=1e-3, atol=2e-3)
+    _close(l1, l2, dtype, scale=2.0)
+    _status_ok()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("per_row", [True, False])
+def test_scale_rows_relative_to_the_factor_already_applied(dtype, per_row):
+    torch.manual_seed(5)
+    rows, cols = 200, 512
+    x = torch.randn(rows, cols, device="cuda", dtype=dtype)
+    keep = x.clone()
+    g = torch.full((rows if per_row else 1,), 128.0, device="cuda")
+    F.scale_rows_(x, g, ref=128.0)
+    assert torch.equal(x, keep)  # the expected factor arrived: nothing is rewritten
+    if per_row:
+        g[::3] = 0.0
+        g[1::3] = 64.0
+    else:
+        g[0] = 32.0
+    F.scale_rows_(x, g, ref=128.0)
+    want = keep.float() * (g / 128.0).reshape(-1, 1)
+    _close(x, want, dtype)
+
+
+def test_cross_entropy_applies_the_announced_loss_scale_in_the_forward_pass():
+    """With the upstream factor announced, the gradient leaves the forward pass already scaled and the backward pass
+    only checks; a different factor in backward is still honoured."""
+    from metaseq_b200.ops import autograd as ops_ag
+
+    torch.manual_seed(9)
+    rows, V = 512, 4096
+    x = (torch.randn(rows, 256, device="cuda") * 0.5).half().requires_grad_(True)
+    w = (torch.randn(V, 256, device="cuda") * 0.2).half().requires_grad_(True)
+    target = torch.randint(2, V, (rows,), device="cuda")
+
+    def run(hint, upstream):
+        ops_ag.set_upstream_grad_hint(hint)
+        try:
+            x.grad = w.grad = None
+            logits = ops_ag.linear(x, w, row_stats=True)
+            assert getattr(logits, "_msq_row_stats", None) is not None
+            loss = ops_ag.cross_entropy_sum(logits, target, 1)
+            (loss * upstream).backward()
+            return float(loss), x.grad.clone(), w.grad.clone()
+        finally:
+            ops_ag.set_upstream_grad_hint(None)
+
+    l0, gx0, gw0 = run(None, 64.0)
+    l1, gx1, gw1 = run(64.0, 64.0)
+    l2, gx2, gw2 = run(8.0, 64.0)
+    assert l0 == pytest.approx(l1, rel=1e-5) and l0 == pytest.approx(l2, rel=1e-5)
+    for a, b in ((gx0, gx1), (gw0, gw1), (gx0, gx2), (gw0, gw2)):
+        torch.testing.assert_close(a.float(), b.float(), rtol=2e-2, atol=2e-2 * float(a.float().abs().max()))
+    ref = torch.nn.functional.cross_entropy(x.detach().float() @ w.detach().float().t(), target, reduction="sum")
+    assert l0 == pytest.approx(float(ref), rel=2e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+def test_sum_of_squares_list_form_matches_the_per_tensor_kernel(dtype):
+    from metaseq_b200 import utils
+
+    torch.manual_seed(13)
+    sizes = [1, 7, 4096, 100_003, 2_000_000, 8, 33]
+    big = torch.randn(sum(sizes) + 64, device="cuda").to(dtype)
+    tensors, off = [], 3  # odd offsets: some tensors are not 16-byte aligned
+    for n in sizes:
+        tensors.append(big[off:off + n])
+        off += n + 1
+    out = torch.full((1,), 5.0, device="cuda")
+    before = _lib.launch_count()
+    F.sumsq_multi(tensors, out, True)
+    assert _lib.launch_count() == before + 1
+    want = 5.0 + sum(float(t.double().pow(2).sum()) for t in tensors)
+    assert float(out) == pytest.approx(want, rel=2e-5)
+    again = torch.zeros(1, device="cuda")
+    F.sumsq_multi(tensors, again, False)
+    twice = torch.zeros(1, device="cuda")
+    F.sumsq_multi(tensors, twice, False)
+    assert float(again) == float(twice)  # same bits from call to call
+    norm = utils.multi_tensor_l2_norm(tensors)
+    assert float(norm) == pytest.approx(math.sqrt(want - 5.0), rel=2e-5)
+
+
+def _attn_fwd_bwd(q, k, v, qkv, d_out, scale, use_ref, **masks):
+    """Forward and backward through the kernels (or the PyTorch restatement): returns (out, lse, dqkv)."""
+    B, T, H, d = q.shape
+    D = H * d
+    fwd = (lambda *a, **kw: _ref(F.flash_attn_fwd, *a, **kw)) if use_ref else F.flash_attn_fwd
+    bwd = (lambda *a, **kw: _ref(F.flash_attn_bwd, *a, **kw)) if use_ref else F.flash_attn_bwd
+    out, lse = fwd(q, k, v, scale, True, **masks)
+    dqkv = torch.zeros_like(qkv)
+    dk, dv, dq = (dqkv[..., i * D:(i + 1) * D].view(B, T, H, d) for i in range(3))
+    bwd(q, k, v, out, d_out, lse, scale, True, dq, dk, dv, **masks)
+    return out, lse, dqkv
+
+
+def _document_starts(B, T, mean_len, seed):
+    g = torch.Generator().manual_seed(seed)
+    starts = torch.zeros(B, T, dtype=torch.int32)
+    for b in range(B):
+        t = 0
+        while t < T:
+            n = int(torch.randint(1, 2 * mean_len, (1,), generator=g))
+            starts[b, t:t + n] = t
+            t += n
+    return starts.cuda()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("d", [80, 96, 32])
+@pytest.mark.parametrize("T", [256, 200])
+def test_flash_attention_head_sizes_between_the_native_ones(dtype, d, T):
+    """Head sizes 80 and 96 (OPT-2.7B, OPT-760M) run the 128-wide kernels on zero-filled columns, 32 the 64-wide."""
+    torch.manual_seed(31)
+    B, H = 2, 3
+    qkv, q, k, v = _attn_inputs(B, T, H, d, dtype)
+    d_out = (torch.randn(B, T, H * d, device="cuda") * 0.5).to(dtype)
+    before = _lib.launch_count()
+    got = _attn_fwd_bwd(q, k, v, qkv, d_out, d ** -0.5, False)
+    assert _lib.launch_count() > before  # the kernel path, not the PyTorch restatement
+    want = _attn_fwd_bwd(q, k, v, qkv, d_out, d ** -0.5, True)
+    _status_ok()
+    _close(got[0], want[0], dtype)
+    torch.testing.assert_close(got[1], want[1], rtol=2e-3, atol=2e-3)
+    _close(got[2], want[2], dtype, scale=4.0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("d,T,mean_len", [(64, 512, 40), (128, 384, 150), (64, 1000, 300), (96, 256, 20)])
+def test_flash_attention_document_starts(dtype, d, T, mean_len):
+    """Queries see only the keys of their own document; kv blocks before a tile's documents are skipped."""
+    torch.manual_seed(32)
+    B, H = 2, 2
+    qkv, q, k, v = _attn_inputs(B, T, H, d, dtype)
+    d_out = (torch.randn(B, T, H * d, device="cuda") * 0.5).to(dtype)
+    starts = _document_starts(B, T, mean_len, 5)
+    got = _attn_fwd_bwd(q, k, v, qkv, d_out, d ** -0.5, False, doc_start=starts)
+    want = _attn_fwd_bwd(q, k, v, qkv, d_out, d ** -0.5, True, doc_start=starts)
+    plain = _attn_fwd_bwd(q, k, v, qkv, d_out, d ** -0.5, True)
+    _status_ok()
+    _close(got[0], want[0], dtype)
+    torch.testing.assert_close(got[1], want[1], rtol=2e-3, atol=2e-3)
+    _close(got[2], want[2], dtype, scale=4.0)
+    assert (want[0].float() - plain[0].float()).abs().max() > 1e-2
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("d,T", [(64, 384), (128, 200)])
+def test_flash_attention_alibi(dtype, d, T):
+    from metaseq_b200.modules.attention_bias import alibi_slopes
+
+    torch.manual_seed(33)
+    B, H = 2, 4
+    qkv, q, k, v = _attn_inputs(B, T, H, d, dtype)
+    d_out = (torch.randn(B, T, H * d, device="cuda") * 0.5).to(dtype)
+    slopes = torch.tensor(alibi_slopes(H), device="cuda")
+    starts = _document_starts(B, T, 90, 6)
+    for masks in (dict(alibi_slopes=slopes), dict(alibi_slopes=slopes, doc_start=starts)):
+        got = _attn_fwd_bwd(q, k, v, qkv, d_out, d ** -0.5, False, **masks)
+        want = _attn_fwd_bwd(q, k, v, qkv, d_out, d ** -0.5, True, **masks)
+        _status_ok()
+        _close(got[0], want[0], dtype)
+        torch.testing.assert_close(got[1], want[1], rtol=2e-3, atol=2e-3)
+        _close(got[2], want[2], dtype, scale=4.0)
+
+
+def test_flash_attention_at_the_benchmarked_shape():
+    """T = 2048 with B * H = 256 (the OPT-1.3B training shape): enough CTAs to fill every SM several times.  The
+    oracle runs per slice of heads to bound its [B, H, T, T] scores."""
+    torch.manual_seed(34)
+    B, T, H, d = 8, 2048, 32, 64
+    qkv, q, k, v = _attn_inputs(B, T, H, d, torch.float16)
+    D = H * d
+    d_out = (torch.randn(B, T, D, device="cuda") * 0.5).half()
+    out, lse, dqkv = _attn_fwd_bwd(q, k, v, qkv, d_out, d ** -0.5, False)
+    _status_ok()
+    for b, h0 in ((0, 0), (3, 8), (7, 28)):
+        sl = slice(h0, h0 + 4)
+        qs, ks, vs = (t[b:b + 1, :, sl].contiguous() for t in (q, k, v))
+        sub = torch.cat([ks.reshape(1, T, -1), vs.reshape(1, T, -1), qs.reshape(1, T, -1)], dim=-1)
+        kk, vv, qq = (sub[..., i * 4 * d:(i + 1) * 4 * d].view(1, T, 4, d) for i in range(3))
+        do = d_out[b:b + 1].view(1, T, H, d)[:, :, sl].reshape(1, T, 4 * d).contiguous()
+        o_r, lse_r, dsub = _attn_fwd_bwd(qq, kk, vv, sub, do, d ** -0.5, True)
+        _close(out[b:b + 1].view(1, T, H, d)[:, :, sl].reshape(1, T, 4 * d), o_r, torch.float16)
+        torch.testing.assert_close(lse[b:b + 1, sl], lse_r, rtol=2e-3, atol=2e-3)
+        got = torch.cat([dqkv[b:b + 1, :, i * D:(i + 1) * D].view(1, T, H, d)[:, :, sl].reshape(1, T, 4 * d)
+                         for i in range(3)], dim=-1)
+        _close(got, dsub, torch.float16, scale=4.0)

@@ -346,3 +346,30 @@ def test_generator_interface_options_on_the_gpu():
                         alpha_presence=0.2, alpha_frequency=0.2, alpha_presence_src=0.1, alpha_frequency_src=0.1, seed=5)
     assert [len(b) for b in fancy] == [1, 1, 1]
     assert _lib.check_status("cuda") == 0
+
+
+def test_cpu_offload_keeps_shards_and_optimizer_state_in_host_memory():
+    """``--cpu-offload``: flat shards, their gradients and the Adam moments are host tensors, the step computes on
+    the GPU through the kernels, and the loss follows the run without offloading."""
+    plain, batch = _trainer(_cfg())
+    ref = []
+    for _ in range(4):
+        out = plain.train_step([batch])
+        if out is not None:
+            ref.append(float(out["loss"]))
+    tr, batch = _trainer(_cfg(["--cpu-offload"]))
+    losses = []
+    _lib.reset_launch_count()
+    for _ in range(4):
+        out = tr.train_step([batch])
+        if out is not None:
+            losses.append(float(out["loss"]))
+    assert _lib.launch_count() > 0
+    units = [m for m in tr.get_model().modules() if getattr(m, "is_fsdp", False) and m.has_params]
+    assert units and all(u.flat_param.device.type == "cpu" for u in units)
+    assert all(u._full_param.device.type == "cuda" for u in units)
+    state = tr.optimizer.optimizer.state
+    assert state and all(t.device.type == "cpu" for st in state.values() for t in st.values() if torch.is_tensor(t))
+    assert len(losses) == len(ref) and losses[-1] < losses[0]
+    for a, b in zip(losses, ref):
+        assert a == pytest.approx(b, abs=5e-2)

@@ -33,15 +33,13 @@ VARIANTS = {
 }
 
 
-@pytest.mark.parametrize("name", sorted(VARIANTS))
-def test_training_option_runs_and_learns(name, tmp_path):
-    extra = VARIANTS[name]
+def _run(save_dir, extra, updates=6):
     argv = ["--task", "dummy_lm", "--dict-size", "124", "--tokens-per-sample", "16", "--batch-size", "2",
             "--arch", "transformer_lm_megatron", "--decoder-layers", "2", "--decoder-embed-dim", "32",
             "--decoder-ffn-embed-dim", "64", "--decoder-attention-heads", "2", "--decoder-learned-pos",
             "--share-decoder-input-output-embed", "--dropout", "0.0", "--attention-dropout", "0.0", "--criterion",
             "cross_entropy", "--optimizer", "adam", "--lr", "1e-2", "--clip-norm", "1.0", "--cpu",
-            "--distributed-world-size", "1", "--save-dir", str(tmp_path), "--disable-validation", "--log-format", "none",
+            "--distributed-world-size", "1", "--save-dir", str(save_dir), "--disable-validation", "--log-format", "none",
             *extra]
     cfg = convert_namespace_to_config(options.parse_args_and_arch(options.get_training_parser(), input_args=argv))
     torch.manual_seed(1)
@@ -51,9 +49,23 @@ def test_training_option_runs_and_learns(name, tmp_path):
     task.load_dataset("train")
     batch = task.dataset("train").collater([0, 1])
     losses = []
-    for _ in range(6):
+    for _ in range(updates):
         log = tr.train_step([batch])
         if log is not None:  # an overflow step of the dynamic loss scaler returns nothing
             losses.append(float(log["loss"]))
+    return losses
+
+
+@pytest.mark.parametrize("name", sorted(VARIANTS))
+def test_training_option_runs_and_learns(name, tmp_path):
+    losses = _run(tmp_path, VARIANTS[name])
     assert len(losses) >= 4 and all(math.isfinite(v) for v in losses), losses
     assert losses[-1] < losses[0], (name, losses)
+
+
+def test_cpu_offload_keeps_shards_on_the_host_and_trains_like_the_plain_run(tmp_path):
+    """``--cpu-offload`` on a CPU-only host moves nothing, so the run must equal the one without the flag; the unit
+    still goes through the offload path (separate gathered copy, gradient copied back to the shard's device)."""
+    base = _run(tmp_path / "a", POLY + ["--ddp-backend", "fully_sharded"])
+    off = _run(tmp_path / "b", POLY + ["--ddp-backend", "fully_sharded", "--cpu-offload"])
+    assert off == pytest.approx(base, abs=1e-4)
