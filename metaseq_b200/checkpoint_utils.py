@@ -62,7 +62,74 @@ def wait_for_pending_writes():
         f.result()
 
 
-def _write_now(state, filename, async_callback_fn, files_to_symlink_to):
+class HostSnapshot:
+    """Device-to-host copy of a checkpoint state that does not stall the training step.
+
+    ``take(state)`` replaces every CUDA tensor of a nested state by a pinned host tensor filled by an asynchronous
+    copy on a side stream (ordered after everything queued on the current stream so far) and returns the new state
+    with an event; the host tensors are valid once ``ready()`` has returned, which the writer thread calls before
+    it serialises.  The caller must keep the device tensors unchanged until the copies have run: the trainer makes
+    the compute stream wait for ``event`` right before its next optimizer step, so forward and backward of that
+    step overlap with the copies.  Pinned buffers are kept and reused by the next snapshot of the same layout
+    (after the previous write has finished).  Host tensors in the state are cloned; on a machine without CUDA the
+    snapshot is an ordinary copy.  The reference copies synchronously inside ``state_dict`` and serialises on the
+    training thread (metaseq/trainer.py:410-448)."""
+
+    def __init__(self):
+        self._pool: Dict[tuple, List[torch.Tensor]] = {}
+        self._stream = None
+        self.event = None
+
+    def _buffer(self, like: torch.Tensor, dtype, taken: Dict[tuple, int]) -> torch.Tensor:
+        key = (tuple(like.shape), dtype)
+        idx = taken.get(key, 0)
+        taken[key] = idx + 1
+        bucket = self._pool.setdefault(key, [])
+        if idx >= len(bucket):
+            bucket.append(torch.empty(like.shape, dtype=dtype, pin_memory=True))
+        return bucket[idx]
+
+    def take(self, state, cast_to_fp32: bool = False):
+        from metaseq_b200 import utils
+
+        if not torch.cuda.is_available():
+            self.event = None
+
+            def clone(t):  # a private copy: the writer thread must not see later in-place updates
+                widen = cast_to_fp32 and t.dtype in (torch.float16, torch.bfloat16)
+                return t.detach().to(torch.float32) if widen else t.detach().clone()
+
+            return utils.apply_to_sample(clone, state)
+        wait_for_pending_writes()  # the previous snapshot's buffers are about to be reused
+        if self._stream is None:
+            self._stream = torch.cuda.Stream()
+        self._stream.wait_stream(torch.cuda.current_stream())
+        taken: Dict[tuple, int] = {}
+
+        def copy(t):
+            dtype = torch.float32 if (cast_to_fp32 and t.dtype in (torch.float16, torch.bfloat16)) else t.dtype
+            if not t.is_cuda:
+                return t.detach().to(dtype).clone()
+            host = self._buffer(t, dtype, taken)
+            src = t.detach()
+            with torch.cuda.stream(self._stream):
+                host.copy_(src if src.dtype == dtype else src.to(dtype), non_blocking=True)
+            src.record_stream(self._stream)
+            return host
+
+        out = utils.apply_to_sample(copy, state)
+        self.event = torch.cuda.Event()
+        self.event.record(self._stream)
+        return out
+
+    def ready(self):
+        if self.event is not None:
+            self.event.synchronize()
+
+
+def _write_now(state, filename, async_callback_fn, files_to_symlink_to, ready: Optional[Callable[[], None]] = None):
+    if ready is not None:
+        ready()  # the host copy of the state is complete
     tmp = filename + ".tmp"
     with PathManager.open(tmp, "wb") as f:
         torch.save(state, f)
@@ -83,14 +150,15 @@ def _symlink_or_copy(src, dst):
         shutil.copyfile(src, dst)
 
 
-def write_checkpoint(state, filename, asynchronous=True, async_callback_fn=None, files_to_symlink_to=None):
-    """``state`` must already live in host memory."""
+def write_checkpoint(state, filename, asynchronous=True, async_callback_fn=None, files_to_symlink_to=None,
+                     ready: Optional[Callable[[], None]] = None):
+    """``state`` lives in host memory, or will once ``ready()`` has returned (``HostSnapshot``)."""
     os.makedirs(os.path.dirname(os.path.abspath(filename)), exist_ok=True)
     if asynchronous:
-        fut = _writer().submit(_write_now, state, filename, async_callback_fn, files_to_symlink_to)
+        fut = _writer().submit(_write_now, state, filename, async_callback_fn, files_to_symlink_to, ready)
         _PENDING.append(fut)
         return fut
-    _write_now(state, filename, async_callback_fn, files_to_symlink_to)
+    _write_now(state, filename, async_callback_fn, files_to_symlink_to, ready)
     return None
 
 

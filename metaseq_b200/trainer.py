@@ -279,17 +279,35 @@ class Trainer:
         ``--save-async`` is on."""
         if mpu.get_tensor_model_parallel_world_size() > 1:
             extra_state["rng_tracker_states"] = mpu.get_cuda_rng_tracker().get_states()
-        state = self.state_dict(filename, training_finished)
+        with self._state_on_device():
+            state = self.state_dict(filename, training_finished)
         state["extra_state"].update(extra_state)
-        state = utils.move_to_cpu(state, cast_to_fp32=not (self.cfg.common.fp16 or self.cfg.common.bf16
-                                                          or self.cfg.common.memory_efficient_fp16))
         if not self.should_save_checkpoint_on_current_rank:
             return
+        # copies to pinned host memory run on a side stream; the writer thread waits for them, this step does not
+        if getattr(self, "_snapshot", None) is None:
+            self._snapshot = checkpoint_utils.HostSnapshot()
+        state = self._snapshot.take(state, cast_to_fp32=not (self.cfg.common.fp16 or self.cfg.common.bf16
+                                                             or self.cfg.common.memory_efficient_fp16))
+        self._snapshot_event = self._snapshot.event  # the next optimizer step must not overtake the copies
         logger.info(f"Saving checkpoint to {filename}")
         checkpoint_utils.write_checkpoint(
             state, filename, asynchronous=bool(self.cfg.checkpoint.write_checkpoints_asynchronously),
-            async_callback_fn=async_callback_fn, files_to_symlink_to=files_to_symlink_to)
+            async_callback_fn=async_callback_fn, files_to_symlink_to=files_to_symlink_to, ready=self._snapshot.ready)
         logger.info(f"Finished saving checkpoint to {filename}")
+
+    @contextlib.contextmanager
+    def _state_on_device(self):
+        """While active, sharded units hand out their flat shards as device tensors (no synchronous copy)."""
+        units = [m for m in self.model.modules() if isinstance(m, FullyShardedDataParallel)]
+        saved = [u.state_dict_device for u in units]
+        for u in units:
+            u.state_dict_device = None
+        try:
+            yield
+        finally:
+            for u, dev in zip(units, saved):
+                u.state_dict_device = dev
 
     def load_checkpoint(self, filename, reset_optimizer=False, reset_lr_scheduler=False, optimizer_overrides=None,
                         reset_meters=False):
@@ -523,6 +541,10 @@ class Trainer:
                 new_lr = self.optimizer.get_lr() / (ratio ** 4)
                 self.optimizer.set_lr(new_lr)
                 logger.info(f"Scaling LR by {1.0 / ratio ** 4:.2f} to {new_lr:.6f}")
+            if getattr(self, "_snapshot_event", None) is not None:
+                # a checkpoint snapshot may still be reading parameters and optimizer state on its side stream
+                torch.cuda.current_stream().wait_event(self._snapshot_event)
+                self._snapshot_event = None
             self.task.optimizer_step(self.optimizer, model=self.model, update_num=self.get_num_updates())
             if self.is_fsdp:
                 self.model.after_optimizer_step()

@@ -224,3 +224,20 @@ def test_loss_spike_guard_keeps_spikes_out_of_the_running_mean():
     Trainer.skip_spike(off, 10.0, -1)
     Trainer.skip_spike(off, 30.0, -1)
     assert off._ewm_loss == pytest.approx(14.0) and off._skipped_loss_spikes == 0
+
+
+def test_host_snapshot_is_a_private_copy_and_the_writer_waits_for_it(tmp_path):
+    from metaseq_b200 import checkpoint_utils
+
+    snap = checkpoint_utils.HostSnapshot()
+    live = {"model": {"w": torch.arange(6.0), "half": torch.ones(3, dtype=torch.float16)}, "n": 3, "name": "x"}
+    state = snap.take(live, cast_to_fp32=True)
+    live["model"]["w"].add_(100)  # training goes on while the writer serialises
+    assert state["model"]["w"].tolist() == [0.0, 1.0, 2.0, 3.0, 4.0, 5.0] and state["n"] == 3 and state["name"] == "x"
+    assert state["model"]["half"].dtype == torch.float32
+    called = []
+    path = str(tmp_path / "ckpt.pt")
+    checkpoint_utils.write_checkpoint(state, path, asynchronous=True, ready=lambda: called.append(1))
+    checkpoint_utils.wait_for_pending_writes()
+    assert called == [1]
+    assert torch.load(path, weights_only=False)["model"]["w"].tolist() == [0.0, 1.0, 2.0, 3.0, 4.0, 5.0]

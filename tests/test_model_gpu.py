@@ -373,3 +373,26 @@ def test_cpu_offload_keeps_shards_and_optimizer_state_in_host_memory():
     assert len(losses) == len(ref) and losses[-1] < losses[0]
     for a, b in zip(losses, ref):
         assert a == pytest.approx(b, abs=5e-2)
+
+
+def test_checkpoint_snapshot_copies_on_a_side_stream_and_keeps_the_values_of_its_moment(tmp_path):
+    """The snapshot returns at once; training steps taken while the writer works do not leak into the file, and the
+    loss after reloading equals the loss of the uninterrupted run at the same update."""
+    from metaseq_b200 import checkpoint_utils
+
+    tr, batch = _trainer(_cfg(["--save-dir", str(tmp_path), "--write-checkpoints-asynchronously"]))
+    for _ in range(3):
+        tr.train_step([batch])
+    before = {k: v.detach().clone() for k, v in tr.get_model().state_dict().items() if torch.is_tensor(v)}
+    path = str(tmp_path / "checkpoint_3-shard0.pt")
+    tr.save_checkpoint(path, {"train_iterator": {"epoch": 1}})
+    after_save = [float(tr.train_step([batch])["loss"]) for _ in range(2)]
+    checkpoint_utils.wait_for_pending_writes()
+    saved = torch.load(path, map_location="cpu", weights_only=False)
+    for k, v in before.items():
+        assert torch.equal(saved["model"][k].cpu(), v.cpu()), k
+    assert saved["optimizer_history"][-1]["num_updates"] == 3
+    tr2, _ = _trainer(_cfg(["--save-dir", str(tmp_path)]))
+    tr2.load_checkpoint(path)
+    resumed = [float(tr2.train_step([batch])["loss"]) for _ in range(2)]
+    assert resumed == pytest.approx(after_save, abs=2e-2)
