@@ -43,7 +43,9 @@ def main(argv=None):
     ap.add_argument("--unit-mb", type=float, default=100.7, help="gathered size of one FSDP unit in MB (OPT-1.3B layer)")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--out", default=None)
-    ap.add_argument("--transport", default="ce", choices=["ce", "sm"])
+    ap.add_argument("--transport", default="all", choices=["all", "ce", "sm", "mm"],
+                    help="bulk transport of the all-gather / reduce-scatter: peer DMA (ce), store kernels (sm), "
+                         "through NVSwitch with multimem (mm), or each of them in turn (all)")
     ap.add_argument("--decode-dim", type=int, default=4096, help="model width for the decode GEMM + all-reduce timing")
     ap.add_argument("--decode-rows", type=int, default=32)
     args = ap.parse_args(argv)
@@ -56,12 +58,11 @@ def main(argv=None):
     from metaseq_b200.parallel.symm import PeerComm
 
     numel = int(args.unit_mb * 1e6 / 2) // (8 * world) * (8 * world)
-    comm = PeerComm(dist.group.WORLD, dev, heap_bytes=4 * numel * 2 + (64 << 20), transport=args.transport)
-    full = comm.alloc_full(numel, torch.float16)
     shard_in = torch.randn(numel // world, device=dev, dtype=torch.float16)
-    grad = torch.randn(numel, device=dev, dtype=torch.float16)
+    grad_src = torch.randn(numel, device=dev, dtype=torch.float16)
     shard_out = torch.empty(numel // world, device=dev, dtype=torch.float16)
     ref_full = torch.empty(numel, device=dev, dtype=torch.float16)
+    ref_shard = torch.empty(numel // world, device=dev, dtype=torch.float16)
     results = []
 
     def rec(op, ms, nccl_ms, bus_bytes):
@@ -72,12 +73,38 @@ def main(argv=None):
             print(json.dumps(r), flush=True)
 
     moved = numel * 2 * (world - 1) / world  # bytes each GPU sends (and receives)
-    rec("fsdp_unit_all_gather",
-        _time(lambda: comm.all_gather(full, shard_in), args.iters),
-        _time(lambda: dist.all_gather_into_tensor(ref_full, shard_in), args.iters), moved)
-    rec("fsdp_unit_reduce_scatter_fp32sum_unscale_norm",
-        _time(lambda: comm.reduce_scatter(shard_out, grad, key=full, scale=1.0 / world, accumulate_norm=True), args.iters),
-        _time(lambda: dist.reduce_scatter_tensor(shard_out, grad), args.iters), moved)
+    nccl_ag = _time(lambda: dist.all_gather_into_tensor(ref_full, shard_in), args.iters)
+    nccl_rs = _time(lambda: dist.reduce_scatter_tensor(ref_shard, grad_src), args.iters)
+    ref_shard.div_(world)
+    comm = None
+    for transport in (["ce", "sm", "mm"] if args.transport == "all" else [args.transport]):
+        comm = PeerComm(dist.group.WORLD, dev, heap_bytes=4 * numel * 2 + (64 << 20), transport=transport)
+        if transport == "mm" and not comm.heap.multicast_ptr:
+            if rank == 0:
+                print(json.dumps(dict(op="transport_mm", skipped="no multicast mapping")), flush=True)
+            continue
+        full = comm.alloc_full(numel, torch.float16)
+        grad = comm.alloc_symmetric(numel, torch.float16) if comm.pulls_gradients else torch.empty_like(grad_src)
+        grad.copy_(grad_src)
+        torch.cuda.synchronize()
+        dist.barrier()
+        ag = _time(lambda: comm.all_gather(full, shard_in), args.iters)
+        ag_err = float((full.float() - ref_full.float()).abs().max())
+        rec(f"fsdp_unit_all_gather[{comm.ag_transport}]", ag, nccl_ag, moved)
+        results[-1]["max_abs_diff_vs_nccl"] = ag_err
+
+        def rs():
+            comm.reduce_scatter(shard_out, grad, key=full, scale=1.0 / world, accumulate_norm=True)
+            if comm.pulls_gradients:
+                comm.barrier()  # as FSDP does once per backward: sources may be overwritten afterwards
+
+        t_rs = _time(rs, args.iters)
+        rs_err = float((shard_out.float() - ref_shard.float()).abs().max())
+        rec(f"fsdp_unit_reduce_scatter_fp32sum_unscale_norm[{comm.rs_transport}]", t_rs, nccl_rs, moved)
+        results[-1]["max_abs_diff_vs_nccl"] = rs_err
+        if rank == 0:
+            print(json.dumps(dict(check=transport, all_gather_max_abs_diff=ag_err, reduce_scatter_max_abs_diff=rs_err)),
+                  flush=True)
     for nbytes in (16 << 10, 256 << 10, 1 << 20):
         x = torch.randn(nbytes // 2, device=dev, dtype=torch.float16)
         y = x.clone()

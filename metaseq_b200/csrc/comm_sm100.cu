@@ -216,6 +216,132 @@ comm_reduce_slots_kernel(const uint4* __restrict__ slots, long long shard_numel,
   if (bad && overflow) *overflow = 1;
 }
 
+// Owner-side ("pull") reduce-scatter, fused with the unscale / norm / overflow epilogue.  Every rank's full-size
+// gradient buffer lives at the same offset of its symmetric region.  A rank publishes flag `flag_base + rank` on
+// every peer when its buffer is complete (msq_comm_signal); the owner of a shard waits for all `world` flags and
+// then reads its slice of all ranks at once:
+//   MC   : one multimem.ld_reduce per 16 bytes on the multicast address: the additions happen inside NVSwitch
+//          (fp32 accumulation for 16-bit inputs) and only the sum crosses the owner's link (ingress 1 x shard);
+//   !MC  : plain 16-byte loads from each peer's mapping, summed in fp32 registers (ingress (world - 1) x shard).
+// No landing slots and no second pass: the value is scaled, squared into the norm accumulator, checked for
+// non-finite values and written as the 16-bit or fp32 shard straight from registers.
+template <bool BF16, bool OUT32, bool MC>
+__global__ void __launch_bounds__(256)
+comm_reduce_scatter_pull_kernel(const void* mc_shard, PeerPtrs src, long long src_off_bytes, long long shard_numel,
+                                int rank, int world, float scale, void* __restrict__ out, float* sumsq_acc,
+                                int* overflow, const uint32_t* flags, long long flag_base, uint32_t epoch, int* status) {
+  __shared__ bool ok_s;
+  if (threadIdx.x == 0) ok_s = !(status && *reinterpret_cast<volatile int*>(status) != 0);
+  __syncthreads();
+  if (threadIdx.x < world && ok_s) {
+    if (!wait_flag(flags + flag_base + threadIdx.x, epoch, status)) ok_s = false;
+  }
+  __syncthreads();
+  if (!ok_s) return;
+  const long long nvec = shard_numel >> 3;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  float ss = 0.f;
+  bool bad = false;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    float acc[8];
+    if (MC) {
+      const uint8_t* a = static_cast<const uint8_t*>(mc_shard) + (i << 4);
+      uint32_t w[4];
+      if (BF16)
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "l"(a) : "memory");
+      else
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "l"(a) : "memory");
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack2<BF16>(w[j]);
+        acc[2 * j] = f.x;
+        acc[2 * j + 1] = f.y;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      for (int s = 0; s < world; ++s) {
+        const int peer = (rank + s) % world;  // own slice first, then round the ring
+        const uint4* base = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(src.p[peer]) + src_off_bytes);
+        uint4 v;
+        asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(base + i) : "memory");
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack2<BF16>(w[j]);
+          acc[2 * j] += f.x;
+          acc[2 * j + 1] += f.y;
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      acc[j] *= scale;
+      ss += acc[j] * acc[j];
+      bad |= !isfinite(acc[j]);
+    }
+    if (OUT32) {
+      float4* o = reinterpret_cast<float4*>(out) + 2 * i;
+      o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    } else {
+      uint4 o;
+      o.x = pack2<BF16>(acc[0], acc[1]);
+      o.y = pack2<BF16>(acc[2], acc[3]);
+      o.z = pack2<BF16>(acc[4], acc[5]);
+      o.w = pack2<BF16>(acc[6], acc[7]);
+      reinterpret_cast<uint4*>(out)[i] = o;
+    }
+  }
+  __shared__ float red[32];
+  ss = block_sum(ss, red);
+  if (threadIdx.x == 0 && sumsq_acc) atomicAdd(sumsq_acc, ss);
+  if (bad && overflow) *overflow = 1;
+}
+
+// All-gather through the switch: a CTA reads one chunk of the local shard and writes it with multimem.st to the
+// multicast address of the gathered buffer, which NVSwitch delivers to every rank (this one included): the shard
+// leaves the GPU once instead of once per peer.  The per-chunk arrival flags are then published on every rank as
+// in comm_allgather_push_kernel, so the GEMM that consumes the gathered weights polls them the same way.
+__global__ void __launch_bounds__(512)
+comm_allgather_multimem_kernel(void* mc_dst, const uint4* __restrict__ src, long long shard_bytes, int chunk_bytes,
+                               int rank, int world, PeerPtrs sig, long long flag_base, uint32_t epoch, int* status) {
+  if (status && *reinterpret_cast<volatile int*>(status) != 0) return;
+  const long long chunks = (shard_bytes + chunk_bytes - 1) / chunk_bytes;
+  for (long long c = blockIdx.x; c < chunks; c += gridDim.x) {
+    const long long b0 = c * chunk_bytes;
+    const long long nb = (shard_bytes - b0 < chunk_bytes) ? (shard_bytes - b0) : chunk_bytes;
+    const int nvec = static_cast<int>(nb >> 4);
+    const uint4* s = src + (b0 >> 4);
+    uint8_t* d = static_cast<uint8_t*>(mc_dst) + static_cast<long long>(rank) * shard_bytes + b0;
+    for (int i0 = threadIdx.x; i0 < nvec; i0 += 4 * blockDim.x) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * blockDim.x;
+        if (i < nvec) v[u] = s[i];
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * blockDim.x;
+        if (i < nvec)
+          asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                       ::"l"(d + (static_cast<long long>(i) << 4)), "r"(v[u].x), "r"(v[u].y), "r"(v[u].z), "r"(v[u].w)
+                       : "memory");
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x < world) {
+      __threadfence_system();
+      st_release_sys(static_cast<uint32_t*>(sig.p[threadIdx.x]) + flag_base + rank * chunks + c, epoch);
+    }
+    __syncthreads();
+  }
+}
+
 // Row-block reduction behind a scattering GEMM: this rank owns `rows` rows of an [*, N] matrix; slot s holds
 // the partial product computed by rank s.  out_row = sum_s slot_s + bias + residual, written to `out_local`
 // (reduce-scatter) and, when bcast.p[0] is set, also stored into every rank's copy of the full matrix at
@@ -514,6 +640,74 @@ comm_allreduce_multimem_kernel(void* mc, long long bytes, int rank, int world, P
   }
 }
 
+// ------------------------------------------- small exchange that a CUDA graph can replay
+// Every rank contributes `words` 32-bit words (two 16-bit values each in the summing modes); every rank ends up with
+// the sum over ranks (MODE 0: fp16 pairs, 1: bf16 pairs, fp32 accumulation) or with all ranks' words side by side
+// (MODE 2: out[src * words + i]).  A word travels as the 8-byte unit {word, epoch}: a thread stores its unit into
+// the receive buffer of every rank at [rank * cap + i] and then polls its own buffer until the unit of every source
+// at index i carries the epoch, so there is no flag, fence or remote load, and the reader of a word is the same
+// thread index on every rank.  The epoch is a counter in device memory that the kernel itself advances (the last CTA
+// to finish stores the new value), which is what allows a captured launch to be replayed; receive buffers
+// alternate with its parity so that a rank that is one call ahead does not overwrite units still being read.
+template <int MODE>
+__global__ void __launch_bounds__(256)
+comm_words_exchange_kernel(const uint32_t* __restrict__ in, long long words, PeerPtrs recv0, PeerPtrs recv1,
+                           long long cap, int rank, int world, uint32_t* epoch_dev, unsigned* ticket,
+                           uint32_t* __restrict__ out, int* status) {
+  if (status && *reinterpret_cast<volatile int*>(status) != 0) return;
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(epoch_dev) + 1u;
+  const PeerPtrs& recv = (epoch & 1u) ? recv1 : recv0;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  bool ok = true;
+  const long long first = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  // all of this thread's units leave before it starts to wait for anybody else's
+  for (long long i = first; i < words; i += stride) {
+    const unsigned long long unit = (static_cast<unsigned long long>(epoch) << 32) | in[i];
+    for (int w = 0; w < world; ++w) {
+      unsigned long long* dst = static_cast<unsigned long long*>(recv.p[(rank + w) % world]) + rank * cap + i;
+      asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst), "l"(unit) : "memory");
+    }
+  }
+  for (long long i = first; i < words && ok; i += stride) {
+    float sx = 0.f, sy = 0.f;
+    const unsigned long long* mine = static_cast<const unsigned long long*>(recv.p[rank]) + i;
+    for (int s = 0; s < world && ok; ++s) {
+      const unsigned long long* src = mine + s * cap;
+      unsigned long long got;
+      const unsigned long long t0 = globaltimer_ns();
+      uint32_t spins = 0;
+      while (true) {
+        asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(got) : "l"(src) : "memory");
+        if (static_cast<uint32_t>(got >> 32) == epoch) break;
+        if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > WAIT_NS_PEER) {
+          if (status) atomicCAS(status, 0, ST_TIMEOUT_PEER_FLAG);
+          ok = false;
+          break;
+        }
+      }
+      if (!ok) break;
+      const uint32_t word = static_cast<uint32_t>(got);
+      if (MODE == 2) {
+        out[s * words + i] = word;
+      } else {
+        const float2 f = unpack2<MODE == 1>(word);
+        sx += f.x;
+        sy += f.y;
+      }
+    }
+    if (MODE != 2 && ok) out[i] = pack2<MODE == 1>(sx, sy);
+  }
+  // advance the epoch once every CTA of this launch has read it (all of them are done when the last one is)
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(ticket, 1u) == gridDim.x - 1) {
+      *epoch_dev = epoch;
+      *ticket = 0;
+    }
+  }
+}
+
 }  // namespace msq
 
 using msq::PeerPtrs;
@@ -677,6 +871,57 @@ extern "C" int msq_comm_reduce_scatter_push(void* const* slot_ptrs, long long sl
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
+// Owner-side reduce-scatter (see comm_reduce_scatter_pull_kernel).  `mc_base` (or null): multicast address of the
+// symmetric regions; `src_ptrs`: the regions as mapped here; `buf_off_bytes`: offset of the full-size gradient
+// buffer inside them.  This rank reduces elements [rank * shard_numel, (rank + 1) * shard_numel) of that buffer
+// over all ranks into `out`.  Sources announce their buffers with msq_comm_signal(flag_base, epoch) beforehand.
+extern "C" int msq_comm_reduce_scatter_pull(void* mc_base, void* const* src_ptrs, long long buf_off_bytes,
+                                            long long shard_numel, int rank, int world, float scale, void* out,
+                                            int out_fp32, int bf16, float* sumsq_acc, int* overflow, const void* flags,
+                                            long long flag_base, unsigned epoch, int max_ctas, int* status,
+                                            cudaStream_t stream) {
+  if (world > msq::MAX_PEERS) return -2;
+  if ((shard_numel & 7) || (buf_off_bytes & 15) || (reinterpret_cast<uintptr_t>(out) & 15)) return -2;
+  if (shard_numel <= 0) return 0;
+  long long want = ((shard_numel >> 3) + 255) / 256;
+  int grid = static_cast<int>(want < max_ctas ? want : max_ctas);
+  if (grid < 1) grid = 1;
+  const long long shard_off = buf_off_bytes + static_cast<long long>(rank) * shard_numel * 2;
+  const void* mc_shard = mc_base ? static_cast<const uint8_t*>(mc_base) + shard_off : nullptr;
+  const uint32_t* f = static_cast<const uint32_t*>(flags);
+  PeerPtrs sp = make_ptrs(src_ptrs, world);
+#define MSQ_PULL(BF, O32, MC) \
+  msq::comm_reduce_scatter_pull_kernel<BF, O32, MC><<<grid, 256, 0, stream>>>(mc_shard, sp, shard_off, shard_numel, rank, world, scale, out, sumsq_acc, overflow, f, flag_base, epoch, status)
+  if (mc_base) {
+    if (bf16) { if (out_fp32) MSQ_PULL(true, true, true); else MSQ_PULL(true, false, true); }
+    else { if (out_fp32) MSQ_PULL(false, true, true); else MSQ_PULL(false, false, true); }
+  } else {
+    if (bf16) { if (out_fp32) MSQ_PULL(true, true, false); else MSQ_PULL(true, false, false); }
+    else { if (out_fp32) MSQ_PULL(false, true, false); else MSQ_PULL(false, false, false); }
+  }
+#undef MSQ_PULL
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// All-gather by multimem.st (see comm_allgather_multimem_kernel).  `mc_dst`: multicast address of the gathered
+// buffer; flags as for msq_comm_allgather_push.
+extern "C" int msq_comm_allgather_multimem(void* mc_dst, const void* src, long long shard_bytes, int chunk_bytes, int rank,
+                                           int world, void* const* sig_ptrs, long long flag_base, unsigned epoch,
+                                           int max_ctas, int* status, cudaStream_t stream) {
+  if (world > msq::MAX_PEERS || !mc_dst) return -2;
+  if ((shard_bytes & 15) || (chunk_bytes & 15) || (reinterpret_cast<uintptr_t>(mc_dst) & 15) ||
+      (reinterpret_cast<uintptr_t>(src) & 15))
+    return -2;
+  if (shard_bytes <= 0) return 0;
+  long long chunks = (shard_bytes + chunk_bytes - 1) / chunk_bytes;
+  int grid = static_cast<int>(chunks < max_ctas ? chunks : max_ctas);
+  if (grid < 1) grid = 1;
+  msq::comm_allgather_multimem_kernel<<<grid, 512, 0, stream>>>(mc_dst, static_cast<const uint4*>(src), shard_bytes,
+                                                               chunk_bytes, rank, world, make_ptrs(sig_ptrs, world),
+                                                               flag_base, epoch, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
 extern "C" int msq_comm_reduce_slots(const void* slots, long long shard_numel, int world, float scale, void* out,
                                      int out_fp32, int bf16, float* sumsq_acc, int* overflow, const void* flags,
                                      long long flag_base, unsigned epoch, int max_ctas, int* status, cudaStream_t stream) {
@@ -766,5 +1011,26 @@ extern "C" int msq_comm_allreduce_multimem(void* mc, long long bytes, int dtype,
   if (dtype == 0) msq::comm_allreduce_multimem_kernel<0><<<grid, 512, 0, stream>>>(mc, bytes, rank, world, sg, flag_base, epoch, status);
   else if (dtype == 1) msq::comm_allreduce_multimem_kernel<1><<<grid, 512, 0, stream>>>(mc, bytes, rank, world, sg, flag_base, epoch, status);
   else msq::comm_allreduce_multimem_kernel<2><<<grid, 512, 0, stream>>>(mc, bytes, rank, world, sg, flag_base, epoch, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// Small sum / gather over ranks that may be captured in a CUDA graph (see comm_words_exchange_kernel).  `in`: `words`
+// 32-bit words; recv0 / recv1: the two receive buffers of every rank (world * cap units of 8 bytes each, zero-filled
+// at creation); `epoch_dev` and `ticket`: one zero-initialised word each, owned by this exchange.  mode 0 / 1: `out`
+// gets the sum of fp16 / bf16 pairs (`words` words); mode 2: `out` gets world * words words, source-major.  Every
+// rank must issue the same sequence of calls (same `words`) on buffers used by nothing else.
+extern "C" int msq_comm_words_exchange(const void* in, long long words, void* const* recv0, void* const* recv1,
+                                       long long cap, int rank, int world, unsigned* epoch_dev, unsigned* ticket,
+                                       void* out, int mode, int* status, cudaStream_t stream) {
+  if (world > msq::MAX_PEERS || words > cap || mode < 0 || mode > 2) return -2;
+  if (words <= 0) return 0;
+  long long want = (words + 255) / 256;
+  const int grid = static_cast<int>(want < 64 ? want : 64);
+  const uint32_t* i32 = static_cast<const uint32_t*>(in);
+  uint32_t* o32 = static_cast<uint32_t*>(out);
+  PeerPtrs r0 = make_ptrs(recv0, world), r1 = make_ptrs(recv1, world);
+  if (mode == 0) msq::comm_words_exchange_kernel<0><<<grid, 256, 0, stream>>>(i32, words, r0, r1, cap, rank, world, epoch_dev, ticket, o32, status);
+  else if (mode == 1) msq::comm_words_exchange_kernel<1><<<grid, 256, 0, stream>>>(i32, words, r0, r1, cap, rank, world, epoch_dev, ticket, o32, status);
+  else msq::comm_words_exchange_kernel<2><<<grid, 256, 0, stream>>>(i32, words, r0, r1, cap, rank, world, epoch_dev, ticket, o32, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

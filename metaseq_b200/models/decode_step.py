@@ -179,8 +179,15 @@ class GraphedDecodeStep:
             # one grid for every row-parallel product of the step (they share flags and epoch counters)
             self._split = min(lib.msq_gemm_skinny_split(D, first.self_attn.out_proj.weight.shape[1]),
                               lib.msq_gemm_skinny_split(D, first.fc2.weight.shape[1]))
-            self.x_in = torch.zeros(rows, D, dtype=self.dtype, device=self.device)
-            self.x_out: Optional[torch.Tensor] = None
+            # the embedding sum and the next-token records travel through one small exchange kernel inside the graph
+            from metaseq_b200.parallel.symm import WordsExchange
+
+            self.exchange = decoder.__dict__.get("_decode_exchange")
+            if self.exchange is None or self.exchange.cap < 64 * D // 2:
+                self.exchange = WordsExchange(mpu.get_tensor_model_parallel_group(), self.device, 64 * D // 2)
+                decoder.__dict__["_decode_exchange"] = self.exchange
+            self.vocab_start = int(decoder.embed_tokens.vocab_start_index)
+            self.local_logits: Optional[torch.Tensor] = None
 
     # ------------------------------------------------------------------ state
     def new_state(self) -> Dict:
@@ -225,11 +232,10 @@ class GraphedDecodeStep:
         w = dec.embed_tokens.weight
         if self.tp == 1:
             return F.embed_fwd(tok, positions, w, pos_w, dec.embed_scale)
-        import torch.distributed as dist
-
+        # each token's row lives on one rank (zeros elsewhere): the sum over ranks is the embedding
         start = dec.embed_tokens.vocab_start_index
         x = F.embed_fwd(tok, None, w, None, dec.embed_scale, start, start + w.shape[0], add_positions=False)
-        dist.all_reduce(x, group=mpu.get_tensor_model_parallel_group())
+        x = self.exchange.sum(x)
         if pos_w is not None:
             x = x + torch.nn.functional.embedding(positions, pos_w)
         return x
@@ -260,19 +266,15 @@ class GraphedDecodeStep:
         return x
 
     def _logits(self, x: torch.Tensor) -> torch.Tensor:
-        local = F.gemm(x, self.decoder.output_projection.weight)
-        if self.tp == 1:
-            return local
-        from metaseq_b200.parallel import mappings
-
-        return mappings.gather_from_tensor_model_parallel_region(local)
+        """This rank's columns of the logits (all of them without tensor parallelism)."""
+        return F.gemm(x, self.decoder.output_projection.weight)
 
     def _run(self) -> torch.Tensor:
-        """What the graph holds: the whole step on one rank, the layers under tensor parallelism."""
+        """What the graph holds: the whole step, embedding to (this rank's slice of the) logits.  Under tensor
+        parallelism the sums over ranks inside it are the fused GEMM + all-reduce of the row-parallel products and
+        the small exchange kernel of the embedding; no library collective is part of a step."""
         with F.dependent_launch():  # every GEMM operand ``b`` in the chain is a model weight
-            if self.tp == 1:
-                return self._logits(self._layers(self._embed()))
-            return self._layers(self.x_in)
+            return self._logits(self._layers(self._embed()))
 
     def _capture(self) -> None:
         # Warm up on a side stream (lazy initialisation of libraries must not happen under capture), then
@@ -293,14 +295,16 @@ class GraphedDecodeStep:
         if self.tp == 1:
             self.logits = out
         else:
-            self.x_out = out
+            self.local_logits = out
             assert self.reduce.calls % 2 == 0  # replays keep the alternation of the staging buffers
         # the capture itself executes nothing, so the state is still the restored one
         self.graph = graph
 
     @torch.no_grad()
-    def step(self, new_tokens: torch.Tensor) -> torch.Tensor:
-        """Feeds one token per row; returns the ``[rows, V]`` logits (a buffer reused by the next step)."""
+    def step(self, new_tokens: torch.Tensor, gather: bool = True) -> torch.Tensor:
+        """Feeds one token per row; returns the ``[rows, V]`` logits (a buffer reused by the next step).  Under
+        tensor parallelism ``gather=False`` returns this rank's ``[rows, V / p]`` columns instead (global column =
+        ``vocab_start`` + local column), for callers that pick the token from the shards (``pick_greedy``)."""
         filled = self.caches[0].length
         if filled + 1 > self.capacity:
             raise RuntimeError(f"decode step beyond the cache capacity of {self.capacity} positions")
@@ -309,8 +313,6 @@ class GraphedDecodeStep:
         else:
             self.tok.fill_(self.pad)
             self.tok[: self.live] = new_tokens
-        if self.tp > 1:
-            self.x_in.copy_(self._embed())
         if self.graph is None:
             self._capture()
         self.graph.replay()
@@ -318,5 +320,46 @@ class GraphedDecodeStep:
             cache.length = filled + 1
         for view in self.views:
             view.length = filled + 1
-        logits = self.logits if self.tp == 1 else self._logits(self.x_out)
+        if self.tp == 1:
+            logits = self.logits
+        elif gather:
+            from metaseq_b200.parallel import mappings
+
+            logits = mappings.gather_from_tensor_model_parallel_region(self.local_logits)
+        else:
+            logits = self.local_logits
         return logits if self.live == self.rows else logits[: self.live]
+
+    @torch.no_grad()
+    def pick_greedy(self, local_logits: torch.Tensor, banned=(), only: Optional[int] = None):
+        """Arg-max token and its log-probability per row from vocabulary-parallel logits, without gathering them.
+        Every rank reduces its own columns to (max, sum-exp, best allowed value, its global index), the records of
+        all ranks are exchanged by one small kernel, and every rank merges them the same way.  ``banned``: global
+        token ids that must not be chosen; ``only``: the one token that may be.  Ties go to the lowest index, as
+        ``torch.max`` does on gathered logits."""
+        lo, width = self.vocab_start, local_logits.shape[1]
+        lf = local_logits.float()
+        lf = torch.where(torch.isnan(lf), torch.full_like(lf, float("-inf")), lf)
+        m = lf.max(dim=-1).values
+        s = torch.exp(lf - m[:, None]).sum(dim=-1)
+        cand = lf.clone()
+        if only is not None:
+            keep = cand[:, only - lo].clone() if lo <= only < lo + width else None
+            cand.fill_(float("-inf"))
+            if keep is not None:
+                cand[:, only - lo] = keep
+        for t in banned:
+            if lo <= t < lo + width:
+                cand[:, t - lo] = float("-inf")
+        bv, bi = cand.max(dim=-1)
+        rec = torch.stack([m, s, bv, (bi + lo).float()], dim=-1).contiguous()  # indices < 2^24 are exact in fp32
+        if rec.shape[0] != self.rows:  # the exchange has one shape per step object: pad to the graph's rows
+            pad = torch.zeros(self.rows - rec.shape[0], 4, dtype=rec.dtype, device=rec.device)
+            rec = torch.cat([rec, pad], dim=0)
+        every = self.exchange.gather(rec)[:, : local_logits.shape[0]]  # [world, rows, 4]
+        gm = every[..., 0].max(dim=0).values
+        lse = gm + torch.log((every[..., 1] * torch.exp(every[..., 0] - gm)).sum(dim=0))
+        winner = every[..., 2].argmax(dim=0, keepdim=True)  # first maximum = lowest rank = lowest token id
+        tok = every[..., 3].gather(0, winner).squeeze(0).long()
+        score = every[..., 2].gather(0, winner).squeeze(0) - lse
+        return score, tok

@@ -152,6 +152,9 @@ _OPTIONAL = {
     "msq_vp_ce_partial": [P, L, P, P, I, I, L, I, P],
     "msq_vp_ce_finish": [P, L, P, P, I, P, I, I, L, L, F, I, P],
     "msq_gemm2_tiles_n": [I],
+    "msq_comm_words_exchange": [P, L, P, P, L, I, I, P, P, P, I, P, P],
+    "msq_comm_reduce_scatter_pull": [P, P, L, L, I, I, F, P, I, I, P, P, P, L, ctypes.c_uint, I, P, P],
+    "msq_comm_allgather_multimem": [P, P, L, I, I, I, P, L, ctypes.c_uint, I, P, P],
     "msq_sumsq_multi": [P, I, I, I, P, P, P, I, P],
     "msq_gemm2_rowstats": [P, P, P, I, I, I, L, L, L, I, I, I, P, P, P, I, P, P, P],
     "msq_ce_merge_rowstats": [P, P, I, I, P, L, P, I, L, P, P, I, I, I, ctypes.c_uint, I, P],

@@ -365,7 +365,12 @@ class FullyShardedDataParallel(nn.Module):
             for u in units:
                 offs[id(u)] = total
                 total += (u.padded_numel + 127) // 128 * 128
-            arena = torch.zeros(total, dtype=cdt, device=self._compute_device)
+            comm = root.__dict__.get("_peer_comm")
+            if comm is not None and comm.pulls_gradients and all(u.comm is comm for u in units):
+                # owners read every rank's gradients in place over NVLink: same offset in every rank's region
+                arena = comm.alloc_symmetric(total, cdt)
+            else:
+                arena = torch.zeros(total, dtype=cdt, device=self._compute_device)
             root.__dict__["_grad_arena"] = arena
             root.__dict__["_grad_arena_offsets"] = offs
         off = root.__dict__["_grad_arena_offsets"].get(id(self))
@@ -429,8 +434,10 @@ class FullyShardedDataParallel(nn.Module):
         need = 0
         for u in units:
             esz = torch.empty((), dtype=u._compute_dtype()).element_size()
-            need += 2 * (u.padded_numel * esz + 2048)  # gathered copy + reduce-scatter landing slots
-        comm = PeerComm(units[0].process_group, units[0]._compute_device, heap_bytes=need)
+            # gathered copy + either the reduce-scatter landing slots or (pull transport) the unit's part of the
+            # gradient arena, which then lives in symmetric memory
+            need += 2 * (u.padded_numel * esz + 2048)
+        comm = PeerComm(units[0].process_group, units[0]._compute_device, heap_bytes=need + (1 << 20))
         for u in units:
             u.comm = comm
         self._peer_comm = comm
@@ -600,6 +607,12 @@ class FullyShardedDataParallel(nn.Module):
         (e.g. the embedding) are reduced here, then compute waits for outstanding collectives."""
         for u in self._units:
             u._post_backward()
+        comm = self.__dict__.get("_peer_comm")
+        if self._reduce_pending and comm is not None and comm.pulls_gradients and self._side_stream is not None:
+            # every rank has read what it needs of this rank's gradient buffers before the next backward may
+            # overwrite them (with --update-freq > 1 no other collective sits in between)
+            with torch.cuda.stream(self._side_stream):
+                comm.barrier()
         if self._reduce_pending and self._side_stream is not None:
             torch.cuda.current_stream().wait_stream(self._side_stream)
         self._reduce_pending = False

@@ -202,9 +202,17 @@ class PeerComm:
 
     def __init__(self, group, device, heap_bytes: int, chunk_bytes: int = 1 << 21, max_ctas: int = 16,
                  provider: str = "auto", small_bytes: int = 1 << 20, transport: Optional[str] = None):
-        # transport of the bulk collectives: "ce" = peer-to-peer DMA copies (no SM taken from concurrent GEMMs) or
-        # "sm" = store kernels with per-chunk arrival flags published as the chunks land
+        # transport of the bulk collectives:
+        #   "ce" = peer-to-peer DMA copies (no SM taken from concurrent GEMMs), flags published afterwards;
+        #   "sm" = store kernels with per-chunk arrival flags published as the chunks land;
+        #   "mm" = through NVSwitch: all-gather by multimem.st (the shard leaves the GPU once), reduce-scatter as an
+        #          owner-side pull with multimem.ld_reduce (the sum is formed in the switch, no landing slots);
+        #          needs the multicast mapping, and gradients that live in symmetric memory (alloc_symmetric).
+        # MSQ_COMM_AG / MSQ_COMM_RS override one direction ("pull" for the reduce-scatter works without multicast
+        # too, with plain peer loads).
         self.transport = transport or os.environ.get("MSQ_COMM_TRANSPORT", "ce")
+        self.ag_transport = os.environ.get("MSQ_COMM_AG", self.transport)
+        self.rs_transport = os.environ.get("MSQ_COMM_RS", "pull" if self.transport == "mm" else self.transport)
         self.group = group
         self.device = torch.device(device)
         self.heap = SymmetricHeap(group, heap_bytes + 2 * small_bytes * dist.get_world_size(group) + (1 << 20),
@@ -228,6 +236,26 @@ class PeerComm:
         self._done = torch.zeros(4, dtype=torch.int32, device=self.device)
         self.grad_sumsq = torch.zeros(1, dtype=torch.float32, device=self.device)
         self.overflow = torch.zeros(1, dtype=torch.int32, device=self.device)
+        if self.ag_transport == "mm" and not self.heap.multicast_ptr:
+            logger.warning("no multicast mapping of the symmetric heap: the all-gather uses peer DMA instead of multimem.st")
+            self.ag_transport = "ce"
+
+    @property
+    def pulls_gradients(self) -> bool:
+        """True when the reduce-scatter reads the other ranks' gradient buffers in place (they must then be
+        allocated with ``alloc_symmetric``) instead of receiving pushed copies in landing slots."""
+        return self.rs_transport == "pull"
+
+    def alloc_symmetric(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        """A zero-filled tensor at the same offset of every rank's region (the heap is zeroed at creation)."""
+        esz = torch.empty((), dtype=dtype).element_size()
+        off = self.heap.alloc(numel * esz)
+        return self.heap.view(off, numel, dtype)
+
+    def heap_offset_of(self, t: torch.Tensor) -> Optional[int]:
+        """Byte offset of ``t`` inside this rank's region, or ``None`` when it lies elsewhere."""
+        off = t.data_ptr() - self.heap.ptrs[self.rank]
+        return off if 0 <= off and off + t.numel() * t.element_size() <= self.heap.nbytes else None
 
     # ------------------------------------------------------------------ helpers
     def _status(self):
@@ -254,9 +282,11 @@ class PeerComm:
         chunk = min(self.chunk_bytes, shard_bytes)
         chunks = (shard_bytes + chunk - 1) // chunk
         off = self.heap.alloc(numel * esz)
+        # landing slots only for the pushing reduce-scatter transports; the pull reads the peers' buffers in place
+        slots = -1 if self.pulls_gradients else self.heap.alloc(numel * esz)
         meta = _Gathered(offset=off, numel=numel, dtype=dtype, shard_bytes=shard_bytes, chunk_bytes=chunk,
                          chunks_per_shard=chunks, flag_base=self.heap.alloc_flags(self.world * chunks),
-                         slots_offset=self.heap.alloc(numel * esz), rs_flag_base=self.heap.alloc_flags(self.world))
+                         slots_offset=slots, rs_flag_base=self.heap.alloc_flags(self.world))
         meta.tensor = self.heap.view(off, numel, dtype)
         self._bufs[meta.tensor.data_ptr()] = meta
         return meta.tensor
@@ -277,11 +307,16 @@ class PeerComm:
         if stream is not None:
             stream.wait_stream(cur)
         with torch.cuda.stream(stream if stream is not None else cur):
-            if self.transport == "ce":
+            if self.ag_transport == "ce":
                 rc = _lib.kernels().msq_comm_allgather_ce(
                     self.heap.ptr_array, meta.offset, _lib.ptr(local), meta.shard_bytes, meta.chunk_bytes, self.rank,
                     self.world, self.heap.ptr_array, meta.flag_base, meta.ag_epoch, _lib.stream_ptr(),
                     _lib.stream_ptr())
+            elif self.ag_transport == "mm":
+                rc = _lib.kernels().msq_comm_allgather_multimem(
+                    ctypes.c_void_p(self.heap.multicast_ptr + meta.offset), _lib.ptr(local), meta.shard_bytes,
+                    meta.chunk_bytes, self.rank, self.world, self.heap.ptr_array, meta.flag_base, meta.ag_epoch,
+                    self.max_ctas, self._status(), _lib.stream_ptr())
             else:
                 rc = _lib.kernels().msq_comm_allgather_push(
                     self.heap.ptr_array, meta.offset, _lib.ptr(local), meta.shard_bytes, meta.chunk_bytes, self.rank,
@@ -308,10 +343,16 @@ class PeerComm:
             meta = self.meta_of(full)
             meta.ag_epoch += 1
             meta.push_event = None
-            if self.transport == "ce":
+            if self.ag_transport == "ce":
                 rc = lib.msq_comm_allgather_ce(self.heap.ptr_array, meta.offset, _lib.ptr(local), meta.shard_bytes,
                                                meta.chunk_bytes, self.rank, self.world, self.heap.ptr_array,
                                                meta.flag_base, meta.ag_epoch, sp, cp)
+            elif self.ag_transport == "mm":
+                rc = lib.msq_comm_allgather_multimem(ctypes.c_void_p(self.heap.multicast_ptr + meta.offset),
+                                                     _lib.ptr(local), meta.shard_bytes, meta.chunk_bytes, self.rank,
+                                                     self.world, self.heap.ptr_array, meta.flag_base, meta.ag_epoch,
+                                                     self.max_ctas, status, sp)
+                meta.push_event = True
             else:
                 rc = lib.msq_comm_allgather_push(self.heap.ptr_array, meta.offset, _lib.ptr(local), meta.shard_bytes,
                                                  meta.chunk_bytes, self.rank, self.world, self.heap.ptr_array,
@@ -319,7 +360,7 @@ class PeerComm:
                 meta.push_event = True
             self._check(rc, "msq_comm_allgather")
             local.record_stream(stream)
-        if self.transport != "ce":
+        if self.ag_transport != "ce":
             ev = torch.cuda.Event()
             ev.record(stream)
             for full, _ in items:
@@ -402,7 +443,26 @@ class PeerComm:
             stream.wait_stream(cur)
         lib = _lib.kernels()
         sp = ctypes.c_void_p((stream if stream is not None else cur).cuda_stream)
-        if self.transport == "ce":
+        if self.pulls_gradients:
+            # announce this rank's buffer, then read this rank's slice of every rank's buffer in place
+            off = self.heap_offset_of(full_grad)
+            if off is None:
+                raise RuntimeError("the pull reduce-scatter needs gradient buffers from PeerComm.alloc_symmetric")
+            rc = lib.msq_comm_signal(self.heap.ptr_array, self.rank, self.world, meta.rs_flag_base, meta.rs_epoch, sp)
+            self._check(rc, "msq_comm_signal")
+            mc = self.heap.multicast_ptr if os.environ.get("MSQ_COMM_PULL_MC", "1") == "1" else 0
+            rc = lib.msq_comm_reduce_scatter_pull(
+                ctypes.c_void_p(mc) if mc else None, self.heap.ptr_array, off, shard.numel(), self.rank, self.world,
+                float(scale), _lib.ptr(shard), int(shard.dtype == torch.float32), int(meta.dtype == torch.bfloat16),
+                _lib.ptr(self.grad_sumsq) if accumulate_norm else None,
+                _lib.ptr(self.overflow) if accumulate_norm else None,
+                self.heap.flags_ptr, meta.rs_flag_base, meta.rs_epoch, 8 * self.max_ctas, self._status(), sp)
+            self._check(rc, "msq_comm_reduce_scatter_pull")
+            if stream is not None:
+                full_grad.record_stream(stream)
+                shard.record_stream(stream)
+            return
+        if self.rs_transport == "ce":
             rc = lib.msq_comm_reduce_scatter_ce(
                 self.heap.ptr_array, meta.slots_offset, _lib.ptr(full_grad), meta.shard_bytes, self.rank,
                 self.world, self.heap.ptr_array, meta.rs_flag_base, meta.rs_epoch, sp)
@@ -707,6 +767,50 @@ class DecodeReduce:
             raise RuntimeError(f"msq_gemm_skinny_allreduce launched {rc} CTAs, more than the {self.MAX_CTAS} counters")
         self.calls += 1
         return out
+
+    def close(self):
+        self.heap.close()
+
+
+class WordsExchange:
+    """Sum or all-gather of a small tensor over a tensor-parallel group in one kernel that a CUDA graph can replay
+    (``msq_comm_words_exchange``): every 32-bit word travels with the epoch of its call to every peer's receive buffer
+    and each rank polls its own buffer; the epoch counter lives in device memory and is advanced by the kernel.
+    Used by the graphed decode step for the vocabulary-parallel embedding (a sum: one rank holds each token's row,
+    metaseq/modules/megatron/mpu/layers.py:229-250) and for picking the next token from vocabulary-parallel logits
+    without gathering them (an all-gather of one small record per row, instead of the ``[B, V]`` gather of
+    metaseq/modules/megatron/mpu/mappings.py:97)."""
+
+    def __init__(self, group, device, max_words: int, provider: str = "auto"):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.cap = int(max_words)
+        nbytes = self.world * self.cap * 8
+        self.heap = SymmetricHeap(group, 2 * (nbytes + 4096) + (1 << 16), device, provider=provider)  # zero-filled
+        offs = [self.heap.alloc(nbytes), self.heap.alloc(nbytes)]
+        self._recv = [(ctypes.c_void_p * self.world)(*[p + off for p in self.heap.ptrs]) for off in offs]
+        self._state = torch.zeros(2, dtype=torch.int32, device=device)  # [epoch, ticket of the kernel]
+
+    def _call(self, x: torch.Tensor, out: torch.Tensor, mode: int):
+        words = x.numel() * x.element_size() // 4
+        assert x.is_contiguous() and out.is_contiguous() and x.numel() * x.element_size() % 4 == 0 and words <= self.cap
+        rc = _lib.kernels().msq_comm_words_exchange(
+            _lib.ptr(x), words, self._recv[0], self._recv[1], self.cap, self.rank, self.world,
+            ctypes.c_void_p(self._state.data_ptr()), ctypes.c_void_p(self._state.data_ptr() + 4), _lib.ptr(out), mode,
+            _lib.ptr(_lib.status_word(x.device)), _lib.stream_ptr())
+        _lib.check_rc(rc, "msq_comm_words_exchange")
+        return out
+
+    def sum(self, x: torch.Tensor) -> torch.Tensor:
+        """Sum over ranks of a contiguous fp16 / bf16 tensor with an even number of elements (fp32 accumulation)."""
+        assert x.dtype in (torch.float16, torch.bfloat16)
+        return self._call(x, torch.empty_like(x), 1 if x.dtype == torch.bfloat16 else 0)
+
+    def gather(self, x: torch.Tensor) -> torch.Tensor:
+        """``[world, *x.shape]``: every rank's ``x`` (any 4-byte dtype, contiguous)."""
+        assert x.element_size() == 4
+        return self._call(x, torch.empty((self.world,) + tuple(x.shape), dtype=x.dtype, device=x.device), 2)
 
     def close(self):
         self.heap.close()

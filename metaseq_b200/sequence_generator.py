@@ -52,6 +52,7 @@ class SequenceGenerator(nn.Module):
         if topp is None:
             topp = 0.0
         self.sampling_topp = max(0.0, topp)
+        self.shard_picks = True  # greedy decoding under tensor parallelism picks tokens from the logit shards
         self.temperature = temperature
         assert temperature >= 0, "--temperature must be >=0"
         self.profile = profile
@@ -128,8 +129,34 @@ class SequenceGenerator(nn.Module):
         eos_mask = torch.zeros(n, dtype=torch.bool, device=dev)
         neg_inf = -math.inf
         sentence_p = torch.full((n,), self.sampling_topp, device=dev) if self.lambda_decay > 0 else None
+        # Greedy decoding over vocabulary-parallel logits picks the token from the shards: the graphed step returns
+        # this rank's columns and a record of four numbers per row and rank replaces the gather of [n, V] logits.
+        sharded = (graphed is not None and getattr(graphed, "tp", 1) > 1 and self._is_greedy() and count_tokens is None
+                   and count_src is None and all_lprobs is None and self.temperature in (0.0, 1.0)
+                   and self.shard_picks)
+        local = None
         # ------------------------------------------------------- decode loop
         for step in range(start, max_len):
+            if sharded and local is not None:
+                banned = [self.pad]
+                if step < min_len and step < max_len - 1:
+                    banned += [self.eos, *self.stop]
+                next_scores, next_toks = graphed.pick_greedy(local, banned=banned,
+                                                             only=self.eos if step >= max_len - 1 else None)
+                # finished hypotheses can only repeat EOS, at no cost
+                next_toks = torch.where(eos_mask, torch.full_like(next_toks, self.eos), next_toks)
+                next_scores = torch.where(eos_mask, torch.zeros_like(next_scores), next_scores)
+                tokens[:, step] = next_toks
+                scores[:, step] = next_scores
+                eos_mask |= next_toks == self.eos
+                for s in self.stop:
+                    eos_mask |= next_toks == s
+                if (step - start) % self.eos_check_interval == 0 and bool(eos_mask.all()):
+                    break
+                if step + 1 >= max_len:
+                    break
+                local = graphed.step(tokens[:, step], gather=False)
+                continue
             if step < min_len and step < max_len - 1:  # the forced EOS of the last position wins over min_len
                 lprobs[:, self.eos] = neg_inf
                 for s in self.stop:
@@ -161,7 +188,9 @@ class SequenceGenerator(nn.Module):
                 break
             if step + 1 >= max_len:
                 break
-            if graphed is not None:
+            if sharded:
+                local = graphed.step(tokens[:, step], gather=False)  # from here on the tokens come from the shards
+            elif graphed is not None:
                 lprobs = self._logprobs(graphed.step(tokens[:, step]))
             else:
                 logits, _ = self.model.decoder(tokens[:, : step + 1], incremental_state=state)
@@ -176,6 +205,9 @@ class SequenceGenerator(nn.Module):
         return out
 
     # -------------------------------------------------------------- sampling
+    def _is_greedy(self) -> bool:
+        return self.temperature == 0.0 or self.sampling_topp == 0.0
+
     def _sample(self, lprobs: Tensor, sentence_p: Optional[Tensor] = None):
         """Returns ``(log-prob of the chosen token, chosen token)`` per row."""
         if self.temperature == 0.0 or self.sampling_topp == 0.0:

@@ -75,10 +75,14 @@ def _worker(rank, world, port, provider, transport, results):
             err = (y.float() - ref).abs().max().item()
             assert err <= 2e-2 * ref.abs().max().item() + 1e-3, f"flag-polling GEMM mismatch at step {step}: {err}"
             dist.barrier()
-        # ---- reduce-scatter with fp32 sum, scale, norm and overflow flag
+        # ---- reduce-scatter with fp32 sum, scale, norm and overflow flag.  The pull transport reads the peers'
+        # buffers in place, so the gradients then live in symmetric memory.
+        gsym = comm.alloc_symmetric(numel, torch.float16) if comm.pulls_gradients else None
         for step in range(3):
             g = torch.Generator(device=dev).manual_seed(7 + 10 * step + rank)
             grad = torch.randn(numel, device=dev, dtype=torch.float16, generator=g)
+            if gsym is not None:
+                grad = gsym.copy_(grad)
             allg = [torch.empty_like(grad) for _ in range(world)]
             dist.all_gather(allg, grad)
             S = numel // world
@@ -94,6 +98,8 @@ def _worker(rank, world, port, provider, transport, results):
             assert comm.overflow.item() == 0
             dist.barrier()
         grad = torch.full((numel,), float("inf") if rank == 0 else 1.0, device=dev, dtype=torch.float16)
+        if gsym is not None:
+            grad = gsym.copy_(grad)
         shard = torch.empty(numel // world, device=dev, dtype=torch.float16)
         comm.reduce_scatter(shard, grad, key=full, scale=1.0, accumulate_norm=True)
         torch.cuda.synchronize()
@@ -113,15 +119,20 @@ def _worker(rank, world, port, provider, transport, results):
                         assert torch.allclose(y.float(), ref.float(), rtol=1e-2, atol=1e-2), (dtype, n, use_mc)
         assert _lib.check_status(dev) == 0
         results[rank] = dict(provider=comm.heap.provider, multicast=bool(comm.heap.multicast_ptr),
-                             fallback=comm.heap.fallback_reason)
+                             fallback=comm.heap.fallback_reason, all_gather=comm.ag_transport,
+                             reduce_scatter=comm.rs_transport)
         dist.barrier()
         comm.close()
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("provider,transport", [("ipc", "sm"), ("auto", "sm"), ("auto", "ce"), ("ipc", "ce")])
+@pytest.mark.parametrize("provider,transport", [("ipc", "sm"), ("auto", "sm"), ("auto", "ce"), ("ipc", "ce"),
+                                                ("auto", "mm"), ("ipc", "mm")])
 def test_peer_collectives(provider, transport):
+    """``mm``: all-gather by multimem.st and reduce-scatter as an owner-side multimem.ld_reduce pull where the heap
+    has a multicast mapping; without one (the ``ipc`` mapping) the all-gather falls back to peer DMA and the pull
+    reads the peers with plain loads."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs at least two GPUs")
     import torch.multiprocessing as mp
@@ -335,6 +346,48 @@ def _decode_worker(rank, world, port, results):
                 assert logits.shape == full[:, t].shape
                 torch.testing.assert_close(logits.float(), full[:, t].float(), rtol=5e-2, atol=5e-2)
         assert runner.reduce is not None and runner.reduce.calls > 0
+        assert _lib.check_status(dev) == 0
+        # ---- the small exchange kernel on its own: sum of 16-bit rows and all-gather of records, eager and replayed
+        from metaseq_b200.parallel.symm import WordsExchange
+
+        ex = WordsExchange(dist.group.WORLD, dev, 4096)
+        for it in range(3):
+            g = torch.Generator(device=dev).manual_seed(300 + 10 * it + rank)
+            x = torch.randn(5, 256, device=dev, dtype=torch.float16, generator=g)
+            ref = x.float()
+            dist.all_reduce(ref)
+            torch.testing.assert_close(ex.sum(x).float(), ref, rtol=2e-3, atol=2e-3)
+            rec = torch.randn(7, 4, device=dev, generator=g)
+            every = ex.gather(rec)
+            refs = [torch.empty_like(rec) for _ in range(world)]
+            dist.all_gather(refs, rec)
+            assert torch.equal(every, torch.stack(refs))
+        xg = torch.zeros(6, 128, device=dev, dtype=torch.float16)
+        ex.sum(xg)
+        torch.cuda.synchronize()
+        dist.barrier()
+        gx = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gx):
+            yg = ex.sum(xg)
+        for it in range(4):
+            xg.copy_(torch.randn(6, 128, device=dev, generator=torch.Generator(device=dev).manual_seed(40 + it + 7 * rank)))
+            gx.replay()
+            ref = xg.float()
+            dist.all_reduce(ref)
+            torch.testing.assert_close(yg.float(), ref, rtol=2e-3, atol=2e-3)
+        # ---- greedy generation: tokens picked from the logit shards equal those picked from gathered logits
+        from metaseq_b200.sequence_generator import SequenceGenerator
+
+        prompts = tokens[:, :16].contiguous()
+        outs = {}
+        for shard_picks in (True, False):
+            sg = SequenceGenerator([model], task.target_dictionary, beam_size=1, max_len_b=40, min_len=30, temperature=1.0,
+                                   topp=-1.0, decode_graph=True)
+            sg.shard_picks = shard_picks
+            with torch.no_grad():
+                outs[shard_picks] = sg.generate([model], {"net_input": {"src_tokens": prompts}})
+        assert torch.equal(outs[True]["tokens"], outs[False]["tokens"])
+        torch.testing.assert_close(outs[True]["scores"], outs[False]["scores"], rtol=1e-3, atol=2e-3)
         assert _lib.check_status(dev) == 0
         results[rank] = True
         dist.barrier()

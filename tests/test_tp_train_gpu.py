@@ -64,7 +64,7 @@ def test_tensor_parallel_fused_matches_nccl(tmp_path, sp):
     assert fused[-1] < fused[0]
 
 
-def _run_fsdp(save, max_update, extra=()):
+def _run_fsdp(save, max_update, extra=(), env=None, backend="fused"):
     cmd = [
         sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
         "--master-port", str(_free_port()), "-m", "metaseq_b200.cli.train",
@@ -78,9 +78,10 @@ def _run_fsdp(save, max_update, extra=()):
         "--use-sharded-state", "--no-reshard-after-forward", "--tensor-parallel-init-model-on-gpu",
         "--distributed-world-size", "2", "--max-update", str(max_update), "--log-format", "json", "--log-interval", "1",
         "--save-dir", str(save), "--disable-validation", "--save-interval-epochs", "0", "--save-interval-updates", "3",
-        "--seed", "3", "--comm-backend", "fused", *extra,
+        "--seed", "3", "--comm-backend", backend, *extra,
     ]
-    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, OMP_NUM_THREADS="1"))
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600,
+                         env=dict(os.environ, OMP_NUM_THREADS="1", **(env or {})))
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     losses = {}
     for line in out.stdout.splitlines():
@@ -112,3 +113,18 @@ def test_sharded_checkpoint_resume_with_peer_memory_collectives(tmp_path):
     assert sorted(resumed) == [4, 5, 6], resumed
     for n in (4, 5, 6):
         assert resumed[n] == pytest.approx(straight[n], abs=2e-2), (n, resumed, straight)
+
+
+@pytest.mark.parametrize("transport", ["mm", "sm"])
+def test_fsdp_collectives_through_the_switch_match_nccl(tmp_path, transport):
+    """Two data-parallel GPUs, gradient accumulation over two micro-batches: the all-gather by multimem.st with the
+    owner-side multimem.ld_reduce reduce-scatter (``mm``) and the store kernels (``sm``) give the losses of the NCCL run."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least two GPUs")
+    extra = ("--update-freq", "2")
+    ours = _run_fsdp(tmp_path / transport, 5, extra, env={"MSQ_COMM_TRANSPORT": transport})
+    nccl = _run_fsdp(tmp_path / "nccl", 5, extra, backend="nccl")
+    assert sorted(ours) == sorted(nccl) == [1, 2, 3, 4, 5]
+    for n in nccl:
+        assert ours[n] == pytest.approx(nccl[n], abs=2e-2), (n, ours, nccl)
+    assert ours[5] < ours[1]

@@ -231,3 +231,46 @@ def test_restore_on_more_ranks(runs, tmp_path):
     assert resized[4][0] == pytest.approx(runs["dp1"][4][0], abs=3e-3)
     names = sorted(os.path.basename(p) for p in glob.glob(str(tmp_path / "wide" / "checkpoint_last*")))
     assert names == [f"checkpoint_last-model_part-0-shard{i}.pt" for i in range(4)]
+
+
+def test_async_sharded_save_then_reshard_to_fewer_model_parts_and_reload(tmp_path):
+    """The checkpoint path of the large tensor-parallel recipe at toy size: four tensor-parallel ranks train and save
+    their shards through the asynchronous writer; the offline tools unflatten every part and re-split the model for
+    two tensor-parallel ranks; a two-rank run restored from those files computes, on its first update, the loss that
+    the four-rank run reports on its next one."""
+    from metaseq_b200.checkpoint import reshard_fsdp, reshard_mp
+
+    heads4 = ["--decoder-attention-heads", "4", "--model-parallel-size", "4", "--write-checkpoints-asynchronously",
+              "--save-interval-updates", "3"]
+    run_train(tmp_path / "tp4", 4, 3, heads4)
+    names = sorted(os.path.basename(p) for p in glob.glob(str(tmp_path / "tp4" / "checkpoint_3*")))
+    assert names == [f"checkpoint_3-model_part-{i}-shard0.pt" for i in range(4)]  # all written, none left as .tmp
+    for part in range(4):
+        reshard_fsdp.reshard_fsdp_checkpoints(str(tmp_path / "tp4" / f"checkpoint_3-model_part-{part}-shard*.pt"),
+                                              str(tmp_path / "unflat" / f"reshard-model_part-{part}-shard{{i}}.pt"),
+                                              num_output_shards=1, unflatten_weights=True)
+        os.rename(tmp_path / "unflat" / f"reshard-model_part-{part}-shard0.pt",
+                  tmp_path / "unflat" / f"reshard-model_part-{part}.pt")
+    two = reshard_mp.reshard_mp(str(tmp_path / "unflat" / "reshard-model_part-*.pt"),
+                                str(tmp_path / "tp2" / "resharded-model_part-{i}.pt"), 2)
+    assert [os.path.basename(p) for p in two] == ["resharded-model_part-0.pt", "resharded-model_part-1.pt"]
+    cont, _ = run_train(tmp_path / "tp4", 4, 4, heads4)  # the four-rank run goes on: update 4
+    flags = [a for a in COMMON if a != "--use-sharded-state"]
+    cmd = [sys.executable, "-m", "metaseq_b200.cli.train", *flags, "--decoder-attention-heads", "4",
+           "--model-parallel-size", "2", "--distributed-world-size", "2", "--max-update", "1",
+           "--save-dir", str(tmp_path / "tp2run"), "--restore-file", str(tmp_path / "tp2" / "resharded.pt"),
+           "--reset-optimizer", "--reset-dataloader", "--reset-meters", "--reset-lr-scheduler",
+           "--save-interval-updates", "0", "--save-interval-epochs", "0"]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=900,
+                         env=dict(os.environ, OMP_NUM_THREADS="2", MASTER_ADDR="127.0.0.1"))
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    first = None
+    for line in out.stdout.splitlines():
+        i = line.find('{"epoch"')
+        if i >= 0:
+            rec = json.loads(line[i:])
+            if "num_updates" in rec and "loss" in rec and "train_loss" not in rec:
+                first = float(rec["loss"])
+                break
+    assert first is not None, out.stdout[-2000:]
+    assert first == pytest.approx(cont[4][0], abs=5e-3)
