@@ -195,7 +195,7 @@ def main(argv=None):
         return torch.nn.functional.scaled_dot_product_attention(
             q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True)
 
-    if d in (64, 128):
+    if F.attn_head_dim_ok(d):
         report("attn_fwd", att_flops, 0, lambda: F.flash_attn_fwd(q, k, v, scale, True), sdpa)
         out, lse = F.flash_attn_fwd(q, k, v, scale, True)
         d_out = torch.randn_like(out)

@@ -29,14 +29,44 @@
 // Q, dO, P and dS for the transposed products without any transposed copy.
 #include "sm100_common.cuh"
 
-namespace msq {
+// 1: half of the exponentials of the unmasked tiles are computed on the FMA pipe (exp2_fma_pair); 0: all on ex2.approx
+#ifndef MSQ_ATTN_FMA_EXP
+#define MSQ_ATTN_FMA_EXP 1
+#endif
 
+namespace msq {
 
 constexpr int ATT_THREADS = 192;      // forward: TMA warp, MMA warp, 4 softmax warps
 constexpr int ATT_BWD_THREADS = 448;  // backward: TMA warp, MMA warp, 8 element-wise warps, 4 dQ-drain warps
 constexpr int TILE = 128;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
+
+// 2^x for a pair of fp32 values on the FMA pipe instead of the special-function unit, which is the busiest unit of
+// these kernels (one exponential per score, 16 per clock and SM, against 128 fused multiply-adds): x is split into
+// the nearest integer n (magic-number rounding) and f = x - n in [-0.5, 0.5], 2^f comes from a degree-4 polynomial
+// (relative error below 5e-5, an order of magnitude under the 16-bit rounding of the result) and n is added into the
+// exponent field.  Inputs are clamped at -126; inputs above about 100 are not expected (the callers keep x <= 8).
+// The kernels send every second pair of a tile through this routine and the rest through ex2.approx.
+__device__ __forceinline__ void exp2_fma_pair(uint64_t x2, float& e0, float& e1) {
+  float x0, x1;
+  f2_unpack(x2, x0, x1);
+  x2 = f2_pack(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
+  const uint64_t magic = f2_pack(12582912.f, 12582912.f);       // 1.5 * 2^23: adding it rounds to an integer
+  const uint64_t neg_magic = f2_pack(-12582912.f, -12582912.f);
+  const uint64_t t2 = f2_add(x2, magic);
+  const uint64_t n2 = f2_add(t2, neg_magic);
+  const uint64_t f2 = f2_fma(n2, f2_pack(-1.f, -1.f), x2);
+  uint64_t p2 = f2_fma(f2_pack(0.00961812911f, 0.00961812911f), f2, f2_pack(0.0555041087f, 0.0555041087f));
+  p2 = f2_fma(p2, f2, f2_pack(0.240226507f, 0.240226507f));
+  p2 = f2_fma(p2, f2, f2_pack(0.693147182f, 0.693147182f));
+  p2 = f2_fma(p2, f2, f2_pack(1.f, 1.f));
+  float p0, p1, t0, t1;
+  f2_unpack(p2, p0, p1);
+  f2_unpack(t2, t0, t1);
+  e0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
+  e1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
+}
 
 // Byte offset of the 16-byte unit `unit` (0..7) of row `r` inside a
 // [rows x 128 B] 128-byte-swizzled chunk.
@@ -337,9 +367,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           } else {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-              float x0, x1;
-              f2_unpack(f2_fma(f2_pack_bits(r[c & 1][2 * i], r[c & 1][2 * i + 1]), scale2, neg_m2), x0, x1);
-              const float a = exp2f(x0), bb = exp2f(x1);
+              const uint64_t x2 = f2_fma(f2_pack_bits(r[c & 1][2 * i], r[c & 1][2 * i + 1]), scale2, neg_m2);
+              float a, bb;
+              if (MSQ_ATTN_FMA_EXP && (i & 1)) {
+                exp2_fma_pair(x2, a, bb);  // every second pair on the FMA pipe
+              } else {
+                float x0, x1;
+                f2_unpack(x2, x0, x1);
+                a = exp2f(x0);
+                bb = exp2f(x1);
+              }
               ps2[i & 1] = f2_add(ps2[i & 1], f2_pack(a, bb));  // the normaliser uses the undropped weights
               float da = a, db = bb;
               if (DROP) {
@@ -795,9 +832,16 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             const uint64_t sc2 = f2_pack(p.scale, p.scale), nds2 = f2_pack(nds, nds);
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-              float x0, x1, d0, d1;
-              f2_unpack(f2_fma(f2_pack_bits(s[2 * i], s[2 * i + 1]), sl2, nl2), x0, x1);
-              const float p0 = exp2f(x0), p1 = exp2f(x1);
+              float d0, d1, p0, p1;
+              const uint64_t x2 = f2_fma(f2_pack_bits(s[2 * i], s[2 * i + 1]), sl2, nl2);
+              if (MSQ_ATTN_FMA_EXP && (i & 1)) {
+                exp2_fma_pair(x2, p0, p1);  // every second pair on the FMA pipe
+              } else {
+                float x0, x1;
+                f2_unpack(x2, x0, x1);
+                p0 = exp2f(x0);
+                p1 = exp2f(x1);
+              }
               const uint64_t g = f2_fma(f2_pack_bits(dp[2 * i], dp[2 * i + 1]), sc2, nds2);
               f2_unpack(f2_mul(f2_pack(p0, p1), g), d0, d1);
               pp[c][i] = pack2<BF16>(p0, p1);

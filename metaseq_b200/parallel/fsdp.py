@@ -520,8 +520,15 @@ class FullyShardedDataParallel(nn.Module):
                 v._grad_filled = True
         full_grad = self._full_grad
         if self.world_size == 1:
-            shard = full_grad if full_grad.dtype == self.flat_param.dtype else full_grad.to(self.flat_param.dtype)
-            self._accumulate_shard_grad(shard, owns_buffer=True)
+            same = full_grad.dtype == self.flat_param.dtype
+            shard = full_grad if same else full_grad.to(self.flat_param.dtype)
+            # the flat buffer doubles as the parameter's gradient only when no cast (or host copy) sits in between;
+            # otherwise each micro-batch's buffer is added to the parameter's gradient and then overwritten
+            self._accumulate_shard_grad(shard, owns_buffer=same)
+            if self.flat_param.grad is None or self.flat_param.grad.data_ptr() != full_grad.data_ptr():
+                for v in self._views:
+                    if hasattr(v, "_grad_filled"):
+                        v._grad_filled = False
         elif self.comm is not None:
             # peer-memory reduce-scatter: slices are pushed to their owners and summed there in fp32 with the
             # 1 / world_size factor applied once, so neither pre-division nor an fp32 copy is needed

@@ -69,3 +69,33 @@ def test_cpu_offload_keeps_shards_on_the_host_and_trains_like_the_plain_run(tmp_
     base = _run(tmp_path / "a", POLY + ["--ddp-backend", "fully_sharded"])
     off = _run(tmp_path / "b", POLY + ["--ddp-backend", "fully_sharded", "--cpu-offload"])
     assert off == pytest.approx(base, abs=1e-4)
+
+
+@pytest.mark.parametrize("flags", [["--fp16", "--fp16-init-scale", "4"], ["--cpu-offload"], []])
+def test_two_identical_micro_batches_give_the_update_of_one(tmp_path, flags):
+    """Sharded model on one rank, also with fp32 master shards or offloaded shards (where the flat gradient buffer
+    is not the parameter's gradient): accumulating two copies of a batch must not count the first one twice."""
+    extra = POLY + ["--ddp-backend", "fully_sharded", "--clip-norm", "0.0"] + flags
+
+    def run(copies):
+        argv = ["--task", "dummy_lm", "--dict-size", "124", "--tokens-per-sample", "16", "--batch-size", "2",
+                "--arch", "transformer_lm_megatron", "--decoder-layers", "2", "--decoder-embed-dim", "32",
+                "--decoder-ffn-embed-dim", "64", "--decoder-attention-heads", "2", "--decoder-learned-pos",
+                "--share-decoder-input-output-embed", "--dropout", "0.0", "--attention-dropout", "0.0", "--criterion",
+                "cross_entropy", "--optimizer", "adam", "--lr", "1e-2", "--cpu", "--distributed-world-size", "1",
+                "--save-dir", str(tmp_path), "--disable-validation", "--log-format", "none", *extra]
+        cfg = convert_namespace_to_config(options.parse_args_and_arch(options.get_training_parser(), input_args=argv))
+        torch.manual_seed(1)
+        task = tasks.setup_task(cfg.task)
+        model, criterion = build_model_and_criterion(cfg, task)
+        tr = Trainer(cfg, task, model, criterion)
+        task.load_dataset("train")
+        batch = task.dataset("train").collater([0, 1])
+        norms = []
+        for _ in range(3):
+            tr.train_step([batch] * copies)
+            norms.append(float(tr.last_grad_norm))
+        return norms
+
+    one, two = run(1), run(2)
+    assert two == pytest.approx(one, rel=2e-2), (one, two)
