@@ -12,11 +12,14 @@
 //
 // Layout: q, k, v are [B, T, H, hd] views with arbitrary row / batch strides
 // (they are column slices of the fused qkv projection output); the output is
-// [B, T, H*hd].  The tensor maps are 4-D (hd, H, T, B): one TMA box is 128 rows x 64 columns of
-// one head with 128-byte swizzle, and a tile of HD columns is HD/64 such boxes.  Head sizes
-// that are not 64 or 128 (80 and 96: OPT-2.7B, OPT-760M) run the HD = 128 kernels: columns
-// past hd lie outside the map's first dimension, so the loads fill them with zeros, which
-// contribute nothing to Q K^T and leave the padded columns of O, dQ, dK, dV unused.
+// [B, T, H*hd].  One TMA box is 128 rows x 64 columns of one head with 128-byte swizzle, and a
+// tile of HD columns is HD/64 such boxes.  Two instantiations of every kernel: the plain one
+// (head sizes 64 and 128, causal mask only; 3-D tensor maps: all heads' columns, token, batch)
+// and the general one, which adds the masks below and head sizes that are other multiples of 8
+// (80 and 96: OPT-2.7B, OPT-760M; run on the HD = 128 kernels, up to 64 on the HD = 64 ones).
+// It uses 4-D maps (hd, head, token, batch): columns past hd lie outside the map's first
+// dimension, so the loads fill them with zeros, which contribute nothing to Q K^T and leave
+// the padded columns of O, dQ, dK, dV unused.
 //
 // Masks beyond causality (both optional): `doc_start[b, t]` = first position of the document
 // that token t belongs to; a query attends to keys in [doc_start, t] only (the reference's
@@ -29,11 +32,6 @@
 // Q, dO, P and dS for the transposed products without any transposed copy.
 #include "sm100_common.cuh"
 
-// 1: half of the exponentials of the unmasked tiles are computed on the FMA pipe (exp2_fma_pair); 0: all on ex2.approx
-#ifndef MSQ_ATTN_FMA_EXP
-#define MSQ_ATTN_FMA_EXP 1
-#endif
-
 namespace msq {
 
 constexpr int ATT_THREADS = 192;      // forward: TMA warp, MMA warp, 4 softmax warps
@@ -42,36 +40,24 @@ constexpr int TILE = 128;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 
-// 2^x for a pair of fp32 values on the FMA pipe instead of the special-function unit, which is the busiest unit of
-// these kernels (one exponential per score, 16 per clock and SM, against 128 fused multiply-adds): x is split into
-// the nearest integer n (magic-number rounding) and f = x - n in [-0.5, 0.5], 2^f comes from a degree-4 polynomial
-// (relative error below 5e-5, an order of magnitude under the 16-bit rounding of the result) and n is added into the
-// exponent field.  Inputs are clamped at -126; inputs above about 100 are not expected (the callers keep x <= 8).
-// The kernels send every second pair of a tile through this routine and the rest through ex2.approx.
-__device__ __forceinline__ void exp2_fma_pair(uint64_t x2, float& e0, float& e1) {
-  float x0, x1;
-  f2_unpack(x2, x0, x1);
-  x2 = f2_pack(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
-  const uint64_t magic = f2_pack(12582912.f, 12582912.f);       // 1.5 * 2^23: adding it rounds to an integer
-  const uint64_t neg_magic = f2_pack(-12582912.f, -12582912.f);
-  const uint64_t t2 = f2_add(x2, magic);
-  const uint64_t n2 = f2_add(t2, neg_magic);
-  const uint64_t f2 = f2_fma(n2, f2_pack(-1.f, -1.f), x2);
-  uint64_t p2 = f2_fma(f2_pack(0.00961812911f, 0.00961812911f), f2, f2_pack(0.0555041087f, 0.0555041087f));
-  p2 = f2_fma(p2, f2, f2_pack(0.240226507f, 0.240226507f));
-  p2 = f2_fma(p2, f2, f2_pack(0.693147182f, 0.693147182f));
-  p2 = f2_fma(p2, f2, f2_pack(1.f, 1.f));
-  float p0, p1, t0, t1;
-  f2_unpack(p2, p0, p1);
-  f2_unpack(t2, t0, t1);
-  e0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
-  e1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
-}
-
 // Byte offset of the 16-byte unit `unit` (0..7) of row `r` inside a
 // [rows x 128 B] 128-byte-swizzled chunk.
 __device__ __forceinline__ uint32_t sw128_offset(int r, int unit) {
   return static_cast<uint32_t>(r) * 128u + (static_cast<uint32_t>(unit ^ (r & 7)) << 4);
+}
+
+// One 64-column box of head `h` at token row `row`: native head sizes use the 3-D map (columns of all heads in
+// one dimension, so that 256-byte L2 promotion spans neighbouring heads), other sizes the 4-D map whose first
+// dimension ends at the head size and zero-fills beyond it.
+__device__ __forceinline__ void attn_load_box(void* dst, const CUtensorMap* tm, uint64_t* bar, bool native, int hd,
+                                              int c, int h, int row, int b) {
+  if (native) tma_load_3d(dst, tm, bar, h * hd + c * 64, row, b);
+  else tma_load_4d(dst, tm, bar, c * 64, h, row, b);
+}
+__device__ __forceinline__ void attn_reduce_box(const CUtensorMap* tm, const void* src, bool native, int hd, int col,
+                                                int h, int row, int b) {
+  if (native) tma_reduce_add_3d(tm, src, h * hd + col, row, b);
+  else tma_reduce_add_4d(tm, src, col, h, row, b);
 }
 
 struct AttnFwdParams {
@@ -109,7 +95,10 @@ struct FwdCfg {
   static constexpr uint32_t TMEM_COLS = (HD == 64) ? 256 : 512;
 };
 
-template <int HD, bool BF16, bool DROP>
+// GEN: the instantiation that also handles document starts, ALiBi and head sizes below HD (4-D tensor maps).  The
+// plain instantiation carries none of that code: the softmax loop is the critical path of the kernel and its speed
+// proved sensitive to the amount of code around it.
+template <int HD, bool BF16, bool DROP, bool GEN>
 __global__ void __launch_bounds__(ATT_THREADS, (HD == 64) ? 2 : 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const AttnFwdParams p) {
@@ -134,9 +123,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int qb = n_qblocks - 1 - blockIdx.x;  // heaviest (longest causal prefix) blocks first
   const int h = blockIdx.y, b = blockIdx.z;
   // With document starts the first row of the tile has the earliest start: kv blocks before it are skipped.
-  const int* dstart = p.doc_start ? p.doc_start + static_cast<long long>(b) * p.T : nullptr;
-  const int j0 = dstart ? dstart[min(qb * TILE, p.T - 1)] / TILE : 0;
+  const int* dstart = (GEN && p.doc_start) ? p.doc_start + static_cast<long long>(b) * p.T : nullptr;
+  const int j0 = (GEN && dstart) ? dstart[min(qb * TILE, p.T - 1)] / TILE : 0;
   const int n_kv = (p.causal ? (qb + 1) : (p.T + TILE - 1) / TILE) - j0;  // blocks j0 .. j0 + n_kv - 1
+  const int hd = GEN ? p.hd : HD;
 
   if (p.status && *reinterpret_cast<volatile int*>(p.status) != 0) return;
 
@@ -169,7 +159,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_expect_tx(q_full, Cfg::TILE_BYTES);
 #pragma unroll
       for (int c = 0; c < Cfg::CHUNKS; ++c)
-        tma_load_4d(sQ + c * Cfg::CHUNK_BYTES, &tmQ, q_full, c * 64, h, qb * TILE, b);
+        attn_load_box(sQ + c * Cfg::CHUNK_BYTES, &tmQ, q_full, !GEN, hd, c, h, qb * TILE, b);
       int slot = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -183,7 +173,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           const CUtensorMap* tm = which ? &tmV : &tmK;
 #pragma unroll
           for (int c = 0; c < Cfg::CHUNKS; ++c)
-            tma_load_4d(dst + c * Cfg::CHUNK_BYTES, tm, &kv_full[slot], c * 64, h, (j0 + j) * TILE, b);
+            attn_load_box(dst + c * Cfg::CHUNK_BYTES, tm, &kv_full[slot], !GEN, hd, c, h, (j0 + j) * TILE, b);
           if (++slot == Cfg::SLOTS) { slot = 0; phase ^= 1; }
         }
       }
@@ -262,8 +252,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const unsigned long long drop_row =
         ((static_cast<unsigned long long>(b) * p.H + h) * p.T + q_idx) * static_cast<unsigned long long>((p.T + 1) >> 1);
     bool ok = true;
-    const int row_start = (dstart && q_idx < p.T) ? dstart[q_idx] : 0;  // first key this row may attend to
-    const float slope2 = p.alibi_slopes ? p.alibi_slopes[h] * LOG2E : 0.f;
+    const int row_start = (GEN && dstart && q_idx < p.T) ? dstart[q_idx] : 0;  // first key this row may attend to
+    const float slope2 = (GEN && p.alibi_slopes) ? p.alibi_slopes[h] * LOG2E : 0.f;
     for (int j = 0; j < n_kv && ok; ++j) {
       ok = mbar_wait_warp(s_full, j & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
       if (!ok) break;
@@ -275,12 +265,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const bool prof_on = p.prof != nullptr && row == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j < 32;
       if (prof_on) p.prof[j * 8 + 0] = clock64();
       const int lo = row_start - ja * TILE;
-      const bool need_mask = (p.causal && ja == qb) || ((ja + 1) * TILE > p.T) || p.alibi_slopes != nullptr ||
-                             __any_sync(0xffffffffu, lo > 0);
+      // `general`: a document start cuts this block for some row of the warp, or ALiBi is on: the per-element path
+      // then also applies the lower bound and the position bias (a separate code path, so that plain causal
+      // attention pays nothing for it)
+      const bool general = GEN && (p.alibi_slopes != nullptr || (dstart != nullptr && __any_sync(0xffffffffu, lo > 0)));
+      const bool need_mask = (p.causal && ja == qb) || ((ja + 1) * TILE > p.T) || general;
       int limit = p.T - ja * TILE;
       if (p.causal) limit = min(limit, q_idx - ja * TILE + 1);
       limit = max(0, min(limit, TILE));
-      const float kpos0 = static_cast<float>(ja * TILE);  // ALiBi: bias of column i is slope2 * (kpos0 + i)
+      const float bias0 = slope2 * static_cast<float>(ja * TILE);  // ALiBi: bias of column i is bias0 + slope2 * i
       float mx;  // row maximum of this block in log2 units (scaled, biased)
       {
         // four independent running maxima keep the dependency chains short
@@ -291,13 +284,18 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int c = 0; c < 4; ++c) {
           tmem_ld_wait();
           if (c + 1 < 4) tmem_ld_32x32(tS + lane_off + (c + 1) * 32, r[(c + 1) & 1]);
-          if (need_mask) {
+          if (GEN && general) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               const int col = c * 32 + i;
               if (col < limit && col >= lo)
-                m4[i & 3] = fmaxf(m4[i & 3], fmaf(__uint_as_float(r[c & 1][i]), p.scale_log2, slope2 * (kpos0 + col)));
+                m4[i & 3] = fmaxf(m4[i & 3], fmaf(__uint_as_float(r[c & 1][i]), p.scale_log2,
+                                                  fmaf(slope2, static_cast<float>(c * 32 + i), bias0)));
             }
+          } else if (need_mask) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (c * 32 + i < limit) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(r[c & 1][i]));
           } else {
 #pragma unroll
             for (int i = 0; i < 16; ++i)
@@ -305,7 +303,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
         }
         mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-        if (!need_mask) mx *= p.scale_log2;  // the per-element path already works in scaled units
+        if (!general) mx *= p.scale_log2;  // the general path already works in scaled, biased units
       }
       if (prof_on) p.prof[j * 8 + 1] = clock64();
       const float m_new = fmaxf(m_run, mx);
@@ -347,13 +345,22 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           if (c + 1 < 4) tmem_ld_32x32(tS + lane_off + (c + 1) * 32, r[(c + 1) & 1]);
           uint32_t packed[16];
           if (need_mask) {
+            const float off0 = bias0 - m_use;
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
               const int col = c * 32 + 2 * i;
-              const float a = (col < limit && col >= lo)
-                                  ? exp2f(fmaf(__uint_as_float(r[c & 1][2 * i]), p.scale_log2, slope2 * (kpos0 + col) - m_use)) : 0.f;
-              const float bb = (col + 1 < limit && col + 1 >= lo)
-                                   ? exp2f(fmaf(__uint_as_float(r[c & 1][2 * i + 1]), p.scale_log2, slope2 * (kpos0 + col + 1) - m_use)) : 0.f;
+              float a, bb;
+              if (GEN && general) {
+                a = (col < limit && col >= lo)
+                        ? exp2f(fmaf(__uint_as_float(r[c & 1][2 * i]), p.scale_log2,
+                                     fmaf(slope2, static_cast<float>(c * 32 + 2 * i), off0))) : 0.f;
+                bb = (col + 1 < limit && col + 1 >= lo)
+                         ? exp2f(fmaf(__uint_as_float(r[c & 1][2 * i + 1]), p.scale_log2,
+                                      fmaf(slope2, static_cast<float>(c * 32 + 2 * i + 1), off0))) : 0.f;
+              } else {
+                a = (col < limit) ? exp2f(fmaf(__uint_as_float(r[c & 1][2 * i]), p.scale_log2, -m_use)) : 0.f;
+                bb = (col + 1 < limit) ? exp2f(fmaf(__uint_as_float(r[c & 1][2 * i + 1]), p.scale_log2, -m_use)) : 0.f;
+              }
               ps4[i & 3] += a + bb;
               float da = a, db = bb;
               if (DROP) {
@@ -367,16 +374,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           } else {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-              const uint64_t x2 = f2_fma(f2_pack_bits(r[c & 1][2 * i], r[c & 1][2 * i + 1]), scale2, neg_m2);
-              float a, bb;
-              if (MSQ_ATTN_FMA_EXP && (i & 1)) {
-                exp2_fma_pair(x2, a, bb);  // every second pair on the FMA pipe
-              } else {
-                float x0, x1;
-                f2_unpack(x2, x0, x1);
-                a = exp2f(x0);
-                bb = exp2f(x1);
-              }
+              float x0, x1;
+              f2_unpack(f2_fma(f2_pack_bits(r[c & 1][2 * i], r[c & 1][2 * i + 1]), scale2, neg_m2), x0, x1);
+              const float a = exp2f(x0), bb = exp2f(x1);
               ps2[i & 1] = f2_add(ps2[i & 1], f2_pack(a, bb));  // the normaliser uses the undropped weights
               float da = a, db = bb;
               if (DROP) {
@@ -408,7 +408,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (ok) {
       const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
       uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + static_cast<long long>(b) * p.o_batch_stride +
-                    static_cast<long long>(q_idx < p.T ? q_idx : 0) * p.o_row_stride + h * p.hd;
+                    static_cast<long long>(q_idx < p.T ? q_idx : 0) * p.o_row_stride + h * hd;
       uint32_t r[2][32];
       tmem_ld_32x32(tO + lane_off, r[0]);
 #pragma unroll
@@ -418,7 +418,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (q_idx < p.T) {
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
-            if (c * 32 + v * 8 >= p.hd) break;  // padded columns of a head size below HD
+            if (GEN && c * 32 + v * 8 >= hd) break;  // padded columns of a head size below HD
             uint4 ov;
             ov.x = pack2<BF16>(__uint_as_float(r[c & 1][v * 8 + 0]) * inv_l, __uint_as_float(r[c & 1][v * 8 + 1]) * inv_l);
             ov.y = pack2<BF16>(__uint_as_float(r[c & 1][v * 8 + 2]) * inv_l, __uint_as_float(r[c & 1][v * 8 + 3]) * inv_l);
@@ -477,7 +477,7 @@ struct BwdCfg {
   static constexpr bool DQ_ALIASES_S = (HD != 64);
 };
 
-template <int HD, bool BF16, bool DROP>
+template <int HD, bool BF16, bool DROP, bool GEN>
 __global__ void __launch_bounds__(ATT_BWD_THREADS, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
@@ -513,9 +513,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int m_start = p.causal ? nb : 0;
   // Document starts never decrease along the sequence: once the first row of a q tile starts after the last key of
   // this block, that tile and every later one see none of its keys.
-  const int* dstart = p.doc_start ? p.doc_start + static_cast<long long>(b) * p.T : nullptr;
+  const int* dstart = (GEN && p.doc_start) ? p.doc_start + static_cast<long long>(b) * p.T : nullptr;
+  const int hd = GEN ? p.hd : HD;
   int m_end = n_q;
-  if (dstart) {
+  if (GEN && dstart) {
     const int kv_last = nb * TILE + TILE - 1;
     for (int m = m_start + 1; m < n_q; ++m)
       if (dstart[min(m * TILE, p.T - 1)] > kv_last) { m_end = m; break; }
@@ -554,8 +555,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_expect_tx(kv_full, 2 * Cfg::TILE_BYTES);
 #pragma unroll
       for (int c = 0; c < Cfg::CHUNKS; ++c) {
-        tma_load_4d(sK + c * Cfg::CHUNK_BYTES, &tmK, kv_full, c * 64, h, nb * TILE, b);
-        tma_load_4d(sV + c * Cfg::CHUNK_BYTES, &tmV, kv_full, c * 64, h, nb * TILE, b);
+        attn_load_box(sK + c * Cfg::CHUNK_BYTES, &tmK, kv_full, !GEN, hd, c, h, nb * TILE, b);
+        attn_load_box(sV + c * Cfg::CHUNK_BYTES, &tmV, kv_full, !GEN, hd, c, h, nb * TILE, b);
       }
       int stage = 0;
       uint32_t phase = 0;
@@ -567,10 +568,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         mbar_expect_tx(&qdo_full[stage], 2 * Cfg::TILE_BYTES);
 #pragma unroll
         for (int c = 0; c < Cfg::CHUNKS; ++c) {
-          tma_load_4d(sQ + stage * Cfg::TILE_BYTES + c * Cfg::CHUNK_BYTES, &tmQ, &qdo_full[stage], c * 64, h,
-                      m * TILE, b);
-          tma_load_4d(sDO + stage * Cfg::TILE_BYTES + c * Cfg::CHUNK_BYTES, &tmDO, &qdo_full[stage], c * 64, h,
-                      m * TILE, b);
+          attn_load_box(sQ + stage * Cfg::TILE_BYTES + c * Cfg::CHUNK_BYTES, &tmQ, &qdo_full[stage], !GEN, hd, c, h,
+                        m * TILE, b);
+          attn_load_box(sDO + stage * Cfg::TILE_BYTES + c * Cfg::CHUNK_BYTES, &tmDO, &qdo_full[stage], !GEN, hd, c, h,
+                        m * TILE, b);
         }
         if (++stage == QS) { stage = 0; phase ^= 1; }
       }
@@ -703,8 +704,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (lane == 0) {
           const int row0 = (m_start + dit) * TILE + quarter * 32;
           if (row0 < p.T) {  // rows past T inside a box are dropped by the copy engine
-            tma_reduce_add_4d(&tmDQ, boxes, 0, h, row0, b);
-            if (p.hd > 32) tma_reduce_add_4d(&tmDQ, boxes + 4096, 32, h, row0, b);
+            attn_reduce_box(&tmDQ, boxes, !GEN, hd, 0, h, row0, b);
+            if (hd > 32) attn_reduce_box(&tmDQ, boxes + 4096, !GEN, hd, 32, h, row0, b);
           }
           bulk_commit_group();
         }
@@ -757,8 +758,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (lane == 0) {
           // a box that starts in the padded columns of a smaller head is dropped; one that straddles the end
           // of the head is clipped by the copy engine
-          if (rows_in_range && half * (HD / 2) + c * 32 < p.hd)
-            tma_reduce_add_4d(&tmDQ, stage_buf, half * (HD / 2) + c * 32, h, dm * TILE + quarter * 32, b);
+          if (rows_in_range && half * (HD / 2) + c * 32 < hd)
+            attn_reduce_box(&tmDQ, stage_buf, !GEN, hd, half * (HD / 2) + c * 32, h, dm * TILE + quarter * 32, b);
           bulk_commit_group();
         }
         ++staged;
@@ -774,12 +775,12 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       int limit = p.T - nb * TILE;
       if (p.causal) limit = min(limit, q_idx - nb * TILE + 1);
       limit = q_ok ? max(0, min(limit, TILE)) : 0;
-      const int lo = (dstart && q_ok) ? dstart[q_idx] - nb * TILE : 0;  // keys before the row's document are masked
-      const float slope2 = p.alibi_slopes ? p.alibi_slopes[h] * LOG2E : 0.f;
+      const int lo = (GEN && dstart && q_ok) ? dstart[q_idx] - nb * TILE : 0;  // keys before the row's document are masked
+      const float slope2 = (GEN && p.alibi_slopes) ? p.alibi_slopes[h] * LOG2E : 0.f;
       // uniform over the warp: only diagonal blocks, ragged tails (rows or columns past T), blocks cut by a
       // document start and ALiBi need the per-element path
-      const bool need_mask = (p.causal && m == nb) || ((m + 1) * TILE > p.T) || ((nb + 1) * TILE > p.T) ||
-                             p.alibi_slopes != nullptr || __any_sync(0xffffffffu, lo > 0);
+      const bool general = GEN && (p.alibi_slopes != nullptr || (dstart != nullptr && __any_sync(0xffffffffu, lo > 0)));
+      const bool need_mask = (p.causal && m == nb) || ((m + 1) * TILE > p.T) || ((nb + 1) * TILE > p.T) || general;
       const bool prof_on = p.prof != nullptr && row == 0 && half == 0 && blockIdx.x == 0 && blockIdx.y == 0 &&
                            blockIdx.z == 0 && it < 32;
       if (prof_on) p.prof[256 + it * 8 + 0] = clock64();
@@ -813,13 +814,16 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 ks1 = k1 ? p.inv_keep : 0.f;
               }
               const int col = cbase + 2 * i;
-              if (col < limit && col >= lo) {
-                p0 = exp2f(fmaf(__uint_as_float(s[2 * i]), scale_log2, slope2 * (nb * TILE + col) - lse2));
+              // plain causal / ragged blocks: lo <= 0 for every row and the bias is zero, so the extra terms fold away
+              const float b0 = (GEN && general) ? fmaf(slope2, static_cast<float>(nb * TILE + col), -lse2) : -lse2;
+              const float b1 = (GEN && general) ? b0 + slope2 : -lse2;
+              if (col < limit && (!(GEN && general) || col >= lo)) {
+                p0 = exp2f(fmaf(__uint_as_float(s[2 * i]), scale_log2, b0));
                 d0 = p0 * (ks0 * __uint_as_float(dp[2 * i]) - delta) * p.scale;
                 p0 *= ks0;
               }
-              if (col + 1 < limit && col + 1 >= lo) {
-                p1 = exp2f(fmaf(__uint_as_float(s[2 * i + 1]), scale_log2, slope2 * (nb * TILE + col + 1) - lse2));
+              if (col + 1 < limit && (!(GEN && general) || col + 1 >= lo)) {
+                p1 = exp2f(fmaf(__uint_as_float(s[2 * i + 1]), scale_log2, b1));
                 d1 = p1 * (ks1 * __uint_as_float(dp[2 * i + 1]) - delta) * p.scale;
                 p1 *= ks1;
               }
@@ -832,16 +836,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             const uint64_t sc2 = f2_pack(p.scale, p.scale), nds2 = f2_pack(nds, nds);
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-              float d0, d1, p0, p1;
-              const uint64_t x2 = f2_fma(f2_pack_bits(s[2 * i], s[2 * i + 1]), sl2, nl2);
-              if (MSQ_ATTN_FMA_EXP && (i & 1)) {
-                exp2_fma_pair(x2, p0, p1);  // every second pair on the FMA pipe
-              } else {
-                float x0, x1;
-                f2_unpack(x2, x0, x1);
-                p0 = exp2f(x0);
-                p1 = exp2f(x1);
-              }
+              float x0, x1, d0, d1;
+              f2_unpack(f2_fma(f2_pack_bits(s[2 * i], s[2 * i + 1]), sl2, nl2), x0, x1);
+              const float p0 = exp2f(x0), p1 = exp2f(x1);
               const uint64_t g = f2_fma(f2_pack_bits(dp[2 * i], dp[2 * i + 1]), sc2, nds2);
               f2_unpack(f2_mul(f2_pack(p0, p1), g), d0, d1);
               pp[c][i] = pack2<BF16>(p0, p1);
@@ -893,9 +890,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const bool kv_ok = kv_idx < p.T;
       const long long kv_row = kv_ok ? kv_idx : 0;
       uint16_t* dk = reinterpret_cast<uint16_t*>(p.dk) + static_cast<long long>(b) * p.dk_batch_stride +
-                     kv_row * p.dk_row_stride + h * p.hd + half * (HD / 2);
+                     kv_row * p.dk_row_stride + h * hd + half * (HD / 2);
       uint16_t* dv = reinterpret_cast<uint16_t*>(p.dv) + static_cast<long long>(b) * p.dv_batch_stride +
-                     kv_row * p.dv_row_stride + h * p.hd + half * (HD / 2);
+                     kv_row * p.dv_row_stride + h * hd + half * (HD / 2);
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {
         uint16_t* dst = which ? dv : dk;
@@ -908,7 +905,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           if (kv_ok) {
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
-              if (half * (HD / 2) + c * 32 + v * 8 >= p.hd) break;  // padded columns of a head size below HD
+              if (GEN && half * (HD / 2) + c * 32 + v * 8 >= hd) break;  // padded columns of a head size below HD
               uint4 ov;
               ov.x = pack2<BF16>(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
               ov.y = pack2<BF16>(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
@@ -972,8 +969,14 @@ attn_delta_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d
 // [B, T, H, hd] view with the given token / batch strides (elements) as a 4-D map (hd, H, T, B); box = 64 columns of
 // one head x 128 rows.  Columns past hd are outside the first dimension: loads fill them with zeros.
 static int make_tmap_bthd(CUtensorMap* out, const void* base, int B, int T, int H, int hd, long long row_stride,
-                          long long batch_stride, int bf16) {
+                          long long batch_stride, int bf16, bool four_d) {
   if ((reinterpret_cast<uintptr_t>(base) & 15) || ((row_stride * 2) & 15) || ((batch_stride * 2) & 15) || (hd & 7)) return -2;
+  if (!four_d) {  // plain instantiation: [B, T, H * hd] with all heads' columns in the first dimension
+    cuuint64_t dims3[3] = {static_cast<cuuint64_t>(H) * hd, static_cast<cuuint64_t>(T), static_cast<cuuint64_t>(B)};
+    cuuint64_t strides3[2] = {static_cast<cuuint64_t>(row_stride) * 2, static_cast<cuuint64_t>(batch_stride) * 2};
+    cuuint32_t box3[3] = {64u, static_cast<cuuint32_t>(TILE), 1u};
+    return encode_tiled_16bit(out, base, 3, dims3, strides3, box3, bf16) == CUDA_SUCCESS ? 0 : -3;
+  }
   cuuint64_t dims[4] = {static_cast<cuuint64_t>(hd), static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(T),
                         static_cast<cuuint64_t>(B)};
   cuuint64_t strides[3] = {static_cast<cuuint64_t>(hd) * 2, static_cast<cuuint64_t>(row_stride) * 2,
@@ -982,10 +985,10 @@ static int make_tmap_bthd(CUtensorMap* out, const void* base, int B, int T, int 
   return encode_tiled_16bit(out, base, 4, dims, strides, box, bf16) == CUDA_SUCCESS ? 0 : -3;
 }
 
-template <int HD, bool BF16, bool DROP>
+template <int HD, bool BF16, bool DROP, bool GEN>
 static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnFwdParams& p,
                       int B, cudaStream_t stream) {
-  auto kern = flash_fwd_kernel<HD, BF16, DROP>;
+  auto kern = flash_fwd_kernel<HD, BF16, DROP, GEN>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdCfg<HD>::SMEM) != cudaSuccess)
@@ -997,10 +1000,10 @@ static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
-template <int HD, bool BF16, bool DROP>
+template <int HD, bool BF16, bool DROP, bool GEN>
 static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
                       const CUtensorMap& tdq, const AttnBwdParams& p, int B, cudaStream_t stream) {
-  auto kern = flash_bwd_kernel<HD, BF16, DROP>;
+  auto kern = flash_bwd_kernel<HD, BF16, DROP, GEN>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg<HD>::SMEM) != cudaSuccess)
@@ -1050,9 +1053,10 @@ extern "C" int msq_flash_fwd(const void* q, const void* k, const void* v, long l
   if ((reinterpret_cast<uintptr_t>(out) & 15) || (o_rs & 7) || (o_bs & 7)) return -2;
   CUtensorMap tq, tk, tv;
   int rc;
-  if ((rc = make_tmap_bthd(&tq, q, B, T, H, HD, q_rs, q_bs, bf16))) return rc;
-  if ((rc = make_tmap_bthd(&tk, k, B, T, H, HD, k_rs, k_bs, bf16))) return rc;
-  if ((rc = make_tmap_bthd(&tv, v, B, T, H, HD, v_rs, v_bs, bf16))) return rc;
+  const bool gen = doc_start != nullptr || alibi_slopes != nullptr || (HD != 64 && HD != 128);
+  if ((rc = make_tmap_bthd(&tq, q, B, T, H, HD, q_rs, q_bs, bf16, gen))) return rc;
+  if ((rc = make_tmap_bthd(&tk, k, B, T, H, HD, k_rs, k_bs, bf16, gen))) return rc;
+  if ((rc = make_tmap_bthd(&tv, v, B, T, H, HD, v_rs, v_bs, bf16, gen))) return rc;
   AttnFwdParams p;
   p.out = out; p.o_row_stride = o_rs; p.o_batch_stride = o_bs; p.lse = lse;
   p.T = T; p.H = H; p.scale_log2 = scale * LOG2E; p.causal = causal; p.bf16 = bf16; p.status = status;
@@ -1060,11 +1064,13 @@ extern "C" int msq_flash_fwd(const void* q, const void* k, const void* v, long l
   p.hd = HD; p.doc_start = doc_start; p.alibi_slopes = alibi_slopes;
   if (!drop_params(dropout_p, p.drop_threshold16, p.inv_keep)) return -2;
   p.seed = seed;
-#define MSQ_FWD(HDV, BF) \
-  (p.drop_threshold16 ? launch_fwd<HDV, BF, true>(tq, tk, tv, p, B, stream) : launch_fwd<HDV, BF, false>(tq, tk, tv, p, B, stream))
+#define MSQ_FWD2(HDV, BF, GN) \
+  (p.drop_threshold16 ? launch_fwd<HDV, BF, true, GN>(tq, tk, tv, p, B, stream) : launch_fwd<HDV, BF, false, GN>(tq, tk, tv, p, B, stream))
+#define MSQ_FWD(HDV, BF) (gen ? MSQ_FWD2(HDV, BF, true) : MSQ_FWD2(HDV, BF, false))
   if (HD <= 64) return bf16 ? MSQ_FWD(64, true) : MSQ_FWD(64, false);
   return bf16 ? MSQ_FWD(128, true) : MSQ_FWD(128, false);
 #undef MSQ_FWD
+#undef MSQ_FWD2
 }
 
 // delta: fp32 [B, H, T] scratch (written here); dq_accum: fp32 [B, T, H*HD], zeroed by the caller.
@@ -1083,20 +1089,28 @@ extern "C" int msq_flash_bwd(const void* q, const void* k, const void* v, const 
   if ((dk_rs & 7) || (dk_bs & 7) || (dv_rs & 7) || (dv_bs & 7)) return -2;
   CUtensorMap tq, tk, tv, tdo;
   int rc;
-  if ((rc = make_tmap_bthd(&tq, q, B, T, H, HD, q_rs, q_bs, bf16))) return rc;
-  if ((rc = make_tmap_bthd(&tk, k, B, T, H, HD, k_rs, k_bs, bf16))) return rc;
-  if ((rc = make_tmap_bthd(&tv, v, B, T, H, HD, v_rs, v_bs, bf16))) return rc;
-  if ((rc = make_tmap_bthd(&tdo, d_out, B, T, H, HD, do_rs, do_bs, bf16))) return rc;
+  const bool gen = doc_start != nullptr || alibi_slopes != nullptr || (HD != 64 && HD != 128);
+  if ((rc = make_tmap_bthd(&tq, q, B, T, H, HD, q_rs, q_bs, bf16, gen))) return rc;
+  if ((rc = make_tmap_bthd(&tk, k, B, T, H, HD, k_rs, k_bs, bf16, gen))) return rc;
+  if ((rc = make_tmap_bthd(&tv, v, B, T, H, HD, v_rs, v_bs, bf16, gen))) return rc;
+  if ((rc = make_tmap_bthd(&tdo, d_out, B, T, H, HD, do_rs, do_bs, bf16, gen))) return rc;
   CUtensorMap tdq;
   {
     // fp32 [B, T, H, HD] accumulator as a 4-D map (HD, H, T, B), reduced into by 32-row x 32-column boxes of one head
     if (reinterpret_cast<uintptr_t>(dq_accum) & 15) return -2;
     const cuuint64_t cols = static_cast<cuuint64_t>(H) * HD;
-    cuuint64_t dims[4] = {static_cast<cuuint64_t>(HD), static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(T),
-                          static_cast<cuuint64_t>(B)};
-    cuuint64_t strides[3] = {static_cast<cuuint64_t>(HD) * 4, cols * 4, cols * 4 * static_cast<cuuint64_t>(T)};
-    cuuint32_t box[4] = {32u, 1u, 32u, 1u};
-    if (encode_tiled(&tdq, dq_accum, 4, dims, strides, box, CU_TENSOR_MAP_DATA_TYPE_FLOAT32) != CUDA_SUCCESS) return -3;
+    if (!gen) {
+      cuuint64_t dims3[3] = {cols, static_cast<cuuint64_t>(T), static_cast<cuuint64_t>(B)};
+      cuuint64_t strides3[2] = {cols * 4, cols * 4 * static_cast<cuuint64_t>(T)};
+      cuuint32_t box3[3] = {32u, 32u, 1u};
+      if (encode_tiled(&tdq, dq_accum, 3, dims3, strides3, box3, CU_TENSOR_MAP_DATA_TYPE_FLOAT32) != CUDA_SUCCESS) return -3;
+    } else {
+      cuuint64_t dims[4] = {static_cast<cuuint64_t>(HD), static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(T),
+                            static_cast<cuuint64_t>(B)};
+      cuuint64_t strides[3] = {static_cast<cuuint64_t>(HD) * 4, cols * 4, cols * 4 * static_cast<cuuint64_t>(T)};
+      cuuint32_t box[4] = {32u, 1u, 32u, 1u};
+      if (encode_tiled(&tdq, dq_accum, 4, dims, strides, box, CU_TENSOR_MAP_DATA_TYPE_FLOAT32) != CUDA_SUCCESS) return -3;
+    }
   }
   {
     const int lpg = HD <= 64 ? 8 : 16;  // lanes per (b, t, h) row
@@ -1122,10 +1136,12 @@ extern "C" int msq_flash_bwd(const void* q, const void* k, const void* v, const 
   p.hd = HD; p.doc_start = doc_start; p.alibi_slopes = alibi_slopes;
   if (!drop_params(dropout_p, p.drop_threshold16, p.inv_keep)) return -2;
   p.seed = seed;
-#define MSQ_BWD(HDV, BF) \
-  (p.drop_threshold16 ? launch_bwd<HDV, BF, true>(tq, tk, tv, tdo, tdq, p, B, stream) \
-                      : launch_bwd<HDV, BF, false>(tq, tk, tv, tdo, tdq, p, B, stream))
+#define MSQ_BWD2(HDV, BF, GN) \
+  (p.drop_threshold16 ? launch_bwd<HDV, BF, true, GN>(tq, tk, tv, tdo, tdq, p, B, stream) \
+                      : launch_bwd<HDV, BF, false, GN>(tq, tk, tv, tdo, tdq, p, B, stream))
+#define MSQ_BWD(HDV, BF) (gen ? MSQ_BWD2(HDV, BF, true) : MSQ_BWD2(HDV, BF, false))
   if (HD <= 64) return bf16 ? MSQ_BWD(64, true) : MSQ_BWD(64, false);
   return bf16 ? MSQ_BWD(128, true) : MSQ_BWD(128, false);
 #undef MSQ_BWD
+#undef MSQ_BWD2
 }

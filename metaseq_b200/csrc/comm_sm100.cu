@@ -242,58 +242,85 @@ comm_reduce_scatter_pull_kernel(const void* mc_shard, PeerPtrs src, long long sr
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   float ss = 0.f;
   bool bad = false;
-  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
-    float acc[8];
+  // Four independent 16-byte requests per thread are in flight before the first result is used: a request that
+  // crosses the switch takes microseconds, so the link is filled by the number of requests outstanding.
+  constexpr int U = 4;
+  for (long long i0 = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < nvec; i0 += U * stride) {
+    uint32_t w[U][4];
+    float acc[U][8];
     if (MC) {
-      const uint8_t* a = static_cast<const uint8_t*>(mc_shard) + (i << 4);
-      uint32_t w[4];
-      if (BF16)
-        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
-                     : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "l"(a) : "memory");
-      else
-        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
-                     : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "l"(a) : "memory");
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 f = unpack2<BF16>(w[j]);
-        acc[2 * j] = f.x;
-        acc[2 * j + 1] = f.y;
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < nvec) {
+          const uint8_t* a = static_cast<const uint8_t*>(mc_shard) + (i << 4);
+          if (BF16)
+            asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(w[u][0]), "=r"(w[u][1]), "=r"(w[u][2]), "=r"(w[u][3]) : "l"(a) : "memory");
+          else
+            asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(w[u][0]), "=r"(w[u][1]), "=r"(w[u][2]), "=r"(w[u][3]) : "l"(a) : "memory");
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack2<BF16>(w[u][j]);
+          acc[u][2 * j] = f.x;
+          acc[u][2 * j + 1] = f.y;
+        }
       }
     } else {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[u][j] = 0.f;
       for (int s = 0; s < world; ++s) {
         const int peer = (rank + s) % world;  // own slice first, then round the ring
         const uint4* base = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(src.p[peer]) + src_off_bytes);
-        uint4 v;
-        asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(base + i) : "memory");
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 f = unpack2<BF16>(w[j]);
-          acc[2 * j] += f.x;
-          acc[2 * j + 1] += f.y;
+        for (int u = 0; u < U; ++u) {
+          const long long i = i0 + u * stride;
+          if (i < nvec)
+            asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(w[u][0]), "=r"(w[u][1]), "=r"(w[u][2]), "=r"(w[u][3]) : "l"(base + i) : "memory");
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (i0 + u * stride < nvec) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 f = unpack2<BF16>(w[u][j]);
+              acc[u][2 * j] += f.x;
+              acc[u][2 * j + 1] += f.y;
+            }
+          }
         }
       }
     }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      acc[j] *= scale;
-      ss += acc[j] * acc[j];
-      bad |= !isfinite(acc[j]);
-    }
-    if (OUT32) {
-      float4* o = reinterpret_cast<float4*>(out) + 2 * i;
-      o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-      o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
-    } else {
-      uint4 o;
-      o.x = pack2<BF16>(acc[0], acc[1]);
-      o.y = pack2<BF16>(acc[2], acc[3]);
-      o.z = pack2<BF16>(acc[4], acc[5]);
-      o.w = pack2<BF16>(acc[6], acc[7]);
-      reinterpret_cast<uint4*>(out)[i] = o;
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i >= nvec) continue;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        acc[u][j] *= scale;
+        ss += acc[u][j] * acc[u][j];
+        bad |= !isfinite(acc[u][j]);
+      }
+      if (OUT32) {
+        float4* o = reinterpret_cast<float4*>(out) + 2 * i;
+        o[0] = make_float4(acc[u][0], acc[u][1], acc[u][2], acc[u][3]);
+        o[1] = make_float4(acc[u][4], acc[u][5], acc[u][6], acc[u][7]);
+      } else {
+        uint4 o;
+        o.x = pack2<BF16>(acc[u][0], acc[u][1]);
+        o.y = pack2<BF16>(acc[u][2], acc[u][3]);
+        o.z = pack2<BF16>(acc[u][4], acc[u][5]);
+        o.w = pack2<BF16>(acc[u][6], acc[u][7]);
+        reinterpret_cast<uint4*>(out)[i] = o;
+      }
     }
   }
   __shared__ float red[32];

@@ -220,6 +220,9 @@ class PeerComm:
         self.rank, self.world = self.heap.rank, self.heap.world
         self.chunk_bytes = int(chunk_bytes)
         self.max_ctas = int(max_ctas)
+        # CTAs of the kernels that move bulk data through the switch (tunable for measurements)
+        self.ag_ctas = int(os.environ.get("MSQ_COMM_AG_CTAS", 2 * self.max_ctas))
+        self.pull_ctas = int(os.environ.get("MSQ_COMM_PULL_CTAS", 8 * self.max_ctas))
         self._bufs: Dict[int, _Gathered] = {}
         self._range_cache = {}
         self._barrier_base = self.heap.alloc_flags(self.world)
@@ -316,7 +319,7 @@ class PeerComm:
                 rc = _lib.kernels().msq_comm_allgather_multimem(
                     ctypes.c_void_p(self.heap.multicast_ptr + meta.offset), _lib.ptr(local), meta.shard_bytes,
                     meta.chunk_bytes, self.rank, self.world, self.heap.ptr_array, meta.flag_base, meta.ag_epoch,
-                    self.max_ctas, self._status(), _lib.stream_ptr())
+                    self.ag_ctas, self._status(), _lib.stream_ptr())
             else:
                 rc = _lib.kernels().msq_comm_allgather_push(
                     self.heap.ptr_array, meta.offset, _lib.ptr(local), meta.shard_bytes, meta.chunk_bytes, self.rank,
@@ -351,7 +354,7 @@ class PeerComm:
                 rc = lib.msq_comm_allgather_multimem(ctypes.c_void_p(self.heap.multicast_ptr + meta.offset),
                                                      _lib.ptr(local), meta.shard_bytes, meta.chunk_bytes, self.rank,
                                                      self.world, self.heap.ptr_array, meta.flag_base, meta.ag_epoch,
-                                                     self.max_ctas, status, sp)
+                                                     self.ag_ctas, status, sp)
                 meta.push_event = True
             else:
                 rc = lib.msq_comm_allgather_push(self.heap.ptr_array, meta.offset, _lib.ptr(local), meta.shard_bytes,
@@ -456,7 +459,7 @@ class PeerComm:
                 float(scale), _lib.ptr(shard), int(shard.dtype == torch.float32), int(meta.dtype == torch.bfloat16),
                 _lib.ptr(self.grad_sumsq) if accumulate_norm else None,
                 _lib.ptr(self.overflow) if accumulate_norm else None,
-                self.heap.flags_ptr, meta.rs_flag_base, meta.rs_epoch, 8 * self.max_ctas, self._status(), sp)
+                self.heap.flags_ptr, meta.rs_flag_base, meta.rs_epoch, self.pull_ctas, self._status(), sp)
             self._check(rc, "msq_comm_reduce_scatter_pull")
             if stream is not None:
                 full_grad.record_stream(stream)
