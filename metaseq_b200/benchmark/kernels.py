@@ -178,6 +178,16 @@ def main(argv=None):
         fl = 2.0 * M * N * K
         report(f"gemm_fwd_{name}", fl, 0, lambda: F.gemm(a, w, bias=bias, out=out),
                lambda: torch.addmm(bias, a, w.t(), out=out))
+        if name == "logits":
+            # the same product with the softmax pieces of every row left by the epilogue, and the loss built on them
+            report("gemm_rowstats_logits", fl, 0, lambda: F.gemm_with_row_stats(a, w), None)
+            lg, st = F.gemm_with_row_stats(a, w)
+            tgt_ce = torch.randint(0, N, (M,), device=dev)
+            if st is not None:
+                report("cross_entropy_from_row_stats", 0, 2.0 * M * N * 2,
+                       lambda: F.cross_entropy_from_row_stats(lg, tgt_ce, 1, 1.0, st),
+                       lambda: F.cross_entropy_fwd_bwd(lg, tgt_ce, 1, 1.0, True) if N * 2 <= 200 * 1024 else None)
+            del lg, st
         report(f"gemm_dgrad_{name}", fl, 0, lambda: F.gemm(dy, w, b_mn=True, out=dx),
                lambda: torch.matmul(dy, w, out=dx))
         report(f"gemm_wgrad_{name}", fl, 0, lambda: F.gemm(dy, a, a_mn=True, b_mn=True, out=dw),
