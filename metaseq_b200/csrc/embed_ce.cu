@@ -581,6 +581,65 @@ colsum_kernel(const uint16_t* __restrict__ x, long long ld, int rows, int N, flo
   }
 }
 
+// One-launch form of the bias gradient: the same slice sums and fp32 atomics as colsum_kernel, after which the CTA
+// that arrives last at a column block (a ticket per block) turns the block's fp32 sums into the 16-bit output
+// (added to it when `accumulate`) and leaves accumulator and ticket at zero for the next call, so the scratch needs
+// no fill and the result no separate conversion pass.
+template <bool BF16>
+__global__ void __launch_bounds__(256)
+colsum_direct_kernel(const uint16_t* __restrict__ x, long long ld, int rows, int N, float* __restrict__ acc,
+                     unsigned* __restrict__ tickets, uint16_t* __restrict__ out, int accumulate, int rows_per_cta) {
+  __shared__ float sm[8][256 + 8];
+  __shared__ bool last;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int col = blockIdx.x * 256 + tx * 8;
+  const int r0 = blockIdx.y * rows_per_cta;
+  const int r1 = min(rows, r0 + rows_per_cta);
+  float s[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) s[j] = 0.f;
+  if (col < N) {
+    for (int r = r0 + ty; r < r1; r += 8) {
+      const uint4 a = *reinterpret_cast<const uint4*>(x + static_cast<long long>(r) * ld + col);
+      const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 t = unpack2<BF16>(w[j]);
+        s[2 * j] += t.x;
+        s[2 * j + 1] += t.y;
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) sm[ty][tx * 8 + j] = s[j];
+  __syncthreads();
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  if (c < N) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += sm[k][threadIdx.x];
+    atomicAdd(acc + c, t);
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) last = atomicAdd(tickets + blockIdx.x, 1u) == gridDim.y - 1;
+  __syncthreads();
+  if (!last) return;
+  __threadfence();
+  if (c < N) {
+    float t = __ldcg(acc + c);
+    if (accumulate) {
+      const uint16_t prev = out[c];
+      t += BF16 ? __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(&prev))
+                : __half2float(*reinterpret_cast<const __half*>(&prev));
+    }
+    if (BF16) *reinterpret_cast<__nv_bfloat16*>(out + c) = __float2bfloat16(t);
+    else *reinterpret_cast<__half*>(out + c) = __float2half(t);
+    acc[c] = 0.f;
+  }
+  if (threadIdx.x == 0) tickets[blockIdx.x] = 0;
+}
+
 }  // namespace msq
 
 extern "C" int msq_embed_fwd(const long long* tokens, const long long* positions, const void* tok_w,
@@ -809,5 +868,24 @@ extern "C" int msq_colsum(const void* x, long long ld, int rows, int N, float* a
   dim3 grid(gx, gy);
   if (bf16) colsum_kernel<true><<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(x), ld, rows, N, acc, rows_per);
   else colsum_kernel<false><<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(x), ld, rows, N, acc, rows_per);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// out16[n] (+)= column sums of x[rows, N] in one launch.  `acc` (N floats) and `tickets` ((N + 255) / 256 words) are
+// scratch that must be zero before the first call; every call leaves them zero.  Calls that share scratch must not
+// overlap on the GPU.
+extern "C" int msq_colsum_direct(const void* x, long long ld, int rows, int N, float* acc, unsigned* tickets, void* out16,
+                                 int accumulate, int bf16, cudaStream_t stream) {
+  using namespace msq;
+  if (rows <= 0 || N <= 0) return 0;
+  if ((N & 7) || (ld & 7)) return -2;
+  const int gx = (N + 255) / 256;
+  int gy = (148 * 8 + gx - 1) / gx;
+  int rows_per = (rows + gy - 1) / gy;
+  rows_per = (rows_per + 7) / 8 * 8;
+  gy = (rows + rows_per - 1) / rows_per;
+  dim3 grid(gx, gy);
+  if (bf16) colsum_direct_kernel<true><<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(x), ld, rows, N, acc, tickets, static_cast<uint16_t*>(out16), accumulate, rows_per);
+  else colsum_direct_kernel<false><<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(x), ld, rows, N, acc, tickets, static_cast<uint16_t*>(out16), accumulate, rows_per);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

@@ -152,6 +152,7 @@ _OPTIONAL = {
     "msq_vp_ce_partial": [P, L, P, P, I, I, L, I, P],
     "msq_vp_ce_finish": [P, L, P, P, I, P, I, I, L, L, F, I, P],
     "msq_gemm2_tiles_n": [I],
+    "msq_colsum_direct": [P, L, I, I, P, P, P, I, I, P],
     "msq_comm_words_exchange": [P, L, P, P, L, I, I, P, P, P, I, P, P],
     "msq_comm_reduce_scatter_pull": [P, P, L, L, I, I, F, P, I, I, P, P, P, L, ctypes.c_uint, I, P, P],
     "msq_comm_allgather_multimem": [P, P, L, I, I, I, P, L, ctypes.c_uint, I, P, P],

@@ -900,9 +900,27 @@ def sample_top_p(lprobs, top_p, uniform=None):
 
 
 # --------------------------------------------------------------------- colsum
+_COLSUM_SCRATCH: dict = {}
+
+
 def colsum(x2d, out16=None, accumulate=False):
     """Column sums of ``[rows, N]`` (bias gradient), fp32 accumulation."""
     rows, N = x2d.shape
+    if out16 is not None and use_kernels(x2d) and N % 8 == 0 and x2d.stride(1) == 1 and x2d.stride(0) % 8 == 0 \
+            and out16.is_contiguous() and out16.dtype == x2d.dtype:
+        # one launch: partial sums by fp32 atomics into a persistent scratch that the kernel itself turns into the
+        # 16-bit result and leaves zeroed (one scratch per device, stream and width)
+        key = (x2d.device.index or 0, torch.cuda.current_stream(x2d.device).cuda_stream, N)
+        scratch = _COLSUM_SCRATCH.get(key)
+        if scratch is None:
+            scratch = (torch.zeros(N, dtype=torch.float32, device=x2d.device),
+                       torch.zeros((N + 255) // 256, dtype=torch.int32, device=x2d.device))
+            _COLSUM_SCRATCH[key] = scratch
+        rc = _lib.kernels().msq_colsum_direct(_lib.ptr(x2d), x2d.stride(0), rows, N, _lib.ptr(scratch[0]),
+                                              _lib.ptr(scratch[1]), _lib.ptr(out16), int(accumulate), _bf(x2d),
+                                              _lib.stream_ptr())
+        _lib.check_rc(rc, "msq_colsum_direct")
+        return out16
     if use_kernels(x2d) and N % 8 == 0 and x2d.stride(1) == 1 and x2d.stride(0) % 8 == 0:
         acc = torch.zeros(N, dtype=torch.float32, device=x2d.device)
         rc = _lib.kernels().msq_colsum(_lib.ptr(x2d), x2d.stride(0), rows, N, _lib.ptr(acc), _bf(x2d),
