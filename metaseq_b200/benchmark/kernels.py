@@ -60,6 +60,9 @@ def time_op(fn, warmup=3, iters=10):
     times = []
     for _ in range(iters):
         flush_l2()
+        # a bounded device-side delay (about a millisecond) lets the host enqueue fn() before the start event runs,
+        # so an op with a long host path (allocations, tensor-map encoding) is not timed with the GPU idle
+        torch.cuda._sleep(1_500_000)
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record()
         fn()

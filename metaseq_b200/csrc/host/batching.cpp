@@ -3,6 +3,8 @@
 //
 //  * msq_batch_by_size        greedy token-budget batching (the reference's Cython
 //                             batch_by_size_vec: metaseq/data/data_utils_fast.pyx:20-103)
+//  * msq_batch_fixed_shapes   batching against a list of allowed (rows, longest) shapes
+//                             (batch_fixed_shapes_fast: metaseq/data/data_utils_fast.pyx:124-172)
 //  * msq_token_block_slices   cut a corpus of variable-length items into blocks for the
 //                             break modes none / complete / complete_doc / eos
 //                             (metaseq/data/token_block_utils_fast.pyx:52-105)
@@ -39,6 +41,35 @@ long long msq_batch_by_size(const int64_t* num_tokens, long long n, long long ma
       for (long long j = start; j <= i; ++j) longest = std::max(longest, num_tokens[j]);
     }
     ++rows;
+  }
+  if (rows > 0) batch_ends[nb++] = n;
+  return nb;
+}
+
+// shapes[2 * s] = rows, shapes[2 * s + 1] = longest element allowed by shape s.  The open batch grows, in iteration
+// order, while some shape holds it (rows and longest element both within the shape); the element that fits no shape
+// together with the open batch closes it and opens the next one.  An element longer than every shape ends up alone.
+// Writes the exclusive end position of every batch and returns their number.
+long long msq_batch_fixed_shapes(const int64_t* num_tokens, long long n, const int64_t* shapes, long long n_shapes,
+                                 int64_t* batch_ends) {
+  long long nb = 0, rows = 0;
+  int64_t longest = 0;
+  // best[r] = the longest element that a batch of r rows may contain (0: no shape has r rows)
+  int64_t max_rows = 0;
+  for (long long s = 0; s < n_shapes; ++s) max_rows = std::max(max_rows, shapes[2 * s]);
+  std::vector<int64_t> best(static_cast<size_t>(max_rows) + 2, 0);
+  for (long long s = 0; s < n_shapes; ++s)
+    for (int64_t r = 1; r <= shapes[2 * s]; ++r) best[r] = std::max(best[r], shapes[2 * s + 1]);
+  for (long long i = 0; i < n; ++i) {
+    const int64_t cand = std::max(longest, num_tokens[i]);
+    const bool fits = rows + 1 <= max_rows && cand <= best[rows + 1];
+    if (!fits && rows > 0) {
+      batch_ends[nb++] = i;
+      rows = 0;
+      longest = 0;
+    }
+    ++rows;
+    longest = std::max(longest, num_tokens[i]);
   }
   if (rows > 0) batch_ends[nb++] = n;
   return nb;

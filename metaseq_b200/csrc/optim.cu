@@ -86,7 +86,19 @@ struct SumsqTensor {
   long long first_block;  // of a table with count + 1 entries; the last entry holds the total block count
 };
 
-template <int DT>
+// INF = false: sum of squares; INF = true: largest magnitude (the inf-norm of the list; a non-finite element,
+// NaN included, gives +inf so that overflow checks see it).
+template <bool INF>
+__device__ __forceinline__ void norm_fold(float& acc, float v) {
+  if constexpr (INF) {
+    const float a = fabsf(v);
+    acc = fmaxf(acc, a <= 3.402823466e38f ? a : INFINITY);
+  } else {
+    acc += v * v;
+  }
+}
+
+template <int DT, bool INF>
 __global__ void __launch_bounds__(SUMSQ_THREADS)
 sumsq_multi_kernel(const SumsqTensor* __restrict__ table, int count, float* __restrict__ scratch,
                    unsigned* __restrict__ ticket, float* __restrict__ out, int accumulate) {
@@ -116,7 +128,10 @@ sumsq_multi_kernel(const SumsqTensor* __restrict__ table, int count, float* __re
       const float4* g4 = static_cast<const float4*>(t.g);
       for (long long i = tid; i < n4; i += stride) {
         const float4 v = g4[i];
-        acc += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        norm_fold<INF>(acc, v.x);
+        norm_fold<INF>(acc, v.y);
+        norm_fold<INF>(acc, v.z);
+        norm_fold<INF>(acc, v.w);
       }
       done = n4 << 2;
     } else {
@@ -128,17 +143,15 @@ sumsq_multi_kernel(const SumsqTensor* __restrict__ table, int count, float* __re
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const float2 f = unpack2<DT == 1>(w[j]);
-          acc += f.x * f.x + f.y * f.y;
+          norm_fold<INF>(acc, f.x);
+          norm_fold<INF>(acc, f.y);
         }
       }
       done = n8 << 3;
     }
   }
-  for (long long i = done + tid; i < t.n; i += stride) {
-    const float v = load_as_float<DT>(t.g, i);
-    acc += v * v;
-  }
-  const float total = block_sum(acc, red);
+  for (long long i = done + tid; i < t.n; i += stride) norm_fold<INF>(acc, load_as_float<DT>(t.g, i));
+  const float total = INF ? block_max(acc, red) : block_sum(acc, red);
   if (threadIdx.x == 0) {
     scratch[b] = total;
     __threadfence();
@@ -148,11 +161,76 @@ sumsq_multi_kernel(const SumsqTensor* __restrict__ table, int count, float* __re
   if (!s_last) return;
   __threadfence();
   float sum = 0.f;
-  for (int i = threadIdx.x; i < static_cast<int>(gridDim.x); i += blockDim.x) sum += __ldcg(scratch + i);
-  sum = block_sum(sum, red);
+  for (int i = threadIdx.x; i < static_cast<int>(gridDim.x); i += blockDim.x) {
+    const float v = __ldcg(scratch + i);
+    sum = INF ? fmaxf(sum, v) : sum + v;
+  }
+  sum = INF ? block_max(sum, red) : block_sum(sum, red);
   if (threadIdx.x == 0) {
-    out[0] = sum + (accumulate ? out[0] : 0.f);
+    if (INF) out[0] = accumulate ? fmaxf(sum, out[0]) : sum;
+    else out[0] = sum + (accumulate ? out[0] : 0.f);
     *ticket = 0;
+  }
+}
+
+// List form of an in-place scale (the reference's apex multi_tensor_scale, metaseq/modules/apex/multi_tensor_scale_kernel.cu):
+// every tensor of the table is multiplied by host_scale * (dev_scale ? dev_scale[0] : 1), the device factor being
+// e.g. a clip coefficient that the host never reads.
+template <int DT>
+__global__ void __launch_bounds__(SUMSQ_THREADS)
+scale_multi_kernel(const SumsqTensor* __restrict__ table, int count, const float* __restrict__ dev_scale,
+                   float host_scale) {
+  __shared__ int s_idx;
+  const int b = blockIdx.x;
+  if (threadIdx.x == 0) {
+    int lo = 0, hi = count - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (table[mid].first_block <= b) lo = mid; else hi = mid - 1;
+    }
+    s_idx = lo;
+  }
+  __syncthreads();
+  const SumsqTensor t = table[s_idx];
+  const float f = host_scale * (dev_scale ? dev_scale[0] : 1.f);
+  if (f == 1.f) return;
+  const long long nblk = table[s_idx + 1].first_block - t.first_block;
+  const long long tid = (static_cast<long long>(b) - t.first_block) * blockDim.x + threadIdx.x;
+  const long long stride = nblk * blockDim.x;
+  void* g = const_cast<void*>(t.g);
+  const bool aligned = (reinterpret_cast<uintptr_t>(g) & 15) == 0;
+  long long done = 0;
+  if (aligned) {
+    if constexpr (DT == 2) {
+      const long long n4 = t.n >> 2;
+      float4* g4 = static_cast<float4*>(g);
+      for (long long i = tid; i < n4; i += stride) {
+        float4 v = g4[i];
+        v.x *= f; v.y *= f; v.z *= f; v.w *= f;
+        g4[i] = v;
+      }
+      done = n4 << 2;
+    } else {
+      const long long n8 = t.n >> 3;
+      uint4* g8 = static_cast<uint4*>(g);
+      for (long long i = tid; i < n8; i += stride) {
+        const uint4 v = g8[i];
+        uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 x = unpack2<DT == 1>(w[j]);
+          w[j] = pack2<DT == 1>(x.x * f, x.y * f);
+        }
+        g8[i] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      done = n8 << 3;
+    }
+  }
+  for (long long i = done + tid; i < t.n; i += stride) {
+    const float v = load_as_float<DT>(g, i) * f;
+    if constexpr (DT == 0) static_cast<__half*>(g)[i] = __float2half(v);
+    else if constexpr (DT == 1) static_cast<__nv_bfloat16*>(g)[i] = __float2bfloat16(v);
+    else static_cast<float*>(g)[i] = v;
   }
 }
 
@@ -322,9 +400,36 @@ extern "C" int msq_sumsq_multi(const void* table, int count, int total_blocks, i
   using namespace msq;
   if (count <= 0 || total_blocks <= 0) return 0;
   const SumsqTensor* tb = static_cast<const SumsqTensor*>(table);
-  if (dtype == 0) sumsq_multi_kernel<0><<<total_blocks, SUMSQ_THREADS, 0, stream>>>(tb, count, scratch, ticket, out, accumulate);
-  else if (dtype == 1) sumsq_multi_kernel<1><<<total_blocks, SUMSQ_THREADS, 0, stream>>>(tb, count, scratch, ticket, out, accumulate);
-  else if (dtype == 2) sumsq_multi_kernel<2><<<total_blocks, SUMSQ_THREADS, 0, stream>>>(tb, count, scratch, ticket, out, accumulate);
+  if (dtype == 0) sumsq_multi_kernel<0, false><<<total_blocks, SUMSQ_THREADS, 0, stream>>>(tb, count, scratch, ticket, out, accumulate);
+  else if (dtype == 1) sumsq_multi_kernel<1, false><<<total_blocks, SUMSQ_THREADS, 0, stream>>>(tb, count, scratch, ticket, out, accumulate);
+  else if (dtype == 2) sumsq_multi_kernel<2, false><<<total_blocks, SUMSQ_THREADS, 0, stream>>>(tb, count, scratch, ticket, out, accumulate);
+  else return -2;
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// Same table and scratch as msq_sumsq_multi; out[0] = max |element| over the list (max with the old out[0] when
+// `accumulate`), +inf when an element is not finite.
+extern "C" int msq_absmax_multi(const void* table, int count, int total_blocks, int dtype, float* scratch,
+                                unsigned* ticket, float* out, int accumulate, cudaStream_t stream) {
+  using namespace msq;
+  if (count <= 0 || total_blocks <= 0) return 0;
+  const SumsqTensor* tb = static_cast<const SumsqTensor*>(table);
+  if (dtype == 0) sumsq_multi_kernel<0, true><<<total_blocks, SUMSQ_THREADS, 0, stream>>>(tb, count, scratch, ticket, out, accumulate);
+  else if (dtype == 1) sumsq_multi_kernel<1, true><<<total_blocks, SUMSQ_THREADS, 0, stream>>>(tb, count, scratch, ticket, out, accumulate);
+  else if (dtype == 2) sumsq_multi_kernel<2, true><<<total_blocks, SUMSQ_THREADS, 0, stream>>>(tb, count, scratch, ticket, out, accumulate);
+  else return -2;
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// Every tensor of the table *= host_scale * (dev_scale ? dev_scale[0] : 1), in place, in one launch.
+extern "C" int msq_scale_multi(const void* table, int count, int total_blocks, int dtype, const float* dev_scale,
+                               float host_scale, cudaStream_t stream) {
+  using namespace msq;
+  if (count <= 0 || total_blocks <= 0) return 0;
+  const SumsqTensor* tb = static_cast<const SumsqTensor*>(table);
+  if (dtype == 0) scale_multi_kernel<0><<<total_blocks, SUMSQ_THREADS, 0, stream>>>(tb, count, dev_scale, host_scale);
+  else if (dtype == 1) scale_multi_kernel<1><<<total_blocks, SUMSQ_THREADS, 0, stream>>>(tb, count, dev_scale, host_scale);
+  else if (dtype == 2) scale_multi_kernel<2><<<total_blocks, SUMSQ_THREADS, 0, stream>>>(tb, count, dev_scale, host_scale);
   else return -2;
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

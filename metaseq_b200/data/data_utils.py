@@ -123,24 +123,52 @@ def batch_by_size(indices, num_tokens_fn=None, num_tokens_vec=None, max_tokens=N
     return batch_by_size_py(indices, num_tokens_vec, max_tokens, max_sentences, bsz_mult)
 
 
-def batch_fixed_shapes(indices, num_tokens_vec, fixed_shapes):
-    """``fixed_shapes``: rows of (batch_size, max_len) sorted by max_len; each sample goes to the
-    smallest shape that fits, batches are emitted when a shape's bucket is full."""
-    order = np.argsort(fixed_shapes[:, 1], kind="stable")
-    shapes = fixed_shapes[order]
-    buckets = [[] for _ in shapes]
-    out = []
+def batch_fixed_shapes_py(indices, num_tokens_vec, fixed_shapes):
+    out, batch, longest = [], [], 0
     for k, idx in enumerate(indices):
-        n = num_tokens_vec[k]
-        j = int(np.searchsorted(shapes[:, 1], n, side="left"))
-        if j >= len(shapes):
-            continue
-        buckets[j].append(int(idx))
-        if len(buckets[j]) == shapes[j, 0]:
-            out.append(buckets[j])
-            buckets[j] = []
-    out.extend(b for b in buckets if b)
+        n = int(num_tokens_vec[k])
+        cand = max(longest, n)
+        fits = any(len(batch) + 1 <= r and cand <= t for r, t in fixed_shapes)
+        if not fits and batch:
+            out.append(batch)
+            batch, longest = [], 0
+        batch.append(int(idx))
+        longest = max(longest, n)
+    if batch:
+        out.append(batch)
     return out
+
+
+def batch_fixed_shapes(indices, num_tokens_vec, fixed_shapes):
+    """``fixed_shapes``: rows of (batch rows, longest element).  Samples are taken in order; the open batch grows
+    while some shape still holds it and is closed by the first sample that fits no shape together with it
+    (reference: ``batch_fixed_shapes_fast``, metaseq/data/data_utils_fast.pyx:124-172, which leaves the sample that
+    opens a batch out of that batch's longest-element count; here it counts).  Native loop when the host library
+    is built."""
+    fixed_shapes = np.ascontiguousarray(fixed_shapes, dtype=np.int64).reshape(-1, 2)
+    lib = _host_lib()
+    if lib is not None and hasattr(lib, "msq_batch_fixed_shapes"):
+        n = len(indices)
+        num_tokens_vec = np.ascontiguousarray(num_tokens_vec, dtype=np.int64)
+        ends = np.zeros(n + 1, dtype=np.int64)
+        fn = lib.msq_batch_fixed_shapes
+        fn.restype = ctypes.c_longlong
+        nb = fn(num_tokens_vec.ctypes.data_as(ctypes.c_void_p), ctypes.c_longlong(n),
+                fixed_shapes.ctypes.data_as(ctypes.c_void_p), ctypes.c_longlong(len(fixed_shapes)),
+                ends.ctypes.data_as(ctypes.c_void_p))
+        out, start = [], 0
+        for b in range(int(nb)):
+            out.append([int(i) for i in indices[start:ends[b]]])
+            start = int(ends[b])
+        return out
+    return batch_fixed_shapes_py(indices, num_tokens_vec, fixed_shapes.tolist())
+
+
+def batch_by_size_fn(indices, num_tokens_fn, max_tokens=None, max_sentences=None, required_batch_size_multiple=1):
+    """The size-callback form (metaseq/data/data_utils_fast.pyx:106-123): sizes are read through ``num_tokens_fn`` once
+    into a vector, the batching itself is the native loop."""
+    return batch_by_size(indices, num_tokens_fn=num_tokens_fn, max_tokens=max_tokens, max_sentences=max_sentences,
+                         required_batch_size_multiple=required_batch_size_multiple)
 
 
 @contextlib.contextmanager

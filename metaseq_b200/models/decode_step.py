@@ -323,12 +323,31 @@ class GraphedDecodeStep:
         if self.tp == 1:
             logits = self.logits
         elif gather:
-            from metaseq_b200.parallel import mappings
-
-            logits = mappings.gather_from_tensor_model_parallel_region(self.local_logits)
+            logits = self._gather_logits(self.local_logits)
         else:
             logits = self.local_logits
         return logits if self.live == self.rows else logits[: self.live]
+
+    def _gather_logits(self, local: torch.Tensor) -> torch.Tensor:
+        """``[rows, V]`` from every rank's ``[rows, V / p]`` columns through the peer-memory exchange kernel (the
+        reference gathers them with a library all-gather per token: metaseq/modules/megatron/mpu/mappings.py:97);
+        the library collective remains only for slices with an odd number of 16-bit columns."""
+        rows, vp = local.shape
+        if local.element_size() != 2 or vp % 2 or not local.is_contiguous():
+            from metaseq_b200.parallel import mappings
+
+            return mappings.gather_from_tensor_model_parallel_region(local)
+        words = rows * vp // 2
+        ex = self.decoder.__dict__.get("_decode_logits_exchange")
+        if ex is None or ex.cap < words:
+            from metaseq_b200.parallel.symm import WordsExchange
+
+            if ex is not None:
+                ex.close()
+            ex = WordsExchange(mpu.get_tensor_model_parallel_group(), self.device, self.rows * vp // 2)
+            self.decoder.__dict__["_decode_logits_exchange"] = ex
+        every = ex.gather(local.view(torch.int32)).view(local.dtype)  # [p, rows, V / p]
+        return every.permute(1, 0, 2).reshape(rows, self.tp * vp)
 
     @torch.no_grad()
     def pick_greedy(self, local_logits: torch.Tensor, banned=(), only: Optional[int] = None):

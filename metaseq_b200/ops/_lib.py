@@ -157,6 +157,8 @@ _OPTIONAL = {
     "msq_comm_reduce_scatter_pull": [P, P, L, L, I, I, F, P, I, I, P, P, P, L, ctypes.c_uint, I, P, P],
     "msq_comm_allgather_multimem": [P, P, L, I, I, I, P, L, ctypes.c_uint, I, P, P],
     "msq_sumsq_multi": [P, I, I, I, P, P, P, I, P],
+    "msq_absmax_multi": [P, I, I, I, P, P, P, I, P],
+    "msq_scale_multi": [P, I, I, I, P, F, P],
     "msq_gemm2_rowstats": [P, P, P, I, I, I, L, L, L, I, I, I, P, P, P, I, P, P, P],
     "msq_ce_merge_rowstats": [P, P, I, I, P, L, P, I, L, P, P, I, I, I, ctypes.c_uint, I, P],
     "msq_vp_ce_finish_exchanged": [P, L, P, P, I, I, ctypes.c_uint, P, I, I, L, L, F, I, P, P],

@@ -956,10 +956,9 @@ def sumsq(g: torch.Tensor, out: torch.Tensor, accumulate: bool):
 _SUMSQ_TABLES: dict = {}
 
 
-def sumsq_multi(tensors, out: torch.Tensor, accumulate: bool):
-    """``out[0] (+)= sum over all tensors of sum(t**2)`` in one launch (contiguous CUDA tensors of one dtype).  The
-    table of pointers and the scratch live on the device, keyed by device and stream, and are rebuilt only when a
-    pointer or size changes."""
+def _tensor_table(tensors):
+    """Device table {pointer, elements, first block} (+ scratch, ticket) that the list-form kernels walk; cached per
+    device and stream and rebuilt only when a pointer or size changes."""
     t0 = tensors[0]
     dev = t0.device
     key = tuple((t.data_ptr(), t.numel()) for t in tensors)
@@ -983,12 +982,48 @@ def sumsq_multi(tensors, out: torch.Tensor, accumulate: bool):
             _SUMSQ_TABLES.clear()
         cached = (key, table, scratch, ticket, first)
         _SUMSQ_TABLES[slot] = cached
-    _, table, scratch, ticket, total_blocks = cached
-    rc = _lib.kernels().msq_sumsq_multi(_lib.ptr(table), len(tensors), total_blocks, _lib.dtype_code(t0.dtype),
+    return cached[1:]
+
+
+def list_kernels_ok(tensors) -> bool:
+    """True when the list-form kernels take ``tensors``: contiguous CUDA tensors of one 16/32-bit float type."""
+    if not tensors or _BACKEND == "torch" or not tensors[0].is_cuda or not _lib.kernels_path().exists():
+        return False
+    dt = tensors[0].dtype
+    return dt in (torch.float16, torch.bfloat16, torch.float32) and \
+        all(t.dtype == dt and t.is_contiguous() and t.is_cuda for t in tensors)
+
+
+def sumsq_multi(tensors, out: torch.Tensor, accumulate: bool):
+    """``out[0] (+)= sum over all tensors of sum(t**2)`` in one launch (contiguous CUDA tensors of one dtype)."""
+    table, scratch, ticket, total_blocks = _tensor_table(tensors)
+    rc = _lib.kernels().msq_sumsq_multi(_lib.ptr(table), len(tensors), total_blocks, _lib.dtype_code(tensors[0].dtype),
                                         _lib.ptr(scratch), _lib.ptr(ticket), _lib.ptr(out), int(accumulate),
                                         _lib.stream_ptr())
     _lib.check_rc(rc, "msq_sumsq_multi")
     return out
+
+
+def absmax_multi(tensors, out: torch.Tensor, accumulate: bool = False):
+    """``out[0] = max |element|`` over the list in one launch (the inf-norm; +inf if any element is not finite)."""
+    table, scratch, ticket, total_blocks = _tensor_table(tensors)
+    rc = _lib.kernels().msq_absmax_multi(_lib.ptr(table), len(tensors), total_blocks,
+                                         _lib.dtype_code(tensors[0].dtype), _lib.ptr(scratch), _lib.ptr(ticket),
+                                         _lib.ptr(out), int(accumulate), _lib.stream_ptr())
+    _lib.check_rc(rc, "msq_absmax_multi")
+    return out
+
+
+def scale_multi_(tensors, dev_scale: Optional[torch.Tensor] = None, host_scale: float = 1.0):
+    """Every tensor of the list ``*= host_scale * dev_scale[0]`` in place, in one launch; ``dev_scale`` is a 1-element
+    fp32 device tensor (e.g. a clip coefficient that never visits the host)."""
+    table, _, _, total_blocks = _tensor_table(tensors)
+    rc = _lib.kernels().msq_scale_multi(_lib.ptr(table), len(tensors), total_blocks,
+                                        _lib.dtype_code(tensors[0].dtype),
+                                        _lib.ptr(dev_scale) if dev_scale is not None else None, float(host_scale),
+                                        _lib.stream_ptr())
+    _lib.check_rc(rc, "msq_scale_multi")
+    return tensors
 
 
 def clip_decision(sumsq_terms: torch.Tensor, pre_factor: float, max_norm: float, ctrl: torch.Tensor):

@@ -87,11 +87,7 @@ def multi_tensor_l2_norm(tensors: List[torch.Tensor]) -> torch.Tensor:
     if dev.type == "cuda":
         flat = [t.detach().reshape(-1) if t.is_contiguous() else t.detach().contiguous().view(-1) for t in tensors]
         acc = torch.empty(1, dtype=torch.float32, device=dev)
-        from metaseq_b200.ops import _lib
-
-        if len(flat) > 1 and ops.get_backend() != "torch" and all(t.dtype == flat[0].dtype for t in flat) \
-                and flat[0].dtype in (torch.float16, torch.bfloat16, torch.float32) \
-                and _lib.kernels_path().exists() and hasattr(_lib.kernels()._lib, "msq_sumsq_multi"):
+        if len(flat) > 1 and ops.list_kernels_ok(flat):
             ops.sumsq_multi(flat, acc, False)  # the whole list in one launch
         else:
             acc.zero_()
@@ -107,6 +103,7 @@ def clip_grad_norm_(params, max_norm, norm_type: str = "l2", aggregate_norm_fn=N
     (``p._is_sharded``) are partial: their squared norm is summed over the data-parallel
     group before being combined with the replicated ones; ``aggregate_norm_fn`` then
     folds in the other tensor-parallel ranks."""
+    from metaseq_b200.ops import functional as ops
     from metaseq_b200.parallel import utils as dist_utils
 
     if isinstance(params, torch.Tensor):
@@ -122,6 +119,8 @@ def clip_grad_norm_(params, max_norm, norm_type: str = "l2", aggregate_norm_fn=N
         if not grads:
             return torch.zeros((), dtype=torch.float32, device=device)
         if norm_type == "inf":
+            if ops.list_kernels_ok(grads):  # one launch over the list
+                return ops.absmax_multi(grads, torch.empty(1, dtype=torch.float32, device=grads[0].device))[0]
             return max(g.abs().max().float() for g in grads)
         return multi_tensor_l2_norm(grads).to(device)
 
@@ -141,8 +140,13 @@ def clip_grad_norm_(params, max_norm, norm_type: str = "l2", aggregate_norm_fn=N
         total = aggregate_norm_fn(total)
     if max_norm is not None and max_norm > 0:
         coef = (float(max_norm) / (total + 1e-6)).clamp(max=1.0)
-        for p in params:
-            p.grad.detach().mul_(coef.to(p.grad.dtype) if p.grad.is_floating_point() else coef)
+        grads = [p.grad.detach() for p in params]
+        if ops.list_kernels_ok(grads) and coef.device == grads[0].device:
+            # one launch for the whole list, the coefficient read on the device
+            ops.scale_multi_(grads, coef.float().reshape(1))
+        else:
+            for g in grads:
+                g.mul_(coef.to(g.dtype) if g.is_floating_point() else coef)
     return total
 
 

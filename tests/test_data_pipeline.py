@@ -200,6 +200,24 @@ def test_token_block_dataset_items_and_targets():
     assert src0[0] == 2 and torch.equal(src0[1:], tgt0[:-1])
 
 
+def test_batch_fixed_shapes_native_matches_python():
+    rng = np.random.RandomState(3)
+    shapes = np.array([[16, 8], [8, 16], [4, 32], [2, 64]], dtype=np.int64)
+    sizes = rng.randint(1, 70, size=400).astype(np.int64)
+    idx = rng.permutation(400).astype(np.int64)
+    a = data_utils.batch_by_size(idx, num_tokens_vec=sizes[idx], fixed_shapes=shapes)
+    b = data_utils.batch_fixed_shapes_py(idx, sizes[idx], shapes.tolist())
+    assert a == b
+    assert [i for batch in a for i in batch] == idx.tolist()  # order kept, nothing dropped
+    for batch in a:
+        longest = int(max(sizes[batch]))
+        assert any(len(batch) <= r and longest <= t for r, t in shapes) or (len(batch) == 1 and longest > 64)
+    # the size-callback form is the vector form
+    c = data_utils.batch_by_size_fn(idx, lambda i: int(sizes[i]), max_tokens=128, max_sentences=9)
+    d = data_utils.batch_by_size(idx, num_tokens_vec=sizes[idx], max_tokens=128, max_sentences=9)
+    assert c == d
+
+
 def test_batch_by_size_native_matches_python():
     rng = np.random.RandomState(0)
     for max_tokens, max_sent, mult in [(100, None, 1), (64, 5, 1), (256, 16, 8), (None, 7, 1)]:

@@ -780,6 +780,63 @@ def test_sum_of_squares_list_form_matches_the_per_tensor_kernel(dtype):
     assert float(norm) == pytest.approx(math.sqrt(want - 5.0), rel=2e-5)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+def test_inf_norm_and_scale_list_forms(dtype):
+    from metaseq_b200 import utils
+
+    torch.manual_seed(14)
+    sizes = [5, 4096, 70_001, 1_000_000, 9]
+    big = torch.randn(sum(sizes) + 64, device="cuda").to(dtype)
+    tensors, off = [], 1
+    for n in sizes:
+        tensors.append(big[off:off + n])
+        off += n + 1
+    out = torch.zeros(1, device="cuda")
+    before = _lib.launch_count()
+    F.absmax_multi(tensors, out)
+    assert _lib.launch_count() == before + 1
+    assert float(out) == max(float(t.float().abs().max()) for t in tensors)
+    copies = [t.clone() for t in tensors]
+    coef = torch.tensor([0.25], device="cuda")
+    before = _lib.launch_count()
+    F.scale_multi_(copies, coef, host_scale=2.0)
+    assert _lib.launch_count() == before + 1
+    for c, t in zip(copies, tensors):
+        assert torch.equal(c, (t.float() * 0.5).to(dtype))
+    # clipping a parameter list: inf-norm and l2-norm through the list kernels equal the PyTorch statement
+    params = [torch.nn.Parameter(torch.zeros_like(t)) for t in tensors]
+    for norm_type in ("l2", "inf"):
+        for p_, t in zip(params, tensors):
+            p_.grad = t.clone()
+        total = utils.clip_grad_norm_(params, 1.0, norm_type=norm_type)
+        flat = torch.cat([t.float().reshape(-1) for t in tensors])
+        want = flat.abs().max() if norm_type == "inf" else flat.norm()
+        assert float(total) == pytest.approx(float(want), rel=2e-5)
+        c = min(1.0, 1.0 / (float(want) + 1e-6))
+        for p_, t in zip(params, tensors):
+            tol = 1e-6 if dtype == torch.float32 else (1e-3 if dtype == torch.float16 else 8e-3)
+            assert torch.allclose(p_.grad.float(), t.float() * c, rtol=tol, atol=tol * 1e-2)
+    bad = [t.clone() for t in tensors]
+    bad[2][17] = float("nan")
+    assert float(F.absmax_multi(bad, out)) == float("inf")
+
+
+def test_bias_gradient_single_launch_leaves_its_scratch_clean():
+    torch.manual_seed(15)
+    for rows, N in [(3001, 776), (16384, 2048), (70, 8192), (3001, 776)]:
+        x = torch.randn(rows, N, device="cuda").to(torch.bfloat16)
+        dst = torch.randn(N, device="cuda").to(torch.bfloat16)
+        keep = dst.clone()
+        before = _lib.launch_count()
+        F.colsum(x, out16=dst, accumulate=True)
+        assert _lib.launch_count() == before + 1
+        want = keep.float() + x.float().sum(0)
+        assert (dst.float() - want).abs().max() <= 0.02 * want.abs().max() + 0.05
+        F.colsum(x, out16=dst, accumulate=False)  # the second call starts from a scratch the first left at zero
+        want = x.float().sum(0)
+        assert (dst.float() - want).abs().max() <= 0.01 * want.abs().max() + 0.05
+
+
 def _attn_fwd_bwd(q, k, v, qkv, d_out, scale, use_ref, **masks):
     """Forward and backward through the kernels (or the PyTorch restatement): returns (out, lse, dqkv)."""
     B, T, H, d = q.shape
