@@ -1,4 +1,9 @@
-"""Minimal path manager with pluggable handlers keyed by URI prefix."""
+"""Path manager with pluggable storage handlers keyed by URI prefix (the role of the reference's iopath-style
+``metaseq/file_io/common/__init__.py``: handler interface :94-470, local handler :471-700, manager :702-1246).
+
+The manager picks the handler with the longest matching prefix and falls back to the local file system.  Handler
+specific keyword arguments pass through the manager's calls; a handler rejects (strict mode, the default) or only
+warns about the ones it does not know.  A copy between two different handlers goes through a local file."""
 from __future__ import annotations
 
 import errno
@@ -13,7 +18,25 @@ logger = logging.getLogger(__name__)
 class PathHandler:
     """Operations a storage backend has to provide."""
 
+    _strict_kwargs_check = True
+
+    def _check_kwargs(self, kwargs: Dict[str, Any]) -> None:
+        """Keyword arguments that reached a handler which has no use for them: an error in strict mode, a warning
+        otherwise."""
+        if not kwargs:
+            return
+        if self._strict_kwargs_check:
+            raise ValueError(f"{type(self).__name__} got unused arguments: {sorted(kwargs)}")
+        for k, v in kwargs.items():
+            logger.warning(f"{type(self).__name__} ignores argument {k}={v!r}")
+
     def _get_supported_prefixes(self) -> List[str]:
+        raise NotImplementedError
+
+    def _mv(self, src: str, dst: str, **kw) -> bool:
+        raise NotImplementedError
+
+    def _set_cwd(self, path: Optional[str], **kw) -> bool:
         raise NotImplementedError
 
     def _get_local_path(self, path: str, **kw) -> str:
@@ -57,16 +80,54 @@ class PathHandler:
 
 
 class NativePathHandler(PathHandler):
+    """The local file system.  Relative paths are taken under the handler's working directory when one is set."""
+
+    _cwd: Optional[str] = None
+
     def _get_supported_prefixes(self):
         return [""]
 
-    def _get_local_path(self, path, **kw):
-        return os.fspath(path)
+    def _abs(self, path):
+        path = os.fspath(path)
+        return path if self._cwd is None or os.path.isabs(path) else os.path.normpath(os.path.join(self._cwd, path))
 
-    def _open(self, path, mode="r", buffering=-1, encoding=None, errors=None, newline=None, **kw):
-        return open(path, mode, buffering=buffering, encoding=encoding, errors=errors, newline=newline)
+    def _set_cwd(self, path, **kw):
+        self._check_kwargs(kw)
+        if path is None:
+            self._cwd = None
+            return True
+        if not os.path.isabs(path) or not os.path.isdir(path):
+            logger.error(f"{path} is not an existing absolute directory")
+            return False
+        self._cwd = path
+        return True
+
+    def _get_local_path(self, path, force: bool = False, **kw):
+        self._check_kwargs(kw)
+        return self._abs(path)
+
+    def _open(self, path, mode="r", buffering=-1, encoding=None, errors=None, newline=None, closefd=True,
+              opener=None, **kw):
+        self._check_kwargs(kw)
+        return open(self._abs(path), mode, buffering=buffering, encoding=encoding, errors=errors, newline=newline,
+                    closefd=closefd, opener=opener)
+
+    def _mv(self, src, dst, **kw):
+        self._check_kwargs(kw)
+        src, dst = self._abs(src), self._abs(dst)
+        if os.path.exists(dst):
+            logger.error(f"Destination file {dst} already exists.")
+            return False
+        try:
+            shutil.move(src, dst)
+            return True
+        except Exception as e:
+            logger.error(f"Error in move operation - {e}")
+            return False
 
     def _copy(self, src, dst, overwrite=False, **kw):
+        self._check_kwargs(kw)
+        src, dst = self._abs(src), self._abs(dst)
         if os.path.exists(dst) and not overwrite:
             logger.error(f"Destination file {dst} already exists.")
             return False
@@ -78,38 +139,46 @@ class NativePathHandler(PathHandler):
             return False
 
     def _copy_from_local(self, local_path, dst_path, overwrite=False, **kw):
-        return self._copy(local_path, dst_path, overwrite)
+        return self._copy(local_path, dst_path, overwrite, **kw)
 
     def _exists(self, path, **kw):
-        return os.path.exists(path)
+        self._check_kwargs(kw)
+        return os.path.exists(self._abs(path))
 
     def _isfile(self, path, **kw):
-        return os.path.isfile(path)
+        self._check_kwargs(kw)
+        return os.path.isfile(self._abs(path))
 
     def _isdir(self, path, **kw):
-        return os.path.isdir(path)
+        self._check_kwargs(kw)
+        return os.path.isdir(self._abs(path))
 
     def _islink(self, path, **kw):
-        return os.path.islink(path)
+        return os.path.islink(self._abs(path))
 
     def _ls(self, path, **kw):
-        return os.listdir(path)
+        self._check_kwargs(kw)
+        return os.listdir(self._abs(path))
 
     def _mkdirs(self, path, **kw):
+        self._check_kwargs(kw)
         try:
-            os.makedirs(path, exist_ok=True)
+            os.makedirs(self._abs(path), exist_ok=True)
         except OSError as e:
             if e.errno != errno.EEXIST:
                 raise
 
     def _rm(self, path, **kw):
-        os.remove(path)
+        self._check_kwargs(kw)
+        os.remove(self._abs(path))
 
     def _rename(self, src, dst, **kw):
-        os.replace(src, dst)
+        os.replace(self._abs(src), self._abs(dst))
         return True
 
     def _symlink(self, src, dst, **kw):
+        self._check_kwargs(kw)
+        src, dst = self._abs(src), self._abs(dst)
         if os.path.lexists(dst):
             os.remove(dst)
         os.symlink(src, dst)
@@ -121,11 +190,24 @@ class PathManagerBase:
         self._handlers: Dict[str, PathHandler] = {}
         self._native = NativePathHandler()
         self._nb = None
+        self._cwd: Optional[str] = None
+        self._enable_logging = True
 
+    # ------------------------------------------------------------- handlers
     def register_handler(self, handler: PathHandler, allow_override: bool = True):
+        """Registers ``handler`` for its prefixes.  A ``NativePathHandler`` replaces the built-in local handler."""
+        assert isinstance(handler, PathHandler), handler
+        if isinstance(handler, NativePathHandler):
+            if not allow_override:
+                raise ValueError("a local-file handler is registered by default; pass allow_override=True to replace it")
+            self._native = handler
+            return
         for prefix in handler._get_supported_prefixes():
-            if prefix in self._handlers and not allow_override:
-                raise KeyError(f"prefix {prefix} already registered")
+            old = self._handlers.get(prefix)
+            if old is not None and not allow_override:
+                raise KeyError(f"prefix {prefix} already registered by {type(old).__name__}")
+            if old is not None and type(old) is not type(handler):
+                logger.warning(f"prefix {prefix!r}: {type(handler).__name__} replaces {type(old).__name__}")
             self._handlers[prefix] = handler
 
     def _handler(self, path) -> PathHandler:
@@ -135,9 +217,32 @@ class PathManagerBase:
                 return self._handlers[prefix]
         return self._native
 
-    def open(self, path, mode="r", buffering=-1, encoding=None, errors=None, newline=None):
+    def path_requires_pathmanager(self, path) -> bool:
+        """True when a non-local handler serves ``path``."""
+        return self._handler(path) is not self._native
+
+    def set_strict_kwargs_checking(self, enable: bool) -> None:
+        """Strict (default): an argument that a handler does not use raises ``ValueError``; otherwise it warns."""
+        self._native._strict_kwargs_check = enable
+        for h in self._handlers.values():
+            h._strict_kwargs_check = enable
+
+    def set_logging(self, enable_logging: bool = True) -> None:
+        self._enable_logging = enable_logging
+
+    def set_cwd(self, path: Optional[str], **kw) -> bool:
+        """Working directory that the handler of ``path`` puts in front of relative paths; ``None`` clears it."""
+        if path is None and self._cwd is None:
+            return True
+        if self._handler(path or self._cwd)._set_cwd(path, **kw):
+            self._cwd = path
+            return True
+        return False
+
+    # ------------------------------------------------------------------ I/O
+    def open(self, path, mode="r", buffering=-1, encoding=None, errors=None, newline=None, **kw):
         return self._handler(path)._open(path, mode, buffering=buffering, encoding=encoding, errors=errors,
-                                         newline=newline)
+                                         newline=newline, **kw)
 
     def opena(self, path, mode="a", callback_after_file_close=None, **kw):
         """Non-blocking write handle: writes are queued to a background thread."""
@@ -145,7 +250,8 @@ class PathManagerBase:
             from .non_blocking_io import NonBlockingIOManager
 
             self._nb = NonBlockingIOManager()
-        return self._nb.get_non_blocking_io(path, self._handler(path)._open(path, mode), callback_after_file_close)
+        return self._nb.get_non_blocking_io(path, self._handler(path)._open(path, mode, **kw),
+                                            callback_after_file_close)
 
     def async_join(self, *paths):
         return self._nb._join(*paths) if self._nb is not None else True
@@ -153,45 +259,63 @@ class PathManagerBase:
     def async_close(self):
         return self._nb._close_thread_pool() if self._nb is not None else True
 
-    def copy(self, src, dst, overwrite=False):
-        return self._handler(src)._copy(src, dst, overwrite)
+    def copy(self, src, dst, overwrite=False, **kw):
+        hs, hd = self._handler(src), self._handler(dst)
+        if hs is not hd:
+            return self._copy_across_handlers(src, dst, overwrite, **kw)
+        return hs._copy(src, dst, overwrite, **kw)
 
-    def copy_from_local(self, local_path, dst_path, overwrite=False):
-        return self._handler(dst_path)._copy_from_local(local_path, dst_path, overwrite)
+    def _copy_across_handlers(self, src, dst, overwrite, **kw):
+        """Source and destination live in different stores: fetch to a local file, then upload."""
+        local = self._handler(src)._get_local_path(src, **kw)
+        return self._handler(dst)._copy_from_local(local, dst, overwrite=overwrite, **kw)
 
-    def get_local_path(self, path, **kw):
-        return self._handler(path)._get_local_path(path, **kw)
+    def mv(self, src, dst, **kw):
+        hs, hd = self._handler(src), self._handler(dst)
+        assert hs is hd, "source and destination must be served by the same handler"
+        return hs._mv(src, dst, **kw)
 
-    def exists(self, path):
-        return self._handler(path)._exists(path)
+    def copy_from_local(self, local_path, dst_path, overwrite=False, **kw):
+        assert os.path.exists(local_path), f"local path {local_path} does not exist"
+        return self._handler(dst_path)._copy_from_local(local_path, dst_path, overwrite, **kw)
 
-    def isfile(self, path):
-        return self._handler(path)._isfile(path)
+    def get_local_path(self, path, force: bool = False, **kw):
+        path = os.fspath(path)
+        return self._handler(path)._get_local_path(path, force=force, **kw)
 
-    def isdir(self, path):
-        return self._handler(path)._isdir(path)
+    def exists(self, path, **kw):
+        return self._handler(path)._exists(path, **kw)
+
+    def isfile(self, path, **kw):
+        return self._handler(path)._isfile(path, **kw)
+
+    def isdir(self, path, **kw):
+        return self._handler(path)._isdir(path, **kw)
 
     def islink(self, path):
         return self._handler(path)._islink(path)
 
-    def ls(self, path):
-        return self._handler(path)._ls(path)
+    def ls(self, path, **kw):
+        return self._handler(path)._ls(path, **kw)
 
-    def mkdirs(self, path):
-        return self._handler(path)._mkdirs(path)
+    def mkdirs(self, path, **kw):
+        return self._handler(path)._mkdirs(path, **kw)
 
-    def rm(self, path):
-        return self._handler(path)._rm(path)
+    def rm(self, path, **kw):
+        return self._handler(path)._rm(path, **kw)
 
     def rename(self, src, dst):
+        if not self.supports_rename(src):
+            raise ValueError(f"{src} is served by {type(self._handler(src)).__name__}, which cannot rename")
         return self._handler(src)._rename(src, dst)
 
-    def symlink(self, src, dst):
-        return self._handler(src)._symlink(src, dst)
+    def symlink(self, src, dst, **kw):
+        assert self._handler(src) is self._handler(dst), "source and destination must be served by the same handler"
+        return self._handler(src)._symlink(src, dst, **kw)
 
     def chmod(self, path, mode):
         if self._handler(path) is self._native:
-            os.chmod(path, mode)
+            os.chmod(self._native._abs(path), mode)
 
     def supports_rename(self, path):
         return self._handler(path) is self._native

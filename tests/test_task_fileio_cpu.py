@@ -221,3 +221,94 @@ def test_cache_dir_and_file_lock(tmp_path, monkeypatch):
                 pass
     with file_lock(target, timeout=0.2):  # free again
         pass
+
+
+def test_path_manager_handlers_cwd_move_and_argument_checks(tmp_path):
+    import io
+
+    from metaseq_b200.file_io.path_manager import NativePathHandler, PathHandler, PathManagerBase
+
+    class MemHandler(PathHandler):
+        """A toy remote store: objects in a dict, fetched to local files on demand."""
+
+        def __init__(self, cache):
+            self.objects, self.cache = {}, cache
+
+        def _get_supported_prefixes(self):
+            return ["mem://"]
+
+        def _get_local_path(self, path, force=False, **kw):
+            self._check_kwargs(kw)
+            local = os.path.join(self.cache, path[len("mem://"):].replace("/", "_"))
+            if force or not os.path.exists(local):
+                with open(local, "wb") as f:
+                    f.write(self.objects[path])
+            return local
+
+        def _copy_from_local(self, local_path, dst_path, overwrite=False, ttl=None, **kw):
+            self._check_kwargs(kw)
+            if dst_path in self.objects and not overwrite:
+                return False
+            with open(local_path, "rb") as f:
+                self.objects[dst_path] = f.read()
+            return True
+
+        def _open(self, path, mode="r", **kw):
+            data = self.objects[path]
+            return io.BytesIO(data) if "b" in mode else io.StringIO(data.decode())
+
+        def _exists(self, path, **kw):
+            return path in self.objects
+
+    pm = PathManagerBase()
+    mem = MemHandler(str(tmp_path))
+    pm.register_handler(mem)
+    with pytest.raises(KeyError):
+        pm.register_handler(MemHandler(str(tmp_path)), allow_override=False)
+    assert pm.path_requires_pathmanager("mem://bucket/x") and not pm.path_requires_pathmanager(str(tmp_path))
+    assert not pm.supports_rename("mem://bucket/x")
+    with pytest.raises(ValueError):
+        pm.rename("mem://bucket/x", "mem://bucket/y")
+
+    # local -> remote -> local through copy(): different handlers go through a local file
+    src = tmp_path / "src.txt"
+    src.write_text("payload")
+    assert pm.copy(str(src), "mem://bucket/x")
+    assert mem.objects["mem://bucket/x"] == b"payload"
+    assert not pm.copy(str(src), "mem://bucket/x")  # exists, no overwrite
+    back = tmp_path / "back.txt"
+    assert pm.copy("mem://bucket/x", str(back))
+    assert back.read_text() == "payload"
+    with pm.open("mem://bucket/x") as f:
+        assert f.read() == "payload"
+    # handler-specific arguments pass through; unknown ones raise in strict mode and only warn otherwise
+    assert pm.copy_from_local(str(src), "mem://bucket/z", ttl=5)
+    with pytest.raises(ValueError):
+        pm.exists(str(src), cache_timeout=3)
+    pm.set_strict_kwargs_checking(False)
+    assert pm.exists(str(src), cache_timeout=3)
+    pm.set_strict_kwargs_checking(True)
+
+    # working directory for relative local paths
+    sub = tmp_path / "wd"
+    sub.mkdir()
+    assert not pm.set_cwd("relative/dir")
+    assert pm.set_cwd(str(sub))
+    with pm.open("note.txt", "w") as f:
+        f.write("x")
+    assert (sub / "note.txt").exists() and pm.isfile("note.txt") and pm.ls(".") == ["note.txt"]
+    assert pm.mv("note.txt", "moved.txt") and (sub / "moved.txt").exists()
+    (sub / "other.txt").write_text("y")
+    assert not pm.mv("other.txt", "moved.txt")  # never overwrites
+    assert pm.get_local_path("moved.txt") == str(sub / "moved.txt")
+    assert pm.set_cwd(None) and pm.get_local_path("moved.txt") == "moved.txt"
+    with pytest.raises(AssertionError):
+        pm.mv(str(src), "mem://bucket/q")
+    # a replacement for the local handler
+    class Quiet(NativePathHandler):
+        pass
+
+    with pytest.raises(ValueError):
+        pm.register_handler(Quiet(), allow_override=False)
+    pm.register_handler(Quiet())
+    assert isinstance(pm._native, Quiet) and pm.exists(str(src))
