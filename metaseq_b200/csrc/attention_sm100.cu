@@ -115,7 +115,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* p_full = s_full + 1;
   uint64_t* o_full = p_full + 1;
   uint64_t* o_empty = o_full + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_empty + 1);
+  uint64_t* s_free = o_empty + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_free + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -140,6 +141,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     mbar_init(p_full, 128);
     mbar_init(o_full, 1);
     mbar_init(o_empty, 128);
+    mbar_init(s_free, 128);
     *abort_flag = 0;
     mbar_fence_init();
     fence_proxy_async_smem();
@@ -214,16 +216,21 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     };
     if (ok) ok = issue_s(0);
     for (int j = 0; j < n_kv && ok; ++j) {
-      // p_full(j): every softmax thread has read S(j), written P(j) and finished any rescale of O.
+      const bool mprof = p.prof != nullptr && lane == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j < 32;
+      // s_free(j): every softmax thread holds the last of S(j) in registers.  That happens a quarter of the
+      // exponential pass before P(j) is complete, so the next score tile is computed under the rest of that pass
+      // and is waiting when the softmax warps come back for it.
+      if (j + 1 < n_kv) {
+        ok = mbar_wait_warp(s_free, j & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
+        if (!ok) break;
+        if (mprof) p.prof[j * 8 + 3] = clock64();
+        ok = issue_s(j + 1);
+        if (!ok) break;
+      }
+      if (mprof) p.prof[j * 8 + 5] = clock64();
+      // p_full(j): every softmax thread has written P(j) and finished any rescale of O.
       ok = mbar_wait_warp(p_full, j & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
       if (!ok) break;
-      const bool mprof = p.prof != nullptr && lane == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j < 32;
-      if (mprof) p.prof[j * 8 + 3] = clock64();
-      // The softmax warps are idle until the next score tile exists, so it goes first; P V (j) then runs
-      // under their first pass over S(j+1).
-      if (j + 1 < n_kv) ok = issue_s(j + 1);
-      if (!ok) break;
-      if (mprof) p.prof[j * 8 + 5] = clock64();
       const int i = 2 * j + 1, slot = i % Cfg::SLOTS;
       ok = mbar_wait_warp(&kv_full[slot], (i / Cfg::SLOTS) & 1, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
       if (!ok) break;
@@ -342,7 +349,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           tmem_ld_wait();
-          if (c + 1 < 4) tmem_ld_32x32(tS + lane_off + (c + 1) * 32, r[(c + 1) & 1]);
+          if (c + 1 < 4) {
+            tmem_ld_32x32(tS + lane_off + (c + 1) * 32, r[(c + 1) & 1]);
+          } else {
+            tc_fence_before();
+            mbar_arrive(s_free);  // all of S(j) is in registers: the tensor pipe may write S(j+1)
+          }
           uint32_t packed[16];
           if (need_mask) {
             const float off0 = bias0 - m_use;
@@ -503,7 +515,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* dq_empty = dq_full + 1;
   uint64_t* dkv_full = dq_empty + 1;
   uint64_t* pds_free = dkv_full + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pds_free + 1);
+  uint64_t* sdp_free = pds_free + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sdp_free + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -537,6 +550,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     mbar_init(dq_empty, Cfg::DQ_ALIASES_S ? 256 : 128);  // drained by the element-wise warps when aliased, else by the drain warps
     mbar_init(dkv_full, 1);
     mbar_init(pds_free, 1);
+    mbar_init(sdp_free, 256);
     *abort_flag = 0;
     mbar_fence_init();
     fence_proxy_async_smem();
@@ -628,13 +642,17 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     for (int it = 0; it < n_it && ok; ++it) {
       const int stage = it % QS;
       const uint32_t st_off = (stage * Cfg::TILE_BYTES) >> 4;
-      // P and dS of this iteration are in shared memory (and S / dP have been read out of TMEM)
-      ok = mbar_wait_warp(pds_full, it & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
-      if (!ok) break;
       if (PIPELINED && it + 1 < n_it) {
+        // S / dP of this iteration are in the element-wise warps' registers: the next pair is computed while
+        // they finish P and dS
+        ok = mbar_wait_warp(sdp_free, it & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
+        if (!ok) break;
         ok = issue_sdp(it + 1);
         if (!ok) break;
       }
+      // P and dS of this iteration are in shared memory
+      ok = mbar_wait_warp(pds_full, it & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
+      if (!ok) break;
       if (it > 0) {  // dQ of the previous iteration has been drained from TMEM
         ok = mbar_wait_warp(dq_empty, (it - 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
         if (!ok) break;
@@ -797,6 +815,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           tmem_ld_wait();
+          if (c == 1) {
+            tc_fence_before();
+            mbar_arrive(sdp_free);  // S and dP of this iteration are in registers
+          }
           const int cbase = col0 + c * 32;
           if (need_mask || DROP) {
             // general path: per-element bounds and, with dropout, the keep factor of each weight.  dV uses the
