@@ -281,6 +281,58 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (p.causal) limit = min(limit, q_idx - ja * TILE + 1);
       limit = max(0, min(limit, TILE));
       const float bias0 = slope2 * static_cast<float>(ja * TILE);  // ALiBi: bias of column i is bias0 + slope2 * i
+      // Unmasked blocks after the first take one pass over S: the exponentials use the running reference maximum
+      // while the block maximum is collected alongside; only if some row of the warp outgrew the reference by more
+      // than RESCALE_LOG2 (rare once a few blocks have been seen) is the block redone by the two-pass code below.
+      bool one_pass_done = false;
+      if (!DROP && !need_mask && j > 0 && __all_sync(0xffffffffu, m_run != -INFINITY)) {
+        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        uint64_t ps2[2] = {0ull, 0ull};
+        const uint64_t scale2 = f2_pack(p.scale_log2, p.scale_log2), neg_m2 = f2_pack(-m_run, -m_run);
+        uint32_t r[2][32];
+        tmem_ld_32x32(tS + lane_off, r[0]);
+        bool overflow = false;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          tmem_ld_wait();
+          if (c + 1 < 4) tmem_ld_32x32(tS + lane_off + (c + 1) * 32, r[(c + 1) & 1]);
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            m4[i & 3] = fmax3(m4[i & 3], __uint_as_float(r[c & 1][2 * i]), __uint_as_float(r[c & 1][2 * i + 1]));
+          if (c == 3) {
+            const float bm = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * p.scale_log2;
+            overflow = __any_sync(0xffffffffu, bm - m_run > RESCALE_LOG2);
+            if (overflow) break;
+            tc_fence_before();
+            mbar_arrive(s_free);  // all of S(j) is in registers: the tensor pipe may write S(j+1)
+          }
+          uint32_t packed[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            float x0, x1;
+            f2_unpack(f2_fma(f2_pack_bits(r[c & 1][2 * i], r[c & 1][2 * i + 1]), scale2, neg_m2), x0, x1);
+            const float a = exp2f(x0), bb = exp2f(x1);
+            ps2[i & 1] = f2_add(ps2[i & 1], f2_pack(a, bb));
+            packed[i] = pack2<BF16>(a, bb);
+          }
+          if (c == 0) {
+            // P V (j-1) must have read P before it is overwritten; it ran under the first chunk's exponentials
+            ok = mbar_wait_warp(o_full, (j - 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
+            if (!ok) break;
+            tc_fence_after();
+          }
+          tmem_st_32x16(tP + lane_off + c * 16, packed);
+        }
+        if (!ok) break;
+        if (!overflow) {
+          float s0, s1, s2, s3;
+          f2_unpack(ps2[0], s0, s1);
+          f2_unpack(ps2[1], s2, s3);
+          l_run += (s0 + s1) + (s2 + s3);
+          one_pass_done = true;
+        }
+      }
+      if (!one_pass_done) {
       float mx;  // row maximum of this block in log2 units (scaled, biased)
       {
         // four independent running maxima keep the dependency chains short
@@ -410,6 +462,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         psum = ((ps4[0] + ps4[1]) + (ps4[2] + ps4[3])) + ((s0 + s1) + (s2 + s3));
       }
       l_run += psum;
+      }  // two-pass path
       tmem_st_wait();
       if (prof_on) p.prof[j * 8 + 2] = clock64();
       tc_fence_before();
