@@ -78,7 +78,50 @@ struct AttnFwdParams {
   int hd;                     // real head size (<= HD of the kernel)
   const int* doc_start;       // [B, T] or null
   const float* alibi_slopes;  // [H] or null
+  int B, n_qblocks;           // work items: one per (batch, head, q tile)
+  unsigned* work;             // {next item, CTAs finished} of this launch, both zero before and after it
 };
+
+// The forward kernel is persistent: CTAs (two per SM at HD = 64) draw work items from a counter.  Item w is q tile
+// n_qblocks - 1 - w % n_qblocks of (batch, head) group w / n_qblocks: the q tiles of one head run at about the same
+// time (its K / V stay in L2) and the heavy ones of each head start first.
+struct FwdItem {
+  int qb, h, b, j0, n_kv;
+};
+template <bool GEN>
+__device__ __forceinline__ FwdItem fwd_item(const AttnFwdParams& p, int w) {
+  FwdItem it;
+  const int group = w / p.n_qblocks;
+  it.qb = p.n_qblocks - 1 - (w - group * p.n_qblocks);
+  it.h = group % p.H;
+  it.b = group / p.H;
+  // With document starts the first row of the tile has the earliest start: kv blocks before it are skipped.
+  it.j0 = (GEN && p.doc_start) ? p.doc_start[static_cast<long long>(it.b) * p.T + min(it.qb * TILE, p.T - 1)] / TILE : 0;
+  it.n_kv = (p.causal ? (it.qb + 1) : (p.T + TILE - 1) / TILE) - it.j0;  // blocks j0 .. j0 + n_kv - 1
+  return it;
+}
+
+// 2^x for a pair of x <= 8 on the FMA pipe (no special-function unit): x = n + f with n = round(x), f in [-0.5, 0.5];
+// 2^f by a cubic (relative error 1.0e-4, under the rounding of the 16-bit result), scaled by adding n to the
+// exponent field.  Inputs below -126 are clamped (their result is a denormal-range value that rounds to zero).
+__device__ __forceinline__ void exp2_poly2(uint64_t x2, float& a, float& b) {
+  const uint64_t magic2 = f2_pack(12582912.f, 12582912.f);  // 1.5 * 2^23
+  const uint64_t neg_magic2 = f2_pack(-12582912.f, -12582912.f);
+  const uint64_t one2 = f2_pack(1.f, 1.f);
+  float x0, x1;
+  f2_unpack(x2, x0, x1);
+  x2 = f2_pack(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
+  const uint64_t t2 = f2_add(x2, magic2);
+  const uint64_t f2 = f2_add(x2, f2_mul(f2_add(t2, neg_magic2), f2_pack(-1.f, -1.f)));
+  uint64_t p2 = f2_fma(f2, f2_pack(0.05500893f, 0.05500893f), f2_pack(0.24221096f, 0.24221096f));
+  p2 = f2_fma(p2, f2, f2_pack(0.69328293f, 0.69328293f));
+  p2 = f2_fma(p2, f2, one2);
+  float t0, t1, p0, p1;
+  f2_unpack(t2, t0, t1);
+  f2_unpack(p2, p0, p1);
+  a = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
+  b = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
+}
 
 template <int HD>
 struct FwdCfg {
@@ -88,7 +131,7 @@ struct FwdCfg {
   // K/V ring.  Four slots at HD = 64 also keep the footprint above a third of an SM's shared memory, so
   // at most two CTAs (2 x 256 TMEM columns) are ever co-resident and tcgen05.alloc never has to wait.
   static constexpr int SLOTS = (HD == 64) ? 4 : 3;
-  static constexpr uint32_t SMEM = TILE_BYTES * (1 + SLOTS) + 1024 + 128;
+  static constexpr uint32_t SMEM = TILE_BYTES * (2 + SLOTS) + 1024 + 256;  // two Q tiles: the next item's is prefetched
   // TMEM columns: S (128 fp32), O (HD fp32), P (128 16-bit values = 64 columns)
   static constexpr uint32_t O_COL = 128;
   static constexpr uint32_t P_COL = 128 + HD;
@@ -105,34 +148,33 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   using Cfg = FwdCfg<HD>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sQ = smem;
-  uint8_t* sKV = sQ + Cfg::TILE_BYTES;
+  uint8_t* sQ = smem;  // two tiles
+  uint8_t* sKV = sQ + 2 * Cfg::TILE_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + Cfg::SLOTS * Cfg::TILE_BYTES);
-  uint64_t* q_full = bars;
-  uint64_t* kv_full = bars + 1;
+  uint64_t* q_full = bars;        // [2]
+  uint64_t* q_empty = bars + 2;   // [2]
+  uint64_t* kv_full = bars + 4;
   uint64_t* kv_empty = kv_full + Cfg::SLOTS;
   uint64_t* s_full = kv_empty + Cfg::SLOTS;
   uint64_t* p_full = s_full + 1;
   uint64_t* o_full = p_full + 1;
   uint64_t* o_empty = o_full + 1;
   uint64_t* s_free = o_empty + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_free + 1);
+  volatile int* work_item = reinterpret_cast<volatile int*>(s_free + 1);  // [2]: item in each Q buffer, -1 = no more
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(const_cast<int*>(work_item) + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_qblocks = gridDim.x;
-  const int qb = n_qblocks - 1 - blockIdx.x;  // heaviest (longest causal prefix) blocks first
-  const int h = blockIdx.y, b = blockIdx.z;
-  // With document starts the first row of the tile has the earliest start: kv blocks before it are skipped.
-  const int* dstart = (GEN && p.doc_start) ? p.doc_start + static_cast<long long>(b) * p.T : nullptr;
-  const int j0 = (GEN && dstart) ? dstart[min(qb * TILE, p.T - 1)] / TILE : 0;
-  const int n_kv = (p.causal ? (qb + 1) : (p.T + TILE - 1) / TILE) - j0;  // blocks j0 .. j0 + n_kv - 1
+  const int total_items = p.n_qblocks * p.H * p.B;
   const int hd = GEN ? p.hd : HD;
 
   if (p.status && *reinterpret_cast<volatile int*>(p.status) != 0) return;
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&q_full[s], 1);
+      mbar_init(&q_empty[s], 5);  // the commit behind the item's last score product + one arrival per softmax warp
+    }
     for (int s = 0; s < Cfg::SLOTS; ++s) {
       mbar_init(&kv_full[s], 1);
       mbar_init(&kv_empty[s], 1);
@@ -158,25 +200,40 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_expect_tx(q_full, Cfg::TILE_BYTES);
-#pragma unroll
-      for (int c = 0; c < Cfg::CHUNKS; ++c)
-        attn_load_box(sQ + c * Cfg::CHUNK_BYTES, &tmQ, q_full, !GEN, hd, c, h, qb * TILE, b);
       int slot = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int j = 0; j < n_kv && ok; ++j) {
-#pragma unroll 1
-        for (int which = 0; which < 2; ++which) {
-          ok = mbar_wait(&kv_empty[slot], phase ^ 1, abort_flag, p.status, ST_TIMEOUT_SMEM_EMPTY);
-          if (!ok) break;
-          mbar_expect_tx(&kv_full[slot], Cfg::TILE_BYTES);
-          uint8_t* dst = sKV + slot * Cfg::TILE_BYTES;
-          const CUtensorMap* tm = which ? &tmV : &tmK;
+      int w = static_cast<int>(atomicAdd(p.work, 1u));
+      for (int seq = 0; ok; ++seq) {
+        const int qbuf = seq & 1;
+        ok = mbar_wait(&q_empty[qbuf], ((seq >> 1) & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_SMEM_EMPTY);
+        if (!ok) break;
+        if (w >= total_items) {
+          work_item[qbuf] = -1;
+          mbar_arrive(&q_full[qbuf]);
+          break;
+        }
+        work_item[qbuf] = w;
+        const FwdItem it = fwd_item<GEN>(p, w);
+        mbar_expect_tx(&q_full[qbuf], Cfg::TILE_BYTES);
 #pragma unroll
-          for (int c = 0; c < Cfg::CHUNKS; ++c)
-            attn_load_box(dst + c * Cfg::CHUNK_BYTES, tm, &kv_full[slot], !GEN, hd, c, h, (j0 + j) * TILE, b);
-          if (++slot == Cfg::SLOTS) { slot = 0; phase ^= 1; }
+        for (int c = 0; c < Cfg::CHUNKS; ++c)
+          attn_load_box(sQ + qbuf * Cfg::TILE_BYTES + c * Cfg::CHUNK_BYTES, &tmQ, &q_full[qbuf], !GEN, hd, c, it.h,
+                        it.qb * TILE, it.b);
+        w = static_cast<int>(atomicAdd(p.work, 1u));  // the next item; its latency hides behind the loads below
+        for (int j = 0; j < it.n_kv && ok; ++j) {
+#pragma unroll 1
+          for (int which = 0; which < 2; ++which) {
+            ok = mbar_wait(&kv_empty[slot], phase ^ 1, abort_flag, p.status, ST_TIMEOUT_SMEM_EMPTY);
+            if (!ok) break;
+            mbar_expect_tx(&kv_full[slot], Cfg::TILE_BYTES);
+            uint8_t* dst = sKV + slot * Cfg::TILE_BYTES;
+            const CUtensorMap* tm = which ? &tmV : &tmK;
+#pragma unroll
+            for (int c = 0; c < Cfg::CHUNKS; ++c)
+              attn_load_box(dst + c * Cfg::CHUNK_BYTES, tm, &kv_full[slot], !GEN, hd, c, it.h, (it.j0 + j) * TILE, it.b);
+            if (++slot == Cfg::SLOTS) { slot = 0; phase ^= 1; }
+          }
         }
       }
       if (!ok) {
@@ -191,17 +248,25 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const bool leader = elect_one();
     const uint32_t idesc_s = make_idesc_f16(BF16 ? 1 : 0, 0, 0, TILE, TILE);
     const uint32_t idesc_o = make_idesc_f16(BF16 ? 1 : 0, 0, 1, TILE, HD);
-    const uint64_t q_desc = make_smem_desc_sw128(smem_u32(sQ), 16, 1024);
+    const uint64_t q_desc0 = make_smem_desc_sw128(smem_u32(sQ), 16, 1024);
     const uint64_t k_desc0 = make_smem_desc_sw128(smem_u32(sKV), 16, 1024);                 // K-major (S = Q K^T)
     const uint64_t v_desc0 = make_smem_desc_sw128(smem_u32(sKV), Cfg::CHUNK_BYTES, 1024);   // MN-major (O = P V)
-    // Ring order is K0 V0 K1 V1 ...: tile i (K of block i/2 when even, V when odd) sits in slot i % SLOTS
-    // and completes phase (i / SLOTS) & 1 of that slot's barriers.
-    bool ok = mbar_wait_warp(q_full, 0, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
-    auto issue_s = [&](int j) -> bool {
-      const int i = 2 * j, slot = i % Cfg::SLOTS;
+    // Ring order is K0 V0 K1 V1 ... over all items of this CTA: tile i (K of block i/2 when even, V when odd) sits
+    // in slot i % SLOTS and completes phase (i / SLOTS) & 1 of that slot's barriers.  `g` counts the blocks of the
+    // items before the current one, so block j of the item is block G = g + j of the CTA, whose parity the
+    // S / P / O barriers follow.
+    // The score product runs one block ahead of the P V product, across item boundaries too: the first scores of
+    // the next item are computed while the softmax warps finish the last block of this one and store its output.
+    bool ok = true;
+    int n_kv_of[2] = {0, 0};  // blocks of the item in each Q buffer
+    int s_seq = 0, s_j = 0;   // the block whose scores were issued last: block s_j of item s_seq
+    bool s_done = false;      // no further scores to issue
+    auto issue_s = [&](int qbuf, bool last_of_item, uint32_t G) -> bool {  // scores of the CTA's block G
+      const uint32_t i = 2 * G, slot = i % Cfg::SLOTS;
       if (!mbar_wait_warp(&kv_full[slot], (i / Cfg::SLOTS) & 1, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL)) return false;
       tc_fence_after();
       if (leader) {
+        const uint64_t q_desc = q_desc0 + ((qbuf * Cfg::TILE_BYTES) >> 4);
         const uint64_t k_desc = k_desc0 + ((slot * Cfg::TILE_BYTES) >> 4);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
@@ -210,66 +275,108 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
         tc_commit(&kv_empty[slot]);
         tc_commit(s_full);
+        if (last_of_item) tc_commit(&q_empty[qbuf]);  // the item's last use of its Q tile
       }
       __syncwarp();
       return true;
     };
-    if (ok) ok = issue_s(0);
-    for (int j = 0; j < n_kv && ok; ++j) {
-      const bool mprof = p.prof != nullptr && lane == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j < 32;
-      // s_free(j): every softmax thread holds the last of S(j) in registers.  That happens a quarter of the
-      // exponential pass before P(j) is complete, so the next score tile is computed under the rest of that pass
-      // and is waiting when the softmax warps come back for it.
-      if (j + 1 < n_kv) {
-        ok = mbar_wait_warp(s_free, j & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
+    // waits for the item in Q buffer seq & 1 and records its length; false when there is none (or on a timeout)
+    auto open_item = [&](int seq) -> bool {
+      const int qbuf = seq & 1;
+      ok = mbar_wait_warp(&q_full[qbuf], (seq >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
+      if (!ok) return false;
+      const int w = work_item[qbuf];
+      if (w < 0) return false;
+      n_kv_of[qbuf] = fwd_item<GEN>(p, w).n_kv;
+      return true;
+    };
+    if (open_item(0)) {
+      ok = issue_s(0, n_kv_of[0] == 1, 0);
+      int p_seq = 0, p_j = 0;  // the block whose P V product comes next
+      for (uint32_t G = 0; ok; ++G) {
+        // scores of block G + 1, as soon as the softmax threads hold the last of S(G) in registers (a quarter of
+        // the exponential pass before P(G) is complete)
+        if (!s_done) {
+          if (s_j + 1 < n_kv_of[s_seq & 1]) {
+            ++s_j;
+          } else if (open_item(s_seq + 1)) {
+            ++s_seq;
+            s_j = 0;
+          } else {
+            s_done = true;
+          }
+          if (!ok) break;
+          if (!s_done) {
+            ok = mbar_wait_warp(s_free, G & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
+            if (!ok) break;
+            ok = issue_s(s_seq & 1, s_j == n_kv_of[s_seq & 1] - 1, G + 1);
+            if (!ok) break;
+          }
+        }
+        // p_full(G): every softmax thread has written P(G) and finished any rescale of O.
+        ok = mbar_wait_warp(p_full, G & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
         if (!ok) break;
-        if (mprof) p.prof[j * 8 + 3] = clock64();
-        ok = issue_s(j + 1);
+        if (p_j == 0 && p_seq > 0) {  // the first product of an item overwrites O: the previous item's must have been read
+          ok = mbar_wait_warp(o_empty, (p_seq - 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
+          if (!ok) break;
+        }
+        const uint32_t i = 2 * G + 1, slot = i % Cfg::SLOTS;
+        ok = mbar_wait_warp(&kv_full[slot], (i / Cfg::SLOTS) & 1, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
         if (!ok) break;
-      }
-      if (mprof) p.prof[j * 8 + 5] = clock64();
-      // p_full(j): every softmax thread has written P(j) and finished any rescale of O.
-      ok = mbar_wait_warp(p_full, j & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
-      if (!ok) break;
-      const int i = 2 * j + 1, slot = i % Cfg::SLOTS;
-      ok = mbar_wait_warp(&kv_full[slot], (i / Cfg::SLOTS) & 1, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
-      if (!ok) break;
-      tc_fence_after();
-      if (leader) {
-        const uint64_t v_desc = v_desc0 + ((slot * Cfg::TILE_BYTES) >> 4);
+        tc_fence_after();
+        if (leader) {
+          const uint64_t v_desc = v_desc0 + ((slot * Cfg::TILE_BYTES) >> 4);
 #pragma unroll
-        for (int kk = 0; kk < TILE / 16; ++kk)  // O += P V: P read from TMEM (8 columns per K = 16), O accumulated there
-          tc_mma_f16_ts(tO, tP + kk * 8, v_desc + ((kk * 2048) >> 4), idesc_o, (kk > 0 || j > 0) ? 1u : 0u);
-        tc_commit(&kv_empty[slot]);
-        tc_commit(o_full);
+          for (int kk = 0; kk < TILE / 16; ++kk)  // O += P V: P read from TMEM (8 columns per K = 16), O accumulated there
+            tc_mma_f16_ts(tO, tP + kk * 8, v_desc + ((kk * 2048) >> 4), idesc_o, (kk > 0 || p_j > 0) ? 1u : 0u);
+          tc_commit(&kv_empty[slot]);
+          tc_commit(o_full);
+        }
+        __syncwarp();
+        if (++p_j == n_kv_of[p_seq & 1]) {
+          p_j = 0;
+          ++p_seq;
+          if (s_done && p_seq > s_seq) break;  // the last block of the last item
+        }
       }
-      __syncwarp();
-      if (mprof) p.prof[j * 8 + 7] = clock64();
     }
   } else {
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;       // row inside the q tile == TMEM lane
-    const int q_idx = qb * TILE + row;         // position in the sequence
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     // m_run is the reference maximum used for P and l; it may lag the true running maximum by up to
     // RESCALE_LOG2 (so P <= 2^RESCALE_LOG2), which keeps rescales of the TMEM accumulator rare.
     constexpr float RESCALE_LOG2 = 8.f;
+    bool ok = true;
+    uint32_t g = 0;  // blocks of the items before the current one (see the MMA warp)
+    for (int seq = 0; ok; ++seq) {
+    const int qbuf = seq & 1;
+    ok = mbar_wait_warp(&q_full[qbuf], (seq >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
+    if (!ok) break;
+    const int w = work_item[qbuf];
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&q_empty[qbuf]);  // the item number has been read by this warp
+    if (w < 0) break;
+    const FwdItem it = fwd_item<GEN>(p, w);
+    const int qb = it.qb, h = it.h, b = it.b, j0 = it.j0, n_kv = it.n_kv;
+    const int* dstart = (GEN && p.doc_start) ? p.doc_start + static_cast<long long>(b) * p.T : nullptr;
+    const int q_idx = qb * TILE + row;         // position in the sequence
     float m_run = -INFINITY, l_run = 0.f;
     // first pair index of this thread's row in the dropout mask: ((b*H + h)*T + q) * ceil(T/2)
     const unsigned long long drop_row =
         ((static_cast<unsigned long long>(b) * p.H + h) * p.T + q_idx) * static_cast<unsigned long long>((p.T + 1) >> 1);
-    bool ok = true;
     const int row_start = (GEN && dstart && q_idx < p.T) ? dstart[q_idx] : 0;  // first key this row may attend to
     const float slope2 = (GEN && p.alibi_slopes) ? p.alibi_slopes[h] * LOG2E : 0.f;
     for (int j = 0; j < n_kv && ok; ++j) {
-      ok = mbar_wait_warp(s_full, j & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
+      const uint32_t G = g + j;
+      ok = mbar_wait_warp(s_full, G & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
       if (!ok) break;
       tc_fence_after();
       const int ja = j0 + j;  // kv block index in the sequence
       // Columns of this block that row q_idx may attend to: [lo, limit).  Only the diagonal block of a
       // causal problem, the last block of a ragged sequence, blocks that a document start cuts and ALiBi need
       // the per-element path; every other block takes the unmasked one (uniform over the warp).
-      const bool prof_on = p.prof != nullptr && row == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j < 32;
+      const bool prof_on = p.prof != nullptr && row == 0 && blockIdx.x == 0 && seq == 0 && j < 32;
       if (prof_on) p.prof[j * 8 + 0] = clock64();
       const int lo = row_start - ja * TILE;
       // `general`: a document start cuts this block for some row of the warp, or ALiBi is on: the per-element path
@@ -285,7 +392,19 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       // while the block maximum is collected alongside; only if some row of the warp outgrew the reference by more
       // than RESCALE_LOG2 (rare once a few blocks have been seen) is the block redone by the two-pass code below.
       bool one_pass_done = false;
-      if (!DROP && !need_mask && j > 0 && __all_sync(0xffffffffu, m_run != -INFINITY)) {
+      if (!DROP && !need_mask && j == 0 && n_kv > 1) {
+        // First block of an item: the maximum of its first 32 columns serves as the reference (in a causal
+        // language model the first key of the sequence, a common attention sink, is among them); should the rest of
+        // the block outgrow it, the block is redone like any other.
+        uint32_t r[32];
+        tmem_ld_32x32(tS + lane_off, r);
+        tmem_ld_wait();
+        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int i = 0; i < 16; ++i) m4[i & 3] = fmax3(m4[i & 3], __uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+        m_run = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * p.scale_log2;
+      }
+      if (!DROP && !need_mask && (j > 0 || n_kv > 1) && __all_sync(0xffffffffu, m_run != -INFINITY)) {
         float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
         uint64_t ps2[2] = {0ull, 0ull};
         const uint64_t scale2 = f2_pack(p.scale_log2, p.scale_log2), neg_m2 = f2_pack(-m_run, -m_run);
@@ -309,15 +428,21 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           uint32_t packed[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            float x0, x1;
-            f2_unpack(f2_fma(f2_pack_bits(r[c & 1][2 * i], r[c & 1][2 * i + 1]), scale2, neg_m2), x0, x1);
-            const float a = exp2f(x0), bb = exp2f(x1);
+            float x0, x1, a, bb;
+            const uint64_t xx = f2_fma(f2_pack_bits(r[c & 1][2 * i], r[c & 1][2 * i + 1]), scale2, neg_m2);
+            if ((i & 3) == 3) {  // every fourth pair on the FMA pipe
+              exp2_poly2(xx, a, bb);
+            } else {
+              f2_unpack(xx, x0, x1);
+              a = exp2f(x0);
+              bb = exp2f(x1);
+            }
             ps2[i & 1] = f2_add(ps2[i & 1], f2_pack(a, bb));
             packed[i] = pack2<BF16>(a, bb);
           }
-          if (c == 0) {
+          if (c == 0 && j > 0) {
             // P V (j-1) must have read P before it is overwritten; it ran under the first chunk's exponentials
-            ok = mbar_wait_warp(o_full, (j - 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
+            ok = mbar_wait_warp(o_full, (G - 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
             if (!ok) break;
             tc_fence_after();
           }
@@ -329,6 +454,71 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           f2_unpack(ps2[0], s0, s1);
           f2_unpack(ps2[1], s2, s3);
           l_run += (s0 + s1) + (s2 + s3);
+          one_pass_done = true;
+        }
+      }
+      // The diagonal block of a causal problem, likewise in one pass: the warp that owns rows 32 q .. 32 q + 31 of
+      // the tile sees chunk c < q whole, chunk q up to its own column, and nothing of the chunks behind it, which
+      // it neither loads nor exponentiates.
+      if (!DROP && !GEN && p.causal && ja == qb && j > 0 && (ja + 1) * TILE <= p.T &&
+          __all_sync(0xffffffffu, m_run != -INFINITY)) {
+        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        float lsum = 0.f;
+        uint64_t ps2[2] = {0ull, 0ull};
+        const uint64_t scale2 = f2_pack(p.scale_log2, p.scale_log2), neg_m2 = f2_pack(-m_run, -m_run);
+        bool overflow = false;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t packed[16];
+          if (c <= quarter) {
+            uint32_t r[32];
+            tmem_ld_32x32(tS + lane_off + c * 32, r);
+            tmem_ld_wait();
+            if (c < quarter) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                m4[i & 3] = fmax3(m4[i & 3], __uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+                float x0, x1;
+                f2_unpack(f2_fma(f2_pack_bits(r[2 * i], r[2 * i + 1]), scale2, neg_m2), x0, x1);
+                const float a = exp2f(x0), bb = exp2f(x1);
+                ps2[i & 1] = f2_add(ps2[i & 1], f2_pack(a, bb));
+                packed[i] = pack2<BF16>(a, bb);
+              }
+            } else {
+              // columns 32 q + i of this chunk are visible to row 32 q + lane for i <= lane
+              float bm = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (i <= lane) bm = fmaxf(bm, __uint_as_float(r[i]));
+              overflow = __any_sync(0xffffffffu, bm * p.scale_log2 - m_run > RESCALE_LOG2);
+              if (overflow) break;
+              tc_fence_before();
+              mbar_arrive(s_free);  // the rest of S(j) is not needed: the tensor pipe may write S(j+1)
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                const float a = (2 * i <= lane) ? exp2f(fmaf(__uint_as_float(r[2 * i]), p.scale_log2, -m_run)) : 0.f;
+                const float bb = (2 * i + 1 <= lane) ? exp2f(fmaf(__uint_as_float(r[2 * i + 1]), p.scale_log2, -m_run)) : 0.f;
+                lsum += a + bb;
+                packed[i] = pack2<BF16>(a, bb);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) packed[i] = 0u;
+          }
+          if (c == 0) {
+            ok = mbar_wait_warp(o_full, (G - 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
+            if (!ok) break;
+            tc_fence_after();
+          }
+          tmem_st_32x16(tP + lane_off + c * 16, packed);
+        }
+        if (!ok) break;
+        if (!overflow) {
+          float s0, s1, s2, s3;
+          f2_unpack(ps2[0], s0, s1);
+          f2_unpack(ps2[1], s2, s3);
+          l_run += ((s0 + s1) + (s2 + s3)) + lsum;
           one_pass_done = true;
         }
       }
@@ -371,7 +561,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       } else {
         // P V (j-1) was issued after S(j); it must have completed before P(j) overwrites its operand or O
         // is rescaled.  It ran under the pass above, so this wait is normally already satisfied.
-        ok = mbar_wait_warp(o_full, (j - 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
+        ok = mbar_wait_warp(o_full, (G - 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
         if (!ok) break;
         tc_fence_after();
         if (__any_sync(0xffffffffu, m_new - m_run > RESCALE_LOG2)) {
@@ -468,7 +658,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tc_fence_before();
       mbar_arrive(p_full);
     }
-    if (ok) ok = mbar_wait_warp(o_full, (n_kv - 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
+    if (ok) ok = mbar_wait_warp(o_full, (g + n_kv - 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
     tc_fence_after();
     if (ok) {
       const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
@@ -479,7 +669,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
       for (int c = 0; c < HD / 32; ++c) {
         tmem_ld_wait();
-        if (c + 1 < HD / 32) tmem_ld_32x32(tO + lane_off + (c + 1) * 32, r[(c + 1) & 1]);
+        if (c + 1 < HD / 32) {
+          tmem_ld_32x32(tO + lane_off + (c + 1) * 32, r[(c + 1) & 1]);
+        } else {
+          tc_fence_before();
+          mbar_arrive(o_empty);  // O is in registers: the next item's first product may overwrite the accumulator
+        }
         if (q_idx < p.T) {
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
@@ -495,6 +690,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       if (p.lse && q_idx < p.T) p.lse[(static_cast<long long>(b) * p.H + h) * p.T + q_idx] = (m_run + log2f(l_run)) * LN2;
     }
+    g += n_kv;
+    }  // items
   }
 
   tc_fence_before();
@@ -502,6 +699,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+  // Every CTA has drawn its last (refused) item by now; the one that finishes last leaves the counters at zero for
+  // the next launch that is given this pair.
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(p.work + 1, 1u) == gridDim.x - 1) {
+      p.work[0] = 0;
+      p.work[1] = 0;
+    }
   }
 }
 
@@ -525,17 +731,49 @@ struct AttnBwdParams {
   int hd;                     // real head size (<= HD of the kernel)
   const int* doc_start;       // [B, T] or null
   const float* alibi_slopes;  // [H] or null
+  int B, n_kvblocks;          // work items: one per (batch, head, kv block)
+  unsigned* work;             // {next item, CTAs finished} of this launch, both zero before and after it
 };
+
+// The backward kernel is persistent too (one CTA per SM).  Item w is kv block w % n_kvblocks of (batch, head) group
+// w / n_kvblocks: low blocks have the longest causal q range and are drawn first within their head.
+struct BwdItem {
+  int nb, h, b, m_start, n_it;
+};
+template <bool GEN>
+__device__ __forceinline__ BwdItem bwd_item(const AttnBwdParams& p, int w) {
+  BwdItem it;
+  const int group = w / p.n_kvblocks;
+  it.nb = w - group * p.n_kvblocks;
+  it.h = group % p.H;
+  it.b = group / p.H;
+  const int n_q = (p.T + TILE - 1) / TILE;
+  it.m_start = p.causal ? it.nb : 0;
+  int m_end = n_q;
+  // Document starts never decrease along the sequence: once the first row of a q tile starts after the last key of
+  // this block, that tile and every later one see none of its keys.
+  if (GEN && p.doc_start) {
+    const int* dstart = p.doc_start + static_cast<long long>(it.b) * p.T;
+    const int kv_last = it.nb * TILE + TILE - 1;
+    for (int m = it.m_start + 1; m < n_q; ++m)
+      if (dstart[min(m * TILE, p.T - 1)] > kv_last) { m_end = m; break; }
+  }
+  it.n_it = m_end - it.m_start;
+  return it;
+}
 
 template <int HD>
 struct BwdCfg {
   static constexpr int CHUNKS = HD / 64;
   static constexpr uint32_t TILE_BYTES = TILE * HD * 2;
   static constexpr uint32_t CHUNK_BYTES = TILE * 128;
-  static constexpr int QSTAGES = (HD == 64) ? 2 : 1;
+  // Q / dO ring: a stage is released by the last products of its iteration and refilled from L2 in one to two
+  // thousand cycles, about two thirds of an iteration, so three stages are needed for the refill to be early enough
+  static constexpr int QSTAGES = (HD == 64) ? 3 : 1;
+  static constexpr int KVBUFS = 1;
   static constexpr uint32_t P_BYTES = TILE * TILE * 2;
   static constexpr uint32_t STAGE_BYTES = 8 * 4096;  // one 32 x 32 fp32 box per element-wise warp
-  static constexpr uint32_t SMEM = TILE_BYTES * (2 + 2 * QSTAGES) + 2 * P_BYTES + STAGE_BYTES + 1024 + 256;
+  static constexpr uint32_t SMEM = TILE_BYTES * (2 * KVBUFS + 2 * QSTAGES) + 2 * P_BYTES + STAGE_BYTES + 1024 + 256;
   static constexpr uint32_t TMEM_COLS = 512;
   static constexpr uint32_t S_COL = 0, DP_COL = 128, DV_COL = 256, DK_COL = 256 + HD;
   static constexpr uint32_t DQ_COL = (HD == 64) ? 384 : 0;  // HD = 128 reuses the S columns
@@ -551,48 +789,45 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   constexpr int QS = Cfg::QSTAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sK = smem;
-  uint8_t* sV = sK + Cfg::TILE_BYTES;
-  uint8_t* sQ = sV + Cfg::TILE_BYTES;
+  constexpr int KVB = Cfg::KVBUFS;
+  uint8_t* sK = smem;                          // KVB tiles
+  uint8_t* sV = sK + KVB * Cfg::TILE_BYTES;    // KVB tiles
+  uint8_t* sQ = sV + KVB * Cfg::TILE_BYTES;
   uint8_t* sDO = sQ + QS * Cfg::TILE_BYTES;
   uint8_t* sP = sDO + QS * Cfg::TILE_BYTES;
   uint8_t* sDS = sP + Cfg::P_BYTES;
   uint8_t* sStage = sDS + Cfg::P_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sStage + Cfg::STAGE_BYTES);
-  uint64_t* kv_full = bars;
-  uint64_t* qdo_full = bars + 1;
+  uint64_t* kv_full = bars;              // [KVB]
+  uint64_t* kv_empty = kv_full + KVB;    // [KVB]
+  uint64_t* qdo_full = kv_empty + KVB;
   uint64_t* qdo_empty = qdo_full + QS;
   uint64_t* sdp_full = qdo_empty + QS;
   uint64_t* pds_full = sdp_full + 1;
   uint64_t* dq_full = pds_full + 1;
   uint64_t* dq_empty = dq_full + 1;
   uint64_t* dkv_full = dq_empty + 1;
-  uint64_t* pds_free = dkv_full + 1;
+  uint64_t* dkv_empty = dkv_full + 1;
+  uint64_t* pds_free = dkv_empty + 1;
   uint64_t* sdp_free = pds_free + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sdp_free + 1);
+  uint64_t* epi_done = sdp_free + 1;
+  volatile int* work_item = reinterpret_cast<volatile int*>(epi_done + 1);  // [KVB]: item in each K / V buffer, -1 = none
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(const_cast<int*>(work_item) + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int nb = blockIdx.x;  // kv block; low indices have the longest causal q range and launch first
-  const int h = blockIdx.y, b = blockIdx.z;
-  const int n_q = (p.T + TILE - 1) / TILE;
-  const int m_start = p.causal ? nb : 0;
-  // Document starts never decrease along the sequence: once the first row of a q tile starts after the last key of
-  // this block, that tile and every later one see none of its keys.
-  const int* dstart = (GEN && p.doc_start) ? p.doc_start + static_cast<long long>(b) * p.T : nullptr;
+  const int total_items = p.n_kvblocks * p.H * p.B;
   const int hd = GEN ? p.hd : HD;
-  int m_end = n_q;
-  if (GEN && dstart) {
-    const int kv_last = nb * TILE + TILE - 1;
-    for (int m = m_start + 1; m < n_q; ++m)
-      if (dstart[min(m * TILE, p.T - 1)] > kv_last) { m_end = m; break; }
-  }
-  const int n_it = m_end - m_start;
+  // readers of work_item besides the MMA warp: the element-wise warps and, when they have work, the drain warps
+  constexpr int ITEM_READERS = 8 + (Cfg::DQ_ALIASES_S ? 0 : 4);
 
   if (p.status && *reinterpret_cast<volatile int*>(p.status) != 0) return;
 
   if (threadIdx.x == 0) {
-    mbar_init(kv_full, 1);
+    for (int s = 0; s < KVB; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1 + ITEM_READERS);  // the commit behind the item's last products + one arrival per reader warp
+    }
     for (int s = 0; s < QS; ++s) {
       mbar_init(&qdo_full[s], 1);
       mbar_init(&qdo_empty[s], 1);
@@ -602,6 +837,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     mbar_init(dq_full, 1);
     mbar_init(dq_empty, Cfg::DQ_ALIASES_S ? 256 : 128);  // drained by the element-wise warps when aliased, else by the drain warps
     mbar_init(dkv_full, 1);
+    mbar_init(dkv_empty, 256);
+    mbar_init(epi_done, 256);
     mbar_init(pds_free, 1);
     mbar_init(sdp_free, 256);
     *abort_flag = 0;
@@ -619,28 +856,42 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_expect_tx(kv_full, 2 * Cfg::TILE_BYTES);
-#pragma unroll
-      for (int c = 0; c < Cfg::CHUNKS; ++c) {
-        attn_load_box(sK + c * Cfg::CHUNK_BYTES, &tmK, kv_full, !GEN, hd, c, h, nb * TILE, b);
-        attn_load_box(sV + c * Cfg::CHUNK_BYTES, &tmV, kv_full, !GEN, hd, c, h, nb * TILE, b);
-      }
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int it = 0; it < n_it && ok; ++it) {
-        const int m = m_start + it;
-        ok = mbar_wait(&qdo_empty[stage], phase ^ 1, abort_flag, p.status, ST_TIMEOUT_SMEM_EMPTY);
+      int w = static_cast<int>(atomicAdd(p.work, 1u));
+      for (int seq = 0; ok; ++seq) {
+        const int kb = seq % KVB;
+        ok = mbar_wait(&kv_empty[kb], ((seq / KVB) & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_SMEM_EMPTY);
         if (!ok) break;
-        mbar_expect_tx(&qdo_full[stage], 2 * Cfg::TILE_BYTES);
+        if (w >= total_items) {
+          work_item[kb] = -1;
+          mbar_arrive(&kv_full[kb]);
+          break;
+        }
+        work_item[kb] = w;
+        const BwdItem it = bwd_item<GEN>(p, w);
+        mbar_expect_tx(&kv_full[kb], 2 * Cfg::TILE_BYTES);
 #pragma unroll
         for (int c = 0; c < Cfg::CHUNKS; ++c) {
-          attn_load_box(sQ + stage * Cfg::TILE_BYTES + c * Cfg::CHUNK_BYTES, &tmQ, &qdo_full[stage], !GEN, hd, c, h,
-                        m * TILE, b);
-          attn_load_box(sDO + stage * Cfg::TILE_BYTES + c * Cfg::CHUNK_BYTES, &tmDO, &qdo_full[stage], !GEN, hd, c, h,
-                        m * TILE, b);
+          attn_load_box(sK + kb * Cfg::TILE_BYTES + c * Cfg::CHUNK_BYTES, &tmK, &kv_full[kb], !GEN, hd, c, it.h, it.nb * TILE, it.b);
+          attn_load_box(sV + kb * Cfg::TILE_BYTES + c * Cfg::CHUNK_BYTES, &tmV, &kv_full[kb], !GEN, hd, c, it.h, it.nb * TILE, it.b);
         }
-        if (++stage == QS) { stage = 0; phase ^= 1; }
+        w = static_cast<int>(atomicAdd(p.work, 1u));  // the next item; its latency hides behind the loads below
+        for (int i = 0; i < it.n_it && ok; ++i) {
+          const int m = it.m_start + i;
+          ok = mbar_wait(&qdo_empty[stage], phase ^ 1, abort_flag, p.status, ST_TIMEOUT_SMEM_EMPTY);
+          if (!ok) break;
+          mbar_expect_tx(&qdo_full[stage], 2 * Cfg::TILE_BYTES);
+#pragma unroll
+          for (int c = 0; c < Cfg::CHUNKS; ++c) {
+            attn_load_box(sQ + stage * Cfg::TILE_BYTES + c * Cfg::CHUNK_BYTES, &tmQ, &qdo_full[stage], !GEN, hd, c, it.h,
+                          m * TILE, it.b);
+            attn_load_box(sDO + stage * Cfg::TILE_BYTES + c * Cfg::CHUNK_BYTES, &tmDO, &qdo_full[stage], !GEN, hd, c, it.h,
+                          m * TILE, it.b);
+          }
+          if (++stage == QS) { stage = 0; phase ^= 1; }
+        }
       }
       if (!ok) {
         const unsigned long long t0 = globaltimer_ns();
@@ -654,9 +905,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const uint32_t idesc_s = make_idesc_f16(dt, 0, 0, TILE, TILE);   // Q K^T and dO V^T
     const uint32_t idesc_t = make_idesc_f16(dt, 1, 1, TILE, HD);     // P^T dO and dS^T Q
     const uint32_t idesc_q = make_idesc_f16(dt, 0, 1, TILE, HD);     // dS K
-    const uint64_t k_km = make_smem_desc_sw128(smem_u32(sK), 16, 1024);
-    const uint64_t v_km = make_smem_desc_sw128(smem_u32(sV), 16, 1024);
-    const uint64_t k_mn = make_smem_desc_sw128(smem_u32(sK), Cfg::CHUNK_BYTES, 1024);
+    const uint64_t k_km0 = make_smem_desc_sw128(smem_u32(sK), 16, 1024);
+    const uint64_t v_km0 = make_smem_desc_sw128(smem_u32(sV), 16, 1024);
+    const uint64_t k_mn0 = make_smem_desc_sw128(smem_u32(sK), Cfg::CHUNK_BYTES, 1024);
     const uint64_t p_mn = make_smem_desc_sw128(smem_u32(sP), Cfg::CHUNK_BYTES, 1024);
     const uint64_t ds_mn = make_smem_desc_sw128(smem_u32(sDS), Cfg::CHUNK_BYTES, 1024);
     const uint64_t ds_km = make_smem_desc_sw128(smem_u32(sDS), 16, 1024);
@@ -664,82 +915,110 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const uint64_t q_mn0 = make_smem_desc_sw128(smem_u32(sQ), Cfg::CHUNK_BYTES, 1024);
     const uint64_t do_km0 = make_smem_desc_sw128(smem_u32(sDO), 16, 1024);
     const uint64_t do_mn0 = make_smem_desc_sw128(smem_u32(sDO), Cfg::CHUNK_BYTES, 1024);
-    bool ok = mbar_wait_warp(kv_full, 0, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
-    // Q / dO tiles of iteration `it` sit in stage it % QS and complete phase (it / QS) & 1 of that stage's barriers.
-    auto issue_sdp = [&](int it) -> bool {  // S = Q K^T and dP = dO V^T of iteration `it`
-      const int stage = it % QS;
-      if (!mbar_wait_warp(&qdo_full[stage], (it / QS) & 1, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL)) return false;
-      tc_fence_after();
-      const uint32_t st_off = (stage * Cfg::TILE_BYTES) >> 4;
-      if (leader) {
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t off = ((kk >> 2) * Cfg::CHUNK_BYTES + (kk & 3) * 32) >> 4;
-          tc_mma_f16(tmem_base + Cfg::S_COL, q_km0 + st_off + off, k_km + off, idesc_s, kk > 0 ? 1u : 0u);
-        }
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t off = ((kk >> 2) * Cfg::CHUNK_BYTES + (kk & 3) * 32) >> 4;
-          tc_mma_f16(tmem_base + Cfg::DP_COL, do_km0 + st_off + off, v_km + off, idesc_s, kk > 0 ? 1u : 0u);
-        }
-        tc_commit(sdp_full);
-      }
-      __syncwarp();
-      return true;
-    };
     // Without aliasing (HD = 64) the scores of the next iteration are issued before the three gradient products
     // of this one: the element-wise warps then work on S / dP (it+1) while dQ, dV, dK (it) run on the tensor
     // pipe.  With dQ aliased onto the S columns (HD = 128) the order stays strictly sequential.
     constexpr bool PIPELINED = !Cfg::DQ_ALIASES_S;
-    if (ok && n_it > 0) ok = issue_sdp(0);
-    for (int it = 0; it < n_it && ok; ++it) {
-      const int stage = it % QS;
-      const uint32_t st_off = (stage * Cfg::TILE_BYTES) >> 4;
-      if (PIPELINED && it + 1 < n_it) {
-        // S / dP of this iteration are in the element-wise warps' registers: the next pair is computed while
-        // they finish P and dS
-        ok = mbar_wait_warp(sdp_free, it & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
-        if (!ok) break;
-        ok = issue_sdp(it + 1);
-        if (!ok) break;
-      }
-      // P and dS of this iteration are in shared memory
-      ok = mbar_wait_warp(pds_full, it & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
+    bool ok = true;
+    uint32_t gi = 0;  // iterations of the items before the current one: iteration `it` of the item is iteration
+                      // G = gi + it of the CTA, whose parity the per-iteration barriers follow; its Q / dO tiles sit in
+                      // stage G % QS and complete phase (G / QS) & 1 of that stage's barriers
+    for (int seq = 0; ok; ++seq) {
+      const int kb = seq % KVB;
+      ok = mbar_wait_warp(&kv_full[kb], (seq / KVB) & 1, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
       if (!ok) break;
-      if (it > 0) {  // dQ of the previous iteration has been drained from TMEM
-        ok = mbar_wait_warp(dq_empty, (it - 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
+      const int w = work_item[kb];
+      if (w < 0) break;
+      const int n_it = bwd_item<GEN>(p, w).n_it;
+      const uint32_t kb_off = (kb * Cfg::TILE_BYTES) >> 4;
+      const uint64_t k_km = k_km0 + kb_off, v_km = v_km0 + kb_off, k_mn = k_mn0 + kb_off;
+      auto issue_sdp = [&](uint32_t G) -> bool {  // S = Q K^T and dP = dO V^T of the CTA's iteration G
+        const int stage = G % QS;
+        if (!mbar_wait_warp(&qdo_full[stage], (G / QS) & 1, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL)) return false;
+        tc_fence_after();
+        const uint32_t st_off = (stage * Cfg::TILE_BYTES) >> 4;
+        if (leader) {
+#pragma unroll
+          for (int kk = 0; kk < HD / 16; ++kk) {
+            const uint32_t off = ((kk >> 2) * Cfg::CHUNK_BYTES + (kk & 3) * 32) >> 4;
+            tc_mma_f16(tmem_base + Cfg::S_COL, q_km0 + st_off + off, k_km + off, idesc_s, kk > 0 ? 1u : 0u);
+          }
+#pragma unroll
+          for (int kk = 0; kk < HD / 16; ++kk) {
+            const uint32_t off = ((kk >> 2) * Cfg::CHUNK_BYTES + (kk & 3) * 32) >> 4;
+            tc_mma_f16(tmem_base + Cfg::DP_COL, do_km0 + st_off + off, v_km + off, idesc_s, kk > 0 ? 1u : 0u);
+          }
+          tc_commit(sdp_full);
+        }
+        __syncwarp();
+        return true;
+      };
+      // The S / dP columns of the previous item's last iteration must be free: read into registers (pipelined), or
+      // the dQ that aliases them drained (HD = 128).
+      if (gi > 0) {
+        ok = PIPELINED ? mbar_wait_warp(sdp_free, (gi - 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)
+                       : mbar_wait_warp(dq_empty, (gi - 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
         if (!ok) break;
       }
-      tc_fence_after();
-      if (leader) {
-        const uint32_t acc = it > 0 ? 1u : 0u;
-#pragma unroll
-        for (int kk = 0; kk < TILE / 16; ++kk) {  // dQ = dS K      (K = kv rows)
-          const uint32_t a_off = ((kk >> 2) * Cfg::CHUNK_BYTES + (kk & 3) * 32) >> 4;
-          tc_mma_f16(tmem_base + Cfg::DQ_COL, ds_km + a_off, k_mn + ((kk * 2048) >> 4), idesc_q, kk > 0 ? 1u : 0u);
+      ok = issue_sdp(gi);
+      for (int it = 0; it < n_it && ok; ++it) {
+        const uint32_t G = gi + it;
+        const int stage = G % QS;
+        const uint32_t st_off = (stage * Cfg::TILE_BYTES) >> 4;
+        if (PIPELINED && it + 1 < n_it) {
+          // S / dP of this iteration are in the element-wise warps' registers: the next pair is computed while
+          // they finish P and dS
+          ok = mbar_wait_warp(sdp_free, G & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
+          if (!ok) break;
+          ok = issue_sdp(G + 1);
+          if (!ok) break;
         }
-        tc_commit(dq_full);
-#pragma unroll
-        for (int kk = 0; kk < TILE / 16; ++kk) {  // dV += P^T dO   (K = q rows)
-          const uint32_t off = (kk * 2048) >> 4;
-          tc_mma_f16(tmem_base + Cfg::DV_COL, p_mn + off, do_mn0 + st_off + off, idesc_t, (kk > 0) ? 1u : acc);
-        }
-#pragma unroll
-        for (int kk = 0; kk < TILE / 16; ++kk) {  // dK += dS^T Q
-          const uint32_t off = (kk * 2048) >> 4;
-          tc_mma_f16(tmem_base + Cfg::DK_COL, ds_mn + off, q_mn0 + st_off + off, idesc_t, (kk > 0) ? 1u : acc);
-        }
-        tc_commit(&qdo_empty[stage]);
-        tc_commit(pds_free);  // P / dS in shared memory may be overwritten
-        if (it == n_it - 1) tc_commit(dkv_full);
-      }
-      __syncwarp();
-      if (!PIPELINED && it + 1 < n_it) {
-        // dQ (it) lives in the S columns: it must be drained before the next scores are written there
-        ok = mbar_wait_warp(dq_empty, it & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
+        // P and dS of this iteration are in shared memory
+        ok = mbar_wait_warp(pds_full, G & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
         if (!ok) break;
-        ok = issue_sdp(it + 1);
+        if (G > 0) {  // dQ of the previous iteration has been drained from TMEM
+          ok = mbar_wait_warp(dq_empty, (G - 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
+          if (!ok) break;
+        }
+        if (it == 0 && seq > 0) {  // dK / dV of the previous item have been read out of their accumulators
+          ok = mbar_wait_warp(dkv_empty, (seq - 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
+          if (!ok) break;
+        }
+        tc_fence_after();
+        if (leader) {
+          const uint32_t acc = it > 0 ? 1u : 0u;
+#pragma unroll
+          for (int kk = 0; kk < TILE / 16; ++kk) {  // dQ = dS K      (K = kv rows)
+            const uint32_t a_off = ((kk >> 2) * Cfg::CHUNK_BYTES + (kk & 3) * 32) >> 4;
+            tc_mma_f16(tmem_base + Cfg::DQ_COL, ds_km + a_off, k_mn + ((kk * 2048) >> 4), idesc_q, kk > 0 ? 1u : 0u);
+          }
+          tc_commit(dq_full);
+#pragma unroll
+          for (int kk = 0; kk < TILE / 16; ++kk) {  // dV += P^T dO   (K = q rows)
+            const uint32_t off = (kk * 2048) >> 4;
+            tc_mma_f16(tmem_base + Cfg::DV_COL, p_mn + off, do_mn0 + st_off + off, idesc_t, (kk > 0) ? 1u : acc);
+          }
+#pragma unroll
+          for (int kk = 0; kk < TILE / 16; ++kk) {  // dK += dS^T Q
+            const uint32_t off = (kk * 2048) >> 4;
+            tc_mma_f16(tmem_base + Cfg::DK_COL, ds_mn + off, q_mn0 + st_off + off, idesc_t, (kk > 0) ? 1u : acc);
+          }
+          tc_commit(&qdo_empty[stage]);
+          tc_commit(pds_free);  // P / dS in shared memory may be overwritten
+          if (it == n_it - 1) {
+            tc_commit(dkv_full);
+            tc_commit(&kv_empty[kb]);  // the item's last use of its K / V tiles
+          }
+        }
+        __syncwarp();
+        if (!PIPELINED && it + 1 < n_it) {
+          // dQ (it) lives in the S columns: it must be drained before the next scores are written there
+          ok = mbar_wait_warp(dq_empty, G & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
+          if (!ok) break;
+          ok = issue_sdp(G + 1);
+        }
       }
+      gi += n_it;
     }
   } else if (warp >= 10) {
     // dQ drain warps (one per TMEM lane quarter): TMEM -> swizzled fp32 staging -> bulk add into dq_accum, off
@@ -749,14 +1028,26 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
       uint8_t* boxes = sStage + (warp - 10) * 8192;  // two 32 x 32 fp32 boxes (dQ columns 0-31 and 32-63)
       bool ok = true;
+      uint32_t gi = 0;
+      for (int seq = 0; ok; ++seq) {
+      const int kb = seq % KVB;
+      ok = mbar_wait_warp(&kv_full[kb], (seq / KVB) & 1, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
+      if (!ok) break;
+      const int w = work_item[kb];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&kv_empty[kb]);  // the item number has been read by this warp
+      if (w < 0) break;
+      const BwdItem item = bwd_item<GEN>(p, w);
+      const int n_it = item.n_it, m_start = item.m_start, h = item.h, b = item.b;
       for (int dit = 0; dit < n_it && ok; ++dit) {
-        ok = mbar_wait_warp(dq_full, dit & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
+        const uint32_t G = gi + dit;
+        ok = mbar_wait_warp(dq_full, G & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
         if (!ok) break;
         tc_fence_after();
         uint32_t r0[32], r1[32];
         tmem_ld_32x32(tmem_base + Cfg::DQ_COL + lane_off, r0);
         tmem_ld_32x32(tmem_base + Cfg::DQ_COL + lane_off + 32, r1);
-        if (dit > 0) {  // the bulk adds of the previous iteration must have read the boxes
+        if (G > 0) {  // the bulk adds of the previous iteration must have read the boxes
           if (lane == 0) bulk_wait_read_all();
           __syncwarp();
         }
@@ -781,6 +1072,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           bulk_commit_group();
         }
       }
+      gi += n_it;
+      }  // items
       if (lane == 0) bulk_wait_all();  // shared memory must outlive the bulk adds that read it
     }
   } else {
@@ -791,20 +1084,28 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t col0 = half * 64;
     const float scale_log2 = p.scale * LOG2E;
-    const long long bh = static_cast<long long>(b) * p.H + h;
     // dQ staging for the bulk reduce: one swizzled 32-row x 32-column fp32 box per warp
     constexpr int DQ_BOXES = HD / 64;  // boxes per warp and iteration
     uint8_t* stage_buf = sStage + (warp - 2) * 4096;
     bool ok = true;
     int staged = 0;  // bulk reduces issued so far from this warp's staging box
-    // dQ tile of iteration `dit`: TMEM -> swizzled fp32 staging -> one bulk add per 32 x 32 box into dq_accum
-    auto drain_dq = [&](int dit) -> bool {
-      const bool dprof = p.prof != nullptr && row == 0 && half == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && dit < 31;
-      if (dprof) p.prof[256 + (dit + 1) * 8 + 5] = clock64();
-      if (!mbar_wait_warp(dq_full, dit & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) return false;
+    uint32_t gi = 0;  // iterations of the items before the current one (see the MMA warp)
+    for (int seq = 0; ok; ++seq) {
+    const int kb = seq % KVB;
+    ok = mbar_wait_warp(&kv_full[kb], (seq / KVB) & 1, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
+    if (!ok) break;
+    const int w = work_item[kb];
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&kv_empty[kb]);  // the item number has been read by this warp
+    if (w < 0) break;
+    const BwdItem item = bwd_item<GEN>(p, w);
+    const int nb = item.nb, h = item.h, b = item.b, m_start = item.m_start, n_it = item.n_it;
+    const int* dstart = (GEN && p.doc_start) ? p.doc_start + static_cast<long long>(b) * p.T : nullptr;
+    const long long bh = static_cast<long long>(b) * p.H + h;
+    // dQ tile of the CTA's iteration G (q tile dm): TMEM -> swizzled fp32 staging -> one bulk add per 32 x 32 box
+    auto drain_dq = [&](uint32_t G, int dm) -> bool {
+      if (!mbar_wait_warp(dq_full, G & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) return false;
       tc_fence_after();
-      if (dprof) p.prof[256 + (dit + 1) * 8 + 6] = clock64();
-      const int dm = m_start + dit;
       const bool rows_in_range = dm * TILE + quarter * 32 < p.T;  // rows past T inside a box are dropped by the copy engine
 #pragma unroll
       for (int c = 0; c < DQ_BOXES; ++c) {
@@ -815,7 +1116,6 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           __syncwarp();
         }
         tmem_ld_wait();
-        if (dprof) p.prof[256 + (dit + 1) * 8 + 7] = clock64();
         uint8_t* dst = stage_buf + lane * 128;
 #pragma unroll
         for (int u = 0; u < 8; ++u)
@@ -837,12 +1137,26 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       return true;
     };
+    // the row statistics of an iteration are fetched one iteration ahead: their latency would otherwise sit in front
+    // of every iteration
+    float lse_next = 0.f, delta_next = 0.f;
+    if (m_start * TILE + row < p.T) {
+      lse_next = p.lse[bh * p.T + m_start * TILE + row];
+      delta_next = p.delta[bh * p.T + m_start * TILE + row];
+    }
     for (int it = 0; it < n_it && ok; ++it) {
       const int m = m_start + it;
       const int q_idx = m * TILE + row;
       const bool q_ok = q_idx < p.T;
-      const float lse2 = q_ok ? p.lse[bh * p.T + q_idx] * LOG2E : 0.f;
-      const float delta = q_ok ? p.delta[bh * p.T + q_idx] : 0.f;
+      const float lse_raw = lse_next, delta = delta_next;
+      if (it + 1 < n_it && q_idx + TILE < p.T) {
+        lse_next = p.lse[bh * p.T + q_idx + TILE];
+        delta_next = p.delta[bh * p.T + q_idx + TILE];
+      } else {
+        lse_next = 0.f;
+        delta_next = 0.f;
+      }
+      const float lse2 = lse_raw * LOG2E;
       int limit = p.T - nb * TILE;
       if (p.causal) limit = min(limit, q_idx - nb * TILE + 1);
       limit = q_ok ? max(0, min(limit, TILE)) : 0;
@@ -852,13 +1166,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       // document start and ALiBi need the per-element path
       const bool general = GEN && (p.alibi_slopes != nullptr || (dstart != nullptr && __any_sync(0xffffffffu, lo > 0)));
       const bool need_mask = (p.causal && m == nb) || ((m + 1) * TILE > p.T) || ((nb + 1) * TILE > p.T) || general;
-      const bool prof_on = p.prof != nullptr && row == 0 && half == 0 && blockIdx.x == 0 && blockIdx.y == 0 &&
-                           blockIdx.z == 0 && it < 32;
-      if (prof_on) p.prof[256 + it * 8 + 0] = clock64();
-      ok = mbar_wait_warp(sdp_full, it & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
+      const uint32_t G = gi + it;
+      ok = mbar_wait_warp(sdp_full, G & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
       if (!ok) break;
       tc_fence_after();
-      if (prof_on) p.prof[256 + it * 8 + 1] = clock64();
       // P and dS of this thread's 64 columns, kept in registers until shared memory is free to take them
       uint32_t pp[2][16], dd[2][16];
       {
@@ -926,9 +1237,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
         }
       }
-      if (it > 0) {
+      if (G > 0) {
         // the products of the previous iteration that read P / dS from shared memory have completed
-        ok = mbar_wait_warp(pds_free, (it - 1) & 1, abort_flag, p.status, ST_TIMEOUT_SMEM_EMPTY);
+        ok = mbar_wait_warp(pds_free, (G - 1) & 1, abort_flag, p.status, ST_TIMEOUT_SMEM_EMPTY);
         if (!ok) break;
       }
       {
@@ -943,55 +1254,76 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
         }
       }
-      if (prof_on) p.prof[256 + it * 8 + 2] = clock64();
       tc_fence_before();
       fence_proxy_async_smem();
       mbar_arrive(pds_full);
       // With aliasing (HD = 128) dQ (it) is drained here, before the next scores overwrite its columns; otherwise
       // the drain warps take care of it concurrently.
       if (Cfg::DQ_ALIASES_S) {
-        ok = drain_dq(it);
+        ok = drain_dq(G, m);
         if (!ok) break;
       }
-      if (prof_on) p.prof[256 + it * 8 + 4] = clock64();
     }
     // dK / dV of this kv block are complete when the products of the last iteration have been committed.
-    const int kv_idx = nb * TILE + row;
-    if (ok && n_it > 0) ok = mbar_wait_warp(dkv_full, 0, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
+    if (ok) ok = mbar_wait_warp(dkv_full, seq & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
     tc_fence_after();
-    if (ok && n_it > 0) {
+    if (ok) {
       // The TMEM loads are warp-wide (.sync.aligned): every lane runs them; only the
       // global stores are predicated on the row being inside the sequence.
-      const bool kv_ok = kv_idx < p.T;
-      const long long kv_row = kv_ok ? kv_idx : 0;
-      uint16_t* dk = reinterpret_cast<uint16_t*>(p.dk) + static_cast<long long>(b) * p.dk_batch_stride +
-                     kv_row * p.dk_row_stride + h * hd + half * (HD / 2);
-      uint16_t* dv = reinterpret_cast<uint16_t*>(p.dv) + static_cast<long long>(b) * p.dv_batch_stride +
-                     kv_row * p.dv_row_stride + h * hd + half * (HD / 2);
+      // Each lane owns one row of the accumulators, so direct stores would touch 32 lines with 16 bytes each.  The
+      // packed values go through a swizzled 32 x 64-byte tile of shared memory instead (this warp's 4 KB of the P
+      // tile, idle until the next item's first iteration) and leave as 8 rows x 64 contiguous bytes per instruction.
+      uint8_t* tbuf = sP + (warp - 2) * 4096;
+      const int st_row = lane >> 2, st_vec = lane & 3;
+      const int row0 = nb * TILE + quarter * 32;
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {
-        uint16_t* dst = which ? dv : dk;
+        uint16_t* base = reinterpret_cast<uint16_t*>(which ? p.dv : p.dk) +
+                         static_cast<long long>(b) * (which ? p.dv_batch_stride : p.dk_batch_stride) + h * hd + half * (HD / 2);
+        const long long rs = which ? p.dv_row_stride : p.dk_row_stride;
         const uint32_t col = (which ? Cfg::DV_COL : Cfg::DK_COL) + half * (HD / 2);
 #pragma unroll 1
         for (int c = 0; c < HD / 64; ++c) {
           uint32_t r[32];
           tmem_ld_32x32(tmem_base + col + lane_off + c * 32, r);
           tmem_ld_wait();
-          if (kv_ok) {
+          if (which == 1 && c == HD / 64 - 1) {
+            tc_fence_before();
+            mbar_arrive(dkv_empty);  // the accumulators are in registers: the next item's products may overwrite them
+          }
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              if (GEN && half * (HD / 2) + c * 32 + v * 8 >= hd) break;  // padded columns of a head size below HD
-              uint4 ov;
-              ov.x = pack2<BF16>(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
-              ov.y = pack2<BF16>(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
-              ov.z = pack2<BF16>(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
-              ov.w = pack2<BF16>(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
-              *reinterpret_cast<uint4*>(dst + c * 32 + v * 8) = ov;
+          for (int v = 0; v < 4; ++v) {
+            uint4 ov;
+            ov.x = pack2<BF16>(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+            ov.y = pack2<BF16>(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+            ov.z = pack2<BF16>(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+            ov.w = pack2<BF16>(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+            *reinterpret_cast<uint4*>(tbuf + lane * 64 + ((v ^ ((lane >> 1) & 3)) << 4)) = ov;
+          }
+          __syncwarp();
+          const int colh = half * (HD / 2) + c * 32 + st_vec * 8;  // first of this lane's 8 columns inside the head
+          if (!GEN || colh < hd) {
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+              const int rr = jj * 8 + st_row;
+              if (row0 + rr < p.T) {
+                const uint4 ov = *reinterpret_cast<const uint4*>(tbuf + rr * 64 + ((st_vec ^ ((rr >> 1) & 3)) << 4));
+                *reinterpret_cast<uint4*>(base + static_cast<long long>(row0 + rr) * rs + c * 32 + st_vec * 8) = ov;
+              }
             }
           }
+          __syncwarp();
         }
       }
     }
+    // the transposition buffers are part of the P tile: every warp must be done with its own before any warp
+    // writes P of the next item
+    if (ok) {
+      mbar_arrive(epi_done);
+      ok = mbar_wait_warp(epi_done, seq & 1, abort_flag, p.status, ST_TIMEOUT_SMEM_EMPTY);
+    }
+    gi += n_it;
+    }  // items
     // shared memory must outlive the bulk reduces that read it
     if (lane == 0) bulk_wait_all();
   }
@@ -1001,6 +1333,15 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+  // Every CTA has drawn its last (refused) item by now; the one that finishes last leaves the counters at zero for
+  // the next launch that is given this pair.
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(p.work + 1, 1u) == gridDim.x - 1) {
+      p.work[0] = 0;
+      p.work[1] = 0;
+    }
   }
 }
 
@@ -1060,32 +1401,72 @@ static int make_tmap_bthd(CUtensorMap* out, const void* base, int B, int T, int 
   return encode_tiled_16bit(out, base, 4, dims, strides, box, bf16) == CUDA_SUCCESS ? 0 : -3;
 }
 
+// Work counters of the persistent forward kernel: a pool of {next item, CTAs finished} pairs handed to launches in
+// rotation, so that launches which overlap on a device (different streams) do not share a pair.  Zero at module
+// load; every launch leaves its pair at zero.
+constexpr int ATT_WORK_PAIRS = 64;
+__device__ unsigned g_attn_work[2 * ATT_WORK_PAIRS];
+
+static unsigned* next_work_pair() {
+  static unsigned* base[64] = {nullptr};
+  static unsigned seq = 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!base[dev]) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_attn_work) != cudaSuccess) return nullptr;
+    base[dev] = static_cast<unsigned*>(ptr);
+  }
+  return base[dev] + 2 * (seq++ % ATT_WORK_PAIRS);
+}
+
 template <int HD, bool BF16, bool DROP, bool GEN>
-static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnFwdParams& p,
+static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, AttnFwdParams p,
                       int B, cudaStream_t stream) {
   auto kern = flash_fwd_kernel<HD, BF16, DROP, GEN>;
   static bool configured = false;
+  static int sms = 0;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdCfg<HD>::SMEM) != cudaSuccess)
       return -10;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return -10;
     configured = true;
   }
-  dim3 grid((p.T + TILE - 1) / TILE, p.H, B);
+  p.B = B;
+  p.n_qblocks = (p.T + TILE - 1) / TILE;
+  p.work = next_work_pair();
+  if (!p.work) return -10;
+  const long long items = static_cast<long long>(p.n_qblocks) * p.H * B;
+  if (items > 0x7fffffffLL - 4096) return -2;
+  const long long resident = static_cast<long long>(sms) * ((HD == 64) ? 2 : 1);
+  const unsigned grid = static_cast<unsigned>(items < resident ? items : resident);
   kern<<<grid, ATT_THREADS, FwdCfg<HD>::SMEM, stream>>>(tq, tk, tv, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
 template <int HD, bool BF16, bool DROP, bool GEN>
 static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
-                      const CUtensorMap& tdq, const AttnBwdParams& p, int B, cudaStream_t stream) {
+                      const CUtensorMap& tdq, AttnBwdParams p, int B, cudaStream_t stream) {
   auto kern = flash_bwd_kernel<HD, BF16, DROP, GEN>;
   static bool configured = false;
+  static int sms = 0;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg<HD>::SMEM) != cudaSuccess)
       return -10;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return -10;
     configured = true;
   }
-  dim3 grid((p.T + TILE - 1) / TILE, p.H, B);
+  p.B = B;
+  p.n_kvblocks = (p.T + TILE - 1) / TILE;
+  p.work = next_work_pair();
+  if (!p.work) return -10;
+  const long long items = static_cast<long long>(p.n_kvblocks) * p.H * B;
+  if (items > 0x7fffffffLL - 4096) return -2;
+  const unsigned grid = static_cast<unsigned>(items < sms ? items : sms);  // one CTA per SM (512 TMEM columns each)
   kern<<<grid, ATT_BWD_THREADS, BwdCfg<HD>::SMEM, stream>>>(tq, tk, tv, tdo, tdq, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
