@@ -235,6 +235,14 @@ def main(argv=None):
     y, mean, rstd = F.layer_norm_fwd(x, g, b, 1e-5)
     dy = torch.randn_like(x)
     report("layernorm_bwd", 0, 3.0 * M * D * 2, lambda: F.layer_norm_bwd(dy, x, mean, rstd, g), None)
+    # with the residual-branch gradient added in the same pass, as the fused layer calls it
+    report("layernorm_bwd_add", 0, 4.0 * M * D * 2, lambda: F.layer_norm_bwd(dy, x, mean, rstd, g, add=y), None)
+    for name, width in (("qkv", 3 * D), ("fc1", FFN)):
+        wide = torch.randn(M, width, device=dev, dtype=dt)
+        db = torch.zeros(width, device=dev, dtype=dt)
+        report(f"bias_grad_colsum_{name}", 0, 1.0 * M * width * 2, lambda: F.colsum(wide, out16=db, accumulate=True),
+               lambda: torch.sum(wide, dim=0, dtype=torch.float32))
+        del wide, db
     rows = min(M, 4096)
     logits = torch.randn(rows, V, device=dev, dtype=dt)
     tgt = torch.randint(0, V, (rows,), device=dev)
