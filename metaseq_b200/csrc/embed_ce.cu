@@ -599,23 +599,14 @@ colsum_direct_kernel(const uint16_t* __restrict__ x, long long ld, int rows, int
 #pragma unroll
   for (int j = 0; j < 8; ++j) s[j] = 0.f;
   if (col < N) {
-    // four rows per trip, their loads issued before any is used: enough bytes in flight to keep HBM busy
-    for (int r = r0 + ty; r < r1; r += 32) {
-      uint4 a[4];
+    for (int r = r0 + ty; r < r1; r += 8) {
+      const uint4 a = *reinterpret_cast<const uint4*>(x + static_cast<long long>(r) * ld + col);
+      const uint32_t w[4] = {a.x, a.y, a.z, a.w};
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int rr = r + 8 * u;
-        a[u] = rr < r1 ? *reinterpret_cast<const uint4*>(x + static_cast<long long>(rr) * ld + col) : make_uint4(0u, 0u, 0u, 0u);
-      }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const uint32_t w[4] = {a[u].x, a[u].y, a[u].z, a[u].w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 t = unpack2<BF16>(w[j]);
-          s[2 * j] += t.x;
-          s[2 * j + 1] += t.y;
-        }
+      for (int j = 0; j < 4; ++j) {
+        const float2 t = unpack2<BF16>(w[j]);
+        s[2 * j] += t.x;
+        s[2 * j + 1] += t.y;
       }
     }
   }

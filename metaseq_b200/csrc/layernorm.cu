@@ -22,16 +22,6 @@ __device__ __forceinline__ void load8(const uint16_t* p, float (&f)[8]) {
   }
 }
 template <bool BF16>
-__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
-  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    float2 t = unpack2<BF16>(w[j]);
-    f[2 * j] = t.x;
-    f[2 * j + 1] = t.y;
-  }
-}
-template <bool BF16>
 __device__ __forceinline__ void store8(uint16_t* p, const float (&f)[8]) {
   uint4 o;
   o.x = pack2<BF16>(f[0], f[1]);
@@ -221,32 +211,9 @@ layernorm_bwd_kernel(const uint16_t* __restrict__ dy, const uint16_t* __restrict
     if (v < nvec && gamma) load8<BF16>(gamma + v * 8, g[i]);
   }
   const float inv_d = 1.f / static_cast<float>(D);
-  // The next row's operands are requested before this row's two block-wide reductions, whose barriers would
-  // otherwise leave the memory system idle once per row.
-  uint4 nx[VPT], nd[VPT], na[VPT];
-  float n_mean = 0.f, n_rstd = 0.f;
-  auto fetch = [&](int row) {
-    const long long off = static_cast<long long>(row) * D;
-    n_mean = rms ? 0.f : mean_in[row];
-    n_rstd = rstd_in[row];
-#pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-      const int v = threadIdx.x + i * LN_THREADS;
-      if (v < nvec) {
-        nx[i] = *reinterpret_cast<const uint4*>(x + off + v * 8);
-        nd[i] = *reinterpret_cast<const uint4*>(dy + off + v * 8);
-        if (add) na[i] = *reinterpret_cast<const uint4*>(add + off + v * 8);
-      }
-    }
-  };
-  if (static_cast<int>(blockIdx.x) < rows) fetch(blockIdx.x);
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const long long off = static_cast<long long>(row) * D;
-    const float mean = n_mean, rstd = n_rstd;
-    uint4 cx[VPT], cd[VPT], ca[VPT];
-#pragma unroll
-    for (int i = 0; i < VPT; ++i) { cx[i] = nx[i]; cd[i] = nd[i]; ca[i] = na[i]; }
-    if (row + static_cast<int>(gridDim.x) < rows) fetch(row + gridDim.x);
+    const float mean = rms ? 0.f : mean_in[row], rstd = rstd_in[row];
     float xh[VPT][8], gd[VPT][8];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
@@ -254,8 +221,8 @@ layernorm_bwd_kernel(const uint16_t* __restrict__ dy, const uint16_t* __restrict
       const int v = threadIdx.x + i * LN_THREADS;
       if (v < nvec) {
         float xv[8], dv[8];
-        unpack8<BF16>(cx[i], xv);
-        unpack8<BF16>(cd[i], dv);
+        load8<BF16>(x + off + v * 8, xv);
+        load8<BF16>(dy + off + v * 8, dv);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           xh[i][j] = (xv[j] - mean) * rstd;
@@ -278,7 +245,7 @@ layernorm_bwd_kernel(const uint16_t* __restrict__ dy, const uint16_t* __restrict
         for (int j = 0; j < 8; ++j) o[j] = rstd * (gd[i][j] - m1 - xh[i][j] * m2);
         if (add) {
           float a[8];
-          unpack8<BF16>(ca[i], a);
+          load8<BF16>(add + off + v * 8, a);
 #pragma unroll
           for (int j = 0; j < 8; ++j) o[j] += a[j];
         }
