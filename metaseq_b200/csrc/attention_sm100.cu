@@ -778,6 +778,10 @@ struct BwdCfg {
   static constexpr uint32_t S_COL = 0, DP_COL = 128, DV_COL = 256, DK_COL = 256 + HD;
   static constexpr uint32_t DQ_COL = (HD == 64) ? 384 : 0;  // HD = 128 reuses the S columns
   static constexpr bool DQ_ALIASES_S = (HD != 64);
+  // At HD = 64 the last 64 columns hold dS as 16-bit values (row = q, two per column): the dQ = dS K product takes
+  // its A operand from there instead of from shared memory, which is the bottleneck of this kernel.
+  static constexpr bool DS_IN_TMEM = (HD == 64);
+  static constexpr uint32_t DS16_COL = 448;
 };
 
 template <int HD, bool BF16, bool DROP, bool GEN>
@@ -989,8 +993,13 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           const uint32_t acc = it > 0 ? 1u : 0u;
 #pragma unroll
           for (int kk = 0; kk < TILE / 16; ++kk) {  // dQ = dS K      (K = kv rows)
-            const uint32_t a_off = ((kk >> 2) * Cfg::CHUNK_BYTES + (kk & 3) * 32) >> 4;
-            tc_mma_f16(tmem_base + Cfg::DQ_COL, ds_km + a_off, k_mn + ((kk * 2048) >> 4), idesc_q, kk > 0 ? 1u : 0u);
+            if (Cfg::DS_IN_TMEM) {
+              tc_mma_f16_ts(tmem_base + Cfg::DQ_COL, tmem_base + Cfg::DS16_COL + kk * 8, k_mn + ((kk * 2048) >> 4), idesc_q,
+                            kk > 0 ? 1u : 0u);
+            } else {
+              const uint32_t a_off = ((kk >> 2) * Cfg::CHUNK_BYTES + (kk & 3) * 32) >> 4;
+              tc_mma_f16(tmem_base + Cfg::DQ_COL, ds_km + a_off, k_mn + ((kk * 2048) >> 4), idesc_q, kk > 0 ? 1u : 0u);
+            }
           }
           tc_commit(dq_full);
 #pragma unroll
@@ -1242,6 +1251,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         ok = mbar_wait_warp(pds_free, (G - 1) & 1, abort_flag, p.status, ST_TIMEOUT_SMEM_EMPTY);
         if (!ok) break;
       }
+      if (Cfg::DS_IN_TMEM) {
+        // pds_free (G - 1) above also covers the dQ product of the previous iteration, the reader of these columns
+#pragma unroll
+        for (int c = 0; c < 2; ++c) tmem_st_32x16(tmem_base + Cfg::DS16_COL + lane_off + half * 32 + c * 16, dd[c]);
+      }
       {
         const uint32_t chunk_off = half * Cfg::CHUNK_BYTES;
 #pragma unroll
@@ -1254,6 +1268,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
         }
       }
+      if (Cfg::DS_IN_TMEM) tmem_st_wait();
       tc_fence_before();
       fence_proxy_async_smem();
       mbar_arrive(pds_full);
