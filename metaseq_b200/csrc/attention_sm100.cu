@@ -131,7 +131,8 @@ struct FwdCfg {
   // K/V ring.  Four slots at HD = 64 also keep the footprint above a third of an SM's shared memory, so
   // at most two CTAs (2 x 256 TMEM columns) are ever co-resident and tcgen05.alloc never has to wait.
   static constexpr int SLOTS = (HD == 64) ? 4 : 3;
-  static constexpr uint32_t SMEM = TILE_BYTES * (2 + SLOTS) + 1024 + 256;  // two Q tiles: the next item's is prefetched
+  static constexpr uint32_t EPI_BYTES = 4 * 2048;  // per softmax warp: a 32-row x 64-byte transposition buffer for O
+  static constexpr uint32_t SMEM = TILE_BYTES * (2 + SLOTS) + EPI_BYTES + 1024 + 256;  // two Q tiles: the next item's is prefetched
   // TMEM columns: S (128 fp32), O (HD fp32), P (128 16-bit values = 64 columns)
   static constexpr uint32_t O_COL = 128;
   static constexpr uint32_t P_COL = 128 + HD;
@@ -150,7 +151,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;  // two tiles
   uint8_t* sKV = sQ + 2 * Cfg::TILE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + Cfg::SLOTS * Cfg::TILE_BYTES);
+  uint8_t* sEpi = sKV + Cfg::SLOTS * Cfg::TILE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sEpi + Cfg::EPI_BYTES);
   uint64_t* q_full = bars;        // [2]
   uint64_t* q_empty = bars + 2;   // [2]
   uint64_t* kv_full = bars + 4;
@@ -662,8 +664,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     tc_fence_after();
     if (ok) {
       const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
-      uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + static_cast<long long>(b) * p.o_batch_stride +
-                    static_cast<long long>(q_idx < p.T ? q_idx : 0) * p.o_row_stride + h * hd;
+      // Each lane owns one row of O, so direct stores would touch 32 lines with 16 bytes each.  The packed values go
+      // through a swizzled 32-row x 64-byte buffer of this warp and leave as 8 rows x 64 contiguous bytes per store.
+      uint8_t* tbuf = sEpi + quarter * 2048;
+      const int st_row = lane >> 2, st_vec = lane & 3;
+      const int row0 = qb * TILE + quarter * 32;
+      uint16_t* obase = reinterpret_cast<uint16_t*>(p.out) + static_cast<long long>(b) * p.o_batch_stride + h * hd;
       uint32_t r[2][32];
       tmem_ld_32x32(tO + lane_off, r[0]);
 #pragma unroll
@@ -675,18 +681,27 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           tc_fence_before();
           mbar_arrive(o_empty);  // O is in registers: the next item's first product may overwrite the accumulator
         }
-        if (q_idx < p.T) {
 #pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            if (GEN && c * 32 + v * 8 >= hd) break;  // padded columns of a head size below HD
-            uint4 ov;
-            ov.x = pack2<BF16>(__uint_as_float(r[c & 1][v * 8 + 0]) * inv_l, __uint_as_float(r[c & 1][v * 8 + 1]) * inv_l);
-            ov.y = pack2<BF16>(__uint_as_float(r[c & 1][v * 8 + 2]) * inv_l, __uint_as_float(r[c & 1][v * 8 + 3]) * inv_l);
-            ov.z = pack2<BF16>(__uint_as_float(r[c & 1][v * 8 + 4]) * inv_l, __uint_as_float(r[c & 1][v * 8 + 5]) * inv_l);
-            ov.w = pack2<BF16>(__uint_as_float(r[c & 1][v * 8 + 6]) * inv_l, __uint_as_float(r[c & 1][v * 8 + 7]) * inv_l);
-            *reinterpret_cast<uint4*>(o + c * 32 + v * 8) = ov;
+        for (int v = 0; v < 4; ++v) {
+          uint4 ov;
+          ov.x = pack2<BF16>(__uint_as_float(r[c & 1][v * 8 + 0]) * inv_l, __uint_as_float(r[c & 1][v * 8 + 1]) * inv_l);
+          ov.y = pack2<BF16>(__uint_as_float(r[c & 1][v * 8 + 2]) * inv_l, __uint_as_float(r[c & 1][v * 8 + 3]) * inv_l);
+          ov.z = pack2<BF16>(__uint_as_float(r[c & 1][v * 8 + 4]) * inv_l, __uint_as_float(r[c & 1][v * 8 + 5]) * inv_l);
+          ov.w = pack2<BF16>(__uint_as_float(r[c & 1][v * 8 + 6]) * inv_l, __uint_as_float(r[c & 1][v * 8 + 7]) * inv_l);
+          *reinterpret_cast<uint4*>(tbuf + lane * 64 + ((v ^ ((lane >> 1) & 3)) << 4)) = ov;
+        }
+        __syncwarp();
+        if (!GEN || c * 32 + st_vec * 8 < hd) {  // padded columns of a head size below HD are not stored
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            const int rr = jj * 8 + st_row;
+            if (row0 + rr < p.T) {
+              const uint4 ov = *reinterpret_cast<const uint4*>(tbuf + rr * 64 + ((st_vec ^ ((rr >> 1) & 3)) << 4));
+              *reinterpret_cast<uint4*>(obase + static_cast<long long>(row0 + rr) * p.o_row_stride + c * 32 + st_vec * 8) = ov;
+            }
           }
         }
+        __syncwarp();
       }
       if (p.lse && q_idx < p.T) p.lse[(static_cast<long long>(b) * p.H + h) * p.T + q_idx] = (m_run + log2f(l_run)) * LN2;
     }
