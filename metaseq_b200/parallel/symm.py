@@ -250,6 +250,34 @@ class PeerComm:
         if self.transport == "auto" and self.rs_transport == "pull" and not self.heap.multicast_ptr \
                 and "MSQ_COMM_RS" not in os.environ:
             self.rs_transport = "ce"  # without the switch doing the additions the pushed form is the faster one
+        if self.transport == "auto" and self.rs_transport == "pull" and "MSQ_COMM_RS" not in os.environ \
+                and not self._pull_self_test():
+            logger.warning("the in-switch reduce-scatter failed its start-up check on this machine: using the "
+                           "pushed form (peer DMA + slot sum) instead")
+            self.rs_transport = "ce"
+
+    def _pull_self_test(self) -> bool:
+        """One small pull reduce-scatter with known values before the default relies on it (group size and switch
+        configuration differ between machines).  Every rank gets the same verdict."""
+        per = 2048  # fp16 elements per shard
+        try:
+            key = self.alloc_full(per * self.world, torch.float16)
+            grads = self.alloc_symmetric(per * self.world, torch.float16)
+            grads.fill_(float(self.rank + 1))
+            shard = torch.empty(per, dtype=torch.float32, device=self.device)
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=self.group)
+            self.reduce_scatter(shard, grads, key, scale=0.5)
+            self.barrier()  # nobody's buffer is reused before every owner has read it
+            torch.cuda.synchronize(self.device)
+            want = 0.5 * self.world * (self.world + 1) / 2.0
+            good = bool(torch.all(shard == want)) and _lib.check_status(self.device) == 0
+        except Exception as e:  # noqa: BLE001
+            logger.warning(f"in-switch reduce-scatter check raised {type(e).__name__}: {e}")
+            good = False
+        verdict = torch.tensor([1 if good else 0], dtype=torch.int32, device=self.device)
+        dist.all_reduce(verdict, op=dist.ReduceOp.MIN, group=self.group)
+        return bool(verdict.item())
 
     @property
     def pulls_gradients(self) -> bool:
