@@ -726,6 +726,456 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
 }
 
+
+// ---------------------------------------------------------- forward, head size 128
+// Two q tiles (256 rows) per work item on one CTA per SM: the tensor pipe alternates between the tiles, so that the
+// score and P V products of one tile run while the softmax warps of the other tile are busy.  With 128 fp32
+// columns each for S and O of both tiles the 512 TMEM columns are full: P is written over the first 64 columns of
+// its own S (the columns it overwrites have been read by then), and the next score product of a tile is issued
+// behind its P V product.  Warps: TMA, MMA issue, four softmax warps per tile (320 threads).  Causal masking only;
+// dropout, document starts, ALiBi and padded head sizes stay on the one-tile kernel above.
+constexpr int ATT128_THREADS = 320;
+struct Fwd128Cfg {
+  static constexpr int HD = 128;
+  static constexpr int CHUNKS = 2;
+  static constexpr uint32_t TILE_BYTES = TILE * HD * 2;  // 32 KB
+  static constexpr uint32_t CHUNK_BYTES = TILE * 128;    // 16 KB
+  static constexpr int SLOTS = 4;                        // K0 V0 K1 V1
+  static constexpr uint32_t EPI_BYTES = 8 * 2048;
+  static constexpr uint32_t SMEM = TILE_BYTES * (2 + SLOTS) + EPI_BYTES + 1024 + 256;
+};
+
+struct Fwd128Item {
+  int qp, h, b;
+  int n[2];    // kv blocks of tile 0 / 1 (0: the tile lies beyond the sequence)
+  int n_iter;  // max of the two
+};
+__device__ __forceinline__ Fwd128Item fwd128_item(const AttnFwdParams& p, int w) {
+  Fwd128Item it;
+  const int group = w / p.n_qblocks;  // n_qblocks counts tile pairs for this kernel
+  it.qp = p.n_qblocks - 1 - (w - group * p.n_qblocks);
+  it.h = group % p.H;
+  it.b = group / p.H;
+  const int n_kv = (p.T + TILE - 1) / TILE;
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int qb = 2 * it.qp + t;
+    it.n[t] = qb * TILE < p.T ? (p.causal ? min(qb + 1, n_kv) : n_kv) : 0;
+  }
+  it.n_iter = max(it.n[0], it.n[1]);
+  return it;
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(ATT128_THREADS, 1)
+flash_fwd128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const AttnFwdParams p) {
+  using Cfg = Fwd128Cfg;
+  constexpr int HD = 128;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;  // tile 0, tile 1
+  uint8_t* sKV = sQ + 2 * Cfg::TILE_BYTES;
+  uint8_t* sEpi = sKV + Cfg::SLOTS * Cfg::TILE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sEpi + Cfg::EPI_BYTES);
+  uint64_t* q_full = bars;
+  uint64_t* q_empty = bars + 1;
+  uint64_t* kv_full = bars + 2;
+  uint64_t* kv_empty = kv_full + Cfg::SLOTS;
+  uint64_t* s_full = kv_empty + Cfg::SLOTS;  // [2]
+  uint64_t* p_full = s_full + 2;             // [2]
+  uint64_t* o_full = p_full + 2;             // [2]
+  uint64_t* o_empty = o_full + 2;            // [2]
+  volatile int* work_item = reinterpret_cast<volatile int*>(o_empty + 2);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(const_cast<int*>(work_item) + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total_items = p.n_qblocks * p.H * p.B;
+
+  if (p.status && *reinterpret_cast<volatile int*>(p.status) != 0) return;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    mbar_init(q_empty, 1 + 8);  // the commit behind the item's last score product + one arrival per softmax warp
+    for (int s = 0; s < Cfg::SLOTS; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&s_full[t], 1);
+      mbar_init(&p_full[t], 128);
+      mbar_init(&o_full[t], 1);
+      mbar_init(&o_empty[t], 128);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int slot = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int w = static_cast<int>(atomicAdd(p.work, 1u));
+      for (int seq = 0; ok; ++seq) {
+        ok = mbar_wait(q_empty, (seq & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_SMEM_EMPTY);
+        if (!ok) break;
+        if (w >= total_items) {
+          *work_item = -1;
+          mbar_arrive(q_full);
+          break;
+        }
+        *work_item = w;
+        const Fwd128Item it = fwd128_item(p, w);
+        mbar_expect_tx(q_full, 2 * Cfg::TILE_BYTES);
+#pragma unroll
+        for (int t = 0; t < 2; ++t)
+#pragma unroll
+          for (int c = 0; c < Cfg::CHUNKS; ++c)  // rows past the sequence are filled with zeros by the copy engine
+            attn_load_box(sQ + t * Cfg::TILE_BYTES + c * Cfg::CHUNK_BYTES, &tmQ, q_full, true, HD, c, it.h,
+                          (2 * it.qp + t) * TILE, it.b);
+        w = static_cast<int>(atomicAdd(p.work, 1u));
+        for (int j = 0; j < it.n_iter && ok; ++j) {
+#pragma unroll 1
+          for (int which = 0; which < 2; ++which) {
+            ok = mbar_wait(&kv_empty[slot], phase ^ 1, abort_flag, p.status, ST_TIMEOUT_SMEM_EMPTY);
+            if (!ok) break;
+            mbar_expect_tx(&kv_full[slot], Cfg::TILE_BYTES);
+            uint8_t* dst = sKV + slot * Cfg::TILE_BYTES;
+            const CUtensorMap* tm = which ? &tmV : &tmK;
+#pragma unroll
+            for (int c = 0; c < Cfg::CHUNKS; ++c)
+              attn_load_box(dst + c * Cfg::CHUNK_BYTES, tm, &kv_full[slot], true, HD, c, it.h, j * TILE, it.b);
+            if (++slot == Cfg::SLOTS) { slot = 0; phase ^= 1; }
+          }
+        }
+      }
+      if (!ok) {
+        const unsigned long long t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 2000000ull) { }
+      }
+    }
+  } else if (warp == 1) {
+    const bool leader = elect_one();
+    const uint32_t idesc_s = make_idesc_f16(BF16 ? 1 : 0, 0, 0, TILE, TILE);
+    const uint32_t idesc_o = make_idesc_f16(BF16 ? 1 : 0, 0, 1, TILE, HD);
+    const uint64_t q_desc0 = make_smem_desc_sw128(smem_u32(sQ), 16, 1024);
+    const uint64_t k_desc0 = make_smem_desc_sw128(smem_u32(sKV), 16, 1024);                // K-major (S = Q K^T)
+    const uint64_t v_desc0 = make_smem_desc_sw128(smem_u32(sKV), Cfg::CHUNK_BYTES, 1024);  // MN-major (O = P V)
+    bool ok = true;
+    uint32_t gkv = 0;             // kv blocks of the items before the current one (ring position)
+    uint32_t g[2] = {0, 0};       // blocks of each tile before the current item (parity of its barriers)
+    uint32_t items_of[2] = {0, 0};  // items in which each tile was active (parity of o_empty)
+    for (int seq = 0; ok; ++seq) {
+      ok = mbar_wait_warp(q_full, seq & 1, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
+      if (!ok) break;
+      const int w = *work_item;
+      if (w < 0) break;
+      const Fwd128Item it = fwd128_item(p, w);
+      // S_t (j): waits for K (j); frees it if no later product of the item reads it; the item's last score product
+      // also frees the Q tiles
+      auto issue_s = [&](int t, int j) -> bool {
+        const uint32_t i = 2 * (gkv + j), slot = i % Cfg::SLOTS;
+        if (!mbar_wait_warp(&kv_full[slot], (i / Cfg::SLOTS) & 1, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL)) return false;
+        tc_fence_after();
+        if (leader) {
+          const uint64_t q_desc = q_desc0 + ((t * Cfg::TILE_BYTES) >> 4);
+          const uint64_t k_desc = k_desc0 + ((slot * Cfg::TILE_BYTES) >> 4);
+#pragma unroll
+          for (int kk = 0; kk < HD / 16; ++kk) {
+            const uint32_t off = ((kk >> 2) * Cfg::CHUNK_BYTES + (kk & 3) * 32) >> 4;
+            tc_mma_f16(tmem_base + t * 128, q_desc + off, k_desc + off, idesc_s, kk > 0 ? 1u : 0u);
+          }
+          tc_commit(&s_full[t]);
+          if (t == 1 || j >= it.n[1]) tc_commit(&kv_empty[slot]);  // tile 1 is the later reader when it is active
+          const bool last_s = (t == 1) ? (j == it.n[1] - 1 && it.n[1] >= it.n[0]) : (j == it.n[0] - 1 && it.n[0] > it.n[1]);
+          if (last_s) tc_commit(q_empty);
+        }
+        __syncwarp();
+        return true;
+      };
+      for (int t = 0; t < 2 && ok; ++t)
+        if (it.n[t] > 0) ok = issue_s(t, 0);
+      for (int j = 0; j < it.n_iter && ok; ++j) {
+#pragma unroll 1
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (j >= it.n[t]) continue;
+          // P_t (j) is in TMEM (over the first half of S_t) and any rescale of O_t is done
+          ok = mbar_wait_warp(&p_full[t], (g[t] + j) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
+          if (!ok) break;
+          if (j == 0 && items_of[t] > 0) {  // the first product of an item overwrites O_t: the previous item's must have been read
+            ok = mbar_wait_warp(&o_empty[t], (items_of[t] - 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY);
+            if (!ok) break;
+          }
+          const uint32_t i = 2 * (gkv + j) + 1, slot = i % Cfg::SLOTS;
+          ok = mbar_wait_warp(&kv_full[slot], (i / Cfg::SLOTS) & 1, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
+          if (!ok) break;
+          tc_fence_after();
+          if (leader) {
+            const uint64_t v_desc = v_desc0 + ((slot * Cfg::TILE_BYTES) >> 4);
+#pragma unroll
+            for (int kk = 0; kk < TILE / 16; ++kk)
+              tc_mma_f16_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + kk * 8, v_desc + ((kk * 2048) >> 4), idesc_o,
+                            (kk > 0 || j > 0) ? 1u : 0u);
+            tc_commit(&o_full[t]);
+            if (t == 1 || j >= it.n[1]) tc_commit(&kv_empty[slot]);
+          }
+          __syncwarp();
+          // the next scores of this tile go behind its P V product (they overwrite P); the other tile's softmax
+          // runs meanwhile
+          if (j + 1 < it.n[t]) ok = issue_s(t, j + 1);
+        }
+      }
+      gkv += it.n_iter;
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        g[t] += it.n[t];
+        if (it.n[t] > 0) ++items_of[t];
+      }
+    }
+  } else {
+    const int t = (warp - 2) >> 2;  // tile of this warp
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t tS = tmem_base + t * 128, tO = tmem_base + 256 + t * 128, tP = tS;
+    constexpr float RESCALE_LOG2 = 8.f;
+    bool ok = true;
+    uint32_t g = 0;
+    for (int seq = 0; ok; ++seq) {
+      ok = mbar_wait_warp(q_full, seq & 1, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL);
+      if (!ok) break;
+      const int w = *work_item;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(q_empty);
+      if (w < 0) break;
+      const Fwd128Item it = fwd128_item(p, w);
+      const int n_kv = it.n[t];
+      if (n_kv == 0) continue;
+      const int qb = 2 * it.qp + t, h = it.h, b = it.b;
+      const int q_idx = qb * TILE + row;
+      float m_run = -INFINITY, l_run = 0.f;
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const uint32_t G = g + j;
+        // S (j) was issued behind P V (j - 1) of this tile: O and the P columns are free as soon as it is here
+        ok = mbar_wait_warp(&s_full[t], G & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
+        if (!ok) break;
+        tc_fence_after();
+        const bool need_mask = (p.causal && j == qb) || ((j + 1) * TILE > p.T);
+        int limit = p.T - j * TILE;
+        if (p.causal) limit = min(limit, q_idx - j * TILE + 1);
+        limit = max(0, min(limit, TILE));
+        bool done = false;
+        // The diagonal tile of a causal problem (full tiles only): the warp that owns rows 32 q .. 32 q + 31 sees chunk
+        // c < q whole, chunk q up to its own column and nothing behind it.
+        const bool diag = p.causal && j == qb && (j + 1) * TILE <= p.T;
+        if (j == 0 && n_kv > 1 && !need_mask) {
+          // first block of an item: the maximum of its first 32 columns serves as the reference; should the rest of
+          // the block outgrow it, the block is redone like any other
+          uint32_t r0[32];
+          tmem_ld_32x32(tS + lane_off, r0);
+          tmem_ld_wait();
+          float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+          for (int i = 0; i < 16; ++i) m4[i & 3] = fmax3(m4[i & 3], __uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1]));
+          m_run = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * p.scale_log2;
+        }
+        if ((!need_mask || (diag && j > 0)) && (j > 0 || n_kv > 1) && __all_sync(0xffffffffu, m_run != -INFINITY)) {
+          // one pass: exponentials against the running reference, P kept in registers until the block maximum has
+          // shown that the reference still holds (P overwrites S, so a redo must be decided before any store)
+          float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+          uint64_t ps2[2] = {0ull, 0ull};
+          float lsum = 0.f;
+          const uint64_t scale2 = f2_pack(p.scale_log2, p.scale_log2), neg_m2 = f2_pack(-m_run, -m_run);
+          uint32_t r[2][32];
+          uint32_t packed[4][16];
+          const int last_c = diag ? quarter : 3;  // chunks behind it are invisible to this warp's rows
+          tmem_ld_32x32(tS + lane_off, r[0]);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            if (c <= last_c) {
+              tmem_ld_wait();
+              if (c + 1 < 4 && c + 1 <= last_c) tmem_ld_32x32(tS + lane_off + (c + 1) * 32, r[(c + 1) & 1]);
+              if (diag && c == last_c) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                  const bool v0 = 2 * i <= lane, v1 = 2 * i + 1 <= lane;
+                  const float e0 = __uint_as_float(r[c & 1][2 * i]), e1 = __uint_as_float(r[c & 1][2 * i + 1]);
+                  if (v0) m4[i & 3] = fmaxf(m4[i & 3], e0);
+                  if (v1) m4[i & 3] = fmaxf(m4[i & 3], e1);
+                  const float a = v0 ? exp2f(fmaf(e0, p.scale_log2, -m_run)) : 0.f;
+                  const float bb = v1 ? exp2f(fmaf(e1, p.scale_log2, -m_run)) : 0.f;
+                  lsum += a + bb;
+                  packed[c][i] = pack2<BF16>(a, bb);
+                }
+              } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                  m4[i & 3] = fmax3(m4[i & 3], __uint_as_float(r[c & 1][2 * i]), __uint_as_float(r[c & 1][2 * i + 1]));
+                  float x0, x1, a, bb;
+                  const uint64_t xx = f2_fma(f2_pack_bits(r[c & 1][2 * i], r[c & 1][2 * i + 1]), scale2, neg_m2);
+                  if ((i & 3) == 3) {
+                    exp2_poly2(xx, a, bb);
+                  } else {
+                    f2_unpack(xx, x0, x1);
+                    a = exp2f(x0);
+                    bb = exp2f(x1);
+                  }
+                  ps2[i & 1] = f2_add(ps2[i & 1], f2_pack(a, bb));
+                  packed[c][i] = pack2<BF16>(a, bb);
+                }
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) packed[c][i] = 0u;
+            }
+          }
+          const float bm = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * p.scale_log2;
+          if (!__any_sync(0xffffffffu, bm - m_run > RESCALE_LOG2)) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_st_32x16(tP + lane_off + c * 16, packed[c]);
+            float s0, s1, s2, s3;
+            f2_unpack(ps2[0], s0, s1);
+            f2_unpack(ps2[1], s2, s3);
+            l_run += ((s0 + s1) + (s2 + s3)) + lsum;
+            done = true;
+          }
+        }
+        if (!done) {
+          float mx;
+          {
+            float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            uint32_t r[2][32];
+            tmem_ld_32x32(tS + lane_off, r[0]);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              tmem_ld_wait();
+              if (c + 1 < 4) tmem_ld_32x32(tS + lane_off + (c + 1) * 32, r[(c + 1) & 1]);
+              if (need_mask) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  if (c * 32 + i < limit) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(r[c & 1][i]));
+              } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                  m4[i & 3] = fmax3(m4[i & 3], __uint_as_float(r[c & 1][2 * i]), __uint_as_float(r[c & 1][2 * i + 1]));
+              }
+            }
+            mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * p.scale_log2;
+          }
+          const float m_new = fmaxf(m_run, mx);
+          if (j == 0) {
+            m_run = m_new;
+          } else if (__any_sync(0xffffffffu, m_new - m_run > RESCALE_LOG2)) {
+            const float alpha = (m_new == -INFINITY) ? 1.f : exp2f(m_run - m_new);
+#pragma unroll 1
+            for (int c = 0; c < HD / 32; ++c) {
+              uint32_t r[32];
+              tmem_ld_32x32(tO + lane_off + c * 32, r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+              tmem_st_32x32(tO + lane_off + c * 32, r);
+            }
+            l_run *= alpha;
+            m_run = m_new;
+          }
+          const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
+          float psum = 0.f;
+          uint32_t r[2][32];
+          tmem_ld_32x32(tS + lane_off, r[0]);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            tmem_ld_wait();
+            if (c + 1 < 4) tmem_ld_32x32(tS + lane_off + (c + 1) * 32, r[(c + 1) & 1]);
+            uint32_t packed[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int col = c * 32 + 2 * i;
+              const float a = (!need_mask || col < limit) ? exp2f(fmaf(__uint_as_float(r[c & 1][2 * i]), p.scale_log2, -m_use)) : 0.f;
+              const float bb = (!need_mask || col + 1 < limit) ? exp2f(fmaf(__uint_as_float(r[c & 1][2 * i + 1]), p.scale_log2, -m_use)) : 0.f;
+              psum += a + bb;
+              packed[i] = pack2<BF16>(a, bb);
+            }
+            // P chunk c lands in columns 16 c .. 16 c + 15 of S, inside chunks that have already been read
+            tmem_st_32x16(tP + lane_off + c * 16, packed);
+          }
+          l_run += psum;
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(&p_full[t]);
+      }
+      if (ok) ok = mbar_wait_warp(&o_full[t], (g + n_kv - 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
+      tc_fence_after();
+      if (ok) {
+        const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
+        uint8_t* tbuf = sEpi + (warp - 2) * 2048;
+        const int st_row = lane >> 2, st_vec = lane & 3;
+        const int row0 = qb * TILE + quarter * 32;
+        uint16_t* obase = reinterpret_cast<uint16_t*>(p.out) + static_cast<long long>(b) * p.o_batch_stride + h * HD;
+        uint32_t r[2][32];
+        tmem_ld_32x32(tO + lane_off, r[0]);
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+          tmem_ld_wait();
+          if (c + 1 < HD / 32) {
+            tmem_ld_32x32(tO + lane_off + (c + 1) * 32, r[(c + 1) & 1]);
+          } else {
+            tc_fence_before();
+            mbar_arrive(&o_empty[t]);
+          }
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 ov;
+            ov.x = pack2<BF16>(__uint_as_float(r[c & 1][v * 8 + 0]) * inv_l, __uint_as_float(r[c & 1][v * 8 + 1]) * inv_l);
+            ov.y = pack2<BF16>(__uint_as_float(r[c & 1][v * 8 + 2]) * inv_l, __uint_as_float(r[c & 1][v * 8 + 3]) * inv_l);
+            ov.z = pack2<BF16>(__uint_as_float(r[c & 1][v * 8 + 4]) * inv_l, __uint_as_float(r[c & 1][v * 8 + 5]) * inv_l);
+            ov.w = pack2<BF16>(__uint_as_float(r[c & 1][v * 8 + 6]) * inv_l, __uint_as_float(r[c & 1][v * 8 + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(tbuf + lane * 64 + ((v ^ ((lane >> 1) & 3)) << 4)) = ov;
+          }
+          __syncwarp();
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            const int rr = jj * 8 + st_row;
+            if (row0 + rr < p.T) {
+              const uint4 ov = *reinterpret_cast<const uint4*>(tbuf + rr * 64 + ((st_vec ^ ((rr >> 1) & 3)) << 4));
+              *reinterpret_cast<uint4*>(obase + static_cast<long long>(row0 + rr) * p.o_row_stride + c * 32 + st_vec * 8) = ov;
+            }
+          }
+          __syncwarp();
+        }
+        if (p.lse && q_idx < p.T) p.lse[(static_cast<long long>(b) * p.H + h) * p.T + q_idx] = (m_run + log2f(l_run)) * LN2;
+      }
+      g += n_kv;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(p.work + 1, 1u) == gridDim.x - 1) {
+      p.work[0] = 0;
+      p.work[1] = 0;
+    }
+  }
+}
+
 // ------------------------------------------------------------------ backward
 struct AttnBwdParams {
   const float* lse;    // [B, H, T]
@@ -1476,6 +1926,30 @@ static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
+template <bool BF16>
+static int launch_fwd128(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, AttnFwdParams p, int B,
+                         cudaStream_t stream) {
+  auto kern = flash_fwd128_kernel<BF16>;
+  static bool configured = false;
+  static int sms = 0;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd128Cfg::SMEM) != cudaSuccess) return -10;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return -10;
+    configured = true;
+  }
+  p.B = B;
+  p.n_qblocks = (p.T + 2 * TILE - 1) / (2 * TILE);  // tile pairs
+  p.work = next_work_pair();
+  if (!p.work) return -10;
+  const long long items = static_cast<long long>(p.n_qblocks) * p.H * B;
+  if (items > 0x7fffffffLL - 4096) return -2;
+  const unsigned grid = static_cast<unsigned>(items < sms ? items : sms);
+  kern<<<grid, ATT128_THREADS, Fwd128Cfg::SMEM, stream>>>(tq, tk, tv, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
 template <int HD, bool BF16, bool DROP, bool GEN>
 static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
                       const CUtensorMap& tdq, AttnBwdParams p, int B, cudaStream_t stream) {
@@ -1514,6 +1988,9 @@ static bool drop_params(float p, uint32_t& threshold16, float& inv_keep) {
 }  // namespace msq
 
 static long long* g_attn_prof = nullptr;
+static int g_fwd128 = 1;
+// Benchmark switch: 0 sends head size 128 through the one-tile forward kernel.
+extern "C" void msq_attn_set_fwd128(int on) { g_fwd128 = on; }
 
 // Debug aid: when set to a device buffer of at least 512 int64, CTA (0,0,0) of the next attention
 // launches records clock64() at its phase boundaries (forward in [0,256), backward in [256,512)).
@@ -1554,6 +2031,8 @@ extern "C" int msq_flash_fwd(const void* q, const void* k, const void* v, long l
   (p.drop_threshold16 ? launch_fwd<HDV, BF, true, GN>(tq, tk, tv, p, B, stream) : launch_fwd<HDV, BF, false, GN>(tq, tk, tv, p, B, stream))
 #define MSQ_FWD(HDV, BF) (gen ? MSQ_FWD2(HDV, BF, true) : MSQ_FWD2(HDV, BF, false))
   if (HD <= 64) return bf16 ? MSQ_FWD(64, true) : MSQ_FWD(64, false);
+  if (HD == 128 && !gen && !p.drop_threshold16 && g_fwd128)  // two q tiles per CTA (see flash_fwd128_kernel)
+    return bf16 ? launch_fwd128<true>(tq, tk, tv, p, B, stream) : launch_fwd128<false>(tq, tk, tv, p, B, stream);
   return bf16 ? MSQ_FWD(128, true) : MSQ_FWD(128, false);
 #undef MSQ_FWD
 #undef MSQ_FWD2
