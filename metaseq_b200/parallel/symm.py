@@ -210,9 +210,10 @@ class PeerComm:
         #          needs the multicast mapping, and gradients that live in symmetric memory (alloc_symmetric).
         # MSQ_COMM_AG / MSQ_COMM_RS override one direction ("pull" for the reduce-scatter works without multicast
         # too, with plain peer loads).
-        # Defaults from measurements of a 100 MB unit on 2 and 4 GPUs: the all-gather by peer DMA (0.15 / 0.19 ms,
-        # level with NCCL, and it takes no SM from the GEMMs it overlaps with), the reduce-scatter as the in-switch
-        # pull (0.21 / 0.19 ms against 0.27 for the DMA push + slot sum; NCCL 0.17 / 0.18 ms).
+        # Defaults from measurements of a 100 MB unit on 2 / 4 / 8 GPUs: the all-gather by peer DMA (0.15 / 0.19 /
+        # 0.22 ms against NCCL's 0.16 / 0.18 / 0.20; it takes no SM from the GEMMs it overlaps with; multimem.st is
+        # 0.19 ms at 8), the reduce-scatter as the in-switch pull (0.21 / 0.19 / 0.18 ms against 0.27 - 0.30 for the DMA
+        # push + slot sum; NCCL 0.17 / 0.18 / 0.19 ms).
         self.transport = transport or os.environ.get("MSQ_COMM_TRANSPORT", "auto")
         ag_default = "ce" if self.transport == "auto" else self.transport
         rs_default = "pull" if self.transport in ("auto", "mm") else self.transport
