@@ -452,3 +452,37 @@ def test_plasma_store_owns_and_unlinks_shared_segments():
     with pytest.raises(FileNotFoundError):
         shared_memory.SharedMemory(name=name)
     store.close()  # idempotent
+
+
+def test_sinusoidal_positions_compile_with_torchscript(tmp_path):
+    """The reference exports this module with torch.jit.script (tests/test_export.py): the compiled module must save,
+    load and give the eager result, including the growth of its table beyond the initial size."""
+    from metaseq_b200.modules.sinusoidal_positional_embedding import SinusoidalPositionalEmbedding
+
+    m = SinusoidalPositionalEmbedding(embedding_dim=8, padding_idx=1, init_size=16)
+    scripted = torch.jit.script(m)
+    path = str(tmp_path / "pos.pt")
+    scripted.save(path)
+    loaded = torch.jit.load(path)
+    x = torch.tensor([[5, 6, 1, 1], [1, 7, 8, 9]])
+    assert torch.equal(loaded(x), m(x))
+    assert torch.all(m(x)[0, 2:] == 0)  # padding rows
+    long = torch.randint(2, 50, (1, 300))
+    assert torch.allclose(loaded(long), m(long))
+
+
+def test_modules_keep_separate_slots_of_one_incremental_state():
+    """Two modules sharing one incremental-state dictionary do not see each other's entries (the reference checks this
+    on scripted attention modules: tests/test_export.py:73-91)."""
+    from metaseq_b200.incremental_decoding_utils import with_incremental_state
+
+    @with_incremental_state
+    class Holder(torch.nn.Module):
+        pass
+
+    a, b = Holder(), Holder()
+    state = {}
+    state = a.set_incremental_state(state, "key", {"a": torch.tensor([1])})
+    state = b.set_incremental_state(state, "key", {"a": torch.tensor([2])})
+    assert int(a.get_incremental_state(state, "key")["a"]) == 1
+    assert int(b.get_incremental_state(state, "key")["a"]) == 2
