@@ -187,6 +187,22 @@ class LanguageModelingTask(LegacyTask):
     def build_dataset_for_inference(self, src_tokens, src_lengths, **kwargs):
         return inference_dataset(src_tokens, src_lengths, self.source_dictionary)
 
+    def eval_lm_dataloader(self, dataset, max_tokens=36000, batch_size=None, max_positions=None, num_shards=1,
+                           shard_id=0, num_workers=0, data_buffer_size=10, context_window=0):
+        """Batches of ``dataset`` in corpus order for perplexity evaluation.  With ``context_window`` > 0 every
+        sample is prefixed with the last ``context_window`` tokens seen so far, and the targets of that prefix are
+        padding so that it is not scored twice (reference: metaseq/tasks/language_modeling.py:332-363)."""
+        if context_window > 0:
+            from metaseq_b200.data.lm_context_window_dataset import LMContextWindowDataset
+
+            dataset = LMContextWindowDataset(dataset=dataset, tokens_per_sample=self.args.tokens_per_sample,
+                                             context_window=context_window, pad_idx=self.source_dictionary.pad())
+        epoch_itr = self.get_batch_iterator(
+            dataset=dataset, max_tokens=max_tokens, max_sentences=batch_size, max_positions=max_positions,
+            ignore_invalid_inputs=True, num_shards=num_shards, shard_id=shard_id, num_workers=num_workers,
+            data_buffer_size=data_buffer_size, disable_iterator_cache=True)
+        return epoch_itr.next_epoch_itr(shuffle=False)
+
     def max_positions(self):
         return getattr(self.args, "max_target_positions", None) or self.args.tokens_per_sample
 
