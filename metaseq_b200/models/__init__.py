@@ -38,6 +38,9 @@ def register_model(name, dataclass=None):
         if dataclass is not None:
             cls.__dataclass = dataclass
             MODEL_DATACLASS_REGISTRY[name] = dataclass
+            from metaseq_b200.dataclass.initialize import ConfigStore
+
+            ConfigStore.instance().store(name=name, group="model", node=dataclass)
         return cls
 
     return wrap

@@ -63,6 +63,9 @@ def setup_registry(registry_name: str, base_class=None, default=None, required: 
             if dataclass is not None:
                 cls.__dataclass = dataclass
                 DATACLASS_REGISTRY[name] = dataclass
+                from metaseq_b200.dataclass.initialize import ConfigStore
+
+                ConfigStore.instance().store(name=name, group=key, node=dataclass)
             REGISTRY[name] = cls
             REGISTRY_CLASS_NAMES.add(cls.__name__)
             return cls

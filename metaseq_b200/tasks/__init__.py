@@ -34,6 +34,9 @@ def register_task(name, dataclass=None):
         if dataclass is not None:
             cls.__dataclass = dataclass
             TASK_DATACLASS_REGISTRY[name] = dataclass
+            from metaseq_b200.dataclass.initialize import ConfigStore
+
+            ConfigStore.instance().store(name=name, group="task", node=dataclass)
         return cls
 
     return wrap

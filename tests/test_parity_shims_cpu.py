@@ -486,3 +486,66 @@ def test_modules_keep_separate_slots_of_one_incremental_state():
     state = b.set_incremental_state(state, "key", {"a": torch.tensor([2])})
     assert int(a.get_incremental_state(state, "key")["a"]) == 1
     assert int(b.get_incremental_state(state, "key")["a"]) == 2
+
+
+def test_standalone_scaled_masked_softmax_functions_match_autograd_of_plain_ops():
+    from metaseq_b200.modules.fused_softmax import scaled_masked_softmax, scaled_upper_triang_masked_softmax
+
+    torch.manual_seed(0)
+    x = torch.randn(6, 5, 5, dtype=torch.double, requires_grad=True)
+    y = scaled_upper_triang_masked_softmax(x, 0.3)
+    hidden = torch.ones(5, 5, dtype=torch.bool).triu(1)
+    ref = torch.softmax((x * 0.3).masked_fill(hidden, float("-inf")), dim=-1)
+    assert torch.allclose(y.double(), ref, atol=1e-6)
+    assert (y.masked_select(hidden.expand_as(y)) == 0).all()
+    w = torch.randn_like(ref)
+    (gx,) = torch.autograd.grad((y * w).sum(), x)
+    (gr,) = torch.autograd.grad((ref * w).sum(), x)
+    assert torch.allclose(gx, gr, atol=1e-6)
+
+    x4 = torch.randn(2, 3, 4, 7, requires_grad=True)
+    mask = torch.rand(2, 1, 4, 7) < 0.3
+    mask[0, 0, 1] = True  # one fully hidden row: uniform, not NaN
+    y4 = scaled_masked_softmax(x4, mask, 0.5)
+    ref4 = torch.softmax((x4 * 0.5).masked_fill(mask, -10000.0), dim=-1)
+    assert torch.allclose(y4, ref4, atol=1e-6)
+    assert torch.allclose(y4[0, :, 1], torch.full((3, 7), 1 / 7), atol=1e-6)
+    w4 = torch.randn_like(ref4)
+    (g4,) = torch.autograd.grad((y4 * w4).sum(), x4)
+    (g4r,) = torch.autograd.grad((ref4 * w4).sum(), x4)
+    # the backward pass sees only the probabilities (as the reference's kernel does), so a fully hidden row gets
+    # the gradient of a plain softmax where autograd through the fill gives zero; every other row agrees
+    keep = torch.ones(2, 3, 4, dtype=torch.bool)
+    keep[0, :, 1] = False
+    assert torch.allclose(g4[keep], g4r[keep], atol=1e-6)
+
+
+def test_config_store_lists_registered_components_and_composes_a_root_config():
+    import metaseq_b200.criterions  # noqa: F401  (registration side effects)
+    import metaseq_b200.models  # noqa: F401
+    import metaseq_b200.optim  # noqa: F401
+    import metaseq_b200.optim.lr_scheduler  # noqa: F401
+    import metaseq_b200.tasks  # noqa: F401
+    from metaseq_b200.dataclass.configs import CommonConfig, MetaseqConfig
+    from metaseq_b200.dataclass.initialize import ConfigStore, compose, hydra_init
+
+    hydra_init()
+    hydra_init()  # idempotent
+    cs = ConfigStore.instance()
+    assert isinstance(cs.load("base_config"), MetaseqConfig)
+    assert isinstance(cs.load("common"), CommonConfig)
+    assert {"task", "model", "optimizer", "lr_scheduler", "criterion"} <= set(cs.groups())
+    assert "language_modeling" in cs.list("task") and "transformer_lm" in cs.list("model")
+    with pytest.raises(KeyError, match="no config named"):
+        cs.load("nope", group="task")
+
+    cfg = compose(["common.seed=7", "task=language_modeling", "common.fp16=true", "task.tokens_per_sample=512",
+                   "optimization.lr=[0.001]", "lr_scheduler=polynomial_decay"])
+    assert cfg.common.seed == 7 and cfg.common.fp16 is True
+    assert cfg.task.tokens_per_sample == 512 and cfg.task._name == "language_modeling"
+    assert cfg.optimization.lr == [0.001]
+    assert cs.load("common").seed != 7  # stored defaults are untouched
+    with pytest.raises(KeyError, match="is not set"):
+        compose(["optimizer.lr=[0.1]"])
+    with pytest.raises(KeyError, match="unknown field"):
+        compose(["common.not_a_field=1"])
