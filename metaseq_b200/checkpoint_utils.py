@@ -373,6 +373,18 @@ def load_checkpoint(cfg, trainer, **passthrough_args):
     if ckpt.restore_file != default_restore_file and ckpt.finetune_from_model:
         raise ValueError("--finetune-from-model and --restore-file (non-default value) can not be specified "
                          f"together: {cfg}")
+    upload = getattr(ckpt, "cloud_upload_path", None)
+    if upload and upload.startswith("nfs:"):
+        # checkpoints were moved to <nfs>/checkpoint_N/checkpoint<suffix>.pt by the post-checkpoint callback:
+        # a requeued job, or one with neither --restore-file nor --finetune-from-model, resumes from the newest
+        # directory that holds one finished file per rank (reference: metaseq/checkpoint_utils.py:230-277)
+        explicit = ckpt.restore_file != default_restore_file
+        requeued = os.environ.get("SLURM_RESTART_COUNT", "0") not in ("0", "")
+        if requeued or (ckpt.finetune_from_model is None and not explicit):
+            latest = get_latest_complete_checkpoint_dir(upload[4:], dist_utils.get_global_world_size(), exact=True)
+            checkpoint_path = os.path.join(latest, f"checkpoint{suffix}.pt") if latest else None
+        elif explicit:
+            checkpoint_path = ckpt.restore_file.replace(".pt", suffix + ".pt")
     if dist_utils.is_initialized():
         torch.distributed.barrier()
     extra_state = trainer.load_checkpoint(checkpoint_path, reset_optimizer, reset_lr_scheduler, optimizer_overrides,
@@ -406,9 +418,10 @@ def _newest_update_checkpoint(save_dir: str, suffix: str) -> Optional[str]:
     return best[1] if best else None
 
 
-def get_latest_complete_checkpoint_dir(base: str, expected_files: int) -> Optional[str]:
-    """Among ``base/checkpoint_<N>/`` directories, the largest N that holds at least
-    ``expected_files`` files (an interrupted copy leaves an incomplete directory behind)."""
+def get_latest_complete_checkpoint_dir(base: str, expected_files: int, exact: bool = False) -> Optional[str]:
+    """Among ``base/checkpoint_<N>/`` directories, the largest N that holds at least (``exact``: exactly)
+    ``expected_files`` finished files.  An interrupted copy leaves an incomplete directory behind, and a file
+    whose name starts with ``_`` is still being copied."""
     best = None
     if not os.path.isdir(base):
         return None
@@ -416,8 +429,11 @@ def get_latest_complete_checkpoint_dir(base: str, expected_files: int) -> Option
         m = re.fullmatch(r"checkpoint_(\d+)", d)
         full = os.path.join(base, d)
         if m and os.path.isdir(full):
-            n_files = len([f for f in os.listdir(full) if f.endswith(".pt")])
-            if n_files >= expected_files and (best is None or int(m.group(1)) > best[0]):
+            n_files = len([f for f in os.listdir(full) if f.endswith(".pt") and not f.startswith("_")])
+            enough = n_files == expected_files if exact else n_files >= expected_files
+            if not enough:
+                logger.info(f"skipping checkpoint {d} because it only has {n_files} files (expected {expected_files})")
+            elif best is None or int(m.group(1)) > best[0]:
                 best = (int(m.group(1)), full)
     return best[1] if best else None
 

@@ -18,7 +18,9 @@ import socket
 import subprocess
 import sys
 import time
+from datetime import datetime, timezone
 from typing import Any, Dict, List, Optional, Tuple
+from urllib.parse import urlparse
 
 import numpy as np
 import torch
@@ -259,66 +261,144 @@ def validate_and_save(cfg, trainer: Trainer, task, epoch_itr, valid_subsets: Lis
     return valid_losses, should_stop
 
 
+_CHECKPOINT_NAME = re.compile(r"(checkpoint(?:\d+|_\d+|_last))(.*)")
+
+
+def _checkpoint_add_directory(basename):
+    """``checkpoint_18-model_part-0-shard0.pt`` -> (``checkpoint_18``, ``checkpoint-model_part-0-shard0.pt``):
+    on a shared file system every checkpoint gets a directory of its own and its files drop the step from their
+    name, so that ``<dir>/checkpoint.pt`` is the prefix that loaders and evaluation scripts are given."""
+    m = _CHECKPOINT_NAME.match(basename)
+    assert m, f"checkpoint file {basename} doesn't follow the pattern {_CHECKPOINT_NAME.pattern}"
+    return m.group(1), "checkpoint" + m.group(2)
+
+
+def _get_basename(path):
+    parsed = urlparse(path)
+    return os.path.basename(parsed.path if parsed.scheme else path)
+
+
+def _get_destination_path(path, destination):
+    """``destination`` joined with the file name of ``path``; for a URL the name goes into the path component,
+    before the query (a SAS token stays at the end)."""
+    name = _get_basename(path)
+    parsed = urlparse(destination)
+    if parsed.scheme:
+        return parsed._replace(path=os.path.join(parsed.path, name)).geturl()
+    return os.path.join(destination, name)
+
+
+def _copy_to_azure(source, destination, log_dir):
+    stamp = datetime.now(timezone.utc).strftime("%Y-%m-%dT%H_%M_%S")
+    azcopy_logs = os.path.join(log_dir, f"{_get_basename(destination)}_azcopy_logs_{stamp}")
+    os.environ["AZCOPY_CONCURRENCY_VALUE"] = "10"
+    os.environ["AZCOPY_LOG_LOCATION"] = azcopy_logs
+    os.makedirs(azcopy_logs, exist_ok=True)
+    logger.info(f"preparing to azcopy {source} to {destination}; logs in {azcopy_logs}")
+    res = _run_azcopy(["azcopy", "copy", "--cap-mbps", "96.0", source, destination], stdout=subprocess.PIPE)
+    if res.returncode != 0:
+        print("Error: {}, azcopy failed".format(res.returncode))
+        print("Azcopy stdout = {}".format(res.stdout))
+        sys.exit(1)
+    logger.info(f"Successfully copied {source} to {destination}")
+
+
 def post_checkpoint_callback(cfg, num_updates, training_finished, filename, files_to_symlink_to):
-    """Runs on the writer thread after a checkpoint file is complete: upload to blob storage
-    with azcopy, copy to an ``nfs:`` directory through a temporary name (atomic rename, so a
-    reader never sees a partial checkpoint), or generic copy; then recreate the symlinks."""
+    """Runs on the writer thread after a checkpoint file is complete (reference: metaseq/cli/train.py:535-645).
+
+    * blob storage URL: ``azcopy`` the file to ``<url path>/<name>?<token>``, remove the local file, and copy the
+      uploaded blob once more under every alias name (blob storage has no symlinks);
+    * ``nfs:<dir>``: copy to ``<dir>/checkpoint_N/_checkpoint<suffix>`` and rename to ``checkpoint<suffix>`` (a
+      reader never sees a partial file), remove the local file, symlink the aliases' directories' entries to it,
+      then start the evaluation script if one is configured;
+    * any other path: copy through the path manager, aliases as full copies;
+    * no upload path: recreate the alias symlinks beside the file."""
     upload = cfg.checkpoint.cloud_upload_path
-    if upload is not None:
-        if "blob.core.windows.net" in upload:
-            azcopy_logs = filename + "_azcopy_logs"
-            os.environ["AZCOPY_CONCURRENCY_VALUE"] = "10"
-            os.environ["AZCOPY_LOG_LOCATION"] = azcopy_logs
-            os.makedirs(azcopy_logs, exist_ok=True)
-            logger.info(f"preparing to azcopy {filename} to {upload}; logs in {azcopy_logs}")
-            cmd = ["azcopy", "copy", "--cap-mbps", "96.0", filename, upload]
-            res = _run_azcopy(cmd, stdout=subprocess.PIPE)
-            if res.returncode != 0:
-                print("Error: {}, azcopy failed".format(res.returncode))
-                print("Azcopy stdout = {}".format(res.stdout))
-                sys.exit(1)
-            logger.info(f"Successfully copied {filename} to {upload}")
-            if os.path.exists(filename):
-                os.remove(filename)
-        elif upload.startswith("nfs:"):
-            path, basename = os.path.split(filename)
-            checkpoint_dir = os.path.join(upload[4:], f"checkpoint_{num_updates}")
-            os.makedirs(checkpoint_dir, exist_ok=True)
-            tmp_name = os.path.join(checkpoint_dir, "_" + basename + ".tmp")
-            shutil.copyfile(filename, tmp_name)
-            os.replace(tmp_name, os.path.join(checkpoint_dir, basename))
-            logger.info(f"Successfully copied {filename} to {checkpoint_dir}")
-            if cfg.checkpoint.nfs_eval_script_path and dist_utils.get_global_rank() == 0 and \
-                    num_updates % max(1, cfg.checkpoint.nfs_eval_frequency) == 0:
-                _run_nfs_eval(cfg, checkpoint_dir)
-            if os.path.exists(filename):
-                os.remove(filename)
-        else:
-            try:
-                PathManager.copy_from_local(filename, os.path.join(upload, os.path.basename(filename)), overwrite=True)
-                if os.path.exists(filename):
-                    os.remove(filename)
-            except (FileNotFoundError, AssertionError) as e:
-                logger.info(f"could not upload {filename}: {e}")
-    elif files_to_symlink_to:
-        for other in files_to_symlink_to:
+    aliases = files_to_symlink_to or []
+    if upload is None:
+        for other in aliases:
             if os.path.lexists(other):
                 os.remove(other)
             os.symlink(os.path.basename(filename), other)
+        return
+    if "blob.core.windows.net" in upload:
+        log_dir = os.path.dirname(filename)
+        final_path = _get_destination_path(filename, upload)
+        _copy_to_azure(filename, final_path, log_dir)
+        if os.path.exists(filename):
+            os.remove(filename)
+        for other in aliases:
+            _copy_to_azure(final_path, _get_destination_path(other, upload), log_dir)
+    elif upload.startswith("nfs:"):
+        root = upload[4:]
+        checkpoint_dir, checkpoint_file = _checkpoint_add_directory(os.path.basename(filename))
+        target_dir = os.path.join(root, checkpoint_dir)
+        os.makedirs(target_dir, exist_ok=True)  # another worker may have made it first
+        tmp_name = os.path.join(target_dir, "_" + checkpoint_file)
+        final_path = os.path.join(target_dir, checkpoint_file)
+        logger.info(f"Beginning copy of {filename} to NFS")
+        shutil.copyfile(filename, tmp_name)
+        os.replace(tmp_name, final_path)
+        logger.info(f"Successfully copied {filename} to {final_path}")
+        if os.path.exists(filename):
+            os.remove(filename)
+        for other in aliases:
+            name = os.path.basename(other)
+            other_dir = os.path.join(root, _checkpoint_add_directory(name)[0])
+            os.makedirs(other_dir, exist_ok=True)
+            dest = os.path.join(other_dir, name)
+            if os.path.lexists(dest):
+                os.remove(dest)
+            os.symlink(final_path, dest)
+        nfs_evaluation(cfg, num_updates, training_finished, checkpoint_dir, root)
+    else:
+        try:
+            final_path = _get_destination_path(filename, upload)
+            PathManager.copy_from_local(filename, final_path, overwrite=True)
+            for other in aliases:
+                PathManager.copy(final_path, _get_destination_path(other, upload), overwrite=True)
+            if os.path.exists(filename):
+                os.remove(filename)
+        except (FileNotFoundError, AssertionError) as e:
+            logger.info(f"could not upload {filename}: {e}")
+
+
+def nfs_evaluation(cfg, num_updates, training_finished, checkpoint_dir, destination_checkpoints_dir):
+    """On global rank 0, for checkpoints whose step is a multiple of ``--nfs-eval-frequency`` (and for the final
+    one): wait until every rank's part has been renamed into place (names that start with ``_`` are still being
+    copied), then run ``bash <script> <dir>/checkpoint.pt``.  The script path is taken relative to
+    ``$METASEQ_SAVE_DIR`` when that is set (reference: metaseq/cli/train.py:648-706)."""
+    ck = cfg.checkpoint
+    if ck.nfs_eval_script_path is None or dist_utils.get_global_rank() != 0:
+        return
+    due = ck.nfs_eval_frequency > 0 and num_updates % ck.nfs_eval_frequency == 0
+    if not (due or training_finished):
+        return
+    current = os.path.join(destination_checkpoints_dir, checkpoint_dir)
+    world = cfg.distributed_training.distributed_world_size
+    done = 0
+    for _ in range(ck.nfs_eval_num_attempts):
+        time.sleep(ck.nfs_eval_attempt_wait_minutes * 60)
+        done = len([f for f in os.listdir(current) if not f.startswith("_")])
+        if done == world:
+            logger.info(f"All checkpoint parts for {checkpoint_dir} are in NFS, will now start to run evals")
+            script = os.path.join(os.environ.get("METASEQ_SAVE_DIR", ""), ck.nfs_eval_script_path)
+            res = subprocess.run(["bash", script, os.path.join(current, "checkpoint.pt")],
+                                 stdout=subprocess.PIPE, stderr=subprocess.PIPE)
+            if res.returncode == 0:
+                logger.info(f"Successfully evaluated {checkpoint_dir}")
+            else:
+                logger.error(f"Error during evaluation: {res.returncode}")
+                logger.error(f"Eval script stdout = {res.stdout}")
+                logger.error(f"Eval script stderr = {res.stderr}")
+            return
+    logger.error(f"Did not evaluate {checkpoint_dir}, as only {done}/{world} checkpoint parts were copied to NFS "
+                 "within waiting time")
 
 
 def add_num_updates_to_stats(trainer: Trainer, stats: Dict[str, Any]) -> Dict[str, Any]:
     stats["num_updates"] = trainer.get_num_updates()
     return stats
-
-
-def _run_nfs_eval(cfg, checkpoint_dir):
-    for attempt in range(max(1, cfg.checkpoint.nfs_eval_num_attempts)):
-        n_files = len([f for f in os.listdir(checkpoint_dir) if f.endswith(".pt")])
-        if n_files >= cfg.distributed_training.distributed_world_size:
-            subprocess.Popen(["bash", cfg.checkpoint.nfs_eval_script_path, checkpoint_dir])
-            return
-        time.sleep(60 * cfg.checkpoint.nfs_eval_attempt_wait_minutes)
 
 
 def _run_azcopy(cmd, stdout):

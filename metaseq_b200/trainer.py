@@ -315,7 +315,8 @@ class Trainer:
         is_distributed = self.data_parallel_world_size > 1
         bexists = False
         logger.info(f"attempting to load checkpoint from: {filename}")
-        if os.path.isfile(filename) or checkpoint_utils.sharded_files_exist(filename, self.checkpoint_suffix):
+        if filename is not None and (os.path.isfile(filename)
+                                     or checkpoint_utils.sharded_files_exist(filename, self.checkpoint_suffix)):
             bexists = True
         if bexists:
             logger.info(f"Preparing to load checkpoint {filename}")

@@ -8,6 +8,7 @@ import types
 import pytest
 import torch
 
+from metaseq_b200 import checkpoint_utils
 from metaseq_b200.cli import train as train_cli
 
 
@@ -31,15 +32,49 @@ def test_checkpoint_callback_copies_to_nfs_atomically_and_removes_the_local_file
     nfs.mkdir()
     f = local / "checkpoint_18-model_part-0-shard0.pt"
     f.write_bytes(b"weights")
-    train_cli.post_checkpoint_callback(_ckpt_cfg(f"nfs:{nfs}"), 18, False, str(f), None)
-    target = nfs / "checkpoint_18" / f.name
+    last = local / "checkpoint_last-model_part-0-shard0.pt"
+    train_cli.post_checkpoint_callback(_ckpt_cfg(f"nfs:{nfs}"), 18, False, str(f), [str(last)])
+    # one directory per checkpoint; the step leaves the file name, so <dir>/checkpoint.pt is the loader's prefix
+    target = nfs / "checkpoint_18" / "checkpoint-model_part-0-shard0.pt"
     assert target.read_bytes() == b"weights" and not f.exists()
-    assert [p.name for p in (nfs / "checkpoint_18").iterdir()] == [f.name]  # no temporary file left behind
+    assert [p.name for p in (nfs / "checkpoint_18").iterdir()] == [target.name]  # no temporary file left behind
+    alias = nfs / "checkpoint_last" / last.name
+    assert os.path.islink(alias) and alias.read_bytes() == b"weights"
+    assert train_cli._checkpoint_add_directory("checkpoint3.pt") == ("checkpoint3", "checkpoint.pt")
+    with pytest.raises(AssertionError):
+        train_cli._checkpoint_add_directory("model.pt")
+
+
+def test_nfs_evaluation_waits_for_all_parts_then_runs_the_script(tmp_path, monkeypatch, caplog):
+    nfs = tmp_path / "nfs"
+    (nfs / "checkpoint_20").mkdir(parents=True)
+    (nfs / "checkpoint_20" / "checkpoint-shard0.pt").write_bytes(b"a")
+    (nfs / "checkpoint_20" / "_checkpoint-shard1.pt").write_bytes(b"b")  # still being copied
+    script = tmp_path / "eval.sh"
+    out = tmp_path / "seen.txt"
+    script.write_text(f'echo "$1" > {out}\n')
+    monkeypatch.setenv("METASEQ_SAVE_DIR", str(tmp_path))
+    cfg = _ckpt_cfg(f"nfs:{nfs}", world=2)
+    cfg.checkpoint.nfs_eval_script_path = "eval.sh"
+    cfg.checkpoint.nfs_eval_frequency = 10
+    cfg.checkpoint.nfs_eval_num_attempts = 2
+    with caplog.at_level("ERROR"):
+        train_cli.nfs_evaluation(cfg, 20, False, "checkpoint_20", str(nfs))
+    assert not out.exists() and "only 1/2 checkpoint parts" in caplog.text
+    os.replace(nfs / "checkpoint_20" / "_checkpoint-shard1.pt", nfs / "checkpoint_20" / "checkpoint-shard1.pt")
+    train_cli.nfs_evaluation(cfg, 25, False, "checkpoint_20", str(nfs))  # not a multiple of the frequency
+    assert not out.exists()
+    train_cli.nfs_evaluation(cfg, 25, True, "checkpoint_20", str(nfs))  # the final checkpoint is always evaluated
+    assert out.read_text().strip() == str(nfs / "checkpoint_20" / "checkpoint.pt")
+    out.unlink()
+    train_cli.nfs_evaluation(cfg, 20, False, "checkpoint_20", str(nfs))
+    assert out.exists()
 
 
 def test_checkpoint_callback_uploads_with_azcopy_and_fails_loudly(tmp_path, monkeypatch):
     f = tmp_path / "checkpoint_6-model_part-0-shard0.pt"
     f.write_bytes(b"w")
+    last = tmp_path / "checkpoint_last-model_part-0-shard0.pt"
     calls = []
 
     def fake_azcopy(cmd, stdout):
@@ -48,12 +83,26 @@ def test_checkpoint_callback_uploads_with_azcopy_and_fails_loudly(tmp_path, monk
 
     monkeypatch.setattr(train_cli, "_run_azcopy", fake_azcopy)
     url = "https://acct.blob.core.windows.net/container/run?sas"
-    train_cli.post_checkpoint_callback(_ckpt_cfg(url), 6, False, str(f), None)
-    assert calls and calls[0][:2] == ["azcopy", "copy"] and calls[0][-2:] == [str(f), url] and not f.exists()
+    dest = f"https://acct.blob.core.windows.net/container/run/{f.name}?sas"  # the name goes before the token
+    train_cli.post_checkpoint_callback(_ckpt_cfg(url), 6, False, str(f), [str(last)])
+    assert calls[0][:2] == ["azcopy", "copy"] and calls[0][-2:] == [str(f), dest] and not f.exists()
+    # blob storage has no symlinks: the alias is a second server-side copy
+    assert calls[1][-2:] == [dest, f"https://acct.blob.core.windows.net/container/run/{last.name}?sas"]
+    assert any(p.name.startswith(f.name + "_azcopy_logs_") for p in tmp_path.iterdir())
     f.write_bytes(b"w")
     monkeypatch.setattr(train_cli, "_run_azcopy", lambda cmd, stdout: types.SimpleNamespace(returncode=3, stdout=b"boom"))
     with pytest.raises(SystemExit):
         train_cli.post_checkpoint_callback(_ckpt_cfg(url), 6, False, str(f), None)
+
+
+def test_checkpoint_callback_copies_to_a_plain_directory_with_aliases_as_full_copies(tmp_path):
+    f = tmp_path / "checkpoint_6.pt"
+    f.write_bytes(b"w")
+    up = tmp_path / "up"
+    up.mkdir()
+    train_cli.post_checkpoint_callback(_ckpt_cfg(str(up)), 6, False, str(f), [str(tmp_path / "checkpoint_last.pt")])
+    assert (up / "checkpoint_6.pt").read_bytes() == b"w" and (up / "checkpoint_last.pt").read_bytes() == b"w"
+    assert not os.path.islink(up / "checkpoint_last.pt")
 
 
 def test_checkpoint_callback_without_upload_recreates_symlinks(tmp_path):
@@ -241,3 +290,45 @@ def test_host_snapshot_is_a_private_copy_and_the_writer_waits_for_it(tmp_path):
     checkpoint_utils.wait_for_pending_writes()
     assert called == [1]
     assert torch.load(path, weights_only=False)["model"]["w"].tolist() == [0.0, 1.0, 2.0, 3.0, 4.0, 5.0]
+
+
+def test_resume_from_shared_directory_takes_the_newest_complete_checkpoint(tmp_path, monkeypatch):
+    """With ``--cloud-upload-path nfs:<dir>`` a restart looks in that directory, not in the local save directory:
+    the newest ``checkpoint_N`` with one finished file per rank wins; unfinished copies do not count."""
+    nfs = tmp_path / "nfs"
+    for step, names in ((10, ["checkpoint-shard0.pt", "checkpoint-shard1.pt"]),
+                        (20, ["checkpoint-shard0.pt", "_checkpoint-shard1.pt"])):
+        d = nfs / f"checkpoint_{step}"
+        d.mkdir(parents=True)
+        for n in names:
+            (d / n).write_bytes(b"x")
+    (nfs / "checkpoint_last").mkdir()
+    seen = {}
+
+    class FakeTrainer:
+        checkpoint_suffix = "-shard0"
+
+        def load_checkpoint(self, path, *a, **k):
+            seen["path"] = path
+            return None
+
+        def get_train_iterator(self, epoch, **k):
+            return types.SimpleNamespace(epoch=epoch)
+
+        def lr_step(self, epoch):
+            pass
+
+    ck = types.SimpleNamespace(
+        reset_optimizer=False, reset_lr_scheduler=False, optimizer_overrides="{}", reset_meters=False,
+        reset_dataloader=False, finetune_from_model=None, restore_file="checkpoint_last.pt",
+        save_dir=str(tmp_path / "local"), cloud_upload_path=f"nfs:{nfs}")
+    cfg = types.SimpleNamespace(checkpoint=ck)
+    monkeypatch.setattr(checkpoint_utils.dist_utils, "get_global_world_size", lambda: 2)
+    checkpoint_utils.load_checkpoint(cfg, FakeTrainer())
+    assert seen["path"] == str(nfs / "checkpoint_10" / "checkpoint-shard0.pt")
+    ck.restore_file = str(nfs / "checkpoint_20" / "checkpoint.pt")  # an explicit file is taken as given
+    checkpoint_utils.load_checkpoint(cfg, FakeTrainer())
+    assert seen["path"] == str(nfs / "checkpoint_20" / "checkpoint-shard0.pt")
+    monkeypatch.setenv("SLURM_RESTART_COUNT", "1")  # ... unless the job was requeued
+    checkpoint_utils.load_checkpoint(cfg, FakeTrainer())
+    assert seen["path"] == str(nfs / "checkpoint_10" / "checkpoint-shard0.pt")
