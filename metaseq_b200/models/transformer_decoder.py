@@ -44,6 +44,21 @@ def _get(args, name, default=None):
 logger = logging.getLogger(__name__)
 
 
+class TransformerDecoderMultiLayerBlockModule(nn.Module):
+    """``--fsdp-checkpoint-wrap-layer-frequency N`` > 1: N consecutive decoder layers that are sharded as one unit
+    (reference: metaseq/models/transformer_decoder.py:41-53, :123-157).  The call takes and returns what one layer
+    takes and returns, so the decoder's loop does not change; activation recomputation stays inside each layer."""
+
+    def __init__(self, layers):
+        super().__init__()
+        self.layers = nn.ModuleList(layers)
+
+    def forward(self, x, **kwargs):
+        for layer in self.layers:
+            x = layer(x, **kwargs)
+        return x
+
+
 def log_weight_stats(tensor, name: str) -> None:
     """Mean, spread and range of a parameter at debug level (metaseq/models/transformer_decoder.py:56)."""
     if logger.isEnabledFor(logging.DEBUG):
@@ -87,11 +102,24 @@ class ModelParallelTransformerDecoder(IncrementalDecoder):
                 pos_init_scalar=_get(args, "pos_init_scalar", 1.0),
                 megatron_init_sigma=_get(args, "megatron_init_sigma", 0.006),
                 truncate_init=_get(args, "truncate_init", False), dtype=dtype, device=device)
-        self.layers = nn.ModuleList([self.build_decoder_layer(args) for _ in range(args.decoder_layers)])
+        group = int(_get(args, "fsdp_checkpoint_wrap_layer_frequency", 1) or 1)
+        if group > 1:
+            # several consecutive layers form one sharded unit (fewer, larger all-gathers and reduce-scatters);
+            # parameter names become layers.<block>.layers.<i>.*
+            assert args.decoder_layers % group == 0, "num layers should be divisible by checkpoint wrap frequency"
+            from metaseq_b200.parallel.fsdp import fsdp_wrap
+
+            raw = [self.build_decoder_layer(args, wrap=False) for _ in range(args.decoder_layers)]
+            min_params = 0 if _get(args, "checkpoint_activations", False) else _get(args, "min_params_to_wrap", None)
+            self.layers = nn.ModuleList([
+                fsdp_wrap(TransformerDecoderMultiLayerBlockModule(raw[i:i + group]), min_num_params=min_params)
+                for i in range(0, len(raw), group)])
+        else:
+            self.layers = nn.ModuleList([self.build_decoder_layer(args) for _ in range(args.decoder_layers)])
         if logger.isEnabledFor(logging.DEBUG):
             for name, param in self.layers.named_parameters():
                 log_weight_stats(param, name)
-        self.num_layers = len(self.layers)
+        self.num_layers = args.decoder_layers
         self.layer_norm = LayerNorm(self.embed_dim, elementwise_affine=not _get(args, "disable_affine_ln", False))
         if dtype != torch.float32:
             self.layer_norm.to(dtype)
@@ -116,11 +144,13 @@ class ModelParallelTransformerDecoder(IncrementalDecoder):
             self.alibi_slopes = torch.tensor(alibi_slopes(args.decoder_attention_heads)[rank * per:(rank + 1) * per],
                                              dtype=torch.float32)
 
-    def build_decoder_layer(self, args):
+    def build_decoder_layer(self, args, wrap: bool = True):
         layer = ModelParallelTransformerDecoderLayer(args)
         dt = utils.get_precise_dtype(args)
         if _get(args, "fp16", False) or _get(args, "memory_efficient_fp16", False) or _get(args, "bf16", False):
             layer = layer.to(dt)
+        if not wrap:
+            return layer
         from metaseq_b200.parallel.fsdp import fsdp_wrap
 
         return fsdp_wrap(layer, min_num_params=_get(args, "min_params_to_wrap", None))

@@ -107,6 +107,24 @@ def _set_rng_state(st):
     mpu.get_cuda_rng_tracker().set_states(st["tracker"])
 
 
+def is_autocast_enabled() -> bool:
+    """Whether the GPU autocast mode is on (the recomputation must run under the mode of the first pass)."""
+    return torch.is_autocast_enabled()
+
+
+@contextlib.contextmanager
+def autocast(enabled: bool):
+    """Re-enters (or leaves) GPU autocast for the recomputation; a no-op where it is already in that state."""
+    if enabled and torch.cuda.is_available():
+        with torch.autocast("cuda", enabled=True):
+            yield
+    elif not enabled and torch.is_autocast_enabled():
+        with torch.autocast("cuda", enabled=False):
+            yield
+    else:
+        yield
+
+
 def _rebuild(meta, tensors):
     flat = [None] * (len(meta["tensor_idx"]) + len(meta["others"]))
     for i, t in zip(meta["tensor_idx"], tensors):
@@ -124,6 +142,7 @@ class _CheckpointFn(torch.autograd.Function):
         ctx.run_fn = run_fn
         ctx.meta = meta
         ctx.rng = _rng_state()
+        ctx.had_autocast = is_autocast_enabled()
         ctx.devices = [t.device for t in tensors]
         ctx.grad_flags = [t.requires_grad for t in tensors]
         saved = []
@@ -157,7 +176,7 @@ class _CheckpointFn(torch.autograd.Function):
             inputs.append(s)
         now = _rng_state()
         _set_rng_state(ctx.rng)
-        with torch.enable_grad(), enable_recomputing():
+        with torch.enable_grad(), enable_recomputing(), autocast(ctx.had_autocast):
             args, kwargs = _rebuild(ctx.meta, inputs)
             out = ctx.run_fn(*args, **kwargs)
         _set_rng_state(now)
@@ -167,3 +186,11 @@ class _CheckpointFn(torch.autograd.Function):
             torch.autograd.backward([o for o, _ in pairs], [g for _, g in pairs])
         in_grads = tuple(t.grad if t.requires_grad else None for t in inputs)
         return (None, None, None) + in_grads
+
+
+# the reference's public names for the pieces above (metaseq/modules/checkpoint_activation_wrapper/
+# checkpoint_activations.py:30, :235-262, :265)
+ThreadLocal = _State
+CheckpointFunction = _CheckpointFn
+get_rng_state = _rng_state
+set_rng_state = _set_rng_state

@@ -76,8 +76,7 @@ class VocabParallelEmbedding(nn.Module):
         if padding_idx is not None and self.vocab_start_index <= padding_idx < self.vocab_end_index:
             with torch.no_grad():
                 self.weight[padding_idx - self.vocab_start_index].zero_()
-        self.weight.model_parallel = world > 1
-        self.weight.partition_dim = 0
+        mpu.set_tensor_model_parallel_attributes(self.weight, world > 1, 0, 1)
 
     def forward(self, tokens):
         world = mpu.get_tensor_model_parallel_world_size()
@@ -99,6 +98,72 @@ def _linear(x, weight, bias=None):
     return TF.linear(x, weight, bias)
 
 
+def _mm(a, b, a_t=False, b_t=False):
+    """``op(a) @ op(b)`` on 2-D operands: the tcgen05 GEMM on a GPU with 16-bit operands, ``torch.matmul`` elsewhere."""
+    if ops_f.use_kernels(a) and a.dtype == b.dtype:
+        # functional.gemm computes a @ b^T for row-major operands; the flags select the transposed reads
+        return ops_f.gemm(a, b, a_mn=a_t, b_mn=not b_t)
+    return (a.t() if a_t else a) @ (b.t() if b_t else b)
+
+
+class LinearWithGradAccumulationAndAsyncCommunication(torch.autograd.Function):
+    """Column-parallel product whose backward pass hides its collective behind the weight-gradient GEMM
+    (reference: metaseq/modules/megatron/mpu/layers.py:253-383).
+
+    Forward: under sequence parallelism the rows of ``x`` are gathered over the tensor-parallel group first;
+    ``y = x W^T + b``.  Backward: the gathered input is rebuilt (asynchronously, behind the data-gradient product),
+    then the data gradient's all-reduce (``async_grad_allreduce``) or reduce-scatter (sequence parallelism) is
+    started, the weight gradient is computed while it runs, and the handle is waited on last.  With
+    ``gradient_accumulation_fusion`` the weight gradient is added into ``weight.main_grad`` (fp32) and ``None`` is
+    returned for it.  The fused decoder layer does the same overlap inside its GEMM kernels over peer memory; this
+    function is the library-collective form for stand-alone column-parallel layers."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, gradient_accumulation_fusion, async_grad_allreduce, sequence_parallel):
+        assert not (async_grad_allreduce and sequence_parallel), "sequence parallelism reduce-scatters instead"
+        ctx.save_for_backward(x, weight)
+        ctx.use_bias = bias is not None
+        ctx.flags = (bool(gradient_accumulation_fusion), bool(async_grad_allreduce), bool(sequence_parallel))
+        total = mappings.gather_along_first_dim(x) if sequence_parallel else x
+        y = _mm(total.reshape(-1, total.shape[-1]), weight, b_t=True).view(*total.shape[:-1], weight.shape[0])
+        return y + bias if bias is not None else y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight = ctx.saved_tensors
+        fuse_accumulation, async_allreduce, sequence_parallel = ctx.flags
+        world = mpu.get_tensor_model_parallel_world_size()
+        group = mpu.get_tensor_model_parallel_group()
+        dy = dy.contiguous()
+        dy2 = dy.view(-1, dy.shape[-1])
+        pending_gather = None
+        if sequence_parallel and world > 1:
+            total = torch.empty((x.shape[0] * world, *x.shape[1:]), dtype=x.dtype, device=x.device)
+            pending_gather = torch.distributed.all_gather_into_tensor(total, x.contiguous(), group=group, async_op=True)
+        else:
+            total = x
+        dx = _mm(dy2, weight).view(*dy.shape[:-1], weight.shape[1])
+        pending, finish = None, None
+        if world > 1 and async_allreduce:
+            pending = torch.distributed.all_reduce(dx, group=group, async_op=True)
+        elif world > 1 and sequence_parallel:
+            pending, finish = mappings.start_reduce_scatter_along_first_dim(dx)
+        if pending_gather is not None:
+            pending_gather.wait()
+        total2 = total.reshape(-1, total.shape[-1])
+        if fuse_accumulation:
+            weight.main_grad.addmm_(dy2.t().float(), total2.float())
+            dw = None
+        else:
+            dw = _mm(dy2, total2, a_t=True)
+        db = dy2.sum(dim=0) if ctx.use_bias else None
+        if pending is not None:
+            pending.wait()
+        if finish is not None:
+            dx = finish()
+        return dx, dw, db, None, None, None
+
+
 class ColumnParallelLinear(nn.Module):
     """``Y = X A^T + b`` with A split along its output dimension: ``A = [A_1; ...; A_p]``."""
 
@@ -114,12 +179,10 @@ class ColumnParallelLinear(nn.Module):
         self.output_size_per_partition = mpu.divide(output_size, world)
         self.weight = nn.Parameter(torch.empty(self.output_size_per_partition, input_size, dtype=dtype, device=device))
         _init_partition(self.weight, (output_size, input_size), 0, init_method, use_cpu_initialization, stride)
-        self.weight.model_parallel = world > 1
-        self.weight.partition_dim = 0
+        mpu.set_tensor_model_parallel_attributes(self.weight, world > 1, 0, stride)
         if bias:
             self.bias = nn.Parameter(torch.zeros(self.output_size_per_partition, dtype=dtype, device=device))
-            self.bias.model_parallel = world > 1
-            self.bias.partition_dim = 0
+            mpu.set_tensor_model_parallel_attributes(self.bias, world > 1, 0, stride)
         else:
             self.register_parameter("bias", None)
 
@@ -151,8 +214,7 @@ class RowParallelLinear(nn.Module):
         self.input_size_per_partition = mpu.divide(input_size, world)
         self.weight = nn.Parameter(torch.empty(output_size, self.input_size_per_partition, dtype=dtype, device=device))
         _init_partition(self.weight, (output_size, input_size), 1, init_method, use_cpu_initialization, stride)
-        self.weight.model_parallel = world > 1
-        self.weight.partition_dim = 1
+        mpu.set_tensor_model_parallel_attributes(self.weight, world > 1, 1, stride)
         if bias:
             self.bias = nn.Parameter(torch.zeros(output_size, dtype=dtype, device=device))
         else:

@@ -75,6 +75,21 @@ def reduce_scatter_along_first_dim(x):
     return out
 
 
+def start_reduce_scatter_along_first_dim(x):
+    """Starts the reduce-scatter of ``x`` over the tensor-parallel group and returns ``(handle, finish)``:
+    ``finish()`` gives this rank's rows once ``handle.wait()`` has returned.  Backends without a reduce-scatter
+    (gloo) all-reduce in place and ``finish`` slices."""
+    w = _world()
+    assert w > 1 and x.shape[0] % w == 0
+    x = x.contiguous()
+    if dist.get_backend(_group()) == "gloo":
+        handle = dist.all_reduce(x, group=_group(), async_op=True)
+        return handle, lambda: _split_first(x)
+    out = torch.empty((x.shape[0] // w, *x.shape[1:]), dtype=x.dtype, device=x.device)
+    handle = dist.reduce_scatter_tensor(out, x, group=_group(), async_op=True)
+    return handle, lambda: out
+
+
 class _CopyToModelParallelRegion(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x):

@@ -107,14 +107,57 @@ def get_data_parallel_rank() -> int:
     return dist.get_rank(group=_DP_GROUP)
 
 
-def divide(a: int, b: int) -> int:
+def ensure_divisibility(a: int, b: int) -> None:
     assert a % b == 0, f"{a} is not divisible by {b}"
+
+
+def divide(a: int, b: int) -> int:
+    ensure_divisibility(a, b)
     return a // b
 
 
 def vocab_range(global_vocab: int, rank: int, world: int):
     per = divide(global_vocab, world)
     return rank * per, (rank + 1) * per
+
+
+class VocabUtility:
+    """[first, last) of the vocabulary rows that ``rank`` owns (reference:
+    metaseq/modules/megatron/mpu/utils.py:47-63)."""
+
+    @staticmethod
+    def vocab_range_from_per_partition_vocab_size(per_partition_vocab_size: int, rank: int):
+        return rank * per_partition_vocab_size, (rank + 1) * per_partition_vocab_size
+
+    @staticmethod
+    def vocab_range_from_global_vocab_size(global_vocab_size: int, rank: int, world_size: int):
+        return vocab_range(global_vocab_size, rank, world_size)
+
+
+def split_tensor_along_last_dim(tensor: torch.Tensor, num_partitions: int, contiguous_split_chunks: bool = False):
+    """``num_partitions`` equal views of the last dimension (copies if ``contiguous_split_chunks``)."""
+    pieces = torch.split(tensor, divide(tensor.size(-1), num_partitions), dim=-1)
+    return tuple(p.contiguous() for p in pieces) if contiguous_split_chunks else pieces
+
+
+_PARTITION_ATTRIBUTES = {"tensor_model_parallel": False, "partition_dim": -1, "partition_stride": 1}
+
+
+def set_tensor_model_parallel_attributes(tensor, is_parallel: bool, dim: int, stride: int = 1) -> None:
+    """Marks a parameter as one rank's slice of a larger tensor: checkpoint tools and gradient-norm code read
+    ``tensor_model_parallel`` / ``partition_dim`` / ``partition_stride`` (reference:
+    metaseq/modules/megatron/mpu/layers.py:34-47); ``model_parallel`` is the flag that the trainer's
+    gradient-norm reduction looks at."""
+    for name in _PARTITION_ATTRIBUTES:
+        assert not hasattr(tensor, name), f"{name} is already set"
+    tensor.tensor_model_parallel = is_parallel
+    tensor.partition_dim = dim
+    tensor.partition_stride = stride
+    tensor.model_parallel = is_parallel
+
+
+def param_is_tensor_parallel(param) -> bool:
+    return bool(getattr(param, "tensor_model_parallel", False))
 
 
 # ------------------------------------------------------------------- RNG
@@ -179,6 +222,9 @@ class RNGStatesTracker:
 
 
 _RNG_TRACKER = RNGStatesTracker()
+
+
+CudaRNGStatesTracker = RNGStatesTracker  # the reference's name (metaseq/modules/megatron/mpu/random.py:98)
 
 
 def get_cuda_rng_tracker() -> RNGStatesTracker:

@@ -2,6 +2,7 @@
 with ``seed + 2718 + tp_rank``) and the 1-D split / gather used by distributed activation checkpointing
 (reference: metaseq/modules/megatron/mpu/random.py:60-220).  The implementations live in ``mpu``."""
 from .mpu import (  # noqa: F401
+    CudaRNGStatesTracker,
     RNGStatesTracker,
     gather_split_1d_tensor,
     get_cuda_rng_tracker,

@@ -332,3 +332,71 @@ def test_resume_from_shared_directory_takes_the_newest_complete_checkpoint(tmp_p
     monkeypatch.setenv("SLURM_RESTART_COUNT", "1")  # ... unless the job was requeued
     checkpoint_utils.load_checkpoint(cfg, FakeTrainer())
     assert seen["path"] == str(nfs / "checkpoint_10" / "checkpoint-shard0.pt")
+
+
+# ------------------------------------------------- column-parallel product with overlapped backward collectives
+def _async_linear_rank(rank, world, port, out):
+    import torch.distributed as dist
+
+    from metaseq_b200.parallel import mpu
+    from metaseq_b200.parallel.layers import LinearWithGradAccumulationAndAsyncCommunication as AsyncLinear
+
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    mpu.initialize_model_parallel(world)
+    torch.manual_seed(0)
+    T, B, K, N = 4 * world, 2, 6, 8 * world
+    x_full = torch.randn(T, B, K, dtype=torch.double)
+    w_full = torch.randn(N, K, dtype=torch.double)
+    b_full = torch.randn(N, dtype=torch.double)
+    g_full = torch.randn(T, B, N, dtype=torch.double)
+    n = N // world
+    w = w_full[rank * n:(rank + 1) * n].clone().requires_grad_()
+    b = b_full[rank * n:(rank + 1) * n].clone().requires_grad_()
+    g = g_full[..., rank * n:(rank + 1) * n]
+    res = {}
+    # plain tensor parallelism: the input is replicated, its gradient is all-reduced behind the weight gradient
+    x = x_full.clone().requires_grad_()
+    y = AsyncLinear.apply(x, w, b, False, True, False)
+    y.backward(g)
+    res["tp"] = (y.detach(), x.grad.clone(), w.grad.clone(), b.grad.clone())
+    # sequence parallelism: rows are gathered going in, the input gradient is reduce-scattered; the weight
+    # gradient goes straight into main_grad
+    w.grad = b.grad = None
+    w.main_grad = torch.zeros(n, K)
+    t = T // world
+    xs = x_full[rank * t:(rank + 1) * t].clone().requires_grad_()
+    y = AsyncLinear.apply(xs, w, b, True, False, True)
+    y.backward(g)
+    res["sp"] = (y.detach(), xs.grad.clone(), w.main_grad.clone(), w.grad, b.grad.clone())
+    out[rank] = res
+    mpu.destroy_model_parallel()
+    dist.destroy_process_group()
+
+
+def test_column_parallel_product_with_async_communication_matches_the_full_product():
+    import torch.multiprocessing as mp
+
+    world = 2
+    with mp.Manager() as mgr:
+        out = mgr.dict()
+        mp.spawn(_async_linear_rank, args=(world, _free_port(), out), nprocs=world, join=True)
+        res = dict(out)
+    torch.manual_seed(0)
+    T, B, K, N = 4 * world, 2, 6, 8 * world
+    x = torch.randn(T, B, K, dtype=torch.double, requires_grad=True)
+    w = torch.randn(N, K, dtype=torch.double, requires_grad=True)
+    b = torch.randn(N, dtype=torch.double, requires_grad=True)
+    g = torch.randn(T, B, N, dtype=torch.double)
+    y = torch.nn.functional.linear(x, w, b)
+    y.backward(g)
+    n, t = N // world, T // world
+    for r in range(world):
+        cols = slice(r * n, (r + 1) * n)
+        y_r, dx_r, dw_r, db_r = res[r]["tp"]
+        assert torch.allclose(y_r, y.detach()[..., cols]) and torch.allclose(dx_r, x.grad)
+        assert torch.allclose(dw_r, w.grad[cols]) and torch.allclose(db_r, b.grad[cols])
+        y_r, dx_r, main_grad, dw_r, db_r = res[r]["sp"]
+        assert torch.allclose(y_r, y.detach()[..., cols]) and torch.allclose(dx_r, x.grad[r * t:(r + 1) * t])
+        assert dw_r is None and torch.allclose(main_grad.double(), w.grad[cols], atol=1e-5)
+        assert torch.allclose(db_r, b.grad[cols])

@@ -30,6 +30,8 @@ VARIANTS = {
     "fully_sharded": POLY + ["--ddp-backend", "fully_sharded", "--use-sharded-state"],
     "fp16_adam_stats": POLY + ["--memory-efficient-fp16", "--fp16-init-scale", "4", "--fp16-adam-stats"],
     "loss_spike_guard": POLY + ["--ewm-ratio-to-skip-batch", "2.0"],
+    "two_layers_per_sharded_unit": POLY + ["--ddp-backend", "fully_sharded", "--checkpoint-activations",
+                                           "--fsdp-checkpoint-wrap-layer-frequency", "2"],
 }
 
 
@@ -99,3 +101,9 @@ def test_two_identical_micro_batches_give_the_update_of_one(tmp_path, flags):
 
     one, two = run(1), run(2)
     assert two == pytest.approx(one, rel=2e-2), (one, two)
+
+
+def test_layers_grouped_into_one_sharded_unit_train_like_one_unit_per_layer(tmp_path):
+    base = _run(tmp_path / "a", POLY + ["--ddp-backend", "fully_sharded"])
+    grouped = _run(tmp_path / "b", POLY + ["--ddp-backend", "fully_sharded", "--fsdp-checkpoint-wrap-layer-frequency", "2"])
+    assert grouped == pytest.approx(base, rel=1e-5)
