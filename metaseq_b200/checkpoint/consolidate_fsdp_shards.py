@@ -67,6 +67,34 @@ def consolidate_fsdp_shards(pth_prefix: str, save_prefix=None, new_arch_name=Non
     return written
 
 
+def consolidate_model_parallel(metadata, names, strict, weights, parts: int = 2, no_stitch_megatron: bool = False):
+    """In memory: ``weights[i]`` / ``metadata[i]`` are the ``model`` dict and ``shard_metadata`` of the file called
+    ``names[i]`` (``...part-<p>...``).  Every model part's shards are unflattened; the parts are then joined into one
+    model unless ``no_stitch_megatron``, in which case ``{part: state dict}`` is returned (reference:
+    metaseq/distributed/stitch_fsdp_ckpt.py:180-200; ``strict`` is accepted for the signature: a missing name
+    always raises here)."""
+    from metaseq_b200.checkpoint.reshard_mp import reshard_megatron_parts
+
+    per_part = {}
+    for p in range(parts):
+        picked = [i for i, n in enumerate(names) if f"part-{p}" in n]
+        if picked:
+            states = [{"model": weights[i], "shard_metadata": metadata[i]} for i in picked]
+            per_part[p] = unflatten_state(states)["model"]
+    if no_stitch_megatron:
+        return per_part
+    return reshard_megatron_parts(per_part, new_model_part_count=1)[0]
+
+
+def handle_qkv_proj(model_parts, key: str, new_model_part_count: int):
+    """The fused projection of every part is three stacked blocks (K, V, Q order); each block is joined over the
+    parts and cut again into ``new_model_part_count`` pieces.  Returns the three tuples of pieces (reference:
+    metaseq/distributed/stitch_fsdp_ckpt.py:203-214)."""
+    blocks = [model_parts[i][key].view(3, -1, *model_parts[i][key].shape[1:]) for i in range(len(model_parts))]
+    joined = torch.cat(blocks, dim=1)
+    return tuple(torch.chunk(joined[j], new_model_part_count) for j in range(3))
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("pth_prefix")

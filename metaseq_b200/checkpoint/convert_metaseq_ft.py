@@ -66,6 +66,23 @@ def symmetric_int8_last_axis(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tenso
     return q, scale.to(w.dtype)
 
 
+def int8_weight_only_quantize(weights: List[torch.Tensor], num_layers: int) -> Tuple[List[torch.Tensor], List[torch.Tensor]]:
+    """The four matrix slots of the consumer's weight list (fused projection, output projection, the two
+    feed-forward matrices) as int8 with one scale per output column; their 16-bit copies are emptied in place.
+    The reference calls the consumer library's own quantiser for this (metaseq/scripts/convert_metaseq_ft.py:99-133);
+    the same symmetric per-column rule is computed here."""
+    q_w: List[torch.Tensor] = []
+    q_s: List[torch.Tensor] = []
+    for slot in _QUANTIZED_SLOTS:
+        for i in range(num_layers):
+            w = weights[slot * num_layers + i]
+            q, s = symmetric_int8_last_axis(w.flatten(1) if w.dim() == 3 else w)
+            q_w.append(q)
+            q_s.append(s)
+            weights[slot * num_layers + i] = w.new_empty(0)
+    return q_w, q_s
+
+
 def convert_weights(state_dict, embedding_tokens, dtype, quantize=False) -> Dict[str, List[torch.Tensor]]:
     n = num_layers_of(state_dict)
     weights: List[torch.Tensor] = []
@@ -78,15 +95,7 @@ def convert_weights(state_dict, embedding_tokens, dtype, quantize=False) -> Dict
     weights += [embedding_tokens, embedding_tokens]
     out = {"weights": weights}
     if quantize:
-        q_w, q_s = [], []
-        for slot in _QUANTIZED_SLOTS:
-            for i in range(n):
-                w = weights[slot * n + i]
-                q, s = symmetric_int8_last_axis(w.flatten(1) if w.dim() == 3 else w)
-                q_w.append(q)
-                q_s.append(s)
-                weights[slot * n + i] = w.new_empty(0)  # the 16-bit copy is not needed any more
-        out["int8_weights"], out["int8_scales"] = q_w, q_s
+        out["int8_weights"], out["int8_scales"] = int8_weight_only_quantize(weights, n)
     return out
 
 

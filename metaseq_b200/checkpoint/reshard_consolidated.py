@@ -11,6 +11,7 @@ metaseq/scripts/reshard_consolidated.py:21-84).
 from __future__ import annotations
 
 import argparse
+import copy
 import logging
 import os
 import re
@@ -78,6 +79,50 @@ def reshard_consolidated(src: str, dst_dir_pattern: str, num_output_shards: int)
         st["model"] = new_model
         st["shard_metadata"] = {"param_metadata": entries, "buffer_names": list(buffers.keys())}
         dst = dst_dir_pattern.format(i=r)
+        os.makedirs(os.path.dirname(os.path.abspath(dst)), exist_ok=True)
+        torch.save(st, dst)
+        written.append(dst)
+    return written
+
+
+def reshard_unflattened_model_weights(unsharded_weights: Dict[str, torch.Tensor], shard_metadata: Dict[str, Any],
+                                      num_output_shards: int = 1):
+    """In memory: named tensors plus the ``shard_metadata`` that says which names form which flat parameter ->
+    ``(weights, metadata)`` with one flat, padded shard dict per output rank.  Buffers are copied to every shard.
+    Used when the checkpoint already carries metadata (``reshard_consolidated`` derives the grouping from the
+    parameter names instead).  Reference: metaseq/scripts/reshard_consolidated.py:53-84."""
+    weights: List[Dict[str, torch.Tensor]] = [dict() for _ in range(num_output_shards)]
+    for name in shard_metadata.get("buffer_names", []):
+        if name not in unsharded_weights:
+            raise ValueError(f"No buffer found for buffer name {name}.")
+        for w in weights:
+            w[name] = unsharded_weights[name]
+    metadata = [copy.deepcopy(shard_metadata) for _ in range(num_output_shards)]
+    for idx, entry in enumerate(shard_metadata["param_metadata"]):
+        path = entry.get("fsdp_path", "")
+        for flat_name, md in entry["params"].items():
+            full = [f"{path}.{n}" if path else n for n in md["names"]]
+            vec = torch.cat([unsharded_weights[f].reshape(-1) for f in full])
+            key = f"{path}.{flat_name}" if path else flat_name
+            for r in range(num_output_shards):
+                weights[r][key], pad = flat_shards.slice_for_rank(vec, r, num_output_shards)
+                metadata[r]["param_metadata"][idx]["params"][flat_name]["padding"] = pad
+    return weights, metadata
+
+
+def reshard_consolidated_checkpoint(input: str, output: str, num_output_shards: int = 1) -> List[str]:
+    """The reference's entry point name and argument names (metaseq/scripts/reshard_consolidated.py:21-50).  A
+    checkpoint that carries ``shard_metadata`` is cut along it; one without is grouped by parameter name."""
+    state = torch_load_cpu(input)
+    if not state.get("shard_metadata"):
+        return reshard_consolidated(input, output, num_output_shards)
+    weights, metadata = reshard_unflattened_model_weights(dict(state["model"]), state["shard_metadata"], num_output_shards)
+    written = []
+    for r in range(num_output_shards):
+        st = {k: v for k, v in state.items() if k not in ("model", "shard_metadata", "optimizer_state",
+                                                           "last_optimizer_state")}
+        st["model"], st["shard_metadata"] = weights[r], metadata[r]
+        dst = output.format(i=r)
         os.makedirs(os.path.dirname(os.path.abspath(dst)), exist_ok=True)
         torch.save(st, dst)
         written.append(dst)

@@ -17,7 +17,7 @@ import glob
 import logging
 import os
 import re
-from typing import Any, Dict, List
+from typing import Any, Dict, List, Optional
 
 import torch
 
@@ -37,28 +37,100 @@ def _sorted_shards(pattern: str) -> List[str]:
     return sorted(files, key=key)
 
 
+_DTYPES = {"fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16}
+
+
+def _cast(t, dtype: Optional[torch.dtype]):
+    return t.to(dtype) if dtype is not None and torch.is_tensor(t) and t.is_floating_point() else t
+
+
+def reshard_fsdp_model_weights(shard_weights: List[Dict[str, torch.Tensor]], shard_metadata: List[Dict[str, Any]],
+                               num_output_shards: int = 1, unflatten_weights: bool = False,
+                               dtype: Optional[torch.dtype] = None):
+    """In memory: the ``model`` dicts and ``shard_metadata`` of every input shard -> ``(weights, metadata)``, one
+    entry per output shard.  With ``unflatten_weights`` (one output shard only) the flat vectors are split back
+    into named tensors (reference: metaseq/scripts/reshard_fsdp.py:143-206)."""
+    if len(shard_weights) != len(shard_metadata):
+        raise ValueError("Expect shard weights and shard metadata to have same length.")
+    if unflatten_weights and num_output_shards > 1:
+        raise ValueError("Unflatten weights only if the number of output shards is 1.")
+    states = [{"model": w, "shard_metadata": m} for w, m in zip(shard_weights, shard_metadata)]
+    if unflatten_weights:
+        model = unflatten_state(states)["model"]
+        return [{k: _cast(v, dtype) for k, v in model.items()}], [shard_metadata[0]]
+    weights, metadata = [], []
+    for r in range(num_output_shards):
+        w, m = flat_shards.reshard_model_state(states, r, num_output_shards)
+        weights.append({k: _cast(v, dtype) for k, v in w.items()})
+        metadata.append(m)
+    return weights, metadata
+
+
+def reshard_fsdp_optim_state(shard_optim_states: List[Dict[str, Any]], shard_metadata: List[Dict[str, Any]],
+                             shard_weights: List[Dict[str, torch.Tensor]], num_output_shards: int = 1,
+                             dtype: Optional[torch.dtype] = None) -> List[Dict[str, Any]]:
+    """In memory: every input shard's optimizer state -> one per output shard.  The i-th optimizer entry belongs
+    to the i-th flat parameter, whose padding comes from the metadata (reference:
+    metaseq/scripts/reshard_fsdp.py:209-250, which is handed the paddings as a list)."""
+    if any("state" not in s for s in shard_optim_states):
+        raise ValueError("Each sharded optimizer state dict should contain `state`.")
+    states = [{"model": w, "shard_metadata": m, "last_optimizer_state": o}
+              for w, m, o in zip(shard_weights, shard_metadata, shard_optim_states)]
+    out = []
+    for r in range(num_output_shards):
+        st = flat_shards.reshard_optimizer_state(states, r, num_output_shards)
+        st["state"] = {i: {k: _cast(v, dtype) if torch.is_tensor(v) and v.dim() > 0 else v for k, v in e.items()}
+                       for i, e in st["state"].items()}
+        out.append(st)
+    return out
+
+
+def reshard_fsdp_state_dicts(shard_state_dicts: List[Dict[str, Any]], num_output_shards: int = 1,
+                             unflatten_weights: bool = True, skip_optimizer_state: bool = False,
+                             dtype: Optional[torch.dtype] = None, drop_metaseq_req: bool = False) -> List[Dict[str, Any]]:
+    """In memory: the checkpoint dicts of all shards of one model part -> ``num_output_shards`` checkpoint dicts.
+    Everything but weights, metadata and optimizer state is copied from the first shard; ``drop_metaseq_req``
+    removes the data iterator's state when it carries a tokenizer cache, which only unpickles with this package
+    importable (reference: metaseq/scripts/reshard_fsdp.py:81-140)."""
+    logger.info(f"Resharding state dicts into {num_output_shards} shard(s)")
+    weights, metadata = reshard_fsdp_model_weights(
+        [s["model"] for s in shard_state_dicts], [s.get("shard_metadata") for s in shard_state_dicts],
+        num_output_shards, unflatten_weights, dtype)
+    out: List[Dict[str, Any]] = []
+    for w, m in zip(weights, metadata):
+        out.append({"model": w} if unflatten_weights else {"model": w, "shard_metadata": m})
+    if not skip_optimizer_state and not unflatten_weights and "last_optimizer_state" in shard_state_dicts[0]:
+        opt = reshard_fsdp_optim_state(
+            [s["last_optimizer_state"] for s in shard_state_dicts], [s.get("shard_metadata") for s in shard_state_dicts],
+            [s["model"] for s in shard_state_dicts], num_output_shards, dtype)
+        for d, o in zip(out, opt):
+            d["last_optimizer_state"] = o
+    first = shard_state_dicts[0]
+    if drop_metaseq_req:
+        itr = (first.get("extra_state") or {}).get("train_iterator")
+        if isinstance(itr, dict) and "tokenization_cache" in itr:
+            first = dict(first, extra_state=dict(first["extra_state"], train_iterator=None))
+    for key, val in first.items():
+        if key not in ("model", "shard_metadata", "last_optimizer_state"):
+            for d in out:
+                d[key] = val
+    return out
+
+
 def reshard_fsdp_checkpoints(src_dir_pattern: str, dst_dir_pattern: str, num_output_shards: int = 1,
-                             unflatten_weights: bool = False, skip_optimizer_state: bool = False) -> List[str]:
+                             unflatten_weights: bool = False, skip_optimizer_state: bool = False,
+                             output_dtype: Optional[str] = None, drop_metaseq_req: bool = False) -> List[str]:
+    if output_dtype and output_dtype not in _DTYPES:
+        raise ValueError(f"The specified output dtype {output_dtype} is not supported.")
     paths = _sorted_shards(src_dir_pattern)
-    assert len(paths) > 0, f"no files match {src_dir_pattern}"
+    if not paths:
+        raise ValueError(f"The glob pattern {src_dir_pattern} doesn't match any sharded checkpoints.")
     logger.info(f"Loading {len(paths)} shards")
     states = [torch_load_cpu(p) for p in paths]
-    if skip_optimizer_state:
-        for s in states:
-            s.pop("last_optimizer_state", None)
+    new_states = reshard_fsdp_state_dicts(states, num_output_shards, unflatten_weights, skip_optimizer_state,
+                                          _DTYPES.get(output_dtype), drop_metaseq_req)
     written = []
-    if unflatten_weights:
-        assert num_output_shards == 1, "unflattening produces a single consolidated file per model part"
-        out = unflatten_state(states)
-        dst = dst_dir_pattern.format(i=0)
-        os.makedirs(os.path.dirname(os.path.abspath(dst)), exist_ok=True)
-        torch.save(out, dst)
-        return [dst]
-    for r in range(num_output_shards):
-        new = {k: v for k, v in states[0].items() if k not in ("model", "shard_metadata", "last_optimizer_state")}
-        new["model"], new["shard_metadata"] = flat_shards.reshard_model_state(states, r, num_output_shards)
-        if not skip_optimizer_state and "last_optimizer_state" in states[0]:
-            new["last_optimizer_state"] = flat_shards.reshard_optimizer_state(states, r, num_output_shards)
+    for r, new in enumerate(new_states):
         dst = dst_dir_pattern.format(i=r)
         os.makedirs(os.path.dirname(os.path.abspath(dst)), exist_ok=True)
         torch.save(new, dst)
@@ -99,10 +171,13 @@ def main(argv=None):
     ap.add_argument("--num-output-shards", type=int, default=1)
     ap.add_argument("--unflatten-weights", action="store_true")
     ap.add_argument("--skip-optimizer-state", action="store_true")
+    ap.add_argument("--output-dtype", choices=sorted(_DTYPES), default=None, help="convert floating-point weights")
+    ap.add_argument("--drop-metaseq-req", action="store_true",
+                    help="drop the data iterator state, which needs this package to unpickle")
     a = ap.parse_args(argv)
     logging.basicConfig(level=logging.INFO)
     for p in reshard_fsdp_checkpoints(a.src_dir_pattern, a.dst_dir_pattern, a.num_output_shards, a.unflatten_weights,
-                                      a.skip_optimizer_state):
+                                      a.skip_optimizer_state, a.output_dtype, a.drop_metaseq_req):
         print(p)
 
 

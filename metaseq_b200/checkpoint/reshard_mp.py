@@ -138,6 +138,24 @@ def reshard_mp(src_dir_pattern: str, dst_dir_pattern: str, num_output_parts: int
     return written
 
 
+def reshard_model_parallel_parts(input: str, output: str, num_output_parts: int = 1, eps: float = 1e-8) -> List[str]:
+    """The reference's entry point name and argument names (metaseq/scripts/reshard_mp.py:17-119): ``input`` is a
+    glob over the parts, ``output`` a pattern with ``{i}``; tensors that every part replicates are taken from
+    part 0, with a warning when another part's copy is further than ``eps`` away."""
+    paths = _sorted_parts(input)
+    if not paths:
+        raise ValueError("The glob pattern doesn't match any model parallel parts.")
+    first = torch_load_cpu(paths[0])["model"]
+    for p in paths[1:]:
+        other = torch_load_cpu(p)["model"]
+        for key, t in first.items():
+            if torch.is_tensor(t) and SHARED.search(key) and "qkv_proj" not in key and t.shape == other[key].shape:
+                diff = float((t.float() - other[key].float()).abs().max()) if t.numel() else 0.0
+                if diff > eps:
+                    logger.warning(f"Max value discrepancy for key '{key}': {diff:.4e}")
+    return reshard_mp(input, output, num_output_parts, drop_optimizer_state=True)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--src-dir-pattern", required=True)

@@ -456,3 +456,91 @@ def test_launcher_tells_failed_runs_from_running_ones(tmp_path):
     log.write_text("")
     slurm.write_git_commit(str(log))
     assert log.read_text() == "" or log.read_text().startswith("commit ")
+
+
+def test_fsdp_reshard_functions_work_on_state_dicts_in_memory():
+    """Two shards of one flat parameter (two tensors, padded) -> three shards -> one unflattened dict."""
+    from metaseq_b200.checkpoint import flat_shards, reshard_fsdp
+
+    a, b = torch.arange(6.0).view(2, 3), torch.arange(6.0, 11.0)
+    full = torch.cat([a.flatten(), b])
+    per = flat_shards.shard_size_for(full.numel(), 2)
+    padded = torch.cat([full, torch.zeros(2 * per - full.numel())])
+
+    def shard(r):
+        pad = max(0, min(per, (r + 1) * per - full.numel()))
+        md = {"param_metadata": [{"fsdp_path": "decoder", "params": {"flat_param_0": {
+            "names": ["w", "v"], "shapes": [[2, 3], [5]], "numels": [6, 5], "padding": pad}},
+            "no_broadcast_optim_state": False, "shared_param_info": []}], "buffer_names": []}
+        piece = padded[r * per:(r + 1) * per].clone()
+        return {"model": {"decoder.flat_param_0": piece, "decoder.version": torch.tensor([3.0])}, "shard_metadata": md,
+                "last_optimizer_state": {"state": {0: {"step": 4, "exp_avg": piece * 0.5}}, "param_groups": [{"lr": 0.1}]},
+                "cfg": {"x": 1}, "extra_state": {"train_iterator": {"tokenization_cache": b"big", "epoch": 2}}}
+
+    three = reshard_fsdp.reshard_fsdp_state_dicts([shard(0), shard(1)], num_output_shards=3, unflatten_weights=False,
+                                                  dtype=torch.float16, drop_metaseq_req=True)
+    assert len(three) == 3 and all(s["cfg"] == {"x": 1} and s["extra_state"]["train_iterator"] is None for s in three)
+    assert all(s["model"]["decoder.flat_param_0"].dtype == torch.float16 for s in three)
+    assert three[0]["last_optimizer_state"]["state"][0]["step"] == 4
+    back = reshard_fsdp.reshard_fsdp_state_dicts(three, num_output_shards=1, unflatten_weights=True)
+    assert set(back[0]) == {"model", "cfg", "extra_state"}
+    assert torch.equal(back[0]["model"]["decoder.w"].float(), a) and torch.equal(back[0]["model"]["decoder.v"].float(), b)
+    opt = reshard_fsdp.reshard_fsdp_optim_state(
+        [s["last_optimizer_state"] for s in three], [s["shard_metadata"] for s in three],
+        [s["model"] for s in three], num_output_shards=1)
+    assert torch.allclose(opt[0]["state"][0]["exp_avg"][:11].float(), full * 0.5)
+    with pytest.raises(ValueError, match="Unflatten weights only"):
+        reshard_fsdp.reshard_fsdp_model_weights([shard(0)["model"]], [shard(0)["shard_metadata"]], 2, True)
+
+
+def test_stitching_functions_consolidate_parts_and_recut_the_fused_projection(tmp_path):
+    from metaseq_b200.checkpoint import consolidate_fsdp_shards as cons
+    from metaseq_b200.checkpoint import reshard_consolidated, reshard_mp
+
+    torch.manual_seed(0)
+    D = 4
+    full = {"decoder.layers.0.self_attn.qkv_proj.weight": torch.randn(3 * D, D),
+            "decoder.layers.0.fc2.weight": torch.randn(D, 2 * D), "decoder.layers.0.fc2.bias": torch.randn(D),
+            "decoder.embed_tokens.weight": torch.randn(8, D)}
+    parts = reshard_mp.reshard_megatron_parts([full], new_model_part_count=2)
+    ks, vs, qs = cons.handle_qkv_proj(parts, "decoder.layers.0.self_attn.qkv_proj.weight", 1)
+    assert torch.equal(torch.cat([ks[0], vs[0], qs[0]]), full["decoder.layers.0.self_attn.qkv_proj.weight"])
+
+    # every part as two flat shards, then back through consolidate_model_parallel
+    weights, metadata, names = [], [], []
+    for p, part in enumerate(parts):
+        md = {"param_metadata": [{"fsdp_path": "", "params": {"flat_param_0": {
+            "names": list(part), "shapes": [list(t.shape) for t in part.values()],
+            "numels": [t.numel() for t in part.values()], "padding": 0}},
+            "no_broadcast_optim_state": False, "shared_param_info": []}], "buffer_names": []}
+        w, m = reshard_consolidated.reshard_unflattened_model_weights(dict(part), md, 2)
+        for r in range(2):
+            weights.append(w[r])
+            metadata.append(m[r])
+            names.append(f"ckpt-model_part-{p}-shard{r}.pt")
+    glued = cons.consolidate_model_parallel(metadata, names, True, weights, parts=2)
+    assert set(glued) == set(full) and all(torch.equal(glued[k], full[k]) for k in full)
+    kept = cons.consolidate_model_parallel(metadata, names, True, weights, parts=2, no_stitch_megatron=True)
+    assert sorted(kept) == [0, 1] and torch.equal(kept[1]["decoder.layers.0.fc2.weight"], parts[1]["decoder.layers.0.fc2.weight"])
+
+    # the file-level entry points under the reference's names
+    for p, part in enumerate(parts):
+        torch.save({"model": part, "cfg": {"model": {"model_parallel_size": 2}}}, tmp_path / f"in-model_part-{p}.pt")
+    out = reshard_mp.reshard_model_parallel_parts(str(tmp_path / "in-model_part-*.pt"), str(tmp_path / "one-{i}.pt"), 1)
+    one = torch.load(out[0], weights_only=False)
+    assert all(torch.equal(one["model"][k], full[k]) for k in full) and one["cfg"]["model"]["model_parallel_size"] == 1
+    with pytest.raises(ValueError, match="doesn't match any"):
+        reshard_mp.reshard_model_parallel_parts(str(tmp_path / "none-*.pt"), str(tmp_path / "x-{i}.pt"))
+
+
+def test_int8_weight_only_quantize_fills_the_four_matrix_slots():
+    from metaseq_b200.checkpoint import convert_metaseq_ft as ft
+
+    n = 2
+    weights = [torch.randn(6, 3, 4) if slot == 2 else torch.randn(6, 8) for slot in range(12) for _ in range(n)]
+    kept = [w.clone() for w in weights]
+    q, s = ft.int8_weight_only_quantize(weights, n)
+    assert len(q) == len(s) == 4 * n and all(t.dtype == torch.int8 for t in q)
+    w0 = kept[2 * n].flatten(1)
+    assert torch.allclose(q[0].float() * s[0], w0, atol=float(w0.abs().max()) / 127 + 1e-6)
+    assert weights[2 * n].numel() == 0 and weights[0].numel() > 0
