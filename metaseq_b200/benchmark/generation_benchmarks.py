@@ -64,7 +64,111 @@ def main(cfg, grid=None, warmup=2, repeats=5, out=None):
                 f.write(json.dumps(r) + "\n")
 
 
+# ---- the reference's fixed-prompt benchmark: one forward pass over 1000 copies of a sentence per released model
+PROMPTS = ["Paris is the capital of France and it"] * 1000
+_RELEASE = "https://dl.fbaipublicfiles.com/opt/v1_20220502"
+_PARTS = {"125m": 2, "1.3b": 2, "2.7b": 4, "6.7b": 2, "13b": 2, "30b": 2}
+LINKS_TO_DATA = {name: [f"{_RELEASE}/{name}/reshard-model_part-{i}.pt" for i in range(n)] for name, n in _PARTS.items()}
+LINKS_TO_DATA["66b"] = [f"{_RELEASE}/66b/reshard-model_part-{i}-shard0.pt" for i in range(8)]
+LINKS_TO_DATA["dependencies"] = ["http://dl.fbaipublicfiles.com/metaseq_benchmark_dependencies.tar.gz"]
+
+
+def load_mp_model_and_run_eval(cfg, model_path: str = "", prompts=None, **_unused):
+    """On every rank: tokenize the prompts, load this rank's model part, score all prompts in one forward pass.
+    Returns the seconds (tokenization + forward) of every rank (reference:
+    metaseq/scripts/generation_benchmarks.py:79-142)."""
+    import time
+
+    from metaseq_b200.hub_utils import setup_vocab_and_merges, tensorize_input
+
+    prompts = PROMPTS if prompts is None else prompts
+    on_gpu = torch.cuda.is_available() and not cfg.common.cpu
+    _, _, tokenizer = setup_vocab_and_merges(model_path)
+    t0 = time.perf_counter()
+    ids = torch.cat([tensorize_input(tokenizer, p) for p in prompts])
+    if on_gpu:
+        ids = ids.cuda()
+    tokenize_s = time.perf_counter() - t0
+    generator = GeneratorInterface(cfg)
+    model = generator.load_model()[0].eval()
+    with torch.no_grad():
+        if on_gpu:
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            model(ids)
+            end.record()
+            torch.cuda.synchronize()
+            forward_s = start.elapsed_time(end) / 1e3
+        else:
+            t0 = time.perf_counter()
+            model(ids)
+            forward_s = time.perf_counter() - t0
+    mine = torch.tensor([tokenize_s + forward_s], device=ids.device)
+    if not torch.distributed.is_initialized():
+        return [mine]
+    times = [torch.zeros_like(mine) for _ in range(dist_utils.get_global_world_size())]
+    torch.distributed.all_gather(times, mine, group=dist_utils.get_global_group())
+    return times
+
+
+def generation_statistics(model_path: str, prompts=None, cpu: bool = False):
+    """Prints the mean time over ranks and characters of prompt per second, as the reference does (it calls them
+    words)."""
+    from metaseq_b200.checkpoint.convert_to_singleton import create_generation_config_with_defaults
+
+    cfg = create_generation_config_with_defaults(model_path)
+    cfg.common.cpu = cfg.common.cpu or cpu
+    prompts = PROMPTS if prompts is None else prompts
+    times = dist_utils.call_main(cfg, load_mp_model_and_run_eval, model_path=model_path, prompts=prompts)
+    mean_s = float(sum(float(t) for t in times) / len(times))
+    print("Total generation time " + str(mean_s))
+    print("Words per second : " + str(len(prompts[0]) * len(prompts) / mean_s))
+    return mean_s
+
+
+def download_data(key: str, into: str = "."):
+    """Fetches the tokenizer files and the released checkpoint parts of ``key`` into ``<into>/dependencies``
+    (needs network access)."""
+    import tarfile
+    import urllib.request
+
+    if key not in LINKS_TO_DATA or key == "dependencies":
+        raise AssertionError(f"You passed model name {key}. Please make sure that model name is in "
+                             f"{[k for k in LINKS_TO_DATA if k != 'dependencies']}")
+    import os
+
+    for url in LINKS_TO_DATA["dependencies"]:
+        archive = os.path.join(into, "dependencies.tar.gz")
+        urllib.request.urlretrieve(url, archive)
+        with tarfile.open(archive) as tar:
+            tar.extractall(into)
+    for url in LINKS_TO_DATA[key]:
+        urllib.request.urlretrieve(url, os.path.join(into, "dependencies", url.rsplit("/", 1)[1]))
+
+
+def cleanup_data(into: str = "."):
+    import os
+    import shutil
+
+    shutil.rmtree(os.path.join(into, "dependencies"), ignore_errors=True)
+    if os.path.exists(os.path.join(into, "dependencies.tar.gz")):
+        os.remove(os.path.join(into, "dependencies.tar.gz"))
+
+
 def cli_main():
+    if any(a.startswith("--model_name") or a.startswith("--model-name") for a in sys.argv[1:]):
+        import argparse
+
+        ap = argparse.ArgumentParser(description="fixed-prompt benchmark over released models (downloads them)")
+        ap.add_argument("--model_name", "--model-name", nargs="+", required=True)
+        names = ap.parse_args().model_name
+        for key in names:
+            print("Now running generation benchmarks for " + str(key))
+            download_data(key)
+            generation_statistics(model_path="./dependencies")
+            cleanup_data()
+        return 0
+
     parser = options.get_generation_parser()
     parser.add_argument("--batch-sizes", default="1,8")
     parser.add_argument("--prompt-lengths", default="32,256")

@@ -32,6 +32,35 @@ def convert_to_singleton(src_dir: str, prefix: str = "reshard", out_name: str = 
     return dst
 
 
+def create_generation_config_with_defaults(model_path: str, ddp_backend: str = "pytorch_ddp"):
+    """A generation config for the checkpoint directory ``model_path`` with everything that can be read off the
+    directory filled in: model-parallel size = number of ``reshard*.pt`` files, tokenizer files from their
+    conventional names (``gpt2-unified.json``, else ``gpt2-vocab.json`` + ``gpt2-merges.txt``), checkpoint path
+    ``<dir>/reshard.pt`` (reference: metaseq/scripts/convert_to_singleton.py:56-117)."""
+    import glob
+
+    from metaseq_b200 import options
+    from metaseq_b200.dataclass.utils import convert_namespace_to_config
+
+    mp = max(1, len(glob.glob(os.path.join(model_path, "reshard*.pt"))))
+    unified = os.path.join(model_path, "gpt2-unified.json")
+    merges, vocab = os.path.join(model_path, "gpt2-merges.txt"), os.path.join(model_path, "gpt2-vocab.json")
+    if os.path.exists(unified):
+        tokenizer_args = ["--hf-tokenizer", unified]
+    else:
+        tokenizer_args = ["--bpe-merges", merges, "--merges-filename", merges, "--bpe-vocab", vocab,
+                          "--vocab-filename", vocab]
+    argv = ["--model-parallel-size", str(mp), "--distributed-world-size", str(mp), "--ddp-backend", ddp_backend,
+            "--task", "language_modeling", *tokenizer_args, "--bpe", "hf_byte_bpe",
+            "--path", os.path.join(model_path, "reshard.pt"), "--checkpoint-shard-count", "1", "--use-sharded-state",
+            model_path]
+    parser = options.get_generation_parser()
+    parser.set_defaults(lr_scheduler=None, criterion=None)
+    cfg = convert_namespace_to_config(options.parse_args_and_arch(parser, input_args=argv))
+    cfg.distributed_training.distributed_world_size = mp
+    return cfg
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("location")

@@ -94,6 +94,7 @@ class BaseModel(nn.Module):
         def train(mode=True):
             if mode:
                 raise RuntimeError("cannot train after make_generation_fast")
+            return self  # .eval() keeps returning the module
 
         self.train = train
 

@@ -231,3 +231,18 @@ def test_profile_flag_writes_a_trace_and_a_memory_table(tmp_path):
     events = json.loads(trace.read_text())
     assert "traceEvents" in events and len(events["traceEvents"]) > 10
     assert (save / "memory_usage.txt").exists()
+
+
+def test_fixed_prompt_generation_benchmark_runs_from_a_checkpoint_directory(trained, tmp_path, capsys):
+    """The directory layout that the released models use: ``reshard*.pt`` beside ``gpt2-vocab.json`` and
+    ``gpt2-merges.txt``; everything else is inferred."""
+    import shutil
+
+    from metaseq_b200.benchmark import generation_benchmarks as gb
+
+    shutil.copy(_checkpoint(trained), tmp_path / "reshard.pt")
+    shutil.copy(trained["vocab"], tmp_path / "gpt2-vocab.json")
+    shutil.copy(trained["merges"], tmp_path / "gpt2-merges.txt")
+    seconds = gb.generation_statistics(str(tmp_path), prompts=["the quick brown fox"] * 8, cpu=True)
+    out = capsys.readouterr().out
+    assert seconds > 0 and "Total generation time" in out and "Words per second" in out

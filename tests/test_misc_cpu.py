@@ -544,3 +544,17 @@ def test_int8_weight_only_quantize_fills_the_four_matrix_slots():
     w0 = kept[2 * n].flatten(1)
     assert torch.allclose(q[0].float() * s[0], w0, atol=float(w0.abs().max()) / 127 + 1e-6)
     assert weights[2 * n].numel() == 0 and weights[0].numel() > 0
+
+
+def test_generation_config_is_inferred_from_a_checkpoint_directory(tmp_path):
+    from metaseq_b200.checkpoint.convert_to_singleton import create_generation_config_with_defaults
+
+    for p in range(2):
+        (tmp_path / f"reshard-model_part-{p}.pt").write_bytes(b"")
+    cfg = create_generation_config_with_defaults(str(tmp_path))
+    assert cfg.common.model_parallel_size == 2 and cfg.distributed_training.distributed_world_size == 2
+    assert cfg.common_eval.path == str(tmp_path / "reshard.pt")
+    assert cfg.task.vocab_filename == str(tmp_path / "gpt2-vocab.json")
+    (tmp_path / "gpt2-unified.json").write_text("{}")
+    cfg = create_generation_config_with_defaults(str(tmp_path))
+    assert cfg.task.hf_tokenizer == str(tmp_path / "gpt2-unified.json")
