@@ -4,6 +4,7 @@ fetch is attempted only when the file is not already cached and fails with a cle
 from __future__ import annotations
 
 import fnmatch
+import functools
 import json
 import logging
 import os
@@ -42,32 +43,76 @@ def split_s3_path(url):
     return parsed.netloc, parsed.path.lstrip("/")
 
 
+def s3_request(func):
+    """Decorator for S3 calls: a missing object becomes ``EnvironmentError("file ... not found")``."""
+
+    @functools.wraps(func)
+    def wrapper(url, *args, **kwargs):
+        from botocore.exceptions import ClientError
+
+        try:
+            return func(url, *args, **kwargs)
+        except ClientError as exc:
+            if str(exc.response.get("Error", {}).get("Code")) == "404":
+                raise EnvironmentError("file {} not found".format(url)) from exc
+            raise
+
+    return wrapper
+
+
+@s3_request
+def s3_etag(url):
+    import boto3
+
+    bucket, key = split_s3_path(url)
+    return boto3.resource("s3").Object(bucket, key).e_tag
+
+
+@s3_request
+def s3_get(url, temp_file):
+    import boto3
+
+    bucket, key = split_s3_path(url)
+    boto3.resource("s3").Bucket(bucket).download_fileobj(key, temp_file)
+
+
+_TIMEOUTS = (10, 20, 40, 60, 60)
+
+
+def request_wrap_timeout(func, url):
+    """Calls ``func(timeout=...)`` with growing timeouts until one attempt does not time out."""
+    import requests
+
+    for attempt, timeout in enumerate(_TIMEOUTS):
+        try:
+            return func(timeout=timeout)
+        except requests.exceptions.Timeout:
+            logger.warning("Request for %s timed-out (attempt %d). Retrying with a timeout of %d secs", url, attempt,
+                           _TIMEOUTS[min(attempt + 1, len(_TIMEOUTS) - 1)])
+    raise RuntimeError(f"Unable to fetch file {url}")
+
+
+def http_get(url, temp_file):
+    import requests
+
+    req = request_wrap_timeout(functools.partial(requests.get, url, stream=True), url)
+    req.raise_for_status()
+    for chunk in req.iter_content(chunk_size=1 << 20):
+        if chunk:
+            temp_file.write(chunk)
+
+
 def _fetch(url, out_file):
-    scheme = urlparse(url).scheme
-    if scheme == "s3":
-        import boto3
-
-        bucket, key = split_s3_path(url)
-        boto3.resource("s3").Bucket(bucket).download_fileobj(key, out_file)
-    else:
-        import requests
-
-        with requests.get(url, stream=True, timeout=60) as r:
-            r.raise_for_status()
-            for chunk in r.iter_content(chunk_size=1 << 20):
-                out_file.write(chunk)
+    (s3_get if urlparse(url).scheme == "s3" else http_get)(url, out_file)
 
 
 def _etag(url):
     try:
         if urlparse(url).scheme == "s3":
-            import boto3
-
-            bucket, key = split_s3_path(url)
-            return boto3.resource("s3").Object(bucket, key).e_tag
+            return s3_etag(url)
         import requests
 
-        r = requests.head(url, allow_redirects=True, timeout=10)
+        r = request_wrap_timeout(functools.partial(requests.head, url, allow_redirects=True), url)
         return r.headers.get("ETag") if r.status_code == 200 else None
     except Exception:  # noqa: BLE001 - offline: fall back to whatever is cached
         return None

@@ -302,6 +302,63 @@ def run_batch(env, sbatch_cmd_str, sbatch_cmd):
     return job_id, stdout
 
 
+def dry_run_batch(env, train_log, train_stderr, sbatch_cmd_str, sbatch_cmd, dry_run):
+    """Says what a submission would do and, where ``sbatch`` exists, asks the scheduler to validate the request
+    without queueing it (``--test-only``)."""
+    dry_run("start remote training")
+    dry_run(f"- log stdout to: {train_log}")
+    dry_run(f"- log stderr to: {train_stderr}")
+    dry_run(f"- run command: {sbatch_cmd_str}")
+    if shutil.which(sbatch_cmd[0]) is None:
+        return None
+    with subprocess.Popen(list(sbatch_cmd) + ["--test-only"], stdout=subprocess.PIPE, env=env) as proc:
+        stdout = proc.stdout.read().decode("utf-8")
+        print(stdout)
+    return stdout
+
+
+def run_setup(args, config, dry_run):
+    """``(save_dir_key, save_dir)`` of one grid point (``config``: name -> hyperparam with its current value) and
+    the directory made, unless this is a dry run."""
+    keys = [hp.get_save_dir_key() for hp in config.values()]
+    save_dir_key = ".".join(k for k in keys if k is not None and len(k) > 0).replace(",", "_")
+    save_dir = os.path.join(args.checkpoints_dir, f"{args.prefix}.{save_dir_key}.ngpu{args.num_nodes * args.num_gpus}")
+    if not os.path.exists(save_dir) and not dry_run(f"create directory: {save_dir}"):
+        os.makedirs(save_dir)
+    return save_dir_key, save_dir
+
+
+def azure_support() -> str:
+    """The Azure fabric settings as shell lines for a batch script (``get_azure_env`` is the dict form that
+    ``set_env`` applies), plus loading the MPI module where the image has environment modules."""
+    lines = [f"export {k}={v}" for k, v in get_azure_env().items()]
+    lines += ["export OMPI_MCA_COLL_HCOLL_ENABLE=0",
+              'if [ -e "/etc/profile.d/modules.sh" ]; then', "    . /etc/profile.d/modules.sh",
+              "    module load mpi/hpcx", "fi"]
+    return "\n" + "\n".join(lines) + "\n"
+
+
+def copy_all_python_files(source, snapshot_main_dir, code_snapshot_hash, recurse_dirs="metaseq_b200"):
+    """Snapshot of a source tree under ``<snapshot_main_dir>/<code_snapshot_hash>``: the ``*.py`` files directly in
+    ``source`` and, for every directory named in the comma-separated ``recurse_dirs``, its ``*.py``, ``*.so``,
+    ``*.yaml``, ``*.cu``, ``*.cuh``, ``*.cpp`` and ``*.h`` files at any depth.  Returns the snapshot directory."""
+    destination = os.path.join(snapshot_main_dir, code_snapshot_hash)
+    os.makedirs(destination, exist_ok=True)
+    for name in os.listdir(source):
+        if name.endswith(".py") and os.path.isfile(os.path.join(source, name)):
+            shutil.copy2(os.path.join(source, name), os.path.join(destination, name))
+    keep = (".py", ".so", ".yaml", ".cu", ".cuh", ".cpp", ".h")
+
+    def ignore(path, names):
+        return [n for n in names if n == "__pycache__" or
+                (not os.path.isdir(os.path.join(path, n)) and not n.endswith(keep))]
+
+    for d in filter(None, (x.strip() for x in recurse_dirs.split(","))):
+        if os.path.isdir(os.path.join(source, d)):
+            shutil.copytree(os.path.join(source, d), os.path.join(destination, d), ignore=ignore, dirs_exist_ok=True)
+    return destination
+
+
 def snapshot_code(args, destination: str) -> str:
     """Copies the package sources so that queued jobs run the code as it was at submission."""
     root = Path(args.snapshot_root).resolve()

@@ -51,6 +51,21 @@ class hyperparam:
         return self.save_dir_key(self.current_value)
 
 
+def get_env_from_args(args):
+    """The cluster named by the reference's switches (``--azure``, ``--aws``, ``--fair``, ``--rsc``) or by
+    ``--cluster-env``."""
+    from .opt_job_constants import ComputeEnvs
+
+    for flag, env in (("azure", ComputeEnvs.AZURE), ("aws", ComputeEnvs.AWS), ("fair", ComputeEnvs.FAIR),
+                      ("rsc", ComputeEnvs.RSC)):
+        if getattr(args, flag, False):
+            return env
+    named = getattr(args, "cluster_env", None)
+    if named:
+        return ComputeEnvs(named)
+    raise NotImplementedError("Env not passed in! Please pass in one of: --azure, --aws, --fair, --rsc")
+
+
 def get_args(add_extra_options_func=None, input_args=None):
     parser = argparse.ArgumentParser("Script for launching hyperparameter sweeps")
     parser.add_argument("--grid", help="grid function to use, e.g. module:function")

@@ -558,3 +558,41 @@ def test_generation_config_is_inferred_from_a_checkpoint_directory(tmp_path):
     (tmp_path / "gpt2-unified.json").write_text("{}")
     cfg = create_generation_config_with_defaults(str(tmp_path))
     assert cfg.task.hf_tokenizer == str(tmp_path / "gpt2-unified.json")
+
+
+def test_launcher_helpers_name_the_run_snapshot_sources_and_pick_the_cluster(tmp_path):
+    import types
+
+    from metaseq_b200.launcher import slurm, sweep
+    from metaseq_b200.launcher.opt_job_constants import ComputeEnvs
+
+    said = []
+    args = types.SimpleNamespace(checkpoints_dir=str(tmp_path), prefix="exp", num_nodes=2, num_gpus=8)
+    config = {"--lr": sweep.hyperparam("--lr", [0.1], save_dir_key=lambda v: f"lr{v}"),
+              "--fp16": sweep.hyperparam("--fp16", binary_flag=True)}
+    for hp in config.values():
+        hp.current_value = hp.values[0]
+    key, save_dir = slurm.run_setup(args, config, lambda msg: said.append(msg) or True)
+    assert key == "lr0.1" and save_dir == str(tmp_path / "exp.lr0.1.ngpu16") and not os.path.exists(save_dir)
+    key, save_dir = slurm.run_setup(args, config, lambda msg: False)
+    assert os.path.isdir(save_dir)
+
+    src = tmp_path / "src"
+    (src / "pkg" / "sub").mkdir(parents=True)
+    (src / "setup.py").write_text("x")
+    (src / "notes.txt").write_text("x")
+    (src / "pkg" / "a.py").write_text("x")
+    (src / "pkg" / "sub" / "k.cu").write_text("x")
+    (src / "pkg" / "sub" / "big.bin").write_text("x")
+    dst = slurm.copy_all_python_files(str(src), str(tmp_path / "snap"), "abc123", recurse_dirs="pkg")
+    got = sorted(os.path.relpath(os.path.join(d, f), dst) for d, _, fs in os.walk(dst) for f in fs)
+    assert got == ["pkg/a.py", "pkg/sub/k.cu", "setup.py"]
+
+    assert "export NCCL_TOPO_FILE=/opt/microsoft/ndv4-topo.xml" in slurm.azure_support()
+    out = slurm.dry_run_batch({}, "log", "err", "no-such-sbatch x", ["no-such-sbatch", "x"], lambda m: said.append(m) or True)
+    assert out is None and "- run command: no-such-sbatch x" in said
+
+    ns = types.SimpleNamespace(azure=False, aws=True, fair=False, rsc=False)
+    assert sweep.get_env_from_args(ns) == ComputeEnvs.AWS
+    with pytest.raises(NotImplementedError):
+        sweep.get_env_from_args(types.SimpleNamespace(azure=False, aws=False, fair=False, rsc=False))

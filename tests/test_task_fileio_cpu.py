@@ -312,3 +312,45 @@ def test_path_manager_handlers_cwd_move_and_argument_checks(tmp_path):
         pm.register_handler(Quiet(), allow_override=False)
     pm.register_handler(Quiet())
     assert isinstance(pm._native, Quiet) and pm.exists(str(src))
+
+
+def test_http_fetch_retries_timeouts_with_growing_limits(monkeypatch, tmp_path):
+    import io
+
+    import requests
+
+    from metaseq_b200 import file_utils
+
+    seen = []
+
+    class Reply:
+        status_code = 200
+        headers = {"ETag": "abc"}
+
+        def raise_for_status(self):
+            pass
+
+        def iter_content(self, chunk_size):
+            yield b"pay"
+            yield b""
+            yield b"load"
+
+    def fake_get(url, stream=False, timeout=None):
+        seen.append(timeout)
+        if len(seen) < 3:
+            raise requests.exceptions.Timeout()
+        return Reply()
+
+    monkeypatch.setattr(requests, "get", fake_get)
+    buf = io.BytesIO()
+    file_utils.http_get("http://example.invalid/f", buf)
+    assert buf.getvalue() == b"payload" and seen == [10, 20, 40]
+    monkeypatch.setattr(requests, "get", lambda *a, **k: (_ for _ in ()).throw(requests.exceptions.Timeout()))
+    with pytest.raises(RuntimeError, match="Unable to fetch"):
+        file_utils.http_get("http://example.invalid/f", io.BytesIO())
+    # the cache goes through the same calls and remembers the ETag in the file name
+    monkeypatch.setattr(requests, "get", lambda url, stream=False, timeout=None: Reply())
+    monkeypatch.setattr(requests, "head", lambda url, allow_redirects=True, timeout=None: Reply())
+    path = file_utils.cached_path("http://example.invalid/f", cache_dir=str(tmp_path))
+    assert open(path, "rb").read() == b"payload"
+    assert os.path.basename(path) == file_utils.url_to_filename("http://example.invalid/f", "abc")
