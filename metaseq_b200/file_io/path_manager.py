@@ -190,6 +190,7 @@ class PathManagerBase:
         self._handlers: Dict[str, PathHandler] = {}
         self._native = NativePathHandler()
         self._nb = None
+        self._nb_buffered = None
         self._cwd: Optional[str] = None
         self._enable_logging = True
 
@@ -244,20 +245,40 @@ class PathManagerBase:
         return self._handler(path)._open(path, mode, buffering=buffering, encoding=encoding, errors=errors,
                                          newline=newline, **kw)
 
-    def opena(self, path, mode="a", callback_after_file_close=None, **kw):
-        """Non-blocking write handle: writes are queued to a background thread."""
-        if self._nb is None:
-            from .non_blocking_io import NonBlockingIOManager
+    def opena(self, path, mode="a", callback_after_file_close=None, buffering=-1, **kw):
+        """Non-blocking write handle: writes are queued to the path's background thread, in order, also across
+        handles on the same path.  ``buffering`` > 0 collects writes into chunks of that many bytes first."""
+        from .non_blocking_io import NonBlockingIOManager
 
+        key = os.path.normpath(path) if "://" not in str(path) else str(path)
+        io_obj = self._handler(path)._open(path, mode, **kw)
+        if buffering is not None and buffering > 0:
+            if self._nb_buffered is None:
+                self._nb_buffered = NonBlockingIOManager(buffered=True)
+            return self._nb_buffered.get_non_blocking_io(key, io_obj, callback_after_file_close, buffering)
+        if self._nb is None:
             self._nb = NonBlockingIOManager()
-        return self._nb.get_non_blocking_io(path, self._handler(path)._open(path, mode, **kw),
-                                            callback_after_file_close)
+        return self._nb.get_non_blocking_io(key, io_obj, callback_after_file_close)
 
     def async_join(self, *paths):
-        return self._nb._join(*paths) if self._nb is not None else True
+        """Waits for the queued writes of ``paths`` (all if none is named); re-raises a failed write's exception."""
+        ok = True
+        for mgr in (self._nb, self._nb_buffered):
+            if mgr is None:
+                continue
+            keys = [os.path.normpath(p) if "://" not in str(p) else str(p) for p in paths]
+            mine = [k for k in keys if k in mgr._paths]
+            if paths and not mine:
+                continue
+            ok = mgr._join(*mine) and ok
+        return ok
 
     def async_close(self):
-        return self._nb._close_thread_pool() if self._nb is not None else True
+        ok = True
+        for mgr in (self._nb, self._nb_buffered):
+            if mgr is not None:
+                ok = mgr._close_thread_pool() and ok
+        return ok
 
     def copy(self, src, dst, overwrite=False, **kw):
         hs, hd = self._handler(src), self._handler(dst)

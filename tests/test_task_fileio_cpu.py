@@ -354,3 +354,61 @@ def test_http_fetch_retries_timeouts_with_growing_limits(monkeypatch, tmp_path):
     path = file_utils.cached_path("http://example.invalid/f", cache_dir=str(tmp_path))
     assert open(path, "rb").read() == b"payload"
     assert os.path.basename(path) == file_utils.url_to_filename("http://example.invalid/f", "abc")
+
+
+def test_async_handles_on_one_path_keep_their_order_buffer_and_report_failures(tmp_path):
+    import io
+
+    from metaseq_b200.file_io import PathManager
+    from metaseq_b200.file_io.non_blocking_io import NonBlockingBufferedIO, NonBlockingIOManager
+
+    # two handles on one path: the second's writes land behind the first's, whatever the thread timing
+    path = str(tmp_path / "log.txt")
+    a = PathManager.opena(path, "a")
+    for i in range(200):
+        a.write(f"a{i}\n")
+    a.close()
+    b = PathManager.opena(str(tmp_path / "." / "log.txt"), "a")  # the same file under another spelling
+    b.write("b0\n")
+    b.close()
+    assert PathManager.async_join(path)
+    assert open(path).read().splitlines() == [f"a{i}" for i in range(200)] + ["b0"]
+
+    # buffered: many small writes become few large ones
+    class Counting(io.BytesIO):
+        writes = 0
+
+        def write(self, data):
+            Counting.writes += 1
+            return super().write(data)
+
+        def close(self):
+            Counting.final = self.getvalue()
+            super().close()
+
+    mgr = NonBlockingIOManager(buffered=True)
+    h = mgr.get_non_blocking_io("mem", Counting(), buffering=64)
+    assert isinstance(h, NonBlockingBufferedIO)
+    for i in range(100):
+        h.write(b"0123456789")
+    h.close()
+    assert mgr._join("mem") and Counting.final == b"0123456789" * 100 and Counting.writes <= 16
+    with pytest.raises(ValueError, match="not using a buffered writer"):
+        NonBlockingIOManager().get_non_blocking_io("mem", io.BytesIO(), buffering=64)
+    with pytest.raises(ValueError, match="no async IO associated"):
+        mgr._join("never-opened")
+
+    # a failed write surfaces at the join, and the callback still runs behind it
+    class Broken(io.BytesIO):
+        def write(self, data):
+            raise OSError("disk full")
+
+    ran = []
+    mgr = NonBlockingIOManager()
+    h = mgr.get_non_blocking_io("bad", Broken(), callback_after_file_close=lambda: ran.append(1))
+    h.write(b"x")
+    h.close()
+    with pytest.raises(OSError, match="disk full"):
+        mgr._close_thread_pool()
+    assert ran == [1]
+    PathManager.async_close()
