@@ -85,23 +85,33 @@ def _parse_scalar(text: str, like: Any) -> Any:
     return text
 
 
-def compose(overrides: Sequence[str] = (), cfg_name: str = "base_config"):
+def compose(overrides: Sequence[str] = (), cfg_name: str = "base_config", deletes: Sequence[str] = ()):
     """Build a root config: ``group=name`` picks a registered component's dataclass for that group (for example
     ``task=language_modeling``), ``a.b=value`` sets one field.  Group choices apply before field overrides,
-    whatever their order on the command line."""
+    whatever their order on the command line; groups named in ``deletes`` are set to ``None`` first.  A group
+    choice that no registry knows (a bare name, as encoders without options are) is stored as that name."""
     hydra_init(cfg_name)
     cs = ConfigStore.instance()
     cfg = cs.load(cfg_name)
+    overrides = list(overrides)
+    for d in deletes:
+        if hasattr(cfg, d):
+            setattr(cfg, d, None)
     picks = [o for o in overrides if "." not in o.split("=", 1)[0]]
     sets = [o for o in overrides if "." in o.split("=", 1)[0]]
     for o in picks:
         key, _, value = o.partition("=")
         if not hasattr(cfg, key):
             raise KeyError(f"unknown config group '{key}'")
-        node = cs.load(value, group=key)
-        if hasattr(node, "_name"):
-            node._name = value
-        setattr(cfg, key, node)
+        if value in cs.list(key):
+            node = cs.load(value, group=key)
+            if hasattr(node, "_name"):
+                node._name = value
+            setattr(cfg, key, node)
+        elif key in cs.groups():
+            raise KeyError(f"no config named '{value}' in group '{key}'; known: {cs.list(key)}")
+        else:
+            setattr(cfg, key, value)
     for o in sets:
         path, _, value = o.partition("=")
         *parents, leaf = path.split(".")

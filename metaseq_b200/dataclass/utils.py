@@ -11,11 +11,12 @@ from __future__ import annotations
 import argparse
 import ast
 import copy
+import enum
 import re
 import typing
 from argparse import ArgumentError, ArgumentParser, Namespace
 from dataclasses import MISSING, fields, is_dataclass
-from typing import Any, Dict, List, Optional
+from typing import Any, Dict, List, Optional, Tuple
 
 from .configs import COMPONENT_GROUPS, GROUPS, MetaseqDataclass
 
@@ -278,16 +279,86 @@ def overwrite_args_by_name(cfg, overrides: Dict[str, Any]):
     return cfg
 
 
-def override_module_args(args: Namespace):
-    """``key=value`` override strings for every non-default flag (parity helper for
-    launch tools that echo the effective configuration)."""
+def interpret_dc_type(field_type):
+    """The type an ``argparse`` argument should parse: ``Optional[T]`` -> ``T``, ``Any`` -> ``str``."""
+    if isinstance(field_type, str):
+        raise RuntimeError("field should be a type")
+    if field_type is Any:
+        return str
+    return _strip_optional(field_type)
+
+
+def _override_value(v) -> str:
+    if v is None:
+        return "null"
+    if isinstance(v, bool):
+        return "true" if v else "false"
+    if isinstance(v, (list, tuple)):
+        return "[" + ",".join(_override_value(x) for x in v) + "]"
+    if isinstance(v, enum.Enum):
+        return str(v.value)
+    return str(v)
+
+
+def _override_attr(prefix: str, dc_cls, args: Namespace) -> List[str]:
+    """``prefix.field=value`` for every field of ``dc_cls`` that ``args`` carries."""
     out = []
-    for gname, gcls in GROUPS.items():
-        inst = gcls()
-        for name in inst.field_names():
-            if hasattr(args, name) and getattr(args, name) != getattr(inst, name):
-                out.append(f"{gname}.{name}={getattr(args, name)!r}")
+    for f in fields(dc_cls):
+        if f.name != "_name" and hasattr(args, f.name):
+            out.append(f"{prefix}.{f.name}={_override_value(getattr(args, f.name))}")
     return out
+
+
+def migrate_registry(name, value, registry, args, overrides, deletes, use_name_as_val=False):
+    """One component group of a flat namespace as overrides: a registered choice with a dataclass becomes
+    ``group=choice``, ``group._name=choice`` and its fields; a bare name is kept if ``use_name_as_val``; anything
+    else puts the group on the delete list."""
+    if value in registry:
+        overrides.append(f"{name}={value}")
+        overrides.append(f"{name}._name={value}")
+        overrides.extend(_override_attr(name, registry[value], args))
+    elif use_name_as_val and value is not None:
+        overrides.append(f"{name}={value}")
+    else:
+        deletes.append(name)
+
+
+def override_module_args(args: Namespace) -> Tuple[List[str], List[str]]:
+    """A flat namespace as ``(overrides, deletes)``: ``key=value`` strings that ``dataclass.initialize.compose``
+    applies to the root config, and the component groups that the namespace does not select (reference:
+    metaseq/dataclass/utils.py:287-345)."""
+    overrides: List[str] = []
+    deletes: List[str] = []
+    for gname, gcls in GROUPS.items():
+        overrides.extend(_override_attr(gname, gcls, args))
+    if args is None:
+        return overrides, deletes
+    if hasattr(args, "task"):
+        from metaseq_b200.tasks import TASK_DATACLASS_REGISTRY
+
+        migrate_registry("task", args.task, TASK_DATACLASS_REGISTRY, args, overrides, deletes)
+    else:
+        deletes.append("task")
+    from metaseq_b200.registry import REGISTRIES
+
+    core = {"criterion", "optimizer", "lr_scheduler"}
+    for key, reg in REGISTRIES.items():
+        if hasattr(args, key):
+            migrate_registry(key, getattr(args, key), reg["dataclass_registry"], args, overrides, deletes,
+                             use_name_as_val=key not in core)
+        else:
+            deletes.append(key)
+    from metaseq_b200.models import ARCH_MODEL_NAME_REGISTRY, ARCH_MODEL_REGISTRY, MODEL_DATACLASS_REGISTRY
+
+    arch = getattr(args, "arch", None)
+    dc = MODEL_DATACLASS_REGISTRY.get(ARCH_MODEL_NAME_REGISTRY.get(arch)) if arch in ARCH_MODEL_REGISTRY else None
+    if dc is not None:
+        overrides.append(f"model={ARCH_MODEL_NAME_REGISTRY[arch]}")
+        overrides.append(f"model._name={arch}")
+        overrides.extend(_override_attr("model", dc, args))
+    else:
+        deletes.append("model")
+    return overrides, deletes
 
 
 def get(cfg_or_ns, key: str, default=None):

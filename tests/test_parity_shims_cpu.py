@@ -549,3 +549,28 @@ def test_config_store_lists_registered_components_and_composes_a_root_config():
         compose(["optimizer.lr=[0.1]"])
     with pytest.raises(KeyError, match="unknown field"):
         compose(["common.not_a_field=1"])
+
+
+def test_flat_namespace_round_trips_through_override_strings():
+    from typing import Any, Optional
+
+    from metaseq_b200 import options
+    from metaseq_b200.dataclass.initialize import compose
+    from metaseq_b200.dataclass.utils import convert_namespace_to_config, interpret_dc_type, override_module_args
+
+    argv = ["--task", "dummy_lm", "--dict-size", "124", "--tokens-per-sample", "16", "--batch-size", "2", "--arch",
+            "transformer_lm_megatron", "--decoder-layers", "2", "--decoder-embed-dim", "32", "--criterion",
+            "cross_entropy", "--optimizer", "adam", "--lr", "1e-2", "--lr-scheduler", "polynomial_decay",
+            "--total-num-update", "100", "--clip-norm", "0.5", "--fp16"]
+    args = options.parse_args_and_arch(options.get_training_parser(), input_args=argv)
+    overrides, deletes = override_module_args(args)
+    assert "task=dummy_lm" in overrides and "task._name=dummy_lm" in overrides
+    assert "model._name=transformer_lm_megatron" in overrides and "optimization.lr=[0.01]" in overrides
+    assert "bpe" in deletes and "tokenizer" in deletes
+    cfg, ref = compose(overrides, deletes=deletes), convert_namespace_to_config(args)
+    assert cfg.optimization.lr == ref.optimization.lr == [0.01] and cfg.optimization.clip_norm == 0.5
+    assert cfg.common.fp16 is True and cfg.task.tokens_per_sample == 16 and cfg.model.decoder_layers == 2
+    assert cfg.lr_scheduler.total_num_update == ref.lr_scheduler.total_num_update and cfg.bpe is None
+    assert interpret_dc_type(Optional[int]) is int and interpret_dc_type(Any) is str
+    with pytest.raises(RuntimeError):
+        interpret_dc_type("int")
