@@ -9,7 +9,7 @@ from torch.utils.data.dataloader import default_collate
 from .base_dataset import BaseDataset
 
 _DELEGATED_METHODS = ("num_tokens", "num_tokens_vec", "size", "ordered_indices", "attr", "prefetch",
-                      "filter_indices_by_size", "batch_by_size")
+                      "filter_indices_by_size", "batch_by_size", "get_batch_shapes")
 _DELEGATED_PROPERTIES = ("sizes", "can_reuse_epoch_itr_across_epochs")
 
 

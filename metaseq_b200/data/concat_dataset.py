@@ -67,6 +67,28 @@ class ConcatDataset(BaseDataset):
     def ordered_indices(self):
         return np.argsort(self.sizes)
 
+    def attr(self, attr: str, index: int):
+        """The attribute as the member dataset that holds ``index`` has it."""
+        ds, _ = self._locate(index)
+        return getattr(self.datasets[ds], attr, None)
+
+    def prefetch(self, indices):
+        """Hands every member the indices that fall into it, in its own numbering."""
+        start = 0
+        for end, real, ds in zip(self.cumulative_sizes, self.real_sizes, self.datasets):
+            if getattr(ds, "supports_prefetch", False):
+                ds.prefetch([(i - start) % real for i in indices if start <= i < end])
+            start = end
+
+    def ordered_indices_per_dataset(self):
+        """Every member's ordered index vectors, shifted into this dataset's numbering."""
+        out, start = [], 0
+        for end, ds in zip(self.cumulative_sizes, self.datasets):
+            for idx in ds.ordered_indices_per_dataset():
+                out.append(np.asarray(idx) + start)
+            start = end
+        return out
+
     def set_epoch(self, epoch):
         for d in self.datasets:
             if hasattr(d, "set_epoch"):

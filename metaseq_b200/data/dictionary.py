@@ -43,6 +43,9 @@ class Dictionary:
     def index(self, sym: str) -> int:
         return self.indices.get(sym, self.unk_index)
 
+    def get_count(self, idx: int) -> int:
+        return self.count[idx]
+
     def string(self, tensor, bpe_symbol=None, escape_unk=False, extra_symbols_to_ignore=None, unk_string=None) -> str:
         if torch.is_tensor(tensor) and tensor.dim() == 2:
             return "\n".join(self.string(t, bpe_symbol, escape_unk, extra_symbols_to_ignore) for t in tensor)
@@ -170,6 +173,41 @@ class Dictionary:
         if append_eos:
             ids[n] = self.eos_index
         return ids
+
+    @staticmethod
+    def _count_words_in_chunk(filename: str, tokenize, eos_word: str, start: int, end: int) -> Counter:
+        from metaseq_b200.file_chunker_utils import Chunker
+
+        counts: Counter = Counter()
+        with Chunker(filename, start, end) as lines:
+            for line in lines:
+                counts.update(tokenize(line))
+                counts[eos_word] += 1
+        return counts
+
+    @staticmethod
+    def add_file_to_dictionary(filename: str, dict: "Dictionary", tokenize, num_workers: int = 1) -> None:
+        """Counts the words of a text file (one end-of-sentence symbol per line) into ``dict``.  The file is cut
+        at line boundaries into ``num_workers`` byte ranges that are counted by a process pool; symbols are added
+        in sorted order per range, so the result does not depend on scheduling (reference:
+        metaseq/data/dictionary.py:320-380)."""
+        from metaseq_b200.file_chunker_utils import find_offsets
+        from metaseq_b200.file_io import PathManager
+
+        local = PathManager.get_local_path(filename)
+        offsets = find_offsets(local, max(1, num_workers))
+        ranges = list(zip(offsets, offsets[1:]))
+        if num_workers > 1:
+            from multiprocessing import Pool
+
+            with Pool(processes=num_workers) as pool:
+                parts = pool.starmap(Dictionary._count_words_in_chunk,
+                                     [(local, tokenize, dict.eos_word, a, b) for a, b in ranges])
+        else:
+            parts = [Dictionary._count_words_in_chunk(local, tokenize, dict.eos_word, a, b) for a, b in ranges]
+        for counts in parts:
+            for word, n in sorted(counts.items()):
+                dict.add_symbol(word, n)
 
     @classmethod
     def synthetic(cls, vocab_size: int) -> "Dictionary":

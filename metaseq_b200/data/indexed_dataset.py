@@ -147,16 +147,26 @@ class IndexedDataset(_SizedCorpus):
         super().__init__()
         self.path = path
         self.fix_lua_indexing = fix_lua_indexing
+        self._data = None
+        self.read_index(path)
+
+    def read_index(self, path):
         ix = _LegacyIndex(index_file_path(path))
         self.dtype, self.element_size, self._len = ix.dtype, ix.element_size, ix.n
         self.dim_offsets, self.data_offsets, self.sizes = ix.dim_offsets, ix.data_offsets, ix.sizes
-        self._data = None
+
+    def read_data(self, path):
+        """Maps the data file (done on first access, and again in every worker process)."""
+        self._data = np.memmap(data_file_path(path), dtype=self.dtype, mode="r")
+
+    def check_index(self, i):
+        if i < 0 or i >= self._len:
+            raise IndexError("index out of range")
 
     def _raw(self, i) -> np.ndarray:
-        if not 0 <= i < self._len:
-            raise IndexError("index out of range")
+        self.check_index(i)
         if self._data is None:
-            self._data = np.memmap(data_file_path(self.path), dtype=self.dtype, mode="r")
+            self.read_data(self.path)
         shape = tuple(self.sizes[self.dim_offsets[i]:self.dim_offsets[i + 1]])
         return np.asarray(self._data[self.data_offsets[i]:self.data_offsets[i + 1]]).reshape(shape)
 
@@ -339,16 +349,25 @@ class IndexedRawTextDataset(_SizedCorpus):
     def __init__(self, path, dictionary, append_eos=True, reverse_order=False):
         super().__init__()
         self.append_eos, self.reverse_order = append_eos, reverse_order
+        self.read_data(path, dictionary)
+
+    def read_data(self, path, dictionary):
         with open(path, "r", encoding="utf-8") as f:
             self.lines = [ln.rstrip("\n") for ln in f]
-        self.tokens_list = [dictionary.encode_line(ln, add_if_not_exist=False, append_eos=append_eos,
-                                                   reverse_order=reverse_order).long() for ln in self.lines]
+        self.tokens_list = [dictionary.encode_line(ln, add_if_not_exist=False, append_eos=self.append_eos,
+                                                   reverse_order=self.reverse_order).long() for ln in self.lines]
         self.sizes = np.array([len(t) for t in self.tokens_list])
 
+    def check_index(self, i):
+        if i < 0 or i >= len(self.tokens_list):
+            raise IndexError("index out of range")
+
     def __getitem__(self, i):
+        self.check_index(i)
         return self.tokens_list[i]
 
     def get_original_text(self, i):
+        self.check_index(i)
         return self.lines[i]
 
     def __len__(self):

@@ -99,6 +99,10 @@ class JsonlDataset(torch.utils.data.Dataset):
                 mm.close()
             f.close()
 
+    @staticmethod
+    def exists(path):
+        return os.path.exists(path)
+
     def __len__(self):
         return len(self.offsets)
 

@@ -31,15 +31,39 @@ class PlasmaArray:
             self._array = np.ndarray(shape, dtype=np.dtype(dtype), buffer=self._shm.buf)
         return self._array
 
+    @property
+    def plasma(self):
+        """The sharing backend (the shared-memory module), or ``None`` when this array is small enough to be
+        pickled by value.  Named after the reference's store."""
+        return None if self.disable else shared_memory
+
+    def start_server(self):
+        """Publishes the array: creates the segment and copies the data in (there is no server process; the
+        kernel keeps the pages).  Called on first pickling; calling it again does nothing."""
+        if self.plasma is None or self._meta is not None:
+            return
+        shm = shared_memory.SharedMemory(create=True, size=max(1, self._array.nbytes))
+        view = np.ndarray(self._array.shape, dtype=self._array.dtype, buffer=shm.buf)
+        view[...] = self._array
+        self._owner = shm
+        self._meta = (shm.name, self._array.shape, self._array.dtype.str)
+
+    @property
+    def client(self):
+        """This process's attachment to the segment (``None`` before the array is published)."""
+        if self._meta is None:
+            return None
+        owner = getattr(self, "_owner", None)
+        if owner is not None:
+            return owner
+        if self._shm is None:
+            self._shm = shared_memory.SharedMemory(name=self._meta[0])
+        return self._shm
+
     def __getstate__(self):
         if self.disable:
             return {"array": self._array, "meta": None}
-        if self._meta is None:
-            shm = shared_memory.SharedMemory(create=True, size=max(1, self._array.nbytes))
-            view = np.ndarray(self._array.shape, dtype=self._array.dtype, buffer=shm.buf)
-            view[...] = self._array
-            self._owner = shm
-            self._meta = (shm.name, self._array.shape, self._array.dtype.str)
+        self.start_server()
         return {"array": None, "meta": self._meta}
 
     def __setstate__(self, state):
@@ -86,6 +110,13 @@ class PlasmaView:
         if self._shm is None:
             self._shm = shared_memory.SharedMemory(name=self.name)
         return np.ndarray(self._shape, dtype=np.dtype(self._dtype), buffer=self._shm.buf)
+
+    @property
+    def client(self):
+        """This process's attachment to the segment."""
+        if self._shm is None:
+            self._shm = shared_memory.SharedMemory(name=self.name)
+        return self._shm
 
     @staticmethod
     def get_object_id(split_path: str, hash_data: Hashable) -> str:

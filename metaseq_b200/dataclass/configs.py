@@ -51,6 +51,10 @@ class MetaseqDataclass:
     def name():
         return None
 
+    def positional_args(self):
+        """Flags that the command line takes by position rather than by ``--name``."""
+        return ["data"]
+
     def field_names(self):
         return [f.name for f in fields(self) if not f.name.startswith("_")]
 

@@ -199,8 +199,15 @@ class GeneratorInterface:
 
     # -------------------------------------------------------------- tokenizer
     def encode_fn(self, x: str):
+        """Token ids of ``x``; line ends are normalised to ``\\n`` first (browsers send ``\\r\\n``)."""
+        from metaseq_b200.service.utils import normalize_newlines
+
         assert self.bpe is not None
-        return self.bpe.bpe.encode(x).ids
+        return self.bpe.bpe.encode(normalize_newlines(x)).ids
+
+    def decode_fn(self, x: List[int]) -> str:
+        assert self.bpe is not None
+        return self.bpe.bpe.decode(x)
 
     # ---------------------------------------------------------------- generate
     def generate(self, inputs: List[List[int]], min_tokens: List[int] = None, max_tokens: List[int] = None,

@@ -30,6 +30,11 @@ class BaseDecoder(nn.Module):
             return utils.log_softmax(logits, dim=-1)
         return utils.softmax(logits, dim=-1)
 
+    def reorder_incremental_state(self, incremental_state, new_order):
+        """Called when the batch order changes between decoding steps (beam search); nothing to do for a decoder
+        without per-step state."""
+        pass
+
     def max_positions(self):
         return 1e6
 

@@ -15,9 +15,45 @@ logger = logging.getLogger(__name__)
 
 
 class BaseModel(nn.Module):
-    def __init__(self):
+    """Decoder-only model: ``forward(src_tokens) -> (logits [B, T, V], extra)``.  ``BaseModel(decoder)`` is the
+    reference's constructor (metaseq/models/base_model.py:33-41); a subclass that builds its decoder later may
+    call it without one."""
+
+    def __init__(self, decoder=None):
         super().__init__()
         self._is_generation_fast = False
+        if decoder is not None:
+            self.decoder = decoder
+
+    @classmethod
+    def from_pretrained(cls, model_name_or_path, checkpoint_file="model.pt", data_name_or_path=".",
+                        skip_prepare_for_inference=False, **kwargs):
+        """The reference leaves this unimplemented as well (metaseq/models/base_model.py:137-146): released
+        checkpoints are loaded through ``hub_utils.GeneratorInterface`` or ``checkpoint_utils``."""
+        raise NotImplementedError
+
+    @classmethod
+    def hub_models(cls):
+        return {}
+
+    def forward(self, src_tokens, **kwargs):
+        return self.decoder(src_tokens, **kwargs)
+
+    def forward_decoder(self, prev_output_tokens, **kwargs):
+        return self.decoder(prev_output_tokens, **kwargs)
+
+    def extract_features(self, src_tokens, **kwargs):
+        return self.decoder.extract_features(src_tokens, **kwargs)
+
+    def output_layer(self, features, **kwargs):
+        return self.decoder.output_layer(features, **kwargs)
+
+    def max_decoder_positions(self):
+        return self.decoder.max_positions()
+
+    @property
+    def supported_targets(self):
+        return {"future"}
 
     @classmethod
     def add_args(cls, parser):
@@ -37,7 +73,8 @@ class BaseModel(nn.Module):
         return self.decoder.get_normalized_probs(logits, log_probs, sample)
 
     def max_positions(self):
-        return None
+        dec = getattr(self, "decoder", None)
+        return dec.max_positions() if dec is not None else None
 
     def load_state_dict(self, state_dict, strict=True, model_cfg=None):
         self.upgrade_state_dict(state_dict)
@@ -100,30 +137,7 @@ class BaseModel(nn.Module):
 
 
 class LanguageModel(BaseModel):
-    """Decoder-only model: ``forward(src_tokens) -> (logits [B, T, V], extra)``."""
+    """Kept as the name that this package's models derive from; everything lives in ``BaseModel``."""
 
     def __init__(self, decoder):
-        super().__init__()
-        self.decoder = decoder
-
-    def forward(self, src_tokens, **kwargs):
-        return self.decoder(src_tokens, **kwargs)
-
-    def forward_decoder(self, prev_output_tokens, **kwargs):
-        return self.decoder(prev_output_tokens, **kwargs)
-
-    def extract_features(self, src_tokens, **kwargs):
-        return self.decoder.extract_features(src_tokens, **kwargs)
-
-    def output_layer(self, features, **kwargs):
-        return self.decoder.output_layer(features, **kwargs)
-
-    def max_positions(self):
-        return self.decoder.max_positions()
-
-    def max_decoder_positions(self):
-        return self.decoder.max_positions()
-
-    @property
-    def supported_targets(self):
-        return {"future"}
+        super().__init__(decoder)

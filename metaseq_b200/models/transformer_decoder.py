@@ -155,6 +155,25 @@ class ModelParallelTransformerDecoder(IncrementalDecoder):
 
         return fsdp_wrap(layer, min_num_params=_get(args, "min_params_to_wrap", None))
 
+    def buffered_future_mask(self, tensor, input_tokens=None):
+        """The dense additive attention mask that the compact form stands for, for code that wants the matrix:
+        ``[T, T]`` causal; ``[B, T, T]`` when documents are separated (``input_tokens`` required);
+        ``[B * heads, T, T]`` with ALiBi.  ``tensor`` is ``[T, B, ...]`` and gives length, batch, dtype and
+        device (reference: metaseq/models/transformer_decoder.py:436-487).  The model itself never builds it."""
+        from metaseq_b200.modules.attention_bias import AttentionBias
+
+        T, B = tensor.size(0), tensor.size(1)
+        doc_start = None
+        if self.self_attn_doc_sep != UNSPECIFIED_DOC_SEP:
+            assert input_tokens is not None
+            _, doc_start = self._doc_sep_positions(input_tokens)
+        mask = AttentionBias(doc_start=doc_start, slopes=self.alibi_slopes).dense(T, T, 0, tensor.device)
+        if self.alibi_slopes is not None:
+            return mask.expand(B, -1, T, T).reshape(-1, T, T).to(tensor.dtype)
+        if doc_start is not None:
+            return mask[:, 0].to(tensor.dtype)
+        return mask[0, 0].to(tensor.dtype)
+
     # ------------------------------------------------------------- embedding
     def _doc_sep_positions(self, tokens):
         """Positions that restart at ``padding_idx + 1`` after every separator token."""

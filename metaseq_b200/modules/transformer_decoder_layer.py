@@ -62,35 +62,76 @@ class ModelParallelTransformerDecoderLayer(nn.Module):
         ffn_dim = args.decoder_ffn_embed_dim
         self.activation_name = _get(args, "activation_fn", "relu") or "relu"
 
-        self.self_attn = ModelParallelMultiheadAttention(
-            self.embed_dim, args.decoder_attention_heads, dropout=_get(args, "attention_dropout", 0.0),
-            bias=not disable_bias, use_cpu_initialization=cpu_init, full_megatron_init=full_init,
-            full_megatron_init_scalar=scalar, megatron_init_sigma=sigma, num_layers=self.num_layers, dtype=dtype,
-            device=device, sequence_parallel=self.sequence_parallel,
-            max_positions=_get(args, "max_target_positions", None) or _get(args, "tokens_per_sample", 2048))
+        self._build = dict(dtype=dtype, device=device, cpu_init=cpu_init)
+        self.self_attn = self.build_self_attention(self.embed_dim, args)
         self.self_attn_layer_norm = LayerNorm(self.embed_dim, elementwise_affine=affine)
-        if full_init:
-            init_fc1 = utils.init_method_normal(sigma * scalar)
-            init_fc2 = utils.scaled_init_method_normal(sigma * scalar, self.num_layers)
-        else:
-            import math
-
-            def init_fc1(w):
-                return nn.init.kaiming_uniform_(w, a=math.sqrt(5))
-
-            init_fc2 = init_fc1
+        truncate = bool(_get(args, "truncate_init", False))
+        fc1 = self.build_fc1(self.embed_dim, ffn_dim, not cpu_init, full_init, sigma * scalar, dtype,
+                             disable_bias=disable_bias, truncate_init=truncate)
         self.activation_fn = ActivationFn(self.activation_name, self._plain_fc1, self.embed_dim, ffn_dim,
-                                          bias=not disable_bias, init=init_fc1, cpu_init=cpu_init, dtype=dtype,
-                                          device=device, sp=self.sequence_parallel)
-        self.fc1 = self._plain_fc1(self.embed_dim, ffn_dim, bias=not disable_bias, init=init_fc1, cpu_init=cpu_init,
-                                   dtype=dtype, device=device, sp=self.sequence_parallel)
-        self.fc2 = RowParallelLinear(ffn_dim, self.embed_dim, bias=not disable_bias, input_is_parallel=True,
-                                     init_method=init_fc2, skip_bias_add=False, use_cpu_initialization=cpu_init,
-                                     dtype=dtype, device=device, sequence_parallel=self.sequence_parallel)
+                                          bias=not disable_bias, init=self.fc1_init_method, cpu_init=cpu_init,
+                                          dtype=dtype, device=device, sp=self.sequence_parallel)
+        self.fc1 = fc1  # registered after the activation's own parameters, which keeps the parameter order
+        self.fc2 = self.build_fc2(ffn_dim, self.embed_dim, not cpu_init, full_init, scalar, sigma, self.num_layers,
+                                  dtype, disable_bias=disable_bias, truncate_init=truncate)
         self.final_layer_norm = LayerNorm(self.embed_dim, elementwise_affine=affine)
         self.checkpoint_activations = bool(_get(args, "checkpoint_activations", False))
         self.use_fused_layer = not bool(_get(args, "no_fused_layer", False))
         self.tp_comm = None  # set by the trainer when fused tensor-parallel communication is on
+
+    # ------------------------------------------------------------- builders (override points)
+    def build_self_attention(self, embed_dim, args):
+        b = self._build
+        return ModelParallelMultiheadAttention(
+            embed_dim, args.decoder_attention_heads, dropout=_get(args, "attention_dropout", 0.0),
+            bias=not bool(_get(args, "disable_bias", False)), use_cpu_initialization=b["cpu_init"],
+            full_megatron_init=bool(_get(args, "full_megatron_init", False)),
+            full_megatron_init_scalar=_get(args, "full_megatron_init_scalar", 1.0),
+            megatron_init_sigma=_get(args, "megatron_init_sigma", 0.006), num_layers=args.decoder_layers,
+            dtype=b["dtype"], device=b["device"], sequence_parallel=self.sequence_parallel,
+            max_positions=_get(args, "max_target_positions", None) or _get(args, "tokens_per_sample", 2048))
+
+    @staticmethod
+    def _default_weight_init(w):
+        import math
+
+        return nn.init.kaiming_uniform_(w, a=math.sqrt(5))
+
+    def build_fc1(self, input_dim, output_dim, initialize_params_on_gpu, full_megatron_init, megatron_init_sigma,
+                  dtype, disable_bias=False, truncate_init=False):
+        """Column-parallel first feed-forward matrix.  ``megatron_init_sigma`` is the standard deviation actually
+        used (the caller has multiplied in ``--full-megatron-init-scalar``)."""
+        if full_megatron_init:
+            self.fc1_init_method = utils.init_method_normal(megatron_init_sigma)
+        else:
+            self.fc1_init_method = self._default_weight_init
+        return self._plain_fc1(input_dim, output_dim, bias=not disable_bias, init=self.fc1_init_method,
+                               cpu_init=not initialize_params_on_gpu, dtype=dtype, device=self._build["device"],
+                               sp=self.sequence_parallel)
+
+    def build_fc2(self, input_dim, output_dim, initialize_params_on_gpu, full_megatron_init, full_megatron_init_scalar,
+                  megatron_init_sigma, num_layers, dtype, disable_bias=False, truncate_init=False):
+        """Row-parallel second feed-forward matrix (its input is already split over the tensor-parallel ranks)."""
+        if full_megatron_init:
+            init = utils.scaled_init_method_normal(megatron_init_sigma * full_megatron_init_scalar, num_layers)
+        else:
+            init = self._default_weight_init
+        return RowParallelLinear(input_dim, output_dim, bias=not disable_bias, input_is_parallel=True,
+                                 init_method=init, skip_bias_add=False,
+                                 use_cpu_initialization=not initialize_params_on_gpu, dtype=dtype,
+                                 device=self._build["device"], sequence_parallel=self.sequence_parallel)
+
+    def forward_attention(self, query, key, value, residual, key_padding_mask=None, incremental_state=None,
+                          attn_mask=None, bt=None):
+        """Self-attention, its bias, dropout and the residual of the modular path (self-attention only: ``key`` and
+        ``value`` are the query)."""
+        if bt is None:
+            bt = (query.shape[0], query.shape[1])
+        h, attn_bias = self.self_attn(query, bt, incremental_state=incremental_state,
+                                      key_padding_mask=key_padding_mask, attn_mask=attn_mask)
+        if attn_bias is not None:
+            h = h + attn_bias
+        return residual + self.dropout_module(h).view_as(residual)
 
     @staticmethod
     def _plain_fc1(embed_dim, ffn_dim, bias, init, cpu_init, dtype, device, sp):
@@ -158,14 +199,9 @@ class ModelParallelTransformerDecoderLayer(nn.Module):
         return self._modular_forward(x, bt, incremental_state, self_attn_padding_mask, self_attn_mask)
 
     def _modular_forward(self, x, bt, incremental_state, key_padding_mask, attn_mask):
-        residual = x
         h = self.self_attn_layer_norm(x)
-        h, attn_bias = self.self_attn(h, bt, incremental_state=incremental_state, key_padding_mask=key_padding_mask,
-                                      attn_mask=attn_mask)
-        if attn_bias is not None:
-            h = h + attn_bias
-        h = self.dropout_module(h)
-        x = residual + h.view_as(residual)
+        x = self.forward_attention(h, h, h, x, key_padding_mask=key_padding_mask,
+                                   incremental_state=incremental_state, attn_mask=attn_mask, bt=bt)
         residual = x
         h = self.final_layer_norm(x)
         fc1_out, _ = self.fc1(h)

@@ -473,6 +473,11 @@ class FullyShardedDataParallel(nn.Module):
         for u in self._units:
             u._gather_full(asynchronous=True)
 
+    @property
+    def unwrapped_module(self) -> nn.Module:
+        """The module that was wrapped (this engine keeps it as is; parameters are views of the flat buffers)."""
+        return self.module
+
     def forward(self, *args, **kwargs):
         self._lazy_init()
         if self._is_root and self.world_size > 1 and not self._step_gathered and not self.reshard_after_forward:

@@ -574,3 +574,30 @@ def test_flat_namespace_round_trips_through_override_strings():
     assert interpret_dc_type(Optional[int]) is int and interpret_dc_type(Any) is str
     with pytest.raises(RuntimeError):
         interpret_dc_type("int")
+
+
+def test_dense_future_mask_matches_its_compact_form():
+    import argparse
+
+    from metaseq_b200.data.dictionary import Dictionary
+    from metaseq_b200.models.transformer_decoder import ModelParallelTransformerDecoder
+    from metaseq_b200.modules.embedding import Embedding
+
+    def build(**kw):
+        args = argparse.Namespace(decoder_embed_dim=16, decoder_attention_heads=2, decoder_ffn_embed_dim=32,
+                                  decoder_layers=1, dropout=0.0, attention_dropout=0.0, activation_fn="relu",
+                                  tokens_per_sample=8, max_target_positions=8, decoder_learned_pos=True,
+                                  share_decoder_input_output_embed=True, **kw)
+        d = Dictionary.synthetic(24)
+        return ModelParallelTransformerDecoder(args, d, Embedding(len(d), 16, d.pad()))
+
+    x = torch.zeros(5, 2, 16)  # [T, B, C]
+    causal = build().buffered_future_mask(x)
+    assert causal.shape == (5, 5) and torch.equal(causal == 0, torch.ones(5, 5).tril().bool())
+    toks = torch.tensor([[5, 6, 2, 7, 8], [5, 6, 7, 8, 9]])
+    docs = build(self_attn_doc_sep=2).buffered_future_mask(x, toks)
+    assert docs.shape == (2, 5, 5)
+    assert torch.isinf(docs[0, 3, :3]).all() and (docs[0, 3, 3] == 0) and (docs[0, 2, :3] == 0).all()
+    assert torch.equal(docs[1], causal)
+    ali = build(alibi=True).buffered_future_mask(x)
+    assert ali.shape == (4, 5, 5) and torch.isinf(ali[0, 0, 1]) and ali[0, 4, 3] > ali[0, 4, 2] > ali[0, 4, 1]
