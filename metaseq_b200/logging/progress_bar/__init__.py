@@ -4,6 +4,7 @@ optionally mirrored to TensorBoard / Weights & Biases / Aim when those packages 
 from __future__ import annotations
 
 import json
+from contextlib import contextmanager
 import logging
 import sys
 from collections import OrderedDict
@@ -92,6 +93,19 @@ class BaseProgressBar:
         return out
 
 
+@contextmanager
+def rename_logger(logger_, new_name):
+    """Log records made inside carry ``new_name`` as their logger name (``... | train_inner | {...}``), which is
+    what log scrapers key on."""
+    old_name = logger_.name
+    if new_name is not None:
+        logger_.name = new_name
+    try:
+        yield logger_
+    finally:
+        logger_.name = old_name
+
+
 class JsonProgressBar(BaseProgressBar):
     """One JSON object per ``log_interval`` steps on the python logger."""
 
@@ -112,14 +126,16 @@ class JsonProgressBar(BaseProgressBar):
         if step > 0 and self.log_interval is not None and step % self.log_interval == 0:
             update = self.epoch - 1 + (self.i + 1) / float(self.size) if (self.epoch is not None and self.size) else None
             stats = self._format_stats(stats, epoch=self.epoch, update=update)
-            logger.info(json.dumps(stats))
+            with rename_logger(logger, tag):
+                logger.info(json.dumps(stats))
 
     def print(self, stats, tag=None, step=None):
         self.stats = stats
         if tag is not None:
             self.stats = OrderedDict([(tag + "_" + k, v) for k, v in self.stats.items()])
         stats = self._format_stats(self.stats, epoch=self.epoch)
-        logger.info(json.dumps(stats))
+        with rename_logger(logger, tag):
+            logger.info(json.dumps(stats))
 
     def _format_stats(self, stats, epoch=None, update=None):
         out = OrderedDict()

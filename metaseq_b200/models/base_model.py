@@ -14,6 +14,12 @@ from metaseq_b200.dataclass.utils import gen_parser_from_dataclass
 logger = logging.getLogger(__name__)
 
 
+def check_type(module, expected_type):
+    """Asserts the type of a module, looking through a sharding wrapper."""
+    inner = getattr(module, "unwrapped_module", module)
+    assert isinstance(inner, expected_type), f"{type(inner)} != {expected_type}"
+
+
 class BaseModel(nn.Module):
     """Decoder-only model: ``forward(src_tokens) -> (logits [B, T, V], extra)``.  ``BaseModel(decoder)`` is the
     reference's constructor (metaseq/models/base_model.py:33-41); a subclass that builds its decoder later may
@@ -23,6 +29,9 @@ class BaseModel(nn.Module):
         super().__init__()
         self._is_generation_fast = False
         if decoder is not None:
+            from .base_decoder import BaseDecoder
+
+            check_type(decoder, BaseDecoder)
             self.decoder = decoder
 
     @classmethod

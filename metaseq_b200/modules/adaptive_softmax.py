@@ -77,6 +77,12 @@ class AdaptiveSoftmax(nn.Module):
             self.tail.append(nn.Sequential(proj, nn.Dropout(dropout), out))
         self.lsm = nn.LogSoftmax(dim=1)
         self.apply(self._init)
+        # state dicts carry the layout version (the reference's checkpoints have this key; older layouts are refused)
+        self.register_buffer("version", torch.LongTensor([1]))
+
+    def upgrade_state_dict_named(self, state_dict, name):
+        if name + ".version" not in state_dict:
+            raise Exception("This version of the model is no longer supported")
 
     @staticmethod
     def _init(m):

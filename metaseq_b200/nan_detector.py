@@ -43,12 +43,24 @@ class NanDetector:
         self._names: Dict[int, str] = {}
         self._handles = []
         self.reset()
+        self._fhook, self._bhook = self._make_hook(False), self._make_hook(True)
         for qualified, module in model.named_modules():
             self._names[id(module)] = qualified or module.__class__.__name__
-            if forward:
-                self._handles.append(module.register_forward_hook(self._make_hook(False)))
-            if backward:
-                self._handles.append(module.register_full_backward_hook(self._make_hook(True)))
+            self.add_hooks(module)
+
+    def add_hooks(self, module):
+        """Watches one more module (every submodule of the model is added at construction)."""
+        self._names.setdefault(id(module), module.__class__.__name__)
+        if self.forward:
+            self._handles.append(module.register_forward_hook(self.fhook_fn))
+        if self.backward:
+            self._handles.append(module.register_full_backward_hook(self.bhook_fn))
+
+    def fhook_fn(self, module, inp, output):
+        self._fhook(module, inp, output)
+
+    def bhook_fn(self, module, inp, output):
+        self._bhook(module, inp, output)
 
     # has_printed_f / has_printed_b: one report per direction
     def reset(self):

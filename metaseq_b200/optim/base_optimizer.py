@@ -109,6 +109,11 @@ class BaseOptimizer:
     def supports_flat_params(self):
         return getattr(self.optimizer, "supports_flat_params", False)
 
+    @property
+    def supports_groups(self):
+        """Whether parameter groups with their own hyper-parameters are honoured."""
+        return getattr(self.optimizer, "supports_groups", False)
+
     def average_params(self):
         pass
 

@@ -256,6 +256,10 @@ class FP16Optimizer(_ScaledMixin, BaseOptimizer):
     def optimizer_config(self):
         return self.fp32_optimizer.optimizer_config
 
+    @property
+    def lr_scheduler(self):
+        return getattr(self.fp32_optimizer, "lr_scheduler", None)
+
     def get_lr(self):
         return self.fp32_optimizer.get_lr()
 

@@ -299,6 +299,21 @@ class EnsembleModel(nn.Module):
     def forward(self):  # scoring goes through forward_decoder
         raise RuntimeError("call forward_decoder")
 
+    def set_decoder_beam_size(self, beam_size):
+        """Tells models that specialise on the beam width (``set_beam_size``) what it is."""
+        if beam_size > 1:
+            for model in self.models:
+                if hasattr(model, "set_beam_size"):
+                    model.set_beam_size(beam_size)
+
+    def forward_encoder(self, net_input):
+        """Decoder-only models have no encoder pass: always ``None``."""
+        return None
+
+    def reorder_encoder_out(self, encoder_outs, new_order):
+        """Nothing to reorder without an encoder: an empty list."""
+        return []
+
     def has_encoder(self) -> bool:
         return hasattr(self.single_model, "encoder")
 

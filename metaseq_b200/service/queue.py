@@ -3,7 +3,9 @@ batched together: ``get_largest_queue`` picks the fullest shard (reference:
 metaseq/service/queue.py:11-108)."""
 from __future__ import annotations
 
+import hashlib
 import queue
+import random
 import threading
 from collections import defaultdict
 
@@ -44,6 +46,19 @@ class PriorityQueueRingShard:
     @staticmethod
     def key_from_dict(d: dict) -> str:
         return ":".join(f"{k}={d[k]}" for k in sorted(d))
+
+    @staticmethod
+    def key_from_dictionary(key_dict: dict) -> str:
+        """The reference's spelling of a shard key: ``k1:v1:k2:v2`` over the sorted keys."""
+        return ":".join(f"{k}:{key_dict[k]}" for k in sorted(key_dict))
+
+    @staticmethod
+    def get_shard_index_for_key(key: str, num_shards: int = 1, deskew_factor: int = 1) -> int:
+        """SHA-1 of the key modulo the number of shards: the same in every process, unlike ``hash``.  A
+        ``deskew_factor`` > 1 spreads a hot key over shards by a random prefix (then it is not deterministic)."""
+        if deskew_factor > 1:
+            key = f"{random.randint(0, deskew_factor * num_shards)}:{key}"
+        return int(hashlib.sha1(key.encode("utf-8")).hexdigest(), 16) % num_shards
 
     def __init__(self):
         self.queues = defaultdict(queue.PriorityQueue)
@@ -88,12 +103,14 @@ class PriorityQueueRingShard:
 class PriorityQueueRing:
     """Several shards; producers hash to a shard, the consumer drains the largest shard."""
 
-    def __init__(self, num_shards: int = 1):
+    def __init__(self, num_shards: int = 1, deskew_factor: int = 1):
         self.shards = [PriorityQueueRingShard() for _ in range(num_shards)]
+        self.deskew_factor = deskew_factor
 
     def put(self, item: PriorityQueueRingShardKeyable):
         key = item.queue_key()
-        self.shards[hash(key) % len(self.shards)].put(key, item)
+        index = PriorityQueueRingShard.get_shard_index_for_key(key, len(self.shards), self.deskew_factor)
+        self.shards[index].put(key, item)
 
     def largest_shard(self):
         return max(self.shards, key=lambda s: s.size)

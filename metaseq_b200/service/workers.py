@@ -30,3 +30,17 @@ class WorkItem(PriorityQueueRingShardKeyable):
         d = {k: v for k, v in self.data.items() if k not in ("input", "seed", "min_tokens", "max_tokens")}
         d = {k: (tuple(v) if isinstance(v, list) else v) for k, v in d.items()}
         return PriorityQueueRingShard.key_from_dict(d)
+
+    @staticmethod
+    def generate_worker(encoded_prompt, batch_queue, **generation_args):
+        """Queues one prompt and blocks until its result comes back.  The cost grows with the prompt length
+        linearly (feed-forward work) plus quadratically (attention), so long prompts sort behind short ones
+        (reference: metaseq/service/workers.py:52-62)."""
+        import math
+
+        answer = queue.Queue()
+        n = len(encoded_prompt)
+        cost = n + int(math.ceil((n / 10) ** 2))
+        batch_queue.put(WorkItem(cost, 0, answer, {"input": encoded_prompt, **generation_args}))
+        _, result = answer.get()
+        return result

@@ -64,6 +64,20 @@ class BaseTask:
         return Dictionary.load(filename)
 
     @classmethod
+    def build_dictionary(cls, filenames, workers=1, threshold=-1, nwords=-1, padding_factor=8):
+        """A dictionary from whitespace-tokenised text files: words counted by ``workers`` processes, then cut to
+        words seen at least ``threshold`` times / the ``nwords`` most frequent, padded to a multiple of
+        ``padding_factor``."""
+        from metaseq_b200.data.dictionary import Dictionary
+        from metaseq_b200.utils import tokenize_line
+
+        d = Dictionary()
+        for filename in filenames:
+            Dictionary.add_file_to_dictionary(filename, d, tokenize_line, workers)
+        d.finalize(threshold=threshold, nwords=nwords, padding_factor=padding_factor)
+        return d
+
+    @classmethod
     def setup_task(cls, cfg, **kwargs):
         return cls(cfg, **kwargs)
 
@@ -169,6 +183,15 @@ class BaseTask:
     def inference_step(self, generator, models, sample, prefix_tokens=None, constraints=None):
         with torch.no_grad():
             return generator.generate(models, sample, prefix_tokens=prefix_tokens)
+
+    def build_dataset_for_inference(self, src_tokens, src_lengths, **kwargs):
+        raise NotImplementedError
+
+    def get_interactive_tokens_and_lengths(self, lines, encode_fn):
+        """Token tensors (and their lengths) of text lines: ``encode_fn`` (the byte-pair encoder) first, then the
+        dictionary lookup without adding new symbols."""
+        tokens = [self.source_dictionary.encode_line(encode_fn(line), add_if_not_exist=False).long() for line in lines]
+        return tokens, [t.numel() for t in tokens]
 
     def begin_epoch(self, epoch, model):
         pass

@@ -412,3 +412,24 @@ def test_async_handles_on_one_path_keep_their_order_buffer_and_report_failures(t
         mgr._close_thread_pool()
     assert ran == [1]
     PathManager.async_close()
+
+
+@pytest.mark.parametrize("workers", [1, 3])
+def test_dictionary_is_built_from_text_files_by_worker_processes(tmp_path, workers):
+    from metaseq_b200.tasks.base_task import BaseTask
+
+    lines = ["the cat sat", "the dog sat down", "a cat"] * 7
+    f = tmp_path / "corpus.txt"
+    f.write_text("\n".join(lines) + "\n")
+    d = BaseTask.build_dictionary([str(f)], workers=workers, padding_factor=1)
+    assert d.get_count(d.index("the")) == 14 and d.get_count(d.index("cat")) == 14 and d.get_count(d.index("down")) == 7
+    assert d.get_count(d.eos()) == len(lines) + 1  # one per line, on top of the symbol's initial count of one
+    assert d[d.nspecial] in ("the", "cat", "sat")  # most frequent first
+    cut = BaseTask.build_dictionary([str(f)], workers=workers, threshold=10, padding_factor=1)
+    assert "down" not in cut and "the" in cut
+
+    class T(BaseTask):
+        source_dictionary = d
+
+    toks, lens = T.__new__(T).get_interactive_tokens_and_lengths(["the cat", "a dog sat"], lambda s: s)
+    assert lens == [3, 4] and toks[0].tolist() == [d.index("the"), d.index("cat"), d.eos()]
