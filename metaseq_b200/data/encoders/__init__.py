@@ -18,16 +18,24 @@ class HuggingFaceByteLevelBPEConfig(MetaseqDataclass):
     bpe_merges: Optional[str] = opt(None, "path to merges.txt")
     bpe_vocab: Optional[str] = opt(None, "path to vocab.json")
     bpe_add_prefix_space: bool = opt(False, "add prefix space before encoding")
+    hf_tokenizer: Optional[str] = opt(None, "path to a unified tokenizer file; takes precedence over vocab + merges")
 
 
 @register_bpe("hf_byte_bpe", dataclass=HuggingFaceByteLevelBPEConfig)
 class HuggingFaceByteLevelBPE:
     def __init__(self, cfg):
         try:
-            from tokenizers import ByteLevelBPETokenizer
+            from tokenizers import ByteLevelBPETokenizer, Tokenizer
         except ImportError:
             raise ImportError("Please install huggingface/tokenizers with: pip install tokenizers")
-        self.bpe = ByteLevelBPETokenizer(cfg.bpe_vocab, cfg.bpe_merges, add_prefix_space=cfg.bpe_add_prefix_space)
+        from metaseq_b200 import file_utils
+
+        if getattr(cfg, "hf_tokenizer", None):
+            self.bpe = Tokenizer.from_file(cfg.hf_tokenizer)
+        else:
+            # either may be a URL: fetched into the local cache once
+            self.bpe = ByteLevelBPETokenizer(file_utils.cached_path(cfg.bpe_vocab), file_utils.cached_path(cfg.bpe_merges),
+                                             add_prefix_space=cfg.bpe_add_prefix_space)
 
     def encode(self, x: str) -> str:
         return " ".join(map(str, self.bpe.encode(x).ids))

@@ -183,7 +183,12 @@ class GeneratorInterface:
             b = getattr(self.cfg, "bpe", None)
             vocab = getattr(b, "bpe_vocab", None) if b is not None else None
             merges = getattr(b, "bpe_merges", None) if b is not None else None
-            if vocab and merges and os.path.exists(vocab) and os.path.exists(merges):
+            unified = getattr(b, "hf_tokenizer", None) if b is not None else None
+            if unified and os.path.exists(unified):
+                from tokenizers import Tokenizer
+
+                tok = Tokenizer.from_file(unified)
+            elif vocab and merges and os.path.exists(vocab) and os.path.exists(merges):
                 from tokenizers import ByteLevelBPETokenizer
 
                 tok = ByteLevelBPETokenizer.from_file(vocab, merges)
