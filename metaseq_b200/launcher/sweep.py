@@ -118,7 +118,7 @@ def get_args(add_extra_options_func=None, input_args=None):
     parser.add_argument("--cpus-per-task", type=int, default=12)
     parser.add_argument("--cpu-bind", default="none")
     parser.add_argument("--no-save-dir", action="store_true")
-    parser.add_argument("--tombstonable", type=bool, default=False, help="make the job killable by writing a tombstone file")
+    parser.add_argument("-ts", "--tombstonable", type=bool, default=False, help="make the job killable by writing a tombstone file")
     parser.add_argument("--use-jobarray", action="store_true")
     parser.add_argument("--jobarray-name", type=str, default=None)
     if add_extra_options_func is not None:
