@@ -17,18 +17,12 @@ logger = logging.getLogger(__name__)
 
 PathManager = PathManagerBase()
 
-try:
-    from .s3 import S3PathHandler
+from .s3 import S3PathHandler  # noqa: E402  (boto3 is imported on first use of an s3:// path)
 
-    PathManager.register_handler(S3PathHandler())
-except Exception:  # boto3 missing
-    pass
-try:
-    from .azure_blob import AzureBlobPathHandler
+PathManager.register_handler(S3PathHandler())
+from .azure_blob import AzureBlobPathHandler  # noqa: E402  (the SDK is imported on first use of an az:// path)
 
-    PathManager.register_handler(AzureBlobPathHandler())
-except Exception:  # azure sdk missing
-    pass
+PathManager.register_handler(AzureBlobPathHandler())
 
 
 def recursively_cast_dictconfigs(cfg):

@@ -433,3 +433,265 @@ def test_dictionary_is_built_from_text_files_by_worker_processes(tmp_path, worke
 
     toks, lens = T.__new__(T).get_interactive_tokens_and_lengths(["the cat", "a dog sat"], lambda s: s)
     assert lens == [3, 4] and toks[0].tolist() == [d.index("the"), d.index("cat"), d.eos()]
+
+
+# ------------------------------------------------------------------ blob storage against an in-memory service
+class ResourceNotFoundError(Exception):
+    pass
+
+
+class _FakeBlobStore:
+    """The slice of the blob service client API that the handler uses, over a dict."""
+
+    def __init__(self):
+        import datetime
+
+        self.blobs = {}  # (container, name) -> (bytes, last_modified)
+        self.staged = {}
+        self.now = lambda: datetime.datetime.now(datetime.timezone.utc)
+        self.downloads = 0
+
+    def get_blob_client(self, container, blob):
+        return _FakeBlobClient(self, container, blob)
+
+    def get_container_client(self, container):
+        store = self
+
+        class Container:
+            def list_blobs(self, name_starts_with=""):
+                import types
+
+                return [types.SimpleNamespace(name=n) for (c, n) in sorted(store.blobs)
+                        if c == container and n.startswith(name_starts_with)]
+
+        return Container()
+
+
+class _FakeBlobClient:
+    def __init__(self, store, container, blob):
+        self.store, self.container, self.blob_name = store, container, blob
+
+    def _get(self):
+        try:
+            return self.store.blobs[(self.container, self.blob_name)]
+        except KeyError:
+            raise ResourceNotFoundError(self.blob_name) from None
+
+    def get_blob_properties(self):
+        import types
+
+        data, when = self._get()
+        return {"size": len(data), "last_modified": when, "copy": types.SimpleNamespace(status="success")} | {}
+
+    def download_blob(self):
+        data, _ = self._get()
+        self.store.downloads += 1
+
+        class Stream:
+            def chunks(self, size=5):
+                return iter([data[i:i + size] for i in range(0, len(data), size)])
+
+            def readinto(self, out):
+                out.write(data)
+
+        return Stream()
+
+    def stage_block(self, block_id, stream, length):
+        self.store.staged.setdefault((self.container, self.blob_name), {})[block_id] = stream.read(length)
+
+    def commit_block_list(self, blocks):
+        staged = self.store.staged.pop((self.container, self.blob_name))
+        self.store.blobs[(self.container, self.blob_name)] = (b"".join(staged[b.id] for b in blocks), self.store.now())
+
+    def upload_blob(self, src, length=None, overwrite=False):
+        self.store.blobs[(self.container, self.blob_name)] = (src.read(), self.store.now())
+
+    def delete_blob(self):
+        self._get()
+        del self.store.blobs[(self.container, self.blob_name)]
+
+    def start_copy_from_url(self, url):
+        assert url.endswith("?sas-token") and ".blob.core.windows.net/" in url
+        container, _, name = url.split(".blob.core.windows.net/")[1].split("?")[0].partition("/")
+        self.store.blobs[(self.container, self.blob_name)] = (self.store.blobs[(container, name)][0], self.store.now())
+
+
+def test_blob_storage_handler_streams_blocks_lists_copies_and_caches(tmp_path, monkeypatch):
+    import types
+
+    from metaseq_b200.file_io import azure_blob
+    from metaseq_b200.file_io.path_manager import PathManagerBase
+
+    store = _FakeBlobStore()
+    seen = {}
+
+    def factory(url, token):
+        seen["url"], seen["token"] = url, token
+        return store
+
+    monkeypatch.setenv(azure_blob.ENV_SAS_TOKEN, "sas-token")
+    handler = azure_blob.AzureBlobPathHandler(cache_dir=str(tmp_path / "cache"), service_factory=factory,
+                                              block_factory=azure_blob.blob_block)
+    # get_blob_properties returns a mapping with attribute access on "copy" in the SDK; adapt the fake's dict
+    real_props = _FakeBlobClient.get_blob_properties
+    monkeypatch.setattr(_FakeBlobClient, "get_blob_properties",
+                        lambda self: type("P", (dict,), {"copy": types.SimpleNamespace(status="success")})(real_props(self)))
+    pm = PathManagerBase()
+    pm.register_handler(handler)
+    root = "az://acct/cont/run1"
+    assert handler._parse_uri(root + "/a/b.pt") == ("acct", "cont", "run1/a/b.pt")
+    with pytest.raises(ValueError):
+        handler._parse_uri("s3://x/y")
+    assert not pm.exists(root + "/ckpt.pt")
+
+    payload = bytes(range(256)) * 5
+    with pm.open(root + "/ckpt.pt", "wb", buffering=300) as f:  # 300-byte blocks
+        for i in range(0, len(payload), 100):
+            f.write(payload[i:i + 100])
+    assert seen == {"url": "https://acct.blob.core.windows.net", "token": "sas-token"}
+    assert store.blobs[("cont", "run1/ckpt.pt")][0] == payload and not store.staged
+    assert pm.isfile(root + "/ckpt.pt") and pm.isdir(root) and not pm.isdir(root + "/ckpt.pt") and pm.exists(root)
+    with pm.open(root + "/ckpt.pt", "rb") as f:
+        assert f.read(7) == payload[:7] and f.read() == payload[7:]
+    with pm.open(root + "/notes.txt", "w") as f:
+        f.write("héllo\nworld\n")
+    with pm.open(root + "/notes.txt", "r") as f:
+        assert f.read().splitlines() == ["héllo", "world"]
+    assert pm.ls(root) == ["run1/ckpt.pt", "run1/notes.txt"]
+
+    # uploads, server-side copies, removal
+    local = tmp_path / "local.bin"
+    local.write_bytes(b"abc")
+    assert pm.copy_from_local(str(local), root + "/up.bin") and not pm.copy_from_local(str(local), root + "/up.bin")
+    assert pm.copy_from_local(str(local), root + "/up.bin", overwrite=True)
+    assert pm.copy(root + "/up.bin", root + "/up2.bin") and store.blobs[("cont", "run1/up2.bin")][0] == b"abc"
+    pm.rm(root + "/up2.bin")
+    assert not pm.exists(root + "/up2.bin")
+    with pytest.raises(OSError):
+        pm.rm(root + "/up2.bin")
+
+    # the local cache is reused until the blob changes
+    before = store.downloads
+    p1 = pm.get_local_path(root + "/up.bin")
+    assert open(p1, "rb").read() == b"abc" and p1.startswith(str(tmp_path / "cache")) and store.downloads == before + 1
+    assert pm.get_local_path(root + "/up.bin") == p1 and store.downloads == before + 1
+    import datetime
+
+    store.blobs[("cont", "run1/up.bin")] = (b"newer", store.now() + datetime.timedelta(seconds=60))
+    assert open(pm.get_local_path(root + "/up.bin"), "rb").read() == b"newer"
+    d = pm.get_local_path(root)  # a directory: everything under it
+    assert sorted(n for n in os.listdir(d) if not n.endswith(".lock")) == ["ckpt.pt", "notes.txt", "up.bin"]
+
+
+class ClientError(Exception):
+    def __init__(self, message="Not Found"):
+        super().__init__(message)
+        self.response = {"Error": {"Message": message}}
+
+
+class _FakeS3:
+    """The slice of the S3 client API that the handler uses, over a dict of one bucket."""
+
+    def __init__(self):
+        import datetime
+
+        self.objects = {}
+        self.now = lambda: datetime.datetime.now(datetime.timezone.utc)
+        self.downloads = 0
+
+    def head_object(self, Bucket, Key):
+        if Key not in self.objects:
+            raise ClientError()
+        return {"ContentLength": len(self.objects[Key][0]), "LastModified": self.objects[Key][1]}
+
+    def list_objects_v2(self, Bucket, Prefix="", Delimiter=None, MaxKeys=1000, ContinuationToken=None):
+        keys = sorted(k for k in self.objects if k.startswith(Prefix))
+        contents, prefixes = [], []
+        for k in keys:
+            rest = k[len(Prefix):]
+            if Delimiter and Delimiter in rest:
+                p = Prefix + rest.split(Delimiter)[0] + Delimiter
+                if p not in prefixes:
+                    prefixes.append(p)
+            else:
+                contents.append({"Key": k})
+        start = int(ContinuationToken or 0)
+        page = contents[start:start + 2]  # tiny pages: the handler must follow the continuation token
+        more = start + 2 < len(contents)
+        out = {"Contents": page[:MaxKeys], "KeyCount": len(page[:MaxKeys]) + len(prefixes), "IsTruncated": more}
+        if not start:
+            out["CommonPrefixes"] = [{"Prefix": p} for p in prefixes]
+        if more:
+            out["NextContinuationToken"] = str(start + 2)
+        return out
+
+    def upload_fileobj(self, f, bucket, key, **kw):
+        self.objects[key] = (f.read(), self.now())
+
+    def upload_file(self, path, bucket, key, **kw):
+        self.objects[key] = (open(path, "rb").read(), self.now())
+
+    def download_file(self, bucket, key, path, **kw):
+        self.downloads += 1
+        open(path, "wb").write(self.objects[key][0])
+
+    def copy(self, src, bucket, key, **kw):
+        self.objects[key] = (self.objects[src["Key"]][0], self.now())
+
+    def put_object(self, Bucket, Key):
+        self.objects[Key] = (b"", self.now())
+
+    def delete_object(self, Bucket, Key):
+        if Key not in self.objects:
+            raise ClientError()
+        del self.objects[Key]
+
+
+def test_s3_handler_uploads_on_close_lists_one_level_and_refreshes_its_cache(tmp_path):
+    import datetime
+
+    from metaseq_b200.file_io.path_manager import PathManagerBase
+    from metaseq_b200.file_io.s3 import S3PathHandler
+
+    s3 = _FakeS3()
+    pm = PathManagerBase()
+    pm.register_handler(S3PathHandler(cache_dir=str(tmp_path / "cache"), client_factory=lambda: s3))
+    root = "s3://bucket/run"
+    with pm.open(root + "/a.bin", "wb") as f:
+        f.write(b"12")
+        f.write(b"345")
+        assert "run/a.bin" not in s3.objects  # nothing leaves before close
+    assert s3.objects["run/a.bin"][0] == b"12345"
+    with pm.open(root + "/notes.txt", "w") as f:
+        f.write("héllo\n")
+    for name in ("b.bin", "c.bin", "sub/d.bin", "sub/deeper/e.bin"):
+        s3.objects["run/" + name] = (b"x", s3.now())
+    assert pm.isfile(root + "/a.bin") and not pm.isfile(root + "/zzz") and pm.isdir(root) and pm.isdir(root + "/sub/")
+    assert not pm.isdir(root + "/a.bin") and pm.exists(root + "/sub") and not pm.exists(root + "/nothing")
+    assert sorted(pm.ls(root)) == ["run/a.bin", "run/b.bin", "run/c.bin", "run/notes.txt", "run/sub/"]
+    pm.mkdirs(root + "/empty/")
+    assert pm.isdir(root + "/empty") and pm.ls(root + "/empty") == []
+
+    with pm.open(root + "/notes.txt", "r") as f:
+        assert f.read() == "héllo\n"
+    before = s3.downloads
+    with pm.open(root + "/a.bin", "rb") as f:
+        assert f.read() == b"12345"
+    p = pm.get_local_path(root + "/a.bin")
+    assert s3.downloads == before + 1 and p.startswith(str(tmp_path / "cache"))
+    s3.objects["run/a.bin"] = (b"changed", s3.now() + datetime.timedelta(seconds=60))
+    assert open(pm.get_local_path(root + "/a.bin"), "rb").read() == b"changed" and s3.downloads == before + 2
+    with pytest.raises(NotImplementedError):
+        pm.get_local_path(root + "/sub/")
+
+    local = tmp_path / "up.bin"
+    local.write_bytes(b"up")
+    assert pm.copy_from_local(str(local), root + "/up.bin") and not pm.copy_from_local(str(local), root + "/up.bin")
+    assert pm.copy(root + "/up.bin", root + "/up2.bin") and s3.objects["run/up2.bin"][0] == b"up"
+    with pytest.raises(AssertionError):
+        pm.copy(root + "/up.bin", "s3://other/up.bin")
+    pm.rm(root + "/up2.bin")
+    with pytest.raises(OSError):
+        pm.rm(root + "/up2.bin")
+    with pytest.raises(ValueError):
+        pm.exists("s3://bucket-without-key")
