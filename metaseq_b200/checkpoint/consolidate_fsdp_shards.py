@@ -17,6 +17,8 @@ from metaseq_b200.checkpoint.reshard_fsdp import _sorted_shards, unflatten_state
 from metaseq_b200.checkpoint.reshard_mp import merge_parts
 from metaseq_b200.file_io import torch_load_cpu
 
+from metaseq_b200.checkpoint._cli import add_option, add_switch  # noqa: E402
+
 logger = logging.getLogger(__name__)
 
 
@@ -98,9 +100,9 @@ def handle_qkv_proj(model_parts, key: str, new_model_part_count: int):
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("pth_prefix")
-    ap.add_argument("--save-prefix", default=None)
-    ap.add_argument("--new-arch-name", default=None)
-    ap.add_argument("--merge-model-parts", action="store_true")
+    add_option(ap, "--save-prefix", default=None)
+    add_option(ap, "--new-arch-name", default=None)
+    add_switch(ap, "--merge-model-parts")
     a = ap.parse_args(argv)
     logging.basicConfig(level=logging.INFO)
     for p in consolidate_fsdp_shards(a.pth_prefix, a.save_prefix, a.new_arch_name, a.merge_model_parts):

@@ -21,6 +21,8 @@ from typing import Any, Dict, List, Tuple
 
 import torch
 
+from metaseq_b200.checkpoint._cli import add_switch
+
 logging.basicConfig(format="%(asctime)s | %(name)s | %(message)s", level=logging.INFO)
 logger = logging.getLogger("metaseq_b200.checkpoint.convert_metaseq_ft")
 
@@ -121,7 +123,7 @@ def main(argv=None):
     ap.add_argument("--input", required=True, help="glob of the model-parallel parts")
     ap.add_argument("--output", required=True, help="output pattern; {i} is replaced by the part index")
     ap.add_argument("--dtype", default="fp16", choices=sorted(_DTYPES))
-    ap.add_argument("--quantize", action="store_true")
+    add_switch(ap, "--quantize")
     a = ap.parse_args(argv)
     convert_metaseq_ft(a.input, a.output, a.dtype, a.quantize)
 

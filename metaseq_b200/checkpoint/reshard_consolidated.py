@@ -23,6 +23,8 @@ import torch
 from metaseq_b200.checkpoint import flat_shards
 from metaseq_b200.file_io import torch_load_cpu
 
+from metaseq_b200.checkpoint._cli import add_option, add_switch  # noqa: E402
+
 logger = logging.getLogger(__name__)
 
 LAYER_ORDER = [
@@ -131,9 +133,9 @@ def reshard_consolidated_checkpoint(input: str, output: str, num_output_shards: 
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--src", required=True)
-    ap.add_argument("--dst-dir-pattern", required=True)
-    ap.add_argument("--num-output-shards", type=int, default=1)
+    add_option(ap, "--src", "--input", dest="src", required=True)
+    add_option(ap, "--dst-dir-pattern", "--output", dest="dst_dir_pattern", required=True)
+    add_option(ap, "--num-output-shards", type=int, default=1)
     a = ap.parse_args(argv)
     logging.basicConfig(level=logging.INFO)
     for p in reshard_consolidated(a.src, a.dst_dir_pattern, a.num_output_shards):

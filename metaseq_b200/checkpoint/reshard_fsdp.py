@@ -24,6 +24,8 @@ import torch
 from metaseq_b200.checkpoint import flat_shards
 from metaseq_b200.file_io import torch_load_cpu
 
+from metaseq_b200.checkpoint._cli import add_option, add_switch  # noqa: E402
+
 logger = logging.getLogger(__name__)
 
 
@@ -166,13 +168,14 @@ def unflatten_state(states: List[Dict[str, Any]]) -> Dict[str, Any]:
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--src-dir-pattern", required=True)
-    ap.add_argument("--dst-dir-pattern", required=True, help="output path with an {i} placeholder for the shard index")
-    ap.add_argument("--num-output-shards", type=int, default=1)
-    ap.add_argument("--unflatten-weights", action="store_true")
-    ap.add_argument("--skip-optimizer-state", action="store_true")
-    ap.add_argument("--output-dtype", choices=sorted(_DTYPES), default=None, help="convert floating-point weights")
-    ap.add_argument("--drop-metaseq-req", action="store_true",
+    add_option(ap, "--src-dir-pattern", "--input", dest="src_dir_pattern", required=True, help="glob of the input shards")
+    add_option(ap, "--dst-dir-pattern", "--output", dest="dst_dir_pattern", required=True,
+               help="output path with an {i} placeholder for the shard index")
+    add_option(ap, "--num-output-shards", type=int, default=1)
+    add_switch(ap, "--unflatten-weights", help="split flat parameters back into named tensors (one output shard)")
+    add_switch(ap, "--skip-optimizer-state")
+    add_option(ap, "--output-dtype", choices=sorted(_DTYPES), default=None, help="convert floating-point weights")
+    add_switch(ap, "--drop-metaseq-req",
                     help="drop the data iterator state, which needs this package to unpickle")
     a = ap.parse_args(argv)
     logging.basicConfig(level=logging.INFO)

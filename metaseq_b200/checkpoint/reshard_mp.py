@@ -22,6 +22,8 @@ import torch
 
 from metaseq_b200.file_io import torch_load_cpu
 
+from metaseq_b200.checkpoint._cli import add_option, add_switch  # noqa: E402
+
 logger = logging.getLogger(__name__)
 
 DIM0 = re.compile(r"embed_tokens|output_projection|ffn_layernorm|fc1|(k|q|v)_proj")
@@ -158,10 +160,10 @@ def reshard_model_parallel_parts(input: str, output: str, num_output_parts: int 
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--src-dir-pattern", required=True)
-    ap.add_argument("--dst-dir-pattern", required=True)
-    ap.add_argument("--num-output-parts", type=int, default=1)
-    ap.add_argument("--keep-optimizer-state", action="store_true")
+    add_option(ap, "--src-dir-pattern", "--input", dest="src_dir_pattern", required=True)
+    add_option(ap, "--dst-dir-pattern", "--output", dest="dst_dir_pattern", required=True)
+    add_option(ap, "--num-output-parts", type=int, default=1)
+    add_switch(ap, "--keep-optimizer-state")
     a = ap.parse_args(argv)
     logging.basicConfig(level=logging.INFO)
     for p in reshard_mp(a.src_dir_pattern, a.dst_dir_pattern, a.num_output_parts, not a.keep_optimizer_state):

@@ -596,3 +596,28 @@ def test_launcher_helpers_name_the_run_snapshot_sources_and_pick_the_cluster(tmp
     assert sweep.get_env_from_args(ns) == ComputeEnvs.AWS
     with pytest.raises(NotImplementedError):
         sweep.get_env_from_args(types.SimpleNamespace(azure=False, aws=False, fair=False, rsc=False))
+
+
+def test_checkpoint_tools_take_the_reference_argument_spellings(tmp_path):
+    """``--input / --output``, underscores for dashes, and booleans with an explicit value, as python-fire takes them."""
+    import argparse
+
+    from metaseq_b200.checkpoint import reshard_mp
+    from metaseq_b200.checkpoint._cli import add_option, add_switch
+
+    ap = argparse.ArgumentParser()
+    add_option(ap, "--src-dir-pattern", "--input", dest="src")
+    add_option(ap, "--num-output-shards", type=int, default=1)
+    add_switch(ap, "--unflatten-weights")
+    add_switch(ap, "--skip-optimizer-state")
+    a = ap.parse_args(["--input", "x*.pt", "--num_output_shards", "2", "--unflatten-weights", "True",
+                       "--skip_optimizer_state=False"])
+    assert (a.src, a.num_output_shards, a.unflatten_weights, a.skip_optimizer_state) == ("x*.pt", 2, True, False)
+    assert ap.parse_args(["--src-dir-pattern", "y", "--unflatten-weights"]).unflatten_weights is True
+    with pytest.raises(SystemExit):
+        ap.parse_args(["--unflatten-weights", "maybe"])
+
+    torch.save({"model": {"decoder.layers.0.fc1.weight": torch.ones(4, 2)}, "cfg": {}}, tmp_path / "in-model_part-0.pt")
+    reshard_mp.main(["--input", str(tmp_path / "in-model_part-*.pt"), "--output", str(tmp_path / "out-{i}.pt"),
+                     "--num_output_parts", "2"])
+    assert torch.load(tmp_path / "out-1.pt", weights_only=False)["model"]["decoder.layers.0.fc1.weight"].shape == (2, 2)
