@@ -25,12 +25,14 @@ import logging
 import os
 import re
 import shutil
+import subprocess
 import threading
 import time
 import traceback
 from argparse import Namespace
 from glob import glob
 from typing import Any, Callable, Dict, List, Optional
+from urllib.parse import urlparse
 
 import torch
 
@@ -385,6 +387,26 @@ def load_checkpoint(cfg, trainer, **passthrough_args):
             checkpoint_path = os.path.join(latest, f"checkpoint{suffix}.pt") if latest else None
         elif explicit:
             checkpoint_path = ckpt.restore_file.replace(".pt", suffix + ".pt")
+    requeued = os.environ.get("SLURM_RESTART_COUNT", "0") not in ("0", "")
+    if upload and "blob.core.windows.net" in upload:
+        # blob storage holds the checkpoints (the callback removes the local files after upload): fetch this rank's
+        # file into save_dir before loading (reference: metaseq/checkpoint_utils.py:277-307, which calls a helper
+        # package that is not public; here the transfers go through azcopy, as the uploads do)
+        local = os.path.join(ckpt.save_dir, f"checkpoint_last{suffix}.pt")
+        explicit = ckpt.restore_file != default_restore_file
+        if (not explicit and ckpt.finetune_from_model is None) or requeued:
+            if download_recent_ckpt(upload, local, suffix + ".pt"):
+                checkpoint_path = local
+        elif explicit and "windows.net" in ckpt.restore_file:
+            download_specific_ckpt(ckpt.restore_file.replace(".pt", suffix + ".pt"), local)
+            checkpoint_path = local
+        else:
+            logger.info(f"Using checkpoint {checkpoint_path} even while uploading to blob storage")
+    elif not upload and ckpt.restore_file != default_restore_file and requeued:
+        # a requeued job that was started from an explicit file continues from its own newest checkpoint
+        mine = os.path.join(ckpt.save_dir, f"checkpoint_last{suffix}.pt")
+        if os.path.isfile(mine) or _shard_files_for(mine):
+            checkpoint_path = mine
     if dist_utils.is_initialized():
         torch.distributed.barrier()
     extra_state = trainer.load_checkpoint(checkpoint_path, reset_optimizer, reset_lr_scheduler, optimizer_overrides,
@@ -401,6 +423,40 @@ def load_checkpoint(cfg, trainer, **passthrough_args):
         epoch_itr = trainer.get_train_iterator(epoch=1, **passthrough_args)
     trainer.lr_step(epoch_itr.epoch)
     return extra_state, epoch_itr
+
+
+def _run_azcopy(args: List[str]):
+    return subprocess.run(["azcopy", *args], stdout=subprocess.PIPE, stderr=subprocess.PIPE)
+
+
+def _blob_child(url: str, name: str) -> str:
+    """``url`` with ``name`` appended to its path, in front of the query (the SAS token stays last)."""
+    parts = urlparse(url)
+    return parts._replace(path=parts.path.rstrip("/") + "/" + name).geturl()
+
+
+def download_specific_ckpt(blob_url: str, local_path: str) -> bool:
+    os.makedirs(os.path.dirname(os.path.abspath(local_path)), exist_ok=True)
+    res = _run_azcopy(["copy", blob_url, local_path])
+    if res.returncode != 0:
+        raise OSError(f"azcopy could not fetch {blob_url.split('?')[0]}: {res.stdout[-500:]!r}")
+    logger.info(f"downloaded {blob_url.split('?')[0]} to {local_path}")
+    return True
+
+
+def download_recent_ckpt(blob_url: str, local_path: str, suffix_pt: str) -> bool:
+    """Fetches ``checkpoint_<N><suffix_pt>`` with the largest N found under ``blob_url`` to ``local_path``.  Returns
+    False when the container holds none (a first launch)."""
+    res = _run_azcopy(["list", blob_url])
+    if res.returncode != 0:
+        raise OSError(f"azcopy could not list {blob_url.split('?')[0]}: {res.stdout[-500:]!r}")
+    pattern = re.compile(r"(checkpoint_(\d+)" + re.escape(suffix_pt) + r")(?=[;\s]|$)")
+    found = [(int(m.group(2)), m.group(1)) for m in pattern.finditer(res.stdout.decode("utf-8", "replace"))]
+    if not found:
+        logger.info(f"no checkpoint for this rank ({suffix_pt}) under {blob_url.split('?')[0]}")
+        return False
+    _, name = max(found)
+    return download_specific_ckpt(_blob_child(blob_url, name), local_path)
 
 
 def _newest_update_checkpoint(save_dir: str, suffix: str) -> Optional[str]:

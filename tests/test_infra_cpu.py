@@ -400,3 +400,59 @@ def test_column_parallel_product_with_async_communication_matches_the_full_produ
         assert torch.allclose(y_r, y.detach()[..., cols]) and torch.allclose(dx_r, x.grad[r * t:(r + 1) * t])
         assert dw_r is None and torch.allclose(main_grad.double(), w.grad[cols], atol=1e-5)
         assert torch.allclose(db_r, b.grad[cols])
+
+
+def test_restart_fetches_the_newest_checkpoint_of_this_rank_from_blob_storage(tmp_path, monkeypatch):
+    calls, seen = [], {}
+    listing = (b"INFO: checkpoint_10-model_part-0-shard0.pt;  Content Length: 1.00 GiB\n"
+               b"INFO: checkpoint_20-model_part-0-shard0.pt;  Content Length: 1.00 GiB\n"
+               b"INFO: checkpoint_30-model_part-0-shard1.pt;  Content Length: 1.00 GiB\n"
+               b"INFO: checkpoint_last-model_part-0-shard0.pt;  Content Length: 1.00 GiB\n")
+
+    def fake_azcopy(args):
+        calls.append(args)
+        if args[0] == "copy":
+            open(args[2], "wb").write(b"ckpt")
+        return types.SimpleNamespace(returncode=0, stdout=listing if args[0] == "list" else b"", stderr=b"")
+
+    monkeypatch.setattr(checkpoint_utils, "_run_azcopy", fake_azcopy)
+
+    class FakeTrainer:
+        checkpoint_suffix = "-model_part-0-shard0"
+
+        def load_checkpoint(self, path, *a, **k):
+            seen["path"] = path
+            return None
+
+        def get_train_iterator(self, epoch, **k):
+            return types.SimpleNamespace(epoch=epoch)
+
+        def lr_step(self, epoch):
+            pass
+
+    url = "https://acct.blob.core.windows.net/cont/run?sig=abc"
+    ck = types.SimpleNamespace(
+        reset_optimizer=False, reset_lr_scheduler=False, optimizer_overrides="{}", reset_meters=False,
+        reset_dataloader=False, finetune_from_model=None, restore_file="checkpoint_last.pt",
+        save_dir=str(tmp_path / "local"), cloud_upload_path=url)
+    checkpoint_utils.load_checkpoint(types.SimpleNamespace(checkpoint=ck), FakeTrainer())
+    local = str(tmp_path / "local" / "checkpoint_last-model_part-0-shard0.pt")
+    assert calls[0] == ["list", url]
+    assert calls[1] == ["copy", "https://acct.blob.core.windows.net/cont/run/checkpoint_20-model_part-0-shard0.pt?sig=abc", local]
+    assert seen["path"] == local and open(local, "rb").read() == b"ckpt"
+
+    # an empty container is a first launch, not an error
+    listing = b""
+    calls.clear()
+    checkpoint_utils.load_checkpoint(types.SimpleNamespace(checkpoint=ck), FakeTrainer())
+    assert [c[0] for c in calls] == ["list"]
+
+    # without an upload path, a requeued job that began from an explicit file continues from its own last checkpoint
+    ck.cloud_upload_path = None
+    ck.restore_file = str(tmp_path / "pretrained" / "model.pt")
+    monkeypatch.setenv("SLURM_RESTART_COUNT", "2")
+    checkpoint_utils.load_checkpoint(types.SimpleNamespace(checkpoint=ck), FakeTrainer())
+    assert seen["path"] == local
+    os.remove(local)
+    checkpoint_utils.load_checkpoint(types.SimpleNamespace(checkpoint=ck), FakeTrainer())
+    assert seen["path"] == str(tmp_path / "pretrained" / "model-model_part-0-shard0.pt")
