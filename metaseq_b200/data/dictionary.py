@@ -47,22 +47,16 @@ class Dictionary:
         return self.count[idx]
 
     def string(self, tensor, bpe_symbol=None, escape_unk=False, extra_symbols_to_ignore=None, unk_string=None) -> str:
+        """Text of a token tensor (one line per row for a matrix).  End-of-sentence, begin-of-sentence and the
+        given extra symbols are left out; ``bpe_symbol`` (a continuation marker such as ``@@ ``) is removed."""
         if torch.is_tensor(tensor) and tensor.dim() == 2:
-            return "\n".join(self.string(t, bpe_symbol, escape_unk, extra_symbols_to_ignore) for t in tensor)
-        ignore = set(extra_symbols_to_ignore or [])
-        ignore.add(self.eos())
-
-        def tok(i):
-            if i == self.unk():
-                return unk_string if unk_string is not None else self.unk_string(escape_unk)
-            return self[i]
-
-        if hasattr(self, "bos_index"):
-            ignore.add(self.bos())
-        sent = " ".join(tok(int(i)) for i in tensor if int(i) not in ignore)
-        if bpe_symbol:
-            sent = (sent + " ").replace(bpe_symbol, "").rstrip()
-        return sent
+            rows = (self.string(row, bpe_symbol, escape_unk, extra_symbols_to_ignore) for row in tensor)
+            return "\n".join(rows)
+        skipped = {self.eos_index, self.bos_index, *(extra_symbols_to_ignore or ())}
+        unknown = unk_string if unk_string is not None else self.unk_string(escape_unk)
+        words = [unknown if i == self.unk_index else self[i] for i in map(int, tensor) if i not in skipped]
+        text = " ".join(words)
+        return (text + " ").replace(bpe_symbol, "").rstrip() if bpe_symbol else text
 
     def unk_string(self, escape=False) -> str:
         return "<{}>".format(self.unk_word) if escape else self.unk_word
@@ -83,28 +77,22 @@ class Dictionary:
             self.add_symbol(word, c)
 
     def finalize(self, threshold: int = -1, nwords: int = -1, padding_factor: int = 8):
-        """Sort by decreasing frequency (specials stay first), drop rare words, pad."""
-        if nwords <= 0:
-            nwords = len(self)
-        new_symbols = self.symbols[: self.nspecial]
-        new_count = self.count[: self.nspecial]
-        c = Counter(dict(sorted(zip(self.symbols[self.nspecial:], self.count[self.nspecial:]))))
-        for sym, cnt in c.most_common(nwords - self.nspecial):
-            if cnt >= threshold:
-                new_symbols.append(sym)
-                new_count.append(cnt)
-            else:
-                break
-        self.symbols, self.count = list(new_symbols), list(new_count)
-        self.indices = {s: i for i, s in enumerate(self.symbols)}
+        """Orders the non-special symbols by falling count (ties alphabetically), keeps at most ``nwords`` entries
+        in total and only symbols seen at least ``threshold`` times, then pads to a multiple of ``padding_factor``."""
+        keep = self.nspecial
+        limit = (nwords if nwords > 0 else len(self)) - keep
+        ranked = sorted(zip(self.symbols[keep:], self.count[keep:]), key=lambda sc: (-sc[1], sc[0]))
+        ranked = [(sym, n) for sym, n in ranked[:max(limit, 0)] if n >= threshold]
+        self.symbols = self.symbols[:keep] + [sym for sym, _ in ranked]
+        self.count = self.count[:keep] + [n for _, n in ranked]
+        self.indices = {sym: i for i, sym in enumerate(self.symbols)}
         self.pad_to_multiple_(padding_factor)
 
     def pad_to_multiple_(self, padding_factor: int):
-        if padding_factor > 1:
-            i = 0
-            while len(self) % padding_factor != 0:
-                self.add_symbol("madeupword{:04d}".format(i), n=0)
-                i += 1
+        """Appends ``madeupwordNNNN`` entries (count 0) until the size is a multiple of ``padding_factor``."""
+        missing = -len(self) % padding_factor if padding_factor > 1 else 0
+        for i in range(missing):
+            self.add_symbol(f"madeupword{i:04d}", n=0)
 
     def bos(self) -> int:
         return self.bos_index
@@ -126,22 +114,25 @@ class Dictionary:
         return d
 
     def add_from_file(self, f):
+        """Appends the entries of a dictionary file (a path or an open text file).  A line that ends in
+        ``#fairseq:overwrite`` may redefine a symbol that exists; any other duplicate is an error."""
         if isinstance(f, str):
-            with open(f, "r", encoding="utf-8") as fd:
-                return self.add_from_file(fd)
-        for line in f.readlines():
-            try:
-                line, field = line.rstrip().rsplit(" ", 1)
-                overwrite = False
-                if field == "#fairseq:overwrite":
-                    overwrite = True
-                    line, field = line.rsplit(" ", 1)
-                count = int(field)
-                if line in self and not overwrite:
-                    raise RuntimeError(f"Duplicate word found when loading Dictionary: '{line}'")
-                self.add_symbol(line, n=count, overwrite=overwrite)
-            except ValueError:
+            with open(f, "r", encoding="utf-8") as handle:
+                return self.add_from_file(handle)
+        flag = "#fairseq:overwrite"
+        for raw in f:
+            fields = raw.rstrip().rsplit(" ", 2)
+            overwrite = fields[-1] == flag
+            if overwrite:
+                fields = fields[:-1]
+            elif len(fields) == 3:
+                fields = [fields[0] + " " + fields[1], fields[2]]
+            if len(fields) != 2 or not fields[1].lstrip("-").isdigit():
                 raise ValueError("Incorrect dictionary format, expected '<token> <cnt> [flags]'")
+            symbol, count = fields[0], int(fields[1])
+            if symbol in self.indices and not overwrite:
+                raise RuntimeError(f"Duplicate word found when loading Dictionary: '{symbol}'")
+            self.add_symbol(symbol, n=count, overwrite=overwrite)
 
     def save(self, f):
         if isinstance(f, str):
@@ -158,21 +149,23 @@ class Dictionary:
 
     def encode_line(self, line: str, line_tokenizer=None, add_if_not_exist=True, consumer=None, append_eos=True,
                     reverse_order=False) -> torch.IntTensor:
+        """Ids of the words of ``line`` (split by ``line_tokenizer``, default: on whitespace), optionally reversed
+        and followed by end-of-sentence.  Unknown words are added or mapped to ``<unk>``; ``consumer(word, id)`` sees
+        every word."""
         from metaseq_b200.utils import tokenize_line
 
-        words = (line_tokenizer or tokenize_line)(line)
+        words = list((line_tokenizer or tokenize_line)(line))
         if reverse_order:
-            words = list(reversed(words))
-        n = len(words)
-        ids = torch.IntTensor(n + 1 if append_eos else n)
-        for i, w in enumerate(words):
-            idx = self.add_symbol(w) if add_if_not_exist else self.index(w)
+            words.reverse()
+        lookup = self.add_symbol if add_if_not_exist else self.index
+        ids = []
+        for word in words:
+            ids.append(lookup(word))
             if consumer is not None:
-                consumer(w, idx)
-            ids[i] = idx
+                consumer(word, ids[-1])
         if append_eos:
-            ids[n] = self.eos_index
-        return ids
+            ids.append(self.eos_index)
+        return torch.tensor(ids, dtype=torch.int32)
 
     @staticmethod
     def _count_words_in_chunk(filename: str, tokenize, eos_word: str, start: int, end: int) -> Counter:

@@ -76,38 +76,39 @@ def _device_count() -> int:
 
 @dataclass
 class CommonConfig(MetaseqDataclass):
-    log_interval: int = opt(100, "log progress every N batches")
-    log_format: Optional[str] = opt(None, "log format to use", choices=LOG_FORMAT_CHOICES)
-    log_file: Optional[str] = opt(None, "log file to copy metrics to")
-    tensorboard_logdir: Optional[str] = opt(None, "path to save logs for tensorboard")
-    aim_repo: Optional[str] = opt(None, "path to Aim repository")
-    aim_run_hash: Optional[str] = opt(None, "Aim run hash")
-    wandb_project: Optional[str] = opt(None, "Weights and Biases project name")
-    azureml_logging: Optional[bool] = opt(False, "log scalars to AzureML context")
-    seed: int = opt(1, "pseudo random number generator seed")
-    seed_per_rank: bool = opt(False, "use different seed per rank")
-    cpu: bool = opt(False, "use CPU instead of CUDA")
-    fp16: bool = opt(False, "use FP16")
-    memory_efficient_fp16: bool = opt(False, "use a memory-efficient version of FP16 training; implies --fp16")
-    bf16: bool = opt(False, "use BF16 format")
-    fp16_no_flatten_grads: bool = opt(False, "don't flatten FP16 grads tensor")
-    fp16_init_scale: int = opt(4, "default FP16 loss scale")
-    fp16_scale_window: Optional[int] = opt(256, "number of updates before increasing loss scale")
-    fp16_scale_tolerance: float = opt(0.0, "pct of updates that can overflow before decreasing the loss scale")
-    min_loss_scale: float = opt(2 ** -5, "minimum FP16 loss scale, after which training is stopped")
-    threshold_loss_scale: Optional[float] = opt(None, "threshold FP16 loss scale from below")
-    user_dir: Optional[str] = opt(None, "path to a python module containing custom extensions")
-    empty_cache_freq: int = opt(0, "how often to clear the PyTorch CUDA cache (0 to disable)")
-    all_gather_list_size: int = opt(16384, "number of bytes reserved for gathering stats from workers")
-    model_parallel_size: int = opt(1, "total number of GPUs to parallelize model over")
-    profile: bool = opt(False, "use pytorch profiler on the 6th step of rank 0")
+    log_interval: int = opt(100, "number of batches between two progress lines")
+    log_format: Optional[str] = opt(None, "how progress is printed", choices=LOG_FORMAT_CHOICES)
+    log_file: Optional[str] = opt(None, "metrics are also appended to this file")
+    tensorboard_logdir: Optional[str] = opt(None, "directory for tensorboard event files")
+    aim_repo: Optional[str] = opt(None, "location of the Aim repository to log to")
+    aim_run_hash: Optional[str] = opt(None, "hash of an existing Aim run to continue")
+    wandb_project: Optional[str] = opt(None, "project name on Weights and Biases")
+    azureml_logging: Optional[bool] = opt(False, "send scalars to the AzureML run context")
+    seed: int = opt(1, "seed of every random number generator")
+    seed_per_rank: bool = opt(False, "offset the seed by the rank")
+    cpu: bool = opt(False, "run on the host even when a GPU is present")
+    fp16: bool = opt(False, "half-precision weights and activations with fp32 master weights")
+    memory_efficient_fp16: bool = opt(False, "half precision without an fp32 master copy (the optimizer "
+                                             "computes in fp32 internally); turns --fp16 on")
+    bf16: bool = opt(False, "bfloat16 weights and activations")
+    fp16_no_flatten_grads: bool = opt(False, "keep half-precision gradients as separate tensors")
+    fp16_init_scale: int = opt(4, "loss scale at the start")
+    fp16_scale_window: Optional[int] = opt(256, "overflow-free updates after which the loss scale doubles")
+    fp16_scale_tolerance: float = opt(0.0, "share of updates that may overflow before the loss scale is halved")
+    min_loss_scale: float = opt(2 ** -5, "training stops when the loss scale falls below this")
+    threshold_loss_scale: Optional[float] = opt(None, "the loss scale is never lowered below this")
+    user_dir: Optional[str] = opt(None, "python module with user-defined tasks, models or criterions to import")
+    empty_cache_freq: int = opt(0, "release the CUDA caching allocator's blocks every N updates (0 = never)")
+    all_gather_list_size: int = opt(16384, "byte size of the buffer for gathering python objects over ranks")
+    model_parallel_size: int = opt(1, "tensor-parallel width (GPUs that share one model replica)")
+    profile: bool = opt(False, "trace a few updates of rank 0 with the torch profiler")
     watchdog_timeout: float = opt(0.0, "seconds without a finished training step (or with a kernel reporting a "
                                        "timed-out wait) after which the host watchdog dumps all thread stacks and "
                                        "interrupts the run; 0 disables it")
-    use_plasma_view: bool = opt(False, "store indices and sizes in shared memory")
-    plasma_path: Optional[str] = opt("/tmp/plasma", "path to run plasma_store")
-    log_nvidia_smi: bool = opt(False, "log output from nvidia-smi during training")
-    quiet_logs: Optional[bool] = opt(False, "don't log per-parameter gnorm/pnorm stats")
+    use_plasma_view: bool = opt(False, "keep dataset index and size arrays in shared memory")
+    plasma_path: Optional[str] = opt("/tmp/plasma", "socket path of the shared-memory store")
+    log_nvidia_smi: bool = opt(False, "add nvidia-smi memory readings to the training log")
+    quiet_logs: Optional[bool] = opt(False, "leave per-parameter gradient / weight norms out of the log")
     log_param_stats: bool = opt(False, "log norm / max / zero share of every flat parameter and its gradient each "
                                        "update (a few hundred small reductions per update; off by default)")
     # additions of this framework
@@ -122,102 +123,113 @@ class CommonConfig(MetaseqDataclass):
 
 @dataclass
 class DistributedTrainingConfig(MetaseqDataclass):
-    distributed_world_size: int = opt(factory=_device_count, help="total number of GPUs across all nodes")
-    distributed_rank: Optional[int] = opt(0, "rank of the current worker")
-    distributed_backend: str = opt("nccl", "distributed backend")
-    distributed_init_method: Optional[str] = opt(None, "typically tcp://hostname:port used to establish the "
-                                                 "initial connection")
-    distributed_port: int = opt(-1, "port number (not required if using --distributed-init-method)")
-    device_id: int = opt(0, "which GPU to use (usually configured automatically)", alias="--local_rank")
-    distributed_no_spawn: bool = opt(False, "do not spawn multiple processes even if multiple GPUs are visible")
-    ddp_backend: str = opt("pytorch_ddp", "DistributedDataParallel backend", choices=DDP_BACKEND_CHOICES)
-    task_ddp_backend: str = opt("none", "if set, overrides --ddp-backend for the task", choices=TASK_DDP_BACKEND_CHOICES)
-    bucket_cap_mb: int = opt(25, "bucket size for reduction")
-    fix_batches_to_gpus: bool = opt(False, "don't shuffle batches between GPUs")
-    find_unused_parameters: bool = opt(False, "disable unused parameter detection")
-    fast_stat_sync: bool = opt(False, "[deprecated] this is now defined per criterion")
-    broadcast_buffers: bool = opt(False, "copy non-trainable parameters between GPUs")
+    distributed_world_size: int = opt(factory=_device_count, help="number of ranks (one per GPU) over all nodes")
+    distributed_rank: Optional[int] = opt(0, "this process's rank")
+    distributed_backend: str = opt("nccl", "torch.distributed backend")
+    distributed_init_method: Optional[str] = opt(None, "rendezvous URL, e.g. tcp://host:port")
+    distributed_port: int = opt(-1, "rendezvous port when no URL is given")
+    device_id: int = opt(0, "local GPU index (normally set by the launcher)", alias="--local_rank")
+    distributed_no_spawn: bool = opt(False, "stay in one process although several GPUs are visible")
+    ddp_backend: str = opt("pytorch_ddp", "data-parallel engine", choices=DDP_BACKEND_CHOICES)
+    task_ddp_backend: str = opt("none", "data-parallel engine chosen by the task, if any",
+                                choices=TASK_DDP_BACKEND_CHOICES)
+    bucket_cap_mb: int = opt(25, "gradient bucket size in MB")
+    fix_batches_to_gpus: bool = opt(False, "every rank keeps the same batches in every epoch")
+    find_unused_parameters: bool = opt(False, "let DDP search for parameters without gradient")
+    fast_stat_sync: bool = opt(False, "no effect (kept for old command lines)")
+    broadcast_buffers: bool = opt(False, "synchronise module buffers over ranks every step")
     fp16: bool = opt(False, link="common.fp16")
     memory_efficient_fp16: bool = opt(False, link="common.memory_efficient_fp16")
     bf16: bool = opt(False, link="common.bf16")
-    no_reshard_after_forward: bool = opt(False, "don't reshard parameters after forward pass")
-    fp32_reduce_scatter: bool = opt(False, "reduce-scatter grads in FP32")
-    cpu_offload: bool = opt(False, "offload FP32 params to CPU")
-    use_sharded_state: Optional[bool] = opt(False, "load and save local state dict")
-    gradient_predivide_factor: Optional[float] = opt(None, "factor to predivide gradients before reduce-scatter")
+    no_reshard_after_forward: bool = opt(False, "keep gathered parameters until backward (ZeRO-2 style)")
+    fp32_reduce_scatter: bool = opt(False, "sum gradient shards in fp32")
+    cpu_offload: bool = opt(False, "keep fp32 shards and optimizer state in host memory")
+    use_sharded_state: Optional[bool] = opt(False, "checkpoints hold each rank's shard, not the full model")
+    gradient_predivide_factor: Optional[float] = opt(None, "divide gradients by this before the reduce-scatter "
+                                                           "and by world / this after")
 
 
 @dataclass
 class DatasetConfig(MetaseqDataclass):
-    num_workers: int = opt(1, "how many subprocesses to use for data loading")
-    num_workers_valid: int = opt(0, "how many subprocesses to use for data loading during validation")
-    skip_invalid_size_inputs_valid_test: bool = opt(False, "ignore too long or too short lines in valid and test set")
-    max_tokens: Optional[int] = opt(None, "maximum number of tokens in a batch")
-    batch_size: Optional[int] = opt(None, "number of examples in a batch", alias="--max-sentences")
-    required_batch_size_multiple: int = opt(8, "batch size will be a multiplier of this value")
-    dataset_impl: Optional[str] = opt(None, "output dataset implementation", choices=DATASET_IMPL_CHOICES)
-    data_buffer_size: int = opt(10, "number of batches to preload")
-    skip_batches: str = opt("", "comma separated list of batch ranges to skip in multiple of num_update, e.g. "
-                            "'100-200,150-250' skips updates [100,200] and [150,250]")
-    train_subset: str = opt("train", "data subset to use for training (e.g. train, valid, test)")
-    valid_subset: str = opt("valid", "comma separated list of data subsets to use for validation")
-    combine_valid_subsets: Optional[bool] = opt(None, "comma separated list of data subsets to use for validation",
+    num_workers: int = opt(1, "data loader worker processes")
+    num_workers_valid: int = opt(0, "data loader worker processes for validation")
+    skip_invalid_size_inputs_valid_test: bool = opt(False, "drop evaluation samples outside the model's length "
+                                                           "limits instead of failing")
+    max_tokens: Optional[int] = opt(None, "token budget of one batch")
+    batch_size: Optional[int] = opt(None, "samples per batch", alias="--max-sentences")
+    required_batch_size_multiple: int = opt(8, "batch sizes are cut to a multiple of this")
+    dataset_impl: Optional[str] = opt(None, "on-disk format of indexed datasets", choices=DATASET_IMPL_CHOICES)
+    data_buffer_size: int = opt(10, "batches prefetched ahead of the training loop")
+    skip_batches: str = opt("", "update ranges whose batches are read but not trained on, e.g. "
+                                "'100-200,150-250'")
+    train_subset: str = opt("train", "split to train on")
+    valid_subset: str = opt("valid", "splits to validate on, comma separated")
+    combine_valid_subsets: Optional[bool] = opt(None, "validate on the union of all valid* splits as one set",
                                                 alias="--combine-val")
-    ignore_unused_valid_subsets: Optional[bool] = opt(False, "do not raise error if valid subsets are ignored")
-    validate_interval_updates: int = opt(0, "validate every N updates")
-    validate_after_updates: int = opt(0, "don't validate until reaching this many updates")
-    fixed_validation_seed: Optional[int] = opt(None, "specified random seed for validation")
-    disable_validation: bool = opt(False, "disable validation")
-    max_tokens_valid: Optional[int] = opt(None, "maximum number of tokens in a validation batch",
+    ignore_unused_valid_subsets: Optional[bool] = opt(False, "valid* directories that are not listed are fine")
+    validate_interval_updates: int = opt(0, "validate every N updates (0 = only at epoch ends)")
+    validate_after_updates: int = opt(0, "no validation before update N")
+    fixed_validation_seed: Optional[int] = opt(None, "reseed before every validation pass")
+    disable_validation: bool = opt(False, "never validate")
+    max_tokens_valid: Optional[int] = opt(None, "token budget of a validation batch",
                                           link="dataset.max_tokens")
-    batch_size_valid: Optional[int] = opt(None, "batch size of the validation batch", link="dataset.batch_size",
+    batch_size_valid: Optional[int] = opt(None, "samples per validation batch", link="dataset.batch_size",
                                           alias="--max-sentences-valid")
-    max_valid_steps: Optional[int] = opt(None, "how many batches to evaluate", alias="--nval")
-    gen_subset: str = opt("test", "data subset to generate (train, valid, test)")
-    num_shards: int = opt(1, "shard generation over N shards")
-    shard_id: int = opt(0, "id of the shard to generate (id < num_shards)")
+    max_valid_steps: Optional[int] = opt(None, "stop a validation pass after N batches", alias="--nval")
+    gen_subset: str = opt("test", "split used for generation")
+    num_shards: int = opt(1, "number of parts the generation set is cut into")
+    shard_id: int = opt(0, "which of those parts this process takes")
 
 
 @dataclass
 class OptimizationConfig(MetaseqDataclass):
-    max_epoch: int = opt(0, "force stop training at specified epoch")
-    max_update: int = opt(0, "force stop training at specified update")
-    clip_norm: float = opt(0.0, "clip threshold of gradients")
-    clip_norm_type: Optional[str] = opt("l2", "either 'l2' or 'inf' to clip by l2 norm or max abs grad",
+    max_epoch: int = opt(0, "last epoch (0 = no limit)")
+    max_update: int = opt(0, "last update (0 = no limit)")
+    clip_norm: float = opt(0.0, "gradient norm above which gradients are scaled down (0 = off)")
+    clip_norm_type: Optional[str] = opt("l2", "norm used for clipping: l2, or inf for the largest absolute "
+                                              "value",
                                         choices=CLIP_GRAD_NORM_TYPE_CHOICES)
-    skip_gradient_update_on_clip_norm: bool = opt(False, "skip gradient update if gnorm is higher than --clip-norm")
+    skip_gradient_update_on_clip_norm: bool = opt(False, "reject the batch when its gradient norm exceeds "
+                                                         "--clip-norm")
     ewm_ratio_to_skip_batch: float = opt(-1, "skip a batch whose loss / ewm(loss) exceeds this ratio (-1 disables)")
-    update_freq: List[int] = opt(factory=lambda: [1], help="update parameters every N_i batches, when in epoch i")
-    lr: List[float] = opt(factory=lambda: [0.25], help="learning rate for the first N epochs; all epochs >N use LR_N")
+    update_freq: List[int] = opt(factory=lambda: [1], help="micro-batches accumulated per update, one entry "
+                                                           "per epoch")
+    lr: List[float] = opt(factory=lambda: [0.25], help="peak learning rate, one entry per epoch (the last one "
+                                                       "repeats)")
 
 
 @dataclass
 class CheckpointConfig(MetaseqDataclass):
-    save_dir: str = opt("checkpoints", "path to save checkpoints")
-    restore_file: str = opt("checkpoint_last.pt", "filename from which to load checkpoint")
-    finetune_from_model: Optional[str] = opt(None, "finetune from a pretrained model; note that meters and lr "
-                                             "scheduler will be reset")
-    reset_dataloader: bool = opt(False, "if set, does not reload dataloader state from the checkpoint")
-    reset_lr_scheduler: bool = opt(False, "if set, does not load lr scheduler state from the checkpoint")
-    reset_meters: bool = opt(False, "if set, does not load meters from the checkpoint")
-    reset_optimizer: bool = opt(False, "if set, does not load optimizer state from the checkpoint")
-    optimizer_overrides: str = opt("{}", "a dictionary used to override optimizer args when loading a checkpoint")
-    save_interval_epochs: int = opt(1, "save a checkpoint every N epochs")
-    save_interval_updates: int = opt(0, "save a checkpoint (and validate) every N updates")
-    local_save_interval_updates: int = opt(0, "save a checkpoint to local disk every N updates")
-    save_last_checkpoint: bool = opt(True, "store a last checkpoint at the end of the training run")
-    keep_last_epochs: int = opt(-1, "keep only the last N epoch checkpoints")
-    keep_last_updates: int = opt(-1, "keep only the last N updates checkpoints")
-    checkpoint_suffix: str = opt("", "suffix to add to the checkpoint file name")
-    checkpoint_shard_count: int = opt(1, "number of shards containing the checkpoint")
-    write_checkpoints_asynchronously: bool = opt(True, "write checkpoints asynchronously in a separate thread",
+    save_dir: str = opt("checkpoints", "directory for checkpoints")
+    restore_file: str = opt("checkpoint_last.pt", "checkpoint to resume from (a name inside --save-dir or a "
+                                                  "path)")
+    finetune_from_model: Optional[str] = opt(None, "start from these weights with fresh optimizer, schedule, "
+                                                   "meters and data position")
+    reset_dataloader: bool = opt(False, "start the data from the beginning although the checkpoint has a "
+                                        "position")
+    reset_lr_scheduler: bool = opt(False, "ignore the schedule state of the checkpoint")
+    reset_meters: bool = opt(False, "ignore the meters of the checkpoint")
+    reset_optimizer: bool = opt(False, "ignore the optimizer state of the checkpoint")
+    optimizer_overrides: str = opt("{}", "python dict of optimizer settings that replace the checkpoint's")
+    save_interval_epochs: int = opt(1, "epochs between checkpoints")
+    save_interval_updates: int = opt(0, "updates between checkpoints (each is followed by a validation pass)")
+    local_save_interval_updates: int = opt(0, "updates between checkpoints that stay on local disk")
+    save_last_checkpoint: bool = opt(True, "write checkpoint_last when training ends")
+    keep_last_epochs: int = opt(-1, "older epoch checkpoints are deleted beyond this many (-1 = keep all)")
+    keep_last_updates: int = opt(-1, "older update checkpoints are deleted beyond this many (-1 = keep all)")
+    checkpoint_suffix: str = opt("", "inserted before .pt in checkpoint names")
+    checkpoint_shard_count: int = opt(1, "files one checkpoint is split over")
+    write_checkpoints_asynchronously: bool = opt(True, "serialise and write on a background thread",
                                                  alias="--save-async")
-    cloud_upload_path: Optional[str] = opt(None, "upload checkpoints asynchronously to this cloud path or nfs: dir")
-    nfs_eval_script_path: Optional[str] = opt(None, "path of eval script to run on checkpoints copied to NFS")
-    nfs_eval_num_attempts: int = opt(10, "number of attempts of running evals on an NFS checkpoint")
-    nfs_eval_attempt_wait_minutes: int = opt(5, "time to wait between attempts of running evals")
-    nfs_eval_frequency: int = opt(5000, "run evaluation only on uploaded checkpoints with multiples of this frequency")
-    cluster_env: str = opt("fair", "cluster we are running on: azure/aws/fair/rsc")
+    cloud_upload_path: Optional[str] = opt(None, "blob-storage URL or nfs:<dir> that finished checkpoints are "
+                                                 "moved to")
+    nfs_eval_script_path: Optional[str] = opt(None, "script started on each checkpoint that has arrived on the "
+                                                    "shared directory")
+    nfs_eval_num_attempts: int = opt(10, "times to look for all parts of a checkpoint before giving up on its "
+                                         "evaluation")
+    nfs_eval_attempt_wait_minutes: int = opt(5, "minutes between those looks")
+    nfs_eval_frequency: int = opt(5000, "only checkpoints whose update is a multiple of this are evaluated")
+    cluster_env: str = opt("fair", "where the job runs: azure, aws, fair or rsc")
     model_parallel_size: int = opt(1, link="common.model_parallel_size")
     sequence_parallel: bool = opt(False, "shard LayerNorm / residual regions along the sequence across the "
                                   "tensor-parallel group (needs --model-parallel-size > 1)")
@@ -225,52 +237,53 @@ class CheckpointConfig(MetaseqDataclass):
 
 @dataclass
 class GenerationConfig(MetaseqDataclass):
-    beam: int = opt(5, "beam size")
-    max_len_a: float = opt(0, "generate sequences of maximum length ax + b, where x is the source length")
-    max_len_b: int = opt(200, "generate sequences of maximum length ax + b, where x is the source length")
-    min_len: int = opt(1, "minimum generation length")
-    sampling: bool = opt(False, "sample hypotheses instead of using beam search")
-    sampling_topp: float = opt(-1.0, "sample from the smallest set whose cumulative probability mass exceeds p")
-    temperature: float = opt(1.0, "temperature for generation")
-    no_seed_provided: bool = opt(False, "if set then no seed was provided for generation")
-    buffer_size: int = opt(0, "read this many sentences into a buffer before processing them")
-    input: str = opt("-", "file to read from; use - for stdin")
+    beam: int = opt(5, "hypotheses kept per prompt")
+    max_len_a: float = opt(0, "a in the length limit a * prompt length + b")
+    max_len_b: int = opt(200, "b in the length limit a * prompt length + b")
+    min_len: int = opt(1, "fewest tokens to generate")
+    sampling: bool = opt(False, "draw tokens at random instead of taking the best")
+    sampling_topp: float = opt(-1.0, "nucleus sampling: restrict to the most probable tokens whose mass "
+                                     "reaches p")
+    temperature: float = opt(1.0, "logits are divided by this before sampling")
+    no_seed_provided: bool = opt(False, "set by the parser when --seed was not given")
+    buffer_size: int = opt(0, "input lines read ahead in interactive mode")
+    input: str = opt("-", "input file (- = standard input)")
 
 
 @dataclass
 class CommonEvalConfig(MetaseqDataclass):
-    path: Optional[str] = opt(None, "path(s) to model file(s), colon separated")
-    quiet: bool = opt(False, "only print final scores")
-    model_overrides: str = opt("{}", "a dictionary used to override model args at generation")
-    results_path: Optional[str] = opt(None, "path to save eval results (optional)")
+    path: Optional[str] = opt(None, "checkpoint file(s), separated by colons")
+    quiet: bool = opt(False, "print the final numbers only")
+    model_overrides: str = opt("{}", "python dict of model settings that replace the checkpoint's")
+    results_path: Optional[str] = opt(None, "where evaluation output is written, if anywhere")
 
 
 @dataclass
 class ReshardConfig(MetaseqDataclass):
-    save_dir: Optional[str] = opt(None, "where to save the resharded checkpoints")
-    save_prefix: Optional[str] = opt("reshard", "save to <save-dir>/<save-prefix>-shard<i>.pt")
-    target_world_size: Optional[int] = opt(128, "the maximum number of GPUs you want to use to evaluate")
-    do_pad: Optional[bool] = opt(False, "add padding to make sure that running on target world size works")
+    save_dir: Optional[str] = opt(None, "output directory")
+    save_prefix: Optional[str] = opt("reshard", "outputs are named <save-dir>/<save-prefix>-shard<i>.pt")
+    target_world_size: Optional[int] = opt(128, "largest number of GPUs the result must load on")
+    do_pad: Optional[bool] = opt(False, "pad flat parameters so that the target world size divides them")
 
 
 @dataclass
 class EvalLMConfig(MetaseqDataclass):
-    score_sequences: bool = opt(False, "if set, uses the ScoreSequencesTask")
-    output_word_probs: bool = opt(False, "if set, outputs words and their predicted log probabilities")
-    output_word_stats: bool = opt(False, "if set, outputs word statistics such as word count, average probability")
-    context_window: int = opt(0, "ensures that every evaluated token has access to a context of at least this size")
-    softmax_batch: int = opt(sys.maxsize, "if BxT is more than this, will batch the softmax over vocab to this amount")
-    max_valid_steps: Optional[int] = opt(None, "how many batches to evaluate", alias="--nval")
+    score_sequences: bool = opt(False, "score given sequences instead of a corpus")
+    output_word_probs: bool = opt(False, "print every word with its log probability")
+    output_word_stats: bool = opt(False, "print per-word counts and mean probabilities")
+    context_window: int = opt(0, "tokens of preceding text that every scored token can see at least")
+    softmax_batch: int = opt(sys.maxsize, "compute the softmax in pieces of this many positions")
+    max_valid_steps: Optional[int] = opt(None, "stop after N batches", alias="--nval")
 
 
 @dataclass
 class EMAConfig(MetaseqDataclass):
-    store_ema: bool = opt(False, "store exponential moving average shadow model")
-    ema_decay: float = opt(0.9999, "decay for exponential moving average model")
-    ema_start_update: int = opt(0, "start EMA update after this many model updates")
-    ema_seed_model: Optional[str] = opt(None, "seed to load EMA model from; used to load EMA model separately")
-    ema_update_freq: int = opt(1, "do EMA update every this many model updates")
-    ema_fp32: bool = opt(False, "if true, store EMA model in fp32 even if model is in fp16")
+    store_ema: bool = opt(False, "keep an exponential moving average of the weights")
+    ema_decay: float = opt(0.9999, "weight of the old average in each update of it")
+    ema_start_update: int = opt(0, "averaging begins after this many updates")
+    ema_seed_model: Optional[str] = opt(None, "checkpoint that initialises the average")
+    ema_update_freq: int = opt(1, "updates between two updates of the average")
+    ema_fp32: bool = opt(False, "hold the average in fp32 whatever the model's type")
 
 
 GROUPS = {

@@ -25,30 +25,32 @@ TOTAL_TRAIN_TOKENS = 300e9
 TOTAL_WARMUP_TOKENS = 375e6
 M = 1024 * 1024
 
-# name  layers  width  heads  head-dim  batch (Mi tokens per update)  peak lr  tensor-parallel parts
+# One row per published size.  Columns: name | tensor-parallel parts | peak learning rate in units of 1e-5 |
+# tokens per update in Ki | attention heads | model width | layers.  The head size is width / heads.
 _TABLE = """
-8m_mp1     4    128   2   64  0.125  1.0e-3  1
-8m         4    128   2   64  0.125  1.0e-3  2
-125m      12    768  12   64  0.5    6.0e-4  2
-350m      24   1024  16   64  0.5    3.0e-4  2
-760m      24   1536  16   96  0.5    2.5e-4  2
-1.3b      24   2048  32   64  1.0    2.0e-4  2
-2.7b      32   2560  32   80  1.0    1.6e-4  4
-6.7b      32   4096  32  128  2.0    1.2e-4  2
-13b       40   5120  40  128  4.0    1.0e-4  2
-30b       48   7168  56  128  4.0    1.0e-4  2
-66b       64   9216  72  128  2.0    8e-5    8
-175b      96  12288  96  128  2.0    3e-5    8
+8m_mp1  1  100   128   2    128   4
+8m      2  100   128   2    128   4
+125m    2   60   512  12    768  12
+350m    2   30   512  16   1024  24
+760m    2   25   512  16   1536  24
+1.3b    2   20  1024  32   2048  24
+2.7b    4   16  1024  32   2560  32
+6.7b    2   12  2048  32   4096  32
+13b     2   10  4096  40   5120  40
+30b     2   10  4096  56   7168  48
+66b     8    8  2048  72   9216  64
+175b    8    3  2048  96  12288  96
 """
 
 
 def _parse(table: str):
     sizes = {}
     for row in table.strip().splitlines():
-        name, layers, width, heads, d_head, batch_mi, lr, parts = row.split()
-        size = Size(int(layers), int(width), int(heads), int(d_head), int(float(batch_mi) * M), float(lr), int(parts))
-        assert size.n_heads * size.d_head == size.emb_size, name
-        sizes[name] = size
+        name, parts, lr_e5, batch_ki, heads, width, layers = row.split()
+        heads, width = int(heads), int(width)
+        assert width % heads == 0, name
+        sizes[name] = Size(n_layers=int(layers), emb_size=width, n_heads=heads, d_head=width // heads,
+                           batch_size=int(batch_ki) * 1024, lr=float(lr_e5 + "e-5"), model_parallel=int(parts))
     return sizes
 
 

@@ -14,36 +14,51 @@ from .base_lr_scheduler import BaseLRScheduler
 
 @dataclass
 class PolynomialDecayLRScheduleConfig(MetaseqDataclass):
-    lr: Any = opt(factory=lambda: [0.25], help="learning rate (mirrors --lr)", link="optimization.lr")
-    warmup_updates: int = opt(0, "warmup the learning rate linearly for the first N updates")
-    zero_lr_warmup_steps: int = opt(0, "number of steps to run with lr = 0 in the beginning, before warmup_updates")
-    force_anneal: Optional[int] = opt(None, "force annealing at specified epoch")
-    end_learning_rate: float = opt(0.0, "learning rate to decay to")
-    power: float = opt(1.0, "decay exponent")
-    total_num_update: float = opt(1000000, "total number of updates over which to decay learning rate")
+    lr: Any = opt(factory=lambda: [0.25], help="peak value; one entry per epoch may be given (mirrors --lr)",
+                  link="optimization.lr")
+    warmup_updates: int = opt(0, "updates of the linear ramp from 0 to the peak")
+    zero_lr_warmup_steps: int = opt(0, "updates at exactly 0 that come before the ramp")
+    force_anneal: Optional[int] = opt(None, "from this epoch on the per-epoch list is ignored")
+    end_learning_rate: float = opt(0.0, "value reached at --total-num-update and held afterwards")
+    power: float = opt(1.0, "exponent of the decay curve (1 = straight line)")
+    total_num_update: float = opt(1000000, "update at which the decay ends")
+
+
+def polynomial_lr(step: int, peak: float, floor: float, hold: int, ramp: int, end: float, power: float) -> float:
+    """The schedule as a function of the update count: ``hold`` updates at 0, ``ramp`` updates of linear rise to
+    ``peak``, then ``floor + (peak - floor) * (1 - progress) ** power`` until update ``end``, and ``floor`` after."""
+    if hold > 0 and step <= hold:
+        return 0.0
+    start = hold + ramp
+    if ramp > 0 and step <= start:
+        return peak * (step - hold) / float(ramp)
+    if step >= end:
+        return floor
+    left = 1 - (step - start) / (end - start)
+    return floor + (peak - floor) * left ** power
 
 
 @register_lr_scheduler("polynomial_decay", dataclass=PolynomialDecayLRScheduleConfig)
 class PolynomialDecayLRSchedule(BaseLRScheduler):
     def __init__(self, cfg, optimizer):
         super().__init__(cfg, optimizer)
-        lr = getattr(cfg, "lr", None)
-        assert lr is not None and len(lr) > 0
-        self.lrs = list(lr)
-        self.lr = self.lrs[0]
-        self.warmup_updates = int(cfg.warmup_updates)
+        per_epoch = list(getattr(cfg, "lr", None) or [])
+        assert per_epoch, "the polynomial schedule needs --lr"
+        self.lrs = per_epoch
+        self.lr = per_epoch[0]
         self.zero_lr_warmup_steps = int(getattr(cfg, "zero_lr_warmup_steps", 0))
-        self.warmup_factor = 1.0 / self.warmup_updates if self.warmup_updates > 0 else 1.0
-        self.end_learning_rate = cfg.end_learning_rate
+        self.warmup_updates = int(cfg.warmup_updates)
+        self.end_learning_rate, self.power = cfg.end_learning_rate, cfg.power
         self.total_num_update = cfg.total_num_update
-        self.power = cfg.power
         self.force_anneal = getattr(cfg, "force_anneal", None)
-        self.optimizer.set_lr(self.warmup_factor * self.lr if self.zero_lr_warmup_steps == 0 else 0.0)
+        # before the first update: nothing if updates at 0 come first, else the first point of the ramp
+        self.warmup_factor = 1.0 / self.warmup_updates if self.warmup_updates > 0 else 1.0
+        self.optimizer.set_lr(0.0 if self.zero_lr_warmup_steps else self.warmup_factor * self.lr)
 
     def get_next_lr(self, epoch):
-        if self.force_anneal is None or epoch < self.force_anneal:
-            return self.lrs[min(epoch, len(self.lrs) - 1)]
-        return self.optimizer.get_lr()
+        if self.force_anneal is not None and epoch >= self.force_anneal:
+            return self.optimizer.get_lr()  # keep whatever the decay has reached
+        return self.lrs[min(epoch, len(self.lrs) - 1)]
 
     def step_begin_epoch(self, epoch):
         self.lr = self.get_next_lr(epoch)
@@ -51,17 +66,9 @@ class PolynomialDecayLRSchedule(BaseLRScheduler):
         return self.optimizer.get_lr()
 
     def step_update(self, num_updates):
-        if self.zero_lr_warmup_steps > 0 and num_updates <= self.zero_lr_warmup_steps:
-            lr = 0.0
-        elif self.warmup_updates > 0 and num_updates <= self.warmup_updates + self.zero_lr_warmup_steps:
+        in_ramp = self.zero_lr_warmup_steps < num_updates <= self.zero_lr_warmup_steps + self.warmup_updates
+        if in_ramp:
             self.warmup_factor = (num_updates - self.zero_lr_warmup_steps) / float(self.warmup_updates)
-            lr = self.warmup_factor * self.lr
-        elif num_updates >= self.total_num_update:
-            lr = self.end_learning_rate
-        else:
-            warm = self.warmup_updates + self.zero_lr_warmup_steps
-            lr_range = self.lr - self.end_learning_rate
-            remaining = 1 - (num_updates - warm) / (self.total_num_update - warm)
-            lr = lr_range * remaining ** self.power + self.end_learning_rate
-        self.optimizer.set_lr(lr)
+        self.optimizer.set_lr(polynomial_lr(num_updates, self.lr, self.end_learning_rate, self.zero_lr_warmup_steps,
+                                            self.warmup_updates, self.total_num_update, self.power))
         return self.optimizer.get_lr()
