@@ -130,32 +130,30 @@ class StreamingCountingIterator:
         return self._itr.has_next()
 
 
+def _abstract(name: str, doc: str):
+    def method(self, *args, **kwargs):
+        raise NotImplementedError(f"{type(self).__name__}.{name}")
+
+    method.__name__, method.__doc__ = name, doc
+    return method
+
+
 class EpochBatchIterating:
-    def __len__(self) -> int:
-        raise NotImplementedError
+    """What the trainer needs of an iterator that spans epochs."""
 
-    @property
-    def next_epoch_idx(self):
-        raise NotImplementedError
-
-    def next_epoch_itr(self, shuffle=True, fix_batches_to_gpus=False, set_dataset_epoch=True):
-        raise NotImplementedError
-
-    def end_of_epoch(self) -> bool:
-        raise NotImplementedError
-
-    @property
-    def iterations_in_epoch(self) -> int:
-        raise NotImplementedError
-
-    def state_dict(self):
-        raise NotImplementedError
-
-    def load_state_dict(self, state_dict):
-        raise NotImplementedError
+    __len__ = _abstract("__len__", "Batches per epoch.")
+    next_epoch_itr = _abstract(
+        "next_epoch_itr", "The iterator of the next epoch: (shuffle=True, fix_batches_to_gpus=False, "
+        "set_dataset_epoch=True).")
+    end_of_epoch = _abstract("end_of_epoch", "True once the current epoch's iterator is used up.")
+    state_dict = _abstract("state_dict", "Position to resume from.")
+    load_state_dict = _abstract("load_state_dict", "Moves to a saved position.")
+    next_epoch_idx = property(_abstract("next_epoch_idx", "Number of the epoch that next_epoch_itr will start."))
+    iterations_in_epoch = property(_abstract("iterations_in_epoch", "Batches consumed in the current epoch."))
 
     @property
     def first_batch(self):
+        """A batch usable as a stand-in on ranks that run dry (or the string DUMMY when none can be made here)."""
         return "DUMMY"
 
 
@@ -310,23 +308,17 @@ class EpochBatchIterator(EpochBatchIterating):
     def __init__(self, dataset, collate_fn, batch_sampler, seed=1, num_shards=1, shard_id=0, num_workers=0, epoch=1,
                  buffer_size=0, timeout=0, disable_shuffling=False, skip_remainder_batch=False):
         assert isinstance(dataset, torch.utils.data.Dataset)
-        self.dataset = dataset
-        self.collate_fn = collate_fn
-        self.batch_sampler = batch_sampler
-        self._frozen_batches = tuple(batch_sampler) if not callable(batch_sampler) else None
-        self.seed = seed
-        self.num_shards = num_shards
-        self.shard_id = shard_id
-        self.num_workers = num_workers
-        self.buffer_size = min(buffer_size, 20)
-        self.timeout = timeout
-        self.disable_shuffling = disable_shuffling
+        self.dataset, self.collate_fn, self.batch_sampler = dataset, collate_fn, batch_sampler
+        # a callable sampler is asked per epoch (lazily); a list of batches is fixed for good
+        self._frozen_batches = None if callable(batch_sampler) else tuple(batch_sampler)
+        self.seed, self.epoch = seed, max(epoch, 1)
+        self.num_shards, self.shard_id = num_shards, shard_id
+        self.num_workers, self.timeout = num_workers, timeout
+        self.buffer_size = min(buffer_size, 20)  # more prefetched batches only cost memory
+        self.disable_shuffling, self.shuffle = disable_shuffling, not disable_shuffling
         self.skip_remainder_batch = skip_remainder_batch
-        self.epoch = max(epoch, 1)
-        self.shuffle = not disable_shuffling
-        self._cur_epoch_itr = None
-        self._next_epoch_itr = None
         self._supports_prefetch = getattr(dataset, "supports_prefetch", False)
+        self._cur_epoch_itr = self._next_epoch_itr = None
 
     @property
     def frozen_batches(self):
@@ -511,19 +503,17 @@ _BackgroundConsumer = BackgroundConsumer
 
 
 class BufferedIterator:
-    """Prefetches up to ``size`` elements on a background thread."""
+    """Keeps up to ``size`` elements of ``iterable`` ready, produced by a background thread that starts with the
+    first ``next``.  Complains (at debug level, at most every 15 minutes) when the buffer runs nearly empty after
+    the first five minutes: a sign that data loading is the bottleneck."""
+
+    _GRACE_S, _REPEAT_S = 5 * 60, 15 * 60
 
     def __init__(self, size: int, iterable):
         self._queue = queue.Queue(size)
-        self._iterable = iterable
+        self._iterable, self.total = iterable, len(iterable)
         self._consumer = None
-        self.start_time = time.time()
-        self.warning_time = None
-        self.total = len(iterable)
-
-    def _start(self):
-        self._consumer = BackgroundConsumer(self._queue, self._iterable, self.total)
-        self._consumer.start()
+        self.start_time, self.warning_time = time.time(), None
 
     def __iter__(self):
         return self
@@ -532,23 +522,30 @@ class BufferedIterator:
         return self.total
 
     def take(self, n):
+        """Ends the stream after ``n`` elements (also told to the source, if it can do the same)."""
         self.total = min(self.total, n)
-        if hasattr(self._iterable, "take"):
-            self._iterable.take(n)
+        inner = getattr(self._iterable, "take", None)
+        if inner is not None:
+            inner(n)
         return self
+
+    def _note_starvation(self):
+        now = time.time()
+        low = self._queue.qsize() < min(2, max(1, self._queue.maxsize // 2))
+        if low and now - self.start_time > self._GRACE_S and \
+                (self.warning_time is None or now - self.warning_time > self._REPEAT_S):
+            logger.debug("Data loading buffer is empty or nearly empty. This may indicate a data loading "
+                         "bottleneck; increasing the number of workers (--num-workers) may help.")
+            self.warning_time = now
 
     def __next__(self):
         if self._consumer is None:
-            self._start()
-        if self._queue.qsize() < min(2, max(1, self._queue.maxsize // 2)):
-            if time.time() - self.start_time > 5 * 60:
-                if self.warning_time is None or time.time() - self.warning_time > 15 * 60:
-                    logger.debug("Data loading buffer is empty or nearly empty. This may indicate a data loading "
-                                 "bottleneck; increasing the number of workers (--num-workers) may help.")
-                    self.warning_time = time.time()
+            self._consumer = BackgroundConsumer(self._queue, self._iterable, self.total)
+            self._consumer.start()
+        self._note_starvation()
         item = self._queue.get(True)
-        if isinstance(item, Exception):
-            raise item
         if item is _SENTINEL:
             raise StopIteration()
+        if isinstance(item, Exception):
+            raise item
         return item

@@ -393,51 +393,38 @@ class Trainer:
         return extra_state
 
     # ------------------------------------------------------------------- data
+    def _batch_iterator(self, split: str, *, training: bool, epoch: int, sharded: bool, disable_iterator_cache: bool):
+        """The task's batch iterator for a split, with the batching limits of training or of validation.  Its first
+        batch becomes the stand-in that a rank trains on (with zero weight) when it runs out of data early."""
+        d = self.cfg.dataset
+        limits = [self.task.max_positions(), self.model.max_positions()] + ([d.max_tokens] if training else [])
+        itr = self.task.get_batch_iterator(
+            dataset=self.task.dataset(split), epoch=epoch, seed=self.cfg.common.seed,
+            max_tokens=d.max_tokens if training else d.max_tokens_valid,
+            max_sentences=d.batch_size if training else d.batch_size_valid,
+            max_positions=utils_resolve_max_positions(*limits),
+            ignore_invalid_inputs=True if training else d.skip_invalid_size_inputs_valid_test,
+            required_batch_size_multiple=d.required_batch_size_multiple,
+            num_shards=self.data_parallel_world_size if sharded else 1,
+            shard_id=self.data_parallel_rank if sharded else 0,
+            num_workers=d.num_workers if training else d.num_workers_valid,
+            data_buffer_size=d.data_buffer_size, disable_iterator_cache=disable_iterator_cache,
+            skip_remainder_batch=training)
+        self.reset_dummy_batch(itr.first_batch)
+        return itr
+
     def get_train_iterator(self, epoch, combine=True, load_dataset=True, data_selector=None, shard_batch_itr=True,
                            disable_iterator_cache=False):
+        split = self.cfg.dataset.train_subset
         if load_dataset:
             logger.info(f"loading train data for epoch {epoch}")
-            self.task.load_dataset(self.cfg.dataset.train_subset, epoch=epoch, combine=combine,
-                                   data_selector=data_selector)
-        batch_iterator = self.task.get_batch_iterator(
-            dataset=self.task.dataset(self.cfg.dataset.train_subset),
-            max_tokens=self.cfg.dataset.max_tokens,
-            max_sentences=self.cfg.dataset.batch_size,
-            max_positions=utils_resolve_max_positions(self.task.max_positions(), self.model.max_positions(),
-                                                      self.cfg.dataset.max_tokens),
-            ignore_invalid_inputs=True,
-            required_batch_size_multiple=self.cfg.dataset.required_batch_size_multiple,
-            seed=self.cfg.common.seed,
-            num_shards=self.data_parallel_world_size if shard_batch_itr else 1,
-            shard_id=self.data_parallel_rank if shard_batch_itr else 0,
-            num_workers=self.cfg.dataset.num_workers,
-            epoch=epoch,
-            data_buffer_size=self.cfg.dataset.data_buffer_size,
-            disable_iterator_cache=disable_iterator_cache,
-            skip_remainder_batch=True,
-        )
-        self.reset_dummy_batch(batch_iterator.first_batch)
-        return batch_iterator
+            self.task.load_dataset(split, epoch=epoch, combine=combine, data_selector=data_selector)
+        return self._batch_iterator(split, training=True, epoch=epoch, sharded=shard_batch_itr,
+                                    disable_iterator_cache=disable_iterator_cache)
 
     def get_valid_iterator(self, subset, disable_iterator_cache=False):
-        batch_iterator = self.task.get_batch_iterator(
-            dataset=self.task.dataset(subset),
-            max_tokens=self.cfg.dataset.max_tokens_valid,
-            max_sentences=self.cfg.dataset.batch_size_valid,
-            max_positions=utils_resolve_max_positions(self.task.max_positions(), self.model.max_positions()),
-            ignore_invalid_inputs=self.cfg.dataset.skip_invalid_size_inputs_valid_test,
-            required_batch_size_multiple=self.cfg.dataset.required_batch_size_multiple,
-            seed=self.cfg.common.seed,
-            num_shards=self.data_parallel_world_size,
-            shard_id=self.data_parallel_rank,
-            num_workers=self.cfg.dataset.num_workers_valid,
-            epoch=1,
-            data_buffer_size=self.cfg.dataset.data_buffer_size,
-            disable_iterator_cache=disable_iterator_cache,
-            skip_remainder_batch=False,
-        )
-        self.reset_dummy_batch(batch_iterator.first_batch)
-        return batch_iterator
+        return self._batch_iterator(subset, training=False, epoch=1, sharded=True,
+                                    disable_iterator_cache=disable_iterator_cache)
 
     def begin_epoch(self, epoch):
         logger.info(f"begin training epoch {epoch}")
@@ -620,35 +607,28 @@ class Trainer:
             self.model.zero_grad()
 
     # ------------------------------------------------------------ lr / updates
+    def _publish_lr(self, value):
+        """Logs what the schedule returned (one number, or one per parameter group) and gives back the headline
+        value."""
+        if not isinstance(value, dict):
+            metrics.log_scalar("lr", value, weight=0, priority=300)
+            return value
+        for group, lr in value.items():
+            metrics.log_scalar(f"lr_{group}", lr, weight=0, priority=300)
+        return value["default"] if "default" in value else next(iter(value.values()))
+
+    def lr_step_update(self):
+        """Moves the schedule to the current update count."""
+        return self._publish_lr(self.lr_scheduler.step_update(self._num_updates))
+
     def lr_step_begin_epoch(self, epoch):
         self.lr_scheduler.step_begin_epoch(epoch)
         return self.lr_step_update()
 
     def lr_step(self, epoch, val_loss=None):
+        """End of an epoch (and of its validation)."""
         self.lr_scheduler.step(epoch, val_loss)
         return self.lr_step_update()
-
-    def lr_step_update(self):
-        new_lr = self.lr_scheduler.step_update(self.get_num_updates())
-        if isinstance(new_lr, dict):
-            for k, v in new_lr.items():
-                metrics.log_scalar(f"lr_{k}", v, weight=0, priority=300)
-            new_lr = new_lr.get("default", next(iter(new_lr.values())))
-        else:
-            metrics.log_scalar("lr", new_lr, weight=0, priority=300)
-        return new_lr
-
-    def get_lr(self):
-        return self.optimizer.get_lr()
-
-    def get_model(self):
-        return self._model
-
-    def get_criterion(self):
-        return self._criterion
-
-    def get_meter(self, name):
-        return metrics.get_meter("train", name)
 
     def get_num_updates(self):
         return self._num_updates
@@ -656,7 +636,20 @@ class Trainer:
     def set_num_updates(self, num_updates):
         self._num_updates = num_updates
         self.lr_step_update()
-        metrics.log_scalar("num_updates", self._num_updates, weight=0, priority=200)
+        metrics.log_scalar("num_updates", num_updates, weight=0, priority=200)
+
+    def get_lr(self):
+        return self.optimizer.get_lr()
+
+    def get_meter(self, name):
+        return metrics.get_meter("train", name)
+
+    def get_model(self):
+        """The model without its data-parallel wrapper."""
+        return self._model
+
+    def get_criterion(self):
+        return self._criterion
 
     def clip_grad_norm(self, clip_norm, clip_norm_type="l2", skip_gradient_update_on_clip_norm=False):
         if self.optimizer.__class__.__name__ in ("MemoryEfficientFP16Optimizer", "FP16Optimizer"):
