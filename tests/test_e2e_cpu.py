@@ -246,3 +246,41 @@ def test_fixed_prompt_generation_benchmark_runs_from_a_checkpoint_directory(trai
     seconds = gb.generation_statistics(str(tmp_path), prompts=["the quick brown fox"] * 8, cpu=True)
     out = capsys.readouterr().out
     assert seconds > 0 and "Total generation time" in out and "Words per second" in out
+
+
+def test_checkpoints_move_to_a_shared_directory_and_a_restart_resumes_from_there(tmp_path):
+    """``--cloud-upload-path nfs:<dir>``: every finished checkpoint ends up in ``<dir>/checkpoint_N/`` under a name
+    without the step, the local copy goes away, and a second launch with an empty save directory continues from the
+    newest complete directory instead of starting over."""
+    vocab, merges = _write_tokenizer(tmp_path)
+    data = tmp_path / "data"
+    _write_shards(data, n_shards=1, docs=60)
+    shared = tmp_path / "shared"
+    shared.mkdir()
+
+    def run(save, max_update):
+        log = _run([sys.executable, "-m", "metaseq_b200.cli.train", str(data), "--task", "streaming_language_modeling",
+                    "--vocab-filename", vocab, "--merges-filename", merges, "--tokens-per-sample", "16",
+                    "--sample-break-mode", "none", "--batch-size", "2", "--arch", "transformer_lm_megatron",
+                    "--decoder-layers", "1", "--decoder-embed-dim", "32", "--decoder-ffn-embed-dim", "64",
+                    "--decoder-attention-heads", "2", "--decoder-learned-pos", "--share-decoder-input-output-embed",
+                    "--dropout", "0.0", "--attention-dropout", "0.0", "--criterion", "cross_entropy", "--optimizer",
+                    "adam", "--lr", "3e-3", "--lr-scheduler", "polynomial_decay", "--warmup-updates", "2",
+                    "--total-num-update", "40", "--max-update", str(max_update), "--cpu", "--distributed-world-size",
+                    "1", "--log-format", "json", "--log-interval", "1", "--save-dir", str(save),
+                    "--save-interval-updates", "4", "--disable-validation", "--seed", "3", "--num-workers", "0",
+                    "--cloud-upload-path", f"nfs:{shared}"])
+        return sorted(int(json.loads(line[line.find('{"epoch"'):])["num_updates"]) for line in log.splitlines()
+                      if '{"epoch"' in line and '"num_updates"' in line and '"train_loss"' not in line)
+
+    first = run(tmp_path / "run1", 8)
+    assert first == list(range(1, 9))
+    dirs = sorted(p.name for p in shared.iterdir())
+    assert "checkpoint_4" in dirs and "checkpoint_8" in dirs, dirs
+    assert [p.name for p in (shared / "checkpoint_8").iterdir()] == ["checkpoint.pt"]
+    assert not [n for n in os.listdir(tmp_path / "run1") if n.startswith("checkpoint_") and n.endswith(".pt")
+                and not os.path.islink(tmp_path / "run1" / n)]
+
+    second = run(tmp_path / "run2", 12)  # a fresh node: nothing local, everything on the shared directory
+    assert second == list(range(9, 13)), second
+    assert (shared / "checkpoint_12" / "checkpoint.pt").exists()
