@@ -274,3 +274,24 @@ def test_async_sharded_save_then_reshard_to_fewer_model_parts_and_reload(tmp_pat
                 break
     assert first is not None, out.stdout[-2000:]
     assert first == pytest.approx(cont[4][0], abs=5e-3)
+
+
+def test_sharded_checkpoints_on_a_shared_directory_resume_only_from_a_complete_set(tmp_path):
+    """Two data-parallel ranks with sharded state and ``--cloud-upload-path nfs:<dir>``: every rank moves its own
+    shard into ``checkpoint_N/``; a restart takes the newest directory that holds one finished file per rank, and an
+    incomplete newer directory (a rank died mid-copy) is passed over."""
+    shared = tmp_path / "shared"
+    shared.mkdir()
+    extra = ["--save-interval-updates", "2", "--cloud-upload-path", f"nfs:{shared}"]
+    losses, _ = run_train(tmp_path / "a", 2, 4, extra)
+    assert sorted(losses) == [1, 2, 3, 4]
+    names = sorted(p.name for p in (shared / "checkpoint_4").iterdir())
+    assert names == ["checkpoint-model_part-0-shard0.pt", "checkpoint-model_part-0-shard1.pt"], names
+    # a newer checkpoint with one part still being copied must not be chosen
+    broken = shared / "checkpoint_6"
+    broken.mkdir()
+    (broken / "checkpoint-model_part-0-shard0.pt").write_bytes(b"partial set")
+    (broken / "_checkpoint-model_part-0-shard1.pt").write_bytes(b"in flight")
+    resumed, log = run_train(tmp_path / "b", 2, 6, extra)
+    assert sorted(resumed) == [5, 6], (sorted(resumed), log[-1500:])
+    assert "skipping checkpoint checkpoint_6" in log
