@@ -394,14 +394,18 @@ def load_checkpoint(cfg, trainer, **passthrough_args):
         # package that is not public; here the transfers go through azcopy, as the uploads do)
         local = os.path.join(ckpt.save_dir, f"checkpoint_last{suffix}.pt")
         explicit = ckpt.restore_file != default_restore_file
-        if (not explicit and ckpt.finetune_from_model is None) or requeued:
-            if download_recent_ckpt(upload, local, suffix + ".pt"):
+        try:
+            if (not explicit and ckpt.finetune_from_model is None) or requeued:
+                if download_recent_ckpt(upload, local, suffix + ".pt"):
+                    checkpoint_path = local
+            elif explicit and "windows.net" in ckpt.restore_file:
+                download_specific_ckpt(ckpt.restore_file.replace(".pt", suffix + ".pt"), local)
                 checkpoint_path = local
-        elif explicit and "windows.net" in ckpt.restore_file:
-            download_specific_ckpt(ckpt.restore_file.replace(".pt", suffix + ".pt"), local)
-            checkpoint_path = local
-        else:
-            logger.info(f"Using checkpoint {checkpoint_path} even while uploading to blob storage")
+            else:
+                logger.info(f"Using checkpoint {checkpoint_path} even while uploading to blob storage")
+        except FileNotFoundError:
+            logger.warning("azcopy is not installed: cannot look for earlier checkpoints in blob storage; "
+                           f"continuing with {checkpoint_path}")
     elif not upload and ckpt.restore_file != default_restore_file and requeued:
         # a requeued job that was started from an explicit file continues from its own newest checkpoint
         mine = os.path.join(ckpt.save_dir, f"checkpoint_last{suffix}.pt")
