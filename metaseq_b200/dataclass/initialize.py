@@ -91,6 +91,11 @@ def compose(overrides: Sequence[str] = (), cfg_name: str = "base_config", delete
     whatever their order on the command line; groups named in ``deletes`` are set to ``None`` first.  A group
     choice that no registry knows (a bare name, as encoders without options are) is stored as that name."""
     hydra_init(cfg_name)
+    import importlib
+
+    # importing a component package registers its members (and their dataclasses) with the store
+    for package in ("tasks", "models", "criterions", "optim", "optim.lr_scheduler", "data.encoders"):
+        importlib.import_module("metaseq_b200." + package)
     cs = ConfigStore.instance()
     cfg = cs.load(cfg_name)
     overrides = list(overrides)
