@@ -77,6 +77,19 @@ def checkpoint_wrapper(module: nn.Module, offload_to_cpu: bool = False,
     return module
 
 
+def checkpoint(fn, owner: nn.Module, *args, offload_to_cpu: bool = False,
+               distribute_checkpointed_activations: bool = False, **kwargs):
+    """Functional form: ``fn(*args, **kwargs)`` with only its tensor arguments kept for backward, where ``fn`` is
+    run again.  ``owner`` is the module whose parameters ``fn`` reads (it decides whether anything needs a gradient)."""
+    shim = _Shim()
+    shim._checkpoint_orig_forward, shim.parameters = fn, owner.parameters
+    return _checkpointed_forward(shim, offload_to_cpu, distribute_checkpointed_activations, *args, **kwargs)
+
+
+class _Shim:
+    pass
+
+
 def _checkpointed_forward(module, offload_to_cpu, distribute, *args, **kwargs):
     flat_kwargs_keys = list(kwargs.keys())
     flat = list(args) + [kwargs[k] for k in flat_kwargs_keys]

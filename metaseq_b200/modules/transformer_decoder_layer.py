@@ -76,6 +76,8 @@ class ModelParallelTransformerDecoderLayer(nn.Module):
                                   dtype, disable_bias=disable_bias, truncate_init=truncate)
         self.final_layer_norm = LayerNorm(self.embed_dim, elementwise_affine=affine)
         self.checkpoint_activations = bool(_get(args, "checkpoint_activations", False))
+        self.offload_activations = bool(_get(args, "offload_activations", False))
+        self.distribute_checkpointed_activations = bool(_get(args, "distribute_checkpointed_activations", False))
         self.use_fused_layer = not bool(_get(args, "no_fused_layer", False))
         self.tp_comm = None  # set by the trainer when fused tensor-parallel communication is on
 
@@ -196,6 +198,14 @@ class ModelParallelTransformerDecoderLayer(nn.Module):
         # the library ops of the modular path do not poll arrival flags: wait for the matrices here
         for w in (self.self_attn.qkv_proj.weight, self.self_attn.out_proj.weight, self.fc1.weight, self.fc2.weight):
             ops_f.ensure_operand_ready(w)
+        if self.checkpoint_activations and self.training and incremental_state is None and torch.is_grad_enabled():
+            # the modular path keeps only the layer input and recomputes the rest in backward, as the fused path
+            # does inside its own backward
+            from .checkpoint_activations import checkpoint
+
+            return checkpoint(self._modular_forward, self, x, bt, None, self_attn_padding_mask, self_attn_mask,
+                              offload_to_cpu=self.offload_activations,
+                              distribute_checkpointed_activations=self.distribute_checkpointed_activations)
         return self._modular_forward(x, bt, incremental_state, self_attn_padding_mask, self_attn_mask)
 
     def _modular_forward(self, x, bt, incremental_state, key_padding_mask, attn_mask):

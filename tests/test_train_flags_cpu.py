@@ -17,6 +17,7 @@ VARIANTS = {
     "fp16_master_weights": POLY + ["--fp16", "--fp16-init-scale", "4"],
     "memory_efficient_fp16": POLY + ["--memory-efficient-fp16", "--fp16-init-scale", "4"],
     "activation_checkpointing": POLY + ["--checkpoint-activations"],
+    "activation_checkpointing_modular_layer": POLY + ["--checkpoint-activations", "--no-fused-layer", "--dropout", "0.1"],
     "sgd": POLY + ["--optimizer", "sgd", "--momentum", "0.9"],
     "cosine": ["--lr-scheduler", "cosine", "--max-lr", "1e-2", "--lr-period-updates", "10", "--warmup-updates", "1"],
     "inverse_sqrt": ["--lr-scheduler", "inverse_sqrt", "--warmup-init-lr", "1e-4", "--warmup-updates", "1"],
@@ -107,3 +108,11 @@ def test_layers_grouped_into_one_sharded_unit_train_like_one_unit_per_layer(tmp_
     base = _run(tmp_path / "a", POLY + ["--ddp-backend", "fully_sharded"])
     grouped = _run(tmp_path / "b", POLY + ["--ddp-backend", "fully_sharded", "--fsdp-checkpoint-wrap-layer-frequency", "2"])
     assert grouped == pytest.approx(base, rel=1e-5)
+
+
+def test_recomputing_the_modular_layer_gives_the_losses_of_keeping_its_activations(tmp_path):
+    """With dropout on: the recomputation must replay the same masks, or the two trajectories drift apart."""
+    flags = POLY + ["--no-fused-layer", "--dropout", "0.1"]
+    kept = _run(tmp_path / "a", flags)
+    recomputed = _run(tmp_path / "b", flags + ["--checkpoint-activations"])
+    assert recomputed == pytest.approx(kept, rel=1e-5)
