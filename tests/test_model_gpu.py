@@ -266,6 +266,7 @@ GPU_VARIANTS = {
     "gelu_modular": ["--activation-fn", "gelu"],
     "bf16": ["--activation-fn", "relu", "--bf16"],
     "activation_checkpointing": ["--activation-fn", "relu", "--checkpoint-activations"],
+    "activation_checkpointing_modular": ["--activation-fn", "gelu", "--checkpoint-activations", "--dropout", "0.1"],
     "alibi": ["--activation-fn", "relu", "--alibi"],
     "document_separator_attention": ["--activation-fn", "relu", "--self-attn-doc-sep", "2"],
     "sinusoidal_positions": ["--activation-fn", "relu", "--decoder-learned-sinusoidal"],
