@@ -192,9 +192,23 @@ class ModelParallelTransformerDecoderLayer(nn.Module):
                 doc_start=self_attn_mask.doc_start if self_attn_mask is not None else None,
                 alibi_slopes=self_attn_mask.slopes if self_attn_mask is not None else None)
             ln1, ln2 = self.self_attn_layer_norm, self.final_layer_norm
-            return fused_decoder_layer(
-                x, spec, ln1.weight, ln1.bias, a.qkv_proj.weight, a.qkv_proj.bias, a.out_proj.weight, a.out_proj.bias,
-                ln2.weight, ln2.bias, self.fc1.weight, self.fc1.bias, self.fc2.weight, self.fc2.bias)
+            weights = (ln1.weight, ln1.bias, a.qkv_proj.weight, a.qkv_proj.bias, a.out_proj.weight, a.out_proj.bias,
+                       ln2.weight, ln2.bias, self.fc1.weight, self.fc1.bias, self.fc2.weight, self.fc2.bias)
+            park_input = spec.recompute and self.training and torch.is_grad_enabled() and \
+                (self.offload_activations or self.distribute_checkpointed_activations)
+            if park_input:
+                # --offload-activations / --distribute-checkpointed-activations: the one tensor that recomputation
+                # keeps (the layer input) goes to host memory or is split over the tensor-parallel ranks, and the
+                # whole layer runs again in backward (with its own activations kept that second time)
+                import dataclasses
+
+                from .checkpoint_activations import checkpoint
+
+                kept = dataclasses.replace(spec, recompute=False)
+                return checkpoint(lambda t: fused_decoder_layer(t, kept, *weights), self, x,
+                                  offload_to_cpu=self.offload_activations,
+                                  distribute_checkpointed_activations=self.distribute_checkpointed_activations)
+            return fused_decoder_layer(x, spec, *weights)
         # the library ops of the modular path do not poll arrival flags: wait for the matrices here
         for w in (self.self_attn.qkv_proj.weight, self.self_attn.out_proj.weight, self.fc1.weight, self.fc2.weight):
             ops_f.ensure_operand_ready(w)

@@ -100,3 +100,30 @@ def test_document_starts_and_alibi_reach_the_fused_layer_and_match_the_dense_mas
     for n in g0:
         torch.testing.assert_close(g1[n], g0[n], rtol=1e-4, atol=1e-6, msg=n)
     assert not torch.allclose(dx1, dx_plain, atol=1e-4)  # the masks change the result
+
+
+@pytest.mark.parametrize("dropout", [0.0, 0.2])
+def test_offloaded_layer_input_gives_the_gradients_of_plain_recomputation(dropout):
+    """``--offload-activations`` on the fused path: the layer input is parked outside and the layer runs again in
+    backward; outputs and gradients equal those of the layer's own recomputation, dropout masks included."""
+    def grads(offload):
+        torch.manual_seed(0)
+        layer = tdl.ModelParallelTransformerDecoderLayer(
+            _args(checkpoint_activations=True, offload_activations=offload, dropout=dropout)).double()
+        layer.train()
+        x = torch.randn(2, 16, 32, dtype=torch.double, requires_grad=True)
+        tdl.FORCE_FUSED_LAYER = True
+        try:
+            torch.manual_seed(7)  # the mask seeds are drawn from the host generator
+            y = layer(x)
+            y.square().sum().backward()
+        finally:
+            tdl.FORCE_FUSED_LAYER = False
+        return y.detach(), x.grad, {n: p.grad for n, p in layer.named_parameters()}
+
+    y0, dx0, g0 = grads(False)
+    y1, dx1, g1 = grads(True)
+    torch.testing.assert_close(y1, y0)
+    torch.testing.assert_close(dx1, dx0)
+    for n in g0:
+        torch.testing.assert_close(g1[n], g0[n], msg=n)
