@@ -288,9 +288,15 @@ class ModelParallelTransformerDecoder(IncrementalDecoder):
         if self.sequence_parallel:
             x = mappings.scatter_to_sequence_parallel_region(x.reshape(B * T, -1))
         inner_states: List[Optional[torch.Tensor]] = []
-        for layer in self.layers:
+        # --recompute-fc1-num-layers N: the first N layers give up their stored activations and recompute them in
+        # backward, whether or not --checkpoint-activations asks that of every layer (the reference recomputes only
+        # the first feed-forward product of those layers; the fused layer here recomputes as a whole)
+        early = int(_get(self.args, "recompute_fc1_num_layers", 0) or 0)
+        per_block = max(1, self.num_layers // max(1, len(self.layers)))
+        for idx, layer in enumerate(self.layers):
+            extra = {"recompute": True} if idx * per_block < early and self.training else {}
             x = layer(x, bt=(B, T), incremental_state=incremental_state,
-                      self_attn_padding_mask=self_attn_padding_mask, self_attn_mask=attn_mask)
+                      self_attn_padding_mask=self_attn_padding_mask, self_attn_mask=attn_mask, **extra)
         x = self.layer_norm(x)
         return x, {"inner_states": inner_states, "tok_emb": tok_emb, "positions": positions, "bt": (B, T),
                    "norm_sums": norms}

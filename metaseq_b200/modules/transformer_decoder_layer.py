@@ -212,7 +212,8 @@ class ModelParallelTransformerDecoderLayer(nn.Module):
         # the library ops of the modular path do not poll arrival flags: wait for the matrices here
         for w in (self.self_attn.qkv_proj.weight, self.self_attn.out_proj.weight, self.fc1.weight, self.fc2.weight):
             ops_f.ensure_operand_ready(w)
-        if self.checkpoint_activations and self.training and incremental_state is None and torch.is_grad_enabled():
+        wanted = self.checkpoint_activations if recompute is None else recompute
+        if wanted and self.training and incremental_state is None and torch.is_grad_enabled():
             # the modular path keeps only the layer input and recomputes the rest in backward, as the fused path
             # does inside its own backward
             from .checkpoint_activations import checkpoint

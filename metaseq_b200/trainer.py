@@ -475,7 +475,7 @@ class Trainer:
                 return contextlib.ExitStack()
 
             try:
-                with maybe_no_sync():
+                with maybe_no_sync(), self._rank_seed(self.get_num_updates()):
                     loss, sample_size_i, logging_output = self.task.train_step(
                         sample=sample, model=self.model, criterion=self.criterion, optimizer=self.optimizer,
                         update_num=self.get_num_updates(), ignore_grad=is_dummy_batch)
@@ -539,7 +539,7 @@ class Trainer:
             logger.debug(f"[{self.get_num_updates()}] done with optimizer step")
         except FloatingPointError:
             self.zero_grad()
-            with NanDetector(self.get_model()):
+            with NanDetector(self.get_model()), self._rank_seed(self.get_num_updates()):
                 for _, sample in enumerate(samples):
                     sample, _ = self._prepare_sample(sample)
                     self.task.train_step(sample, self.model, self.criterion, self.optimizer, self.get_num_updates(),
@@ -581,7 +581,8 @@ class Trainer:
             self.zero_grad()
             sample, is_dummy_batch = self._prepare_sample(sample)
             try:
-                _loss, sample_size, logging_output = self.task.valid_step(sample, self.model, self.criterion)
+                with self._rank_seed(num_step + self.get_num_updates()):
+                    _loss, sample_size, logging_output = self.task.valid_step(sample, self.model, self.criterion)
             except RuntimeError as e:
                 if "out of memory" in str(e):
                     self._log_oom(e)
@@ -600,6 +601,13 @@ class Trainer:
         if self.data_parallel_world_size > 1:
             logging_outputs, (sample_size,) = self._aggregate_logging_outputs(logging_outputs, sample_size)
         return self._reduce_and_log_stats(logging_outputs, sample_size)
+
+    def _rank_seed(self, update: int):
+        """``--seed-per-rank``: inside the block every rank draws from its own stream, seeded from (seed, update,
+        rank); the generators are put back afterwards.  Without the flag: nothing."""
+        if getattr(self.cfg.common, "seed_per_rank", False):
+            return utils.set_rank_seed(self.cfg.common.seed, update)
+        return contextlib.nullcontext()
 
     def zero_grad(self):
         self.optimizer.zero_grad()

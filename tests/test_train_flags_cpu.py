@@ -17,6 +17,8 @@ VARIANTS = {
     "fp16_master_weights": POLY + ["--fp16", "--fp16-init-scale", "4"],
     "memory_efficient_fp16": POLY + ["--memory-efficient-fp16", "--fp16-init-scale", "4"],
     "activation_checkpointing": POLY + ["--checkpoint-activations"],
+    "seed_per_rank": POLY + ["--seed-per-rank", "--dropout", "0.1"],
+    "recompute_first_layer": POLY + ["--recompute-fc1-num-layers", "1"],
     "offloaded_checkpoints": POLY + ["--checkpoint-activations", "--offload-activations"],
     "activation_checkpointing_modular_layer": POLY + ["--checkpoint-activations", "--no-fused-layer", "--dropout", "0.1"],
     "sgd": POLY + ["--optimizer", "sgd", "--momentum", "0.9"],
