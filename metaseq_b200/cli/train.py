@@ -150,7 +150,8 @@ def train(cfg, trainer: Trainer, task, epoch_itr) -> Tuple[List[Optional[float]]
         wandb_project=cfg.common.wandb_project if dist_utils.is_master(cfg.distributed_training) else None,
         wandb_run_name=os.environ.get("WANDB_NAME", os.path.basename(cfg.checkpoint.save_dir)),
         aim_repo=cfg.common.aim_repo if dist_utils.is_master(cfg.distributed_training) else None,
-        aim_run_hash=cfg.common.aim_run_hash if dist_utils.is_master(cfg.distributed_training) else None)
+        aim_run_hash=cfg.common.aim_run_hash if dist_utils.is_master(cfg.distributed_training) else None,
+        aim_param_checkpoint_dir=cfg.checkpoint.save_dir)
     progress.update_config(_flatten_config(cfg))
     trainer.begin_epoch(epoch_itr.epoch)
     valid_subsets = cfg.dataset.valid_subset.split(",")
@@ -423,7 +424,11 @@ def validate(cfg, trainer: Trainer, task, epoch_itr, subsets: List[str]) -> List
                 itr, log_format=cfg.common.log_format, log_interval=cfg.common.log_interval, epoch=epoch_itr.epoch,
                 prefix=f"valid on '{subset}' subset",
                 tensorboard_logdir=cfg.common.tensorboard_logdir if dist_utils.is_master(cfg.distributed_training) else None,
-                wandb_project=cfg.common.wandb_project if dist_utils.is_master(cfg.distributed_training) else None)
+                wandb_project=cfg.common.wandb_project if dist_utils.is_master(cfg.distributed_training) else None,
+                wandb_run_name=os.environ.get("WANDB_NAME", os.path.basename(cfg.checkpoint.save_dir)),
+                aim_repo=cfg.common.aim_repo if dist_utils.is_master(cfg.distributed_training) else None,
+                aim_run_hash=cfg.common.aim_run_hash if dist_utils.is_master(cfg.distributed_training) else None,
+                aim_param_checkpoint_dir=cfg.checkpoint.save_dir)
             with metrics.aggregate(new_root=True) as agg:
                 for i, sample in enumerate(progress):
                     if cfg.dataset.max_valid_steps is not None and i > cfg.dataset.max_valid_steps:
