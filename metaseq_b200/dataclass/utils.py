@@ -118,12 +118,15 @@ def gen_parser_from_dataclass(parser: ArgumentParser, dataclass_instance, delete
 
     bool fields become ``store_true`` (``store_false`` when they default to True), list
     fields parse python-literal strings, ``choices`` / aliases / ``const`` come from the
-    field metadata.  Fields that mirror another group (``link``) get no flag.  A flag that
-    already exists on the parser is skipped, so several groups may share one parser.
+    field metadata.  A field that mirrors another group (``link``) gets a flag only if it has a help text of its
+    own (``--batch-size-valid`` mirrors ``--batch-size`` unless given); the flag then has no default, so that the
+    mirrored value fills it in.  A flag that already exists on the parser is skipped, so several groups may share
+    one parser.
     """
     hints = _resolved_types(type(dataclass_instance))
     for f in fields(dataclass_instance):
-        if f.name.startswith("_") or f.metadata.get("link"):
+        linked = bool(f.metadata.get("link"))
+        if f.name.startswith("_") or (linked and not f.metadata.get("help")):
             continue
         name = f.name
         flag = _flag(name) if with_prefix is None else _flag(with_prefix + "_" + name)
@@ -148,6 +151,8 @@ def gen_parser_from_dataclass(parser: ArgumentParser, dataclass_instance, delete
             if f.metadata.get("argparse_const") is not None:
                 kwargs["const"] = f.metadata["argparse_const"]
                 kwargs["nargs"] = "?"
+        if linked and tp is not bool:
+            kwargs["default"] = None
         if delete_default:
             kwargs["default"] = argparse.SUPPRESS if tp is not bool else kwargs["default"]
         names = [flag]

@@ -284,3 +284,27 @@ def test_checkpoints_move_to_a_shared_directory_and_a_restart_resumes_from_there
     second = run(tmp_path / "run2", 12)  # a fresh node: nothing local, everything on the shared directory
     assert second == list(range(9, 13)), second
     assert (shared / "checkpoint_12" / "checkpoint.pt").exists()
+
+
+def test_training_validates_on_its_interval_and_logs_under_the_subset_name(tmp_path):
+    """``--validate-interval-updates``: a validation pass over ``valid`` after every fourth update and at the end,
+    each logged as one JSON line under the logger name of the subset, with loss and perplexity."""
+    vocab, merges = _write_tokenizer(tmp_path)
+    data = tmp_path / "data"
+    _write_shards(data, n_shards=1, docs=60)
+    log = _run([sys.executable, "-m", "metaseq_b200.cli.train", str(data), "--task", "streaming_language_modeling",
+                "--vocab-filename", vocab, "--merges-filename", merges, "--tokens-per-sample", "16",
+                "--sample-break-mode", "none", "--batch-size", "2", "--arch", "transformer_lm_megatron",
+                "--decoder-layers", "1", "--decoder-embed-dim", "32", "--decoder-ffn-embed-dim", "64",
+                "--decoder-attention-heads", "2", "--decoder-learned-pos", "--share-decoder-input-output-embed",
+                "--dropout", "0.0", "--attention-dropout", "0.0", "--criterion", "cross_entropy", "--optimizer", "adam",
+                "--lr", "3e-3", "--lr-scheduler", "polynomial_decay", "--warmup-updates", "2", "--total-num-update",
+                "40", "--max-update", "8", "--cpu", "--distributed-world-size", "1", "--log-format", "json",
+                "--log-interval", "1", "--save-dir", str(tmp_path / "ckpt"), "--seed", "3",
+                "--num-workers", "0", "--valid-subset", "valid", "--validate-interval-updates", "4",
+                "--batch-size-valid", "2"])
+    valid = [json.loads(line[line.find("{"):]) for line in log.splitlines() if '"valid_loss"' in line]
+    assert [int(r["valid_num_updates"]) for r in valid] == [4, 8], log[-3000:]
+    assert all(float(r["valid_loss"]) > 0 and float(r["valid_ppl"]) > 1 for r in valid)
+    assert float(valid[1]["valid_loss"]) < float(valid[0]["valid_loss"])
+    assert any("| valid |" in line for line in log.splitlines() if '"valid_loss"' in line)
