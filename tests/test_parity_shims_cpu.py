@@ -601,3 +601,59 @@ def test_dense_future_mask_matches_its_compact_form():
     assert torch.equal(docs[1], causal)
     ali = build(alibi=True).buffered_future_mask(x)
     assert ali.shape == (4, 5, 5) and torch.isinf(ali[0, 0, 1]) and ali[0, 4, 3] > ali[0, 4, 2] > ali[0, 4, 1]
+
+
+def test_base_model_takes_its_decoder_in_the_constructor_and_checks_its_type():
+    from metaseq_b200.models.base_decoder import BaseDecoder
+    from metaseq_b200.models.base_model import BaseModel, check_type
+
+    class Dec(BaseDecoder):
+        def __init__(self):
+            super().__init__(dictionary=None)
+
+        def forward(self, tokens, **kw):
+            return tokens.float().unsqueeze(-1), {"inner_states": []}
+
+        def max_positions(self):
+            return 77
+
+    class Wrapper(torch.nn.Module):  # what a sharding wrapper looks like from outside
+        def __init__(self, inner):
+            super().__init__()
+            self.unwrapped_module = inner
+
+    class MyLM(BaseModel):
+        def __init__(self, decoder):
+            super().__init__(decoder)
+
+    m = MyLM(Dec())
+    assert m.max_positions() == 77 and m.max_decoder_positions() == 77 and m.supported_targets == {"future"}
+    assert m(torch.tensor([[1, 2]]))[0].shape == (1, 2, 1)
+    assert m.eval() is m
+    check_type(Wrapper(Dec()), BaseDecoder)
+    with pytest.raises(AssertionError):
+        MyLM(torch.nn.Linear(2, 2))
+    with pytest.raises(NotImplementedError):
+        MyLM.from_pretrained("anything")
+    assert MyLM.hub_models() == {}
+
+
+def test_generator_interface_text_codec_normalises_line_ends():
+    from metaseq_b200.hub_utils import GeneratorInterface
+
+    class Tok:
+        def encode(self, text):
+            import types
+
+            assert "\r" not in text
+            return types.SimpleNamespace(ids=[ord(c) for c in text])
+
+        def decode(self, ids):
+            return "".join(chr(i) for i in ids)
+
+    gi = GeneratorInterface.__new__(GeneratorInterface)
+    import types
+
+    gi.bpe = types.SimpleNamespace(bpe=Tok())
+    ids = gi.encode_fn("a\r\nb\rc")
+    assert gi.decode_fn(ids) == "a\nb\nc"
