@@ -9,7 +9,7 @@ from torch.utils.data.dataloader import default_collate
 from .base_dataset import BaseDataset
 
 _DELEGATED_METHODS = ("num_tokens", "num_tokens_vec", "size", "ordered_indices", "attr", "prefetch",
-                      "filter_indices_by_size", "batch_by_size", "get_batch_shapes")
+                      "filter_indices_by_size", "batch_by_size")
 _DELEGATED_PROPERTIES = ("sizes", "can_reuse_epoch_itr_across_epochs")
 
 
@@ -31,6 +31,10 @@ class BaseWrapperDataset(BaseDataset):
     @property
     def supports_prefetch(self):
         return bool(getattr(self.dataset, "supports_prefetch", False))
+
+    def get_batch_shapes(self):
+        inner = getattr(self.dataset, "get_batch_shapes", None)  # the wrapped object may be a plain sequence
+        return inner() if inner is not None else None
 
     def set_epoch(self, epoch):
         super().set_epoch(epoch)

@@ -657,3 +657,117 @@ def test_generator_interface_text_codec_normalises_line_ends():
     gi.bpe = types.SimpleNamespace(bpe=Tok())
     ids = gi.encode_fn("a\r\nb\rc")
     assert gi.decode_fn(ids) == "a\nb\nc"
+
+
+def test_dataset_protocol_extras_batch_shapes_member_attributes_and_per_dataset_order():
+    from metaseq_b200.data.concat_dataset import ConcatDataset
+    from metaseq_b200.data.token_transforms import ListDataset
+
+    from metaseq_b200.data.base_dataset import BaseDataset
+
+    sizes = np.array([1, 2, 5, 2, 1, 4, 2])
+
+    class Shaped(BaseDataset):
+        def __len__(self):
+            return len(sizes)
+
+        def __getitem__(self, i):
+            return list(range(sizes[i]))
+
+        def num_tokens(self, i):
+            return int(sizes[i])
+
+        def num_tokens_vec(self, indices):
+            return sizes[indices]
+
+        def get_batch_shapes(self):
+            return [(4, 2), (None, 5)]  # up to 4 samples of <= 2 tokens, or as many of <= 5 as the token budget allows
+
+    ds = Shaped()
+    batches = ds.batch_by_size(np.argsort(sizes, kind="stable"), max_tokens=10)
+    assert sorted(i for b in batches for i in b) == list(range(len(sizes)))
+    for b in batches:
+        longest = max(sizes[i] for i in b)
+        assert (len(b) <= 4 and longest <= 2) or (len(b) <= 2 and longest <= 5)
+    assert ListDataset([1], np.array([1])).get_batch_shapes() is None
+
+    class Plain(BaseDataset):
+        def __init__(self, items, tag):
+            super().__init__()
+            self.items, self.tag = items, tag
+            self.sizes = np.array([len(x) for x in items])
+
+        def __len__(self):
+            return len(self.items)
+
+        def __getitem__(self, i):
+            return self.items[i]
+
+        def size(self, i):
+            return int(self.sizes[i])
+
+        def ordered_indices(self):
+            return np.argsort(self.sizes, kind="stable")
+
+    a, b = Plain([[1], [2, 2]], "first"), Plain([[3, 3, 3]], "second")
+    cat = ConcatDataset([a, b])
+    assert cat.attr("tag", 0) == "first" and cat.attr("tag", 2) == "second" and cat.attr("missing", 2) is None
+    per = cat.ordered_indices_per_dataset()
+    assert [p.tolist() for p in per] == [[0, 1], [2]]
+
+
+def test_service_queue_keys_hashing_and_the_blocking_worker_entry():
+    import queue
+    import threading
+
+    from metaseq_b200.service.queue import PriorityQueueRingShard
+    from metaseq_b200.service.workers import WorkItem
+
+    key = PriorityQueueRingShard.key_from_dictionary({"top_p": 0.9, "n": 1})
+    assert key == "n:1:top_p:0.9"
+    idx = PriorityQueueRingShard.get_shard_index_for_key(key, num_shards=8)
+    assert idx == PriorityQueueRingShard.get_shard_index_for_key(key, num_shards=8) and 0 <= idx < 8
+    assert PriorityQueueRingShard.get_shard_index_for_key(key, num_shards=1) == 0
+
+    batch_queue = queue.PriorityQueue()
+
+    def serve():
+        item = batch_queue.get()
+        assert item.cost == 25 + 7 and item.data["input"] == list(range(25)) and item.data["temperature"] == 0.5
+        item.return_queue.put((item.uid, {"text": "done"}))
+
+    threading.Thread(target=serve, daemon=True).start()
+    assert WorkItem.generate_worker(list(range(25)), batch_queue, temperature=0.5) == {"text": "done"}
+
+
+def test_nan_detector_watches_added_modules_and_names_the_first_bad_one(caplog):
+    from metaseq_b200.nan_detector import NanDetector
+
+    class Bad(torch.nn.Module):
+        def forward(self, x):
+            return x / 0.0
+
+    net = torch.nn.Sequential(torch.nn.Linear(4, 4), Bad())
+    extra = Bad()
+    with caplog.at_level("WARNING"):
+        with NanDetector(net, backward=False) as det:
+            det.add_hooks(extra)
+            net(torch.ones(2, 4))
+            det.reset()
+            extra(torch.ones(2, 4))
+    assert caplog.text.count("detected in output of") == 2 and "forward" in caplog.text
+
+
+def test_shared_memory_array_publishes_once_and_reattaches_after_pickling():
+    from metaseq_b200.data.plasma_utils import PlasmaArray
+
+    small = PlasmaArray(np.arange(10))
+    assert small.plasma is None and small.client is None
+    big = PlasmaArray(np.arange(400_000, dtype=np.int64))
+    assert big.plasma is not None and big.client is None
+    big.start_server()
+    name = big.client.name
+    big.start_server()
+    assert big.client.name == name
+    clone = pickle.loads(pickle.dumps(big))
+    assert clone.client.name == name and int(clone.array[-1]) == 399_999
