@@ -59,7 +59,7 @@ def main(cfg: Cfg) -> None:
     checkpoint_utils.verify_checkpoint_directory(cfg.checkpoint.save_dir)
     if dist_utils.is_master(cfg.distributed_training):
         logger.info(cfg.to_container() if isinstance(cfg, Cfg) else cfg)
-    task = tasks.setup_task(cfg.task)
+    task = _setup_task(cfg)
     model, criterion = build_model_and_criterion(cfg, task)
     n_params = sum(p.numel() for p in model.parameters())
     logger.info(f"task: {task.__class__.__name__}; model: {model.__class__.__name__}; "
@@ -227,6 +227,23 @@ def _flatten_config(cfg):
         else:
             out[k] = str(v)
     return out
+
+
+def _setup_task(cfg):
+    """The task; with ``--task-ddp-backend fully_sharded`` it is set up inside the sharding context, so that a model
+    the task itself holds (frozen: a scorer, a teacher) is sharded too, with the settings that suit a module that is
+    never updated: no fp32 master copy unless plain fp16 asks for one, fp32 gradient reduction only outside fp16
+    (reference: metaseq/cli/train.py:117-136)."""
+    d = cfg.distributed_training
+    if getattr(d, "task_ddp_backend", "none") != "fully_sharded":
+        return tasks.setup_task(cfg.task)
+    saved = (d.memory_efficient_fp16, d.fp32_reduce_scatter, getattr(d, "ddp_backend", None))
+    d.memory_efficient_fp16, d.fp32_reduce_scatter, d.ddp_backend = d.fp16, not d.fp16, "fully_sharded"
+    try:
+        with fsdp_enable_wrap(d, use_sharded_state=d.use_sharded_state):
+            return tasks.setup_task(cfg.task)
+    finally:
+        d.memory_efficient_fp16, d.fp32_reduce_scatter, d.ddp_backend = saved
 
 
 def validate_and_save(cfg, trainer: Trainer, task, epoch_itr, valid_subsets: List[str], end_of_epoch: bool,

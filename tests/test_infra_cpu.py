@@ -456,3 +456,27 @@ def test_restart_fetches_the_newest_checkpoint_of_this_rank_from_blob_storage(tm
     os.remove(local)
     checkpoint_utils.load_checkpoint(types.SimpleNamespace(checkpoint=ck), FakeTrainer())
     assert seen["path"] == str(tmp_path / "pretrained" / "model-model_part-0-shard0.pt")
+
+
+def test_task_is_set_up_inside_the_sharding_context_when_asked(monkeypatch):
+    from metaseq_b200.parallel import fsdp
+
+    seen = {}
+
+    def fake_setup(task_cfg):
+        seen["inside"] = fsdp._WRAP_KWARGS is not None
+        seen["flags"] = (d.memory_efficient_fp16, d.fp32_reduce_scatter)
+        return "task"
+
+    monkeypatch.setattr(train_cli.tasks, "setup_task", fake_setup)
+    d = types.SimpleNamespace(task_ddp_backend="fully_sharded", fp16=True, memory_efficient_fp16=False,
+                              fp32_reduce_scatter=True, use_sharded_state=True, no_reshard_after_forward=False,
+                              cpu_offload=False, bf16=False, bucket_cap_mb=25, gradient_predivide_factor=None)
+    cfg = types.SimpleNamespace(distributed_training=d, task=None,
+                                common=types.SimpleNamespace(fp16=True, memory_efficient_fp16=False, bf16=False))
+    assert train_cli._setup_task(cfg) == "task"
+    assert seen == {"inside": True, "flags": (True, False)}
+    assert (d.memory_efficient_fp16, d.fp32_reduce_scatter) == (False, True)  # put back afterwards
+    d.task_ddp_backend = "none"
+    train_cli._setup_task(cfg)
+    assert seen["inside"] is False
