@@ -23,3 +23,31 @@ from .indexed_dataset import (  # noqa: F401,E402
 )
 from .streaming_blocks import StreamingSrcTgtDataset, StreamingTokenBlockDataset  # noqa: F401,E402
 from .cm3_dataset import CausalMaskedDocumentToSequenceDataset  # noqa: F401,E402
+
+
+# Names that the reference exports at package level, resolved on first use (importing them eagerly here would pull
+# the kernel loader and the parallel layers into every ``import metaseq_b200.data``).
+_LAZY = {
+    "CountingIterator": (".iterators", "CountingIterator"),
+    "EpochBatchIterator": (".iterators", "EpochBatchIterator"),
+    "GroupedIterator": (".iterators", "GroupedIterator"),
+    "ShardedIterator": (".iterators", "ShardedIterator"),
+    "StreamingEpochBatchIterator": (".iterators", "StreamingEpochBatchIterator"),
+    "MultiplePadDataset": (".token_transforms", "MultiplePadDataset"),
+}
+
+
+def __getattr__(name):
+    try:
+        module, attr = _LAZY[name]
+    except KeyError:
+        raise AttributeError(f"module {__name__!r} has no attribute {name!r}") from None
+    import importlib
+
+    value = getattr(importlib.import_module(module, __name__), attr)
+    globals()[name] = value
+    return value
+
+
+def __dir__():
+    return sorted(list(globals()) + list(_LAZY))

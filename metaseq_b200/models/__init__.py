@@ -66,3 +66,26 @@ def register_model_architecture(model_name, arch_name):
 from .base_model import BaseModel, LanguageModel  # noqa: E402
 from .base_decoder import BaseDecoder, IncrementalDecoder  # noqa: E402
 from . import transformer_lm  # noqa: E402,F401  (registers the architectures)
+
+
+# Names that the reference exports at package level, resolved on first use (importing them eagerly here would pull
+# the kernel loader and the parallel layers into every ``import metaseq_b200.models``).
+_LAZY = {
+    "DistributedModel": (".distributed_model", "DistributedModel"),
+}
+
+
+def __getattr__(name):
+    try:
+        module, attr = _LAZY[name]
+    except KeyError:
+        raise AttributeError(f"module {__name__!r} has no attribute {name!r}") from None
+    import importlib
+
+    value = getattr(importlib.import_module(module, __name__), attr)
+    globals()[name] = value
+    return value
+
+
+def __dir__():
+    return sorted(list(globals()) + list(_LAZY))

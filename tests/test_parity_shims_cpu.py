@@ -771,3 +771,24 @@ def test_shared_memory_array_publishes_once_and_reattaches_after_pickling():
     assert big.client.name == name
     clone = pickle.loads(pickle.dumps(big))
     assert clone.client.name == name and int(clone.array[-1]) == 399_999
+
+
+def test_packages_export_the_names_that_reference_code_imports_from_them():
+    import importlib
+
+    wanted = {
+        "modules": ["ActivationFn", "Dropout", "FeedForward", "LayerNorm", "LayerNormFp32", "LearnedPositionalEmbedding",
+                    "Linear", "ModelParallelMultiheadAttention", "ModelParallelTransformerDecoderLayer",
+                    "PositionalEmbedding", "SinusoidalPositionalEmbedding", "gelu", "AdaptiveSoftmax"],
+        "data": ["CountingIterator", "EpochBatchIterator", "GroupedIterator", "ShardedIterator", "MultiplePadDataset",
+                 "Dictionary", "JsonlDataset", "MonolingualDataset", "TokenBlockDataset"],
+        "models": ["DistributedModel", "BaseModel", "BaseDecoder", "IncrementalDecoder"],
+        "optim": ["LegacyOptimizer", "shard_", "FP16Optimizer", "MemoryEfficientFP16Optimizer", "BaseOptimizer"],
+    }
+    for pkg, names in wanted.items():
+        module = importlib.import_module("metaseq_b200." + pkg)
+        for name in names:
+            assert getattr(module, name) is not None, (pkg, name)
+        assert set(names) <= set(dir(module))
+    with pytest.raises(AttributeError):
+        importlib.import_module("metaseq_b200.modules").NoSuchLayer
