@@ -792,3 +792,15 @@ def test_packages_export_the_names_that_reference_code_imports_from_them():
         assert set(names) <= set(dir(module))
     with pytest.raises(AttributeError):
         importlib.import_module("metaseq_b200.modules").NoSuchLayer
+
+
+def test_distributed_import_path_of_the_reference_resolves_to_the_parallel_package():
+    import metaseq_b200.distributed.utils as by_path
+    import metaseq_b200.parallel.utils as real
+    from metaseq_b200.distributed import FullyShardedDataParallel, ModuleProxyWrapper, fsdp_enable_wrap, fsdp_wrap  # noqa: F401
+    from metaseq_b200.distributed import utils as distributed_utils
+    from metaseq_b200.distributed.rendezvous import ComplicitStore  # noqa: F401
+    from metaseq_b200.distributed.stitch_fsdp_ckpt import consolidate_fsdp_shards, reshard_megatron_parts  # noqa: F401
+
+    assert by_path is real and distributed_utils is real
+    assert distributed_utils.get_global_world_size() == 1
