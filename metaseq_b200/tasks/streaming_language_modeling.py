@@ -65,7 +65,8 @@ class StreamingLanguageModelingConfig(MetaseqDataclass):
     cm3_num_sentinel_tokens: int = opt(512, "number of special sentinel tokens to add to the vocabulary")
     cm3_lambda_sentinel_tokens: int = opt(1, "poisson rate of the number of masked spans (cm3)")
     cm3_mode: str = opt("poisson", "how to sample the number of spans", choices=("poisson", "fixed"))
-    cm3_allow_across_eod_boundaries: bool = opt(False, "allow masked spans to cross document boundaries")
+    cm3_allow_across_eod_boundaries: bool = opt(True, "masked spans may cross document boundaries (the original objective); "
+                                                "giving the flag turns that off")
     cm3_percent_full_document_rotation: float = opt(0.0, "fraction of documents rotated as a whole")
     num_retrieved_doc: int = opt(2, "number of retrieved documents (racm3)")
     synthetic_data: int = opt(0, "if > 0, train on this many seeded synthetic documents instead of files")
