@@ -225,7 +225,7 @@ class DocumentToSequenceDataset(torch.utils.data.IterableDataset):
         source_target: documents are ``(source, target)`` pairs (fine-tuning).
     """
 
-    def __init__(self, dataset, block_size: int, break_mode: str = "none", drop_last: bool = False,
+    def __init__(self, dataset, block_size: int, break_mode: str = "none", drop_last: bool = True,
                  padding_idx: Optional[int] = None, shuffle_buffer_size: int = 1, seed: Optional[int] = None,
                  len_cache: Optional[LockingArray] = None, to_skip: Union[int, Sequence[int]] = 0,
                  permute_documents: bool = True, source_target: bool = False):

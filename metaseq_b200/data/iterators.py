@@ -306,7 +306,7 @@ class EpochBatchIterator(EpochBatchIterating):
     """Multi-epoch iterator over a map-style dataset with a precomputed batch sampler."""
 
     def __init__(self, dataset, collate_fn, batch_sampler, seed=1, num_shards=1, shard_id=0, num_workers=0, epoch=1,
-                 buffer_size=0, timeout=0, disable_shuffling=False, skip_remainder_batch=False):
+                 buffer_size=0, timeout=0, disable_shuffling=False, skip_remainder_batch=True):
         assert isinstance(dataset, torch.utils.data.Dataset)
         self.dataset, self.collate_fn, self.batch_sampler = dataset, collate_fn, batch_sampler
         # a callable sampler is asked per epoch (lazily); a list of batches is fixed for good

@@ -63,8 +63,13 @@ class ModelParallelMultiheadAttention(nn.Module):
                  use_cpu_initialization: bool = True, full_megatron_init: bool = False,
                  full_megatron_init_scalar: float = 1.0, megatron_init_sigma: Optional[float] = None,
                  num_layers: Optional[int] = None, dtype=None, device=None, sequence_parallel: bool = False,
-                 truncate_init: bool = False, max_positions: int = 2048):
+                 truncate_init: bool = False, max_positions: int = 2048, kdim: Optional[int] = None,
+                 vdim: Optional[int] = None, self_attention: bool = True, attn_variant=None, xf_attn_op=None):
         super().__init__()
+        # arguments of the reference's constructor that have one admissible value here: keys and values come from
+        # the same input as the queries, and the attention kernel is not selectable
+        assert self_attention and kdim in (None, embed_dim) and vdim in (None, embed_dim), \
+            "only self-attention over inputs of the model width is built"
         self.embed_dim = embed_dim
         self.num_heads = num_heads
         self.head_dim = embed_dim // num_heads

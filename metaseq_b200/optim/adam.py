@@ -62,7 +62,10 @@ class Adam(torch.optim.Optimizer):
     FLOAT16_MAX = 65504.0
 
     def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, use_kernels=True,
-                 use_fp16_stats=False):
+                 use_fp16_stats=False, amsgrad=False):
+        if amsgrad:
+            raise NotImplementedError("the AMSGrad variant (running maximum of the second moment) is not built; "
+                                      "the OPT recipes do not use it")
         defaults = dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
         super().__init__(params, defaults)
         self.use_kernels = use_kernels

@@ -13,8 +13,8 @@ import math
 
 
 class DynamicLossScaler:
-    def __init__(self, init_scale=2.0 ** 15, scale_factor=2.0, scale_window=2000, tolerance=0.0, threshold=None,
-                 min_loss_scale=1e-4):
+    def __init__(self, init_scale=4.0, scale_factor=2.0, scale_window=256, tolerance=0.0, threshold=None,
+                 min_loss_scale=2 ** -5):
         self.loss_scale = init_scale
         self.scale_factor = scale_factor
         self.scale_window = scale_window
