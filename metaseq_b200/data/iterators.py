@@ -438,7 +438,7 @@ class EpochBatchIterator(EpochBatchIterating):
 class GroupedIterator(CountingIterator):
     """Yields lists of ``chunk_size`` consecutive elements (gradient accumulation groups)."""
 
-    def __init__(self, iterable, chunk_size: int, skip_remainder_batch: bool = False):
+    def __init__(self, iterable, chunk_size: int, skip_remainder_batch: bool = True):
         if skip_remainder_batch:
             total = int(math.floor(len(iterable) / float(chunk_size)))
         else:

@@ -9,7 +9,7 @@ import torch
 
 class PartitionedStreamingDataset(torch.utils.data.IterableDataset):
     def __init__(self, dataset: torch.utils.data.IterableDataset, num_shards: int, shard_id: int,
-                 drop_last: bool = False):
+                 drop_last: bool = True):
         super().__init__()
         self.dataset = dataset
         self.num_shards = num_shards

@@ -22,8 +22,11 @@ class SGDConfig(MetaseqDataclass):
 
 
 class SGDW(torch.optim.Optimizer):
-    def __init__(self, params, lr=1e-3, momentum=0.0, weight_decay=0.0):
-        super().__init__(params, dict(lr=lr, momentum=momentum, weight_decay=weight_decay))
+    def __init__(self, params, lr=1e-3, momentum=0.0, dampening=0, weight_decay=0.0, nesterov=False):
+        if nesterov and (momentum <= 0 or dampening != 0):
+            raise ValueError("Nesterov momentum requires a momentum and zero dampening")
+        super().__init__(params, dict(lr=lr, momentum=momentum, dampening=dampening, weight_decay=weight_decay,
+                                      nesterov=nesterov))
 
     @property
     def supports_memory_efficient_fp16(self):
@@ -53,8 +56,8 @@ class SGDW(torch.optim.Optimizer):
                     if buf is None:
                         buf = st["momentum_buffer"] = g.clone()
                     else:
-                        buf.mul_(group["momentum"]).add_(g)
-                    g = buf
+                        buf.mul_(group["momentum"]).add_(g, alpha=1 - group.get("dampening", 0))
+                    g = g.add(buf, alpha=group["momentum"]) if group.get("nesterov", False) else buf
                 p32.add_(g, alpha=-group["lr"])
                 if p.dtype != torch.float32:
                     p.data.copy_(p32)

@@ -60,7 +60,7 @@ class VocabParallelEmbedding(nn.Module):
     outside this rank's range contribute zero and the partial results are all-reduced."""
 
     def __init__(self, num_embeddings: int, embedding_dim: int, padding_idx: Optional[int] = None,
-                 init_method: Callable = nn.init.xavier_normal_, use_cpu_initialization: bool = False, dtype=None,
+                 init_method: Callable = nn.init.xavier_normal_, use_cpu_initialization: bool = True, dtype=None,
                  device=None):
         super().__init__()
         self.num_embeddings = num_embeddings
@@ -169,7 +169,13 @@ class ColumnParallelLinear(nn.Module):
 
     def __init__(self, input_size: int, output_size: int, bias: bool = True, gather_output: bool = True,
                  init_method: Callable = nn.init.xavier_normal_, stride: int = 1, skip_bias_add: bool = False,
-                 use_cpu_initialization: bool = False, dtype=None, device=None, sequence_parallel: bool = False):
+                 use_cpu_initialization: bool = True, dtype=None, device=None, sequence_parallel: bool = False,
+                 init_method_bias: Optional[Callable] = None, keep_master_weight_for_test: bool = False,
+                 no_async_tensor_model_parallel_allreduce: bool = True, gradient_accumulation_fusion: bool = False):
+        """The last four arguments are the reference's (metaseq/modules/megatron/mpu/layers.py:386-470):
+        ``init_method_bias`` fills the bias (zeros without it); the others select library-collective variants
+        there and are accepted here without effect (``LinearWithGradAccumulationAndAsyncCommunication`` is the
+        stand-alone form of those variants)."""
         super().__init__()
         self.input_size, self.output_size = input_size, output_size
         self.gather_output = gather_output
@@ -183,6 +189,9 @@ class ColumnParallelLinear(nn.Module):
         if bias:
             self.bias = nn.Parameter(torch.zeros(self.output_size_per_partition, dtype=dtype, device=device))
             mpu.set_tensor_model_parallel_attributes(self.bias, world > 1, 0, stride)
+            if init_method_bias is not None:
+                with torch.no_grad():
+                    init_method_bias(self.bias)
         else:
             self.register_parameter("bias", None)
 
@@ -204,7 +213,8 @@ class RowParallelLinear(nn.Module):
 
     def __init__(self, input_size: int, output_size: int, bias: bool = True, input_is_parallel: bool = False,
                  init_method: Callable = nn.init.xavier_normal_, stride: int = 1, skip_bias_add: bool = False,
-                 use_cpu_initialization: bool = False, dtype=None, device=None, sequence_parallel: bool = False):
+                 use_cpu_initialization: bool = True, dtype=None, device=None, sequence_parallel: bool = False,
+                 keep_master_weight_for_test: bool = False, gradient_accumulation_fusion: bool = False):
         super().__init__()
         self.input_size, self.output_size = input_size, output_size
         self.input_is_parallel = input_is_parallel
