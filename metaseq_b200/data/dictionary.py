@@ -46,13 +46,18 @@ class Dictionary:
     def get_count(self, idx: int) -> int:
         return self.count[idx]
 
-    def string(self, tensor, bpe_symbol=None, escape_unk=False, extra_symbols_to_ignore=None, unk_string=None) -> str:
-        """Text of a token tensor (one line per row for a matrix).  End-of-sentence, begin-of-sentence and the
-        given extra symbols are left out; ``bpe_symbol`` (a continuation marker such as ``@@ ``) is removed."""
+    def string(self, tensor, bpe_symbol=None, escape_unk=False, extra_symbols_to_ignore=None, unk_string=None,
+               include_eos=False) -> str:
+        """Text of a token tensor (one line per row for a matrix).  End-of-sentence (unless ``include_eos``),
+        begin-of-sentence and the given extra symbols are left out; ``bpe_symbol`` (a continuation marker such as
+        ``@@ ``) is removed."""
         if torch.is_tensor(tensor) and tensor.dim() == 2:
-            rows = (self.string(row, bpe_symbol, escape_unk, extra_symbols_to_ignore) for row in tensor)
+            rows = (self.string(row, bpe_symbol, escape_unk, extra_symbols_to_ignore, unk_string, include_eos)
+                    for row in tensor)
             return "\n".join(rows)
-        skipped = {self.eos_index, self.bos_index, *(extra_symbols_to_ignore or ())}
+        skipped = {self.bos_index, *(extra_symbols_to_ignore or ())}
+        if not include_eos:
+            skipped.add(self.eos_index)
         unknown = unk_string if unk_string is not None else self.unk_string(escape_unk)
         words = [unknown if i == self.unk_index else self[i] for i in map(int, tensor) if i not in skipped]
         text = " ".join(words)
@@ -72,8 +77,9 @@ class Dictionary:
         self.count.append(n)
         return idx
 
-    def update(self, other: "Dictionary"):
-        for word, c in zip(other.symbols, other.count):
+    def update(self, new_dict: "Dictionary"):
+        """Adds every symbol of ``new_dict`` with its count."""
+        for word, c in zip(new_dict.symbols, new_dict.count):
             self.add_symbol(word, c)
 
     def finalize(self, threshold: int = -1, nwords: int = -1, padding_factor: int = 8):
